@@ -1,0 +1,506 @@
+// Attention over the paged KV cache.
+//
+//   attn_decode_kernel   one query token per row, GQA group packed into the MMA M dimension, keys split
+//                        across the four warps of a CTA (each with a private cp.async pipeline) and
+//                        optionally across CTAs (split-KV with a second combine pass).
+//   attn_prefill_kernel  causal flash attention for ragged (padding-free) prompt chunks; K and V are read
+//                        from the paged cache, so plain prefill, chunked prefill and prefill on top of a
+//                        cached prefix are the same code path.
+//
+// Both honour a sliding window and logit soft-capping.  They stand in for the reference's third-party
+// kernels: vLLM `paged_attention_v1/v2` (call site server/lorax_server/utils/paged_attention.py:127-178) and
+// flash-attn `varlen_fwd` (utils/flash_attn.py:180-201).
+//
+// Cache layout (one tensor per layer): [num_blocks, kv_heads, 2, PAGE, D] -- for each (block, head) the K
+// plane [PAGE, D] is followed by the V plane, so one page of one head is a single contiguous 2*PAGE*D run.
+#include "common.cuh"
+
+namespace lx {
+
+constexpr int kPage = 32;
+constexpr float kLog2e = 1.4426950408889634f;
+
+LX_DEVICE void mma_bf16_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+LX_DEVICE void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+LX_DEVICE void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+// A [ROWS, D] bf16 plane in shared memory; 16-byte chunk c of row r lives at chunk (c ^ (r & 7)) so that
+// ldmatrix (8 rows, same logical chunk) touches 8 different bank groups.
+template <int D>
+LX_DEVICE uint32_t swz(int r, int c) { return (uint32_t)((r * (D / 8) + (c ^ (r & 7))) * 16); }
+
+// Copy ROWS x D bf16 (contiguous in global memory) into a swizzled plane with `NT` cooperating threads.
+template <int D, int ROWS, int NT>
+LX_DEVICE void load_plane(uint32_t smem_base, const __nv_bfloat16* g, int tid, bool valid) {
+  constexpr int CPR = D / 8;
+  constexpr int CHUNKS = ROWS * CPR;
+#pragma unroll
+  for (int c = tid; c < CHUNKS; c += NT) {
+    const int r = c / CPR, cc = c % CPR;
+    const uint32_t dst = smem_base + swz<D>(r, cc);
+    const int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(g + (long long)c * 8), "r"(sz) : "memory");
+  }
+}
+
+// S[16, NKEYS] (+)= Q[16, D] K[NKEYS, D]^T for one warp.  qf holds the A fragments of Q.
+template <int D, int NKEYS>
+LX_DEVICE void qk_tile(float (&sacc)[NKEYS / 8][4], const uint32_t (&qf)[D / 16][4], uint32_t k_smem, int lane) {
+#pragma unroll
+  for (int nt = 0; nt < NKEYS / 8; ++nt) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) sacc[nt][q] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ks += 2) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(b0, b1, b2, b3, k_smem + swz<D>(nt * 8 + (lane & 7), 2 * ks + (lane >> 3)));
+      mma_bf16_16816(sacc[nt], qf[ks], b0, b1);
+      mma_bf16_16816(sacc[nt], qf[ks + 1], b2, b3);
+    }
+  }
+}
+
+// O[16, D] += P[16, NKEYS] V[NKEYS, D]
+template <int D, int NKEYS>
+LX_DEVICE void pv_tile(float (&oacc)[D / 8][4], const float (&sacc)[NKEYS / 8][4], uint32_t v_smem, int lane) {
+#pragma unroll
+  for (int kk = 0; kk < NKEYS / 16; ++kk) {
+    uint32_t pa[4];
+    pa[0] = pack_bf16x2(sacc[2 * kk][0], sacc[2 * kk][1]);
+    pa[1] = pack_bf16x2(sacc[2 * kk][2], sacc[2 * kk][3]);
+    pa[2] = pack_bf16x2(sacc[2 * kk + 1][0], sacc[2 * kk + 1][1]);
+    pa[3] = pack_bf16x2(sacc[2 * kk + 1][2], sacc[2 * kk + 1][3]);
+#pragma unroll
+    for (int nd = 0; nd < D / 8; nd += 2) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4_t(b0, b1, b2, b3, v_smem + swz<D>(kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, nd + (lane >> 4)));
+      mma_bf16_16816(oacc[nd], pa, b0, b1);
+      mma_bf16_16816(oacc[nd + 1], pa, b2, b3);
+    }
+  }
+}
+
+// Online-softmax update for the two rows (lane/4 and lane/4 + 8) a thread owns.  `sacc` holds raw dot
+// products on entry and probabilities on exit.  key0 = index of column 0; keys outside [lo, hi) are masked.
+template <int D, int NKEYS>
+LX_DEVICE void softmax_tile(float (&sacc)[NKEYS / 8][4], float (&oacc)[D / 8][4], float (&m)[2], float (&l)[2], int key0,
+                            int lo0, int hi0, int lo1, int hi1, float scale, float softcap, int lane) {
+  float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+  for (int nt = 0; nt < NKEYS / 8; ++nt) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int key = key0 + nt * 8 + 2 * (lane & 3) + (q & 1);
+      const int r = q >> 1;
+      float s = sacc[nt][q] * scale;
+      if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      const bool ok = r == 0 ? (key >= lo0 && key < hi0) : (key >= lo1 && key < hi1);
+      s = ok ? s : -INFINITY;
+      sacc[nt][q] = s;
+      mx[r] = fmaxf(mx[r], s);
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 1));
+    mx[r] = fmaxf(mx[r], __shfl_xor_sync(0xffffffffu, mx[r], 2));
+  }
+  float corr[2], mnew[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    mnew[r] = fmaxf(m[r], mx[r]);
+    corr[r] = (mnew[r] == -INFINITY) ? 1.f : exp2f((m[r] - mnew[r]) * kLog2e);
+    m[r] = mnew[r];
+    l[r] *= corr[r];
+  }
+#pragma unroll
+  for (int nt = 0; nt < NKEYS / 8; ++nt) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int r = q >> 1;
+      const float pz = (mnew[r] == -INFINITY) ? 0.f : exp2f((sacc[nt][q] - mnew[r]) * kLog2e);
+      sacc[nt][q] = pz;
+      l[r] += pz;
+    }
+  }
+#pragma unroll
+  for (int nd = 0; nd < D / 8; ++nd) {
+    oacc[nd][0] *= corr[0]; oacc[nd][1] *= corr[0];
+    oacc[nd][2] *= corr[1]; oacc[nd][3] *= corr[1];
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Decode
+// ------------------------------------------------------------------------------------------------
+struct DecodeParams {
+  const __nv_bfloat16* q;     // [T, ldq], head h at column h * D
+  long long ldq;
+  const __nv_bfloat16* kv;    // cache of this layer
+  const int* block_tables;    // [T, max_blocks]
+  int max_blocks;
+  const int* ctx_lens;        // [T] number of keys visible to the token (includes itself); <= 0: skip row
+  __nv_bfloat16* out;         // [T, ldo]
+  long long ldo;
+  float* part_o;              // split-KV partials [T, nh, nsplit, D]
+  float* part_lse;            // [T, nh, nsplit]
+  int nh, nkv, group, gchunks;
+  int window;                 // <= 0: none
+  float scale, softcap;
+  int nsplit;
+};
+
+template <int D, int STAGES>
+__global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams p) {
+  extern __shared__ __align__(1024) uint8_t dsm[];
+  constexpr int PLANE = kPage * D * 2;
+  constexpr int STAGE = 2 * PLANE;
+  const int t = blockIdx.x;
+  const int kvh = blockIdx.y / p.gchunks, gc = blockIdx.y % p.gchunks;
+  const int split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ctx = p.ctx_lens[t];
+  const int g0 = gc * 16;
+  const int grows = min(16, p.group - g0);
+  const int head0 = kvh * p.group + g0;
+
+  int key_lo = 0;
+  if (p.window > 0 && ctx > p.window) key_lo = ctx - p.window;
+  const int page_lo = key_lo / kPage;
+  const int page_hi = ctx > 0 ? (ctx + kPage - 1) / kPage : 0;
+  const int npages = max(page_hi - page_lo, 0);
+  const int per_split = (npages + p.nsplit - 1) / p.nsplit;
+  const int pb = page_lo + split * per_split;
+  const int pe = min(pb + per_split, page_hi);
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float oacc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
+
+  // Q fragments straight from global memory (row = head in group, zero beyond the group).
+  uint32_t qf[D / 16][4];
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    const __nv_bfloat16* q0 = p.q + (long long)t * p.ldq + (long long)(head0 + r0) * D;
+    const __nv_bfloat16* q1 = p.q + (long long)t * p.ldq + (long long)(head0 + r1) * D;
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) {
+      const int c = ks * 16 + 2 * (lane & 3);
+      qf[ks][0] = r0 < grows ? *reinterpret_cast<const uint32_t*>(q0 + c) : 0u;
+      qf[ks][1] = r1 < grows ? *reinterpret_cast<const uint32_t*>(q1 + c) : 0u;
+      qf[ks][2] = r0 < grows ? *reinterpret_cast<const uint32_t*>(q0 + c + 8) : 0u;
+      qf[ks][3] = r1 < grows ? *reinterpret_cast<const uint32_t*>(q1 + c + 8) : 0u;
+    }
+  }
+
+  const uint32_t wbase = smem_u32(dsm) + warp * STAGES * STAGE;
+  const int* bt = p.block_tables + (long long)t * p.max_blocks;
+  const int my_first = pb + warp;
+  const int my_count = my_first < pe ? (pe - my_first + 3) / 4 : 0;
+
+  auto issue = [&](int i) {
+    if (i < my_count) {
+      const int page = my_first + 4 * i;
+      const long long blk = bt[page];
+      const __nv_bfloat16* src = p.kv + ((blk * p.nkv + kvh) * 2) * (long long)(kPage * D);
+      const uint32_t sb = wbase + (i % STAGES) * STAGE;
+      load_plane<D, kPage, 32>(sb, src, lane, true);
+      load_plane<D, kPage, 32>(sb + PLANE, src + kPage * D, lane, true);
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) issue(s);
+
+  for (int i = 0; i < my_count; ++i) {
+    issue(i + STAGES - 1);
+    cp_async_wait<STAGES - 1>();
+    __syncwarp();
+    const uint32_t sb = wbase + (i % STAGES) * STAGE;
+    const int page = my_first + 4 * i;
+    float sacc[kPage / 8][4];
+    qk_tile<D, kPage>(sacc, qf, sb, lane);
+    softmax_tile<D, kPage>(sacc, oacc, m, l, page * kPage, key_lo, ctx, key_lo, ctx, p.scale, p.softcap, lane);
+    pv_tile<D, kPage>(oacc, sacc, sb + PLANE, lane);
+    __syncwarp();
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // ---- combine the four warps through shared memory (pipeline buffers are free now)
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  float* so = reinterpret_cast<float*>(dsm);            // [4][16][D]
+  float* sm = so + 4 * 16 * D;                           // [4][16]
+  float* sl = sm + 4 * 16;                               // [4][16]
+  {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+#pragma unroll
+    for (int nd = 0; nd < D / 8; ++nd) {
+      const int c = nd * 8 + 2 * (lane & 3);
+      *reinterpret_cast<float2*>(so + (warp * 16 + r0) * D + c) = make_float2(oacc[nd][0], oacc[nd][1]);
+      *reinterpret_cast<float2*>(so + (warp * 16 + r1) * D + c) = make_float2(oacc[nd][2], oacc[nd][3]);
+    }
+    if ((lane & 3) == 0) {
+      sm[warp * 16 + r0] = m[0]; sm[warp * 16 + r1] = m[1];
+      sl[warp * 16 + r0] = l[0]; sl[warp * 16 + r1] = l[1];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < grows * D; idx += 128) {
+    const int g = idx / D, d = idx % D;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + g]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float mw = sm[w * 16 + g];
+      const float wgt = (mw == -INFINITY) ? 0.f : exp2f((mw - M) * kLog2e);
+      num += wgt * so[(w * 16 + g) * D + d];
+      den += wgt * sl[w * 16 + g];
+    }
+    const float o = den > 0.f ? num / den : 0.f;
+    const int head = head0 + g;
+    if (p.nsplit == 1) {
+      p.out[(long long)t * p.ldo + (long long)head * D + d] = __float2bfloat16(o);
+    } else {
+      const long long pi = ((long long)t * p.nh + head) * p.nsplit + split;
+      p.part_o[pi * D + d] = o;
+      if (d == 0) p.part_lse[pi] = den > 0.f ? M + __logf(den) : -INFINITY;
+    }
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(D) attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
+                                                         __nv_bfloat16* __restrict__ out, long long ldo, int nh, int nsplit) {
+  const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+  const long long base = ((long long)t * nh + h) * nsplit;
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, part_lse[base + s]);
+  float num = 0.f, den = 0.f;
+  for (int s = 0; s < nsplit; ++s) {
+    const float ls = part_lse[base + s];
+    const float w = (ls == -INFINITY) ? 0.f : __expf(ls - M);
+    num += w * part_o[(base + s) * D + d];
+    den += w;
+  }
+  out[(long long)t * ldo + (long long)h * D + d] = __float2bfloat16(den > 0.f ? num / den : 0.f);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Prefill: 64 queries x 1 head per CTA (16 query rows per warp), 64-key tiles = two cache pages.
+// ------------------------------------------------------------------------------------------------
+struct PrefillParams {
+  const __nv_bfloat16* q;     // [T, ldq]
+  long long ldq;
+  const __nv_bfloat16* kv;
+  const int* block_tables;    // [B, max_blocks]
+  int max_blocks;
+  const int* cu_q;            // [B + 1] start of each sequence's chunk in the ragged token dimension
+  const int* cache_lens;      // [B] keys already cached before this chunk
+  const int* tile_seq;        // [num_tiles] sequence of each 64-query tile
+  const int* tile_q0;         // [num_tiles] first query (within the chunk) of the tile
+  __nv_bfloat16* out;
+  long long ldo;
+  int nh, nkv;
+  int window;
+  float scale, softcap;
+};
+
+template <int D>
+__global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillParams p) {
+  extern __shared__ __align__(1024) uint8_t psm[];
+  constexpr int KT = 64;                         // keys per tile
+  constexpr int PLANE = kPage * D * 2;           // one page of K or V
+  constexpr int STAGE = 4 * PLANE;               // K page0, K page1, V page0, V page1
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int kvh = head / (p.nh / p.nkv);
+  const int b = p.tile_seq[tile];
+  const int q0 = p.tile_q0[tile];
+  const int qlen = p.cu_q[b + 1] - p.cu_q[b];
+  const int cache = p.cache_lens[b];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int* bt = p.block_tables + (long long)b * p.max_blocks;
+
+  // rows owned by this thread
+  const int qr0 = q0 + warp * 16 + (lane >> 2), qr1 = qr0 + 8;
+  const long long tok0 = (long long)p.cu_q[b] + qr0, tok1 = (long long)p.cu_q[b] + qr1;
+  uint32_t qf[D / 16][4];
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    const int c = ks * 16 + 2 * (lane & 3);
+    const __nv_bfloat16* a0 = p.q + tok0 * p.ldq + (long long)head * D + c;
+    const __nv_bfloat16* a1 = p.q + tok1 * p.ldq + (long long)head * D + c;
+    qf[ks][0] = qr0 < qlen ? *reinterpret_cast<const uint32_t*>(a0) : 0u;
+    qf[ks][1] = qr1 < qlen ? *reinterpret_cast<const uint32_t*>(a1) : 0u;
+    qf[ks][2] = qr0 < qlen ? *reinterpret_cast<const uint32_t*>(a0 + 8) : 0u;
+    qf[ks][3] = qr1 < qlen ? *reinterpret_cast<const uint32_t*>(a1 + 8) : 0u;
+  }
+  // visible key range per row: [lo, hi) with hi = position + 1
+  const int pos0 = cache + qr0, pos1 = cache + qr1;
+  const int hi0 = qr0 < qlen ? pos0 + 1 : 0, hi1 = qr1 < qlen ? pos1 + 1 : 0;
+  const int lo0 = (p.window > 0 && hi0 > p.window) ? hi0 - p.window : 0;
+  const int lo1 = (p.window > 0 && hi1 > p.window) ? hi1 - p.window : 0;
+
+  // key tiles needed by the CTA
+  const int last_q = min(q0 + 63, qlen - 1);
+  const int key_hi = cache + last_q + 1;
+  int key_lo = 0;
+  if (p.window > 0) key_lo = max(cache + q0 + 1 - p.window, 0);
+  const int t_lo = key_lo / KT, t_hi = (key_hi + KT - 1) / KT;
+  const int total_pages = (key_hi + kPage - 1) / kPage;
+
+  const uint32_t base = smem_u32(psm);
+  auto issue = [&](int kt) {
+    if (kt < t_hi) {
+      const uint32_t sb = base + (kt & 1) * STAGE;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int page = kt * 2 + h;
+        const bool valid = page < total_pages;
+        const long long blk = valid ? bt[page] : 0;
+        const __nv_bfloat16* src = p.kv + ((blk * p.nkv + kvh) * 2) * (long long)(kPage * D);
+        load_plane<D, kPage, 128>(sb + h * PLANE, src, threadIdx.x, valid);
+        load_plane<D, kPage, 128>(sb + (2 + h) * PLANE, src + kPage * D, threadIdx.x, valid);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float oacc[D / 8][4];
+#pragma unroll
+  for (int i = 0; i < D / 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
+
+  issue(t_lo);
+  for (int kt = t_lo; kt < t_hi; ++kt) {
+    issue(kt + 1);
+    cp_async_wait<1>();
+    __syncthreads();
+    const uint32_t sb = base + (kt & 1) * STAGE;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      float sacc[kPage / 8][4];
+      qk_tile<D, kPage>(sacc, qf, sb + h * PLANE, lane);
+      softmax_tile<D, kPage>(sacc, oacc, m, l, kt * KT + h * kPage, lo0, hi0, lo1, hi1, p.scale, p.softcap, lane);
+      pv_tile<D, kPage>(oacc, sacc, sb + (2 + h) * PLANE, lane);
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+    l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+  }
+  const float inv0 = l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
+#pragma unroll
+  for (int nd = 0; nd < D / 8; ++nd) {
+    const int c = nd * 8 + 2 * (lane & 3);
+    if (qr0 < qlen)
+      *reinterpret_cast<uint32_t*>(p.out + tok0 * p.ldo + (long long)head * D + c) = pack_bf16x2(oacc[nd][0] * inv0, oacc[nd][1] * inv0);
+    if (qr1 < qlen)
+      *reinterpret_cast<uint32_t*>(p.out + tok1 * p.ldo + (long long)head * D + c) = pack_bf16x2(oacc[nd][2] * inv1, oacc[nd][3] * inv1);
+  }
+}
+
+template <int D, int STAGES>
+static int launch_decode(const DecodeParams& p, int T, cudaStream_t s) {
+  constexpr int SMEM = 4 * STAGES * 2 * kPage * D * 2;
+  static_assert(SMEM >= (4 * 16 * D + 128) * 4, "combine buffer must fit in the pipeline buffers");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return -(int)e;
+    configured = true;
+  }
+  dim3 grid(T, p.nkv * p.gchunks, p.nsplit);
+  attn_decode_kernel<D, STAGES><<<grid, 128, SMEM, s>>>(p);
+  if (p.nsplit > 1) {
+    dim3 g2(T, p.nh);
+    attn_combine_kernel<D><<<g2, D, 0, s>>>(p.part_o, p.part_lse, p.out, p.ldo, p.nh, p.nsplit);
+  }
+  return -(int)cudaGetLastError();
+}
+
+template <int D>
+static int launch_prefill(const PrefillParams& p, int num_tiles, cudaStream_t s) {
+  constexpr int SMEM = 2 * 4 * kPage * D * 2;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return -(int)e;
+    configured = true;
+  }
+  dim3 grid(num_tiles, p.nh);
+  attn_prefill_kernel<D><<<grid, 128, SMEM, s>>>(p);
+  return -(int)cudaGetLastError();
+}
+
+}  // namespace lx
+
+extern "C" {
+
+int lx_attn_page_size() { return lx::kPage; }
+
+// part_o / part_lse are only touched when nsplit > 1: sizes T*nh*nsplit*D and T*nh*nsplit floats.
+int lx_attn_decode(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* ctx_lens,
+                   void* out, long long ldo, float* part_o, float* part_lse, int T, int nh, int nkv, int d, int window, float scale,
+                   float softcap, int nsplit, void* stream) {
+  using namespace lx;
+  if (T <= 0) return 0;
+  if (nh % nkv != 0) return -1;
+  DecodeParams p{};
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q); p.ldq = ldq;
+  p.kv = reinterpret_cast<const __nv_bfloat16*>(kv);
+  p.block_tables = block_tables; p.max_blocks = max_blocks; p.ctx_lens = ctx_lens;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
+  p.part_o = part_o; p.part_lse = part_lse;
+  p.nh = nh; p.nkv = nkv; p.group = nh / nkv; p.gchunks = (p.group + 15) / 16;
+  p.window = window; p.scale = scale; p.softcap = softcap;
+  p.nsplit = nsplit < 1 ? 1 : nsplit;
+  if (p.nsplit > 1 && (part_o == nullptr || part_lse == nullptr)) return -2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (d == 128) return launch_decode<128, 3>(p, T, s);
+  if (d == 64) return launch_decode<64, 4>(p, T, s);
+  return -3;
+}
+
+int lx_attn_prefill(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
+                    const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
+                    int nkv, int d, int window, float scale, float softcap, void* stream) {
+  using namespace lx;
+  if (num_tiles <= 0) return 0;
+  if (nh % nkv != 0) return -1;
+  PrefillParams p{};
+  p.q = reinterpret_cast<const __nv_bfloat16*>(q); p.ldq = ldq;
+  p.kv = reinterpret_cast<const __nv_bfloat16*>(kv);
+  p.block_tables = block_tables; p.max_blocks = max_blocks; p.cu_q = cu_q; p.cache_lens = cache_lens;
+  p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
+  p.nh = nh; p.nkv = nkv; p.window = window; p.scale = scale; p.softcap = softcap;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (d == 128) return launch_prefill<128>(p, num_tiles, s);
+  if (d == 64) return launch_prefill<64>(p, num_tiles, s);
+  return -3;
+}
+
+}  // extern "C"

@@ -1,0 +1,446 @@
+// bf16 GEMM on the 5th-generation tensor cores (tcgen05.mma, accumulators in TMEM, operands fed by TMA).
+//
+//   out[i, j] = sum_k A[i, k] * B[j, k]  (+ bias)          A: [a_rows, K]   B: [b_rows, K]   both K-contiguous
+//
+// One kernel serves every dense projection of the decoder (QKV, O, gate_up, down, lm_head), which the
+// reference computes with cuBLAS through `torch.nn.functional.linear` (server/lorax_server/layers/linear.py:38).
+// Both operands are "K-major", which is how activations [tokens, K] and nn.Linear weights [N, K] already sit in
+// memory, so either can take the UMMA M side:
+//   * prefill (many tokens):  A = activations, B = weights, 128 x 256 tiles, compute bound;
+//   * decode (few tokens):    A = weights (128 output features per tile), B = activations (UMMA N = tokens
+//     rounded up to 16), so the tensor core does no work for padding rows and each weight byte is read from
+//     HBM exactly once.  Small grids are widened with split-K; the last CTA to finish a tile reduces the
+//     fp32 partials in a fixed order (deterministic) and writes bf16.
+//
+// Structure: persistent CTAs of 6 warps.  Warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and
+// TMEM owner, warps 2..5 = epilogue (each warp reads its own 32-lane TMEM quadrant with tcgen05.ld).  A STAGES
+// deep smem ring is guarded by full/empty mbarriers; the accumulator is double buffered in TMEM so the epilogue
+// of tile i overlaps the main loop of tile i+1.
+#include "common.cuh"
+
+namespace lx {
+
+constexpr int kBM = 128;   // UMMA M (rows of operand A per tile)
+constexpr int kBK = 64;    // K per pipeline stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kGemmThreads = 192;
+
+struct GemmParams {
+  int a_rows, b_rows, K;
+  int umma_n;                 // runtime UMMA N (multiple of 16, <= BN)
+  __nv_bfloat16* out;
+  long long ldo_a, ldo_b;     // out[i * ldo_a + j * ldo_b]
+  const __nv_bfloat16* bias;  // optional, indexed by the feature dimension
+  int bias_on_a;              // 1: bias[i] (weights are operand A), 0: bias[j]
+  int split_k;
+  float* ws;                  // split-K partials: [tile][split][128][BN] fp32
+  int* counters;              // split-K arrival counters, one per tile, zero between launches
+  int* status;                // [2] status word + detail
+  int hint_a_first;           // 1: operand A is streamed once (weights) -> evict_first, B evict_last; 0: opposite
+  float out_scale;            // multiplies the accumulator (logit scaling); 1.0 normally
+};
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // +1024 for manual alignment
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const GemmParams p) {
+  using S = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + STAGES * S::kStageBytes);
+  uint64_t* empty_bar = full_bar + STAGES;
+  uint64_t* tmem_full = empty_bar + STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
+  int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_base_slot + 2));
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+
+  const int tiles_a = (p.a_rows + kBM - 1) / kBM;
+  const int tiles_b = (p.b_rows + BN - 1) / BN;
+  const int num_tiles = tiles_a * tiles_b;
+  const int num_work = num_tiles * p.split_k;
+  const int kblocks = (p.K + kBK - 1) / kBK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tmem_full[s], 1);
+      mbar_init(&tmem_empty[s], 4);
+    }
+    *abort_flag = 0;
+    *last_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_base_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_base_slot;
+
+  // Work item w -> (tile, split).  Tiles are ordered with the A tile index fastest inside one B tile so that
+  // CTAs running at the same time share the B operand through L2.
+  if (warp == 0) {
+    if (lane == 0) {
+      const uint64_t pol_a = p.hint_a_first ? policy_evict_first() : policy_evict_last();
+      const uint64_t pol_b = p.hint_a_first ? policy_evict_last() : policy_evict_first();
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int tile = w / p.split_k, split = w % p.split_k;
+        const int ta = tile % tiles_a, tb = tile / tiles_a;
+        const int kb0 = (int)((long long)kblocks * split / p.split_k);
+        const int kb1 = (int)((long long)kblocks * (split + 1) / p.split_k);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+            report_status(p.status, kTimeoutEmptyBarrier, w);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          uint8_t* sa = tiles + stage * S::kStageBytes;
+          uint8_t* sb = sa + S::kABytes;
+          mbar_expect_tx(&full_bar[stage], S::kStageBytes);
+          tma_load_2d_hint(sa, &tmap_a, &full_bar[stage], kb * kBK, ta * kBM, pol_a);
+          tma_load_2d_hint(sb, &tmap_b, &full_bar[stage], kb * kBK, tb * BN, pol_b);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc(kBM, (uint32_t)p.umma_n, kFmtBF16, kFmtBF16);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        const int split = w % p.split_k;
+        const int kb0 = (int)((long long)kblocks * split / p.split_k);
+        const int kb1 = (int)((long long)kblocks * (split + 1) / p.split_k);
+        if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1, abort_flag)) {
+          report_status(p.status, kTimeoutTmemEmpty, w);
+          *abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+            report_status(p.status, kTimeoutFullBarrier, w);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
+          const uint64_t da = make_desc_k_sw128(sa);
+          const uint64_t db = make_desc_k_sw128(sa + S::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            umma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);   // releases the smem stage when these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        tc_commit(&tmem_full[acc]);       // accumulator complete
+        acc_phase[acc] ^= 1;
+        acc ^= 1;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------------ epilogue warps (2..5)
+    const int quad = warp & 3;                 // TMEM lane quadrant this warp may access
+    const int row_in_tile = quad * 32 + lane;
+    int acc = 0;
+    uint32_t acc_phase[2] = {0, 0};
+    for (int w = blockIdx.x; w < num_work; w += gridDim.x) {
+      const int tile = w / p.split_k, split = w % p.split_k;
+      const int ta = tile % tiles_a, tb = tile / tiles_a;
+      if (!mbar_wait(&tmem_full[acc], acc_phase[acc], abort_flag)) {
+        report_status(p.status, kTimeoutTmemFull, w);
+        *abort_flag = 1;
+        break;
+      }
+      tc_fence_after();
+      acc_phase[acc] ^= 1;
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+      const int i = ta * kBM + row_in_tile;
+      const int j0 = tb * BN;
+      const int ncols = min(BN, p.umma_n);
+      constexpr int CH = (BN >= 32) ? 32 : 16;
+
+      if (p.split_k == 1) {
+#pragma unroll 1
+        for (int c = 0; c < ncols; c += CH) {
+          float v[CH];
+          if constexpr (CH == 32) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + c, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int q = 0; q < 32; ++q) v[q] = __uint_as_float(r[q]);
+          } else {
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(taddr + c, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int q = 0; q < 16; ++q) v[q] = __uint_as_float(r[q]);
+          }
+          if (i < p.a_rows) {
+            const float bias_i = (p.bias != nullptr && p.bias_on_a) ? __bfloat162float(p.bias[i]) : 0.f;
+            __nv_bfloat16* orow = p.out + (long long)i * p.ldo_a;
+            const int j = j0 + c;
+            if (p.ldo_b == 1 && j + CH <= p.b_rows && ((reinterpret_cast<uintptr_t>(orow + j) & 15) == 0)) {
+              uint32_t pk[CH / 2];
+#pragma unroll
+              for (int q = 0; q < CH; q += 2) {
+                float b0 = bias_i, b1 = bias_i;
+                if (p.bias != nullptr && !p.bias_on_a) {
+                  b0 = __bfloat162float(p.bias[j + q]);
+                  b1 = __bfloat162float(p.bias[j + q + 1]);
+                }
+                pk[q / 2] = pack_bf16x2(v[q] * p.out_scale + b0, v[q + 1] * p.out_scale + b1);
+              }
+              uint4* dst = reinterpret_cast<uint4*>(orow + j);
+#pragma unroll
+              for (int q = 0; q < CH / 8; ++q) dst[q] = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+            } else {
+#pragma unroll
+              for (int q = 0; q < CH; ++q) {
+                if (j + q < p.b_rows) {
+                  float b = bias_i;
+                  if (p.bias != nullptr && !p.bias_on_a) b = __bfloat162float(p.bias[j + q]);
+                  orow[(long long)(j + q) * p.ldo_b] = __float2bfloat16(v[q] * p.out_scale + b);
+                }
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      } else {
+        // ---- split-K: park the fp32 partial, count arrivals, the last CTA of the tile reduces.
+        float* wsp = p.ws + ((long long)(tile * p.split_k + split) * kBM + row_in_tile) * BN;
+#pragma unroll 1
+        for (int c = 0; c < ncols; c += CH) {
+          if constexpr (CH == 32) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(taddr + c, r);
+            tc_wait_ld();
+            uint4* dst = reinterpret_cast<uint4*>(wsp + c);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) dst[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+          } else {
+            uint32_t r[16];
+            tmem_ld_32x32b_x16(taddr + c, r);
+            tc_wait_ld();
+            uint4* dst = reinterpret_cast<uint4*>(wsp + c);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) dst[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const int prev = atomicAdd(&p.counters[tile], 1);
+          *last_flag = (prev == p.split_k - 1) ? 1 : 0;
+          if (prev == p.split_k - 1) p.counters[tile] = 0;   // ready for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool is_last = (*last_flag != 0);
+        if (is_last) {
+          __threadfence();
+          if (i < p.a_rows) {
+            const float bias_i = (p.bias != nullptr && p.bias_on_a) ? __bfloat162float(p.bias[i]) : 0.f;
+            __nv_bfloat16* orow = p.out + (long long)i * p.ldo_a;
+            const float* base = p.ws + ((long long)(tile * p.split_k) * kBM + row_in_tile) * BN;
+#pragma unroll 1
+            for (int c = 0; c < ncols; c += 4) {
+              float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+              for (int sp = 0; sp < p.split_k; ++sp) {
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(base + (long long)sp * kBM * BN + c));
+                s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+              }
+              const float vv[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int j = j0 + c + q;
+                if (j < p.b_rows) {
+                  float b = bias_i;
+                  if (p.bias != nullptr && !p.bias_on_a) b = __bfloat162float(p.bias[j]);
+                  orow[(long long)j * p.ldo_b] = __float2bfloat16(vv[q] * p.out_scale + b);
+                }
+              }
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is reused by the next tile
+      }
+      acc ^= 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  }
+  return fn;
+}
+
+// 2-D K-major bf16 tensor map: dims {K, rows}, box {64, box_rows}, 128-byte swizzle, zero fill outside.
+int make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uint64_t K, uint64_t row_stride_elems,
+                          uint32_t box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return -1;
+  cuuint64_t dims[2] = {K, rows};
+  cuuint64_t strides[1] = {row_stride_elems * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kBK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  using S = GemmSmem<BN, STAGES>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (e != cudaSuccess) return -(int)e;
+    configured = true;
+  }
+  const int tiles = ((p.a_rows + kBM - 1) / kBM) * ((p.b_rows + BN - 1) / BN);
+  const int work = tiles * p.split_k;
+  const int grid = work < num_sms ? work : num_sms;
+  gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
+}
+
+}  // namespace lx
+
+extern "C" {
+
+// Workspace sizes the caller must provide for split-K (bytes).
+long long lx_gemm_ws_bytes() { return 64ll << 20; }
+int lx_gemm_max_tiles() { return 8192; }
+
+// out[T, N] = x[T, K] @ w[N, K]^T (+ bias[N]).  `ldx`, `ldw`, `ldo` are row strides in elements.
+// mode: 0 = choose, 1 = force weights on the M side (small T), 2 = force activations on the M side.
+// Returns 0 or a negative error; device-side timeouts are reported through `status` (2 ints, zeroed by the caller).
+int lx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
+                 long long ldw, long long ldo, float out_scale, void* ws, long long ws_bytes, int* counters,
+                 int* status, int num_sms, int mode, int force_split, void* stream_) {
+  using namespace lx;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (T <= 0 || N <= 0) return 0;
+  if ((K % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return -1000;
+  const bool swap = (mode == 1) || (mode == 0 && T <= 256);
+  GemmParams p{};
+  p.K = K;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.ws = reinterpret_cast<float*>(ws);
+  p.counters = counters;
+  p.status = status;
+  p.out_scale = out_scale;
+  p.split_k = 1;
+  CUtensorMap ta, tb;
+  int bn;
+  if (swap) {
+    if (T > 256) return -1001;
+    bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+    p.a_rows = N; p.b_rows = T;
+    p.umma_n = (T + 15) / 16 * 16;
+    p.ldo_a = 1; p.ldo_b = ldo;
+    p.bias_on_a = 1;
+    p.hint_a_first = 1;
+    if (make_tmap_bf16_kmajor(&ta, w, N, K, ldw, kBM)) return -1002;
+    if (make_tmap_bf16_kmajor(&tb, x, T, K, ldx, bn)) return -1003;
+    // split-K so that the grid covers the machine; keep >= 4 k-blocks per split.
+    const int tiles = (N + kBM - 1) / kBM;
+    const int kblocks = (K + kBK - 1) / kBK;
+    int split = 1;
+    if (force_split > 0) split = force_split;
+    else {
+      while (tiles * split < num_sms && kblocks / (split * 2) >= 4 && split < 16) split *= 2;
+    }
+    if (split > kblocks) split = kblocks;
+    if (split > 1) {
+      const long long need = (long long)tiles * split * kBM * bn * 4;
+      if (ws == nullptr || counters == nullptr || need > ws_bytes || tiles > lx_gemm_max_tiles()) split = 1;
+    }
+    p.split_k = split;
+  } else {
+    bn = 256;
+    p.a_rows = T; p.b_rows = N;
+    p.umma_n = 256;
+    p.ldo_a = ldo; p.ldo_b = 1;
+    p.bias_on_a = 0;
+    p.hint_a_first = 0;
+    if (make_tmap_bf16_kmajor(&ta, x, T, K, ldx, kBM)) return -1002;
+    if (make_tmap_bf16_kmajor(&tb, w, N, K, ldw, bn)) return -1003;
+  }
+  switch (bn) {
+    case 16:  return launch_gemm<16, 8>(ta, tb, p, num_sms, stream);
+    case 32:  return launch_gemm<32, 8>(ta, tb, p, num_sms, stream);
+    case 64:  return launch_gemm<64, 8>(ta, tb, p, num_sms, stream);
+    case 128: return launch_gemm<128, 6>(ta, tb, p, num_sms, stream);
+    default:  return launch_gemm<256, 4>(ta, tb, p, num_sms, stream);
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,335 @@
+"""One config-driven decoder for the whole causal-LM zoo.
+
+The reference keeps one hand-written module per architecture (`server/lorax_server/models/custom_modeling/
+flash_{llama,mistral,mixtral,qwen2,gemma,gemma2,phi3,gpt2,...}_modeling.py`); they differ in a handful of
+switches (norm type, bias, activation, rotary fraction, soft-capping, parallel residual, MoE), which
+:class:`lorax_b200.config.ModelConfig` carries.  The layer sequence matches the reference Mistral decoder
+(`flash_mistral_modeling.py:230-645`): fused QKV (+LoRA) -> RoPE + KV write -> attention -> O (+LoRA) ->
+residual-fused norm -> fused gate_up (+LoRA) -> act*mul -> down (+LoRA), vocab-parallel lm_head.
+
+The forward is ragged (padding-free) over a paged KV cache and is written once against the operator
+interface of :mod:`lorax_b200.ops`; on a B200 those are the sm_100a kernels, on CPU the PyTorch oracle.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import ModelConfig
+from ..ops import get_ops, reference
+from ..parallel.tp import TensorParallel
+from ..utils.weights import AbstractWeights
+
+# projection groups that share one base GEMM; LoRA blobs follow the same grouping
+GROUPS = ("qkv", "o", "gate_up", "down")
+
+
+@dataclass
+class LayerWeights:
+    input_norm: torch.Tensor
+    qkv_w: torch.Tensor
+    o_w: torch.Tensor
+    post_norm: Optional[torch.Tensor]
+    gate_up_w: Optional[torch.Tensor]
+    down_w: Optional[torch.Tensor]
+    input_norm_b: Optional[torch.Tensor] = None
+    post_norm_b: Optional[torch.Tensor] = None
+    qkv_b: Optional[torch.Tensor] = None
+    o_b: Optional[torch.Tensor] = None
+    gate_up_b: Optional[torch.Tensor] = None
+    down_b: Optional[torch.Tensor] = None
+    pre_ffn_norm: Optional[torch.Tensor] = None       # gemma2
+    post_ffn_norm: Optional[torch.Tensor] = None      # gemma2
+    router_w: Optional[torch.Tensor] = None           # MoE gate [E, H]
+    experts_w13: Optional[torch.Tensor] = None        # [E_local, 2I, H]
+    experts_w2: Optional[torch.Tensor] = None         # [E_local, H, I]
+
+
+@dataclass
+class StepInputs:
+    """Everything one forward needs, already on the model's device (int32 index tensors)."""
+    input_ids: torch.Tensor
+    positions: torch.Tensor
+    slots: Optional[torch.Tensor]
+    is_prefill: bool
+    block_tables: torch.Tensor                       # prefill: [B, max_blocks]; decode: [T, max_blocks]
+    ctx_lens: Optional[torch.Tensor] = None          # decode: [T]
+    cu_q: Optional[torch.Tensor] = None              # prefill: [B+1]
+    cache_lens: Optional[torch.Tensor] = None        # prefill: [B]
+    tile_seq: Optional[torch.Tensor] = None
+    tile_q0: Optional[torch.Tensor] = None
+    lm_head_indices: Optional[torch.Tensor] = None   # rows that need logits (None = all)
+    tok_slot: Optional[torch.Tensor] = None          # [T] adapter slot per token (-1 = base); None = no LoRA this step
+    head_tok_slot: Optional[torch.Tensor] = None     # adapter slot per lm_head row
+    attn_nsplit: int = 1
+    num_tokens: Optional[int] = None                 # live rows when the tensors are padded (graphs)
+
+
+class DecoderModel:
+    def __init__(self, config: ModelConfig, device, dtype: torch.dtype, tp: Optional[TensorParallel] = None,
+                 max_positions: Optional[int] = None):
+        self.config = config
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.tp = tp or TensorParallel.single()
+        ws = self.tp.world_size
+        c = config
+        if c.num_attention_heads % ws != 0:
+            raise ValueError(f"{c.num_attention_heads} heads cannot be split over {ws} shards")
+        self.nh = c.num_attention_heads // ws
+        # KV heads are split when possible and replicated otherwise (reference: flash_causal_lm.py:1139-1149)
+        self.nkv = max(c.num_key_value_heads // ws, 1)
+        self.kv_replicas = max(ws // c.num_key_value_heads, 1)
+        self.d = c.head_dim
+        self.inter = c.intermediate_size // ws if not c.is_moe else c.intermediate_size
+        self.hidden = c.hidden_size
+        self.vocab = c.vocab_size
+        self.vocab_local = (c.vocab_size + ws - 1) // ws
+        self.vocab_start = self.tp.rank * self.vocab_local
+        self.ops = get_ops(self.device, dtype)
+        self.layers: List[LayerWeights] = []
+        self.embed: Optional[torch.Tensor] = None
+        self.pos_embed: Optional[torch.Tensor] = None
+        self.final_norm: Optional[torch.Tensor] = None
+        self.final_norm_b: Optional[torch.Tensor] = None
+        self.lm_head: Optional[torch.Tensor] = None
+        self.lm_head_b: Optional[torch.Tensor] = None
+        self.max_positions = max_positions or min(c.max_position_embeddings, 32768)
+        self.cos_sin = reference.rope_cache(c.rotary_dim, self.max_positions, c.rope_theta, c.rope_scaling, device=self.device)
+        self.adapters = None     # AdapterManager, attached by the runtime
+        self.gated = c.model_type not in ("gpt2", "gpt_bigcode", "gpt_neox", "falcon", "RefinedWeb", "RefinedWebModel", "phi")
+
+    # ------------------------------------------------------------------ shapes
+    @property
+    def q_size(self):
+        return self.nh * self.d
+
+    @property
+    def kv_size(self):
+        return self.nkv * self.d
+
+    @property
+    def qkv_size(self):
+        return self.q_size + 2 * self.kv_size
+
+    def group_shapes(self) -> Dict[str, dict]:
+        """Per projection group: K (input features on this rank), N (outputs on this rank), output part sizes,
+        and which side is sharded (column groups shard N, row groups shard K)."""
+        g = {
+            "qkv": dict(K=self.hidden, parts=[self.q_size, self.kv_size, self.kv_size], shard="col",
+                        names=["q_proj", "k_proj", "v_proj"]),
+            "o": dict(K=self.q_size, parts=[self.hidden], shard="row", names=["o_proj"]),
+        }
+        if not self.config.is_moe:
+            if self.gated:
+                g["gate_up"] = dict(K=self.hidden, parts=[self.inter, self.inter], shard="col", names=["gate_proj", "up_proj"])
+            else:
+                g["gate_up"] = dict(K=self.hidden, parts=[self.inter], shard="col", names=["up_proj"])
+            g["down"] = dict(K=self.inter, parts=[self.hidden], shard="row", names=["down_proj"])
+        for v in g.values():
+            v["N"] = sum(v["parts"])
+        return g
+
+    # ------------------------------------------------------------------ init
+    @classmethod
+    def random_init(cls, config: ModelConfig, device, dtype, seed: int = 0, tp: Optional[TensorParallel] = None,
+                    std: float = 0.02, max_positions: Optional[int] = None) -> "DecoderModel":
+        """Random weights of the right shapes.  Every rank draws the FULL tensors from the same seed and keeps its
+        shard, so TP=k and TP=1 hold the same model (needed for the rank-consistency tests)."""
+        m = cls(config, device, dtype, tp, max_positions)
+        c, ws, rk = config, m.tp.world_size, m.tp.rank
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+
+        def rnd(*shape, s=std):
+            return torch.randn(*shape, generator=gen, dtype=torch.float32) * s
+
+        def put(t):
+            return t.to(dtype).to(m.device).contiguous()
+
+        def rows(t, n_total):      # shard dim 0 into ws blocks
+            b = n_total // ws
+            return t[rk * b:(rk + 1) * b]
+
+        H, d = c.hidden_size, c.head_dim
+        emb = rnd(c.vocab_size, H)
+        m.embed = put(emb if ws == 1 else _pad_rows(emb, m.vocab_local * ws)[m.vocab_start:m.vocab_start + m.vocab_local])
+        if c.learned_positions:
+            m.pos_embed = put(rnd(c.max_position_embeddings, H))
+        ln = c.norm_type.startswith("layernorm")
+        has_ln_bias = c.norm_type == "layernorm"
+        for _ in range(c.num_hidden_layers):
+            q = rnd(c.num_attention_heads * d, H)
+            k = rnd(c.num_key_value_heads * d, H)
+            v = rnd(c.num_key_value_heads * d, H)
+            o = rnd(H, c.num_attention_heads * d)
+            kv_rank = (rk // m.kv_replicas) if c.num_key_value_heads < ws else rk
+            ksh = k.view(c.num_key_value_heads, d, H)[kv_rank * m.nkv:(kv_rank + 1) * m.nkv].reshape(-1, H)
+            vsh = v.view(c.num_key_value_heads, d, H)[kv_rank * m.nkv:(kv_rank + 1) * m.nkv].reshape(-1, H)
+            qkv = torch.cat([rows(q, q.shape[0]), ksh, vsh], 0)
+            ob = o.shape[1] // ws
+            lw = LayerWeights(
+                input_norm=put(torch.ones(H) - c.norm_weight_offset + rnd(H, s=0.01)),
+                qkv_w=put(qkv), o_w=put(o[:, rk * ob:(rk + 1) * ob]),
+                post_norm=put(torch.ones(H) - c.norm_weight_offset + rnd(H, s=0.01)) if not c.parallel_residual or c.model_type in ("gpt_neox",) else None,
+                gate_up_w=None, down_w=None)
+            if ln and has_ln_bias:
+                lw.input_norm_b = put(rnd(H, s=0.01))
+                if lw.post_norm is not None:
+                    lw.post_norm_b = put(rnd(H, s=0.01))
+            if c.attention_bias:
+                qb, kb, vb = rnd(q.shape[0]), rnd(k.shape[0]), rnd(v.shape[0])
+                kbs = kb.view(c.num_key_value_heads, d)[kv_rank * m.nkv:(kv_rank + 1) * m.nkv].reshape(-1)
+                vbs = vb.view(c.num_key_value_heads, d)[kv_rank * m.nkv:(kv_rank + 1) * m.nkv].reshape(-1)
+                lw.qkv_b = put(torch.cat([rows(qb, qb.shape[0]), kbs, vbs]))
+                if c.model_type not in ("qwen2", "qwen"):
+                    lw.o_b = put(rnd(H)) if rk == 0 else put(torch.zeros(H))
+            I = c.intermediate_size
+            if c.is_moe:
+                E = c.num_local_experts
+                lw.router_w = put(rnd(E, H))
+                w1, w3, w2 = rnd(E, I, H), rnd(E, I, H), rnd(E, H, I)
+                lw.experts_w13 = put(torch.cat([w1, w3], 1))
+                lw.experts_w2 = put(w2)
+            else:
+                ib = I // ws
+                up = rnd(I, H)
+                down = rnd(H, I)
+                if m.gated:
+                    gate = rnd(I, H)
+                    lw.gate_up_w = put(torch.cat([gate[rk * ib:(rk + 1) * ib], up[rk * ib:(rk + 1) * ib]], 0))
+                else:
+                    lw.gate_up_w = put(up[rk * ib:(rk + 1) * ib])
+                lw.down_w = put(down[:, rk * ib:(rk + 1) * ib])
+                if c.mlp_bias:
+                    ub = rnd(I)
+                    lw.gate_up_b = put(ub[rk * ib:(rk + 1) * ib])
+                    lw.down_b = put(rnd(H)) if rk == 0 else put(torch.zeros(H))
+            if c.model_type == "gemma2":
+                lw.pre_ffn_norm = put(torch.ones(H) - c.norm_weight_offset + rnd(H, s=0.01))
+                lw.post_ffn_norm = put(torch.ones(H) - c.norm_weight_offset + rnd(H, s=0.01))
+            m.layers.append(lw)
+        m.final_norm = put(torch.ones(H) - c.norm_weight_offset + rnd(H, s=0.01))
+        if ln and has_ln_bias:
+            m.final_norm_b = put(rnd(H, s=0.01))
+        if c.tie_word_embeddings:
+            m.lm_head = m.embed
+        else:
+            head = rnd(c.vocab_size, H)
+            m.lm_head = put(head if ws == 1 else _pad_rows(head, m.vocab_local * ws)[m.vocab_start:m.vocab_start + m.vocab_local])
+        return m
+
+    @classmethod
+    def from_weights(cls, config: ModelConfig, weights: AbstractWeights, device, dtype, tp: Optional[TensorParallel] = None,
+                     max_positions: Optional[int] = None) -> "DecoderModel":
+        from .loading import load_decoder_weights
+        m = cls(config, device, dtype, tp, max_positions)
+        load_decoder_weights(m, weights)
+        return m
+
+    # ------------------------------------------------------------------ forward
+    def _norm(self, x, residual, w, b=None, x_scale: float = 1.0):
+        c = self.config
+        return self.ops.norm_residual(x, residual, w, c.rms_norm_eps, bias=b, weight_offset=c.norm_weight_offset,
+                                      x_scale=x_scale, layernorm=c.norm_type.startswith("layernorm"))
+
+    def _linear(self, x, w, b, group: str, layer: int, inp: StepInputs, tok_slot=None):
+        """Base GEMM plus the multi-adapter LoRA delta for the projection group."""
+        y = self.ops.gemm(x, w, bias=b)
+        ts = tok_slot if tok_slot is not None else inp.tok_slot
+        if ts is not None and self.adapters is not None:
+            self.adapters.apply(self.ops, x, y, ts, group, layer)
+        return y
+
+    def forward(self, inp: StepInputs, kv_cache: List[torch.Tensor]) -> torch.Tensor:
+        """-> logits [n_out, vocab] (full vocabulary on every rank)."""
+        c, ops = self.config, self.ops
+        h = ops.embed(inp.input_ids, self.embed, v0=self.vocab_start, v1=self.vocab_start + self.embed.shape[0],
+                      mult=c.embedding_multiplier)
+        if self.tp.world_size > 1:
+            h = self.tp.all_reduce(h)
+        if self.pos_embed is not None:
+            h = h + self.pos_embed[inp.positions.long()]
+        residual = h
+        pending = None      # output of the previous block that still has to be added to the residual stream
+        rm = c.residual_multiplier
+        for li, lw in enumerate(self.layers):
+            if pending is None:
+                normed = self._norm(residual, None, lw.input_norm, lw.input_norm_b)
+            else:
+                normed = self._norm(pending, residual, lw.input_norm, lw.input_norm_b, x_scale=rm)
+            attn_out = self._attention(normed, lw, li, inp, kv_cache[li])
+            if c.parallel_residual:
+                mlp_in = normed if lw.post_norm is None else self._norm(residual, None, lw.post_norm, lw.post_norm_b)
+                mlp_out = self._mlp(mlp_in, lw, li, inp)
+                pending = attn_out + mlp_out
+                continue
+            if lw.post_ffn_norm is not None:      # gemma2: norm the block output before it joins the residual
+                attn_out = self._norm(attn_out, None, lw.post_norm)
+                normed2 = self._norm(attn_out, residual, lw.pre_ffn_norm)
+                mlp_out = self._mlp(normed2, lw, li, inp)
+                pending = self._norm(mlp_out, None, lw.post_ffn_norm)
+                continue
+            normed2 = self._norm(attn_out, residual, lw.post_norm, lw.post_norm_b, x_scale=rm)
+            pending = self._moe(normed2, lw, li, inp) if c.is_moe else self._mlp(normed2, lw, li, inp)
+        hidden = self._norm(pending, residual, self.final_norm, self.final_norm_b, x_scale=rm)
+        if inp.lm_head_indices is not None:
+            hidden = hidden.index_select(0, inp.lm_head_indices.long()) if hidden.device.type == "cpu" else hidden[inp.lm_head_indices.long()]
+        return self.lm_head_forward(hidden, inp)
+
+    def lm_head_forward(self, hidden: torch.Tensor, inp: StepInputs) -> torch.Tensor:
+        c = self.config
+        scale = c.logit_scale / c.logits_scaling if c.logits_scaling != 1.0 else c.logit_scale
+        logits = self.ops.gemm(hidden, self.lm_head, bias=self.lm_head_b, out_scale=scale)
+        ts = inp.head_tok_slot
+        if ts is not None and self.adapters is not None and self.adapters.layout.has_lm_head:
+            self.adapters.apply(self.ops, hidden, logits, ts, "lm_head", 0)
+        if self.tp.world_size > 1:
+            logits = self.tp.all_gather_cols(logits)[:, : self.vocab]
+        elif logits.shape[1] != self.vocab:
+            logits = logits[:, : self.vocab]
+        return logits
+
+    def _attention(self, x, lw: LayerWeights, li: int, inp: StepInputs, kv: torch.Tensor):
+        c, ops = self.config, self.ops
+        qkv = self._linear(x, lw.qkv_w, lw.qkv_b, "qkv", li, inp)
+        ops.rope_kvwrite(qkv, inp.positions, self.cos_sin, kv, inp.slots, self.nh, self.nkv, self.d, c.rotary_dim,
+                         not c.learned_positions)
+        window = c.sliding_window or 0
+        if c.model_type == "gemma2" and li % 2 == 1:
+            window = 0
+        softcap = c.attn_logit_softcapping or 0.0
+        if inp.is_prefill:
+            attn = ops.attn_prefill(qkv, kv, inp.block_tables, inp.cu_q, inp.cache_lens, inp.tile_seq, inp.tile_q0,
+                                    self.nh, self.nkv, self.d, c.attn_scale, window, softcap)
+        else:
+            attn = ops.attn_decode(qkv, kv, inp.block_tables, inp.ctx_lens, self.nh, self.nkv, self.d, c.attn_scale, window,
+                                   softcap, inp.attn_nsplit)
+        out = self._linear(attn, lw.o_w, lw.o_b, "o", li, inp)
+        if self.tp.world_size > 1:
+            out = self.tp.all_reduce(out)
+        return out
+
+    def _mlp(self, x, lw: LayerWeights, li: int, inp: StepInputs):
+        c, ops = self.config, self.ops
+        gu = self._linear(x, lw.gate_up_w, lw.gate_up_b, "gate_up", li, inp)
+        act = ops.act_mul(gu, self.inter, c.hidden_act, gated=self.gated)
+        out = self._linear(act, lw.down_w, lw.down_b, "down", li, inp)
+        if self.tp.world_size > 1:
+            out = self.tp.all_reduce(out)
+        return out
+
+    def _moe(self, x, lw: LayerWeights, li: int, inp: StepInputs):
+        """Top-k mixture of experts (reference math: flash_mixtral_modeling.py:449-459, 668-716): softmax over all
+        experts, keep top-k, renormalise.  Experts are expert-parallel: rank r owns experts [r*E/ws, (r+1)*E/ws)."""
+        from .moe import moe_forward
+        return moe_forward(self, x, lw, li, inp)
+
+
+def _pad_rows(t: torch.Tensor, n: int) -> torch.Tensor:
+    if t.shape[0] >= n:
+        return t
+    return torch.cat([t, torch.zeros(n - t.shape[0], *t.shape[1:], dtype=t.dtype)], 0)

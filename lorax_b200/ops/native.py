@@ -1,0 +1,274 @@
+"""ctypes bindings for ``_lx_kernels.so`` (the sm_100a CUDA kernels).
+
+The library exports a plain C ABI; tensors are passed as raw device pointers together with the current
+CUDA stream, so a call is a direct kernel launch with no framework dispatch in between and is safe to
+capture into a CUDA graph.  Loading fails loudly on a GPU machine when the library is missing: there is
+no silent eager fallback.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_PKG = Path(__file__).resolve().parent.parent
+_LIB_PATH = _PKG / "_lx_kernels.so"
+_lib: Optional[ctypes.CDLL] = None
+
+# number of kernel launches issued through this module (bench.py reports it as `gpu_launches`)
+launch_count = 0
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB_PATH.exists():
+        if os.environ.get("LORAX_B200_NO_BUILD") != "1":
+            from lorax_b200.csrc import build as _build
+            _build.build_kernels()
+        if not _LIB_PATH.exists():
+            raise NativeError(f"{_LIB_PATH} is missing; run `python -m lorax_b200.csrc.build`")
+    lib = ctypes.CDLL(str(_LIB_PATH))
+    P, I, L, F = c_void_p, c_int, c_longlong, c_float
+    sigs = {
+        "lx_gemm_ws_bytes": ([], L),
+        "lx_gemm_max_tiles": ([], I),
+        "lx_gemm_bf16": ([P, P, P, P, I, I, I, L, L, L, F, P, L, P, P, I, I, I, P], I),
+        "lx_norm_residual": ([P, P, P, P, P, I, I, L, L, L, F, F, F, I, P], I),
+        "lx_rope_kvwrite": ([P, P, P, P, P, I, I, I, I, I, I, L, I, P], I),
+        "lx_act_mul": ([P, P, I, I, L, L, I, I, P], I),
+        "lx_embed": ([P, P, P, I, I, I, I, F, P], I),
+        "lx_argmax_logprob": ([P, L, I, I, P, P, F, P], I),
+        "lx_advance_decode": ([P, P, P, P, P, P, I, I, I, P], I),
+        "lx_attn_page_size": ([], I),
+        "lx_attn_decode": ([P, L, P, P, I, P, P, L, P, P, I, I, I, I, I, F, F, I, P], I),
+        "lx_attn_prefill": ([P, L, P, P, I, P, P, P, P, I, P, L, I, I, I, I, F, F, P], I),
+        "lx_lora_shrink": ([P, L, P, P, P, P, I, L, I, P, I, I, I, I, P, P], I),
+        "lx_lora_expand": ([P, I, P, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
+    }
+    for name, (argtypes, restype) in sigs.items():
+        fn = getattr(lib, name)
+        fn.argtypes = argtypes
+        fn.restype = restype
+    _lib = lib
+    return lib
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(rc: int, what: str):
+    global launch_count
+    launch_count += 1
+    if rc != 0:
+        raise NativeError(f"{what} failed with code {rc}")
+
+
+class Workspace:
+    """Device scratch shared by the kernels of one process: split-K partials and counters, split-KV partials,
+    the status words written by bounded waits, and the LoRA intermediate."""
+
+    def __init__(self, device: torch.device, max_tokens: int = 8192, max_lora_cols: int = 3 * 128,
+                 attn_splits: int = 16, num_heads: int = 64, head_dim: int = 128):
+        lib = load()
+        self.device = device
+        self.gemm_ws = torch.empty(lib.lx_gemm_ws_bytes(), dtype=torch.uint8, device=device)
+        self.gemm_counters = torch.zeros(lib.lx_gemm_max_tiles(), dtype=torch.int32, device=device)
+        self.status = torch.zeros(2, dtype=torch.int32, device=device)
+        self.lora_v = torch.zeros(max_tokens, max_lora_cols, dtype=torch.float32, device=device)
+        self.attn_part_tokens = 512
+        self.attn_splits = attn_splits
+        self.attn_part_o = torch.empty(self.attn_part_tokens * num_heads * attn_splits * head_dim, dtype=torch.float32, device=device)
+        self.attn_part_lse = torch.empty(self.attn_part_tokens * num_heads * attn_splits, dtype=torch.float32, device=device)
+        self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
+
+    def check_status(self):
+        """Raise if a bounded device-side wait ran out since the last check (one D2H of 8 bytes)."""
+        st = self.status.tolist()
+        if st[0] != 0:
+            self.status.zero_()
+            names = {1: "TMA data never landed", 2: "smem stage never released", 3: "accumulator never completed",
+                     4: "accumulator never drained", 5: "peer flag timeout", 6: "split-K timeout", 7: "index out of range"}
+            raise NativeError(f"device status {st[0]} ({names.get(st[0], '?')}), detail {st[1]}")
+
+
+_workspaces = {}
+
+
+def workspace(device=None) -> Workspace:
+    device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+    if device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    ws = _workspaces.get(device)
+    if ws is None:
+        ws = _workspaces[device] = Workspace(device)
+    return ws
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+         out_scale: float = 1.0, mode: int = 0, force_split: int = 0) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ w[N, K]^T (+ bias).  bf16 in, fp32 accumulate on tcgen05, bf16 out."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
+    assert x.stride(1) == 1 and w.stride(1) == 1
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    assert out.stride(1) == 1
+    ws = workspace(x.device)
+    lib = load()
+    if mode == 0 and T > 256:
+        mode = 2
+    rc = lib.lx_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), _ptr(bias), T, N, K, x.stride(0), w.stride(0), out.stride(0),
+                          out_scale, _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.gemm_counters), _ptr(ws.status),
+                          ws.num_sms, mode, force_split, _stream())
+    _check(rc, "lx_gemm_bf16")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ elementwise
+def norm_residual(x: torch.Tensor, residual: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                  bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, weight_offset: float = 0.0,
+                  x_scale: float = 1.0, layernorm: bool = False) -> torch.Tensor:
+    """h = x * x_scale (+ residual); residual <- h (in place); returns norm(h) * (weight + offset) (+ bias)."""
+    T, H = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    rc = load().lx_norm_residual(_ptr(x), _ptr(residual), _ptr(weight), _ptr(bias), _ptr(out), T, H, x.stride(0),
+                                 residual.stride(0) if residual is not None else 0, out.stride(0), eps, weight_offset,
+                                 x_scale, int(layernorm), _stream())
+    _check(rc, "lx_norm_residual")
+    return out
+
+
+def rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, kv_cache: torch.Tensor,
+                 slots: Optional[torch.Tensor], nh: int, nkv: int, d: int, rot: int, apply_rope: bool = True):
+    T = qkv.shape[0]
+    page = kv_cache.shape[3]
+    rc = load().lx_rope_kvwrite(_ptr(qkv), _ptr(positions), _ptr(cos_sin), _ptr(kv_cache), _ptr(slots), T, nh, nkv, d, rot,
+                                page, qkv.stride(0), int(apply_rope), _stream())
+    _check(rc, "lx_rope_kvwrite")
+
+
+_ACTS = {"silu": 0, "swish": 0, "gelu": 1, "gelu_new": 2, "gelu_pytorch_tanh": 2, "gelu_fast": 2, "gelu_tanh": 2, "relu": 3}
+
+
+def act_mul(x: torch.Tensor, inter: int, act: str = "silu", gated: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T = x.shape[0]
+    if out is None:
+        out = torch.empty(T, inter, dtype=x.dtype, device=x.device)
+    rc = load().lx_act_mul(_ptr(x), _ptr(out), T, inter, x.stride(0), out.stride(0), _ACTS[act], int(gated), _stream())
+    _check(rc, "lx_act_mul")
+    return out
+
+
+def embed(ids: torch.Tensor, table: torch.Tensor, v0: int = 0, v1: Optional[int] = None, mult: float = 1.0,
+          out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T = ids.shape[0]
+    H = table.shape[1]
+    if v1 is None:
+        v1 = v0 + table.shape[0]
+    if out is None:
+        out = torch.empty(T, H, dtype=table.dtype, device=table.device)
+    rc = load().lx_embed(_ptr(ids), _ptr(table), _ptr(out), T, H, v0, v1, mult, _stream())
+    _check(rc, "lx_embed")
+    return out
+
+
+def argmax_logprob(logits: torch.Tensor, ids: Optional[torch.Tensor] = None, logprobs: Optional[torch.Tensor] = None,
+                   softcap: float = 0.0):
+    T, V = logits.shape
+    if ids is None:
+        ids = torch.empty(T, dtype=torch.int32, device=logits.device)
+    if logprobs is None:
+        logprobs = torch.empty(T, dtype=torch.float32, device=logits.device)
+    rc = load().lx_argmax_logprob(_ptr(logits), logits.stride(0), T, V, _ptr(ids), _ptr(logprobs), softcap, _stream())
+    _check(rc, "lx_argmax_logprob")
+    return ids, logprobs
+
+
+def advance_decode(input_ids, next_ids, positions, ctx_lens, slots, block_tables, page: int):
+    B = input_ids.shape[0]
+    rc = load().lx_advance_decode(_ptr(input_ids), _ptr(next_ids), _ptr(positions), _ptr(ctx_lens), _ptr(slots),
+                                  _ptr(block_tables), block_tables.shape[1], page, B, _stream())
+    _check(rc, "lx_advance_decode")
+
+
+# ------------------------------------------------------------------------------------------------ attention
+def attn_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Tensor, ctx_lens: torch.Tensor, nh: int, nkv: int,
+                d: int, scale: float, window: int = 0, softcap: float = 0.0, nsplit: int = 1,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q: [T, >= nh*d] (row stride arbitrary), one query token per row.  Returns [T, nh*d]."""
+    T = q.shape[0]
+    if out is None:
+        out = torch.empty(T, nh * d, dtype=q.dtype, device=q.device)
+    ws = workspace(q.device)
+    if nsplit > 1:
+        nsplit = min(nsplit, ws.attn_splits)
+        if T > ws.attn_part_tokens:
+            nsplit = 1
+    rc = load().lx_attn_decode(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(ctx_lens),
+                               _ptr(out), out.stride(0), _ptr(ws.attn_part_o), _ptr(ws.attn_part_lse), T, nh, nkv, d, window,
+                               scale, softcap, nsplit, _stream())
+    _check(rc, "lx_attn_decode")
+    return out
+
+
+def attn_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Tensor, cu_q: torch.Tensor, cache_lens: torch.Tensor,
+                 tile_seq: torch.Tensor, tile_q0: torch.Tensor, nh: int, nkv: int, d: int, scale: float, window: int = 0,
+                 softcap: float = 0.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T = q.shape[0]
+    if out is None:
+        out = torch.empty(T, nh * d, dtype=q.dtype, device=q.device)
+    rc = load().lx_attn_prefill(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(cu_q),
+                                _ptr(cache_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0], _ptr(out), out.stride(0), nh,
+                                nkv, d, window, scale, softcap, _stream())
+    _check(rc, "lx_attn_prefill")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ LoRA
+def lora_shrink(x: torch.Tensor, tok_slot: torch.Tensor, arena: torch.Tensor, slot_base: torch.Tensor, slot_rank: torch.Tensor,
+                unit_off: int, nparts: int, max_rank: int, v: Optional[torch.Tensor] = None) -> torch.Tensor:
+    T, K = x.shape
+    ws = workspace(x.device)
+    if v is None:
+        v = ws.lora_v
+    rc = load().lx_lora_shrink(_ptr(x), x.stride(0), _ptr(tok_slot), _ptr(arena), _ptr(slot_base), _ptr(slot_rank),
+                               slot_rank.shape[0], unit_off, nparts, _ptr(v), v.stride(0), T, K, max_rank, _ptr(ws.status), _stream())
+    _check(rc, "lx_lora_shrink")
+    return v
+
+
+def lora_expand(v: torch.Tensor, tok_slot: torch.Tensor, arena: torch.Tensor, slot_base: torch.Tensor, slot_rank: torch.Tensor,
+                unit_off: int, y: torch.Tensor, n0: int, n1: int):
+    T, N = y.shape
+    ws = workspace(y.device)
+    rc = load().lx_lora_expand(_ptr(v), v.stride(0), _ptr(tok_slot), _ptr(arena), _ptr(slot_base), _ptr(slot_rank),
+                               slot_rank.shape[0], unit_off, _ptr(y), y.stride(0), T, N, n0, n1, _ptr(ws.status), _stream())
+    _check(rc, "lx_lora_expand")

@@ -1,0 +1,303 @@
+"""Plain PyTorch statements of every operator.
+
+They are the oracle for the CUDA kernels (tests compare a kernel against the fp32 version of the same
+function) and the compute path of the engine on a machine without a GPU.  Signatures mirror
+:mod:`lorax_b200.ops.native`.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+
+def gemm(x, w, bias=None, out=None, out_scale: float = 1.0, **_):
+    y = (x.float() @ w.float().t()) * out_scale
+    if bias is not None:
+        y = y + bias.float()
+    y = y.to(x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def norm_residual(x, residual, weight, eps, bias=None, out=None, weight_offset: float = 0.0, x_scale: float = 1.0,
+                  layernorm: bool = False):
+    h = x.float() * x_scale
+    if residual is not None:
+        h = h + residual.float()
+        residual.copy_(h.to(residual.dtype))
+        h = residual.float()
+    if layernorm:
+        mean = h.mean(-1, keepdim=True)
+        var = (h * h).mean(-1, keepdim=True) - mean * mean
+        y = (h - mean) * torch.rsqrt(var.clamp_min(0) + eps)
+    else:
+        y = h * torch.rsqrt((h * h).mean(-1, keepdim=True) + eps)
+    y = y * (weight.float() + weight_offset)
+    if bias is not None:
+        y = y + bias.float()
+    y = y.to(x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def apply_rope(x, cos, sin, rot):
+    """x: [T, heads, d]; cos/sin: [T, rot/2].  Rotate-half convention on the first `rot` dims."""
+    half = rot // 2
+    x1, x2, rest = x[..., :half].float(), x[..., half:rot].float(), x[..., rot:]
+    c, s = cos[:, None, :], sin[:, None, :]
+    o1 = x1 * c - x2 * s
+    o2 = x2 * c + x1 * s
+    return torch.cat([o1.to(x.dtype), o2.to(x.dtype), rest], dim=-1)
+
+
+def rope_kvwrite(qkv, positions, cos_sin, kv_cache, slots, nh, nkv, d, rot, apply_rope_flag: bool = True):
+    """In place on qkv [T, (nh+2nkv)*d]; kv_cache [blocks, nkv, 2, page, d]."""
+    T = qkv.shape[0]
+    page = kv_cache.shape[3]
+    q = qkv[:, : nh * d].view(T, nh, d)
+    k = qkv[:, nh * d: (nh + nkv) * d].view(T, nkv, d)
+    v = qkv[:, (nh + nkv) * d: (nh + 2 * nkv) * d].view(T, nkv, d)
+    if apply_rope_flag:
+        cs = cos_sin[positions.long()]
+        cos, sin = cs[:, : rot // 2], cs[:, rot // 2: rot]
+        q.copy_(apply_rope(q, cos, sin, rot))
+        k.copy_(apply_rope(k, cos, sin, rot))
+    if slots is not None:
+        ok = slots >= 0
+        s = slots[ok].long()
+        blk, off = s // page, s % page
+        kv_cache[blk, :, 0, off, :] = k[ok]
+        kv_cache[blk, :, 1, off, :] = v[ok]
+
+
+def _act(x, act):
+    if act in ("silu", "swish"):
+        return F.silu(x)
+    if act == "gelu":
+        return F.gelu(x)
+    if act in ("gelu_new", "gelu_pytorch_tanh", "gelu_fast", "gelu_tanh"):
+        return F.gelu(x, approximate="tanh")
+    if act == "relu":
+        return F.relu(x)
+    raise ValueError(act)
+
+
+def act_mul(x, inter, act="silu", gated=True, out=None):
+    g = _act(x[:, :inter].float(), act)
+    if gated:
+        g = g * x[:, inter: 2 * inter].float()
+    g = g.to(x.dtype)
+    if out is not None:
+        out.copy_(g)
+        return out
+    return g
+
+
+def embed(ids, table, v0=0, v1=None, mult=1.0, out=None):
+    if v1 is None:
+        v1 = v0 + table.shape[0]
+    idl = ids.long()
+    ok = (idl >= v0) & (idl < v1)
+    y = table[(idl - v0).clamp(0, table.shape[0] - 1)]
+    if mult != 1.0:
+        y = (y.float() * mult).to(table.dtype)
+    y = torch.where(ok[:, None], y, torch.zeros_like(y))
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def argmax_logprob(logits, ids=None, logprobs=None, softcap: float = 0.0):
+    x = logits.float()
+    if softcap > 0:
+        x = softcap * torch.tanh(x / softcap)
+    i = x.argmax(-1)
+    lp = torch.log_softmax(x, -1).gather(1, i[:, None])[:, 0]
+    if ids is not None:
+        ids.copy_(i.to(ids.dtype))
+        logprobs.copy_(lp)
+        return ids, logprobs
+    return i.to(torch.int32), lp
+
+
+def advance_decode(input_ids, next_ids, positions, ctx_lens, slots, block_tables, page):
+    live = ctx_lens > 0
+    input_ids[live] = next_ids[live].to(input_ids.dtype)
+    positions[live] += 1
+    ctx_lens[live] = positions[live] + 1
+    pos = positions.long()
+    blk = block_tables.gather(1, (pos // page).clamp(0, block_tables.shape[1] - 1)[:, None])[:, 0]
+    new_slots = blk * page + (pos % page).to(blk.dtype)
+    slots.copy_(torch.where(live, new_slots.to(slots.dtype), torch.full_like(slots, -1)))
+
+
+def _gather_kv(kv_cache, block_table, n_keys, kvh):
+    """-> K [n_keys, d], V [n_keys, d] for one sequence and kv head."""
+    page = kv_cache.shape[3]
+    nblk = (n_keys + page - 1) // page
+    blocks = block_table[:nblk].long()
+    k = kv_cache[blocks, kvh, 0].reshape(-1, kv_cache.shape[-1])[:n_keys]
+    v = kv_cache[blocks, kvh, 1].reshape(-1, kv_cache.shape[-1])[:n_keys]
+    return k, v
+
+
+def _attend(q, k, v, q_pos, scale, window, softcap):
+    """q: [nq, d] at absolute positions q_pos [nq]; k, v: [nk, d] at positions 0..nk-1."""
+    s = (q.float() @ k.float().t()) * scale
+    if softcap and softcap > 0:
+        s = softcap * torch.tanh(s / softcap)
+    kp = torch.arange(k.shape[0], device=q.device)[None, :]
+    mask = kp <= q_pos[:, None]
+    if window and window > 0:
+        mask &= kp > (q_pos[:, None] - window)
+    s = s.masked_fill(~mask, float("-inf"))
+    p = torch.softmax(s, -1)
+    p = torch.nan_to_num(p, nan=0.0)
+    return p @ v.float()
+
+
+def attn_decode(q, kv_cache, block_tables, ctx_lens, nh, nkv, d, scale, window=0, softcap=0.0, nsplit=1, out=None):
+    T = q.shape[0]
+    res = torch.zeros(T, nh * d, dtype=q.dtype, device=q.device)
+    g = nh // nkv
+    for t in range(T):
+        n = int(ctx_lens[t])
+        if n <= 0:
+            continue
+        for kvh in range(nkv):
+            k, v = _gather_kv(kv_cache, block_tables[t], n, kvh)
+            qh = q[t, kvh * g * d: (kvh + 1) * g * d].view(g, d)
+            o = _attend(qh, k, v, torch.full((g,), n - 1, device=q.device), scale, window, softcap)
+            res[t, kvh * g * d: (kvh + 1) * g * d] = o.reshape(-1).to(q.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def attn_prefill(q, kv_cache, block_tables, cu_q, cache_lens, tile_seq, tile_q0, nh, nkv, d, scale, window=0, softcap=0.0,
+                 out=None):
+    T = q.shape[0]
+    res = torch.zeros(T, nh * d, dtype=q.dtype, device=q.device)
+    g = nh // nkv
+    B = cache_lens.shape[0]
+    for b in range(B):
+        s, e = int(cu_q[b]), int(cu_q[b + 1])
+        if e <= s:
+            continue
+        c = int(cache_lens[b])
+        n = c + (e - s)
+        pos = torch.arange(c, n, device=q.device)
+        for kvh in range(nkv):
+            k, v = _gather_kv(kv_cache, block_tables[b], n, kvh)
+            for gi in range(g):
+                h = kvh * g + gi
+                o = _attend(q[s:e, h * d: (h + 1) * d], k, v, pos, scale, window, softcap)
+                res[s:e, h * d: (h + 1) * d] = o.to(q.dtype)
+    if out is not None:
+        out.copy_(res)
+        return out
+    return res
+
+
+def prefill_tiles(q_lens, tile: int = 64):
+    """Host-side tile map for attn_prefill: (tile_seq, tile_q0) int32 lists."""
+    seq, q0 = [], []
+    for b, n in enumerate(q_lens):
+        for s in range(0, n, tile):
+            seq.append(b)
+            q0.append(s)
+    return seq, q0
+
+
+def lora_shrink(x, tok_slot, arena, slot_base, slot_rank, unit_off, nparts, max_rank, v=None):
+    T, K = x.shape
+    if v is None:
+        v = torch.zeros(T, nparts * max_rank, dtype=torch.float32, device=x.device)
+    for t in range(T):
+        s = int(tok_slot[t])
+        if s < 0 or int(slot_base[s]) < 0:
+            continue
+        r = int(slot_rank[s])
+        off = int(slot_base[s]) + r * unit_off
+        A = arena[off: off + nparts * r * K].view(nparts * r, K)
+        v[t, : nparts * r] = x[t].float() @ A.float().t()
+    return v
+
+
+def lora_expand(v, tok_slot, arena, slot_base, slot_rank, unit_off, y, n0, n1):
+    T, N = y.shape
+    bounds = [0, n0, n1, N]
+    for t in range(T):
+        s = int(tok_slot[t])
+        if s < 0 or int(slot_base[s]) < 0:
+            continue
+        r = int(slot_rank[s])
+        off = int(slot_base[s]) + r * unit_off
+        B = arena[off: off + N * r].view(N, r).float()
+        delta = torch.zeros(N, dtype=torch.float32, device=y.device)
+        for part in range(3):
+            a, b = bounds[part], bounds[part + 1]
+            if b > a:
+                delta[a:b] = B[a:b] @ v[t, part * r: (part + 1) * r].float()
+        y[t] = (y[t].float() + delta).to(y.dtype)
+
+
+def rope_cache(rot: int, max_pos: int, theta: float, scaling: Optional[dict] = None, device="cpu") -> torch.Tensor:
+    """[max_pos, rot] fp32 table: cos in the first half, sin in the second.
+
+    Scaling variants follow `server/lorax_server/utils/layers.py:484-816` of the reference: linear,
+    dynamic NTK, YaRN, Su/LongRoPE and llama3.
+    """
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    mscale = 1.0
+    t = torch.arange(max_pos, dtype=torch.float32)
+    if scaling:
+        kind = scaling.get("rope_type", scaling.get("type", "default"))
+        factor = float(scaling.get("factor", 1.0))
+        if kind == "linear":
+            t = t / factor
+        elif kind == "dynamic":
+            orig = int(scaling.get("original_max_position_embeddings", max_pos))
+            if max_pos > orig:
+                base = theta * ((factor * max_pos / orig) - (factor - 1)) ** (rot / (rot - 2))
+                inv_freq = 1.0 / (base ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+        elif kind == "llama3":
+            low = float(scaling.get("low_freq_factor", 1.0))
+            high = float(scaling.get("high_freq_factor", 4.0))
+            orig = float(scaling.get("original_max_position_embeddings", 8192))
+            wavelen = 2 * math.pi / inv_freq
+            smooth = ((orig / wavelen) - low) / (high - low)
+            scaled = torch.where(wavelen > orig / low, inv_freq / factor, inv_freq)
+            mid = (wavelen <= orig / low) & (wavelen >= orig / high)
+            inv_freq = torch.where(mid, (1 - smooth) * inv_freq / factor + smooth * inv_freq, scaled)
+        elif kind == "yarn":
+            orig = float(scaling.get("original_max_position_embeddings", 4096))
+            beta_fast, beta_slow = float(scaling.get("beta_fast", 32)), float(scaling.get("beta_slow", 1))
+
+            def corr_dim(nrot):
+                return (rot * math.log(orig / (nrot * 2 * math.pi))) / (2 * math.log(theta))
+
+            lo = max(math.floor(corr_dim(beta_fast)), 0)
+            hi = min(math.ceil(corr_dim(beta_slow)), rot - 1)
+            ramp = ((torch.arange(rot // 2, dtype=torch.float32) - lo) / max(hi - lo, 1e-3)).clamp(0, 1)
+            inv_mask = 1 - ramp
+            inv_freq = (inv_freq / factor) * (1 - inv_mask) + inv_freq * inv_mask
+            mscale = float(scaling.get("attention_factor") or (0.1 * math.log(factor) + 1.0 if factor > 1 else 1.0))
+        elif kind in ("su", "longrope"):
+            orig = int(scaling.get("original_max_position_embeddings", max_pos))
+            ext = torch.tensor(scaling["long_factor"] if max_pos > orig else scaling["short_factor"], dtype=torch.float32)
+            inv_freq = inv_freq / ext
+            sc = max_pos / orig
+            mscale = 1.0 if sc <= 1 else math.sqrt(1 + math.log(sc) / math.log(orig))
+    freqs = torch.outer(t, inv_freq)
+    return torch.cat([freqs.cos() * mscale, freqs.sin() * mscale], dim=-1).to(device)

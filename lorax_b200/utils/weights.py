@@ -1,0 +1,214 @@
+"""Checkpoint access: tensor-name -> file routing over safetensors shards, lazy handles, and the
+tensor-parallel slicing helpers the model loaders use.
+
+Behavioural counterpart of `server/lorax_server/utils/weights.py:43-407` in the reference (`get_tensor`,
+`get_sharded`, `get_partial_sharded` with block = size // world_size, packed QKV handling, and an
+in-memory variant for adapters).  `.bin` checkpoints are converted once to safetensors next to the
+source (`utils/convert.py:62-114`).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import struct
+from pathlib import Path
+from typing import Dict, Iterable, List, Optional, Sequence
+
+import torch
+from safetensors import safe_open
+from safetensors.torch import load_file, save_file
+
+
+class AbstractWeights:
+    def get_tensor(self, name: str) -> torch.Tensor:  # pragma: no cover - interface
+        raise NotImplementedError
+
+    def has_tensor(self, name: str) -> bool:  # pragma: no cover - interface
+        raise NotImplementedError
+
+    def get_shape(self, name: str):
+        return tuple(self.get_tensor(name).shape)
+
+
+class Weights(AbstractWeights):
+    def __init__(self, filenames: Sequence[os.PathLike], device="cpu", dtype: Optional[torch.dtype] = None,
+                 rank: int = 0, world_size: int = 1, aliases: Optional[Dict[str, List[str]]] = None, prefix: str = ""):
+        self.routing: Dict[str, str] = {}
+        for fn in filenames:
+            with safe_open(str(fn), framework="pt") as f:
+                for k in f.keys():
+                    if k in self.routing:
+                        raise RuntimeError(f"key {k} found in {fn} and {self.routing[k]}")
+                    self.routing[k] = str(fn)
+        self.aliases = aliases or {}
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.rank = rank
+        self.world_size = world_size
+        self.prefix = prefix
+        self._handles: Dict[str, object] = {}
+
+    # ---------------------------------------------------------------- routing
+    def _handle(self, filename: str):
+        h = self._handles.get(filename)
+        if h is None:
+            h = self._handles[filename] = safe_open(filename, framework="pt")
+        return h
+
+    def _resolve(self, name: str):
+        for cand in [self.prefix + name, name] + self.aliases.get(name, []):
+            fn = self.routing.get(cand)
+            if fn is not None:
+                return fn, cand
+        raise KeyError(f"weight {name} does not exist")
+
+    def has_tensor(self, name: str) -> bool:
+        try:
+            self._resolve(name)
+            return True
+        except KeyError:
+            return False
+
+    def _slice(self, name: str):
+        fn, key = self._resolve(name)
+        return self._handle(fn).get_slice(key)
+
+    def get_shape(self, name: str):
+        return tuple(self._slice(name).get_shape())
+
+    def _finish(self, t: torch.Tensor) -> torch.Tensor:
+        if self.dtype is not None and t.dtype.is_floating_point and t.dtype not in (torch.float8_e4m3fn, torch.float8_e5m2):
+            t = t.to(self.dtype)
+        return t.to(self.device)
+
+    # ---------------------------------------------------------------- getters
+    def get_tensor(self, name: str) -> torch.Tensor:
+        fn, key = self._resolve(name)
+        return self._finish(self._handle(fn).get_tensor(key))
+
+    def get_partial_sharded(self, name: str, dim: int) -> torch.Tensor:
+        """This rank's contiguous block of `dim` (block = size // world_size; the tail goes to the last rank's
+        neighbour by the same rule as the reference: start = rank * block)."""
+        sl = self._slice(name)
+        size = sl.get_shape()[dim]
+        block = size // self.world_size
+        start, stop = self.rank * block, (self.rank + 1) * block
+        if dim == 0:
+            t = sl[start:stop]
+        elif dim == 1:
+            t = sl[:, start:stop]
+        else:
+            raise NotImplementedError("only dims 0 and 1 are sharded")
+        return self._finish(t)
+
+    def get_sharded(self, name: str, dim: int) -> torch.Tensor:
+        size = self.get_shape(name)[dim]
+        if size % self.world_size != 0:
+            raise ValueError(f"{name}: dim {dim} of size {size} is not divisible by {self.world_size} shards")
+        return self.get_partial_sharded(name, dim)
+
+    def get_rows(self, name: str, start: int, stop: int) -> torch.Tensor:
+        return self._finish(self._slice(name)[start:stop])
+
+    def get_multi_sharded(self, names: Iterable[str], dim: int) -> torch.Tensor:
+        """Concatenate the per-rank shards of several tensors (fused QKV / gate_up)."""
+        return torch.cat([self.get_sharded(n, dim) for n in names], dim=0 if dim == 0 else dim)
+
+
+class InMemoryWeights(AbstractWeights):
+    """Tensors already in memory (adapter module maps)."""
+
+    def __init__(self, tensors: Dict[str, torch.Tensor], device="cpu", dtype=None, rank: int = 0, world_size: int = 1):
+        self.tensors = tensors
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.rank, self.world_size = rank, world_size
+
+    def has_tensor(self, name):
+        return name in self.tensors
+
+    def get_tensor(self, name):
+        t = self.tensors[name]
+        if self.dtype is not None and t.dtype.is_floating_point:
+            t = t.to(self.dtype)
+        return t.to(self.device)
+
+    def get_partial_sharded(self, name, dim):
+        t = self.tensors[name]
+        block = t.shape[dim] // self.world_size
+        t = t.narrow(dim, self.rank * block, block)
+        return self.get_tensor_from(t)
+
+    get_sharded = get_partial_sharded
+
+    def get_tensor_from(self, t):
+        if self.dtype is not None and t.dtype.is_floating_point:
+            t = t.to(self.dtype)
+        return t.to(self.device)
+
+
+# -------------------------------------------------------------------------------------------- files
+def safetensors_header(path: os.PathLike) -> dict:
+    """Parse the JSON header of a safetensors file without reading tensor data."""
+    with open(path, "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        return json.loads(f.read(n))
+
+
+def safetensors_nbytes(path: os.PathLike) -> int:
+    """Sum of the tensor byte sizes recorded in the header (`utils/sources/source.py:75-130` of the reference
+    uses the same figure as the adapter's memory cost)."""
+    total = 0
+    for k, v in safetensors_header(path).items():
+        if k == "__metadata__":
+            continue
+        a, b = v["data_offsets"]
+        total += b - a
+    return total
+
+
+def weight_files(model_dir: os.PathLike, extension: str = ".safetensors") -> List[Path]:
+    d = Path(model_dir)
+    files = sorted(p for p in d.glob(f"*{extension}") if not p.name.startswith("adapter_") and "training_args" not in p.name)
+    if not files and extension == ".safetensors":
+        bins = sorted(p for p in d.glob("*.bin") if "training_args" not in p.name and not p.name.startswith("adapter_"))
+        if bins:
+            return convert_files(bins)
+    if not files:
+        raise FileNotFoundError(f"no {extension} weights under {d}")
+    return files
+
+
+def convert_file(pt_file: Path, sf_file: Path, discard_names: Sequence[str] = ()):
+    """torch pickle -> safetensors, dropping tied duplicates and checking for NaN/Inf and round-trip equality."""
+    loaded = torch.load(str(pt_file), map_location="cpu", weights_only=True)
+    if "state_dict" in loaded:
+        loaded = loaded["state_dict"]
+    seen, out = {}, {}
+    for k, v in sorted(loaded.items()):
+        if not isinstance(v, torch.Tensor) or k in discard_names:
+            continue
+        key = (v.data_ptr(), tuple(v.shape), v.dtype)
+        if key in seen:                       # shared storage (tied weights): keep the first name only
+            continue
+        seen[key] = k
+        if v.dtype.is_floating_point and not torch.isfinite(v).all():
+            raise ValueError(f"{pt_file}: tensor {k} has NaN/Inf values")
+        out[k] = v.contiguous()
+    sf_file.parent.mkdir(parents=True, exist_ok=True)
+    save_file(out, str(sf_file), metadata={"format": "pt"})
+    back = load_file(str(sf_file))
+    for k, v in out.items():
+        if not torch.equal(v, back[k]):
+            raise RuntimeError(f"{k} changed in the safetensors round trip")
+
+
+def convert_files(pt_files: Sequence[Path], discard_names: Sequence[str] = ()) -> List[Path]:
+    outs = []
+    for p in pt_files:
+        sf = p.with_name(p.stem.replace("pytorch_model", "model") + ".safetensors")
+        if not sf.exists():
+            convert_file(p, sf, discard_names)
+        outs.append(sf)
+    return outs

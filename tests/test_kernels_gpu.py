@@ -1,0 +1,229 @@
+"""Numerics of every CUDA kernel against the fp32 PyTorch statement of the same operator."""
+import math
+
+import pytest
+import torch
+
+from lorax_b200.ops import reference as ref
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def nat():
+    from lorax_b200.ops import native
+    native.load()
+    return native
+
+
+def _rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / b.norm().clamp_min(1e-6)).item()
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 512, 256), (7, 384, 512), (16, 4096, 4096), (33, 1024, 14336), (100, 6144, 4096),
+                                   (128, 4096, 4096), (200, 1000, 520), (256, 2048, 1024)])
+def test_gemm_small_t(nat, T, N, K):
+    torch.manual_seed(T * 7 + N)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K)
+    out = nat.gemm(x, w)
+    torch.cuda.synchronize()
+    nat.workspace().check_status()
+    want = x.float() @ w.float().t()
+    assert _rel_err(out, want) < 6e-3
+    # deterministic (split-K reduces in a fixed order)
+    out2 = nat.gemm(x, w)
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("T,N,K", [(257, 512, 512), (1000, 4096, 4096), (4096, 6144, 4096), (300, 1000, 520)])
+def test_gemm_large_t(nat, T, N, K):
+    torch.manual_seed(T + N)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K)
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    out = nat.gemm(x, w, bias=b)
+    torch.cuda.synchronize()
+    nat.workspace().check_status()
+    want = x.float() @ w.float().t() + b.float()
+    assert _rel_err(out, want) < 6e-3
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_gemm_modes_bias_split(nat, mode):
+    torch.manual_seed(3)
+    T, N, K = 48, 640, 2048
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K)
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    want = x.float() @ w.float().t() + b.float()
+    for split in ([1, 2, 4] if mode == 1 else [0]):
+        out = nat.gemm(x, w, bias=b, mode=mode, force_split=split)
+        torch.cuda.synchronize()
+        nat.workspace().check_status()
+        assert _rel_err(out, want) < 6e-3, (mode, split)
+
+
+def test_gemm_strided_views(nat):
+    torch.manual_seed(4)
+    big = torch.randn(40, 3 * 1024, device="cuda", dtype=torch.bfloat16)
+    x = big[:, 1024:2048]
+    w = torch.randn(256, 1024, device="cuda", dtype=torch.bfloat16) / 32
+    outbuf = torch.zeros(40, 512, device="cuda", dtype=torch.bfloat16)
+    nat.gemm(x, w, out=outbuf[:, 256:])
+    torch.cuda.synchronize()
+    assert _rel_err(outbuf[:, 256:], x.float() @ w.float().t()) < 6e-3
+    assert outbuf[:, :256].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("T,H,layernorm", [(5, 4096, False), (64, 8192, False), (3, 256, False), (9, 1024, True)])
+def test_norm_residual(nat, T, H, layernorm):
+    torch.manual_seed(0)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    r = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(H, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(H, device="cuda", dtype=torch.bfloat16) if layernorm else None
+    r_ref = r.clone()
+    want = ref.norm_residual(x, r_ref, w, 1e-5, bias=b, layernorm=layernorm, weight_offset=1.0 if not layernorm else 0.0)
+    got = nat.norm_residual(x, r, w, 1e-5, bias=b, layernorm=layernorm, weight_offset=1.0 if not layernorm else 0.0)
+    assert torch.equal(r, r_ref)
+    assert _rel_err(got, want) < 5e-3
+    got2 = nat.norm_residual(x, None, w, 1e-5, bias=b, layernorm=layernorm)
+    want2 = ref.norm_residual(x, None, w, 1e-5, bias=b, layernorm=layernorm)
+    assert _rel_err(got2, want2) < 5e-3
+
+
+@pytest.mark.parametrize("nh,nkv,d,rot", [(32, 8, 128, 128), (4, 2, 64, 64), (8, 8, 64, 32)])
+def test_rope_kvwrite(nat, nh, nkv, d, rot):
+    torch.manual_seed(1)
+    T, page, blocks = 37, 32, 12
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, device="cuda", dtype=torch.bfloat16)
+    pos = torch.randint(0, 500, (T,), device="cuda", dtype=torch.int32)
+    cs = ref.rope_cache(rot, 512, 10000.0, device="cuda")
+    slots = torch.randperm(blocks * page, device="cuda")[:T].to(torch.int32)
+    slots[3] = -1
+    cache = torch.zeros(blocks, nkv, 2, page, d, device="cuda", dtype=torch.bfloat16)
+    cache_ref = cache.clone()
+    qkv_ref = qkv.clone()
+    ref.rope_kvwrite(qkv_ref, pos, cs, cache_ref, slots, nh, nkv, d, rot)
+    nat.rope_kvwrite(qkv, pos, cs, cache, slots, nh, nkv, d, rot)
+    assert _rel_err(qkv, qkv_ref) < 4e-3
+    assert _rel_err(cache, cache_ref) < 4e-3
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu", "gelu_pytorch_tanh"])
+def test_act_mul(nat, act):
+    x = torch.randn(19, 2 * 1376, device="cuda", dtype=torch.bfloat16)
+    assert _rel_err(nat.act_mul(x, 1376, act), ref.act_mul(x, 1376, act)) < 4e-3
+    assert _rel_err(nat.act_mul(x, 1376, act, gated=False), ref.act_mul(x, 1376, act, gated=False)) < 4e-3
+
+
+def test_embed_argmax_advance(nat):
+    table = torch.randn(1000, 256, device="cuda", dtype=torch.bfloat16)
+    ids = torch.randint(0, 2000, (50,), device="cuda", dtype=torch.int32)
+    got = nat.embed(ids, table, v0=500, v1=1500, mult=2.0)
+    want = ref.embed(ids, table, v0=500, v1=1500, mult=2.0)
+    assert torch.equal(got, want)
+    logits = torch.randn(33, 32000, device="cuda", dtype=torch.bfloat16)
+    i, lp = nat.argmax_logprob(logits)
+    wi, wlp = ref.argmax_logprob(logits)
+    assert torch.equal(i.long(), wi.long())
+    assert torch.allclose(lp, wlp, atol=2e-3)
+    B, page = 9, 32
+    bt = torch.randint(1, 100, (B, 8), device="cuda", dtype=torch.int32)
+    state = [torch.randint(0, 100, (B,), device="cuda", dtype=torch.int32) for _ in range(2)]
+    inp, pos = state
+    ctx = pos + 1
+    ctx[2] = 0
+    slots = torch.zeros(B, device="cuda", dtype=torch.int32)
+    nxt = torch.randint(0, 100, (B,), device="cuda", dtype=torch.int32)
+    a = [t.clone() for t in (inp, pos, ctx, slots)]
+    b = [t.clone() for t in (inp, pos, ctx, slots)]
+    nat.advance_decode(a[0], nxt, a[1], a[2], a[3], bt, page)
+    ref.advance_decode(b[0], nxt, b[1], b[2], b[3], bt, page)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
+def _make_cache(B, max_len, nkv, d, page=32, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    max_blocks = (max_len + page - 1) // page
+    nblocks = B * max_blocks + 1
+    cache = torch.randn(nblocks, nkv, 2, page, d, device="cuda", dtype=torch.bfloat16, generator=g)
+    perm = torch.randperm(nblocks - 1, device="cuda", generator=g)[: B * max_blocks] + 1
+    bt = perm.view(B, max_blocks).to(torch.int32)
+    return cache, bt
+
+
+@pytest.mark.parametrize("nh,nkv,d,window,softcap,nsplit", [(32, 8, 128, 0, 0.0, 1), (32, 8, 128, 100, 0.0, 1),
+                                                             (4, 2, 64, 0, 0.0, 1), (8, 8, 128, 0, 30.0, 1),
+                                                             (32, 8, 128, 0, 0.0, 4), (32, 1, 128, 0, 0.0, 2)])
+def test_attn_decode(nat, nh, nkv, d, window, softcap, nsplit):
+    torch.manual_seed(5)
+    B, max_len = 11, 700
+    cache, bt = _make_cache(B, max_len, nkv, d)
+    ctx = torch.randint(1, max_len, (B,), device="cuda", dtype=torch.int32)
+    ctx[0] = 1
+    ctx[1] = max_len
+    ctx[2] = 0
+    q = torch.randn(B, nh * d, device="cuda", dtype=torch.bfloat16)
+    scale = d ** -0.5
+    got = nat.attn_decode(q, cache, bt, ctx, nh, nkv, d, scale, window, softcap, nsplit)
+    want = ref.attn_decode(q, cache, bt, ctx, nh, nkv, d, scale, window, softcap)
+    assert _rel_err(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("nh,nkv,d,window,cached", [(32, 8, 128, 0, False), (4, 2, 64, 0, True), (8, 2, 128, 70, True)])
+def test_attn_prefill(nat, nh, nkv, d, window, cached):
+    torch.manual_seed(6)
+    q_lens = [5, 64, 130, 257, 1]
+    B = len(q_lens)
+    cache_lens = [0, 3, 64, 100, 31] if cached else [0] * B
+    max_len = max(a + b for a, b in zip(q_lens, cache_lens))
+    cache, bt = _make_cache(B, max_len, nkv, d, seed=1)
+    T = sum(q_lens)
+    q = torch.randn(T, nh * d, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    cl = torch.tensor(cache_lens, device="cuda", dtype=torch.int32)
+    ts, tq = ref.prefill_tiles(q_lens)
+    ts = torch.tensor(ts, device="cuda", dtype=torch.int32)
+    tq = torch.tensor(tq, device="cuda", dtype=torch.int32)
+    scale = d ** -0.5
+    got = nat.attn_prefill(q, cache, bt, cu, cl, ts, tq, nh, nkv, d, scale, window)
+    want = ref.attn_prefill(q, cache, bt, cu, cl, ts, tq, nh, nkv, d, scale, window)
+    assert _rel_err(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("T", [3, 100, 700])
+def test_lora_shrink_expand(nat, T):
+    torch.manual_seed(8)
+    K, parts = 1024, [512, 128, 128]
+    N = sum(parts)
+    ranks = [8, 16, 64, 32]
+    unit_a, unit_b = 0, 3 * K        # per-unit-rank offsets of A_cat and B_cat inside a blob
+    unit_total = 3 * K + N
+    bases, off = [], 0
+    for r in ranks:
+        bases.append(off)
+        off += r * unit_total
+    arena = (torch.randn(off, device="cuda") * 0.05).to(torch.bfloat16)
+    slot_base = torch.tensor(bases + [-1], device="cuda", dtype=torch.int64)
+    slot_rank = torch.tensor(ranks + [0], device="cuda", dtype=torch.int32)
+    # runs of equal slots plus base-model tokens
+    tok_slot = torch.randint(-1, len(ranks), (T,), device="cuda", dtype=torch.int32)
+    if T > 64:
+        tok_slot = tok_slot[torch.arange(T, device="cuda") // 37 % tok_slot.numel()].contiguous()
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    v = torch.zeros(T, 3 * 64, device="cuda", dtype=torch.float32)
+    v_ref = v.clone()
+    nat.lora_shrink(x, tok_slot, arena, slot_base, slot_rank, unit_a, 3, 64, v)
+    ref.lora_shrink(x, tok_slot, arena, slot_base, slot_rank, unit_a, 3, 64, v_ref)
+    torch.cuda.synchronize()
+    assert _rel_err(v, v_ref) < 2e-3
+    y = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
+    y_ref = y.clone()
+    nat.lora_expand(v_ref, tok_slot, arena, slot_base, slot_rank, unit_b, y, parts[0], parts[0] + parts[1])
+    ref.lora_expand(v_ref, tok_slot, arena, slot_base, slot_rank, unit_b, y_ref, parts[0], parts[0] + parts[1])
+    nat.workspace().check_status()
+    assert _rel_err(y, y_ref) < 5e-3
