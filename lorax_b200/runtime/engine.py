@@ -1,0 +1,268 @@
+"""In-process serving engine: continuous heterogeneous batching over one model shard group.
+
+It plays the roles that the reference splits between the router's batching task
+(`router/src/infer.rs:1051-1248`), the adapter scheduler (`router/src/scheduler.rs:283-546`) and the shard's
+`generate_token` loop, for users who embed the library (and for `bench.py`).  The C++ router drives the same
+:class:`ModelRunner` through the gRPC servicer when the full server stack is used.
+
+Scheduling rules kept from the reference: new prefills interrupt decoding only when enough requests wait
+(`waiting_served_ratio`) or the oldest has waited `max_waiting_tokens` decode steps; a prefill step is bounded
+by `max_batch_prefill_tokens`; the running batch by `max_batch_total_tokens` (KV blocks); requests of adapters
+that are not resident wait for the exchange engine; adapters idle while others wait are evicted first.
+The host runs one decode step behind the GPU (results arrive through a pinned ring), and rows that end by
+length are retired without waiting for their last token.
+"""
+
+from __future__ import annotations
+
+import collections
+import time
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config import EngineConfig
+from ..models.decoder import DecoderModel
+from ..sampling.chooser import (FINISH_EOS, FINISH_LENGTH, FINISH_STOP, HeterogeneousNextTokenChooser, NextTokenParams,
+                                StoppingCriteria)
+from .kv_cache import BlockAllocator, KVCache
+from .runner import ModelRunner, PrefillItem
+
+
+@dataclass
+class GenRequest:
+    request_id: int
+    prompt_ids: List[int]
+    max_new_tokens: int = 20
+    adapter_index: int = 0               # 0 = base model
+    params: NextTokenParams = field(default_factory=NextTokenParams)
+    eos_token_ids: frozenset = frozenset()
+    ignore_eos_token: bool = False
+    stop_sequences: List[str] = field(default_factory=list)
+    arrival_time: float = 0.0
+
+
+@dataclass
+class TokenEvent:
+    request_id: int
+    token_id: int
+    logprob: float
+    index: int                           # 0-based index of the generated token
+    finished: bool
+    finish_reason: Optional[int] = None
+    time: float = 0.0
+
+
+@dataclass
+class _Seq:
+    req: GenRequest
+    blocks: List[int]
+    row: int = -1
+    output_ids: List[int] = field(default_factory=list)
+    launched: int = 0                    # tokens whose computation has been launched (incl. the prefill token)
+    finished: bool = False
+    retired: bool = False
+    first_token_time: float = 0.0
+    last_token_time: float = 0.0
+    stopping: Optional[StoppingCriteria] = None
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, cfg: Optional[EngineConfig] = None, num_blocks: Optional[int] = None,
+                 max_batch: int = 256, decode_text: Optional[Callable[[int], str]] = None, use_graphs: Optional[bool] = None):
+        self.model = model
+        self.cfg = cfg or EngineConfig()
+        c = model.config
+        page = self.cfg.block_size
+        if num_blocks is None:
+            num_blocks = self._auto_blocks(page)
+        self.kv = KVCache(c.num_hidden_layers, num_blocks, model.nkv, model.d, model.dtype, model.device, page)
+        self.alloc = BlockAllocator(num_blocks, page, c.sliding_window)
+        self.runner = ModelRunner(model, self.kv, max_batch=max_batch, max_seq_tokens=self.cfg.max_total_tokens,
+                                  max_prefill_tokens=self.cfg.max_batch_prefill_tokens,
+                                  use_graphs=self.cfg.compile if use_graphs is None else use_graphs)
+        self.waiting: Deque[GenRequest] = collections.deque()
+        self.running: Dict[int, _Seq] = {}
+        self.draining: Dict[int, _Seq] = {}
+        self.inflight: Deque[Tuple[int, int, Dict[int, int]]] = collections.deque()   # (ring idx, bucket, row->req snapshot)
+        self.steps_since_prefill = 0
+        self.decode_text = decode_text
+        self.stats = dict(prefill_steps=0, decode_steps=0, prefill_tokens=0, generated_tokens=0)
+        self.finished: Dict[int, _Seq] = {}
+        self.on_adapter_needed: Optional[Callable[[int], bool]] = None     # exchange hook: make adapter resident
+
+    def _auto_blocks(self, page: int) -> int:
+        m, c = self.model, self.model.config
+        per_block = KVCache.bytes_per_block(c.num_hidden_layers, m.nkv, m.d, m.dtype, page)
+        if m.device.type == "cuda":
+            free, _ = torch.cuda.mem_get_info(m.device)
+            budget = int(free * self.cfg.memory_wiggle_room) - (6 << 30)
+            return max(int(budget // per_block), 64)
+        return 512
+
+    # ------------------------------------------------------------------ API
+    def add_request(self, req: GenRequest):
+        if not req.arrival_time:
+            req.arrival_time = time.perf_counter()
+        if len(req.prompt_ids) + req.max_new_tokens > self.cfg.max_total_tokens:
+            raise ValueError("inputs tokens + max_new_tokens must be <= %d" % self.cfg.max_total_tokens)
+        self.waiting.append(req)
+
+    @property
+    def idle(self) -> bool:
+        return not (self.waiting or self.running or self.draining or self.inflight)
+
+    # ------------------------------------------------------------------ scheduling
+    def _adapter_ready(self, adapter_index: int) -> bool:
+        ad = self.model.adapters
+        if adapter_index == 0 or ad is None:
+            return True
+        if ad.is_loaded(adapter_index):
+            return True
+        if self.on_adapter_needed is not None:
+            return bool(self.on_adapter_needed(adapter_index))
+        return False
+
+    def _select_prefill(self) -> List[Tuple[GenRequest, List[int]]]:
+        if not self.waiting:
+            return []
+        free_rows = len(self.runner.state.free_rows)
+        if free_rows == 0:
+            return []
+        n_run = len(self.running)
+        if n_run > 0 and self.steps_since_prefill < self.cfg.max_waiting_tokens:
+            min_size = int(n_run * self.cfg.waiting_served_ratio)
+            # a shrinking batch makes room: admit when the gap to the target batch is worth a prefill step
+            if len(self.waiting) < min(min_size, free_rows):
+                return []
+        picked: List[Tuple[GenRequest, List[int]]] = []
+        budget = self.cfg.max_batch_prefill_tokens
+        skipped: List[GenRequest] = []
+        while self.waiting and len(picked) < free_rows:
+            req = self.waiting[0]
+            n = len(req.prompt_ids)
+            if n > budget:
+                if not picked and n > self.cfg.max_batch_prefill_tokens:
+                    self.waiting.popleft()
+                    raise ValueError(f"prompt of {n} tokens exceeds max_batch_prefill_tokens")
+                break
+            if not self._adapter_ready(req.adapter_index):
+                skipped.append(self.waiting.popleft())
+                continue
+            blocks = self.alloc.allocate(n + req.max_new_tokens + 1)
+            if blocks is None:
+                break
+            self.waiting.popleft()
+            picked.append((req, blocks))
+            budget -= n
+        for r in reversed(skipped):
+            self.waiting.appendleft(r)
+        return picked
+
+    def _finish(self, seq: _Seq, reason: int):
+        seq.finished = True
+        if not seq.retired:
+            self.runner.retire([seq.row])
+            seq.retired = True
+        self.runner.state.drop_row(seq.row)
+        self.alloc.release(seq.blocks)
+        self.running.pop(seq.req.request_id, None)
+        self.draining.pop(seq.req.request_id, None)
+        self.finished[seq.req.request_id] = seq
+
+    def _emit(self, seq: _Seq, token: int, lp: float, now: float, events: List[TokenEvent]):
+        if seq.finished:
+            return
+        idx = len(seq.output_ids)
+        seq.output_ids.append(token)
+        if idx == 0:
+            seq.first_token_time = now
+        seq.last_token_time = now
+        text = self.decode_text(token) if (self.decode_text and seq.stopping.stop_sequences) else ""
+        stop, reason = seq.stopping(token, text)
+        events.append(TokenEvent(seq.req.request_id, token, lp, idx, stop, reason, now))
+        self.stats["generated_tokens"] += 1
+        if stop:
+            self._finish(seq, reason)
+
+    # ------------------------------------------------------------------ one iteration
+    def step(self) -> List[TokenEvent]:
+        events: List[TokenEvent] = []
+        picked = self._select_prefill()
+        if picked:
+            items = [PrefillItem(r.prompt_ids, 0, b, r.adapter_index) for r, b in picked]
+            next_ids, lps, _ = self.runner.prefill(items)
+            ids_h = next_ids.tolist()
+            lps_h = lps.tolist()
+            now = time.perf_counter()
+            rows, firsts, poss, blks, ads = [], [], [], [], []
+            for (req, blocks), tok, lp in zip(picked, ids_h, lps_h):
+                seq = _Seq(req, blocks, stopping=StoppingCriteria(req.max_new_tokens, req.eos_token_ids, list(req.stop_sequences),
+                                                                  req.ignore_eos_token))
+                seq.row = self.runner.state.take_row(req.request_id)
+                seq.launched = 1
+                self.running[req.request_id] = seq
+                self._emit(seq, tok, lp, now, events)
+                if not seq.finished:
+                    rows.append(seq.row); firsts.append(tok); poss.append(len(req.prompt_ids)); blks.append(blocks)
+                    ads.append(req.adapter_index)
+            self.runner.install(rows, firsts, poss, blks, ads)
+            self.stats["prefill_steps"] += 1
+            self.stats["prefill_tokens"] += sum(len(r.prompt_ids) for r, _ in picked)
+            self.steps_since_prefill = 0
+
+        launched = None
+        if self.running:
+            snapshot = {s.row: rid for rid, s in self.running.items() if not s.retired}
+            if snapshot:
+                launched = self.runner.decode()
+            if launched is not None:
+                k, b, _ = launched
+                self.inflight.append((k, b, snapshot))
+                self.stats["decode_steps"] += 1
+                self.steps_since_prefill += 1
+                # rows that reach max_new_tokens with this step need no further steps: retire them now
+                done_rows = []
+                for rid in list(snapshot.values()):
+                    s = self.running.get(rid)
+                    if s is None:
+                        continue
+                    s.launched += 1
+                    if s.launched >= s.req.max_new_tokens and not s.retired:
+                        s.retired = True
+                        done_rows.append(s.row)
+                        self.draining[rid] = self.running.pop(rid)
+                self.runner.retire(done_rows)
+
+        # process results one step behind the GPU (or everything when nothing new was launched)
+        keep = 1 if launched is not None else 0
+        while len(self.inflight) > keep:
+            k, b, snapshot = self.inflight.popleft()
+            ids_p, lps_p = self.runner.wait(k)
+            now = time.perf_counter()
+            ids_h, lps_h = ids_p[:b].tolist(), lps_p[:b].tolist()
+            for row, rid in snapshot.items():
+                seq = self.running.get(rid) or self.draining.get(rid)
+                if seq is None or seq.finished:
+                    continue
+                self._emit(seq, ids_h[row], lps_h[row], now, events)
+        return events
+
+    def run(self, max_steps: Optional[int] = None) -> List[TokenEvent]:
+        out: List[TokenEvent] = []
+        n = 0
+        while not self.idle and (max_steps is None or n < max_steps):
+            out += self.step()
+            n += 1
+        return out
+
+    # ------------------------------------------------------------------ convenience
+    def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 20, adapter_indices: Optional[Sequence[int]] = None,
+                 params: Optional[Sequence[NextTokenParams]] = None, eos_token_ids: frozenset = frozenset()) -> List[List[int]]:
+        base = max(list(self.finished.keys()) + [0]) + 1
+        for i, p in enumerate(prompts):
+            self.add_request(GenRequest(base + i, list(p), max_new_tokens, adapter_indices[i] if adapter_indices else 0,
+                                        params[i] if params else NextTokenParams(), eos_token_ids))
+        self.run()
+        return [self.finished[base + i].output_ids for i in range(len(prompts))]

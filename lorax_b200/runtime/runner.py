@@ -1,0 +1,301 @@
+"""Model runner: turns scheduler decisions into device work.
+
+Design points that differ from the reference runtime (`server/lorax_server/models/flash_causal_lm.py`):
+
+* Decode state is device resident and row-stable.  Every running request owns a row of a few static tensors
+  (input id, position, context length, KV slot, block-table row, adapter slot).  A step needs no host to device
+  traffic unless a request joins or leaves: a tiny kernel advances positions / slots from the block tables
+  (`advance_decode`).  The reference rebuilds index tensors on the host and syncs three `.tolist()` per step
+  (`flash_causal_lm.py:1617-1626, 1813-1816`).
+* The whole decode step (embedding .. lm_head .. greedy argmax .. advance) is one CUDA graph per padded batch
+  size.  Adapter identity and rank are data (slot ids), not graph structure, so one graph serves any adapter
+  mix; the reference needs a graph per (batch, rank) and falls back to eager on mixed ranks
+  (`utils/graph.py:478-498`).
+* Results come back through pinned host buffers with an event, so the host can run one step behind the GPU.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..models.decoder import DecoderModel, StepInputs
+from ..ops import reference
+from .kv_cache import KVCache
+
+GRAPH_BUCKETS = [1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512]
+
+
+@dataclass
+class PrefillItem:
+    """One sequence (or chunk of one) in a prefill step."""
+    token_ids: Sequence[int]        # tokens of this chunk
+    cache_len: int                  # tokens already in the KV cache (prefix hit or earlier chunks)
+    blocks: Sequence[int]           # block table of the sequence
+    adapter_index: int = 0
+    want_logits: bool = True        # False for a non-final chunk
+    all_logprobs: bool = False      # prefill token log-probs requested (decoder_input_details)
+
+
+class DecodeState:
+    def __init__(self, max_batch: int, max_blocks: int, device):
+        i32 = dict(dtype=torch.int32, device=device)
+        self.max_batch, self.max_blocks = max_batch, max_blocks
+        self.input_ids = torch.zeros(max_batch, **i32)
+        self.positions = torch.zeros(max_batch, **i32)
+        self.ctx_lens = torch.zeros(max_batch, **i32)
+        self.slots = torch.full((max_batch,), -1, **i32)
+        self.block_tables = torch.zeros(max_batch, max_blocks, **i32)
+        self.tok_slot = torch.full((max_batch,), -1, **i32)
+        self.next_ids = torch.zeros(max_batch, **i32)
+        self.logprobs = torch.zeros(max_batch, dtype=torch.float32, device=device)
+        self.free_rows = list(range(max_batch - 1, -1, -1))
+        self.live: Dict[int, int] = {}          # row -> request id
+        self.high_water = 0
+
+    def take_row(self, request_id: int) -> int:
+        self.free_rows.sort(reverse=True)
+        r = self.free_rows.pop()
+        self.live[r] = request_id
+        self.high_water = max(self.live) + 1
+        return r
+
+    def drop_row(self, row: int):
+        self.live.pop(row, None)
+        self.free_rows.append(row)
+        self.high_water = (max(self.live) + 1) if self.live else 0
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, kv: KVCache, max_batch: int = 256, max_seq_tokens: int = 4096,
+                 max_prefill_tokens: int = 4096, use_graphs: bool = True):
+        self.model = model
+        self.kv = kv
+        self.device = model.device
+        self.is_cuda = self.device.type == "cuda"
+        self.page = kv.page
+        self.max_blocks = (max_seq_tokens + self.page - 1) // self.page + 1
+        self.max_batch = max_batch
+        self.max_prefill_tokens = max_prefill_tokens
+        self.state = DecodeState(max_batch, self.max_blocks, self.device)
+        self.use_graphs = use_graphs and self.is_cuda
+        self.graphs: Dict[Tuple[int, bool], object] = {}
+        self.graph_pool = None
+        self.graph_out: Dict[Tuple[int, bool], torch.Tensor] = {}
+        self.buckets = [b for b in GRAPH_BUCKETS if b <= max_batch]
+        if self.buckets[-1] != max_batch:
+            self.buckets.append(max_batch)
+        # pinned result ring (two steps in flight at most)
+        self.n_ring = 4
+        pin = dict(pin_memory=True) if self.is_cuda else {}
+        self.ring_ids = [torch.zeros(max_batch, dtype=torch.int32, **pin) for _ in range(self.n_ring)]
+        self.ring_lp = [torch.zeros(max_batch, dtype=torch.float32, **pin) for _ in range(self.n_ring)]
+        self.ring_ev = [torch.cuda.Event() if self.is_cuda else None for _ in range(self.n_ring)]
+        self.ring_pos = 0
+        self.steps = 0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    # ------------------------------------------------------------------ helpers
+    def _to_dev(self, values, dtype=torch.int32) -> torch.Tensor:
+        t = torch.tensor(values, dtype=dtype)
+        if self.is_cuda:
+            t = t.pin_memory().to(self.device, non_blocking=True)
+        self.h2d_bytes += t.numel() * t.element_size()
+        return t
+
+    def _slot_of(self, adapter_index: int) -> int:
+        ad = self.model.adapters
+        if ad is None or adapter_index == 0:
+            return -1
+        return ad.slot_of(adapter_index)
+
+    def _table_row(self, blocks: Sequence[int]) -> List[int]:
+        n = len(blocks)
+        if n >= self.max_blocks:
+            return list(blocks[: self.max_blocks])
+        window = self.model.config.sliding_window
+        if window and n * self.page < self.max_blocks * self.page and n > 0 and n * self.page >= window + self.page:
+            # sliding window: pages are recycled cyclically, so the table repeats
+            return [blocks[i % n] for i in range(self.max_blocks)]
+        return list(blocks) + [0] * (self.max_blocks - n)
+
+    # ------------------------------------------------------------------ prefill
+    def prefill(self, items: Sequence[PrefillItem]):
+        """Run one ragged prefill step.  Returns (next_ids, logprobs, logits) for the rows that wanted logits:
+        device tensors; `logits` is None unless some item asked for sampling on the host."""
+        page = self.page
+        ids: List[int] = []
+        pos: List[int] = []
+        slots: List[int] = []
+        cu = [0]
+        cache_lens, tables, head_idx, tok_slot, head_slot, q_lens = [], [], [], [], [], []
+        any_lora = False
+        for it in items:
+            n = len(it.token_ids)
+            row = self._table_row(it.blocks)
+            slot_id = self._slot_of(it.adapter_index)
+            any_lora |= slot_id >= 0
+            for j, tok in enumerate(it.token_ids):
+                p = it.cache_len + j
+                ids.append(int(tok))
+                pos.append(p)
+                slots.append(row[p // page] * page + p % page)
+            tok_slot += [slot_id] * n
+            base = cu[-1]
+            cu.append(base + n)
+            cache_lens.append(it.cache_len)
+            tables.append(row)
+            q_lens.append(n)
+            if it.want_logits:
+                if it.all_logprobs:
+                    head_idx += list(range(base, base + n))
+                    head_slot += [slot_id] * n
+                else:
+                    head_idx.append(base + n - 1)
+                    head_slot.append(slot_id)
+        T = len(ids)
+        if T > self.max_prefill_tokens:
+            raise ValueError(f"prefill of {T} tokens exceeds max_prefill_tokens={self.max_prefill_tokens}")
+        ts, tq = reference.prefill_tiles(q_lens)
+        # one packed H2D transfer for every int array
+        segs = [ids, pos, slots, cu, cache_lens, ts, tq, head_idx, tok_slot, head_slot]
+        flat = [x for s in segs for x in s] + [x for row in tables for x in row]
+        dev = self._to_dev(flat)
+        views, o = [], 0
+        for s in segs:
+            views.append(dev[o:o + len(s)])
+            o += len(s)
+        bt = dev[o:].view(len(items), self.max_blocks)
+        d_ids, d_pos, d_slots, d_cu, d_cl, d_ts, d_tq, d_head, d_tokslot, d_headslot = views
+        if any_lora and self.model.adapters is not None:
+            self.model.adapters.fence()
+        inp = StepInputs(input_ids=d_ids, positions=d_pos, slots=d_slots, is_prefill=True, block_tables=bt, cu_q=d_cu,
+                         cache_lens=d_cl, tile_seq=d_ts, tile_q0=d_tq, lm_head_indices=d_head if len(head_idx) else None,
+                         tok_slot=d_tokslot if any_lora else None, head_tok_slot=d_headslot if any_lora else None)
+        if not head_idx:
+            inp.lm_head_indices = d_ids[:0]
+        logits = self.model.forward(inp, self.kv.layers)
+        if logits.shape[0] == 0:
+            return None, None, logits
+        next_ids, lps = self.model.ops.argmax_logprob(logits, softcap=self.model.config.final_logit_softcapping or 0.0)
+        return next_ids, lps, logits
+
+    # ------------------------------------------------------------------ decode rows
+    def install(self, rows: Sequence[int], first_tokens: Sequence[int], positions: Sequence[int], blocks: Sequence[Sequence[int]],
+                adapter_indices: Sequence[int]):
+        """Write freshly prefilled sequences into their decode rows (one packed H2D + six scatters)."""
+        if not rows:
+            return
+        page = self.page
+        st = self.state
+        tabs = [self._table_row(b) for b in blocks]
+        slots = [tabs[i][positions[i] // page] * page + positions[i] % page for i in range(len(rows))]
+        ctx = [p + 1 for p in positions]
+        tslot = [self._slot_of(a) for a in adapter_indices]
+        n = len(rows)
+        flat = list(rows) + list(first_tokens) + list(positions) + ctx + slots + tslot + [x for t in tabs for x in t]
+        dev = self._to_dev(flat)
+        r = dev[:n].long()
+        st.input_ids.index_copy_(0, r, dev[n:2 * n])
+        st.positions.index_copy_(0, r, dev[2 * n:3 * n])
+        st.ctx_lens.index_copy_(0, r, dev[3 * n:4 * n])
+        st.slots.index_copy_(0, r, dev[4 * n:5 * n])
+        st.tok_slot.index_copy_(0, r, dev[5 * n:6 * n])
+        st.block_tables.index_copy_(0, r, dev[6 * n:].view(n, self.max_blocks))
+
+    def retire(self, rows: Sequence[int]):
+        """Mark rows as padding: they stop advancing and attention skips them."""
+        if not rows:
+            return
+        r = self._to_dev(list(rows)).long()
+        self.state.ctx_lens.index_fill_(0, r, 0)
+        self.state.slots.index_fill_(0, r, -1)
+        self.state.tok_slot.index_fill_(0, r, -1)
+
+    def rebind_adapter_slots(self, rows: Sequence[int], adapter_indices: Sequence[int]):
+        if rows:
+            r = self._to_dev(list(rows)).long()
+            self.state.tok_slot.index_copy_(0, r, self._to_dev([self._slot_of(a) for a in adapter_indices]))
+
+    # ------------------------------------------------------------------ decode
+    def _bucket(self, n: int) -> int:
+        for b in self.buckets:
+            if b >= n:
+                return b
+        return self.buckets[-1]
+
+    def _decode_body(self, b: int, lora: bool):
+        st = self.state
+        nsplit = 1
+        if self.is_cuda and b * self.model.nkv < 96:
+            nsplit = max(1, min(8, 192 // max(b * self.model.nkv, 1)))
+        inp = StepInputs(input_ids=st.input_ids[:b], positions=st.positions[:b], slots=st.slots[:b], is_prefill=False,
+                         block_tables=st.block_tables[:b], ctx_lens=st.ctx_lens[:b], tok_slot=st.tok_slot[:b] if lora else None,
+                         head_tok_slot=st.tok_slot[:b] if lora else None, attn_nsplit=nsplit)
+        logits = self.model.forward(inp, self.kv.layers)
+        self.model.ops.argmax_logprob(logits, st.next_ids[:b], st.logprobs[:b], softcap=self.model.config.final_logit_softcapping or 0.0)
+        return logits
+
+    def _advance(self, b: int):
+        st = self.state
+        self.model.ops.advance_decode(st.input_ids[:b], st.next_ids[:b], st.positions[:b], st.ctx_lens[:b], st.slots[:b],
+                                      st.block_tables[:b], self.page)
+
+    def capture(self, b: int, lora: bool):
+        key = (b, lora)
+        if key in self.graphs:
+            return
+        # warm up outside capture (lazy cudaFuncSetAttribute calls, workspace allocation)
+        saved = [t.clone() for t in (self.state.input_ids, self.state.positions, self.state.ctx_lens, self.state.slots)]
+        self._decode_body(b, lora)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=self.graph_pool):
+            logits = self._decode_body(b, lora)
+            self._advance(b)
+        if self.graph_pool is None:
+            self.graph_pool = g.pool()
+        for t, s in zip((self.state.input_ids, self.state.positions, self.state.ctx_lens, self.state.slots), saved):
+            t.copy_(s)
+        self.graphs[key] = g
+        self.graph_out[key] = logits
+
+    def decode(self, lora: Optional[bool] = None, need_logits: bool = False):
+        """One decode step over rows [0, high_water).  Returns (ring index, bucket, logits or None); the sampled
+        ids / log-probs land in the pinned ring entry once its event has completed."""
+        st = self.state
+        n = st.high_water
+        if n == 0:
+            return None
+        b = self._bucket(n)
+        ad = self.model.adapters
+        if lora is None:
+            lora = ad is not None and ad.max_rank > 0
+        if lora:
+            ad.fence()
+        logits = None
+        if self.use_graphs:
+            self.capture(b, lora)
+            self.graphs[(b, lora)].replay()
+            logits = self.graph_out[(b, lora)] if need_logits else None
+        else:
+            logits = self._decode_body(b, lora)
+            self._advance(b)
+        k = self.ring_pos
+        self.ring_pos = (k + 1) % self.n_ring
+        self.ring_ids[k][:b].copy_(st.next_ids[:b], non_blocking=True)
+        self.ring_lp[k][:b].copy_(st.logprobs[:b], non_blocking=True)
+        self.d2h_bytes += b * 8
+        if self.is_cuda:
+            self.ring_ev[k].record()
+        self.steps += 1
+        return k, b, logits
+
+    def wait(self, k: int):
+        if self.is_cuda:
+            self.ring_ev[k].synchronize()
+        return self.ring_ids[k], self.ring_lp[k]
