@@ -1,0 +1,300 @@
+#!/usr/bin/env python
+"""Headline benchmark: output tokens/s while serving 100 LoRA adapters on the Mistral-7B architecture.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched with torch.distributed.run)
+    python bench.py --impl reference ...                     (the unmodified reference, if it could be installed)
+
+Workload (synthetic, random-init weights): Mistral-7B, bf16, tensor parallel over N GPUs, 100 random LoRA
+adapters of rank 16 on q,k,v,o,gate,up,down, adapter per request ~ Zipf(1.1), prompts of uniform-random token
+ids with length uniform in [128, 1024], 256 new tokens, greedy.  Requests arrive as a closed loop that keeps
+`--batch` requests in flight (a saturating Poisson stream and a closed loop admit the same way once a backlog
+exists).  A "step" is one iteration of the serving engine: admission + prefill of newly arrived requests when
+the scheduler decides to, then one decode step over the running batch.
+
+Two numbers are reported.  `value` is device-timed with CUDA events over exactly K steps.  `e2e.value` runs
+K more steps through the same public API (`Engine.add_request` / `Engine.step`) timed on the host clock; in
+both windows every step copies the new requests' token ids from pinned host memory to the device and reads the
+sampled tokens back, and the bytes of those copies are counted from the tensors.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, REPO)
+
+
+def reference_arm(args):
+    """The reference needs its Rust router/launcher (no cargo here), generated protobuf stubs (no grpcio-tools),
+    poetry-core to build, and kernels (punica with empty submodules, flash-attn, vLLM) that are fetched over the
+    network at build time; `pip install` of /root/reference fails offline."""
+    ref_pkg = os.path.join(REPO, "baseline", "_ref", "lorax_server")
+    why = ("reference not installable offline: pip install fails (no setup.py/pyproject at the repo root; server/ needs the "
+           "poetry-core backend, protoc-generated stubs, a Rust toolchain for router+launcher and network-fetched CUDA kernels)")
+    if os.path.isdir(ref_pkg):
+        why = "reference python package present but its router/launcher (Rust) and CUDA kernels cannot be built offline"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
+    return 0
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs (read-only)."""
+
+    def __init__(self, index: int, period_s: float = 0.2):
+        super().__init__(daemon=True)
+        self.index, self.period = index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._halt = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception:
+            self.nv = None
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+            getattr(nv, "nvmlClocksEventReasonHwPowerBrakeSlowdown", 0x80): "hw_power_brake",
+        }
+        while not self._halt.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._halt.wait(self.period)
+
+    def stop(self):
+        self._halt.set()
+        self.join(timeout=2)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def zipf_sampler(n: int, s: float, gen):
+    import torch
+    w = torch.tensor([1.0 / (k ** s) for k in range(1, n + 1)], dtype=torch.float64)
+    w /= w.sum()
+    cdf = w.cumsum(0)
+
+    def draw():
+        u = torch.rand(1, generator=gen, dtype=torch.float64)
+        return int(torch.searchsorted(cdf, u).clamp(max=n - 1))
+    return draw
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="mistral-7b", choices=["mistral-7b", "llama3-8b", "llama3-70b", "tiny"])
+    ap.add_argument("--batch", type=int, default=256, help="requests kept in flight")
+    ap.add_argument("--adapters", type=int, default=100)
+    ap.add_argument("--rank", type=int, default=16)
+    ap.add_argument("--min-prompt", type=int, default=128)
+    ap.add_argument("--max-prompt", type=int, default=1024)
+    ap.add_argument("--new-tokens", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: the reported config names the change")
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--baseline-mode", action="store_true", help="NCCL collectives instead of the fused NVLink kernels")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch
+    from lorax_b200 import config as cfgs
+    from lorax_b200.adapters.manager import AdapterManager
+    from lorax_b200.config import EngineConfig
+    from lorax_b200.models.decoder import DecoderModel
+    from lorax_b200.parallel.tp import TensorParallel
+    from lorax_b200.runtime.engine import Engine, GenRequest
+
+    if not torch.cuda.is_available():
+        print(json.dumps({"error": "bench.py needs a CUDA device"}))
+        return 1
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            print(json.dumps({"error": f"--gpus {args.gpus} must be launched with torch.distributed.run --nproc-per-node {args.gpus}"}))
+            return 1
+    tp = TensorParallel.init_from_env()
+    dev = tp.device
+    rank0 = tp.rank == 0
+
+    mc = {"mistral-7b": cfgs.mistral_7b, "llama3-8b": cfgs.llama3_8b, "llama3-70b": cfgs.llama3_70b, "tiny": cfgs.tiny_llama}[args.model]()
+    if args.model == "tiny":
+        mc.torch_dtype = "bfloat16"
+    if args.layers:
+        mc.num_hidden_layers = args.layers
+    max_total = args.max_prompt + args.new_tokens + 32
+    t_setup = time.perf_counter()
+    model = DecoderModel.random_init_on_device(mc, dev, torch.bfloat16, seed=0, tp=tp, max_positions=max_total + 64)
+    if tp.world_size > 1 and not args.baseline_mode:
+        try:
+            from lorax_b200.parallel import fused
+            fused.enable(tp, model)
+        except Exception as e:  # fall back to NCCL, and say so
+            if rank0:
+                print(f"[bench] fused NVLink path unavailable ({e}); using NCCL", file=sys.stderr)
+
+    # ---- adapters: random blobs generated on the device, parked in the pinned host tier, loaded through the exchange path
+    esize = 2
+    from lorax_b200.adapters.lora import BlobLayout, pad_rank
+    layout_units = BlobLayout(model, with_lm_head=False).units
+    rp = pad_rank(args.rank)
+    blob_elems = rp * layout_units
+    arena_bytes = int(blob_elems * esize * (args.adapters + 2) * 1.02) + (64 << 20)
+    mgr = AdapterManager(model, arena_bytes=arena_bytes, host_bytes=int(blob_elems * esize * (args.adapters + 4)))
+    g_dev = torch.Generator(device=dev).manual_seed(1234 + tp.rank)
+    scale = 2.0 * 16 / args.rank        # alpha / r folded into B (alpha = 32)
+    for a in range(args.adapters):
+        blob = torch.randn(blob_elems, generator=g_dev, device=dev, dtype=torch.float32).mul_(0.02).to(torch.bfloat16)
+        if rp != args.rank:
+            pass   # padded rows stay random here; only throughput is measured
+        host = torch.empty(blob_elems, dtype=torch.bfloat16, pin_memory=True)
+        host.copy_(blob)
+        mgr.register_blob(f"adapter-{a}", host, rp)
+        del blob
+    torch.cuda.synchronize(dev)
+    for a in range(args.adapters):
+        assert mgr.load(a + 1, f"adapter-{a}"), "adapter arena too small"
+    mgr.fence()
+    torch.cuda.synchronize(dev)
+
+    ecfg = EngineConfig(max_total_tokens=max_total, max_batch_prefill_tokens=4096, max_input_length=args.max_prompt,
+                        compile=not args.no_graphs)
+    eng = Engine(model, ecfg, max_batch=args.batch)
+
+    gen = torch.Generator().manual_seed(42)          # identical on every rank: ranks schedule in lockstep
+    draw_adapter = zipf_sampler(args.adapters, 1.1, gen) if args.adapters > 0 else (lambda: -1)
+    next_id = [1]
+
+    def new_request(ramp: bool = False):
+        n = int(torch.randint(args.min_prompt, args.max_prompt + 1, (1,), generator=gen))
+        ids = torch.randint(0, mc.vocab_size, (n,), generator=gen).tolist()
+        new = args.new_tokens
+        if ramp:       # requests of the ramp start "mid flight" so that the batch is a steady-state mix of progress
+            new = int(torch.randint(1, args.new_tokens + 1, (1,), generator=gen))
+        r = GenRequest(next_id[0], ids, max_new_tokens=new, adapter_index=draw_adapter() + 1, ignore_eos_token=True)
+        next_id[0] += 1
+        return r
+
+    done_stats = {"ttft": [], "tpot": []}
+
+    def harvest(events):
+        n = 0
+        for ev in events:
+            n += 1
+            if ev.finished:
+                seq = eng.finished.pop(ev.request_id, None)
+                if seq is not None and len(seq.output_ids) > 1 and seq.req.max_new_tokens == args.new_tokens:
+                    done_stats["ttft"].append(seq.first_token_time - seq.req.arrival_time)
+                    done_stats["tpot"].append((seq.last_token_time - seq.first_token_time) / (len(seq.output_ids) - 1))
+                eng.add_request(new_request())
+        return n
+
+    # ---- ramp: fill the batch (not part of warm-up or timing)
+    for _ in range(args.batch):
+        eng.add_request(new_request(ramp=True))
+    ramp_steps = 0
+    while len(eng.waiting) > 0 and ramp_steps < 400:
+        harvest(eng.step())
+        ramp_steps += 1
+    for _ in range(args.warmup):
+        harvest(eng.step())
+    torch.cuda.synchronize(dev)
+    setup_s = time.perf_counter() - t_setup
+
+    def window(n_steps: int, device_timed: bool):
+        runner = eng.runner
+        h0, d0, l0 = runner.h2d_bytes, runner.d2h_bytes, runner.kernel_launches()
+        p0 = dict(eng.stats)
+        tp.barrier()
+        torch.cuda.synchronize(dev)
+        sampler = ClockSampler(dev.index or 0)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record()
+        toks = 0
+        for _ in range(n_steps):
+            toks += harvest(eng.step())
+        e1.record()
+        tp.barrier()
+        torch.cuda.synchronize(dev)
+        t1 = time.perf_counter()
+        clocks = sampler.stop()
+        dev_s = e0.elapsed_time(e1) / 1e3
+        secs = tp.max_scalar(dev_s if device_timed else (t1 - t0))
+        return dict(tokens=toks, seconds=secs, h2d=(runner.h2d_bytes - h0) / n_steps, d2h=(runner.d2h_bytes - d0) / n_steps,
+                    launches=runner.kernel_launches() - l0, clocks=clocks,
+                    prefill_tokens=eng.stats["prefill_tokens"] - p0["prefill_tokens"],
+                    prefill_steps=eng.stats["prefill_steps"] - p0["prefill_steps"],
+                    decode_steps=eng.stats["decode_steps"] - p0["decode_steps"])
+
+    w1 = window(args.steps, device_timed=True)
+    w2 = window(args.steps, device_timed=False)
+    if not rank0:
+        tp.destroy()
+        return 0
+    value = w1["tokens"] / w1["seconds"]
+    e2e = w2["tokens"] / w2["seconds"]
+    med = lambda xs: (statistics.median(xs) if xs else None)
+    out = {
+        "metric": "output tok/s at 100 adapters, Mistral-7B arch, TP1-8; p50 TTFT/TPOT",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": tp.world_size, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(1e3 * w1["seconds"] / args.steps, 3), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random token ids, random-init base and adapter weights)",
+        "impl": "ours",
+        "config": {
+            "model": args.model + (f"-{args.layers}layers-DEBUG" if args.layers else ""), "global_batch": args.batch,
+            "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {args.new_tokens} new",
+            "parallelism": f"tp{tp.world_size}", "adapters": args.adapters, "lora_rank": args.rank,
+            "lora_targets": "q,k,v,o,gate,up,down", "adapter_choice": "zipf(1.1)", "arrivals": "closed loop (saturated)",
+            "l2": "inputs larger than L2: each step streams >14 GB of weights, adapters and KV cache",
+            "cuda_graphs": not args.no_graphs, "collectives": "nccl" if (args.baseline_mode or tp.fused is None) else "fused-nvlink",
+            "prefill_tokens_in_window": w1["prefill_tokens"], "prefill_steps": w1["prefill_steps"], "decode_steps": w1["decode_steps"],
+        },
+        "p50_ttft_ms": round(1e3 * med(done_stats["ttft"]), 2) if done_stats["ttft"] else None,
+        "p50_tpot_ms": round(1e3 * med(done_stats["tpot"]), 3) if done_stats["tpot"] else None,
+        "clocks": {k: w1["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
+        "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": round(w2["h2d"], 1),
+                "d2h_bytes_per_step": round(w2["d2h"], 1), "timing": "host wall clock around Engine.step()",
+                "clocks": {k: w2["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")}},
+        "gpu_launches": int(w1["launches"]),
+        "setup_s": round(setup_s, 1),
+    }
+    print(json.dumps(out))
+    tp.destroy()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

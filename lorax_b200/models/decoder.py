@@ -223,6 +223,45 @@ class DecoderModel:
         return m
 
     @classmethod
+    def random_init_on_device(cls, config: ModelConfig, device, dtype, seed: int = 0, tp: Optional[TensorParallel] = None,
+                              std: float = 0.02, max_positions: Optional[int] = None) -> "DecoderModel":
+        """Random weights generated directly on the device, one shard per rank (benchmarks with 7B-70B shapes:
+        drawing the full tensors on the host as `random_init` does would take minutes).  Ranks use different
+        seeds, so this is a statistically equivalent model per TP degree, not the same model."""
+        m = cls(config, device, dtype, tp, max_positions)
+        c, ws = config, m.tp.world_size
+        gen = torch.Generator(device=m.device).manual_seed(seed * 1000 + m.tp.rank)
+
+        def rnd(*shape, s=std):
+            return (torch.randn(*shape, generator=gen, device=m.device, dtype=torch.float32) * s).to(dtype)
+
+        def ones(n):
+            return (torch.ones(n, device=m.device) - c.norm_weight_offset).to(dtype)
+
+        H = c.hidden_size
+        m.embed = rnd(m.vocab_local if ws > 1 else c.vocab_size, H)
+        if c.learned_positions:
+            m.pos_embed = rnd(c.max_position_embeddings, H)
+        for _ in range(c.num_hidden_layers):
+            lw = LayerWeights(input_norm=ones(H), qkv_w=rnd(m.qkv_size, H), o_w=rnd(H, m.q_size), post_norm=ones(H),
+                              gate_up_w=None, down_w=None)
+            if c.attention_bias:
+                lw.qkv_b = rnd(m.qkv_size)
+            if c.is_moe:
+                E, I = c.num_local_experts, c.intermediate_size
+                e_local = max(E // ws, 1)
+                lw.router_w = rnd(E, H)
+                lw.experts_w13 = rnd(e_local, 2 * I, H)
+                lw.experts_w2 = rnd(e_local, H, I)
+            else:
+                lw.gate_up_w = rnd((2 if m.gated else 1) * m.inter, H)
+                lw.down_w = rnd(H, m.inter)
+            m.layers.append(lw)
+        m.final_norm = ones(H)
+        m.lm_head = m.embed if c.tie_word_embeddings else rnd(m.vocab_local if ws > 1 else c.vocab_size, H)
+        return m
+
+    @classmethod
     def from_weights(cls, config: ModelConfig, weights: AbstractWeights, device, dtype, tp: Optional[TensorParallel] = None,
                      max_positions: Optional[int] = None) -> "DecoderModel":
         from .loading import load_decoder_weights

@@ -98,6 +98,16 @@ class ModelRunner:
         self.steps = 0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self.graph_kernels: Dict[Tuple[int, bool], int] = {}
+        self.replayed_launches = 0
+
+    def kernel_launches(self) -> int:
+        """Kernels of this library launched so far: eager launches plus the kernels inside every graph replay."""
+        eager = 0
+        if self.is_cuda:
+            from ..ops import native
+            eager = native.launch_count
+        return eager + self.replayed_launches
 
     # ------------------------------------------------------------------ helpers
     def _to_dev(self, values, dtype=torch.int32) -> torch.Tensor:
@@ -254,9 +264,13 @@ class ModelRunner:
         self._decode_body(b, lora)
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
+        from ..ops import native
+        before = native.launch_count
         with torch.cuda.graph(g, pool=self.graph_pool):
             logits = self._decode_body(b, lora)
             self._advance(b)
+        self.graph_kernels[key] = native.launch_count - before
+        native.launch_count = before          # captured, not executed
         if self.graph_pool is None:
             self.graph_pool = g.pool()
         for t, s in zip((self.state.input_ids, self.state.positions, self.state.ctx_lens, self.state.slots), saved):
@@ -281,6 +295,7 @@ class ModelRunner:
         if self.use_graphs:
             self.capture(b, lora)
             self.graphs[(b, lora)].replay()
+            self.replayed_launches += self.graph_kernels[(b, lora)]
             logits = self.graph_out[(b, lora)] if need_logits else None
         else:
             logits = self._decode_body(b, lora)
