@@ -23,6 +23,7 @@ namespace lx {
 constexpr int kBM = 128;   // UMMA M (rows of operand A per tile)
 constexpr int kBK = 64;    // K per pipeline stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kGemmThreads = 192;
+constexpr int lx_gemm_max_tiles_const = 8192;
 
 struct GemmParams {
   int a_rows, b_rows, K;
@@ -247,23 +248,23 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         if (lane == 0) mbar_arrive(&tmem_empty[acc]);
       } else {
         // ---- split-K: park the fp32 partial, count arrivals, the last CTA of the tile reduces.
-        float* wsp = p.ws + ((long long)(tile * p.split_k + split) * kBM + row_in_tile) * BN;
+        // Partial layout [split][column][128 rows]: for a fixed column the 32 lanes of a warp touch 32
+        // consecutive floats, so both the parking stores and the reducer's loads are fully coalesced.
+        float* __restrict__ wsp = p.ws + ((long long)(tile * p.split_k + split) * BN) * kBM + row_in_tile;
 #pragma unroll 1
         for (int c = 0; c < ncols; c += CH) {
           if constexpr (CH == 32) {
             uint32_t r[32];
             tmem_ld_32x32b_x32(taddr + c, r);
             tc_wait_ld();
-            uint4* dst = reinterpret_cast<uint4*>(wsp + c);
 #pragma unroll
-            for (int q = 0; q < 8; ++q) dst[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+            for (int q = 0; q < 32; ++q) __stcg(wsp + (long long)(c + q) * kBM, __uint_as_float(r[q]));
           } else {
             uint32_t r[16];
             tmem_ld_32x32b_x16(taddr + c, r);
             tc_wait_ld();
-            uint4* dst = reinterpret_cast<uint4*>(wsp + c);
 #pragma unroll
-            for (int q = 0; q < 4; ++q) dst[q] = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+            for (int q = 0; q < 16; ++q) __stcg(wsp + (long long)(c + q) * kBM, __uint_as_float(r[q]));
           }
         }
         tc_fence_before();
@@ -282,23 +283,30 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           __threadfence();
           if (i < p.a_rows) {
             const float bias_i = (p.bias != nullptr && p.bias_on_a) ? __bfloat162float(p.bias[i]) : 0.f;
-            __nv_bfloat16* orow = p.out + (long long)i * p.ldo_a;
-            const float* base = p.ws + ((long long)(tile * p.split_k) * kBM + row_in_tile) * BN;
+            __nv_bfloat16* __restrict__ orow = p.out + (long long)i * p.ldo_a;
+            const float* __restrict__ base = p.ws + ((long long)(tile * p.split_k) * BN) * kBM + row_in_tile;
+            const long long sstride = (long long)BN * kBM;
+            constexpr int RC = 8;       // columns reduced together: RC * split independent loads in flight
 #pragma unroll 1
-            for (int c = 0; c < ncols; c += 4) {
-              float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-              for (int sp = 0; sp < p.split_k; ++sp) {
-                const float4 t = __ldcg(reinterpret_cast<const float4*>(base + (long long)sp * kBM * BN + c));
-                s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
-              }
-              const float vv[4] = {s.x, s.y, s.z, s.w};
+            for (int c = 0; c < ncols; c += RC) {
+              float acc8[RC];
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
+              for (int q = 0; q < RC; ++q) acc8[q] = 0.f;
+#pragma unroll 4
+              for (int sp = 0; sp < p.split_k; ++sp) {
+                float t[RC];
+#pragma unroll
+                for (int q = 0; q < RC; ++q) t[q] = __ldcg(base + sp * sstride + (long long)(c + q) * kBM);
+#pragma unroll
+                for (int q = 0; q < RC; ++q) acc8[q] += t[q];
+              }
+#pragma unroll
+              for (int q = 0; q < RC; ++q) {
                 const int j = j0 + c + q;
                 if (j < p.b_rows) {
                   float b = bias_i;
                   if (p.bias != nullptr && !p.bias_on_a) b = __bfloat162float(p.bias[j]);
-                  orow[(long long)j * p.ldo_b] = __float2bfloat16(vv[q] * p.out_scale + b);
+                  orow[(long long)j * p.ldo_b] = __float2bfloat16(acc8[q] * p.out_scale + b);
                 }
               }
             }
@@ -370,6 +378,47 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   return e == cudaSuccess ? 0 : -(int)e;
 }
 
+// Pick the token tile (UMMA N) and the K split for the weights-on-M path with a small cost model.
+// A work unit streams (128 + bn) * 2 * K / split bytes into shared memory (the weight tile from HBM, the token
+// tile from L2); units run in waves of one per SM; a split adds the fp32 partial round trip plus the serial
+// reduction by the last CTA.  Few tokens -> split K (partials are tiny); many tokens -> tile the tokens
+// (partials would be large, while re-reading a weight tile from L2 is cheap).
+static void choose_tile_and_split(int T, int N, int K, int num_sms, long long ws_bytes, int force_split, int* bn_out, int* split_out) {
+  const int tiles_a = (N + kBM - 1) / kBM;
+  const int kblocks = (K + kBK - 1) / kBK;
+  const int bn_full = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  if (force_split > 0) {            // tests and the no-allocation entry ask for an exact split on the full token tile
+    int s = force_split > kblocks ? kblocks : force_split;
+    if (s > 1 && ((long long)tiles_a * s * kBM * bn_full * 4 > ws_bytes || tiles_a > lx_gemm_max_tiles_const)) s = 1;
+    *bn_out = bn_full;
+    *split_out = s;
+    return;
+  }
+  const int splits[] = {1, 2, 3, 4, 6, 8, 12, 16};
+  double best = 1e30;
+  int best_bn = bn_full, best_split = 1;
+  for (int bn = bn_full; bn >= 16; bn >>= 1) {
+    const int ttiles = (T + bn - 1) / bn;
+    if (tiles_a * ttiles > lx_gemm_max_tiles_const) continue;
+    for (int s : splits) {
+      if (s > 1) {
+        if (kblocks / s < 2) continue;
+        if ((long long)tiles_a * ttiles * s * kBM * bn * 4 > ws_bytes) continue;
+      }
+      const long long units = (long long)tiles_a * ttiles * s;
+      const double waves = (double)((units + num_sms - 1) / num_sms);
+      const double fill = (double)(kBM + bn) * 2.0 * K / s;
+      const double part = s > 1 ? (double)kBM * bn * 4.0 * 2.5 : 0.0;
+      const double fixed = 48e3;
+      const double tail = s > 1 ? (double)kBM * bn * 4.0 * s : 0.0;
+      const double cost = waves * (fill + part + fixed) + tail;
+      if (cost < best) { best = cost; best_bn = bn; best_split = s; }
+    }
+  }
+  *bn_out = best_bn;
+  *split_out = best_split;
+}
+
 }  // namespace lx
 
 extern "C" {
@@ -402,27 +451,15 @@ int lx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, int 
   int bn;
   if (swap) {
     if (T > 256) return -1001;
-    bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
     p.a_rows = N; p.b_rows = T;
-    p.umma_n = (T + 15) / 16 * 16;
     p.ldo_a = 1; p.ldo_b = ldo;
     p.bias_on_a = 1;
     p.hint_a_first = 1;
+    int split = 1;
+    choose_tile_and_split(T, N, K, num_sms, (ws != nullptr && counters != nullptr) ? ws_bytes : 0, force_split, &bn, &split);
+    p.umma_n = T >= bn ? bn : (T + 15) / 16 * 16;
     if (make_tmap_bf16_kmajor(&ta, w, N, K, ldw, kBM)) return -1002;
     if (make_tmap_bf16_kmajor(&tb, x, T, K, ldx, bn)) return -1003;
-    // split-K so that the grid covers the machine; keep >= 4 k-blocks per split.
-    const int tiles = (N + kBM - 1) / kBM;
-    const int kblocks = (K + kBK - 1) / kBK;
-    int split = 1;
-    if (force_split > 0) split = force_split;
-    else {
-      while (tiles * split < num_sms && kblocks / (split * 2) >= 4 && split < 16) split *= 2;
-    }
-    if (split > kblocks) split = kblocks;
-    if (split > 1) {
-      const long long need = (long long)tiles * split * kBM * bn * 4;
-      if (ws == nullptr || counters == nullptr || need > ws_bytes || tiles > lx_gemm_max_tiles()) split = 1;
-    }
     p.split_k = split;
   } else {
     bn = 256;

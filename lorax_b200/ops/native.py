@@ -272,3 +272,64 @@ def lora_expand(v: torch.Tensor, tok_slot: torch.Tensor, arena: torch.Tensor, sl
     rc = load().lx_lora_expand(_ptr(v), v.stride(0), _ptr(tok_slot), _ptr(arena), _ptr(slot_base), _ptr(slot_rank),
                                slot_rank.shape[0], unit_off, _ptr(y), y.stride(0), T, N, n0, n1, _ptr(ws.status), _stream())
     _check(rc, "lx_lora_expand")
+
+
+# ------------------------------------------------------------------------------------------------ per-op timing
+_TIMED_OPS = ("gemm", "norm_residual", "rope_kvwrite", "act_mul", "embed", "argmax_logprob", "advance_decode", "attn_decode",
+              "attn_prefill", "lora_shrink", "lora_expand")
+_timing_records = None
+_timing_originals = {}
+
+
+def enable_timing():
+    """Bracket every operator call with CUDA events (eager mode only; do not use while capturing a graph).
+    `timing_report()` returns the accumulated device time per (operator, shape)."""
+    global _timing_records
+    if _timing_records is not None:
+        return
+    _timing_records = []
+    g = globals()
+
+    def wrap(name, fn):
+        def timed(*a, **kw):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            out = fn(*a, **kw)
+            e.record()
+            shapes = tuple(tuple(x.shape) for x in a[:2] if isinstance(x, torch.Tensor))
+            _timing_records.append((name, shapes, s, e))
+            return out
+        return timed
+
+    for name in _TIMED_OPS:
+        _timing_originals[name] = g[name]
+        g[name] = wrap(name, g[name])
+
+
+def disable_timing():
+    global _timing_records
+    g = globals()
+    for name, fn in _timing_originals.items():
+        g[name] = fn
+    _timing_originals.clear()
+    _timing_records = None
+
+
+def timing_report(reset: bool = True):
+    """-> list of dicts sorted by total time: op, shapes, calls, total_ms, mean_us."""
+    global _timing_records
+    if _timing_records is None:
+        return []
+    torch.cuda.synchronize()
+    agg = {}
+    for name, shapes, s, e in _timing_records:
+        k = (name, shapes)
+        t = s.elapsed_time(e)
+        c = agg.setdefault(k, [0, 0.0])
+        c[0] += 1
+        c[1] += t
+    if reset:
+        _timing_records = []
+    rows = [dict(op=k[0], shapes=str(k[1]), calls=v[0], total_ms=round(v[1], 4), mean_us=round(1e3 * v[1] / v[0], 2)) for k, v in agg.items()]
+    rows.sort(key=lambda r: -r["total_ms"])
+    return rows
