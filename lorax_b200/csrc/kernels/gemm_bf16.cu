@@ -481,3 +481,142 @@ int lx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, int 
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (declared in lx_noalloc.h).
+//
+// The split-K path above needs scratch: fp32 partial tiles plus one arrival counter per output tile.  The
+// regular entry point takes that scratch from its caller.  Some callers cannot provide any: code that runs
+// inside a stream capture, a real-time or safety-partitioned host that forbids cudaMalloc after start-up, a
+// plugin living in another framework's process whose allocator it must not touch.  For them the same kernel is
+// offered with its scratch in a fixed array that is part of this library's image.
+//
+// Limits, because the array is static: it is kNoAllocPartialBytes + kNoAllocCounters*4 + 16 bytes on EVERY
+// GPU that loads this library, from load until the process exits.  Problems whose split-K partials would not
+// fit are rejected (or, with split_k = 0, run with a smaller split that fits, down to no split at all).
+// All calls share the one array and it keeps what the previous call left: the counters are cleared on the
+// stream before every launch, the partials are fully overwritten before they are read.  Two calls that
+// overlap on the GPU (different streams, or different host threads without ordering) would race on it.
+// ------------------------------------------------------------------------------------------------
+namespace lx {
+
+constexpr long long kNoAllocPartialBytes = 8ll << 20;   // 8 MiB of fp32 partial tiles
+constexpr int kNoAllocCounters = 1024;                  // one per 128-row output tile
+constexpr int kNoAllocMaxDevices = 64;
+
+struct NoAllocScratch {
+  float partials[kNoAllocPartialBytes / 4];
+  int counters[kNoAllocCounters];
+  int status[4];
+};
+
+// In host code this name is only a handle for cudaGetSymbolAddress; it is NOT a device pointer.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[sizeof(NoAllocScratch)];
+
+// Device address of the array, per device, resolved on the first call made while that device is current.
+static NoAllocScratch* g_noalloc_ptr[kNoAllocMaxDevices] = {nullptr};
+
+static int noalloc_scratch_for_current_device(NoAllocScratch** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoAllocMaxDevices) return -2001;
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) return -2002;
+    g_noalloc_ptr[dev] = reinterpret_cast<NoAllocScratch*>(p);
+  }
+  *out = g_noalloc_ptr[dev];
+  return 0;
+}
+
+}  // namespace lx
+
+extern "C" {
+
+long long lx_gemm_bf16_noalloc_scratch_bytes() { return (long long)sizeof(lx::NoAllocScratch); }
+int lx_gemm_bf16_noalloc_max_tokens() { return 256; }
+
+const char* lx_gemm_bf16_noalloc_strerror(int code) {
+  switch (code) {
+    case 0: return "ok";
+    case -2001: return "no current CUDA device (or device ordinal >= 64)";
+    case -2002: return "cudaGetSymbolAddress failed for the static scratch array";
+    case -2003: return "T exceeds the 256-token maximum of the no-allocation entry point";
+    case -2004: return "N needs more than 1024 output tiles (N > 131072): beyond the static counter array";
+    case -2005: return "requested split_k does not fit the 8 MiB static scratch for this N and T";
+    case -2006: return "K, ldx and ldw must be multiples of 8 elements (16-byte TMA alignment)";
+    case -2007: return "clearing the arrival counters failed";
+    default: return "launch or tensor-map error (negative CUDA / driver code)";
+  }
+}
+
+// out[T, N] = x[T, K] @ w[N, K]^T (+ bias[N]), T <= 256, same math and the same kernel as lx_gemm_bf16 in its
+// weights-on-M mode.  split_k: 0 = largest power of two that fits the static scratch and fills the GPU,
+// otherwise the exact split to use (rejected with -2005 when its partials do not fit).
+//
+// The first call made on a device resolves the device address of the static array (cudaGetSymbolAddress) and
+// sets the kernel's shared-memory attribute; make that first call outside any stream capture.  No cudaMalloc,
+// cudaFree or other allocating routine is called, on any call.
+int lx_gemm_bf16_noalloc(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
+                         long long ldw, long long ldo, int split_k, void* stream_) {
+  using namespace lx;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (T <= 0 || N <= 0) return 0;
+  if (T > 256) return -2003;
+  if ((K % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return -2006;
+  NoAllocScratch* sc = nullptr;
+  if (int rc = noalloc_scratch_for_current_device(&sc)) return rc;
+  const int tiles = (N + kBM - 1) / kBM;
+  if (tiles > kNoAllocCounters) return -2004;
+  const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  const int kblocks = (K + kBK - 1) / kBK;
+  const long long per_split = (long long)tiles * kBM * bn * 4;
+  int num_sms = 0, dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev);
+  if (num_sms <= 0) num_sms = 148;
+  int split = 1;
+  if (split_k > 0) {
+    split = split_k > kblocks ? kblocks : split_k;
+    if (split > 1 && per_split * split > kNoAllocPartialBytes) return -2005;
+  } else {
+    while (tiles * split < num_sms && kblocks / (split * 2) >= 4 && split < 16 && per_split * split * 2 <= kNoAllocPartialBytes) split *= 2;
+  }
+  GemmParams p{};
+  p.K = K;
+  p.out = reinterpret_cast<__nv_bfloat16*>(out);
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.ws = sc->partials;
+  p.counters = sc->counters;
+  p.status = sc->status;
+  p.out_scale = 1.f;
+  p.split_k = split;
+  p.a_rows = N; p.b_rows = T;
+  p.umma_n = (T + 15) / 16 * 16;
+  p.ldo_a = 1; p.ldo_b = ldo;
+  p.bias_on_a = 1;
+  p.hint_a_first = 1;
+  CUtensorMap ta, tb;
+  if (make_tmap_bf16_kmajor(&ta, w, N, K, ldw, kBM)) return -1002;
+  if (make_tmap_bf16_kmajor(&tb, x, T, K, ldx, bn)) return -1003;
+  // The array keeps the previous call's contents: counters (and the status words) must start at zero.
+  if (cudaMemsetAsync(sc->counters, 0, sizeof(int) * (kNoAllocCounters + 4), stream) != cudaSuccess) return -2007;
+  switch (bn) {
+    case 16:  return launch_gemm<16, 8>(ta, tb, p, num_sms, stream);
+    case 32:  return launch_gemm<32, 8>(ta, tb, p, num_sms, stream);
+    case 64:  return launch_gemm<64, 8>(ta, tb, p, num_sms, stream);
+    case 128: return launch_gemm<128, 6>(ta, tb, p, num_sms, stream);
+    default:  return launch_gemm<256, 4>(ta, tb, p, num_sms, stream);
+  }
+}
+
+// Copies the two status words of the last launch on the current device to host memory (synchronises the device).
+// 0 in out2[0] means every bounded wait inside the kernel completed.
+int lx_gemm_bf16_noalloc_status(int* out2) {
+  using namespace lx;
+  NoAllocScratch* sc = nullptr;
+  if (int rc = noalloc_scratch_for_current_device(&sc)) return rc;
+  return -(int)cudaMemcpy(out2, sc->status, 2 * sizeof(int), cudaMemcpyDeviceToHost);
+}
+
+}  // extern "C"
