@@ -28,6 +28,17 @@ import torch
 
 from .lora import LM_HEAD, BlobLayout, LoraConfig, ModuleMap, check_architecture, pad_rank
 
+TMAP_GROUPS = ("qkv", "o", "gate_up", "down", LM_HEAD)     # index of a group inside a slot's tensor-map row
+TMAP_BYTES = 128
+
+
+@dataclass
+class LoraTiles:
+    """Tile table of one step: int32 [n, 4] rows (slot, first row, rows, 0) on the model's device."""
+    table: torch.Tensor
+    num_tiles: int
+    max_rows: int
+
 
 class ArenaAllocator:
     """First-fit allocator with coalescing over a 1-D element range (offsets aligned to `align` elements)."""
@@ -149,7 +160,26 @@ class AdapterManager:
         # staging for slot-table updates (pinned so the H2D is async)
         self._stage_base = torch.zeros(1, dtype=torch.int64).pin_memory() if self.is_cuda else None
         self._stage_rank = torch.zeros(1, dtype=torch.int32).pin_memory() if self.is_cuda else None
+        # per-slot TMA descriptors of the A_cat matrices (one per projection group), read by the tensor-core shrink
+        self.groups_per_slot = len(TMAP_GROUPS)
+        self.slot_tmaps = (torch.zeros(max_slots * self.groups_per_slot * TMAP_BYTES, dtype=torch.uint8, device=self.device)
+                           if self.is_cuda else None)
         model.adapters = self
+
+    def _encode_slot_tmaps(self, off: int, rp: int) -> torch.Tensor:
+        """Host-side encoding of the slot's tensor maps {K, R, layers} for every projection group."""
+        from ..ops import native
+        host = torch.zeros(self.groups_per_slot * TMAP_BYTES, dtype=torch.uint8).pin_memory()
+        esize = self.arena.element_size()
+        for gi_idx, gname in enumerate(TMAP_GROUPS):
+            gi = self.layout.groups.get(gname)
+            if gi is None:
+                continue
+            nparts = len(gi.parts)
+            base = self.arena.data_ptr() + (off + rp * self.layout.unit_off(gname, 0, "A")) * esize
+            layers = 1 if gname == LM_HEAD else self.layout.num_layers
+            native.lora_encode_tmap(host[gi_idx * TMAP_BYTES:], base, gi.K, nparts * rp, rp * self.layout.layer_units, layers)
+        return host
 
     # ------------------------------------------------------------------ host tier
     def register(self, key: str, cfg: LoraConfig, mm: ModuleMap) -> HostBlob:
@@ -197,8 +227,11 @@ class AdapterManager:
         slot = self.free_slots.pop()
         ev = None
         if self.is_cuda:
+            tm_host = self._encode_slot_tmaps(off, hb.rank)
+            g = self.groups_per_slot * TMAP_BYTES
             with torch.cuda.stream(self.copy_stream):
                 self.arena[off: off + n].copy_(hb.blob, non_blocking=True)
+                self.slot_tmaps[slot * g:(slot + 1) * g].copy_(tm_host, non_blocking=True)
                 self._stage_base[0] = off
                 self._stage_rank[0] = hb.rank
                 self.slot_base[slot: slot + 1].copy_(self._stage_base, non_blocking=True)
@@ -253,15 +286,30 @@ class AdapterManager:
         return adapter_index in self.resident
 
     # ------------------------------------------------------------------ compute
-    def apply(self, ops, x: torch.Tensor, y: torch.Tensor, tok_slot: torch.Tensor, group: str, layer: int):
-        """y += LoRA_{slot(t)}(x) for the projection group: one shrink and one expand launch."""
+    def apply(self, ops, x: torch.Tensor, y: torch.Tensor, tok_slot: Optional[torch.Tensor], group: str, layer: int,
+              tiles: Optional[LoraTiles] = None):
+        """y += LoRA_{slot(t)}(x) for the projection group: one shrink and one expand launch.
+
+        With a tile table (rows grouped by adapter) the shrink runs on the tensor cores; without one, the
+        per-token kernels are used (rows in any order)."""
         if self.max_rank == 0:
             return
         gi = self.layout.groups.get(group)
         if gi is None:
             return
         nparts = len(gi.parts)
-        v = ops.lora_shrink(x, tok_slot, self.arena, self.slot_base, self.slot_rank, self.layout.unit_off(group, layer, "A"),
-                            nparts, self.max_rank)
         n0, n1 = gi.bounds
-        ops.lora_expand(v, tok_slot, self.arena, self.slot_base, self.slot_rank, self.layout.unit_off(group, layer, "B"), y, n0, n1)
+        offA, offB = self.layout.unit_off(group, layer, "A"), self.layout.unit_off(group, layer, "B")
+        if tiles is not None:
+            if tiles.num_tiles == 0:
+                return
+            if self.is_cuda:
+                v = ops.lora_shrink_tiles(x, tiles.table, tiles.num_tiles, tiles.max_rows, self.slot_tmaps, self.groups_per_slot,
+                                          TMAP_GROUPS.index(group), self.slot_rank, nparts, 0 if group == LM_HEAD else layer, self.max_rank)
+            else:
+                v = ops.lora_shrink_tiles(x, tiles.table, tiles.num_tiles, tiles.max_rows, self.arena, self.slot_base, self.slot_rank,
+                                          offA, nparts, self.max_rank)
+            ops.lora_expand_tiles(v, tiles.table, tiles.num_tiles, tiles.max_rows, self.arena, self.slot_base, self.slot_rank, offB, y, n0, n1)
+            return
+        v = ops.lora_shrink(x, tok_slot, self.arena, self.slot_base, self.slot_rank, offA, nparts, self.max_rank)
+        ops.lora_expand(v, tok_slot, self.arena, self.slot_base, self.slot_rank, offB, y, n0, n1)

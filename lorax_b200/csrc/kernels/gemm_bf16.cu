@@ -383,13 +383,19 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 // tile from L2); units run in waves of one per SM; a split adds the fp32 partial round trip plus the serial
 // reduction by the last CTA.  Few tokens -> split K (partials are tiny); many tokens -> tile the tokens
 // (partials would be large, while re-reading a weight tile from L2 is cheap).
-static void choose_tile_and_split(int T, int N, int K, int num_sms, long long ws_bytes, int force_split, int* bn_out, int* split_out) {
+static void choose_tile_and_split(int T, int N, int K, int num_sms, long long ws_bytes, int force_split, int force_bn, int* bn_out,
+                                  int* split_out) {
   const int tiles_a = (N + kBM - 1) / kBM;
   const int kblocks = (K + kBK - 1) / kBK;
-  const int bn_full = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  int bn_full = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  if (force_bn == 16 || force_bn == 32 || force_bn == 64 || force_bn == 128 || force_bn == 256) {
+    if (force_bn < bn_full) bn_full = force_bn;
+    if (force_split <= 0) force_split = 1;
+  }
   if (force_split > 0) {            // tests and the no-allocation entry ask for an exact split on the full token tile
     int s = force_split > kblocks ? kblocks : force_split;
-    if (s > 1 && ((long long)tiles_a * s * kBM * bn_full * 4 > ws_bytes || tiles_a > lx_gemm_max_tiles_const)) s = 1;
+    const int tt = (T + bn_full - 1) / bn_full;
+    if (s > 1 && ((long long)tiles_a * tt * s * kBM * bn_full * 4 > ws_bytes || tiles_a * tt > lx_gemm_max_tiles_const)) s = 1;
     *bn_out = bn_full;
     *split_out = s;
     return;
@@ -410,7 +416,7 @@ static void choose_tile_and_split(int T, int N, int K, int num_sms, long long ws
       const double fill = (double)(kBM + bn) * 2.0 * K / s;
       const double part = s > 1 ? (double)kBM * bn * 4.0 * 2.5 : 0.0;
       const double fixed = 48e3;
-      const double tail = s > 1 ? (double)kBM * bn * 4.0 * s : 0.0;
+      const double tail = s > 1 ? (double)kBM * bn * 4.0 * s * 4.0 : 0.0;   // serial reduction by the last CTA (fitted to a sweep)
       const double cost = waves * (fill + part + fixed) + tail;
       if (cost < best) { best = cost; best_bn = bn; best_split = s; }
     }
@@ -456,7 +462,7 @@ int lx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, int 
     p.bias_on_a = 1;
     p.hint_a_first = 1;
     int split = 1;
-    choose_tile_and_split(T, N, K, num_sms, (ws != nullptr && counters != nullptr) ? ws_bytes : 0, force_split, &bn, &split);
+    choose_tile_and_split(T, N, K, num_sms, (ws != nullptr && counters != nullptr) ? ws_bytes : 0, force_split & 0xffff, force_split >> 16, &bn, &split);
     p.umma_n = T >= bn ? bn : (T + 15) / 16 * 16;
     if (make_tmap_bf16_kmajor(&ta, w, N, K, ldw, kBM)) return -1002;
     if (make_tmap_bf16_kmajor(&tb, x, T, K, ldx, bn)) return -1003;

@@ -65,6 +65,7 @@ class StepInputs:
     lm_head_indices: Optional[torch.Tensor] = None   # rows that need logits (None = all)
     tok_slot: Optional[torch.Tensor] = None          # [T] adapter slot per token (-1 = base); None = no LoRA this step
     head_tok_slot: Optional[torch.Tensor] = None     # adapter slot per lm_head row
+    lora_tiles: Optional[object] = None              # adapters.manager.LoraTiles: rows grouped by adapter (tensor-core shrink)
     attn_nsplit: int = 1
     num_tokens: Optional[int] = None                 # live rows when the tensors are padded (graphs)
 
@@ -279,8 +280,8 @@ class DecoderModel:
         """Base GEMM plus the multi-adapter LoRA delta for the projection group."""
         y = self.ops.gemm(x, w, bias=b)
         ts = tok_slot if tok_slot is not None else inp.tok_slot
-        if ts is not None and self.adapters is not None:
-            self.adapters.apply(self.ops, x, y, ts, group, layer)
+        if self.adapters is not None and (ts is not None or inp.lora_tiles is not None):
+            self.adapters.apply(self.ops, x, y, ts, group, layer, tiles=inp.lora_tiles)
         return y
 
     def forward(self, inp: StepInputs, kv_cache: List[torch.Tensor]) -> torch.Tensor:

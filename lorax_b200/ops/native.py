@@ -63,6 +63,10 @@ def load() -> ctypes.CDLL:
         "lx_attn_prefill": ([P, L, P, P, I, P, P, P, P, I, P, L, I, I, I, I, F, F, P], I),
         "lx_lora_shrink": ([P, L, P, P, P, P, I, L, I, P, I, I, I, I, P, P], I),
         "lx_lora_expand": ([P, I, P, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
+        "lx_tensormap_bytes": ([], I),
+        "lx_lora_encode_tmap": ([P, P, I, I, L, I], I),
+        "lx_lora_shrink_tc": ([P, L, P, I, I, P, I, I, P, I, I, I, P, I, L, I, I, I, I, P, P], I),
+        "lx_lora_expand_tiled": ([P, I, L, I, P, I, I, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
     }
     for name, (argtypes, restype) in sigs.items():
         fn = getattr(lib, name)
@@ -91,15 +95,19 @@ class Workspace:
     """Device scratch shared by the kernels of one process: split-K partials and counters, split-KV partials,
     the status words written by bounded waits, and the LoRA intermediate."""
 
-    def __init__(self, device: torch.device, max_tokens: int = 8192, max_lora_cols: int = 3 * 128,
-                 attn_splits: int = 16, num_heads: int = 64, head_dim: int = 128):
+    LORA_KSPLIT = 8
+
+    def __init__(self, device: torch.device, max_tokens: int = 8192, max_lora_cols: int = 3 * 64,
+                 attn_splits: int = 8, num_heads: int = 64, head_dim: int = 128):
         lib = load()
         self.device = device
         self.gemm_ws = torch.empty(lib.lx_gemm_ws_bytes(), dtype=torch.uint8, device=device)
         self.gemm_counters = torch.zeros(lib.lx_gemm_max_tiles(), dtype=torch.int32, device=device)
         self.status = torch.zeros(2, dtype=torch.int32, device=device)
-        self.lora_v = torch.zeros(max_tokens, max_lora_cols, dtype=torch.float32, device=device)
-        self.attn_part_tokens = 512
+        # LoRA intermediate: [K-split][token][nparts * rank] fp32 partial sums (split 0 alone for the per-token kernels)
+        self.lora_v3 = torch.zeros(self.LORA_KSPLIT, max_tokens, max_lora_cols, dtype=torch.float32, device=device)
+        self.lora_v = self.lora_v3[0]
+        self.attn_part_tokens = 256
         self.attn_splits = attn_splits
         self.attn_part_o = torch.empty(self.attn_part_tokens * num_heads * attn_splits * head_dim, dtype=torch.float32, device=device)
         self.attn_part_lse = torch.empty(self.attn_part_tokens * num_heads * attn_splits, dtype=torch.float32, device=device)
@@ -274,9 +282,50 @@ def lora_expand(v: torch.Tensor, tok_slot: torch.Tensor, arena: torch.Tensor, sl
     _check(rc, "lx_lora_expand")
 
 
+def lora_encode_tmap(out_host: torch.Tensor, base_ptr: int, K: int, R: int, layer_stride: int, layers: int):
+    """Encode the 3-D tensor map {K, R, layers} of one adapter's A_cat family into 128 bytes of host memory."""
+    rc = load().lx_lora_encode_tmap(out_host.data_ptr(), base_ptr, K, R, layer_stride, layers)
+    if rc != 0:
+        raise NativeError(f"lx_lora_encode_tmap failed with code {rc}")
+
+
+def lora_shrink_tiles(x: torch.Tensor, tiles: torch.Tensor, num_tiles: int, max_tile_rows: int, slot_tmaps: torch.Tensor,
+                      groups_per_slot: int, group: int, slot_rank: torch.Tensor, nparts: int, layer: int, max_rank: int,
+                      v: Optional[torch.Tensor] = None):
+    """Tensor-core shrink over a tile table.  Returns (v3, ksplit): fp32 partial sums [ksplit, rows, cols]; the
+    expand adds the splits in a fixed order.  K is split when the table alone cannot fill the GPU."""
+    T, K = x.shape
+    ws = workspace(x.device)
+    v3 = ws.lora_v3 if v is None else v
+    if v3.dim() == 2:
+        v3 = v3.unsqueeze(0)
+    kblocks = (K + 63) // 64
+    chunks = (nparts * max_rank + 127) // 128
+    ksplit = 1
+    while num_tiles * chunks * ksplit < 2 * ws.num_sms and kblocks // (ksplit * 2) >= 8 and ksplit * 2 <= v3.shape[0]:
+        ksplit *= 2
+    rc = load().lx_lora_shrink_tc(_ptr(x), x.stride(0), _ptr(tiles), num_tiles, max_tile_rows, _ptr(slot_tmaps), groups_per_slot, group,
+                                  _ptr(slot_rank), slot_rank.shape[0], nparts, layer, _ptr(v3), v3.stride(1), v3.stride(0), ksplit,
+                                  T, K, max_rank, _ptr(ws.status), _stream())
+    _check(rc, "lx_lora_shrink_tc")
+    return v3, ksplit
+
+
+def lora_expand_tiles(v, tiles: torch.Tensor, num_tiles: int, max_tile_rows: int, arena: torch.Tensor, slot_base: torch.Tensor,
+                      slot_rank: torch.Tensor, unit_off: int, y: torch.Tensor, n0: int, n1: int):
+    v3, ksplit = v if isinstance(v, tuple) else (v, 1)
+    if v3.dim() == 2:
+        v3 = v3.unsqueeze(0)
+    T, N = y.shape
+    ws = workspace(y.device)
+    rc = load().lx_lora_expand_tiled(_ptr(v3), v3.stride(1), v3.stride(0), ksplit, _ptr(tiles), num_tiles, max_tile_rows, _ptr(arena),
+                                     _ptr(slot_base), _ptr(slot_rank), slot_rank.shape[0], unit_off, _ptr(y), y.stride(0), T, N, n0, n1,
+                                     _ptr(ws.status), _stream())
+    _check(rc, "lx_lora_expand_tiled")
+
 # ------------------------------------------------------------------------------------------------ per-op timing
 _TIMED_OPS = ("gemm", "norm_residual", "rope_kvwrite", "act_mul", "embed", "argmax_logprob", "advance_decode", "attn_decode",
-              "attn_prefill", "lora_shrink", "lora_expand")
+              "attn_prefill", "lora_shrink", "lora_expand", "lora_shrink_tiles", "lora_expand_tiles")
 _timing_records = None
 _timing_originals = {}
 

@@ -252,6 +252,58 @@ def lora_expand(v, tok_slot, arena, slot_base, slot_rank, unit_off, y, n0, n1):
         y[t] = (y[t].float() + delta).to(y.dtype)
 
 
+def lora_shrink_tiles(x, tiles, num_tiles, max_tile_rows, arena, slot_base, slot_rank, unit_off, nparts, max_rank, v=None):
+    """Tile-table form (tiles: int32 [n, 4] = slot, row0, nrows, -).  The CPU oracle reads A_cat straight from the
+    arena; the CUDA kernel reads the same bytes through the per-slot tensor maps."""
+    T, K = x.shape
+    if v is None:
+        v = torch.zeros(T, nparts * max_rank, dtype=torch.float32, device=x.device)
+    for i in range(num_tiles):
+        s, row0, n, _ = (int(q) for q in tiles[i])
+        if s < 0 or n <= 0 or int(slot_base[s]) < 0:
+            continue
+        r = int(slot_rank[s])
+        off = int(slot_base[s]) + r * unit_off
+        A = arena[off: off + nparts * r * K].view(nparts * r, K).float()
+        v[row0:row0 + n, : nparts * r] = x[row0:row0 + n].float() @ A.t()
+    return v
+
+
+def lora_expand_tiles(v, tiles, num_tiles, max_tile_rows, arena, slot_base, slot_rank, unit_off, y, n0, n1):
+    T, N = y.shape
+    bounds = [0, n0, n1, N]
+    for i in range(num_tiles):
+        s, row0, n, _ = (int(q) for q in tiles[i])
+        if s < 0 or n <= 0 or int(slot_base[s]) < 0:
+            continue
+        r = int(slot_rank[s])
+        off = int(slot_base[s]) + r * unit_off
+        B = arena[off: off + N * r].view(N, r).float()
+        delta = torch.zeros(n, N, dtype=torch.float32, device=y.device)
+        for part in range(3):
+            a, b = bounds[part], bounds[part + 1]
+            if b > a:
+                delta[:, a:b] = v[row0:row0 + n, part * r:(part + 1) * r].float() @ B[a:b].t()
+        y[row0:row0 + n] = (y[row0:row0 + n].float() + delta).to(y.dtype)
+
+
+def build_lora_tiles(slots_per_row, max_rows: int):
+    """Host helper: rows with equal adapter slot that are adjacent form a segment; segments are cut into tiles of at
+    most `max_rows` rows.  -> list of (slot, row0, nrows, 0); rows without adapter (slot < 0) get no tile."""
+    tiles = []
+    i, n = 0, len(slots_per_row)
+    while i < n:
+        s = slots_per_row[i]
+        j = i
+        while j < n and slots_per_row[j] == s:
+            j += 1
+        if s >= 0:
+            for a in range(i, j, max_rows):
+                tiles.append((s, a, min(max_rows, j - a), 0))
+        i = j
+    return tiles
+
+
 def rope_cache(rot: int, max_pos: int, theta: float, scaling: Optional[dict] = None, device="cpu") -> torch.Tensor:
     """[max_pos, rot] fp32 table: cos in the first half, sin in the second.
 

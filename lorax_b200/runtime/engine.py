@@ -208,6 +208,10 @@ class Engine:
                     rows.append(seq.row); firsts.append(tok); poss.append(len(req.prompt_ids)); blks.append(blocks)
                     ads.append(req.adapter_index)
             self.runner.install(rows, firsts, poss, blks, ads)
+            mapping = self.runner.resort()
+            for s_ in list(self.running.values()) + list(self.draining.values()):
+                if s_.row in mapping:
+                    s_.row = mapping[s_.row]
             self.stats["prefill_steps"] += 1
             self.stats["prefill_tokens"] += sum(len(r.prompt_ids) for r, _ in picked)
             self.steps_since_prefill = 0

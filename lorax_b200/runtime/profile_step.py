@@ -58,6 +58,7 @@ def main():
     blocks = [[1 + i * blocks_per + j for j in range(blocks_per)] for i in range(a.batch)]
     ads = [int(torch.randint(0, a.adapters + 1, (1,), generator=g)) for _ in range(a.batch)] if a.adapters else [0] * a.batch
     runner.install(rows, [1] * a.batch, [a.ctx] * a.batch, blocks, ads)
+    runner.resort()
     results = {}
     # ---- decode
     for _ in range(2):

@@ -22,6 +22,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
+from ..adapters.manager import LoraTiles
 from ..models.decoder import DecoderModel, StepInputs
 from ..ops import reference
 from .kv_cache import KVCache
@@ -52,6 +53,10 @@ class DecodeState:
         self.tok_slot = torch.full((max_batch,), -1, **i32)
         self.next_ids = torch.zeros(max_batch, **i32)
         self.logprobs = torch.zeros(max_batch, dtype=torch.float32, device=device)
+        # LoRA tile table of the decode batch (rows are kept sorted by adapter slot): [max_batch, 4], unused = slot -1
+        self.lora_tiles = torch.full((max_batch, 4), -1, **i32)
+        self.row_slot: Dict[int, int] = {}      # row -> adapter slot (host mirror)
+        self.num_lora_tiles = 0
         self.free_rows = list(range(max_batch - 1, -1, -1))
         self.live: Dict[int, int] = {}          # row -> request id
         self.high_water = 0
@@ -65,6 +70,7 @@ class DecodeState:
 
     def drop_row(self, row: int):
         self.live.pop(row, None)
+        self.row_slot.pop(row, None)
         self.free_rows.append(row)
         self.high_water = (max(self.live) + 1) if self.live else 0
 
@@ -99,6 +105,7 @@ class ModelRunner:
         self.h2d_bytes = 0
         self.d2h_bytes = 0
         self.graph_kernels: Dict[Tuple[int, bool], int] = {}
+        self.tiles_valid = False
         self.replayed_launches = 0
 
     def kernel_launches(self) -> int:
@@ -183,9 +190,14 @@ class ModelRunner:
         d_ids, d_pos, d_slots, d_cu, d_cl, d_ts, d_tq, d_head, d_tokslot, d_headslot = views
         if any_lora and self.model.adapters is not None:
             self.model.adapters.fence()
+        tiles = None
+        if any_lora:
+            tl = reference.build_lora_tiles(tok_slot, 128)
+            tiles = LoraTiles(self._to_dev([x for t in tl for x in t]).view(-1, 4), len(tl), 128)
         inp = StepInputs(input_ids=d_ids, positions=d_pos, slots=d_slots, is_prefill=True, block_tables=bt, cu_q=d_cu,
                          cache_lens=d_cl, tile_seq=d_ts, tile_q0=d_tq, lm_head_indices=d_head if len(head_idx) else None,
-                         tok_slot=d_tokslot if any_lora else None, head_tok_slot=d_headslot if any_lora else None)
+                         tok_slot=d_tokslot if any_lora else None, head_tok_slot=d_headslot if any_lora else None,
+                         lora_tiles=tiles)
         if not head_idx:
             inp.lm_head_indices = d_ids[:0]
         logits = self.model.forward(inp, self.kv.layers)
@@ -216,6 +228,38 @@ class ModelRunner:
         st.slots.index_copy_(0, r, dev[4 * n:5 * n])
         st.tok_slot.index_copy_(0, r, dev[5 * n:6 * n])
         st.block_tables.index_copy_(0, r, dev[6 * n:].view(n, self.max_blocks))
+        for row, sl in zip(rows, tslot):
+            st.row_slot[row] = sl
+        self.tiles_valid = False        # rows are no longer grouped by adapter until resort() runs
+
+    def resort(self) -> Dict[int, int]:
+        """Compact the live rows to [0, n) ordered by adapter slot, so that rows of one adapter are adjacent and the
+        LoRA kernels can work on (slot, first row, rows) tiles.  Device state is permuted with a handful of gathers;
+        the returned dict maps old row -> new row for the caller's bookkeeping."""
+        st = self.state
+        old_rows = sorted(st.live.keys(), key=lambda r: (st.row_slot.get(r, -1), r))
+        n = len(old_rows)
+        mapping = {old: new for new, old in enumerate(old_rows)}
+        if n and any(o != nw for o, nw in mapping.items()):
+            perm = self._to_dev(old_rows).long()
+            for t in (st.input_ids, st.positions, st.ctx_lens, st.slots, st.tok_slot, st.block_tables):
+                t[:n] = t.index_select(0, perm)
+        hw = st.high_water
+        if hw > n:
+            st.ctx_lens[n:hw] = 0
+            st.slots[n:hw] = -1
+            st.tok_slot[n:hw] = -1
+        st.live = {mapping[o]: rid for o, rid in st.live.items()}
+        st.row_slot = {mapping[o]: sl for o, sl in st.row_slot.items() if o in mapping}
+        st.free_rows = list(range(st.max_batch - 1, n - 1, -1))
+        st.high_water = n
+        # tile table: decode tiles hold at most 32 rows
+        tl = reference.build_lora_tiles([st.row_slot.get(r, -1) for r in range(n)], 32)
+        st.num_lora_tiles = len(tl)
+        flat = [x for t in tl for x in t] + [-1, 0, 0, 0] * (st.max_batch - len(tl))
+        st.lora_tiles.copy_(self._to_dev(flat).view(-1, 4))
+        self.tiles_valid = True
+        return mapping
 
     def retire(self, rows: Sequence[int]):
         """Mark rows as padding: they stop advancing and attention skips them."""
@@ -243,9 +287,11 @@ class ModelRunner:
         nsplit = 1
         if self.is_cuda and b * self.model.nkv < 96:
             nsplit = max(1, min(8, 192 // max(b * self.model.nkv, 1)))
+        # the table always has max_batch rows; a graph launches one CTA per possible tile of the bucket (unused: slot -1)
+        tiles = LoraTiles(st.lora_tiles, b, 32) if (lora and self.tiles_valid) else None
         inp = StepInputs(input_ids=st.input_ids[:b], positions=st.positions[:b], slots=st.slots[:b], is_prefill=False,
                          block_tables=st.block_tables[:b], ctx_lens=st.ctx_lens[:b], tok_slot=st.tok_slot[:b] if lora else None,
-                         head_tok_slot=st.tok_slot[:b] if lora else None, attn_nsplit=nsplit)
+                         head_tok_slot=st.tok_slot[:b] if lora else None, attn_nsplit=nsplit, lora_tiles=tiles)
         logits = self.model.forward(inp, self.kv.layers)
         self.model.ops.argmax_logprob(logits, st.next_ids[:b], st.logprobs[:b], softcap=self.model.config.final_logit_softcapping or 0.0)
         return logits
@@ -256,7 +302,7 @@ class ModelRunner:
                                       st.block_tables[:b], self.page)
 
     def capture(self, b: int, lora: bool):
-        key = (b, lora)
+        key = (b, lora, self.tiles_valid)
         if key in self.graphs:
             return
         # warm up outside capture (lazy cudaFuncSetAttribute calls, workspace allocation)
@@ -293,10 +339,11 @@ class ModelRunner:
             ad.fence()
         logits = None
         if self.use_graphs:
+            key = (b, lora, self.tiles_valid)
             self.capture(b, lora)
-            self.graphs[(b, lora)].replay()
-            self.replayed_launches += self.graph_kernels[(b, lora)]
-            logits = self.graph_out[(b, lora)] if need_logits else None
+            self.graphs[key].replay()
+            self.replayed_launches += self.graph_kernels[key]
+            logits = self.graph_out[key] if need_logits else None
         else:
             logits = self._decode_body(b, lora)
             self._advance(b)

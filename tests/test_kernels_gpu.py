@@ -227,3 +227,58 @@ def test_lora_shrink_expand(nat, T):
     ref.lora_expand(v_ref, tok_slot, arena, slot_base, slot_rank, unit_b, y_ref, parts[0], parts[0] + parts[1])
     nat.workspace().check_status()
     assert _rel_err(y, y_ref) < 5e-3
+
+
+@pytest.mark.parametrize("T,max_rows", [(40, 32), (300, 32), (700, 128)])
+def test_lora_tiled_tensor_core(nat, T, max_rows):
+    """Tile-table LoRA: tcgen05 shrink through per-slot tensor maps + tiled expand, against the PyTorch loop."""
+    torch.manual_seed(9)
+    K, parts, L = 1024, [512, 128, 128], 3
+    N = sum(parts)
+    ranks = [8, 16, 64, 32]
+    layer_units = 3 * K + N                    # A_cat (3 parts) then B_cat, per unit rank
+    bases, off = [], 0
+    for r in ranks:
+        bases.append(off)
+        off += r * layer_units * L
+        off = (off + 63) // 64 * 64
+    arena = (torch.randn(off, device="cuda") * 0.05).to(torch.bfloat16)
+    slot_base = torch.tensor(bases, device="cuda", dtype=torch.int64)
+    slot_rank = torch.tensor(ranks, device="cuda", dtype=torch.int32)
+    G = 5
+    tm_host = torch.zeros(len(ranks) * G * 128, dtype=torch.uint8).pin_memory()
+    for s, r in enumerate(ranks):
+        nat.lora_encode_tmap(tm_host[(s * G + 0) * 128:], arena.data_ptr() + bases[s] * 2, K, 3 * r, r * layer_units, L)
+    tmaps = tm_host.cuda()
+    # rows grouped by slot, with base-model rows in between
+    seg = [(-1, 3), (0, 5), (2, T // 3), (1, 1), (3, T // 4)]
+    rows = []
+    for sl, n in seg:
+        rows += [sl] * n
+    rows = (rows + [1] * T)[:T]
+    tl = ref.build_lora_tiles(rows, max_rows)
+    tiles = torch.tensor(tl, device="cuda", dtype=torch.int32).view(-1, 4)
+    pad = torch.full((7, 4), -1, device="cuda", dtype=torch.int32)
+    tiles_padded = torch.cat([tiles, pad])
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    layer = 2
+    offA = layer * layer_units
+    offB = layer * layer_units + 3 * K
+    nat.workspace().lora_v3.zero_()      # columns past a slot's rank are never written; other tests leave values there
+    v3, ksplit = nat.lora_shrink_tiles(x, tiles_padded, tiles_padded.shape[0], max_rows, tmaps, G, 0, slot_rank, 3, layer, 64)
+    torch.cuda.synchronize()
+    nat.workspace().check_status()
+    v = v3[:ksplit, :T].sum(0)
+    v_ref = torch.zeros_like(v)
+    ref.lora_shrink_tiles(x, tiles.cpu(), len(tl), max_rows, arena, slot_base, slot_rank, offA, 3, 64, v_ref)
+    live = torch.tensor([s >= 0 for s in rows], device="cuda")
+    assert _rel_err(v[live], v_ref[live]) < 4e-3
+    y = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
+    y_ref = y.clone()
+    nat.lora_expand_tiles((v3, ksplit), tiles_padded, tiles_padded.shape[0], max_rows, arena, slot_base, slot_rank, offB, y, parts[0], parts[0] + parts[1])
+    ref.lora_expand_tiles(v_ref, tiles.cpu(), len(tl), max_rows, arena, slot_base, slot_rank, offB, y_ref, parts[0], parts[0] + parts[1])
+    nat.workspace().check_status()
+    assert _rel_err(y, y_ref) < 5e-3
+    # rows without a tile are untouched
+    untouched = [i for i, s in enumerate(rows) if s < 0]
+    assert torch.equal(y[untouched], y_ref[untouched])
