@@ -108,6 +108,18 @@ def zipf_sampler(n: int, s: float, gen):
     return draw
 
 
+def _finish(tp):
+    """Leave without tearing the NCCL communicator down: destroying a process group whose collectives were captured
+    in CUDA graphs can block forever at interpreter exit."""
+    try:
+        tp.barrier()
+    except Exception:
+        pass
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -262,8 +274,7 @@ def main():
     w1 = window(args.steps, device_timed=True)
     w2 = window(args.steps, device_timed=False)
     if not rank0:
-        tp.destroy()
-        return 0
+        _finish(tp)
     value = w1["tokens"] / w1["seconds"]
     e2e = w2["tokens"] / w2["seconds"]
     med = lambda xs: (statistics.median(xs) if xs else None)
@@ -292,8 +303,7 @@ def main():
         "setup_s": round(setup_s, 1),
     }
     print(json.dumps(out))
-    tp.destroy()
-    return 0
+    _finish(tp)
 
 
 if __name__ == "__main__":

@@ -32,7 +32,7 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr",
 ]
-CXX_FLAGS = ["-O2", "-g", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter", "-pthread"]
+CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter", "-pthread"]
 
 
 def _nvcc() -> str:
@@ -94,9 +94,12 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
 
 def build_host(force: bool = False, verbose: bool = False):
     sources = sorted(HOST_DIR.glob("*.cpp"))
-    headers = sorted(HOST_DIR.glob("*.h")) + sorted(HOST_DIR.glob("*.hpp"))
     if not sources:
         return None
+    # the protobuf codec of the wire contract is generated from proto/generate.proto
+    from lorax_b200.server import protogen
+    protogen.main([str(HOST_DIR / "pb_gen.hpp")])
+    headers = sorted(HOST_DIR.glob("*.h")) + sorted(HOST_DIR.glob("*.hpp"))
     BUILD_DIR.mkdir(exist_ok=True)
     BIN_DIR.mkdir(exist_ok=True)
     stamp = BUILD_DIR / "host.sha256"
@@ -116,7 +119,9 @@ def build_host(force: bool = False, verbose: bool = False):
     with cf.ThreadPoolExecutor(max_workers=8) as ex:
         objs = dict(zip([s.name for s in sources], ex.map(compile_one, sources)))
     lib_objs = [str(objs[s.name]) for s in lib_srcs]
-    _run([cxx, "-shared", "-o", str(HOST_SO), *lib_objs, "-pthread"], verbose)
+    # -Bsymbolic: the library is loaded into Python processes next to other C++ libraries (torch); its own
+    # definitions must win over same-named vague-linkage symbols already in the process.
+    _run([cxx, "-shared", "-o", str(HOST_SO), *lib_objs, "-pthread", "-Wl,-Bsymbolic"], verbose)
     for main_src, exe in mains.items():
         if main_src in objs:
             _run([cxx, "-o", str(BIN_DIR / exe), str(objs[main_src]), *lib_objs, "-pthread"], verbose)

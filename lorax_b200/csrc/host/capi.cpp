@@ -1,0 +1,312 @@
+// C ABI over the router's data structures, for the Python bindings and the tests (ctypes):
+// block allocator / radix trie, adapter queues, JSON, and an in-process Infer driven by a fake shard, which is
+// how the scheduler and the batching loop are tested without a GPU or sockets (the reference left those tests
+// commented out: router/src/loader.rs:345-564).
+#include <cstring>
+
+#include "infer.hpp"
+#include "json.hpp"
+
+using namespace lx;
+
+namespace {
+
+thread_local std::string g_ret;
+const char* ret(const std::string& s) { g_ret = s; return g_ret.c_str(); }
+
+// A shard that "generates" deterministic tokens: token k of request id r is (r * 1000 + k) % 50000.  Adapter ids
+// containing "missing" fail to download; ids containing "slow" take 50 ms to load.
+class FakeShard : public ShardClient {
+ public:
+  struct Live { uint32_t max_new; uint32_t produced; uint64_t id; };
+  std::mutex mu;
+  std::map<uint64_t, std::vector<Live>> batches;
+  std::vector<std::string> log;                       // method trace
+  std::atomic<int> fail_decode_after{-1};
+  int decodes = 0;
+  uint32_t block_size = 16;
+  std::set<uint32_t> loaded;
+
+  std::string call(uint32_t method, const std::string& payload) override {
+    std::lock_guard<std::mutex> g(mu);
+    switch (method) {
+      case gen::M_Info: {
+        gen::InfoResponse r;
+        r.requires_padding = false; r.dtype = "bfloat16"; r.device_type = "cuda"; r.block_size = block_size;
+        r.supports_generation = true; r.requires_block_allocator = true;
+        return r.serialize();
+      }
+      case gen::M_Health: return gen::HealthResponse{}.serialize();
+      case gen::M_ClearCache: {
+        gen::ClearCacheRequest q; q.parse(payload);
+        if (q.id) batches.erase(*q.id); else batches.clear();
+        log.push_back("clear");
+        return gen::ClearCacheResponse{}.serialize();
+      }
+      case gen::M_Warmup: { gen::WarmupResponse r; r.max_supported_total_tokens = 100000; return r.serialize(); }
+      case gen::M_Prefill: {
+        gen::PrefillRequest q; q.parse(payload);
+        gen::PrefillResponse resp;
+        std::vector<Live> live;
+        std::string l = "prefill";
+        for (auto& r : q.batch->requests) {
+          l += " " + std::to_string(r.id) + "@" + std::to_string(r.adapter_index);
+          if (r.adapter_index != 0 && !loaded.count(r.adapter_index)) throw ShardError("adapter not loaded");
+          Live lv{r.stopping_parameters->max_new_tokens, 1, r.id};
+          resp.generations.push_back(make_gen(lv));
+          if (lv.produced < lv.max_new) live.push_back(lv);
+        }
+        log.push_back(l);
+        if (!live.empty()) {
+          batches[q.batch->id] = live;
+          resp.batch = cached(q.batch->id, live);
+        }
+        return resp.serialize();
+      }
+      case gen::M_Decode: {
+        if (fail_decode_after >= 0 && decodes++ >= fail_decode_after) throw ShardError("injected decode failure");
+        gen::DecodeRequest q; q.parse(payload);
+        std::vector<Live> merged;
+        for (auto& b : q.batches) {
+          auto it = batches.find(b.id);
+          if (it == batches.end()) throw ShardError("batch not in cache");
+          for (auto& lv : it->second) merged.push_back(lv);
+          batches.erase(it);
+        }
+        gen::DecodeResponse resp;
+        std::vector<Live> live;
+        for (auto& lv : merged) {
+          lv.produced++;
+          resp.generations.push_back(make_gen(lv));
+          if (lv.produced < lv.max_new) live.push_back(lv);
+        }
+        uint64_t id = q.batches.front().id;
+        log.push_back("decode " + std::to_string(merged.size()));
+        if (!live.empty()) { batches[id] = live; resp.batch = cached(id, live); }
+        return resp.serialize();
+      }
+      case gen::M_FilterBatch: {
+        gen::FilterBatchRequest q; q.parse(payload);
+        auto& v = batches[q.batch_id];
+        std::vector<Live> keep;
+        for (auto& lv : v) if (std::find(q.request_ids.begin(), q.request_ids.end(), lv.id) != q.request_ids.end()) keep.push_back(lv);
+        v = keep;
+        gen::FilterBatchResponse resp;
+        resp.batch = cached(q.batch_id, keep);
+        return resp.serialize();
+      }
+      case gen::M_DownloadAdapter: {
+        gen::DownloadAdapterRequest q; q.parse(payload);
+        const std::string id = q.adapter_parameters->adapter_ids.empty() ? "" : q.adapter_parameters->adapter_ids[0];
+        if (id.find("missing") != std::string::npos) throw ShardError("adapter " + id + " not found");
+        gen::DownloadAdapterResponse r; r.downloaded = true; r.memory_fraction = 0.3f;
+        log.push_back("download " + id);
+        return r.serialize();
+      }
+      case gen::M_LoadAdapter: {
+        gen::LoadAdapterRequest q; q.parse(payload);
+        loaded.insert(q.adapter_index);
+        log.push_back("load " + std::to_string(q.adapter_index));
+        gen::LoadAdapterResponse r; r.loaded = true; return r.serialize();
+      }
+      case gen::M_OffloadAdapter: {
+        gen::OffloadAdapterRequest q; q.parse(payload);
+        loaded.erase(q.adapter_index);
+        log.push_back("offload " + std::to_string(q.adapter_index));
+        gen::OffloadAdapterResponse r; r.offloaded = true; return r.serialize();
+      }
+      case gen::M_Tokenize: {
+        std::vector<uint32_t> ids;
+        std::string wd;
+        for (size_t i = 1; i <= payload.size(); ++i) {
+          if (i == payload.size() || payload[i] == ' ' || payload[i] == '\n' || payload[i] == '\t') {
+            if (!wd.empty()) ids.push_back((uint32_t)(std::hash<std::string>{}(wd) % 50000));
+            wd.clear();
+          } else {
+            wd += payload[i];
+          }
+        }
+        return std::string((const char*)ids.data(), ids.size() * 4);
+      }
+      default: throw ShardError("method not implemented by the fake shard");
+    }
+  }
+
+ private:
+  static gen::Generation make_gen(const Live& lv) {
+    gen::Generation g;
+    g.request_id = lv.id;
+    g.next_tokens.emplace();
+    uint32_t tok = (uint32_t)((lv.id * 1000 + lv.produced) % 50000);
+    g.next_tokens->ids = {tok};
+    g.next_tokens->logprobs = {-0.5f};
+    g.next_tokens->texts = {" t" + std::to_string(tok)};
+    g.next_tokens->is_special = {false};
+    if (lv.produced >= lv.max_new) {
+      g.generated_text.emplace();
+      g.generated_text->text = "done-" + std::to_string(lv.id);
+      g.generated_text->generated_tokens = lv.produced;
+      g.generated_text->finish_reason = gen::FinishReason_FINISH_REASON_LENGTH;
+    }
+    return g;
+  }
+  static gen::CachedBatch cached(uint64_t id, const std::vector<Live>& live) {
+    gen::CachedBatch b;
+    b.id = id;
+    for (auto& lv : live) { b.request_ids.push_back(lv.id); b.max_tokens += lv.max_new; }
+    b.size = (uint32_t)live.size();
+    return b;
+  }
+};
+
+}  // namespace
+
+extern "C" {
+
+// ---------------------------------------------------------------- allocators
+void* lx_alloc_new(uint32_t num_blocks, uint32_t block_size, int window, int prefix_caching) {
+  return make_allocator(num_blocks, block_size, window > 0 ? std::optional<uint32_t>((uint32_t)window) : std::nullopt, prefix_caching != 0).release();
+}
+void lx_alloc_delete(void* a) { delete static_cast<Allocator*>(a); }
+uint64_t lx_alloc_free_blocks(void* a) { return static_cast<Allocator*>(a)->free_blocks(); }
+// Returns a handle (BlockAllocation*) or null.  tokens_ptr may be null (no prefix lookup).
+void* lx_alloc_allocate(void* a, uint32_t adapter, uint32_t tokens, const uint32_t* prompt, uint32_t prompt_len) {
+  std::vector<uint32_t> p;
+  if (prompt) p.assign(prompt, prompt + prompt_len);
+  auto r = static_cast<Allocator*>(a)->allocate(adapter, tokens, prompt ? &p : nullptr);
+  if (!r) return nullptr;
+  return new BlockAllocation(std::move(*r));
+}
+uint32_t lx_allocation_num_blocks(void* h) { return (uint32_t) static_cast<BlockAllocation*>(h)->blocks.size(); }
+uint32_t lx_allocation_prefix_len(void* h) { return static_cast<BlockAllocation*>(h)->prefix_len; }
+uint32_t lx_allocation_num_slots(void* h) { return (uint32_t) static_cast<BlockAllocation*>(h)->slots.size(); }
+void lx_allocation_blocks(void* h, uint32_t* out) { auto& b = static_cast<BlockAllocation*>(h)->blocks; std::memcpy(out, b.data(), b.size() * 4); }
+void lx_allocation_slots(void* h, uint32_t* out) { auto& b = static_cast<BlockAllocation*>(h)->slots; std::memcpy(out, b.data(), b.size() * 4); }
+void lx_alloc_free(void* a, void* h, uint32_t adapter, const uint32_t* all_tokens, uint32_t n) {
+  std::vector<uint32_t> t;
+  if (all_tokens) t.assign(all_tokens, all_tokens + n);
+  static_cast<Allocator*>(a)->free(*static_cast<BlockAllocation*>(h), adapter, all_tokens ? &t : nullptr);
+  delete static_cast<BlockAllocation*>(h);
+}
+
+// ---------------------------------------------------------------- JSON round trip (parser conformance tests)
+const char* lx_json_roundtrip(const char* s) {
+  json::Value v;
+  std::string err;
+  if (!json::parse(s, v, &err)) return ret("ERROR: " + err);
+  return ret(v.dump());
+}
+
+// ---------------------------------------------------------------- adapter queues
+// Script-driven: ops is a JSON array of [op, args...]; returns a JSON trace.  Ops:
+//   ["append", adapter_index]  ["downloaded", idx, cost]  ["ready", idx]  ["update", [in_use...], now_s]  ["next", now_s]
+const char* lx_queues_script(int max_active, double cycle_s, const char* ops_json) {
+  json::Value ops;
+  if (!json::parse(ops_json, ops)) return ret("ERROR: bad script");
+  AdapterQueues q((size_t)max_active, cycle_s, 1.0f);
+  json::Value out = json::Value::array();
+  auto t0 = Clock::now();
+  uint64_t next_id = 1;
+  for (auto& op : ops.items()) {
+    const std::string name = op.items()[0].as_string();
+    auto at = [&](double s) { return t0 + std::chrono::microseconds((long long)(s * 1e6)); };
+    if (name == "append") {
+      auto e = std::make_shared<Entry>();
+      e->id = next_id++;
+      e->request.adapter.index = (uint32_t)op.items()[1].as_int();
+      e->request.adapter.ids = {"a" + std::to_string(e->request.adapter.index)};
+      e->queue_time = at(op.items().size() > 2 ? op.items()[2].as_double() : 0.0);
+      e->sink = std::make_shared<ResponseSink>();
+      out.push(json::Value(q.append(e)));
+    } else if (name == "downloaded") {
+      q.set_downloaded((uint32_t)op.items()[1].as_int(), (float)op.items()[2].as_double());
+      out.push(json::Value());
+    } else if (name == "ready") {
+      q.set_ready((uint32_t)op.items()[1].as_int());
+      out.push(json::Value());
+    } else if (name == "update") {
+      std::set<uint32_t> in_use;
+      for (auto& x : op.items()[1].items()) in_use.insert((uint32_t)x.as_int());
+      auto up = q.update_adapters(in_use, at(op.items()[2].as_double()));
+      json::Value r = json::Value::object();
+      json::Value l = json::Value::array(), o = json::Value::array();
+      for (auto& a : up.load) l.push(a.index);
+      for (auto& a : up.offload) o.push(a.index);
+      r.set("load", l);
+      r.set("offload", o);
+      r.set("budget", q.budget_remaining());
+      out.push(r);
+    } else if (name == "next") {
+      auto e = q.next_entry(at(op.items()[1].as_double()));
+      out.push(e ? json::Value((unsigned long long)e->id) : json::Value());
+    }
+  }
+  return ret(out.dump());
+}
+
+// ---------------------------------------------------------------- Infer against a fake shard
+// requests_json: [{"inputs": "...", "adapter_id": "...", "max_new_tokens": n}, ...] submitted concurrently.
+// Returns {"results": [{"ok":bool,"text":..,"tokens":n,"error":..}], "log": [...shard trace...]}.
+const char* lx_infer_fake_run(const char* requests_json, int max_active_adapters, int fail_decode_after, uint32_t num_blocks,
+                              int prefix_caching) {
+  json::Value reqs;
+  if (!json::parse(requests_json, reqs)) return ret("ERROR: bad requests");
+  auto fake = std::make_shared<FakeShard>();
+  fake->fail_decode_after = fail_decode_after;
+  auto client = std::make_shared<ShardedClient>(std::vector<std::shared_ptr<ShardClient>>{fake});
+  RouterConfig cfg;
+  cfg.max_input_length = 512;
+  cfg.max_total_tokens = 1024;
+  cfg.max_batch_prefill_tokens = 1024;
+  cfg.max_batch_total_tokens = 100000;
+  cfg.max_active_adapters = (size_t)max_active_adapters;
+  cfg.adapter_cycle_time_s = 0.05;
+  cfg.prefix_caching = prefix_caching != 0;
+  cfg.waiting_served_ratio = 0.3f;
+  Metrics metrics;
+  json::Value results = json::Value::array();
+  {
+    Infer infer(client, cfg, client->info(), num_blocks, &metrics);
+    infer.start();
+    std::vector<std::future<json::Value>> futs;
+    for (auto& r : reqs.items()) {
+      futs.push_back(std::async(std::launch::async, [&infer, r] {
+        json::Value out = json::Value::object();
+        try {
+          GenerateParams p;
+          if (r["adapter_id"].is_string()) p.adapter_id = r["adapter_id"].as_string();
+          p.max_new_tokens = (uint32_t)r["max_new_tokens"].as_int(4);
+          if (r["temperature"].is_number()) p.temperature = (float)r["temperature"].as_double();
+          if (r["top_p"].is_number()) p.top_p = (float)r["top_p"].as_double();
+          auto sink = infer.generate_stream(r["inputs"].as_string(), p);
+          int tokens = 0;
+          while (true) {
+            StreamEvent ev;
+            if (!sink->pop(ev, 10000)) { out.set("ok", false); out.set("error", "timeout"); break; }
+            if (ev.kind == StreamEvent::Token) { ++tokens; continue; }
+            if (ev.kind == StreamEvent::Error) { out.set("ok", false); out.set("error", ev.error); out.set("error_type", ev.error_type); break; }
+            if (ev.kind == StreamEvent::End) { out.set("ok", true); out.set("text", ev.generated_text->text); out.set("tokens", tokens); break; }
+          }
+          infer.request_done();
+        } catch (const ApiError& e) {
+          out.set("ok", false);
+          out.set("error", e.what());
+          out.set("error_type", e.type);
+          out.set("status", e.status);
+        }
+        return out;
+      }));
+    }
+    for (auto& f : futs) results.push(f.get());
+    infer.stop();
+  }
+  json::Value out = json::Value::object();
+  out.set("results", results);
+  json::Value log = json::Value::array();
+  for (auto& l : fake->log) log.push(l);
+  out.set("log", log);
+  out.set("metrics", metrics.render());
+  return ret(out.dump());
+}
+
+}  // extern "C"

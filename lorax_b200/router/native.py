@@ -1,0 +1,108 @@
+"""ctypes bindings of ``_lx_host.so``: the C++ router's block allocator, radix trie, adapter queues and the
+in-process Infer harness that runs against a fake shard (used by the tests and by tools that want the exact
+scheduling behaviour of the router without starting it)."""
+
+from __future__ import annotations
+
+import ctypes
+import json
+from ctypes import c_char_p, c_double, c_int, c_uint32, c_uint64, c_void_p
+from pathlib import Path
+from typing import List, Optional, Sequence
+
+_PKG = Path(__file__).resolve().parent.parent
+_LIB = _PKG / "_lx_host.so"
+_lib = None
+
+
+def load():
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not _LIB.exists():
+        from lorax_b200.csrc import build
+        build.build_host()
+    lib = ctypes.CDLL(str(_LIB))
+    U32P = ctypes.POINTER(c_uint32)
+    sig = {
+        "lx_alloc_new": ([c_uint32, c_uint32, c_int, c_int], c_void_p),
+        "lx_alloc_delete": ([c_void_p], None),
+        "lx_alloc_free_blocks": ([c_void_p], c_uint64),
+        "lx_alloc_allocate": ([c_void_p, c_uint32, c_uint32, U32P, c_uint32], c_void_p),
+        "lx_allocation_num_blocks": ([c_void_p], c_uint32),
+        "lx_allocation_prefix_len": ([c_void_p], c_uint32),
+        "lx_allocation_num_slots": ([c_void_p], c_uint32),
+        "lx_allocation_blocks": ([c_void_p, U32P], None),
+        "lx_allocation_slots": ([c_void_p, U32P], None),
+        "lx_alloc_free": ([c_void_p, c_void_p, c_uint32, U32P, c_uint32], None),
+        "lx_json_roundtrip": ([c_char_p], c_char_p),
+        "lx_queues_script": ([c_int, c_double, c_char_p], c_char_p),
+        "lx_infer_fake_run": ([c_char_p, c_int, c_int, c_uint32, c_int], c_char_p),
+    }
+    for name, (args, res) in sig.items():
+        f = getattr(lib, name)
+        f.argtypes, f.restype = args, res
+    _lib = lib
+    return lib
+
+
+def _arr(xs: Optional[Sequence[int]]):
+    if xs is None:
+        return None, 0
+    a = (c_uint32 * len(xs))(*xs)
+    return a, len(xs)
+
+
+class Allocation:
+    def __init__(self, handle, lib):
+        self._h = handle
+        n = lib.lx_allocation_num_blocks(handle)
+        b = (c_uint32 * n)()
+        lib.lx_allocation_blocks(handle, b)
+        self.blocks: List[int] = list(b)
+        ns = lib.lx_allocation_num_slots(handle)
+        s = (c_uint32 * ns)()
+        lib.lx_allocation_slots(handle, s)
+        self.slots: List[int] = list(s)
+        self.prefix_len: int = lib.lx_allocation_prefix_len(handle)
+
+
+class BlockAllocator:
+    """The router's allocator (free list, or radix trie when `prefix_caching`)."""
+
+    def __init__(self, num_blocks: int, block_size: int, window: Optional[int] = None, prefix_caching: bool = False):
+        self._lib = load()
+        self._a = self._lib.lx_alloc_new(num_blocks, block_size, window or 0, int(prefix_caching))
+
+    def __del__(self):
+        if getattr(self, "_a", None):
+            self._lib.lx_alloc_delete(self._a)
+            self._a = None
+
+    @property
+    def free_blocks(self) -> int:
+        return self._lib.lx_alloc_free_blocks(self._a)
+
+    def allocate(self, tokens: int, adapter_index: int = 0, prompt: Optional[Sequence[int]] = None) -> Optional[Allocation]:
+        a, n = _arr(prompt)
+        h = self._lib.lx_alloc_allocate(self._a, adapter_index, tokens, a, n)
+        return Allocation(h, self._lib) if h else None
+
+    def free(self, alloc: Allocation, adapter_index: int = 0, all_tokens: Optional[Sequence[int]] = None):
+        a, n = _arr(all_tokens)
+        self._lib.lx_alloc_free(self._a, alloc._h, adapter_index, a, n)
+        alloc._h = None
+
+
+def json_roundtrip(s: str) -> str:
+    return load().lx_json_roundtrip(s.encode()).decode()
+
+
+def queues_script(ops, max_active: int = 2, cycle_s: float = 2.0):
+    return json.loads(load().lx_queues_script(max_active, cycle_s, json.dumps(ops).encode()).decode())
+
+
+def infer_fake_run(requests, max_active_adapters: int = 8, fail_decode_after: int = -1, num_blocks: int = 4096,
+                   prefix_caching: bool = False):
+    out = load().lx_infer_fake_run(json.dumps(requests).encode(), max_active_adapters, fail_decode_after, num_blocks, int(prefix_caching))
+    return json.loads(out.decode())
