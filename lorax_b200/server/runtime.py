@@ -1,0 +1,459 @@
+"""Shard runtime: what the 13 RPCs of `LoraxService` operate on.
+
+One instance per GPU process.  It owns the model shard, the paged KV cache, the adapter manager with its
+host / HBM tiers, the tokenizer, and the cached batches.  Block tables come from the router (Request.blocks);
+the runtime maps every running request to a row of the device-resident decode state.
+
+Counterpart of `server/lorax_server/models/flash_causal_lm.py` (`FlashCausalLMBatch.from_pb / filter /
+concatenate`, `generate_token`) and `models/model.py` (`decode_token`, `load_adapter`, `offload_adapter`).
+"""
+
+from __future__ import annotations
+
+import json
+import os
+import threading
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..adapters.lora import LoraConfig, load_peft_adapter
+from ..adapters.manager import AdapterManager
+from ..adapters.merges import merge_adapters
+from ..config import EngineConfig, ModelConfig
+from ..models.decoder import DecoderModel
+from ..parallel.tp import TensorParallel
+from ..runtime.kv_cache import KVCache
+from ..runtime.runner import ModelRunner, PrefillItem
+from ..sampling.chooser import (FINISH_EOS, FINISH_LENGTH, FINISH_STOP, HeterogeneousNextTokenChooser, NextTokenParams,
+                                StoppingCriteria)
+from ..sampling.grammar import compile_schema
+from ..utils.sources import resolve_adapter, resolve_model
+from ..utils.weights import Weights, safetensors_nbytes, weight_files
+from .proto import load_pb
+
+
+class Detokenizer:
+    """Incremental detokenisation with a sliding window of ids, so that multi-token characters and
+    leading-space conventions come out right (same scheme as `models/model.py:195-219` of the reference)."""
+
+    def __init__(self, tokenizer, prompt_ids: Sequence[int]):
+        self.tok = tokenizer
+        self.ids = list(prompt_ids[-8:])
+        self.prefix = 0
+        self.read = len(self.ids)
+
+    def push(self, token_id: int) -> str:
+        self.ids.append(token_id)
+        if self.tok is None:
+            return ""
+        prefix_text = self.tok.decode(self.ids[self.prefix:self.read], skip_special_tokens=False)
+        new_text = self.tok.decode(self.ids[self.prefix:], skip_special_tokens=False)
+        if len(new_text) > len(prefix_text) and not new_text.endswith("�"):
+            out = new_text[len(prefix_text):]
+            self.prefix = self.read
+            self.read = len(self.ids)
+            return out
+        return ""
+
+
+@dataclass
+class SeqState:
+    request_id: int
+    batch_id: int
+    prompt_ids: List[int]
+    blocks: List[int]
+    adapter_index: int
+    params: NextTokenParams
+    stopping: StoppingCriteria
+    detok: Detokenizer
+    row: int = -1
+    output_ids: List[int] = field(default_factory=list)
+    output_text: str = ""
+    grammar: Optional[object] = None
+    seed: int = 0
+
+
+class ShardRuntime:
+    def __init__(self, model: DecoderModel, tokenizer=None, cfg: Optional[EngineConfig] = None, model_id: str = "",
+                 num_blocks: Optional[int] = None, max_batch: int = 256, adapter_arena_bytes: Optional[int] = None):
+        self.pb = load_pb()
+        self.model = model
+        self.tokenizer = tokenizer
+        self.cfg = cfg or EngineConfig()
+        self.model_id = model_id
+        self.tp = model.tp
+        c = model.config
+        dev = model.device
+        if adapter_arena_bytes is None:
+            if dev.type == "cuda":
+                total = torch.cuda.get_device_properties(dev).total_memory
+                adapter_arena_bytes = int(total * self.cfg.adapter_memory_fraction)
+            else:
+                adapter_arena_bytes = 256 << 20
+        self.adapters = AdapterManager(model, arena_bytes=adapter_arena_bytes,
+                                       host_bytes=int(self.cfg.host_adapter_cache_gb * (1 << 30)))
+        page = self.cfg.block_size
+        if num_blocks is None:
+            per_block = KVCache.bytes_per_block(c.num_hidden_layers, model.nkv, model.d, model.dtype, page)
+            if dev.type == "cuda":
+                free, _ = torch.cuda.mem_get_info(dev)
+                num_blocks = max(int((free * self.cfg.memory_wiggle_room - (4 << 30)) // per_block), 64)
+            else:
+                num_blocks = 1024
+        self.kv = KVCache(c.num_hidden_layers, num_blocks, model.nkv, model.d, model.dtype, dev, page)
+        self.runner = ModelRunner(model, self.kv, max_batch=max_batch, max_seq_tokens=self.cfg.max_total_tokens,
+                                  max_prefill_tokens=max(self.cfg.max_batch_prefill_tokens, 16), use_graphs=self.cfg.compile)
+        self.seqs: Dict[int, SeqState] = {}
+        self.batches: Dict[int, List[int]] = {}
+        eos = c.eos_token_id
+        self.eos_ids = frozenset(eos if isinstance(eos, (list, tuple)) else ([eos] if eos is not None else []))
+        self.special_ids = set(self.eos_ids)
+        self.downloaded: Dict[str, Tuple[LoraConfig, object]] = {}
+        self.lock = threading.Lock()
+
+    # ------------------------------------------------------------------ info / health
+    def info(self):
+        pb = self.pb
+        c = self.model.config
+        r = pb.InfoResponse(requires_padding=False, dtype=str(self.model.dtype).replace("torch.", ""),
+                            device_type=self.model.device.type, block_size=self.kv.page, speculate=self.cfg.speculative_tokens,
+                            supports_generation=True, supports_embeddings=False, supports_classification=False,
+                            chunked_prefill=self.cfg.chunked_prefill, requires_block_allocator=True)
+        if c.sliding_window:
+            r.window_size = c.sliding_window
+        return r
+
+    def health(self):
+        if self.model.device.type == "cuda":
+            torch.zeros(2, 2, device=self.model.device)
+        return self.pb.HealthResponse()
+
+    def warmup(self, req):
+        """The KV cache is sized at construction from free memory; report what it can hold."""
+        return self.pb.WarmupResponse(max_supported_total_tokens=self.kv.max_tokens)
+
+    # ------------------------------------------------------------------ tokenizer helpers
+    def tokenize(self, text: str, add_special: bool = True) -> List[int]:
+        if self.tokenizer is None:
+            return [int(x) for x in text.split()] if text.replace(" ", "").isdigit() else [ord(ch) % self.model.config.vocab_size for ch in text]
+        return self.tokenizer.encode(text, add_special_tokens=add_special).ids
+
+    def tokenize_detailed(self, body: dict) -> list:
+        text = body.get("inputs", "")
+        if self.tokenizer is None:
+            return [{"id": i, "text": str(i), "start": 0, "stop": 0} for i in self.tokenize(text)]
+        enc = self.tokenizer.encode(text, add_special_tokens=body.get("add_special_tokens", True))
+        return [{"id": i, "text": t, "start": o[0], "stop": o[1]} for i, t, o in zip(enc.ids, enc.tokens, enc.offsets)]
+
+    def apply_chat_template(self, body: dict) -> str:
+        from .chat_template import render_chat
+        return render_chat(body.get("messages", []), self.chat_template, tools=body.get("tools"), bos_token=self.bos_token,
+                           eos_token=self.eos_token)
+
+    chat_template: Optional[str] = None
+    bos_token: str = ""
+    eos_token: str = ""
+
+    # ------------------------------------------------------------------ adapters
+    def _adapter_key(self, params, source: int) -> str:
+        ids = list(params.adapter_ids)
+        if len(ids) == 1:
+            return f"{source}:{ids[0]}"
+        return f"{source}:" + ",".join(ids) + f"|{params.merge_strategy}|{params.density}|{params.majority_sign_method}|" + \
+            ",".join(f"{w:.6g}" for w in params.weights)
+
+    def download_adapter(self, req):
+        pb = self.pb
+        params, source = req.adapter_parameters, req.adapter_source
+        key = self._adapter_key(params, source)
+        src_name = {0: "hub", 1: "s3", 2: "local", 3: "pbase"}.get(source, "hub")
+        loaded = []
+        for aid in params.adapter_ids:
+            if aid in ("", "__base_model__"):
+                continue
+            path = resolve_adapter(aid, src_name, api_token=req.api_token if req.HasField("api_token") else None)
+            loaded.append(load_peft_adapter(path))
+        if not loaded:
+            return pb.DownloadAdapterResponse(downloaded=False, memory_fraction=0.0)
+        if len(loaded) == 1:
+            cfg, mm = loaded[0]
+        else:
+            strategy = {0: "linear", 1: "ties", 2: "dare_linear", 3: "dare_ties"}[params.merge_strategy]
+            cfg, mm = merge_adapters(loaded, list(params.weights) or [1.0] * len(loaded), strategy, params.density or 1.0,
+                                     "frequency" if params.majority_sign_method == 1 else "total")
+        self.adapters.register(key, cfg, mm)
+        return pb.DownloadAdapterResponse(downloaded=True, memory_fraction=self.adapters.memory_fraction(key))
+
+    def load_adapter(self, req):
+        key = self._adapter_key(req.adapter_parameters, req.adapter_source)
+        if self.adapters.host.get(key) is None:
+            self.download_adapter(self.pb.DownloadAdapterRequest(adapter_parameters=req.adapter_parameters, adapter_source=req.adapter_source))
+        ok = self.adapters.load(req.adapter_index, key)
+        if not ok:
+            raise RuntimeError(f"adapter {key} does not fit in the adapter memory reservation")
+        return self.pb.LoadAdapterResponse(loaded=True)
+
+    def offload_adapter(self, req):
+        return self.pb.OffloadAdapterResponse(offloaded=self.adapters.offload(req.adapter_index))
+
+    # ------------------------------------------------------------------ batches
+    def clear_cache(self, req):
+        ids = [req.id] if req.HasField("id") else list(self.batches.keys())
+        for bid in ids:
+            for rid in self.batches.pop(bid, []):
+                self._drop(rid)
+        if self.seqs:
+            self._resort()
+        return self.pb.ClearCacheResponse()
+
+    def _drop(self, rid: int):
+        s = self.seqs.pop(rid, None)
+        if s is not None and s.row >= 0:
+            self.runner.retire([s.row])
+            self.runner.state.drop_row(s.row)
+
+    def _resort(self):
+        mapping = self.runner.resort()
+        for s in self.seqs.values():
+            if s.row in mapping:
+                s.row = mapping[s.row]
+
+    def filter_batch(self, req):
+        keep = set(req.request_ids)
+        for rid in self.batches.get(req.batch_id, []):
+            if rid not in keep:
+                self._drop(rid)
+        self.batches[req.batch_id] = [r for r in self.batches.get(req.batch_id, []) if r in keep]
+        self._resort()
+        return self.pb.FilterBatchResponse(batch=self._cached(req.batch_id))
+
+    def _cached(self, bid: int):
+        rids = self.batches.get(bid, [])
+        mt = sum(len(self.seqs[r].prompt_ids) + self.seqs[r].stopping.max_new_tokens for r in rids)
+        cur = sum(len(self.seqs[r].prompt_ids) + len(self.seqs[r].output_ids) for r in rids)
+        return self.pb.CachedBatch(id=bid, request_ids=rids, size=len(rids), max_tokens=mt, current_tokens=cur)
+
+    # ------------------------------------------------------------------ token post-processing
+    def _params_from_pb(self, p) -> NextTokenParams:
+        return NextTokenParams(temperature=p.temperature or 1.0, top_k=p.top_k, top_p=p.top_p or 1.0, typical_p=p.typical_p or 1.0,
+                               do_sample=p.do_sample, seed=p.seed, repetition_penalty=p.repetition_penalty or 1.0,
+                               frequency_penalty=p.frequency_penalty, presence_penalty=p.presence_penalty, watermark=p.watermark,
+                               return_k_alternatives=p.return_k_alternatives, schema=p.schema if p.HasField("schema") else None)
+
+    def _emit(self, s: SeqState, token: int, logprob: float, alts=None):
+        """Append a token; returns (Generation or None for other ranks' requests, finished)."""
+        pb = self.pb
+        s.output_ids.append(token)
+        text = s.detok.push(token)
+        s.output_text += text
+        stop, reason = s.stopping(token, text)
+        mine = (s.request_id % self.tp.world_size) == self.tp.rank
+        gen = None
+        if mine:
+            nt = pb.NextTokens(ids=[token], logprobs=[logprob], texts=[text], is_special=[token in self.special_ids])
+            if alts is not None:
+                ids, lps = alts
+                nt.alternative_tokens.append(pb.AlternativeTokens(ids=ids, logprobs=lps, texts=[self._tok_text(i) for i in ids]))
+            gen = pb.Generation(request_id=s.request_id, next_tokens=nt, prefill_tokens_length=len(s.prompt_ids))
+            if stop:
+                out_text = s.output_text
+                if reason == FINISH_STOP:
+                    for ss in s.stopping.stop_sequences:
+                        if ss and out_text.endswith(ss):
+                            break
+                gt = pb.GeneratedText(text=out_text, generated_tokens=len(s.output_ids), skipped_tokens=0, finish_reason=reason)
+                if s.params.do_sample:
+                    gt.seed = s.seed
+                gen.generated_text.CopyFrom(gt)
+        return gen, stop
+
+    def _tok_text(self, tid: int) -> str:
+        return self.tokenizer.decode([tid], skip_special_tokens=False) if self.tokenizer is not None else ""
+
+    def _sample_rows(self, seqs: List[SeqState], logits: torch.Tensor, greedy_ids: List[int], greedy_lps: List[float]):
+        """Per-request sampling for the rows whose parameters need more than an argmax; the rest keep the result of
+        the fused greedy kernel.  Returns (ids, logprobs, alternatives)."""
+        need = [i for i, s in enumerate(seqs) if not (s.params.plain and s.grammar is None)]
+        ids, lps, alts = list(greedy_ids), list(greedy_lps), [None] * len(seqs)
+        if not need:
+            return ids, lps, alts
+        sub = [seqs[i] for i in need]
+        chooser = HeterogeneousNextTokenChooser([s.params for s in sub], logits.device, logits.shape[-1],
+                                                grammars=[s.grammar for s in sub])
+        for j, s in enumerate(sub):
+            g = getattr(s, "_gen", None)
+            if g is not None:
+                chooser.generators[j] = g
+        L = max(len(s.prompt_ids) + len(s.output_ids) for s in sub)
+        hist = torch.zeros(len(sub), L, dtype=torch.long, device=logits.device)
+        mask = torch.zeros(len(sub), L, dtype=torch.bool, device=logits.device)
+        for j, s in enumerate(sub):
+            h = s.prompt_ids + s.output_ids
+            hist[j, :len(h)] = torch.tensor(h, device=logits.device)
+            mask[j, :len(h)] = True
+        rows = torch.tensor(need, device=logits.device)
+        nid, nlp, nalts = chooser(hist, mask, logits.index_select(0, rows).float(),
+                                  last_tokens=[(s.prompt_ids + s.output_ids)[-1] for s in sub])
+        for j, s in enumerate(sub):
+            s._gen = chooser.generators.get(j)
+        nid_l, nlp_l = nid.tolist(), nlp.tolist()
+        for j, i in enumerate(need):
+            ids[i], lps[i] = nid_l[j], nlp_l[j]
+            k = seqs[i].params.return_k_alternatives
+            if nalts is not None and k > 0:
+                alts[i] = (nalts[0][j, :k].tolist(), nalts[1][j, :k].tolist())
+        return ids, lps, alts
+
+    # ------------------------------------------------------------------ Prefill / Decode
+    def prefill(self, req):
+        pb = self.pb
+        batch = req.batch
+        items, seqs = [], []
+        max_in = self.cfg.max_input_length
+        for r in batch.requests:
+            ids = list(r.tokenized_inputs.ids) if r.HasField("tokenized_inputs") and len(r.tokenized_inputs.ids) else self.tokenize(r.inputs)
+            trunc = r.truncate or max_in
+            ids = ids[-trunc:]
+            params = self._params_from_pb(r.parameters)
+            stopping = StoppingCriteria(r.stopping_parameters.max_new_tokens or 1, self.eos_ids, list(r.stopping_parameters.stop_sequences),
+                                        r.stopping_parameters.ignore_eos_token)
+            if r.adapter_index != 0 and not self.adapters.is_loaded(r.adapter_index):
+                raise RuntimeError(f"adapter index {r.adapter_index} is not loaded on this shard")
+            s = SeqState(r.id, batch.id, ids, list(r.blocks), r.adapter_index, params, stopping, Detokenizer(self.tokenizer, ids), seed=params.seed)
+            if params.schema:
+                s.grammar = compile_schema(params.schema, self.tokenizer, self.eos_ids)
+            seqs.append(s)
+            items.append(PrefillItem(ids[r.cache_len:] if r.cache_len else ids, r.cache_len, list(r.blocks), r.adapter_index,
+                                     all_logprobs=r.prefill_logprobs))
+        next_ids, lps, logits = self.runner.prefill(items)
+        # rows of `logits` per request: the last one when prefill log-probs were requested
+        row_of, o = [], 0
+        for it in items:
+            n = len(it.token_ids) if it.all_logprobs else 1
+            row_of.append(o + n - 1)
+            o += n
+        last_rows = torch.tensor(row_of, device=logits.device)
+        gid = next_ids.index_select(0, last_rows).tolist()
+        glp = lps.index_select(0, last_rows).tolist()
+        ids_l, lps_l, alts = self._sample_rows(seqs, logits.index_select(0, last_rows), gid, glp)
+        gens, live, rows, firsts, poss, blks, ads = [], [], [], [], [], [], []
+        o = 0
+        for s, it, tok, lp, alt in zip(seqs, items, ids_l, lps_l, alts):
+            gen, stop = self._emit(s, int(tok), float(lp), alt)
+            if gen is not None and it.all_logprobs:
+                n = len(it.token_ids)
+                plp = torch.log_softmax(logits[o:o + n].float(), -1)
+                tgt = torch.tensor(it.token_ids[1:], device=logits.device)
+                vals = [float("nan")] + plp[:-1].gather(1, tgt[:, None])[:, 0].tolist() if n > 1 else [float("nan")]
+                gen.prefill_tokens.CopyFrom(pb.NextTokens(ids=list(it.token_ids), logprobs=vals,
+                                                          texts=[self._tok_text(i) for i in it.token_ids]))
+            o += len(it.token_ids) if it.all_logprobs else 1
+            if gen is not None:
+                gens.append(gen)
+            if not stop:
+                self.seqs[s.request_id] = s
+                s.row = self.runner.state.take_row(s.request_id)
+                live.append(s.request_id)
+                rows.append(s.row); firsts.append(int(tok)); poss.append(len(s.prompt_ids)); blks.append(s.blocks); ads.append(s.adapter_index)
+        resp = pb.PrefillResponse(generations=gens)
+        if live:
+            self.runner.install(rows, firsts, poss, blks, ads)
+            self._resort()
+            self.batches[batch.id] = live
+            resp.batch.CopyFrom(self._cached(batch.id))
+        return resp
+
+    def decode(self, req):
+        pb = self.pb
+        bids = [b.id for b in req.batches]
+        rids = [r for b in bids for r in self.batches.get(b, [])]
+        if not rids:
+            raise RuntimeError("all batches of the Decode request are missing from the cache")
+        seqs = [self.seqs[r] for r in rids]
+        need_logits = any(not (s.params.plain and s.grammar is None) for s in seqs)
+        k, b, logits = self.runner.decode(need_logits=need_logits)
+        ids_p, lps_p = self.runner.wait(k)
+        rows = [s.row for s in seqs]
+        gid = [int(ids_p[r]) for r in rows]
+        glp = [float(lps_p[r]) for r in rows]
+        alts = [None] * len(seqs)
+        if need_logits:
+            sel = logits.index_select(0, torch.tensor(rows, device=logits.device))
+            gid2, glp2, alts = self._sample_rows(seqs, sel, gid, glp)
+            changed = [(r, t) for r, t, t0 in zip(rows, gid2, gid) if t != t0]
+            if changed:
+                # the graph already advanced the state with the greedy token: overwrite the next input id
+                rr = torch.tensor([c[0] for c in changed], device=logits.device)
+                self.runner.state.input_ids.index_copy_(0, rr, torch.tensor([c[1] for c in changed], dtype=torch.int32, device=logits.device))
+            gid, glp = gid2, glp2
+        gens, finished = [], []
+        for s, tok, lp, alt in zip(seqs, gid, glp, alts):
+            gen, stop = self._emit(s, tok, lp, alt)
+            if gen is not None:
+                gens.append(gen)
+            if stop:
+                finished.append(s.request_id)
+        new_id = bids[0]
+        merged = [r for r in rids if r not in finished]
+        for bid in bids:
+            self.batches.pop(bid, None)
+        for rid in finished:
+            self._drop(rid)
+        resp = pb.DecodeResponse(generations=gens)
+        if merged:
+            self.batches[new_id] = merged
+            for r in merged:
+                self.seqs[r].batch_id = new_id
+            resp.batch.CopyFrom(self._cached(new_id))
+        return resp
+
+    def embed(self, req):
+        return self.pb.EmbedResponse(errorMsg="this model does not produce embeddings")
+
+    def classify(self, req):
+        return self.pb.ClassifyResponse(errorMsg="this model is not a classifier")
+
+
+# ---------------------------------------------------------------------------------------------- construction
+def load_tokenizer(model_dir: str):
+    path = os.path.join(model_dir, "tokenizer.json")
+    if os.path.exists(path):
+        from tokenizers import Tokenizer
+        return Tokenizer.from_file(path)
+    return None
+
+
+def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel] = None, dtype: Optional[torch.dtype] = None,
+                  device: Optional[str] = None, source: str = "hub", revision: Optional[str] = None, **kw) -> ShardRuntime:
+    tp = tp or TensorParallel.init_from_env()
+    model_dir = resolve_model(model_id, source, revision)
+    mc = ModelConfig.from_pretrained(model_dir)
+    dev = torch.device(device) if device else (tp.device or torch.device("cpu"))
+    if dtype is None:
+        dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    w = Weights(weight_files(model_dir), device="cpu", dtype=dtype, rank=tp.rank, world_size=tp.world_size)
+    tp.barrier()
+    model = DecoderModel.from_weights(mc, w, dev, dtype, tp, max_positions=min(mc.max_position_embeddings, max(cfg.max_total_tokens + 64, 2048)))
+    tp.barrier()
+    tok = load_tokenizer(model_dir)
+    rt = ShardRuntime(model, tok, cfg, model_id=model_id, **kw)
+    tc_path = os.path.join(model_dir, "tokenizer_config.json")
+    if os.path.exists(tc_path):
+        with open(tc_path) as f:
+            tc = json.load(f)
+        rt.chat_template = tc.get("chat_template")
+
+        def _tok(v):
+            return v.get("content", "") if isinstance(v, dict) else (v or "")
+        rt.bos_token, rt.eos_token = _tok(tc.get("bos_token")), _tok(tc.get("eos_token"))
+    gc_path = os.path.join(model_dir, "generation_config.json")
+    if os.path.exists(gc_path):
+        with open(gc_path) as f:
+            eos = json.load(f).get("eos_token_id")
+        if eos is not None:
+            rt.eos_ids = frozenset(eos if isinstance(eos, list) else [eos])
+            rt.special_ids |= set(rt.eos_ids)
+    return rt

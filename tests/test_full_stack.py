@@ -1,0 +1,172 @@
+"""Launcher-less full stack on CPU: a Python shard (framed UDS transport + gRPC) serving a tiny Llama checkpoint
+with PEFT adapters on disk, the C++ `lorax-router` binary in front of it, and HTTP clients."""
+import json
+import os
+import socket
+import subprocess
+import time
+import urllib.request
+
+import pytest
+import torch
+from safetensors.torch import save_file
+
+from lorax_b200.adapters.lora import random_adapter, save_peft_adapter
+from lorax_b200.config import EngineConfig, tiny_llama
+from lorax_b200.models.decoder import DecoderModel
+from lorax_b200.models.loading import export_hf_state_dict
+
+ROUTER = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lorax_b200", "bin", "lorax-router")
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _post(port, path, body, stream=False, headers=None):
+    req = urllib.request.Request(f"http://127.0.0.1:{port}{path}", data=json.dumps(body).encode(),
+                                 headers={"Content-Type": "application/json", **(headers or {})})
+    try:
+        with urllib.request.urlopen(req, timeout=60) as r:
+            data = r.read().decode()
+            return r.status, data, dict(r.headers)
+    except urllib.error.HTTPError as e:
+        return e.code, e.read().decode(), dict(e.headers)
+
+
+@pytest.fixture(scope="module")
+def stack(tmp_path_factory):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from lorax_b200.csrc import build
+    build.build_host()
+    root = tmp_path_factory.mktemp("stack")
+    cfg = tiny_llama(vocab_size=512)
+    cfg.eos_token_id = 1
+    model = DecoderModel.random_init(cfg, "cpu", torch.float32, seed=0)
+    mdir = root / "model"
+    mdir.mkdir()
+    save_file(export_hf_state_dict(model), str(mdir / "model.safetensors"), metadata={"format": "pt"})
+    d = cfg.to_dict()
+    d["architectures"] = ["LlamaForCausalLM"]
+    (mdir / "config.json").write_text(json.dumps(d))
+    vocab = {f"w{i}": i for i in range(512)}
+    vocab["<unk>"] = 0
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    tok.save(str(mdir / "tokenizer.json"))
+    (mdir / "tokenizer_config.json").write_text(json.dumps({"chat_template": "{% for m in messages %}{{ m['content'] }} {% endfor %}"}))
+    for i in range(2):
+        c, mm = random_adapter(cfg, r=8, alpha=16, target_modules=["q_proj", "v_proj", "down_proj"], seed=50 + i, std_a=0.1, std_b=0.1)
+        save_peft_adapter(root / f"adapter{i}", c, mm)
+
+    from lorax_b200.server.runtime import build_runtime
+    from lorax_b200.server.transport import FramedServer
+    ecfg = EngineConfig(max_input_length=64, max_total_tokens=128, max_batch_prefill_tokens=256, compile=False)
+    rt = build_runtime(str(mdir), ecfg, device="cpu", dtype=torch.float32, source="local", num_blocks=256, max_batch=16)
+    uds = str(root / "shard")
+    srv = FramedServer(rt, uds + "-0.lx").start()
+    port = _free_port()
+    proc = subprocess.Popen([ROUTER, "--port", str(port), "--hostname", "127.0.0.1", "--master-shard-uds-path", uds, "--num-shard", "1",
+                             "--max-input-length", "64", "--max-total-tokens", "128", "--max-batch-prefill-tokens", "256",
+                             "--model-id", "tiny", "--adapter-source", "local", "--waiting-served-ratio", "0.3"],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    ok = False
+    for _ in range(100):
+        try:
+            with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1) as r:
+                ok = r.status == 200
+                break
+        except Exception:
+            time.sleep(0.1)
+    if not ok:
+        proc.kill()
+        raise RuntimeError("router did not come up: " + proc.stdout.read().decode()[-2000:])
+    yield dict(port=port, root=root, rt=rt, model=model, cfg=cfg)
+    proc.terminate()
+    try:
+        proc.wait(timeout=10)
+    except subprocess.TimeoutExpired:
+        proc.kill()
+    srv.stop()
+
+
+def test_generate_base_and_adapters_match_engine(stack):
+    port, root = stack["port"], stack["root"]
+    prompt = " ".join(f"w{i}" for i in (5, 17, 200, 33, 8, 91))
+    outs = {}
+    for name, params in (("base", {}), ("a0", {"adapter_id": str(root / "adapter0"), "adapter_source": "local"}),
+                         ("a1", {"adapter_id": str(root / "adapter1"), "adapter_source": "local"})):
+        st, body, hdr = _post(port, "/generate", {"inputs": prompt, "parameters": {"max_new_tokens": 8, "details": True, "ignore_eos_token": True, **params}})
+        assert st == 200, body
+        j = json.loads(body)
+        assert j["details"]["generated_tokens"] == 8 and j["details"]["finish_reason"] == "length"
+        assert len(j["details"]["tokens"]) == 8 and j["details"]["prompt_tokens"] == 6
+        assert "x-generated-tokens" in {k.lower() for k in hdr}
+        outs[name] = [t["id"] for t in j["details"]["tokens"]]
+    assert outs["base"] != outs["a0"] or outs["base"] != outs["a1"]
+    # oracle: the in-process engine with the same model
+    from lorax_b200.runtime.engine import Engine
+    eng = Engine(stack["model"], EngineConfig(max_total_tokens=128, max_batch_prefill_tokens=256), num_blocks=64, max_batch=4)
+    base = eng.generate([[5, 17, 200, 33, 8, 91]], max_new_tokens=8)[0]
+    assert outs["base"] == base
+
+
+def test_stream_and_openai_routes(stack):
+    port = stack["port"]
+    st, body, _ = _post(port, "/generate_stream", {"inputs": "w1 w2 w3", "parameters": {"max_new_tokens": 5, "ignore_eos_token": True, "details": True}})
+    assert st == 200
+    events = [json.loads(l[5:]) for l in body.replace("\r", "").split("\n") if l.startswith("data:")]
+    assert len(events) == 5 and events[-1]["generated_text"] is not None and events[0]["generated_text"] is None
+    assert events[-1]["details"]["generated_tokens"] == 5
+    st, body, _ = _post(port, "/v1/chat/completions", {"model": "tiny", "messages": [{"role": "user", "content": "w4 w5"}], "max_tokens": 4})
+    assert st == 200, body
+    j = json.loads(body)
+    assert j["object"] == "chat.completion" and j["choices"][0]["message"]["role"] == "assistant" and j["usage"]["completion_tokens"] <= 4
+    st, body, _ = _post(port, "/v1/completions", {"model": "tiny", "prompt": "w4 w5", "max_tokens": 3, "stream": True})
+    assert st == 200 and "[DONE]" in body
+
+
+def test_errors_and_misc_routes(stack):
+    port = stack["port"]
+    st, body, _ = _post(port, "/generate", {"inputs": "w1", "parameters": {"max_new_tokens": 4, "top_p": 2.0}})
+    assert st == 422 and json.loads(body)["error_type"] == "validation"
+    st, body, _ = _post(port, "/generate", {"inputs": "w1", "parameters": {"max_new_tokens": 4, "adapter_id": "/nonexistent/adapter", "adapter_source": "local"}})
+    assert st == 424 and "adapter" in json.loads(body)["error"]
+    st, body, _ = _post(port, "/generate", {"inputs": "w1 w2", "parameters": {"max_new_tokens": 3}})     # still healthy afterwards
+    assert st == 200
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/info", timeout=5) as r:
+        info = json.loads(r.read())
+    assert info["max_total_tokens"] == 128 and info["block_size"] == 32
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5) as r:
+        m = r.read().decode()
+    assert "lorax_request_success" in m and "lorax_batch_inference_duration_bucket" in m
+    st, body, _ = _post(port, "/tokenize", {"inputs": "w7 w8"})
+    assert st == 200 and [t["id"] for t in json.loads(body)] == [7, 8]
+
+
+def test_concurrent_heterogeneous_requests(stack):
+    import concurrent.futures as cf
+    port, root = stack["port"], stack["root"]
+
+    def one(i):
+        params = {"max_new_tokens": 4 + i % 4, "ignore_eos_token": True, "details": True}
+        if i % 3:
+            params.update(adapter_id=str(root / f"adapter{i % 3 - 1}"), adapter_source="local")
+        return _post(port, "/generate", {"inputs": f"w{i} w{i + 1} w{i + 2}", "parameters": params})
+    with cf.ThreadPoolExecutor(12) as ex:
+        res = list(ex.map(one, range(12)))
+    assert all(st == 200 for st, _, _ in res)
+    assert [json.loads(b)["details"]["generated_tokens"] for _, b, _ in res] == [4 + i % 4 for i in range(12)]
+
+
+def test_sampling_and_seed(stack):
+    port = stack["port"]
+    p = {"max_new_tokens": 6, "ignore_eos_token": True, "do_sample": True, "temperature": 1.5, "top_k": 50, "seed": 7, "details": True}
+    a = json.loads(_post(port, "/generate", {"inputs": "w9 w10", "parameters": p})[1])
+    b = json.loads(_post(port, "/generate", {"inputs": "w9 w10", "parameters": p})[1])
+    assert [t["id"] for t in a["details"]["tokens"]] == [t["id"] for t in b["details"]["tokens"]]
+    assert a["details"]["seed"] == 7
