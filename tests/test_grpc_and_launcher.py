@@ -1,0 +1,125 @@
+"""The gRPC face of the shard (generate.v1.LoraxService over a unix socket, runtime-built descriptors) and the
+C++ launcher supervising a shard + router."""
+import asyncio
+import json
+import os
+import signal
+import socket
+import subprocess
+import sys
+import time
+import urllib.request
+
+import pytest
+import torch
+from safetensors.torch import save_file
+
+from lorax_b200.config import EngineConfig, tiny_llama
+from lorax_b200.models.decoder import DecoderModel
+from lorax_b200.models.loading import export_hf_state_dict
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+LAUNCHER = os.path.join(REPO, "lorax_b200", "bin", "lorax-launcher")
+
+
+def _model_dir(root):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    cfg = tiny_llama(vocab_size=512)
+    model = DecoderModel.random_init(cfg, "cpu", torch.float32, seed=0)
+    mdir = root / "model"
+    mdir.mkdir()
+    save_file(export_hf_state_dict(model), str(mdir / "model.safetensors"), metadata={"format": "pt"})
+    (mdir / "config.json").write_text(json.dumps(cfg.to_dict()))
+    vocab = {f"w{i}": i for i in range(512)}
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="w0"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    tok.save(str(mdir / "tokenizer.json"))
+    return mdir
+
+
+def test_grpc_contract(tmp_path):
+    import grpc
+    from lorax_b200.server.proto import load_pb
+    from lorax_b200.server.runtime import build_runtime
+    from lorax_b200.server.transport import serve_grpc
+    pb = load_pb()
+    mdir = _model_dir(tmp_path)
+    rt = build_runtime(str(mdir), EngineConfig(max_input_length=64, max_total_tokens=128, max_batch_prefill_tokens=256, compile=False),
+                       device="cpu", dtype=torch.float32, source="local", num_blocks=64, max_batch=8)
+    uds = str(tmp_path / "s")
+
+    async def run():
+        server = await serve_grpc(rt, uds, 0, 1)
+        async with grpc.aio.insecure_channel(f"unix://{uds}-0") as ch:
+            def call(name, req):
+                rq, rs = pb.RPCS[name]
+                return ch.unary_unary(f"/{pb.SERVICE}/{name}", request_serializer=rq.SerializeToString, response_deserializer=rs.FromString)(req)
+            info = await call("Info", pb.InfoRequest())
+            assert info.block_size == 32 and info.supports_generation and info.requires_block_allocator
+            sd = await call("ServiceDiscovery", pb.ServiceDiscoveryRequest())
+            assert list(sd.urls) == [f"unix://{uds}-0"]
+            req = pb.Request(id=0, inputs="w1 w2 w3", truncate=64, adapter_index=0, blocks=[1, 2],
+                             parameters=pb.NextTokenChooserParameters(temperature=1.0, top_p=1.0, typical_p=1.0, repetition_penalty=1.0),
+                             stopping_parameters=pb.StoppingCriteriaParameters(max_new_tokens=3, ignore_eos_token=True))
+            resp = await call("Prefill", pb.PrefillRequest(batch=pb.Batch(id=7, requests=[req], size=1, max_tokens=6)))
+            assert len(resp.generations) == 1 and resp.batch.id == 7 and list(resp.batch.request_ids) == [0]
+            toks = [resp.generations[0].next_tokens.ids[0]]
+            cached = resp.batch
+            while True:
+                d = await call("Decode", pb.DecodeRequest(batches=[cached]))
+                toks.append(d.generations[0].next_tokens.ids[0])
+                if d.generations[0].HasField("generated_text"):
+                    assert d.generations[0].generated_text.generated_tokens == 3
+                    assert not d.HasField("batch")
+                    break
+                cached = d.batch
+            assert len(toks) == 3
+            # an unknown batch is an INTERNAL error, and the server keeps working
+            with pytest.raises(grpc.aio.AioRpcError) as ei:
+                await call("Decode", pb.DecodeRequest(batches=[pb.CachedBatch(id=99)]))
+            assert ei.value.code() == grpc.StatusCode.INTERNAL
+            await call("Health", pb.HealthRequest())
+        await server.stop(0)
+    asyncio.run(run())
+
+
+def test_launcher_supervises_shard_and_router(tmp_path):
+    from lorax_b200.csrc import build
+    build.build_host()
+    mdir = _model_dir(tmp_path)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, PYTHONPATH=REPO, CUDA_VISIBLE_DEVICES="", LORAX_COMPILE="0")
+    proc = subprocess.Popen([LAUNCHER, "--model-id", str(mdir), "--source", "local", "--port", str(port), "--hostname", "127.0.0.1",
+                             "--shard-uds-path", str(tmp_path / "uds"), "--python", sys.executable, "--max-input-length", "64",
+                             "--max-total-tokens", "128", "--json-output", "--master-port", "29611"],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env)
+    try:
+        ok = False
+        for _ in range(600):
+            if proc.poll() is not None:
+                break
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1) as r:
+                    ok = r.status == 200
+                    break
+            except Exception:
+                time.sleep(0.2)
+        if not ok:
+            proc.kill()
+            raise AssertionError("deployment did not come up:\n" + proc.stdout.read().decode()[-3000:])
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/generate", data=json.dumps({"inputs": "w1 w2", "parameters": {"max_new_tokens": 3}}).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=60) as r:
+            assert "generated_text" in json.loads(r.read())
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            raise
+    out = proc.stdout.read().decode()
+    assert "shard 0 ready" in out and proc.returncode == 0, out[-2000:]
