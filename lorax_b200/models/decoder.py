@@ -68,6 +68,7 @@ class StepInputs:
     lora_tiles: Optional[object] = None              # adapters.manager.LoraTiles: rows grouped by adapter (tensor-core shrink)
     attn_nsplit: int = 1
     num_tokens: Optional[int] = None                 # live rows when the tensors are padded (graphs)
+    local_logits: bool = False                       # TP: return this rank's vocabulary shard instead of gathering
 
 
 class DecoderModel:
@@ -284,6 +285,21 @@ class DecoderModel:
             self.adapters.apply(self.ops, x, y, ts, group, layer, tiles=inp.lora_tiles)
         return y
 
+    def _row_parallel(self, x, w, b, group: str, layer: int, inp: StepInputs):
+        """Row-parallel projection + all-reduce.  With the NVLink kernels enabled and a decode-sized batch this is one
+        fused GEMM -> reduce-scatter -> all-gather kernel; the rank's partial LoRA delta is reduced with it."""
+        fused = self.tp.fused if self.tp.world_size > 1 else None
+        if (fused is not None and x.is_cuda and x.shape[0] <= fused.MAX_TOKENS and b is None and not self.config.parallel_residual):
+            addend = None
+            if self.adapters is not None and (inp.tok_slot is not None or inp.lora_tiles is not None) and self.adapters.max_rank > 0:
+                addend = torch.zeros(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
+                self.adapters.apply(self.ops, x, addend, inp.tok_slot, group, layer, tiles=inp.lora_tiles)
+            return fused.gemm_allreduce(x, w, None, addend)
+        out = self._linear(x, w, b, group, layer, inp)
+        if self.tp.world_size > 1:
+            out = self.tp.all_reduce(out)
+        return out
+
     def forward(self, inp: StepInputs, kv_cache: List[torch.Tensor]) -> torch.Tensor:
         """-> logits [n_out, vocab] (full vocabulary on every rank)."""
         c, ops = self.config, self.ops
@@ -328,6 +344,8 @@ class DecoderModel:
         if ts is not None and self.adapters is not None and self.adapters.layout.has_lm_head:
             self.adapters.apply(self.ops, hidden, logits, ts, "lm_head", 0)
         if self.tp.world_size > 1:
+            if inp.local_logits:
+                return logits
             logits = self.tp.all_gather_cols(logits)[:, : self.vocab]
         elif logits.shape[1] != self.vocab:
             logits = logits[:, : self.vocab]
@@ -348,19 +366,13 @@ class DecoderModel:
         else:
             attn = ops.attn_decode(qkv, kv, inp.block_tables, inp.ctx_lens, self.nh, self.nkv, self.d, c.attn_scale, window,
                                    softcap, inp.attn_nsplit)
-        out = self._linear(attn, lw.o_w, lw.o_b, "o", li, inp)
-        if self.tp.world_size > 1:
-            out = self.tp.all_reduce(out)
-        return out
+        return self._row_parallel(attn, lw.o_w, lw.o_b, "o", li, inp)
 
     def _mlp(self, x, lw: LayerWeights, li: int, inp: StepInputs):
         c, ops = self.config, self.ops
         gu = self._linear(x, lw.gate_up_w, lw.gate_up_b, "gate_up", li, inp)
         act = ops.act_mul(gu, self.inter, c.hidden_act, gated=self.gated)
-        out = self._linear(act, lw.down_w, lw.down_b, "down", li, inp)
-        if self.tp.world_size > 1:
-            out = self.tp.all_reduce(out)
-        return out
+        return self._row_parallel(act, lw.down_w, lw.down_b, "down", li, inp)
 
     def _moe(self, x, lw: LayerWeights, li: int, inp: StepInputs):
         """Top-k mixture of experts (reference math: flash_mixtral_modeling.py:449-459, 668-716): softmax over all

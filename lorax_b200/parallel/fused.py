@@ -1,0 +1,91 @@
+"""In-kernel NVLink collectives for tensor parallelism.
+
+`enable(tp, model)` allocates one symmetric buffer per rank (CUDA VMM allocation exported to every peer through
+`torch.distributed._symmetric_memory`, which is only used for the rendezvous and the peer pointers) and attaches a
+:class:`FusedCollectives` to the process group.  The data movement itself happens inside this library's kernels
+(`csrc/kernels/gemm_allreduce.cu`): peer stores and system-scope atomics over NVLink, no NCCL call on the hot path.
+
+* `gemm_allreduce`  row-parallel O / down projection: GEMM -> reduce-scatter -> all-gather in one kernel, with the
+  rank's partial LoRA delta riding along as an addend (replaces GEMM + NCCL all-reduce + LoRA collectives, call
+  sites C2 / C3 / C5 of the reference: `utils/layers.py:279-300, 329-374`).
+* `argmax_tp`       greedy sampling over vocabulary-parallel logits exchanging 16 bytes per row instead of
+  all-gathering the logits (C6, `layers/tensor_parallel.py:50-79`).
+
+Every device-side wait is bounded; `check()` reads the status word.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..ops import native
+
+
+class FusedCollectives:
+    MAX_TOKENS = 256
+
+    def __init__(self, tp, n_max: int, max_rows: int = 512):
+        import torch.distributed._symmetric_memory as symm
+        lib = native.load()
+        P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        lib.lx_ar_layout.argtypes = [I, I, I, ctypes.POINTER(L)]
+        lib.lx_ar_layout.restype = L
+        lib.lx_gemm_allreduce.argtypes = [P, L, P, L, P, P, L, I, I, I, P, I, I, ctypes.POINTER(L), I, P, I, P]
+        lib.lx_gemm_allreduce.restype = I
+        lib.lx_argmax_tp.argtypes = [P, L, I, I, I, P, P, P, I, I, ctypes.POINTER(L), I, P, P]
+        lib.lx_argmax_tp.restype = I
+        self.lib = lib
+        self.tp = tp
+        self.rank, self.world = tp.rank, tp.world_size
+        self.n_max, self.max_rows = n_max, max_rows
+        self.layout = (L * 8)()
+        nbytes = lib.lx_ar_layout(self.world, n_max, max_rows, self.layout)
+        self.buf = symm.empty(nbytes, dtype=torch.uint8, device=tp.device)
+        self.buf.zero_()
+        torch.cuda.synchronize(tp.device)
+        self.handle = symm.rendezvous(self.buf, tp.group)
+        ptrs = list(self.handle.buffer_ptrs)
+        self.peer_ptrs = (ctypes.c_ulonglong * self.world)(*ptrs)
+        out_off = self.layout[1]
+        self.out = self.buf[out_off: out_off + self.MAX_TOKENS * n_max * 2].view(torch.bfloat16).view(self.MAX_TOKENS, n_max)
+        self.ws = native.workspace(tp.device)
+        tp.barrier()
+        self.calls = 0
+
+    def gemm_allreduce(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                       addend: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """-> view [T, N] of the symmetric output buffer, valid until the next fused call."""
+        T, K = x.shape
+        N = w.shape[0]
+        assert T <= self.MAX_TOKENS and N <= self.n_max
+        rc = self.lib.lx_gemm_allreduce(x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), bias.data_ptr() if bias is not None else None,
+                                        addend.data_ptr() if addend is not None else None, addend.stride(0) if addend is not None else 0,
+                                        T, N, K, ctypes.cast(self.peer_ptrs, ctypes.c_void_p), self.rank, self.world, self.layout, self.n_max,
+                                        self.ws.status.data_ptr(), self.ws.num_sms, torch.cuda.current_stream().cuda_stream)
+        native._check(rc, "lx_gemm_allreduce")
+        self.calls += 1
+        return self.out[:T, :N]
+
+    def argmax_tp(self, logits: torch.Tensor, vocab_start: int, ids: torch.Tensor, logprobs: torch.Tensor):
+        T, V = logits.shape
+        rc = self.lib.lx_argmax_tp(logits.data_ptr(), logits.stride(0), T, V, vocab_start, ids.data_ptr(), logprobs.data_ptr(),
+                                   ctypes.cast(self.peer_ptrs, ctypes.c_void_p), self.rank, self.world, self.layout, self.max_rows,
+                                   self.ws.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        native._check(rc, "lx_argmax_tp")
+
+    def all_reduce(self, x: torch.Tensor):
+        return None      # plain all-reduces (embedding, large prefill activations) stay on NCCL
+
+    def check(self):
+        self.ws.check_status()
+
+
+def enable(tp, model, max_rows: int = 512) -> FusedCollectives:
+    if tp.world_size == 1:
+        raise ValueError("fused collectives need a tensor-parallel group")
+    fc = FusedCollectives(tp, n_max=model.hidden, max_rows=max_rows)
+    tp.fused = fc
+    return fc

@@ -82,9 +82,13 @@ class TensorParallel:
             return x
         self.nccl_calls += 1
         T, n = x.shape
-        out = torch.empty(self.world_size, T, n, dtype=x.dtype, device=x.device)
-        dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
-        return out.permute(1, 0, 2).reshape(T, self.world_size * n)
+        if x.is_cuda:
+            out = torch.empty(self.world_size * T, n, dtype=x.dtype, device=x.device)
+            dist.all_gather_into_tensor(out, x.contiguous(), group=self.group)
+            return out.view(self.world_size, T, n).permute(1, 0, 2).reshape(T, self.world_size * n)
+        parts = [torch.empty_like(x) for _ in range(self.world_size)]     # Gloo has no all_gather_into_tensor
+        dist.all_gather(parts, x.contiguous(), group=self.group)
+        return torch.cat(parts, dim=1)
 
     def barrier(self):
         if self.world_size > 1:

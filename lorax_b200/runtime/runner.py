@@ -282,18 +282,25 @@ class ModelRunner:
                 return b
         return self.buckets[-1]
 
-    def _decode_body(self, b: int, lora: bool):
+    def _decode_body(self, b: int, lora: bool, need_logits: bool = False):
         st = self.state
         nsplit = 1
         if self.is_cuda and b * self.model.nkv < 96:
             nsplit = max(1, min(8, 192 // max(b * self.model.nkv, 1)))
         # the table always has max_batch rows; a graph launches one CTA per possible tile of the bucket (unused: slot -1)
         tiles = LoraTiles(st.lora_tiles, b, 32) if (lora and self.tiles_valid) else None
+        fused = self.model.tp.fused if self.model.tp.world_size > 1 else None
+        fused_head = (fused is not None and not need_logits and b <= fused.max_rows
+                      and not (self.model.config.final_logit_softcapping or 0.0))
         inp = StepInputs(input_ids=st.input_ids[:b], positions=st.positions[:b], slots=st.slots[:b], is_prefill=False,
                          block_tables=st.block_tables[:b], ctx_lens=st.ctx_lens[:b], tok_slot=st.tok_slot[:b] if lora else None,
-                         head_tok_slot=st.tok_slot[:b] if lora else None, attn_nsplit=nsplit, lora_tiles=tiles)
+                         head_tok_slot=st.tok_slot[:b] if lora else None, attn_nsplit=nsplit, lora_tiles=tiles, local_logits=fused_head)
         logits = self.model.forward(inp, self.kv.layers)
-        self.model.ops.argmax_logprob(logits, st.next_ids[:b], st.logprobs[:b], softcap=self.model.config.final_logit_softcapping or 0.0)
+        if fused_head:
+            # vocabulary-parallel greedy head: 16 bytes per row and rank cross NVLink instead of the logits
+            fused.argmax_tp(logits, self.model.vocab_start, st.next_ids[:b], st.logprobs[:b])
+        else:
+            self.model.ops.argmax_logprob(logits, st.next_ids[:b], st.logprobs[:b], softcap=self.model.config.final_logit_softcapping or 0.0)
         return logits
 
     def _advance(self, b: int):
@@ -301,19 +308,19 @@ class ModelRunner:
         self.model.ops.advance_decode(st.input_ids[:b], st.next_ids[:b], st.positions[:b], st.ctx_lens[:b], st.slots[:b],
                                       st.block_tables[:b], self.page)
 
-    def capture(self, b: int, lora: bool):
-        key = (b, lora, self.tiles_valid)
+    def capture(self, b: int, lora: bool, need_logits: bool = False):
+        key = (b, lora, self.tiles_valid, need_logits)
         if key in self.graphs:
             return
         # warm up outside capture (lazy cudaFuncSetAttribute calls, workspace allocation)
         saved = [t.clone() for t in (self.state.input_ids, self.state.positions, self.state.ctx_lens, self.state.slots)]
-        self._decode_body(b, lora)
+        self._decode_body(b, lora, need_logits)
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
         from ..ops import native
         before = native.launch_count
         with torch.cuda.graph(g, pool=self.graph_pool):
-            logits = self._decode_body(b, lora)
+            logits = self._decode_body(b, lora, need_logits)
             self._advance(b)
         self.graph_kernels[key] = native.launch_count - before
         native.launch_count = before          # captured, not executed
@@ -339,13 +346,14 @@ class ModelRunner:
             ad.fence()
         logits = None
         if self.use_graphs:
-            key = (b, lora, self.tiles_valid)
-            self.capture(b, lora)
+            variant = need_logits and self.model.tp.world_size > 1      # only TP has two head variants
+            key = (b, lora, self.tiles_valid, variant)
+            self.capture(b, lora, variant)
             self.graphs[key].replay()
             self.replayed_launches += self.graph_kernels[key]
             logits = self.graph_out[key] if need_logits else None
         else:
-            logits = self._decode_body(b, lora)
+            logits = self._decode_body(b, lora, need_logits)
             self._advance(b)
         k = self.ring_pos
         self.ring_pos = (k + 1) % self.n_ring

@@ -1,0 +1,128 @@
+"""Worker for the tensor-parallel tests (launched with torch.distributed.run; rank 0 prints one JSON line).
+
+Checks, on every rank: (1) the TP=k forward of a tiny Llama with LoRA adapters equals the TP=1 forward of the same
+model (same seed -> same full weights), which is the rank-consistency requirement for the LoRA sharding scheme;
+(2) on GPUs, the fused GEMM + reduce-scatter + all-gather kernel and the vocabulary-parallel greedy head against
+fp32 references assembled with NCCL collectives, twice in a row (the counters are cumulative across launches)."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from lorax_b200.adapters.lora import random_adapter  # noqa: E402
+from lorax_b200.adapters.manager import AdapterManager  # noqa: E402
+from lorax_b200.config import tiny_llama  # noqa: E402
+from lorax_b200.models.decoder import DecoderModel  # noqa: E402
+from lorax_b200.parallel.tp import TensorParallel  # noqa: E402
+from lorax_b200.runtime.kv_cache import KVCache  # noqa: E402
+from lorax_b200.runtime.runner import ModelRunner, PrefillItem  # noqa: E402
+
+TARGETS = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
+
+
+def build(cfg, device, dtype, tp):
+    model = DecoderModel.random_init(cfg, device, dtype, seed=0, tp=tp)
+    mgr = AdapterManager(model, arena_bytes=64 << 20, host_bytes=128 << 20)
+    for i in range(2):
+        c, mm = random_adapter(cfg, r=8 * (i + 1), alpha=16, target_modules=TARGETS, seed=20 + i, std_a=0.05, std_b=0.05)
+        mgr.register(f"a{i}", c, mm)
+        assert mgr.load(i + 1, f"a{i}")
+    return model
+
+
+def run_model(model, prompts, ads, n_decode, graphs):
+    cfg = model.config
+    kv = KVCache(cfg.num_hidden_layers, 64, model.nkv, model.d, model.dtype, model.device)
+    r = ModelRunner(model, kv, max_batch=8, max_seq_tokens=256, max_prefill_tokens=1024, use_graphs=graphs)
+    blocks = [[1 + 4 * i + j for j in range(4)] for i in range(len(prompts))]
+    ids, _, logits = r.prefill([PrefillItem(p, 0, blocks[i], adapter_index=ads[i]) for i, p in enumerate(prompts)])
+    outs = [logits.float().cpu().clone()]
+    rows = [r.state.take_row(i) for i in range(len(prompts))]
+    r.install(rows, ids.tolist(), [len(p) for p in prompts], blocks, ads)
+    r.resort()
+    toks = [ids.tolist()]
+    for _ in range(n_decode):
+        k, b, logits = r.decode(need_logits=False)
+        idp, _ = r.wait(k)
+        toks.append(idp[:len(prompts)].tolist())
+    return outs, toks
+
+
+def main():
+    tp = TensorParallel.init_from_env()
+    dev = tp.device
+    cuda = dev.type == "cuda"
+    dtype = torch.bfloat16 if cuda else torch.float32
+    out = {"world": tp.world_size, "device": dev.type}
+    cfg = tiny_llama()
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (20, 33, 47)]
+    ads = [1, 0, 2]
+    # ---- TP=k model vs TP=1 model
+    full = build(cfg, dev, dtype, TensorParallel.single())
+    ref_logits, ref_toks = run_model(full, prompts, ads, 4, graphs=False)
+    for mode in (["nccl", "fused"] if cuda else ["gloo"]):
+        shard = build(cfg, dev, dtype, tp)
+        if mode == "fused":
+            from lorax_b200.parallel import fused
+            fused.enable(tp, shard)
+        else:
+            tp.fused = None
+        got_logits, got_toks = run_model(shard, prompts, ads, 4, graphs=cuda)
+        err = ((got_logits[0] - ref_logits[0]).norm() / ref_logits[0].norm()).item()
+        out[f"model_{mode}_logits_relerr"] = err
+        out[f"model_{mode}_first_tokens_equal"] = got_toks[0] == ref_toks[0]
+        out[f"model_{mode}_decode_tokens_equal"] = sum(a == b for a, b in zip(got_toks, ref_toks)) / len(ref_toks)
+        if mode == "fused":
+            tp.fused.check()
+            out["fused_calls"] = tp.fused.calls
+    # ---- kernels
+    if cuda:
+        from lorax_b200.parallel import fused as fz
+        fc = tp.fused
+        errs, eq = [], []
+        for it, (T, N, K) in enumerate([(5, 256, 128), (64, 256, 512), (200, 256, 192), (17, 256, 64)]):
+            gen = torch.Generator(device=dev).manual_seed(100 * it + tp.rank)
+            x = torch.randn(T, K, device=dev, dtype=dtype, generator=gen)
+            w = torch.randn(N, K, device=dev, dtype=dtype, generator=gen) / K ** 0.5
+            add = torch.randn(T, N, device=dev, dtype=dtype, generator=gen) * 0.1
+            res = fc.gemm_allreduce(x, w, None, add).clone()
+            part = x.float() @ w.float().t() + add.float()
+            dist.all_reduce(part)
+            torch.cuda.synchronize()
+            errs.append(((res.float() - part).norm() / part.norm()).item())
+            gathered = [torch.empty_like(res) for _ in range(tp.world_size)]
+            dist.all_gather(gathered, res)
+            eq.append(all(torch.equal(gathered[0], t) for t in gathered))      # every rank holds the same bits
+        fc.check()
+        out["gemm_allreduce_relerr"] = max(errs)
+        out["gemm_allreduce_ranks_identical"] = all(eq)
+        # vocabulary-parallel greedy head
+        ok = []
+        for it, T in enumerate([3, 40]):
+            gen = torch.Generator(device=dev).manual_seed(7 + it)           # same full logits on every rank
+            full_logits = torch.randn(T, 1000 * tp.world_size, device=dev, dtype=dtype, generator=gen)
+            local = full_logits[:, tp.rank * 1000:(tp.rank + 1) * 1000].contiguous()
+            ids = torch.empty(T, dtype=torch.int32, device=dev)
+            lps = torch.empty(T, dtype=torch.float32, device=dev)
+            fc.argmax_tp(local, tp.rank * 1000, ids, lps)
+            torch.cuda.synchronize()
+            want = full_logits.float().argmax(-1)
+            wlp = torch.log_softmax(full_logits.float(), -1).gather(1, want[:, None])[:, 0]
+            ok.append(bool(torch.equal(ids.long(), want)) and bool(torch.allclose(lps, wlp, atol=2e-3)))
+        fc.check()
+        out["argmax_tp_ok"] = all(ok)
+    flags = torch.tensor([1.0], device=dev if cuda else "cpu")
+    dist.all_reduce(flags)
+    if tp.rank == 0:
+        print("RESULT " + json.dumps(out), flush=True)
+    dist.barrier()
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()
