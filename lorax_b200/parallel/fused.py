@@ -28,7 +28,15 @@ class FusedCollectives:
     MAX_TOKENS = 256
 
     def __init__(self, tp, n_max: int, max_rows: int = 512):
+        import os
+        # plain peer mappings only: this library never issues multimem instructions, and memory that is not bound to an
+        # NVLink multicast object cannot fault peers if a rank dies
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         import torch.distributed._symmetric_memory as symm
+        try:
+            symm.set_backend("CUDA")
+        except Exception:
+            pass
         lib = native.load()
         P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
         lib.lx_ar_layout.argtypes = [I, I, I, ctypes.POINTER(L)]

@@ -170,3 +170,25 @@ def test_sampling_and_seed(stack):
     b = json.loads(_post(port, "/generate", {"inputs": "w9 w10", "parameters": p})[1])
     assert [t["id"] for t in a["details"]["tokens"]] == [t["id"] for t in b["details"]["tokens"]]
     assert a["details"]["seed"] == 7
+
+
+def test_python_client_sync_and_async(stack):
+    import asyncio
+    from lorax_b200.client import AsyncClient, Client
+    from lorax_b200.client.errors import ValidationError as ServerValidationError
+    c = Client(f"http://127.0.0.1:{stack['port']}")
+    assert c.health()
+    r = c.generate("w1 w2 w3", max_new_tokens=4, ignore_eos_token=True)
+    assert r.details.generated_tokens == 4 and len(r.details.tokens) == 4
+    toks = list(c.generate_stream("w1 w2 w3", max_new_tokens=4, ignore_eos_token=True))
+    assert [t.token.id for t in toks] == [t.id for t in r.details.tokens] and toks[-1].generated_text is not None
+    with pytest.raises(ServerValidationError):
+        c.generate("w1", max_new_tokens=100000)
+
+    async def go():
+        ac = AsyncClient(f"http://127.0.0.1:{stack['port']}")
+        outs = await asyncio.gather(*[ac.generate(f"w{i} w2", max_new_tokens=3, ignore_eos_token=True) for i in range(4)])
+        streamed = [t async for t in ac.generate_stream("w1 w2 w3", max_new_tokens=4, ignore_eos_token=True)]
+        return outs, streamed
+    outs, streamed = asyncio.run(go())
+    assert all(o.details.generated_tokens == 3 for o in outs) and len(streamed) == 4
