@@ -194,8 +194,10 @@ class DecoderModel:
                 E = c.num_local_experts
                 lw.router_w = put(rnd(E, H))
                 w1, w3, w2 = rnd(E, I, H), rnd(E, I, H), rnd(E, H, I)
-                lw.experts_w13 = put(torch.cat([w1, w3], 1))
-                lw.experts_w2 = put(w2)
+                el = max(E // ws, 1)                 # expert parallel: rank r owns experts [r*el, (r+1)*el)
+                esl = slice(rk * el, (rk + 1) * el) if el < E else slice(0, E)
+                lw.experts_w13 = put(torch.cat([w1, w3], 1)[esl])
+                lw.experts_w2 = put(w2[esl])
             else:
                 ib = I // ws
                 up = rnd(I, H)

@@ -1,0 +1,64 @@
+"""Mixture-of-experts feed-forward (Mixtral / DBRX style top-k routing).
+
+Routing math follows the reference (`custom_modeling/flash_mixtral_modeling.py:449-459`): softmax over all experts,
+keep the top k, renormalise the kept weights.  Expert weights are laid out expert-parallel: rank r holds experts
+[r*E/ws, (r+1)*E/ws) in full (the reference shards every expert's FFN dimension across ranks instead,
+`flash_mixtral_modeling.py:202-233`).  Hidden states are replicated after attention, so "dispatch" is a local
+row selection and "combine" is the sum over ranks of the per-expert contributions.
+
+Two execution shapes:
+  * decode-sized batches: every local expert runs over all tokens and the routing weight (zero for unrouted tokens)
+    scales its output -- static shapes, CUDA-graph friendly, and the expert weights are read once either way;
+  * prefill: tokens are gathered per expert, so each expert only computes the rows routed to it.
+"""
+
+from __future__ import annotations
+
+import torch
+
+DENSE_MAX_TOKENS = 256
+
+
+def route(router_logits: torch.Tensor, k: int):
+    """-> dense routing weights [T, E] (zero where an expert is not selected)."""
+    probs = torch.softmax(router_logits.float(), dim=-1)
+    topv, topi = probs.topk(k, dim=-1)
+    topv = topv / topv.sum(-1, keepdim=True)
+    w = torch.zeros_like(probs)
+    w.scatter_(1, topi, topv)
+    return w
+
+
+def moe_forward(model, x: torch.Tensor, lw, li: int, inp) -> torch.Tensor:
+    c, ops = model.config, model.ops
+    E = c.num_local_experts
+    ws, rk = model.tp.world_size, model.tp.rank
+    e_local = lw.experts_w13.shape[0]
+    e0 = rk * e_local if e_local < E else 0
+    T = x.shape[0]
+    # the router is tiny (E output features): plain matmul keeps it exact across ranks
+    router_logits = x.float() @ lw.router_w.float().t()
+    w = route(router_logits, c.num_experts_per_tok)
+    out = torch.zeros(T, model.hidden, dtype=torch.float32, device=x.device)
+    I = c.intermediate_size
+    for j in range(e_local):
+        e = e0 + j
+        we = w[:, e]
+        if T <= DENSE_MAX_TOKENS:
+            gu = ops.gemm(x, lw.experts_w13[j])
+            a = ops.act_mul(gu, I, c.hidden_act, gated=True)
+            dn = ops.gemm(a, lw.experts_w2[j])
+            out.addcmul_(dn.float(), we[:, None])
+        else:
+            idx = torch.nonzero(we > 0, as_tuple=False)[:, 0]
+            if idx.numel() == 0:
+                continue
+            xe = x.index_select(0, idx).contiguous()
+            gu = ops.gemm(xe, lw.experts_w13[j])
+            a = ops.act_mul(gu, I, c.hidden_act, gated=True)
+            dn = ops.gemm(a, lw.experts_w2[j])
+            out.index_add_(0, idx, dn.float() * we.index_select(0, idx)[:, None])
+    out = out.to(x.dtype)
+    if ws > 1 and e_local < E:
+        out = model.tp.all_reduce(out)
+    return out
