@@ -15,6 +15,10 @@
 //            then bumps each rank's completion counter;
 //   phase C  a rank leaves the kernel when its completion counter shows that all of its output has landed.
 //
+// Small batches (<= 64 tokens) use a one-hop variant of the same kernel: every rank stores its partial tiles into
+// every rank's receive buffer and every rank reduces all tiles itself.  That moves `world` times more bytes, which is
+// irrelevant at this size, and removes the second NVLink round trip, which is what decode latency is made of.
+//
 // `addend` carries this rank's partial LoRA delta (x_r A_r^T) B^T, so the LoRA intermediate is reduced by the same
 // reduce-scatter and no separate collective is needed for it.
 //
@@ -32,11 +36,14 @@ constexpr int kArBK = 64;
 constexpr int kArThreads = 192;
 constexpr int kArMaxRanks = 8;
 constexpr int kArMaxTokens = 256;
-constexpr int kArTokChunk = 32;
+constexpr int kArMaxSlots = 16;       // partial-sum slots per owned tile: world * K-splits
+constexpr int kArTokChunkOne = 8;      // tokens per phase-B work item, one-hop mode
+constexpr int kArTokChunkTwo = 32;     // ... two-hop mode (fewer, fatter items: each one ends with a system fence)
+constexpr int kArOneShotTokens = 64;   // batches up to this size use the one-hop variant
 
 // Layout of the symmetric communication buffer (identical on every rank).
 struct ArLayout {
-  long long recv_off;      // float  [world][tiles_owned_max][kArMaxTokens][128]
+  long long recv_off;      // float  [kArMaxSlots][tiles_owned_max][kArMaxTokens][128]   slot = rank * ksplit + split
   long long out_off;       // bf16   [kArMaxTokens][N_max]
   long long arrived_off;   // int    [tiles_max]
   long long ctrl_off;      // int    [8]: 0 done, 2 cta_done (3 argmax arrivals, 5 argmax cta_done)
@@ -52,6 +59,10 @@ struct ArParams {
   int rank, world;
   int T, N, K;
   int umma_n;
+  int ttiles;                          // token tiles of BN tokens per feature tile (phase A parallelism)
+  int ksplit;                          // K splits per (feature tile, token tile): their partials are summed by the owner too
+  int oneshot;                         // 1: partials go to EVERY rank and every rank reduces all tiles (one NVLink hop)
+  int tok_cap, tiles_cap;              // strides of the receive buffer in this mode
   const __nv_bfloat16* bias;
   const __nv_bfloat16* addend;         // optional [T, lda] local partial to add before the reduction
   long long lda;
@@ -108,7 +119,10 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
   int* targets = reinterpret_cast<int*>(local + p.lay.target_off);
   const int num_tiles = (p.N + kArBM - 1) / kArBM;
   const int kblocks = (p.K + kArBK - 1) / kArBK;
-  const int n_chunks = (p.T + kArTokChunk - 1) / kArTokChunk;
+  const int tok_chunk = p.oneshot ? kArTokChunkOne : kArTokChunkTwo;
+  const int n_chunks = (p.T + tok_chunk - 1) / tok_chunk;
+  const int per_tile = p.ttiles * p.ksplit;
+  const int num_units = num_tiles * per_tile;      // phase A work: (feature tile, token tile, K split)
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -127,13 +141,15 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       const uint64_t pol_w = policy_evict_first(), pol_x = policy_evict_last();
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        for (int kb = 0; kb < kblocks; ++kb) {
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        const int t = u / per_tile, j = (u % per_tile) / p.ksplit, sp = u % p.ksplit;
+        const int kb0 = (int)((long long)kblocks * sp / p.ksplit), kb1 = (int)((long long)kblocks * (sp + 1) / p.ksplit);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { report_status(p.status, kTimeoutEmptyBarrier, t); *abort_flag = 1; ok = false; break; }
           uint8_t* sa = smem + stage * S::kStage;
           mbar_expect_tx(&full_bar[stage], S::kStage);
           tma_load_2d_hint(sa, &tmap_w, &full_bar[stage], kb * kArBK, t * kArBM, pol_w);
-          tma_load_2d_hint(sa + S::kABytes, &tmap_x, &full_bar[stage], kb * kArBK, 0, pol_x);
+          tma_load_2d_hint(sa + S::kABytes, &tmap_x, &full_bar[stage], kb * kArBK, j * BN, pol_x);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -146,17 +162,19 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       int acc = 0;
       uint32_t acc_phase[2] = {0, 0};
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int t = blockIdx.x; t < num_units && ok; t += gridDim.x) {
         if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1, abort_flag)) { report_status(p.status, kTimeoutTmemEmpty, t); *abort_flag = 1; break; }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-        for (int kb = 0; kb < kblocks; ++kb) {
+        const int sp = t % p.ksplit;
+        const int kb0 = (int)((long long)kblocks * sp / p.ksplit), kb1 = (int)((long long)kblocks * (sp + 1) / p.ksplit);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { report_status(p.status, kTimeoutFullBarrier, t); *abort_flag = 1; ok = false; break; }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * S::kStage);
           const uint64_t da = make_desc_k_sw128(sa), db = make_desc_k_sw128(sa + S::kABytes);
 #pragma unroll
-          for (int k = 0; k < kArBK / 16; ++k) umma_f16_ss(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < kArBK / 16; ++k) umma_f16_ss(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           tc_commit(&empty_bar[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -176,13 +194,14 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     uint32_t acc_phase[2] = {0, 0};
     bool ok = true;
     // ---- phase A: ship partial tiles to their owners
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+      const int t = u / per_tile, tok_base = ((u % per_tile) / p.ksplit) * BN, sp = u % p.ksplit;
       if (!mbar_wait(&tmem_full[acc], acc_phase[acc], abort_flag)) { report_status(p.status, kTimeoutTmemFull, t); *abort_flag = 1; ok = false; break; }
       tc_fence_after();
       acc_phase[acc] ^= 1;
-      const int owner = t % p.world, t_local = t / p.world;
-      float* dst = reinterpret_cast<float*>(p.peers[owner] + p.lay.recv_off) +
-                   (((long long)p.rank * p.lay.tiles_owned_max + t_local) * kArMaxTokens) * kArBM + f;
+      const int owner = t % p.world, t_local = p.oneshot ? t : t / p.world;
+      const long long slot_off = (((long long)(p.rank * p.ksplit + sp) * p.tiles_cap + t_local) * p.tok_cap) * kArBM + f;
+      float* dst = reinterpret_cast<float*>(p.peers[owner] + p.lay.recv_off) + slot_off;
       const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
       const int n = t * kArBM + f;
       constexpr int CH = BN >= 32 ? 32 : 16;
@@ -204,49 +223,65 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
         }
 #pragma unroll
         for (int q = 0; q < CH; ++q) {
-          const int tok = c + q;
+          const int tok = tok_base + c + q;
           if (tok < p.T) {
             float val = v[q];
-            if (p.addend != nullptr && n < p.N) val += __bfloat162float(p.addend[(long long)tok * p.lda + n]);
-            dst[(long long)tok * kArBM] = val;           // peer store: 32 lanes -> 128 contiguous bytes
+            if (p.addend != nullptr && sp == 0 && n < p.N) val += __bfloat162float(p.addend[(long long)tok * p.lda + n]);
+            if (!p.oneshot) {
+              dst[(long long)tok * kArBM] = val;         // peer store: 32 lanes -> 128 contiguous bytes
+            } else {
+#pragma unroll
+              for (int r = 0; r < kArMaxRanks; ++r)
+                if (r < p.world) reinterpret_cast<float*>(p.peers[r] + p.lay.recv_off)[slot_off + (long long)tok * kArBM] = val;
+            }
           }
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      __threadfence_system();
+      // the barrier orders every thread's peer stores before the signalling threads, whose cumulative system-scope
+      // fence then publishes them before the arrival is counted
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et == 0) red_release_sys_add(reinterpret_cast<int*>(p.peers[owner] + p.lay.arrived_off) + t, 1);
+      if (et < p.world) __threadfence_system();
+      if (!p.oneshot) {
+        if (et == 0) red_release_sys_add(reinterpret_cast<int*>(p.peers[owner] + p.lay.arrived_off) + t, 1);
+      } else if (et < p.world) {
+        red_release_sys_add(reinterpret_cast<int*>(p.peers[et] + p.lay.arrived_off) + t, 1);
+      }
       acc ^= 1;
     }
     // ---- phase B: reduce the tiles this rank owns and broadcast the result
-    const int n_owned = (num_tiles - p.rank + p.world - 1) / p.world;
+    const int n_owned = p.oneshot ? num_tiles : (num_tiles - p.rank + p.world - 1) / p.world;
     const int items = n_owned * n_chunks;
     const float* recv = reinterpret_cast<const float*>(local + p.lay.recv_off);
     const int* arrived = reinterpret_cast<const int*>(local + p.lay.arrived_off);
     for (int it = blockIdx.x; it < items && ok; it += gridDim.x) {
       const int t_local = it / n_chunks, chunk = it % n_chunks;
-      const int t = t_local * p.world + p.rank;
+      const int t = p.oneshot ? t_local : t_local * p.world + p.rank;
       if (et == 0) {
-        if (!wait_counter(arrived + t, targets[t] + p.world, p.status, 1000 + t)) *abort_flag = 1;
+        if (!wait_counter(arrived + t, targets[t] + p.world * per_tile, p.status, 1000 + t)) *abort_flag = 1;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (*abort_flag) { ok = false; break; }
       const int n = t * kArBM + f;
       const float b = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
-      const int tok0 = chunk * kArTokChunk, tok1 = min(tok0 + kArTokChunk, p.T);
+      const int tok0 = chunk * tok_chunk, tok1 = min(tok0 + tok_chunk, p.T);
       for (int tok = tok0; tok < tok1; tok += 4) {
         float s[4] = {b, b, b, b};
 #pragma unroll
-        for (int r = 0; r < kArMaxRanks; ++r) {
-          if (r < p.world) {
-            const float* src = recv + (((long long)r * p.lay.tiles_owned_max + t_local) * kArMaxTokens + tok) * kArBM + f;
+        for (int r = 0; r < kArMaxSlots; ++r) {
+          if (r < p.world * p.ksplit) {
+            const float* src = recv + (((long long)r * p.tiles_cap + t_local) * p.tok_cap + tok) * kArBM + f;
 #pragma unroll
             for (int q = 0; q < 4; ++q) if (tok + q < tok1) s[q] += __ldcg(src + (long long)q * kArBM);
           }
         }
-        if (n < p.N) {
+        if (n < p.N && p.oneshot) {
+          __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(local + p.lay.out_off) + n;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) if (tok + q < tok1) o[(long long)(tok + q) * p.lay.n_max] = __float2bfloat16(s[q]);
+        } else if (n < p.N) {
 #pragma unroll
           for (int r = 0; r < kArMaxRanks; ++r) {
             if (r < p.world) {
@@ -257,12 +292,16 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
           }
         }
       }
-      __threadfence_system();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et < p.world) red_release_sys_add(reinterpret_cast<int*>(p.peers[et] + p.lay.ctrl_off), 1);
+      if (!p.oneshot) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et < p.world) {
+          __threadfence_system();
+          red_release_sys_add(reinterpret_cast<int*>(p.peers[et] + p.lay.ctrl_off), 1);
+        }
+      }
     }
-    // ---- phase C: my whole output has been written by its owners
-    if (et == 0 && ok) {
+    // ---- phase C: my whole output has been written by its owners (not needed when every rank reduced for itself)
+    if (et == 0 && ok && !p.oneshot) {
       if (!wait_counter(ctrl, targets[p.lay.tiles_max] + num_tiles * n_chunks, p.status, 2000)) *abort_flag = 1;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -278,8 +317,9 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     if (prev == (int)gridDim.x - 1) {
       // every CTA of this launch has read its targets: move them to where the counters stand after this launch
       ctrl[2] = 0;
-      for (int t = 0; t < num_tiles; ++t) targets[t] += p.world;
-      targets[p.lay.tiles_max] += num_tiles * n_chunks;
+      for (int t = 0; t < num_tiles; ++t)
+        if (p.oneshot || t % p.world == p.rank) targets[t] += p.world * per_tile;     // only counters that received arrivals
+      if (!p.oneshot) targets[p.lay.tiles_max] += num_tiles * n_chunks;
       __threadfence();
     }
   }
@@ -403,9 +443,11 @@ static int launch_ar(const CUtensorMap& tw, const CUtensorMap& tx, const ArParam
     configured = true;
   }
   const int num_tiles = (p.N + kArBM - 1) / kArBM;
-  const int n_chunks = (p.T + kArTokChunk - 1) / kArTokChunk;
-  const int n_owned = (num_tiles + p.world - 1) / p.world;
-  int grid = num_tiles > n_owned * n_chunks ? num_tiles : n_owned * n_chunks;
+  const int tok_chunk = p.oneshot ? kArTokChunkOne : kArTokChunkTwo;
+  const int n_chunks = (p.T + tok_chunk - 1) / tok_chunk;
+  const int n_owned = p.oneshot ? num_tiles : (num_tiles + p.world - 1) / p.world;
+  const int units = num_tiles * p.ttiles * p.ksplit;
+  int grid = units > n_owned * n_chunks ? units : n_owned * n_chunks;
   if (grid > num_sms) grid = num_sms;          // all CTAs must be co-resident: they wait on peers
   gemm_allreduce_kernel<BN, STAGES><<<grid, kArThreads, S::kTotal, s>>>(tw, tx, p);
   return -(int)cudaGetLastError();
@@ -424,7 +466,11 @@ long long lx_ar_layout(int world, int n_max, int max_rows, long long* layout_out
   const int tiles_max = (n_max + kArBM - 1) / kArBM;
   const int tiles_owned_max = (tiles_max + world - 1) / world;
   long long off = 0;
-  layout_out[0] = off; off += (long long)world * tiles_owned_max * kArMaxTokens * kArBM * 4;
+  {
+    const long long two_shot = (long long)kArMaxSlots * tiles_owned_max * kArMaxTokens * kArBM * 4;
+    const long long one_shot = (long long)kArMaxSlots * tiles_max * kArOneShotTokens * kArBM * 4;
+    layout_out[0] = off; off += two_shot > one_shot ? two_shot : one_shot;
+  }
   layout_out[1] = off; off += (long long)kArMaxTokens * n_max * 2;
   off = (off + 255) & ~255ll;
   layout_out[2] = off; off += (long long)tiles_max * 4;
@@ -454,12 +500,26 @@ int lx_gemm_allreduce(const void* x, long long ldx, const void* w, long long ldw
   p.lay.tiles_owned_max = (int)layout[4]; p.lay.n_max = n_max;
   p.lay.target_off = layout[6]; p.lay.tiles_max = (int)layout[7];
   p.rank = rank; p.world = world; p.T = T; p.N = N; p.K = K;
-  p.umma_n = (T + 15) / 16 * 16;
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.addend = reinterpret_cast<const __nv_bfloat16*>(addend);
   p.lda = lda;
   p.status = status;
-  const int bn = T <= 16 ? 16 : T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  // token tile: the whole batch when it is small, otherwise 64-token tiles so that phase A spreads over the machine
+  // (N / 128 feature tiles alone would occupy a quarter of the SMs)
+  const int bn = T <= 16 ? 16 : T <= 32 ? 32 : 64;
+  p.ttiles = (T + bn - 1) / bn;
+  p.umma_n = T >= bn ? bn : (T + 15) / 16 * 16;
+  p.oneshot = T <= kArOneShotTokens ? 1 : 0;
+  p.tok_cap = p.oneshot ? kArOneShotTokens : kArMaxTokens;
+  p.tiles_cap = p.oneshot ? p.lay.tiles_max : p.lay.tiles_owned_max;
+  // K splits: their partial sums travel to the owner exactly like the other ranks' partials, so splitting K costs no
+  // extra pass; use it to spread short batches over the machine
+  {
+    const int tiles = (N + kArBM - 1) / kArBM, kblocks = (K + kArBK - 1) / kArBK;
+    int ks = 1;
+    while (tiles * p.ttiles * ks * 2 <= num_sms && kblocks / (ks * 2) >= 4 && world * ks * 2 <= kArMaxSlots) ks *= 2;
+    p.ksplit = ks;
+  }
   CUtensorMap tw, tx;
   if (make_map(&tw, w, N, K, ldw, kArBM)) return -3;
   if (make_map(&tx, x, T, K, ldx, bn)) return -4;
@@ -467,9 +527,7 @@ int lx_gemm_allreduce(const void* x, long long ldx, const void* w, long long ldw
   switch (bn) {
     case 16: return launch_ar<16, 8>(tw, tx, p, num_sms, s);
     case 32: return launch_ar<32, 8>(tw, tx, p, num_sms, s);
-    case 64: return launch_ar<64, 8>(tw, tx, p, num_sms, s);
-    case 128: return launch_ar<128, 6>(tw, tx, p, num_sms, s);
-    default: return launch_ar<256, 4>(tw, tx, p, num_sms, s);
+    default: return launch_ar<64, 8>(tw, tx, p, num_sms, s);
   }
 }
 
