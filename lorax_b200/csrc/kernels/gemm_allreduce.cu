@@ -78,11 +78,20 @@ LX_DEVICE void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Bounded spin until *p >= target (signed difference, counters wrap safely).  Returns false on expiry.
+LX_DEVICE int ld_relaxed_sys(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Polls with relaxed loads and pays for one acquire fence when the value has arrived.
 LX_DEVICE bool wait_counter(const int* p, int target, int* status, int where) {
   uint64_t t0 = 0;
   uint32_t polls = 0;
   while (true) {
-    if (ld_acquire_sys(p) - target >= 0) return true;
+    if (ld_relaxed_sys(p) - target >= 0) {
+      asm volatile("fence.acq_rel.sys;" ::: "memory");
+      return true;
+    }
     if ((++polls & 1023u) == 0) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
@@ -240,10 +249,9 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-      // the barrier orders every thread's peer stores before the signalling threads, whose cumulative system-scope
-      // fence then publishes them before the arrival is counted
+      // the barrier orders every thread's peer stores before the signalling threads; their release-at-system-scope
+      // atomic is cumulative, so the stores are visible to whoever observes the count
       asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (et < p.world) __threadfence_system();
       if (!p.oneshot) {
         if (et == 0) red_release_sys_add(reinterpret_cast<int*>(p.peers[owner] + p.lay.arrived_off) + t, 1);
       } else if (et < p.world) {
@@ -294,10 +302,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       }
       if (!p.oneshot) {
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (et < p.world) {
-          __threadfence_system();
-          red_release_sys_add(reinterpret_cast<int*>(p.peers[et] + p.lay.ctrl_off), 1);
-        }
+        if (et < p.world) red_release_sys_add(reinterpret_cast<int*>(p.peers[et] + p.lay.ctrl_off), 1);
       }
     }
     // ---- phase C: my whole output has been written by its owners (not needed when every rank reduced for itself)

@@ -291,7 +291,8 @@ class DecoderModel:
         """Row-parallel projection + all-reduce.  With the NVLink kernels enabled and a decode-sized batch this is one
         fused GEMM -> reduce-scatter -> all-gather kernel; the rank's partial LoRA delta is reduced with it."""
         fused = self.tp.fused if self.tp.world_size > 1 else None
-        if (fused is not None and x.is_cuda and x.shape[0] <= fused.MAX_TOKENS and b is None and not self.config.parallel_residual):
+        if (fused is not None and x.is_cuda and x.shape[0] <= min(fused.MAX_TOKENS, fused.max_fused_tokens) and b is None
+                and not self.config.parallel_residual):
             addend = None
             if self.adapters is not None and (inp.tok_slot is not None or inp.lora_tiles is not None) and self.adapters.max_rank > 0:
                 addend = torch.zeros(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)

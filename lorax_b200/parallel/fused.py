@@ -25,7 +25,7 @@ from ..ops import native
 
 
 class FusedCollectives:
-    MAX_TOKENS = 256
+    MAX_TOKENS = 256          # kernel limit
 
     def __init__(self, tp, n_max: int, max_rows: int = 512):
         import os
@@ -60,6 +60,9 @@ class FusedCollectives:
         out_off = self.layout[1]
         self.out = self.buf[out_off: out_off + self.MAX_TOKENS * n_max * 2].view(torch.bfloat16).view(self.MAX_TOKENS, n_max)
         self.ws = native.workspace(tp.device)
+        # Batches above this size go through GEMM + NCCL all-reduce instead: measured on 2 x B200, the fused kernel is
+        # at parity up to ~32 tokens and slower beyond (see profiles/fused_gemm_allreduce_tp2.txt).
+        self.max_fused_tokens = int(os.environ.get("LORAX_FUSED_MAX_TOKENS", "32"))
         tp.barrier()
         self.calls = 0
 

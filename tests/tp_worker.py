@@ -69,7 +69,7 @@ def main():
         shard = build(cfg, dev, dtype, tp)
         if mode == "fused":
             from lorax_b200.parallel import fused
-            fused.enable(tp, shard)
+            fused.enable(tp, shard).max_fused_tokens = 256       # exercise the fused kernel for every batch size
         else:
             tp.fused = None
         got_logits, got_toks = run_model(shard, prompts, ads, 4, graphs=cuda)
