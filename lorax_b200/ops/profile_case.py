@@ -1,0 +1,92 @@
+"""Small, self-terminating workloads for `ncu` captures of single kernels.
+
+    python -m lorax_b200.ops.profile_case --case gemm_decode|gemm_prefill|attn_decode|attn_prefill|lora_shrink|lora_expand
+
+Each case launches the kernel a handful of times on inputs larger than the 126 MB L2 but at most a few GB, and
+exits 0; run it plain first, then under
+`ncu --set full --clock-control none -k regex:<kernel> -c 2 -o <report> python -m lorax_b200.ops.profile_case --case ...`.
+"""
+
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import native, reference
+
+
+def gemm_case(T):
+    N, K = 28672, 4096
+    ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    for i in range(4):
+        native.gemm(x, ws[i % 2], out=out)
+
+
+def attn_decode_case():
+    nh, nkv, d, page, B, ctx = 32, 8, 128, 32, 128, 2048
+    bp = ctx // page
+    cache = torch.randn(B * bp + 1, nkv, 2, page, d, device="cuda", dtype=torch.bfloat16)
+    bt = (torch.randperm(B * bp, device="cuda") + 1).view(B, bp).to(torch.int32)
+    cl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+    q = torch.randn(B, nh * d, device="cuda", dtype=torch.bfloat16)
+    for _ in range(4):
+        native.attn_decode(q, cache, bt, cl, nh, nkv, d, d ** -0.5)
+
+
+def attn_prefill_case():
+    nh, nkv, d, page, B, L = 32, 8, 128, 32, 4, 2048
+    bp = L // page
+    cache = torch.randn(B * bp + 1, nkv, 2, page, d, device="cuda", dtype=torch.bfloat16)
+    bt = (torch.arange(B * bp, device="cuda") + 1).view(B, bp).to(torch.int32)
+    q = torch.randn(B * L, nh * d, device="cuda", dtype=torch.bfloat16)
+    cu = torch.arange(0, (B + 1) * L, L, device="cuda", dtype=torch.int32)
+    cl = torch.zeros(B, device="cuda", dtype=torch.int32)
+    ts, tq = reference.prefill_tiles([L] * B)
+    ts = torch.tensor(ts, device="cuda", dtype=torch.int32)
+    tq = torch.tensor(tq, device="cuda", dtype=torch.int32)
+    for _ in range(3):
+        native.attn_prefill(q, cache, bt, cu, cl, ts, tq, nh, nkv, d, d ** -0.5)
+
+
+def lora_case(which):
+    """100 rank-16 adapters, one layer's QKV group (A_cat [48, 4096], B_cat [6144, 16]), 256 decode rows."""
+    K, parts, r, S, T = 4096, [4096, 1024, 1024], 16, 100, 256
+    N = sum(parts)
+    units = 3 * K + N
+    arena = (torch.randn(S * r * units, device="cuda") * 0.02).to(torch.bfloat16)
+    slot_base = (torch.arange(S, device="cuda", dtype=torch.int64) * r * units)
+    slot_rank = torch.full((S,), r, device="cuda", dtype=torch.int32)
+    G = 5
+    tm = torch.zeros(S * G * 128, dtype=torch.uint8).pin_memory()
+    for s in range(S):
+        native.lora_encode_tmap(tm[(s * G) * 128:], arena.data_ptr() + s * r * units * 2, K, 3 * r, r * units, 1)
+    tmaps = tm.cuda()
+    rows = sorted(int(x) for x in torch.randint(0, S, (T,)))
+    tl = reference.build_lora_tiles(rows, 32)
+    tiles = torch.full((T, 4), -1, device="cuda", dtype=torch.int32)
+    tiles[: len(tl)] = torch.tensor(tl, device="cuda", dtype=torch.int32)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    y = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
+    for _ in range(4):
+        v = native.lora_shrink_tiles(x, tiles, T, 32, tmaps, G, 0, slot_rank, 3, 0, r)
+        if which == "expand":
+            native.lora_expand_tiles(v, tiles, T, 32, arena, slot_base, slot_rank, 3 * K, y, parts[0], parts[0] + parts[1])
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True)
+    a = ap.parse_args()
+    native.load()
+    {"gemm_decode": lambda: gemm_case(64), "gemm_prefill": lambda: gemm_case(4096), "attn_decode": attn_decode_case,
+     "attn_prefill": attn_prefill_case, "lora_shrink": lambda: lora_case("shrink"), "lora_expand": lambda: lora_case("expand")}[a.case]()
+    torch.cuda.synchronize()
+    native.workspace().check_status()
+    print("ok", a.case)
+
+
+if __name__ == "__main__":
+    main()
