@@ -286,30 +286,46 @@ class AdapterManager:
         return adapter_index in self.resident
 
     # ------------------------------------------------------------------ compute
-    def apply(self, ops, x: torch.Tensor, y: torch.Tensor, tok_slot: Optional[torch.Tensor], group: str, layer: int,
-              tiles: Optional[LoraTiles] = None):
-        """y += LoRA_{slot(t)}(x) for the projection group: one shrink and one expand launch.
+    def shrink(self, ops, x: torch.Tensor, tok_slot: Optional[torch.Tensor], group: str, layer: int,
+               tiles: Optional[LoraTiles] = None):
+        """v = x A_cat(slot(t))^T for the projection group (one launch) -> the descriptor `ops.gemm(..., lora=)` takes to
+        add the delta in its epilogue, or None when no row of the step has an adapter.
 
-        With a tile table (rows grouped by adapter) the shrink runs on the tensor cores; without one, the
-        per-token kernels are used (rows in any order)."""
-        if self.max_rank == 0:
-            return
+        With a tile table (rows grouped by adapter) the shrink runs on the tensor cores; without one, the per-token
+        kernel is used (rows in any order)."""
+        from ..ops.native import LoraEpilogue
+        if self.max_rank == 0 or tok_slot is None:
+            return None
         gi = self.layout.groups.get(group)
         if gi is None:
-            return
+            return None
         nparts = len(gi.parts)
         n0, n1 = gi.bounds
         offA, offB = self.layout.unit_off(group, layer, "A"), self.layout.unit_off(group, layer, "B")
         if tiles is not None:
             if tiles.num_tiles == 0:
-                return
+                return None
             if self.is_cuda:
                 v = ops.lora_shrink_tiles(x, tiles.table, tiles.num_tiles, tiles.max_rows, self.slot_tmaps, self.groups_per_slot,
                                           TMAP_GROUPS.index(group), self.slot_rank, nparts, 0 if group == LM_HEAD else layer, self.max_rank)
             else:
                 v = ops.lora_shrink_tiles(x, tiles.table, tiles.num_tiles, tiles.max_rows, self.arena, self.slot_base, self.slot_rank,
                                           offA, nparts, self.max_rank)
-            ops.lora_expand_tiles(v, tiles.table, tiles.num_tiles, tiles.max_rows, self.arena, self.slot_base, self.slot_rank, offB, y, n0, n1)
+        else:
+            v = ops.lora_shrink(x, tok_slot, self.arena, self.slot_base, self.slot_rank, offA, nparts, self.max_rank)
+        return LoraEpilogue(v, tok_slot, self.arena, self.slot_base, self.slot_rank, offB, n0, n1)
+
+    def expand(self, ops, epi, y: torch.Tensor, tiles: Optional[LoraTiles] = None):
+        """y += v B_cat(slot(t))^T: the second half of the LoRA delta as its own launch (`epi` comes from `shrink`)."""
+        if epi is None:
             return
-        v = ops.lora_shrink(x, tok_slot, self.arena, self.slot_base, self.slot_rank, offA, nparts, self.max_rank)
-        ops.lora_expand(v, tok_slot, self.arena, self.slot_base, self.slot_rank, offB, y, n0, n1)
+        if tiles is not None:
+            ops.lora_expand_tiles(epi.v[: y.shape[0]], tiles.table, tiles.num_tiles, tiles.max_rows, epi.arena, epi.slot_base, epi.slot_rank,
+                                  epi.unit_off, y, epi.n0, epi.n1)
+        else:
+            ops.lora_expand(epi.v, epi.tok_slot, epi.arena, epi.slot_base, epi.slot_rank, epi.unit_off, y, epi.n0, epi.n1)
+
+    def apply(self, ops, x: torch.Tensor, y: torch.Tensor, tok_slot: Optional[torch.Tensor], group: str, layer: int,
+              tiles: Optional[LoraTiles] = None):
+        """y += LoRA_{slot(t)}(x) for the projection group: one shrink and one expand launch."""
+        self.expand(ops, self.shrink(ops, x, tok_slot, group, layer, tiles=tiles), y, tiles=tiles)

@@ -35,10 +35,12 @@ struct ShrinkTcParams {
   int num_slots;
   int nparts;                      // R = nparts * rank
   int layer;
-  float* v;                        // [ksplit][v_rows][ldv] fp32 partial sums (the expand adds the splits up)
+  float* v;                        // [ksplit][v_rows][ldv] fp32 partial sums of the K splits (unused when ksplit == 1)
   int ldv;
   long long v_split_stride;        // elements between two K-splits
   int ksplit;
+  float* v_final;                  // [v_rows][ldv] the result: the last split CTA of a tile sums the partials in split order
+  int* counters;                   // one arrival counter per (tile, row chunk), zero between launches
   int K, T;
   int* status;
 };
@@ -90,7 +92,8 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const ShrinkTc
   const int kb_begin = (int)((long long)kblocks_all * blockIdx.z / p.ksplit);
   const int kb_end = (int)((long long)kblocks_all * (blockIdx.z + 1) / p.ksplit);
   const int kblocks = kb_end - kb_begin;
-  float* __restrict__ vout = p.v + (long long)blockIdx.z * p.v_split_stride;
+  float* __restrict__ vout = p.ksplit > 1 ? p.v + (long long)blockIdx.z * p.v_split_stride : p.v_final;
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -171,6 +174,42 @@ lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const ShrinkTc
           }
         }
       }
+      if (p.ksplit > 1) {
+        // The K splits of a tile finish in any order; whichever arrives last adds them up in split order, so the
+        // result does not depend on the order of arrival.
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          int* ctr = p.counters + blockIdx.x * gridDim.y + blockIdx.y;
+          const int prev = atomicAdd(ctr, 1);
+          *last_flag = (prev == p.ksplit - 1) ? 1 : 0;
+          if (prev == p.ksplit - 1) *ctr = 0;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag != 0 && j < R) {
+          __threadfence();
+          constexpr int QU = 8;           // rows summed together: QU * ksplit independent loads in flight
+          for (int q0 = 0; q0 < tile.nrows; q0 += QU) {
+            float acc[QU];
+#pragma unroll
+            for (int u = 0; u < QU; ++u) acc[u] = 0.f;
+            for (int sp = 0; sp < p.ksplit; ++sp) {
+              float t[QU];
+#pragma unroll
+              for (int u = 0; u < QU; ++u) {
+                const int q = min(q0 + u, tile.nrows - 1);
+                t[u] = __ldcg(p.v + (long long)sp * p.v_split_stride + (long long)(tile.row0 + q) * p.ldv + j);
+              }
+#pragma unroll
+              for (int u = 0; u < QU; ++u) acc[u] += t[u];
+            }
+#pragma unroll
+            for (int u = 0; u < QU; ++u) {
+              if (q0 + u < tile.nrows) p.v_final[(long long)(tile.row0 + q0 + u) * p.ldv + j] = acc[u];
+            }
+          }
+        }
+      }
     } else {
       report_status(p.status, kTimeoutTmemFull, blockIdx.x);
       *abort_flag = 1;
@@ -189,85 +228,113 @@ struct ExpandTiledParams {
   const int* slot_rank;
   int num_slots;
   long long unit_off;
-  const float* v;
+  const float* v;                  // [T, ldv] shrink result
   int ldv;
-  long long v_split_stride;
-  int ksplit;
-  int subtiles;                    // each tile is cut into `subtiles` pieces of kExpTok rows, one CTA each
   __nv_bfloat16* y;
   long long ldy;
   int n0, n1, N, T;
+  int num_tiles, col_blocks;
   int* status;
 };
 
-constexpr int kExpTok = 16;      // tokens staged in shared memory at a time
-constexpr int kExpMaxR = 3 * 128;
+constexpr int kExpThreads = 256;
+constexpr int kExpCols = 4;                          // adjacent output features per thread: 128 contiguous bytes of B_cat at rank 16
+constexpr int kExpBlockCols = kExpThreads * kExpCols;
+constexpr int kExpMaxRows = 128;                     // rows of a tile staged at once
+constexpr int kExpStage = 16;                        // ranks per pass
+constexpr int kExpRowsInFlight = 4;                  // rows whose y loads are issued together
 
-__global__ void __launch_bounds__(256) lora_expand_tiled_kernel(const ExpandTiledParams p) {
-  __shared__ __align__(16) float vs[kExpTok * kExpMaxR];
-  const LoraTile tile = p.tiles[blockIdx.x / p.subtiles];
-  const int sub0 = (blockIdx.x % p.subtiles) * kExpTok;
-  if (tile.slot < 0 || tile.nrows <= sub0) return;
-  if (tile.slot >= p.num_slots) {
-    if (threadIdx.x == 0) report_status(p.status, kBadIndex, tile.slot);
-    return;
-  }
-  const int r = p.slot_rank[tile.slot];
-  const long long base = p.slot_base[tile.slot];
-  if (base < 0 || r <= 0) return;
+// One unit of work = one tile (a run of rows of one adapter) x 1024 output features.  A thread keeps the B_cat rows
+// of its four features in registers (16 ranks at a time, packed bf16) and walks the rows of the tile: v comes from
+// shared memory as broadcasts, y is read and written 8 bytes per thread, 256 contiguous bytes per warp.  The loads
+// of B, of v and of the first rows of y are all issued before the first barrier, so a unit costs about one trip to
+// memory.  Ranks above 16 take one pass over the tile's rows per 16 ranks.
+//
+// The grid is a fixed number of CTAs that walk the units; live tiles come first in the table, so the walk stops at
+// the first dead one and padding entries cost nothing.
+__global__ void __launch_bounds__(kExpThreads, 2) lora_expand_tiled_kernel(const ExpandTiledParams p) {
+  __shared__ __align__(16) float vs[kExpMaxRows * 3 * kExpStage];   // [row][part][16]
   const int nparts = p.n1 < p.N ? 3 : (p.n0 < p.N ? 2 : 1);
-  const int R = nparts * r;
-  {
-    const int t0 = sub0;
-    const int nt = min(kExpTok, tile.nrows - t0);
-    for (int c = threadIdx.x; c < nt * R; c += 256) {
-      const int m = c / R, jj = c % R;
-      const float* src = p.v + (long long)(tile.row0 + t0 + m) * p.ldv + jj;
-      float acc = 0.f;
-      for (int sp = 0; sp < p.ksplit; ++sp) acc += src[(long long)sp * p.v_split_stride];    // fixed order: deterministic
-      vs[m * kExpMaxR + jj] = acc;
+  for (int w = blockIdx.x; w < p.num_tiles * p.col_blocks; w += gridDim.x) {
+    const LoraTile tile = p.tiles[w / p.col_blocks];
+    if (tile.slot < 0) break;
+    if (tile.nrows <= 0) continue;
+    if (tile.slot >= p.num_slots) {
+      if (threadIdx.x == 0) report_status(p.status, kBadIndex, tile.slot);
+      continue;
     }
-    __syncthreads();
-   for (int n = (blockIdx.y * 256 + threadIdx.x) * 2; n < p.N; n += gridDim.y * 512) {
+    const int r = p.slot_rank[tile.slot];
+    const long long base = p.slot_base[tile.slot];
+    if (base < 0 || r <= 0) continue;
+    const int n = (w % p.col_blocks) * kExpBlockCols + threadIdx.x * kExpCols;
+    const bool col_ok = n < p.N;                        // N is a multiple of 4: a thread's four features are all in or all out
     const int part = n < p.n0 ? 0 : (n < p.n1 ? 1 : 2);
     const __nv_bfloat16* B = p.arena + base + (long long)r * p.unit_off + (long long)n * r;
-    float acc[kExpTok][2];
+    const int nrows = min(tile.nrows, kExpMaxRows);
+    __nv_bfloat16* yrow0 = p.y + (long long)tile.row0 * p.ldy + n;
+
+    for (int jc = 0; jc < r; jc += kExpStage) {
+      const int rs = min(kExpStage, r - jc);            // 8 or 16 live ranks in this pass
+      uint4 bw[kExpCols][kExpStage / 8];
 #pragma unroll
-    for (int m = 0; m < kExpTok; ++m) acc[m][0] = acc[m][1] = 0.f;
-    for (int jc = 0; jc < r; jc += 8) {
-      const uint4 b0 = __ldg(reinterpret_cast<const uint4*>(B + jc));
-      const uint4 b1 = __ldg(reinterpret_cast<const uint4*>(B + r + jc));
-      const uint32_t w0[4] = {b0.x, b0.y, b0.z, b0.w}, w1[4] = {b1.x, b1.y, b1.z, b1.w};
-      float f0[8], f1[8];
+      for (int c = 0; c < kExpCols; ++c) {
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        const float2 a = unpack_bf16x2(w0[q]), b = unpack_bf16x2(w1[q]);
-        f0[2 * q] = a.x; f0[2 * q + 1] = a.y; f1[2 * q] = b.x; f1[2 * q + 1] = b.y;
+        for (int h = 0; h < kExpStage / 8; ++h) {
+          bw[c][h] = make_uint4(0u, 0u, 0u, 0u);
+          if (col_ok && h * 8 < rs) bw[c][h] = __ldg(reinterpret_cast<const uint4*>(B + (long long)c * r + jc + h * 8));
+        }
       }
-      const float* vp = vs + part * r + jc;
+      uint2 old[kExpRowsInFlight];
 #pragma unroll
-      for (int m = 0; m < kExpTok; ++m) {
-        if (m < nt) {
-          const float4 va = *reinterpret_cast<const float4*>(vp + m * kExpMaxR);
-          const float4 vb = *reinterpret_cast<const float4*>(vp + m * kExpMaxR + 4);
-          const float vv[8] = {va.x, va.y, va.z, va.w, vb.x, vb.y, vb.z, vb.w};
+      for (int u = 0; u < kExpRowsInFlight; ++u) {
+        if (col_ok && u < nrows) old[u] = *reinterpret_cast<const uint2*>(yrow0 + (long long)u * p.ldy);
+      }
+      // stage v[row][part][jc .. jc+16) (zeros past the rank)
+      __syncthreads();                                   // the previous unit's readers are done with vs
+      for (int e = threadIdx.x; e < nrows * nparts * kExpStage; e += kExpThreads) {
+        const int j = e % kExpStage, pr = e / kExpStage;
+        const int pp = pr % nparts, m = pr / nparts;
+        vs[(m * 3 + pp) * kExpStage + j] = (j < rs) ? p.v[(long long)(tile.row0 + m) * p.ldv + pp * r + jc + j] : 0.f;
+      }
+      __syncthreads();
+      if (col_ok) {
+        for (int m0 = 0; m0 < nrows; m0 += kExpRowsInFlight) {
+          uint2 nxt[kExpRowsInFlight];
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            acc[m][0] = fmaf(vv[q], f0[q], acc[m][0]);
-            acc[m][1] = fmaf(vv[q], f1[q], acc[m][1]);
+          for (int u = 0; u < kExpRowsInFlight; ++u) {      // next group's y while this one is computed
+            const int m = m0 + kExpRowsInFlight + u;
+            if (m < nrows) nxt[u] = *reinterpret_cast<const uint2*>(yrow0 + (long long)m * p.ldy);
           }
+#pragma unroll
+          for (int u = 0; u < kExpRowsInFlight; ++u) {
+            if (m0 + u < nrows) {
+              const float4* vp = reinterpret_cast<const float4*>(vs + ((m0 + u) * 3 + part) * kExpStage);
+              float acc[kExpCols] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+              for (int h = 0; h < kExpStage / 8; ++h) {
+                const float4 va = vp[2 * h], vb = vp[2 * h + 1];
+#pragma unroll
+                for (int c = 0; c < kExpCols; ++c) {
+                  const float2 b0 = unpack_bf16x2(bw[c][h].x), b1 = unpack_bf16x2(bw[c][h].y);
+                  const float2 b2 = unpack_bf16x2(bw[c][h].z), b3 = unpack_bf16x2(bw[c][h].w);
+                  acc[c] = fmaf(va.x, b0.x, acc[c]); acc[c] = fmaf(va.y, b0.y, acc[c]);
+                  acc[c] = fmaf(va.z, b1.x, acc[c]); acc[c] = fmaf(va.w, b1.y, acc[c]);
+                  acc[c] = fmaf(vb.x, b2.x, acc[c]); acc[c] = fmaf(vb.y, b2.y, acc[c]);
+                  acc[c] = fmaf(vb.z, b3.x, acc[c]); acc[c] = fmaf(vb.w, b3.y, acc[c]);
+                }
+              }
+              const float2 o0 = unpack_bf16x2(old[u].x), o1 = unpack_bf16x2(old[u].y);
+              uint2 nw;
+              nw.x = pack_bf16x2(o0.x + acc[0], o0.y + acc[1]);
+              nw.y = pack_bf16x2(o1.x + acc[2], o1.y + acc[3]);
+              *reinterpret_cast<uint2*>(yrow0 + (long long)(m0 + u) * p.ldy) = nw;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < kExpRowsInFlight; ++u) old[u] = nxt[u];
         }
       }
     }
-#pragma unroll
-    for (int m = 0; m < kExpTok; ++m) {
-      if (m < nt) {
-        uint32_t* yp = reinterpret_cast<uint32_t*>(p.y + (long long)(tile.row0 + t0 + m) * p.ldy + n);
-        const float2 old = unpack_bf16x2(*yp);
-        *yp = pack_bf16x2(old.x + acc[m][0], old.y + acc[m][1]);
-      }
-    }
-   }
   }
 }
 
@@ -328,7 +395,8 @@ int lx_lora_encode_tmap(void* out, const void* base, int K, int R, long long lay
 // (<= 32: decode, <= 128: prefill); max_rank bounds the number of 128-row chunks of A_cat.
 int lx_lora_shrink_tc(const void* x, long long ldx, const void* tiles, int num_tiles, int max_tile_rows, const void* slot_tmaps,
                       int groups_per_slot, int group, const int* slot_rank, int num_slots, int nparts, int layer, float* v, int ldv,
-                      long long v_split_stride, int ksplit, int T, int K, int max_rank, int* status, void* stream) {
+                      long long v_split_stride, int ksplit, float* v_final, int* counters, int num_counters, int T, int K, int max_rank,
+                      int* status, void* stream) {
   using namespace lx;
   if (num_tiles <= 0 || max_rank <= 0) return 0;
   if (K % 8 != 0 || ldx % 8 != 0 || nparts * max_rank > ldv) return -1;
@@ -341,6 +409,8 @@ int lx_lora_shrink_tc(const void* x, long long ldx, const void* tiles, int num_t
   p.ksplit = ksplit < 1 ? 1 : ksplit;
   if (p.ksplit > (K + kLtBK - 1) / kLtBK) p.ksplit = (K + kLtBK - 1) / kLtBK;
   const int chunks = (nparts * max_rank + 127) / 128;
+  if (counters == nullptr || num_tiles * chunks > num_counters || v == nullptr) p.ksplit = 1;
+  p.v_final = v_final; p.counters = counters;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int bn = max_tile_rows <= 32 ? 32 : 128;
   // activations: 2-D K-major map with a BN-row box (same encoding as the GEMM's operands)
@@ -362,19 +432,21 @@ int lx_lora_expand_tiled(const float* v, int ldv, long long v_split_stride, int 
                          int max_tile_rows, const void* arena, const long long* slot_base, const int* slot_rank, int num_slots,
                          long long unit_off, void* y, long long ldy, int T, int N, int n0, int n1, int* status, void* stream) {
   using namespace lx;
+  (void)v_split_stride;
   if (num_tiles <= 0) return 0;
-  if ((N | n0 | n1) & 1 || ldy % 2 != 0) return -1;
+  if ((N | n0 | n1) & 3 || ldy % 4 != 0 || (reinterpret_cast<uintptr_t>(y) & 7) != 0) return -1;
+  if (ksplit != 1 || max_tile_rows > kExpMaxRows) return -2;          // the shrink hands over the summed result
   ExpandTiledParams p{};
   p.tiles = reinterpret_cast<const LoraTile*>(tiles);
   p.arena = reinterpret_cast<const __nv_bfloat16*>(arena);
   p.slot_base = slot_base; p.slot_rank = slot_rank; p.num_slots = num_slots; p.unit_off = unit_off;
   p.v = v; p.ldv = ldv; p.y = reinterpret_cast<__nv_bfloat16*>(y); p.ldy = ldy; p.n0 = n0; p.n1 = n1; p.N = N; p.T = T;
   p.status = status;
-  p.v_split_stride = v_split_stride; p.ksplit = ksplit < 1 ? 1 : ksplit;
-  p.subtiles = (max_tile_rows + kExpTok - 1) / kExpTok;
-  const int col_blocks = (N + 511) / 512;
-  dim3 grid(num_tiles * p.subtiles, col_blocks < 8 ? col_blocks : 8);
-  lora_expand_tiled_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  p.num_tiles = num_tiles;
+  p.col_blocks = (N + kExpBlockCols - 1) / kExpBlockCols;
+  const long long work = (long long)num_tiles * p.col_blocks;
+  const int grid = (int)(work < 148 * 2 ? work : 148 * 2);
+  lora_expand_tiled_kernel<<<grid, kExpThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
   return -(int)cudaGetLastError();
 }
 

@@ -13,6 +13,7 @@ interface of :mod:`lorax_b200.ops`; on a B200 those are the sm_100a kernels, on 
 
 from __future__ import annotations
 
+import os
 import math
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
@@ -103,6 +104,9 @@ class DecoderModel:
         self.max_positions = max_positions or min(c.max_position_embeddings, 32768)
         self.cos_sin = reference.rope_cache(c.rotary_dim, self.max_positions, c.rope_theta, c.rope_scaling, device=self.device)
         self.adapters = None     # AdapterManager, attached by the runtime
+        # LoRA expand inside the GEMM epilogue instead of its own launch (slower than the separate kernel at present:
+        # four epilogue warps cannot hide the latency of the per-token B rows)
+        self.fused_lora_epilogue = os.environ.get("LORAX_FUSED_LORA_EPILOGUE", "0") == "1"
         self.gated = c.model_type not in ("gpt2", "gpt_bigcode", "gpt_neox", "falcon", "RefinedWeb", "RefinedWebModel", "phi")
 
     # ------------------------------------------------------------------ shapes
@@ -280,11 +284,18 @@ class DecoderModel:
                                       x_scale=x_scale, layernorm=c.norm_type.startswith("layernorm"))
 
     def _linear(self, x, w, b, group: str, layer: int, inp: StepInputs, tok_slot=None):
-        """Base GEMM plus the multi-adapter LoRA delta for the projection group."""
-        y = self.ops.gemm(x, w, bias=b)
+        """Base GEMM plus the multi-adapter LoRA delta for the projection group.  The shrink x A^T is one small launch;
+        the expand is a second one, or rides in the GEMM epilogue when `fused_lora_epilogue` is set."""
         ts = tok_slot if tok_slot is not None else inp.tok_slot
-        if self.adapters is not None and (ts is not None or inp.lora_tiles is not None):
-            self.adapters.apply(self.ops, x, y, ts, group, layer, tiles=inp.lora_tiles)
+        epi = None
+        if self.adapters is not None and ts is not None:
+            epi = self.adapters.shrink(self.ops, x, ts, group, layer, tiles=inp.lora_tiles)
+        if epi is None:
+            return self.ops.gemm(x, w, bias=b)
+        if self.fused_lora_epilogue:
+            return self.ops.gemm(x, w, bias=b, lora=epi)
+        y = self.ops.gemm(x, w, bias=b)
+        self.adapters.expand(self.ops, epi, y, tiles=inp.lora_tiles)
         return y
 
     def _row_parallel(self, x, w, b, group: str, layer: int, inp: StepInputs):

@@ -12,7 +12,7 @@ import ctypes
 import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from pathlib import Path
-from typing import Optional
+from typing import NamedTuple, Optional
 
 import torch
 
@@ -51,6 +51,7 @@ def load() -> ctypes.CDLL:
     sigs = {
         "lx_gemm_ws_bytes": ([], L),
         "lx_gemm_max_tiles": ([], I),
+        "lx_gemm_plan": ([I, I, I, I, L, I, I, P], I),
         "lx_gemm_bf16": ([P, P, P, P, I, I, I, L, L, L, F, P, L, P, P, I, I, I, P], I),
         "lx_norm_residual": ([P, P, P, P, P, I, I, L, L, L, F, F, F, I, P], I),
         "lx_rope_kvwrite": ([P, P, P, P, P, I, I, I, I, I, I, L, I, P], I),
@@ -65,7 +66,8 @@ def load() -> ctypes.CDLL:
         "lx_lora_expand": ([P, I, P, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
         "lx_tensormap_bytes": ([], I),
         "lx_lora_encode_tmap": ([P, P, I, I, L, I], I),
-        "lx_lora_shrink_tc": ([P, L, P, I, I, P, I, I, P, I, I, I, P, I, L, I, I, I, I, P, P], I),
+        "lx_lora_shrink_tc": ([P, L, P, I, I, P, I, I, P, I, I, I, P, I, L, I, P, P, I, I, I, I, P, P], I),
+        "lx_gemm_bf16_lora": ([P, P, P, P, I, I, I, L, L, L, F, P, L, P, P, I, I, I, P, I, P, P, P, P, I, L, I, I, P], I),
         "lx_lora_expand_tiled": ([P, I, L, I, P, I, I, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
     }
     for name, (argtypes, restype) in sigs.items():
@@ -106,7 +108,8 @@ class Workspace:
         self.status = torch.zeros(2, dtype=torch.int32, device=device)
         # LoRA intermediate: [K-split][token][nparts * rank] fp32 partial sums (split 0 alone for the per-token kernels)
         self.lora_v3 = torch.zeros(self.LORA_KSPLIT, max_tokens, max_lora_cols, dtype=torch.float32, device=device)
-        self.lora_v = self.lora_v3[0]
+        self.lora_v = torch.zeros(max_tokens, max_lora_cols, dtype=torch.float32, device=device)     # shrink result
+        self.lora_counters = torch.zeros(16384, dtype=torch.int32, device=device)
         self.attn_part_tokens = 256
         self.attn_splits = attn_splits
         self.attn_part_o = torch.empty(self.attn_part_tokens * num_heads * attn_splits * head_dim, dtype=torch.float32, device=device)
@@ -137,9 +140,29 @@ def workspace(device=None) -> Workspace:
 
 
 # ------------------------------------------------------------------------------------------------ GEMM
+def gemm_plan(T: int, N: int, K: int, num_sms: int = 148, ws_bytes: int = 64 << 20, force_split: int = 0, sk_policy: int = 0) -> dict:
+    """Tiling the weights-on-M GEMM path would choose for a shape (no GPU needed)."""
+    out = (ctypes.c_int * 5)()
+    load().lx_gemm_plan(T, N, K, num_sms, ws_bytes, force_split, sk_policy, out)
+    return dict(zip(("bn", "split", "dp_tiles", "sk_ctas", "grid"), out))
+
+
+class LoraEpilogue(NamedTuple):
+    """What the GEMM epilogue needs to add the multi-adapter LoRA delta: the shrink result and where each slot's
+    B_cat of this projection group sits in the arena."""
+    v: torch.Tensor            # [T, ldv] fp32
+    tok_slot: torch.Tensor     # [T] int32, -1 = no adapter
+    arena: torch.Tensor
+    slot_base: torch.Tensor
+    slot_rank: torch.Tensor
+    unit_off: int
+    n0: int
+    n1: int
+
+
 def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-         out_scale: float = 1.0, mode: int = 0, force_split: int = 0) -> torch.Tensor:
-    """out[T, N] = x[T, K] @ w[N, K]^T (+ bias).  bf16 in, fp32 accumulate on tcgen05, bf16 out."""
+         out_scale: float = 1.0, mode: int = 0, force_split: int = 0, lora: Optional[LoraEpilogue] = None) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ w[N, K]^T (+ bias) (+ LoRA delta).  bf16 in, fp32 accumulate on tcgen05, bf16 out."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
     assert x.stride(1) == 1 and w.stride(1) == 1
     T, K = x.shape
@@ -150,8 +173,15 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, 
     assert out.stride(1) == 1
     ws = workspace(x.device)
     lib = load()
-    if mode == 0 and T > 256:
-        mode = 2
+    if lora is not None:
+        assert lora.v.dtype == torch.float32 and lora.tok_slot.dtype == torch.int32 and lora.tok_slot.shape[0] >= T
+        rc = lib.lx_gemm_bf16_lora(_ptr(x), _ptr(w), _ptr(out), _ptr(bias), T, N, K, x.stride(0), w.stride(0), out.stride(0),
+                                   out_scale, _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.gemm_counters), _ptr(ws.status),
+                                   ws.num_sms, mode, force_split, _ptr(lora.v), lora.v.stride(0), _ptr(lora.tok_slot),
+                                   _ptr(lora.arena), _ptr(lora.slot_base), _ptr(lora.slot_rank), lora.slot_rank.shape[0],
+                                   lora.unit_off, lora.n0, lora.n1, _stream())
+        _check(rc, "lx_gemm_bf16_lora")
+        return out
     rc = lib.lx_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), _ptr(bias), T, N, K, x.stride(0), w.stride(0), out.stride(0),
                           out_scale, _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.gemm_counters), _ptr(ws.status),
                           ws.num_sms, mode, force_split, _stream())
@@ -292,30 +322,29 @@ def lora_encode_tmap(out_host: torch.Tensor, base_ptr: int, K: int, R: int, laye
 def lora_shrink_tiles(x: torch.Tensor, tiles: torch.Tensor, num_tiles: int, max_tile_rows: int, slot_tmaps: torch.Tensor,
                       groups_per_slot: int, group: int, slot_rank: torch.Tensor, nparts: int, layer: int, max_rank: int,
                       v: Optional[torch.Tensor] = None):
-    """Tensor-core shrink over a tile table.  Returns (v3, ksplit): fp32 partial sums [ksplit, rows, cols]; the
-    expand adds the splits in a fixed order.  K is split when the table alone cannot fill the GPU."""
+    """Tensor-core shrink over a tile table -> v [rows, cols] fp32.  K is split over CTAs when the table alone
+    cannot fill the GPU; the last split CTA of a tile adds the partial sums in a fixed order."""
     T, K = x.shape
     ws = workspace(x.device)
-    v3 = ws.lora_v3 if v is None else v
-    if v3.dim() == 2:
-        v3 = v3.unsqueeze(0)
+    vf = ws.lora_v if v is None else v
+    v3 = ws.lora_v3
+    assert vf.stride(0) == v3.stride(1)
     kblocks = (K + 63) // 64
     chunks = (nparts * max_rank + 127) // 128
-    ksplit = 1
-    while num_tiles * chunks * ksplit < 2 * ws.num_sms and kblocks // (ksplit * 2) >= 8 and ksplit * 2 <= v3.shape[0]:
-        ksplit *= 2
+    # K split: these skinny tiles are latency bound, so aim for about 16 k-blocks per CTA and enough CTAs to cover the
+    # GPU several times over (in decode most table entries are padding and their CTAs exit at once)
+    want = -(-8 * ws.num_sms // max(1, num_tiles * chunks))
+    ksplit = max(1, min(v3.shape[0], kblocks // 16, want))
     rc = load().lx_lora_shrink_tc(_ptr(x), x.stride(0), _ptr(tiles), num_tiles, max_tile_rows, _ptr(slot_tmaps), groups_per_slot, group,
                                   _ptr(slot_rank), slot_rank.shape[0], nparts, layer, _ptr(v3), v3.stride(1), v3.stride(0), ksplit,
-                                  T, K, max_rank, _ptr(ws.status), _stream())
+                                  _ptr(vf), _ptr(ws.lora_counters), ws.lora_counters.numel(), T, K, max_rank, _ptr(ws.status), _stream())
     _check(rc, "lx_lora_shrink_tc")
-    return v3, ksplit
+    return vf
 
 
 def lora_expand_tiles(v, tiles: torch.Tensor, num_tiles: int, max_tile_rows: int, arena: torch.Tensor, slot_base: torch.Tensor,
                       slot_rank: torch.Tensor, unit_off: int, y: torch.Tensor, n0: int, n1: int):
-    v3, ksplit = v if isinstance(v, tuple) else (v, 1)
-    if v3.dim() == 2:
-        v3 = v3.unsqueeze(0)
+    v3, ksplit = v.unsqueeze(0), 1
     T, N = y.shape
     ws = workspace(y.device)
     rc = load().lx_lora_expand_tiled(_ptr(v3), v3.stride(1), v3.stride(0), ksplit, _ptr(tiles), num_tiles, max_tile_rows, _ptr(arena),

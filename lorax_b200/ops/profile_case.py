@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for `ncu` captures of single kernels.
 
-    python -m lorax_b200.ops.profile_case --case gemm_decode|gemm_prefill|attn_decode|attn_prefill|lora_shrink|lora_expand
+    python -m lorax_b200.ops.profile_case --case gemm_decode|gemm_prefill|gemm_lora_decode|gemm_lora_decode_gateup|gemm_lora_prefill|attn_decode|attn_prefill|lora_shrink|lora_expand
 
 Each case launches the kernel a handful of times on inputs larger than the 126 MB L2 but at most a few GB, and
 exits 0; run it plain first, then under
@@ -73,7 +73,27 @@ def lora_case(which):
     for _ in range(4):
         v = native.lora_shrink_tiles(x, tiles, T, 32, tmaps, G, 0, slot_rank, 3, 0, r)
         if which == "expand":
-            native.lora_expand_tiles(v, tiles, T, 32, arena, slot_base, slot_rank, 3 * K, y, parts[0], parts[0] + parts[1])
+            native.lora_expand_tiles(v[:T], tiles, T, 32, arena, slot_base, slot_rank, 3 * K, y, parts[0], parts[0] + parts[1])
+
+
+def gemm_lora_case(T, parts=(4096, 1024, 1024)):
+    """QKV (or gate_up) projection with the LoRA delta in the epilogue: 100 rank-16 adapters, rows sorted by adapter."""
+    import math
+    K, r, S = 4096, 16, 100
+    N = sum(parts)
+    units = len(parts) * K + N
+    arena = (torch.randn(S * r * units, device="cuda") * 0.02).to(torch.bfloat16)
+    slot_base = torch.arange(S, device="cuda", dtype=torch.int64) * r * units
+    slot_rank = torch.full((S,), r, device="cuda", dtype=torch.int32)
+    ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K) for _ in range(4)]
+    rows = sorted(int(x) for x in torch.randint(0, S, (T,))) if T <= 256 else [int(i * 3 // T) for i in range(T)]
+    tok_slot = torch.tensor(rows, device="cuda", dtype=torch.int32)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(T, 192, device="cuda", dtype=torch.float32)
+    epi = native.LoraEpilogue(v, tok_slot, arena, slot_base, slot_rank, len(parts) * K, parts[0], parts[0] + parts[1] if len(parts) > 2 else N)
+    out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    for i in range(4):
+        native.gemm(x, ws[i], out=out, lora=epi)
 
 
 def main():
@@ -82,7 +102,8 @@ def main():
     a = ap.parse_args()
     native.load()
     {"gemm_decode": lambda: gemm_case(64), "gemm_prefill": lambda: gemm_case(4096), "attn_decode": attn_decode_case,
-     "attn_prefill": attn_prefill_case, "lora_shrink": lambda: lora_case("shrink"), "lora_expand": lambda: lora_case("expand")}[a.case]()
+     "attn_prefill": attn_prefill_case, "gemm_lora_decode": lambda: gemm_lora_case(256), "gemm_lora_decode_gateup": lambda: gemm_lora_case(256, (14336, 14336)), "gemm_lora_prefill": lambda: gemm_lora_case(576),
+     "lora_shrink": lambda: lora_case("shrink"), "lora_expand": lambda: lora_case("expand")}[a.case]()
     torch.cuda.synchronize()
     native.workspace().check_status()
     print("ok", a.case)

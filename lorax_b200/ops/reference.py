@@ -14,10 +14,14 @@ import torch
 import torch.nn.functional as F
 
 
-def gemm(x, w, bias=None, out=None, out_scale: float = 1.0, **_):
+def gemm(x, w, bias=None, out=None, out_scale: float = 1.0, lora=None, **_):
     y = (x.float() @ w.float().t()) * out_scale
     if bias is not None:
         y = y + bias.float()
+    if lora is not None:      # the CUDA kernel adds the delta in its epilogue, before the one rounding to bf16
+        d = torch.zeros_like(y)
+        lora_expand(lora.v, lora.tok_slot, lora.arena, lora.slot_base, lora.slot_rank, lora.unit_off, d, lora.n0, lora.n1)
+        y = y + d
     y = y.to(x.dtype)
     if out is not None:
         out.copy_(y)

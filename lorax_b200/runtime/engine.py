@@ -85,7 +85,7 @@ class Engine:
         self.waiting: Deque[GenRequest] = collections.deque()
         self.running: Dict[int, _Seq] = {}
         self.draining: Dict[int, _Seq] = {}
-        self.inflight: Deque[Tuple[int, int, Dict[int, int]]] = collections.deque()   # (ring idx, bucket, row->req snapshot)
+        self.inflight: Deque[tuple] = collections.deque()   # ("decode", ring idx, bucket, row->req) | ("first", ring idx, n, [req])
         self.steps_since_prefill = 0
         self.decode_text = decode_text
         self.stats = dict(prefill_steps=0, decode_steps=0, prefill_tokens=0, generated_tokens=0)
@@ -162,10 +162,11 @@ class Engine:
 
     def _finish(self, seq: _Seq, reason: int):
         seq.finished = True
-        if not seq.retired:
+        if not seq.retired and seq.row >= 0:
             self.runner.retire([seq.row])
-            seq.retired = True
-        self.runner.state.drop_row(seq.row)
+        seq.retired = True
+        if seq.row >= 0:
+            self.runner.state.drop_row(seq.row)
         self.alloc.release(seq.blocks)
         self.running.pop(seq.req.request_id, None)
         self.draining.pop(seq.req.request_id, None)
@@ -193,25 +194,30 @@ class Engine:
         if picked:
             items = [PrefillItem(r.prompt_ids, 0, b, r.adapter_index) for r, b in picked]
             next_ids, lps, _ = self.runner.prefill(items)
-            ids_h = next_ids.tolist()
-            lps_h = lps.tolist()
-            now = time.perf_counter()
-            rows, firsts, poss, blks, ads = [], [], [], [], []
-            for (req, blocks), tok, lp in zip(picked, ids_h, lps_h):
+            # The first tokens stay on the device: they are scattered into the decode rows there and reach the host
+            # through the pinned ring like every later token, so the host never waits for the prefill to finish.
+            rows, sel, poss, blks, ads, rids = [], [], [], [], [], []
+            for i, (req, blocks) in enumerate(picked):
                 seq = _Seq(req, blocks, stopping=StoppingCriteria(req.max_new_tokens, req.eos_token_ids, list(req.stop_sequences),
                                                                   req.ignore_eos_token))
-                seq.row = self.runner.state.take_row(req.request_id)
                 seq.launched = 1
-                self.running[req.request_id] = seq
-                self._emit(seq, tok, lp, now, events)
-                if not seq.finished:
-                    rows.append(seq.row); firsts.append(tok); poss.append(len(req.prompt_ids)); blks.append(blocks)
+                rids.append(req.request_id)
+                if req.max_new_tokens > 1:
+                    seq.row = self.runner.state.take_row(req.request_id)
+                    self.running[req.request_id] = seq
+                    rows.append(seq.row); sel.append(i); poss.append(len(req.prompt_ids)); blks.append(blocks)
                     ads.append(req.adapter_index)
-            self.runner.install(rows, firsts, poss, blks, ads)
+                else:                       # only the prefill token is wanted: no decode row
+                    seq.retired = True
+                    self.draining[req.request_id] = seq
+            if rows:
+                first = next_ids if len(sel) == len(picked) else next_ids[torch.tensor(sel, device=next_ids.device)]
+                self.runner.install(rows, first, poss, blks, ads)
             mapping = self.runner.resort()
             for s_ in list(self.running.values()) + list(self.draining.values()):
                 if s_.row in mapping:
                     s_.row = mapping[s_.row]
+            self.inflight.append(("first", self.runner.stash(next_ids, lps), len(picked), rids))
             self.stats["prefill_steps"] += 1
             self.stats["prefill_tokens"] += sum(len(r.prompt_ids) for r, _ in picked)
             self.steps_since_prefill = 0
@@ -223,7 +229,7 @@ class Engine:
                 launched = self.runner.decode()
             if launched is not None:
                 k, b, _ = launched
-                self.inflight.append((k, b, snapshot))
+                self.inflight.append(("decode", k, b, snapshot))
                 self.stats["decode_steps"] += 1
                 self.steps_since_prefill += 1
                 # rows that reach max_new_tokens with this step need no further steps: retire them now
@@ -242,11 +248,17 @@ class Engine:
         # process results one step behind the GPU (or everything when nothing new was launched)
         keep = 1 if launched is not None else 0
         while len(self.inflight) > keep:
-            k, b, snapshot = self.inflight.popleft()
+            kind, k, b, who = self.inflight.popleft()
             ids_p, lps_p = self.runner.wait(k)
             now = time.perf_counter()
             ids_h, lps_h = ids_p[:b].tolist(), lps_p[:b].tolist()
-            for row, rid in snapshot.items():
+            if kind == "first":
+                for i, rid in enumerate(who):
+                    seq = self.running.get(rid) or self.draining.get(rid)
+                    if seq is not None and not seq.finished:
+                        self._emit(seq, ids_h[i], lps_h[i], now, events)
+                continue
+            for row, rid in who.items():
                 seq = self.running.get(rid) or self.draining.get(rid)
                 if seq is None or seq.finished:
                     continue

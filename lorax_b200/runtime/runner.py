@@ -95,7 +95,7 @@ class ModelRunner:
         if self.buckets[-1] != max_batch:
             self.buckets.append(max_batch)
         # pinned result ring (two steps in flight at most)
-        self.n_ring = 4
+        self.n_ring = 8
         pin = dict(pin_memory=True) if self.is_cuda else {}
         self.ring_ids = [torch.zeros(max_batch, dtype=torch.int32, **pin) for _ in range(self.n_ring)]
         self.ring_lp = [torch.zeros(max_batch, dtype=torch.float32, **pin) for _ in range(self.n_ring)]
@@ -192,8 +192,8 @@ class ModelRunner:
             self.model.adapters.fence()
         tiles = None
         if any_lora:
-            tl = reference.build_lora_tiles(tok_slot, 128)
-            tiles = LoraTiles(self._to_dev([x for t in tl for x in t]).view(-1, 4), len(tl), 128)
+            tl = reference.build_lora_tiles(tok_slot, 32)
+            tiles = LoraTiles(self._to_dev([x for t in tl for x in t]).view(-1, 4), len(tl), 32)
         inp = StepInputs(input_ids=d_ids, positions=d_pos, slots=d_slots, is_prefill=True, block_tables=bt, cu_q=d_cu,
                          cache_lens=d_cl, tile_seq=d_ts, tile_q0=d_tq, lm_head_indices=d_head if len(head_idx) else None,
                          tok_slot=d_tokslot if any_lora else None, head_tok_slot=d_headslot if any_lora else None,
@@ -207,11 +207,15 @@ class ModelRunner:
         return next_ids, lps, logits
 
     # ------------------------------------------------------------------ decode rows
-    def install(self, rows: Sequence[int], first_tokens: Sequence[int], positions: Sequence[int], blocks: Sequence[Sequence[int]],
+    def install(self, rows: Sequence[int], first_tokens, positions: Sequence[int], blocks: Sequence[Sequence[int]],
                 adapter_indices: Sequence[int]):
-        """Write freshly prefilled sequences into their decode rows (one packed H2D + six scatters)."""
+        """Write freshly prefilled sequences into their decode rows (one packed H2D + six scatters).  `first_tokens` is a
+        host list or the device tensor the prefill's argmax left behind (the host then never waits for the prefill)."""
         if not rows:
             return
+        dev_first = first_tokens if isinstance(first_tokens, torch.Tensor) else None
+        if dev_first is not None:
+            first_tokens = [0] * len(rows)
         page = self.page
         st = self.state
         tabs = [self._table_row(b) for b in blocks]
@@ -222,7 +226,7 @@ class ModelRunner:
         flat = list(rows) + list(first_tokens) + list(positions) + ctx + slots + tslot + [x for t in tabs for x in t]
         dev = self._to_dev(flat)
         r = dev[:n].long()
-        st.input_ids.index_copy_(0, r, dev[n:2 * n])
+        st.input_ids.index_copy_(0, r, dev[n:2 * n] if dev_first is None else dev_first.to(torch.int32))
         st.positions.index_copy_(0, r, dev[2 * n:3 * n])
         st.ctx_lens.index_copy_(0, r, dev[3 * n:4 * n])
         st.slots.index_copy_(0, r, dev[4 * n:5 * n])
@@ -364,6 +368,18 @@ class ModelRunner:
             self.ring_ev[k].record()
         self.steps += 1
         return k, b, logits
+
+    def stash(self, ids: torch.Tensor, lps: torch.Tensor) -> int:
+        """Queue an asynchronous copy of `ids` / `lps` (device) into a pinned ring entry; `wait(k)` returns them."""
+        k = self.ring_pos
+        self.ring_pos = (k + 1) % self.n_ring
+        n = ids.shape[0]
+        self.ring_ids[k][:n].copy_(ids, non_blocking=True)
+        self.ring_lp[k][:n].copy_(lps, non_blocking=True)
+        self.d2h_bytes += n * 8
+        if self.is_cuda:
+            self.ring_ev[k].record()
+        return k
 
     def wait(self, k: int):
         if self.is_cuda:

@@ -65,6 +65,27 @@ def test_gemm_modes_bias_split(nat, mode):
         assert _rel_err(out, want) < 6e-3, (mode, split)
 
 
+@pytest.mark.parametrize("T,N,K,bn", [(16, 4096, 4096, 0), (64, 28672, 4096, 0), (256, 6144, 4096, 64), (256, 4096, 14336, 256),
+                                      (200, 1000, 520, 0), (576, 4096, 4096, 0), (700, 28672, 1024, 0), (1000, 4096, 14336, 0)])
+def test_gemm_stream_k(nat, T, N, K, bn):
+    """The partly filled last wave is cut along K across all SMs (policy 2 forces it); policy 1 computes whole tiles."""
+    torch.manual_seed(T + N + K)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K)
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    want = x.float() @ w.float().t() + b.float()
+    base = 1 if T <= 256 else 2
+    outs = []
+    for policy in (1, 2, 2):
+        out = nat.gemm(x, w, bias=b, mode=base | (policy << 8), force_split=bn << 16)
+        torch.cuda.synchronize()
+        nat.workspace().check_status()
+        assert _rel_err(out, want) < 6e-3, policy
+        outs.append(out)
+    assert torch.equal(outs[1], outs[2])          # fixed reduction order
+    assert _rel_err(outs[1], outs[0]) < 2e-3
+
+
 def test_gemm_strided_views(nat):
     torch.manual_seed(4)
     big = torch.randn(40, 3 * 1024, device="cuda", dtype=torch.bfloat16)
@@ -264,21 +285,35 @@ def test_lora_tiled_tensor_core(nat, T, max_rows):
     layer = 2
     offA = layer * layer_units
     offB = layer * layer_units + 3 * K
-    nat.workspace().lora_v3.zero_()      # columns past a slot's rank are never written; other tests leave values there
-    v3, ksplit = nat.lora_shrink_tiles(x, tiles_padded, tiles_padded.shape[0], max_rows, tmaps, G, 0, slot_rank, 3, layer, 64)
+    nat.workspace().lora_v.zero_()      # columns past a slot's rank are never written; other tests leave values there
+    vf = nat.lora_shrink_tiles(x, tiles_padded, tiles_padded.shape[0], max_rows, tmaps, G, 0, slot_rank, 3, layer, 64)
     torch.cuda.synchronize()
     nat.workspace().check_status()
-    v = v3[:ksplit, :T].sum(0)
+    v = vf[:T].clone()
     v_ref = torch.zeros_like(v)
     ref.lora_shrink_tiles(x, tiles.cpu(), len(tl), max_rows, arena, slot_base, slot_rank, offA, 3, 64, v_ref)
     live = torch.tensor([s >= 0 for s in rows], device="cuda")
     assert _rel_err(v[live], v_ref[live]) < 4e-3
     y = torch.randn(T, N, device="cuda", dtype=torch.bfloat16)
     y_ref = y.clone()
-    nat.lora_expand_tiles((v3, ksplit), tiles_padded, tiles_padded.shape[0], max_rows, arena, slot_base, slot_rank, offB, y, parts[0], parts[0] + parts[1])
+    nat.lora_expand_tiles(vf[:T], tiles_padded, tiles_padded.shape[0], max_rows, arena, slot_base, slot_rank, offB, y, parts[0], parts[0] + parts[1])
     ref.lora_expand_tiles(v_ref, tiles.cpu(), len(tl), max_rows, arena, slot_base, slot_rank, offB, y_ref, parts[0], parts[0] + parts[1])
     nat.workspace().check_status()
     assert _rel_err(y, y_ref) < 5e-3
     # rows without a tile are untouched
     untouched = [i for i, s in enumerate(rows) if s < 0]
     assert torch.equal(y[untouched], y_ref[untouched])
+    # the same delta folded into the GEMM epilogue (both operand orientations, whole tiles / stream-K / classic split)
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K)
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    tok_slot = torch.tensor(rows, device="cuda", dtype=torch.int32)
+    epi = nat.LoraEpilogue(v_ref, tok_slot, arena, slot_base, slot_rank, offB, parts[0], parts[0] + parts[1])
+    want = ref.gemm(x, w, bias=b, lora=epi)
+    modes = [(1, 0), (1 | (2 << 8), 0), (1, 2), (2, 0), (2 | (2 << 8), 0)] if T <= 256 else [(2, 0), (2 | (2 << 8), 0)]
+    for mode, split in modes:
+        got = nat.gemm(x, w, bias=b, mode=mode, force_split=split, lora=epi)
+        torch.cuda.synchronize()
+        nat.workspace().check_status()
+        assert _rel_err(got, want) < 6e-3, (mode, split)
+        base = nat.gemm(x, w, bias=b, mode=mode, force_split=split)
+        assert torch.equal(got[untouched], base[untouched])
