@@ -676,8 +676,9 @@ static GemmPlan plan_tiles(int tiles, int kblocks, int K, int bn, int num_sms, l
   const double L = (double)units / (double)ctas;                     // k-blocks per CTA
   const double nparts = (double)kblocks / L + 1.0;
   const double part = (double)kBM * bn * 4.0;
-  const double sk_cost = (double)(dp ? full_waves : 0) * t_tile + (t_tile - kTileFixedNs) * L / kblocks + kTileFixedNs +
-                         2.0 * part / kFillBytesPerNs + 1500.0 + nparts * part / 60.0;
+  // measured: a partial costs about 1 ns per 5 bytes end to end (store, fence, arrival, the last CTA's sum), whatever the part count
+  (void)nparts;
+  const double sk_cost = (double)(dp ? full_waves : 0) * t_tile + (t_tile - kTileFixedNs) * L / kblocks + kTileFixedNs + part / 5.0 + 1500.0;
   if (sk_policy == 2 || sk_cost < pl.cost) {
     pl.dp_tiles = dp;
     pl.sk_ctas = (int)ctas;
@@ -748,10 +749,6 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   if ((K % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return -1000;
   const int sk_policy = (mode >> 8) & 3;      // 0 by cost, 1 whole tiles only, 2 stream-K whenever a wave is partly filled
   mode &= 0xff;
-  // Weights on the M side while the token count is small enough for the 2-byte strided stores of that orientation
-  // not to matter, and always when the LoRA delta rides in the epilogue (its fast path is written for it).
-  const bool has_lora = (lora != nullptr && lora->v != nullptr);
-  const bool swap = (mode == 1) || (mode == 0 && (T <= 256 || (has_lora && T <= 2048)));
   const bool have_counters = (ws != nullptr && counters != nullptr);
   const long long usable_ws = have_counters ? ws_bytes : 0;
   GemmPlan pl{};
@@ -766,6 +763,35 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   p.split_k = 1;
   CUtensorMap ta, tb;
   int bn;
+  const bool has_lora = (lora != nullptr && lora->v != nullptr);
+  const int force_bn = force_split >> 16;
+  const int kblocks_all = (K + kBK - 1) / kBK;
+  // Tokens on the M side: the feature tile (UMMA N) whose tile count wastes the fewest SM slots in the last wave;
+  // 32-wide steps keep the epilogue's 16-byte stores whole.
+  GemmPlan pl_tok{};
+  pl_tok.cost = 1e30;
+  {
+    const int tiles_t = (T + kBM - 1) / kBM;
+    for (int cand = 256; cand >= 64; cand -= 32) {
+      if (force_bn >= 32 && force_bn <= 256 && force_bn % 32 == 0 && cand != force_bn) continue;
+      GemmPlan c = plan_tiles(tiles_t * ((N + cand - 1) / cand), kblocks_all, K, cand, num_sms, usable_ws, have_counters, sk_policy);
+      if (c.cost < pl_tok.cost) pl_tok = c;
+    }
+    if (pl_tok.cost >= 1e30) pl_tok = plan_tiles(tiles_t * ((N + 255) / 256), kblocks_all, K, 256, num_sms, usable_ws, have_counters, sk_policy);
+  }
+  // Orientation.  Up to 128 tokens the weights take the M side (no padded MMA rows, the token tile is the small
+  // operand).  Above that both plans are costed; the weights-on-M epilogue writes 2 bytes per thread and store, which
+  // measures about 15 % slower at equal tiling.  The LoRA epilogue's fast path is written for weights on M.
+  bool swap;
+  GemmPlan pl_swap{};
+  if (mode == 1 || (mode == 0 && (T <= 128 || (has_lora && T <= 2048)))) {
+    swap = true;
+  } else if (mode == 2 || T > 2048) {
+    swap = false;
+  } else {
+    pl_swap = choose_plan_swap(T, N, K, num_sms, usable_ws, have_counters, force_split & 0xffff, force_bn, sk_policy);
+    swap = pl_swap.cost * 1.15 < pl_tok.cost;
+  }
   if (swap) {
     p.a_rows = N; p.b_rows = T;
     p.ldo_a = 1; p.ldo_b = ldo;
@@ -778,15 +804,14 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
     if (make_tmap_bf16_kmajor(&ta, w, N, K, ldw, kBM)) return -1002;
     if (make_tmap_bf16_kmajor(&tb, x, T, K, ldx, bn)) return -1003;
   } else {
-    bn = 256;
+    pl = pl_tok;
+    bn = pl.bn;
     p.a_rows = T; p.b_rows = N;
-    p.umma_n = 256;
+    p.umma_n = bn;
     p.ldo_a = ldo; p.ldo_b = 1;
     p.bias_on_a = 0;
     p.hint_a_first = 0;
     p.b_fastest = 0;
-    const int tiles = ((T + kBM - 1) / kBM) * ((N + bn - 1) / bn);
-    pl = plan_tiles(tiles, (K + kBK - 1) / kBK, K, bn, num_sms, usable_ws, have_counters, sk_policy);
     if (make_tmap_bf16_kmajor(&ta, x, T, K, ldx, kBM)) return -1002;
     if (make_tmap_bf16_kmajor(&tb, w, N, K, ldw, bn)) return -1003;
   }

@@ -63,7 +63,8 @@ template <int BN>
 __global__ void __launch_bounds__(kLtThreads)
 lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const ShrinkTcParams p) {
   using S = LtSmem<BN>;
-  const LoraTile tile = p.tiles[blockIdx.x];
+  LoraTile tile = p.tiles[blockIdx.x];
+  tile.nrows = min(tile.nrows, p.T - tile.row0);       // a table may be older than the batch: rows past T are gone
   if (tile.slot < 0 || tile.nrows <= 0) return;
   if (tile.slot >= p.num_slots) {
     if (threadIdx.x == 0) report_status(p.status, kBadIndex, tile.slot);
@@ -270,7 +271,8 @@ __global__ void __launch_bounds__(kExpThreads, 2) lora_expand_tiled_kernel(const
     const bool col_ok = n < p.N;                        // N is a multiple of 4: a thread's four features are all in or all out
     const int part = n < p.n0 ? 0 : (n < p.n1 ? 1 : 2);
     const __nv_bfloat16* B = p.arena + base + (long long)r * p.unit_off + (long long)n * r;
-    const int nrows = min(tile.nrows, kExpMaxRows);
+    const int nrows = min(min(tile.nrows, kExpMaxRows), p.T - tile.row0);
+    if (nrows <= 0) continue;
     __nv_bfloat16* yrow0 = p.y + (long long)tile.row0 * p.ldy + n;
 
     for (int jc = 0; jc < r; jc += kExpStage) {

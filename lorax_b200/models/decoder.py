@@ -70,6 +70,11 @@ class StepInputs:
     attn_nsplit: int = 1
     num_tokens: Optional[int] = None                 # live rows when the tensors are padded (graphs)
     local_logits: bool = False                       # TP: return this rank's vocabulary shard instead of gathering
+    # Mixed step: rows [0, n_decode) are decode rows (one token each, described by ctx_lens / dec_block_tables), the
+    # rows after them are prefill tokens (described by cu_q / cache_lens / block_tables / tile_*).  One pass over
+    # the weights then serves both, which is what a prefill costs least when a decode batch is running anyway.
+    n_decode: int = 0
+    dec_block_tables: Optional[torch.Tensor] = None
 
 
 class DecoderModel:
@@ -374,7 +379,17 @@ class DecoderModel:
         if c.model_type == "gemma2" and li % 2 == 1:
             window = 0
         softcap = c.attn_logit_softcapping or 0.0
-        if inp.is_prefill:
+        if inp.n_decode:
+            nd = inp.n_decode
+            attn = torch.empty(qkv.shape[0], self.nh * self.d, dtype=qkv.dtype, device=qkv.device)
+            a = ops.attn_decode(qkv[:nd], kv, inp.dec_block_tables, inp.ctx_lens, self.nh, self.nkv, self.d, c.attn_scale, window,
+                                softcap, inp.attn_nsplit, out=attn[:nd])
+            b = ops.attn_prefill(qkv[nd:], kv, inp.block_tables, inp.cu_q, inp.cache_lens, inp.tile_seq, inp.tile_q0,
+                                 self.nh, self.nkv, self.d, c.attn_scale, window, softcap, out=attn[nd:])
+            if a.data_ptr() != attn.data_ptr():      # ops that ignore `out`
+                attn[:nd] = a
+                attn[nd:] = b
+        elif inp.is_prefill:
             attn = ops.attn_prefill(qkv, kv, inp.block_tables, inp.cu_q, inp.cache_lens, inp.tile_seq, inp.tile_q0,
                                     self.nh, self.nkv, self.d, c.attn_scale, window, softcap)
         else:

@@ -264,6 +264,7 @@ def lora_shrink_tiles(x, tiles, num_tiles, max_tile_rows, arena, slot_base, slot
         v = torch.zeros(T, nparts * max_rank, dtype=torch.float32, device=x.device)
     for i in range(num_tiles):
         s, row0, n, _ = (int(q) for q in tiles[i])
+        n = min(n, T - row0)                 # a table may be older than the batch: rows past T are gone
         if s < 0 or n <= 0 or int(slot_base[s]) < 0:
             continue
         r = int(slot_rank[s])
@@ -278,6 +279,7 @@ def lora_expand_tiles(v, tiles, num_tiles, max_tile_rows, arena, slot_base, slot
     bounds = [0, n0, n1, N]
     for i in range(num_tiles):
         s, row0, n, _ = (int(q) for q in tiles[i])
+        n = min(n, T - row0)
         if s < 0 or n <= 0 or int(slot_base[s]) < 0:
             continue
         r = int(slot_rank[s])

@@ -16,6 +16,7 @@ length are retired without waiting for their last token.
 from __future__ import annotations
 
 import collections
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
@@ -91,6 +92,7 @@ class Engine:
         self.stats = dict(prefill_steps=0, decode_steps=0, prefill_tokens=0, generated_tokens=0)
         self.finished: Dict[int, _Seq] = {}
         self.on_adapter_needed: Optional[Callable[[int], bool]] = None     # exchange hook: make adapter resident
+        self.mixed_steps = os.environ.get("LORAX_MIXED_STEPS", "1") != "0"   # prefills ride along with the decode batch
 
     def _auto_blocks(self, page: int) -> int:
         m, c = self.model, self.model.config
@@ -188,65 +190,81 @@ class Engine:
             self._finish(seq, reason)
 
     # ------------------------------------------------------------------ one iteration
+    def _admit(self, picked, next_ids, lps):
+        """Give freshly prefilled requests their decode rows.  The first tokens stay on the device: they are scattered
+        into the rows there and reach the host through the pinned ring like every later token, so the host never waits
+        for a prefill to finish."""
+        rows, sel, poss, blks, ads, rids = [], [], [], [], [], []
+        for i, (req, blocks) in enumerate(picked):
+            seq = _Seq(req, blocks, stopping=StoppingCriteria(req.max_new_tokens, req.eos_token_ids, list(req.stop_sequences),
+                                                              req.ignore_eos_token))
+            seq.launched = 1
+            rids.append(req.request_id)
+            if req.max_new_tokens > 1:
+                seq.row = self.runner.state.take_row(req.request_id)
+                self.running[req.request_id] = seq
+                rows.append(seq.row); sel.append(i); poss.append(len(req.prompt_ids)); blks.append(blocks)
+                ads.append(req.adapter_index)
+            else:                       # only the prefill token is wanted: no decode row
+                seq.retired = True
+                self.draining[req.request_id] = seq
+        if rows:
+            first = next_ids if len(sel) == len(picked) else next_ids[torch.tensor(sel, device=next_ids.device)]
+            self.runner.install(rows, first, poss, blks, ads)
+        mapping = self.runner.resort()
+        for s_ in list(self.running.values()) + list(self.draining.values()):
+            if s_.row in mapping:
+                s_.row = mapping[s_.row]
+        self.inflight.append(("first", self.runner.stash(next_ids, lps), len(picked), rids))
+        self.stats["prefill_steps"] += 1
+        self.stats["prefill_tokens"] += sum(len(r.prompt_ids) for r, _ in picked)
+        self.steps_since_prefill = 0
+
+    def _after_decode_launch(self, k: int, b: int, snapshot: Dict[int, int]):
+        self.inflight.append(("decode", k, b, snapshot))
+        self.stats["decode_steps"] += 1
+        self.steps_since_prefill += 1
+        # rows that reach max_new_tokens with this step need no further steps: retire them now
+        done_rows = []
+        for rid in list(snapshot.values()):
+            s = self.running.get(rid)
+            if s is None:
+                continue
+            s.launched += 1
+            if s.launched >= s.req.max_new_tokens and not s.retired:
+                s.retired = True
+                done_rows.append(s.row)
+                self.draining[rid] = self.running.pop(rid)
+        self.runner.retire(done_rows)
+
+    # ------------------------------------------------------------------ one iteration
     def step(self) -> List[TokenEvent]:
         events: List[TokenEvent] = []
+        queued_before = len(self.inflight)
         picked = self._select_prefill()
+        launched = False
         if picked:
             items = [PrefillItem(r.prompt_ids, 0, b, r.adapter_index) for r, b in picked]
-            next_ids, lps, _ = self.runner.prefill(items)
-            # The first tokens stay on the device: they are scattered into the decode rows there and reach the host
-            # through the pinned ring like every later token, so the host never waits for the prefill to finish.
-            rows, sel, poss, blks, ads, rids = [], [], [], [], [], []
-            for i, (req, blocks) in enumerate(picked):
-                seq = _Seq(req, blocks, stopping=StoppingCriteria(req.max_new_tokens, req.eos_token_ids, list(req.stop_sequences),
-                                                                  req.ignore_eos_token))
-                seq.launched = 1
-                rids.append(req.request_id)
-                if req.max_new_tokens > 1:
-                    seq.row = self.runner.state.take_row(req.request_id)
-                    self.running[req.request_id] = seq
-                    rows.append(seq.row); sel.append(i); poss.append(len(req.prompt_ids)); blks.append(blocks)
-                    ads.append(req.adapter_index)
-                else:                       # only the prefill token is wanted: no decode row
-                    seq.retired = True
-                    self.draining[req.request_id] = seq
-            if rows:
-                first = next_ids if len(sel) == len(picked) else next_ids[torch.tensor(sel, device=next_ids.device)]
-                self.runner.install(rows, first, poss, blks, ads)
-            mapping = self.runner.resort()
-            for s_ in list(self.running.values()) + list(self.draining.values()):
-                if s_.row in mapping:
-                    s_.row = mapping[s_.row]
-            self.inflight.append(("first", self.runner.stash(next_ids, lps), len(picked), rids))
-            self.stats["prefill_steps"] += 1
-            self.stats["prefill_tokens"] += sum(len(r.prompt_ids) for r, _ in picked)
-            self.steps_since_prefill = 0
-
-        launched = None
-        if self.running:
             snapshot = {s.row: rid for rid, s in self.running.items() if not s.retired}
-            if snapshot:
-                launched = self.runner.decode()
-            if launched is not None:
-                k, b, _ = launched
-                self.inflight.append(("decode", k, b, snapshot))
-                self.stats["decode_steps"] += 1
-                self.steps_since_prefill += 1
-                # rows that reach max_new_tokens with this step need no further steps: retire them now
-                done_rows = []
-                for rid in list(snapshot.values()):
-                    s = self.running.get(rid)
-                    if s is None:
-                        continue
-                    s.launched += 1
-                    if s.launched >= s.req.max_new_tokens and not s.retired:
-                        s.retired = True
-                        done_rows.append(s.row)
-                        self.draining[rid] = self.running.pop(rid)
-                self.runner.retire(done_rows)
+            if self.mixed_steps and snapshot and self.runner.can_mix():
+                # one pass over the weights for the running decode rows and the new prompts together
+                k, b, next_ids, lps = self.runner.mixed_step(items)
+                self._after_decode_launch(k, b, snapshot)
+                self._admit(picked, next_ids, lps)
+                launched = True
+            else:
+                next_ids, lps, _ = self.runner.prefill(items)
+                self._admit(picked, next_ids, lps)
 
-        # process results one step behind the GPU (or everything when nothing new was launched)
-        keep = 1 if launched is not None else 0
+        if not launched and self.running:
+            snapshot = {s.row: rid for rid, s in self.running.items() if not s.retired}
+            out = self.runner.decode() if snapshot else None
+            if out is not None:
+                self._after_decode_launch(out[0], out[1], snapshot)
+                launched = True
+
+        # results are read one step behind the GPU: what this step queued stays queued (everything, once idle)
+        keep = (len(self.inflight) - queued_before) if launched else 0
         while len(self.inflight) > keep:
             kind, k, b, who = self.inflight.popleft()
             ids_p, lps_p = self.runner.wait(k)

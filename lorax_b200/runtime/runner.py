@@ -57,6 +57,7 @@ class DecodeState:
         self.lora_tiles = torch.full((max_batch, 4), -1, **i32)
         self.row_slot: Dict[int, int] = {}      # row -> adapter slot (host mirror)
         self.num_lora_tiles = 0
+        self.tile_list: List[Tuple[int, int, int, int]] = []      # host copy of the live part of lora_tiles
         self.free_rows = list(range(max_batch - 1, -1, -1))
         self.live: Dict[int, int] = {}          # row -> request id
         self.high_water = 0
@@ -141,9 +142,10 @@ class ModelRunner:
         return list(blocks) + [0] * (self.max_blocks - n)
 
     # ------------------------------------------------------------------ prefill
-    def prefill(self, items: Sequence[PrefillItem]):
-        """Run one ragged prefill step.  Returns (next_ids, logprobs, logits) for the rows that wanted logits:
-        device tensors; `logits` is None unless some item asked for sampling on the host."""
+    def _prefill_inputs(self, items: Sequence[PrefillItem], row_offset: int = 0, lead_tiles: Sequence[Tuple[int, int, int, int]] = ()):
+        """Host-side assembly of a ragged prefill: one packed H2D transfer for every int array.  Returns the
+        StepInputs and whether any prefill row has an adapter.  In the LoRA tile table the prefill rows are numbered
+        from `row_offset` and `lead_tiles` (tiles of rows that precede them in a mixed step) come first."""
         page = self.page
         ids: List[int] = []
         pos: List[int] = []
@@ -156,11 +158,10 @@ class ModelRunner:
             row = self._table_row(it.blocks)
             slot_id = self._slot_of(it.adapter_index)
             any_lora |= slot_id >= 0
-            for j, tok in enumerate(it.token_ids):
-                p = it.cache_len + j
-                ids.append(int(tok))
-                pos.append(p)
-                slots.append(row[p // page] * page + p % page)
+            c0 = it.cache_len
+            ids.extend(int(t) for t in it.token_ids)
+            pos.extend(range(c0, c0 + n))
+            slots.extend(row[p // page] * page + p % page for p in range(c0, c0 + n))
             tok_slot += [slot_id] * n
             base = cu[-1]
             cu.append(base + n)
@@ -178,8 +179,10 @@ class ModelRunner:
         if T > self.max_prefill_tokens:
             raise ValueError(f"prefill of {T} tokens exceeds max_prefill_tokens={self.max_prefill_tokens}")
         ts, tq = reference.prefill_tiles(q_lens)
-        # one packed H2D transfer for every int array
-        segs = [ids, pos, slots, cu, cache_lens, ts, tq, head_idx, tok_slot, head_slot]
+        tl = reference.build_lora_tiles(tok_slot, 32) if any_lora else []
+        tl = list(lead_tiles) + [(sl, r0 + row_offset, nr, z) for (sl, r0, nr, z) in tl]
+        tl_flat = [x for t in tl for x in t]
+        segs = [ids, pos, slots, cu, cache_lens, ts, tq, head_idx, tok_slot, head_slot, tl_flat]
         flat = [x for s in segs for x in s] + [x for row in tables for x in row]
         dev = self._to_dev(flat)
         views, o = [], 0
@@ -187,24 +190,73 @@ class ModelRunner:
             views.append(dev[o:o + len(s)])
             o += len(s)
         bt = dev[o:].view(len(items), self.max_blocks)
-        d_ids, d_pos, d_slots, d_cu, d_cl, d_ts, d_tq, d_head, d_tokslot, d_headslot = views
+        d_ids, d_pos, d_slots, d_cu, d_cl, d_ts, d_tq, d_head, d_tokslot, d_headslot, d_tiles = views
         if any_lora and self.model.adapters is not None:
             self.model.adapters.fence()
-        tiles = None
-        if any_lora:
-            tl = reference.build_lora_tiles(tok_slot, 32)
-            tiles = LoraTiles(self._to_dev([x for t in tl for x in t]).view(-1, 4), len(tl), 32)
+        tiles = LoraTiles(d_tiles.view(-1, 4), len(tl), 32) if tl else None
         inp = StepInputs(input_ids=d_ids, positions=d_pos, slots=d_slots, is_prefill=True, block_tables=bt, cu_q=d_cu,
-                         cache_lens=d_cl, tile_seq=d_ts, tile_q0=d_tq, lm_head_indices=d_head if len(head_idx) else None,
+                         cache_lens=d_cl, tile_seq=d_ts, tile_q0=d_tq, lm_head_indices=d_head if len(head_idx) else d_ids[:0],
                          tok_slot=d_tokslot if any_lora else None, head_tok_slot=d_headslot if any_lora else None,
                          lora_tiles=tiles)
-        if not head_idx:
-            inp.lm_head_indices = d_ids[:0]
+        return inp, any_lora
+
+    def prefill(self, items: Sequence[PrefillItem]):
+        """Run one ragged prefill step.  Returns (next_ids, logprobs, logits) for the rows that wanted logits:
+        device tensors; `logits` is None unless some item asked for sampling on the host."""
+        inp, _ = self._prefill_inputs(items)
         logits = self.model.forward(inp, self.kv.layers)
         if logits.shape[0] == 0:
             return None, None, logits
         next_ids, lps = self.model.ops.argmax_logprob(logits, softcap=self.model.config.final_logit_softcapping or 0.0)
         return next_ids, lps, logits
+
+    def can_mix(self) -> bool:
+        """A prefill can ride along with the decode rows when those are grouped by adapter (or no adapter is in use)."""
+        ad = self.model.adapters
+        lora = ad is not None and ad.max_rank > 0
+        return self.state.high_water > 0 and (self.tiles_valid or not lora)
+
+    def mixed_step(self, items: Sequence[PrefillItem]):
+        """One forward pass over the decode rows [0, high_water) AND the tokens of a ragged prefill: the weights, the
+        adapters and every elementwise kernel are paid once for both.  Returns (ring index, decode rows, first ids,
+        first log-probs); the decode results land in the pinned ring entry, the prefill's first tokens stay on the
+        device for `install`."""
+        st = self.state
+        nd = st.high_water
+        ad = self.model.adapters
+        lora = ad is not None and ad.max_rank > 0
+        # decode tiles as of the last resort(), clipped to the rows that still exist (rows above them have finished)
+        lead = [(sl, r0, min(nr, nd - r0), 0) for (sl, r0, nr, _) in st.tile_list if r0 < nd] if lora else []
+        pin, any_lora = self._prefill_inputs(items, row_offset=nd, lead_tiles=lead)
+        if lora:
+            ad.fence()
+        dev = self.device
+        cat = torch.cat
+        tok_slot = head_slot = tiles = None
+        if lora:
+            none = torch.full((pin.input_ids.shape[0],), -1, dtype=torch.int32, device=dev)
+            p_tok = pin.tok_slot if pin.tok_slot is not None else none
+            p_head = pin.head_tok_slot if pin.head_tok_slot is not None else none[: pin.lm_head_indices.shape[0]]
+            tok_slot = cat([st.tok_slot[:nd], p_tok])
+            head_slot = cat([st.tok_slot[:nd], p_head])
+            tiles = pin.lora_tiles
+        nsplit = 1
+        if self.is_cuda and nd * self.model.nkv < 96:
+            nsplit = max(1, min(8, 192 // max(nd * self.model.nkv, 1)))
+        head = cat([torch.arange(nd, dtype=torch.int32, device=dev), pin.lm_head_indices + nd])
+        inp = StepInputs(input_ids=cat([st.input_ids[:nd], pin.input_ids]), positions=cat([st.positions[:nd], pin.positions]),
+                         slots=cat([st.slots[:nd], pin.slots]), is_prefill=True, block_tables=pin.block_tables, cu_q=pin.cu_q,
+                         cache_lens=pin.cache_lens, tile_seq=pin.tile_seq, tile_q0=pin.tile_q0, lm_head_indices=head,
+                         tok_slot=tok_slot, head_tok_slot=head_slot, lora_tiles=tiles, attn_nsplit=nsplit, n_decode=nd,
+                         dec_block_tables=st.block_tables[:nd], ctx_lens=st.ctx_lens[:nd])
+        logits = self.model.forward(inp, self.kv.layers)
+        ids, lps = self.model.ops.argmax_logprob(logits, softcap=self.model.config.final_logit_softcapping or 0.0)
+        st.next_ids[:nd].copy_(ids[:nd])
+        st.logprobs[:nd].copy_(lps[:nd])
+        self._advance(nd)
+        k = self.stash(st.next_ids[:nd], st.logprobs[:nd])
+        self.steps += 1
+        return k, nd, ids[nd:], lps[nd:]
 
     # ------------------------------------------------------------------ decode rows
     def install(self, rows: Sequence[int], first_tokens, positions: Sequence[int], blocks: Sequence[Sequence[int]],
@@ -260,6 +312,7 @@ class ModelRunner:
         # tile table: decode tiles hold at most 32 rows
         tl = reference.build_lora_tiles([st.row_slot.get(r, -1) for r in range(n)], 32)
         st.num_lora_tiles = len(tl)
+        st.tile_list = tl
         flat = [x for t in tl for x in t] + [-1, 0, 0, 0] * (st.max_batch - len(tl))
         st.lora_tiles.copy_(self._to_dev(flat).view(-1, 4))
         self.tiles_valid = True

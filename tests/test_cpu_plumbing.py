@@ -89,3 +89,38 @@ def test_logits_close_to_hf(setup):
     with torch.no_grad():
         want = hf(torch.tensor([p])).logits[0]
     assert torch.allclose(logits, want, atol=2e-4, rtol=1e-4)
+
+
+def test_prefill_riding_on_decode_steps_gives_same_tokens(setup):
+    """Requests that arrive while others decode are prefilled in the same forward pass as the decode rows (one pass
+    over the weights for both).  Tokens must equal those of the run where prefill and decode are separate passes."""
+    cfg, model, mgr, adapters = setup
+    g = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, cfg.vocab_size, (int(torch.randint(8, 40, (1,), generator=g)),), generator=g).tolist() for _ in range(7)]
+    adapter_idx = [(i * 2) % 5 for i in range(7)]
+    new_tokens = [12, 1, 9, 14, 6, 10, 8]
+
+    def run(mixed: bool):
+        from lorax_b200.runtime.engine import GenRequest
+        eng = Engine(model, EngineConfig(max_total_tokens=128, max_batch_prefill_tokens=512, waiting_served_ratio=0.0), num_blocks=128,
+                     max_batch=8)
+        eng.mixed_steps = mixed
+        arrivals = {0: [0, 1, 2], 2: [3], 3: [4, 5], 7: [6]}
+        step, n_mixed = 0, 0
+        while step < 200 and (step <= 7 or not eng.idle):
+            for i in arrivals.get(step, []):
+                eng.add_request(GenRequest(i + 1, prompts[i], new_tokens[i], adapter_idx[i]))
+            before = eng.runner.steps
+            had_running = bool(eng.running)
+            will_prefill = bool(eng.waiting)
+            eng.step()
+            n_mixed += int(mixed and had_running and will_prefill)
+            step += 1
+        assert eng.idle
+        return [eng.finished[i + 1].output_ids for i in range(7)], n_mixed
+
+    sep, _ = run(False)
+    mix, n_mixed = run(True)
+    assert n_mixed >= 2
+    assert [len(o) for o in mix] == new_tokens
+    assert mix == sep
