@@ -30,6 +30,17 @@ GROUPS = ("qkv", "o", "gate_up", "down")
 
 
 @dataclass
+class Fp8Weight:
+    """A projection matrix in block-scaled fp8: e4m3 values [N, K] and one fp32 scale per 128 x 128 block."""
+    q: torch.Tensor
+    scale: torch.Tensor
+
+    @property
+    def shape(self):
+        return self.q.shape
+
+
+@dataclass
 class LayerWeights:
     input_norm: torch.Tensor
     qkv_w: torch.Tensor
@@ -109,6 +120,7 @@ class DecoderModel:
         self.max_positions = max_positions or min(c.max_position_embeddings, 32768)
         self.cos_sin = reference.rope_cache(c.rotary_dim, self.max_positions, c.rope_theta, c.rope_scaling, device=self.device)
         self.adapters = None     # AdapterManager, attached by the runtime
+        self.quantized: Optional[str] = None
         # LoRA expand inside the GEMM epilogue instead of its own launch (slower than the separate kernel at present:
         # four epilogue warps cannot hide the latency of the per-token B rows)
         self.fused_lora_epilogue = os.environ.get("LORAX_FUSED_LORA_EPILOGUE", "0") == "1"
@@ -288,6 +300,24 @@ class DecoderModel:
         return self.ops.norm_residual(x, residual, w, c.rms_norm_eps, bias=b, weight_offset=c.norm_weight_offset,
                                       x_scale=x_scale, layernorm=c.norm_type.startswith("layernorm"))
 
+    def quantize_fp8(self):
+        """Replace the dense projection matrices of every layer by block-scaled fp8 (e4m3, 128 x 128 scales) for the
+        fp8 tensor-core GEMM; embeddings, norms, the lm_head, MoE experts and every LoRA adapter stay as they are.
+        The reference's `--quantize fp8` does the same on load with per-tensor scales (layers/fp8.py:14-45)."""
+        for lw in self.layers:
+            for name in ("qkv_w", "o_w", "gate_up_w", "down_w"):
+                w = getattr(lw, name)
+                if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 16 == 0:
+                    q, s = reference.quantize_weight_fp8_block128(w)
+                    setattr(lw, name, Fp8Weight(q.view(torch.uint8) if q.is_cuda else q, s))
+        self.quantized = "fp8"
+
+    def _gemm(self, x, w, b, lora=None):
+        if isinstance(w, Fp8Weight):
+            y = self.ops.gemm_fp8(x if x.dtype == torch.bfloat16 or not x.is_cuda else x.to(torch.bfloat16), w.q, w.scale, bias=b)
+            return y if y.dtype == x.dtype else y.to(x.dtype)
+        return self.ops.gemm(x, w, bias=b, lora=lora) if lora is not None else self.ops.gemm(x, w, bias=b)
+
     def _linear(self, x, w, b, group: str, layer: int, inp: StepInputs, tok_slot=None):
         """Base GEMM plus the multi-adapter LoRA delta for the projection group.  The shrink x A^T is one small launch;
         the expand is a second one, or rides in the GEMM epilogue when `fused_lora_epilogue` is set."""
@@ -296,10 +326,10 @@ class DecoderModel:
         if self.adapters is not None and ts is not None:
             epi = self.adapters.shrink(self.ops, x, ts, group, layer, tiles=inp.lora_tiles)
         if epi is None:
-            return self.ops.gemm(x, w, bias=b)
-        if self.fused_lora_epilogue:
-            return self.ops.gemm(x, w, bias=b, lora=epi)
-        y = self.ops.gemm(x, w, bias=b)
+            return self._gemm(x, w, b)
+        if self.fused_lora_epilogue and not isinstance(w, Fp8Weight):
+            return self._gemm(x, w, b, lora=epi)
+        y = self._gemm(x, w, b)
         self.adapters.expand(self.ops, epi, y, tiles=inp.lora_tiles)
         return y
 
@@ -308,7 +338,7 @@ class DecoderModel:
         fused GEMM -> reduce-scatter -> all-gather kernel; the rank's partial LoRA delta is reduced with it."""
         fused = self.tp.fused if self.tp.world_size > 1 else None
         if (fused is not None and x.is_cuda and x.shape[0] <= min(fused.MAX_TOKENS, fused.max_fused_tokens) and b is None
-                and not self.config.parallel_residual):
+                and not self.config.parallel_residual and not isinstance(w, Fp8Weight)):
             addend = None
             if self.adapters is not None and (inp.tok_slot is not None or inp.lora_tiles is not None) and self.adapters.max_rank > 0:
                 addend = torch.zeros(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)

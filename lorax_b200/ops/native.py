@@ -68,6 +68,8 @@ def load() -> ctypes.CDLL:
         "lx_lora_encode_tmap": ([P, P, I, I, L, I], I),
         "lx_lora_shrink_tc": ([P, L, P, I, I, P, I, I, P, I, I, I, P, I, L, I, P, P, I, I, I, I, P, P], I),
         "lx_gemm_bf16_lora": ([P, P, P, P, I, I, I, L, L, L, F, P, L, P, P, I, I, I, P, I, P, P, P, P, I, L, I, I, P], I),
+        "lx_quant_act_fp8": ([P, L, P, L, P, I, I, I, P], I),
+        "lx_gemm_fp8_block128": ([P, L, P, I, P, L, P, P, L, P, I, I, I, P, L, P, I, P], I),
         "lx_lora_expand_tiled": ([P, I, L, I, P, I, I, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
     }
     for name, (argtypes, restype) in sigs.items():
@@ -186,6 +188,35 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, 
                           out_scale, _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.gemm_counters), _ptr(ws.status),
                           ws.num_sms, mode, force_split, _stream())
     _check(rc, "lx_gemm_bf16")
+    return out
+
+
+def quant_act_fp8(x: torch.Tensor):
+    """x [T, K] bf16 -> (xq [T, K] uint8 holding e4m3, sa [K/128, T16] fp32): one scale per token and 128-wide K block."""
+    T, K = x.shape
+    xq = torch.empty(T, K, dtype=torch.uint8, device=x.device)
+    sa = torch.empty((K + 127) // 128, (T + 15) // 16 * 16, dtype=torch.float32, device=x.device)
+    rc = load().lx_quant_act_fp8(_ptr(x), x.stride(0), _ptr(xq), xq.stride(0), _ptr(sa), sa.stride(0), T, K, _stream())
+    _check(rc, "lx_quant_act_fp8")
+    return xq, sa
+
+
+def gemm_fp8(x: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, bias: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ dequant(wq[N, K], w_scale[N/128, K/128])^T (+ bias): activations are quantised to e4m3 per
+    token and 128-wide K block on the fly, the product runs on the fp8 tensor cores, bf16 out."""
+    assert x.dtype == torch.bfloat16 and wq.dtype in (torch.uint8, torch.float8_e4m3fn) and w_scale.dtype == torch.float32
+    T, K = x.shape
+    N = wq.shape[0]
+    assert wq.shape[1] == K and w_scale.shape == ((N + 127) // 128, (K + 127) // 128) and w_scale.is_contiguous()
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    xq, sa = quant_act_fp8(x)
+    ws = workspace(x.device)
+    rc = load().lx_gemm_fp8_block128(_ptr(xq), xq.stride(0), _ptr(sa), sa.stride(0), _ptr(wq), wq.stride(0), _ptr(w_scale), _ptr(out),
+                                     out.stride(0), _ptr(bias), T, N, K, _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.status),
+                                     ws.num_sms, _stream())
+    _check(rc, "lx_gemm_fp8_block128")
     return out
 
 
@@ -353,7 +384,7 @@ def lora_expand_tiles(v, tiles: torch.Tensor, num_tiles: int, max_tile_rows: int
     _check(rc, "lx_lora_expand_tiled")
 
 # ------------------------------------------------------------------------------------------------ per-op timing
-_TIMED_OPS = ("gemm", "norm_residual", "rope_kvwrite", "act_mul", "embed", "argmax_logprob", "advance_decode", "attn_decode",
+_TIMED_OPS = ("gemm", "gemm_fp8", "norm_residual", "rope_kvwrite", "act_mul", "embed", "argmax_logprob", "advance_decode", "attn_decode",
               "attn_prefill", "lora_shrink", "lora_expand", "lora_shrink_tiles", "lora_expand_tiles")
 _timing_records = None
 _timing_originals = {}

@@ -29,6 +29,54 @@ def gemm(x, w, bias=None, out=None, out_scale: float = 1.0, lora=None, **_):
     return y
 
 
+FP8_MAX = 448.0
+
+
+def quantize_weight_fp8_block128(w: torch.Tensor):
+    """[N, K] -> (e4m3 [N, K], fp32 scales [ceil(N/128), ceil(K/128)]): w ~= q * scale of its 128 x 128 block."""
+    N, K = w.shape
+    nb, kb = (N + 127) // 128, (K + 127) // 128
+    wp = torch.zeros(nb * 128, kb * 128, dtype=torch.float32, device=w.device)
+    wp[:N, :K] = w.float()
+    blocks = wp.view(nb, 128, kb, 128)
+    scale = blocks.abs().amax(dim=(1, 3)).clamp_min(1e-12) / FP8_MAX
+    q = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).view(nb * 128, kb * 128)[:N, :K].to(torch.float8_e4m3fn)
+    return q.contiguous(), scale.contiguous()
+
+
+def dequantize_weight_fp8_block128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    N, K = q.shape
+    s = scale.repeat_interleave(128, 0)[:N].repeat_interleave(128, 1)[:, :K]
+    return q.view(torch.float8_e4m3fn).float() * s
+
+
+def quant_act_fp8(x):
+    """Per token and 128-wide K block: (e4m3 [T, K], scales [K/128, T])."""
+    T, K = x.shape
+    kb = (K + 127) // 128
+    xp = torch.zeros(T, kb * 128, dtype=torch.float32, device=x.device)
+    xp[:, :K] = x.float()
+    b = xp.view(T, kb, 128)
+    scale = b.abs().amax(dim=2).clamp_min(1e-12) / FP8_MAX
+    q = (b / scale[:, :, None]).clamp(-FP8_MAX, FP8_MAX).view(T, kb * 128)[:, :K].to(torch.float8_e4m3fn)
+    return q.contiguous(), scale.t().contiguous()
+
+
+def gemm_fp8(x, wq, w_scale, bias=None, out=None):
+    """Oracle of the block-scaled fp8 GEMM: both operands rounded to e4m3 with their scales, product in fp32."""
+    xq, sa = quant_act_fp8(x)
+    T, K = x.shape
+    xd = xq.float() * sa.t().repeat_interleave(128, 1)[:, :K]
+    y = xd @ dequantize_weight_fp8_block128(wq, w_scale).t()
+    if bias is not None:
+        y = y + bias.float()
+    y = y.to(x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
 def norm_residual(x, residual, weight, eps, bias=None, out=None, weight_offset: float = 0.0, x_scale: float = 1.0,
                   layernorm: bool = False):
     h = x.float() * x_scale

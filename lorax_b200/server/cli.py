@@ -71,8 +71,8 @@ def download_weights(args):
 
 def quantize(args):
     from ..utils.quantize import quantize_checkpoint
-    quantize_checkpoint(args.model_id, args.output_dir, scheme=args.scheme)
-    _log("INFO", f"quantised checkpoint written to {args.output_dir}", args.json_output)
+    stats = quantize_checkpoint(args.model_id, args.output_dir, method=args.scheme)
+    _log("INFO", f"quantised checkpoint written to {args.output_dir}: {stats['quantized']} of {stats['tensors']} tensors in fp8", args.json_output)
 
 
 def main(argv=None):
@@ -111,7 +111,7 @@ def main(argv=None):
     q = sub.add_parser("quantize")
     q.add_argument("model_id")
     q.add_argument("output_dir")
-    q.add_argument("--scheme", default="fp8-block128")
+    q.add_argument("--scheme", default="fp8", choices=["fp8"])
     q.add_argument("--json-output", action="store_true")
     q.set_defaults(fn=quantize)
     args = ap.parse_args(argv)

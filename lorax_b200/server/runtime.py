@@ -437,6 +437,14 @@ def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel]
     w = Weights(weight_files(model_dir), device="cpu", dtype=dtype, rank=tp.rank, world_size=tp.world_size)
     tp.barrier()
     model = DecoderModel.from_weights(mc, w, dev, dtype, tp, max_positions=min(mc.max_position_embeddings, max(cfg.max_total_tokens + 64, 2048)))
+    quantize = kw.pop("quantize", None) or cfg.quantize
+    qc = getattr(mc, "quantization_config", None) or {}
+    if quantize is None and isinstance(qc, dict) and qc.get("quant_method") == "fp8":
+        quantize = "fp8"
+    if quantize == "fp8":
+        model.quantize_fp8()
+    elif quantize is not None:
+        raise ValueError(f"--quantize {quantize}: this build serves bf16/fp16/fp32 and block-scaled fp8 (`--quantize fp8`)")
     tp.barrier()
     tok = load_tokenizer(model_dir)
     rt = ShardRuntime(model, tok, cfg, model_id=model_id, **kw)

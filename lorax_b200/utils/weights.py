@@ -82,10 +82,24 @@ class Weights(AbstractWeights):
             t = t.to(self.dtype)
         return t.to(self.device)
 
+    def _dequant_fp8(self, name: str, t: torch.Tensor, row0: int = 0, col0: int = 0) -> torch.Tensor:
+        """Block-scaled fp8 checkpoints (`<name>` in e4m3 next to `<name>_scale_inv`, one fp32 scale per 128 x 128 block):
+        return the slice starting at (row0, col0) in the loader's dtype.  The model re-quantises for its own kernels."""
+        if t.dtype != torch.float8_e4m3fn or not self.has_tensor(name + "_scale_inv"):
+            return t
+        if row0 % 128 or col0 % 128:
+            raise ValueError(f"{name}: an fp8 shard must start on a 128-element block boundary (got {row0}, {col0})")
+        fn, key = self._resolve(name + "_scale_inv")
+        scale = self._handle(fn).get_tensor(key).float()
+        r, c = t.shape
+        s = scale[row0 // 128: row0 // 128 + (r + 127) // 128, col0 // 128: col0 // 128 + (c + 127) // 128]
+        s = s.repeat_interleave(128, 0)[:r].repeat_interleave(128, 1)[:, :c]
+        return (t.float() * s).to(self.dtype or torch.bfloat16)
+
     # ---------------------------------------------------------------- getters
     def get_tensor(self, name: str) -> torch.Tensor:
         fn, key = self._resolve(name)
-        return self._finish(self._handle(fn).get_tensor(key))
+        return self._finish(self._dequant_fp8(name, self._handle(fn).get_tensor(key)))
 
     def get_partial_sharded(self, name: str, dim: int) -> torch.Tensor:
         """This rank's contiguous block of `dim` (block = size // world_size; the tail goes to the last rank's
@@ -95,9 +109,9 @@ class Weights(AbstractWeights):
         block = size // self.world_size
         start, stop = self.rank * block, (self.rank + 1) * block
         if dim == 0:
-            t = sl[start:stop]
+            t = self._dequant_fp8(name, sl[start:stop], row0=start)
         elif dim == 1:
-            t = sl[:, start:stop]
+            t = self._dequant_fp8(name, sl[:, start:stop], col0=start)
         else:
             raise NotImplementedError("only dims 0 and 1 are sharded")
         return self._finish(t)
@@ -109,7 +123,7 @@ class Weights(AbstractWeights):
         return self.get_partial_sharded(name, dim)
 
     def get_rows(self, name: str, start: int, stop: int) -> torch.Tensor:
-        return self._finish(self._slice(name)[start:stop])
+        return self._finish(self._dequant_fp8(name, self._slice(name)[start:stop], row0=start))
 
     def get_multi_sharded(self, names: Iterable[str], dim: int) -> torch.Tensor:
         """Concatenate the per-rank shards of several tensors (fused QKV / gate_up)."""

@@ -46,6 +46,33 @@ def test_prefill_logits_match_cpu_oracle():
     assert (outs[1][1] - outs[1][0]).norm() > 0
 
 
+def test_fp8_model_prefill_matches_cpu_oracle():
+    """`quantize_fp8()` on both devices: the tcgen05 fp8 GEMM path against the PyTorch oracle of the same quantised
+    model (same e4m3 weights and scales, activations rounded the same way), adapters included."""
+    cfg, gm, _ = _build("cuda", torch.bfloat16)
+    _, cm, _ = _build("cpu", torch.float32)
+    _, base, _ = _build("cpu", torch.float32)
+    gm.quantize_fp8()
+    cm.quantize_fp8()
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 40, 70)]
+    outs = []
+    for m in (gm, cm, base):
+        kv = KVCache(cfg.num_hidden_layers, 32, m.nkv, m.d, m.dtype, m.device)
+        r = ModelRunner(m, kv, max_batch=4, max_seq_tokens=256, max_prefill_tokens=512, use_graphs=False)
+        items = [PrefillItem(p, 0, [1 + 3 * i, 2 + 3 * i, 3 + 3 * i], adapter_index=i) for i, p in enumerate(prompts)]
+        _, _, logits = r.prefill(items)
+        outs.append(logits.float().cpu())
+    from lorax_b200.ops import native
+    native.workspace().check_status()
+    # the two devices round activations that differ by bf16 noise, so some e4m3 roundings flip (one step = 6 %); what must
+    # hold is that the GPU path is as close to the unquantised model as the oracle of the quantised model is
+    e_gpu = ((outs[0] - outs[2]).norm() / outs[2].norm()).item()
+    e_cpu = ((outs[1] - outs[2]).norm() / outs[2].norm()).item()
+    assert e_cpu < 0.15 and e_gpu < 1.25 * e_cpu + 0.01, (e_gpu, e_cpu)
+    assert (outs[0] - outs[1]).norm() / outs[1].norm() < 0.1
+
+
 @pytest.mark.parametrize("graphs", [False, True])
 def test_decode_logits_match_cpu_oracle_teacher_forced(graphs):
     """Prefill 8 requests over 4 adapters, then 12 decode steps; both devices are fed the oracle's tokens so

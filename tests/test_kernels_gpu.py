@@ -317,3 +317,32 @@ def test_lora_tiled_tensor_core(nat, T, max_rows):
         assert _rel_err(got, want) < 6e-3, (mode, split)
         base = nat.gemm(x, w, bias=b, mode=mode, force_split=split)
         assert torch.equal(got[untouched], base[untouched])
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 256, 256), (16, 4096, 4096), (48, 1024, 14336), (100, 6144, 4096), (128, 384, 512),
+                                   (300, 4096, 4096), (1000, 1024, 1024)])
+def test_gemm_fp8_block128(nat, T, N, K):
+    """Block-scaled e4m3 GEMM (128x128 weight scales, 1x128 activation scales) on tcgen05 kind::f8f6f4 against the
+    PyTorch oracle that rounds both operands the same way and multiplies in fp32."""
+    torch.manual_seed(T + N + K)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    x[:, ::97] *= 8.0                                  # a few outlier columns: the per-block scales must absorb them
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K)
+    b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
+    wq, ws = ref.quantize_weight_fp8_block128(w)
+    # the activation quantiser alone
+    xq, sa = nat.quant_act_fp8(x)
+    xq_ref, sa_ref = ref.quant_act_fp8(x)
+    torch.cuda.synchronize()
+    assert torch.allclose(sa[:, :T], sa_ref, rtol=1e-6, atol=0)
+    a, b_ = xq.view(torch.float8_e4m3fn).float(), xq_ref.float()
+    assert ((a - b_).abs() <= b_.abs() * 0.13 + 2e-3).all()          # x * (1 / s) against x / s: at most one e4m3 step apart
+    assert (a != b_).float().mean().item() < 0.03
+    out = nat.gemm_fp8(x, wq, ws, bias=b)
+    torch.cuda.synchronize()
+    nat.workspace().check_status()
+    want = ref.gemm_fp8(x, wq, ws, bias=b)
+    assert _rel_err(out, want) < 6e-3
+    # and the quantised product is close to the bf16 one
+    full = x.float() @ w.float().t() + b.float()
+    assert _rel_err(out, full) < 6e-2

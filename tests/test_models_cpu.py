@@ -103,3 +103,44 @@ def test_merge_strategies():
     big = torch.ones(1000)
     dare = merge_tensors([big], [1.0], "dare_linear", density=0.5, generator=torch.Generator().manual_seed(0))
     assert 0.8 < dare.mean().item() < 1.2 and set(dare.unique().tolist()) <= {0.0, 2.0}
+
+
+def test_fp8_block128_quantiser_roundtrip(tmp_path):
+    """128 x 128 block scales: the round trip stays within e4m3 precision even with an outlier block, and the
+    checkpoint quantiser writes fp8 tensors plus `_scale_inv` tensors and marks the config."""
+    import json
+    import torch
+    from safetensors.torch import load_file, save_file
+    from lorax_b200.ops import reference as ref
+    from lorax_b200.utils.quantize import dequantize_state_dict, quantize_checkpoint
+
+    torch.manual_seed(0)
+    w = torch.randn(300, 520) * 0.05
+    w[:128, :128] *= 50.0                      # an outlier block must not cost the others their precision
+    q, s = ref.quantize_weight_fp8_block128(w)
+    assert q.dtype == torch.float8_e4m3fn and s.shape == (3, 5)
+    back = ref.dequantize_weight_fp8_block128(q, s)
+    rel = ((back - w).abs() / w.abs().clamp_min(1e-3))
+    assert rel[200:, 300:].median().item() < 0.04 and (back - w).abs().max().item() <= w.abs().max().item() * 0.07
+    x = torch.randn(5, 520).to(torch.bfloat16)
+    y = ref.gemm_fp8(x, q, s)
+    want = x.float() @ w.t()
+    assert ((y.float() - want).norm() / want.norm()).item() < 0.05
+
+    src, dst = tmp_path / "m", tmp_path / "q"
+    src.mkdir()
+    sd = {"model.layers.0.self_attn.q_proj.weight": torch.randn(256, 256).to(torch.bfloat16),
+          "model.layers.0.input_layernorm.weight": torch.ones(256).to(torch.bfloat16),
+          "model.embed_tokens.weight": torch.randn(512, 256).to(torch.bfloat16)}
+    save_file(sd, str(src / "model.safetensors"))
+    (src / "config.json").write_text(json.dumps({"model_type": "llama"}))
+    stats = quantize_checkpoint(str(src), str(dst))
+    assert stats == {"tensors": 3, "quantized": 1}
+    out = load_file(str(dst / "model.safetensors"))
+    assert out["model.layers.0.self_attn.q_proj.weight"].dtype == torch.float8_e4m3fn
+    assert out["model.layers.0.self_attn.q_proj.weight_scale_inv"].shape == (2, 2)
+    assert out["model.embed_tokens.weight"].dtype == torch.bfloat16
+    assert json.loads((dst / "config.json").read_text())["quantization_config"]["weight_block_size"] == [128, 128]
+    deq = dequantize_state_dict(out)
+    err = (deq["model.layers.0.self_attn.q_proj.weight"].float() - sd["model.layers.0.self_attn.q_proj.weight"].float()).abs().max()
+    assert err.item() < 0.3
