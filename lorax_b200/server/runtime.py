@@ -426,14 +426,94 @@ def load_tokenizer(model_dir: str):
     return None
 
 
+class EncoderRuntime:
+    """Shard runtime of an embedding / token-classification model (BERT, RoBERTa, DistilBERT): `Embed` and `Classify`
+    are served, every generation RPC answers with an error (reference: `FlashBert.embed/classify`,
+    `server/lorax_server/models/flash_bert.py:186-218`)."""
+
+    chat_template: Optional[str] = None
+    bos_token: str = ""
+    eos_token: str = ""
+
+    def __init__(self, model, tokenizer=None, cfg: Optional[EngineConfig] = None, model_id: str = ""):
+        self.pb = load_pb()
+        self.model = model
+        self.tokenizer = tokenizer
+        self.cfg = cfg or EngineConfig()
+        self.model_id = model_id
+        self.lock = threading.Lock()
+
+    def info(self):
+        return self.pb.InfoResponse(requires_padding=False, dtype=str(self.model.dtype).replace("torch.", ""),
+                                    device_type=self.model.device.type, block_size=self.cfg.block_size, speculate=0,
+                                    supports_generation=False, supports_embeddings=True,
+                                    supports_classification=self.model.cls_w is not None, chunked_prefill=False,
+                                    requires_block_allocator=False)
+
+    def health(self):
+        return self.pb.HealthResponse()
+
+    def warmup(self, req):
+        return self.pb.WarmupResponse(max_supported_total_tokens=self.cfg.max_batch_prefill_tokens)
+
+    def tokenize(self, text: str, add_special: bool = True) -> List[int]:
+        if self.tokenizer is None:
+            return [int(x) for x in text.split()] if text.replace(" ", "").isdigit() else [ord(ch) % self.model.config.vocab_size for ch in text]
+        return self.tokenizer.encode(text, add_special_tokens=add_special).ids
+
+    def tokenize_detailed(self, body: dict) -> list:
+        return [{"id": i, "text": str(i), "start": 0, "stop": 0} for i in self.tokenize(body.get("inputs", ""))]
+
+    def apply_chat_template(self, body: dict) -> str:
+        raise ValueError("an embedding model has no chat template")
+
+    def _ids(self, r) -> List[int]:
+        ids = list(r.tokenized_inputs.ids) if r.HasField("tokenized_inputs") and len(r.tokenized_inputs.ids) else self.tokenize(r.inputs)
+        if r.truncate:
+            ids = ids[: r.truncate]
+        return ids
+
+    def embed(self, req):
+        try:
+            with self.lock:
+                vecs = self.model.embed([self._ids(r) for r in req.batch.requests])
+            return self.pb.EmbedResponse(embeddings=[self.pb.Embedding(request_id=r.id, values=v) for r, v in zip(req.batch.requests, vecs)])
+        except Exception as e:      # surfaced to the router as the RPC's error string, as the reference does
+            return self.pb.EmbedResponse(errorMsg=str(e))
+
+    def classify(self, req):
+        try:
+            with self.lock:
+                labels, scores = self.model.classify([self._ids(r) for r in req.batch.requests])
+            return self.pb.ClassifyResponse(classify_prediction_lists=[
+                self.pb.ClassifyPredictionList(request_id=r.id, predictions=l, scores=sc) for r, l, sc in zip(req.batch.requests, labels, scores)])
+        except Exception as e:
+            return self.pb.ClassifyResponse(errorMsg=str(e))
+
+    def _no_generation(self, *_a, **_k):
+        raise ValueError("this model serves embeddings / classification, not text generation")
+
+    prefill = decode = filter_batch = download_adapter = load_adapter = offload_adapter = _no_generation
+
+    def clear_cache(self, req):
+        return self.pb.ClearCacheResponse()
+
+
 def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel] = None, dtype: Optional[torch.dtype] = None,
                   device: Optional[str] = None, source: str = "hub", revision: Optional[str] = None, **kw) -> ShardRuntime:
     tp = tp or TensorParallel.init_from_env()
     model_dir = resolve_model(model_id, source, revision)
-    mc = ModelConfig.from_pretrained(model_dir)
     dev = torch.device(device) if device else (tp.device or torch.device("cpu"))
     if dtype is None:
         dtype = torch.bfloat16 if dev.type == "cuda" else torch.float32
+    with open(os.path.join(model_dir, "config.json")) as f:
+        raw_cfg = json.load(f)
+    from ..models.encoder import ENCODER_TYPES, EncoderConfig, EncoderModel
+    if raw_cfg.get("model_type") in ENCODER_TYPES:
+        w = Weights(weight_files(model_dir), device="cpu", dtype=dtype)
+        enc = EncoderModel.from_weights(EncoderConfig.from_dict(raw_cfg), w, dev, dtype)
+        return EncoderRuntime(enc, load_tokenizer(model_dir), cfg, model_id=model_id)
+    mc = ModelConfig.from_pretrained(model_dir)
     w = Weights(weight_files(model_dir), device="cpu", dtype=dtype, rank=tp.rank, world_size=tp.world_size)
     tp.barrier()
     model = DecoderModel.from_weights(mc, w, dev, dtype, tp, max_positions=min(mc.max_position_embeddings, max(cfg.max_total_tokens + 64, 2048)))

@@ -1,0 +1,98 @@
+"""Embedding / token-classification model behind the C++ router on CPU: `/embed`, `/v1/embeddings`, `/classify`,
+`/classify_batch`, and the generation routes refusing politely."""
+import json
+import os
+import subprocess
+import time
+import urllib.request
+
+import pytest
+import torch
+from safetensors.torch import save_file
+
+from test_full_stack import ROUTER, _free_port, _post
+
+
+@pytest.fixture(scope="module")
+def emb_stack(tmp_path_factory):
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from lorax_b200.csrc import build
+    from lorax_b200.models.encoder import EncoderConfig, random_encoder_state_dict
+    build.build_host()
+    root = tmp_path_factory.mktemp("emb")
+    raw = {"model_type": "distilbert", "vocab_size": 512, "dim": 64, "n_layers": 2, "n_heads": 4, "hidden_dim": 128,
+           "max_position_embeddings": 64, "id2label": {str(i): f"TAG{i}" for i in range(4)}}
+    cfg = EncoderConfig.from_dict(raw)
+    sd = random_encoder_state_dict(cfg, seed=11, num_labels=4)
+    mdir = root / "model"
+    mdir.mkdir()
+    save_file({("distilbert." + k if not k.startswith("classifier") else k): v for k, v in sd.items()}, str(mdir / "model.safetensors"),
+              metadata={"format": "pt"})
+    (mdir / "config.json").write_text(json.dumps(raw))
+    vocab = {f"w{i}": i for i in range(512)}
+    vocab["<unk>"] = 0
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    tok.save(str(mdir / "tokenizer.json"))
+
+    from lorax_b200.config import EngineConfig
+    from lorax_b200.server.runtime import EncoderRuntime, build_runtime
+    from lorax_b200.server.transport import FramedServer
+    rt = build_runtime(str(mdir), EngineConfig(max_input_length=32, max_total_tokens=64, max_batch_prefill_tokens=128, compile=False),
+                       device="cpu", dtype=torch.float32, source="local")
+    assert isinstance(rt, EncoderRuntime)
+    uds = str(root / "shard")
+    srv = FramedServer(rt, uds + "-0.lx").start()
+    port = _free_port()
+    proc = subprocess.Popen([ROUTER, "--port", str(port), "--hostname", "127.0.0.1", "--master-shard-uds-path", uds, "--num-shard", "1",
+                             "--max-input-length", "32", "--max-total-tokens", "64", "--max-batch-prefill-tokens", "128",
+                             "--model-id", "tiny-distilbert"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    ok = False
+    for _ in range(100):
+        try:
+            with urllib.request.urlopen(f"http://127.0.0.1:{port}/info", timeout=1) as r:
+                ok = r.status == 200
+                break
+        except Exception:
+            time.sleep(0.1)
+    if not ok:
+        proc.kill()
+        raise RuntimeError("router did not come up: " + proc.stdout.read().decode()[-2000:])
+    yield dict(port=port, rt=rt)
+    proc.terminate()
+    try:
+        proc.wait(timeout=10)
+    except subprocess.TimeoutExpired:
+        proc.kill()
+    srv.stop()
+
+
+def test_embed_and_classify_routes(emb_stack):
+    port, rt = emb_stack["port"], emb_stack["rt"]
+    text = "w5 w9 w77 w3"
+    want = rt.model.embed([rt.tokenize(text)])[0]
+    st, body, _ = _post(port, "/embed", {"inputs": text})
+    assert st == 200, body
+    got = json.loads(body)["embeddings"]
+    assert len(got) == 64 and max(abs(a - b) for a, b in zip(got, want)) < 1e-4
+
+    st, body, _ = _post(port, "/v1/embeddings", {"input": [text, "w1 w2"], "model": "x"})
+    assert st == 200, body
+    data = json.loads(body)["data"]
+    assert [d["index"] for d in data] == [0, 1] and len(data[1]["embedding"]) == 64
+    assert max(abs(a - b) for a, b in zip(data[0]["embedding"], want)) < 1e-4
+
+    labels, scores = rt.model.classify([rt.tokenize(text)])
+    st, body, _ = _post(port, "/classify", {"inputs": text})
+    assert st == 200, body
+    ents = json.loads(body)
+    assert [e["entity_group"] for e in ents] == labels[0]
+    assert max(abs(e["score"] - s) for e, s in zip(ents, scores[0])) < 1e-4
+
+    st, body, _ = _post(port, "/classify_batch", {"inputs": [text, "w8"]})
+    assert st == 200, body
+    out = json.loads(body)
+    assert len(out) == 2 and len(out[1]) == 1
+
+    st, body, _ = _post(port, "/generate", {"inputs": text, "parameters": {"max_new_tokens": 2}})
+    assert st in (422, 424), body

@@ -144,3 +144,64 @@ def test_fp8_block128_quantiser_roundtrip(tmp_path):
     deq = dequantize_state_dict(out)
     err = (deq["model.layers.0.self_attn.q_proj.weight"].float() - sd["model.layers.0.self_attn.q_proj.weight"].float()).abs().max()
     assert err.item() < 0.3
+
+
+def test_encoders_match_hf():
+    """BERT / RoBERTa embeddings (first-token hidden state) and DistilBERT token classification against HuggingFace,
+    ragged batch of three sequences."""
+    from transformers import BertConfig, BertModel, DistilBertConfig, DistilBertForTokenClassification, RobertaConfig, RobertaModel
+    from lorax_b200.models.encoder import EncoderConfig, EncoderModel, random_encoder_state_dict
+    from lorax_b200.utils.weights import InMemoryWeights
+
+    torch.manual_seed(0)
+    seqs = [[5, 9, 77, 3, 12], [101, 7, 8], [4, 4, 250, 17, 90, 33, 2, 6]]
+
+    # ---- BERT
+    hc = BertConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+                    max_position_embeddings=64, type_vocab_size=2)
+    hc._attn_implementation = "eager"
+    cfg = EncoderConfig.from_dict(hc.to_dict())
+    sd = random_encoder_state_dict(cfg, seed=1)
+    hf = BertModel(hc, add_pooling_layer=False).eval()
+    missing, unexpected = hf.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected
+    ours = EncoderModel.from_weights(cfg, InMemoryWeights(sd), "cpu", torch.float32)
+    got = torch.tensor(ours.embed(seqs))
+    with torch.no_grad():
+        want = torch.stack([hf(torch.tensor([s])).last_hidden_state[0, 0] for s in seqs])
+    assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
+
+    # ---- RoBERTa (positions start at pad_token_id + 1)
+    rc = RobertaConfig(vocab_size=300, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, intermediate_size=128,
+                       max_position_embeddings=66, type_vocab_size=1, pad_token_id=1)
+    rc._attn_implementation = "eager"
+    cfg = EncoderConfig.from_dict(rc.to_dict())
+    sd = random_encoder_state_dict(cfg, seed=2)
+    hf = RobertaModel(rc, add_pooling_layer=False).eval()
+    missing, unexpected = hf.load_state_dict(sd, strict=False)
+    assert not missing and not unexpected
+    ours = EncoderModel.from_weights(cfg, InMemoryWeights({"roberta." + k: v for k, v in sd.items()}), "cpu", torch.float32)
+    got = torch.tensor(ours.embed(seqs))
+    with torch.no_grad():
+        want = torch.stack([hf(torch.tensor([s])).last_hidden_state[0, 0] for s in seqs])
+    assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
+
+    # ---- DistilBERT token classification
+    dc = DistilBertConfig(vocab_size=300, dim=64, n_layers=2, n_heads=4, hidden_dim=128, max_position_embeddings=64, num_labels=5,
+                          id2label={i: f"T{i}" for i in range(5)}, label2id={f"T{i}": i for i in range(5)})
+    dc._attn_implementation = "eager"
+    cfg = EncoderConfig.from_dict(dc.to_dict())
+    sd = random_encoder_state_dict(cfg, seed=3, num_labels=5)
+    hf = DistilBertForTokenClassification(dc).eval()
+    missing, unexpected = hf.load_state_dict({("distilbert." + k if not k.startswith("classifier") else k): v for k, v in sd.items()},
+                                             strict=False)
+    assert not missing and not unexpected
+    ours = EncoderModel.from_weights(cfg, InMemoryWeights({("distilbert." + k if not k.startswith("classifier") else k): v
+                                                           for k, v in sd.items()}), "cpu", torch.float32)
+    labels, scores = ours.classify(seqs)
+    for s, lab, sc in zip(seqs, labels, scores):
+        with torch.no_grad():
+            p = torch.softmax(hf(torch.tensor([s])).logits[0], -1)
+        conf, pred = p.max(-1)
+        assert lab == [f"T{i}" for i in pred.tolist()]
+        assert torch.allclose(torch.tensor(sc), conf, atol=2e-4)
