@@ -236,6 +236,37 @@ act_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__
 
 // ------------------------------------------------------------------------------------------------
 // Embedding gather with vocabulary range [v0, v1): rows outside are written as zero (vocab-parallel).
+struct EmbedPeerParams {
+  const __nv_bfloat16* tables[8];     // every rank's shard, as mapped into this process
+  int rows_per_rank, world, vocab, H;
+  float mult;
+};
+
+__global__ void __launch_bounds__(128) embed_peer_kernel(const int* __restrict__ ids, const EmbedPeerParams p, __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  uint4* o = reinterpret_cast<uint4*>(out + (long long)t * p.H);
+  const int owner = id >= 0 ? id / p.rows_per_rank : p.world;
+  if (id < 0 || id >= p.vocab || owner >= p.world) {
+    for (int v = threadIdx.x; v < p.H / 8; v += blockDim.x) o[v] = make_uint4(0, 0, 0, 0);
+    return;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(p.tables[owner] + (long long)(id - owner * p.rows_per_rank) * p.H);
+  for (int v = threadIdx.x; v < p.H / 8; v += blockDim.x) {
+    uint4 a = src[v];
+    if (p.mult != 1.f) {
+      uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float2 f = unpack_bf16x2(w[q]);
+        w[q] = pack_bf16x2(f.x * p.mult, f.y * p.mult);
+      }
+      a = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    o[v] = a;
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(128)
 embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out, int H,
@@ -387,6 +418,23 @@ int lx_embed(const int* ids, const void* table, void* out, int T, int H, int v0,
   if (H % 8 != 0) return -1;
   embed_kernel<<<T, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ids, reinterpret_cast<const __nv_bfloat16*>(table),
                                                                       reinterpret_cast<__nv_bfloat16*>(out), H, v0, v1, mult);
+  return -(int)cudaGetLastError();
+}
+
+// Vocabulary-parallel embedding without a collective: rank r owns rows [r * rows_per_rank, (r + 1) * rows_per_rank) of the
+// table in peer-mapped memory and every rank reads the rows it needs straight from the owner over NVLink (plain peer loads of
+// a table that never changes: nothing to wait for).  Replaces embedding lookup + all-reduce of [T, H]
+// (server/lorax_server/layers/tensor_parallel.py:153-190 masks out-of-shard ids and all-reduces).
+int lx_embed_peer(const int* ids, const void* peer_tables, void* out, int T, int H, int rows_per_rank, int world, int vocab, float mult,
+                  void* stream) {
+  using namespace lx;
+  if (T <= 0) return 0;
+  if (H % 8 != 0 || world < 1 || world > 8) return -1;
+  EmbedPeerParams p{};
+  const unsigned long long* tabs = reinterpret_cast<const unsigned long long*>(peer_tables);
+  for (int r = 0; r < world; ++r) p.tables[r] = reinterpret_cast<const __nv_bfloat16*>(tabs[r]);
+  p.rows_per_rank = rows_per_rank; p.world = world; p.vocab = vocab; p.H = H; p.mult = mult;
+  embed_peer_kernel<<<T, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ids, p, reinterpret_cast<__nv_bfloat16*>(out));
   return -(int)cudaGetLastError();
 }
 

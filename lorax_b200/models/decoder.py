@@ -352,10 +352,14 @@ class DecoderModel:
     def forward(self, inp: StepInputs, kv_cache: List[torch.Tensor]) -> torch.Tensor:
         """-> logits [n_out, vocab] (full vocabulary on every rank)."""
         c, ops = self.config, self.ops
-        h = ops.embed(inp.input_ids, self.embed, v0=self.vocab_start, v1=self.vocab_start + self.embed.shape[0],
-                      mult=c.embedding_multiplier)
-        if self.tp.world_size > 1:
-            h = self.tp.all_reduce(h)
+        fused = self.tp.fused if self.tp.world_size > 1 else None
+        if fused is not None and fused.embed_ptrs is not None and inp.input_ids.is_cuda:
+            h = fused.embed(inp.input_ids, c.embedding_multiplier)       # peer reads, no collective
+        else:
+            h = ops.embed(inp.input_ids, self.embed, v0=self.vocab_start, v1=self.vocab_start + self.embed.shape[0],
+                          mult=c.embedding_multiplier)
+            if self.tp.world_size > 1:
+                h = self.tp.all_reduce(h)
         if self.pos_embed is not None:
             h = h + self.pos_embed[inp.positions.long()]
         residual = h

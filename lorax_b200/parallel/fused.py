@@ -8,6 +8,8 @@
 * `gemm_allreduce`  row-parallel O / down projection: GEMM -> reduce-scatter -> all-gather in one kernel, with the
   rank's partial LoRA delta riding along as an addend (replaces GEMM + NCCL all-reduce + LoRA collectives, call
   sites C2 / C3 / C5 of the reference: `utils/layers.py:279-300, 329-374`).
+* `embed`           vocabulary-parallel embedding by peer reads: every rank fetches the rows it needs from the owner's shard,
+  the [T, H] all-reduce of call site C1 (`layers/tensor_parallel.py:153-190`) disappears.
 * `argmax_tp`       greedy sampling over vocabulary-parallel logits exchanging 16 bytes per row instead of
   all-gathering the logits (C6, `layers/tensor_parallel.py:50-79`).
 
@@ -45,6 +47,9 @@ class FusedCollectives:
         lib.lx_gemm_allreduce.restype = I
         lib.lx_argmax_tp.argtypes = [P, L, I, I, I, P, P, P, I, I, ctypes.POINTER(L), I, P, P]
         lib.lx_argmax_tp.restype = I
+        lib.lx_embed_peer.argtypes = [P, P, P, I, I, I, I, I, ctypes.c_float, P]
+        lib.lx_embed_peer.restype = I
+        self.embed_ptrs = None
         self.lib = lib
         self.tp = tp
         self.rank, self.world = tp.rank, tp.world_size
@@ -87,6 +92,29 @@ class FusedCollectives:
                                    self.ws.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
         native._check(rc, "lx_argmax_tp")
 
+    def share_embedding(self, table: torch.Tensor, vocab: int) -> torch.Tensor:
+        """Move this rank's embedding shard [rows, H] into peer-mapped memory and exchange the pointers.  Returns the new
+        home of the shard (the caller drops the old tensor)."""
+        import torch.distributed._symmetric_memory as symm
+        shared = symm.empty(table.shape, dtype=table.dtype, device=table.device)
+        shared.copy_(table)
+        torch.cuda.synchronize(table.device)
+        self.embed_handle = symm.rendezvous(shared, self.tp.group)
+        self.embed_ptrs = (ctypes.c_ulonglong * self.world)(*list(self.embed_handle.buffer_ptrs))
+        self.embed_rows, self.embed_vocab, self.embed_h = table.shape[0], vocab, table.shape[1]
+        self.tp.barrier()
+        return shared
+
+    def embed(self, ids: torch.Tensor, mult: float = 1.0) -> torch.Tensor:
+        """Embedding rows read from their owner's memory: [T] ids -> [T, H], no all-reduce."""
+        T = ids.shape[0]
+        out = torch.empty(T, self.embed_h, dtype=torch.bfloat16, device=ids.device)
+        rc = self.lib.lx_embed_peer(ids.data_ptr(), ctypes.cast(self.embed_ptrs, ctypes.c_void_p), out.data_ptr(), T, self.embed_h,
+                                    self.embed_rows, self.world, self.embed_vocab, mult, torch.cuda.current_stream().cuda_stream)
+        native._check(rc, "lx_embed_peer")
+        native.launch_count += 1
+        return out
+
     def all_reduce(self, x: torch.Tensor):
         return None      # plain all-reduces (embedding, large prefill activations) stay on NCCL
 
@@ -98,5 +126,7 @@ def enable(tp, model, max_rows: int = 512) -> FusedCollectives:
     if tp.world_size == 1:
         raise ValueError("fused collectives need a tensor-parallel group")
     fc = FusedCollectives(tp, n_max=model.hidden, max_rows=max_rows)
+    if model.embed is not None and model.embed.is_cuda and model.embed.dtype == torch.bfloat16 and model.pos_embed is None:
+        model.embed = fc.share_embedding(model.embed, model.vocab_local * tp.world_size)
     tp.fused = fc
     return fc
