@@ -121,6 +121,8 @@ class DecoderModel:
         self.cos_sin = reference.rope_cache(c.rotary_dim, self.max_positions, c.rope_theta, c.rope_scaling, device=self.device)
         self.adapters = None     # AdapterManager, attached by the runtime
         self.quantized: Optional[str] = None
+        self._native = None
+        self.use_native_layers = self.device.type == "cuda" and os.environ.get("LORAX_NATIVE_LAYERS", "1") != "0"
         # LoRA expand inside the GEMM epilogue instead of its own launch (slower than the separate kernel at present:
         # four epilogue warps cannot hide the latency of the per-token B rows)
         self.fused_lora_epilogue = os.environ.get("LORAX_FUSED_LORA_EPILOGUE", "0") == "1"
@@ -311,6 +313,7 @@ class DecoderModel:
                     q, s = reference.quantize_weight_fp8_block128(w)
                     setattr(lw, name, Fp8Weight(q.view(torch.uint8) if q.is_cuda else q, s))
         self.quantized = "fp8"
+        self._native = None
 
     def _gemm(self, x, w, b, lora=None):
         if isinstance(w, Fp8Weight):
@@ -349,6 +352,20 @@ class DecoderModel:
             out = self.tp.all_reduce(out)
         return out
 
+    def _native_executor(self, inp: StepInputs, kv_cache: List[torch.Tensor]):
+        """The C++ layer executor for eager steps (prefill, mixed prefill + decode) of the architectures it covers;
+        None keeps the per-kernel Python path (decode steps are CUDA graphs, where host time does not matter)."""
+        if not inp.is_prefill or not self.use_native_layers or torch.cuda.is_current_stream_capturing():
+            return None
+        from . import native_exec
+        ex = self._native
+        if ex is not None and ex.matches(self, kv_cache):
+            return ex
+        if not native_exec.supported(self):
+            return None
+        self._native = native_exec.NativeExecutor(self, kv_cache)
+        return self._native
+
     def forward(self, inp: StepInputs, kv_cache: List[torch.Tensor]) -> torch.Tensor:
         """-> logits [n_out, vocab] (full vocabulary on every rank)."""
         c, ops = self.config, self.ops
@@ -365,7 +382,10 @@ class DecoderModel:
         residual = h
         pending = None      # output of the previous block that still has to be added to the residual stream
         rm = c.residual_multiplier
-        for li, lw in enumerate(self.layers):
+        native_exec = self._native_executor(inp, kv_cache)
+        if native_exec is not None:
+            pending, residual = native_exec.run_layers(inp, h.contiguous())
+        for li, lw in enumerate(self.layers if native_exec is None else ()):
             if pending is None:
                 normed = self._norm(residual, None, lw.input_norm, lw.input_norm_b)
             else:

@@ -46,6 +46,36 @@ def test_prefill_logits_match_cpu_oracle():
     assert (outs[1][1] - outs[1][0]).norm() > 0
 
 
+def test_native_layer_executor_equals_python_path():
+    """The C++ layer executor issues the same kernels with the same arguments as the per-kernel Python path: prefill
+    logits and a mixed prefill + decode step must be bit-identical."""
+    cfg, gm, _ = _build("cuda", torch.bfloat16)
+    g = torch.Generator().manual_seed(11)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (17, 64, 90, 33)]
+    results = []
+    for native_on in (True, False):
+        gm.use_native_layers = native_on
+        kv = KVCache(cfg.num_hidden_layers, 64, gm.nkv, gm.d, gm.dtype, gm.device)
+        r = ModelRunner(gm, kv, max_batch=8, max_seq_tokens=256, max_prefill_tokens=512, use_graphs=False)
+        blocks = [[1 + 4 * i + j for j in range(4)] for i in range(4)]
+        items = [PrefillItem(p, 0, blocks[i], adapter_index=i) for i, p in enumerate(prompts[:2])]
+        ids, lps, logits = r.prefill(items)
+        rows = [r.state.take_row(i) for i in range(2)]
+        r.install(rows, ids, [len(p) for p in prompts[:2]], blocks[:2], [0, 1])
+        r.resort()
+        # prompts 2 and 3 ride along with the two decode rows
+        k, nd, first_ids, first_lps = r.mixed_step([PrefillItem(p, 0, blocks[2 + i], adapter_index=2 + i) for i, p in enumerate(prompts[2:])])
+        dec_ids, dec_lps = r.wait(k)
+        torch.cuda.synchronize()
+        results.append((logits.clone(), dec_ids[:nd].clone(), dec_lps[:nd].clone(), first_ids.clone(), first_lps.clone()))
+        assert (gm._native is not None) == native_on or not native_on
+    from lorax_b200.ops import native
+    native.workspace().check_status()
+    for a, b in zip(*results):
+        assert torch.equal(a, b)
+    gm.use_native_layers = True
+
+
 def test_fp8_model_prefill_matches_cpu_oracle():
     """`quantize_fp8()` on both devices: the tcgen05 fp8 GEMM path against the PyTorch oracle of the same quantised
     model (same e4m3 weights and scales, activations rounded the same way), adapters included."""
