@@ -163,6 +163,8 @@ struct DecodeParams {
 
 template <int D, int STAGES>
 __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams p) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   extern __shared__ __align__(1024) uint8_t dsm[];
   constexpr int PLANE = kPage * D * 2;
   constexpr int STAGE = 2 * PLANE;
@@ -290,6 +292,8 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
 template <int D>
 __global__ void __launch_bounds__(D) attn_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_lse,
                                                          __nv_bfloat16* __restrict__ out, long long ldo, int nh, int nsplit) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
   const long long base = ((long long)t * nh + h) * nsplit;
   float M = -INFINITY;
@@ -326,6 +330,8 @@ struct PrefillParams {
 
 template <int D>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillParams p) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   extern __shared__ __align__(1024) uint8_t psm[];
   constexpr int KT = 64;                         // keys per tile
   constexpr int PLANE = kPage * D * 2;           // one page of K or V
@@ -433,10 +439,10 @@ static int launch_decode(const DecodeParams& p, int T, cudaStream_t s) {
     configured = true;
   }
   dim3 grid(T, p.nkv * p.gchunks, p.nsplit);
-  attn_decode_kernel<D, STAGES><<<grid, 128, SMEM, s>>>(p);
+  launch_pdl(attn_decode_kernel<D, STAGES>, grid, dim3(128), (size_t)SMEM, s, p);
   if (p.nsplit > 1) {
     dim3 g2(T, p.nh);
-    attn_combine_kernel<D><<<g2, D, 0, s>>>(p.part_o, p.part_lse, p.out, p.ldo, p.nh, p.nsplit);
+    launch_pdl(attn_combine_kernel<D>, g2, dim3(D), 0, s, p.part_o, p.part_lse, p.out, p.ldo, p.nh, p.nsplit);
   }
   return -(int)cudaGetLastError();
 }
@@ -451,7 +457,7 @@ static int launch_prefill(const PrefillParams& p, int num_tiles, cudaStream_t s)
     configured = true;
   }
   dim3 grid(num_tiles, p.nh);
-  attn_prefill_kernel<D><<<grid, 128, SMEM, s>>>(p);
+  launch_pdl(attn_prefill_kernel<D>, grid, dim3(128), (size_t)SMEM, s, p);
   return -(int)cudaGetLastError();
 }
 

@@ -11,6 +11,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define LX_DEVICE __device__ __forceinline__
 
@@ -98,6 +99,20 @@ LX_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_fla
     }
   }
 }
+
+// ------------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with `launch_pdl` may start while its predecessor on the stream
+// is still running: it must call pdl_wait() before it touches global memory (the wait returns when the predecessor
+// has completed and its writes are visible), and EVERY thread block must reach pdl_wait() before it exits, also on
+// early-return paths -- a grid that completes without waiting would let ITS successor run ahead of the kernels before
+// it.  pdl_trigger() lets the successor's blocks be scheduled as soon as all of this grid's blocks have started.
+// ------------------------------------------------------------------------------------------------
+LX_DEVICE void pdl_trigger() {
+#ifdef LX_PDL_EARLY_TRIGGER
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#endif
+}
+LX_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // ------------------------------------------------------------------------------------------------
 // Async proxy fences + TMA
@@ -305,5 +320,31 @@ LX_DEVICE void cp_async_16(void* smem_dst, const void* gsrc, bool valid) {
 LX_DEVICE void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 LX_DEVICE void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// Host side: launch with the programmatic-serialization attribute (LORAX_PDL=0 turns it off; the device-side calls
+// are then no-ops).  Works under stream capture: the graph gets programmatic dependency edges.
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("LORAX_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 }  // namespace lx

@@ -23,6 +23,8 @@ norm_residual_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restr
                      const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
                      __nv_bfloat16* __restrict__ out, int H, long long ldx, long long ldr, long long ldo, float eps,
                      float w_offset, float x_scale) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   const int row = blockIdx.x;
   const int nvec = H / 8;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * ldx);
@@ -133,6 +135,8 @@ __global__ void __launch_bounds__(256)
 rope_kvwrite_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ cos_sin,
                     __nv_bfloat16* __restrict__ kv_cache, const int* __restrict__ slots, int nh, int nkv, int d, int rot,
                     int page, long long ldq, int apply_rope, float k_scale_unused) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int slot = slots ? slots[t] : -1;
@@ -210,6 +214,8 @@ LX_DEVICE float act_fn(float x) {
 template <int ACT, bool GATED>
 __global__ void __launch_bounds__(256)
 act_mul_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, int I, long long ldi, long long ldo, long long total_vec) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   const int vec_per_row = I / 8;
   for (long long v = blockIdx.x * (long long)blockDim.x + threadIdx.x; v < total_vec; v += (long long)gridDim.x * blockDim.x) {
     const long long t = v / vec_per_row;
@@ -243,6 +249,8 @@ struct EmbedPeerParams {
 };
 
 __global__ void __launch_bounds__(128) embed_peer_kernel(const int* __restrict__ ids, const EmbedPeerParams p, __nv_bfloat16* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   const int t = blockIdx.x;
   const int id = ids[t];
   uint4* o = reinterpret_cast<uint4*>(out + (long long)t * p.H);
@@ -271,6 +279,8 @@ __global__ void __launch_bounds__(128) embed_peer_kernel(const int* __restrict__
 __global__ void __launch_bounds__(128)
 embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table, __nv_bfloat16* __restrict__ out, int H,
              int v0, int v1, float mult) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   const int t = blockIdx.x;
   const int id = ids[t];
   uint4* o = reinterpret_cast<uint4*>(out + (long long)t * H);
@@ -301,6 +311,8 @@ embed_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ tabl
 __global__ void __launch_bounds__(512)
 argmax_logprob_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int V, int* __restrict__ ids,
                       float* __restrict__ logprobs, float softcap) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   const int t = blockIdx.x;
   const __nv_bfloat16* row = logits + t * ld;
   float best = -INFINITY;
@@ -348,6 +360,8 @@ argmax_logprob_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, in
 __global__ void advance_decode_kernel(int* __restrict__ input_ids, const int* __restrict__ next_ids, int* __restrict__ positions,
                                       int* __restrict__ ctx_lens, int* __restrict__ slots, const int* __restrict__ block_tables,
                                       int max_blocks, int page, int B) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= B) return;
   if (ctx_lens[b] <= 0) { slots[b] = -1; return; }
@@ -374,8 +388,8 @@ int lx_norm_residual(const void* x, void* residual, const void* w, const void* b
   auto W = reinterpret_cast<const __nv_bfloat16*>(w);
   auto Bv = reinterpret_cast<const __nv_bfloat16*>(b);
   auto O = reinterpret_cast<__nv_bfloat16*>(out);
-  if (layernorm) norm_residual_kernel<true><<<T, kNormThreads, 0, s>>>(X, R, W, Bv, O, H, ldx, ldr, ldo, eps, w_offset, x_scale);
-  else norm_residual_kernel<false><<<T, kNormThreads, 0, s>>>(X, R, W, Bv, O, H, ldx, ldr, ldo, eps, w_offset, x_scale);
+  if (layernorm) launch_pdl(norm_residual_kernel<true>, dim3(T), dim3(kNormThreads), 0, s, X, R, W, Bv, O, H, ldx, ldr, ldo, eps, w_offset, x_scale);
+  else launch_pdl(norm_residual_kernel<false>, dim3(T), dim3(kNormThreads), 0, s, X, R, W, Bv, O, H, ldx, ldr, ldo, eps, w_offset, x_scale);
   return -(int)cudaGetLastError();
 }
 
@@ -384,7 +398,7 @@ int lx_rope_kvwrite(void* qkv, const int* positions, const float* cos_sin, void*
   using namespace lx;
   if (T <= 0) return 0;
   if (d % 8 != 0 || rot % 8 != 0 || rot > d) return -1;
-  rope_kvwrite_kernel<<<T, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+  launch_pdl(rope_kvwrite_kernel, dim3(T), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<__nv_bfloat16*>(qkv), positions, cos_sin, reinterpret_cast<__nv_bfloat16*>(kv_cache), slots, nh, nkv, d,
       rot, page, ldq, apply_rope, 1.f);
   return -(int)cudaGetLastError();
@@ -400,8 +414,8 @@ int lx_act_mul(const void* in, void* out, int T, int I, long long ldi, long long
   auto X = reinterpret_cast<const __nv_bfloat16*>(in);
   auto O = reinterpret_cast<__nv_bfloat16*>(out);
 #define LX_ACT(A)                                                                         \
-  if (gated) act_mul_kernel<A, true><<<grid, 256, 0, s>>>(X, O, I, ldi, ldo, total);      \
-  else act_mul_kernel<A, false><<<grid, 256, 0, s>>>(X, O, I, ldi, ldo, total);
+  if (gated) launch_pdl(act_mul_kernel<A, true>, dim3(grid), dim3(256), 0, s, X, O, I, ldi, ldo, total);      \
+  else launch_pdl(act_mul_kernel<A, false>, dim3(grid), dim3(256), 0, s, X, O, I, ldi, ldo, total);
   switch (act) {
     case kSilu: LX_ACT(kSilu); break;
     case kGelu: LX_ACT(kGelu); break;
@@ -416,7 +430,7 @@ int lx_embed(const int* ids, const void* table, void* out, int T, int H, int v0,
   using namespace lx;
   if (T <= 0) return 0;
   if (H % 8 != 0) return -1;
-  embed_kernel<<<T, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ids, reinterpret_cast<const __nv_bfloat16*>(table),
+  launch_pdl(embed_kernel, dim3(T), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), ids, reinterpret_cast<const __nv_bfloat16*>(table),
                                                                       reinterpret_cast<__nv_bfloat16*>(out), H, v0, v1, mult);
   return -(int)cudaGetLastError();
 }
@@ -434,14 +448,14 @@ int lx_embed_peer(const int* ids, const void* peer_tables, void* out, int T, int
   const unsigned long long* tabs = reinterpret_cast<const unsigned long long*>(peer_tables);
   for (int r = 0; r < world; ++r) p.tables[r] = reinterpret_cast<const __nv_bfloat16*>(tabs[r]);
   p.rows_per_rank = rows_per_rank; p.world = world; p.vocab = vocab; p.H = H; p.mult = mult;
-  embed_peer_kernel<<<T, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ids, p, reinterpret_cast<__nv_bfloat16*>(out));
+  launch_pdl(embed_peer_kernel, dim3(T), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), ids, p, reinterpret_cast<__nv_bfloat16*>(out));
   return -(int)cudaGetLastError();
 }
 
 int lx_argmax_logprob(const void* logits, long long ld, int T, int V, int* ids, float* logprobs, float softcap, void* stream) {
   using namespace lx;
   if (T <= 0) return 0;
-  argmax_logprob_kernel<<<T, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(logits), ld, V,
+  launch_pdl(argmax_logprob_kernel, dim3(T), dim3(512), 0, reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const __nv_bfloat16*>(logits), ld, V,
                                                                              ids, logprobs, softcap);
   return -(int)cudaGetLastError();
 }
@@ -450,7 +464,7 @@ int lx_advance_decode(int* input_ids, const int* next_ids, int* positions, int* 
                       int max_blocks, int page, int B, void* stream) {
   using namespace lx;
   if (B <= 0) return 0;
-  advance_decode_kernel<<<(B + 127) / 128, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(input_ids, next_ids, positions, ctx_lens,
+  launch_pdl(advance_decode_kernel, dim3((B + 127) / 128), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), input_ids, next_ids, positions, ctx_lens,
                                                                                           slots, block_tables, max_blocks, page, B);
   return -(int)cudaGetLastError();
 }

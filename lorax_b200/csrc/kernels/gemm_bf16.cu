@@ -269,6 +269,7 @@ template <int BN, int STAGES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                          const GemmParams p) {
+  pdl_trigger();
   using S = GemmSmem<BN, STAGES>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -314,6 +315,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
+  pdl_wait();      // barriers, TMEM and descriptors are set up while the previous kernel drains; its data is read from here on
 
   // Work item w -> (tile, split).  Tiles are ordered with the A tile index fastest inside one B tile so that
   // CTAs running at the same time share the B operand through L2.
@@ -623,7 +625,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     if (e != cudaSuccess) return -(int)e;
     configured = true;
   }
-  gemm_bf16_tcgen05_kernel<BN, STAGES><<<grid, kGemmThreads, S::kTotal, stream>>>(ta, tb, p);
+  launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES>, dim3(grid), dim3(kGemmThreads), (size_t)S::kTotal, stream, ta, tb, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }

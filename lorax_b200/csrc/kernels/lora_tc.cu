@@ -62,6 +62,8 @@ struct LtSmem {
 template <int BN>
 __global__ void __launch_bounds__(kLtThreads)
 lora_shrink_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const ShrinkTcParams p) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   using S = LtSmem<BN>;
   LoraTile tile = p.tiles[blockIdx.x];
   tile.nrows = min(tile.nrows, p.T - tile.row0);       // a table may be older than the batch: rows past T are gone
@@ -254,6 +256,8 @@ constexpr int kExpRowsInFlight = 4;                  // rows whose y loads are i
 // The grid is a fixed number of CTAs that walk the units; live tiles come first in the table, so the walk stops at
 // the first dead one and padding entries cost nothing.
 __global__ void __launch_bounds__(kExpThreads, 2) lora_expand_tiled_kernel(const ExpandTiledParams p) {
+  pdl_trigger();
+  pdl_wait();      // every block waits, also those that return early below
   __shared__ __align__(16) float vs[kExpMaxRows * 3 * kExpStage];   // [row][part][16]
   const int nparts = p.n1 < p.N ? 3 : (p.n0 < p.N ? 2 : 1);
   for (int w = blockIdx.x; w < p.num_tiles * p.col_blocks; w += gridDim.x) {
@@ -364,7 +368,7 @@ static int launch_shrink_tc(const CUtensorMap& tx, const ShrinkTcParams& p, int 
     configured = true;
   }
   dim3 grid(num_tiles, chunks, p.ksplit);
-  lora_shrink_tc_kernel<BN><<<grid, kLtThreads, S::kTotal, s>>>(tx, p);
+  launch_pdl(lora_shrink_tc_kernel<BN>, grid, dim3(kLtThreads), (size_t)S::kTotal, s, tx, p);
   return -(int)cudaGetLastError();
 }
 
@@ -448,7 +452,7 @@ int lx_lora_expand_tiled(const float* v, int ldv, long long v_split_stride, int 
   p.col_blocks = (N + kExpBlockCols - 1) / kExpBlockCols;
   const long long work = (long long)num_tiles * p.col_blocks;
   const int grid = (int)(work < 148 * 2 ? work : 148 * 2);
-  lora_expand_tiled_kernel<<<grid, kExpThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  launch_pdl(lora_expand_tiled_kernel, dim3(grid), dim3(kExpThreads), 0, reinterpret_cast<cudaStream_t>(stream), p);
   return -(int)cudaGetLastError();
 }
 
