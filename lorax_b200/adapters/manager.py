@@ -38,6 +38,7 @@ class LoraTiles:
     table: torch.Tensor
     num_tiles: int
     max_rows: int
+    live: int = 0               # live entries when the table is padded with dead ones to a fixed size (0: all of them)
 
 
 class ArenaAllocator:
@@ -307,7 +308,8 @@ class AdapterManager:
                 return None
             if self.is_cuda:
                 v = ops.lora_shrink_tiles(x, tiles.table, tiles.num_tiles, tiles.max_rows, self.slot_tmaps, self.groups_per_slot,
-                                          TMAP_GROUPS.index(group), self.slot_rank, nparts, 0 if group == LM_HEAD else layer, self.max_rank)
+                                          TMAP_GROUPS.index(group), self.slot_rank, nparts, 0 if group == LM_HEAD else layer, self.max_rank,
+                                          live_tiles=tiles.live)
             else:
                 v = ops.lora_shrink_tiles(x, tiles.table, tiles.num_tiles, tiles.max_rows, self.arena, self.slot_base, self.slot_rank,
                                           offA, nparts, self.max_rank)

@@ -113,8 +113,8 @@ int linear_with_lora(const LxModelDesc& m, const LxLayerDesc& l, const LxStepDes
     if (s.lora_tiles != nullptr) {
       const int kblocks = (K + 63) / 64;
       const int chunks = (site.nparts * m.max_rank + 127) / 128;
-      int want = (8 * m.num_sms + s.num_tiles * chunks - 1) / (s.num_tiles * chunks);
-      int ksplit = kblocks / 16 < want ? kblocks / 16 : want;
+      int ksplit = (2 * m.num_sms) / (s.num_tiles * chunks);       // one wave of CTAs (two per SM), see ops/native.py
+      if (ksplit > kblocks / 8) ksplit = kblocks / 8;
       if (ksplit > m.v3_planes) ksplit = m.v3_planes;
       if (ksplit < 1) ksplit = 1;
       LX_TRY(lx_lora_shrink_tc(x, ldx, s.lora_tiles, s.num_tiles, s.max_tile_rows, m.slot_tmaps, m.groups_per_slot, site.tmap_group,

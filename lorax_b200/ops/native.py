@@ -352,7 +352,7 @@ def lora_encode_tmap(out_host: torch.Tensor, base_ptr: int, K: int, R: int, laye
 
 def lora_shrink_tiles(x: torch.Tensor, tiles: torch.Tensor, num_tiles: int, max_tile_rows: int, slot_tmaps: torch.Tensor,
                       groups_per_slot: int, group: int, slot_rank: torch.Tensor, nparts: int, layer: int, max_rank: int,
-                      v: Optional[torch.Tensor] = None):
+                      v: Optional[torch.Tensor] = None, ksplit: Optional[int] = None, live_tiles: int = 0):
     """Tensor-core shrink over a tile table -> v [rows, cols] fp32.  K is split over CTAs when the table alone
     cannot fill the GPU; the last split CTA of a tile adds the partial sums in a fixed order."""
     T, K = x.shape
@@ -362,10 +362,12 @@ def lora_shrink_tiles(x: torch.Tensor, tiles: torch.Tensor, num_tiles: int, max_
     assert vf.stride(0) == v3.stride(1)
     kblocks = (K + 63) // 64
     chunks = (nparts * max_rank + 127) // 128
-    # K split: these skinny tiles are latency bound, so aim for about 16 k-blocks per CTA and enough CTAs to cover the
-    # GPU several times over (in decode most table entries are padding and their CTAs exit at once)
-    want = -(-8 * ws.num_sms // max(1, num_tiles * chunks))
-    ksplit = max(1, min(v3.shape[0], kblocks // 16, want))
+    # K split: these skinny tiles are latency bound, so K is cut over as many CTAs as the GPU holds at once (two per SM)
+    # and no more: a second, partly filled wave doubles the time.  `live_tiles` is the number of entries that are not
+    # padding (CTAs of dead entries exit at once).
+    if ksplit is None:
+        ksplit = max(1, (2 * ws.num_sms) // max(1, (live_tiles or num_tiles) * chunks))
+    ksplit = max(1, min(v3.shape[0], kblocks // 8 if kblocks >= 8 else 1, ksplit))
     rc = load().lx_lora_shrink_tc(_ptr(x), x.stride(0), _ptr(tiles), num_tiles, max_tile_rows, _ptr(slot_tmaps), groups_per_slot, group,
                                   _ptr(slot_rank), slot_rank.shape[0], nparts, layer, _ptr(v3), v3.stride(1), v3.stride(0), ksplit,
                                   _ptr(vf), _ptr(ws.lora_counters), ws.lora_counters.numel(), T, K, max_rank, _ptr(ws.status), _stream())

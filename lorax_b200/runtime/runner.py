@@ -345,7 +345,7 @@ class ModelRunner:
         if self.is_cuda and b * self.model.nkv < 96:
             nsplit = max(1, min(8, 192 // max(b * self.model.nkv, 1)))
         # the table always has max_batch rows; a graph launches one CTA per possible tile of the bucket (unused: slot -1)
-        tiles = LoraTiles(st.lora_tiles, b, 32) if (lora and self.tiles_valid) else None
+        tiles = LoraTiles(st.lora_tiles, b, 32, live=st.num_lora_tiles) if (lora and self.tiles_valid) else None
         fused = self.model.tp.fused if self.model.tp.world_size > 1 else None
         fused_head = (fused is not None and not need_logits and b <= fused.max_rows
                       and not (self.model.config.final_logit_softcapping or 0.0))
@@ -365,8 +365,14 @@ class ModelRunner:
         self.model.ops.advance_decode(st.input_ids[:b], st.next_ids[:b], st.positions[:b], st.ctx_lens[:b], st.slots[:b],
                                       st.block_tables[:b], self.page)
 
+    def _ks_class(self, lora: bool) -> int:
+        """The LoRA shrink's K split is baked into a captured graph; it depends on how many tiles are live."""
+        if not (lora and self.tiles_valid):
+            return 0
+        return min(8, (2 * 148) // max(1, self.state.num_lora_tiles))
+
     def capture(self, b: int, lora: bool, need_logits: bool = False):
-        key = (b, lora, self.tiles_valid, need_logits)
+        key = (b, lora, self.tiles_valid, need_logits, self._ks_class(lora))
         if key in self.graphs:
             return
         # warm up outside capture (lazy cudaFuncSetAttribute calls, workspace allocation)
@@ -404,7 +410,7 @@ class ModelRunner:
         logits = None
         if self.use_graphs:
             variant = need_logits and self.model.tp.world_size > 1      # only TP has two head variants
-            key = (b, lora, self.tiles_valid, variant)
+            key = (b, lora, self.tiles_valid, variant, self._ks_class(lora))
             self.capture(b, lora, variant)
             self.graphs[key].replay()
             self.replayed_launches += self.graph_kernels[key]
