@@ -318,6 +318,23 @@ class ModelRunner:
         self.tiles_valid = True
         return mapping
 
+    def reposition(self, rows: Sequence[int], tokens: Sequence[int], positions: Sequence[int], blocks: Sequence[Sequence[int]]):
+        """Point decode rows at new (input token, position) pairs without touching their order, adapters or block tables:
+        used after a speculative step accepted several tokens of a row at once."""
+        if not rows:
+            return
+        page = self.page
+        tabs = [self._table_row(b) for b in blocks]
+        slots = [tabs[i][positions[i] // page] * page + positions[i] % page for i in range(len(rows))]
+        n = len(rows)
+        dev = self._to_dev(list(rows) + list(tokens) + list(positions) + [p + 1 for p in positions] + slots)
+        r = dev[:n].long()
+        st = self.state
+        st.input_ids.index_copy_(0, r, dev[n:2 * n])
+        st.positions.index_copy_(0, r, dev[2 * n:3 * n])
+        st.ctx_lens.index_copy_(0, r, dev[3 * n:4 * n])
+        st.slots.index_copy_(0, r, dev[4 * n:5 * n])
+
     def retire(self, rows: Sequence[int]):
         """Mark rows as padding: they stop advancing and attention skips them."""
         if not rows:

@@ -27,7 +27,7 @@ from ..models.decoder import DecoderModel
 from ..parallel.tp import TensorParallel
 from ..runtime.kv_cache import KVCache
 from ..runtime.runner import ModelRunner, PrefillItem
-from ..sampling.chooser import (FINISH_EOS, FINISH_LENGTH, FINISH_STOP, HeterogeneousNextTokenChooser, NextTokenParams,
+from ..sampling.chooser import (FINISH_EOS, FINISH_LENGTH, FINISH_STOP, HeterogeneousNextTokenChooser, NextTokenParams, ngram_speculate,
                                 StoppingCriteria)
 from ..sampling.grammar import compile_schema
 from ..utils.sources import resolve_adapter, resolve_model
@@ -113,6 +113,7 @@ class ShardRuntime:
         self.special_ids = set(self.eos_ids)
         self.downloaded: Dict[str, Tuple[LoraConfig, object]] = {}
         self.lock = threading.Lock()
+        self.spec_stats = {"steps": 0, "tokens": 0}          # speculative decoding: row-steps and tokens they produced
 
     # ------------------------------------------------------------------ info / health
     def info(self):
@@ -270,6 +271,61 @@ class ShardRuntime:
                 gen.generated_text.CopyFrom(gt)
         return gen, stop
 
+    def _emit_many(self, s: SeqState, tokens: Sequence[int], logprobs: Sequence[float]):
+        """Append the tokens a speculative step accepted (stopping at the first that ends the request) as ONE Generation
+        whose NextTokens lists them in order.  Returns (Generation or None, finished, number of tokens kept)."""
+        pb = self.pb
+        mine = (s.request_id % self.tp.world_size) == self.tp.rank
+        ids, lps, texts, special = [], [], [], []
+        stop, reason = False, None
+        for tok, lp in zip(tokens, logprobs):
+            s.output_ids.append(tok)
+            text = s.detok.push(tok)
+            s.output_text += text
+            ids.append(tok); lps.append(lp); texts.append(text); special.append(tok in self.special_ids)
+            stop, reason = s.stopping(tok, text)
+            if stop:
+                break
+        gen = None
+        if mine:
+            gen = pb.Generation(request_id=s.request_id, next_tokens=pb.NextTokens(ids=ids, logprobs=lps, texts=texts, is_special=special),
+                                prefill_tokens_length=len(s.prompt_ids))
+            if stop:
+                gen.generated_text.CopyFrom(pb.GeneratedText(text=s.output_text, generated_tokens=len(s.output_ids), skipped_tokens=0,
+                                                             finish_reason=reason))
+        return gen, stop, len(ids)
+
+    def _decode_speculative(self, seqs: List[SeqState], n_spec: int):
+        """Greedy decoding with prompt-lookup proposals (reference: `utils/tokens.py:594-615` proposes, `:363-460` verifies).
+        Every row is run as a short ragged prefill over [last token, proposals...] against its cached context; the model's
+        arg-max at each position is compared with the proposal that follows, and the longest agreeing prefix plus one
+        token is emitted.  Rejected positions leave stale K/V behind the new context length, where nothing reads them
+        before they are overwritten."""
+        page = self.kv.page
+        items, props = [], []
+        for s in seqs:
+            h = s.prompt_ids + s.output_ids
+            room = len(s.blocks) * page - len(h) - 1                 # slots left after the token that must be written anyway
+            want = max(0, min(n_spec, room, s.stopping.max_new_tokens - len(s.output_ids) - 1))
+            hist = torch.tensor([h], dtype=torch.long)
+            cand = ngram_speculate(hist, [len(h)], [h[-1]], want)[0].tolist() if want > 0 else []
+            props.append(cand)
+            items.append(PrefillItem([h[-1]] + cand, len(h) - 1, list(s.blocks), s.adapter_index, all_logprobs=True))
+        next_ids, lps, _ = self.runner.prefill(items)
+        ids_h, lps_h = next_ids.tolist(), lps.tolist()
+        out, o = [], 0
+        for s, cand in zip(seqs, props):
+            n = 1 + len(cand)
+            toks, tlps = [int(ids_h[o])], [float(lps_h[o])]
+            for j, c in enumerate(cand):
+                if c != toks[-1]:
+                    break
+                toks.append(int(ids_h[o + j + 1]))
+                tlps.append(float(lps_h[o + j + 1]))
+            out.append((toks, tlps))
+            o += n
+        return out
+
     def _tok_text(self, tid: int) -> str:
         return self.tokenizer.decode([tid], skip_special_tokens=False) if self.tokenizer is not None else ""
 
@@ -374,6 +430,8 @@ class ShardRuntime:
             raise RuntimeError("all batches of the Decode request are missing from the cache")
         seqs = [self.seqs[r] for r in rids]
         need_logits = any(not (s.params.plain and s.grammar is None) for s in seqs)
+        if self.cfg.speculative_tokens > 0 and not need_logits:
+            return self._decode_spec_step(bids, rids, seqs)
         k, b, logits = self.runner.decode(need_logits=need_logits)
         ids_p, lps_p = self.runner.wait(k)
         rows = [s.row for s in seqs]
@@ -396,6 +454,36 @@ class ShardRuntime:
                 gens.append(gen)
             if stop:
                 finished.append(s.request_id)
+        new_id = bids[0]
+        merged = [r for r in rids if r not in finished]
+        for bid in bids:
+            self.batches.pop(bid, None)
+        for rid in finished:
+            self._drop(rid)
+        resp = pb.DecodeResponse(generations=gens)
+        if merged:
+            self.batches[new_id] = merged
+            for r in merged:
+                self.seqs[r].batch_id = new_id
+            resp.batch.CopyFrom(self._cached(new_id))
+        return resp
+
+    def _decode_spec_step(self, bids, rids, seqs):
+        pb = self.pb
+        accepted = self._decode_speculative(seqs, self.cfg.speculative_tokens)
+        gens, finished, rows, toks, poss, blks = [], [], [], [], [], []
+        for s, (tk, lp) in zip(seqs, accepted):
+            gen, stop, kept = self._emit_many(s, tk, lp)
+            self.spec_stats["steps"] += 1
+            self.spec_stats["tokens"] += kept
+            if gen is not None:
+                gens.append(gen)
+            if stop:
+                finished.append(s.request_id)
+            else:
+                rows.append(s.row); toks.append(s.output_ids[-1]); poss.append(len(s.prompt_ids) + len(s.output_ids) - 1); blks.append(s.blocks)
+        # the device-resident decode state follows, so that plain decode steps (sampling rows joining later) stay possible
+        self.runner.reposition(rows, toks, poss, blks)
         new_id = bids[0]
         merged = [r for r in rids if r not in finished]
         for bid in bids:
