@@ -156,3 +156,27 @@ def test_engine_generate_runs_with_graphs():
 def test_smoke_entry():
     import __graft_entry__ as ge
     ge.smoke()
+
+
+def test_mixtral_moe_gpu_matches_cpu_oracle():
+    """Top-2 mixture of experts on the GPU kernels (dense form for decode-sized batches, gathered form for long prompts)
+    against the fp32 CPU oracle of the same random model."""
+    from lorax_b200.config import ModelConfig
+    cfg = ModelConfig(model_type="mixtral", vocab_size=512, hidden_size=256, intermediate_size=384, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, head_dim=64, rope_theta=1e4, max_position_embeddings=1024,
+                      num_local_experts=4, num_experts_per_tok=2, torch_dtype="bfloat16")
+    gm = DecoderModel.random_init(cfg, "cuda", torch.bfloat16, seed=2, std=0.05)
+    cm = DecoderModel.random_init(cfg, "cpu", torch.float32, seed=2, std=0.05)
+    g = torch.Generator().manual_seed(9)
+    for n in (40, 300):                       # below / above the dense-form limit of 256 tokens
+        prompt = torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist()
+        outs = []
+        for m in (gm, cm):
+            kv = KVCache(cfg.num_hidden_layers, 32, m.nkv, m.d, m.dtype, m.device)
+            r = ModelRunner(m, kv, max_batch=2, max_seq_tokens=512, max_prefill_tokens=512, use_graphs=False)
+            _, _, logits = r.prefill([PrefillItem(prompt, 0, list(range(1, 12)), adapter_index=0)])
+            outs.append(logits.float().cpu())
+        err = ((outs[0] - outs[1]).norm() / outs[1].norm()).item()
+        assert err < 4e-2, (n, err)
+    from lorax_b200.ops import native
+    native.workspace().check_status()
