@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for `ncu` captures of single kernels.
 
-    python -m lorax_b200.ops.profile_case --case gemm_decode|gemm_prefill|gemm_lora_decode|gemm_lora_decode_gateup|gemm_lora_prefill|attn_decode|attn_prefill|lora_shrink|lora_expand
+    python -m lorax_b200.ops.profile_case --case gemm_decode|gemm_mid|gemm_prefill|gemm_fp8_decode|gemm_fp8_prefill|gemm_lora_decode|gemm_lora_decode_gateup|gemm_lora_prefill|attn_decode|attn_prefill|lora_shrink|lora_expand
 
 Each case launches the kernel a handful of times on inputs larger than the 126 MB L2 but at most a few GB, and
 exits 0; run it plain first, then under
@@ -96,6 +96,20 @@ def gemm_lora_case(T, parts=(4096, 1024, 1024)):
         native.gemm(x, ws[i], out=out, lora=epi)
 
 
+def gemm_fp8_case(T):
+    """Block-scaled fp8 GEMM, gate_up shape, weights rotating over > L2."""
+    N, K = 28672, 4096
+    ws = []
+    for _ in range(3):
+        w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / 64
+        ws.append(reference.quantize_weight_fp8_block128(w))
+        del w
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    for i in range(4):
+        native.gemm_fp8(x, ws[i % 3][0].view(torch.uint8), ws[i % 3][1], out=out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", required=True)
@@ -103,6 +117,7 @@ def main():
     native.load()
     {"gemm_decode": lambda: gemm_case(64), "gemm_prefill": lambda: gemm_case(4096), "attn_decode": attn_decode_case,
      "attn_prefill": attn_prefill_case, "gemm_lora_decode": lambda: gemm_lora_case(256), "gemm_lora_decode_gateup": lambda: gemm_lora_case(256, (14336, 14336)), "gemm_lora_prefill": lambda: gemm_lora_case(576),
+     "gemm_fp8_decode": lambda: gemm_fp8_case(64), "gemm_fp8_prefill": lambda: gemm_fp8_case(2048), "gemm_mid": lambda: gemm_case(256),
      "lora_shrink": lambda: lora_case("shrink"), "lora_expand": lambda: lora_case("expand")}[a.case]()
     torch.cuda.synchronize()
     native.workspace().check_status()
