@@ -130,11 +130,14 @@ def main():
     ap.add_argument("--batch", type=int, default=256, help="requests kept in flight")
     ap.add_argument("--adapters", type=int, default=100)
     ap.add_argument("--rank", type=int, default=16)
+    ap.add_argument("--resident", type=int, default=None,
+                    help="adapters that fit the HBM arena (default: all). Fewer makes the engine exchange adapters with the pinned host tier")
     ap.add_argument("--min-prompt", type=int, default=128)
     ap.add_argument("--max-prompt", type=int, default=1024)
     ap.add_argument("--new-tokens", type=int, default=256)
     ap.add_argument("--layers", type=int, default=None, help="debug only: the reported config names the change")
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--waiting-served-ratio", type=float, default=None, help="scheduler knob (default: the engine's)")
     ap.add_argument("--baseline-mode", action="store_true", help="NCCL collectives instead of the fused NVLink kernels")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -182,7 +185,8 @@ def main():
     layout_units = BlobLayout(model, with_lm_head=False).units
     rp = pad_rank(args.rank)
     blob_elems = rp * layout_units
-    arena_bytes = int(blob_elems * esize * (args.adapters + 2) * 1.02) + (64 << 20)
+    resident = args.adapters if args.resident is None else max(1, min(args.resident, args.adapters))
+    arena_bytes = int(blob_elems * esize * (resident + 2) * 1.02) + (64 << 20)
     mgr = AdapterManager(model, arena_bytes=arena_bytes, host_bytes=int(blob_elems * esize * (args.adapters + 4)))
     g_dev = torch.Generator(device=dev).manual_seed(1234 + tp.rank)
     scale = 2.0 * 16 / args.rank        # alpha / r folded into B (alpha = 32)
@@ -195,14 +199,18 @@ def main():
         mgr.register_blob(f"adapter-{a}", host, rp)
         del blob
     torch.cuda.synchronize(dev)
-    for a in range(args.adapters):
+    for a in range(resident):
         assert mgr.load(a + 1, f"adapter-{a}"), "adapter arena too small"
     mgr.fence()
     torch.cuda.synchronize(dev)
 
     ecfg = EngineConfig(max_total_tokens=max_total, max_batch_prefill_tokens=4096, max_input_length=args.max_prompt,
                         compile=not args.no_graphs)
+    if args.waiting_served_ratio is not None:
+        ecfg.waiting_served_ratio = args.waiting_served_ratio
     eng = Engine(model, ecfg, max_batch=args.batch)
+    for a in range(args.adapters):
+        eng.register_adapter(a + 1, f"adapter-{a}")
 
     gen = torch.Generator().manual_seed(42)          # identical on every rank: ranks schedule in lockstep
     draw_adapter = zipf_sampler(args.adapters, 1.1, gen) if args.adapters > 0 else (lambda: -1)
@@ -269,7 +277,8 @@ def main():
                     launches=runner.kernel_launches() - l0, clocks=clocks,
                     prefill_tokens=eng.stats["prefill_tokens"] - p0["prefill_tokens"],
                     prefill_steps=eng.stats["prefill_steps"] - p0["prefill_steps"],
-                    decode_steps=eng.stats["decode_steps"] - p0["decode_steps"])
+                    decode_steps=eng.stats["decode_steps"] - p0["decode_steps"],
+                    adapter_loads=eng.stats.get("adapter_loads", 0) - p0.get("adapter_loads", 0))
 
     w1 = window(args.steps, device_timed=True)
     w2 = window(args.steps, device_timed=False)
@@ -287,7 +296,8 @@ def main():
         "config": {
             "model": args.model + (f"-{args.layers}layers-DEBUG" if args.layers else ""), "global_batch": args.batch,
             "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {args.new_tokens} new",
-            "parallelism": f"tp{tp.world_size}", "adapters": args.adapters, "lora_rank": args.rank,
+            "parallelism": f"tp{tp.world_size}", "adapters": args.adapters, "resident_adapters": resident,
+            "adapter_loads_in_window": w1["adapter_loads"], "lora_rank": args.rank,
             "lora_targets": "q,k,v,o,gate,up,down", "adapter_choice": "zipf(1.1)", "arrivals": "closed loop (saturated)",
             "l2": "inputs larger than L2: each step streams >14 GB of weights, adapters and KV cache",
             "cuda_graphs": not args.no_graphs, "collectives": "nccl" if (args.baseline_mode or tp.fused is None) else "fused-nvlink",

@@ -92,6 +92,11 @@ class Engine:
         self.stats = dict(prefill_steps=0, decode_steps=0, prefill_tokens=0, generated_tokens=0)
         self.finished: Dict[int, _Seq] = {}
         self.on_adapter_needed: Optional[Callable[[int], bool]] = None     # exchange hook: make adapter resident
+        # built-in exchange policy: adapters registered here are brought into HBM on demand; when the arena is full the
+        # least recently used adapter that no running request needs goes back to the pinned host tier
+        self.adapter_keys: Dict[int, str] = {}
+        self.adapter_lru: "collections.OrderedDict[int, None]" = collections.OrderedDict()
+        self._picking: set = set()
         self.mixed_steps = os.environ.get("LORAX_MIXED_STEPS", "1") != "0"   # prefills ride along with the decode batch
 
     def _auto_blocks(self, page: int) -> int:
@@ -116,15 +121,36 @@ class Engine:
         return not (self.waiting or self.running or self.draining or self.inflight)
 
     # ------------------------------------------------------------------ scheduling
+    def register_adapter(self, adapter_index: int, key: str):
+        """Tell the engine which registered adapter (host-tier key) a request's `adapter_index` means, so that it can be
+        loaded on demand and offloaded when others need the room."""
+        self.adapter_keys[adapter_index] = key
+
     def _adapter_ready(self, adapter_index: int) -> bool:
         ad = self.model.adapters
         if adapter_index == 0 or ad is None:
             return True
         if ad.is_loaded(adapter_index):
+            self.adapter_lru[adapter_index] = None
+            self.adapter_lru.move_to_end(adapter_index)
             return True
         if self.on_adapter_needed is not None:
             return bool(self.on_adapter_needed(adapter_index))
-        return False
+        key = self.adapter_keys.get(adapter_index)
+        if key is None:
+            return False
+        in_use = ({s.req.adapter_index for s in self.running.values()} | {s.req.adapter_index for s in self.draining.values()}
+                  | self._picking)
+        while not ad.load(adapter_index, key):
+            victim = next((i for i in self.adapter_lru if i not in in_use and ad.is_loaded(i)), None)
+            if victim is None:
+                return False                    # everything resident is in use: the request waits
+            ad.offload(victim)
+            del self.adapter_lru[victim]
+            self.stats["adapter_evictions"] = self.stats.get("adapter_evictions", 0) + 1
+        self.stats["adapter_loads"] = self.stats.get("adapter_loads", 0) + 1
+        self.adapter_lru[adapter_index] = None
+        return True
 
     def _select_prefill(self) -> List[Tuple[GenRequest, List[int]]]:
         if not self.waiting:
@@ -139,6 +165,7 @@ class Engine:
             if len(self.waiting) < min(min_size, free_rows):
                 return []
         picked: List[Tuple[GenRequest, List[int]]] = []
+        self._picking = set()           # adapters of requests admitted in this pass: not eviction candidates
         budget = self.cfg.max_batch_prefill_tokens
         skipped: List[GenRequest] = []
         while self.waiting and len(picked) < free_rows:
@@ -157,6 +184,7 @@ class Engine:
                 break
             self.waiting.popleft()
             picked.append((req, blocks))
+            self._picking.add(req.adapter_index)
             budget -= n
         for r in reversed(skipped):
             self.waiting.appendleft(r)

@@ -124,3 +124,37 @@ def test_prefill_riding_on_decode_steps_gives_same_tokens(setup):
     assert n_mixed >= 2
     assert [len(o) for o in mix] == new_tokens
     assert mix == sep
+
+
+def test_adapter_exchange_under_memory_pressure():
+    """Six adapters, an HBM arena that holds two: the engine loads on demand and evicts the least recently used idle
+    adapter.  Tokens equal the run in which every adapter is resident."""
+    from lorax_b200.runtime.engine import GenRequest
+    cfg = tiny_llama()
+    model = DecoderModel.random_init(cfg, "cpu", torch.float32, seed=0)
+    ads = [random_adapter(cfg, r=8, alpha=16, target_modules=["q_proj", "v_proj"], seed=200 + i, std_a=0.05, std_b=0.05) for i in range(6)]
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab_size, (int(torch.randint(6, 20, (1,), generator=g)),), generator=g).tolist() for _ in range(12)]
+    which = [1, 2, 3, 1, 4, 5, 6, 2, 0, 3, 6, 1]
+
+    def run(arena_adapters):
+        mgr = AdapterManager(model, arena_bytes=64 << 20, host_bytes=256 << 20)
+        for i, (c, mm) in enumerate(ads):
+            mgr.register(f"x{i}", c, mm)
+        one = mgr.host.get("x0").blob.numel()
+        mgr2 = AdapterManager(model, arena_bytes=int(one * 4 * arena_adapters * 1.05) + 4096, host_bytes=256 << 20)   # fp32 blobs
+        for i, (c, mm) in enumerate(ads):
+            mgr2.register(f"x{i}", c, mm)
+        eng = Engine(model, EngineConfig(max_total_tokens=64, max_batch_prefill_tokens=256, waiting_served_ratio=0.0), num_blocks=64, max_batch=3)
+        for i in range(6):
+            eng.register_adapter(i + 1, f"x{i}")
+        for i, p in enumerate(prompts):
+            eng.add_request(GenRequest(i + 1, p, 6, which[i]))
+        eng.run(max_steps=500)
+        assert eng.idle
+        return [eng.finished[i + 1].output_ids for i in range(12)], eng.stats, mgr2
+
+    full, _, _ = run(6)
+    tight, stats, mgr = run(2)
+    assert tight == full
+    assert stats.get("adapter_evictions", 0) >= 3 and len(mgr.resident) <= 2
