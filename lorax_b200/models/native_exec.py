@@ -187,6 +187,8 @@ class NativeExecutor:
             if inp.lora_tiles is not None:
                 s.lora_tiles, s.num_tiles, s.max_tile_rows = _p(inp.lora_tiles.table), inp.lora_tiles.num_tiles, inp.lora_tiles.max_rows
         s.normed, s.qkv, s.attn, s.gate_up, s.act = normed.data_ptr(), qkv.data_ptr(), attn.data_ptr(), gate_up.data_ptr(), act.data_ptr()
+        if self.adapters is not None:
+            m.max_rank = self.adapters.max_rank if self.adapters.is_cuda else 0      # changes as adapters come and go
         stream = torch.cuda.current_stream().cuda_stream
         tp = model.tp
         rm = float(c.residual_multiplier)
