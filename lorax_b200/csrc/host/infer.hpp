@@ -79,7 +79,8 @@ class Infer {
         Metrics* metrics)
       : client_(std::move(client)), cfg_(cfg), metrics_(metrics),
         queues_(cfg.max_active_adapters, cfg.adapter_cycle_time_s), block_size_(info.block_size ? info.block_size : 16),
-        window_(info.window_size), speculate_(info.speculate), requires_padding_(info.requires_padding) {
+        window_(info.window_size), speculate_(info.speculate), requires_padding_(info.requires_padding),
+        fused_prefill_decode_(info.fused_prefill_decode) {
     allocator_ = make_allocator(num_blocks, block_size_, window_, cfg.prefix_caching);
     for (auto& p : info.preloaded_adapters) {
       if (!p.adapter_parameters || p.adapter_parameters->adapter_ids.empty()) continue;
@@ -424,6 +425,19 @@ class Infer {
           if (more) {
             if (metrics_) metrics_->inc("lorax_batch_concat", {{"reason", min_size ? "backpressure" : "wait_exceeded"}});
             waiting_tokens = 1;
+            if (fused_prefill_decode_) {
+              // one forward pass on the shards: the new prompts AND one decode step of everything that is running
+              for (auto& e : more->entries) entries[e->id] = e;
+              auto t0 = Clock::now();
+              auto res = client_->prefill(more->batch, std::nullopt, batches);
+              if (metrics_) { metrics_->inc("lorax_batch_inference_count", {{"method", "prefill_decode"}}); metrics_->observe("lorax_batch_inference_duration", secs(t0), {{"method", "prefill_decode"}}); }
+              deliver(res.generations, entries, t0);
+              batches.clear();
+              auto next = filter(res.batch, entries);
+              if (next) batches.push_back(*next);
+              waiting_tokens++;
+              continue;
+            }
             auto c2 = run_prefill(*more, entries);
             if (c2) batches.push_back(*c2);
           }
@@ -531,6 +545,7 @@ class Infer {
   uint32_t block_size_;
   std::optional<uint32_t> window_;
   uint32_t speculate_;
+  bool fused_prefill_decode_ = false;
   bool requires_padding_;
   std::mutex index_mu_;
   std::unordered_map<std::string, uint32_t> adapter_index_;

@@ -145,10 +145,12 @@ class ShardedClient {
     std::vector<gen::Generation> generations;
     std::optional<gen::CachedBatch> batch;
   };
-  StepResult prefill(const gen::Batch& b, const std::optional<gen::CachedBatch>& cached) {
+  StepResult prefill(const gen::Batch& b, const std::optional<gen::CachedBatch>& cached,
+                     const std::vector<gen::CachedBatch>& decode_batches = {}) {
     gen::PrefillRequest r;
     r.batch = b;
     r.cached_batch = cached;
+    r.decode_batches = decode_batches;
     StepResult out;
     for (auto& resp : all<gen::PrefillResponse>(gen::M_Prefill, r)) {
       for (auto& g : resp.generations) out.generations.push_back(std::move(g));

@@ -114,6 +114,7 @@ class ShardRuntime:
         self.downloaded: Dict[str, Tuple[LoraConfig, object]] = {}
         self.lock = threading.Lock()
         self.spec_stats = {"steps": 0, "tokens": 0}          # speculative decoding: row-steps and tokens they produced
+        self.fused_stats = {"one_pass": 0, "two_pass": 0}    # fused Prefill + Decode requests served in one / two forward passes
 
     # ------------------------------------------------------------------ info / health
     def info(self):
@@ -122,7 +123,8 @@ class ShardRuntime:
         r = pb.InfoResponse(requires_padding=False, dtype=str(self.model.dtype).replace("torch.", ""),
                             device_type=self.model.device.type, block_size=self.kv.page, speculate=self.cfg.speculative_tokens,
                             supports_generation=True, supports_embeddings=False, supports_classification=False,
-                            chunked_prefill=self.cfg.chunked_prefill, requires_block_allocator=True)
+                            chunked_prefill=self.cfg.chunked_prefill, requires_block_allocator=True,
+                            fused_prefill_decode=True)
         if c.sliding_window:
             r.window_size = c.sliding_window
         return r
@@ -365,8 +367,15 @@ class ShardRuntime:
 
     # ------------------------------------------------------------------ Prefill / Decode
     def prefill(self, req):
-        pb = self.pb
-        batch = req.batch
+        """Prefill of a new batch.  With `decode_batches` set, the running batches take one decode step in the same
+        forward pass (one pass over the weights for both) and the response merges everything into one cached batch."""
+        if len(req.decode_batches):
+            return self._prefill_and_decode(req)
+        seqs, items = self._new_sequences(req.batch)
+        next_ids, lps, logits = self.runner.prefill(items)
+        return self._finish_prefill(req.batch, seqs, items, next_ids, lps, logits)
+
+    def _new_sequences(self, batch):
         items, seqs = [], []
         max_in = self.cfg.max_input_length
         for r in batch.requests:
@@ -384,17 +393,24 @@ class ShardRuntime:
             seqs.append(s)
             items.append(PrefillItem(ids[r.cache_len:] if r.cache_len else ids, r.cache_len, list(r.blocks), r.adapter_index,
                                      all_logprobs=r.prefill_logprobs))
-        next_ids, lps, logits = self.runner.prefill(items)
+        return seqs, items
+
+    def _finish_prefill(self, batch, seqs, items, next_ids, lps, logits, merge_with: Optional[List[int]] = None, merged_id: Optional[int] = None,
+                        extra_generations=()):
+        """Sample / emit the first tokens, give the survivors decode rows and answer with the cached batch.  With
+        `merge_with` (request ids that survived a decode step of the same pass) everything lands in batch `merged_id`."""
+        pb = self.pb
         # rows of `logits` per request: the last one when prefill log-probs were requested
         row_of, o = [], 0
         for it in items:
             n = len(it.token_ids) if it.all_logprobs else 1
             row_of.append(o + n - 1)
             o += n
-        last_rows = torch.tensor(row_of, device=logits.device)
+        last_rows = torch.tensor(row_of, device=next_ids.device)
         gid = next_ids.index_select(0, last_rows).tolist()
         glp = lps.index_select(0, last_rows).tolist()
-        ids_l, lps_l, alts = self._sample_rows(seqs, logits.index_select(0, last_rows), gid, glp)
+        # (a fused prefill + decode pass keeps no logits: it is only taken when every request is plain greedy)
+        ids_l, lps_l, alts = self._sample_rows(seqs, logits.index_select(0, last_rows) if logits is not None else None, gid, glp)
         gens, live, rows, firsts, poss, blks, ads = [], [], [], [], [], [], []
         o = 0
         for s, it, tok, lp, alt in zip(seqs, items, ids_l, lps_l, alts):
@@ -414,13 +430,55 @@ class ShardRuntime:
                 s.row = self.runner.state.take_row(s.request_id)
                 live.append(s.request_id)
                 rows.append(s.row); firsts.append(int(tok)); poss.append(len(s.prompt_ids)); blks.append(s.blocks); ads.append(s.adapter_index)
-        resp = pb.PrefillResponse(generations=gens)
+        resp = pb.PrefillResponse(generations=list(extra_generations) + gens)
         if live:
             self.runner.install(rows, firsts, poss, blks, ads)
             self._resort()
-            self.batches[batch.id] = live
-            resp.batch.CopyFrom(self._cached(batch.id))
+        bid = batch.id if merged_id is None else merged_id
+        members = list(merge_with or []) + live
+        if members:
+            self.batches[bid] = members
+            for r in members:
+                self.seqs[r].batch_id = bid
+            resp.batch.CopyFrom(self._cached(bid))
         return resp
+
+    def _prefill_and_decode(self, req):
+        """One decode step of the running batches fused with the prefill of a new one."""
+        pb = self.pb
+        bids = [b.id for b in req.decode_batches]
+        rids = [r for b in bids for r in self.batches.get(b, [])]
+        if not rids:
+            raise RuntimeError("all batches of the fused Prefill request are missing from the cache")
+        old = [self.seqs[r] for r in rids]
+        seqs, items = self._new_sequences(req.batch)
+        plain = all(s.params.plain and s.grammar is None for s in old + seqs)
+        if not (plain and self.cfg.speculative_tokens == 0 and not any(it.all_logprobs for it in items) and self.runner.can_mix()
+                and self.runner.state.high_water + sum(len(it.token_ids) for it in items) <= self.runner.max_prefill_tokens):
+            # same result in two passes: decode the running batches, then prefill the new one into the merged batch
+            self.fused_stats["two_pass"] += 1
+            d = self.decode(pb.DecodeRequest(batches=list(req.decode_batches)))
+            survivors = list(self.batches.pop(bids[0], [])) if d.HasField("batch") else []
+            next_ids, lps, logits = self.runner.prefill(items)
+            return self._finish_prefill(req.batch, seqs, items, next_ids, lps, logits, merge_with=survivors, merged_id=bids[0],
+                                        extra_generations=d.generations)
+        self.fused_stats["one_pass"] += 1
+        k, nd, first_ids, first_lps = self.runner.mixed_step(items)
+        ids_p, lps_p = self.runner.wait(k)
+        gens, finished = [], []
+        for s in old:
+            gen, stop = self._emit(s, int(ids_p[s.row]), float(lps_p[s.row]))
+            if gen is not None:
+                gens.append(gen)
+            if stop:
+                finished.append(s.request_id)
+        for bid in bids:
+            self.batches.pop(bid, None)
+        for rid in finished:
+            self._drop(rid)
+        survivors = [r for r in rids if r not in finished]
+        return self._finish_prefill(req.batch, seqs, items, first_ids, first_lps, None, merge_with=survivors, merged_id=bids[0],
+                                    extra_generations=gens)
 
     def decode(self, req):
         pb = self.pb

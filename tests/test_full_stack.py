@@ -161,6 +161,31 @@ def test_concurrent_heterogeneous_requests(stack):
         res = list(ex.map(one, range(12)))
     assert all(st == 200 for st, _, _ in res)
     assert [json.loads(b)["details"]["generated_tokens"] for _, b, _ in res] == [4 + i % 4 for i in range(12)]
+    # staggered arrivals: prompts that arrive while others decode ride along with the decode step (one forward pass), and the
+    # tokens equal those of the same requests sent alone
+    import threading
+    import time as _t
+    prompts = [" ".join(f"w{(11 * i + j) % 500 + 2}" for j in range(5 + i % 5)) for i in range(6)]
+
+    def gen(i):
+        params = {"max_new_tokens": 12, "ignore_eos_token": True, "details": True}
+        if i % 2:
+            params.update(adapter_id=str(root / f"adapter{i % 2 - 1}"), adapter_source="local")
+        st, body, _ = _post(port, "/generate", {"inputs": prompts[i], "parameters": params})
+        assert st == 200, body
+        return [t["id"] for t in json.loads(body)["details"]["tokens"]]
+    alone = [gen(i) for i in range(6)]
+    before = dict(stack["rt"].fused_stats)
+    out = [None] * 6
+
+    def worker(i):
+        _t.sleep(0.03 * i)
+        out[i] = gen(i)
+    ths = [threading.Thread(target=worker, args=(i,)) for i in range(6)]
+    [t.start() for t in ths]
+    [t.join() for t in ths]
+    assert out == alone
+    assert stack["rt"].fused_stats["one_pass"] > before["one_pass"]
 
 
 def test_sampling_and_seed(stack):
