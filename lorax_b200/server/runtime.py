@@ -172,6 +172,8 @@ class ShardRuntime:
         pb = self.pb
         params, source = req.adapter_parameters, req.adapter_source
         key = self._adapter_key(params, source)
+        if self.adapters.host.get(key) is not None:          # already packed in the pinned host tier
+            return pb.DownloadAdapterResponse(downloaded=True, memory_fraction=self.adapters.memory_fraction(key))
         src_name = {0: "hub", 1: "s3", 2: "local", 3: "pbase"}.get(source, "hub")
         loaded = []
         for aid in params.adapter_ids:
