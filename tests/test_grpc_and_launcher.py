@@ -83,7 +83,9 @@ def test_grpc_contract(tmp_path):
     asyncio.run(run())
 
 
-def test_launcher_supervises_shard_and_router(tmp_path):
+@pytest.mark.parametrize("num_shard", [1, 2])
+def test_launcher_supervises_shard_and_router(tmp_path, num_shard):
+    """`lorax-launcher` end to end on CPU: one shard, and two tensor-parallel shards (Gloo) behind one router."""
     from lorax_b200.csrc import build
     build.build_host()
     mdir = _model_dir(tmp_path)
@@ -94,7 +96,7 @@ def test_launcher_supervises_shard_and_router(tmp_path):
     env = dict(os.environ, PYTHONPATH=REPO, CUDA_VISIBLE_DEVICES="", LORAX_COMPILE="0")
     proc = subprocess.Popen([LAUNCHER, "--model-id", str(mdir), "--source", "local", "--port", str(port), "--hostname", "127.0.0.1",
                              "--shard-uds-path", str(tmp_path / "uds"), "--python", sys.executable, "--max-input-length", "64",
-                             "--max-total-tokens", "128", "--json-output", "--master-port", "29611"],
+                             "--max-total-tokens", "128", "--json-output", "--master-port", str(29611 + num_shard), "--num-shard", str(num_shard)],
                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env)
     try:
         ok = False
@@ -113,7 +115,17 @@ def test_launcher_supervises_shard_and_router(tmp_path):
         req = urllib.request.Request(f"http://127.0.0.1:{port}/generate", data=json.dumps({"inputs": "w1 w2", "parameters": {"max_new_tokens": 3}}).encode(),
                                      headers={"Content-Type": "application/json"})
         with urllib.request.urlopen(req, timeout=60) as r:
-            assert "generated_text" in json.loads(r.read())
+            text = json.loads(r.read())["generated_text"]
+        # tensor parallelism must not change the tokens: compare with the single-process model
+        from lorax_b200.config import EngineConfig
+        from lorax_b200.server.runtime import build_runtime
+        rt = build_runtime(str(mdir), EngineConfig(max_input_length=64, max_total_tokens=128, compile=False), device="cpu",
+                           dtype=torch.float32, source="local", num_blocks=64, max_batch=4)
+        ids = rt.tokenize("w1 w2")
+        from lorax_b200.runtime.engine import Engine
+        eng = Engine(rt.model, EngineConfig(max_total_tokens=128, max_batch_prefill_tokens=256), num_blocks=64, max_batch=2)
+        want = eng.generate([ids], max_new_tokens=3, eos_token_ids=frozenset(rt.eos_ids))[0]
+        assert text.strip() == rt.tokenizer.decode(want, skip_special_tokens=True).strip(), (text, want)
     finally:
         proc.send_signal(signal.SIGTERM)
         try:
@@ -123,3 +135,5 @@ def test_launcher_supervises_shard_and_router(tmp_path):
             raise
     out = proc.stdout.read().decode()
     assert "shard 0 ready" in out and proc.returncode == 0, out[-2000:]
+    if num_shard == 2:
+        assert "shard 1 ready" in out
