@@ -399,7 +399,7 @@ class ModelRunner:
         g = torch.cuda.CUDAGraph()
         from ..ops import native
         before = native.launch_count
-        with torch.cuda.graph(g, pool=self.graph_pool):
+        with torch.cuda.graph(g, pool=self.graph_pool, capture_error_mode="thread_local"):      # other threads (NCCL watchdog, RPC handlers) may touch CUDA meanwhile
             logits = self._decode_body(b, lora, need_logits)
             self._advance(b)
         self.graph_kernels[key] = native.launch_count - before

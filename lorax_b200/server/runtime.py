@@ -673,6 +673,14 @@ def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel]
         model.quantize_fp8()
     elif quantize is not None:
         raise ValueError(f"--quantize {quantize}: this build serves bf16/fp16/fp32 and block-scaled fp8 (`--quantize fp8`)")
+    if tp.world_size > 1 and dev.type == "cuda" and os.environ.get("LORAX_FUSED_COLLECTIVES", "1") != "0":
+        # in-kernel NVLink collectives (fused GEMM + all-reduce for small batches, peer-read embedding, arg-max exchange);
+        # every rank takes the same branch, NCCL stays as the path for everything else
+        try:
+            from ..parallel import fused
+            fused.enable(tp, model)
+        except Exception as e:          # no peer access / symmetric memory: NCCL only
+            print(json.dumps({"level": "WARN", "message": f"fused NVLink collectives unavailable: {e}"}), flush=True)
     tp.barrier()
     tok = load_tokenizer(model_dir)
     rt = ShardRuntime(model, tok, cfg, model_id=model_id, **kw)

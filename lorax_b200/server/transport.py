@@ -78,6 +78,10 @@ class FramedServer:
                     raise ConnectionError
                 buf += chunk
             return bytes(buf)
+        # the CUDA "current device" is a per-thread setting and new threads start on device 0: the kernels of this library are
+        # launched through the raw runtime API, so the handler thread must select the shard's GPU itself
+        if self.rt.model.device.type == "cuda":
+            torch.cuda.set_device(self.rt.model.device)
         try:
             while not self._stop.is_set():
                 method, length = struct.unpack("<II", read_exact(8))
@@ -141,6 +145,8 @@ async def serve_grpc(runtime, uds_path: str, rank: int, world_size: int, lock: O
                 if name == "ServiceDiscovery":
                     return pb.ServiceDiscoveryResponse(urls=urls)
                 with lock:
+                    if runtime.model.device.type == "cuda":
+                        torch.cuda.set_device(runtime.model.device)      # per-thread setting, see FramedServer._serve_conn
                     return _dispatch(runtime, name, request)
             except Exception as e:
                 if runtime.model.device.type == "cuda":

@@ -111,7 +111,7 @@ def test_launcher_supervises_shard_and_router(tmp_path, num_shard):
                 time.sleep(0.2)
         if not ok:
             proc.kill()
-            raise AssertionError("deployment did not come up:\n" + proc.stdout.read().decode()[-3000:])
+            raise AssertionError("deployment did not come up:\n" + proc.stdout.read().decode()[-9000:])
         req = urllib.request.Request(f"http://127.0.0.1:{port}/generate", data=json.dumps({"inputs": "w1 w2", "parameters": {"max_new_tokens": 3}}).encode(),
                                      headers={"Content-Type": "application/json"})
         with urllib.request.urlopen(req, timeout=60) as r:
@@ -137,3 +137,59 @@ def test_launcher_supervises_shard_and_router(tmp_path, num_shard):
     assert "shard 0 ready" in out and proc.returncode == 0, out[-2000:]
     if num_shard == 2:
         assert "shard 1 ready" in out
+
+
+@pytest.mark.gpu
+def test_launcher_two_gpu_shards(tmp_path):
+    """Two CUDA shards (NCCL + the in-kernel NVLink collectives) behind the router, started by the launcher."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from lorax_b200.csrc import build
+    build.build_host()
+    mdir = _model_dir(tmp_path)
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    env = dict(os.environ, PYTHONPATH=REPO, NCCL_NVLS_ENABLE="0", LORAX_B200_DEBUG="1")
+    proc = subprocess.Popen([LAUNCHER, "--model-id", str(mdir), "--source", "local", "--port", str(port), "--hostname", "127.0.0.1",
+                             "--shard-uds-path", str(tmp_path / "uds"), "--python", sys.executable, "--max-input-length", "64",
+                             "--max-total-tokens", "128", "--json-output", "--master-port", "29631", "--num-shard", "2", "--dtype", "bfloat16"],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env)
+    try:
+        ok = False
+        for _ in range(900):
+            if proc.poll() is not None:
+                break
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1) as r:
+                    ok = r.status == 200
+                    break
+            except Exception:
+                time.sleep(0.2)
+        if not ok:
+            proc.kill()
+            raise AssertionError("deployment did not come up:\n" + proc.stdout.read().decode()[-9000:])
+        outs = []
+        for n in (3, 9):
+            req = urllib.request.Request(f"http://127.0.0.1:{port}/generate",
+                                         data=json.dumps({"inputs": "w1 w2 w7 w9", "parameters": {"max_new_tokens": n, "ignore_eos_token": True, "details": True}}).encode(),
+                                         headers={"Content-Type": "application/json"})
+            try:
+                with urllib.request.urlopen(req, timeout=120) as r:
+                    j = json.loads(r.read())
+            except urllib.error.HTTPError as e:
+                proc.send_signal(signal.SIGTERM)
+                raise AssertionError(f"HTTP {e.code}: {e.read().decode()[:600]}\n" + proc.stdout.read().decode()[-9000:])
+            assert j["details"]["generated_tokens"] == n
+            outs.append([t["id"] for t in j["details"]["tokens"]])
+        assert outs[1][:3] == outs[0]
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        try:
+            proc.wait(timeout=60)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            raise
+    out = proc.stdout.read().decode()
+    assert "shard 1 ready" in out and proc.returncode == 0, out[-2000:]
