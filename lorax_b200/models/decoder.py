@@ -315,13 +315,15 @@ class DecoderModel:
         self.quantized = "fp8"
         self._native = None
 
-    def _gemm(self, x, w, b, lora=None):
+    def _gemm(self, x, w, b, lora=None, out=None):
+        if out is not None and not isinstance(w, Fp8Weight):
+            return self.ops.gemm(x, w, bias=b, lora=lora, out=out) if lora is not None else self.ops.gemm(x, w, bias=b, out=out)
         if isinstance(w, Fp8Weight):
             y = self.ops.gemm_fp8(x if x.dtype == torch.bfloat16 or not x.is_cuda else x.to(torch.bfloat16), w.q, w.scale, bias=b)
             return y if y.dtype == x.dtype else y.to(x.dtype)
         return self.ops.gemm(x, w, bias=b, lora=lora) if lora is not None else self.ops.gemm(x, w, bias=b)
 
-    def _linear(self, x, w, b, group: str, layer: int, inp: StepInputs, tok_slot=None):
+    def _linear(self, x, w, b, group: str, layer: int, inp: StepInputs, tok_slot=None, out=None):
         """Base GEMM plus the multi-adapter LoRA delta for the projection group.  The shrink x A^T is one small launch;
         the expand is a second one, or rides in the GEMM epilogue when `fused_lora_epilogue` is set."""
         ts = tok_slot if tok_slot is not None else inp.tok_slot
@@ -329,10 +331,10 @@ class DecoderModel:
         if self.adapters is not None and ts is not None:
             epi = self.adapters.shrink(self.ops, x, ts, group, layer, tiles=inp.lora_tiles)
         if epi is None:
-            return self._gemm(x, w, b)
+            return self._gemm(x, w, b, out=out)
         if self.fused_lora_epilogue and not isinstance(w, Fp8Weight):
-            return self._gemm(x, w, b, lora=epi)
-        y = self._gemm(x, w, b)
+            return self._gemm(x, w, b, lora=epi, out=out)
+        y = self._gemm(x, w, b, out=out)
         self.adapters.expand(self.ops, epi, y, tiles=inp.lora_tiles)
         return y
 
@@ -347,7 +349,10 @@ class DecoderModel:
                 addend = torch.zeros(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
                 self.adapters.apply(self.ops, x, addend, inp.tok_slot, group, layer, tiles=inp.lora_tiles)
             return fused.gemm_allreduce(x, w, None, addend)
-        out = self._linear(x, w, b, group, layer, inp)
+        dst = None
+        if fused is not None and x.is_cuda and not isinstance(w, Fp8Weight):
+            dst = fused.all_reduce_input(x.shape[0], w.shape[0])      # the GEMM writes where the all-reduce kernel reads
+        out = self._linear(x, w, b, group, layer, inp, out=dst)
         if self.tp.world_size > 1:
             out = self.tp.all_reduce(out)
         return out

@@ -194,18 +194,20 @@ class NativeExecutor:
         rm = float(c.residual_multiplier)
         residual = h
         pending = None
-        n_launch = 0
+        # under tensor parallelism the O / down projections write their partial sums straight into the symmetric input
+        # area of the all-reduce kernel when it fits; the reduced result comes back as a view that the next half consumes
+        fused = tp.fused if tp.world_size > 1 else None
+        dst = fused.all_reduce_input(T, m.H) if fused is not None else None
+        buf_a = dst if dst is not None else out_a
+        buf_b = dst if dst is not None else out_b
         for li in range(len(model.layers)):
             l = ctypes.byref(self.layers[li])
-            rc = lib.lx_layer_attention(ctypes.byref(m), l, ctypes.byref(s), _p(pending), residual.data_ptr(), rm, out_a.data_ptr(), stream)
+            rc = lib.lx_layer_attention(ctypes.byref(m), l, ctypes.byref(s), _p(pending), residual.data_ptr(), rm, buf_a.data_ptr(), stream)
             native._check(rc, "lx_layer_attention")
-            if tp.world_size > 1:
-                tp.all_reduce(out_a)
-            rc = lib.lx_layer_mlp(ctypes.byref(m), l, ctypes.byref(s), out_a.data_ptr(), residual.data_ptr(), rm, out_b.data_ptr(), stream)
+            a_res = tp.all_reduce(buf_a) if tp.world_size > 1 else buf_a
+            rc = lib.lx_layer_mlp(ctypes.byref(m), l, ctypes.byref(s), a_res.data_ptr(), residual.data_ptr(), rm, buf_b.data_ptr(), stream)
             native._check(rc, "lx_layer_mlp")
-            if tp.world_size > 1:
-                tp.all_reduce(out_b)
-            pending = out_b
+            pending = tp.all_reduce(buf_b) if tp.world_size > 1 else buf_b
         lora_sites = 4 if s.tok_slot else 0
         attn_kernels = (1 if s.n_decode else 0) + (1 if T > s.n_decode else 0)
         native.launch_count += len(model.layers) * (8 + attn_kernels + 2 * lora_sites)

@@ -4,7 +4,7 @@ roofline of the fused path: the slower of FLOPs / measured GEMM peak and NVLink 
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m lorax_b200.parallel.bench_fused
 
 Both arms are captured in a CUDA graph (20 calls rotating through >126 MB of weights) and device-timed; the number
-reported is the maximum over ranks.
+reported is the maximum over ranks.  With `--allreduce` the two-shot all-reduce kernel is timed against NCCL's instead.
 """
 
 from __future__ import annotations
@@ -48,9 +48,36 @@ def gtime(fn, n_rot, reps=20):
     return float(t.item())
 
 
+def bench_allreduce(tp):
+    """Two-shot all-reduce kernel against NCCL's all-reduce on bf16 [T, 4096]; results are compared bit for bit."""
+    from . import fused
+    fc = fused.FusedCollectives(tp, n_max=4096, max_rows=512)
+    fc.setup_all_reduce(4352, 4096)
+    for T in (16, 256, 1216, 4096):
+        x = torch.randn(T, 4096, device="cuda", dtype=torch.bfloat16)
+        src = fc.all_reduce_input(T, 4096)
+        src.copy_(x)
+        want = x.clone()
+        dist.all_reduce(want)
+        got = fc.all_reduce(src).clone()
+        torch.cuda.synchronize()
+        err = (got.float() - want.float()).abs().max().item()
+        t_nccl = gtime(lambda i: dist.all_reduce(x), 1)
+        t_mine = gtime(lambda i: fc.all_reduce(src), 1)
+        fc.check()
+        if tp.rank == 0:
+            print(json.dumps(dict(op="all_reduce", T=T, mbytes=round(T * 4096 * 2 / 1e6, 1), world=tp.world_size, nccl_us=round(t_nccl, 1),
+                                  two_shot_us=round(t_mine, 1), max_abs_diff=err)), flush=True)
+    dist.barrier()
+    os._exit(0)
+
+
 def main():
+    import sys
     tp = TensorParallel.init_from_env()
     ws = tp.world_size
+    if "--allreduce" in sys.argv:
+        bench_allreduce(tp)
     from . import fused
 
     class _M:

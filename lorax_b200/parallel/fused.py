@@ -10,6 +10,9 @@
   sites C2 / C3 / C5 of the reference: `utils/layers.py:279-300, 329-374`).
 * `embed`           vocabulary-parallel embedding by peer reads: every rank fetches the rows it needs from the owner's shard,
   the [T, H] all-reduce of call site C1 (`layers/tensor_parallel.py:153-190`) disappears.
+* `all_reduce`      two-shot all-reduce kernel (`csrc/kernels/allreduce_sym.cu`): every rank reduces its slice with
+  16-byte peer loads and stores the result to all ranks; the row-parallel GEMM writes its partial straight into the
+  symmetric input area, so there is no staging copy.
 * `argmax_tp`       greedy sampling over vocabulary-parallel logits exchanging 16 bytes per row instead of
   all-gathering the logits (C6, `layers/tensor_parallel.py:50-79`).
 
@@ -19,6 +22,7 @@ Every device-side wait is bounded; `check()` reads the status word.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -50,6 +54,10 @@ class FusedCollectives:
         lib.lx_embed_peer.argtypes = [P, P, P, I, I, I, I, I, ctypes.c_float, P]
         lib.lx_embed_peer.restype = I
         self.embed_ptrs = None
+        lib.lx_allreduce_sym.argtypes = [P, I, I, L, L, L, L, P, P, P]
+        lib.lx_allreduce_sym.restype = I
+        lib.lx_allreduce_sym_counter_bytes.restype = I
+        self.ar_ptrs = None
         self.lib = lib
         self.tp = tp
         self.rank, self.world = tp.rank, tp.world_size
@@ -115,8 +123,48 @@ class FusedCollectives:
         native.launch_count += 1
         return out
 
+    def setup_all_reduce(self, max_tokens: int, hidden: int):
+        """Symmetric buffer of the two-shot all-reduce kernel: [input | output | counters]."""
+        import torch.distributed._symmetric_memory as symm
+        area = (max_tokens * hidden * 2 + 255) // 256 * 256
+        cnt = self.lib.lx_allreduce_sym_counter_bytes()
+        self.ar_buf = symm.empty(2 * area + cnt, dtype=torch.uint8, device=self.tp.device)
+        self.ar_buf.zero_()
+        torch.cuda.synchronize(self.tp.device)
+        self.ar_handle = symm.rendezvous(self.ar_buf, self.tp.group)
+        self.ar_ptrs = (ctypes.c_ulonglong * self.world)(*list(self.ar_handle.buffer_ptrs))
+        self.ar_area, self.ar_capacity = area, max_tokens * hidden
+        self.ar_state = torch.zeros(2, dtype=torch.int32, device=self.tp.device)
+        self.ar_in = self.ar_buf[:area].view(torch.bfloat16)
+        self.ar_out = self.ar_buf[area: 2 * area].view(torch.bfloat16)
+        self.ar_calls = 0
+        self.tp.barrier()
+
+    def all_reduce_input(self, T: int, N: int) -> Optional[torch.Tensor]:
+        """Where the producer of an all-reduce operand should write it ([T, N] bf16 inside the symmetric buffer), or None
+        when the operand does not fit (the caller then takes NCCL)."""
+        if self.ar_ptrs is None or T * N > self.ar_capacity or (T * N) % 8:
+            return None
+        return self.ar_in[: T * N].view(T, N)
+
     def all_reduce(self, x: torch.Tensor):
-        return None      # plain all-reduces (embedding, large prefill activations) stay on NCCL
+        """Sum over the ranks with the in-kernel two-shot all-reduce.  Returns a [T, N] view of the output area, valid until
+        the next call, or None when the tensor is not eligible (NCCL is used then).  An operand that already sits in
+        `all_reduce_input` is reduced in place, anything else is copied there first."""
+        if self.ar_ptrs is None or x.dtype != torch.bfloat16 or x.dim() != 2 or not x.is_contiguous():
+            return None
+        T, N = x.shape
+        src = self.all_reduce_input(T, N)
+        if src is None:
+            return None
+        if x.data_ptr() != src.data_ptr():
+            src.copy_(x)
+        rc = self.lib.lx_allreduce_sym(ctypes.cast(self.ar_ptrs, ctypes.c_void_p), self.rank, self.world, 0, self.ar_area, 2 * self.ar_area,
+                                       T * N, self.ar_state.data_ptr(), self.ws.status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+        native._check(rc, "lx_allreduce_sym")
+        native.launch_count += 1
+        self.ar_calls += 1
+        return self.ar_out[: T * N].view(T, N)
 
     def check(self):
         self.ws.check_status()
@@ -126,6 +174,9 @@ def enable(tp, model, max_rows: int = 512) -> FusedCollectives:
     if tp.world_size == 1:
         raise ValueError("fused collectives need a tensor-parallel group")
     fc = FusedCollectives(tp, n_max=model.hidden, max_rows=max_rows)
+    if os.environ.get("LORAX_SYM_ALLREDUCE", "1") != "0" and not model.config.parallel_residual:
+        # (with parallel residuals two all-reduce results are alive at once; the kernel keeps one output area)
+        fc.setup_all_reduce(int(os.environ.get("LORAX_SYM_ALLREDUCE_TOKENS", "4352")), model.hidden)
     if model.embed is not None and model.embed.is_cuda and model.embed.dtype == torch.bfloat16 and model.pos_embed is None:
         model.embed = fc.share_embedding(model.embed, model.vocab_local * tp.world_size)
     tp.fused = fc

@@ -37,4 +37,5 @@ def test_tp2_nccl_and_fused_kernels():
     assert r["model_fused_first_tokens_equal"]
     assert r["fused_calls"] > 0
     assert r["gemm_allreduce_relerr"] < 6e-3 and r["gemm_allreduce_ranks_identical"]
+    assert r["allreduce_sym_relerr"] < 6e-3 and r["allreduce_sym_ranks_identical"]
     assert r["argmax_tp_ok"]

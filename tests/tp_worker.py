@@ -101,6 +101,23 @@ def main():
         fc.check()
         out["gemm_allreduce_relerr"] = max(errs)
         out["gemm_allreduce_ranks_identical"] = all(eq)
+        # two-shot all-reduce kernel against an fp32 sum of the ranks' inputs
+        if fc.all_reduce_input(1, cfg.hidden_size) is not None:
+            errs, eq = [], []
+            for it, T in enumerate([1, 7, 64, 300]):
+                gen = torch.Generator(device=dev).manual_seed(900 + 10 * it + tp.rank)
+                x = torch.randn(T, cfg.hidden_size, device=dev, dtype=dtype, generator=gen)
+                want = x.float()
+                dist.all_reduce(want)
+                got = fc.all_reduce(x.clone() if it % 2 else fc.all_reduce_input(T, cfg.hidden_size).copy_(x)).clone()
+                torch.cuda.synchronize()
+                errs.append(((got.float() - want).norm() / want.norm()).item())
+                gathered = [torch.empty_like(got) for _ in range(tp.world_size)]
+                dist.all_gather(gathered, got)
+                eq.append(all(torch.equal(gathered[0], t) for t in gathered))
+            fc.check()
+            out["allreduce_sym_relerr"] = max(errs)
+            out["allreduce_sym_ranks_identical"] = all(eq)
         # vocabulary-parallel greedy head
         ok = []
         for it, T in enumerate([3, 40]):
