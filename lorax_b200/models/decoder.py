@@ -23,6 +23,7 @@ import torch
 from ..config import ModelConfig
 from ..ops import get_ops, reference
 from ..parallel.tp import TensorParallel
+from ..utils.quant_formats import GroupQuantWeight
 from ..utils.weights import AbstractWeights
 
 # projection groups that share one base GEMM; LoRA blobs follow the same grouping
@@ -315,8 +316,31 @@ class DecoderModel:
         self.quantized = "fp8"
         self._native = None
 
+    def quantize(self, method: str, group: int = 128):
+        """Weight-only quantisation of the dense projection matrices on load (`--quantize` of the reference's shard CLI,
+        cli.py:15-28): 4-bit groups (`gptq`, `awq`, `int4`), int8 per channel (`eetq`, `bitsandbytes`, `int8`), the nf4 / fp4
+        code books (`bitsandbytes-nf4`, `bitsandbytes-fp4`) and HQQ at 4 / 3 / 2 bits.  Matrices the checkpoint already
+        holds in packed form are left as loaded."""
+        if method == "fp8":
+            return self.quantize_fp8()
+        from ..utils.quant_formats import quantize_weight
+        for lw in self.layers:
+            for name in ("qkv_w", "o_w", "gate_up_w", "down_w"):
+                w = getattr(lw, name)
+                if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 128 == 0 and w.shape[0] % 16 == 0:
+                    setattr(lw, name, quantize_weight(w, method, group))
+        self.quantized = method
+        self._native = None
+
     def _gemm(self, x, w, b, lora=None, out=None):
-        if out is not None and not isinstance(w, Fp8Weight):
+        if isinstance(w, GroupQuantWeight):
+            xb = x if x.dtype == torch.bfloat16 or not x.is_cuda else x.to(torch.bfloat16)
+            y = self.ops.gemm_wq(xb, w, bias=b, out=out if out is not None and out.dtype == xb.dtype else None)
+            if out is not None and y is not out:
+                out.copy_(y)
+                return out
+            return y if y.dtype == x.dtype else y.to(x.dtype)
+        if out is not None and isinstance(w, torch.Tensor):
             return self.ops.gemm(x, w, bias=b, lora=lora, out=out) if lora is not None else self.ops.gemm(x, w, bias=b, out=out)
         if isinstance(w, Fp8Weight):
             y = self.ops.gemm_fp8(x if x.dtype == torch.bfloat16 or not x.is_cuda else x.to(torch.bfloat16), w.q, w.scale, bias=b)
@@ -332,7 +356,7 @@ class DecoderModel:
             epi = self.adapters.shrink(self.ops, x, ts, group, layer, tiles=inp.lora_tiles)
         if epi is None:
             return self._gemm(x, w, b, out=out)
-        if self.fused_lora_epilogue and not isinstance(w, Fp8Weight):
+        if self.fused_lora_epilogue and isinstance(w, torch.Tensor):
             return self._gemm(x, w, b, lora=epi, out=out)
         y = self._gemm(x, w, b, out=out)
         self.adapters.expand(self.ops, epi, y, tiles=inp.lora_tiles)
@@ -343,14 +367,14 @@ class DecoderModel:
         fused GEMM -> reduce-scatter -> all-gather kernel; the rank's partial LoRA delta is reduced with it."""
         fused = self.tp.fused if self.tp.world_size > 1 else None
         if (fused is not None and x.is_cuda and x.shape[0] <= min(fused.MAX_TOKENS, fused.max_fused_tokens) and b is None
-                and not self.config.parallel_residual and not isinstance(w, Fp8Weight)):
+                and not self.config.parallel_residual and isinstance(w, torch.Tensor)):
             addend = None
             if self.adapters is not None and (inp.tok_slot is not None or inp.lora_tiles is not None) and self.adapters.max_rank > 0:
                 addend = torch.zeros(x.shape[0], w.shape[0], dtype=x.dtype, device=x.device)
                 self.adapters.apply(self.ops, x, addend, inp.tok_slot, group, layer, tiles=inp.lora_tiles)
             return fused.gemm_allreduce(x, w, None, addend)
         dst = None
-        if fused is not None and x.is_cuda and not isinstance(w, Fp8Weight):
+        if fused is not None and x.is_cuda and isinstance(w, torch.Tensor):
             dst = fused.all_reduce_input(x.shape[0], w.shape[0])      # the GEMM writes where the all-reduce kernel reads
         out = self._linear(x, w, b, group, layer, inp, out=dst)
         if self.tp.world_size > 1:

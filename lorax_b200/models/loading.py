@@ -11,6 +11,7 @@ from typing import Dict, List, Optional
 
 import torch
 
+from ..utils.quant_formats import GroupQuantWeight, cat_rows, dequantize
 from ..utils.weights import AbstractWeights
 from .decoder import DecoderModel, LayerWeights
 
@@ -83,6 +84,14 @@ def _split_qkv_full(m: DecoderModel, qkv: torch.Tensor, nm: dict):
     return qkv[: nh * d], qkv[nh * d: (nh + nkv) * d], qkv[(nh + nkv) * d: (nh + 2 * nkv) * d]
 
 
+def _cat0(parts):
+    """Row concatenation of dense matrices or of packed ones (fused QKV / gate_up of a GPTQ / AWQ checkpoint)."""
+    if all(isinstance(p, GroupQuantWeight) for p in parts):
+        return cat_rows(parts)
+    dt = next(p.dtype for p in parts if isinstance(p, torch.Tensor))
+    return torch.cat([dequantize(p, dt) if isinstance(p, GroupQuantWeight) else p for p in parts], 0)
+
+
 def _shard_qkv(m: DecoderModel, q, k, v):
     c, ws, rk = m.config, m.tp.world_size, m.tp.rank
     d = c.head_dim
@@ -90,7 +99,7 @@ def _shard_qkv(m: DecoderModel, q, k, v):
     kv_rank = (rk // m.kv_replicas) if c.num_key_value_heads < ws else rk
     ks = k[kv_rank * m.nkv * d:(kv_rank + 1) * m.nkv * d]
     vs = v[kv_rank * m.nkv * d:(kv_rank + 1) * m.nkv * d]
-    return torch.cat([q[rk * qb:(rk + 1) * qb], ks, vs], 0)
+    return _cat0([q[rk * qb:(rk + 1) * qb], ks, vs])
 
 
 def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
@@ -104,10 +113,17 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
     conv1d = nm.get("conv1d", False)
 
     def fin(t):
+        if isinstance(t, GroupQuantWeight):
+            return t.to(dev)
         return t.to(dt).to(dev).contiguous() if t is not None else None
 
-    def lin(name):            # weight as [out, in]
+    def dense(t):
+        return dequantize(t, dt) if isinstance(t, GroupQuantWeight) else t
+
+    def lin(name, packed=True):            # weight as [out, in]; a packed checkpoint layer stays packed unless asked otherwise
         t = _need(w, name + ".weight", pre)
+        if conv1d or not packed:
+            t = dense(t)
         return t.t() if conv1d else t
 
     def bias(name):
@@ -152,7 +168,7 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
     for i in range(c.num_hidden_layers):
         L = nm["layer"].format(i=i)
         if nm.get("qkv"):
-            q, k, v = _split_qkv_full(m, lin(L + nm["qkv"]), nm)
+            q, k, v = _split_qkv_full(m, lin(L + nm["qkv"], packed=not (nm.get("qkv_interleaved") or nm.get("qkv_grouped"))), nm)
             qb_ = bias(L + nm["qkv"])
             qkv_b = _shard_qkv(m, *_split_qkv_full(m, qb_, nm)) if qb_ is not None else None
         else:
@@ -179,17 +195,17 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
             w13, w2 = [], []
             for e in range(E):
                 P = L + nm["expert"].format(e=e)
-                w13.append(torch.cat([_need(w, P + "w1.weight", pre), _need(w, P + "w3.weight", pre)], 0))
-                w2.append(_need(w, P + "w2.weight", pre))
+                w13.append(torch.cat([dense(_need(w, P + "w1.weight", pre)), dense(_need(w, P + "w3.weight", pre))], 0))
+                w2.append(dense(_need(w, P + "w2.weight", pre)))
             lw.experts_w13 = fin(torch.stack(w13))
             lw.experts_w2 = fin(torch.stack(w2))
         else:
             if nm.get("gate_up"):
                 gu = lin(L + nm["gate_up"])
                 I = gu.shape[0] // 2
-                lw.gate_up_w = fin(torch.cat([rows(gu[:I]), rows(gu[I:])], 0))
+                lw.gate_up_w = fin(_cat0([rows(gu[:I]), rows(gu[I:])]))
             elif nm.get("gate"):
-                lw.gate_up_w = fin(torch.cat([rows(lin(L + nm["gate"])), rows(lin(L + nm["up"]))], 0))
+                lw.gate_up_w = fin(_cat0([rows(lin(L + nm["gate"])), rows(lin(L + nm["up"]))]))
             else:
                 lw.gate_up_w = fin(rows(lin(L + nm["up"])))
                 ub = bias(L + nm["up"])
@@ -200,6 +216,9 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
             if db is not None:
                 lw.down_b = fin(db if rk == 0 else torch.zeros_like(db))
         m.layers.append(lw)
+    if any(isinstance(getattr(lw, n, None), GroupQuantWeight) for lw in m.layers for n in ("qkv_w", "o_w", "gate_up_w", "down_w")):
+        m.quantized = (getattr(w, "quant", None) or {}).get("quant_method", "int4")
+        m._native = None
 
 
 def export_hf_state_dict(m: DecoderModel) -> Dict[str, torch.Tensor]:

@@ -70,6 +70,8 @@ def load() -> ctypes.CDLL:
         "lx_gemm_bf16_lora": ([P, P, P, P, I, I, I, L, L, L, F, P, L, P, P, I, I, I, P, I, P, P, P, P, I, L, I, I, P], I),
         "lx_quant_act_fp8": ([P, L, P, L, P, I, I, I, P], I),
         "lx_gemm_fp8_block128": ([P, L, P, I, P, L, P, P, L, P, I, I, I, P, L, P, I, P], I),
+        "lx_wq_dequant": ([P, P, P, P, L, I, I, I, I, P], I),
+        "lx_wq4_gemm": ([P, L, P, P, P, P, L, I, I, I, I, P], I),
         "lx_lora_expand_tiled": ([P, I, L, I, P, I, I, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
     }
     for name, (argtypes, restype) in sigs.items():
@@ -218,6 +220,38 @@ def gemm_fp8(x: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, bias: Opt
                                      ws.num_sms, _stream())
     _check(rc, "lx_gemm_fp8_block128")
     return out
+
+
+def wq_dequant(w, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Packed group-quantised weight (`utils.quant_formats.GroupQuantWeight`) -> bf16 [N, K]."""
+    N, K = w.shape
+    if out is None:
+        out = torch.empty(N, K, dtype=torch.bfloat16, device=w.codes.device)
+    rc = load().lx_wq_dequant(_ptr(w.codes), _ptr(w.sz), _ptr(w.table), _ptr(out), out.stride(0), N, K, w.bits, w.group, _stream())
+    _check(rc, "lx_wq_dequant")
+    return out
+
+
+WQ4_DIRECT_MAX_TOKENS = int(os.environ.get("LORAX_WQ4_DIRECT_TOKENS", "32"))
+
+
+def gemm_wq(x: torch.Tensor, w, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ dequant(w)^T (+ bias) for a weight-only quantised matrix.  Few tokens and affine 4-bit codes:
+    the tensor-core kernel that multiplies straight from the packed codes (HBM traffic = the packed weights).  Otherwise
+    the codes are expanded to bf16 once and the tcgen05 GEMM runs on the expansion."""
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    T, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    if (w.bits == 4 and w.table is None and T <= WQ4_DIRECT_MAX_TOKENS and N % 16 == 0 and K % 128 == 0 and w.group % 32 == 0
+            and x.stride(0) % 8 == 0):
+        rc = load().lx_wq4_gemm(_ptr(x), x.stride(0), _ptr(w.codes), _ptr(w.sz), _ptr(bias), _ptr(out), out.stride(0), T, N, K, w.group,
+                                _stream())
+        _check(rc, "lx_wq4_gemm")
+        return out
+    return gemm(x, wq_dequant(w), bias=bias, out=out)
 
 
 # ------------------------------------------------------------------------------------------------ elementwise

@@ -62,6 +62,19 @@ def quant_act_fp8(x):
     return q.contiguous(), scale.t().contiguous()
 
 
+def gemm_wq(x, w, bias=None, out=None):
+    """Oracle of the weight-only quantised GEMM: the packed matrix expanded to the activation dtype, then a plain product."""
+    from ..utils.quant_formats import dequantize
+    y = x.float() @ dequantize(w, torch.float32).to(x.dtype).float().t()
+    if bias is not None:
+        y = y + bias.float()
+    y = y.to(x.dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
 def gemm_fp8(x, wq, w_scale, bias=None, out=None):
     """Oracle of the block-scaled fp8 GEMM: both operands rounded to e4m3 with their scales, product in fp32."""
     xq, sa = quant_act_fp8(x)

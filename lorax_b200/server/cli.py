@@ -71,8 +71,13 @@ def download_weights(args):
 
 def quantize(args):
     from ..utils.quantize import quantize_checkpoint
-    stats = quantize_checkpoint(args.model_id, args.output_dir, method=args.scheme)
-    _log("INFO", f"quantised checkpoint written to {args.output_dir}: {stats['quantized']} of {stats['tensors']} tensors in fp8", args.json_output)
+    extra = {}
+    if args.scheme == "gptq":
+        extra = dict(bits=args.bits, group=args.groupsize, nsamples=args.nsamples, seqlen=args.seqlen, dataset=args.dataset,
+                     damp=args.percdamp)
+    stats = quantize_checkpoint(args.model_id, args.output_dir, method=args.scheme, **extra)
+    _log("INFO", f"quantised checkpoint written to {args.output_dir}: {stats['quantized']} of {stats['tensors']} tensors in {args.scheme}",
+         args.json_output)
 
 
 def main(argv=None):
@@ -111,7 +116,13 @@ def main(argv=None):
     q = sub.add_parser("quantize")
     q.add_argument("model_id")
     q.add_argument("output_dir")
-    q.add_argument("--scheme", default="fp8", choices=["fp8"])
+    q.add_argument("--scheme", default="gptq", choices=["fp8", "gptq"])
+    q.add_argument("--bits", type=int, default=4, choices=[2, 4, 8])
+    q.add_argument("--groupsize", type=int, default=128)
+    q.add_argument("--nsamples", type=int, default=128)
+    q.add_argument("--seqlen", type=int, default=2048)
+    q.add_argument("--percdamp", type=float, default=0.01)
+    q.add_argument("--dataset", default="", help="UTF-8 text file with one calibration sample per line (default: random token ids)")
     q.add_argument("--json-output", action="store_true")
     q.set_defaults(fn=quantize)
     args = ap.parse_args(argv)

@@ -31,7 +31,7 @@ from ..sampling.chooser import (FINISH_EOS, FINISH_LENGTH, FINISH_STOP, Heteroge
                                 StoppingCriteria)
 from ..sampling.grammar import compile_schema
 from ..utils.sources import resolve_adapter, resolve_model
-from ..utils.weights import Weights, safetensors_nbytes, weight_files
+from ..utils.weights import Weights, checkpoint_quantization, safetensors_nbytes, weight_files
 from .proto import load_pb
 
 
@@ -663,16 +663,21 @@ def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel]
         return EncoderRuntime(enc, load_tokenizer(model_dir), cfg, model_id=model_id)
     mc = ModelConfig.from_pretrained(model_dir)
     w = Weights(weight_files(model_dir), device="cpu", dtype=dtype, rank=tp.rank, world_size=tp.world_size)
+    quantize = kw.pop("quantize", None) or cfg.quantize
+    # a GPTQ / AWQ checkpoint: its packed layers are served as they are unless another scheme is asked for
+    w.quant = checkpoint_quantization(model_dir, raw_cfg)
+    w.keep_packed = quantize in (None, "gptq", "awq")
     tp.barrier()
     model = DecoderModel.from_weights(mc, w, dev, dtype, tp, max_positions=min(mc.max_position_embeddings, max(cfg.max_total_tokens + 64, 2048)))
-    quantize = kw.pop("quantize", None) or cfg.quantize
     qc = getattr(mc, "quantization_config", None) or {}
     if quantize is None and isinstance(qc, dict) and qc.get("quant_method") == "fp8":
         quantize = "fp8"
-    if quantize == "fp8":
-        model.quantize_fp8()
-    elif quantize is not None:
-        raise ValueError(f"--quantize {quantize}: this build serves bf16/fp16/fp32 and block-scaled fp8 (`--quantize fp8`)")
+    if quantize == "fp8-kv":
+        quantize = "fp8"                   # the KV cache stays in the model dtype; the weights take the fp8 path
+    if quantize in ("gptq", "awq") and w.quant is None:
+        raise ValueError(f"--quantize {quantize} needs a {quantize} checkpoint (no quantization_config / quantize_config.json found)")
+    if quantize is not None and not (quantize in ("gptq", "awq") and model.quantized):
+        model.quantize(quantize)           # on-load quantisation of whatever is still dense
     if tp.world_size > 1 and dev.type == "cuda" and os.environ.get("LORAX_FUSED_COLLECTIVES", "1") != "0":
         # in-kernel NVLink collectives (fused GEMM + all-reduce for small batches, peer-read embedding, arg-max exchange);
         # every rank takes the same branch, NCCL stays as the path for everything else

@@ -21,11 +21,47 @@ from safetensors.torch import load_file, save_file
 
 
 class AbstractWeights:
+    # GPTQ / AWQ checkpoints: {"quant_method", "bits", "group_size", "zero_offset"} (see `checkpoint_quantization`); a linear
+    # layer stored as `<name>.qweight / .qzeros / .scales [/ .g_idx]` is then visible under `<name>.weight`, either in the
+    # packed resident form (`keep_packed`) or expanded to the loader's dtype
+    quant: Optional[dict] = None
+    keep_packed: bool = True
+
     def get_tensor(self, name: str) -> torch.Tensor:  # pragma: no cover - interface
         raise NotImplementedError
 
     def has_tensor(self, name: str) -> bool:  # pragma: no cover - interface
         raise NotImplementedError
+
+    def _raw(self, name: str) -> Optional[torch.Tensor]:  # pragma: no cover - interface
+        """The stored tensor without any conversion, or None."""
+        raise NotImplementedError
+
+    def _quant_base(self, name: str) -> Optional[str]:
+        if self.quant is None or not name.endswith(".weight"):
+            return None
+        base = name[: -len("weight")]
+        return base if self._raw_exists(base + "qweight") else None
+
+    def _raw_exists(self, name: str) -> bool:
+        return self._raw(name) is not None
+
+    def get_quantized_linear(self, name: str):
+        """`<name>` ends in `.weight`: the packed `GroupQuantWeight` of that layer when its groups are contiguous and
+        `keep_packed` is set, else the dense [out, in] matrix."""
+        from .quant_formats import from_checkpoint
+        base = self._quant_base(name)
+        q = self.quant
+        tensors = {k: self._raw(base + k) for k in ("qweight", "qzeros", "scales")}
+        g = self._raw(base + "g_idx")
+        if g is not None:
+            tensors["g_idx"] = g
+        dt = getattr(self, "dtype", None) or torch.float32
+        packed, dense = from_checkpoint(tensors, q.get("quant_method", "gptq"), int(q.get("bits", 4)), int(q.get("group_size", 128)),
+                                        int(q.get("zero_offset", 1)), dtype=dt, want_dense=not self.keep_packed)
+        if packed is not None and self.keep_packed:
+            return packed
+        return dense
 
     def get_shape(self, name: str):
         return tuple(self.get_tensor(name).shape)
@@ -68,6 +104,20 @@ class Weights(AbstractWeights):
             self._resolve(name)
             return True
         except KeyError:
+            return self._quant_base(name) is not None
+
+    def _raw(self, name: str) -> Optional[torch.Tensor]:
+        try:
+            fn, key = self._resolve(name)
+        except KeyError:
+            return None
+        return self._handle(fn).get_tensor(key)
+
+    def _raw_exists(self, name: str) -> bool:
+        try:
+            self._resolve(name)
+            return True
+        except KeyError:
             return False
 
     def _slice(self, name: str):
@@ -98,7 +148,13 @@ class Weights(AbstractWeights):
 
     # ---------------------------------------------------------------- getters
     def get_tensor(self, name: str) -> torch.Tensor:
-        fn, key = self._resolve(name)
+        try:
+            fn, key = self._resolve(name)
+        except KeyError:
+            if self._quant_base(name) is None:
+                raise
+            t = self.get_quantized_linear(name)
+            return t if not isinstance(t, torch.Tensor) else self._finish(t)
         return self._finish(self._dequant_fp8(name, self._handle(fn).get_tensor(key)))
 
     def get_partial_sharded(self, name: str, dim: int) -> torch.Tensor:
@@ -140,9 +196,15 @@ class InMemoryWeights(AbstractWeights):
         self.rank, self.world_size = rank, world_size
 
     def has_tensor(self, name):
-        return name in self.tensors
+        return name in self.tensors or self._quant_base(name) is not None
+
+    def _raw(self, name):
+        return self.tensors.get(name)
 
     def get_tensor(self, name):
+        if name not in self.tensors and self._quant_base(name) is not None:
+            t = self.get_quantized_linear(name)
+            return t if not isinstance(t, torch.Tensor) else self.get_tensor_from(t)
         t = self.tensors[name]
         if self.dtype is not None and t.dtype.is_floating_point:
             t = t.to(self.dtype)
@@ -160,6 +222,29 @@ class InMemoryWeights(AbstractWeights):
         if self.dtype is not None and t.dtype.is_floating_point:
             t = t.to(self.dtype)
         return t.to(self.device)
+
+
+def checkpoint_quantization(model_dir: os.PathLike, config: Optional[dict] = None) -> Optional[dict]:
+    """How the checkpoint's linear layers are stored, from `config.json` (`quantization_config`), AutoGPTQ's
+    `quantize_config.json` or AutoAWQ's `quant_config.json`; None for a dense (or block-fp8) checkpoint.  The reference reads
+    the same files in `Weights._set_gptq_params` (utils/weights.py:409-447)."""
+    d = Path(model_dir)
+    qc = dict((config or {}).get("quantization_config") or {})
+    if not qc:
+        for fn in ("quantize_config.json", "quant_config.json"):
+            if (d / fn).exists():
+                qc = json.loads((d / fn).read_text())
+                break
+    if not qc:
+        return None
+    method = qc.get("quant_method") or ("awq" if "w_bit" in qc else "gptq")
+    if method not in ("gptq", "awq"):
+        return None
+    bits = int(qc.get("bits", qc.get("w_bit", 4)))
+    group = int(qc.get("group_size", qc.get("q_group_size", 128)))
+    v2 = qc.get("checkpoint_format") == "gptq_v2"
+    return {"quant_method": method, "bits": bits, "group_size": group, "zero_offset": 0 if (v2 or method == "awq") else 1,
+            "desc_act": bool(qc.get("desc_act", False))}
 
 
 # -------------------------------------------------------------------------------------------- files
