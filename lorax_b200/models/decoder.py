@@ -122,6 +122,8 @@ class DecoderModel:
         self.cos_sin = reference.rope_cache(c.rotary_dim, self.max_positions, c.rope_theta, c.rope_scaling, device=self.device)
         self.adapters = None     # AdapterManager, attached by the runtime
         self.quantized: Optional[str] = None
+        self.keep_hidden = False                 # keep the head's input rows of the last eager forward pass in `last_hidden`
+        self.last_hidden: Optional[torch.Tensor] = None
         self._native = None
         self.use_native_layers = self.device.type == "cuda" and os.environ.get("LORAX_NATIVE_LAYERS", "1") != "0"
         # LoRA expand inside the GEMM epilogue instead of its own launch (slower than the separate kernel at present:
@@ -436,6 +438,8 @@ class DecoderModel:
         hidden = self._norm(pending, residual, self.final_norm, self.final_norm_b, x_scale=rm)
         if inp.lm_head_indices is not None:
             hidden = hidden.index_select(0, inp.lm_head_indices.long()) if hidden.device.type == "cpu" else hidden[inp.lm_head_indices.long()]
+        if self.keep_hidden:
+            self.last_hidden = hidden          # rows match the returned logits (Medusa heads read them)
         return self.lm_head_forward(hidden, inp)
 
     def lm_head_forward(self, hidden: torch.Tensor, inp: StepInputs) -> torch.Tensor:

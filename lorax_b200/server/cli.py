@@ -40,9 +40,7 @@ def serve(args):
     _log("INFO", f"loading {args.model_id} on rank {tp.rank}/{tp.world_size}", args.json_output)
     rt = build_runtime(args.model_id, cfg, tp=tp, dtype=dtype, source=args.source, revision=args.revision, device=args.device)
     if args.adapter_id:
-        req = rt.pb.LoadAdapterRequest(adapter_parameters=rt.pb.AdapterParameters(adapter_ids=[args.adapter_id]),
-                                       adapter_source={"hub": 0, "s3": 1, "local": 2, "pbase": 3}[args.adapter_source], adapter_index=1)
-        rt.load_adapter(req)
+        rt.load_default_adapter(args.adapter_id, {"hub": 0, "s3": 1, "local": 2, "pbase": 3}[args.adapter_source])
     framed = FramedServer(rt, f"{args.uds_path}-{tp.rank}.lx").start()
     _log("INFO", f"Server started at unix://{args.uds_path}-{tp.rank}", args.json_output)
 

@@ -15,12 +15,14 @@ import os
 import threading
 import time
 from dataclasses import dataclass, field
+from types import SimpleNamespace
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
 from ..adapters.lora import LoraConfig, load_peft_adapter
 from ..adapters.manager import AdapterManager
+from ..adapters.medusa import MedusaHeads, is_medusa_dir, load_medusa_adapter
 from ..adapters.merges import merge_adapters
 from ..config import EngineConfig, ModelConfig
 from ..models.decoder import DecoderModel
@@ -74,6 +76,8 @@ class SeqState:
     output_text: str = ""
     grammar: Optional[object] = None
     seed: int = 0
+    spec_next: Optional[List[int]] = None        # Medusa guesses for the tokens after the last emitted one
+    medusa_index: int = 0                        # whose heads guess for this request (0 = the default heads)
 
 
 class ShardRuntime:
@@ -114,6 +118,10 @@ class ShardRuntime:
         self.downloaded: Dict[str, Tuple[LoraConfig, object]] = {}
         self.lock = threading.Lock()
         self.spec_stats = {"steps": 0, "tokens": 0}          # speculative decoding: row-steps and tokens they produced
+        # Medusa heads: pinned host copies by adapter key, device copies by adapter index (0 = the default adapter, applied to
+        # every request whose own adapter has no heads)
+        self.medusa_host: Dict[str, tuple] = {}
+        self.medusa: Dict[int, "MedusaHeads"] = {}
         self.fused_stats = {"one_pass": 0, "two_pass": 0}    # fused Prefill + Decode requests served in one / two forward passes
 
     # ------------------------------------------------------------------ info / health
@@ -180,6 +188,14 @@ class ShardRuntime:
             if aid in ("", "__base_model__"):
                 continue
             path = resolve_adapter(aid, src_name, api_token=req.api_token if req.HasField("api_token") else None)
+            if is_medusa_dir(path):
+                if len(params.adapter_ids) > 1:
+                    raise ValueError("Medusa adapters cannot be merged with other adapters")
+                self.medusa_host[key] = load_medusa_adapter(path)
+                if not os.path.exists(os.path.join(path, "adapter_config.json")):           # heads only, no LoRA part
+                    total = torch.cuda.get_device_properties(self.model.device).total_memory if self.model.device.type == "cuda" else 1 << 40
+                    nbytes = sum(v.numel() * 2 for v in self.medusa_host[key][1].values())
+                    return pb.DownloadAdapterResponse(downloaded=True, memory_fraction=nbytes / (total * max(self.cfg.adapter_memory_fraction, 1e-6)))
             loaded.append(load_peft_adapter(path))
         if not loaded:
             return pb.DownloadAdapterResponse(downloaded=False, memory_fraction=0.0)
@@ -194,15 +210,66 @@ class ShardRuntime:
 
     def load_adapter(self, req):
         key = self._adapter_key(req.adapter_parameters, req.adapter_source)
-        if self.adapters.host.get(key) is None:
+        if self.adapters.host.get(key) is None and key not in self.medusa_host:
             self.download_adapter(self.pb.DownloadAdapterRequest(adapter_parameters=req.adapter_parameters, adapter_source=req.adapter_source))
+        if key in self.medusa_host:
+            self.load_medusa(req.adapter_index, *self.medusa_host[key])
+            if self.adapters.host.get(key) is None:          # heads only; a Medusa + LoRA adapter goes on below
+                return self.pb.LoadAdapterResponse(loaded=True)
         ok = self.adapters.load(req.adapter_index, key)
         if not ok:
             raise RuntimeError(f"adapter {key} does not fit in the adapter memory reservation")
         return self.pb.LoadAdapterResponse(loaded=True)
 
     def offload_adapter(self, req):
-        return self.pb.OffloadAdapterResponse(offloaded=self.adapters.offload(req.adapter_index))
+        had_heads = self.medusa.pop(req.adapter_index, None) is not None if req.adapter_index != 0 else False
+        return self.pb.OffloadAdapterResponse(offloaded=self.adapters.offload(req.adapter_index) or had_heads)
+
+    def load_default_adapter(self, adapter_id: str, source: int = 0):
+        """The adapter named on the command line: a LoRA goes to adapter index 1; Medusa heads become the default heads
+        (index 0), which also turns speculation on with one token per head."""
+        pb = self.pb
+        params = pb.AdapterParameters(adapter_ids=[adapter_id])
+        self.download_adapter(pb.DownloadAdapterRequest(adapter_parameters=params, adapter_source=source))
+        key = self._adapter_key(params, source)
+        if key in self.medusa_host:
+            self.load_medusa(0, *self.medusa_host[key])
+        if self.adapters.host.get(key) is not None:
+            self.load_adapter(pb.LoadAdapterRequest(adapter_parameters=params, adapter_source=source, adapter_index=1))
+
+    def load_medusa(self, adapter_index: int, config, tensors):
+        """Put Medusa heads on the device under `adapter_index` (0 = default heads for every request).  As in the reference
+        (adapters/medusa.py:52-71) heads loaded at request time need speculation to be on and must not have more heads than
+        the configured number of speculative tokens; the first heads loaded as index 0 turn speculation on."""
+        heads = MedusaHeads(config, tensors, self.model.device, self.model.dtype)
+        if adapter_index == 0 and self.cfg.speculative_tokens == 0:
+            self.cfg.speculative_tokens = heads.num_heads
+        if self.cfg.speculative_tokens == 0:
+            raise ValueError("Medusa adapters can only be loaded at request time when the server was started with speculation on "
+                             "(a default Medusa adapter or --speculative-tokens)")
+        if heads.num_heads > self.cfg.speculative_tokens and adapter_index != 0:
+            raise ValueError(f"cannot load a Medusa adapter with {heads.num_heads} heads: the server speculates "
+                             f"{self.cfg.speculative_tokens} tokens")
+        self.medusa[adapter_index] = heads
+        self.model.keep_hidden = True
+
+    def _medusa_guess(self, seqs: List[SeqState], hidden: torch.Tensor):
+        """Fill `spec_next` of every sequence from the hidden state (one row per sequence) that produced its last token."""
+        if not self.medusa:
+            return
+        groups: Dict[int, List[int]] = {}
+        for i, s in enumerate(seqs):
+            idx = s.medusa_index if s.medusa_index in self.medusa else 0
+            if idx in self.medusa:
+                groups.setdefault(idx, []).append(i)
+            else:
+                s.spec_next = None
+        inp = SimpleNamespace(head_tok_slot=None, local_logits=False)
+        for idx, members in groups.items():
+            rows = hidden.index_select(0, torch.tensor(members, device=hidden.device))
+            guesses = self.medusa[idx].propose(rows, lambda x: self.model.lm_head_forward(x, inp)).tolist()
+            for i, gs in zip(members, guesses):
+                seqs[i].spec_next = [int(t) for t in gs]
 
     # ------------------------------------------------------------------ batches
     def clear_cache(self, req):
@@ -311,13 +378,18 @@ class ShardRuntime:
             h = s.prompt_ids + s.output_ids
             room = len(s.blocks) * page - len(h) - 1                 # slots left after the token that must be written anyway
             want = max(0, min(n_spec, room, s.stopping.max_new_tokens - len(s.output_ids) - 1))
-            hist = torch.tensor([h], dtype=torch.long)
-            cand = ngram_speculate(hist, [len(h)], [h[-1]], want)[0].tolist() if want > 0 else []
+            if want > 0 and s.spec_next:                            # Medusa heads guessed after the previous pass
+                cand = list(s.spec_next[:want])
+            elif want > 0:
+                hist = torch.tensor([h], dtype=torch.long)
+                cand = ngram_speculate(hist, [len(h)], [h[-1]], want)[0].tolist()
+            else:
+                cand = []
             props.append(cand)
             items.append(PrefillItem([h[-1]] + cand, len(h) - 1, list(s.blocks), s.adapter_index, all_logprobs=True))
         next_ids, lps, _ = self.runner.prefill(items)
         ids_h, lps_h = next_ids.tolist(), lps.tolist()
-        out, o = [], 0
+        out, o, last_rows = [], 0, []
         for s, cand in zip(seqs, props):
             n = 1 + len(cand)
             toks, tlps = [int(ids_h[o])], [float(lps_h[o])]
@@ -327,7 +399,10 @@ class ShardRuntime:
                 toks.append(int(ids_h[o + j + 1]))
                 tlps.append(float(lps_h[o + j + 1]))
             out.append((toks, tlps))
+            last_rows.append(o + len(toks) - 1)                     # the position whose arg-max is the last token kept
             o += n
+        if self.medusa and self.model.last_hidden is not None:
+            self._medusa_guess(seqs, self.model.last_hidden.index_select(0, torch.tensor(last_rows, device=self.model.last_hidden.device)))
         return out
 
     def _tok_text(self, tid: int) -> str:
@@ -387,13 +462,17 @@ class ShardRuntime:
             params = self._params_from_pb(r.parameters)
             stopping = StoppingCriteria(r.stopping_parameters.max_new_tokens or 1, self.eos_ids, list(r.stopping_parameters.stop_sequences),
                                         r.stopping_parameters.ignore_eos_token)
+            lora_index = r.adapter_index
             if r.adapter_index != 0 and not self.adapters.is_loaded(r.adapter_index):
-                raise RuntimeError(f"adapter index {r.adapter_index} is not loaded on this shard")
-            s = SeqState(r.id, batch.id, ids, list(r.blocks), r.adapter_index, params, stopping, Detokenizer(self.tokenizer, ids), seed=params.seed)
+                if r.adapter_index not in self.medusa:
+                    raise RuntimeError(f"adapter index {r.adapter_index} is not loaded on this shard")
+                lora_index = 0                                      # Medusa heads only: the base model's weights
+            s = SeqState(r.id, batch.id, ids, list(r.blocks), lora_index, params, stopping, Detokenizer(self.tokenizer, ids), seed=params.seed,
+                         medusa_index=r.adapter_index)
             if params.schema:
                 s.grammar = compile_schema(params.schema, self.tokenizer, self.eos_ids)
             seqs.append(s)
-            items.append(PrefillItem(ids[r.cache_len:] if r.cache_len else ids, r.cache_len, list(r.blocks), r.adapter_index,
+            items.append(PrefillItem(ids[r.cache_len:] if r.cache_len else ids, r.cache_len, list(r.blocks), lora_index,
                                      all_logprobs=r.prefill_logprobs))
         return seqs, items
 
@@ -413,6 +492,8 @@ class ShardRuntime:
         glp = lps.index_select(0, last_rows).tolist()
         # (a fused prefill + decode pass keeps no logits: it is only taken when every request is plain greedy)
         ids_l, lps_l, alts = self._sample_rows(seqs, logits.index_select(0, last_rows) if logits is not None else None, gid, glp)
+        if self.medusa and self.model.last_hidden is not None and self.model.last_hidden.shape[0] == next_ids.shape[0]:
+            self._medusa_guess(seqs, self.model.last_hidden.index_select(0, last_rows))
         gens, live, rows, firsts, poss, blks, ads = [], [], [], [], [], [], []
         o = 0
         for s, it, tok, lp, alt in zip(seqs, items, ids_l, lps_l, alts):

@@ -74,8 +74,9 @@ def resolve_model(model_id: str, source: str = HUB, revision: Optional[str] = No
 
 def resolve_adapter(adapter_id: str, source: str = HUB, api_token: Optional[str] = None, revision: Optional[str] = None) -> str:
     if os.path.isdir(adapter_id):
-        if not os.path.exists(os.path.join(adapter_id, "adapter_config.json")):
-            raise SourceError(f"{adapter_id} has no adapter_config.json")
+        medusa = any(os.path.exists(os.path.join(adapter_id, f)) for f in ("medusa_lm_head.safetensors", "medusa_lm_head.pt"))
+        if not os.path.exists(os.path.join(adapter_id, "adapter_config.json")) and not medusa:
+            raise SourceError(f"{adapter_id} has neither adapter_config.json (LoRA) nor medusa_lm_head.* (Medusa)")
         return adapter_id
     if source == LOCAL:
         raise SourceError(f"local adapter directory {adapter_id} does not exist")
@@ -90,4 +91,4 @@ def resolve_adapter(adapter_id: str, source: str = HUB, api_token: Optional[str]
         r = requests.get(f"{gateway}/v2/repos/{name}/version/{version or 'latest'}", headers={"Authorization": f"Bearer {api_token}"}, timeout=30)
         r.raise_for_status()
         return _s3_sync(r.json()["adapterPath"])
-    return _hub_snapshot(adapter_id, revision, api_token, ["adapter_config.json", "adapter_model.*", "tokenizer*", "config.json"])
+    return _hub_snapshot(adapter_id, revision, api_token, ["adapter_config.json", "adapter_model.*", "tokenizer*", "config.json", "medusa_lm_head.*"])
