@@ -65,8 +65,16 @@ class ModelConfig:
     partial_rotary_factor: float = 1.0
     # parallel attention+mlp blocks (falcon, neox, phi, cohere)
     parallel_residual: bool = False
-    # learned absolute positions (gpt2, bigcode)
+    # learned absolute positions (gpt2, bigcode, opt); OPT's table starts at position_offset = 2
     learned_positions: bool = False
+    position_offset: int = 0
+    # ALiBi instead of any position embedding (bloom, mpt): bias -slope_h * distance on the attention scores
+    alibi: bool = False
+    alibi_bias_max: float = 8.0
+    # LayerNorm right after the embedding lookup (bloom)
+    embed_norm: bool = False
+    # clamp of the fused QKV projection's output (mpt, dbrx)
+    clip_qkv: Optional[float] = None
     eos_token_id: Any = None
     bos_token_id: Any = None
     pad_token_id: Any = None
@@ -153,6 +161,35 @@ class ModelConfig:
             kw.setdefault("attention_bias", True)
         if mt == "granite":
             kw.setdefault("embedding_multiplier", d.get("embedding_multiplier", 1.0))
+        if mt == "bloom":
+            kw.update(norm_type="layernorm", alibi=True, embed_norm=True, attention_bias=True, mlp_bias=True, hidden_act="gelu_tanh",
+                      tie_word_embeddings=True, hidden_size=d.get("hidden_size", d.get("n_embed", 4096)))
+            kw["intermediate_size"] = 4 * kw["hidden_size"]
+            kw.setdefault("max_position_embeddings", d.get("seq_length", 2048))
+        if mt == "mpt":
+            attn = d.get("attn_config", {}) or {}
+            no_bias = d.get("no_bias", True)
+            kw.update(hidden_size=d["d_model"], num_hidden_layers=d["n_layers"], num_attention_heads=d["n_heads"],
+                      intermediate_size=int(d.get("expansion_ratio", 4) * d["d_model"]), max_position_embeddings=d.get("max_seq_len", 2048),
+                      norm_type="layernorm_nobias" if no_bias else "layernorm", attention_bias=not no_bias, mlp_bias=not no_bias,
+                      hidden_act="gelu", alibi=bool(attn.get("alibi", True)), alibi_bias_max=float(attn.get("alibi_bias_max", 8)),
+                      clip_qkv=attn.get("clip_qkv"), learned_positions=not attn.get("alibi", True), tie_word_embeddings=True,
+                      rms_norm_eps=d.get("layer_norm_epsilon", 1e-5))
+            if attn.get("qk_ln"):
+                raise NotImplementedError("mpt with qk_ln")
+            ls = d.get("logit_scale")
+            kw["logit_scale"] = 1.0 if ls is None else (float(d["d_model"]) ** -0.5 if ls == "inv_sqrt_d_model" else float(ls))
+        if mt == "opt":
+            if d.get("word_embed_proj_dim", d["hidden_size"]) != d["hidden_size"] or not d.get("do_layer_norm_before", True):
+                raise NotImplementedError("opt with a projected embedding or post-layer-norm blocks (opt-350m)")
+            kw.update(norm_type="layernorm", learned_positions=True, position_offset=2, attention_bias=d.get("enable_bias", True),
+                      mlp_bias=d.get("enable_bias", True), hidden_act=d.get("activation_function", "relu"), intermediate_size=d["ffn_dim"],
+                      tie_word_embeddings=d.get("tie_word_embeddings", True))
+        if mt == "qwen":
+            # first-generation Qwen: intermediate_size counts both halves of the gated MLP; fused c_attn with bias
+            kw.update(intermediate_size=d["intermediate_size"] // 2, attention_bias=True, head_dim=d.get("kv_channels"),
+                      max_position_embeddings=d.get("seq_length", d.get("max_position_embeddings", 8192)),
+                      tie_word_embeddings=d.get("tie_word_embeddings", False))
         if mt == "dbrx":
             ffn = d.get("ffn_config", {})
             attn = d.get("attn_config", {})
@@ -160,7 +197,7 @@ class ModelConfig:
                       num_key_value_heads=attn.get("kv_n_heads", d["n_heads"]),
                       intermediate_size=ffn.get("ffn_hidden_size", 4 * d["d_model"]),
                       num_local_experts=ffn.get("moe_num_experts", 0), num_experts_per_tok=ffn.get("moe_top_k", 0),
-                      rope_theta=attn.get("rope_theta", 10000.0), norm_type="layernorm_nobias",
+                      rope_theta=attn.get("rope_theta", 10000.0), norm_type="layernorm_nobias", clip_qkv=attn.get("clip_qkv"),
                       max_position_embeddings=d.get("max_seq_len", 2048))
         kw["model_type"] = mt
         kw["extra"] = extra

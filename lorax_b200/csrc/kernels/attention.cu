@@ -95,7 +95,8 @@ LX_DEVICE void pv_tile(float (&oacc)[D / 8][4], const float (&sacc)[NKEYS / 8][4
 // products on entry and probabilities on exit.  key0 = index of column 0; keys outside [lo, hi) are masked.
 template <int D, int NKEYS>
 LX_DEVICE void softmax_tile(float (&sacc)[NKEYS / 8][4], float (&oacc)[D / 8][4], float (&m)[2], float (&l)[2], int key0,
-                            int lo0, int hi0, int lo1, int hi1, float scale, float softcap, int lane) {
+                            int lo0, int hi0, int lo1, int hi1, float scale, float softcap, int lane, float slope0 = 0.f,
+                            float slope1 = 0.f) {
   float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
   for (int nt = 0; nt < NKEYS / 8; ++nt) {
@@ -105,6 +106,9 @@ LX_DEVICE void softmax_tile(float (&sacc)[NKEYS / 8][4], float (&oacc)[D / 8][4]
       const int r = q >> 1;
       float s = sacc[nt][q] * scale;
       if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+      // ALiBi: the bias -slope * (query position - key position) differs from slope * key position by a per-row constant,
+      // which the softmax does not see
+      s += (r == 0 ? slope0 : slope1) * (float)key;
       const bool ok = r == 0 ? (key >= lo0 && key < hi0) : (key >= lo1 && key < hi1);
       s = ok ? s : -INFINITY;
       sacc[nt][q] = s;
@@ -159,6 +163,7 @@ struct DecodeParams {
   int window;                 // <= 0: none
   float scale, softcap;
   int nsplit;
+  const float* alibi;         // [nh] ALiBi slopes, or null
 };
 
 template <int D, int STAGES>
@@ -209,6 +214,12 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
 
   const uint32_t wbase = smem_u32(dsm) + warp * STAGES * STAGE;
   const int* bt = p.block_tables + (long long)t * p.max_blocks;
+  float slope0 = 0.f, slope1 = 0.f;
+  if (p.alibi != nullptr) {
+    const int r0 = lane >> 2, r1 = r0 + 8;
+    slope0 = r0 < grows ? p.alibi[head0 + r0] : 0.f;
+    slope1 = r1 < grows ? p.alibi[head0 + r1] : 0.f;
+  }
   const int my_first = pb + warp;
   const int my_count = my_first < pe ? (pe - my_first + 3) / 4 : 0;
 
@@ -234,7 +245,7 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
     const int page = my_first + 4 * i;
     float sacc[kPage / 8][4];
     qk_tile<D, kPage>(sacc, qf, sb, lane);
-    softmax_tile<D, kPage>(sacc, oacc, m, l, page * kPage, key_lo, ctx, key_lo, ctx, p.scale, p.softcap, lane);
+    softmax_tile<D, kPage>(sacc, oacc, m, l, page * kPage, key_lo, ctx, key_lo, ctx, p.scale, p.softcap, lane, slope0, slope1);
     pv_tile<D, kPage>(oacc, sacc, sb + PLANE, lane);
     __syncwarp();
   }
@@ -326,6 +337,7 @@ struct PrefillParams {
   int nh, nkv;
   int window;
   float scale, softcap;
+  const float* alibi;         // [nh] ALiBi slopes, or null
 };
 
 template <int D>
@@ -394,6 +406,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillParams p
   float oacc[D / 8][4];
 #pragma unroll
   for (int i = 0; i < D / 8; ++i) { oacc[i][0] = oacc[i][1] = oacc[i][2] = oacc[i][3] = 0.f; }
+  const float slope = p.alibi != nullptr ? p.alibi[head] : 0.f;
 
   issue(t_lo);
   for (int kt = t_lo; kt < t_hi; ++kt) {
@@ -405,7 +418,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillParams p
     for (int h = 0; h < 2; ++h) {
       float sacc[kPage / 8][4];
       qk_tile<D, kPage>(sacc, qf, sb + h * PLANE, lane);
-      softmax_tile<D, kPage>(sacc, oacc, m, l, kt * KT + h * kPage, lo0, hi0, lo1, hi1, p.scale, p.softcap, lane);
+      softmax_tile<D, kPage>(sacc, oacc, m, l, kt * KT + h * kPage, lo0, hi0, lo1, hi1, p.scale, p.softcap, lane, slope, slope);
       pv_tile<D, kPage>(oacc, sacc, sb + (2 + h) * PLANE, lane);
     }
     __syncthreads();
@@ -468,9 +481,24 @@ extern "C" {
 int lx_attn_page_size() { return lx::kPage; }
 
 // part_o / part_lse are only touched when nsplit > 1: sizes T*nh*nsplit*D and T*nh*nsplit floats.
+int lx_attn_decode_alibi(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* ctx_lens,
+                         void* out, long long ldo, float* part_o, float* part_lse, int T, int nh, int nkv, int d, int window, float scale,
+                         float softcap, int nsplit, const float* alibi, void* stream);
+int lx_attn_prefill_alibi(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
+                          const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
+                          int nkv, int d, int window, float scale, float softcap, const float* alibi, void* stream);
+
 int lx_attn_decode(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* ctx_lens,
                    void* out, long long ldo, float* part_o, float* part_lse, int T, int nh, int nkv, int d, int window, float scale,
                    float softcap, int nsplit, void* stream) {
+  return lx_attn_decode_alibi(q, ldq, kv, block_tables, max_blocks, ctx_lens, out, ldo, part_o, part_lse, T, nh, nkv, d, window, scale,
+                              softcap, nsplit, nullptr, stream);
+}
+
+// `alibi`: [nh] fp32 slopes on the device (BLOOM, MPT), or null.
+int lx_attn_decode_alibi(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* ctx_lens,
+                         void* out, long long ldo, float* part_o, float* part_lse, int T, int nh, int nkv, int d, int window, float scale,
+                         float softcap, int nsplit, const float* alibi, void* stream) {
   using namespace lx;
   if (T <= 0) return 0;
   if (nh % nkv != 0) return -1;
@@ -481,7 +509,7 @@ int lx_attn_decode(const void* q, long long ldq, const void* kv, const int* bloc
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
   p.part_o = part_o; p.part_lse = part_lse;
   p.nh = nh; p.nkv = nkv; p.group = nh / nkv; p.gchunks = (p.group + 15) / 16;
-  p.window = window; p.scale = scale; p.softcap = softcap;
+  p.window = window; p.scale = scale; p.softcap = softcap; p.alibi = alibi;
   p.nsplit = nsplit < 1 ? 1 : nsplit;
   if (p.nsplit > 1 && (part_o == nullptr || part_lse == nullptr)) return -2;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -493,6 +521,13 @@ int lx_attn_decode(const void* q, long long ldq, const void* kv, const int* bloc
 int lx_attn_prefill(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
                     const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
                     int nkv, int d, int window, float scale, float softcap, void* stream) {
+  return lx_attn_prefill_alibi(q, ldq, kv, block_tables, max_blocks, cu_q, cache_lens, tile_seq, tile_q0, num_tiles, out, ldo, nh, nkv, d,
+                               window, scale, softcap, nullptr, stream);
+}
+
+int lx_attn_prefill_alibi(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
+                          const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
+                          int nkv, int d, int window, float scale, float softcap, const float* alibi, void* stream) {
   using namespace lx;
   if (num_tiles <= 0) return 0;
   if (nh % nkv != 0) return -1;
@@ -502,7 +537,7 @@ int lx_attn_prefill(const void* q, long long ldq, const void* kv, const int* blo
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.cu_q = cu_q; p.cache_lens = cache_lens;
   p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
-  p.nh = nh; p.nkv = nkv; p.window = window; p.scale = scale; p.softcap = softcap;
+  p.nh = nh; p.nkv = nkv; p.window = window; p.scale = scale; p.softcap = softcap; p.alibi = alibi;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (d == 128) return launch_prefill<128>(p, num_tiles, s);
   if (d == 64) return launch_prefill<64>(p, num_tiles, s);

@@ -30,6 +30,23 @@ from ..utils.weights import AbstractWeights
 GROUPS = ("qkv", "o", "gate_up", "down")
 
 
+def alibi_slopes(n_heads: int, bias_max: float = 8.0, interleave: bool = False) -> torch.Tensor:
+    """ALiBi slopes [n_heads] fp32.  Powers of two: slope_i = 2^(-bias_max * i / n), i = 1..n.  Otherwise BLOOM appends the odd
+    powers of the next finer base to those of the largest power of two below n (modeling_bloom.py: build_alibi_tensor), and MPT
+    (`interleave`) takes the slopes of the next power of two above n, odd positions first."""
+    import math
+    if interleave:
+        m = 2 ** math.ceil(math.log2(n_heads))
+        s = torch.pow(2.0, -torch.arange(1, m + 1, dtype=torch.float32) * (bias_max / m))
+        return (torch.cat([s[1::2], s[::2]])[:n_heads] if m != n_heads else s).contiguous()
+    m = 2 ** math.floor(math.log2(n_heads))
+    s = torch.pow(2.0, -torch.arange(1, m + 1, dtype=torch.float32) * (bias_max / m))
+    if m < n_heads:
+        extra = torch.pow(2.0, -torch.arange(1, 2 * (n_heads - m), 2, dtype=torch.float32) * (bias_max / (2 * m)))
+        s = torch.cat([s, extra])
+    return s.contiguous()
+
+
 @dataclass
 class Fp8Weight:
     """A projection matrix in block-scaled fp8: e4m3 values [N, K] and one fp32 scale per 128 x 128 block."""
@@ -114,6 +131,9 @@ class DecoderModel:
         self.layers: List[LayerWeights] = []
         self.embed: Optional[torch.Tensor] = None
         self.pos_embed: Optional[torch.Tensor] = None
+        self.embed_norm: Optional[torch.Tensor] = None          # BLOOM normalises the embeddings
+        self.embed_norm_b: Optional[torch.Tensor] = None
+        self.alibi_slopes: Optional[torch.Tensor] = None        # [local heads] fp32 (BLOOM, MPT)
         self.final_norm: Optional[torch.Tensor] = None
         self.final_norm_b: Optional[torch.Tensor] = None
         self.lm_head: Optional[torch.Tensor] = None
@@ -129,7 +149,11 @@ class DecoderModel:
         # LoRA expand inside the GEMM epilogue instead of its own launch (slower than the separate kernel at present:
         # four epilogue warps cannot hide the latency of the per-token B rows)
         self.fused_lora_epilogue = os.environ.get("LORAX_FUSED_LORA_EPILOGUE", "0") == "1"
-        self.gated = c.model_type not in ("gpt2", "gpt_bigcode", "gpt_neox", "falcon", "RefinedWeb", "RefinedWebModel", "phi")
+        self.gated = c.model_type not in ("gpt2", "gpt_bigcode", "gpt_neox", "falcon", "RefinedWeb", "RefinedWebModel", "phi", "bloom",
+                                          "mpt", "opt")
+        if c.alibi:
+            full = alibi_slopes(c.num_attention_heads, c.alibi_bias_max, interleave=c.model_type == "mpt")
+            self.alibi_slopes = full[self.tp.rank * self.nh:(self.tp.rank + 1) * self.nh].to(self.device).contiguous()
 
     # ------------------------------------------------------------------ shapes
     @property
@@ -186,7 +210,9 @@ class DecoderModel:
         emb = rnd(c.vocab_size, H)
         m.embed = put(emb if ws == 1 else _pad_rows(emb, m.vocab_local * ws)[m.vocab_start:m.vocab_start + m.vocab_local])
         if c.learned_positions:
-            m.pos_embed = put(rnd(c.max_position_embeddings, H))
+            m.pos_embed = put(rnd(c.max_position_embeddings + c.position_offset, H))
+        if c.embed_norm:
+            m.embed_norm, m.embed_norm_b = put(torch.ones(H) + rnd(H, s=0.01)), put(rnd(H, s=0.01))
         ln = c.norm_type.startswith("layernorm")
         has_ln_bias = c.norm_type == "layernorm"
         for _ in range(c.num_hidden_layers):
@@ -409,7 +435,9 @@ class DecoderModel:
             if self.tp.world_size > 1:
                 h = self.tp.all_reduce(h)
         if self.pos_embed is not None:
-            h = h + self.pos_embed[inp.positions.long()]
+            h = h + self.pos_embed[inp.positions.long() + c.position_offset]
+        if self.embed_norm is not None:
+            h = self._norm(h, None, self.embed_norm, self.embed_norm_b)
         residual = h
         pending = None      # output of the previous block that still has to be added to the residual stream
         rm = c.residual_multiplier
@@ -460,8 +488,11 @@ class DecoderModel:
     def _attention(self, x, lw: LayerWeights, li: int, inp: StepInputs, kv: torch.Tensor):
         c, ops = self.config, self.ops
         qkv = self._linear(x, lw.qkv_w, lw.qkv_b, "qkv", li, inp)
+        if c.clip_qkv:
+            qkv.clamp_(-c.clip_qkv, c.clip_qkv)
         ops.rope_kvwrite(qkv, inp.positions, self.cos_sin, kv, inp.slots, self.nh, self.nkv, self.d, c.rotary_dim,
-                         not c.learned_positions)
+                         not (c.learned_positions or c.alibi))
+        ali = {"alibi": self.alibi_slopes} if self.alibi_slopes is not None else {}
         window = c.sliding_window or 0
         if c.model_type == "gemma2" and li % 2 == 1:
             window = 0
@@ -470,18 +501,18 @@ class DecoderModel:
             nd = inp.n_decode
             attn = torch.empty(qkv.shape[0], self.nh * self.d, dtype=qkv.dtype, device=qkv.device)
             a = ops.attn_decode(qkv[:nd], kv, inp.dec_block_tables, inp.ctx_lens, self.nh, self.nkv, self.d, c.attn_scale, window,
-                                softcap, inp.attn_nsplit, out=attn[:nd])
+                                softcap, inp.attn_nsplit, out=attn[:nd], **ali)
             b = ops.attn_prefill(qkv[nd:], kv, inp.block_tables, inp.cu_q, inp.cache_lens, inp.tile_seq, inp.tile_q0,
-                                 self.nh, self.nkv, self.d, c.attn_scale, window, softcap, out=attn[nd:])
+                                 self.nh, self.nkv, self.d, c.attn_scale, window, softcap, out=attn[nd:], **ali)
             if a.data_ptr() != attn.data_ptr():      # ops that ignore `out`
                 attn[:nd] = a
                 attn[nd:] = b
         elif inp.is_prefill:
             attn = ops.attn_prefill(qkv, kv, inp.block_tables, inp.cu_q, inp.cache_lens, inp.tile_seq, inp.tile_q0,
-                                    self.nh, self.nkv, self.d, c.attn_scale, window, softcap)
+                                    self.nh, self.nkv, self.d, c.attn_scale, window, softcap, **ali)
         else:
             attn = ops.attn_decode(qkv, kv, inp.block_tables, inp.ctx_lens, self.nh, self.nkv, self.d, c.attn_scale, window,
-                                   softcap, inp.attn_nsplit)
+                                   softcap, inp.attn_nsplit, **ali)
         return self._row_parallel(attn, lw.o_w, lw.o_b, "o", li, inp)
 
     def _mlp(self, x, lw: LayerWeights, li: int, inp: StepInputs):

@@ -53,7 +53,32 @@ NAME_MAPS: Dict[str, dict] = {
                         up="mlp.c_fc", down="mlp.c_proj", q=None, k=None, v=None, gate=None),
 }
 NAME_MAPS["RefinedWeb"] = NAME_MAPS["RefinedWebModel"] = NAME_MAPS["falcon"]
-NAME_MAPS["qwen"] = NAME_MAPS["qwen2"]
+NAME_MAPS.update({
+    # first-generation Qwen: fused c_attn (q | k | v) with bias, mlp.w2 is the gate, mlp.w1 the up projection
+    "qwen": dict(embed="transformer.wte.weight", final_norm="transformer.ln_f.weight", lm_head="lm_head.weight", layer="transformer.h.{i}.",
+                 input_norm="ln_1.weight", post_norm="ln_2.weight", qkv="attn.c_attn", o="attn.c_proj", gate="mlp.w2", up="mlp.w1",
+                 down="mlp.c_proj", q=None, k=None, v=None),
+    "bloom": dict(embed="word_embeddings.weight", embed_norm="word_embeddings_layernorm.weight", embed_norm_b="word_embeddings_layernorm.bias",
+                  final_norm="ln_f.weight", final_norm_b="ln_f.bias", lm_head=None, layer="h.{i}.", input_norm="input_layernorm.weight",
+                  input_norm_b="input_layernorm.bias", post_norm="post_attention_layernorm.weight",
+                  post_norm_b="post_attention_layernorm.bias", qkv="self_attention.query_key_value", o="self_attention.dense",
+                  up="mlp.dense_h_to_4h", down="mlp.dense_4h_to_h", qkv_interleaved=True, q=None, k=None, v=None, gate=None,
+                  prefixes=["transformer.", ""]),
+    "mpt": dict(embed="wte.weight", pos_embed="wpe.weight", final_norm="norm_f.weight", final_norm_b="norm_f.bias", lm_head=None,
+                layer="blocks.{i}.", input_norm="norm_1.weight", input_norm_b="norm_1.bias", post_norm="norm_2.weight",
+                post_norm_b="norm_2.bias", qkv="attn.Wqkv", o="attn.out_proj", up="ffn.up_proj", down="ffn.down_proj", q=None, k=None,
+                v=None, gate=None, prefixes=["transformer.", ""]),
+    "opt": dict(embed="decoder.embed_tokens.weight", pos_embed="decoder.embed_positions.weight", final_norm="decoder.final_layer_norm.weight",
+                final_norm_b="decoder.final_layer_norm.bias", lm_head=None, layer="decoder.layers.{i}.",
+                input_norm="self_attn_layer_norm.weight", input_norm_b="self_attn_layer_norm.bias", post_norm="final_layer_norm.weight",
+                post_norm_b="final_layer_norm.bias", q="self_attn.q_proj", k="self_attn.k_proj", v="self_attn.v_proj",
+                o="self_attn.out_proj", up="fc1", down="fc2", gate=None, prefixes=["model.", ""]),
+    # DBRX: fused Wqkv (clamped), LayerNorm without bias, experts stacked along rows: w1 / v1 / w2 are [E * I, H]
+    "dbrx": dict(embed="transformer.wte.weight", final_norm="transformer.norm_f.weight", lm_head="lm_head.weight",
+                 layer="transformer.blocks.{i}.", input_norm="norm_attn_norm.norm_1.weight", post_norm="norm_attn_norm.norm_2.weight",
+                 qkv="norm_attn_norm.attn.Wqkv", o="norm_attn_norm.attn.out_proj", router="ffn.router.layer.weight",
+                 experts_stacked="ffn.experts.mlp.", q=None, k=None, v=None, gate=None, up=None, down=None),
+})
 
 
 def _get(w: AbstractWeights, name: str, prefixes=("",)) -> Optional[torch.Tensor]:
@@ -145,8 +170,11 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
     else:
         emb_l = emb
     m.embed = fin(emb_l)
-    if nm.get("pos_embed"):
+    if nm.get("pos_embed") and c.learned_positions:
         m.pos_embed = fin(_need(w, nm["pos_embed"], pre))
+    if nm.get("embed_norm"):
+        m.embed_norm = fin(_need(w, nm["embed_norm"], pre))
+        m.embed_norm_b = fin(_get(w, nm["embed_norm_b"], pre))
     m.final_norm = fin(_need(w, nm["final_norm"], pre))
     if nm.get("final_norm_b"):
         m.final_norm_b = fin(_get(w, nm["final_norm_b"], pre))
@@ -193,7 +221,13 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
             lw.router_w = fin(_need(w, L + nm["router"], pre))
             E = c.num_local_experts
             w13, w2 = [], []
-            for e in range(E):
+            if nm.get("experts_stacked"):
+                P = L + nm["experts_stacked"]
+                I = c.intermediate_size
+                w1s, v1s, w2s = (dense(_need(w, P + n, pre)).view(E, I, -1) for n in ("w1", "v1", "w2"))
+                w13 = [torch.cat([w1s[e], v1s[e]], 0) for e in range(E)]
+                w2 = [w2s[e].t() for e in range(E)]
+            for e in range(E if not nm.get("experts_stacked") else 0):
                 P = L + nm["expert"].format(e=e)
                 w13.append(torch.cat([dense(_need(w, P + "w1.weight", pre)), dense(_need(w, P + "w3.weight", pre))], 0))
                 w2.append(dense(_need(w, P + "w2.weight", pre)))

@@ -68,6 +68,8 @@ def supported(model) -> bool:
         return False
     if c.is_moe or c.parallel_residual or model.pos_embed is not None or c.model_type == "gemma2" or model.fused_lora_epilogue:
         return False
+    if model.alibi_slopes is not None or c.clip_qkv or model.embed_norm is not None:
+        return False
     for lw in model.layers:
         if lw.post_norm is None or lw.gate_up_w is None or lw.down_w is None or lw.post_ffn_norm is not None:
             return False

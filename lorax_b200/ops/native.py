@@ -62,6 +62,8 @@ def load() -> ctypes.CDLL:
         "lx_attn_page_size": ([], I),
         "lx_attn_decode": ([P, L, P, P, I, P, P, L, P, P, I, I, I, I, I, F, F, I, P], I),
         "lx_attn_prefill": ([P, L, P, P, I, P, P, P, P, I, P, L, I, I, I, I, F, F, P], I),
+        "lx_attn_decode_alibi": ([P, L, P, P, I, P, P, L, P, P, I, I, I, I, I, F, F, I, P, P], I),
+        "lx_attn_prefill_alibi": ([P, L, P, P, I, P, P, P, P, I, P, L, I, I, I, I, F, F, P, P], I),
         "lx_lora_shrink": ([P, L, P, P, P, P, I, L, I, P, I, I, I, I, P, P], I),
         "lx_lora_expand": ([P, I, P, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
         "lx_tensormap_bytes": ([], I),
@@ -325,8 +327,8 @@ def advance_decode(input_ids, next_ids, positions, ctx_lens, slots, block_tables
 # ------------------------------------------------------------------------------------------------ attention
 def attn_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Tensor, ctx_lens: torch.Tensor, nh: int, nkv: int,
                 d: int, scale: float, window: int = 0, softcap: float = 0.0, nsplit: int = 1,
-                out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q: [T, >= nh*d] (row stride arbitrary), one query token per row.  Returns [T, nh*d]."""
+                out: Optional[torch.Tensor] = None, alibi: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q: [T, >= nh*d] (row stride arbitrary), one query token per row.  Returns [T, nh*d].  `alibi`: [nh] fp32 slopes."""
     T = q.shape[0]
     if out is None:
         out = torch.empty(T, nh * d, dtype=q.dtype, device=q.device)
@@ -335,22 +337,22 @@ def attn_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Ten
         nsplit = min(nsplit, ws.attn_splits)
         if T > ws.attn_part_tokens:
             nsplit = 1
-    rc = load().lx_attn_decode(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(ctx_lens),
-                               _ptr(out), out.stride(0), _ptr(ws.attn_part_o), _ptr(ws.attn_part_lse), T, nh, nkv, d, window,
-                               scale, softcap, nsplit, _stream())
+    rc = load().lx_attn_decode_alibi(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(ctx_lens),
+                                     _ptr(out), out.stride(0), _ptr(ws.attn_part_o), _ptr(ws.attn_part_lse), T, nh, nkv, d, window,
+                                     scale, softcap, nsplit, _ptr(alibi), _stream())
     _check(rc, "lx_attn_decode")
     return out
 
 
 def attn_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Tensor, cu_q: torch.Tensor, cache_lens: torch.Tensor,
                  tile_seq: torch.Tensor, tile_q0: torch.Tensor, nh: int, nkv: int, d: int, scale: float, window: int = 0,
-                 softcap: float = 0.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 softcap: float = 0.0, out: Optional[torch.Tensor] = None, alibi: Optional[torch.Tensor] = None) -> torch.Tensor:
     T = q.shape[0]
     if out is None:
         out = torch.empty(T, nh * d, dtype=q.dtype, device=q.device)
-    rc = load().lx_attn_prefill(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(cu_q),
-                                _ptr(cache_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0], _ptr(out), out.stride(0), nh,
-                                nkv, d, window, scale, softcap, _stream())
+    rc = load().lx_attn_prefill_alibi(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(cu_q),
+                                      _ptr(cache_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0], _ptr(out), out.stride(0), nh,
+                                      nkv, d, window, scale, softcap, _ptr(alibi), _stream())
     _check(rc, "lx_attn_prefill")
     return out
 

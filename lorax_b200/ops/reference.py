@@ -215,12 +215,16 @@ def _gather_kv(kv_cache, block_table, n_keys, kvh):
     return k, v
 
 
-def _attend(q, k, v, q_pos, scale, window, softcap):
-    """q: [nq, d] at absolute positions q_pos [nq]; k, v: [nk, d] at positions 0..nk-1."""
+def _attend(q, k, v, q_pos, scale, window, softcap, slope=None):
+    """q: [nq, d] at absolute positions q_pos [nq]; k, v: [nk, d] at positions 0..nk-1.  `slope` (scalar or [nq]) adds the
+    ALiBi bias -slope * (query position - key position)."""
     s = (q.float() @ k.float().t()) * scale
     if softcap and softcap > 0:
         s = softcap * torch.tanh(s / softcap)
     kp = torch.arange(k.shape[0], device=q.device)[None, :]
+    if slope is not None:
+        sl = slope if torch.is_tensor(slope) and slope.dim() else torch.as_tensor(slope, device=q.device).reshape(1)
+        s = s - sl.float().reshape(-1, 1) * (q_pos[:, None] - kp).float()
     mask = kp <= q_pos[:, None]
     if window and window > 0:
         mask &= kp > (q_pos[:, None] - window)
@@ -230,7 +234,7 @@ def _attend(q, k, v, q_pos, scale, window, softcap):
     return p @ v.float()
 
 
-def attn_decode(q, kv_cache, block_tables, ctx_lens, nh, nkv, d, scale, window=0, softcap=0.0, nsplit=1, out=None):
+def attn_decode(q, kv_cache, block_tables, ctx_lens, nh, nkv, d, scale, window=0, softcap=0.0, nsplit=1, out=None, alibi=None):
     T = q.shape[0]
     res = torch.zeros(T, nh * d, dtype=q.dtype, device=q.device)
     g = nh // nkv
@@ -241,7 +245,8 @@ def attn_decode(q, kv_cache, block_tables, ctx_lens, nh, nkv, d, scale, window=0
         for kvh in range(nkv):
             k, v = _gather_kv(kv_cache, block_tables[t], n, kvh)
             qh = q[t, kvh * g * d: (kvh + 1) * g * d].view(g, d)
-            o = _attend(qh, k, v, torch.full((g,), n - 1, device=q.device), scale, window, softcap)
+            o = _attend(qh, k, v, torch.full((g,), n - 1, device=q.device), scale, window, softcap,
+                        None if alibi is None else alibi[kvh * g: (kvh + 1) * g])
             res[t, kvh * g * d: (kvh + 1) * g * d] = o.reshape(-1).to(q.dtype)
     if out is not None:
         out.copy_(res)
@@ -250,7 +255,7 @@ def attn_decode(q, kv_cache, block_tables, ctx_lens, nh, nkv, d, scale, window=0
 
 
 def attn_prefill(q, kv_cache, block_tables, cu_q, cache_lens, tile_seq, tile_q0, nh, nkv, d, scale, window=0, softcap=0.0,
-                 out=None):
+                 out=None, alibi=None):
     T = q.shape[0]
     res = torch.zeros(T, nh * d, dtype=q.dtype, device=q.device)
     g = nh // nkv
@@ -266,7 +271,7 @@ def attn_prefill(q, kv_cache, block_tables, cu_q, cache_lens, tile_seq, tile_q0,
             k, v = _gather_kv(kv_cache, block_tables[b], n, kvh)
             for gi in range(g):
                 h = kvh * g + gi
-                o = _attend(q[s:e, h * d: (h + 1) * d], k, v, pos, scale, window, softcap)
+                o = _attend(q[s:e, h * d: (h + 1) * d], k, v, pos, scale, window, softcap, None if alibi is None else alibi[h])
                 res[s:e, h * d: (h + 1) * d] = o.to(q.dtype)
     if out is not None:
         out.copy_(res)

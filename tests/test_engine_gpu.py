@@ -180,3 +180,34 @@ def test_mixtral_moe_gpu_matches_cpu_oracle():
         assert err < 4e-2, (n, err)
     from lorax_b200.ops import native
     native.workspace().check_status()
+
+
+@pytest.mark.parametrize("family", ["bloom", "opt"])
+def test_alibi_and_learned_position_families_match_cpu_oracle(family):
+    """BLOOM (ALiBi, embedding LayerNorm, ungated GELU MLP) and OPT (learned positions with an offset, ReLU): prefill logits
+    and teacher-forced decode logits on the GPU kernels against the fp32 CPU path of the same weights."""
+    from lorax_b200.config import ModelConfig
+    if family == "bloom":
+        cfg = ModelConfig.from_dict({"model_type": "bloom", "vocab_size": 1000, "hidden_size": 256, "n_layer": 2, "n_head": 4,
+                                     "layer_norm_epsilon": 1e-5, "seq_length": 512})
+    else:
+        cfg = ModelConfig.from_dict({"model_type": "opt", "vocab_size": 1000, "hidden_size": 256, "ffn_dim": 512, "num_hidden_layers": 2,
+                                     "num_attention_heads": 4, "max_position_embeddings": 512, "word_embed_proj_dim": 256})
+    gm = DecoderModel.random_init(cfg, "cuda", torch.bfloat16, seed=4, std=0.05)
+    cm = DecoderModel.random_init(cfg, "cpu", torch.float32, seed=4, std=0.05)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 75)]
+    forced = torch.randint(0, cfg.vocab_size, (2,), generator=g).tolist()
+    outs = []
+    for m in (gm, cm):
+        kv = KVCache(cfg.num_hidden_layers, 32, m.nkv, m.d, m.dtype, m.device)
+        r = ModelRunner(m, kv, max_batch=4, max_seq_tokens=256, max_prefill_tokens=512, use_graphs=False)
+        blocks = [[1, 2, 3, 4], [5, 6, 7, 8]]
+        _, _, logits = r.prefill([PrefillItem(p, 0, b) for p, b in zip(prompts, blocks)])
+        # one more token per sequence through the cached-context path
+        _, _, step = r.prefill([PrefillItem([t], len(p), b) for t, p, b in zip(forced, prompts, blocks)])
+        outs.append(torch.cat([logits.float().cpu(), step.float().cpu()]))
+    from lorax_b200.ops import native
+    native.workspace().check_status()
+    err = (outs[0] - outs[1]).norm() / outs[1].norm()
+    assert err < 3e-2, err

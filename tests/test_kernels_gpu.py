@@ -216,6 +216,36 @@ def test_attn_prefill(nat, nh, nkv, d, window, cached):
     assert _rel_err(got, want) < 1e-2
 
 
+@pytest.mark.parametrize("nh,nkv,d,nsplit", [(12, 12, 64, 1), (32, 8, 128, 3), (6, 6, 128, 1)])
+def test_attn_alibi(nat, nh, nkv, d, nsplit):
+    """ALiBi slopes in both attention kernels (BLOOM, MPT): bias -slope_h * (query position - key position)."""
+    from lorax_b200.models.decoder import alibi_slopes
+    torch.manual_seed(15)
+    slopes = alibi_slopes(nh).cuda()
+    scale = d ** -0.5
+    B, max_len = 7, 500
+    cache, bt = _make_cache(B, max_len, nkv, d, seed=2)
+    ctx = torch.randint(1, max_len, (B,), device="cuda", dtype=torch.int32)
+    ctx[0], ctx[1] = 1, max_len
+    q = torch.randn(B, nh * d, device="cuda", dtype=torch.bfloat16)
+    got = nat.attn_decode(q, cache, bt, ctx, nh, nkv, d, scale, 0, 0.0, nsplit, alibi=slopes)
+    want = ref.attn_decode(q, cache, bt, ctx, nh, nkv, d, scale, alibi=slopes)
+    plain = ref.attn_decode(q, cache, bt, ctx, nh, nkv, d, scale)
+    assert _rel_err(got, want) < 1e-2 and _rel_err(plain, want) > 0.1
+    q_lens, cache_lens = [9, 150, 64], [0, 70, 33]
+    cache, bt = _make_cache(3, 256, nkv, d, seed=3)
+    T = sum(q_lens)
+    q = torch.randn(T, nh * d, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    cl = torch.tensor(cache_lens, device="cuda", dtype=torch.int32)
+    ts, tq = ref.prefill_tiles(q_lens)
+    ts = torch.tensor(ts, device="cuda", dtype=torch.int32)
+    tq = torch.tensor(tq, device="cuda", dtype=torch.int32)
+    got = nat.attn_prefill(q, cache, bt, cu, cl, ts, tq, nh, nkv, d, scale, alibi=slopes)
+    want = ref.attn_prefill(q, cache, bt, cu, cl, ts, tq, nh, nkv, d, scale, alibi=slopes)
+    assert _rel_err(got, want) < 1e-2
+
+
 @pytest.mark.parametrize("T", [3, 100, 700])
 def test_lora_shrink_expand(nat, T):
     torch.manual_seed(8)

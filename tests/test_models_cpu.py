@@ -205,3 +205,136 @@ def test_encoders_match_hf():
         conf, pred = p.max(-1)
         assert lab == [f"T{i}" for i in pred.tolist()]
         assert torch.allclose(torch.tensor(sc), conf, atol=2e-4)
+
+
+def _from_hf(hf, **over):
+    """Our decoder loaded from a HuggingFace model's own state dict and config."""
+    from lorax_b200.utils.weights import InMemoryWeights
+    d = hf.config.to_dict()
+    d.update(over)
+    cfg = ModelConfig.from_dict(d)
+    cfg.torch_dtype = "float32"
+    sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
+    return DecoderModel.from_weights(cfg, InMemoryWeights(sd, dtype=torch.float32), "cpu", torch.float32)
+
+
+def _check_against_hf(hf, model, vocab, n=23, tol=2e-3):
+    torch.manual_seed(1)
+    ids = torch.randint(0, vocab, (n,)).tolist()
+    with torch.no_grad():
+        want = hf(torch.tensor([ids])).logits[0]
+    got = _logits(model, ids)
+    assert got.shape == want.shape
+    assert (got - want).abs().max().item() < tol * max(1.0, want.abs().max().item()), (got - want).abs().max()
+
+
+def test_bloom_alibi_matches_hf():
+    """ALiBi bias in the attention scores, LayerNorm on the embeddings, interleaved fused QKV, 6 heads (not a power of two)."""
+    from transformers import BloomConfig, BloomForCausalLM
+    torch.manual_seed(0)
+    hc = BloomConfig(vocab_size=200, hidden_size=96, n_layer=2, n_head=6, layer_norm_epsilon=1e-5)
+    hc._attn_implementation = "eager"
+    hf = BloomForCausalLM(hc).eval()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.08)
+    m = _from_hf(hf)
+    assert m.alibi_slopes is not None and m.embed_norm is not None and m.alibi_slopes.shape[0] == 6
+    _check_against_hf(hf, m, 200)
+
+
+def test_mpt_alibi_matches_hf():
+    from transformers import MptConfig, MptForCausalLM
+    torch.manual_seed(0)
+    hc = MptConfig(d_model=64, n_heads=4, n_layers=2, expansion_ratio=4, max_seq_len=128, vocab_size=180, no_bias=True)
+    hc._attn_implementation = "eager"
+    hf = MptForCausalLM(hc).eval()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.08)
+    m = _from_hf(hf)
+    assert m.alibi_slopes is not None and m.pos_embed is None
+    _check_against_hf(hf, m, 180)
+
+
+def test_opt_matches_hf():
+    """Learned positions with OPT's offset of two, ReLU MLP, biased projections."""
+    from transformers import OPTConfig, OPTForCausalLM
+    torch.manual_seed(0)
+    hc = OPTConfig(vocab_size=190, hidden_size=64, ffn_dim=160, num_hidden_layers=2, num_attention_heads=4, max_position_embeddings=96,
+                   word_embed_proj_dim=64, do_layer_norm_before=True)
+    hc._attn_implementation = "eager"
+    hf = OPTForCausalLM(hc).eval()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.08)
+    m = _from_hf(hf)
+    assert m.pos_embed.shape[0] == 98 and m.config.hidden_act == "relu"
+    _check_against_hf(hf, m, 190)
+
+
+def test_qwen_v1_names_load_like_qwen2():
+    """First-generation Qwen checkpoints (fused c_attn with bias, mlp.w2 = gate, mlp.w1 = up) against a Qwen2 model holding the
+    same weights under its own names."""
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+    from lorax_b200.utils.weights import InMemoryWeights
+    torch.manual_seed(0)
+    hc = Qwen2Config(vocab_size=210, hidden_size=64, intermediate_size=112, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=4,
+                     max_position_embeddings=128, rope_theta=1e4, rms_norm_eps=1e-6, tie_word_embeddings=False, use_sliding_window=False)
+    hc._attn_implementation = "eager"
+    hf = Qwen2ForCausalLM(hc).eval()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.08)
+    sd = hf.state_dict()
+    q1 = {"transformer.wte.weight": sd["model.embed_tokens.weight"], "transformer.ln_f.weight": sd["model.norm.weight"],
+          "lm_head.weight": sd["lm_head.weight"]}
+    for i in range(2):
+        a, b = f"model.layers.{i}.", f"transformer.h.{i}."
+        q1[b + "ln_1.weight"] = sd[a + "input_layernorm.weight"]
+        q1[b + "ln_2.weight"] = sd[a + "post_attention_layernorm.weight"]
+        q1[b + "attn.c_attn.weight"] = torch.cat([sd[a + f"self_attn.{n}_proj.weight"] for n in "qkv"], 0)
+        q1[b + "attn.c_attn.bias"] = torch.cat([sd[a + f"self_attn.{n}_proj.bias"] for n in "qkv"], 0)
+        q1[b + "attn.c_proj.weight"] = sd[a + "self_attn.o_proj.weight"]
+        q1[b + "mlp.w2.weight"] = sd[a + "mlp.gate_proj.weight"]
+        q1[b + "mlp.w1.weight"] = sd[a + "mlp.up_proj.weight"]
+        q1[b + "mlp.c_proj.weight"] = sd[a + "mlp.down_proj.weight"]
+    cfg = ModelConfig.from_dict({"model_type": "qwen", "vocab_size": 210, "hidden_size": 64, "intermediate_size": 224, "num_hidden_layers": 2,
+                                 "num_attention_heads": 4, "kv_channels": 16, "layer_norm_epsilon": 1e-6, "rotary_emb_base": 1e4,
+                                 "seq_length": 128, "torch_dtype": "float32"})
+    assert cfg.intermediate_size == 112 and cfg.attention_bias
+    m = DecoderModel.from_weights(cfg, InMemoryWeights({k: v.detach().clone() for k, v in q1.items()}, dtype=torch.float32), "cpu", torch.float32)
+    _check_against_hf(hf, m, 210)
+
+
+def test_dbrx_names_load_like_mixtral():
+    """DBRX checkpoints (fused clamped Wqkv, LayerNorm without bias, experts stacked along rows as w1 / v1 / w2 of shape
+    [E * I, H]) against the same weights under Mixtral's per-expert names in a model with the same switches.  (The DBRX class of
+    the installed transformers multiplies by the untransposed expert matrices and only runs with I == H, so it is no oracle.)"""
+    from lorax_b200.utils.weights import InMemoryWeights
+    E, I, H = 4, 96, 64
+    base = dict(vocab_size=170, hidden_size=H, intermediate_size=I, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                head_dim=16, rope_theta=1e4, max_position_embeddings=128, num_local_experts=E, num_experts_per_tok=2, torch_dtype="float32",
+                norm_type="layernorm_nobias", clip_qkv=0.6)
+    mix = DecoderModel.random_init(ModelConfig(model_type="mixtral", **base), "cpu", torch.float32, seed=3, std=0.1)
+    sd = export_hf_state_dict(mix)
+    dsd = {"transformer.wte.weight": sd["model.embed_tokens.weight"], "transformer.norm_f.weight": sd["model.norm.weight"],
+           "lm_head.weight": sd["lm_head.weight"]}
+    for i in range(2):
+        a, b = f"model.layers.{i}.", f"transformer.blocks.{i}."
+        dsd[b + "norm_attn_norm.norm_1.weight"] = sd[a + "input_layernorm.weight"]
+        dsd[b + "norm_attn_norm.norm_2.weight"] = sd[a + "post_attention_layernorm.weight"]
+        dsd[b + "norm_attn_norm.attn.Wqkv.weight"] = torch.cat([sd[a + f"self_attn.{n}_proj.weight"] for n in "qkv"], 0)
+        dsd[b + "norm_attn_norm.attn.out_proj.weight"] = sd[a + "self_attn.o_proj.weight"]
+        dsd[b + "ffn.router.layer.weight"] = sd[a + "block_sparse_moe.gate.weight"]
+        ex = a + "block_sparse_moe.experts."
+        dsd[b + "ffn.experts.mlp.w1"] = torch.cat([sd[ex + f"{e}.w1.weight"] for e in range(E)], 0)
+        dsd[b + "ffn.experts.mlp.v1"] = torch.cat([sd[ex + f"{e}.w3.weight"] for e in range(E)], 0)
+        dsd[b + "ffn.experts.mlp.w2"] = torch.cat([sd[ex + f"{e}.w2.weight"].t() for e in range(E)], 0)
+    cfg = ModelConfig.from_dict({"model_type": "dbrx", "d_model": H, "n_heads": 4, "n_layers": 2, "max_seq_len": 128, "vocab_size": 170,
+                                 "attn_config": {"kv_n_heads": 2, "clip_qkv": 0.6, "rope_theta": 1e4},
+                                 "ffn_config": {"ffn_hidden_size": I, "moe_num_experts": E, "moe_top_k": 2}, "torch_dtype": "float32"})
+    assert cfg.clip_qkv == 0.6 and cfg.num_local_experts == E and cfg.norm_type == "layernorm_nobias"
+    dbrx = DecoderModel.from_weights(cfg, InMemoryWeights(dsd, dtype=torch.float32), "cpu", torch.float32)
+    ids = list(range(7, 40))
+    a, b = _logits(mix, ids), _logits(dbrx, ids)
+    assert torch.allclose(a, b, atol=1e-5)
+    # the clamp is live: without it the logits move
+    mix.config.clip_qkv = None
+    assert not torch.allclose(_logits(mix, ids), b, atol=1e-4)
