@@ -115,6 +115,7 @@ struct ValidRequest {
   gen::NextTokenChooserParameters parameters;
   gen::StoppingCriteriaParameters stopping;
   AdapterKey adapter;
+  std::string trace_id, span_id;         // the request's span (empty when tracing is off): batch spans link to it
 };
 
 struct Entry {

@@ -17,6 +17,7 @@
 #include "adapter_queues.hpp"
 #include "metrics.hpp"
 #include "shard_client.hpp"
+#include "telemetry.hpp"
 
 namespace lx {
 
@@ -47,6 +48,8 @@ struct ApiError : std::runtime_error {
 inline ApiError validation_error(const std::string& m) { return ApiError(m, "validation", 422); }
 
 struct GenerateParams {
+  std::string traceparent;                // the caller's W3C trace context (request header), if any
+  std::string trace_id, span_id;          // this request's own span, set by the router when tracing is on
   std::optional<std::string> adapter_id;
   std::optional<std::string> adapter_source;
   std::vector<std::string> merged_ids;
@@ -93,6 +96,15 @@ class Infer {
   }
   ~Infer() { stop(); }
 
+  // Must be called before `start`.  Batch spans become children of one "batching_task" span per process.
+  void set_tracer(telemetry::Tracer* t) {
+    tracer_ = t;
+    if (t && t->enabled()) {
+      auto root = t->start("batching_task");
+      loop_ctx_ = root.ctx;
+      t->end(root);
+    }
+  }
   void start() {
     running_ = true;
     batch_thread_ = std::thread([this] { batching_loop(); });
@@ -178,6 +190,8 @@ class Infer {
     v.inputs = inputs;
     v.input_ids = p.input_ids.empty() ? client_->tokenize(inputs) : p.input_ids;
     if (p.truncate && v.input_ids.size() > *p.truncate) v.input_ids.erase(v.input_ids.begin(), v.input_ids.end() - *p.truncate);
+    v.trace_id = p.trace_id;
+    v.span_id = p.span_id;
     v.truncate = p.truncate.value_or(cfg_.max_input_length);
     v.input_length = (uint32_t)v.input_ids.size();
     if (v.input_length == 0) throw validation_error("`inputs` cannot be empty");
@@ -429,7 +443,9 @@ class Infer {
               // one forward pass on the shards: the new prompts AND one decode step of everything that is running
               for (auto& e : more->entries) entries[e->id] = e;
               auto t0 = Clock::now();
+              BatchSpan bs(this, "prefill_decode", entries);
               auto res = client_->prefill(more->batch, std::nullopt, batches);
+              bs.finish(res.generations.size());
               if (metrics_) { metrics_->inc("lorax_batch_inference_count", {{"method", "prefill_decode"}}); metrics_->observe("lorax_batch_inference_duration", secs(t0), {{"method", "prefill_decode"}}); }
               deliver(res.generations, entries, t0);
               batches.clear();
@@ -443,7 +459,9 @@ class Infer {
           }
           waiting_tokens++;
           auto t0 = Clock::now();
+          BatchSpan bs(this, "decode", entries);
           auto res = client_->decode(batches);
+          bs.finish(res.generations.size());
           if (metrics_) { metrics_->inc("lorax_batch_inference_count", {{"method", "decode"}}); metrics_->observe("lorax_batch_inference_duration", secs(t0), {{"method", "decode"}}); }
           deliver(res.generations, entries, t0);
           batches.clear();
@@ -463,12 +481,46 @@ class Infer {
   std::optional<gen::CachedBatch> run_prefill(NextBatch& nb, EntryMap& entries) {
     for (auto& e : nb.entries) entries[e->id] = e;
     auto t0 = Clock::now();
+    BatchSpan bs(this, "prefill", entries);
     auto res = client_->prefill(nb.batch, std::nullopt);
+    bs.finish(res.generations.size());
     if (metrics_) { metrics_->inc("lorax_batch_inference_count", {{"method", "prefill"}}); metrics_->observe("lorax_batch_inference_duration", secs(t0), {{"method", "prefill"}}); }
     deliver(res.generations, entries, t0);
     return filter(res.batch, entries);
   }
   static double secs(Clock::time_point t0) { return std::chrono::duration<double>(Clock::now() - t0).count(); }
+
+  // One span per shard call of the batching loop, in the loop's own trace, linked to the request spans of the entries in
+  // the batch; its context goes to the shards in front of the message.  An exception between construction and `finish`
+  // marks the span as failed.
+  struct BatchSpan {
+    Infer* self;
+    telemetry::Span span;
+    BatchSpan(Infer* s, const char* method, const EntryMap& entries) : self(s) {
+      if (!s->tracer_ || !s->tracer_->enabled()) return;
+      span = s->tracer_->start(method, s->loop_ctx_, 3);
+      span.set("batch.size", json::Value((long long)entries.size()));
+      for (auto& kv : entries) {
+        if (span.links.size() >= 32) break;
+        if (!kv.second->request.trace_id.empty()) span.links.push_back({kv.second->request.trace_id, kv.second->request.span_id});
+      }
+      s->client_->set_trace(telemetry::format_traceparent(span.ctx));
+    }
+    void finish(size_t generations) {
+      if (!span.recording()) return;
+      span.set("generations", json::Value((long long)generations));
+      self->client_->set_trace("");
+      self->tracer_->end(span);
+      span.ctx = {};
+    }
+    ~BatchSpan() {
+      if (!span.recording()) return;                      // finished (moved out) or tracing off
+      span.error = true;
+      span.error_message = "shard call failed";
+      self->client_->set_trace("");
+      self->tracer_->end(span);
+    }
+  };
 
   // ---------------------------------------------------------------- adapter loader thread
   struct LoaderCmd {
@@ -537,6 +589,8 @@ class Infer {
   std::shared_ptr<ShardedClient> client_;
   RouterConfig cfg_;
   Metrics* metrics_;
+  telemetry::Tracer* tracer_ = nullptr;
+  telemetry::SpanContext loop_ctx_;        // parent of every batch span: the "batching_task" span of this process
   std::mutex mu_;
   std::condition_variable cv_, loader_cv_;
   AdapterQueues queues_;

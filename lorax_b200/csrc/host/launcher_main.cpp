@@ -350,7 +350,7 @@ int main(int argc, char** argv) {
   for (const char* opt : {"max-concurrent-requests", "max-best-of", "max-stop-sequences", "max-input-length", "max-total-tokens",
                           "max-batch-prefill-tokens", "max-batch-total-tokens", "waiting-served-ratio", "max-waiting-tokens",
                           "max-active-adapters", "adapter-cycle-time-s", "eager-prefill", "prefix-caching", "chunked-prefill", "hostname",
-                          "port", "adapter-source", "cors-allow-origin"})
+                          "port", "adapter-source", "cors-allow-origin", "otlp-endpoint"})
     if (!c.get(opt).empty()) { rargs.push_back(std::string("--") + opt); rargs.push_back(c.get(opt)); }
   Child router = spawn("router", rargs, {});
   if (router.pid <= 0) { terminate_all(all, 10); return 1; }

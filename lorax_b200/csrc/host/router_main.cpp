@@ -146,16 +146,77 @@ Value token_json(const StreamEvent& ev) {
 
 class App {
  public:
-  App(std::shared_ptr<ShardedClient> client, RouterConfig cfg, gen::InfoResponse info, uint32_t num_blocks)
+  App(std::shared_ptr<ShardedClient> client, RouterConfig cfg, gen::InfoResponse info, uint32_t num_blocks,
+      const std::string& otlp_endpoint = "", const std::string& request_logger_url = "")
       : client_(client), cfg_(cfg), info_(info), metrics_(cfg.max_input_length, cfg.max_total_tokens),
-        infer_(client, cfg, info, num_blocks, &metrics_) {
+        infer_(client, cfg, info, num_blocks, &metrics_), tracer_(otlp_endpoint, "lorax.router"),
+        request_logger_(telemetry::parse_url(request_logger_url), telemetry::parse_url(request_logger_url).path) {
+    infer_.set_tracer(&tracer_);
     infer_.start();
   }
-  void stop() { infer_.stop(); }
+  void stop() {
+    infer_.stop();
+    tracer_.shutdown();
+    request_logger_.stop();
+  }
+  bool tracing() const { return tracer_.enabled(); }
 
   // Runs one request to completion; `on_event` sees every stream event (used by the SSE routes).
   Collected run(const std::string& inputs, const GenerateParams& p, const std::function<bool(const StreamEvent&)>& on_event = nullptr,
                 http::ResponseWriter* w = nullptr) {
+    // the request span: child of the caller's trace context when the request carried one
+    telemetry::Span span = tracer_.start(on_event ? "generate_stream" : "generate", telemetry::parse_traceparent(p.traceparent), 2);
+    try {
+      Collected c;
+      if (span.recording()) {
+        GenerateParams traced = p;
+        traced.trace_id = span.ctx.trace_id;
+        traced.span_id = span.ctx.span_id;
+        c = run_inner(inputs, traced, on_event, w);
+      } else {
+        c = run_inner(inputs, p, on_event, w);
+      }
+      if (span.recording()) {
+        span.set("total_time_ms", Value(c.total_s * 1e3));
+        span.set("queue_time_ms", Value(c.queue_s * 1e3));
+        span.set("inference_time_ms", Value(c.inference_s * 1e3));
+        span.set("time_to_first_token_ms", Value(c.ttft_s * 1e3));
+        span.set("prompt_tokens", Value((long long)c.prompt_tokens));
+        span.set("generated_tokens", Value((long long)c.generated_tokens));
+        if (c.seed) span.set("seed", Value((unsigned long long)*c.seed));
+        if (p.adapter_id) span.set("adapter_id", Value(*p.adapter_id));
+        tracer_.end(span);
+      }
+      log_request(inputs, p, c);
+      return c;
+    } catch (const std::exception& e) {
+      if (span.recording()) {
+        span.error = true;
+        span.error_message = e.what();
+        tracer_.end(span);
+      }
+      throw;
+    }
+  }
+
+  // REQUEST_LOGGER_URL: every finished request as one JSON document (reference: server.rs:1314-1349).
+  void log_request(const std::string& inputs, const GenerateParams& p, const Collected& c) {
+    if (!request_logger_.enabled()) return;
+    Value v = Value::object();
+    v.set("model_id", cfg_.model_id);
+    v.set("adapter_id", p.adapter_id ? Value(*p.adapter_id) : Value());
+    v.set("adapter_source", p.adapter_source ? Value(*p.adapter_source) : Value());
+    v.set("input", inputs);
+    v.set("output", c.text);
+    v.set("prompt_tokens", (long long)c.prompt_tokens);
+    v.set("generated_tokens", (long long)c.generated_tokens);
+    v.set("finish_reason", finish_reason_name(c.finish_reason));
+    v.set("total_time_ms", c.total_s * 1e3);
+    request_logger_.post(v.dump());
+  }
+
+  Collected run_inner(const std::string& inputs, const GenerateParams& p, const std::function<bool(const StreamEvent&)>& on_event,
+                      http::ResponseWriter* w) {
     auto t0 = Clock::now();
     ValidRequest valid;
     auto sink = infer_.generate_stream(inputs, p, &valid);
@@ -274,6 +335,7 @@ class App {
     Value body;
     if (!parse_body(req, w, body)) return;
     GenerateParams p = params_from_json(body["parameters"]);
+    p.traceparent = req.header("traceparent");
     apply_auth(req, p);
     if (body["stream"].as_bool(false)) return generate_stream_body(body, p, w);
     try {
@@ -322,6 +384,7 @@ class App {
     Value body;
     if (!parse_body(req, w, body)) return;
     GenerateParams p = params_from_json(body["parameters"]);
+    p.traceparent = req.header("traceparent");
     apply_auth(req, p);
     generate_stream_body(body, p, w);
   }
@@ -368,6 +431,7 @@ class App {
     Value body;
     if (!parse_body(req, w, body)) return;
     GenerateParams p = openai_params(body);
+    p.traceparent = req.header("traceparent");
     apply_auth(req, p);
     std::string prompt = body["prompt"].is_array() ? body["prompt"].items().front().as_string() : body["prompt"].as_string();
     openai_run(body, prompt, p, w, false);
@@ -376,6 +440,7 @@ class App {
     Value body;
     if (!parse_body(req, w, body)) return;
     GenerateParams p = openai_params(body);
+    p.traceparent = req.header("traceparent");
     apply_auth(req, p);
     // tools -> JSON schema grammar: {"_name": const tool name, ...arguments} or the no_tool fallback
     if (body["tools"].is_array() && body["tools"].size() > 0) p.schema = tool_schema(body["tools"], body["tool_choice"]);
@@ -684,6 +749,8 @@ class App {
   gen::InfoResponse info_;
   Metrics metrics_;
   Infer infer_;
+  telemetry::Tracer tracer_;
+  telemetry::BackgroundPoster request_logger_;
   std::atomic<uint64_t> openai_id_{0};
 };
 
@@ -754,7 +821,11 @@ int main(int argc, char** argv) {
   }
   log_json("INFO", "connected to " + std::to_string(num_shard) + " shard(s); max_batch_total_tokens=" + std::to_string(cfg.max_batch_total_tokens));
 
-  App app(client, cfg, info, num_blocks);
+  const std::string otlp = a.get("otlp-endpoint", "");
+  const char* logger_env = std::getenv("REQUEST_LOGGER_URL");
+  App app(client, cfg, info, num_blocks, otlp, logger_env ? logger_env : "");
+  if (!otlp.empty()) log_json(app.tracing() ? "INFO" : "WARN", app.tracing() ? "tracing to " + otlp + " (OTLP/HTTP JSON)"
+                                                                              : "otlp endpoint must be an http:// URL; tracing is off");
   http::Server server;
   std::vector<std::string> cors;
   std::string cors_arg = a.get("cors-allow-origin", "");

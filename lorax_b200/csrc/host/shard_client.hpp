@@ -7,6 +7,10 @@
 //     request   u32 method | u32 length | bytes            (little endian; method ids: gen::Method)
 //     response  u32 status | u32 length | bytes            (status 0 = ok, otherwise bytes = error text)
 //
+// With bit 31 of `method` set, the first 55 bytes are a W3C `traceparent` ("00-<trace id>-<span id>-01") naming the
+// router span this call belongs to; the message follows (the reference carries the same context in gRPC metadata,
+// router/grpc-metadata/src/lib.rs:45-63).
+//
 // The Python shard serves both this framing and a regular grpc.aio LoraxService endpoint on `{uds_path}-{rank}`.
 // `ShardedClient` fans every call out to all shards in parallel and merges the answers the way the reference
 // does (sharded_client.rs:112-273): generations are concatenated, the last shard's CachedBatch wins, warmup takes
@@ -39,10 +43,11 @@ class ShardClient {
   // Raw call: returns the response payload or throws ShardError.
   virtual std::string call(uint32_t method, const std::string& payload) = 0;
 
+  static constexpr uint32_t kTraceFlag = 0x80000000u;
   template <class Resp, class Req>
-  Resp rpc(uint32_t method, const Req& req) {
+  Resp rpc(uint32_t method, const Req& req, const std::string& traceparent = std::string()) {
     Resp resp;
-    std::string out = call(method, req.serialize());
+    std::string out = traceparent.size() == 55 ? call(method | kTraceFlag, traceparent + req.serialize()) : call(method, req.serialize());
     if (!resp.parse(out)) throw ShardError("malformed response for method " + std::to_string(method));
     return resp;
   }
@@ -121,6 +126,8 @@ class ShardedClient {
     return ShardedClient(std::move(v));
   }
   size_t size() const { return shards_.size(); }
+  // Trace context of the calls that follow (the batching loop sets it around every Prefill / Decode; empty = none).
+  void set_trace(std::string traceparent) { std::lock_guard<std::mutex> g(trace_slot_.mu); trace_slot_.tp = std::move(traceparent); }
 
   gen::InfoResponse info() { return all<gen::InfoResponse>(gen::M_Info, gen::InfoRequest{}).front(); }
   void health() { all<gen::HealthResponse>(gen::M_Health, gen::HealthRequest{}); }
@@ -204,9 +211,11 @@ class ShardedClient {
  private:
   template <class Resp, class Req>
   std::vector<Resp> all(uint32_t method, const Req& req) {
-    if (shards_.size() == 1) return {shards_[0]->rpc<Resp>(method, req)};
+    std::string tp;
+    if (method == gen::M_Prefill || method == gen::M_Decode) { std::lock_guard<std::mutex> g(trace_slot_.mu); tp = trace_slot_.tp; }
+    if (shards_.size() == 1) return {shards_[0]->rpc<Resp>(method, req, tp)};
     std::vector<std::future<Resp>> futs;
-    for (auto& s : shards_) futs.push_back(std::async(std::launch::async, [s, method, &req] { return s->template rpc<Resp>(method, req); }));
+    for (auto& s : shards_) futs.push_back(std::async(std::launch::async, [s, method, &req, tp] { return s->template rpc<Resp>(method, req, tp); }));
     std::vector<Resp> out;
     std::exception_ptr err;
     for (auto& f : futs) {
@@ -216,6 +225,12 @@ class ShardedClient {
     return out;
   }
   std::vector<std::shared_ptr<ShardClient>> shards_;
+  struct TraceSlot {                      // movable holder: the client itself is passed around by value once
+    std::mutex mu;
+    std::string tp;
+    TraceSlot() = default;
+    TraceSlot(TraceSlot&& o) noexcept : tp(std::move(o.tp)) {}
+  } trace_slot_;
 };
 
 }  // namespace lx

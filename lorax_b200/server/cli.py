@@ -41,6 +41,9 @@ def serve(args):
     rt = build_runtime(args.model_id, cfg, tp=tp, dtype=dtype, source=args.source, revision=args.revision, device=args.device)
     if args.adapter_id:
         rt.load_default_adapter(args.adapter_id, {"hub": 0, "s3": 1, "local": 2, "pbase": 3}[args.adapter_source])
+    from .tracing import PrefillProfiler, Tracer
+    rt.tracer = Tracer(args.otlp_endpoint or os.environ.get("OTLP_ENDPOINT"), f"lorax.server-{tp.rank}")
+    rt.profiler = PrefillProfiler(cfg.profiler_dir)
     framed = FramedServer(rt, f"{args.uds_path}-{tp.rank}.lx").start()
     _log("INFO", f"Server started at unix://{args.uds_path}-{tp.rank}", args.json_output)
 

@@ -446,6 +446,9 @@ class ShardRuntime:
     def prefill(self, req):
         """Prefill of a new batch.  With `decode_batches` set, the running batches take one decode step in the same
         forward pass (one pass over the weights for both) and the response merges everything into one cached batch."""
+        prof = getattr(self, "profiler", None)
+        if prof is not None:
+            prof.step()
         if len(req.decode_batches):
             return self._prefill_and_decode(req)
         seqs, items = self._new_sequences(req.batch)

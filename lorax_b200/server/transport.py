@@ -24,6 +24,7 @@ from typing import Optional
 import torch
 
 from .proto import load_pb
+from .tracing import TRACE_FLAG, TRACEPARENT_BYTES
 
 HELPER_TOKENIZE, HELPER_TOKENIZE_JSON, HELPER_CHAT_TEMPLATE = 100, 101, 102
 
@@ -86,8 +87,17 @@ class FramedServer:
             while not self._stop.is_set():
                 method, length = struct.unpack("<II", read_exact(8))
                 payload = read_exact(length) if length else b""
+                traceparent = None
+                if method & TRACE_FLAG:                 # the router's span context in front of the message
+                    method &= ~TRACE_FLAG
+                    traceparent, payload = payload[:TRACEPARENT_BYTES].decode("ascii", "replace"), payload[TRACEPARENT_BYTES:]
                 try:
-                    out = self.handle(method, payload)
+                    tracer = getattr(self.rt, "tracer", None)
+                    if tracer is not None and tracer.enabled and traceparent:
+                        with tracer.span(self.ids.get(method, str(method)), traceparent, {"rpc.payload_bytes": len(payload)}):
+                            out = self.handle(method, payload)
+                    else:
+                        out = self.handle(method, payload)
                     conn.sendall(struct.pack("<II", 0, len(out)) + out)
                 except Exception as e:  # report, keep the connection
                     if self.rt.model.device.type == "cuda":

@@ -68,12 +68,33 @@ def stack(tmp_path_factory):
     ecfg = EngineConfig(max_input_length=64, max_total_tokens=128, max_batch_prefill_tokens=256, compile=False)
     rt = build_runtime(str(mdir), ecfg, device="cpu", dtype=torch.float32, source="local", num_blocks=256, max_batch=16)
     uds = str(root / "shard")
+    # a stand-in for an OTLP/HTTP collector and a request-log sink: records every JSON document posted to it
+    import http.server
+    import threading
+    received = []
+
+    class Sink(http.server.BaseHTTPRequestHandler):
+        def do_POST(self):
+            body = self.rfile.read(int(self.headers.get("Content-Length", "0")))
+            received.append((self.path, json.loads(body.decode())))
+            self.send_response(200)
+            self.send_header("Content-Length", "2")
+            self.end_headers()
+            self.wfile.write(b"{}")
+
+        def log_message(self, *a):
+            pass
+    sink = http.server.ThreadingHTTPServer(("127.0.0.1", 0), Sink)
+    threading.Thread(target=sink.serve_forever, daemon=True).start()
+    sink_url = f"http://127.0.0.1:{sink.server_address[1]}"
+    from lorax_b200.server.tracing import Tracer
+    rt.tracer = Tracer(sink_url, "lorax.server-0", flush_s=0.1)
     srv = FramedServer(rt, uds + "-0.lx").start()
     port = _free_port()
     proc = subprocess.Popen([ROUTER, "--port", str(port), "--hostname", "127.0.0.1", "--master-shard-uds-path", uds, "--num-shard", "1",
                              "--max-input-length", "64", "--max-total-tokens", "128", "--max-batch-prefill-tokens", "256",
-                             "--model-id", "tiny", "--adapter-source", "local", "--waiting-served-ratio", "0.3"],
-                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+                             "--model-id", "tiny", "--adapter-source", "local", "--waiting-served-ratio", "0.3", "--otlp-endpoint", sink_url],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env={**os.environ, "REQUEST_LOGGER_URL": sink_url + "/log"})
     ok = False
     for _ in range(100):
         try:
@@ -85,7 +106,9 @@ def stack(tmp_path_factory):
     if not ok:
         proc.kill()
         raise RuntimeError("router did not come up: " + proc.stdout.read().decode()[-2000:])
-    yield dict(port=port, root=root, rt=rt, model=model, cfg=cfg)
+    yield dict(port=port, root=root, rt=rt, model=model, cfg=cfg, received=received)
+    sink.shutdown()
+    rt.tracer.shutdown()
     proc.terminate()
     try:
         proc.wait(timeout=10)
@@ -217,3 +240,49 @@ def test_python_client_sync_and_async(stack):
         return outs, streamed
     outs, streamed = asyncio.run(go())
     assert all(o.details.generated_tokens == 3 for o in outs) and len(streamed) == 4
+
+
+def test_tracing_and_request_logger(stack):
+    """OTLP/HTTP JSON spans from the router and the shard, stitched together: the request span continues the caller's
+    `traceparent`; the batch spans of the batching loop link to it and carry their own context to the shard, whose RPC spans are
+    their children.  REQUEST_LOGGER_URL receives one JSON document per finished request."""
+    received = stack["received"]
+    trace_id, parent = "4bf92f3577b34da6a3ce929d0e0e4736", "00f067aa0ba902b7"
+    status, data, _ = _post(stack["port"], "/generate", {"inputs": "w5 w6 w7 w8", "parameters": {"max_new_tokens": 4}},
+                            headers={"traceparent": f"00-{trace_id}-{parent}-01"})
+    assert status == 200
+    want_text = json.loads(data)["generated_text"]
+
+    def spans_of(service):
+        out = []
+        for path, doc in list(received):
+            if path != "/v1/traces":
+                continue
+            for rs in doc["resourceSpans"]:
+                attrs = {a["key"]: a["value"] for a in rs["resource"]["attributes"]}
+                if attrs["service.name"]["stringValue"] == service:
+                    for ss in rs["scopeSpans"]:
+                        out += ss["spans"]
+        return out
+    req_span = None
+    for _ in range(100):
+        req_span = next((s for s in spans_of("lorax.router") if s["traceId"] == trace_id), None)
+        shard_spans = spans_of("lorax.server-0")
+        logged = [d for p, d in list(received) if p == "/log" and d.get("input") == "w5 w6 w7 w8"]
+        if req_span is not None and any(s["name"] == "Decode" for s in shard_spans) and logged:
+            break
+        time.sleep(0.1)
+    assert req_span is not None and req_span["parentSpanId"] == parent and req_span["name"] == "generate" and req_span["kind"] == 2
+    attrs = {a["key"]: a["value"] for a in req_span["attributes"]}
+    assert attrs["generated_tokens"]["intValue"] == "4" and attrs["prompt_tokens"]["intValue"] == "4" and "inference_time_ms" in attrs
+    assert int(req_span["endTimeUnixNano"]) > int(req_span["startTimeUnixNano"])
+    router_spans = spans_of("lorax.router")
+    linked = [s for s in router_spans if any(l["traceId"] == trace_id and l["spanId"] == req_span["spanId"] for l in s.get("links", []))]
+    assert {s["name"] for s in linked} >= {"prefill", "decode"}
+    root = next(s for s in router_spans if s["name"] == "batching_task")
+    assert all(s["traceId"] == root["traceId"] and s["parentSpanId"] == root["spanId"] for s in linked)
+    by_id = {s["spanId"]: s for s in linked}
+    children = [s for s in shard_spans if s.get("parentSpanId") in by_id]
+    assert {s["name"] for s in children} >= {"Prefill", "Decode"}
+    assert all(s["traceId"] == root["traceId"] for s in children)
+    assert logged[0]["output"] == want_text and logged[0]["generated_tokens"] == 4 and logged[0]["model_id"] == "tiny"
