@@ -27,6 +27,8 @@ from ..config import EngineConfig
 from ..models.decoder import DecoderModel
 from ..sampling.chooser import (FINISH_EOS, FINISH_LENGTH, FINISH_STOP, HeterogeneousNextTokenChooser, NextTokenParams,
                                 StoppingCriteria)
+from ..sampling.device import RowSampler
+from ..sampling.device import supported as device_sampling_supported
 from .kv_cache import BlockAllocator, KVCache
 from .runner import ModelRunner, PrefillItem
 
@@ -86,6 +88,7 @@ class Engine:
         self.waiting: Deque[GenRequest] = collections.deque()
         self.running: Dict[int, _Seq] = {}
         self.draining: Dict[int, _Seq] = {}
+        self._row_sampler = RowSampler(model.device)
         self.inflight: Deque[tuple] = collections.deque()   # ("decode", ring idx, bucket, row->req) | ("first", ring idx, n, [req])
         self.steps_since_prefill = 0
         self.decode_text = decode_text
@@ -110,6 +113,10 @@ class Engine:
 
     # ------------------------------------------------------------------ API
     def add_request(self, req: GenRequest):
+        if not req.params.plain and not device_sampling_supported(req.params):
+            raise ValueError("the in-process engine samples on the device (temperature, top-k, top-p, typical-p, seed); repetition / "
+                             "frequency / presence penalties, watermarking, grammars and alternative tokens are served by the "
+                             "shard runtime behind the router")
         if not req.arrival_time:
             req.arrival_time = time.perf_counter()
         if len(req.prompt_ids) + req.max_new_tokens > self.cfg.max_total_tokens:
@@ -266,6 +273,35 @@ class Engine:
         self.runner.retire(done_rows)
 
     # ------------------------------------------------------------------ one iteration
+    def _sample_first(self, picked, next_ids, lps, logits):
+        """Requests that sample draw their first token on the device from the prefill logits (one row per request)."""
+        idx = [i for i, (r, _) in enumerate(picked) if r.params.do_sample]
+        if not idx:
+            return
+        sampler = RowSampler(logits.device)
+        sampler.bind(idx, [picked[i][0].params for i in idx])
+        ids, lp = sampler(logits, [0] * len(idx))
+        next_ids.index_copy_(0, sampler.rows, ids.to(next_ids.dtype))
+        lps.index_copy_(0, sampler.rows, lp.to(lps.dtype))
+
+    def _decode_sampler(self, snapshot: Dict[int, int]):
+        """The device-side hook of a decode step, or None when every running request is greedy."""
+        rows = sorted(r for r, rid in snapshot.items() if self.running[rid].req.params.do_sample)
+        if not rows:
+            return None
+        seqs = [self.running[snapshot[r]] for r in rows]
+        self._row_sampler.bind(rows, [s.req.params for s in seqs])
+        steps = [s.launched for s in seqs]                   # index of the token this step generates for the row
+        rs = self._row_sampler
+
+        def hook(logits, st):
+            ids, lp = rs(logits, steps)
+            ids32 = ids.to(st.next_ids.dtype)
+            st.next_ids.index_copy_(0, rs.rows, ids32)
+            st.logprobs.index_copy_(0, rs.rows, lp.to(st.logprobs.dtype))
+            st.input_ids.index_copy_(0, rs.rows, ids32)      # the step advanced the state with the arg-max
+        return hook
+
     def step(self) -> List[TokenEvent]:
         events: List[TokenEvent] = []
         queued_before = len(self.inflight)
@@ -274,19 +310,21 @@ class Engine:
         if picked:
             items = [PrefillItem(r.prompt_ids, 0, b, r.adapter_index) for r, b in picked]
             snapshot = {s.row: rid for rid, s in self.running.items() if not s.retired}
-            if self.mixed_steps and snapshot and self.runner.can_mix():
+            sampling = any(r.params.do_sample for r, _ in picked) or any(s.req.params.do_sample for s in self.running.values())
+            if self.mixed_steps and snapshot and self.runner.can_mix() and not sampling:
                 # one pass over the weights for the running decode rows and the new prompts together
                 k, b, next_ids, lps = self.runner.mixed_step(items)
                 self._after_decode_launch(k, b, snapshot)
                 self._admit(picked, next_ids, lps)
                 launched = True
             else:
-                next_ids, lps, _ = self.runner.prefill(items)
+                next_ids, lps, logits = self.runner.prefill(items)
+                self._sample_first(picked, next_ids, lps, logits)
                 self._admit(picked, next_ids, lps)
 
         if not launched and self.running:
             snapshot = {s.row: rid for rid, s in self.running.items() if not s.retired}
-            out = self.runner.decode() if snapshot else None
+            out = self.runner.decode(sampler=self._decode_sampler(snapshot)) if snapshot else None
             if out is not None:
                 self._after_decode_launch(out[0], out[1], snapshot)
                 launched = True

@@ -411,10 +411,13 @@ class ModelRunner:
         self.graphs[key] = g
         self.graph_out[key] = logits
 
-    def decode(self, lora: Optional[bool] = None, need_logits: bool = False):
+    def decode(self, lora: Optional[bool] = None, need_logits: bool = False, sampler=None):
         """One decode step over rows [0, high_water).  Returns (ring index, bucket, logits or None); the sampled
-        ids / log-probs land in the pinned ring entry once its event has completed."""
+        ids / log-probs land in the pinned ring entry once its event has completed.  `sampler(logits, state)` runs on the
+        device right after the step and may overwrite `next_ids`, `logprobs` and the next `input_ids` of some rows (the
+        step itself has already advanced the state with the arg-max)."""
         st = self.state
+        need_logits = need_logits or sampler is not None
         n = st.high_water
         if n == 0:
             return None
@@ -435,6 +438,8 @@ class ModelRunner:
         else:
             logits = self._decode_body(b, lora, need_logits)
             self._advance(b)
+        if sampler is not None:
+            sampler(logits, st)
         k = self.ring_pos
         self.ring_pos = (k + 1) % self.n_ring
         self.ring_ids[k][:b].copy_(st.next_ids[:b], non_blocking=True)

@@ -9,7 +9,7 @@ from lorax_b200.adapters.manager import AdapterManager
 from lorax_b200.config import EngineConfig, tiny_llama
 from lorax_b200.models.decoder import DecoderModel
 from lorax_b200.models.loading import export_hf_state_dict
-from lorax_b200.runtime.engine import Engine
+from lorax_b200.runtime.engine import Engine, GenRequest
 
 
 def _hf_model(cfg, sd):
@@ -158,3 +158,68 @@ def test_adapter_exchange_under_memory_pressure():
     tight, stats, mgr = run(2)
     assert tight == full
     assert stats.get("adapter_evictions", 0) >= 3 and len(mgr.resident) <= 2
+
+
+def test_device_sampler_distribution_and_filters():
+    """The exponential-noise draw follows the warped distribution; top-k / top-p / typical-p keep exactly the reference's sets;
+    the noise depends on (seed, step) only."""
+    from lorax_b200.sampling import device as ds
+    torch.manual_seed(0)
+    V = 12
+    logits = torch.randn(1, V) * 2
+    t = torch.tensor
+    # filters against the per-row warpers of the host chooser's definitions
+    x = ds.warp(logits, t([0.7]), t([5]), t([0.8]), t([1.0]))
+    scaled = logits[0] / 0.7
+    top5 = scaled.topk(5).indices
+    p = torch.softmax(scaled[top5], -1)
+    keep = top5[: int(((p.cumsum(0) - p) < 0.8).sum())]
+    assert set(torch.isfinite(x[0]).nonzero()[:, 0].tolist()) == set(keep.tolist())
+    off = ds.warp(logits, t([1.0]), t([0]), t([1.0]), t([1.0]))
+    assert torch.allclose(off, logits.float())
+    typ = ds.warp(logits, t([1.0]), t([0]), t([1.0]), t([0.5]))
+    logp = torch.log_softmax(logits[0], -1)
+    ent = -(logp.exp() * logp).sum()
+    order = (-logp - ent).abs().argsort()
+    mass = logp.exp()[order]
+    n_keep = int(((mass.cumsum(0) - mass) < 0.5).sum())
+    assert set(torch.isfinite(typ[0]).nonzero()[:, 0].tolist()) == set(order[:n_keep].tolist())
+    # the draw: empirical frequencies over many steps match softmax
+    R = 20000
+    scores = logits.expand(R, V).contiguous()
+    ids, lp = ds.draw(scores, torch.full((R,), 1234, dtype=torch.int64), torch.arange(R, dtype=torch.int64))
+    freq = torch.bincount(ids, minlength=V).float() / R
+    assert (freq - torch.softmax(logits[0], -1)).abs().max().item() < 0.012
+    assert torch.allclose(lp, torch.log_softmax(logits[0], -1)[ids])
+    # determinism: same (seed, step) -> same noise whatever the row; different seeds differ
+    a = ds.uniform_noise(t([7, 9, 7]), t([3, 3, 3]), 1000)
+    assert torch.equal(a[0], a[2]) and not torch.equal(a[0], a[1]) and 0 < a.min() and a.max() < 1
+    assert abs(a.mean().item() - 0.5) < 0.02
+
+
+def test_engine_samples_on_device_reproducibly(setup):
+    """Sampling requests in the in-process engine: a request's tokens depend on its seed only (not on its neighbours or its
+    decode row), greedy requests in the same batch are untouched, and unsupported parameters are refused."""
+    from lorax_b200.sampling.chooser import NextTokenParams
+    cfg, model, mgr, _ = setup
+    g = torch.Generator().manual_seed(21)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 17, 12, 30)]
+
+    def run(order, params):
+        eng = Engine(model, EngineConfig(max_input_length=64, max_total_tokens=128, max_batch_prefill_tokens=256, compile=False), num_blocks=64)
+        for rid in order:
+            eng.add_request(GenRequest(rid, prompts[rid], max_new_tokens=10, params=params[rid]))
+        eng.run()
+        return {rid: eng.finished[rid].output_ids for rid in order}
+    sample = NextTokenParams(temperature=1.3, top_k=50, top_p=0.95, do_sample=True, seed=11)
+    params = {0: NextTokenParams(), 1: sample, 2: NextTokenParams(temperature=0.8, do_sample=True, seed=5), 3: NextTokenParams()}
+    a = run([0, 1, 2, 3], params)
+    b = run([3, 2, 1], params)                              # other neighbours, other rows
+    greedy = run([0, 3], params)
+    assert a[1] == b[1] and a[2] == b[2]
+    assert a[0] == greedy[0] and a[3] == greedy[3] == b[3]
+    c = run([1], {1: NextTokenParams(temperature=1.3, top_k=50, top_p=0.95, do_sample=True, seed=12)})
+    assert c[1] != a[1]                                     # another seed, another continuation
+    assert all(len(v) == 10 for v in a.values())
+    with pytest.raises(ValueError):
+        run([0], {0: NextTokenParams(do_sample=True, repetition_penalty=1.2)})
