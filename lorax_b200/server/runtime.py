@@ -658,6 +658,136 @@ def load_tokenizer(model_dir: str):
     return None
 
 
+class Seq2SeqRuntime(ShardRuntime):
+    """Shard runtime of an encoder-decoder model (T5 family): Prefill runs the encoder once per request and the first decoder
+    step, Decode advances every request of the batch by one decoder position.  The decoding state (cross-attention projections,
+    self-attention keys / values) lives with the request, not in the paged KV cache, and adapters are not applied
+    (reference: `Seq2SeqLM`, `server/lorax_server/models/seq2seq_lm.py`: padded batches, `past_key_values`, no adapters)."""
+
+    def __init__(self, model, tokenizer=None, cfg: Optional[EngineConfig] = None, model_id: str = ""):
+        self.pb = load_pb()
+        self.model = model
+        self.tokenizer = tokenizer
+        self.cfg = cfg or EngineConfig()
+        self.model_id = model_id
+        self.tp = model.tp
+        self.seqs: Dict[int, SeqState] = {}
+        self.batches: Dict[int, List[int]] = {}
+        self.states: Dict[int, object] = {}
+        c = model.config
+        self.eos_ids = frozenset([c.eos_token_id])
+        self.special_ids = {c.eos_token_id, c.pad_token_id}
+        self.lock = threading.Lock()
+        self.spec_stats = {"steps": 0, "tokens": 0}
+        self.fused_stats = {"one_pass": 0, "two_pass": 0}
+        self.medusa_host, self.medusa = {}, {}
+
+    def info(self):
+        return self.pb.InfoResponse(requires_padding=True, dtype=str(self.model.dtype).replace("torch.", ""),
+                                    device_type=self.model.device.type, block_size=16, speculate=0, supports_generation=True,
+                                    supports_embeddings=False, supports_classification=False, chunked_prefill=False,
+                                    requires_block_allocator=False, fused_prefill_decode=False)
+
+    def warmup(self, req):
+        return self.pb.WarmupResponse(max_supported_total_tokens=max(self.cfg.max_batch_total_tokens or 0, 16 * self.cfg.max_total_tokens))
+
+    def _no_adapters(self, *_a, **_k):
+        raise ValueError("adapters are not supported for encoder-decoder models")
+
+    download_adapter = load_adapter = offload_adapter = _no_adapters
+
+    def _drop(self, rid: int):
+        self.seqs.pop(rid, None)
+        self.states.pop(rid, None)
+
+    def _resort(self):
+        pass
+
+    def _step(self, seqs: List[SeqState]):
+        """One decoder position for `seqs`; returns the generations and the ids of the finished requests."""
+        states = [self.states[s.request_id] for s in seqs]
+        logits = self.model.decode_step(states)
+        lps_all = torch.log_softmax(logits, -1)
+        gid = logits.argmax(-1)
+        glp = lps_all.gather(1, gid[:, None])[:, 0]
+        ids, lps, alts = self._sample_rows(seqs, logits, gid.tolist(), glp.tolist())
+        gens, finished = [], []
+        for s, st, tok, lp, alt in zip(seqs, states, ids, lps, alts):
+            st.last_token, st.position = int(tok), st.position + 1
+            gen, stop = self._emit(s, int(tok), float(lp), alt)
+            if gen is not None:
+                gens.append(gen)
+            if stop:
+                finished.append(s.request_id)
+        return gens, finished
+
+    def prefill(self, req):
+        pb = self.pb
+        batch = req.batch
+        seqs = []
+        for r in batch.requests:
+            ids = list(r.tokenized_inputs.ids) if r.HasField("tokenized_inputs") and len(r.tokenized_inputs.ids) else self.tokenize(r.inputs)
+            ids = ids[-(r.truncate or self.cfg.max_input_length):]
+            params = self._params_from_pb(r.parameters)
+            stopping = StoppingCriteria(r.stopping_parameters.max_new_tokens or 1, self.eos_ids, list(r.stopping_parameters.stop_sequences),
+                                        r.stopping_parameters.ignore_eos_token)
+            s = SeqState(r.id, batch.id, ids, [], 0, params, stopping, Detokenizer(self.tokenizer, []), seed=params.seed)
+            if params.schema:
+                s.grammar = compile_schema(params.schema, self.tokenizer, self.eos_ids)
+            with torch.inference_mode():
+                self.states[r.id] = self.model.encode(ids)
+            self.seqs[r.id] = s
+            seqs.append(s)
+        with torch.inference_mode():
+            gens, finished = self._step(seqs)
+        for rid in finished:
+            self._drop(rid)
+        live = [s.request_id for s in seqs if s.request_id not in finished]
+        resp = pb.PrefillResponse(generations=gens)
+        if live:
+            self.batches[batch.id] = live
+            resp.batch.CopyFrom(self._cached(batch.id))
+        return resp
+
+    def decode(self, req):
+        pb = self.pb
+        bids = [b.id for b in req.batches]
+        rids = [r for b in bids for r in self.batches.get(b, [])]
+        if not rids:
+            raise RuntimeError("all batches of the Decode request are missing from the cache")
+        with torch.inference_mode():
+            gens, finished = self._step([self.seqs[r] for r in rids])
+        for bid in bids:
+            self.batches.pop(bid, None)
+        for rid in finished:
+            self._drop(rid)
+        merged = [r for r in rids if r not in finished]
+        resp = pb.DecodeResponse(generations=gens)
+        if merged:
+            self.batches[bids[0]] = merged
+            for r in merged:
+                self.seqs[r].batch_id = bids[0]
+            resp.batch.CopyFrom(self._cached(bids[0]))
+        return resp
+
+    def filter_batch(self, req):
+        keep = set(req.request_ids)
+        for rid in self.batches.get(req.batch_id, []):
+            if rid not in keep:
+                self._drop(rid)
+        self.batches[req.batch_id] = [r for r in self.batches.get(req.batch_id, []) if r in keep]
+        return self.pb.FilterBatchResponse(batch=self._cached(req.batch_id))
+
+    def health(self):
+        return self.pb.HealthResponse()
+
+    def embed(self, req):
+        return self.pb.EmbedResponse(errorMsg="this model does not serve embeddings")
+
+    def classify(self, req):
+        return self.pb.ClassifyResponse(errorMsg="this model is not a classifier")
+
+
 class EncoderRuntime:
     """Shard runtime of an embedding / token-classification model (BERT, RoBERTa, DistilBERT): `Embed` and `Classify`
     are served, every generation RPC answers with an error (reference: `FlashBert.embed/classify`,
@@ -741,6 +871,13 @@ def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel]
     with open(os.path.join(model_dir, "config.json")) as f:
         raw_cfg = json.load(f)
     from ..models.encoder import ENCODER_TYPES, EncoderConfig, EncoderModel
+    from ..models.seq2seq import SEQ2SEQ_TYPES, Seq2SeqConfig, Seq2SeqModel
+    if raw_cfg.get("model_type") in SEQ2SEQ_TYPES:
+        if tp.world_size > 1:
+            raise ValueError("encoder-decoder models are served on one shard")
+        w = Weights(weight_files(model_dir), device="cpu", dtype=dtype)
+        s2s = Seq2SeqModel.from_weights(Seq2SeqConfig.from_dict(raw_cfg), w, dev, dtype)
+        return Seq2SeqRuntime(s2s, load_tokenizer(model_dir), cfg, model_id=model_id)
     if raw_cfg.get("model_type") in ENCODER_TYPES:
         w = Weights(weight_files(model_dir), device="cpu", dtype=dtype)
         enc = EncoderModel.from_weights(EncoderConfig.from_dict(raw_cfg), w, dev, dtype)
