@@ -29,6 +29,19 @@ from .tracing import TRACE_FLAG, TRACEPARENT_BYTES
 HELPER_TOKENIZE, HELPER_TOKENIZE_JSON, HELPER_CHAT_TEMPLATE = 100, 101, 102
 
 
+def _resolve_device(dev: torch.device) -> torch.device:
+    """`cuda` without an index names the current device of the thread that built the runtime: pin it down once."""
+    if dev.type == "cuda" and dev.index is None:
+        return torch.device("cuda", torch.cuda.current_device())
+    return dev
+
+
+def _select_device(dev: torch.device):
+    """Make `dev` the calling thread's current CUDA device."""
+    if dev.type == "cuda" and dev.index is not None:
+        torch.cuda.set_device(dev.index)
+
+
 def _dispatch(runtime, name: str, request):
     fn = {
         "Info": lambda r: runtime.info(), "ServiceDiscovery": None, "ClearCache": runtime.clear_cache,
@@ -43,6 +56,7 @@ def _dispatch(runtime, name: str, request):
 class FramedServer:
     def __init__(self, runtime, path: str, urls=None):
         self.rt = runtime
+        self.device = _resolve_device(runtime.model.device)
         self.path = path
         self.pb = load_pb()
         self.ids = {v: k for k, v in self.pb.METHOD_IDS.items()}
@@ -81,8 +95,7 @@ class FramedServer:
             return bytes(buf)
         # the CUDA "current device" is a per-thread setting and new threads start on device 0: the kernels of this library are
         # launched through the raw runtime API, so the handler thread must select the shard's GPU itself
-        if self.rt.model.device.type == "cuda":
-            torch.cuda.set_device(self.rt.model.device)
+        _select_device(self.device)
         try:
             while not self._stop.is_set():
                 method, length = struct.unpack("<II", read_exact(8))
@@ -147,6 +160,7 @@ async def serve_grpc(runtime, uds_path: str, rank: int, world_size: int, lock: O
     import grpc
     pb = load_pb()
     lock = lock or threading.Lock()
+    device = _resolve_device(runtime.model.device)
     urls = [f"unix://{uds_path}-{r}" for r in range(world_size)]
 
     def make(name, req_cls, resp_cls):
@@ -155,8 +169,7 @@ async def serve_grpc(runtime, uds_path: str, rank: int, world_size: int, lock: O
                 if name == "ServiceDiscovery":
                     return pb.ServiceDiscoveryResponse(urls=urls)
                 with lock:
-                    if runtime.model.device.type == "cuda":
-                        torch.cuda.set_device(runtime.model.device)      # per-thread setting, see FramedServer._serve_conn
+                    _select_device(device)                               # per-thread setting, see FramedServer._serve_conn
                     return _dispatch(runtime, name, request)
             except Exception as e:
                 if runtime.model.device.type == "cuda":

@@ -211,3 +211,27 @@ def test_alibi_and_learned_position_families_match_cpu_oracle(family):
     native.workspace().check_status()
     err = (outs[0] - outs[1]).norm() / outs[1].norm()
     assert err < 3e-2, err
+
+
+def test_engine_device_sampling_with_graphs():
+    """Sampling rows inside graph-replayed decode steps: tokens depend on the request's seed only, greedy neighbours keep the
+    tokens they have without any sampling request in the batch."""
+    from lorax_b200.runtime.engine import GenRequest
+    from lorax_b200.sampling.chooser import NextTokenParams
+    cfg, gm, _ = _build("cuda", torch.bfloat16)
+    g = torch.Generator().manual_seed(31)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (9, 40, 17, 25)]
+    sample = NextTokenParams(temperature=1.2, top_k=40, top_p=0.9, do_sample=True, seed=7)
+    params = {0: NextTokenParams(), 1: sample, 2: NextTokenParams(temperature=0.7, typical_p=0.8, do_sample=True, seed=3), 3: NextTokenParams()}
+
+    def run(order):
+        eng = Engine(gm, EngineConfig(max_input_length=64, max_total_tokens=128, max_batch_prefill_tokens=256, compile=True), num_blocks=64)
+        for rid in order:
+            eng.add_request(GenRequest(rid, prompts[rid], max_new_tokens=12, params=params[rid], adapter_index=rid % 3))
+        eng.run()
+        return {rid: eng.finished[rid].output_ids for rid in order}
+    a, b, greedy = run([0, 1, 2, 3]), run([2, 3, 1]), run([0, 3])
+    assert a[1] == b[1] and a[2] == b[2] and a[3] == b[3] == greedy[3] and a[0] == greedy[0]
+    assert all(len(v) == 12 for v in a.values())
+    from lorax_b200.ops import native
+    native.workspace().check_status()
