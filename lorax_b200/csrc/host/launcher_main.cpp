@@ -48,6 +48,7 @@ const Flag kFlags[] = {
     {"quantize", "QUANTIZE", "", "fp8 | gptq | awq | eetq | bitsandbytes ..."},
     {"dtype", "DTYPE", "", "float16 | bfloat16"},
     {"compile", "COMPILE", "true", "capture decode steps in CUDA graphs"},
+    {"skip-download", "SKIP_DOWNLOAD", "false", "do not run the download-weights step before the shards start"},
     {"speculative-tokens", "SPECULATIVE_TOKENS", "", "tokens proposed per step"},
     {"preloaded-adapter-ids", "PRELOADED_ADAPTER_IDS", "", "comma separated"},
     {"max-concurrent-requests", "MAX_CONCURRENT_REQUESTS", "1024", ""},
@@ -289,6 +290,31 @@ int main(int argc, char** argv) {
   }
   const int num_shard = find_num_shards(c);
   emit("INFO", "lorax_launcher", "starting " + std::to_string(num_shard) + " shard(s) for " + c.get("model-id"));
+
+  // ---- weights: one download / conversion step before any shard starts (the reference runs `lorax-server download-weights`
+  // the same way, launcher/src/main.rs:1166-1313); a local model directory needs none
+  struct stat model_sb;
+  const bool local_dir = stat(c.get("model-id").c_str(), &model_sb) == 0 && S_ISDIR(model_sb.st_mode);
+  if (!local_dir && !c.truthy("skip-download")) {
+    std::vector<std::string> dargs = {c.get("python"), "-m", "lorax_b200.server.cli", "download-weights", c.get("model-id"),
+                                      "--source", c.get("source"), "--json-output"};
+    if (!c.get("revision").empty()) { dargs.push_back("--revision"); dargs.push_back(c.get("revision")); }
+    emit("INFO", "lorax_launcher", "Starting download process.");
+    Child dl = spawn("download", dargs, {});
+    if (dl.pid <= 0) return 1;
+    int st = 0;
+    while (!exited(dl, &st)) {
+      pump(dl);
+      if (g_signal) { terminate_all({&dl}, 10); return 0; }
+      std::this_thread::sleep_for(std::chrono::milliseconds(100));
+    }
+    pump(dl);
+    if (!WIFEXITED(st) || WEXITSTATUS(st) != 0) {
+      emit("ERROR", "lorax_launcher", "download of " + c.get("model-id") + " failed (status " + std::to_string(st) + ")");
+      return 1;
+    }
+    emit("INFO", "lorax_launcher", "Successfully downloaded weights.");
+  }
 
   // ---- shards
   const std::string uds = c.get("shard-uds-path");
