@@ -126,6 +126,7 @@ struct Entry {
   Clock::time_point batch_time{};
   std::optional<BlockAllocation> allocation;
   std::vector<uint32_t> generated;       // for the radix trie on free
+  uint32_t prefilled = 0;                // prompt tokens whose keys / values the shards hold (chunked prefill)
 };
 
 enum class AdapterStatus { Downloading, Downloaded, Ready, Errored };

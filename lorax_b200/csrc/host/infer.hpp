@@ -244,41 +244,12 @@ class Infer {
     for (auto& a : up.offload) loader_queue_.push_back({LoaderCmd::Offload, a});
     for (auto& a : up.load) loader_queue_.push_back({LoaderCmd::Load, a});
     if (!up.offload.empty() || !up.load.empty()) loader_cv_.notify_one();
-    if (min_size && queues_.queued() < *min_size) return std::nullopt;
+    if (min_size && chunking_.empty() && queues_.queued() < *min_size) return std::nullopt;
 
     NextBatch nb;
     uint32_t prefill_tokens = 0, decode_tokens = 0, max_blocks = 0;
     uint32_t max_input = 0;
-    while (true) {
-      auto e = queues_.next_entry();
-      if (!e) break;
-      const uint32_t in_len = e->request.input_length, max_new = e->request.stopping.max_new_tokens;
-      if (requires_padding_) {
-        // padded models are budgeted by (n + 1) * longest prompt (scheduler.rs:348-368 of the reference)
-        max_input = std::max(max_input, in_len);
-        prefill_tokens = (uint32_t)(nb.entries.size() + 1) * max_input;
-        decode_tokens += max_new;
-        if (prefill_tokens > prefill_budget || prefill_tokens + decode_tokens > token_budget) { queues_.push_front(e); break; }
-      } else {
-        const uint32_t need = in_len + max_new + (speculate_ ? speculate_ - 1 : 0);
-        if (prefill_tokens + in_len > prefill_budget && !nb.entries.empty()) { queues_.push_front(e); break; }
-        if (in_len > prefill_budget) {          // can never fit: fail it instead of blocking the queue
-          StreamEvent ev;
-          ev.kind = StreamEvent::Error;
-          ev.error = "`inputs` exceed the prefill token budget";
-          ev.error_type = "validation";
-          e->sink->push(ev);
-          continue;
-        }
-        if (decode_tokens + prefill_tokens + need > token_budget && token_budget > 0) { queues_.push_front(e); break; }
-        auto alloc = allocator_->allocate(e->request.adapter.index, need, cfg_.prefix_caching ? &e->request.input_ids : nullptr);
-        if (!alloc) { queues_.push_front(e); break; }
-        e->allocation = std::move(alloc);
-        prefill_tokens += in_len;
-        decode_tokens += max_new;
-        max_blocks = std::max(max_blocks, (uint32_t)e->allocation->blocks.size());
-      }
-      e->batch_time = Clock::now();
+    auto to_request = [&](const std::shared_ptr<Entry>& e) {
       gen::Request r;
       r.id = e->id;
       r.inputs = e->request.inputs;
@@ -295,11 +266,80 @@ class Infer {
         // slots are implied by the blocks (slot = block * block_size + offset); sent only for sliding windows
         if (window_) r.slots = e->allocation->slots;
       }
+      return r;
+    };
+    // Chunked prefill: prompts that did not fit the prefill budget of an earlier step continue first.  Every step carries at
+    // most `prefill_budget` prompt tokens, so the decode steps of the running batch are never held up by one long prompt.
+    bool continued = false;
+    while (!chunking_.empty() && prefill_tokens < prefill_budget) {
+      auto e = chunking_.front();
+      const uint32_t remaining = e->request.input_length - e->prefilled;
+      const uint32_t take = std::min(remaining, prefill_budget - prefill_tokens);
+      gen::Request r = to_request(e);
+      r.cache_len = e->prefilled;
+      if (take < remaining) r.chunk_len = take; else chunking_.pop_front();
+      e->prefilled += take;
+      prefill_tokens += take;
+      max_blocks = std::max(max_blocks, (uint32_t)e->allocation->blocks.size());
       nb.batch.requests.push_back(std::move(r));
+      nb.entries.push_back(e);
+      continued = true;
+      if (take < remaining) break;
+    }
+    while (chunking_.empty() || !continued) {
+      auto e = queues_.next_entry();
+      if (!e) break;
+      const uint32_t in_len = e->request.input_length, max_new = e->request.stopping.max_new_tokens;
+      if (requires_padding_) {
+        // padded models are budgeted by (n + 1) * longest prompt (scheduler.rs:348-368 of the reference)
+        max_input = std::max(max_input, in_len);
+        prefill_tokens = (uint32_t)(nb.entries.size() + 1) * max_input;
+        decode_tokens += max_new;
+        if (prefill_tokens > prefill_budget || prefill_tokens + decode_tokens > token_budget) { queues_.push_front(e); break; }
+      } else {
+        const uint32_t need = in_len + max_new + (speculate_ ? speculate_ - 1 : 0);
+        const bool chunk = cfg_.chunked_prefill && prefill_tokens + in_len > prefill_budget;
+        if (chunk && prefill_tokens >= prefill_budget) { queues_.push_front(e); break; }
+        if (!chunk && prefill_tokens + in_len > prefill_budget && !nb.entries.empty()) { queues_.push_front(e); break; }
+        if (!chunk && in_len > prefill_budget) {          // can never fit: fail it instead of blocking the queue
+          StreamEvent ev;
+          ev.kind = StreamEvent::Error;
+          ev.error = "`inputs` exceed the prefill token budget";
+          ev.error_type = "validation";
+          e->sink->push(ev);
+          continue;
+        }
+        if (decode_tokens + prefill_tokens + need > token_budget && token_budget > 0) { queues_.push_front(e); break; }
+        auto alloc = allocator_->allocate(e->request.adapter.index, need, cfg_.prefix_caching ? &e->request.input_ids : nullptr);
+        if (!alloc) { queues_.push_front(e); break; }
+        e->allocation = std::move(alloc);
+        decode_tokens += max_new;
+        max_blocks = std::max(max_blocks, (uint32_t)e->allocation->blocks.size());
+        e->batch_time = Clock::now();
+        gen::Request r = to_request(e);
+        if (chunk && r.cache_len + (prefill_budget - prefill_tokens) < in_len) {
+          // only the first part of this prompt fits the step: the rest follows in later steps
+          const uint32_t take = prefill_budget - prefill_tokens;
+          r.chunk_len = take;
+          e->prefilled = r.cache_len + take;
+          prefill_tokens += take;
+          chunking_.push_back(e);
+          continued = true;
+          nb.batch.requests.push_back(std::move(r));
+          nb.entries.push_back(e);
+          break;
+        }
+        prefill_tokens += in_len;
+        nb.batch.requests.push_back(std::move(r));
+        nb.entries.push_back(e);
+        continue;
+      }
+      e->batch_time = Clock::now();
+      nb.batch.requests.push_back(to_request(e));
       nb.entries.push_back(e);
     }
     if (nb.entries.empty()) return std::nullopt;
-    if (min_size && nb.entries.size() < *min_size) {
+    if (min_size && !continued && nb.entries.size() < *min_size) {
       // not worth interrupting decode: put everything back in order
       for (auto it = nb.entries.rbegin(); it != nb.entries.rend(); ++it) {
         if ((*it)->allocation) { allocator_->free(*(*it)->allocation, (*it)->request.adapter.index, nullptr); (*it)->allocation.reset(); }
@@ -410,7 +450,7 @@ class Infer {
       std::optional<NextBatch> nb;
       {
         std::unique_lock<std::mutex> g(mu_);
-        cv_.wait_for(g, std::chrono::milliseconds(50), [&] { return !running_ || queues_.queued() > 0; });
+        cv_.wait_for(g, std::chrono::milliseconds(50), [&] { return !running_ || queues_.queued() > 0 || !chunking_.empty(); });
         if (!running_) break;
         nb = next_batch({}, std::nullopt, cfg_.max_batch_prefill_tokens, cfg_.max_batch_total_tokens);
       }
@@ -421,25 +461,29 @@ class Infer {
         auto cached = run_prefill(*nb, entries);
         if (cached) batches.push_back(*cached);
         uint32_t waiting_tokens = 1;
-        while (!batches.empty() && running_) {
+        while (running_) {
+          bool chunks_pending;
+          { std::lock_guard<std::mutex> g(mu_); chunks_pending = !chunking_.empty(); }
+          if (batches.empty() && !chunks_pending) break;
           uint32_t batch_size = 0, batch_max_tokens = 0;
           for (auto& b : batches) { batch_size += b.size; batch_max_tokens += b.max_tokens; }
           if (metrics_) { metrics_->set("lorax_batch_current_size", batch_size); metrics_->set("lorax_batch_current_max_tokens", batch_max_tokens); }
           std::optional<size_t> min_size;
           if (waiting_tokens < cfg_.max_waiting_tokens) min_size = (size_t)(batch_size * cfg_.waiting_served_ratio);
           if (cfg_.eager_prefill && min_size) min_size = std::min<size_t>(*min_size, 1);
+          if (chunks_pending) min_size.reset();            // the rest of a started prompt does not wait
           uint32_t token_budget = cfg_.max_batch_total_tokens > batch_max_tokens ? cfg_.max_batch_total_tokens - batch_max_tokens : 0;
           std::optional<NextBatch> more;
           if (token_budget > 0) {
             std::set<uint32_t> in_use;
             for (auto& kv : entries) in_use.insert(kv.second->request.adapter.index);
             std::lock_guard<std::mutex> g(mu_);
-            if (queues_.queued() > 0) more = next_batch(in_use, min_size, cfg_.max_batch_prefill_tokens, token_budget);
+            if (queues_.queued() > 0 || !chunking_.empty()) more = next_batch(in_use, min_size, cfg_.max_batch_prefill_tokens, token_budget);
           }
           if (more) {
             if (metrics_) metrics_->inc("lorax_batch_concat", {{"reason", min_size ? "backpressure" : "wait_exceeded"}});
             waiting_tokens = 1;
-            if (fused_prefill_decode_) {
+            if (fused_prefill_decode_ && !batches.empty()) {
               // one forward pass on the shards: the new prompts AND one decode step of everything that is running
               for (auto& e : more->entries) entries[e->id] = e;
               auto t0 = Clock::now();
@@ -458,6 +502,7 @@ class Infer {
             if (c2) batches.push_back(*c2);
           }
           waiting_tokens++;
+          if (batches.empty()) continue;                     // only prompt chunks so far: nothing decodes yet
           auto t0 = Clock::now();
           BatchSpan bs(this, "decode", entries);
           auto res = client_->decode(batches);
@@ -471,6 +516,7 @@ class Infer {
         healthy_ = true;
       } catch (const std::exception& ex) {
         healthy_ = false;
+        { std::lock_guard<std::mutex> g(mu_); chunking_.clear(); }
         if (metrics_) metrics_->inc("lorax_batch_inference_failure");
         fail_all(entries, std::string("Request failed during generation: ") + ex.what());
         try { client_->clear_cache(std::nullopt); } catch (...) {}
@@ -589,6 +635,7 @@ class Infer {
   std::shared_ptr<ShardedClient> client_;
   RouterConfig cfg_;
   Metrics* metrics_;
+  std::deque<std::shared_ptr<Entry>> chunking_;      // entries whose prompt is only partly prefilled (guarded by mu_)
   telemetry::Tracer* tracer_ = nullptr;
   telemetry::SpanContext loop_ctx_;        // parent of every batch span: the "batching_task" span of this process
   std::mutex mu_;

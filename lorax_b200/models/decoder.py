@@ -468,6 +468,8 @@ class DecoderModel:
             hidden = hidden.index_select(0, inp.lm_head_indices.long()) if hidden.device.type == "cpu" else hidden[inp.lm_head_indices.long()]
         if self.keep_hidden:
             self.last_hidden = hidden          # rows match the returned logits (Medusa heads read them)
+        if hidden.shape[0] == 0:               # a step of prompt chunks only: keys and values are written, no row is scored
+            return torch.empty(0, self.vocab, dtype=hidden.dtype, device=hidden.device)
         return self.lm_head_forward(hidden, inp)
 
     def lm_head_forward(self, hidden: torch.Tensor, inp: StepInputs) -> torch.Tensor:

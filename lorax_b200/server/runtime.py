@@ -451,17 +451,28 @@ class ShardRuntime:
             prof.step()
         if len(req.decode_batches):
             return self._prefill_and_decode(req)
-        seqs, items = self._new_sequences(req.batch)
-        next_ids, lps, logits = self.runner.prefill(items)
+        seqs, items, chunks = self._new_sequences(req.batch)
+        next_ids, lps, logits = self.runner.prefill(items + chunks)
+        if not items:                                       # prompt chunks only: nothing to emit yet
+            return self.pb.PrefillResponse()
         return self._finish_prefill(req.batch, seqs, items, next_ids, lps, logits)
 
     def _new_sequences(self, batch):
-        items, seqs = [], []
+        """-> (sequences, their prefill items, items of prompt chunks that do not reach the end of their prompt).  A request
+        with `chunk_len` set and `cache_len + chunk_len` short of its prompt is such a chunk: its keys and values are written
+        and nothing else happens; the router sends the rest of the prompt in later Prefill calls with a larger `cache_len`
+        (chunked prefill: reference `server.py:93-123`, `flash_causal_lm.py:171-389`)."""
+        items, seqs, chunks = [], [], []
         max_in = self.cfg.max_input_length
         for r in batch.requests:
             ids = list(r.tokenized_inputs.ids) if r.HasField("tokenized_inputs") and len(r.tokenized_inputs.ids) else self.tokenize(r.inputs)
             trunc = r.truncate or max_in
             ids = ids[-trunc:]
+            if r.HasField("chunk_len") and r.cache_len + r.chunk_len < len(ids):
+                lora_index = r.adapter_index if (r.adapter_index == 0 or self.adapters.is_loaded(r.adapter_index)) else 0
+                chunks.append(PrefillItem(ids[r.cache_len: r.cache_len + r.chunk_len], r.cache_len, list(r.blocks), lora_index,
+                                          want_logits=False))
+                continue
             params = self._params_from_pb(r.parameters)
             stopping = StoppingCriteria(r.stopping_parameters.max_new_tokens or 1, self.eos_ids, list(r.stopping_parameters.stop_sequences),
                                         r.stopping_parameters.ignore_eos_token)
@@ -477,7 +488,7 @@ class ShardRuntime:
             seqs.append(s)
             items.append(PrefillItem(ids[r.cache_len:] if r.cache_len else ids, r.cache_len, list(r.blocks), lora_index,
                                      all_logprobs=r.prefill_logprobs))
-        return seqs, items
+        return seqs, items, chunks
 
     def _finish_prefill(self, batch, seqs, items, next_ids, lps, logits, merge_with: Optional[List[int]] = None, merged_id: Optional[int] = None,
                         extra_generations=()):
@@ -537,15 +548,21 @@ class ShardRuntime:
         if not rids:
             raise RuntimeError("all batches of the fused Prefill request are missing from the cache")
         old = [self.seqs[r] for r in rids]
-        seqs, items = self._new_sequences(req.batch)
+        seqs, items, chunks = self._new_sequences(req.batch)
         plain = all(s.params.plain and s.grammar is None for s in old + seqs)
-        if not (plain and self.cfg.speculative_tokens == 0 and not any(it.all_logprobs for it in items) and self.runner.can_mix()
+        if not (plain and not chunks and self.cfg.speculative_tokens == 0 and not any(it.all_logprobs for it in items) and self.runner.can_mix()
                 and self.runner.state.high_water + sum(len(it.token_ids) for it in items) <= self.runner.max_prefill_tokens):
             # same result in two passes: decode the running batches, then prefill the new one into the merged batch
             self.fused_stats["two_pass"] += 1
             d = self.decode(pb.DecodeRequest(batches=list(req.decode_batches)))
             survivors = list(self.batches.pop(bids[0], [])) if d.HasField("batch") else []
-            next_ids, lps, logits = self.runner.prefill(items)
+            next_ids, lps, logits = self.runner.prefill(items + chunks)
+            if not items:                                   # prompt chunks only: the decode step is the whole answer
+                resp = pb.PrefillResponse(generations=d.generations)
+                if survivors:
+                    self.batches[bids[0]] = survivors
+                    resp.batch.CopyFrom(self._cached(bids[0]))
+                return resp
             return self._finish_prefill(req.batch, seqs, items, next_ids, lps, logits, merge_with=survivors, merged_id=bids[0],
                                         extra_generations=d.generations)
         self.fused_stats["one_pass"] += 1

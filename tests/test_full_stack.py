@@ -106,7 +106,7 @@ def stack(tmp_path_factory):
     if not ok:
         proc.kill()
         raise RuntimeError("router did not come up: " + proc.stdout.read().decode()[-2000:])
-    yield dict(port=port, root=root, rt=rt, model=model, cfg=cfg, received=received)
+    yield dict(port=port, root=root, rt=rt, model=model, cfg=cfg, received=received, uds=uds)
     sink.shutdown()
     rt.tracer.shutdown()
     proc.terminate()
@@ -286,3 +286,48 @@ def test_tracing_and_request_logger(stack):
     assert {s["name"] for s in children} >= {"Prefill", "Decode"}
     assert all(s["traceId"] == root["traceId"] for s in children)
     assert logged[0]["output"] == want_text and logged[0]["generated_tokens"] == 4 and logged[0]["model_id"] == "tiny"
+
+
+def test_chunked_prefill_matches_unchunked(stack):
+    """A second router on the same shard with `--chunked-prefill` and a prefill budget of 24 tokens: prompts of up to 60 tokens
+    are prefilled in several steps (interleaved with the decode steps of running requests) and generate the same tokens."""
+    import concurrent.futures as cf
+    prompts = [" ".join(f"w{(7 * i + 3 * j) % 500 + 2}" for i in range(n)) for j, n in enumerate((60, 9, 47, 30))]
+    bodies = [{"inputs": p, "parameters": {"max_new_tokens": 6, "details": True, **({"adapter_id": str(stack["root"] / "adapter0"),
+                                                                                      "adapter_source": "local"} if j == 2 else {})}}
+              for j, p in enumerate(prompts)]
+    want = [json.loads(_post(stack["port"], "/generate", b)[1])["generated_text"] for b in bodies]
+    port = _free_port()
+    proc = subprocess.Popen([ROUTER, "--port", str(port), "--hostname", "127.0.0.1", "--master-shard-uds-path", stack["uds"], "--num-shard", "1",
+                             "--max-input-length", "64", "--max-total-tokens", "128", "--max-batch-prefill-tokens", "24",
+                             "--chunked-prefill", "true", "--model-id", "tiny", "--adapter-source", "local"],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    try:
+        for _ in range(100):
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1) as r:
+                    if r.status == 200:
+                        break
+            except Exception:
+                time.sleep(0.1)
+        seen = []
+        inner = stack["rt"]._new_sequences
+
+        def spy(batch):
+            out = inner(batch)
+            seen.append((len(out[1]), [len(c.token_ids) for c in out[2]]))
+            return out
+        stack["rt"]._new_sequences = spy
+        with cf.ThreadPoolExecutor(4) as ex:
+            got = list(ex.map(lambda b: _post(port, "/generate", b), bodies))
+        stack["rt"]._new_sequences = inner
+        assert [g[0] for g in got] == [200] * 4, got
+        assert [json.loads(g[1])["generated_text"] for g in got] == want
+        assert any(chunks for _, chunks in seen) and all(sum(c) <= 24 for _, c in seen)       # some steps carried prompt chunks
+        assert not stack["rt"].seqs
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=10)
+        except subprocess.TimeoutExpired:
+            proc.kill()
