@@ -22,6 +22,7 @@ Every device-side wait is bounded; `check()` reads the status word.
 from __future__ import annotations
 
 import ctypes
+import json
 import os
 from typing import Optional
 
@@ -166,6 +167,30 @@ class FusedCollectives:
         self.ar_calls += 1
         return self.ar_out[: T * N].view(T, N)
 
+    def all_reduce_self_test(self) -> bool:
+        """Two reductions of known values (a small and a large one, odd sizes) against the exact sums.  The verdict is combined
+        over the ranks with NCCL, so either every rank uses the kernel or none does."""
+        import torch.distributed as dist
+        ok = True
+        for T in (3, 517):
+            N = 4096 if self.ar_capacity >= 517 * 4096 else max(8, (self.ar_capacity // 517) // 8 * 8)
+            x = torch.arange(T * N, device=self.tp.device, dtype=torch.float32).remainder(7).add(self.rank + 1).view(T, N).to(torch.bfloat16)
+            got = self.all_reduce(x)
+            if got is None:
+                ok = False
+                break
+            want = torch.arange(T * N, device=self.tp.device, dtype=torch.float32).remainder(7).view(T, N) * self.world + \
+                self.world * (self.world + 1) / 2
+            torch.cuda.synchronize(self.tp.device)
+            ok = ok and bool(torch.equal(got.float(), want))
+        try:
+            self.ws.check_status()
+        except Exception:
+            ok = False
+        flag = torch.tensor([1.0 if ok else 0.0], device=self.tp.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.tp.group)
+        return bool(flag.item() > 0)
+
     def check(self):
         self.ws.check_status()
 
@@ -177,6 +202,9 @@ def enable(tp, model, max_rows: int = 512) -> FusedCollectives:
     if os.environ.get("LORAX_SYM_ALLREDUCE", "1") != "0" and not model.config.parallel_residual:
         # (with parallel residuals two all-reduce results are alive at once; the kernel keeps one output area)
         fc.setup_all_reduce(int(os.environ.get("LORAX_SYM_ALLREDUCE_TOKENS", "4352")), model.hidden)
+        if not fc.all_reduce_self_test():
+            fc.ar_ptrs = None                   # every rank agrees (the verdict is itself reduced): NCCL carries the all-reduces
+            print(json.dumps({"level": "WARN", "message": "two-shot all-reduce kernel failed its self test; using NCCL"}), flush=True)
     if model.embed is not None and model.embed.is_cuda and model.embed.dtype == torch.bfloat16 and model.pos_embed is None:
         model.embed = fc.share_embedding(model.embed, model.vocab_local * tp.world_size)
     tp.fused = fc
