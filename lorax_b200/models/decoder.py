@@ -104,6 +104,9 @@ class StepInputs:
     # the weights then serves both, which is what a prefill costs least when a decode batch is running anyway.
     n_decode: int = 0
     dec_block_tables: Optional[torch.Tensor] = None
+    # vision-language prompts: rows of the embedded sequence that are replaced by projected image features
+    embed_rows: Optional[torch.Tensor] = None
+    embed_values: Optional[torch.Tensor] = None
 
 
 class DecoderModel:
@@ -434,6 +437,8 @@ class DecoderModel:
                           mult=c.embedding_multiplier)
             if self.tp.world_size > 1:
                 h = self.tp.all_reduce(h)
+        if inp.embed_rows is not None:
+            h = h.index_copy(0, inp.embed_rows + inp.n_decode, inp.embed_values.to(h.dtype))
         if self.pos_embed is not None:
             h = h + self.pos_embed[inp.positions.long() + c.position_offset]
         if self.embed_norm is not None:

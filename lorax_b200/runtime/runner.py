@@ -39,6 +39,10 @@ class PrefillItem:
     adapter_index: int = 0
     want_logits: bool = True        # False for a non-final chunk
     all_logprobs: bool = False      # prefill token log-probs requested (decoder_input_details)
+    # vision-language prompts: rows `embed_index` (positions within token_ids) take `embeds` [len(embed_index), hidden] instead
+    # of the embedding of their (placeholder) token id
+    embed_index: Optional[Sequence[int]] = None
+    embeds: Optional[torch.Tensor] = None
 
 
 class DecodeState:
@@ -153,8 +157,13 @@ class ModelRunner:
         cu = [0]
         cache_lens, tables, head_idx, tok_slot, head_slot, q_lens = [], [], [], [], [], []
         any_lora = False
+        over_rows: List[int] = []
+        over_vals: List[torch.Tensor] = []
         for it in items:
             n = len(it.token_ids)
+            if it.embeds is not None and len(it.embed_index or ()):
+                over_rows += [cu[-1] + int(i) for i in it.embed_index]
+                over_vals.append(it.embeds)
             row = self._table_row(it.blocks)
             slot_id = self._slot_of(it.adapter_index)
             any_lora |= slot_id >= 0
@@ -198,6 +207,9 @@ class ModelRunner:
                          cache_lens=d_cl, tile_seq=d_ts, tile_q0=d_tq, lm_head_indices=d_head if len(head_idx) else d_ids[:0],
                          tok_slot=d_tokslot if any_lora else None, head_tok_slot=d_headslot if any_lora else None,
                          lora_tiles=tiles)
+        if over_rows:
+            inp.embed_rows = torch.tensor(over_rows, dtype=torch.long, device=self.model.device)
+            inp.embed_values = torch.cat(over_vals, 0).to(self.model.dtype).to(self.model.device)
         return inp, any_lora
 
     def prefill(self, items: Sequence[PrefillItem]):
@@ -248,7 +260,8 @@ class ModelRunner:
                          slots=cat([st.slots[:nd], pin.slots]), is_prefill=True, block_tables=pin.block_tables, cu_q=pin.cu_q,
                          cache_lens=pin.cache_lens, tile_seq=pin.tile_seq, tile_q0=pin.tile_q0, lm_head_indices=head,
                          tok_slot=tok_slot, head_tok_slot=head_slot, lora_tiles=tiles, attn_nsplit=nsplit, n_decode=nd,
-                         dec_block_tables=st.block_tables[:nd], ctx_lens=st.ctx_lens[:nd])
+                         dec_block_tables=st.block_tables[:nd], ctx_lens=st.ctx_lens[:nd], embed_rows=pin.embed_rows,
+                         embed_values=pin.embed_values)
         logits = self.model.forward(inp, self.kv.layers)
         ids, lps = self.model.ops.argmax_logprob(logits, softcap=self.model.config.final_logit_softcapping or 0.0)
         st.next_ids[:nd].copy_(ids[:nd])

@@ -10,6 +10,7 @@ concatenate`, `generate_token`) and `models/model.py` (`decode_token`, `load_ada
 
 from __future__ import annotations
 
+import collections
 import json
 import os
 import threading
@@ -805,6 +806,85 @@ class Seq2SeqRuntime(ShardRuntime):
         return self.pb.ClassifyResponse(errorMsg="this model is not a classifier")
 
 
+class VlmRuntime(ShardRuntime):
+    """Shard runtime of a vision-language model (LLaVA-NeXT): prompts may contain images as markdown, `![](data:image/png;base64,...)`
+    or `![](http://...)`.  Tokenisation (which the router delegates to shard 0) replaces every image by as many `<image>` token ids
+    as the image yields feature rows; Prefill computes those rows (vision tower, projector, any-resolution packing) and splices
+    them into the decoder's input embeddings.  Everything else is the decoder runtime (reference: `VlmCausalLM`,
+    `server/lorax_server/models/vlm_causal_lm.py`; image chunking `router/src/validation.rs:498-638`)."""
+
+    def __init__(self, vlm_model, tokenizer=None, cfg: Optional[EngineConfig] = None, model_id: str = "", **kw):
+        super().__init__(vlm_model.text, tokenizer, cfg, model_id=model_id, **kw)
+        self.vlm = vlm_model
+        self._images: "collections.OrderedDict[str, tuple]" = collections.OrderedDict()      # uri -> (tiles, (h, w)), most recent last
+
+    def _image(self, uri: str):
+        hit = self._images.get(uri)
+        if hit is not None:
+            self._images.move_to_end(uri)
+            return hit
+        from ..models.vlm import load_image
+        tiles, size = self.vlm.pixel_values(load_image(uri))
+        self._images[uri] = (tiles, size)
+        while len(self._images) > 32:
+            self._images.popitem(last=False)
+        return tiles, size
+
+    def tokenize(self, text: str, add_special: bool = True) -> List[int]:
+        from ..models.vlm import split_prompt
+        parts = split_prompt(text)
+        if not any(k == "image" for k, _ in parts):
+            return super().tokenize(text, add_special)
+        ids: List[int] = []
+        first = True
+        for kind, val in parts:
+            if kind == "text":
+                ids += super().tokenize(val, add_special and first)
+            else:
+                _, (h, w) = self._image(val)
+                ids += [self.vlm.config.image_token_index] * self.vlm.num_image_features(h, w)
+            first = False
+        return ids
+
+    def tokenize_detailed(self, body: dict) -> list:
+        text = body.get("inputs", "")
+        if "![](" not in text:
+            return super().tokenize_detailed(body)
+        return [{"id": i, "text": "<image>" if i == self.vlm.config.image_token_index else self._tok_text(i), "start": 0, "stop": 0}
+                for i in self.tokenize(text, body.get("add_special_tokens", True))]
+
+    def _new_sequences(self, batch):
+        from ..models.vlm import split_prompt
+        seqs, items, chunks = super()._new_sequences(batch)
+        tok = self.vlm.config.image_token_index
+        ii = ci = 0
+        for r in batch.requests:
+            ids = list(r.tokenized_inputs.ids) if r.HasField("tokenized_inputs") and len(r.tokenized_inputs.ids) else self.tokenize(r.inputs)
+            ids = ids[-(r.truncate or self.cfg.max_input_length):]
+            is_chunk = r.HasField("chunk_len") and r.cache_len + r.chunk_len < len(ids)
+            item = chunks[ci] if is_chunk else items[ii]
+            if is_chunk:
+                ci += 1
+            else:
+                ii += 1
+            where = [p for p, t in enumerate(ids) if t == tok]
+            if not where:
+                continue
+            uris = [v for k, v in split_prompt(r.inputs) if k == "image"]
+            with torch.inference_mode():
+                feats = torch.cat([self.vlm.image_features(*self._image(u)) for u in uris], 0) if uris else None
+            if feats is None or feats.shape[0] != len(where):
+                raise ValueError(f"request {r.id}: the prompt holds {len(where)} image positions but its images yield "
+                                 f"{0 if feats is None else feats.shape[0]} feature rows (was the prompt truncated inside an image?)")
+            lo = r.cache_len
+            hi = lo + len(item.token_ids)
+            sel = [j for j, p in enumerate(where) if lo <= p < hi]
+            if sel:
+                item.embed_index = [where[j] - lo for j in sel]
+                item.embeds = feats[sel[0]: sel[-1] + 1]
+        return seqs, items, chunks
+
+
 class EncoderRuntime:
     """Shard runtime of an embedding / token-classification model (BERT, RoBERTa, DistilBERT): `Embed` and `Classify`
     are served, every generation RPC answers with an error (reference: `FlashBert.embed/classify`,
@@ -895,6 +975,15 @@ def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel]
         w = Weights(weight_files(model_dir), device="cpu", dtype=dtype)
         s2s = Seq2SeqModel.from_weights(Seq2SeqConfig.from_dict(raw_cfg), w, dev, dtype)
         return Seq2SeqRuntime(s2s, load_tokenizer(model_dir), cfg, model_id=model_id)
+    from ..models.vlm import VLM_TYPES, LlavaNextConfig, LlavaNextModel
+    if raw_cfg.get("model_type") in VLM_TYPES:
+        vcfg = LlavaNextConfig.from_dict(raw_cfg)
+        w = Weights(weight_files(model_dir), device="cpu", dtype=dtype, rank=tp.rank, world_size=tp.world_size)
+        tp.barrier()
+        vm = LlavaNextModel.from_weights(vcfg, w, dev, dtype, tp, max_positions=min(vcfg.text.max_position_embeddings,
+                                                                                    max(cfg.max_total_tokens + 64, 2048)))
+        kw.pop("quantize", None)
+        return VlmRuntime(vm, load_tokenizer(model_dir), cfg, model_id=model_id, **kw)
     if raw_cfg.get("model_type") in ENCODER_TYPES:
         w = Weights(weight_files(model_dir), device="cpu", dtype=dtype)
         enc = EncoderModel.from_weights(EncoderConfig.from_dict(raw_cfg), w, dev, dtype)

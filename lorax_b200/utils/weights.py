@@ -127,6 +127,9 @@ class Weights(AbstractWeights):
     def get_shape(self, name: str):
         return tuple(self._slice(name).get_shape())
 
+    def keys(self):
+        return list(self.routing.keys())
+
     def _finish(self, t: torch.Tensor) -> torch.Tensor:
         if self.dtype is not None and t.dtype.is_floating_point and t.dtype not in (torch.float8_e4m3fn, torch.float8_e5m2):
             t = t.to(self.dtype)
@@ -200,6 +203,9 @@ class InMemoryWeights(AbstractWeights):
 
     def _raw(self, name):
         return self.tensors.get(name)
+
+    def keys(self):
+        return list(self.tensors.keys())
 
     def get_tensor(self, name):
         if name not in self.tensors and self._quant_base(name) is not None:
