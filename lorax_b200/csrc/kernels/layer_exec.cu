@@ -43,6 +43,18 @@ int lx_lora_expand_tiled(const float* v, int ldv, long long v_split_stride, int 
 int lx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
                  long long ldw, long long ldo, float out_scale, void* ws, long long ws_bytes, int* counters,
                  int* status, int num_sms, int mode, int force_split, void* stream_);
+int lx_allreduce_sym(const unsigned long long* peer_ptrs, int rank, int world, long long in_off, long long out_off, long long cnt_off,
+                     long long n_elems, int* state, int* status, void* stream);
+
+// The two-shot all-reduce of a tensor-parallel group as the layer loop needs it: every partial sum is written into the input
+// area of the rank's symmetric buffer and the reduced activations are read from its output area.
+struct LxAllReduce {
+  const unsigned long long* peer_ptrs;   // base of every rank's symmetric buffer
+  long long in_off, out_off, cnt_off;    // byte offsets inside the buffer
+  int* state;                            // two device ints (launch counter, finished blocks)
+  int* status;
+  int rank, world;
+};
 
 // One LoRA site of a layer (QKV, O, gate_up, down): where its A_cat / B_cat sit inside every adapter blob.
 struct LxLoraSite {
@@ -195,6 +207,30 @@ int lx_layer_mlp(const LxModelDesc* m, const LxLayerDesc* l, const LxStepDesc* s
                           stream));
   LX_TRY(lx_act_mul(s->gate_up, s->act, T, m->inter, m->n_gate_up, m->inter, m->act, m->gated, stream));
   return linear_with_lora(*m, *l, *s, 3, s->act, m->inter, l->down_w, l->ld_down, l->down_b, out, H, H, m->n_down_in, stream);
+}
+
+int lx_allreduce_desc_bytes() { return (int)sizeof(LxAllReduce); }
+
+// Every layer of the model in one call: attention half, all-reduce, MLP half, all-reduce (the collectives only with `ar`, i.e.
+// under tensor parallelism).  `residual` [T, H] holds the embedded tokens on entry and the residual stream on return; the output
+// of the last MLP half that still has to be added to it is at `*pending_out` (inside the symmetric buffer with `ar`, else `scratch`,
+// which must hold T * H elements).
+int lx_run_layers(const LxModelDesc* m, const LxLayerDesc* layers, int n_layers, const LxStepDesc* s, void* residual, float x_scale,
+                  const LxAllReduce* ar, void* scratch, void** pending_out, void* stream) {
+  const long long n = (long long)s->T * m->H;
+  unsigned char* base = ar ? reinterpret_cast<unsigned char*>(ar->peer_ptrs[ar->rank]) : nullptr;
+  void* part = ar ? static_cast<void*>(base + ar->in_off) : scratch;      // where a half writes its (partial) result
+  void* full = ar ? static_cast<void*>(base + ar->out_off) : scratch;     // where the next half reads the complete one
+  const void* pending = nullptr;
+  for (int li = 0; li < n_layers; ++li) {
+    LX_TRY(lx_layer_attention(m, &layers[li], s, pending, residual, x_scale, part, stream));
+    if (ar) LX_TRY(lx_allreduce_sym(ar->peer_ptrs, ar->rank, ar->world, ar->in_off, ar->out_off, ar->cnt_off, n, ar->state, ar->status, stream));
+    LX_TRY(lx_layer_mlp(m, &layers[li], s, full, residual, x_scale, part, stream));
+    if (ar) LX_TRY(lx_allreduce_sym(ar->peer_ptrs, ar->rank, ar->world, ar->in_off, ar->out_off, ar->cnt_off, n, ar->state, ar->status, stream));
+    pending = full;
+  }
+  *pending_out = const_cast<void*>(pending);
+  return 0;
 }
 
 }  // extern "C"

@@ -58,6 +58,10 @@ class LxStepDesc(Structure):
                 ("normed", P), ("qkv", P), ("attn", P), ("gate_up", P), ("act", P)]
 
 
+class LxAllReduce(ctypes.Structure):
+    _fields_ = [("peer_ptrs", P), ("in_off", L), ("out_off", L), ("cnt_off", L), ("state", P), ("status", P), ("rank", I), ("world", I)]
+
+
 def _p(t: Optional[torch.Tensor]):
     return None if t is None else t.data_ptr()
 
@@ -89,6 +93,11 @@ class NativeExecutor:
             fn.restype = I
             if fn() != ctypes.sizeof(st):
                 raise RuntimeError(f"{name}: C++ says {fn()} bytes, ctypes says {ctypes.sizeof(st)}")
+        if lib.lx_allreduce_desc_bytes() != ctypes.sizeof(LxAllReduce):
+            raise RuntimeError("lx_allreduce_desc_bytes: C++ and ctypes disagree")
+        lib.lx_run_layers.argtypes = [POINTER(LxModelDesc), POINTER(LxLayerDesc), I, POINTER(LxStepDesc), P, F, POINTER(LxAllReduce), P,
+                                      POINTER(ctypes.c_void_p), P]
+        lib.lx_run_layers.restype = I
         for name in ("lx_layer_attention", "lx_layer_mlp"):
             fn = getattr(lib, name)
             fn.argtypes = [POINTER(LxModelDesc), POINTER(LxLayerDesc), POINTER(LxStepDesc), P, P, F, P, P]
@@ -202,7 +211,27 @@ class NativeExecutor:
         dst = fused.all_reduce_input(T, m.H) if fused is not None else None
         buf_a = dst if dst is not None else out_a
         buf_b = dst if dst is not None else out_b
-        for li in range(len(model.layers)):
+        nL = len(model.layers)
+        if tp.world_size == 1 or dst is not None:
+            # the whole layer loop in one native call (under tensor parallelism with the all-reduce kernel launched from there too)
+            ar = None
+            if tp.world_size > 1:
+                ar = LxAllReduce(peer_ptrs=ctypes.cast(fused.ar_ptrs, P), in_off=0, out_off=fused.ar_area, cnt_off=2 * fused.ar_area,
+                                 state=fused.ar_state.data_ptr(), status=fused.ws.status.data_ptr(), rank=tp.rank, world=tp.world_size)
+            out_ptr = ctypes.c_void_p()
+            rc = lib.lx_run_layers(ctypes.byref(m), self.layers, nL, ctypes.byref(s), residual.data_ptr(), rm,
+                                   ctypes.byref(ar) if ar is not None else None, out_a.data_ptr(), ctypes.byref(out_ptr), stream)
+            native._check(rc, "lx_run_layers")
+            pending = fused.ar_out[: T * m.H].view(T, m.H) if ar is not None else out_a
+            assert out_ptr.value == pending.data_ptr()
+            lora_sites = 4 if s.tok_slot else 0
+            attn_kernels = (1 if s.n_decode else 0) + (1 if T > s.n_decode else 0)
+            native.launch_count += nL * (10 + attn_kernels + 2 * lora_sites + (2 if ar is not None else 0)) - 1      # `_check` counted one
+            if ar is not None:
+                fused.ar_calls += 2 * nL
+            self._keep = [normed, qkv, attn, gate_up, act, out_a, inp, ar]
+            return pending, residual
+        for li in range(nL):
             l = ctypes.byref(self.layers[li])
             rc = lib.lx_layer_attention(ctypes.byref(m), l, ctypes.byref(s), _p(pending), residual.data_ptr(), rm, buf_a.data_ptr(), stream)
             native._check(rc, "lx_layer_attention")
