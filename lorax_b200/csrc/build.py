@@ -50,12 +50,13 @@ def _digest(paths) -> str:
     return h.hexdigest()
 
 
-def _run(cmd, verbose: bool, log_path: Path | None = None) -> str:
+def _run(cmd, verbose: bool, log_path: Path | None = None, quiet: bool = False) -> str:
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if log_path is not None:
         log_path.write_text(proc.stdout)
     if proc.returncode != 0:
-        sys.stderr.write(" ".join(map(str, cmd)) + "\n" + proc.stdout + "\n")
+        if not quiet:
+            sys.stderr.write(" ".join(map(str, cmd)) + "\n" + proc.stdout + "\n")
         raise RuntimeError(f"build step failed: {cmd[0]} {cmd[-1]}")
     if verbose:
         print(proc.stdout)
@@ -127,6 +128,38 @@ def build_host(force: bool = False, verbose: bool = False):
             _run([cxx, "-o", str(BIN_DIR / exe), str(objs[main_src]), *lib_objs, "-pthread"], verbose)
     stamp.write_text(digest)
     return HOST_SO
+
+
+class SanitizerUnavailable(RuntimeError):
+    pass
+
+
+def build_host_selftest(sanitizer: str, verbose: bool = False) -> Path:
+    """The host code's self test (`csrc/host/selftest/selftest_main.cpp` + the C API) under a sanitizer: "address" (with
+    undefined-behaviour checks) or "thread".  Returns the binary; running it prints OK and exits 0 when nothing was found."""
+    from lorax_b200.server import protogen
+    protogen.main([str(HOST_DIR / "pb_gen.hpp")])
+    BUILD_DIR.mkdir(exist_ok=True)
+    flags = {"address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], "thread": ["-fsanitize=thread"]}[sanitizer]
+    out = BUILD_DIR / f"host_selftest_{sanitizer}"
+    srcs = [HOST_DIR / "selftest" / "selftest_main.cpp", HOST_DIR / "capi.cpp"]
+    stamp = BUILD_DIR / f"host_selftest_{sanitizer}.sha256"
+    digest = _digest(srcs + sorted(HOST_DIR.glob("*.hpp")) + [Path(__file__)])
+    if out.exists() and stamp.exists() and stamp.read_text() == digest:
+        return out
+    # not every toolchain ships the sanitizer runtimes: take the first compiler that links against them
+    last = None
+    for cxx in dict.fromkeys([os.environ.get("CXX", "g++"), "g++", "/usr/bin/g++", "clang++"]):
+        if shutil.which(cxx) is None:
+            continue
+        try:
+            _run([cxx, "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", *flags, "-I", str(HOST_DIR), *map(str, srcs), "-o", str(out),
+                  "-pthread"], verbose, quiet=True)
+            stamp.write_text(digest)
+            return out
+        except RuntimeError as e:
+            last = e
+    raise SanitizerUnavailable(f"no compiler on this machine links -fsanitize={sanitizer}: {last}")
 
 
 def build_all(force: bool = False, verbose: bool = False):

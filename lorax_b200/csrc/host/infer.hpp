@@ -179,7 +179,7 @@ class Infer {
     np.watermark = p.watermark;
     np.return_k_alternatives = p.return_k_alternatives.value_or(0);
     np.schema = p.schema;
-    np.seed = p.seed ? *p.seed : rng_();
+    np.seed = p.seed ? *p.seed : random_seed();
     if (p.stop.size() > cfg_.max_stop_sequences) throw validation_error("`stop` supports up to " + std::to_string(cfg_.max_stop_sequences) + " stop sequences. Given: " + std::to_string(p.stop.size()));
     if (p.truncate && (*p.truncate == 0 || *p.truncate > cfg_.max_input_length)) throw validation_error("`truncate` must be strictly positive and less than " + std::to_string(cfg_.max_input_length) + ". Given: " + std::to_string(*p.truncate));
     if (p.max_new_tokens && *p.max_new_tokens == 0) throw validation_error("`max_new_tokens` must be strictly positive");
@@ -655,7 +655,12 @@ class Infer {
   std::atomic<bool> running_{false}, healthy_{true};
   std::atomic<size_t> in_flight_{0};
   std::thread batch_thread_, loader_thread_;
-  std::mt19937_64 rng_{std::random_device{}()};
+  // validation runs on the HTTP worker threads: one generator per thread (a shared one was a data race, found by the
+  // ThreadSanitizer build of csrc/host/selftest)
+  static uint64_t random_seed() {
+    static thread_local std::mt19937_64 rng{std::random_device{}()};
+    return rng();
+  }
 };
 
 }  // namespace lx

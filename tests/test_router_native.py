@@ -132,3 +132,19 @@ def test_validation_errors():
     out = rn.infer_fake_run([{"inputs": "", "max_new_tokens": 4}, {"inputs": "a", "max_new_tokens": 5000},
                              {"inputs": "a", "max_new_tokens": 2, "top_p": 1.5}])
     assert [r.get("status") for r in out["results"]] == [422, 422, 422]
+
+
+@pytest.mark.parametrize("sanitizer", ["address", "thread"])
+def test_host_code_under_sanitizers(sanitizer):
+    """The allocator, the queues and the batching loop (36 concurrent requests over 6 adapters against the fake shard, then the
+    same with a shard that starts failing) built with AddressSanitizer + UBSan and with ThreadSanitizer: no finding, exit 0."""
+    import os
+    import subprocess
+    from lorax_b200.csrc import build
+    try:
+        exe = build.build_host_selftest(sanitizer)
+    except build.SanitizerUnavailable as e:
+        pytest.skip(str(e))
+    env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", TSAN_OPTIONS="halt_on_error=1", UBSAN_OPTIONS="print_stacktrace=1")
+    r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
+    assert r.returncode == 0 and "OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
