@@ -170,6 +170,13 @@ async def serve_grpc(runtime, uds_path: str, rank: int, world_size: int, lock: O
                     return pb.ServiceDiscoveryResponse(urls=urls)
                 with lock:
                     _select_device(device)                               # per-thread setting, see FramedServer._serve_conn
+                    tracer = getattr(runtime, "tracer", None)
+                    if tracer is not None and tracer.enabled:
+                        # gRPC callers carry the W3C context as metadata (reference: tracing.py:15-53, grpc-metadata/src/lib.rs)
+                        md = {k: v for k, v in (context.invocation_metadata() or ())}
+                        if md.get("traceparent"):
+                            with tracer.span(name, md["traceparent"]):
+                                return _dispatch(runtime, name, request)
                     return _dispatch(runtime, name, request)
             except Exception as e:
                 if runtime.model.device.type == "cuda":
