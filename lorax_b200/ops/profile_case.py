@@ -110,6 +110,18 @@ def gemm_fp8_case(T):
         native.gemm_fp8(x, ws[i % 3][0].view(torch.uint8), ws[i % 3][1], out=out)
 
 
+def gemm_int4_case(T):
+    """Weight-only 4-bit GEMM straight from the packed codes, gate_up shape, three weight sets (> L2 in total)."""
+    from ..utils import quant_formats as qf
+    N, K = 28672, 4096
+    base = qf.quantize_rtn(torch.randn(N, K) * 0.02, 4, 128).to("cuda")
+    ws = [qf.GroupQuantWeight(base.codes.clone(), base.sz.clone(), 4, 128, (N, K)) for _ in range(3)]
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    for i in range(4):
+        native.gemm_wq(x, ws[i % 3], out=out)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", required=True)
@@ -118,6 +130,7 @@ def main():
     {"gemm_decode": lambda: gemm_case(64), "gemm_prefill": lambda: gemm_case(4096), "attn_decode": attn_decode_case,
      "attn_prefill": attn_prefill_case, "gemm_lora_decode": lambda: gemm_lora_case(256), "gemm_lora_decode_gateup": lambda: gemm_lora_case(256, (14336, 14336)), "gemm_lora_prefill": lambda: gemm_lora_case(576),
      "gemm_fp8_decode": lambda: gemm_fp8_case(64), "gemm_fp8_prefill": lambda: gemm_fp8_case(2048), "gemm_mid": lambda: gemm_case(256),
+     "gemm_int4_decode": lambda: gemm_int4_case(8),
      "lora_shrink": lambda: lora_case("shrink"), "lora_expand": lambda: lora_case("expand")}[a.case]()
     torch.cuda.synchronize()
     native.workspace().check_status()
