@@ -39,6 +39,8 @@ def serve(args):
     dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32, None: None}[args.dtype]
     _log("INFO", f"loading {args.model_id} on rank {tp.rank}/{tp.world_size}", args.json_output)
     rt = build_runtime(args.model_id, cfg, tp=tp, dtype=dtype, source=args.source, revision=args.revision, device=args.device)
+    if args.preloaded_adapter_ids:
+        rt.preload_adapters([a.strip() for a in args.preloaded_adapter_ids.split(",")], {"hub": 0, "s3": 1, "local": 2, "pbase": 3}[args.adapter_source])
     if args.adapter_id:
         rt.load_default_adapter(args.adapter_id, {"hub": 0, "s3": 1, "local": 2, "pbase": 3}[args.adapter_source])
     from .tracing import PrefillProfiler, Tracer

@@ -136,6 +136,9 @@ class ShardRuntime:
                             fused_prefill_decode=True)
         if c.sliding_window:
             r.window_size = c.sliding_window
+        for aid, idx in getattr(self, "preloaded", {}).items():
+            r.preloaded_adapters.append(pb.PreloadedAdapter(adapter_parameters=pb.AdapterParameters(adapter_ids=[aid]),
+                                                            adapter_source=getattr(self, "preloaded_source", 0), adapter_index=idx))
         return r
 
     def health(self):
@@ -236,7 +239,32 @@ class ShardRuntime:
         if key in self.medusa_host:
             self.load_medusa(0, *self.medusa_host[key])
         if self.adapters.host.get(key) is not None:
-            self.load_adapter(pb.LoadAdapterRequest(adapter_parameters=params, adapter_source=source, adapter_index=1))
+            idx = 1 + max(list(getattr(self, "preloaded", {}).values()) + [0])
+            self.load_adapter(pb.LoadAdapterRequest(adapter_parameters=params, adapter_source=source, adapter_index=idx))
+            self.preloaded = dict(getattr(self, "preloaded", {}), **{adapter_id: idx})      # announced to the router like a preloaded one
+            self.preloaded_source = source
+
+    def preload_adapters(self, adapter_ids: Sequence[str], source: int = 0, threads: int = 20):
+        """Adapters named at start-up (`--preloaded-adapter-ids`): fetched in parallel, loaded under indices 1..n and announced in
+        `Info`, so the router maps requests for them to those indices and never has to load them on demand (reference:
+        `server.py:342-417`: 20 download threads, then `register_preloaded_adapters`)."""
+        from concurrent.futures import ThreadPoolExecutor
+        pb = self.pb
+        ids = [a for a in adapter_ids if a]
+        if not ids:
+            return
+        first = 1 + max([i for i in getattr(self, "preloaded", {}).values()] + [0])
+
+        def fetch(aid):
+            self.download_adapter(pb.DownloadAdapterRequest(adapter_parameters=pb.AdapterParameters(adapter_ids=[aid]), adapter_source=source))
+        with ThreadPoolExecutor(max_workers=max(1, min(threads, len(ids)))) as ex:
+            list(ex.map(fetch, ids))
+        self.preloaded = dict(getattr(self, "preloaded", {}))
+        self.preloaded_source = source
+        for k, aid in enumerate(ids):
+            self.load_adapter(pb.LoadAdapterRequest(adapter_parameters=pb.AdapterParameters(adapter_ids=[aid]), adapter_source=source,
+                                                    adapter_index=first + k))
+            self.preloaded[aid] = first + k
 
     def load_medusa(self, adapter_index: int, config, tensors):
         """Put Medusa heads on the device under `adapter_index` (0 = default heads for every request).  As in the reference

@@ -181,3 +181,28 @@ def test_medusa_speculation_matches_greedy_and_follows_the_heads(tmp_path):
     got2, steps2 = _run(rt2, prompts, [0, 0], new_tokens)
     assert got2 == want and steps2 <= (max(new_tokens) - 1 + 3) // 4 + 1
     model.keep_hidden = False
+
+
+def test_preloaded_adapters_are_loaded_and_announced(tmp_path):
+    """`--preloaded-adapter-ids`: adapters are fetched in parallel at start-up, sit under indices 1..n and are listed in Info, so
+    the router can address them without a load on demand."""
+    from lorax_b200.adapters.lora import save_peft_adapter
+    cfg = tiny_llama()
+    model = DecoderModel.random_init(cfg, "cpu", torch.float32, seed=0)
+    rt = _runtime(model, 0)
+    dirs = []
+    for i in range(3):
+        c, mm = random_adapter(cfg, r=8, alpha=16, target_modules=["q_proj", "v_proj"], seed=40 + i, std_a=0.05, std_b=0.05)
+        save_peft_adapter(tmp_path / f"ad{i}", c, mm)
+        dirs.append(str(tmp_path / f"ad{i}"))
+    rt.preload_adapters(dirs[:2], source=2)
+    rt.load_default_adapter(dirs[2], source=2)
+    info = rt.info()
+    got = {p.adapter_parameters.adapter_ids[0]: (p.adapter_index, p.adapter_source) for p in info.preloaded_adapters}
+    assert got == {dirs[0]: (1, 2), dirs[1]: (2, 2), dirs[2]: (3, 2)}
+    assert all(rt.adapters.is_loaded(i) for i in (1, 2, 3))
+    g = torch.Generator().manual_seed(8)
+    prompts = [torch.randint(0, cfg.vocab_size, (11,), generator=g).tolist()] * 3
+    out, _ = _run(rt, prompts, [0, 1, 3], [6, 6, 6])
+    assert len({tuple(v) for v in out.values()}) >= 2          # the adapters change the continuation
+    model.adapters = None
