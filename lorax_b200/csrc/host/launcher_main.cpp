@@ -49,6 +49,7 @@ const Flag kFlags[] = {
     {"dtype", "DTYPE", "", "float16 | bfloat16"},
     {"compile", "COMPILE", "true", "capture decode steps in CUDA graphs"},
     {"skip-download", "SKIP_DOWNLOAD", "false", "do not run the download-weights step before the shards start"},
+    {"merge-adapter-weights", "MERGE_ADAPTER_WEIGHTS", "false", "fold --adapter-id into the base weights at load time"},
     {"speculative-tokens", "SPECULATIVE_TOKENS", "", "tokens proposed per step"},
     {"preloaded-adapter-ids", "PRELOADED_ADAPTER_IDS", "", "comma separated"},
     {"max-concurrent-requests", "MAX_CONCURRENT_REQUESTS", "1024", ""},
@@ -332,6 +333,7 @@ int main(int argc, char** argv) {
       if (!c.get(opt).empty()) { args.push_back(std::string("--") + opt); args.push_back(c.get(opt)); }
     if (!c.truthy("compile")) args.push_back("--no-compile");
     if (c.truthy("prefix-caching")) args.push_back("--prefix-caching");
+    if (c.truthy("merge-adapter-weights")) args.push_back("--merge-adapter-weights");
     if (c.truthy("chunked-prefill")) args.push_back("--chunked-prefill");
     std::vector<std::string> env = {"RANK=" + std::to_string(r), "LOCAL_RANK=" + std::to_string(r), "WORLD_SIZE=" + std::to_string(num_shard),
                                     "MASTER_ADDR=" + c.get("master-addr"), "MASTER_PORT=" + c.get("master-port"),

@@ -38,7 +38,10 @@ def serve(args):
     tp = TensorParallel.init_from_env()
     dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32, None: None}[args.dtype]
     _log("INFO", f"loading {args.model_id} on rank {tp.rank}/{tp.world_size}", args.json_output)
-    rt = build_runtime(args.model_id, cfg, tp=tp, dtype=dtype, source=args.source, revision=args.revision, device=args.device)
+    merge = dict(merge_adapter=args.adapter_id, merge_adapter_source=args.adapter_source) if (args.merge_adapter_weights and args.adapter_id) else {}
+    rt = build_runtime(args.model_id, cfg, tp=tp, dtype=dtype, source=args.source, revision=args.revision, device=args.device, **merge)
+    if merge:
+        args.adapter_id = ""                                # it is part of the base weights now
     if args.preloaded_adapter_ids:
         rt.preload_adapters([a.strip() for a in args.preloaded_adapter_ids.split(",")], {"hub": 0, "s3": 1, "local": 2, "pbase": 3}[args.adapter_source])
     if args.adapter_id:
@@ -104,6 +107,7 @@ def main(argv=None):
     s.add_argument("--speculative-tokens", type=int, default=0)
     s.add_argument("--preloaded-adapter-ids", default="")
     s.add_argument("--otlp-endpoint", default=None)
+    s.add_argument("--merge-adapter-weights", action="store_true", help="fold --adapter-id into the base weights at load time")
     s.add_argument("--no-compile", action="store_true")
     s.add_argument("--prefix-caching", action="store_true")
     s.add_argument("--chunked-prefill", action="store_true")

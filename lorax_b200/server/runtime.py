@@ -620,7 +620,9 @@ class ShardRuntime:
             raise RuntimeError("all batches of the Decode request are missing from the cache")
         seqs = [self.seqs[r] for r in rids]
         need_logits = any(not (s.params.plain and s.grammar is None) for s in seqs)
-        if self.cfg.speculative_tokens > 0 and not need_logits:
+        # (large batches decode one token per row: verifying guesses multiplies the rows of the step; reference
+        # LORAX_SPECULATION_MAX_BATCH_SIZE, adapters/medusa.py:162-166)
+        if self.cfg.speculative_tokens > 0 and not need_logits and len(seqs) <= self.cfg.speculation_max_batch_size:
             return self._decode_spec_step(bids, rids, seqs)
         k, b, logits = self.runner.decode(need_logits=need_logits)
         ids_p, lps_p = self.runner.wait(k)
@@ -1022,6 +1024,12 @@ def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel]
     # a GPTQ / AWQ checkpoint: its packed layers are served as they are unless another scheme is asked for
     w.quant = checkpoint_quantization(model_dir, raw_cfg)
     w.keep_packed = quantize in (None, "gptq", "awq")
+    merge_id = kw.pop("merge_adapter", None)
+    if merge_id:
+        # one adapter folded into the base weights while they load; requests then need no adapter id for it
+        from ..utils.weights import MergedWeights
+        lcfg, mm = load_peft_adapter(resolve_adapter(merge_id, kw.pop("merge_adapter_source", "hub")))
+        w = MergedWeights(w, lcfg, mm)
     tp.barrier()
     model = DecoderModel.from_weights(mc, w, dev, dtype, tp, max_positions=min(mc.max_position_embeddings, max(cfg.max_total_tokens + 64, 2048)))
     qc = getattr(mc, "quantization_config", None) or {}

@@ -230,6 +230,40 @@ class InMemoryWeights(AbstractWeights):
         return t.to(self.device)
 
 
+class MergedWeights(AbstractWeights):
+    """A checkpoint with one LoRA adapter folded into it: every `<module>.weight` the adapter targets comes back as
+    W + scale * B A (`--merge-adapter-weights`; the reference writes such a checkpoint to disk first, `utils/adapter.py:331-399`)."""
+
+    def __init__(self, inner: AbstractWeights, lora_config, module_map):
+        self.inner, self.cfg, self.mm = inner, lora_config, module_map
+        self.quant = getattr(inner, "quant", None)
+        self.keep_packed = False                            # the sum needs the dense matrix
+        self.dtype = getattr(inner, "dtype", None)
+        self.merged = 0
+
+    def has_tensor(self, name):
+        return self.inner.has_tensor(name)
+
+    def keys(self):
+        return self.inner.keys()
+
+    def _raw(self, name):
+        return self.inner._raw(name)
+
+    def get_tensor(self, name):
+        keep, self.inner.keep_packed = getattr(self.inner, "keep_packed", True), False
+        try:
+            t = self.inner.get_tensor(name)
+        finally:
+            self.inner.keep_packed = keep
+        mod = name[: -len(".weight")] if name.endswith(".weight") else None
+        if mod in self.mm:
+            from ..adapters.merges import merge_into_base
+            self.merged += 1
+            return merge_into_base(t, self.cfg, {k: v.to(t.device) for k, v in self.mm[mod].items()})
+        return t
+
+
 def checkpoint_quantization(model_dir: os.PathLike, config: Optional[dict] = None) -> Optional[dict]:
     """How the checkpoint's linear layers are stored, from `config.json` (`quantization_config`), AutoGPTQ's
     `quantize_config.json` or AutoAWQ's `quant_config.json`; None for a dense (or block-fp8) checkpoint.  The reference reads

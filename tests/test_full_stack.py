@@ -331,3 +331,35 @@ def test_chunked_prefill_matches_unchunked(stack):
             proc.wait(timeout=10)
         except subprocess.TimeoutExpired:
             proc.kill()
+
+
+def test_merge_adapter_weights_equals_the_adapter_applied_at_run_time(stack):
+    """`--merge-adapter-weights`: the adapter folded into the base weights at load time generates what the same adapter applied
+    per request generates."""
+    from lorax_b200.server.runtime import build_runtime
+    root = stack["root"]
+    ecfg = EngineConfig(max_input_length=64, max_total_tokens=128, max_batch_prefill_tokens=256, compile=False)
+    merged = build_runtime(str(root / "model"), ecfg, device="cpu", dtype=torch.float32, source="local", num_blocks=64, max_batch=4,
+                           merge_adapter=str(root / "adapter1"), merge_adapter_source="local")
+    pb = merged.pb
+    ids = [7, 99, 12, 300, 45, 6]
+
+    def gen(rt, adapter_index):
+        req = pb.Request(id=1, tokenized_inputs=pb.TokenizedInputs(ids=ids), truncate=64, adapter_index=adapter_index, blocks=[1, 2, 3],
+                         parameters=pb.NextTokenChooserParameters(temperature=1.0, top_p=1.0, typical_p=1.0, repetition_penalty=1.0),
+                         stopping_parameters=pb.StoppingCriteriaParameters(max_new_tokens=8, ignore_eos_token=True))
+        resp = rt.prefill(pb.PrefillRequest(batch=pb.Batch(id=900, requests=[req], size=1, max_tokens=64)))
+        out = list(resp.generations[0].next_tokens.ids)
+        cached = resp.batch
+        while True:
+            d = rt.decode(pb.DecodeRequest(batches=[cached]))
+            out += list(d.generations[0].next_tokens.ids)
+            if not d.HasField("batch"):
+                return out
+            cached = d.batch
+    rt = stack["rt"]
+    params = pb.AdapterParameters(adapter_ids=[str(root / "adapter1")])
+    rt.load_adapter(pb.LoadAdapterRequest(adapter_parameters=params, adapter_source=2, adapter_index=77))
+    want = gen(rt, 77)
+    assert gen(merged, 0) == want and gen(rt, 0) != want
+    rt.offload_adapter(pb.OffloadAdapterRequest(adapter_parameters=params, adapter_source=2, adapter_index=77))
