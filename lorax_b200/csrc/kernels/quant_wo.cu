@@ -129,6 +129,16 @@ LX_DEVICE void wq4_expand(uint32_t w, __nv_bfloat162 bias128z, __nv_bfloat162 s2
   }
 }
 
+// The same without the scale: (code - zero) as exact small integers.
+LX_DEVICE void wq4_expand_int(uint32_t w, __nv_bfloat162 bias128z, uint32_t (&o)[4]) {
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint32_t v = ((w >> (4 * j)) & 0x000f000fu) | 0x43004300u;
+    __nv_bfloat162 f = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), bias128z);
+    o[j] = *reinterpret_cast<uint32_t*>(&f);
+  }
+}
+
 struct Wq4Group {
   __nv_bfloat162 bias128z, s2, c2;
 };
@@ -144,7 +154,10 @@ LX_DEVICE Wq4Group wq4_group(__half2 szv) {
 
 // Every warp owns the k-blocks warp, warp + 8, ... of the block's 16 * MT weight rows; the next k-block's codes are in flight
 // while the current one is multiplied.  One activation fragment feeds MT row tiles.
-template <int NT, int MT>                              // token tiles of 8, row tiles of 16
+// EXACT: every 128-wide k-block lies inside one group and the zero points are integers.  The codes then go to the tensor cores as
+// the exact integers (code - zero); the k-block's partial product is scaled by the group's fp16 scale in fp32 on its way into the
+// accumulator: no fma per pair of weights and no bf16 rounding of the scale.
+template <int NT, int MT, bool EXACT>                  // token tiles of 8, row tiles of 16
 __global__ void __launch_bounds__(kWqWarps * 32, 2) wq4_mma_kernel(const Wq4Params p) {
   __shared__ float red[kWqWarps][kWqRows * MT][8 * NT + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -177,8 +190,23 @@ __global__ void __launch_bounds__(kWqWarps * 32, 2) wq4_mma_kernel(const Wq4Para
   if (kb < kblocks) fetch(kb);
   for (; kb < kblocks; kb += kWqWarps) {
     uint32_t a0[MT][4][4], a1[MT][4][4];               // [row tile][word][pair]: rows g and g + 8
+    float s0[MT], s1[MT];
 #pragma unroll
     for (int m = 0; m < MT; ++m) {
+      if constexpr (EXACT) {
+        s0[m] = __low2float(nsz0[m]);
+        s1[m] = __low2float(nsz1[m]);
+        const __nv_bfloat162 z0 = __float2bfloat162_rn(128.f + __high2float(nsz0[m])), z1 = __float2bfloat162_rn(128.f + __high2float(nsz1[m]));
+        wq4_expand_int(nc0[m].x, z0, a0[m][0]);
+        wq4_expand_int(nc0[m].y, z0, a0[m][1]);
+        wq4_expand_int(nc0[m].z, z0, a0[m][2]);
+        wq4_expand_int(nc0[m].w, z0, a0[m][3]);
+        wq4_expand_int(nc1[m].x, z1, a1[m][0]);
+        wq4_expand_int(nc1[m].y, z1, a1[m][1]);
+        wq4_expand_int(nc1[m].z, z1, a1[m][2]);
+        wq4_expand_int(nc1[m].w, z1, a1[m][3]);
+        continue;
+      }
       const Wq4Group g0 = wq4_group(nsz0[m]), g1 = wq4_group(nsz1[m]);
       wq4_expand(nc0[m].x, g0.bias128z, g0.s2, g0.c2, a0[m][0]);
       wq4_expand(nc0[m].y, g0.bias128z, g0.s2, g0.c2, a0[m][1]);
@@ -200,11 +228,19 @@ __global__ void __launch_bounds__(kWqWarps * 32, 2) wq4_mma_kernel(const Wq4Para
         xv[q] = tok < p.T ? __ldg(reinterpret_cast<const uint4*>(p.x + tok * p.ldx + kx + 8 * q)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+        float (&dst)[4] = EXACT ? part : acc[m][j];
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           // the k order inside an MMA is (pair 0 | pair 1) resp. (pair 2 | pair 3) of this lane's word: the same for A and B
-          mma_bf16_16816(acc[m][j], a0[m][q][0], a1[m][q][0], a0[m][q][1], a1[m][q][1], xv[q].x, xv[q].y);
-          mma_bf16_16816(acc[m][j], a0[m][q][2], a1[m][q][2], a0[m][q][3], a1[m][q][3], xv[q].z, xv[q].w);
+          mma_bf16_16816(dst, a0[m][q][0], a1[m][q][0], a0[m][q][1], a1[m][q][1], xv[q].x, xv[q].y);
+          mma_bf16_16816(dst, a0[m][q][2], a1[m][q][2], a0[m][q][3], a1[m][q][3], xv[q].z, xv[q].w);
+        }
+        if constexpr (EXACT) {                         // rows g (c0, c1) and g + 8 (c2, c3) have their own scales
+          acc[m][j][0] = fmaf(s0[m], part[0], acc[m][j][0]);
+          acc[m][j][1] = fmaf(s0[m], part[1], acc[m][j][1]);
+          acc[m][j][2] = fmaf(s1[m], part[2], acc[m][j][2]);
+          acc[m][j][3] = fmaf(s1[m], part[3], acc[m][j][3]);
         }
       }
     }
@@ -234,8 +270,9 @@ __global__ void __launch_bounds__(kWqWarps * 32, 2) wq4_mma_kernel(const Wq4Para
 }
 
 template <int NT, int MT>
-int wq4_launch(const Wq4Params& p, cudaStream_t s) {
-  wq4_mma_kernel<NT, MT><<<p.N / (kWqRows * MT), kWqWarps * 32, 0, s>>>(p);
+int wq4_launch(const Wq4Params& p, bool exact, cudaStream_t s) {
+  if (exact) wq4_mma_kernel<NT, MT, true><<<p.N / (kWqRows * MT), kWqWarps * 32, 0, s>>>(p);
+  else wq4_mma_kernel<NT, MT, false><<<p.N / (kWqRows * MT), kWqWarps * 32, 0, s>>>(p);
   return -(int)cudaGetLastError();
 }
 
@@ -263,8 +300,18 @@ int lx_wq4_max_tokens() { return 32; }
 
 // out[T, N] = x[T, K] . W^T (+ bias) for T <= 32 from affine 4-bit codes.  N % 16 == 0, K % 128 == 0, group % 32 == 0, x rows
 // 16-byte aligned.
+int lx_wq4_gemm_ex(const void* x, long long ldx, const void* codes, const void* sz, const void* bias, void* out, long long ldo, int T, int N,
+                   int K, int group, int integer_zeros, void* stream);
+
 int lx_wq4_gemm(const void* x, long long ldx, const void* codes, const void* sz, const void* bias, void* out, long long ldo, int T, int N,
                 int K, int group, void* stream) {
+  return lx_wq4_gemm_ex(x, ldx, codes, sz, bias, out, ldo, T, N, K, group, 0, stream);
+}
+
+// `integer_zeros` != 0 promises that every zero point is an integer (GPTQ, AWQ, round-to-nearest; not HQQ): with groups that are
+// multiples of 128 the kernel then multiplies exact integers and scales the partial sums (see EXACT above).
+int lx_wq4_gemm_ex(const void* x, long long ldx, const void* codes, const void* sz, const void* bias, void* out, long long ldo, int T, int N,
+                   int K, int group, int integer_zeros, void* stream) {
   using namespace lx;
   if (T <= 0 || T > 32 || N % kWqRows != 0 || K % 128 != 0 || group % 32 != 0 || K % group != 0 || ldx % 8 != 0) return -1;
   Wq4Params p{static_cast<const uint8_t*>(codes), static_cast<const __half2*>(sz), static_cast<const __nv_bfloat16*>(x),
@@ -273,9 +320,12 @@ int lx_wq4_gemm(const void* x, long long ldx, const void* codes, const void* sz,
   // two row tiles per warp halve the re-reads of the activations (every block reads all of x); with few rows and few tokens
   // the larger grid of single tiles fills the machine better
   const bool two = N % (2 * kWqRows) == 0 && (N >= 8192 || T > 8);
-  if (T <= 8) return two ? wq4_launch<1, 2>(p, s) : wq4_launch<1, 1>(p, s);
-  if (T <= 16) return two ? wq4_launch<2, 2>(p, s) : wq4_launch<2, 1>(p, s);
-  return wq4_launch<4, 1>(p, s);
+  // measured: the exact-integer path wins 6-15 % on the large projections at up to 8 tokens and loses elsewhere (register
+  // pressure with two token tiles; small grids)
+  const bool exact = integer_zeros != 0 && group % 128 == 0 && T <= 8 && (N >= 16384 || K >= 8192);
+  if (T <= 8) return two ? wq4_launch<1, 2>(p, exact, s) : wq4_launch<1, 1>(p, exact, s);
+  if (T <= 16) return two ? wq4_launch<2, 2>(p, exact, s) : wq4_launch<2, 1>(p, exact, s);
+  return wq4_launch<4, 1>(p, exact, s);
 }
 
 }  // extern "C"

@@ -34,7 +34,7 @@ for (N, K) in ((6144, 4096), (28672, 4096), (4096, 14336)):
         lib = native.load()
         def f4(i=0):
             w = wq[i % nrot]
-            lib.lx_wq4_gemm(x.data_ptr(), x.stride(0), w.codes.data_ptr(), w.sz.data_ptr(), None, out.data_ptr(), out.stride(0), T, N, K, 128, torch.cuda.current_stream().cuda_stream)
+            lib.lx_wq4_gemm_ex(x.data_ptr(), x.stride(0), w.codes.data_ptr(), w.sz.data_ptr(), None, out.data_ptr(), out.stride(0), T, N, K, 128, 1, torch.cuda.current_stream().cuda_stream)
         def fb(i=0):
             native.gemm(x, wb[i % nrot_b], out=out)
         t4, tb = timeit(f4), timeit(fb)

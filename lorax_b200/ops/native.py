@@ -74,6 +74,7 @@ def load() -> ctypes.CDLL:
         "lx_gemm_fp8_block128": ([P, L, P, I, P, L, P, P, L, P, I, I, I, P, L, P, I, P], I),
         "lx_wq_dequant": ([P, P, P, P, L, I, I, I, I, P], I),
         "lx_wq4_gemm": ([P, L, P, P, P, P, L, I, I, I, I, P], I),
+        "lx_wq4_gemm_ex": ([P, L, P, P, P, P, L, I, I, I, I, I, P], I),
         "lx_lora_expand_tiled": ([P, I, L, I, P, I, I, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
     }
     for name, (argtypes, restype) in sigs.items():
@@ -249,8 +250,8 @@ def gemm_wq(x: torch.Tensor, w, bias: Optional[torch.Tensor] = None, out: Option
         out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
     if (w.bits == 4 and w.table is None and T <= WQ4_DIRECT_MAX_TOKENS and N % 16 == 0 and K % 128 == 0 and w.group % 32 == 0
             and x.stride(0) % 8 == 0):
-        rc = load().lx_wq4_gemm(_ptr(x), x.stride(0), _ptr(w.codes), _ptr(w.sz), _ptr(bias), _ptr(out), out.stride(0), T, N, K, w.group,
-                                _stream())
+        rc = load().lx_wq4_gemm_ex(_ptr(x), x.stride(0), _ptr(w.codes), _ptr(w.sz), _ptr(bias), _ptr(out), out.stride(0), T, N, K, w.group,
+                                   1 if getattr(w, "int_zero", False) else 0, _stream())
         _check(rc, "lx_wq4_gemm")
         return out
     return gemm(x, wq_dequant(w), bias=bias, out=out)

@@ -47,6 +47,7 @@ class GroupQuantWeight:
     shape: Tuple[int, int]
     table: Optional[torch.Tensor] = None
     method: str = "int4"
+    int_zero: bool = False          # every zero point is an integer (GPTQ, AWQ, round-to-nearest): the 4-bit kernel's exact path
 
     @property
     def device(self):
@@ -54,7 +55,7 @@ class GroupQuantWeight:
 
     def to(self, device) -> "GroupQuantWeight":
         return GroupQuantWeight(self.codes.to(device), self.sz.to(device), self.bits, self.group, self.shape,
-                                None if self.table is None else self.table.to(device), self.method)
+                                None if self.table is None else self.table.to(device), self.method, self.int_zero)
 
     def nbytes(self) -> int:
         return self.codes.numel() + self.sz.numel() * 2
@@ -71,7 +72,7 @@ class GroupQuantWeight:
 
     def rows(self, start: int, stop: int) -> "GroupQuantWeight":
         return GroupQuantWeight(self.codes[start:stop].contiguous(), self.sz[start:stop].contiguous(), self.bits, self.group,
-                                (stop - start, self.shape[1]), self.table, self.method)
+                                (stop - start, self.shape[1]), self.table, self.method, self.int_zero)
 
     def cols(self, start: int, stop: int) -> "GroupQuantWeight":
         if start % self.group or stop % self.group:
@@ -79,14 +80,14 @@ class GroupQuantWeight:
         b = self.bits
         return GroupQuantWeight(self.codes[:, start * b // 8: stop * b // 8].contiguous(),
                                 self.sz[:, start // self.group: stop // self.group].contiguous(), self.bits, self.group,
-                                (self.shape[0], stop - start), self.table, self.method)
+                                (self.shape[0], stop - start), self.table, self.method, self.int_zero)
 
 
 def cat_rows(parts) -> GroupQuantWeight:
     p0 = parts[0]
     assert all(p.bits == p0.bits and p.group == p0.group and p.shape[1] == p0.shape[1] for p in parts)
     return GroupQuantWeight(torch.cat([p.codes for p in parts], 0), torch.cat([p.sz for p in parts], 0), p0.bits, p0.group,
-                            (sum(p.shape[0] for p in parts), p0.shape[1]), p0.table, p0.method)
+                            (sum(p.shape[0] for p in parts), p0.shape[1]), p0.table, p0.method, all(p.int_zero for p in parts))
 
 
 # ------------------------------------------------------------------------------------------------ resident layout
@@ -134,7 +135,8 @@ def make_weight(q: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor, bits: 
     N, K = q.shape
     sz = torch.stack([scale.float(), zero.float()], -1).to(torch.float16).contiguous()
     tab = None if table is None else torch.tensor(table, dtype=torch.float32, device=q.device)
-    return GroupQuantWeight(pack_codes(q, bits), sz, bits, group, (N, K), tab, method)
+    int_zero = table is None and bool(torch.equal(sz[..., 1].float(), sz[..., 1].float().round()))
+    return GroupQuantWeight(pack_codes(q, bits), sz, bits, group, (N, K), tab, method, int_zero)
 
 
 def dequantize(w: GroupQuantWeight, dtype=torch.float32) -> torch.Tensor:

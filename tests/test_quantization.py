@@ -233,13 +233,17 @@ def test_int4_tensor_core_gemm_matches_fp32_reference(T):
         x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
         bias = torch.randn(N, device="cuda").to(torch.bfloat16)
         out = torch.full((T, N), 7.0, device="cuda", dtype=torch.bfloat16)
-        rc = native.load().lx_wq4_gemm(x.data_ptr(), x.stride(0), gd.codes.data_ptr(), gd.sz.data_ptr(), bias.data_ptr(), out.data_ptr(),
-                                       out.stride(0), T, N, K, gd.group, torch.cuda.current_stream().cuda_stream)
-        assert rc == 0
-        torch.cuda.synchronize()
         want = x.float().cpu() @ qf.dequantize(g).t() + bias.float().cpu()
-        err = ((out.float().cpu() - want).norm() / want.norm()).item()
-        assert err < 6e-3, (T, g.group, err)
+        # general path (scale folded into the operand) and, where the zero points are integers, the exact-integer path
+        for flag in ([0, 1] if g.int_zero else [0]):
+            out.fill_(7.0)
+            rc = native.load().lx_wq4_gemm_ex(x.data_ptr(), x.stride(0), gd.codes.data_ptr(), gd.sz.data_ptr(), bias.data_ptr(), out.data_ptr(),
+                                              out.stride(0), T, N, K, gd.group, flag, torch.cuda.current_stream().cuda_stream)
+            assert rc == 0
+            torch.cuda.synchronize()
+            err = ((out.float().cpu() - want).norm() / want.norm()).item()
+            assert err < 6e-3, (T, g.group, flag, err)
+        assert g.int_zero == (g.method != "hqq-4bit")
 
 
 @pytest.mark.gpu
