@@ -225,8 +225,8 @@ def test_int4_tensor_core_gemm_matches_fp32_reference(T):
     """out = x . dequant(W)^T straight from the packed codes, against an fp32 product of the same expanded matrix."""
     from lorax_b200.ops import native
     torch.manual_seed(8 + T)
-    K = 1536
-    for N, g in ((1040, None), (1056, None), (1040, 64), (1056, 32)):      # one and two row tiles per warp
+    # one and two row tiles per warp; the last shape (K >= 8192) takes the exact-integer variant at up to 8 tokens
+    for N, g, K in ((1040, None, 1536), (1056, None, 1536), (1040, 64, 1536), (1056, 32, 1536), (272, None, 8192), (16384, None, 256)):
         w = torch.randn(N, K) * 0.05
         g = qf.quantize_rtn(w, 4, 128) if g is None else (qf.quantize_hqq(w, 4, g) if g == 64 else qf.quantize_rtn(w, 4, g))
         gd = g.to("cuda")
