@@ -150,8 +150,17 @@ class ModelConfig:
         if mt in ("falcon", "RefinedWeb", "RefinedWebModel"):
             kw.update(norm_type="layernorm", parallel_residual=d.get("parallel_attn", True),
                       hidden_act="gelu", attention_bias=d.get("bias", False), mlp_bias=d.get("bias", False))
-            if d.get("multi_query", False) and "num_key_value_heads" not in kw:
-                kw["num_key_value_heads"] = 1
+            # key/value heads: the 40b layout (new_decoder_architecture; "RefinedWeb" checkpoints imply it) names them, the
+            # 7b layout has one shared head when multi_query is set, falcon-rw has as many as query heads
+            new_arch = bool(d.get("new_decoder_architecture", mt == "RefinedWeb"))
+            nh = kw.get("num_attention_heads", 32)
+            if new_arch:
+                kw["num_key_value_heads"] = d.get("num_kv_heads") or d.get("n_head_kv") or nh
+            else:
+                kw["num_key_value_heads"] = 1 if d.get("multi_query", mt != "falcon") else nh
+            if d.get("alibi", False):
+                raise NotImplementedError("falcon with ALiBi (falcon-rw): its bias is scaled with the scores, unlike bloom's")
+            kw["rms_norm_eps"] = d.get("layer_norm_epsilon", 1e-5)
         if mt == "phi":
             kw.update(norm_type="layernorm", parallel_residual=True, attention_bias=True, mlp_bias=True,
                       hidden_act=d.get("hidden_act", "gelu_new"))

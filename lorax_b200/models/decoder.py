@@ -142,7 +142,11 @@ class DecoderModel:
         self.lm_head: Optional[torch.Tensor] = None
         self.lm_head_b: Optional[torch.Tensor] = None
         self.max_positions = max_positions or min(c.max_position_embeddings, 32768)
-        self.cos_sin = reference.rope_cache(c.rotary_dim, self.max_positions, c.rope_theta, c.rope_scaling, device=self.device)
+        scaling = c.rope_scaling
+        if scaling and scaling.get("rope_type", scaling.get("type")) == "dynamic" and "original_max_position_embeddings" not in scaling:
+            # dynamic NTK stretches the base once the table is longer than the length the model was trained at
+            scaling = dict(scaling, original_max_position_embeddings=c.max_position_embeddings)
+        self.cos_sin = reference.rope_cache(c.rotary_dim, self.max_positions, c.rope_theta, scaling, device=self.device)
         self.adapters = None     # AdapterManager, attached by the runtime
         self.quantized: Optional[str] = None
         self.keep_hidden = False                 # keep the head's input rows of the last eager forward pass in `last_hidden`

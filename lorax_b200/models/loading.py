@@ -102,7 +102,7 @@ def _split_qkv_full(m: DecoderModel, qkv: torch.Tensor, nm: dict):
     if nm.get("qkv_interleaved"):            # neox: [nh, 3, d]
         x = qkv.view(nh, 3, d, *qkv.shape[1:])
         return (x[:, 0].reshape(nh * d, *qkv.shape[1:]), x[:, 1].reshape(nh * d, *qkv.shape[1:]), x[:, 2].reshape(nh * d, *qkv.shape[1:]))
-    if nm.get("qkv_grouped") and nkv not in (1, nh):   # falcon new arch: [nkv, group + 2, d]
+    if nm.get("qkv_grouped"):   # falcon: [nkv, group + 2, d]; one kv head gives q | k | v, as many as q heads gives [nh, 3, d]
         g = nh // nkv
         x = qkv.view(nkv, g + 2, d, *qkv.shape[1:])
         return (x[:, :g].reshape(nh * d, *qkv.shape[1:]), x[:, g].reshape(nkv * d, *qkv.shape[1:]), x[:, g + 1].reshape(nkv * d, *qkv.shape[1:]))
@@ -195,6 +195,14 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
     m.layers = []
     for i in range(c.num_hidden_layers):
         L = nm["layer"].format(i=i)
+        if nm.get("qkv_grouped"):
+            # falcon: the 40b layout has one LayerNorm per branch (ln_attn, ln_mlp); blocks without parallel attention
+            # carry a post_attention_layernorm instead
+            nm = dict(nm)
+            if w.has_tensor(pre[0] + L + "ln_attn.weight"):
+                nm.update(input_norm="ln_attn.weight", input_norm_b="ln_attn.bias", post_norm="ln_mlp.weight", post_norm_b="ln_mlp.bias")
+            elif w.has_tensor(pre[0] + L + "post_attention_layernorm.weight"):
+                nm.update(post_norm="post_attention_layernorm.weight", post_norm_b="post_attention_layernorm.bias")
         if nm.get("qkv"):
             q, k, v = _split_qkv_full(m, lin(L + nm["qkv"], packed=not (nm.get("qkv_interleaved") or nm.get("qkv_grouped"))), nm)
             qb_ = bias(L + nm["qkv"])
@@ -240,6 +248,9 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
                 lw.gate_up_w = fin(_cat0([rows(gu[:I]), rows(gu[I:])]))
             elif nm.get("gate"):
                 lw.gate_up_w = fin(_cat0([rows(lin(L + nm["gate"])), rows(lin(L + nm["up"]))]))
+                gb, ub = bias(L + nm["gate"]), bias(L + nm["up"])
+                if gb is not None and ub is not None:      # llama / granite with mlp_bias
+                    lw.gate_up_b = fin(torch.cat([rows(gb), rows(ub)], 0))
             else:
                 lw.gate_up_w = fin(rows(lin(L + nm["up"])))
                 ub = bias(L + nm["up"])

@@ -220,7 +220,15 @@ class ModelRunner:
         if logits.shape[0] == 0:
             return None, None, logits
         next_ids, lps = self.model.ops.argmax_logprob(logits, softcap=self.model.config.final_logit_softcapping or 0.0)
-        return next_ids, lps, logits
+        return next_ids, lps, self._cap(logits)
+
+    def _cap(self, logits):
+        """Logits as a sampler must see them: gemma2 squashes the head's output with cap * tanh(x / cap).  The greedy
+        arg-max applies the cap inside its own kernel; rows handed to a sampler or scored as log-probs get it here."""
+        cap = self.model.config.final_logit_softcapping or 0.0
+        if logits is None or cap <= 0:
+            return logits
+        return torch.tanh(logits.float() / cap).mul_(cap).to(logits.dtype)
 
     def can_mix(self) -> bool:
         """A prefill can ride along with the decode rows when those are grouped by adapter (or no adapter is in use)."""
@@ -451,6 +459,7 @@ class ModelRunner:
         else:
             logits = self._decode_body(b, lora, need_logits)
             self._advance(b)
+        logits = self._cap(logits)
         if sampler is not None:
             sampler(logits, st)
         k = self.ring_pos

@@ -207,7 +207,7 @@ def test_encoders_match_hf():
         assert torch.allclose(torch.tensor(sc), conf, atol=2e-4)
 
 
-def _from_hf(hf, **over):
+def _from_hf(hf, max_positions=None, **over):
     """Our decoder loaded from a HuggingFace model's own state dict and config."""
     from lorax_b200.utils.weights import InMemoryWeights
     d = hf.config.to_dict()
@@ -215,7 +215,7 @@ def _from_hf(hf, **over):
     cfg = ModelConfig.from_dict(d)
     cfg.torch_dtype = "float32"
     sd = {k: v.detach().clone() for k, v in hf.state_dict().items()}
-    return DecoderModel.from_weights(cfg, InMemoryWeights(sd, dtype=torch.float32), "cpu", torch.float32)
+    return DecoderModel.from_weights(cfg, InMemoryWeights(sd, dtype=torch.float32), "cpu", torch.float32, max_positions=max_positions)
 
 
 def _check_against_hf(hf, model, vocab, n=23, tol=2e-3):
@@ -382,3 +382,68 @@ def test_t5_matches_hf(ff, tied):
         for s, row in zip((a, b), lg):
             s.last_token, s.position = int(row.argmax()), s.position + 1
     assert [b.last_token] == got[2:3]
+
+
+def _family(name):
+    """A two-layer HuggingFace model of one architecture variant, with every parameter (biases and norm weights
+    included) drawn at random so that a tensor the loader drops or misplaces shows in the logits."""
+    import transformers as T
+    common = dict(vocab_size=200, hidden_size=64, num_hidden_layers=2, num_attention_heads=4, max_position_embeddings=128)
+    llama = dict(common, intermediate_size=96, num_key_value_heads=2)
+    table = {
+        "llama3_rope": (T.LlamaForCausalLM, T.LlamaConfig, dict(llama, rope_theta=5e5, rope_scaling=dict(
+            rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max_position_embeddings=32))),
+        "llama_yarn": (T.LlamaForCausalLM, T.LlamaConfig, dict(llama, rope_scaling=dict(
+            rope_type="yarn", factor=4.0, original_max_position_embeddings=32))),
+        "llama_linear": (T.LlamaForCausalLM, T.LlamaConfig, dict(llama, rope_scaling=dict(rope_type="linear", factor=2.0))),
+        "llama_dynamic_ntk": (T.LlamaForCausalLM, T.LlamaConfig, dict(llama, max_position_embeddings=16,
+                                                                       rope_scaling=dict(rope_type="dynamic", factor=2.0))),
+        "llama_biases": (T.LlamaForCausalLM, T.LlamaConfig, dict(llama, attention_bias=True, mlp_bias=True)),
+        "mistral_window": (T.MistralForCausalLM, T.MistralConfig, dict(llama, sliding_window=8)),
+        "phi3": (T.Phi3ForCausalLM, T.Phi3Config, dict(llama, pad_token_id=0)),
+        "phi3_longrope": (T.Phi3ForCausalLM, T.Phi3Config, dict(
+            llama, pad_token_id=0, original_max_position_embeddings=16, rope_scaling=dict(
+                type="longrope", short_factor=[1.0 + 0.1 * i for i in range(8)], long_factor=[2.0 + 0.3 * i for i in range(8)]))),
+        "gemma2": (T.Gemma2ForCausalLM, T.Gemma2Config, dict(llama, head_dim=16, sliding_window=8, query_pre_attn_scalar=24,
+                                                             attn_logit_softcapping=20.0, final_logit_softcapping=10.0)),
+        "cohere": (T.CohereForCausalLM, T.CohereConfig, dict(llama, logit_scale=0.25)),
+        "granite": (T.GraniteForCausalLM, T.GraniteConfig, dict(llama, embedding_multiplier=3.0, logits_scaling=2.0,
+                                                                residual_multiplier=0.5, attention_multiplier=0.1)),
+        "gpt2": (T.GPT2LMHeadModel, T.GPT2Config, dict(vocab_size=200, n_embd=64, n_layer=2, n_head=4, n_positions=128)),
+        "gpt_bigcode": (T.GPTBigCodeForCausalLM, T.GPTBigCodeConfig, dict(vocab_size=200, n_embd=64, n_layer=2, n_head=4,
+                                                                          n_positions=128, multi_query=True)),
+        "gpt_neox_parallel": (T.GPTNeoXForCausalLM, T.GPTNeoXConfig, dict(common, intermediate_size=160, rotary_pct=0.25,
+                                                                          use_parallel_residual=True)),
+        "gpt_neox_sequential": (T.GPTNeoXForCausalLM, T.GPTNeoXConfig, dict(common, intermediate_size=160, rotary_pct=0.5,
+                                                                            use_parallel_residual=False)),
+        "falcon_7b": (T.FalconForCausalLM, T.FalconConfig, dict(common, multi_query=True, parallel_attn=True, bias=False,
+                                                                new_decoder_architecture=False, alibi=False)),
+        "falcon_40b": (T.FalconForCausalLM, T.FalconConfig, dict(common, num_kv_heads=2, parallel_attn=True, bias=False,
+                                                                 new_decoder_architecture=True, alibi=False)),
+        "falcon_rw": (T.FalconForCausalLM, T.FalconConfig, dict(common, multi_query=False, parallel_attn=False, bias=True,
+                                                                new_decoder_architecture=False, alibi=False)),
+        "phi": (T.PhiForCausalLM, T.PhiConfig, dict(common, intermediate_size=160, partial_rotary_factor=0.5)),
+    }
+    cls, cfg_cls, kw = table[name]
+    torch.manual_seed(0)
+    hc = cfg_cls(**kw)
+    hc._attn_implementation = "eager"
+    hf = cls(hc).eval()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.08)
+    return hf
+
+
+@pytest.mark.parametrize("name", ["llama3_rope", "llama_yarn", "llama_linear", "llama_dynamic_ntk", "llama_biases", "mistral_window", "phi3",
+                                  "phi3_longrope", "gemma2", "cohere", "granite", "gpt2", "gpt_bigcode", "gpt_neox_parallel",
+                                  "gpt_neox_sequential", "falcon_7b", "falcon_40b", "falcon_rw", "phi"])
+def test_decoder_family_matches_hf(name):
+    """Every decoder architecture the registry names that has no test of its own above, loaded from a HuggingFace model's own
+    state dict and config: prompt logits over 23 tokens equal HuggingFace's eager implementation.  The variants pin the RoPE
+    scalings (llama3, YaRN, linear, dynamic NTK, LongRoPE), sliding windows (every layer for mistral, alternate layers for
+    gemma2), both soft caps of gemma2, the multipliers of granite and cohere, fused and interleaved QKV packings, and the three
+    falcon block layouts."""
+    hf = _family(name)
+    # dynamic NTK stretches the rotary base with the table length; HuggingFace stretches it with the sequence length
+    m = _from_hf(hf, max_positions=23 if name == "llama_dynamic_ntk" else None)
+    _check_against_hf(hf, m, 200)
