@@ -1,8 +1,8 @@
-"""Vision-language serving: LLaVA-NeXT (CLIP vision tower + two-layer projector + any-resolution tiling) in front of the paged
-decoder.
+"""Vision-language serving: LLaVA-NeXT (CLIP or SigLIP vision tower + two-layer projector + any-resolution tiling) in front of
+the paged decoder.
 
 The reference serves LLaVA-NeXT through `VlmCausalLM` (`server/lorax_server/models/vlm_causal_lm.py`, model code
-`custom_modeling/llava_next.py`, `clip.py`), with the router expanding every image into as many `<image>` tokens as the model
+`custom_modeling/llava_next.py`, `clip.py`, `siglip.py`), with the router expanding every image into as many `<image>` tokens as the model
 will produce features (`router/src/config.rs:6-190`, `validation.rs:498-638`).  The same three steps here:
 
 1. `num_image_features(height, width)`: how many rows of the prompt an image takes;
@@ -48,10 +48,26 @@ class ClipVisionConfig:
     patch_size: int = 14
     layer_norm_eps: float = 1e-5
     hidden_act: str = "quick_gelu"
+    # "clip_vision_model": class token in front of the patches, LayerNorm before the encoder, patch convolution without bias.
+    # "siglip_vision_model" (reference: `custom_modeling/siglip.py`): patches only, no LayerNorm in front, biased convolution.
+    model_type: str = "clip_vision_model"
 
     @classmethod
     def from_dict(cls, d: dict) -> "ClipVisionConfig":
-        return cls(**{k: v for k, v in d.items() if k in cls.__dataclass_fields__ and v is not None})
+        kw = {k: v for k, v in d.items() if k in cls.__dataclass_fields__ and v is not None}
+        if kw.get("model_type") == "siglip_vision_model":
+            kw.setdefault("layer_norm_eps", 1e-6)
+            kw.setdefault("hidden_act", "gelu_pytorch_tanh")
+        return cls(**kw)
+
+    @property
+    def is_siglip(self) -> bool:
+        return self.model_type == "siglip_vision_model"
+
+    @property
+    def extra_tokens(self) -> int:
+        """Rows the tower emits per tile besides the patches (CLIP's class token)."""
+        return 0 if self.is_siglip else 1
 
 
 @dataclass
@@ -66,8 +82,9 @@ class LlavaNextConfig:
 
     @classmethod
     def from_dict(cls, d: dict) -> "LlavaNextConfig":
-        if d.get("vision_config", {}).get("model_type", "clip_vision_model") != "clip_vision_model":
-            raise NotImplementedError("only CLIP vision towers are built")
+        tower = d.get("vision_config", {}).get("model_type", "clip_vision_model")
+        if tower not in ("clip_vision_model", "siglip_vision_model"):
+            raise NotImplementedError(f"vision tower {tower}: CLIP and SigLIP towers are built")
         kw = {k: d[k] for k in ("image_token_index", "vision_feature_layer", "vision_feature_select_strategy", "image_grid_pinpoints",
                                 "projector_hidden_act") if d.get(k) is not None}
         if "image_token_index" not in kw and d.get("image_token_id") is not None:
@@ -110,6 +127,8 @@ class LlavaNextModel:
         self.text = text
         self.device, self.dtype = text.device, text.dtype
         self.w = {}
+        # normalisation of the pixels: CLIP's statistics, 0.5 / 0.5 for SigLIP (the defaults of their image processors)
+        self.image_mean, self.image_std = CLIP_MEAN, CLIP_STD
 
     # ------------------------------------------------------------------ loading
     @classmethod
@@ -127,16 +146,24 @@ class LlavaNextModel:
                              if any(k.endswith("lm_head.weight") for k in names) else "lm_head."})
         text = DecoderModel.from_weights(config.text, lang, device, dtype, tp, max_positions=max_positions)
         m = cls(config, text)
-        vt = prefix_of("embeddings.class_embedding")
+        vt = prefix_of("embeddings.position_embedding.weight")
+        sig = config.vision.is_siglip
+        if sig:
+            m.image_mean = m.image_std = (0.5, 0.5, 0.5)
+            if config.vision_feature_select_strategy == "default":
+                raise ValueError("a SigLIP tower has no class token to drop: vision_feature_select_strategy must be 'full'")
         pj = prefix_of("linear_1.weight")
         nl = prefix_of("image_newline") + "image_newline"
 
         def get(name):
             return w.get_tensor(name).to(dtype).to(m.device).contiguous()
         g = m.w
-        g["cls"], g["patch"], g["pos"] = get(vt + "embeddings.class_embedding"), get(vt + "embeddings.patch_embedding.weight"), \
-            get(vt + "embeddings.position_embedding.weight")
-        g["pre_w"], g["pre_b"] = get(vt + "pre_layrnorm.weight"), get(vt + "pre_layrnorm.bias")
+        g["patch"], g["pos"] = get(vt + "embeddings.patch_embedding.weight"), get(vt + "embeddings.position_embedding.weight")
+        if sig:
+            g["patch_b"] = get(vt + "embeddings.patch_embedding.bias")
+        else:
+            g["cls"] = get(vt + "embeddings.class_embedding")
+            g["pre_w"], g["pre_b"] = get(vt + "pre_layrnorm.weight"), get(vt + "pre_layrnorm.bias")
         n_layers = config.vision.num_hidden_layers
         last = n_layers + config.vision_feature_layer + 1 if config.vision_feature_layer < 0 else config.vision_feature_layer
         g["layers"] = []
@@ -157,7 +184,7 @@ class LlavaNextModel:
     def num_image_features(self, height: int, width: int) -> int:
         v = self.config.vision
         side = v.image_size // v.patch_size
-        base = side * side + (0 if self.config.vision_feature_select_strategy == "default" else 1)
+        base = side * side + v.extra_tokens - (1 if self.config.vision_feature_select_strategy == "default" else 0)
         bh, bw = select_best_resolution((height, width), self.config.image_grid_pinpoints)
         gh, gw = bh // v.image_size * side, bw // v.image_size * side
         _, rows, _, cols = unpadded_grid((height, width), (gh, gw))
@@ -187,18 +214,21 @@ class LlavaNextModel:
                 tiles.append(canvas.crop((x, y, x + S, y + S)))
         import numpy as np
         arr = torch.from_numpy(np.stack([np.asarray(t, dtype=np.float32) / 255.0 for t in tiles])).permute(0, 3, 1, 2)
-        mean = torch.tensor(CLIP_MEAN).view(1, 3, 1, 1)
-        std = torch.tensor(CLIP_STD).view(1, 3, 1, 1)
+        mean = torch.tensor(self.image_mean).view(1, 3, 1, 1)
+        std = torch.tensor(self.image_std).view(1, 3, 1, 1)
         return ((arr - mean) / std).contiguous(), (h0, w0)
 
     # ------------------------------------------------------------------ step 3: features
     def _tower(self, tiles: torch.Tensor) -> torch.Tensor:
-        """[n, 3, S, S] -> hidden state of the chosen layer [n, 1 + patches, hidden]."""
+        """[n, 3, S, S] -> hidden state of the chosen layer [n, (1 +) patches, hidden]."""
         v, g = self.config.vision, self.w
-        x = F.conv2d(tiles.to(self.dtype).to(self.device), g["patch"], stride=v.patch_size)          # [n, hidden, side, side]
+        x = F.conv2d(tiles.to(self.dtype).to(self.device), g["patch"], g.get("patch_b"), stride=v.patch_size)   # [n, hidden, side, side]
         x = x.flatten(2).transpose(1, 2)
-        x = torch.cat([g["cls"].view(1, 1, -1).expand(x.shape[0], 1, -1), x], 1) + g["pos"][None]
-        x = F.layer_norm(x, (v.hidden_size,), g["pre_w"], g["pre_b"], v.layer_norm_eps)
+        if "cls" in g:
+            x = torch.cat([g["cls"].view(1, 1, -1).expand(x.shape[0], 1, -1), x], 1) + g["pos"][None]
+            x = F.layer_norm(x, (v.hidden_size,), g["pre_w"], g["pre_b"], v.layer_norm_eps)
+        else:
+            x = x + g["pos"][None]
         nh, d = v.num_attention_heads, v.hidden_size // v.num_attention_heads
         for l in g["layers"]:
             h = F.layer_norm(x, (v.hidden_size,), l["ln1_w"], l["ln1_b"], v.layer_norm_eps)
@@ -209,7 +239,10 @@ class LlavaNextModel:
             x = x + F.linear(a, l["o_w"], l["o_b"])
             h = F.layer_norm(x, (v.hidden_size,), l["ln2_w"], l["ln2_b"], v.layer_norm_eps)
             h = F.linear(h, l["fc1_w"], l["fc1_b"])
-            h = h * torch.sigmoid(1.702 * h) if v.hidden_act == "quick_gelu" else F.gelu(h)
+            if v.hidden_act == "quick_gelu":
+                h = h * torch.sigmoid(1.702 * h)
+            else:
+                h = F.gelu(h, approximate="tanh" if v.hidden_act in ("gelu_pytorch_tanh", "gelu_new", "gelu_fast") else "none")
             x = x + F.linear(h, l["fc2_w"], l["fc2_b"])
         return x
 

@@ -26,6 +26,23 @@ def _tiny_hf(seed=0):
     return hf, hc
 
 
+def _tiny_hf_siglip(seed=0):
+    """The same model with a SigLIP tower: no class token, biased patch convolution, tanh GELU, strategy "full"."""
+    from transformers import LlamaConfig, LlavaNextConfig, LlavaNextForConditionalGeneration, SiglipVisionConfig
+    torch.manual_seed(seed)
+    vc = SiglipVisionConfig(hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4, image_size=28, patch_size=14)
+    tc = LlamaConfig(vocab_size=300, hidden_size=64, intermediate_size=112, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                     max_position_embeddings=512, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    hc = LlavaNextConfig(vision_config=vc, text_config=tc, image_token_index=299, vision_feature_layer=-2,
+                         vision_feature_select_strategy="full",
+                         image_grid_pinpoints=[[28, 56], [56, 28], [56, 56], [28, 84], [84, 28]], projector_hidden_act="gelu")
+    hc._attn_implementation = "eager"
+    hf = LlavaNextForConditionalGeneration(hc).eval()
+    for p in hf.parameters():
+        torch.nn.init.normal_(p, std=0.08)
+    return hf, hc
+
+
 def _ours(hf, hc):
     from lorax_b200.utils.weights import InMemoryWeights
     cfg = vlm.LlavaNextConfig.from_dict(hc.to_dict())
@@ -47,6 +64,24 @@ def test_feature_count_matches_packing(size):
     with torch.no_grad():
         want = hf.model.get_image_features(pixel_values=tiles[None], image_sizes=torch.tensor([[h, w]]), vision_feature_layer=-2,
                                            vision_feature_select_strategy="default")
+    want = want.pooler_output if hasattr(want, "pooler_output") else want
+    want = torch.cat(list(want), 0) if isinstance(want, (list, tuple)) else want
+    assert want.shape == feats.shape and (want - feats).abs().max().item() < 1e-4
+
+
+@pytest.mark.parametrize("size", [(28, 28), (40, 100), (333, 90)])
+def test_siglip_tower_features_match_hf(size):
+    hf, hc = _tiny_hf_siglip()
+    m = _ours(hf, hc)
+    assert m.config.vision.is_siglip and "cls" not in m.w and m.image_mean == (0.5, 0.5, 0.5)
+    h, w = size
+    bh, bw = vlm.select_best_resolution((h, w), hc.image_grid_pinpoints)
+    tiles = torch.randn(1 + (bh // 28) * (bw // 28), 3, 28, 28)
+    feats = m.image_features(tiles, (h, w))
+    assert feats.shape == (m.num_image_features(h, w), 64)
+    with torch.no_grad():
+        want = hf.model.get_image_features(pixel_values=tiles[None], image_sizes=torch.tensor([[h, w]]), vision_feature_layer=-2,
+                                           vision_feature_select_strategy="full")
     want = want.pooler_output if hasattr(want, "pooler_output") else want
     want = torch.cat(list(want), 0) if isinstance(want, (list, tuple)) else want
     assert want.shape == feats.shape and (want - feats).abs().max().item() < 1e-4
