@@ -11,7 +11,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from ..utils.quant_formats import GroupQuantWeight, cat_rows, dequantize
+from ..utils.quant_formats import GroupQuantWeight, cat_rows, dequantize, same_perm
 from ..utils.weights import AbstractWeights
 from .decoder import DecoderModel, LayerWeights
 
@@ -111,7 +111,7 @@ def _split_qkv_full(m: DecoderModel, qkv: torch.Tensor, nm: dict):
 
 def _cat0(parts):
     """Row concatenation of dense matrices or of packed ones (fused QKV / gate_up of a GPTQ / AWQ checkpoint)."""
-    if all(isinstance(p, GroupQuantWeight) for p in parts):
+    if all(isinstance(p, GroupQuantWeight) for p in parts) and same_perm(parts):
         return cat_rows(parts)
     dt = next(p.dtype for p in parts if isinstance(p, torch.Tensor))
     return torch.cat([dequantize(p, dt) if isinstance(p, GroupQuantWeight) else p for p in parts], 0)
@@ -159,6 +159,8 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
         return t[rk * b:(rk + 1) * b]
 
     def cols(t):
+        if ws > 1 and isinstance(t, GroupQuantWeight) and t.perm is not None:
+            t = dense(t)                    # an act-order layer's groups mix the column shards of all ranks
         b = t.shape[1] // ws
         return t[:, rk * b:(rk + 1) * b]
 

@@ -9,6 +9,7 @@ no silent eager fallback.
 from __future__ import annotations
 
 import ctypes
+import dataclasses
 import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from pathlib import Path
@@ -232,6 +233,8 @@ def wq_dequant(w, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         out = torch.empty(N, K, dtype=torch.bfloat16, device=w.codes.device)
     rc = load().lx_wq_dequant(_ptr(w.codes), _ptr(w.sz), _ptr(w.table), _ptr(out), out.stride(0), N, K, w.bits, w.group, _stream())
     _check(rc, "lx_wq_dequant")
+    if getattr(w, "perm", None) is not None:          # act-order GPTQ: stored column i is input feature perm[i]
+        out.copy_(torch.empty_like(out).index_copy_(1, w.perm.long(), out))
     return out
 
 
@@ -248,6 +251,11 @@ def gemm_wq(x: torch.Tensor, w, bias: Optional[torch.Tensor] = None, out: Option
     assert w.shape[1] == K
     if out is None:
         out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    if getattr(w, "perm", None) is not None:
+        # act-order GPTQ: the stored columns are sorted by group, so the activations are gathered into that order first
+        # (2 * T * K bytes against N * K / 2 of weights) and both kernels below see an ordinary grouped matrix
+        x = x.index_select(1, w.perm)
+        w = dataclasses.replace(w, perm=None)
     if (w.bits == 4 and w.table is None and T <= WQ4_DIRECT_MAX_TOKENS and N % 16 == 0 and K % 128 == 0 and w.group % 32 == 0
             and x.stride(0) % 8 == 0):
         rc = load().lx_wq4_gemm_ex(_ptr(x), x.stride(0), _ptr(w.codes), _ptr(w.sz), _ptr(bias), _ptr(out), out.stride(0), T, N, K, w.group,

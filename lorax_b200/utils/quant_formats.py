@@ -48,6 +48,9 @@ class GroupQuantWeight:
     table: Optional[torch.Tensor] = None
     method: str = "int4"
     int_zero: bool = False          # every zero point is an integer (GPTQ, AWQ, round-to-nearest): the 4-bit kernel's exact path
+    # act-order GPTQ: stored column i is input feature perm[i] (int32 [K]), which makes every group a contiguous run again; the
+    # caller multiplies x[:, perm] by this matrix (exllama's x_map: exllama_kernels/cuda_func/q4_matmul.cu in the reference)
+    perm: Optional[torch.Tensor] = None
 
     @property
     def device(self):
@@ -55,10 +58,11 @@ class GroupQuantWeight:
 
     def to(self, device) -> "GroupQuantWeight":
         return GroupQuantWeight(self.codes.to(device), self.sz.to(device), self.bits, self.group, self.shape,
-                                None if self.table is None else self.table.to(device), self.method, self.int_zero)
+                                None if self.table is None else self.table.to(device), self.method, self.int_zero,
+                                None if self.perm is None else self.perm.to(device))
 
     def nbytes(self) -> int:
-        return self.codes.numel() + self.sz.numel() * 2
+        return self.codes.numel() + self.sz.numel() * 2 + (0 if self.perm is None else self.perm.numel() * 4)
 
     # ---- slicing used by tensor-parallel sharding (`w[a:b]` = rows, `w[:, a:b]` = columns, like a tensor)
     def __getitem__(self, key):
@@ -72,9 +76,13 @@ class GroupQuantWeight:
 
     def rows(self, start: int, stop: int) -> "GroupQuantWeight":
         return GroupQuantWeight(self.codes[start:stop].contiguous(), self.sz[start:stop].contiguous(), self.bits, self.group,
-                                (stop - start, self.shape[1]), self.table, self.method, self.int_zero)
+                                (stop - start, self.shape[1]), self.table, self.method, self.int_zero, self.perm)
 
     def cols(self, start: int, stop: int) -> "GroupQuantWeight":
+        if start == 0 and stop == self.shape[1]:
+            return self
+        if self.perm is not None:
+            raise ValueError("an act-order layer cannot be sharded by input columns while packed: its groups mix columns of all shards")
         if start % self.group or stop % self.group:
             raise ValueError(f"a column shard must start and end on a group boundary ({self.group}); got [{start}, {stop})")
         b = self.bits
@@ -86,8 +94,18 @@ class GroupQuantWeight:
 def cat_rows(parts) -> GroupQuantWeight:
     p0 = parts[0]
     assert all(p.bits == p0.bits and p.group == p0.group and p.shape[1] == p0.shape[1] for p in parts)
+    assert same_perm(parts), "projections with different act-order permutations cannot share one packed matrix"
     return GroupQuantWeight(torch.cat([p.codes for p in parts], 0), torch.cat([p.sz for p in parts], 0), p0.bits, p0.group,
-                            (sum(p.shape[0] for p in parts), p0.shape[1]), p0.table, p0.method, all(p.int_zero for p in parts))
+                            (sum(p.shape[0] for p in parts), p0.shape[1]), p0.table, p0.method, all(p.int_zero for p in parts), p0.perm)
+
+
+def same_perm(parts) -> bool:
+    """Whether packed matrices read their input in the same column order (q / k / v, or gate / up, of an act-order GPTQ
+    checkpoint do: the order comes from the Hessian of their common input)."""
+    p0 = parts[0].perm
+    if p0 is None:
+        return all(p.perm is None for p in parts)
+    return all(p.perm is not None and torch.equal(p.perm.cpu(), p0.cpu()) for p in parts)
 
 
 # ------------------------------------------------------------------------------------------------ resident layout
@@ -145,9 +163,12 @@ def dequantize(w: GroupQuantWeight, dtype=torch.float32) -> torch.Tensor:
     q = unpack_codes(w.codes, w.bits, K)
     s = w.sz[..., 0].float().repeat_interleave(w.group, 1)
     if w.table is not None:
-        return (w.table.float()[q.long()] * s).to(dtype)
-    z = w.sz[..., 1].float().repeat_interleave(w.group, 1)
-    return ((q.float() - z) * s).to(dtype)
+        d = w.table.float()[q.long()] * s
+    else:
+        d = (q.float() - w.sz[..., 1].float().repeat_interleave(w.group, 1)) * s
+    if w.perm is not None:                             # stored column i is input feature perm[i]
+        d = torch.empty_like(d).index_copy_(1, w.perm.long(), d)
+    return d.to(dtype)
 
 
 # ------------------------------------------------------------------------------------------------ on-load quantisers
@@ -316,8 +337,9 @@ def from_checkpoint(tensors: dict, quant_method: str, bits: int, group: int, zer
                     want_dense: bool = True):
     """One linear layer of a GPTQ / AWQ checkpoint -> (GroupQuantWeight or None, dense [N, K] in `dtype`).
 
-    The packed form is returned when the layer's groups are contiguous along K; an act-order GPTQ layer (`g_idx` not
-    monotone) only has the dense form, because the resident layout keeps one (scale, zero) per run of `group` inputs."""
+    The resident layout keeps one (scale, zero) per run of `group` inputs.  An act-order GPTQ layer (`g_idx` not monotone)
+    is stored with its columns sorted by group, which makes the runs contiguous again, and carries the order in `perm`; only a
+    layer whose groups are not all of `group` columns has the dense form alone."""
     if quant_method == "awq":
         q, s, z = awq_unpack(tensors["qweight"], tensors["qzeros"], tensors["scales"])
         g_idx = None
@@ -331,7 +353,12 @@ def from_checkpoint(tensors: dict, quant_method: str, bits: int, group: int, zer
     if trivial:
         packed = make_weight(q, s, z, bits, grp, method=quant_method)
         return packed, (dequantize(packed, dtype) if want_dense else None)
-    gi = g_idx.to(torch.int64)
+    gi = g_idx.to(torch.int64).cpu()
+    perm = torch.argsort(gi, stable=True)
+    if bool(torch.equal(gi[perm], torch.arange(K) // grp)):
+        packed = make_weight(q[:, perm].contiguous(), s, z, bits, grp, method=quant_method)
+        packed.perm = perm.to(torch.int32)
+        return packed, (dequantize(packed, dtype) if want_dense else None)
     dense = (q.float() - z[:, gi]) * s[:, gi]
     return None, dense.to(dtype)
 

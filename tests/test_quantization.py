@@ -75,13 +75,26 @@ def test_gptq_and_awq_checkpoint_layouts_match_their_specification():
     packed, dense = qf.from_checkpoint(t, "gptq", 4, group)
     assert packed is not None and torch.allclose(dense.float(), want, atol=2e-3)
     assert torch.allclose(qf.dequantize(packed), want, atol=1e-6)
-    # act-order: groups are no longer runs of consecutive inputs -> only the dense form exists, and it honours g_idx
+    # act-order: groups are no longer runs of consecutive inputs -> the packed form keeps the columns sorted by group and the
+    # order they came from; expanded, it honours g_idx
     perm = torch.randperm(K)
     t2 = dict(t)
     t2["g_idx"] = (perm // group).to(torch.int32)
+    want2 = _naive_gptq_dequant(t2["qweight"], t2["qzeros"], t2["scales"], t2["g_idx"], 4)
     packed2, dense2 = qf.from_checkpoint(t2, "gptq", 4, group)
-    assert packed2 is None
-    assert torch.allclose(dense2.float(), _naive_gptq_dequant(t2["qweight"], t2["qzeros"], t2["scales"], t2["g_idx"], 4), atol=2e-3)
+    assert packed2 is not None and packed2.perm is not None and sorted(packed2.perm.tolist()) == list(range(K))
+    assert torch.allclose(dense2.float(), want2, atol=2e-3) and torch.allclose(qf.dequantize(packed2), want2, atol=1e-6)
+    x = torch.randn(5, K)
+    assert torch.allclose(x[:, packed2.perm.long()] @ qf.dequantize(qf.GroupQuantWeight(
+        packed2.codes, packed2.sz, 4, group, packed2.shape)).t(), x @ want2.t(), atol=1e-4)
+    with pytest.raises(ValueError):
+        packed2.cols(0, group)
+    # groups of unequal size have no packed form
+    t3 = dict(t)
+    t3["g_idx"] = torch.cat([torch.zeros(group + 8), torch.ones(K - group - 8)]).to(torch.int32)
+    packed3, dense3 = qf.from_checkpoint(t3, "gptq", 4, group)
+    assert packed3 is None
+    assert torch.allclose(dense3.float(), _naive_gptq_dequant(t3["qweight"], t3["qzeros"], t3["scales"], t3["g_idx"], 4), atol=2e-3)
     # 8-bit GPTQ and the v2 zero convention
     q8 = torch.randint(0, 256, (N, K), dtype=torch.int32)
     z8 = torch.randint(1, 255, (N, K // group)).float()
@@ -193,6 +206,45 @@ def test_gptq_checkpoint_loads_packed_and_matches_its_dense_expansion(tmp_path):
     assert checkpoint_quantization(tmp_path, {"quantization_config": {"quant_method": "fp8"}}) is None
 
 
+def test_act_order_gptq_checkpoint_is_served_packed():
+    """`desc_act` checkpoints: every projection stays packed (columns sorted by group, activations gathered in that order in
+    front of the GEMM) and the model's logits equal those of the checkpoint expanded to dense matrices."""
+    cfg = _tiny()
+    dense_model = DecoderModel.random_init(cfg, torch.device("cpu"), torch.float32, seed=7, std=0.05)
+    sd = export_hf_state_dict(dense_model)
+    gen = torch.Generator().manual_seed(3)
+    orders = {}                                            # one column order per layer input, as the Hessian of that input gives
+    qsd, deq = {}, {}
+    for k, t in sd.items():
+        if not k.endswith("_proj.weight"):
+            qsd[k] = deq[k] = t
+            continue
+        site = k.rsplit(".", 3)[0] + (".in_h" if any(n in k for n in ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj")) else k)
+        K = t.shape[1]
+        perm = orders.setdefault((site, K), torch.randperm(K, generator=gen))
+        g = qf.quantize_rtn(t[:, perm].contiguous(), 4, 128)
+        codes = torch.empty(t.shape, dtype=torch.int32)
+        codes[:, perm] = qf.unpack_codes(g.codes, 4, K).to(torch.int32)
+        tens = qf.gptq_pack(codes, g.sz[..., 0].float(), g.sz[..., 1].float(), 4, 128)
+        g_idx = torch.empty(K, dtype=torch.int32)
+        g_idx[perm] = (torch.arange(K) // 128).to(torch.int32)
+        tens["g_idx"] = g_idx
+        for n, v in tens.items():
+            qsd[k[:-6] + n] = v
+        d = torch.empty_like(t)
+        d[:, perm] = qf.dequantize(g)
+        deq[k] = d
+    w = InMemoryWeights(qsd, dtype=torch.float32)
+    w.quant = {"quant_method": "gptq", "bits": 4, "group_size": 128, "zero_offset": 1, "desc_act": True}
+    mq = DecoderModel.from_weights(cfg, w, torch.device("cpu"), torch.float32)
+    assert all(isinstance(getattr(lw, n), qf.GroupQuantWeight) and getattr(lw, n).perm is not None
+               for lw in mq.layers for n in ("qkv_w", "o_w", "gate_up_w", "down_w"))
+    md = DecoderModel.from_weights(cfg, InMemoryWeights(deq, dtype=torch.float32), torch.device("cpu"), torch.float32)
+    ids = list(range(3, 40))
+    a, b = _forward(mq, ids), _forward(md, ids)
+    assert torch.allclose(a, b, atol=2e-4), (a - b).abs().max()
+
+
 @pytest.mark.parametrize("method,tol", [("int4", 0.5), ("eetq", 0.04), ("bitsandbytes-nf4", 0.5), ("hqq-4bit", 0.5)])
 def test_model_quantised_on_load_stays_close_to_dense(method, tol):
     cfg = _tiny()
@@ -244,6 +296,29 @@ def test_int4_tensor_core_gemm_matches_fp32_reference(T):
             err = ((out.float().cpu() - want).norm() / want.norm()).item()
             assert err < 6e-3, (T, g.group, flag, err)
         assert g.int_zero == (g.method != "hqq-4bit")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T", [3, 48])
+def test_act_order_gemm_on_gpu_matches_fp32_reference(T):
+    """A packed matrix with a column order (act-order GPTQ) through both kernels behind `gemm_wq` (the 4-bit tensor-core GEMM at
+    few tokens, expansion + bf16 GEMM above), and through the expansion kernel alone, against fp32 products on the CPU."""
+    from lorax_b200.ops import native
+    torch.manual_seed(40 + T)
+    N, K = 1056, 1536
+    w = torch.randn(N, K) * 0.05
+    perm = torch.randperm(K)
+    g = qf.quantize_rtn(w[:, perm].contiguous(), 4, 128)
+    g.perm = perm.to(torch.int32)
+    dense = qf.dequantize(g)
+    assert ((dense - w).norm() / w.norm()).item() < 0.12          # the order is honoured: it is w, up to 4-bit rounding
+    gd = g.to("cuda")
+    assert (native.wq_dequant(gd).float().cpu() - dense).abs().max().item() < 2e-3
+    x = torch.randn(T, K, device="cuda").to(torch.bfloat16)
+    out = native.gemm_wq(x, gd)
+    torch.cuda.synchronize()
+    want = x.float().cpu() @ dense.t()
+    assert ((out.float().cpu() - want).norm() / want.norm()).item() < 6e-3
 
 
 @pytest.mark.gpu
