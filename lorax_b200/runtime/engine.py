@@ -27,7 +27,7 @@ from ..config import EngineConfig
 from ..models.decoder import DecoderModel
 from ..sampling.chooser import (FINISH_EOS, FINISH_LENGTH, FINISH_STOP, HeterogeneousNextTokenChooser, NextTokenParams,
                                 StoppingCriteria)
-from ..sampling.device import RowSampler
+from ..sampling.device import RowSampler, has_penalties, needs_device_step
 from ..sampling.device import supported as device_sampling_supported
 from .kv_cache import BlockAllocator, KVCache
 from .runner import ModelRunner, PrefillItem
@@ -89,6 +89,7 @@ class Engine:
         self.running: Dict[int, _Seq] = {}
         self.draining: Dict[int, _Seq] = {}
         self._row_sampler = RowSampler(model.device)
+        self._hist: Dict[int, torch.Tensor] = {}     # request id -> token-count histogram on the device (requests with penalties)
         self.inflight: Deque[tuple] = collections.deque()   # ("decode", ring idx, bucket, row->req) | ("first", ring idx, n, [req])
         self.steps_since_prefill = 0
         self.decode_text = decode_text
@@ -114,9 +115,8 @@ class Engine:
     # ------------------------------------------------------------------ API
     def add_request(self, req: GenRequest):
         if not req.params.plain and not device_sampling_supported(req.params):
-            raise ValueError("the in-process engine samples on the device (temperature, top-k, top-p, typical-p, seed); repetition / "
-                             "frequency / presence penalties, watermarking, grammars and alternative tokens are served by the "
-                             "shard runtime behind the router")
+            raise ValueError("the in-process engine samples on the device (penalties, temperature, top-k, top-p, typical-p, seed); "
+                             "watermarking, grammars and alternative tokens are served by the shard runtime behind the router")
         if not req.arrival_time:
             req.arrival_time = time.perf_counter()
         if len(req.prompt_ids) + req.max_new_tokens > self.cfg.max_total_tokens:
@@ -275,22 +275,30 @@ class Engine:
     # ------------------------------------------------------------------ one iteration
     def _sample_first(self, picked, next_ids, lps, logits):
         """Requests that sample draw their first token on the device from the prefill logits (one row per request)."""
-        idx = [i for i, (r, _) in enumerate(picked) if r.params.do_sample]
+        idx = [i for i, (r, _) in enumerate(picked) if needs_device_step(r.params)]
         if not idx:
             return
+        V = logits.shape[1]
+        for i in idx:                                        # the prompt opens the history of a request with penalties
+            r = picked[i][0]
+            if has_penalties(r.params):
+                prompt = torch.tensor(r.prompt_ids, dtype=torch.int64, device=logits.device).clamp_(0, V - 1)
+                self._hist[r.request_id] = torch.bincount(prompt, minlength=V).to(torch.float32)
         sampler = RowSampler(logits.device)
-        sampler.bind(idx, [picked[i][0].params for i in idx])
+        sampler.bind(idx, [picked[i][0].params for i in idx], [picked[i][0].request_id for i in idx], self._hist)
         ids, lp = sampler(logits, [0] * len(idx))
+        sampler.release()
         next_ids.index_copy_(0, sampler.rows, ids.to(next_ids.dtype))
         lps.index_copy_(0, sampler.rows, lp.to(lps.dtype))
 
     def _decode_sampler(self, snapshot: Dict[int, int]):
         """The device-side hook of a decode step, or None when every running request is greedy."""
-        rows = sorted(r for r, rid in snapshot.items() if self.running[rid].req.params.do_sample)
+        rows = sorted(r for r, rid in snapshot.items() if needs_device_step(self.running[rid].req.params))
         if not rows:
+            self._row_sampler.release()
             return None
         seqs = [self.running[snapshot[r]] for r in rows]
-        self._row_sampler.bind(rows, [s.req.params for s in seqs])
+        self._row_sampler.bind(rows, [s.req.params for s in seqs], [snapshot[r] for r in rows], self._hist)
         steps = [s.launched for s in seqs]                   # index of the token this step generates for the row
         rs = self._row_sampler
 
@@ -310,7 +318,7 @@ class Engine:
         if picked:
             items = [PrefillItem(r.prompt_ids, 0, b, r.adapter_index) for r, b in picked]
             snapshot = {s.row: rid for rid, s in self.running.items() if not s.retired}
-            sampling = any(r.params.do_sample for r, _ in picked) or any(s.req.params.do_sample for s in self.running.values())
+            sampling = any(needs_device_step(r.params) for r, _ in picked) or any(needs_device_step(s.req.params) for s in self.running.values())
             if self.mixed_steps and snapshot and self.runner.can_mix() and not sampling:
                 # one pass over the weights for the running decode rows and the new prompts together
                 k, b, next_ids, lps = self.runner.mixed_step(items)
@@ -347,6 +355,11 @@ class Engine:
                 if seq is None or seq.finished:
                     continue
                 self._emit(seq, ids_h[row], lps_h[row], now, events)
+        if self._hist:                                         # histories of requests that no longer decode
+            for rid in [k for k in self._hist if k not in self.running]:
+                del self._hist[rid]
+            if not self._hist:
+                self._row_sampler.release()
         return events
 
     def run(self, max_steps: Optional[int] = None) -> List[TokenEvent]:

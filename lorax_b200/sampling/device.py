@@ -1,8 +1,10 @@
 """Per-row sampling on the device, with no host synchronisation.
 
 The continuous-batching engine reads results one step behind the GPU, so a sampler that pulls logits to the host would stall
-the pipeline.  Here the rows that sample are warped (temperature, top-k, top-p, typical-p) and drawn on the device inside the
-step; the drawn ids overwrite the greedy ids before the asynchronous copy to the host is queued.
+the pipeline.  Here the rows that sample are penalised (repetition, frequency, presence), warped (temperature, top-k, top-p,
+typical-p) and drawn on the device inside the step; the drawn ids overwrite the greedy ids before the asynchronous copy to the
+host is queued.  The penalties need every request's history, which the host only learns a step late, so the history lives on the
+device too: one histogram of token counts per request (prompt and generated tokens), bumped at the drawn id inside the step.
 
 The draw is the exponential-noise arg-max the reference uses to avoid a synchronising `multinomial`
 (`server/lorax_server/utils/tokens.py:533-544`): argmax_i p_i / e_i with e_i ~ Exp(1).  The noise comes from a counter-based
@@ -77,19 +79,43 @@ def warp(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, t
     return x
 
 
-def draw(scores: torch.Tensor, seeds: torch.Tensor, steps: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
-    """One token per row from softmax(scores): ids [R] int64 and their log-probabilities under the warped distribution."""
+def penalise(logits: torch.Tensor, counts: torch.Tensor, repetition: torch.Tensor, frequency: torch.Tensor,
+             presence: torch.Tensor) -> torch.Tensor:
+    """The history penalties in the reference's order (`utils/logits_process.py:181-300`): scores of tokens already seen are
+    divided by the repetition penalty (multiplied when negative), then lowered by frequency * count + presence.  `counts` is
+    [R, V]: how often each token occurs in the row's prompt and output so far."""
+    x = logits.float()
+    seen = counts > 0
+    r = repetition[:, None]
+    x = torch.where(seen, torch.where(x < 0, x * r, x / r), x)
+    return x - counts * frequency[:, None] - seen.to(x.dtype) * presence[:, None]
+
+
+def draw(scores: torch.Tensor, seeds: torch.Tensor, steps: torch.Tensor, sample: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One token per row from softmax(scores): ids [R] int64 and their log-probabilities under the warped distribution.
+    Rows where `sample` is False take the arg-max (greedy requests that only carry penalties)."""
     logp = torch.log_softmax(scores, -1)
     e = -torch.log(uniform_noise(seeds, steps, scores.shape[1]))
-    ids = (logp - torch.log(e)).argmax(-1)
+    noisy = logp - torch.log(e)
+    if sample is not None:
+        noisy = torch.where(sample[:, None], noisy, logp)
+    ids = noisy.argmax(-1)
     return ids, logp.gather(1, ids[:, None])[:, 0]
 
 
+def has_penalties(p: NextTokenParams) -> bool:
+    return p.repetition_penalty != 1.0 or p.frequency_penalty != 0.0 or p.presence_penalty != 0.0
+
+
+def needs_device_step(p: NextTokenParams) -> bool:
+    """Whether a request's token cannot be the plain arg-max of the logits."""
+    return p.do_sample or has_penalties(p)
+
+
 def supported(p: NextTokenParams) -> bool:
-    """What the device sampler covers; penalties over the history, watermarking, grammars and alternative tokens need the
-    host-side chooser of the served path."""
-    return (p.repetition_penalty == 1.0 and p.frequency_penalty == 0.0 and p.presence_penalty == 0.0 and not p.watermark
-            and p.schema is None and p.return_k_alternatives == 0)
+    """What the device sampler covers; watermarking, grammars and alternative tokens need the host-side chooser of the served
+    path."""
+    return not p.watermark and p.schema is None and p.return_k_alternatives == 0
 
 
 class RowSampler:
@@ -98,23 +124,57 @@ class RowSampler:
     def __init__(self, device):
         self.device = device
         self.key = None
-        self.rows = self.temperature = self.top_k = self.top_p = self.typical_p = self.seeds = None
+        self.rows = self.temperature = self.top_k = self.top_p = self.typical_p = self.seeds = self.sample = None
+        self.counts = self.rep = self.freq = self.pres = None
+        self._owners: List[Tuple[int, object]] = []      # (index in the bound set, key of the histogram in the store)
+        self._store = None
 
-    def bind(self, rows: Sequence[int], params: Sequence[NextTokenParams]):
-        key = (tuple(rows), tuple(id(p) for p in params))
+    def release(self):
+        """Hand the histograms back to the store they came from (as views of the stacked tensor: nothing is copied)."""
+        if self.counts is not None and self._store is not None:
+            for i, k in self._owners:
+                if k in self._store:
+                    self._store[k] = self.counts[i]
+        self.counts, self._owners, self._store, self.key = None, [], None, None
+
+    def bind(self, rows: Sequence[int], params: Sequence[NextTokenParams], keys: Optional[Sequence[object]] = None,
+             store: Optional[dict] = None):
+        """`store[keys[i]]` is the token-count histogram [V] (fp32, on the device) of request i; only requests with penalties
+        need one.  While bound, the histograms live stacked in `self.counts` and are bumped by every call."""
+        key = (tuple(rows), tuple(id(p) for p in params), tuple(keys) if keys is not None else None)
         if key == self.key:
             return
+        self.release()
         self.key = key
         dev = self.device
+        f32 = lambda vals: torch.tensor(list(vals), dtype=torch.float32, device=dev)
         self.rows = torch.tensor(list(rows), dtype=torch.int64, device=dev)
-        self.temperature = torch.tensor([p.temperature for p in params], dtype=torch.float32, device=dev)
-        self.top_k = torch.tensor([p.top_k for p in params], dtype=torch.int64, device=dev)
-        self.top_p = torch.tensor([p.top_p for p in params], dtype=torch.float32, device=dev)
-        self.typical_p = torch.tensor([p.typical_p for p in params], dtype=torch.float32, device=dev)
-        self.seeds = torch.tensor([p.seed for p in params], dtype=torch.int64, device=dev)
+        # greedy requests that only carry penalties pass the warpers untouched
+        self.temperature = f32(p.temperature if p.do_sample else 1.0 for p in params)
+        self.top_k = torch.tensor([p.top_k if p.do_sample else 0 for p in params], dtype=torch.int64, device=dev)
+        self.top_p = f32(p.top_p if p.do_sample else 1.0 for p in params)
+        self.typical_p = f32(p.typical_p if p.do_sample else 1.0 for p in params)
+        self.seeds = torch.tensor([p.seed or 0 for p in params], dtype=torch.int64, device=dev)
+        self.sample = torch.tensor([bool(p.do_sample) for p in params], dtype=torch.bool, device=dev)
+        owners = [(i, keys[i]) for i, p in enumerate(params) if has_penalties(p)] if (keys is not None and store is not None) else []
+        if owners:
+            first = store[owners[0][1]]
+            blank = torch.zeros_like(first)
+            own = dict(owners)
+            self.counts = torch.stack([store[own[i]] if i in own else blank for i in range(len(params))])
+            self.rep, self.freq, self.pres = (f32(getattr(p, n) for p in params) for n in
+                                              ("repetition_penalty", "frequency_penalty", "presence_penalty"))
+            self._owners, self._store = owners, store
+            for i, k in owners:
+                store[k] = self.counts[i]
 
     def __call__(self, logits: torch.Tensor, steps: Sequence[int]) -> Tuple[torch.Tensor, torch.Tensor]:
         """logits: all rows of the step; returns (ids, logprobs) for the bound rows."""
         sel = logits.index_select(0, self.rows)
         st = torch.tensor(list(steps), dtype=torch.int64, device=self.device)
-        return draw(warp(sel, self.temperature, self.top_k, self.top_p, self.typical_p), self.seeds, st)
+        if self.counts is not None:
+            sel = penalise(sel[:, : self.counts.shape[1]], self.counts, self.rep, self.freq, self.pres)
+        ids, lp = draw(warp(sel, self.temperature, self.top_k, self.top_p, self.typical_p), self.seeds, st, self.sample)
+        if self.counts is not None:
+            self.counts.scatter_add_(1, ids[:, None], torch.ones_like(ids, dtype=self.counts.dtype)[:, None])
+        return ids, lp

@@ -222,4 +222,49 @@ def test_engine_samples_on_device_reproducibly(setup):
     assert c[1] != a[1]                                     # another seed, another continuation
     assert all(len(v) == 10 for v in a.values())
     with pytest.raises(ValueError):
-        run([0], {0: NextTokenParams(do_sample=True, repetition_penalty=1.2)})
+        run([0], {0: NextTokenParams(do_sample=True, watermark=True)})
+
+
+def test_engine_penalties_on_device_match_the_host_chooser(setup):
+    """Repetition, frequency and presence penalties in the in-process engine, whose history is a histogram on the device: a
+    greedy request with penalties yields the tokens of a step-by-step oracle (full forward pass over prompt + output, the
+    served path's host-side chooser over the whole history, arg-max), whatever shares its batch; a sampling request with
+    penalties is reproducible from its seed."""
+    from lorax_b200.runtime.kv_cache import KVCache
+    from lorax_b200.runtime.runner import ModelRunner, PrefillItem
+    from lorax_b200.sampling.chooser import HeterogeneousNextTokenChooser, NextTokenParams
+    from lorax_b200.sampling import device as ds
+    cfg, model, mgr, _ = setup
+    g = torch.Generator().manual_seed(33)
+    # prompts over a small alphabet so that tokens repeat and the penalties bite
+    prompts = [torch.randint(0, 40, (n,), generator=g).tolist() for n in (14, 25, 11)]
+    pen = NextTokenParams(repetition_penalty=1.8, frequency_penalty=0.7, presence_penalty=0.4)
+    assert ds.supported(pen) and ds.needs_device_step(pen) and not pen.plain
+    n_new = 12
+
+    def oracle(prompt):
+        kv = KVCache(cfg.num_hidden_layers, 16, model.nkv, model.d, model.dtype, model.device)
+        r = ModelRunner(model, kv, max_batch=2, max_seq_tokens=128, max_prefill_tokens=256, use_graphs=False)
+        chooser = HeterogeneousNextTokenChooser([pen], "cpu", cfg.vocab_size)
+        ids = list(prompt)
+        for _ in range(n_new):
+            logits = r.prefill([PrefillItem(ids, 0, [1, 2, 3, 4], all_logprobs=True)])[2][-1:].float()
+            hist = torch.tensor([ids])
+            ids.append(int(chooser.warp(hist, torch.ones_like(hist, dtype=torch.bool), logits.clone()).argmax(-1)))
+        return ids[len(prompt):]
+
+    def run(order, params):
+        eng = Engine(model, EngineConfig(max_input_length=64, max_total_tokens=128, max_batch_prefill_tokens=256, compile=False), num_blocks=64)
+        for rid in order:
+            eng.add_request(GenRequest(rid, prompts[rid], max_new_tokens=n_new, params=params[rid]))
+        eng.run()
+        assert not eng._hist or all(k in eng.running for k in eng._hist)
+        return {rid: eng.finished[rid].output_ids for rid in order}
+    sample = NextTokenParams(temperature=1.1, top_k=30, do_sample=True, seed=4, repetition_penalty=1.5, presence_penalty=0.5)
+    params = {0: pen, 1: NextTokenParams(), 2: sample}
+    a = run([0, 1, 2], params)
+    b = run([2, 0], params)
+    plain = run([0, 1], {0: NextTokenParams(), 1: NextTokenParams()})
+    assert a[0] == oracle(prompts[0]) == b[0]
+    assert a[0] != plain[0] and a[1] == plain[1]            # the penalties change the tokens; the greedy neighbour is untouched
+    assert a[2] == b[2]
