@@ -235,3 +235,30 @@ def test_engine_device_sampling_with_graphs():
     assert all(len(v) == 12 for v in a.values())
     from lorax_b200.ops import native
     native.workspace().check_status()
+
+
+def test_engine_device_penalties_with_graphs():
+    """History penalties inside graph-replayed decode steps: the token histograms live on the device and are bumped in the step.
+    A presence penalty far above the logits' range forbids every token already seen, so a greedy request's output neither
+    repeats itself nor its prompt; the result does not depend on the batch around it, and a sampling request with penalties is
+    reproducible from its seed."""
+    from lorax_b200.runtime.engine import GenRequest
+    from lorax_b200.sampling.chooser import NextTokenParams
+    cfg, gm, _ = _build("cuda", torch.bfloat16)
+    g = torch.Generator().manual_seed(37)
+    prompts = [torch.randint(0, 60, (n,), generator=g).tolist() for n in (12, 33, 20)]
+    params = {0: NextTokenParams(presence_penalty=1e4), 1: NextTokenParams(),
+              2: NextTokenParams(temperature=0.9, top_k=30, do_sample=True, seed=5, repetition_penalty=1.4, frequency_penalty=0.3)}
+
+    def run(order):
+        eng = Engine(gm, EngineConfig(max_input_length=64, max_total_tokens=128, max_batch_prefill_tokens=256, compile=True), num_blocks=64)
+        for rid in order:
+            eng.add_request(GenRequest(rid, prompts[rid], max_new_tokens=16, params=params[rid], adapter_index=rid % 3))
+        eng.run()
+        assert not eng._hist
+        return {rid: eng.finished[rid].output_ids for rid in order}
+    a, b, greedy = run([0, 1, 2]), run([2, 0]), run([1])
+    assert len(set(a[0])) == 16 and not set(a[0]) & set(prompts[0])
+    assert a[0] == b[0] and a[2] == b[2] and a[1] == greedy[1]
+    from lorax_b200.ops import native
+    native.workspace().check_status()
