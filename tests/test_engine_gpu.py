@@ -262,3 +262,48 @@ def test_engine_device_penalties_with_graphs():
     assert a[0] == b[0] and a[2] == b[2] and a[1] == greedy[1]
     from lorax_b200.ops import native
     native.workspace().check_status()
+
+
+_FAMILY_CONFIGS = {
+    "gemma2": {"model_type": "gemma2", "num_key_value_heads": 2, "head_dim": 64, "sliding_window": 32, "query_pre_attn_scalar": 64,
+               "attn_logit_softcapping": 30.0, "final_logit_softcapping": 20.0, "rms_norm_eps": 1e-6},
+    "phi3": {"model_type": "phi3", "num_key_value_heads": 2},
+    "gpt_neox": {"model_type": "gpt_neox", "rotary_pct": 0.25, "use_parallel_residual": True, "layer_norm_eps": 1e-5},
+    "falcon": {"model_type": "falcon", "multi_query": True, "parallel_attn": True, "bias": False, "new_decoder_architecture": False},
+    "cohere": {"model_type": "cohere", "num_key_value_heads": 2, "logit_scale": 0.25, "layer_norm_eps": 1e-5},
+    "granite": {"model_type": "granite", "num_key_value_heads": 2, "embedding_multiplier": 3.0, "logits_scaling": 2.0,
+                "residual_multiplier": 0.5, "attention_multiplier": 0.1},
+    "gpt2": {"model_type": "gpt2", "n_embd": 256, "n_layer": 2, "n_head": 4, "n_positions": 512},
+    "phi": {"model_type": "phi", "partial_rotary_factor": 0.5, "layer_norm_eps": 1e-5},
+    "mistral_window": {"model_type": "mistral", "num_key_value_heads": 2, "sliding_window": 32},
+}
+
+
+@pytest.mark.parametrize("family", sorted(_FAMILY_CONFIGS))
+def test_decoder_families_match_cpu_oracle(family):
+    """The architecture switches of the config-driven decoder on the GPU kernels (soft caps and alternating windows of gemma2,
+    partial rotary and parallel residuals of neox / phi / falcon, multi-query attention, bias-free LayerNorm of cohere, the
+    multipliers of granite, learned positions of gpt2, a sliding window shorter than the prompt): prefill logits and
+    teacher-forced decode logits against the fp32 CPU path of the same random weights."""
+    from lorax_b200.config import ModelConfig
+    d = {"vocab_size": 1000, "hidden_size": 256, "intermediate_size": 512, "num_hidden_layers": 2, "num_attention_heads": 4,
+         "max_position_embeddings": 512}
+    d.update(_FAMILY_CONFIGS[family])
+    cfg = ModelConfig.from_dict(d)
+    gm = DecoderModel.random_init(cfg, "cuda", torch.bfloat16, seed=4, std=0.05)
+    cm = DecoderModel.random_init(cfg, "cpu", torch.float32, seed=4, std=0.05)
+    g = torch.Generator().manual_seed(5)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (40, 75)]
+    forced = torch.randint(0, cfg.vocab_size, (2,), generator=g).tolist()
+    outs = []
+    for m in (gm, cm):
+        kv = KVCache(cfg.num_hidden_layers, 32, m.nkv, m.d, m.dtype, m.device)
+        r = ModelRunner(m, kv, max_batch=4, max_seq_tokens=256, max_prefill_tokens=512, use_graphs=False)
+        blocks = [[1, 2, 3, 4], [5, 6, 7, 8]]
+        _, _, logits = r.prefill([PrefillItem(p, 0, b) for p, b in zip(prompts, blocks)])
+        _, _, step = r.prefill([PrefillItem([t], len(p), b) for t, p, b in zip(forced, prompts, blocks)])
+        outs.append(torch.cat([logits.float().cpu(), step.float().cpu()]))
+    from lorax_b200.ops import native
+    native.workspace().check_status()
+    err = (outs[0] - outs[1]).norm() / outs[1].norm()
+    assert err < 3e-2, err
