@@ -75,8 +75,8 @@ class LayerWeights:
     pre_ffn_norm: Optional[torch.Tensor] = None       # gemma2
     post_ffn_norm: Optional[torch.Tensor] = None      # gemma2
     router_w: Optional[torch.Tensor] = None           # MoE gate [E, H]
-    experts_w13: Optional[torch.Tensor] = None        # [E_local, 2I, H]
-    experts_w2: Optional[torch.Tensor] = None         # [E_local, H, I]
+    experts_w13: Optional[torch.Tensor] = None        # [E_local, 2I, H], or a list of E_local packed matrices
+    experts_w2: Optional[torch.Tensor] = None         # [E_local, H, I], likewise
 
 
 @dataclass
@@ -364,6 +364,10 @@ class DecoderModel:
                 w = getattr(lw, name)
                 if isinstance(w, torch.Tensor) and w.dim() == 2 and w.shape[1] % 128 == 0 and w.shape[0] % 16 == 0:
                     setattr(lw, name, quantize_weight(w, method, group))
+            for name in ("experts_w13", "experts_w2"):       # mixture of experts: one packed matrix per local expert
+                w = getattr(lw, name)
+                if isinstance(w, torch.Tensor) and w.dim() == 3 and w.shape[2] % 128 == 0 and w.shape[1] % 16 == 0:
+                    setattr(lw, name, [quantize_weight(w[e], method, group) for e in range(w.shape[0])])
         self.quantized = method
         self._native = None
 

@@ -230,19 +230,25 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
         if c.is_moe:
             lw.router_w = fin(_need(w, L + nm["router"], pre))
             E = c.num_local_experts
+            el = max(E // ws, 1)                     # expert parallel: rank r owns experts [r*el, (r+1)*el) in full
+            mine = range(rk * el, (rk + 1) * el) if el < E else range(E)
             w13, w2 = [], []
             if nm.get("experts_stacked"):
                 P = L + nm["experts_stacked"]
                 I = c.intermediate_size
                 w1s, v1s, w2s = (dense(_need(w, P + n, pre)).view(E, I, -1) for n in ("w1", "v1", "w2"))
-                w13 = [torch.cat([w1s[e], v1s[e]], 0) for e in range(E)]
-                w2 = [w2s[e].t() for e in range(E)]
-            for e in range(E if not nm.get("experts_stacked") else 0):
+                w13 = [torch.cat([w1s[e], v1s[e]], 0) for e in mine]
+                w2 = [w2s[e].t() for e in mine]
+            for e in (mine if not nm.get("experts_stacked") else ()):
                 P = L + nm["expert"].format(e=e)
-                w13.append(torch.cat([dense(_need(w, P + "w1.weight", pre)), dense(_need(w, P + "w3.weight", pre))], 0))
-                w2.append(dense(_need(w, P + "w2.weight", pre)))
-            lw.experts_w13 = fin(torch.stack(w13))
-            lw.experts_w2 = fin(torch.stack(w2))
+                w13.append(_cat0([_need(w, P + "w1.weight", pre), _need(w, P + "w3.weight", pre)]))
+                w2.append(_need(w, P + "w2.weight", pre))
+            if all(isinstance(t, GroupQuantWeight) for t in w13 + w2):
+                # a GPTQ / AWQ checkpoint: every expert stays packed, one matrix each
+                lw.experts_w13, lw.experts_w2 = [fin(t) for t in w13], [fin(t) for t in w2]
+            else:
+                lw.experts_w13 = fin(torch.stack([dense(t) for t in w13]))
+                lw.experts_w2 = fin(torch.stack([dense(t) for t in w2]))
         else:
             if nm.get("gate_up"):
                 gu = lin(L + nm["gate_up"])
@@ -263,7 +269,8 @@ def load_decoder_weights(m: DecoderModel, w: AbstractWeights):
             if db is not None:
                 lw.down_b = fin(db if rk == 0 else torch.zeros_like(db))
         m.layers.append(lw)
-    if any(isinstance(getattr(lw, n, None), GroupQuantWeight) for lw in m.layers for n in ("qkv_w", "o_w", "gate_up_w", "down_w")):
+    if any(isinstance(getattr(lw, n, None), (GroupQuantWeight, list)) for lw in m.layers
+           for n in ("qkv_w", "o_w", "gate_up_w", "down_w", "experts_w13")):
         m.quantized = (getattr(w, "quant", None) or {}).get("quant_method", "int4")
         m._native = None
 

@@ -33,7 +33,7 @@ def moe_forward(model, x: torch.Tensor, lw, li: int, inp) -> torch.Tensor:
     c, ops = model.config, model.ops
     E = c.num_local_experts
     ws, rk = model.tp.world_size, model.tp.rank
-    e_local = lw.experts_w13.shape[0]
+    e_local = len(lw.experts_w13)             # a stacked tensor, or a list of packed (weight-only quantised) matrices
     e0 = rk * e_local if e_local < E else 0
     T = x.shape[0]
     # the router is tiny (E output features): plain matmul keeps it exact across ranks
@@ -45,18 +45,18 @@ def moe_forward(model, x: torch.Tensor, lw, li: int, inp) -> torch.Tensor:
         e = e0 + j
         we = w[:, e]
         if T <= DENSE_MAX_TOKENS:
-            gu = ops.gemm(x, lw.experts_w13[j])
+            gu = model._gemm(x, lw.experts_w13[j], None)
             a = ops.act_mul(gu, I, c.hidden_act, gated=True)
-            dn = ops.gemm(a, lw.experts_w2[j])
+            dn = model._gemm(a, lw.experts_w2[j], None)
             out.addcmul_(dn.float(), we[:, None])
         else:
             idx = torch.nonzero(we > 0, as_tuple=False)[:, 0]
             if idx.numel() == 0:
                 continue
             xe = x.index_select(0, idx).contiguous()
-            gu = ops.gemm(xe, lw.experts_w13[j])
+            gu = model._gemm(xe, lw.experts_w13[j], None)
             a = ops.act_mul(gu, I, c.hidden_act, gated=True)
-            dn = ops.gemm(a, lw.experts_w2[j])
+            dn = model._gemm(a, lw.experts_w2[j], None)
             out.index_add_(0, idx, dn.float() * we.index_select(0, idx)[:, None])
     out = out.to(x.dtype)
     if ws > 1 and e_local < E:

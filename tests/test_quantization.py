@@ -384,3 +384,91 @@ def test_gptq_checkpoint_quantiser_writes_a_loadable_checkpoint(tmp_path):
     dense.quantize("int4")
     e_rtn = ((_forward(dense, ids) - want).norm() / want.norm()).item()
     assert e_gptq < e_rtn, (e_gptq, e_rtn)
+
+
+def _tiny_mixtral():
+    return cfgs.ModelConfig(model_type="mixtral", vocab_size=300, hidden_size=128, intermediate_size=256, num_hidden_layers=2,
+                            num_attention_heads=4, num_key_value_heads=2, head_dim=32, rope_theta=1e4, max_position_embeddings=256,
+                            num_local_experts=4, num_experts_per_tok=2, torch_dtype="float32")
+
+
+def test_mixture_of_experts_is_served_packed():
+    """Mixtral's experts under weight-only quantisation: one packed matrix per expert, whether quantised on load or read from a
+    GPTQ checkpoint, and logits equal to those of the model holding the same matrices expanded."""
+    cfg = _tiny_mixtral()
+    dense_model = DecoderModel.random_init(cfg, torch.device("cpu"), torch.float32, seed=9, std=0.05)
+    ids = list(range(3, 50))
+    # quantised on load
+    mq = DecoderModel.random_init(cfg, torch.device("cpu"), torch.float32, seed=9, std=0.05)
+    mq.quantize("int4")
+    lw = mq.layers[0]
+    assert isinstance(lw.experts_w13, list) and len(lw.experts_w13) == 4 and all(isinstance(t, qf.GroupQuantWeight) for t in lw.experts_w13 + lw.experts_w2)
+    md = DecoderModel.random_init(cfg, torch.device("cpu"), torch.float32, seed=9, std=0.05)
+    for a, b in zip(md.layers, mq.layers):
+        for n in ("qkv_w", "o_w"):
+            setattr(a, n, qf.dequantize(getattr(b, n)))
+        a.experts_w13 = torch.stack([qf.dequantize(t) for t in b.experts_w13])
+        a.experts_w2 = torch.stack([qf.dequantize(t) for t in b.experts_w2])
+    got, want = _forward(mq, ids), _forward(md, ids)
+    assert torch.allclose(got, want, atol=2e-4), (got - want).abs().max()
+    assert not torch.allclose(want, _forward(dense_model, ids), atol=1e-3)      # 4 bits do change the logits
+    # read from a GPTQ checkpoint
+    sd = export_hf_state_dict(dense_model)
+    qsd, deq = {}, {}
+    for k, t in sd.items():
+        if k.endswith("_proj.weight") or ".experts." in k:
+            g = qf.quantize_rtn(t, 4, 128)
+            for n, v in qf.gptq_pack(qf.unpack_codes(g.codes, 4, t.shape[1]), g.sz[..., 0].float(), g.sz[..., 1].float(), 4, 128).items():
+                qsd[k[:-6] + n] = v
+            deq[k] = qf.dequantize(g)
+        else:
+            qsd[k] = deq[k] = t
+    w = InMemoryWeights(qsd, dtype=torch.float32)
+    w.quant = {"quant_method": "gptq", "bits": 4, "group_size": 128, "zero_offset": 1}
+    mc = DecoderModel.from_weights(cfg, w, torch.device("cpu"), torch.float32)
+    assert mc.quantized == "gptq" and isinstance(mc.layers[1].experts_w2, list) and isinstance(mc.layers[1].experts_w2[3], qf.GroupQuantWeight)
+    mcd = DecoderModel.from_weights(cfg, InMemoryWeights(deq, dtype=torch.float32), torch.device("cpu"), torch.float32)
+    assert isinstance(mcd.layers[1].experts_w2, torch.Tensor)
+    a, b = _forward(mc, ids), _forward(mcd, ids)
+    assert torch.allclose(a, b, atol=2e-4), (a - b).abs().max()
+
+
+def test_checkpoint_experts_are_loaded_expert_parallel():
+    """A rank of a tensor-parallel group reads only the experts it owns from a checkpoint (rank r of ws: experts
+    [r * E / ws, (r + 1) * E / ws)), like a randomly initialised model does."""
+    from lorax_b200.parallel.tp import TensorParallel
+    cfg = _tiny_mixtral()
+    full = DecoderModel.random_init(cfg, torch.device("cpu"), torch.float32, seed=9, std=0.05)
+    sd = export_hf_state_dict(full)
+    for rank in (0, 1):
+        m = DecoderModel.from_weights(cfg, InMemoryWeights(dict(sd), dtype=torch.float32), torch.device("cpu"), torch.float32,
+                                      TensorParallel(rank, 2))
+        for lw, fw in zip(m.layers, full.layers):
+            assert lw.experts_w13.shape[0] == 2
+            assert torch.equal(lw.experts_w13, fw.experts_w13[2 * rank: 2 * rank + 2])
+            assert torch.equal(lw.experts_w2, fw.experts_w2[2 * rank: 2 * rank + 2])
+
+
+@pytest.mark.gpu
+def test_quantised_mixture_of_experts_on_gpu():
+    """Mixtral with 4-bit experts on the GPU kernels (the direct 4-bit GEMM for a short prompt, expansion + bf16 GEMM for a long
+    one) against the CPU oracle holding the very same packed matrices."""
+    from lorax_b200.ops import native
+    cfg = _tiny_mixtral()
+    cfg.torch_dtype = "bfloat16"
+    cfg.hidden_size, cfg.head_dim, cfg.intermediate_size = 256, 64, 384
+    cpu = DecoderModel.random_init(cfg, torch.device("cpu"), torch.float32, seed=6, std=0.05)
+    gpu = DecoderModel.random_init(cfg, torch.device("cuda"), torch.bfloat16, seed=6, std=0.05)
+    cpu.quantize("int4")
+    for lc, lg in zip(cpu.layers, gpu.layers):
+        for name in ("qkv_w", "o_w"):
+            setattr(lg, name, getattr(lc, name).to("cuda"))
+        lg.experts_w13 = [t.to("cuda") for t in lc.experts_w13]
+        lg.experts_w2 = [t.to("cuda") for t in lc.experts_w2]
+    gpu.quantized = "int4"
+    gpu._native = None
+    for n in (20, 90):
+        ids = list(range(5, 5 + n))
+        a, b = _forward(gpu, ids).float().cpu(), _forward(cpu, ids)
+        assert ((a - b).norm() / b.norm()).item() < 0.06, n
+    native.workspace(torch.device("cuda")).check_status()
