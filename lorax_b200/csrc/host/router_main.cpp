@@ -824,8 +824,8 @@ int main(int argc, char** argv) {
   const std::string otlp = a.get("otlp-endpoint", "");
   const char* logger_env = std::getenv("REQUEST_LOGGER_URL");
   App app(client, cfg, info, num_blocks, otlp, logger_env ? logger_env : "");
-  if (!otlp.empty()) log_json(app.tracing() ? "INFO" : "WARN", app.tracing() ? "tracing to " + otlp + " (OTLP/HTTP JSON)"
-                                                                              : "otlp endpoint must be an http:// URL; tracing is off");
+  if (!otlp.empty()) log_json(app.tracing() ? "INFO" : "WARN", app.tracing() ? "tracing to " + otlp + (lx::telemetry::parse_url(otlp).grpc ? " (OTLP/gRPC)" : " (OTLP/HTTP JSON)")
+                                                                              : "otlp endpoint must be an http:// or grpc:// URL; tracing is off");
   http::Server server;
   std::vector<std::string> cors;
   std::string cors_arg = a.get("cors-allow-origin", "");

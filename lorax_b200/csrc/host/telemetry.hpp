@@ -20,6 +20,7 @@
 #include <sys/time.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
 #include <chrono>
 #include <condition_variable>
@@ -40,11 +41,15 @@ struct Url {
   std::string host, path = "/";
   int port = 80;
   bool ok = false;
+  bool grpc = false;                                     // OTLP/gRPC (h2c) instead of OTLP/HTTP JSON
 };
+// "http://host:port/path" speaks HTTP/1.1; "grpc://host:port" speaks gRPC over clear-text HTTP/2, and so does an http:// URL
+// on 4317, the port collectors reserve for OTLP/gRPC.
 inline Url parse_url(const std::string& u) {
   Url r;
-  const std::string pre = "http://";
-  if (u.compare(0, pre.size(), pre) != 0) return r;      // plain HTTP only: collectors and log sinks on the cluster network
+  std::string pre = "http://";
+  if (u.compare(0, 7, "grpc://") == 0) { pre = "grpc://"; r.grpc = true; r.port = 4317; }
+  else if (u.compare(0, pre.size(), pre) != 0) return r;  // no TLS: collectors and log sinks on the cluster network
   size_t p = pre.size(), slash = u.find('/', p);
   std::string hp = u.substr(p, slash == std::string::npos ? std::string::npos : slash - p);
   if (slash != std::string::npos) r.path = u.substr(slash);
@@ -56,7 +61,129 @@ inline Url parse_url(const std::string& u) {
     r.host = hp;
   }
   r.ok = !r.host.empty() && r.port > 0;
+  if (r.port == 4317) r.grpc = true;
   return r;
+}
+
+inline int connect_tcp(const Url& url, int timeout_ms) {
+  addrinfo hints{}, *res = nullptr;
+  hints.ai_family = AF_UNSPEC;
+  hints.ai_socktype = SOCK_STREAM;
+  if (getaddrinfo(url.host.c_str(), std::to_string(url.port).c_str(), &hints, &res) != 0 || !res) return -1;
+  int fd = -1;
+  for (addrinfo* a = res; a; a = a->ai_next) {
+    fd = ::socket(a->ai_family, a->ai_socktype, a->ai_protocol);
+    if (fd < 0) continue;
+    timeval tv{timeout_ms / 1000, (timeout_ms % 1000) * 1000};
+    setsockopt(fd, SOL_SOCKET, SO_RCVTIMEO, &tv, sizeof tv);
+    setsockopt(fd, SOL_SOCKET, SO_SNDTIMEO, &tv, sizeof tv);
+    if (::connect(fd, a->ai_addr, a->ai_addrlen) == 0) break;
+    ::close(fd);
+    fd = -1;
+  }
+  freeaddrinfo(res);
+  return fd;
+}
+inline bool send_all(int fd, const std::string& b) {
+  size_t off = 0;
+  while (off < b.size()) {
+    ssize_t w = ::send(fd, b.data() + off, b.size() - off, MSG_NOSIGNAL);
+    if (w <= 0) return false;
+    off += (size_t)w;
+  }
+  return true;
+}
+inline bool recv_exact(int fd, char* dst, size_t n) {
+  size_t off = 0;
+  while (off < n) {
+    ssize_t r = ::recv(fd, dst + off, n - off, 0);
+    if (r <= 0) return false;
+    off += (size_t)r;
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------------ protobuf writer
+// The few wire types OTLP's trace messages use (opentelemetry/proto/trace/v1/trace.proto).
+struct Pb {
+  std::string b;
+  void varint(uint64_t v) { while (v >= 0x80) { b.push_back((char)(v | 0x80)); v >>= 7; } b.push_back((char)v); }
+  void tag(int field, int wire) { varint(((uint64_t)field << 3) | (uint64_t)wire); }
+  void bytes(int field, const std::string& v) { tag(field, 2); varint(v.size()); b += v; }
+  void msg(int field, const Pb& m) { bytes(field, m.b); }
+  void u64(int field, uint64_t v) { tag(field, 0); varint(v); }
+  void fixed64(int field, uint64_t v) { tag(field, 1); for (int i = 0; i < 8; ++i) b.push_back((char)((v >> (8 * i)) & 0xff)); }
+  void f64(int field, double d) { uint64_t v; std::memcpy(&v, &d, 8); fixed64(field, v); }
+};
+inline std::string unhex(const std::string& h) {
+  auto nib = [](char c) { return c <= '9' ? c - '0' : c - 'a' + 10; };
+  std::string o;
+  for (size_t i = 0; i + 1 < h.size(); i += 2) o.push_back((char)((nib(h[i]) << 4) | nib(h[i + 1])));
+  return o;
+}
+
+// ------------------------------------------------------------------------------------------------ minimal gRPC unary call
+// One call per connection over clear-text HTTP/2 with prior knowledge: preface, SETTINGS, HEADERS (HPACK literals without
+// indexing, no Huffman), DATA, then frames are read until the stream ends.  A unary call that succeeded answers with headers,
+// one DATA frame and trailers; a refusal answers with trailers only, so "a DATA frame arrived before the stream ended" tells
+// them apart without an HPACK decoder.  Returns true on success.
+inline bool grpc_unary(const Url& url, const std::string& method_path, const std::string& message, int timeout_ms = 2000) {
+  if (message.size() + 5 > 60000) return false;          // one flow-control window of the default size; batches here are far smaller
+  int fd = connect_tcp(url, timeout_ms);
+  if (fd < 0) return false;
+  auto frame = [](int type, int flags, uint32_t stream, const std::string& payload) {
+    std::string f;
+    uint32_t n = (uint32_t)payload.size();
+    f.push_back((char)(n >> 16)); f.push_back((char)(n >> 8)); f.push_back((char)n);
+    f.push_back((char)type); f.push_back((char)flags);
+    f.push_back((char)(stream >> 24)); f.push_back((char)(stream >> 16)); f.push_back((char)(stream >> 8)); f.push_back((char)stream);
+    return f + payload;
+  };
+  auto lit = [](std::string& h, const std::string& name, const std::string& value) {
+    auto len = [&h](size_t n) {                           // 7-bit prefix integer, Huffman bit clear
+      if (n < 127) { h.push_back((char)n); return; }
+      h.push_back((char)127);
+      n -= 127;
+      while (n >= 128) { h.push_back((char)((n & 127) | 128)); n >>= 7; }
+      h.push_back((char)n);
+    };
+    h.push_back((char)0x00);                              // literal header field without indexing, new name
+    len(name.size()); h += name;
+    len(value.size()); h += value;
+  };
+  std::string hdr;
+  lit(hdr, ":method", "POST");
+  lit(hdr, ":scheme", "http");
+  lit(hdr, ":path", method_path);
+  lit(hdr, ":authority", url.host + ":" + std::to_string(url.port));
+  lit(hdr, "content-type", "application/grpc");
+  lit(hdr, "te", "trailers");
+  std::string body(5, '\0');
+  uint32_t n = (uint32_t)message.size();
+  body[1] = (char)(n >> 24); body[2] = (char)(n >> 16); body[3] = (char)(n >> 8); body[4] = (char)n;
+  body += message;
+  std::string out = "PRI * HTTP/2.0\r\n\r\nSM\r\n\r\n" + frame(4, 0, 0, "") + frame(1, 0x4, 1, hdr);
+  for (size_t off = 0; off < body.size(); off += 16384) {
+    size_t len = std::min<size_t>(16384, body.size() - off);
+    out += frame(0, off + len == body.size() ? 0x1 : 0, 1, body.substr(off, len));
+  }
+  bool ok = send_all(fd, out), got_data = false, done = false;
+  for (int guard = 0; ok && !done && guard < 64; ++guard) {
+    unsigned char h[9];
+    if (!recv_exact(fd, (char*)h, 9)) { ok = false; break; }
+    uint32_t len = ((uint32_t)h[0] << 16) | ((uint32_t)h[1] << 8) | h[2];
+    int type = h[3], flags = h[4];
+    uint32_t stream = (((uint32_t)h[5] & 0x7f) << 24) | ((uint32_t)h[6] << 16) | ((uint32_t)h[7] << 8) | h[8];
+    std::string payload(len, '\0');
+    if (len > (1u << 20) || (len && !recv_exact(fd, &payload[0], len))) { ok = false; break; }
+    if (type == 4 && !(flags & 0x1)) ok = send_all(fd, frame(4, 0x1, 0, ""));          // SETTINGS -> ACK
+    else if (type == 6 && !(flags & 0x1)) ok = send_all(fd, frame(6, 0x1, 0, payload)); // PING -> ACK
+    else if (type == 3 || type == 7) ok = false;                                        // RST_STREAM, GOAWAY
+    else if (type == 0 && stream == 1) { got_data = got_data || len >= 5; done = flags & 0x1; }
+    else if (type == 1 && stream == 1) done = flags & 0x1;                              // trailers end the stream
+  }
+  ::close(fd);
+  return ok && done && got_data;
 }
 
 // Blocking POST with a timeout on every socket operation.  Returns the HTTP status, or 0 when the peer could not be reached.
@@ -102,6 +229,7 @@ class BackgroundPoster {
   }
   ~BackgroundPoster() { stop(); }
   bool enabled() const { return url_.ok; }
+  bool grpc() const { return url_.grpc; }
   void post(std::string body) {
     if (!url_.ok) return;
     std::lock_guard<std::mutex> g(mu_);
@@ -129,8 +257,12 @@ class BackgroundPoster {
       }
       bool ok = false;
       for (int a = 0; a < attempts_ && !ok; ++a) {
-        int st = http_post(url_, path_, body, "application/json");
-        ok = st >= 200 && st < 300;
+        if (url_.grpc) {
+          ok = grpc_unary(url_, "/opentelemetry.proto.collector.trace.v1.TraceService/Export", body);
+        } else {
+          int st = http_post(url_, path_, body, "application/json");
+          ok = st >= 200 && st < 300;
+        }
         if (!ok && a + 1 < attempts_) std::this_thread::sleep_for(std::chrono::milliseconds(100 << a));
       }
       if (ok) ++sent_; else ++dropped_;
@@ -235,6 +367,59 @@ inline json::Value otlp_span(const Span& s) {
   return o;
 }
 
+// The same span as an opentelemetry.proto.trace.v1.Span message.
+inline Pb otlp_any_pb(const json::Value& v) {
+  Pb a;                                                    // AnyValue: string 1, bool 2, int 3, double 4
+  if (v.is_string()) a.bytes(1, v.as_string());
+  else if (v.is_bool()) a.u64(2, v.as_bool() ? 1 : 0);
+  else if (v.is_number() && v.as_double() == (double)(long long)v.as_double()) a.u64(3, (uint64_t)(long long)v.as_double());
+  else if (v.is_number()) a.f64(4, v.as_double());
+  else a.bytes(1, v.dump());
+  return a;
+}
+inline Pb otlp_kv_pb(const std::string& k, const json::Value& v) {
+  Pb kv;
+  kv.bytes(1, k);
+  kv.msg(2, otlp_any_pb(v));
+  return kv;
+}
+inline Pb otlp_span_pb(const Span& s) {
+  Pb o;
+  o.bytes(1, unhex(s.ctx.trace_id));
+  o.bytes(2, unhex(s.ctx.span_id));
+  if (!s.parent_span_id.empty()) o.bytes(4, unhex(s.parent_span_id));
+  o.bytes(5, s.name);
+  o.u64(6, (uint64_t)s.kind);
+  o.fixed64(7, s.start_ns);
+  o.fixed64(8, s.end_ns);
+  for (auto& kv : s.attrs) o.msg(9, otlp_kv_pb(kv.first, kv.second));
+  for (auto& l : s.links) {
+    Pb x;
+    x.bytes(1, unhex(l.trace_id));
+    x.bytes(2, unhex(l.span_id));
+    o.msg(13, x);
+  }
+  if (s.error) {
+    Pb st;
+    st.bytes(2, s.error_message);
+    st.u64(3, 2);
+    o.msg(15, st);
+  }
+  return o;
+}
+// ExportTraceServiceRequest { resource_spans { resource { attributes }, scope_spans { scope { name }, spans } } }
+inline std::string otlp_request_pb(const std::string& service, const std::vector<Span>& batch, size_t begin, size_t end) {
+  Pb scope_spans, scope, resource, rs, root;
+  scope.bytes(1, "lorax_b200");
+  scope_spans.msg(1, scope);
+  for (size_t i = begin; i < end; ++i) scope_spans.msg(2, otlp_span_pb(batch[i]));
+  resource.msg(1, otlp_kv_pb("service.name", json::Value(service)));
+  rs.msg(1, resource);
+  rs.msg(2, scope_spans);
+  root.msg(1, rs);
+  return root.b;
+}
+
 // Collects finished spans and ships them in batches (every `flush_ms` or 64 spans).
 class Tracer {
  public:
@@ -283,6 +468,11 @@ class Tracer {
     std::vector<Span> batch;
     batch.swap(done_);
     g.unlock();
+    if (poster_.grpc()) {                                  // OTLP/gRPC: protobuf, at most 32 spans per call
+      for (size_t i = 0; i < batch.size(); i += 32) poster_.post(otlp_request_pb(service_, batch, i, std::min(batch.size(), i + 32)));
+      g.lock();
+      return;
+    }
     json::Value spans = json::Value::array();
     for (auto& s : batch) spans.push(otlp_span(s));
     json::Value scope = json::Value::object();

@@ -1,4 +1,5 @@
-"""Request tracing on the shard: one span per RPC, child of the router's batch span, exported as OTLP/HTTP JSON.
+"""Request tracing on the shard: one span per RPC, child of the router's batch span, exported as OTLP/HTTP JSON or, for a
+`grpc://host:port` endpoint (or any endpoint on port 4317), as OTLP/gRPC protobuf through `TraceService/Export`.
 
 The router puts its batch span's W3C `traceparent` in front of the framed message (`csrc/host/shard_client.hpp`); the shard
 wraps the RPC in a span of service `lorax.server-{rank}` and posts finished spans to `{endpoint}/v1/traces` from a
@@ -49,16 +50,94 @@ def _any(v):
     return {"stringValue": str(v)}
 
 
+# ---- protobuf wire format for opentelemetry.proto.collector.trace.v1.ExportTraceServiceRequest (field numbers of trace.proto)
+def _varint(v: int) -> bytes:
+    out = bytearray()
+    while v >= 0x80:
+        out.append((v & 0x7F) | 0x80)
+        v >>= 7
+    out.append(v)
+    return bytes(out)
+
+
+def _ld(field: int, payload: bytes) -> bytes:
+    return _varint((field << 3) | 2) + _varint(len(payload)) + payload
+
+
+def _vi(field: int, v: int) -> bytes:
+    return _varint(field << 3) + _varint(v & 0xFFFFFFFFFFFFFFFF)
+
+
+def _f64(field: int, v: int) -> bytes:
+    return _varint((field << 3) | 1) + int(v).to_bytes(8, "little")
+
+
+def _any_pb(v: dict) -> bytes:
+    if "boolValue" in v:
+        return _vi(2, int(v["boolValue"]))
+    if "intValue" in v:
+        return _vi(3, int(v["intValue"]))
+    if "doubleValue" in v:
+        import struct
+        return _varint((4 << 3) | 1) + struct.pack("<d", v["doubleValue"])
+    return _ld(1, str(v.get("stringValue", "")).encode())
+
+
+def _kv_pb(key: str, value: dict) -> bytes:
+    return _ld(1, key.encode()) + _ld(2, _any_pb(value))
+
+
+def span_to_pb(span: dict) -> bytes:
+    """One span in the JSON form used above -> an opentelemetry.proto.trace.v1.Span message."""
+    out = _ld(1, bytes.fromhex(span["traceId"])) + _ld(2, bytes.fromhex(span["spanId"]))
+    if span.get("parentSpanId"):
+        out += _ld(4, bytes.fromhex(span["parentSpanId"]))
+    out += _ld(5, span["name"].encode()) + _vi(6, int(span.get("kind", 1)))
+    out += _f64(7, int(span["startTimeUnixNano"])) + _f64(8, int(span["endTimeUnixNano"]))
+    for a in span.get("attributes", []):
+        out += _ld(9, _kv_pb(a["key"], a["value"]))
+    st = span.get("status") or {}
+    if st.get("code"):
+        out += _ld(15, _ld(2, str(st.get("message", "")).encode()) + _vi(3, int(st["code"])))
+    return out
+
+
+def export_request_pb(service: str, spans: List[dict]) -> bytes:
+    scope_spans = _ld(1, _ld(1, b"lorax_b200")) + b"".join(_ld(2, span_to_pb(s)) for s in spans)
+    resource = _ld(1, _kv_pb("service.name", {"stringValue": service}))
+    return _ld(1, _ld(1, resource) + _ld(2, scope_spans))
+
+
+def _grpc_target(endpoint: Optional[str]) -> Optional[str]:
+    """host:port when the endpoint names an OTLP/gRPC collector, else None."""
+    if not endpoint:
+        return None
+    for pre in ("grpc://", "http://"):
+        if endpoint.startswith(pre):
+            hp = endpoint[len(pre):].split("/", 1)[0]
+            if pre == "grpc://":
+                return hp if ":" in hp else hp + ":4317"
+            return hp if hp.endswith(":4317") else None
+    return None
+
+
 class Tracer:
     def __init__(self, endpoint: Optional[str], service: str, flush_s: float = 0.5):
         self.service = service
-        self.enabled = bool(endpoint) and endpoint.startswith("http://")
+        self.grpc_target = _grpc_target(endpoint)
+        self.enabled = bool(endpoint) and (endpoint.startswith("http://") or self.grpc_target is not None)
         self.url = None
+        self._export = None
         self.sent_batches = 0
         self.dropped = 0
         if self.enabled:
             base = endpoint.rstrip("/")
             self.url = base if base.endswith("/v1/traces") else base + "/v1/traces"
+            if self.grpc_target is not None:
+                import grpc
+                self._channel = grpc.insecure_channel(self.grpc_target)
+                self._export = self._channel.unary_unary("/opentelemetry.proto.collector.trace.v1.TraceService/Export",
+                                                         request_serializer=None, response_deserializer=None)
             self._q: "queue.Queue[dict]" = queue.Queue(maxsize=8192)
             self._stop = threading.Event()
             self._flush_s = flush_s
@@ -94,6 +173,16 @@ class Tracer:
                 self.dropped += 1
 
     def _post(self, spans: List[dict]):
+        if self._export is not None:
+            for attempt in range(3):
+                try:
+                    self._export(export_request_pb(self.service, spans), timeout=2)
+                    self.sent_batches += 1
+                    return
+                except Exception:
+                    time.sleep(0.1 * (1 << attempt))
+            self.dropped += len(spans)
+            return
         body = json.dumps({"resourceSpans": [{"resource": {"attributes": [{"key": "service.name", "value": {"stringValue": self.service}}]},
                                               "scopeSpans": [{"scope": {"name": "lorax_b200"}, "spans": spans}]}]}).encode()
         req = urllib.request.Request(self.url, data=body, headers={"Content-Type": "application/json"}, method="POST")

@@ -363,3 +363,156 @@ def test_merge_adapter_weights_equals_the_adapter_applied_at_run_time(stack):
     want = gen(rt, 77)
     assert gen(merged, 0) == want and gen(rt, 0) != want
     rt.offload_adapter(pb.OffloadAdapterRequest(adapter_parameters=params, adapter_source=2, adapter_index=77))
+
+
+def _pb_fields(buf: bytes):
+    """Protobuf wire format -> list of (field, wire type, value); enough to read an OTLP export request."""
+    out, i = [], 0
+    while i < len(buf):
+        key = shift = 0
+        while True:
+            b = buf[i]; i += 1
+            key |= (b & 0x7F) << shift; shift += 7
+            if b < 0x80:
+                break
+        field, wire = key >> 3, key & 7
+        if wire == 0:
+            v = shift = 0
+            while True:
+                b = buf[i]; i += 1
+                v |= (b & 0x7F) << shift; shift += 7
+                if b < 0x80:
+                    break
+        elif wire == 1:
+            v = int.from_bytes(buf[i:i + 8], "little"); i += 8
+        elif wire == 2:
+            n = shift = 0
+            while True:
+                b = buf[i]; i += 1
+                n |= (b & 0x7F) << shift; shift += 7
+                if b < 0x80:
+                    break
+            v = buf[i:i + n]; i += n
+        else:
+            raise ValueError(f"wire type {wire}")
+        out.append((field, wire, v))
+    return out
+
+
+def test_tracing_over_otlp_grpc(stack):
+    """A router whose `--otlp-endpoint` is a gRPC collector (`grpc://host:port`, or any URL on port 4317): spans arrive as
+    protobuf `ExportTraceServiceRequest`s through `TraceService/Export`, which is the transport the reference's exporter speaks
+    (router/src/main.rs:492-541).  The collector here is a grpcio server that keeps the raw request bytes."""
+    import grpc
+    from concurrent import futures
+    got = []
+
+    class Collector(grpc.GenericRpcHandler):
+        def service(self, details):
+            if details.method != "/opentelemetry.proto.collector.trace.v1.TraceService/Export":
+                return None
+            return grpc.unary_unary_rpc_method_handler(lambda req, ctx: (got.append(req), b"")[1],
+                                                       request_deserializer=None, response_serializer=None)
+    server = grpc.server(futures.ThreadPoolExecutor(2))
+    server.add_generic_rpc_handlers((Collector(),))
+    cport = server.add_insecure_port("127.0.0.1:0")
+    server.start()
+    port = _free_port()
+    proc = subprocess.Popen([ROUTER, "--port", str(port), "--hostname", "127.0.0.1", "--master-shard-uds-path", stack["uds"], "--num-shard", "1",
+                             "--max-input-length", "64", "--max-total-tokens", "128", "--model-id", "tiny", "--adapter-source", "local",
+                             "--otlp-endpoint", f"grpc://127.0.0.1:{cport}"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    try:
+        for _ in range(100):
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1) as r:
+                    if r.status == 200:
+                        break
+            except Exception:
+                time.sleep(0.1)
+        trace_id, parent = "0af7651916cd43dd8448eb211c80319c", "b7ad6b7169203331"
+        status, _, _ = _post(port, "/generate", {"inputs": "w5 w6 w7", "parameters": {"max_new_tokens": 3}},
+                             headers={"traceparent": f"00-{trace_id}-{parent}-01"})
+        assert status == 200
+
+        def spans():
+            out = []
+            for req in list(got):
+                for f, _, rs in _pb_fields(req):
+                    assert f == 1
+                    rsf = _pb_fields(rs)
+                    resource = next(v for k, _, v in rsf if k == 1)
+                    kv = _pb_fields(next(v for k, _, v in _pb_fields(resource) if k == 1))
+                    assert kv[0][2] == b"service.name" and _pb_fields(kv[1][2])[0][2] == b"lorax.router"
+                    for k, _, ss in rsf:
+                        if k == 2:
+                            out += [dict((ff, vv) for ff, _, vv in _pb_fields(v) if ff != 9) | {"attrs": [vv for ff, _, vv in _pb_fields(v) if ff == 9]}
+                                    for kk, _, v in _pb_fields(ss) if kk == 2]
+            return out
+        mine = None
+        for _ in range(100):
+            mine = next((s for s in spans() if s[1] == bytes.fromhex(trace_id)), None)
+            if mine is not None:
+                break
+            time.sleep(0.1)
+        assert mine is not None, "no span of the request reached the collector"
+        assert mine[5] == b"generate" and mine[4] == bytes.fromhex(parent) and mine[6] == 2 and len(mine[2]) == 8
+        assert mine[8] > mine[7] > 1_600_000_000 * 10 ** 9          # fixed64 start / end in unix nanoseconds
+        attrs = {}
+        for a in mine["attrs"]:
+            f = _pb_fields(a)
+            attrs[f[0][2].decode()] = _pb_fields(f[1][2])[0]
+        assert attrs["generated_tokens"][0] == 3 and attrs["generated_tokens"][2] == 3       # AnyValue.int_value
+        assert any(s[5] in (b"prefill", b"decode") for s in spans())
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=10)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+        server.stop(0)
+
+
+def test_shard_tracer_exports_over_otlp_grpc():
+    """The shard's tracer against the same kind of collector: a span with a parent, attributes of every type and an error
+    status, read back from the protobuf request."""
+    import grpc
+    from concurrent import futures
+    from lorax_b200.server.tracing import Tracer
+    got = []
+
+    class Collector(grpc.GenericRpcHandler):
+        def service(self, details):
+            return grpc.unary_unary_rpc_method_handler(lambda req, ctx: (got.append((details.method, req)), b"")[1])
+    server = grpc.server(futures.ThreadPoolExecutor(2))
+    server.add_generic_rpc_handlers((Collector(),))
+    cport = server.add_insecure_port("127.0.0.1:0")
+    server.start()
+    try:
+        tr = Tracer(f"grpc://127.0.0.1:{cport}", "lorax.server-0", flush_s=0.05)
+        assert tr.enabled and tr.grpc_target == f"127.0.0.1:{cport}"
+        tp = "00-0af7651916cd43dd8448eb211c80319c-b7ad6b7169203331-01"
+        with pytest.raises(RuntimeError):
+            with tr.span("Prefill", tp, {"batch": 3, "ratio": 0.5, "ok": True, "who": "x"}):
+                raise RuntimeError("boom")
+        for _ in range(100):
+            if got:
+                break
+            time.sleep(0.05)
+        tr.shutdown()
+        assert got and got[0][0] == "/opentelemetry.proto.collector.trace.v1.TraceService/Export" and tr.sent_batches >= 1
+        rs = _pb_fields(_pb_fields(got[0][1])[0][2])
+        span = _pb_fields(next(v for k, _, v in _pb_fields(next(v for k, _, v in rs if k == 2)) if k == 2))
+        d = {k: v for k, _, v in span if k != 9}
+        assert d[1] == bytes.fromhex("0af7651916cd43dd8448eb211c80319c") and d[4] == bytes.fromhex("b7ad6b7169203331") and d[5] == b"Prefill"
+        assert d[8] >= d[7] and dict((k, v) for k, _, v in _pb_fields(d[15]))[3] == 2
+        attrs = {}
+        for k, _, v in span:
+            if k == 9:
+                f = _pb_fields(v)
+                attrs[f[0][2]] = _pb_fields(f[1][2])[0]
+        import struct
+        assert attrs[b"batch"][::2] == (3, 3) and attrs[b"ok"][::2] == (2, 1) and attrs[b"who"][::2] == (1, b"x")
+        assert attrs[b"ratio"][0] == 4 and struct.unpack("<d", attrs[b"ratio"][2].to_bytes(8, "little"))[0] == 0.5
+        assert Tracer("http://collector:4317", "s").grpc_target == "collector:4317" and Tracer("http://c:4318", "s").grpc_target is None
+    finally:
+        server.stop(0)
