@@ -157,7 +157,7 @@ class ModelConfig:
             if new_arch:
                 kw["num_key_value_heads"] = d.get("num_kv_heads") or d.get("n_head_kv") or nh
             else:
-                kw["num_key_value_heads"] = 1 if d.get("multi_query", mt != "falcon") else nh
+                kw["num_key_value_heads"] = 1 if d.get("multi_query", True) else nh
             if d.get("alibi", False):
                 raise NotImplementedError("falcon with ALiBi (falcon-rw): its bias is scaled with the scores, unlike bloom's")
             kw["rms_norm_eps"] = d.get("layer_norm_epsilon", 1e-5)
