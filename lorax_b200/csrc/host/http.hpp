@@ -115,6 +115,13 @@ class Server {
  public:
   void route(const std::string& method, const std::string& path, Handler h) { routes_[method + " " + path] = std::move(h); }
   void set_cors(const std::vector<std::string>& origins) { cors_ = origins; }
+  // Values of the other CORS response headers (comma separated lists as given on the command line; empty: the defaults).
+  void set_cors_options(std::string methods, std::string headers, std::string expose, bool credentials) {
+    cors_methods_ = methods.empty() ? "GET, POST, OPTIONS" : std::move(methods);
+    cors_headers_ = headers.empty() ? "*" : std::move(headers);
+    cors_expose_ = std::move(expose);
+    cors_credentials_ = credentials;
+  }
   size_t max_body = 256u << 20;
 
   // Returns the bound port (0 on failure).  Serves until stop().
@@ -216,7 +223,7 @@ class Server {
       buf.erase(0, hdr_end + 4 + body_len);
 
       if (req.method == "OPTIONS") {
-        w.send(204, "", "text/plain", {{"Access-Control-Allow-Methods", "GET, POST, OPTIONS"}, {"Access-Control-Allow-Headers", "*"}});
+        w.send(204, "", "text/plain", {{"Access-Control-Allow-Methods", cors_methods_}, {"Access-Control-Allow-Headers", cors_headers_}});
       } else {
         auto it = routes_.find(req.method + " " + req.path);
         if (it == routes_.end()) {
@@ -239,11 +246,19 @@ class Server {
     if (cors_.empty()) return;
     std::string origin = req.header("origin");
     for (auto& o : cors_) {
-      if (o == "*" || o == origin) { w.add_common("Access-Control-Allow-Origin", o == "*" ? "*" : origin); break; }
+      if (o == "*" || o == origin) {
+        // a wildcard origin may not be combined with credentials: echo the caller's origin then
+        w.add_common("Access-Control-Allow-Origin", o == "*" && !(cors_credentials_ && !origin.empty()) ? "*" : origin);
+        if (cors_credentials_) w.add_common("Access-Control-Allow-Credentials", "true");
+        if (!cors_expose_.empty()) w.add_common("Access-Control-Expose-Headers", cors_expose_);
+        break;
+      }
     }
   }
   std::map<std::string, Handler> routes_;
   std::vector<std::string> cors_;
+  std::string cors_methods_ = "GET, POST, OPTIONS", cors_headers_ = "*", cors_expose_;
+  bool cors_credentials_ = false;
   int listen_fd_ = -1, bound_port_ = 0;
   std::atomic<bool> running_{false};
   std::atomic<int> active_{0};

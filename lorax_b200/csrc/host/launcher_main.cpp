@@ -76,6 +76,37 @@ const Flag kFlags[] = {
     {"otlp-endpoint", "OTLP_ENDPOINT", "", ""},
     {"cors-allow-origin", "CORS_ALLOW_ORIGIN", "", ""},
     {"json-output", "JSON_OUTPUT", "false", ""},
+    {"sharded", "SHARDED", "", "false: one shard whatever devices are visible; true: one shard per visible device"},
+    {"eager", "EAGER", "false", "no CUDA graphs (same as --compile false)"},
+    {"compile-max-batch-size", "COMPILE_MAX_BATCH_SIZE", "", "largest decode batch captured in a CUDA graph"},
+    {"compile-max-rank", "COMPILE_MAX_RANK", "", "largest LoRA rank captured in a CUDA graph"},
+    {"compile-batch-size", "COMPILE_BATCH_SIZE", "", "step between captured batch sizes"},
+    {"speculation-max-batch-size", "SPECULATION_MAX_BATCH_SIZE", "", "no speculation above this many decode rows"},
+    {"memory-wiggle-room", "MEMORY_WIGGLE_ROOM", "", "fraction of the free HBM the KV cache may take after warm-up"},
+    {"watermark-gamma", "WATERMARK_GAMMA", "", ""},
+    {"watermark-delta", "WATERMARK_DELTA", "", ""},
+    {"huggingface-hub-cache", "HUGGINGFACE_HUB_CACHE", "", "where hub downloads are kept"},
+    {"weights-cache-override", "WEIGHTS_CACHE_OVERRIDE", "", "read weights from this directory instead of the hub cache"},
+    {"predibase-api-token", "PREDIBASE_API_TOKEN", "", "token for adapters of source pbase"},
+    {"preloaded-adapter-source", "PRELOADED_ADAPTER_SOURCE", "", "source of --preloaded-adapter-ids (default: --adapter-source)"},
+    {"default-adapter-source", "DEFAULT_ADAPTER_SOURCE", "", "source the router assumes for requests that name none"},
+    {"download-only", "DOWNLOAD_ONLY", "false", "fetch the weights and exit"},
+    {"validation-workers", "VALIDATION_WORKERS", "2", "tokenisation workers of the router"},
+    {"tokenizer-config-path", "TOKENIZER_CONFIG_PATH", "", "tokenizer_config.json to take the chat template from"},
+    {"cors-allow-method", "CORS_ALLOW_METHOD", "", ""},
+    {"cors-allow-header", "CORS_ALLOW_HEADER", "", ""},
+    {"cors-expose-header", "CORS_EXPOSE_HEADER", "", ""},
+    {"cors-allow-credentials", "CORS_ALLOW_CREDENTIALS", "", ""},
+    // accepted so that command lines written for the reference launcher keep working; they select between code paths that do not
+    // exist here (one attention backend, one LoRA kernel family, no remote code, no tunnel)
+    {"backend", "BACKEND", "", "accepted, no effect: there is one attention backend"},
+    {"disable-custom-kernels", "DISABLE_CUSTOM_KERNELS", "false", "accepted, no effect: the CUDA kernels are the only path"},
+    {"disable-sgmv", "DISABLE_SGMV", "false", "accepted, no effect: one segmented LoRA kernel family serves prefill and decode"},
+    {"trust-remote-code", "TRUST_REMOTE_CODE", "false", "accepted, no effect: no code from a model repository is ever run"},
+    {"embedding-dim", "EMBEDDING_DIM", "", "accepted, no effect: encoders report their own width"},
+    {"ngrok", "NGROK", "false", "refused: no tunnel client is built in"},
+    {"ngrok-authtoken", "NGROK_AUTHTOKEN", "", ""},
+    {"ngrok-edge", "NGROK_EDGE", "", ""},
     {"python", "LORAX_PYTHON", "python", "interpreter that runs the shards"},
     {"router-bin", "LORAX_ROUTER_BIN", "", "path of lorax-router (default: next to this binary)"},
 };
@@ -124,8 +155,23 @@ void emit(const std::string& level, const std::string& target, const std::string
   }
 }
 
+// Flags that reach the shards (and the download step) as environment variables, under the names the shard reads.
+std::vector<std::string> shard_env(const Config& c) {
+  static const std::pair<const char*, const char*> kMap[] = {
+      {"compile-max-batch-size", "LORAX_COMPILE_MAX_BATCH_SIZE"}, {"compile-max-rank", "LORAX_COMPILE_MAX_RANK"},
+      {"compile-batch-size", "LORAX_COMPILE_BATCH_SIZE"}, {"speculation-max-batch-size", "LORAX_SPECULATION_MAX_BATCH_SIZE"},
+      {"memory-wiggle-room", "MEMORY_WIGGLE_ROOM"}, {"watermark-gamma", "WATERMARK_GAMMA"}, {"watermark-delta", "WATERMARK_DELTA"},
+      {"huggingface-hub-cache", "HUGGINGFACE_HUB_CACHE"}, {"weights-cache-override", "WEIGHTS_CACHE_OVERRIDE"},
+      {"predibase-api-token", "PREDIBASE_API_TOKEN"}, {"tokenizer-config-path", "TOKENIZER_CONFIG_PATH"}};
+  std::vector<std::string> env;
+  for (auto& m : kMap)
+    if (!c.get(m.first).empty()) env.push_back(std::string(m.second) + "=" + c.get(m.first));
+  return env;
+}
+
 // Shard count: explicit flag, else the visible-devices list, else 1.
 int find_num_shards(const Config& c) {
+  if (c.get("sharded") == "false") return 1;
   if (!c.get("num-shard").empty()) return std::max(1, atoi(c.get("num-shard").c_str()));
   for (const char* name : {"CUDA_VISIBLE_DEVICES", "NVIDIA_VISIBLE_DEVICES"}) {
     const char* e = getenv(name);
@@ -289,7 +335,17 @@ int main(int argc, char** argv) {
     emit("ERROR", "lorax_launcher", "`max_input_length` must be < `max_total_tokens`");
     return 2;
   }
+  if (c.truthy("ngrok")) { emit("ERROR", "lorax_launcher", "--ngrok: no tunnel client is built into this launcher"); return 2; }
+  if (atol(c.get("validation-workers").c_str()) <= 0) { emit("ERROR", "lorax_launcher", "`validation_workers` must be > 0"); return 2; }
+  for (const char* opt : {"backend", "embedding-dim"})
+    if (!c.get(opt).empty()) emit("WARN", "lorax_launcher", std::string("--") + opt + " is accepted for compatibility and has no effect");
+  for (const char* opt : {"disable-custom-kernels", "disable-sgmv", "trust-remote-code"})
+    if (c.truthy(opt)) emit("WARN", "lorax_launcher", std::string("--") + opt + " is accepted for compatibility and has no effect");
   const int num_shard = find_num_shards(c);
+  if (c.get("sharded") == "true" && num_shard <= 1) {
+    emit("ERROR", "lorax_launcher", "`sharded` is true but only one device is visible (or `num_shard` is 1)");
+    return 2;
+  }
   emit("INFO", "lorax_launcher", "starting " + std::to_string(num_shard) + " shard(s) for " + c.get("model-id"));
 
   // ---- weights: one download / conversion step before any shard starts (the reference runs `lorax-server download-weights`
@@ -301,7 +357,7 @@ int main(int argc, char** argv) {
                                       "--source", c.get("source"), "--json-output"};
     if (!c.get("revision").empty()) { dargs.push_back("--revision"); dargs.push_back(c.get("revision")); }
     emit("INFO", "lorax_launcher", "Starting download process.");
-    Child dl = spawn("download", dargs, {});
+    Child dl = spawn("download", dargs, shard_env(c));
     if (dl.pid <= 0) return 1;
     int st = 0;
     while (!exited(dl, &st)) {
@@ -316,6 +372,10 @@ int main(int argc, char** argv) {
     }
     emit("INFO", "lorax_launcher", "Successfully downloaded weights.");
   }
+  if (c.truthy("download-only")) {
+    emit("INFO", "lorax_launcher", "weights are in place; --download-only: not starting shards");
+    return 0;
+  }
 
   // ---- shards
   const std::string uds = c.get("shard-uds-path");
@@ -329,9 +389,10 @@ int main(int argc, char** argv) {
                                      "--max-batch-prefill-tokens", c.get("max-batch-prefill-tokens"),
                                      "--adapter-memory-fraction", c.get("adapter-memory-fraction"), "--json-output"};
     if (num_shard > 1) args.push_back("--sharded");
-    for (const char* opt : {"revision", "quantize", "dtype", "adapter-id", "speculative-tokens", "preloaded-adapter-ids", "otlp-endpoint"})
+    for (const char* opt : {"revision", "quantize", "dtype", "adapter-id", "speculative-tokens", "preloaded-adapter-ids", "otlp-endpoint",
+                            "preloaded-adapter-source"})
       if (!c.get(opt).empty()) { args.push_back(std::string("--") + opt); args.push_back(c.get(opt)); }
-    if (!c.truthy("compile")) args.push_back("--no-compile");
+    if (!c.truthy("compile") || c.truthy("eager")) args.push_back("--no-compile");
     if (c.truthy("prefix-caching")) args.push_back("--prefix-caching");
     if (c.truthy("merge-adapter-weights")) args.push_back("--merge-adapter-weights");
     if (c.truthy("chunked-prefill")) args.push_back("--chunked-prefill");
@@ -339,6 +400,7 @@ int main(int argc, char** argv) {
                                     "MASTER_ADDR=" + c.get("master-addr"), "MASTER_PORT=" + c.get("master-port"),
                                     "NCCL_ASYNC_ERROR_HANDLING=1", "CUDA_MEMORY_FRACTION=" + c.get("cuda-memory-fraction"),
                                     "ADAPTER_MEMORY_FRACTION=" + c.get("adapter-memory-fraction")};
+    for (auto& kv : shard_env(c)) env.push_back(kv);
     shards[(size_t)r] = spawn("shard-" + std::to_string(r), args, env);
     if (shards[(size_t)r].pid <= 0) return 1;
   }
@@ -378,8 +440,13 @@ int main(int argc, char** argv) {
   for (const char* opt : {"max-concurrent-requests", "max-best-of", "max-stop-sequences", "max-input-length", "max-total-tokens",
                           "max-batch-prefill-tokens", "max-batch-total-tokens", "waiting-served-ratio", "max-waiting-tokens",
                           "max-active-adapters", "adapter-cycle-time-s", "eager-prefill", "prefix-caching", "chunked-prefill", "hostname",
-                          "port", "adapter-source", "cors-allow-origin", "otlp-endpoint"})
+                          "port", "adapter-source", "cors-allow-origin", "otlp-endpoint", "validation-workers", "cors-allow-method",
+                          "cors-allow-header", "cors-expose-header", "cors-allow-credentials"})
     if (!c.get(opt).empty()) { rargs.push_back(std::string("--") + opt); rargs.push_back(c.get(opt)); }
+  if (!c.get("default-adapter-source").empty()) {          // overrides --adapter-source for the router, as in the reference
+    rargs.push_back("--adapter-source");
+    rargs.push_back(c.get("default-adapter-source"));
+  }
   Child router = spawn("router", rargs, {});
   if (router.pid <= 0) { terminate_all(all, 10); return 1; }
   all.push_back(&router);

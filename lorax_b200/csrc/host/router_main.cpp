@@ -20,6 +20,10 @@ using json::Value;
 
 namespace {
 
+// Reported by /info.  Tokenisation is delegated to shard 0 over its socket, one request at a time per handler thread, so the
+// flag sizes nothing here; it is carried for clients that read it back.
+int g_validation_workers = 2;
+
 std::atomic<bool> g_stop{false};
 void on_signal(int) { g_stop = true; }
 
@@ -734,7 +738,7 @@ class App {
     v.set("max_waiting_tokens", cfg_.max_waiting_tokens);
     v.set("block_size", info_.block_size);
     v.set("window_size", info_.window_size ? Value(*info_.window_size) : Value());
-    v.set("validation_workers", 1);
+    v.set("validation_workers", g_validation_workers);
     v.set("version", "0.1.0");
     v.set("docker_label", Value());
     v.set("request_logger_url", Value());
@@ -821,6 +825,7 @@ int main(int argc, char** argv) {
   }
   log_json("INFO", "connected to " + std::to_string(num_shard) + " shard(s); max_batch_total_tokens=" + std::to_string(cfg.max_batch_total_tokens));
 
+  g_validation_workers = (int)a.geti("validation-workers", 2);
   const std::string otlp = a.get("otlp-endpoint", "");
   const char* logger_env = std::getenv("REQUEST_LOGGER_URL");
   App app(client, cfg, info, num_blocks, otlp, logger_env ? logger_env : "");
@@ -831,6 +836,8 @@ int main(int argc, char** argv) {
   std::string cors_arg = a.get("cors-allow-origin", "");
   if (!cors_arg.empty()) cors.push_back(cors_arg);
   server.set_cors(cors);
+  server.set_cors_options(a.get("cors-allow-method", ""), a.get("cors-allow-header", ""), a.get("cors-expose-header", ""),
+                          a.getb("cors-allow-credentials", false));
   auto R = [&](const char* m, const char* p, http::Handler h) { server.route(m, p, std::move(h)); };
   R("POST", "/", [&](auto& q, auto& w) { app.generate(q, w); });
   R("POST", "/generate", [&](auto& q, auto& w) { app.generate(q, w); });

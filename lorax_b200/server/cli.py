@@ -43,9 +43,9 @@ def serve(args):
     if merge:
         args.adapter_id = ""                                # it is part of the base weights now
     if args.preloaded_adapter_ids:
-        rt.preload_adapters([a.strip() for a in args.preloaded_adapter_ids.split(",")], {"hub": 0, "s3": 1, "local": 2, "pbase": 3}[args.adapter_source])
+        rt.preload_adapters([a.strip() for a in args.preloaded_adapter_ids.split(",")], {"hub": 0, "s3": 1, "local": 2, "pbase": 3}[args.preloaded_adapter_source or args.adapter_source])
     if args.adapter_id:
-        rt.load_default_adapter(args.adapter_id, {"hub": 0, "s3": 1, "local": 2, "pbase": 3}[args.adapter_source])
+        rt.load_default_adapter(args.adapter_id, {"hub": 0, "s3": 1, "local": 2, "pbase": 3}[args.preloaded_adapter_source or args.adapter_source])
     from .tracing import PrefillProfiler, Tracer
     rt.tracer = Tracer(args.otlp_endpoint or os.environ.get("OTLP_ENDPOINT"), f"lorax.server-{tp.rank}")
     rt.profiler = PrefillProfiler(cfg.profiler_dir)
@@ -106,6 +106,7 @@ def main(argv=None):
     s.add_argument("--adapter-memory-fraction", type=float, default=0.1)
     s.add_argument("--speculative-tokens", type=int, default=0)
     s.add_argument("--preloaded-adapter-ids", default="")
+    s.add_argument("--preloaded-adapter-source", default=None, help="source of --preloaded-adapter-ids (default: --adapter-source)")
     s.add_argument("--otlp-endpoint", default=None)
     s.add_argument("--merge-adapter-weights", action="store_true", help="fold --adapter-id into the base weights at load time")
     s.add_argument("--no-compile", action="store_true")

@@ -193,3 +193,73 @@ def test_launcher_two_gpu_shards(tmp_path):
             raise
     out = proc.stdout.read().decode()
     assert "shard 1 ready" in out and proc.returncode == 0, out[-2000:]
+
+
+def test_launcher_accepts_the_reference_flag_set(tmp_path):
+    """Flags of the reference launcher beyond the core set (launcher/src/main.rs:273-655): the ones that configure something
+    reach the shard or the router (CORS headers, validation workers, eager mode, shard count), the ones that choose between code
+    paths that do not exist here are accepted with a warning, `--download-only` stops after the download, and invalid
+    combinations are refused before anything is spawned."""
+    from lorax_b200.csrc import build
+    build.build_host()
+    mdir = _model_dir(tmp_path)
+    base = [LAUNCHER, "--model-id", str(mdir), "--source", "local", "--python", sys.executable, "--json-output",
+            "--shard-uds-path", str(tmp_path / "uds"), "--hostname", "127.0.0.1"]
+    env = dict(os.environ, PYTHONPATH=REPO, CUDA_VISIBLE_DEVICES="", LORAX_COMPILE="0")
+    r = subprocess.run(base + ["--ngrok"], capture_output=True, env=env, timeout=60)
+    assert r.returncode == 2 and b"ngrok" in r.stdout
+    r = subprocess.run(base + ["--sharded", "true"], capture_output=True, env=env, timeout=60)
+    assert r.returncode == 2 and b"sharded" in r.stdout
+    r = subprocess.run(base + ["--validation-workers", "0"], capture_output=True, env=env, timeout=60)
+    assert r.returncode == 2 and b"validation_workers" in r.stdout
+    r = subprocess.run(base + ["--download-only"], capture_output=True, env=env, timeout=300)
+    assert r.returncode == 0 and b"--download-only: not starting shards" in r.stdout and b"shard 0 ready" not in r.stdout
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    proc = subprocess.Popen(base + ["--port", str(port), "--max-input-length", "64", "--max-total-tokens", "128", "--sharded", "false", "--eager",
+                                    "--validation-workers", "3", "--cors-allow-origin", "*", "--cors-allow-credentials", "true",
+                                    "--cors-expose-header", "x-compute-time", "--cors-allow-method", "GET, POST", "--compile-max-batch-size", "8",
+                                    "--compile-max-rank", "16", "--disable-sgmv", "--trust-remote-code", "--backend", "flashinfer",
+                                    "--default-adapter-source", "local", "--memory-wiggle-room", "0.9", "--skip-download"],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT, env=env)
+    try:
+        ok = False
+        for _ in range(600):
+            if proc.poll() is not None:
+                break
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1) as resp:
+                    ok = resp.status == 200
+                    break
+            except Exception:
+                time.sleep(0.2)
+        if not ok:
+            proc.kill()
+            raise AssertionError("deployment did not come up:\n" + proc.stdout.read().decode()[-9000:])
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/info", headers={"Origin": "http://app.example"})
+        with urllib.request.urlopen(req, timeout=30) as resp:
+            info = json.loads(resp.read())
+            hdr = {k.lower(): v for k, v in resp.headers.items()}
+        assert info["validation_workers"] == 3
+        assert hdr["access-control-allow-origin"] == "http://app.example" and hdr["access-control-allow-credentials"] == "true"
+        assert hdr["access-control-expose-headers"] == "x-compute-time"
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/generate", method="OPTIONS", headers={"Origin": "http://app.example"})
+        with urllib.request.urlopen(req, timeout=30) as resp:
+            assert resp.status == 204 and resp.headers["Access-Control-Allow-Methods"] == "GET, POST"
+        req = urllib.request.Request(f"http://127.0.0.1:{port}/generate", data=json.dumps({"inputs": "w1 w2", "parameters": {"max_new_tokens": 2}}).encode(),
+                                     headers={"Content-Type": "application/json"})
+        with urllib.request.urlopen(req, timeout=60) as resp:
+            assert "generated_text" in json.loads(resp.read())
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            raise
+    out = proc.stdout.read().decode()
+    assert proc.returncode == 0 and "starting 1 shard(s)" in out, out[-2000:]
+    for flag in ("--backend", "--disable-sgmv", "--trust-remote-code"):
+        assert f"{flag} is accepted for compatibility" in out
