@@ -1052,7 +1052,8 @@ def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel]
     tp.barrier()
     tok = load_tokenizer(model_dir)
     rt = ShardRuntime(model, tok, cfg, model_id=model_id, **kw)
-    tc_path = os.path.join(model_dir, "tokenizer_config.json")
+    # the launcher's --tokenizer-config-path (router/src/main.rs:196-363 of the reference reads the same override)
+    tc_path = os.environ.get("TOKENIZER_CONFIG_PATH") or os.path.join(model_dir, "tokenizer_config.json")
     if os.path.exists(tc_path):
         with open(tc_path) as f:
             tc = json.load(f)

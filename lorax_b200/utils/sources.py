@@ -65,6 +65,11 @@ def _s3_sync(uri: str) -> str:
 def resolve_model(model_id: str, source: str = HUB, revision: Optional[str] = None) -> str:
     if os.path.isdir(model_id):
         return model_id
+    # WEIGHTS_CACHE_OVERRIDE (the launcher's --weights-cache-override): a directory that already holds the files of the model,
+    # read instead of any download (utils/weights.py:460-552 of the reference checks the same variable first)
+    override = os.environ.get("WEIGHTS_CACHE_OVERRIDE")
+    if override and os.path.isdir(override) and os.path.exists(os.path.join(override, "config.json")):
+        return override
     if source == LOCAL:
         raise SourceError(f"local model directory {model_id} does not exist")
     if source == S3:
@@ -84,6 +89,7 @@ def resolve_adapter(adapter_id: str, source: str = HUB, api_token: Optional[str]
         return _s3_sync(adapter_id)
     if source == PBASE:
         gateway = os.environ.get("PREDIBASE_GATEWAY_ENDPOINT")
+        api_token = api_token or os.environ.get("PREDIBASE_API_TOKEN")      # the launcher's --predibase-api-token
         if not gateway:
             raise SourceError("the pbase source needs PREDIBASE_GATEWAY_ENDPOINT and an api_token")
         import requests
