@@ -80,7 +80,7 @@ def quantize(args):
     extra = {}
     if args.scheme == "gptq":
         extra = dict(bits=args.bits, group=args.groupsize, nsamples=args.nsamples, seqlen=args.seqlen, dataset=args.dataset,
-                     damp=args.percdamp)
+                     damp=args.percdamp, act_order=args.act_order)
     stats = quantize_checkpoint(args.model_id, args.output_dir, method=args.scheme, **extra)
     _log("INFO", f"quantised checkpoint written to {args.output_dir}: {stats['quantized']} of {stats['tensors']} tensors in {args.scheme}",
          args.json_output)
@@ -113,6 +113,12 @@ def main(argv=None):
     s.add_argument("--prefix-caching", action="store_true")
     s.add_argument("--chunked-prefill", action="store_true")
     s.add_argument("--json-output", action="store_true")
+    # options of the reference's shard CLI that select nothing here: graphs are on unless --no-compile, no remote code is ever
+    # run, encoders report their own width, and log lines carry their level
+    s.add_argument("--compile", action="store_true", help=argparse.SUPPRESS)
+    s.add_argument("--trust-remote-code", action="store_true", help=argparse.SUPPRESS)
+    s.add_argument("--embedding-dim", type=int, default=None, help=argparse.SUPPRESS)
+    s.add_argument("--logger-level", default="INFO", help=argparse.SUPPRESS)
     s.set_defaults(fn=serve)
     d = sub.add_parser("download-weights")
     d.add_argument("model_id")
@@ -130,6 +136,7 @@ def main(argv=None):
     q.add_argument("--nsamples", type=int, default=128)
     q.add_argument("--seqlen", type=int, default=2048)
     q.add_argument("--percdamp", type=float, default=0.01)
+    q.add_argument("--act-order", action="store_true", help="quantise the most active input channels first (desc_act checkpoints)")
     q.add_argument("--dataset", default="", help="UTF-8 text file with one calibration sample per line (default: random token ids)")
     q.add_argument("--json-output", action="store_true")
     q.set_defaults(fn=quantize)

@@ -126,8 +126,10 @@ def collect_hessians(model, token_batches) -> Dict[tuple, torch.Tensor]:
 
 
 def gptq_quantize_checkpoint(model_dir: str, out_dir: str, bits: int = 4, group: int = 128, nsamples: int = 32, seqlen: int = 256,
-                             dataset: str = "", device: str = "", damp: float = 0.01, seed: int = 0) -> Dict[str, int]:
-    """GPTQ over every decoder projection of the checkpoint.  `dataset` is a UTF-8 text file (one sample per line, cut to
+                             dataset: str = "", device: str = "", damp: float = 0.01, seed: int = 0, act_order: bool = False) -> Dict[str, int]:
+    """GPTQ over every decoder projection of the checkpoint.  `act_order` quantises the input channels of every layer from the
+    most to the least active one (largest diagonal entry of the Hessian first; `--act-order` of the reference's quantize
+    command, cli.py:145-176) and records the order in `g_idx`, which the loader serves packed.  `dataset` is a UTF-8 text file (one sample per line, cut to
     `seqlen` tokens); without it the calibration inputs are random token ids, which still yields the correlations between a
     layer's input channels but not the token statistics of real text."""
     from safetensors.torch import load_file, save_file
@@ -182,13 +184,26 @@ def gptq_quantize_checkpoint(model_dir: str, out_dir: str, bits: int = 4, group:
                 out[name] = t
                 continue
             H = hess[key].to(dev)
-            Q, sc, zp = gptq_quantize(t.to(dev).float(), H, bits=bits, group=group, damp=damp)
-            for suffix, v in gptq_pack(Q.cpu(), sc.cpu(), zp.cpu(), bits, g).items():
+            W = t.to(dev).float()
+            perm = None
+            if act_order:
+                perm = torch.argsort(torch.diag(H), descending=True, stable=True)
+                W, H = W[:, perm], H[perm][:, perm]
+            Q, sc, zp = gptq_quantize(W, H, bits=bits, group=group, damp=damp)
+            g_idx = None
+            if perm is not None:                 # back to the checkpoint's column order; column perm[i] belongs to group i // g
+                inv = torch.argsort(perm)
+                Q = Q[:, inv]
+                g_idx = (inv // g).to(torch.int32).cpu()
+            tensors = gptq_pack(Q.cpu(), sc.cpu(), zp.cpu(), bits, g)
+            if g_idx is not None:
+                tensors["g_idx"] = g_idx
+            for suffix, v in tensors.items():
                 out[name[: -len("weight")] + suffix] = v.contiguous()
             n_q += 1
         save_file(out, str(dst / Path(shard).name), metadata={"format": "pt"})
     _copy_side_files(src, dst)
-    qcfg = {"quant_method": "gptq", "bits": bits, "group_size": group, "desc_act": False, "sym": False, "damp_percent": damp,
+    qcfg = {"quant_method": "gptq", "bits": bits, "group_size": group, "desc_act": bool(act_order), "sym": False, "damp_percent": damp,
             "checkpoint_format": "gptq"}
     cfg_path = dst / "config.json"
     if cfg_path.exists():

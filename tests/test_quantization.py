@@ -351,9 +351,10 @@ def test_quantised_gemm_dispatch_and_model_on_gpu():
     assert ((a - b).norm() / b.norm()).item() < 0.06
 
 
-def test_gptq_checkpoint_quantiser_writes_a_loadable_checkpoint(tmp_path):
-    """`lorax-server quantize --scheme gptq`: calibrate, quantise, write the AutoGPTQ layout; the result loads packed, and its
-    logits are closer to the dense model's than round-to-nearest at the same bit width."""
+@pytest.mark.parametrize("act_order", [False, True])
+def test_gptq_checkpoint_quantiser_writes_a_loadable_checkpoint(tmp_path, act_order):
+    """`lorax-server quantize --scheme gptq` (with and without `--act-order`): calibrate, quantise, write the AutoGPTQ layout; the
+    result loads packed, and its logits are closer to the dense model's than round-to-nearest at the same bit width."""
     from safetensors.torch import load_file, save_file
     from lorax_b200.server import cli
     from lorax_b200.utils.weights import Weights, weight_files
@@ -367,7 +368,8 @@ def test_gptq_checkpoint_quantiser_writes_a_loadable_checkpoint(tmp_path):
                                                  "num_attention_heads": cfg.num_attention_heads, "num_key_value_heads": cfg.num_key_value_heads,
                                                  "rms_norm_eps": cfg.rms_norm_eps, "rope_theta": cfg.rope_theta,
                                                  "max_position_embeddings": 2048, "torch_dtype": "float32"}))
-    cli.main(["quantize", str(src), str(dst), "--scheme", "gptq", "--nsamples", "8", "--seqlen", "96", "--json-output"])
+    cli.main(["quantize", str(src), str(dst), "--scheme", "gptq", "--nsamples", "8", "--seqlen", "96", "--json-output"] +
+             (["--act-order"] if act_order else []))
     out = load_file(str(dst / "model.safetensors"))
     assert "model.layers.0.self_attn.q_proj.qweight" in out and "model.layers.0.self_attn.q_proj.weight" not in out
     assert out["model.layers.1.mlp.down_proj.qweight"].dtype == torch.int32 and "model.embed_tokens.weight" in out
@@ -377,6 +379,13 @@ def test_gptq_checkpoint_quantiser_writes_a_loadable_checkpoint(tmp_path):
     w.quant = checkpoint_quantization(dst, raw)
     mq = DecoderModel.from_weights(cfg, w, torch.device("cpu"), torch.float32)
     assert mq.quantized == "gptq" and isinstance(mq.layers[1].down_w, qf.GroupQuantWeight)
+    assert raw["quantization_config"]["desc_act"] is act_order
+    if act_order:                # every projection keeps its channel order, and the fused ones share it
+        assert all(isinstance(getattr(lw, n), qf.GroupQuantWeight) and getattr(lw, n).perm is not None
+                   for lw in mq.layers for n in ("qkv_w", "o_w", "gate_up_w", "down_w"))
+        assert not torch.equal(out["model.layers.0.mlp.down_proj.g_idx"].long(), torch.arange(cfg.intermediate_size) // 128)
+    else:
+        assert mq.layers[0].qkv_w.perm is None
     g = torch.Generator().manual_seed(0)
     ids = torch.randint(0, cfg.vocab_size, (64,), generator=g).tolist()
     want = _forward(dense, ids)
