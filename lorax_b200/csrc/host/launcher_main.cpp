@@ -356,6 +356,9 @@ int main(int argc, char** argv) {
     std::vector<std::string> dargs = {c.get("python"), "-m", "lorax_b200.server.cli", "download-weights", c.get("model-id"),
                                       "--source", c.get("source"), "--json-output"};
     if (!c.get("revision").empty()) { dargs.push_back("--revision"); dargs.push_back(c.get("revision")); }
+    if (!c.get("adapter-id").empty()) {
+      dargs.insert(dargs.end(), {"--adapter-id", c.get("adapter-id"), "--adapter-source", c.get("adapter-source")});
+    }
     emit("INFO", "lorax_launcher", "Starting download process.");
     Child dl = spawn("download", dargs, shard_env(c));
     if (dl.pid <= 0) return 1;

@@ -73,6 +73,10 @@ def download_weights(args):
     d = resolve_model(args.model_id, args.source, args.revision)
     files = weight_files(d, args.extension)
     _log("INFO", f"{len(files)} weight file(s) ready under {d}", args.json_output)
+    if args.adapter_id:              # the default adapter is fetched with the base model (cli.py:113-143 of the reference)
+        from ..utils.sources import resolve_adapter
+        a = resolve_adapter(args.adapter_id, args.adapter_source, args.api_token)
+        _log("INFO", f"adapter {args.adapter_id} ready under {a}", args.json_output)
 
 
 def quantize(args):
@@ -125,6 +129,12 @@ def main(argv=None):
     d.add_argument("--revision", default=None)
     d.add_argument("--source", default="hub")
     d.add_argument("--extension", default=".safetensors")
+    d.add_argument("--adapter-id", default="")
+    d.add_argument("--adapter-source", default="hub")
+    d.add_argument("--api-token", default=None)
+    d.add_argument("--auto-convert", default="true", help=argparse.SUPPRESS)      # .bin checkpoints are always converted
+    d.add_argument("--logger-level", default="INFO", help=argparse.SUPPRESS)
+    d.add_argument("--embedding-dim", type=int, default=None, help=argparse.SUPPRESS)
     d.add_argument("--json-output", action="store_true")
     d.set_defaults(fn=download_weights)
     q = sub.add_parser("quantize")

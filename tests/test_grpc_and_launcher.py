@@ -263,3 +263,19 @@ def test_launcher_accepts_the_reference_flag_set(tmp_path):
     assert proc.returncode == 0 and "starting 1 shard(s)" in out, out[-2000:]
     for flag in ("--backend", "--disable-sgmv", "--trust-remote-code"):
         assert f"{flag} is accepted for compatibility" in out
+
+
+def test_download_weights_fetches_the_default_adapter(tmp_path, capsys):
+    """`lorax-server download-weights <model> --adapter-id <adapter>`: the step the launcher runs before the shards start makes
+    the base weights and the default adapter available, and fails when either is missing."""
+    from lorax_b200.adapters.lora import random_adapter, save_peft_adapter
+    from lorax_b200.server import cli
+    mdir = _model_dir(tmp_path)
+    c, mm = random_adapter(tiny_llama(vocab_size=512), r=8, alpha=16, target_modules=["q_proj", "v_proj"], seed=1)
+    save_peft_adapter(tmp_path / "ad", c, mm)
+    cli.main(["download-weights", str(mdir), "--source", "local", "--adapter-id", str(tmp_path / "ad"), "--adapter-source", "local",
+              "--json-output", "--logger-level", "INFO"])
+    out = capsys.readouterr().out
+    assert "1 weight file(s) ready" in out and f"adapter {tmp_path / 'ad'} ready" in out
+    with pytest.raises(Exception):
+        cli.main(["download-weights", str(mdir), "--source", "local", "--adapter-id", str(tmp_path / "nope"), "--adapter-source", "local"])
