@@ -6,7 +6,7 @@ from __future__ import annotations
 from enum import Enum
 from typing import Any, Dict, List, Optional, Union
 
-from pydantic import BaseModel, field_validator, model_validator
+from pydantic import AliasChoices, BaseModel, ConfigDict, Field, field_validator, model_validator
 
 ADAPTER_SOURCES = ["hub", "local", "s3", "pbase"]
 MERGE_STRATEGIES = ["linear", "ties", "dare_linear", "dare_ties"]
@@ -46,8 +46,16 @@ class ResponseFormatType(str, Enum):
 
 
 class ResponseFormat(BaseModel):
+    # `ResponseFormat(type="json_object", schema={...})`, as with the reference client (types.py:65-71 there names the field
+    # `schema_spec` with the same alias); `schema_=` and `schema_spec=` are accepted too
+    model_config = ConfigDict(populate_by_name=True)
+
     type: ResponseFormatType
-    schema_: Optional[Union[Dict[str, Any], str]] = None
+    schema_: Optional[Union[Dict[str, Any], str]] = Field(None, validation_alias=AliasChoices("schema", "schema_", "schema_spec"))
+
+    @property
+    def schema_spec(self):
+        return self.schema_
 
     def to_dict(self):
         d: Dict[str, Any] = {"type": self.type.value}
@@ -81,6 +89,14 @@ class Parameters(BaseModel):
     decoder_input_details: bool = False
     return_k_alternatives: Optional[int] = None
     response_format: Optional[Dict[str, Any]] = None
+
+    @field_validator("response_format", mode="before")
+    def _response_format_as_dict(cls, v):
+        if isinstance(v, ResponseFormat):
+            return v.to_dict()
+        if isinstance(v, dict) and "type" in v:          # same checks and spelling whichever way it was given
+            return ResponseFormat(**v).to_dict()
+        return v
 
     @model_validator(mode="after")
     def _check(self):
@@ -131,6 +147,25 @@ class Request(BaseModel):
         if self.stream and self.parameters is not None and self.parameters.best_of is not None and self.parameters.best_of > 1:
             raise ValidationError("`best_of` != 1 is not supported when `stream` == True")
         return self
+
+
+class BatchRequest(BaseModel):
+    """Several prompts under one set of parameters (`clients/python/lorax/types.py:238-250` of the reference)."""
+    inputs: List[str]
+    parameters: Optional[Parameters] = None
+    stream: bool = False
+
+    @field_validator("inputs")
+    def _not_empty(cls, v):
+        if not v:
+            raise ValidationError("`inputs` cannot be empty")
+        return v
+
+
+class DeployedModel(BaseModel):
+    model_config = ConfigDict(protected_namespaces=())
+    model_id: str
+    sha: str
 
 
 class InputToken(BaseModel):

@@ -71,3 +71,20 @@ def test_merged_adapters_and_request_rules():
 def test_error_mapping(status, payload, exc):
     e = errors.parse_error(status, payload)
     assert type(e) is exc and str(e) == payload["error"]
+
+
+def test_response_format_takes_the_schema_under_its_public_name():
+    """`ResponseFormat(type=..., schema=...)` is how callers of the reference client pass a JSON schema; the schema must reach the
+    request body under `schema` whichever spelling built the object."""
+    from lorax_b200.client import BatchRequest, DeployedModel
+    from lorax_b200.client.types import Parameters, ResponseFormat
+    schema = {"type": "object", "properties": {"a": {"type": "integer"}}}
+    for fmt in (ResponseFormat(type="json_object", schema=schema), ResponseFormat(type="json_object", schema_=schema),
+                ResponseFormat(type="json_object", schema_spec=schema), {"type": "json_object", "schema": schema}):
+        body = Parameters(response_format=fmt).model_dump(by_alias=True, exclude_none=True)
+        assert body["response_format"] == {"type": "json_object", "schema": schema}
+    assert ResponseFormat(type="json_object", schema=schema).schema_spec == schema
+    assert BatchRequest(inputs=["a", "b"]).stream is False and DeployedModel(model_id="m", sha="0").sha == "0"
+    import pytest
+    with pytest.raises(ValueError, match="cannot be empty"):
+        BatchRequest(inputs=[])
