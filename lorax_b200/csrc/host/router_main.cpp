@@ -447,12 +447,16 @@ class App {
     p.traceparent = req.header("traceparent");
     apply_auth(req, p);
     // tools -> JSON schema grammar: {"_name": const tool name, ...arguments} or the no_tool fallback
-    if (body["tools"].is_array() && body["tools"].size() > 0) p.schema = tool_schema(body["tools"], body["tool_choice"]);
+    if (body["tools"].is_array() && body["tools"].size() > 0 && !body["response_format"].is_object())
+      p.schema = tool_schema(body["tools"], body["tool_choice"]);
     std::string prompt;
     try {
       Value treq = Value::object();
       treq.set("messages", body["messages"]);
-      if (body["tools"].is_array()) treq.set("tools", body["tools"]);
+      // a response_format takes precedence over tools: the template is then applied without them (server.rs:436-440 of the reference)
+      if (body["tools"].is_array() && !body["response_format"].is_object()) treq.set("tools", body["tools"]);
+      if (body["tool_prompt"].is_string()) treq.set("tool_prompt", body["tool_prompt"]);
+      if (body["guideline"].is_string()) treq.set("guideline", body["guideline"]);
       treq.set("adapter_id", p.adapter_id ? Value(*p.adapter_id) : Value());
       prompt = client_->helper(102, treq.dump());
     } catch (const std::exception& e) {
@@ -602,7 +606,8 @@ class App {
         }
         choice.set("message", msg);
       } else {
-        choice.set("text", c.text);
+        // `echo`: the completion is returned behind its prompt (return_full_text, server.rs:1272 of the reference)
+        choice.set("text", body["echo"].is_bool() && body["echo"].as_bool() ? prompt + c.text : c.text);
       }
       choice.set("finish_reason", openai_finish_reason(c.finish_reason));
       Value choices = Value::array();

@@ -17,8 +17,19 @@ class TemplateError(ValueError):
     pass
 
 
+DEFAULT_TOOL_PROMPT = ("\nGiven the functions available, please respond with a JSON for a function call with its proper arguments that "
+                       "best answers the given prompt. Respond in the format {name: function name, parameters: dictionary of argument "
+                       "name and its value}.Do not use variables.\n")
+
+
 def render_chat(messages: List[dict], template: Optional[str], tools=None, bos_token: str = "", eos_token: str = "",
-                add_generation_prompt: bool = True) -> str:
+                add_generation_prompt: bool = True, guideline: Optional[str] = None, tool_prompt: Optional[str] = None) -> str:
+    """Prompt text of a chat request.  As in the reference (`router/src/infer.rs:97-147`): a template that names `guideline`
+    needs one; with tools, the tool prompt is appended to the last message, preceded by the tools as JSON when the template
+    itself has no place for them."""
+    import json
+
+    from jinja2 import meta
     from jinja2.sandbox import ImmutableSandboxedEnvironment
 
     def raise_exception(msg):
@@ -27,6 +38,13 @@ def render_chat(messages: List[dict], template: Optional[str], tools=None, bos_t
     env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True)
     env.globals["raise_exception"] = raise_exception
     env.globals["strftime_now"] = lambda fmt: datetime.datetime.now().strftime(fmt)
+    source = template or DEFAULT_TEMPLATE
+    try:
+        variables = meta.find_undeclared_variables(env.parse(source))
+    except Exception as e:
+        raise TemplateError(str(e)) from e
+    if "guideline" in variables and guideline is None:
+        raise TemplateError("Missing template vatiable: guideline")
     norm = []
     for m in messages:
         m = dict(m)
@@ -34,10 +52,15 @@ def render_chat(messages: List[dict], template: Optional[str], tools=None, bos_t
         if isinstance(c, list):       # OpenAI content parts -> text
             m["content"] = "".join(p.get("text", "") for p in c if isinstance(p, dict))
         norm.append(m)
+    if tools:
+        prompt = DEFAULT_TOOL_PROMPT if tool_prompt is None else tool_prompt
+        text = f"\n---\n{prompt}" if "tools" in variables else f"\n---\n{json.dumps(tools, separators=(',', ':'))}\n{prompt}"
+        if norm:
+            norm[-1]["content"] = (norm[-1].get("content") or "") + text
     try:
-        return env.from_string(template or DEFAULT_TEMPLATE).render(
+        return env.from_string(source).render(
             messages=norm, bos_token=bos_token, eos_token=eos_token, add_generation_prompt=add_generation_prompt,
-            tools=tools, tools_in_user_message=False)
+            tools=tools or None, tools_in_user_message=False, guideline=guideline)
     except TemplateError:
         raise
     except Exception as e:

@@ -166,7 +166,7 @@ class ShardRuntime:
     def apply_chat_template(self, body: dict) -> str:
         from .chat_template import render_chat
         return render_chat(body.get("messages", []), self.chat_template, tools=body.get("tools"), bos_token=self.bos_token,
-                           eos_token=self.eos_token)
+                           eos_token=self.eos_token, guideline=body.get("guideline"), tool_prompt=body.get("tool_prompt"))
 
     chat_template: Optional[str] = None
     bos_token: str = ""

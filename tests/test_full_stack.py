@@ -516,3 +516,33 @@ def test_shard_tracer_exports_over_otlp_grpc():
         assert Tracer("http://collector:4317", "s").grpc_target == "collector:4317" and Tracer("http://c:4318", "s").grpc_target is None
     finally:
         server.stop(0)
+
+
+def test_chat_template_tools_guideline_and_echo(stack):
+    """Chat-template inputs as the reference applies them (router/src/infer.rs:97-147): tools reach the prompt even when the
+    template has no `tools` variable (as JSON behind the last message, followed by the tool prompt), a template that names
+    `guideline` refuses a request without one, and `/v1/completions` with `echo` returns the prompt in front of the completion."""
+    from lorax_b200.server.chat_template import DEFAULT_TOOL_PROMPT, TemplateError, render_chat
+    plain = "{% for m in messages %}<{{ m.role }}>{{ m.content }}{% endfor %}"
+    tools = [{"type": "function", "function": {"name": "get_weather", "parameters": {"type": "object", "properties": {"city": {"type": "string"}}}}}]
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "weather in Paris?"}]
+    out = render_chat(msgs, plain, tools=tools)
+    assert out.startswith("<system>be brief<user>weather in Paris?\n---\n[{\"type\":\"function\"") and out.endswith(DEFAULT_TOOL_PROMPT)
+    assert msgs[1]["content"] == "weather in Paris?"                       # the caller's messages are left alone
+    aware = plain + "{% if tools %}[TOOLS {{ tools | length }}]{% endif %}"
+    out = render_chat(msgs, aware, tools=tools, tool_prompt="pick one")
+    assert out == "<system>be brief<user>weather in Paris?\n---\npick one[TOOLS 1]"
+    assert render_chat(msgs, plain) == "<system>be brief<user>weather in Paris?"
+    guided = "{{ guideline }}|" + plain
+    assert render_chat(msgs, guided, guideline="G").startswith("G|<system>")
+    with pytest.raises(TemplateError):
+        render_chat(msgs, guided)
+    # through the router
+    status, data, _ = _post(stack["port"], "/v1/completions", {"model": "tiny", "prompt": "w5 w6 w7", "max_tokens": 3, "echo": True})
+    assert status == 200
+    echoed = json.loads(data)["choices"][0]["text"]
+    status, data, _ = _post(stack["port"], "/v1/completions", {"model": "tiny", "prompt": "w5 w6 w7", "max_tokens": 3})
+    assert status == 200 and echoed == "w5 w6 w7" + json.loads(data)["choices"][0]["text"]
+    status, data, _ = _post(stack["port"], "/v1/chat/completions", {"model": "tiny", "max_tokens": 3, "guideline": "g", "tool_prompt": "p",
+                                                                     "messages": [{"role": "user", "content": "w5 w6"}]})
+    assert status == 200 and json.loads(data)["choices"][0]["message"]["role"] == "assistant"
