@@ -490,7 +490,7 @@ class Infer {
               BatchSpan bs(this, "prefill_decode", entries);
               auto res = client_->prefill(more->batch, std::nullopt, batches);
               bs.finish(res.generations.size());
-              if (metrics_) { metrics_->inc("lorax_batch_inference_count", {{"method", "prefill_decode"}}); metrics_->observe("lorax_batch_inference_duration", secs(t0), {{"method", "prefill_decode"}}); }
+              if (metrics_) { metrics_->inc("lorax_batch_inference_count", {{"method", "prefill_decode"}}); metrics_->inc("lorax_batch_inference_success", {{"method", "prefill_decode"}}); metrics_->observe("lorax_batch_inference_duration", secs(t0), {{"method", "prefill_decode"}}); }
               deliver(res.generations, entries, t0);
               batches.clear();
               auto next = filter(res.batch, entries);
@@ -507,7 +507,7 @@ class Infer {
           BatchSpan bs(this, "decode", entries);
           auto res = client_->decode(batches);
           bs.finish(res.generations.size());
-          if (metrics_) { metrics_->inc("lorax_batch_inference_count", {{"method", "decode"}}); metrics_->observe("lorax_batch_inference_duration", secs(t0), {{"method", "decode"}}); }
+          if (metrics_) { metrics_->inc("lorax_batch_inference_count", {{"method", "decode"}}); metrics_->inc("lorax_batch_inference_success", {{"method", "decode"}}); metrics_->observe("lorax_batch_inference_duration", secs(t0), {{"method", "decode"}}); }
           deliver(res.generations, entries, t0);
           batches.clear();
           auto next = filter(res.batch, entries);
@@ -530,7 +530,7 @@ class Infer {
     BatchSpan bs(this, "prefill", entries);
     auto res = client_->prefill(nb.batch, std::nullopt);
     bs.finish(res.generations.size());
-    if (metrics_) { metrics_->inc("lorax_batch_inference_count", {{"method", "prefill"}}); metrics_->observe("lorax_batch_inference_duration", secs(t0), {{"method", "prefill"}}); }
+    if (metrics_) { metrics_->inc("lorax_batch_inference_count", {{"method", "prefill"}}); metrics_->inc("lorax_batch_inference_success", {{"method", "prefill"}}); metrics_->observe("lorax_batch_inference_duration", secs(t0), {{"method", "prefill"}}); }
     deliver(res.generations, entries, t0);
     return filter(res.batch, entries);
   }

@@ -123,7 +123,7 @@ struct Collected {
   std::optional<uint64_t> seed;
   Value prefill = Value::array();
   Value tokens = Value::array();
-  double queue_s = 0, inference_s = 0, ttft_s = 0, total_s = 0;
+  double queue_s = 0, inference_s = 0, ttft_s = 0, total_s = 0, validation_s = 0;
   double sum_logprob = 0;
 };
 
@@ -227,6 +227,9 @@ class App {
     metrics_.inc("lorax_request_count");
     Collected c;
     c.prompt_tokens = valid.input_length;
+    c.validation_s = std::chrono::duration<double>(Clock::now() - t0).count();      // tokenisation and parameter checks
+    metrics_.observe("lorax_request_validation_duration", c.validation_s);
+    metrics_.observe("lorax_request_max_new_tokens", valid.stopping.max_new_tokens);
     struct Done { Infer& i; ~Done() { i.request_done(); } } done{infer_};
     bool first = true;
     while (true) {
@@ -298,7 +301,7 @@ class App {
         {"x-compute-time", ms(c.total_s)},
         {"x-compute-characters", std::to_string(c.text.size())},
         {"x-total-time", ms(c.total_s)},
-        {"x-validation-time", "0"},
+        {"x-validation-time", ms(c.validation_s)},
         {"x-queue-time", ms(c.queue_s)},
         {"x-inference-time", ms(c.inference_s)},
         {"x-time-per-token", ms(c.generated_tokens ? c.inference_s / c.generated_tokens : 0)},
@@ -650,6 +653,8 @@ class App {
     else inputs.push_back(in.as_string());
     try {
       auto resp = client_->embed(one_shot_batch(inputs));
+      metrics_.inc("lorax_batch_inference_success", {{"method", "embed"}});
+      metrics_.observe("lorax_request_input_count", (double)inputs.size());
       if (!resp.errorMsg.empty()) throw ApiError(resp.errorMsg, "generation", 424);
       Value out = Value::object();
       if (openai) {
@@ -686,8 +691,15 @@ class App {
     if (batch) for (auto& s : body["inputs"].items()) inputs.push_back(s.as_string());
     else inputs.push_back(body["inputs"].as_string());
     try {
+      auto t0 = Clock::now();
       auto resp = client_->classify(one_shot_batch(inputs));
       if (!resp.errorMsg.empty()) throw ApiError(resp.errorMsg, "generation", 424);
+      metrics_.inc("lorax_batch_inference_success", {{"method", "classify"}});
+      metrics_.observe("lorax_request_input_count", (double)inputs.size());
+      metrics_.observe("lorax_request_inference_duration", std::chrono::duration<double>(Clock::now() - t0).count());
+      size_t n_out = 0;
+      for (auto& l : resp.classify_prediction_lists) n_out += l.predictions.size();
+      metrics_.observe("lorax_request_classify_output_count", (double)n_out);
       Value all = Value::array();
       for (auto& l : resp.classify_prediction_lists) {
         Value ents = Value::array();

@@ -96,3 +96,9 @@ def test_embed_and_classify_routes(emb_stack):
 
     st, body, _ = _post(port, "/generate", {"inputs": text, "parameters": {"max_new_tokens": 2}})
     assert st in (422, 424), body
+    import urllib.request
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5) as r:
+        m = r.read().decode()
+    for name in ('lorax_batch_inference_success{method="classify"}', 'lorax_batch_inference_success{method="embed"}',
+                 "lorax_request_input_count_bucket", "lorax_request_classify_output_count_bucket"):
+        assert name in m, name

@@ -167,6 +167,9 @@ def test_errors_and_misc_routes(stack):
     with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5) as r:
         m = r.read().decode()
     assert "lorax_request_success" in m and "lorax_batch_inference_duration_bucket" in m
+    for name in ('lorax_batch_inference_success{method="prefill"}', 'lorax_batch_inference_success{method="decode"}',
+                 "lorax_request_validation_duration_bucket", "lorax_request_max_new_tokens_bucket"):
+        assert name in m, name
     st, body, _ = _post(port, "/tokenize", {"inputs": "w7 w8"})
     assert st == 200 and [t["id"] for t in json.loads(body)] == [7, 8]
 
