@@ -32,14 +32,47 @@ sys.path.insert(0, REPO)
 
 
 def reference_arm(args):
-    """The reference needs its Rust router/launcher (no cargo here), generated protobuf stubs (no grpcio-tools),
-    poetry-core to build, and kernels (punica with empty submodules, flash-attn, vLLM) that are fetched over the
-    network at build time; `pip install` of /root/reference fails offline."""
-    ref_pkg = os.path.join(REPO, "baseline", "_ref", "lorax_server")
-    why = ("reference not installable offline: pip install fails (no setup.py/pyproject at the repo root; server/ needs the "
-           "poetry-core backend, protoc-generated stubs, a Rust toolchain for router+launcher and network-fetched CUDA kernels)")
-    if os.path.isdir(ref_pkg):
-        why = "reference python package present but its router/launcher (Rust) and CUDA kernels cannot be built offline"
+    """Tries the unmodified reference: its Python shard package as copied into baseline/_ref by
+    baseline/install_reference.py (the package directory plus the protobuf stubs its Makefile would generate).  The
+    stock Mistral path is imported in this process on this machine; when an import fails the JSON line names the
+    module, the importing file and the other native modules of that path that are missing here."""
+    import importlib
+    import traceback
+    ref_root = os.path.join(REPO, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_root, "lorax_server")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/lorax_server is absent: run baseline/install_reference.py "
+                          "<reference checkout> (pip cannot install the reference offline: no poetry-core backend)"}))
+        return 0
+    sys.path.insert(0, ref_root)
+    try:
+        import torch  # noqa: F401  (CUDA extensions link against torch's libraries)
+    except Exception:
+        pass
+    missing = []
+    # third-party modules the stock FlashMistral path imports (file:line in the reference's server/lorax_server)
+    for mod, where in (("peft", "utils/adapter.py:13"), ("dropout_layer_norm", "models/custom_modeling/flash_mistral_modeling.py:24"),
+                       ("rotary_emb", "layers/rotary.py:10"), ("flash_attn_2_cuda", "utils/flash_attn.py"),
+                       ("punica_kernels", "utils/punica.py"), ("grpc_interceptor", "interceptor.py")):
+        try:
+            importlib.import_module(mod)
+        except BaseException as e:      # a CUDA extension built for another torch raises ImportError/OSError
+            missing.append(f"{mod} ({where}): {type(e).__name__}: {str(e)[:80]}")
+    try:
+        import torch  # noqa: F401
+        importlib.import_module("lorax_server.models.flash_mistral")
+        first = None
+    except BaseException as e:
+        tb = traceback.extract_tb(e.__traceback__)
+        site = next((f"{fr.filename.split('_ref/')[-1]}:{fr.lineno}" for fr in reversed(tb) if "_ref/" in fr.filename), "?")
+        first = f"{type(e).__name__}: {e} at {site}"
+    if first is None and not missing:
+        why = ("the reference's FlashMistral stack imports on this machine, but its router and launcher are Rust (no cargo) and no "
+               "in-process driver for it ships with this benchmark")
+    else:
+        why = ("importing the reference's stock lorax_server.models.flash_mistral fails on this machine: " + (first or "ok") +
+               "; modules of that path missing here: " + ("; ".join(missing) if missing else "none") +
+               ". None is in the offline wheelhouse; dropout_layer_norm / rotary_emb / punica_kernels are CUDA extensions the "
+               "reference builds from network-fetched sources for sm_80")
     print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
@@ -108,11 +141,23 @@ def zipf_sampler(n: int, s: float, gen):
     return draw
 
 
-def _finish(tp):
-    """Leave without tearing the NCCL communicator down: destroying a process group whose collectives were captured
-    in CUDA graphs can block forever at interpreter exit."""
+def _finish(tp, eng=None):
+    """World 1 returns to the interpreter.  With several ranks the NCCL communicator is not torn down (destroying a process
+    group whose collectives were captured in CUDA graphs can block at interpreter exit): the graphs are dropped, the ranks
+    meet at a barrier, the interpreter's exit handlers run, and the process leaves."""
+    sys.stdout.flush()
+    sys.stderr.flush()
+    if tp.world_size == 1:
+        return 0
     try:
+        if eng is not None:
+            eng.runner.graphs.clear()
         tp.barrier()
+    except Exception:
+        pass
+    import atexit
+    try:
+        atexit._run_exitfuncs()
     except Exception:
         pass
     sys.stdout.flush()
@@ -126,10 +171,14 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--model", default="mistral-7b", choices=["mistral-7b", "llama3-8b", "llama3-70b", "tiny"])
+    ap.add_argument("--model", default="mistral-7b", choices=["mistral-7b", "llama3-8b", "llama3-70b", "mixtral-8x7b", "tiny"])
     ap.add_argument("--batch", type=int, default=256, help="requests kept in flight")
     ap.add_argument("--adapters", type=int, default=100)
-    ap.add_argument("--rank", type=int, default=16)
+    ap.add_argument("--ranks", default="16", help="LoRA rank, or a comma list of ranks dealt round-robin over the adapters")
+    ap.add_argument("--arrivals", default="poisson", choices=["poisson", "closed"])
+    ap.add_argument("--requests", type=int, default=2000, help="poisson: number of arrivals")
+    ap.add_argument("--rate", type=float, default=400.0, help="poisson: arrivals per second")
+    ap.add_argument("--quantize", default=None, choices=[None, "fp8"], help="base linear weights in block-scaled fp8 e4m3")
     ap.add_argument("--resident", type=int, default=None,
                     help="adapters that fit the HBM arena (default: all). Fewer makes the engine exchange adapters with the pinned host tier")
     ap.add_argument("--min-prompt", type=int, default=128)
@@ -163,7 +212,8 @@ def main():
     dev = tp.device
     rank0 = tp.rank == 0
 
-    mc = {"mistral-7b": cfgs.mistral_7b, "llama3-8b": cfgs.llama3_8b, "llama3-70b": cfgs.llama3_70b, "tiny": cfgs.tiny_llama}[args.model]()
+    mc = {"mistral-7b": cfgs.mistral_7b, "llama3-8b": cfgs.llama3_8b, "llama3-70b": cfgs.llama3_70b, "mixtral-8x7b": cfgs.mixtral_8x7b,
+          "tiny": cfgs.tiny_llama}[args.model]()
     if args.model == "tiny":
         mc.torch_dtype = "bfloat16"
     if args.layers:
@@ -171,6 +221,8 @@ def main():
     max_total = args.max_prompt + args.new_tokens + 32
     t_setup = time.perf_counter()
     model = DecoderModel.random_init_on_device(mc, dev, torch.bfloat16, seed=0, tp=tp, max_positions=max_total + 64)
+    if args.quantize == "fp8":
+        model.quantize_fp8()
     if tp.world_size > 1 and not args.baseline_mode:
         try:
             from lorax_b200.parallel import fused
@@ -183,20 +235,20 @@ def main():
     esize = 2
     from lorax_b200.adapters.lora import BlobLayout, pad_rank
     layout_units = BlobLayout(model, with_lm_head=False).units
-    rp = pad_rank(args.rank)
-    blob_elems = rp * layout_units
+    ranks = [int(x) for x in str(args.ranks).split(",")]
+    rps = [pad_rank(r) for r in ranks]
+    elems = [rp * layout_units for rp in rps]                     # adapter a has rank ranks[a % len(ranks)]
+    mean_elems = sum(elems) / len(elems)
     resident = args.adapters if args.resident is None else max(1, min(args.resident, args.adapters))
-    arena_bytes = int(blob_elems * esize * (resident + 2) * 1.02) + (64 << 20)
-    mgr = AdapterManager(model, arena_bytes=arena_bytes, host_bytes=int(blob_elems * esize * (args.adapters + 4)))
+    arena_bytes = int(mean_elems * esize * (resident + 2) * 1.02) + int(max(elems) * esize) + (64 << 20)
+    mgr = AdapterManager(model, arena_bytes=arena_bytes, host_bytes=int(mean_elems * esize * (args.adapters + 4)) + (64 << 20))
     g_dev = torch.Generator(device=dev).manual_seed(1234 + tp.rank)
-    scale = 2.0 * 16 / args.rank        # alpha / r folded into B (alpha = 32)
     for a in range(args.adapters):
-        blob = torch.randn(blob_elems, generator=g_dev, device=dev, dtype=torch.float32).mul_(0.02).to(torch.bfloat16)
-        if rp != args.rank:
-            pass   # padded rows stay random here; only throughput is measured
-        host = torch.empty(blob_elems, dtype=torch.bfloat16, pin_memory=True)
+        n_el = elems[a % len(elems)]
+        blob = torch.randn(n_el, generator=g_dev, device=dev, dtype=torch.float32).mul_(0.02).to(torch.bfloat16)
+        host = torch.empty(n_el, dtype=torch.bfloat16, pin_memory=True)
         host.copy_(blob)
-        mgr.register_blob(f"adapter-{a}", host, rp)
+        mgr.register_blob(f"adapter-{a}", host, rps[a % len(rps)])
         del blob
     torch.cuda.synchronize(dev)
     for a in range(resident):
@@ -215,29 +267,60 @@ def main():
     gen = torch.Generator().manual_seed(42)          # identical on every rank: ranks schedule in lockstep
     draw_adapter = zipf_sampler(args.adapters, 1.1, gen) if args.adapters > 0 else (lambda: -1)
     next_id = [1]
+    meta = {}                                        # request id -> (arrival time, counts for latency stats)
 
-    def new_request(ramp: bool = False):
+    def new_request(ramp: bool = False, arrival: float = 0.0):
         n = int(torch.randint(args.min_prompt, args.max_prompt + 1, (1,), generator=gen))
         ids = torch.randint(0, mc.vocab_size, (n,), generator=gen).tolist()
         new = args.new_tokens
         if ramp:       # requests of the ramp start "mid flight" so that the batch is a steady-state mix of progress
             new = int(torch.randint(1, args.new_tokens + 1, (1,), generator=gen))
-        r = GenRequest(next_id[0], ids, max_new_tokens=new, adapter_index=draw_adapter() + 1, ignore_eos_token=True)
+        r = GenRequest(next_id[0], ids, max_new_tokens=new, adapter_index=draw_adapter() + 1, ignore_eos_token=True,
+                       arrival_time=arrival)
         next_id[0] += 1
         return r
 
-    done_stats = {"ttft": [], "tpot": []}
+    # ---- arrivals.  "poisson": `--requests` arrivals with exponential gaps at `--rate` requests/s on the wall clock that
+    # starts when the ramp ends (every rank draws the same gaps and follows rank 0's clock through the step barrier of the
+    # collectives; admission itself is deterministic given the queue).  "closed": a finished request is replaced at once.
+    lat = {"ttft": [], "ttft_sched": [], "itl": []}
+    last_tok = {}
+    poisson = args.arrivals == "poisson"
+    gaps = (torch.empty(args.requests, dtype=torch.float64).exponential_(args.rate, generator=gen).cumsum(0).tolist()
+            if poisson else [])
+    arr = {"next": 0, "t0": None, "admitted": 0}
 
-    def harvest(events):
+    def feed(now: float):
+        """Hand the engine every request whose arrival time has passed."""
+        if not poisson:
+            return
+        if tp.world_size > 1:                        # one clock for all ranks: rank 0's
+            now = tp.broadcast_scalar(now)
+        while arr["next"] < len(gaps) and arr["t0"] + gaps[arr["next"]] <= now:
+            r = new_request(arrival=arr["t0"] + gaps[arr["next"]])
+            meta[r.request_id] = r.arrival_time
+            eng.add_request(r)
+            arr["next"] += 1
+
+    def harvest(events, record: bool = False):
         n = 0
         for ev in events:
             n += 1
+            rid = ev.request_id
+            if record:
+                if ev.index == 0 and rid in meta:
+                    lat["ttft"].append(ev.device_time - meta[rid])
+                elif ev.index > 0 and rid in last_tok:
+                    lat["itl"].append(ev.device_time - last_tok[rid])
+            last_tok[rid] = ev.device_time
             if ev.finished:
-                seq = eng.finished.pop(ev.request_id, None)
-                if seq is not None and len(seq.output_ids) > 1 and seq.req.max_new_tokens == args.new_tokens:
-                    done_stats["ttft"].append(seq.first_token_time - seq.req.arrival_time)
-                    done_stats["tpot"].append((seq.last_token_time - seq.first_token_time) / (len(seq.output_ids) - 1))
-                eng.add_request(new_request())
+                eng.finished.pop(rid, None)
+                last_tok.pop(rid, None)
+                meta.pop(rid, None)
+                if not poisson:
+                    r = new_request(arrival=time.perf_counter())
+                    meta[r.request_id] = r.arrival_time
+                    eng.add_request(r)
         return n
 
     # ---- ramp: fill the batch (not part of warm-up or timing)
@@ -247,7 +330,9 @@ def main():
     while len(eng.waiting) > 0 and ramp_steps < 400:
         harvest(eng.step())
         ramp_steps += 1
+    arr["t0"] = time.perf_counter()
     for _ in range(args.warmup):
+        feed(time.perf_counter())
         harvest(eng.step())
     torch.cuda.synchronize(dev)
     setup_s = time.perf_counter() - t_setup
@@ -265,7 +350,8 @@ def main():
         e0.record()
         toks = 0
         for _ in range(n_steps):
-            toks += harvest(eng.step())
+            feed(time.perf_counter())
+            toks += harvest(eng.step(), record=True)
         e1.record()
         tp.barrier()
         torch.cuda.synchronize(dev)
@@ -281,30 +367,37 @@ def main():
                     adapter_loads=eng.stats.get("adapter_loads", 0) - p0.get("adapter_loads", 0))
 
     w1 = window(args.steps, device_timed=True)
+    n_lat = {k: len(v) for k, v in lat.items()}
     w2 = window(args.steps, device_timed=False)
     if not rank0:
-        _finish(tp)
+        return _finish(tp, eng)
     value = w1["tokens"] / w1["seconds"]
     e2e = w2["tokens"] / w2["seconds"]
-    med = lambda xs: (statistics.median(xs) if xs else None)
+    pct = lambda xs, q: (round(1e3 * sorted(xs)[min(len(xs) - 1, int(q * len(xs)))], 3) if xs else None)
     out = {
         "metric": "output tok/s at 100 adapters, Mistral-7B arch, TP1-8; p50 TTFT/TPOT",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": tp.world_size, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(1e3 * w1["seconds"] / args.steps, 3), "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random token ids, random-init base and adapter weights)",
+        "vs_baseline": None, "dtype": "bf16" if not args.quantize else f"bf16 activations, {args.quantize} base weights",
+        "data": "synthetic (random token ids, random-init base and adapter weights)",
         "impl": "ours",
         "config": {
             "model": args.model + (f"-{args.layers}layers-DEBUG" if args.layers else ""), "global_batch": args.batch,
             "seq_len": f"prompt U[{args.min_prompt},{args.max_prompt}] + {args.new_tokens} new",
             "parallelism": f"tp{tp.world_size}", "adapters": args.adapters, "resident_adapters": resident,
-            "adapter_loads_in_window": w1["adapter_loads"], "lora_rank": args.rank,
-            "lora_targets": "q,k,v,o,gate,up,down", "adapter_choice": "zipf(1.1)", "arrivals": "closed loop (saturated)",
+            "adapter_loads_in_window": w1["adapter_loads"], "lora_rank": args.ranks,
+            "lora_targets": "q,k,v,o,gate,up,down", "adapter_choice": "zipf(1.1)",
+            "arrivals": (f"poisson, {args.requests} requests at {args.rate:g}/s (more than the engine serves: the queue never empties), after a ramp "
+                         f"that fills {args.batch} decode rows" if poisson else "closed loop (saturated)"),
+            "requests_arrived": arr["next"] if poisson else None, "waiting_at_end": len(eng.waiting),
             "l2": "inputs larger than L2: each step streams >14 GB of weights, adapters and KV cache",
             "cuda_graphs": not args.no_graphs, "collectives": "nccl" if (args.baseline_mode or tp.fused is None) else "fused-nvlink",
             "prefill_tokens_in_window": w1["prefill_tokens"], "prefill_steps": w1["prefill_steps"], "decode_steps": w1["decode_steps"],
         },
-        "p50_ttft_ms": round(1e3 * med(done_stats["ttft"]), 2) if done_stats["ttft"] else None,
-        "p50_tpot_ms": round(1e3 * med(done_stats["tpot"]), 3) if done_stats["tpot"] else None,
+        # device timestamps (CUDA events of the steps that produced the tokens) of both windows.  TTFT = first token - arrival, which
+        # under saturating arrivals is mostly time in the queue; TPOT = gap between consecutive tokens of a running request.
+        "p50_ttft_ms": pct(lat["ttft"], 0.5), "p50_tpot_ms": pct(lat["itl"], 0.5),
+        "p99_tpot_ms": pct(lat["itl"], 0.99), "latency_samples": {"ttft": len(lat["ttft"]), "tpot": len(lat["itl"])},
         "clocks": {k: w1["clocks"][k] for k in ("sm_mhz", "sm_max_mhz", "reasons")},
         "e2e": {"value": round(e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": round(w2["h2d"], 1),
                 "d2h_bytes_per_step": round(w2["d2h"], 1), "timing": "host wall clock around Engine.step()",
@@ -313,7 +406,7 @@ def main():
         "setup_s": round(setup_s, 1),
     }
     print(json.dumps(out))
-    _finish(tp)
+    return _finish(tp, eng)
 
 
 if __name__ == "__main__":

@@ -9,6 +9,11 @@ Strategies and their parameters follow the reference (`server/lorax_server/utils
   dare_linear  drop entries at random with probability 1 - density, rescale survivors by 1 / density, weighted sum
   dare_ties    random drop + rescale, then the sign election and disjoint mean of TIES
 
+The sign of TIES / DARE-TIES is elected on the pruned tensors before the weights are applied, as the reference does.
+One deliberate difference: the DARE strategies do rescale the survivors by 1 / density, as the DARE method and PEFT
+define it; the reference computes that quotient and discards it (`utils/merges/utils.py:51-53`), so its DARE output is
+smaller by the factor `density`.
+
 lora_A and lora_B are merged separately per module; ranks are zero-padded to the largest rank; each adapter's
 alpha / r is folded into its B first so that adapters with different scales combine correctly.
 """
@@ -68,10 +73,13 @@ def merge_tensors(tensors: Sequence[torch.Tensor], weights: Sequence[float], str
         ts = [prune_random(t, density, rescale=True, generator=generator) for t in ts]
     else:
         raise ValueError(f"unknown merge strategy {strategy!r}")
-    stacked = torch.stack(ts) * w
+    unweighted = torch.stack(ts)
+    stacked = unweighted * w
     if strategy == "dare_linear":
         return stacked.sum(0)
-    return disjoint_merge(stacked, majority_sign_mask(stacked, majority_sign_method))
+    # the sign is elected on the pruned tensors BEFORE the weights are applied (reference utils/merges/strategies.py:62-66,
+    # 93-97), so a negative or a large weight does not change which entries take part
+    return disjoint_merge(stacked, majority_sign_mask(unweighted, majority_sign_method))
 
 
 def _pad_rank(t: torch.Tensor, r: int, dim: int) -> torch.Tensor:

@@ -171,22 +171,27 @@ class RadixAllocator : public Allocator {
     }
     return node;
   }
-  // Split `child` so that its edge holds exactly `len` tokens; the tail becomes its only child.  Returns the head.
+  // Split `child` so that a NEW node holding its first `len` tokens sits between it and its parent; `child` itself keeps
+  // the rest of the edge.  Live allocations point at `child` and release their references by walking up from it, so the
+  // node they know must stay the deepest part; the new head starts with the same count because every one of those walks
+  // passes through it.  Returns the head.
   Node* split(Node* child, size_t len) {
-    auto tail = std::make_unique<Node>();
-    tail->key.assign(child->key.begin() + len, child->key.end());
-    tail->blocks.assign(child->blocks.begin() + len / block_size_, child->blocks.end());
-    tail->children = std::move(child->children);
-    for (auto& kv : tail->children) kv.second->parent = tail.get();
-    tail->ref_count = child->ref_count;
-    tail->last_access = child->last_access;
-    tail->parent = child;
-    child->key.resize(len);
-    child->blocks.resize(len / block_size_);
-    child->children.clear();
-    uint32_t first = tail->key[0];
-    child->children[first] = std::move(tail);
-    return child;
+    Node* parent = child->parent;
+    const uint32_t first = child->key[0];
+    std::unique_ptr<Node> owned = std::move(parent->children[first]);
+    auto head = std::make_unique<Node>();
+    head->key.assign(child->key.begin(), child->key.begin() + len);
+    head->blocks.assign(child->blocks.begin(), child->blocks.begin() + len / block_size_);
+    head->parent = parent;
+    head->ref_count = child->ref_count;
+    head->last_access = child->last_access;
+    child->key.erase(child->key.begin(), child->key.begin() + len);
+    child->blocks.erase(child->blocks.begin(), child->blocks.begin() + len / block_size_);
+    child->parent = head.get();
+    Node* raw = head.get();
+    head->children[child->key[0]] = std::move(owned);
+    parent->children[first] = std::move(head);
+    return raw;
   }
   // Insert the first `full` blocks of a finished sequence.  Returns how many leading blocks are now owned by the trie
   // (either adopted from this allocation or already present from another one).

@@ -369,16 +369,24 @@ class Infer {
       ev.error = msg;
       ev.error_type = "generation";
       kv.second->sink->push(ev);
-      release(kv.second);
+      release(kv.second, false);
     }
     entries.clear();
   }
-  void release(const std::shared_ptr<Entry>& e) {
+  // Returns the entry's blocks.  Only tokens whose keys / values the shards have written may become a cached prefix:
+  // the whole prompt once a first token came back (the prefill finished), plus every generated token except the last,
+  // which was sampled but never fed through the model.  After a failed step nothing is known to be written, so
+  // nothing is cached (`kv_valid` false).
+  void release(const std::shared_ptr<Entry>& e, bool kv_valid = true) {
     std::lock_guard<std::mutex> g(mu_);
     if (e->allocation) {
-      std::vector<uint32_t> all = e->request.input_ids;
-      all.insert(all.end(), e->generated.begin(), e->generated.end());
-      allocator_->free(*e->allocation, e->request.adapter.index, cfg_.prefix_caching ? &all : nullptr);
+      std::vector<uint32_t> all;
+      const bool cache = cfg_.prefix_caching && kv_valid && !e->generated.empty();
+      if (cache) {
+        all = e->request.input_ids;
+        all.insert(all.end(), e->generated.begin(), e->generated.end() - 1);
+      }
+      allocator_->free(*e->allocation, e->request.adapter.index, cache ? &all : nullptr);
       e->allocation.reset();
     }
   }

@@ -619,11 +619,14 @@ int make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uin
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES>;
-  static bool configured = false;
-  if (!configured) {
+  // the shared-memory opt-in is a per-device attribute: one flag per device ordinal
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return -(int)e;
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES>, dim3(grid), dim3(kGemmThreads), (size_t)S::kTotal, stream, ta, tb, p);
   cudaError_t e = cudaGetLastError();
@@ -748,7 +751,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   using namespace lx;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (T <= 0 || N <= 0) return 0;
-  if ((K % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return -1000;
+  if (K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return -1000;
   const int sk_policy = (mode >> 8) & 3;      // 0 by cost, 1 whole tiles only, 2 stream-K whenever a wave is partly filled
   mode &= 0xff;
   const bool have_counters = (ws != nullptr && counters != nullptr);
@@ -933,7 +936,7 @@ const char* lx_gemm_bf16_noalloc_strerror(int code) {
     case -2003: return "T exceeds the 256-token maximum of the no-allocation entry point";
     case -2004: return "N needs more than 1024 output tiles (N > 131072): beyond the static counter array";
     case -2005: return "requested split_k does not fit the 8 MiB static scratch for this N and T";
-    case -2006: return "K, ldx and ldw must be multiples of 8 elements (16-byte TMA alignment)";
+    case -2006: return "K must be positive; K, ldx and ldw must be multiples of 8 elements (16-byte TMA alignment)";
     case -2007: return "clearing the arrival counters failed";
     default: return "launch or tensor-map error (negative CUDA / driver code)";
   }
@@ -952,7 +955,7 @@ int lx_gemm_bf16_noalloc(const void* x, const void* w, void* out, const void* bi
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (T <= 0 || N <= 0) return 0;
   if (T > 256) return -2003;
-  if ((K % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return -2006;
+  if (K <= 0 || (K % 8) != 0 || (ldx % 8) != 0 || (ldw % 8) != 0) return -2006;
   NoAllocScratch* sc = nullptr;
   if (int rc = noalloc_scratch_for_current_device(&sc)) return rc;
   const int tiles = (N + kBM - 1) / kBM;
@@ -1005,13 +1008,17 @@ int lx_gemm_bf16_noalloc(const void* x, const void* w, void* out, const void* bi
   }
 }
 
-// Copies the two status words of the last launch on the current device to host memory (synchronises the device).
+// Copies the two status words of the last launch on the current device to host memory.  The copy is queued on `stream`
+// (pass the stream the GEMM was launched on, non-blocking streams included) and the call returns when it has completed.
 // 0 in out2[0] means every bounded wait inside the kernel completed.
-int lx_gemm_bf16_noalloc_status(int* out2) {
+int lx_gemm_bf16_noalloc_status(int* out2, void* stream_) {
   using namespace lx;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   NoAllocScratch* sc = nullptr;
   if (int rc = noalloc_scratch_for_current_device(&sc)) return rc;
-  return -(int)cudaMemcpy(out2, sc->status, 2 * sizeof(int), cudaMemcpyDeviceToHost);
+  cudaError_t e = cudaMemcpyAsync(out2, sc->status, 2 * sizeof(int), cudaMemcpyDeviceToHost, stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+  return -(int)e;
 }
 
 }  // extern "C"

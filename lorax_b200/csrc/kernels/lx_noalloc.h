@@ -25,8 +25,9 @@ extern "C" {
 int lx_gemm_bf16_noalloc(const void* x, const void* w, void* out, const void* bias, int T, int N, int K,
                          long long ldx, long long ldw, long long ldo, int split_k, void* stream);
 
-/* Device-side status of the last launch on the current device (synchronising): out2[0] == 0 means ok. */
-int lx_gemm_bf16_noalloc_status(int* out2);
+/* Device-side status of the last launch on the current device: out2[0] == 0 means ok.  The read is queued on `stream`
+ * (a cudaStream_t: the one the GEMM ran on, which may be a non-blocking stream) and the call waits for it. */
+int lx_gemm_bf16_noalloc_status(int* out2, void* stream);
 
 const char* lx_gemm_bf16_noalloc_strerror(int code);
 long long lx_gemm_bf16_noalloc_scratch_bytes(void);

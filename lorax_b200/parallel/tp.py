@@ -108,6 +108,17 @@ class TensorParallel:
         dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
         return float(t.item())
 
+    def broadcast_scalar(self, v: float, src: int = 0) -> float:
+        """Rank `src`'s value on every rank, through a host-side (Gloo) group so that no GPU work is queued or waited for:
+        used for decisions every rank must take alike from a host clock (request arrivals).  Collective on first use."""
+        if self.world_size == 1:
+            return v
+        if getattr(self, "_host_group", None) is None:
+            self._host_group = dist.new_group(backend="gloo")
+        t = torch.tensor([v], dtype=torch.float64)
+        dist.broadcast(t, src=src, group=self._host_group)
+        return float(t[0])
+
     def destroy(self):
         if self.world_size > 1 and dist.is_initialized():
             dist.destroy_process_group()

@@ -54,7 +54,8 @@ class TokenEvent:
     index: int                           # 0-based index of the generated token
     finished: bool
     finish_reason: Optional[int] = None
-    time: float = 0.0
+    time: float = 0.0                    # host clock when the host read the token
+    device_time: float = 0.0             # when the step that produced it completed on the device (same clock)
 
 
 @dataclass
@@ -209,7 +210,7 @@ class Engine:
         self.draining.pop(seq.req.request_id, None)
         self.finished[seq.req.request_id] = seq
 
-    def _emit(self, seq: _Seq, token: int, lp: float, now: float, events: List[TokenEvent]):
+    def _emit(self, seq: _Seq, token: int, lp: float, now: float, events: List[TokenEvent], dev_now: float = 0.0):
         if seq.finished:
             return
         idx = len(seq.output_ids)
@@ -219,7 +220,7 @@ class Engine:
         seq.last_token_time = now
         text = self.decode_text(token) if (self.decode_text and seq.stopping.stop_sequences) else ""
         stop, reason = seq.stopping(token, text)
-        events.append(TokenEvent(seq.req.request_id, token, lp, idx, stop, reason, now))
+        events.append(TokenEvent(seq.req.request_id, token, lp, idx, stop, reason, now, dev_now or now))
         self.stats["generated_tokens"] += 1
         if stop:
             self._finish(seq, reason)
@@ -343,18 +344,19 @@ class Engine:
             kind, k, b, who = self.inflight.popleft()
             ids_p, lps_p = self.runner.wait(k)
             now = time.perf_counter()
+            dev_now = self.runner.ring_time(k)
             ids_h, lps_h = ids_p[:b].tolist(), lps_p[:b].tolist()
             if kind == "first":
                 for i, rid in enumerate(who):
                     seq = self.running.get(rid) or self.draining.get(rid)
                     if seq is not None and not seq.finished:
-                        self._emit(seq, ids_h[i], lps_h[i], now, events)
+                        self._emit(seq, ids_h[i], lps_h[i], now, events, dev_now)
                 continue
             for row, rid in who.items():
                 seq = self.running.get(rid) or self.draining.get(rid)
                 if seq is None or seq.finished:
                     continue
-                self._emit(seq, ids_h[row], lps_h[row], now, events)
+                self._emit(seq, ids_h[row], lps_h[row], now, events, dev_now)
         if self._hist:                                         # histories of requests that no longer decode
             for rid in [k for k in self._hist if k not in self.running]:
                 del self._hist[rid]

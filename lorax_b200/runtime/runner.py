@@ -17,6 +17,7 @@ Design points that differ from the reference runtime (`server/lorax_server/model
 from __future__ import annotations
 
 import math
+import time
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -104,7 +105,17 @@ class ModelRunner:
         pin = dict(pin_memory=True) if self.is_cuda else {}
         self.ring_ids = [torch.zeros(max_batch, dtype=torch.int32, **pin) for _ in range(self.n_ring)]
         self.ring_lp = [torch.zeros(max_batch, dtype=torch.float32, **pin) for _ in range(self.n_ring)]
-        self.ring_ev = [torch.cuda.Event() if self.is_cuda else None for _ in range(self.n_ring)]
+        # the ring events carry device timestamps: a token's time is the completion of its step on the GPU, on the
+        # host's clock through an anchor pair (event, perf_counter) taken at a synchronised moment
+        self.ring_ev = [torch.cuda.Event(enable_timing=True) if self.is_cuda else None for _ in range(self.n_ring)]
+        self.anchor_ev = None
+        self.anchor_host = time.perf_counter()
+        if self.is_cuda:
+            torch.cuda.synchronize(self.device)
+            self.anchor_ev = torch.cuda.Event(enable_timing=True)
+            self.anchor_ev.record()
+            self.anchor_ev.synchronize()
+            self.anchor_host = time.perf_counter()
         self.ring_pos = 0
         self.steps = 0
         self.h2d_bytes = 0
@@ -488,3 +499,9 @@ class ModelRunner:
         if self.is_cuda:
             self.ring_ev[k].synchronize()
         return self.ring_ids[k], self.ring_lp[k]
+
+    def ring_time(self, k: int) -> float:
+        """When ring entry `k` (already waited for) completed on the device, in seconds on the host's perf_counter clock."""
+        if not self.is_cuda:
+            return time.perf_counter()
+        return self.anchor_host + self.anchor_ev.elapsed_time(self.ring_ev[k]) * 1e-3

@@ -133,8 +133,9 @@ class HeterogeneousNextTokenChooser:
             h = history.long().clamp(0, V - 1)
             m = history_mask if history_mask is not None else torch.ones_like(h, dtype=torch.bool)
             if self.any_rep:
-                seen = torch.zeros(B, V, dtype=torch.bool, device=scores.device)
-                seen.scatter_(1, h, m)
+                # padded history slots carry token id 0 with mask False: accumulate instead of overwriting, so that they can
+                # never clear the mark of a real token 0 in the same row
+                seen = torch.zeros(B, V, dtype=torch.int32, device=scores.device).scatter_add_(1, h, m.to(torch.int32)) > 0
                 pen = self.rep[:, None]
                 scores = torch.where(seen, torch.where(scores < 0, scores * pen, scores / pen), scores)
             if self.any_freq:

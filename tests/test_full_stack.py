@@ -336,6 +336,55 @@ def test_chunked_prefill_matches_unchunked(stack):
             proc.kill()
 
 
+def test_prefix_cache_holds_only_tokens_whose_kv_was_written(stack):
+    """A second router with `--prefix-caching`.  A request whose prompt plus generated tokens end exactly on a KV block
+    boundary leaves its last sampled token without keys / values (it was never fed back).  A follow-up prompt that extends
+    that text must not reuse the boundary block: its output has to equal the answer of the router without a prefix cache."""
+    bs = stack["rt"].runner.page
+    words = [f"w{(11 * i) % 500 + 2}" for i in range(2 * bs - 3)]
+    first = {"inputs": " ".join(words), "parameters": {"max_new_tokens": 3, "details": True, "ignore_eos_token": True}}
+    port = _free_port()
+    proc = subprocess.Popen([ROUTER, "--port", str(port), "--hostname", "127.0.0.1", "--master-shard-uds-path", stack["uds"], "--num-shard", "1",
+                             "--max-input-length", "100", "--max-total-tokens", "128", "--max-batch-prefill-tokens", "256",
+                             "--prefix-caching", "true", "--model-id", "tiny", "--adapter-source", "local"],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    try:
+        for _ in range(100):
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1) as r:
+                    if r.status == 200:
+                        break
+            except Exception:
+                time.sleep(0.1)
+        st, body, _ = _post(port, "/generate", first)
+        assert st == 200, body
+        toks = [t["id"] for t in json.loads(body)["details"]["tokens"]]
+        assert len(toks) == 3                                            # prompt + generated = 2 whole blocks
+        follow = {"inputs": " ".join(words + [f"w{t}" for t in toks] + ["w7", "w8", "w9"]),
+                  "parameters": {"max_new_tokens": 6, "details": True, "ignore_eos_token": True}}
+        from lorax_b200.runtime.engine import Engine
+        eng = Engine(stack["model"], EngineConfig(max_total_tokens=128, max_batch_prefill_tokens=256), num_blocks=64, max_batch=4)
+        want = eng.generate([[int(w[1:]) for w in follow["inputs"].split()]], max_new_tokens=6)[0]
+        seen = []
+        inner = stack["rt"]._new_sequences
+
+        def spy(batch):
+            seen.extend(int(r.cache_len) for r in batch.requests)
+            return inner(batch)
+        stack["rt"]._new_sequences = spy
+        st, body, _ = _post(port, "/generate", follow)
+        stack["rt"]._new_sequences = inner
+        assert st == 200, body
+        assert [t["id"] for t in json.loads(body)["details"]["tokens"]] == want
+        assert seen and seen[0] == bs                                    # the first block is reused, the boundary block is not
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=10)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+
+
 def test_merge_adapter_weights_equals_the_adapter_applied_at_run_time(stack):
     """`--merge-adapter-weights`: the adapter folded into the base weights at load time generates what the same adapter applied
     per request generates."""

@@ -97,12 +97,29 @@ def test_merge_strategies():
     ties = merge_tensors([a, b], [1.0, 1.0], "ties", density=1.0)
     # sign election by total mass, then mean of the agreeing entries
     assert ties[0, 1].item() == pytest.approx(-1.5) and ties[1, 1].item() in (3.0, -3.0) and ties[0, 0].item() in (1.0, -1.0)
+    # the sign is elected before the weights are applied: a negative weight flips the contribution, not the election
+    t1, t2 = torch.tensor([2.0, -1.0]), torch.tensor([-1.0, -3.0])
+    got = merge_tensors([t1, t2], [1.0, -2.0], "ties", density=1.0)
+    # position 0: unweighted sum +1 elects "+", only t1 agrees -> 2.0; position 1: both negative -> mean(-1, +6) = 2.5
+    assert got.tolist() == pytest.approx([2.0, 2.5])
     pruned = merge_tensors([a], [1.0], "ties", density=0.34)
     assert (pruned != 0).sum().item() == 2
     torch.manual_seed(0)
     big = torch.ones(1000)
     dare = merge_tensors([big], [1.0], "dare_linear", density=0.5, generator=torch.Generator().manual_seed(0))
     assert 0.8 < dare.mean().item() < 1.2 and set(dare.unique().tolist()) <= {0.0, 2.0}
+
+
+def test_repetition_penalty_reaches_token_zero_in_padded_batches():
+    """Rows with shorter histories are padded with id 0 / mask False; that padding must not hide a real token 0."""
+    from lorax_b200.sampling.chooser import HeterogeneousNextTokenChooser, NextTokenParams
+    ch = HeterogeneousNextTokenChooser([NextTokenParams(repetition_penalty=2.0), NextTokenParams(repetition_penalty=2.0)], "cpu", 8)
+    hist = torch.tensor([[0, 3, 0, 0, 0], [5, 6, 7, 1, 2]])
+    mask = torch.tensor([[True, True, False, False, False], [True] * 5])
+    scores = torch.ones(2, 8)
+    out = ch.warp(hist, mask, scores.clone())
+    assert out[0, 0].item() == 0.5 and out[0, 3].item() == 0.5 and out[0, 1].item() == 1.0
+    assert out[1, 0].item() == 1.0 and out[1, 5].item() == 0.5
 
 
 def test_fp8_block128_quantiser_roundtrip(tmp_path):

@@ -58,6 +58,21 @@ def test_radix_evicts_lru_unreferenced_leaves():
     assert again is None or again.prefix_len == 0
 
 
+def test_radix_split_of_a_referenced_node_keeps_blocks_evictable():
+    """A live allocation points at the deepest node it matched.  When a second request shares only a shorter prefix the
+    node is split; both parts must lose their reference when the requests end, or the blocks are stuck for good."""
+    a = rn.BlockAllocator(num_blocks=9, block_size=4, prefix_caching=True)       # 8 usable blocks
+    prompt = list(range(100, 117))                                               # 17 tokens
+    first = a.allocate(17, prompt=prompt); a.free(first, all_tokens=prompt)      # 4 whole blocks cached
+    x = a.allocate(17, prompt=prompt)                                            # references the 16-token node
+    assert x.prefix_len == 16
+    y = a.allocate(12, prompt=prompt[:8] + [7, 7, 7, 7])                         # shares 8 tokens: splits that node
+    assert y.prefix_len == 8
+    a.free(x, all_tokens=prompt); a.free(y, all_tokens=prompt[:8] + [7, 7, 7, 7])
+    big = a.allocate(32, prompt=[9] * 32)                                        # needs every block: all must be evictable
+    assert big is not None and len(big.blocks) == 8
+
+
 def test_json_parser_roundtrip_and_errors():
     s = '{"a": [1, 2.5, true, null, "x\\n\\u00e9\\ud83d\\ude00"], "b": {"c": -3}}'
     out = json.loads(rn.json_roundtrip(s))

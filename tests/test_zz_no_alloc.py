@@ -24,7 +24,7 @@ def _lib():
     f.restype = ctypes.c_int
     lib.lx_gemm_bf16_noalloc_strerror.argtypes = [ctypes.c_int]
     lib.lx_gemm_bf16_noalloc_strerror.restype = ctypes.c_char_p
-    lib.lx_gemm_bf16_noalloc_status.argtypes = [ctypes.c_void_p]
+    lib.lx_gemm_bf16_noalloc_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
     lib.lx_gemm_bf16_noalloc_status.restype = ctypes.c_int
     lib.lx_gemm_bf16_noalloc_scratch_bytes.restype = ctypes.c_longlong
     return native, lib
@@ -50,7 +50,7 @@ def test_noalloc_matches_regular_entry_twice(T, N, K, split):
         rc = _call(lib, x, w, got, b, split)
         assert rc == 0, lib.lx_gemm_bf16_noalloc_strerror(rc)
         st = (ctypes.c_int * 2)()
-        assert lib.lx_gemm_bf16_noalloc_status(st) == 0 and st[0] == 0, list(st)
+        assert lib.lx_gemm_bf16_noalloc_status(st, torch.cuda.current_stream().cuda_stream) == 0 and st[0] == 0, list(st)
         want = native.gemm(x, w, bias=b, mode=1, force_split=split)
         torch.cuda.synchronize()
         native.workspace().check_status()
@@ -59,6 +59,26 @@ def test_noalloc_matches_regular_entry_twice(T, N, K, split):
         ref = x.float() @ w.float().t() + b.float()
         assert ((got.float() - ref).norm() / ref.norm()).item() < 6e-3
         outs.append(err)
+
+
+def test_noalloc_on_a_non_blocking_stream():
+    """The status read is ordered on the caller's stream, so it is right on streams that do not synchronise with the
+    default stream too."""
+    native, lib = _lib()
+    torch.manual_seed(5)
+    s = torch.cuda.Stream()
+    x = torch.randn(32, 2048, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(1024, 2048, device="cuda", dtype=torch.bfloat16) / math.sqrt(2048)
+    got = torch.empty(32, 1024, device="cuda", dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    with torch.cuda.stream(s):
+        rc = _call(lib, x, w, got, None, 4)
+        assert rc == 0, lib.lx_gemm_bf16_noalloc_strerror(rc)
+        st = (ctypes.c_int * 2)()
+        assert lib.lx_gemm_bf16_noalloc_status(st, s.cuda_stream) == 0 and st[0] == 0, list(st)
+    ref = x.float() @ w.float().t()
+    assert ((got.float() - ref).norm() / ref.norm()).item() < 6e-3
+    assert _call(lib, x[:, :0], w[:, :0], got, None, 0) == -2006            # K = 0 is refused, not launched
 
 
 def test_noalloc_rejects_oversize():
