@@ -302,6 +302,8 @@ def main():
             eng.add_request(r)
             arr["next"] += 1
 
+    ramping = [True]
+
     def harvest(events, record: bool = False):
         n = 0
         for ev in events:
@@ -317,19 +319,21 @@ def main():
                 eng.finished.pop(rid, None)
                 last_tok.pop(rid, None)
                 meta.pop(rid, None)
-                if not poisson:
+                if not poisson or ramping[0]:        # closed loop (and the ramp of either mode): replace at once
                     r = new_request(arrival=time.perf_counter())
                     meta[r.request_id] = r.arrival_time
                     eng.add_request(r)
         return n
 
-    # ---- ramp: fill the batch (not part of warm-up or timing)
+    # ---- ramp: fill the batch with requests that are "mid flight" and keep it full (finished requests are replaced at once)
+    # until every row is taken, so that the timed windows see the steady-state mix of progress (not part of warm-up or timing)
     for _ in range(args.batch):
         eng.add_request(new_request(ramp=True))
     ramp_steps = 0
-    while len(eng.waiting) > 0 and ramp_steps < 400:
+    while (len(eng.waiting) > 0 or len(eng.running) < args.batch - 8) and ramp_steps < 600:
         harvest(eng.step())
         ramp_steps += 1
+    ramping[0] = False
     arr["t0"] = time.perf_counter()
     for _ in range(args.warmup):
         feed(time.perf_counter())

@@ -35,11 +35,9 @@ LM_HEAD = "lm_head"
 
 
 def pad_rank(r: int) -> int:
-    """8 for tiny ranks, otherwise the next multiple of 16 (the reference pads to 8*world_size or a multiple of
-    16, `utils/punica.py:46-76`)."""
-    if r <= 8:
-        return 8
-    return (r + 15) // 16 * 16
+    """The next multiple of 16: one K step of a bf16 tensor-core instruction, so that the LoRA delta can be added by
+    UMMAs inside the base GEMM (the reference pads to 8*world_size or a multiple of 16, `utils/punica.py:46-76`)."""
+    return max(16, (r + 15) // 16 * 16)
 
 
 @dataclass

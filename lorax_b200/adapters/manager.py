@@ -161,8 +161,9 @@ class AdapterManager:
         # staging for slot-table updates (pinned so the H2D is async)
         self._stage_base = torch.zeros(1, dtype=torch.int64).pin_memory() if self.is_cuda else None
         self._stage_rank = torch.zeros(1, dtype=torch.int32).pin_memory() if self.is_cuda else None
-        # per-slot TMA descriptors of the A_cat matrices (one per projection group), read by the tensor-core shrink
-        self.groups_per_slot = len(TMAP_GROUPS)
+        # per-slot TMA descriptors, read by the tensor-core LoRA kernels: for every projection group the A_cat family
+        # {K, nparts * r, layers} at index g and the B_cat family {r, N, layers} at index len(TMAP_GROUPS) + g
+        self.groups_per_slot = 2 * len(TMAP_GROUPS)
         self.slot_tmaps = (torch.zeros(max_slots * self.groups_per_slot * TMAP_BYTES, dtype=torch.uint8, device=self.device)
                            if self.is_cuda else None)
         model.adapters = self
@@ -180,6 +181,8 @@ class AdapterManager:
             base = self.arena.data_ptr() + (off + rp * self.layout.unit_off(gname, 0, "A")) * esize
             layers = 1 if gname == LM_HEAD else self.layout.num_layers
             native.lora_encode_tmap(host[gi_idx * TMAP_BYTES:], base, gi.K, nparts * rp, rp * self.layout.layer_units, layers)
+            base_b = self.arena.data_ptr() + (off + rp * self.layout.unit_off(gname, 0, "B")) * esize
+            native.lora_encode_tmap(host[(len(TMAP_GROUPS) + gi_idx) * TMAP_BYTES:], base_b, rp, gi.N, rp * self.layout.layer_units, layers)
         return host
 
     # ------------------------------------------------------------------ host tier
@@ -316,6 +319,20 @@ class AdapterManager:
         else:
             v = ops.lora_shrink(x, tok_slot, self.arena, self.slot_base, self.slot_rank, offA, nparts, self.max_rank)
         return LoraEpilogue(v, tok_slot, self.arena, self.slot_base, self.slot_rank, offB, n0, n1)
+
+    def fused(self, group: str, layer: int, tiles: Optional[LoraTiles]):
+        """Descriptor of the projection group's LoRA for the GEMM that carries shrink and expand in its own launch
+        (`ops.gemm_lora_fused`); None when the step has no tile table or nothing is resident."""
+        from ..ops.native import LoraFused
+        if not self.is_cuda or self.max_rank == 0 or tiles is None or tiles.num_tiles == 0:
+            return None
+        gi = self.layout.groups.get(group)
+        if gi is None:
+            return None
+        n0, n1 = gi.bounds
+        g = TMAP_GROUPS.index(group)
+        return LoraFused(tiles.table, tiles.num_tiles, tiles.live, self.slot_tmaps, self.groups_per_slot, g, len(TMAP_GROUPS) + g,
+                         self.slot_rank, self.slot_base, len(gi.parts), n0, n1, 0 if group == LM_HEAD else layer, self.max_rank)
 
     def expand(self, ops, epi, y: torch.Tensor, tiles: Optional[LoraTiles] = None):
         """y += v B_cat(slot(t))^T: the second half of the LoRA delta as its own launch (`epi` comes from `shrink`)."""

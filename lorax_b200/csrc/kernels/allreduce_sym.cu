@@ -34,6 +34,7 @@ struct ArSymParams {
   int rank, world;
   long long n_vec;                      // 16-byte vectors to reduce (tokens * hidden / 8)
   int* status;
+  unsigned long long budget_ns;         // how long a block waits for a peer's flag before it gives up
 };
 
 // One flag per (stage, block, source rank), written with a release store by the source and polled with acquire loads by the
@@ -44,7 +45,7 @@ LX_DEVICE int ars_peek(const int* p) {
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-LX_DEVICE bool ars_wait(const int* p, int value, int* status, int where) {
+LX_DEVICE bool ars_wait(const int* p, int value, int* status, int where, unsigned long long budget_ns) {
   uint64_t t0 = 0;
   uint32_t polls = 0;
   while (true) {
@@ -52,7 +53,7 @@ LX_DEVICE bool ars_wait(const int* p, int value, int* status, int where) {
     if ((++polls & 1023u) == 0) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitBudgetNs) { report_status(status, kTimeoutPeerFlag, where); return false; }
+      else if (now - t0 > budget_ns) { report_status(status, kTimeoutPeerFlag, where); return false; }
     }
   }
 }
@@ -75,7 +76,7 @@ LX_DEVICE bool ars_barrier(const ArSymParams& p, int stage, int b, int value, in
   if ((int)threadIdx.x < p.world) {
     const int r = threadIdx.x;
     ars_post(ars_flag(p.peers[r], p.cnt_off, stage, b, p.rank), value);
-    if (!ars_wait(ars_flag(p.peers[p.rank], p.cnt_off, stage, b, r), value, p.status, 4000 + 1000 * stage + b)) *ok_flag = 0;
+    if (!ars_wait(ars_flag(p.peers[p.rank], p.cnt_off, stage, b, r), value, p.status, 4000 + 1000 * stage + b, p.budget_ns)) *ok_flag = 0;
   }
   __syncthreads();
   return *ok_flag != 0;
@@ -142,6 +143,11 @@ extern "C" {
 
 int lx_allreduce_sym_blocks() { return lx::kArsBlocks; }
 
+// How long the kernels that wait for another GPU (this all-reduce, the GEMM + all-reduce) poll a peer's flag before they set
+// the status word and return.  Applies to launches made after the call; 0 restores the default of two seconds.
+void lx_set_wait_budget_ns(unsigned long long ns) { lx::host_wait_budget_ns() = ns ? ns : lx::kWaitBudgetNs; }
+unsigned long long lx_get_wait_budget_ns() { return lx::host_wait_budget_ns(); }
+
 // Bytes of the flag area (2 stages x blocks x 8 ranks ints) a rank must zero once before the first launch.
 int lx_allreduce_sym_counter_bytes() { return 2 * lx::kArsBlocks * lx::kArsMaxRanks * 4; }
 
@@ -157,6 +163,7 @@ int lx_allreduce_sym(const unsigned long long* peer_ptrs, int rank, int world, l
   p.in_off = in_off; p.out_off = out_off; p.cnt_off = cnt_off;
   p.epoch = state; p.done = state + 1;
   p.rank = rank; p.world = world; p.n_vec = n_elems / 8; p.status = status;
+  p.budget_ns = host_wait_budget_ns();
   // all blocks of all ranks wait on one another: 64 blocks of 512 threads are always co-resident on a B200
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (world == 2) allreduce_sym_kernel<2><<<kArsBlocks, kArsThreads, 0, s>>>(p);

@@ -45,6 +45,13 @@ LX_DEVICE uint64_t global_timer_ns() {
 
 // Spin budget for any single wait: 2 s of wall clock, checked every 2048 polls.
 constexpr uint64_t kWaitBudgetNs = 2000ull * 1000ull * 1000ull;
+// The kernels that wait for another GPU take their budget as a launch parameter instead, read from this process-wide
+// setting (lx_set_wait_budget_ns): a failure-detection test, or a deployment that wants to give up on a dead peer sooner,
+// shortens it.
+inline unsigned long long& host_wait_budget_ns() {
+  static unsigned long long v = kWaitBudgetNs;
+  return v;
+}
 
 LX_DEVICE uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 

@@ -67,6 +67,7 @@ struct ArParams {
   const __nv_bfloat16* addend;         // optional [T, lda] local partial to add before the reduction
   long long lda;
   int* status;
+  unsigned long long budget_ns;        // how long a wait for another GPU lasts before the kernel gives up
 };
 
 LX_DEVICE int ld_acquire_sys(const int* p) {
@@ -84,7 +85,7 @@ LX_DEVICE int ld_relaxed_sys(const int* p) {
   return v;
 }
 // Polls with relaxed loads and pays for one acquire fence when the value has arrived.
-LX_DEVICE bool wait_counter(const int* p, int target, int* status, int where) {
+LX_DEVICE bool wait_counter(const int* p, int target, int* status, int where, unsigned long long budget_ns) {
   uint64_t t0 = 0;
   uint32_t polls = 0;
   while (true) {
@@ -95,7 +96,7 @@ LX_DEVICE bool wait_counter(const int* p, int target, int* status, int where) {
     if ((++polls & 1023u) == 0) {
       const uint64_t now = global_timer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitBudgetNs) { report_status(status, kTimeoutPeerFlag, where); return false; }
+      else if (now - t0 > budget_ns) { report_status(status, kTimeoutPeerFlag, where); return false; }
     }
   }
 }
@@ -268,7 +269,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
       const int t_local = it / n_chunks, chunk = it % n_chunks;
       const int t = p.oneshot ? t_local : t_local * p.world + p.rank;
       if (et == 0) {
-        if (!wait_counter(arrived + t, targets[t] + p.world * per_tile, p.status, 1000 + t)) *abort_flag = 1;
+        if (!wait_counter(arrived + t, targets[t] + p.world * per_tile, p.status, 1000 + t, p.budget_ns)) *abort_flag = 1;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (*abort_flag) { ok = false; break; }
@@ -307,7 +308,7 @@ gemm_allreduce_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_c
     }
     // ---- phase C: my whole output has been written by its owners (not needed when every rank reduced for itself)
     if (et == 0 && ok && !p.oneshot) {
-      if (!wait_counter(ctrl, targets[p.lay.tiles_max] + num_tiles * n_chunks, p.status, 2000)) *abort_flag = 1;
+      if (!wait_counter(ctrl, targets[p.lay.tiles_max] + num_tiles * n_chunks, p.status, 2000, p.budget_ns)) *abort_flag = 1;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
   }
@@ -350,6 +351,7 @@ struct ArgmaxTpParams {
   int* ids;
   float* logprobs;
   int* status;
+  unsigned long long budget_ns;        // how long a wait for another GPU lasts before the kernel gives up
 };
 
 __global__ void __launch_bounds__(512) argmax_tp_kernel(const ArgmaxTpParams p) {
@@ -393,7 +395,7 @@ __global__ void __launch_bounds__(512) argmax_tp_kernel(const ArgmaxTpParams p) 
     __threadfence_system();
     for (int r = 0; r < p.world; ++r) red_release_sys_add(reinterpret_cast<int*>(p.peers[r] + p.ctrl_off) + 3, 1);
     // all rows of all ranks: world * T arrivals per launch
-    if (wait_counter(ctrl + 3, *target + p.world * p.T, p.status, 3000 + t)) {
+    if (wait_counter(ctrl + 3, *target + p.world * p.T, p.status, 3000 + t, p.budget_ns)) {
       const float4* c = reinterpret_cast<const float4*>(local + p.cand_off);
       float gb = -INFINITY, gm = -INFINITY, gs = 0.f;
       int gi = 0x7fffffff;
@@ -509,6 +511,7 @@ int lx_gemm_allreduce(const void* x, long long ldx, const void* w, long long ldw
   p.addend = reinterpret_cast<const __nv_bfloat16*>(addend);
   p.lda = lda;
   p.status = status;
+  p.budget_ns = host_wait_budget_ns();
   // token tile: the whole batch when it is small, otherwise 64-token tiles so that phase A spreads over the machine
   // (N / 128 feature tiles alone would occupy a quarter of the SMs)
   const int bn = T <= 16 ? 16 : T <= 32 ? 32 : 64;
@@ -548,6 +551,7 @@ int lx_argmax_tp(const void* logits, long long ld, int T, int V_local, int vocab
   p.rank = rank; p.world = world; p.max_rows = max_rows;
   p.logits = reinterpret_cast<const __nv_bfloat16*>(logits); p.ld = ld; p.T = T; p.V_local = V_local; p.vocab_start = vocab_start;
   p.ids = ids; p.logprobs = logprobs; p.status = status;
+  p.budget_ns = host_wait_budget_ns();
   argmax_tp_kernel<<<T, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);     // T <= 512 rows: all CTAs co-resident
   return -(int)cudaGetLastError();
 }

@@ -12,6 +12,15 @@
 //     HBM exactly once.  Small grids are widened with split-K; the last CTA to finish a tile reduces the
 //     fp32 partials in a fixed order (deterministic) and writes bf16.
 //
+// Multi-adapter LoRA rides in the same launch (template flag LORA, weights on the M side).  The reference runs a
+// shrink kernel, the base GEMM and an expand kernel per projection and rank group
+// (server/lorax_server/utils/layers.py:114-164); here a CTA first works through "shrink items" -- for one run of rows of
+// one adapter, v = x A_cat^T on the tensor cores, stored as a bf16 image already in the shared-memory layout of a UMMA
+// operand -- and then through the base tiles, where after the K loop the delta is added by further UMMAs
+// (B_cat tile of the adapter x that image, K = rank) straight into the TMEM accumulator.  The epilogue is unchanged.
+// Base tiles wait for the images they need on per-item flags; every CTA finishes its shrink items before its first
+// base tile, so those waits cannot deadlock, and they are bounded like every other wait.
+//
 // Structure: persistent CTAs of 6 warps.  Warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and
 // TMEM owner, warps 2..5 = epilogue (each warp reads its own 32-lane TMEM quadrant with tcgen05.ld).  A STAGES
 // deep smem ring is guarded by full/empty mbarriers; the accumulator is double buffered in TMEM so the epilogue
@@ -24,6 +33,8 @@ constexpr int kBM = 128;   // UMMA M (rows of operand A per tile)
 constexpr int kBK = 64;    // K per pipeline stage: 64 bf16 = one 128-byte swizzle row
 constexpr int kGemmThreads = 192;
 constexpr int lx_gemm_max_tiles_const = 8192;
+
+struct LoraTileG { int slot, row0, nrows, pad; };
 
 struct GemmParams {
   int a_rows, b_rows, K;
@@ -45,139 +56,100 @@ struct GemmParams {
   // filled wave costs its share of a wave instead of a whole one.  dp_tiles == all tiles switches it off.
   int dp_tiles;
   int sk_ctas;
-  // Multi-adapter LoRA delta added in the epilogue (lora_v == nullptr: none):
-  //   out[t, n] += sum_j lora_v[t, part(n) * r + j] * B_cat(slot(t))[n, j],   r = slot_rank[slot(t)]
-  // lora_v is the shrink result x A^T (fp32), B_cat [N, r] sits in the adapter arena at
-  // slot_base[slot] + r * lora_unit_off and already carries the alpha / r scaling.
-  const float* lora_v;
-  int lora_ldv;
-  const int* lora_tok_slot;            // [tokens] adapter slot per token, -1 = none
-  const __nv_bfloat16* lora_arena;
-  const long long* lora_slot_base;
+  // Multi-adapter LoRA in the same launch (LORA kernels only; lora_tiles == nullptr otherwise).  Rows of the step are grouped
+  // by adapter: the table holds (slot, first row, rows <= 32, -) entries, live ones first, then entries with slot < 0.
+  const LoraTileG* lora_tiles;
+  int lora_num_tiles;
+  const CUtensorMap* lora_slot_tmaps;  // [num_slots][maps_per_slot]: {K, nparts * r, layers} of A_cat and {r, N, layers} of B_cat
+  int lora_maps_per_slot, lora_map_a, lora_map_b;
   const int* lora_slot_rank;
+  const long long* lora_slot_base;
   int lora_num_slots;
-  long long lora_unit_off;
-  int lora_n0, lora_n1;                // part boundaries along the feature dimension (q | k | v, gate | up)
-  int tokens_on_a;                     // 1: tile rows are tokens (activations are operand A), 0: tile rows are features
+  int lora_nparts, lora_n0, lora_n1;   // parts of the fused projection (q | k | v, gate | up) and their boundaries (multiples of 128)
+  int lora_layer;
+  __nv_bfloat16* lora_vimg;            // [tile][part][48 rows][64] bf16: v as a K-major, 128-byte-swizzled UMMA operand image
+  float* lora_vpart;                   // [ksplit][tile * chunks][48][128] fp32 partials of the K splits (ksplit > 1)
+  int lora_ksplit, lora_chunks;        // K splits of a shrink item; 128-row chunks of A_cat (nparts * max rank / 128, rounded up)
+  int* lora_flags;                     // [tile * chunks] generation in which the image chunk was completed
+  int* lora_counters;                  // [tile * chunks] arrivals of the K splits, zero between launches
+  int* lora_gen;                       // [2] generation of the last finished launch, CTAs of this launch that have finished
+  int lora_T;                          // rows of the step
 };
 
-// ---- LoRA epilogue ------------------------------------------------------------------------------------------
-// The delta is added to NC accumulator columns at a time, rank in slices of 8 (16 bytes of B, two float4 of v).
-// Every load address is computed without a branch (dead lanes read a valid dummy address and multiply by zero), so
-// the loads of all NC columns are independent and the compiler can keep many in flight: the epilogue warps have no
-// other warps to hide memory latency behind.
-LX_DEVICE float lora_dot8(const uint4 b, const float4 v0, const float4 v1) {
-  const float2 b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y), b2 = unpack_bf16x2(b.z), b3 = unpack_bf16x2(b.w);
-  float acc = v0.x * b0.x;
-  acc = fmaf(v0.y, b0.y, acc); acc = fmaf(v0.z, b1.x, acc); acc = fmaf(v0.w, b1.y, acc);
-  acc = fmaf(v1.x, b2.x, acc); acc = fmaf(v1.y, b2.y, acc); acc = fmaf(v1.z, b3.x, acc); acc = fmaf(v1.w, b3.y, acc);
-  return acc;
+// ---- LoRA items ----------------------------------------------------------------------------------------------
+constexpr int kLoraWin = 48;            // a run of <= 32 rows lies inside a 16-aligned window of at most 48 rows
+constexpr int kLoraImgElems = kLoraWin * 64;
+
+LX_DEVICE int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+LX_DEVICE void st_release_gpu(int* p, int v) { asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+LX_DEVICE void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded wait for *flag == want.  False when the budget ran out.
+LX_DEVICE bool wait_flag(const int* flag, int want, volatile int* abort_flag) {
+  uint64_t t0 = 0;
+  uint32_t polls = 0;
+  while (ld_acquire_gpu(flag) != want) {
+    if ((++polls & 255u) == 0) {
+      if (abort_flag != nullptr && *abort_flag != 0) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitBudgetNs) return false;
+    }
+  }
+  return true;
 }
 
-// Adapter of one token, resolved once: rank (0 = no adapter), where its B_cat of this projection group starts, its v row.
-struct LoraTok {
-  int r;
-  const __nv_bfloat16* b;
-  const float* v;
+// One shrink item: k-blocks [kb0, kb1) of chunk `chunk` (128 rows of A_cat) of table entry `lt`.
+struct ShrinkItem {
+  int lt, chunk, split, slot, row0, nrows, r, R, box_rows, w0, wn, kb0, kb1;
 };
-LX_DEVICE LoraTok lora_token(const GemmParams& p, int t, int num_tokens) {
-  LoraTok k{0, p.lora_arena, p.lora_v};
-  if (t < num_tokens) {
-    const int s = p.lora_tok_slot[t];
-    if (s >= 0 && s < p.lora_num_slots) {
-      const int r = p.lora_slot_rank[s];
-      const long long base = p.lora_slot_base[s];
-      if (r > 0 && base >= 0) {
-        k.r = r;
-        k.b = p.lora_arena + base + (long long)r * p.lora_unit_off;
-        k.v = p.lora_v + (long long)t * p.lora_ldv;
-      }
-    }
-  }
-  return k;
+LX_DEVICE bool decode_shrink_item(const GemmParams& p, int idx, int kblocks, ShrinkItem& it) {
+  const int per_tile = p.lora_chunks * p.lora_ksplit;
+  it.lt = idx / per_tile;
+  const int rem = idx - it.lt * per_tile;
+  it.chunk = rem / p.lora_ksplit;
+  it.split = rem - it.chunk * p.lora_ksplit;
+  const LoraTileG t = p.lora_tiles[it.lt];
+  it.slot = t.slot; it.row0 = t.row0;
+  it.nrows = min(min(t.nrows, 32), p.lora_T - t.row0);
+  if (t.slot < 0 || t.slot >= p.lora_num_slots || it.nrows <= 0 || t.row0 < 0) return false;
+  it.r = p.lora_slot_rank[t.slot];
+  if (it.r <= 0 || it.r > 64 || (it.r & 15) != 0 || p.lora_slot_base[t.slot] < 0) return false;
+  it.R = it.r * p.lora_nparts;
+  if (it.chunk * kBM >= it.R) return false;
+  it.box_rows = min(kBM, (it.R + 15) / 16 * 16);       // must match the encoder of the A_cat maps
+  it.w0 = t.row0 & ~15;
+  it.wn = ((t.row0 + it.nrows + 15) & ~15) - it.w0;    // 16, 32 or 48
+  it.kb0 = (int)((long long)kblocks * it.split / p.lora_ksplit);
+  it.kb1 = (int)((long long)kblocks * (it.split + 1) / p.lora_ksplit);
+  return it.kb1 > it.kb0;
 }
 
-// acc[q] += delta(feature row i, token column j + q) for q < NC (weights-on-A orientation, NC <= 32).
-// Lane q of the warp resolves token j + q and copies that token's slice of the shrink result into the warp's
-// staging area, 16 ranks at a time; every lane then reads it back as broadcasts while its own B row (32 bytes per
-// 16 ranks) comes straight from the arena, eight columns' loads issued before the first is used.
-template <int NC>
-LX_DEVICE void lora_add_token_columns(const GemmParams& p, float (&acc)[NC], int i, int j, int jend, float* stage) {
-  const int lane = threadIdx.x & 31;
-  const LoraTok tok = lora_token(p, j + lane, (lane < NC) ? jend : 0);
-  const int rmax = __reduce_max_sync(0xffffffffu, tok.r);
-  if (rmax == 0) return;
-  const int part = i < p.lora_n0 ? 0 : (i < p.lora_n1 ? 1 : 2);
-  const int part0 = __shfl_sync(0xffffffffu, part, 0);
-  const bool part_uniform = __all_sync(0xffffffffu, part == part0);
-  const bool row_ok = i < p.a_rows;
-  constexpr int NB = NC < 8 ? NC : 8;
-  for (int jc = 0; jc < rmax; jc += 16) {
-    if (part_uniform) {
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (jc + 4 * h < tok.r) z = __ldg(reinterpret_cast<const float4*>(tok.v + part0 * tok.r + jc + 4 * h));
-        *reinterpret_cast<float4*>(stage + lane * 16 + 4 * h) = z;
-      }
-      __syncwarp();
-    }
-#pragma unroll
-    for (int q0 = 0; q0 < NC; q0 += NB) {
-      uint4 b0[NB], b1[NB];
-      int rq[NB];
-#pragma unroll
-      for (int u = 0; u < NB; ++u) {
-        rq[u] = __shfl_sync(0xffffffffu, tok.r, q0 + u);
-        const __nv_bfloat16* bq = reinterpret_cast<const __nv_bfloat16*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(tok.b), q0 + u));
-        const __nv_bfloat16* row = bq + (long long)i * rq[u] + jc;
-        b0[u] = __ldg(reinterpret_cast<const uint4*>((row_ok && jc < rq[u]) ? row : p.lora_arena));
-        b1[u] = __ldg(reinterpret_cast<const uint4*>((row_ok && jc + 8 < rq[u]) ? row + 8 : p.lora_arena));
-      }
-#pragma unroll
-      for (int u = 0; u < NB; ++u) {
-        float4 v0, v1, v2, v3;
-        if (part_uniform) {
-          const float4* sv = reinterpret_cast<const float4*>(stage + (q0 + u) * 16);
-          v0 = sv[0]; v1 = sv[1]; v2 = sv[2]; v3 = sv[3];
-        } else {                  // a part boundary inside the warp's 32 features: every lane reads its own part
-          const float* vq = reinterpret_cast<const float*>(__shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(tok.v), q0 + u));
-          const float* vp = vq + part * rq[u] + jc;
-          const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
-          v0 = jc < rq[u] ? __ldg(reinterpret_cast<const float4*>(vp)) : zero;
-          v1 = jc + 4 < rq[u] ? __ldg(reinterpret_cast<const float4*>(vp + 4)) : zero;
-          v2 = jc + 8 < rq[u] ? __ldg(reinterpret_cast<const float4*>(vp + 8)) : zero;
-          v3 = jc + 12 < rq[u] ? __ldg(reinterpret_cast<const float4*>(vp + 12)) : zero;
-        }
-        const float d0 = (row_ok && jc < rq[u]) ? lora_dot8(b0[u], v0, v1) : 0.f;
-        const float d1 = (row_ok && jc + 8 < rq[u]) ? lora_dot8(b1[u], v2, v3) : 0.f;
-        acc[q0 + u] += d0 + d1;
-      }
-    }
-    __syncwarp();
-  }
-}
-
-// acc[q] += delta(token row i, feature column j + q) for q < NC (tokens-on-A orientation): the thread's token is
-// fixed, its B rows change with the column.  Plain loads; the serving paths use the other orientation.
-template <int NC>
-LX_DEVICE void lora_add_feature_columns(const GemmParams& p, float (&acc)[NC], int j, int jend, const LoraTok& mine) {
-  const int rmax = __reduce_max_sync(0xffffffffu, mine.r);
-  for (int jc = 0; jc < rmax; jc += 8) {
-    const bool live_row = jc < mine.r;
-#pragma unroll
-    for (int q = 0; q < NC; ++q) {
-      const int n = j + q;
-      const bool live = live_row && n < jend;
-      const int part = n < p.lora_n0 ? 0 : (n < p.lora_n1 ? 1 : 2);
-      const __nv_bfloat16* bp = live ? mine.b + (long long)n * mine.r + jc : p.lora_arena;
-      const float* vp = live ? mine.v + part * mine.r + jc : p.lora_v;
-      const uint4 b = __ldg(reinterpret_cast<const uint4*>(bp));
-      const float4 v0 = __ldg(reinterpret_cast<const float4*>(vp));
-      const float4 v1 = __ldg(reinterpret_cast<const float4*>(vp + 4));
-      acc[q] += live ? lora_dot8(b, v0, v1) : 0.f;
-    }
-  }
+// The part of table entry `lt` that adds to accumulator columns [c0, c1) of the token tile whose rows are [j0, jlim).
+struct ExpandItem {
+  int slot, r, w0, c0, c1, chunk_lo, chunk_hi;
+};
+// -1: end of the live entries, 0: nothing to add for this entry, 1: `e` is valid.
+LX_DEVICE int decode_expand_item(const GemmParams& p, int lt, int part, int j0, int jlim, ExpandItem& e) {
+  const LoraTileG t = p.lora_tiles[lt];
+  if (t.slot < 0) return -1;
+  const int nrows = min(min(t.nrows, 32), p.lora_T - t.row0);
+  if (t.slot >= p.lora_num_slots || nrows <= 0 || t.row0 < 0) return 0;
+  e.slot = t.slot;
+  e.r = p.lora_slot_rank[t.slot];
+  if (e.r <= 0 || e.r > 64 || (e.r & 15) != 0 || p.lora_slot_base[t.slot] < 0) return 0;
+  e.w0 = t.row0 & ~15;
+  const int w1 = (t.row0 + nrows + 15) & ~15;
+  e.c0 = max(e.w0, j0);
+  e.c1 = min(w1, jlim);
+  if (e.c0 >= e.c1) return 0;
+  e.chunk_lo = (part * e.r) / kBM;
+  e.chunk_hi = ((part + 1) * e.r - 1) / kBM;
+  return 1;
 }
 
 // One unit of work of a CTA: k-blocks [kb0, kb1) of one output tile.  nparts == 0: the CTA owns the whole tile and
@@ -255,22 +227,30 @@ struct GemmWorkIter {
   }
 };
 
-template <int BN, int STAGES>
+// x through boxes of 16, 32 and 48 rows: a shrink item loads only the 16-aligned window its rows lie in.
+struct LoraXMaps { CUtensorMap m[3]; };
+
+LX_DEVICE void tensormap_fence_acquire_g(const CUtensorMap* m) {
+  asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+
+template <int BN, int STAGES, bool LORA>
 struct GemmSmem {
+  static constexpr int kBRows = (LORA && BN < 64) ? 64 : BN;      // a LoRA stage holds a 48-row image in the B region
+  static constexpr int kAcc = kBRows;                             // TMEM columns per accumulator (a shrink item needs 48)
   static constexpr int kABytes = kBM * kBK * 2;
-  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kLoraBytes = 4 * 32 * 16 * 4;   // per epilogue warp: 32 tokens x 16 ranks of the shrink result
-  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + kLoraBytes + 1024;  // +1024 for manual alignment
+  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // +1024 for manual alignment
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool LORA>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const GemmParams p) {
+                         const __grid_constant__ LoraXMaps xmaps, const GemmParams p) {
   pdl_trigger();
-  using S = GemmSmem<BN, STAGES>;
+  using S = GemmSmem<BN, STAGES, LORA>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
@@ -281,16 +261,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_base_slot + 2));
-  float* lora_stage_all = reinterpret_cast<float*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr uint32_t kTmemCols = (2 * BN < 32) ? 32 : 2 * BN;
+  constexpr uint32_t kTmemCols = (2 * S::kAcc < 32) ? 32 : 2 * S::kAcc;
 
   const int tiles_a = (p.a_rows + kBM - 1) / kBM;
   const int tiles_b = (p.b_rows + p.bn - 1) / p.bn;
   const int num_tiles = tiles_a * tiles_b;
   const int kblocks = (p.K + kBK - 1) / kBK;
+  const bool lora = LORA && p.lora_tiles != nullptr;
+  const int n_shrink = lora ? p.lora_num_tiles * p.lora_chunks * p.lora_ksplit : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -316,6 +297,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   pdl_wait();      // barriers, TMEM and descriptors are set up while the previous kernel drains; its data is read from here on
+  // Flags of this launch carry generation + 1; the generation only moves when the last CTA of a launch has finished.
+  const int want = lora ? ld_acquire_gpu(p.lora_gen) + 1 : 0;
 
   // Work item w -> (tile, split).  Tiles are ordered with the A tile index fastest inside one B tile so that
   // CTAs running at the same time share the B operand through L2.
@@ -326,6 +309,29 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      if constexpr (LORA) {
+        for (int idx = (int)blockIdx.x; ok && idx < n_shrink; idx += (int)gridDim.x) {
+          ShrinkItem it;
+          if (!decode_shrink_item(p, idx, kblocks, it)) continue;
+          const CUtensorMap* ma = p.lora_slot_tmaps + (long long)it.slot * p.lora_maps_per_slot + p.lora_map_a;
+          tensormap_fence_acquire_g(ma);
+          const CUtensorMap* mx = &xmaps.m[it.wn / 16 - 1];
+          const uint32_t bytes = (uint32_t)((it.box_rows + it.wn) * kBK * 2);
+          for (int kb = it.kb0; kb < it.kb1; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+              report_status(p.status, kTimeoutEmptyBarrier, -1 - idx);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            uint8_t* sa = tiles + stage * S::kStageBytes;
+            mbar_expect_tx(&full_bar[stage], bytes);
+            tma_load_3d(sa, ma, &full_bar[stage], kb * kBK, it.chunk * kBM, p.lora_layer);
+            tma_load_2d_hint(sa + S::kABytes, mx, &full_bar[stage], kb * kBK, it.w0, pol_b);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+        }
+      }
       GemmWorkIter<BN> it(p, num_tiles, kblocks);
       GemmWork w;
       while (ok && it.next(w)) {
@@ -345,6 +351,44 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           tma_load_2d_hint(sb, &tmap_b, &full_bar[stage], kb * kBK, tb * p.bn, pol_b);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
+        if constexpr (LORA) {
+          if (ok && lora && w.kb0 == 0) {
+            // the LoRA delta of this tile: one stage per table entry whose rows meet the token tile
+            const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
+            const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
+            for (int lt = 0; ok && lt < p.lora_num_tiles; ++lt) {
+              ExpandItem e;
+              const int rc = decode_expand_item(p, lt, part, j0, jlim, e);
+              if (rc < 0) break;
+              if (rc == 0) continue;
+              for (int ch = e.chunk_lo; ch <= e.chunk_hi; ++ch) {
+                if (!wait_flag(&p.lora_flags[lt * p.lora_chunks + ch], want, abort_flag)) {
+                  report_status(p.status, kTimeoutSplitK, lt);
+                  *abort_flag = 1;
+                  ok = false;
+                  break;
+                }
+              }
+              if (!ok) break;
+              fence_proxy_async_all();       // the image was written with ordinary stores; the bulk copy reads it
+              if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+                report_status(p.status, kTimeoutEmptyBarrier, w.tile);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+              uint8_t* sa = tiles + stage * S::kStageBytes;
+              const CUtensorMap* mb = p.lora_slot_tmaps + (long long)e.slot * p.lora_maps_per_slot + p.lora_map_b;
+              tensormap_fence_acquire_g(mb);
+              const uint32_t vbytes = (uint32_t)((e.c1 - e.c0) * kBK * 2);
+              mbar_expect_tx(&full_bar[stage], (uint32_t)S::kABytes + vbytes);
+              tma_load_3d(sa, mb, &full_bar[stage], 0, i0, p.lora_layer);
+              bulk_load_1d(sa + S::kABytes, p.lora_vimg + ((long long)(lt * p.lora_nparts + part) * kLoraWin + (e.c0 - e.w0)) * 64, vbytes,
+                           &full_bar[stage]);
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+          }
+        }
       }
     }
     __syncwarp();
@@ -356,6 +400,43 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       int acc = 0;
       uint32_t acc_phase[2] = {0, 0};
       bool ok = true;
+      if constexpr (LORA) {
+        for (int idx = (int)blockIdx.x; ok && idx < n_shrink; idx += (int)gridDim.x) {
+          ShrinkItem it;
+          if (!decode_shrink_item(p, idx, kblocks, it)) continue;
+          if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1, abort_flag)) {
+            report_status(p.status, kTimeoutTmemEmpty, -1 - idx);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t tmem_d = tmem_base + (uint32_t)(acc * S::kAcc);
+          const uint32_t idesc_s = make_idesc(kBM, (uint32_t)it.wn, kFmtBF16, kFmtBF16);
+          for (int kb = it.kb0; kb < it.kb1; ++kb) {
+            if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+              report_status(p.status, kTimeoutFullBarrier, -1 - idx);
+              *abort_flag = 1;
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
+            const uint64_t da = make_desc_k_sw128(sa);
+            const uint64_t db = make_desc_k_sw128(sa + S::kABytes);
+#pragma unroll
+            for (int k = 0; k < kBK / 16; ++k) {
+              umma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb > it.kb0 || k > 0) ? 1u : 0u);
+            }
+            tc_commit(&empty_bar[stage]);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          }
+          if (!ok) break;
+          tc_commit(&tmem_full[acc]);
+          acc_phase[acc] ^= 1;
+          acc ^= 1;
+        }
+      }
       GemmWorkIter<BN> it(p, num_tiles, kblocks);
       GemmWork w;
       while (ok && it.next(w)) {
@@ -366,7 +447,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           break;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * S::kAcc);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
             report_status(p.status, kTimeoutFullBarrier, w.tile);
@@ -386,6 +467,37 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
+        if constexpr (LORA) {
+          if (lora && kb0 == 0) {
+            const int ta = p.b_fastest ? w.tile / tiles_b : w.tile % tiles_a;
+            const int tb = p.b_fastest ? w.tile % tiles_b : w.tile / tiles_a;
+            const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
+            const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
+            for (int lt = 0; ok && lt < p.lora_num_tiles; ++lt) {
+              ExpandItem e;
+              const int rc = decode_expand_item(p, lt, part, j0, jlim, e);
+              if (rc < 0) break;
+              if (rc == 0) continue;
+              if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+                report_status(p.status, kTimeoutFullBarrier, w.tile);
+                *abort_flag = 1;
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
+              const uint64_t da = make_desc_k_sw128(sa);
+              const uint64_t db = make_desc_k_sw128(sa + S::kABytes);
+              const uint32_t idesc_e = make_idesc(kBM, (uint32_t)(e.c1 - e.c0), kFmtBF16, kFmtBF16);
+              for (int k = 0; k < e.r / 16; ++k) {
+                umma_f16_ss(tmem_d + (uint32_t)(e.c0 - j0), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_e, 1u);
+              }
+              tc_commit(&empty_bar[stage]);
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) break;
+          }
+        }
         tc_commit(&tmem_full[acc]);       // accumulator complete
         acc_phase[acc] ^= 1;
         acc ^= 1;
@@ -398,9 +510,94 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int row_in_tile = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
+    bool alive = true;
+    if constexpr (LORA) {
+      const int n_ids = p.lora_num_tiles * p.lora_chunks;
+      for (int idx = (int)blockIdx.x; alive && idx < n_shrink; idx += (int)gridDim.x) {
+        ShrinkItem it;
+        if (!decode_shrink_item(p, idx, kblocks, it)) continue;
+        if (!mbar_wait(&tmem_full[acc], acc_phase[acc], abort_flag)) {
+          report_status(p.status, kTimeoutTmemFull, -1 - idx);
+          *abort_flag = 1;
+          alive = false;
+          break;
+        }
+        tc_fence_after();
+        acc_phase[acc] ^= 1;
+        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * S::kAcc);
+        float v[kLoraWin];
+        {
+          uint32_t ra[32], rb[16];
+          tmem_ld_32x32b_x32(taddr, ra);
+          tmem_ld_32x32b_x16(taddr + 32, rb);     // columns 32..47: defined only when the window is 48 wide, masked below
+          tc_wait_ld();
+#pragma unroll
+          for (int q = 0; q < 32; ++q) v[q] = __uint_as_float(ra[q]);
+#pragma unroll
+          for (int q = 0; q < 16; ++q) v[32 + q] = __uint_as_float(rb[q]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+        acc ^= 1;
+        const int item_id = it.lt * p.lora_chunks + it.chunk;
+        bool writer = true;
+        if (p.lora_ksplit > 1) {
+          // park the partial [column][128 rows]; the last split to arrive adds them up in split order
+          float* __restrict__ mine = p.lora_vpart + ((long long)it.split * n_ids + item_id) * (kLoraWin * kBM) + row_in_tile;
+#pragma unroll
+          for (int c = 0; c < kLoraWin; ++c) {
+            if (c < it.wn) __stcg(mine + c * kBM, v[c]);
+          }
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 64) {
+            const int prev = atomicAdd(&p.lora_counters[item_id], 1);
+            *last_flag = (prev == p.lora_ksplit - 1) ? 1 : 0;
+            if (prev == p.lora_ksplit - 1) p.lora_counters[item_id] = 0;
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          writer = (*last_flag != 0);
+          if (writer) {
+            __threadfence();
+#pragma unroll
+            for (int c = 0; c < kLoraWin; ++c) v[c] = 0.f;
+            for (int sp = 0; sp < p.lora_ksplit; ++sp) {
+              const float* __restrict__ src = p.lora_vpart + ((long long)sp * n_ids + item_id) * (kLoraWin * kBM) + row_in_tile;
+#pragma unroll
+              for (int c = 0; c < kLoraWin; ++c) {
+                if (c < it.wn) v[c] += __ldcg(src + c * kBM);
+              }
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");      // last_flag is reused by the next item
+        }
+        if (writer) {
+          const int j = it.chunk * kBM + row_in_tile;          // row of A_cat = (part, rank index)
+          if (j < it.R) {
+            const int pp = j / it.r, i = j - pp * it.r;
+            __nv_bfloat16* img = p.lora_vimg + (long long)(it.lt * p.lora_nparts + pp) * kLoraImgElems;
+#pragma unroll
+            for (int c = 0; c < kLoraWin; ++c) {
+              if (c < it.wn) {
+                const int t = it.w0 + c;
+                const bool live = t >= it.row0 && t < it.row0 + it.nrows;
+                img[c * 64 + ((((i >> 3) ^ (c & 7)) << 3) | (i & 7))] = __float2bfloat16(live ? v[c] : 0.f);
+              }
+            }
+          }
+          __threadfence();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (threadIdx.x == 64) {
+            fence_proxy_async_all();
+            st_release_gpu(&p.lora_flags[item_id], want);
+          }
+        }
+      }
+    }
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
     GemmWork w;
-    while (it.next(w)) {
+    while (alive && it.next(w)) {
       const int ta = p.b_fastest ? w.tile / tiles_b : w.tile % tiles_a;
       const int tb = p.b_fastest ? w.tile % tiles_b : w.tile / tiles_a;
       if (!mbar_wait(&tmem_full[acc], acc_phase[acc], abort_flag)) {
@@ -410,15 +607,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       }
       tc_fence_after();
       acc_phase[acc] ^= 1;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * BN);
+      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * S::kAcc);
       const int i = ta * kBM + row_in_tile;
       const int j0 = tb * p.bn;
       const int ncols = min(p.bn, p.umma_n);
       const int jend = min(p.b_rows, j0 + ncols);     // columns past it belong to the next tile (or to nobody)
       constexpr int CH = (BN >= 32) ? 32 : 16;
-      float* lora_stage = lora_stage_all + quad * (32 * 16);
-      LoraTok lora_mine{0, nullptr, nullptr};
-      if (p.lora_v != nullptr && p.tokens_on_a) lora_mine = lora_token(p, i, p.a_rows);
 
       if (w.nparts == 0) {
 #pragma unroll 1
@@ -439,10 +633,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           }
 #pragma unroll
           for (int q = 0; q < CH; ++q) v[q] *= p.out_scale;
-          if (p.lora_v != nullptr) {
-            if (p.tokens_on_a) lora_add_feature_columns<CH>(p, v, j0 + c, jend, lora_mine);
-            else lora_add_token_columns<CH>(p, v, i, j0 + c, jend, lora_stage);
-          }
           if (i < p.a_rows) {
             const float bias_i = (p.bias != nullptr && p.bias_on_a) ? __bfloat162float(p.bias[i]) : 0.f;
             __nv_bfloat16* orow = p.out + (long long)i * p.ldo_a;
@@ -534,10 +724,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             }
 #pragma unroll
             for (int q = 0; q < RC; ++q) acc8[q] *= p.out_scale;
-            if (p.lora_v != nullptr) {
-              if (p.tokens_on_a) lora_add_feature_columns<RC>(p, acc8, j0 + c, jend, lora_mine);
-              else lora_add_token_columns<RC>(p, acc8, i, j0 + c, jend, lora_stage);
-            }
             if (row_ok) {
               const int j = j0 + c;
               if (p.ldo_b == 1 && j + RC <= jend && ((reinterpret_cast<uintptr_t>(orow + j) & 15) == 0)) {
@@ -579,6 +765,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if constexpr (LORA) {
+    // the generation moves when every CTA of the launch is past its waits
+    if (lora && threadIdx.x == 0) {
+      __threadfence();
+      const int prev = atomicAdd(&p.lora_gen[1], 1);
+      if (prev == (int)gridDim.x - 1) {
+        p.lora_gen[1] = 0;
+        __threadfence();
+        st_release_gpu(p.lora_gen, want);
+      }
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -616,21 +814,28 @@ int make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uin
   return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
 }
 
-template <int BN, int STAGES>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
-  using S = GemmSmem<BN, STAGES>;
+template <int BN, int STAGES, bool LORA>
+static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const LoraXMaps& xm, const GemmParams& p, int grid,
+                         cudaStream_t stream) {
+  using S = GemmSmem<BN, STAGES, LORA>;
   // the shared-memory opt-in is a per-device attribute: one flag per device ordinal
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(gemm_bf16_tcgen05_kernel<BN, STAGES, LORA>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return -(int)e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES>, dim3(grid), dim3(kGemmThreads), (size_t)S::kTotal, stream, ta, tb, p);
+  launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, LORA>, dim3(grid), dim3(kGemmThreads), (size_t)S::kTotal, stream, ta, tb, xm, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
+  static const LoraXMaps none{};
+  return launch_gemm_t<BN, STAGES, false>(ta, tb, none, p, grid, stream);
 }
 
 // ---- planning -----------------------------------------------------------------------------------------------
@@ -733,21 +938,22 @@ extern "C" {
 long long lx_gemm_ws_bytes() { return 64ll << 20; }
 int lx_gemm_max_tiles() { return 8192; }
 
-struct LxLoraEpilogue {
-  const float* v;               // [T, ldv] shrink result
-  int ldv;
-  const int* tok_slot;          // [T]
-  const void* arena;
-  const long long* slot_base;
-  const int* slot_rank;
-  int num_slots;
-  long long unit_off;           // B_cat of this projection group sits at slot_base + rank * unit_off
-  int n0, n1;                   // part boundaries (N when the group has fewer parts)
+// Everything the LoRA part of a launch needs (see GemmParams).  `ksplit` is the K split of the shrink items the caller
+// wants (it knows how many table entries are live); the scratch sizes bound what can be served.
+struct LxLoraFused {
+  const void* tiles; int num_tiles;
+  const void* slot_tmaps; int maps_per_slot, map_a, map_b;
+  const int* slot_rank; const long long* slot_base; int num_slots;
+  int nparts, n0, n1, layer, max_rank, ksplit;
+  void* vimg; long long vimg_bytes;
+  float* vpart; long long vpart_bytes;
+  int* flags; int* counters; int n_flags;
+  int* gen;
 };
 
 static int gemm_impl(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
                      long long ldw, long long ldo, float out_scale, void* ws, long long ws_bytes, int* counters,
-                     int* status, int num_sms, int mode, int force_split, const LxLoraEpilogue* lora, void* stream_) {
+                     int* status, int num_sms, int mode, int force_split, const LxLoraFused* lora, void* stream_) {
   using namespace lx;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (T <= 0 || N <= 0) return 0;
@@ -768,7 +974,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   p.split_k = 1;
   CUtensorMap ta, tb;
   int bn;
-  const bool has_lora = (lora != nullptr && lora->v != nullptr);
+  const bool has_lora = (lora != nullptr && lora->tiles != nullptr && lora->num_tiles > 0);
   const int force_bn = force_split >> 16;
   const int kblocks_all = (K + kBK - 1) / kBK;
   // Tokens on the M side: the feature tile (UMMA N) whose tile count wastes the fewest SM slots in the last wave;
@@ -789,7 +995,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   // measures about 15 % slower at equal tiling.  The LoRA epilogue's fast path is written for weights on M.
   bool swap;
   GemmPlan pl_swap{};
-  if (mode == 1 || (mode == 0 && (T <= 128 || (has_lora && T <= 2048)))) {
+  if (mode == 1 || has_lora || (mode == 0 && T <= 128)) {
     swap = true;
   } else if (mode == 2 || T > 2048) {
     swap = false;
@@ -824,12 +1030,34 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   p.split_k = pl.split;
   p.dp_tiles = pl.dp_tiles;
   p.sk_ctas = pl.sk_ctas;
-  p.tokens_on_a = swap ? 0 : 1;
-  if (lora != nullptr && lora->v != nullptr) {
-    p.lora_v = lora->v; p.lora_ldv = lora->ldv; p.lora_tok_slot = lora->tok_slot;
-    p.lora_arena = reinterpret_cast<const __nv_bfloat16*>(lora->arena);
-    p.lora_slot_base = lora->slot_base; p.lora_slot_rank = lora->slot_rank; p.lora_num_slots = lora->num_slots;
-    p.lora_unit_off = lora->unit_off; p.lora_n0 = lora->n0; p.lora_n1 = lora->n1;
+  if (has_lora) {
+    p.lora_tiles = reinterpret_cast<const LoraTileG*>(lora->tiles);
+    p.lora_num_tiles = lora->num_tiles;
+    p.lora_slot_tmaps = reinterpret_cast<const CUtensorMap*>(lora->slot_tmaps);
+    p.lora_maps_per_slot = lora->maps_per_slot; p.lora_map_a = lora->map_a; p.lora_map_b = lora->map_b;
+    p.lora_slot_rank = lora->slot_rank; p.lora_slot_base = lora->slot_base; p.lora_num_slots = lora->num_slots;
+    p.lora_nparts = lora->nparts; p.lora_n0 = lora->n0; p.lora_n1 = lora->n1; p.lora_layer = lora->layer;
+    p.lora_vimg = reinterpret_cast<__nv_bfloat16*>(lora->vimg);
+    p.lora_vpart = lora->vpart;
+    p.lora_chunks = (lora->nparts * lora->max_rank + kBM - 1) / kBM;
+    int ks = lora->ksplit < 1 ? 1 : lora->ksplit;
+    if (ks > kblocks_all / 4) ks = kblocks_all / 4 < 1 ? 1 : kblocks_all / 4;
+    const long long ids = (long long)lora->num_tiles * p.lora_chunks;
+    while (ks > 1 && (long long)ks * ids * kLoraWin * kBM * 4 > lora->vpart_bytes) --ks;
+    p.lora_ksplit = ks;
+    p.lora_flags = lora->flags; p.lora_counters = lora->counters; p.lora_gen = lora->gen;
+    p.lora_T = T;
+    LoraXMaps xm;
+    for (int i = 0; i < 3; ++i) {
+      if (make_tmap_bf16_kmajor(&xm.m[i], x, T, K, ldx, 16 * (i + 1))) return -1004;
+    }
+    switch (template_bn(bn)) {
+      case 16:  return launch_gemm_t<16, 8, true>(ta, tb, xm, p, pl.grid, stream);
+      case 32:  return launch_gemm_t<32, 8, true>(ta, tb, xm, p, pl.grid, stream);
+      case 64:  return launch_gemm_t<64, 8, true>(ta, tb, xm, p, pl.grid, stream);
+      case 128: return launch_gemm_t<128, 6, true>(ta, tb, xm, p, pl.grid, stream);
+      default:  return launch_gemm_t<256, 4, true>(ta, tb, xm, p, pl.grid, stream);
+    }
   }
   switch (template_bn(bn)) {
     case 16:  return launch_gemm<16, 8>(ta, tb, p, pl.grid, stream);
@@ -859,18 +1087,25 @@ int lx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, int 
                    nullptr, stream_);
 }
 
-// The same GEMM with the multi-adapter LoRA delta added in the epilogue: one kernel replaces the base GEMM plus the
-// expand kernel of the reference (server/lorax_server/utils/layers.py:114-164 runs them as separate launches and the
-// expand reads and rewrites the whole output).
+// The same GEMM with the multi-adapter LoRA of the step in the same launch: shrink items first, then the base tiles with the
+// delta added by UMMAs into their accumulators (see the top of this file).  One launch replaces the shrink kernel, the base
+// GEMM and the expand kernel of the reference (server/lorax_server/utils/layers.py:114-164).
+// Returns 1 (nothing launched) when the launch cannot serve the step: a part boundary that is not a multiple of 128, a rank
+// above 64, or scratch too small for the table; the caller then runs shrink, GEMM and expand as separate launches.
 int lx_gemm_bf16_lora(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
-                      long long ldw, long long ldo, float out_scale, void* ws, long long ws_bytes, int* counters,
-                      int* status, int num_sms, int mode, int force_split, const float* lora_v, int lora_ldv,
-                      const int* tok_slot, const void* arena, const long long* slot_base, const int* slot_rank, int num_slots,
-                      long long unit_off, int n0, int n1, void* stream_) {
-  LxLoraEpilogue l{lora_v, lora_ldv, tok_slot, arena, slot_base, slot_rank, num_slots, unit_off, n0, n1};
-  return gemm_impl(x, w, out, bias, T, N, K, ldx, ldw, ldo, out_scale, ws, ws_bytes, counters, status, num_sms, mode, force_split,
-                   &l, stream_);
+                      long long ldw, long long ldo, void* ws, long long ws_bytes, int* counters, int* status, int num_sms,
+                      const LxLoraFused* lora, void* stream_) {
+  if (lora == nullptr || lora->tiles == nullptr || lora->num_tiles <= 0)
+    return gemm_impl(x, w, out, bias, T, N, K, ldx, ldw, ldo, 1.f, ws, ws_bytes, counters, status, num_sms, 0, 0, nullptr, stream_);
+  const int chunks = (lora->nparts * lora->max_rank + lx::kBM - 1) / lx::kBM;
+  const bool bounds_ok = (lora->nparts == 1) || ((lora->n0 % lx::kBM) == 0 && (lora->nparts == 2 || (lora->n1 % lx::kBM) == 0));
+  if (!bounds_ok || lora->max_rank > 64 || lora->max_rank <= 0 || lora->nparts < 1 || lora->nparts > 3 || N < lx::kBM) return 1;
+  if ((long long)lora->num_tiles * lora->nparts * lx::kLoraImgElems * 2 > lora->vimg_bytes) return 1;
+  if ((long long)lora->num_tiles * chunks > lora->n_flags) return 1;
+  return gemm_impl(x, w, out, bias, T, N, K, ldx, ldw, ldo, 1.f, ws, ws_bytes, counters, status, num_sms, 1, 0, lora, stream_);
 }
+
+int lx_lora_fused_desc_bytes() { return (int)sizeof(LxLoraFused); }
 
 }  // extern "C"
 

@@ -43,6 +43,19 @@ int lx_lora_expand_tiled(const float* v, int ldv, long long v_split_stride, int 
 int lx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
                  long long ldw, long long ldo, float out_scale, void* ws, long long ws_bytes, int* counters,
                  int* status, int num_sms, int mode, int force_split, void* stream_);
+struct LxLoraFused {
+  const void* tiles; int num_tiles;
+  const void* slot_tmaps; int maps_per_slot, map_a, map_b;
+  const int* slot_rank; const long long* slot_base; int num_slots;
+  int nparts, n0, n1, layer, max_rank, ksplit;
+  void* vimg; long long vimg_bytes;
+  float* vpart; long long vpart_bytes;
+  int* flags; int* counters; int n_flags;
+  int* gen;
+};
+int lx_gemm_bf16_lora(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
+                      long long ldw, long long ldo, void* ws, long long ws_bytes, int* counters, int* status, int num_sms,
+                      const LxLoraFused* lora, void* stream_);
 int lx_allreduce_sym(const unsigned long long* peer_ptrs, int rank, int world, long long in_off, long long out_off, long long cnt_off,
                      long long n_elems, int* state, int* status, void* stream);
 
@@ -90,7 +103,10 @@ struct LxModelDesc {
   float* attn_part_o; float* attn_part_lse; int attn_splits; int attn_part_tokens;
   // adapters
   const void* arena; const long long* slot_base; const int* slot_rank; const void* slot_tmaps;
-  int num_slots, max_rank, groups_per_slot, pad3_;
+  int num_slots, max_rank, groups_per_slot, fused_lora;      // fused_lora: LoRA inside the GEMM launch where it can serve the step
+  // scratch of the GEMM that carries LoRA in its own launch
+  void* lora_vimg; long long lora_vimg_bytes; float* lora_vpart; long long lora_vpart_bytes;
+  int* lora_flags; int* lora_item_counters; int n_lora_flags; int pad4_; int* lora_gen;
 };
 
 struct LxStepDesc {
@@ -102,6 +118,7 @@ struct LxStepDesc {
   const int* tok_slot;           // nullptr: no adapter in this step
   const void* lora_tiles;        // nullptr: rows are not grouped by adapter, use the per-token kernels
   int num_tiles, max_tile_rows;
+  int live_tiles, pad5_;         // live entries of the table (0: all)
   // activations of the step (allocated by the caller, reused by every layer)
   void* normed; void* qkv; void* attn; void* gate_up; void* act;
 };
@@ -121,6 +138,25 @@ int linear_with_lora(const LxModelDesc& m, const LxLayerDesc& l, const LxStepDes
                      const void* w, long long ldw, const void* bias, void* y, long long ldy, int N, int K, void* stream) {
   const LxLoraSite& site = l.lora[site_idx];
   const bool lora = s.tok_slot != nullptr && site.enabled && m.max_rank > 0 && (s.lora_tiles == nullptr || s.num_tiles > 0);
+  if (lora && s.lora_tiles != nullptr && m.fused_lora && s.max_tile_rows <= 32) {
+    // one launch: shrink items, base tiles, expand UMMAs
+    LxLoraFused f{};
+    f.tiles = s.lora_tiles; f.num_tiles = s.num_tiles;
+    f.slot_tmaps = m.slot_tmaps; f.maps_per_slot = m.groups_per_slot; f.map_a = site.tmap_group; f.map_b = m.groups_per_slot / 2 + site.tmap_group;
+    f.slot_rank = m.slot_rank; f.slot_base = m.slot_base; f.num_slots = m.num_slots;
+    f.nparts = site.nparts; f.n0 = site.n0; f.n1 = site.n1; f.layer = l.layer_index; f.max_rank = m.max_rank;
+    const int chunks = (site.nparts * m.max_rank + 127) / 128;
+    const int live = s.live_tiles > 0 ? s.live_tiles : s.num_tiles;
+    int ks = m.num_sms / (live * chunks > 0 ? live * chunks : 1);
+    if (ks > 8) ks = 8;
+    if (ks > ((K + 63) / 64) / 8) ks = ((K + 63) / 64) / 8;
+    f.ksplit = ks < 1 ? 1 : ks;
+    f.vimg = m.lora_vimg; f.vimg_bytes = m.lora_vimg_bytes; f.vpart = m.lora_vpart; f.vpart_bytes = m.lora_vpart_bytes;
+    f.flags = m.lora_flags; f.counters = m.lora_item_counters; f.n_flags = m.n_lora_flags; f.gen = m.lora_gen;
+    const int rc = lx_gemm_bf16_lora(x, w, y, bias, s.T, N, K, ldx, ldw, ldy, m.gemm_ws, m.gemm_ws_bytes, m.gemm_counters, m.status, m.num_sms,
+                                     &f, stream);
+    if (rc != 1) return rc;          // 1: this step does not fit the fused launch, use the separate kernels below
+  }
   if (lora) {
     if (s.lora_tiles != nullptr) {
       const int kblocks = (K + 63) / 64;

@@ -155,7 +155,7 @@ class DecoderModel:
         self.use_native_layers = self.device.type == "cuda" and os.environ.get("LORAX_NATIVE_LAYERS", "1") != "0"
         # LoRA expand inside the GEMM epilogue instead of its own launch (slower than the separate kernel at present:
         # four epilogue warps cannot hide the latency of the per-token B rows)
-        self.fused_lora_epilogue = os.environ.get("LORAX_FUSED_LORA_EPILOGUE", "0") == "1"
+        self.fused_lora = os.environ.get("LORAX_FUSED_LORA", "0") != "0"      # LoRA inside the GEMM launch (0: separate kernels)
         self.gated = c.model_type not in ("gpt2", "gpt_bigcode", "gpt_neox", "falcon", "RefinedWeb", "RefinedWebModel", "phi", "bloom",
                                           "mpt", "opt")
         if c.alibi:
@@ -371,7 +371,7 @@ class DecoderModel:
         self.quantized = method
         self._native = None
 
-    def _gemm(self, x, w, b, lora=None, out=None):
+    def _gemm(self, x, w, b, out=None):
         if isinstance(w, GroupQuantWeight):
             xb = x if x.dtype == torch.bfloat16 or not x.is_cuda else x.to(torch.bfloat16)
             y = self.ops.gemm_wq(xb, w, bias=b, out=out if out is not None and out.dtype == xb.dtype else None)
@@ -380,23 +380,28 @@ class DecoderModel:
                 return out
             return y if y.dtype == x.dtype else y.to(x.dtype)
         if out is not None and isinstance(w, torch.Tensor):
-            return self.ops.gemm(x, w, bias=b, lora=lora, out=out) if lora is not None else self.ops.gemm(x, w, bias=b, out=out)
+            return self.ops.gemm(x, w, bias=b, out=out)
         if isinstance(w, Fp8Weight):
             y = self.ops.gemm_fp8(x if x.dtype == torch.bfloat16 or not x.is_cuda else x.to(torch.bfloat16), w.q, w.scale, bias=b)
             return y if y.dtype == x.dtype else y.to(x.dtype)
-        return self.ops.gemm(x, w, bias=b, lora=lora) if lora is not None else self.ops.gemm(x, w, bias=b)
+        return self.ops.gemm(x, w, bias=b)
 
     def _linear(self, x, w, b, group: str, layer: int, inp: StepInputs, tok_slot=None, out=None):
-        """Base GEMM plus the multi-adapter LoRA delta for the projection group.  The shrink x A^T is one small launch;
-        the expand is a second one, or rides in the GEMM epilogue when `fused_lora_epilogue` is set."""
+        """Base GEMM plus the multi-adapter LoRA delta for the projection group.  On a GPU with the rows grouped by adapter
+        that is ONE launch (shrink items, base tiles, expand UMMAs); otherwise a shrink launch, the GEMM and an expand launch."""
         ts = tok_slot if tok_slot is not None else inp.tok_slot
         epi = None
+        if (self.fused_lora and self.adapters is not None and ts is not None and inp.lora_tiles is not None and x.is_cuda
+                and isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16):
+            lf = self.adapters.fused(group, layer, inp.lora_tiles)
+            if lf is not None:
+                y = self.ops.gemm_lora_fused(x, w, lf, bias=b, out=out)      # shrink, base GEMM and expand: one launch
+                if y is not None:
+                    return y
         if self.adapters is not None and ts is not None:
             epi = self.adapters.shrink(self.ops, x, ts, group, layer, tiles=inp.lora_tiles)
         if epi is None:
             return self._gemm(x, w, b, out=out)
-        if self.fused_lora_epilogue and isinstance(w, torch.Tensor):
-            return self._gemm(x, w, b, lora=epi, out=out)
         y = self._gemm(x, w, b, out=out)
         self.adapters.expand(self.ops, epi, y, tiles=inp.lora_tiles)
         return y

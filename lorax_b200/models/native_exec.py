@@ -46,7 +46,9 @@ class LxModelDesc(Structure):
                 ("n_lora_counters", I), ("pad2_", I),
                 ("attn_part_o", P), ("attn_part_lse", P), ("attn_splits", I), ("attn_part_tokens", I),
                 ("arena", P), ("slot_base", P), ("slot_rank", P), ("slot_tmaps", P),
-                ("num_slots", I), ("max_rank", I), ("groups_per_slot", I), ("pad3_", I)]
+                ("num_slots", I), ("max_rank", I), ("groups_per_slot", I), ("fused_lora", I),
+                ("lora_vimg", P), ("lora_vimg_bytes", L), ("lora_vpart", P), ("lora_vpart_bytes", L),
+                ("lora_flags", P), ("lora_item_counters", P), ("n_lora_flags", I), ("pad4_", I), ("lora_gen", P)]
 
 
 class LxStepDesc(Structure):
@@ -54,7 +56,7 @@ class LxStepDesc(Structure):
                 ("dec_block_tables", P), ("ctx_lens", P), ("dec_max_blocks", I), ("nsplit", I),
                 ("block_tables", P), ("cu_q", P), ("cache_lens", P), ("tile_seq", P), ("tile_q0", P),
                 ("max_blocks", I), ("n_attn_tiles", I),
-                ("tok_slot", P), ("lora_tiles", P), ("num_tiles", I), ("max_tile_rows", I),
+                ("tok_slot", P), ("lora_tiles", P), ("num_tiles", I), ("max_tile_rows", I), ("live_tiles", I), ("pad5_", I),
                 ("normed", P), ("qkv", P), ("attn", P), ("gate_up", P), ("act", P)]
 
 
@@ -70,7 +72,7 @@ def supported(model) -> bool:
     c = model.config
     if model.device.type != "cuda" or model.dtype != torch.bfloat16 or model.quantized is not None:
         return False
-    if c.is_moe or c.parallel_residual or model.pos_embed is not None or c.model_type == "gemma2" or model.fused_lora_epilogue:
+    if c.is_moe or c.parallel_residual or model.pos_embed is not None or c.model_type == "gemma2":
         return False
     if model.alibi_slopes is not None or c.clip_qkv or model.embed_norm is not None:
         return False
@@ -134,6 +136,11 @@ class NativeExecutor:
             m.arena, m.slot_base, m.slot_rank, m.slot_tmaps = (ad.arena.data_ptr(), ad.slot_base.data_ptr(), ad.slot_rank.data_ptr(),
                                                                ad.slot_tmaps.data_ptr())
             m.num_slots, m.max_rank, m.groups_per_slot = ad.slot_rank.shape[0], ad.max_rank, ad.groups_per_slot
+            m.fused_lora = int(model.fused_lora)
+            m.lora_vimg, m.lora_vimg_bytes = ws.lora_vimg.data_ptr(), ws.lora_vimg.numel() * 2
+            m.lora_vpart, m.lora_vpart_bytes = ws.lora_vpart.data_ptr(), ws.lora_vpart.numel() * 4
+            m.lora_flags, m.lora_item_counters, m.n_lora_flags = ws.lora_flags.data_ptr(), ws.lora_item_counters.data_ptr(), ws.lora_flags.numel()
+            m.lora_gen = ws.lora_gen.data_ptr()
         self.m = m
         self.layers = (LxLayerDesc * len(model.layers))()
         for li, lw in enumerate(model.layers):
@@ -197,6 +204,7 @@ class NativeExecutor:
             s.tok_slot = _p(inp.tok_slot)
             if inp.lora_tiles is not None:
                 s.lora_tiles, s.num_tiles, s.max_tile_rows = _p(inp.lora_tiles.table), inp.lora_tiles.num_tiles, inp.lora_tiles.max_rows
+                s.live_tiles = inp.lora_tiles.live
         s.normed, s.qkv, s.attn, s.gate_up, s.act = normed.data_ptr(), qkv.data_ptr(), attn.data_ptr(), gate_up.data_ptr(), act.data_ptr()
         if self.adapters is not None:
             m.max_rank = self.adapters.max_rank if self.adapters.is_cuda else 0      # changes as adapters come and go
@@ -224,7 +232,8 @@ class NativeExecutor:
             native._check(rc, "lx_run_layers")
             pending = fused.ar_out[: T * m.H].view(T, m.H) if ar is not None else out_a
             assert out_ptr.value == pending.data_ptr()
-            lora_sites = 4 if s.tok_slot else 0
+            fused_lora = bool(m.fused_lora) and s.lora_tiles and s.max_tile_rows <= 32 and m.max_rank <= 64     # LoRA adds no launch then
+            lora_sites = 4 if (s.tok_slot and not fused_lora) else 0
             attn_kernels = (1 if s.n_decode else 0) + (1 if T > s.n_decode else 0)
             native.launch_count += nL * (10 + attn_kernels + 2 * lora_sites + (2 if ar is not None else 0)) - 1      # `_check` counted one
             if ar is not None:

@@ -70,7 +70,8 @@ def load() -> ctypes.CDLL:
         "lx_tensormap_bytes": ([], I),
         "lx_lora_encode_tmap": ([P, P, I, I, L, I], I),
         "lx_lora_shrink_tc": ([P, L, P, I, I, P, I, I, P, I, I, I, P, I, L, I, P, P, I, I, I, I, P, P], I),
-        "lx_gemm_bf16_lora": ([P, P, P, P, I, I, I, L, L, L, F, P, L, P, P, I, I, I, P, I, P, P, P, P, I, L, I, I, P], I),
+        "lx_gemm_bf16_lora": ([P, P, P, P, I, I, I, L, L, L, P, L, P, P, I, P, P], I),
+        "lx_lora_fused_desc_bytes": ([], I),
         "lx_quant_act_fp8": ([P, L, P, L, P, I, I, I, P], I),
         "lx_gemm_fp8_block128": ([P, L, P, I, P, L, P, P, L, P, I, I, I, P, L, P, I, P], I),
         "lx_wq_dequant": ([P, P, P, P, L, I, I, I, I, P], I),
@@ -118,6 +119,14 @@ class Workspace:
         self.lora_v3 = torch.zeros(self.LORA_KSPLIT, max_tokens, max_lora_cols, dtype=torch.float32, device=device)
         self.lora_v = torch.zeros(max_tokens, max_lora_cols, dtype=torch.float32, device=device)     # shrink result
         self.lora_counters = torch.zeros(16384, dtype=torch.int32, device=device)
+        # LoRA inside the GEMM launch: bf16 operand images of the shrink results (6 KB per table entry and part), fp32 partials
+        # of their K splits, completion flags and split counters per (entry, 128-row chunk), and the launch generation
+        self.lora_max_entries = 1024
+        self.lora_vimg = torch.zeros(self.lora_max_entries * 3 * 48 * 64, dtype=torch.bfloat16, device=device)
+        self.lora_vpart = torch.empty(1024 * 48 * 128, dtype=torch.float32, device=device)
+        self.lora_flags = torch.zeros(2 * self.lora_max_entries, dtype=torch.int32, device=device)
+        self.lora_item_counters = torch.zeros(2 * self.lora_max_entries, dtype=torch.int32, device=device)
+        self.lora_gen = torch.zeros(2, dtype=torch.int32, device=device)
         self.attn_part_tokens = 256
         self.attn_splits = attn_splits
         self.attn_part_o = torch.empty(self.attn_part_tokens * num_heads * attn_splits * head_dim, dtype=torch.float32, device=device)
@@ -156,8 +165,8 @@ def gemm_plan(T: int, N: int, K: int, num_sms: int = 148, ws_bytes: int = 64 << 
 
 
 class LoraEpilogue(NamedTuple):
-    """What the GEMM epilogue needs to add the multi-adapter LoRA delta: the shrink result and where each slot's
-    B_cat of this projection group sits in the arena."""
+    """Result of a stand-alone shrink, as the stand-alone expand kernels take it: v and where each slot's B_cat of the
+    projection group sits in the arena."""
     v: torch.Tensor            # [T, ldv] fp32
     tok_slot: torch.Tensor     # [T] int32, -1 = no adapter
     arena: torch.Tensor
@@ -168,9 +177,56 @@ class LoraEpilogue(NamedTuple):
     n1: int
 
 
+class LxLoraFused(ctypes.Structure):
+    """Mirror of the C struct of the same name (csrc/kernels/gemm_bf16.cu)."""
+    _fields_ = [("tiles", ctypes.c_void_p), ("num_tiles", ctypes.c_int),
+                ("slot_tmaps", ctypes.c_void_p), ("maps_per_slot", ctypes.c_int), ("map_a", ctypes.c_int), ("map_b", ctypes.c_int),
+                ("slot_rank", ctypes.c_void_p), ("slot_base", ctypes.c_void_p), ("num_slots", ctypes.c_int),
+                ("nparts", ctypes.c_int), ("n0", ctypes.c_int), ("n1", ctypes.c_int), ("layer", ctypes.c_int),
+                ("max_rank", ctypes.c_int), ("ksplit", ctypes.c_int),
+                ("vimg", ctypes.c_void_p), ("vimg_bytes", ctypes.c_longlong),
+                ("vpart", ctypes.c_void_p), ("vpart_bytes", ctypes.c_longlong),
+                ("flags", ctypes.c_void_p), ("counters", ctypes.c_void_p), ("n_flags", ctypes.c_int),
+                ("gen", ctypes.c_void_p)]
+
+
+class LoraFused(NamedTuple):
+    """The multi-adapter LoRA of one projection group for the GEMM that carries it in its own launch."""
+    tiles: torch.Tensor        # [n, 4] int32 (slot, first row, rows <= 32, -), live entries first
+    num_tiles: int
+    live: int                  # live entries (0: all of them); sizes the K split of the shrink items
+    slot_tmaps: torch.Tensor
+    maps_per_slot: int
+    map_a: int
+    map_b: int
+    slot_rank: torch.Tensor
+    slot_base: torch.Tensor
+    nparts: int
+    n0: int
+    n1: int
+    layer: int
+    max_rank: int
+
+
+def lora_fused_desc(ws: "Workspace", lf: LoraFused, K: int) -> LxLoraFused:
+    d = LxLoraFused()
+    d.tiles, d.num_tiles = lf.tiles.data_ptr(), lf.num_tiles
+    d.slot_tmaps, d.maps_per_slot, d.map_a, d.map_b = lf.slot_tmaps.data_ptr(), lf.maps_per_slot, lf.map_a, lf.map_b
+    d.slot_rank, d.slot_base, d.num_slots = lf.slot_rank.data_ptr(), lf.slot_base.data_ptr(), lf.slot_rank.shape[0]
+    d.nparts, d.n0, d.n1, d.layer, d.max_rank = lf.nparts, lf.n0, lf.n1, lf.layer, lf.max_rank
+    chunks = (lf.nparts * lf.max_rank + 127) // 128
+    live = lf.live or lf.num_tiles
+    d.ksplit = max(1, min(8, ws.num_sms // max(1, live * chunks), ((K + 63) // 64) // 8))      # about one round of shrink items per CTA
+    d.vimg, d.vimg_bytes = ws.lora_vimg.data_ptr(), ws.lora_vimg.numel() * 2
+    d.vpart, d.vpart_bytes = ws.lora_vpart.data_ptr(), ws.lora_vpart.numel() * 4
+    d.flags, d.counters, d.n_flags = ws.lora_flags.data_ptr(), ws.lora_item_counters.data_ptr(), ws.lora_flags.numel()
+    d.gen = ws.lora_gen.data_ptr()
+    return d
+
+
 def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-         out_scale: float = 1.0, mode: int = 0, force_split: int = 0, lora: Optional[LoraEpilogue] = None) -> torch.Tensor:
-    """out[T, N] = x[T, K] @ w[N, K]^T (+ bias) (+ LoRA delta).  bf16 in, fp32 accumulate on tcgen05, bf16 out."""
+         out_scale: float = 1.0, mode: int = 0, force_split: int = 0) -> torch.Tensor:
+    """out[T, N] = x[T, K] @ w[N, K]^T (+ bias).  bf16 in, fp32 accumulate on tcgen05, bf16 out."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2 and w.dim() == 2
     assert x.stride(1) == 1 and w.stride(1) == 1
     T, K = x.shape
@@ -181,20 +237,36 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, 
     assert out.stride(1) == 1
     ws = workspace(x.device)
     lib = load()
-    if lora is not None:
-        assert lora.v.dtype == torch.float32 and lora.tok_slot.dtype == torch.int32 and lora.tok_slot.shape[0] >= T
-        rc = lib.lx_gemm_bf16_lora(_ptr(x), _ptr(w), _ptr(out), _ptr(bias), T, N, K, x.stride(0), w.stride(0), out.stride(0),
-                                   out_scale, _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.gemm_counters), _ptr(ws.status),
-                                   ws.num_sms, mode, force_split, _ptr(lora.v), lora.v.stride(0), _ptr(lora.tok_slot),
-                                   _ptr(lora.arena), _ptr(lora.slot_base), _ptr(lora.slot_rank), lora.slot_rank.shape[0],
-                                   lora.unit_off, lora.n0, lora.n1, _stream())
-        _check(rc, "lx_gemm_bf16_lora")
-        return out
     rc = lib.lx_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), _ptr(bias), T, N, K, x.stride(0), w.stride(0), out.stride(0),
                           out_scale, _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.gemm_counters), _ptr(ws.status),
                           ws.num_sms, mode, force_split, _stream())
     _check(rc, "lx_gemm_bf16")
     return out
+
+
+def gemm_lora_fused(x: torch.Tensor, w: torch.Tensor, lf: LoraFused, bias: Optional[torch.Tensor] = None,
+                    out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """out[T, N] = x @ w^T (+ bias) + the LoRA delta of every row's adapter, in one launch (shrink items, base tiles and
+    the expand UMMAs of `gemm_bf16_tcgen05_kernel<.., true>`).  None when the launch cannot serve the step (rank above 64,
+    part boundaries off the 128 grid, table larger than the scratch): the caller then uses the separate kernels."""
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
+    T, K = x.shape
+    N = w.shape[0]
+    given = out
+    if out is None:
+        out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
+    ws = workspace(x.device)
+    lib = load()
+    if lib.lx_lora_fused_desc_bytes() != ctypes.sizeof(LxLoraFused):
+        raise NativeError("LxLoraFused: C++ and ctypes disagree")
+    d = lora_fused_desc(ws, lf, K)
+    rc = lib.lx_gemm_bf16_lora(_ptr(x), _ptr(w), _ptr(out), _ptr(bias), T, N, K, x.stride(0), w.stride(0), out.stride(0),
+                               _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.gemm_counters), _ptr(ws.status), ws.num_sms,
+                               ctypes.byref(d), _stream())
+    if rc == 1:
+        return None
+    _check(rc, "lx_gemm_bf16_lora")
+    return out if given is None else given
 
 
 def quant_act_fp8(x: torch.Tensor):

@@ -333,20 +333,69 @@ def test_lora_tiled_tensor_core(nat, T, max_rows):
     # rows without a tile are untouched
     untouched = [i for i, s in enumerate(rows) if s < 0]
     assert torch.equal(y[untouched], y_ref[untouched])
-    # the same delta folded into the GEMM epilogue (both operand orientations, whole tiles / stream-K / classic split)
+
+
+@pytest.mark.parametrize("T,K,parts,ranks", [(40, 1024, [512, 128, 128], [16, 48, 64, 32]),
+                                             (256, 4096, [1024, 256, 256], [16, 16, 32, 64]),
+                                             (700, 2048, [768, 768], [16, 32, 16, 64]),
+                                             (300, 14336, [512], [16, 64, 32, 16])])
+def test_gemm_with_lora_in_the_same_launch(nat, T, K, parts, ranks):
+    """Shrink items, base tiles and expand UMMAs in ONE launch of the GEMM kernel against fp32 PyTorch:
+    x W^T + b + (x A_slot^T) B_slot^T per row, several adapters and ranks, base-model rows in between, rows of one adapter
+    crossing 16-row and 256-row boundaries, rank 48 (a part that straddles two 128-row chunks of A_cat), two calls in a row."""
+    torch.manual_seed(T + K)
+    nparts, L = len(parts), 2
+    N = sum(parts)
+    layer_units = nparts * K + N
+    bases, off = [], 0
+    for r in ranks:
+        bases.append(off)
+        off += r * layer_units * L
+        off = (off + 63) // 64 * 64
+    arena = (torch.randn(off, device="cuda") * 0.05).to(torch.bfloat16)
+    slot_base = torch.tensor(bases, device="cuda", dtype=torch.int64)
+    slot_rank = torch.tensor(ranks, device="cuda", dtype=torch.int32)
+    G = 5
+    tm_host = torch.zeros(len(ranks) * 2 * G * 128, dtype=torch.uint8).pin_memory()
+    for s, r in enumerate(ranks):
+        nat.lora_encode_tmap(tm_host[(s * 2 * G + 0) * 128:], arena.data_ptr() + bases[s] * 2, K, nparts * r, r * layer_units, L)
+        nat.lora_encode_tmap(tm_host[(s * 2 * G + G) * 128:], arena.data_ptr() + (bases[s] + r * nparts * K) * 2, r, N, r * layer_units, L)
+    tmaps = tm_host.cuda()
+    seg = [(-1, 3), (0, 5), (2, T // 3), (1, 1), (3, T // 4), (-1, 2)]
+    rows = []
+    for sl, n in seg:
+        rows += [sl] * n
+    rows = (rows + [1] * T)[:T]
+    tl = ref.build_lora_tiles(rows, 32)
+    tiles = torch.cat([torch.tensor(tl, device="cuda", dtype=torch.int32).view(-1, 4), torch.full((9, 4), -1, device="cuda", dtype=torch.int32)])
+    n0 = parts[0] if nparts > 1 else N
+    n1 = parts[0] + parts[1] if nparts > 2 else N
+    layer = 1
     w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K)
     b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
-    tok_slot = torch.tensor(rows, device="cuda", dtype=torch.int32)
-    epi = nat.LoraEpilogue(v_ref, tok_slot, arena, slot_base, slot_rank, offB, parts[0], parts[0] + parts[1])
-    want = ref.gemm(x, w, bias=b, lora=epi)
-    modes = [(1, 0), (1 | (2 << 8), 0), (1, 2), (2, 0), (2 | (2 << 8), 0)] if T <= 256 else [(2, 0), (2 | (2 << 8), 0)]
-    for mode, split in modes:
-        got = nat.gemm(x, w, bias=b, mode=mode, force_split=split, lora=epi)
+    for call in range(2):
+        x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+        lf = nat.LoraFused(tiles, tiles.shape[0], len(tl), tmaps, 2 * G, 0, G, slot_rank, slot_base, nparts, n0, n1, layer, max(ranks))
+        got = nat.gemm_lora_fused(x, w, lf, bias=b)
+        assert got is not None
         torch.cuda.synchronize()
         nat.workspace().check_status()
-        assert _rel_err(got, want) < 6e-3, (mode, split)
-        base = nat.gemm(x, w, bias=b, mode=mode, force_split=split)
-        assert torch.equal(got[untouched], base[untouched])
+        want = x.float() @ w.float().t() + b.float()
+        bounds = [0, n0, n1, N] if nparts == 3 else ([0, n0, N] if nparts == 2 else [0, N])
+        for t, sl in enumerate(rows):
+            if sl < 0:
+                continue
+            r = ranks[sl]
+            A = arena[bases[sl] + r * layer * layer_units:][: nparts * r * K].view(nparts * r, K).float()
+            B = arena[bases[sl] + r * (layer * layer_units + nparts * K):][: N * r].view(N, r).float()
+            v = (A @ x[t].float()).to(torch.bfloat16).float()            # the kernel rounds the shrink result to bf16
+            for pp in range(nparts):
+                lo, hi = bounds[pp], bounds[pp + 1]
+                want[t, lo:hi] += B[lo:hi] @ v[pp * r:(pp + 1) * r]
+        assert _rel_err(got, want) < 6e-3, call
+        untouched = [i for i, s_ in enumerate(rows) if s_ < 0]
+        base = nat.gemm(x, w, bias=b, mode=1)
+        assert _rel_err(got[untouched], base[untouched]) < 1e-6
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 256, 256), (16, 4096, 4096), (48, 1024, 14336), (100, 6144, 4096), (128, 384, 512),
