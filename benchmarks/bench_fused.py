@@ -1,13 +1,18 @@
 """Fused row-parallel GEMM + all-reduce kernel against the NCCL baseline (GEMM kernel, then `all_reduce`), with the
 roofline of the fused path: the slower of FLOPs / measured GEMM peak and NVLink bytes / measured link bandwidth.
 
-    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m lorax_b200.parallel.bench_fused
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 benchmarks/bench_fused.py
 
 Both arms are captured in a CUDA graph (20 calls rotating through >126 MB of weights) and device-timed; the number
 reported is the maximum over ranks.  With `--allreduce` the two-shot all-reduce kernel is timed against NCCL's instead.
 """
 
 from __future__ import annotations
+
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import json
 import math
@@ -16,8 +21,8 @@ import os
 import torch
 import torch.distributed as dist
 
-from ..ops import native
-from .tp import TensorParallel
+from lorax_b200.ops import native
+from lorax_b200.parallel.tp import TensorParallel
 
 NVLINK_GBS = 770.0         # measured peer copy bandwidth per direction on this machine class
 PEAK_TFLOPS = 1640.9
@@ -50,7 +55,7 @@ def gtime(fn, n_rot, reps=20):
 
 def bench_allreduce(tp):
     """Two-shot all-reduce kernel against NCCL's all-reduce on bf16 [T, 4096]; results are compared bit for bit."""
-    from . import fused
+    from lorax_b200.parallel import fused
     fc = fused.FusedCollectives(tp, n_max=4096, max_rows=512)
     fc.setup_all_reduce(4352, 4096)
     for T in (16, 256, 1216, 4096):
@@ -78,7 +83,7 @@ def main():
     ws = tp.world_size
     if "--allreduce" in sys.argv:
         bench_allreduce(tp)
-    from . import fused
+    from lorax_b200.parallel import fused
 
     class _M:
         hidden = 4096

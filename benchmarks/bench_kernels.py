@@ -1,10 +1,15 @@
 """Micro-benchmarks of the CUDA kernels against their roofline (and cuBLAS for the GEMM).
 
-``python -m lorax_b200.ops.bench_kernels [--json out.json]`` times each kernel with CUDA events after a
+``python benchmarks/bench_kernels.py [--json out.json]`` times each kernel with CUDA events after a
 warm-up, rotating through enough distinct buffers that the working set exceeds the 126 MB L2.
 """
 
 from __future__ import annotations
+
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import argparse
 import json
@@ -111,6 +116,52 @@ def bench_small(results, peaks):
         print(results[-1], flush=True)
 
 
+def bench_lora(results, peaks):
+    """One projection with 100 rank-16 adapters over the rows (Zipf 1.1, rows grouped by adapter): the GEMM that carries LoRA in
+    its own launch against shrink + GEMM + expand as three launches, and against the base GEMM alone."""
+    from lorax_b200.ops import reference
+    r, S, G = 16, 100, 5
+    sites = [("qkv", [4096, 1024, 1024], 4096), ("o", [4096], 4096), ("gate_up", [14336, 14336], 4096), ("down", [4096], 14336)]
+    wz = torch.tensor([1.0 / (k ** 1.1) for k in range(1, S + 1)], dtype=torch.float64)
+    for T in (64, 256, 1024):
+        rows = sorted(int(v) for v in torch.multinomial(wz / wz.sum(), T, replacement=True, generator=torch.Generator().manual_seed(T)))
+        tl = reference.build_lora_tiles(rows, 32)
+        tiles = torch.full((len(tl) + 16, 4), -1, device="cuda", dtype=torch.int32)
+        tiles[: len(tl)] = torch.tensor(tl, device="cuda", dtype=torch.int32)
+        for name, parts, K in sites:
+            N, nparts = sum(parts), len(parts)
+            units = nparts * K + N
+            arena = (torch.randn(S * r * units, device="cuda") * 0.02).to(torch.bfloat16)
+            slot_base = torch.arange(S, device="cuda", dtype=torch.int64) * r * units
+            slot_rank = torch.full((S,), r, device="cuda", dtype=torch.int32)
+            tm = torch.zeros(S * 2 * G * 128, dtype=torch.uint8).pin_memory()
+            for s_ in range(S):
+                base = arena.data_ptr() + s_ * r * units * 2
+                native.lora_encode_tmap(tm[(s_ * 2 * G) * 128:], base, K, nparts * r, r * units, 1)
+                native.lora_encode_tmap_b(tm[(s_ * 2 * G + G) * 128:], base + r * nparts * K * 2, r, N, r * units, 1)
+            tmaps = tm.cuda()
+            n_rot = max(2, int(math.ceil(300e6 / (N * K * 2))))
+            ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K) for _ in range(n_rot)]
+            x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+            out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+            n0 = parts[0] if nparts > 1 else N
+            n1 = parts[0] + parts[1] if nparts > 2 else N
+            lf = native.LoraFused(tiles, tiles.shape[0], len(tl), tmaps, 2 * G, 0, G, slot_rank, slot_base, nparts, n0, n1, 0, r)
+
+            def separate(i):
+                v = native.lora_shrink_tiles(x, tiles, tiles.shape[0], 32, tmaps, 2 * G, 0, slot_rank, nparts, 0, r, live_tiles=len(tl))
+                native.gemm(x, ws[i], out=out)
+                native.lora_expand_tiles(v[:T], tiles, tiles.shape[0], 32, arena, slot_base, slot_rank, nparts * K, out, n0, n1)
+            ms_f = _time(lambda i: native.gemm_lora_fused(x, ws[i], lf, out=out), n_rot)
+            ms_s = _time(separate, n_rot)
+            ms_b = _time(lambda i: native.gemm(x, ws[i], out=out), n_rot)
+            native.workspace().check_status()
+            results.append({"kernel": "gemm_bf16_tcgen05<lora>", "shape": f"{name} T={T} N={N} K={K} entries={len(tl)}",
+                            "ms_one_launch": round(ms_f, 4), "ms_three_launches": round(ms_s, 4), "ms_base_gemm": round(ms_b, 4)})
+            print(results[-1], flush=True)
+            del ws, arena
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
@@ -123,7 +174,8 @@ def main():
     except OSError:
         pass
     results = []
-    for name, fn in (("gemm", bench_gemm), ("attn_decode", bench_attn_decode), ("attn_prefill", bench_attn_prefill), ("small", bench_small)):
+    for name, fn in (("gemm", bench_gemm), ("lora", bench_lora), ("attn_decode", bench_attn_decode), ("attn_prefill", bench_attn_prefill),
+                     ("small", bench_small)):
         if a.only and a.only != name:
             continue
         fn(results, peaks)

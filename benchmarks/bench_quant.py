@@ -1,11 +1,15 @@
-"""Weight-only 4-bit GEMM against the bf16 tcgen05 GEMM on the projection shapes of a 7B model (python -m lorax_b200.ops.bench_quant).
+"""Weight-only 4-bit GEMM against the bf16 tcgen05 GEMM on the projection shapes of a 7B model (python benchmarks/bench_quant.py).
 
 Every timing is a CUDA graph of 20 calls rotating through more than 126 MB of weights (larger than L2), best of 5 replays,
 CUDA events on the launching stream."""
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import torch
 
-from . import native
-from ..utils import quant_formats as qf
+from lorax_b200.ops import native
+from lorax_b200.utils import quant_formats as qf
 
 def timeit(fn, reps=20):
     for _ in range(3): fn()

@@ -1,6 +1,6 @@
 """Throughput of the SERVED path: HTTP clients -> C++ router -> shard runtime -> kernels, on one GPU.
 
-    python -m lorax_b200.server.bench_served [--model mistral-7b] [--adapters 100] [--concurrency 256] [--seconds 30]
+    python benchmarks/bench_served.py [--model mistral-7b] [--adapters 100] [--concurrency 256] [--seconds 30]
 
 Builds a random-weight model of the named architecture in this process, parks random rank-r adapters in the pinned
 host tier, starts the framed-socket shard server and the `lorax-router` binary, then runs a closed-loop load generator
@@ -11,6 +11,11 @@ timing headers.
 """
 
 from __future__ import annotations
+
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import argparse
 import asyncio
@@ -100,12 +105,12 @@ def main():
 
     import tempfile
     import torch
-    from .. import config as cfgs
-    from ..adapters.lora import BlobLayout, pad_rank
-    from ..config import EngineConfig
-    from ..models.decoder import DecoderModel
-    from .runtime import ShardRuntime
-    from .transport import FramedServer
+    from lorax_b200 import config as cfgs
+    from lorax_b200.adapters.lora import BlobLayout, pad_rank
+    from lorax_b200.config import EngineConfig
+    from lorax_b200.models.decoder import DecoderModel
+    from lorax_b200.server.runtime import ShardRuntime
+    from lorax_b200.server.transport import FramedServer
 
     on_gpu = torch.cuda.is_available()
     dev = torch.device("cuda", 0) if on_gpu else torch.device("cpu")
@@ -158,7 +163,7 @@ def main():
         router.kill()
         raise RuntimeError("router did not come up: " + router.stdout.read().decode()[-2000:])
     try:
-        out = subprocess.run([sys.executable, "-m", "lorax_b200.server.bench_served", "--client", "--url", f"http://127.0.0.1:{port}",
+        out = subprocess.run([sys.executable, os.path.abspath(__file__), "--client", "--url", f"http://127.0.0.1:{port}",
                               "--adapters", str(a.adapters), "--concurrency", str(a.concurrency), "--seconds", str(a.seconds),
                               "--warmup-seconds", str(a.warmup_seconds), "--min-prompt", str(a.min_prompt), "--max-prompt", str(a.max_prompt),
                               "--new-tokens", str(a.new_tokens), "--vocab", str(mc.vocab_size)], capture_output=True, text=True, timeout=1800)

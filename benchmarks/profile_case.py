@@ -1,19 +1,24 @@
 """Small, self-terminating workloads for `ncu` captures of single kernels.
 
-    python -m lorax_b200.ops.profile_case --case gemm_decode|gemm_mid|gemm_prefill|gemm_fp8_decode|gemm_fp8_prefill|gemm_lora_decode|gemm_lora_decode_gateup|gemm_lora_prefill|attn_decode|attn_prefill|lora_shrink|lora_expand
+    python benchmarks/profile_case.py --case gemm_decode|gemm_mid|gemm_prefill|gemm_fp8_decode|gemm_fp8_prefill|gemm_lora_decode|gemm_lora_decode_gateup|gemm_lora_prefill|attn_decode|attn_prefill|lora_shrink|lora_expand
 
 Each case launches the kernel a handful of times on inputs larger than the 126 MB L2 but at most a few GB, and
 exits 0; run it plain first, then under
-`ncu --set full --clock-control none -k regex:<kernel> -c 2 -o <report> python -m lorax_b200.ops.profile_case --case ...`.
+`ncu --set full --clock-control none -k regex:<kernel> -c 2 -o <report> python benchmarks/profile_case.py --case ...`.
 """
 
 from __future__ import annotations
+
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 import argparse
 
 import torch
 
-from . import native, reference
+from lorax_b200.ops import native, reference
 
 
 def gemm_case(T):
@@ -77,23 +82,36 @@ def lora_case(which):
 
 
 def gemm_lora_case(T, parts=(4096, 1024, 1024)):
-    """QKV (or gate_up) projection with the LoRA delta in the epilogue: 100 rank-16 adapters, rows sorted by adapter."""
+    """QKV (or gate_up) projection with the multi-adapter LoRA in the same launch: 100 rank-16 adapters drawn like the
+    benchmark does (Zipf 1.1), rows sorted by adapter, weights rotating over more than L2."""
     import math
     K, r, S = 4096, 16, 100
     N = sum(parts)
-    units = len(parts) * K + N
+    nparts = len(parts)
+    units = nparts * K + N
     arena = (torch.randn(S * r * units, device="cuda") * 0.02).to(torch.bfloat16)
     slot_base = torch.arange(S, device="cuda", dtype=torch.int64) * r * units
     slot_rank = torch.full((S,), r, device="cuda", dtype=torch.int32)
+    G = 5
+    tm = torch.zeros(S * 2 * G * 128, dtype=torch.uint8).pin_memory()
+    for s_ in range(S):
+        base = arena.data_ptr() + s_ * r * units * 2
+        native.lora_encode_tmap(tm[(s_ * 2 * G) * 128:], base, K, nparts * r, r * units, 1)
+        native.lora_encode_tmap_b(tm[(s_ * 2 * G + G) * 128:], base + r * nparts * K * 2, r, N, r * units, 1)
+    tmaps = tm.cuda()
+    w_ = torch.tensor([1.0 / (k ** 1.1) for k in range(1, S + 1)], dtype=torch.float64)
+    rows = sorted(int(x) for x in torch.multinomial(w_ / w_.sum(), T, replacement=True))
+    tl = reference.build_lora_tiles(rows, 32)
+    tiles = torch.full((max(T, len(tl)), 4), -1, device="cuda", dtype=torch.int32)
+    tiles[: len(tl)] = torch.tensor(tl, device="cuda", dtype=torch.int32)
     ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K) for _ in range(4)]
-    rows = sorted(int(x) for x in torch.randint(0, S, (T,))) if T <= 256 else [int(i * 3 // T) for i in range(T)]
-    tok_slot = torch.tensor(rows, device="cuda", dtype=torch.int32)
     x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
-    v = torch.randn(T, 192, device="cuda", dtype=torch.float32)
-    epi = native.LoraEpilogue(v, tok_slot, arena, slot_base, slot_rank, len(parts) * K, parts[0], parts[0] + parts[1] if len(parts) > 2 else N)
     out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+    n0 = parts[0] if nparts > 1 else N
+    n1 = parts[0] + parts[1] if nparts > 2 else N
+    lf = native.LoraFused(tiles, tiles.shape[0], len(tl), tmaps, 2 * G, 0, G, slot_rank, slot_base, nparts, n0, n1, 0, r)
     for i in range(4):
-        native.gemm(x, ws[i], out=out, lora=epi)
+        assert native.gemm_lora_fused(x, ws[i], lf, out=out) is not None
 
 
 def gemm_fp8_case(T):
@@ -112,7 +130,7 @@ def gemm_fp8_case(T):
 
 def gemm_int4_case(T):
     """Weight-only 4-bit GEMM straight from the packed codes, gate_up shape, three weight sets (> L2 in total)."""
-    from ..utils import quant_formats as qf
+    from lorax_b200.utils import quant_formats as qf
     N, K = 28672, 4096
     base = qf.quantize_rtn(torch.randn(N, K) * 0.02, 4, 128).to("cuda")
     ws = [qf.GroupQuantWeight(base.codes.clone(), base.sz.clone(), 4, 128, (N, K)) for _ in range(3)]

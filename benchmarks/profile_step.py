@@ -1,6 +1,6 @@
 """Per-operator device-time breakdown of one prefill step and one decode step of the serving engine.
 
-    python -m lorax_b200.runtime.profile_step [--model mistral-7b] [--batch 256] [--ctx 700] [--prefill 1024] [--adapters 100]
+    python benchmarks/profile_step.py [--model mistral-7b] [--batch 256] [--ctx 700] [--prefill 1024] [--adapters 100]
 
 Runs the steps eagerly (no CUDA graph) with every operator bracketed by CUDA events, so the numbers include the
 launch gap of each kernel; the shares tell where a step spends its time.
@@ -8,18 +8,23 @@ launch gap of each kernel; the shares tell where a step spends its time.
 
 from __future__ import annotations
 
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
 import argparse
 import json
 
 import torch
 
-from .. import config as cfgs
-from ..adapters.lora import BlobLayout, pad_rank
-from ..adapters.manager import AdapterManager
-from ..models.decoder import DecoderModel
-from ..ops import native
-from .kv_cache import KVCache
-from .runner import ModelRunner, PrefillItem
+from lorax_b200 import config as cfgs
+from lorax_b200.adapters.lora import BlobLayout, pad_rank
+from lorax_b200.adapters.manager import AdapterManager
+from lorax_b200.models.decoder import DecoderModel
+from lorax_b200.ops import native
+from lorax_b200.runtime.kv_cache import KVCache
+from lorax_b200.runtime.runner import ModelRunner, PrefillItem
 
 
 def main():

@@ -182,7 +182,7 @@ class AdapterManager:
             layers = 1 if gname == LM_HEAD else self.layout.num_layers
             native.lora_encode_tmap(host[gi_idx * TMAP_BYTES:], base, gi.K, nparts * rp, rp * self.layout.layer_units, layers)
             base_b = self.arena.data_ptr() + (off + rp * self.layout.unit_off(gname, 0, "B")) * esize
-            native.lora_encode_tmap(host[(len(TMAP_GROUPS) + gi_idx) * TMAP_BYTES:], base_b, rp, gi.N, rp * self.layout.layer_units, layers)
+            native.lora_encode_tmap_b(host[(len(TMAP_GROUPS) + gi_idx) * TMAP_BYTES:], base_b, rp, gi.N, rp * self.layout.layer_units, layers)
         return host
 
     # ------------------------------------------------------------------ host tier

@@ -18,8 +18,10 @@
 // one adapter, v = x A_cat^T on the tensor cores, stored as a bf16 image already in the shared-memory layout of a UMMA
 // operand -- and then through the base tiles, where after the K loop the delta is added by further UMMAs
 // (B_cat tile of the adapter x that image, K = rank) straight into the TMEM accumulator.  The epilogue is unchanged.
-// Base tiles wait for the images they need on per-item flags; every CTA finishes its shrink items before its first
-// base tile, so those waits cannot deadlock, and they are bounded like every other wait.
+// The operands of those UMMAs are 32-byte-swizzled K slices of 16 ranks (4 KB of B_cat, 1.5 KB of image), four of them per
+// pipeline stage, so a base tile pays one stage per four adapters of its rows.  A CTA counts itself in when its shrink
+// items are done and the first base tile that needs an image waits until every CTA of the launch has; every CTA
+// finishes its shrink items before its first base tile, so that wait cannot deadlock, and it is bounded like the others.
 //
 // Structure: persistent CTAs of 6 warps.  Warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and
 // TMEM owner, warps 2..5 = epilogue (each warp reads its own 32-lane TMEM quadrant with tcgen05.ld).  A STAGES
@@ -67,18 +69,23 @@ struct GemmParams {
   int lora_num_slots;
   int lora_nparts, lora_n0, lora_n1;   // parts of the fused projection (q | k | v, gate | up) and their boundaries (multiples of 128)
   int lora_layer;
-  __nv_bfloat16* lora_vimg;            // [tile][part][48 rows][64] bf16: v as a K-major, 128-byte-swizzled UMMA operand image
+  __nv_bfloat16* lora_vimg;            // [tile][part][4 K slices][48 rows][16] bf16: v as K-major, 32-byte-swizzled UMMA operand images
   float* lora_vpart;                   // [ksplit][tile * chunks][48][128] fp32 partials of the K splits (ksplit > 1)
   int lora_ksplit, lora_chunks;        // K splits of a shrink item; 128-row chunks of A_cat (nparts * max rank / 128, rounded up)
-  int* lora_flags;                     // [tile * chunks] generation in which the image chunk was completed
   int* lora_counters;                  // [tile * chunks] arrivals of the K splits, zero between launches
-  int* lora_gen;                       // [2] generation of the last finished launch, CTAs of this launch that have finished
+  int* lora_sync;                      // [2] CTAs of this launch that have finished / whose shrink items are done; zero between launches
+  int lora_fence_maps;                 // 1: acquire-fence a slot's B_cat map before every use (0: once, with its A_cat map, per shrink item)
+  int lora_skip;                       // measurement only: bit 0 leaves out the shrink items, bit 1 the expand stages (results are then wrong)
   int lora_T;                          // rows of the step
 };
 
 // ---- LoRA items ----------------------------------------------------------------------------------------------
 constexpr int kLoraWin = 48;            // a run of <= 32 rows lies inside a 16-aligned window of at most 48 rows
-constexpr int kLoraImgElems = kLoraWin * 64;
+constexpr int kLoraSliceElems = kLoraWin * 16;      // one K slice (16 ranks) of an image: 48 rows of 32 bytes
+constexpr int kLoraSliceBytes = kLoraSliceElems * 2;
+constexpr int kLoraImgElems = 4 * kLoraSliceElems;  // ranks up to 64
+constexpr int kLoraBTileBytes = kBM * 32;           // 128 features x 16 ranks of B_cat
+constexpr int kLoraUnitsPerStage = 4;
 
 LX_DEVICE int ld_acquire_gpu(const int* p) {
   int v;
@@ -87,6 +94,18 @@ LX_DEVICE int ld_acquire_gpu(const int* p) {
 }
 LX_DEVICE void st_release_gpu(int* p, int v) { asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
 LX_DEVICE void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+LX_DEVICE void red_release_gpu_add(int* p, int v) { asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+// K-major operand with 32-byte swizzle: rows of 32 bytes (16 bf16), 8-row groups 256 bytes apart.
+LX_DEVICE uint64_t make_desc_k_sw32(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(256 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(6) << 61;
+  return d;
+}
 
 // Bounded wait for *flag == want.  False when the budget ran out.
 LX_DEVICE bool wait_flag(const int* flag, int want, volatile int* abort_flag) {
@@ -103,22 +122,39 @@ LX_DEVICE bool wait_flag(const int* flag, int want, volatile int* abort_flag) {
   return true;
 }
 
+// The table of the step, checked once per CTA and kept in shared memory: the producer and the MMA thread walk it for every
+// base tile, and a walk through global memory (entry -> slot -> rank, each a trip to L2) costs more than the tile itself.
+constexpr int kLoraMaxEntries = 512;
+struct LoraEnt { int slot, row0, nrows, r; };          // r == 0: nothing to do for the entry; slot < 0: end of the live entries
+LX_DEVICE void load_lora_entries(const GemmParams& p, LoraEnt* ents) {
+  for (int lt = threadIdx.x; lt < p.lora_num_tiles; lt += blockDim.x) {
+    const LoraTileG t = p.lora_tiles[lt];
+    LoraEnt e{t.slot, t.row0, min(min(t.nrows, 32), p.lora_T - t.row0), 0};
+    if (t.slot >= 0 && t.slot < p.lora_num_slots && e.nrows > 0 && t.row0 >= 0) {
+      const int r = p.lora_slot_rank[t.slot];
+      if (r > 0 && r <= 64 && (r & 15) == 0 && p.lora_slot_base[t.slot] >= 0) e.r = r;
+    }
+    ents[lt] = e;
+  }
+}
+
+LX_DEVICE int shrink_kblocks_per_stage(int a_region, int x_region, int a_sub, int x_sub) {
+  return max(1, min(min(a_region / a_sub, x_region / x_sub), 4));
+}
+
 // One shrink item: k-blocks [kb0, kb1) of chunk `chunk` (128 rows of A_cat) of table entry `lt`.
 struct ShrinkItem {
   int lt, chunk, split, slot, row0, nrows, r, R, box_rows, w0, wn, kb0, kb1;
 };
-LX_DEVICE bool decode_shrink_item(const GemmParams& p, int idx, int kblocks, ShrinkItem& it) {
+LX_DEVICE bool decode_shrink_item(const GemmParams& p, const LoraEnt* ents, int idx, int kblocks, ShrinkItem& it) {
   const int per_tile = p.lora_chunks * p.lora_ksplit;
   it.lt = idx / per_tile;
   const int rem = idx - it.lt * per_tile;
   it.chunk = rem / p.lora_ksplit;
   it.split = rem - it.chunk * p.lora_ksplit;
-  const LoraTileG t = p.lora_tiles[it.lt];
-  it.slot = t.slot; it.row0 = t.row0;
-  it.nrows = min(min(t.nrows, 32), p.lora_T - t.row0);
-  if (t.slot < 0 || t.slot >= p.lora_num_slots || it.nrows <= 0 || t.row0 < 0) return false;
-  it.r = p.lora_slot_rank[t.slot];
-  if (it.r <= 0 || it.r > 64 || (it.r & 15) != 0 || p.lora_slot_base[t.slot] < 0) return false;
+  const LoraEnt t = ents[it.lt];
+  if (t.r == 0) return false;
+  it.slot = t.slot; it.row0 = t.row0; it.nrows = t.nrows; it.r = t.r;
   it.R = it.r * p.lora_nparts;
   if (it.chunk * kBM >= it.R) return false;
   it.box_rows = min(kBM, (it.R + 15) / 16 * 16);       // must match the encoder of the A_cat maps
@@ -131,24 +167,20 @@ LX_DEVICE bool decode_shrink_item(const GemmParams& p, int idx, int kblocks, Shr
 
 // The part of table entry `lt` that adds to accumulator columns [c0, c1) of the token tile whose rows are [j0, jlim).
 struct ExpandItem {
-  int slot, r, w0, c0, c1, chunk_lo, chunk_hi;
+  int slot, r, w0, c0, c1;
 };
 // -1: end of the live entries, 0: nothing to add for this entry, 1: `e` is valid.
-LX_DEVICE int decode_expand_item(const GemmParams& p, int lt, int part, int j0, int jlim, ExpandItem& e) {
-  const LoraTileG t = p.lora_tiles[lt];
+LX_DEVICE int decode_expand_item(const LoraEnt* ents, int lt, int j0, int jlim, ExpandItem& e) {
+  const LoraEnt t = ents[lt];
   if (t.slot < 0) return -1;
-  const int nrows = min(min(t.nrows, 32), p.lora_T - t.row0);
-  if (t.slot >= p.lora_num_slots || nrows <= 0 || t.row0 < 0) return 0;
+  if (t.r == 0) return 0;
   e.slot = t.slot;
-  e.r = p.lora_slot_rank[t.slot];
-  if (e.r <= 0 || e.r > 64 || (e.r & 15) != 0 || p.lora_slot_base[t.slot] < 0) return 0;
+  e.r = t.r;
   e.w0 = t.row0 & ~15;
-  const int w1 = (t.row0 + nrows + 15) & ~15;
+  const int w1 = (t.row0 + t.nrows + 15) & ~15;
   e.c0 = max(e.w0, j0);
   e.c1 = min(w1, jlim);
   if (e.c0 >= e.c1) return 0;
-  e.chunk_lo = (part * e.r) / kBM;
-  e.chunk_hi = ((part + 1) * e.r - 1) / kBM;
   return 1;
 }
 
@@ -242,7 +274,8 @@ struct GemmSmem {
   static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + 1024;  // +1024 for manual alignment
+  static constexpr int kEntBytes = LORA ? kLoraMaxEntries * (int)sizeof(LoraEnt) : 0;
+  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + kEntBytes + 1024;  // +1024 for manual alignment
 };
 
 template <int BN, int STAGES, bool LORA>
@@ -261,6 +294,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_base_slot + 2));
+  LoraEnt* ents = reinterpret_cast<LoraEnt*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -271,7 +305,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const int num_tiles = tiles_a * tiles_b;
   const int kblocks = (p.K + kBK - 1) / kBK;
   const bool lora = LORA && p.lora_tiles != nullptr;
-  const int n_shrink = lora ? p.lora_num_tiles * p.lora_chunks * p.lora_ksplit : 0;
+  const int n_shrink = (lora && !(p.lora_skip & 1)) ? p.lora_num_tiles * p.lora_chunks * p.lora_ksplit : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -297,8 +331,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
   pdl_wait();      // barriers, TMEM and descriptors are set up while the previous kernel drains; its data is read from here on
-  // Flags of this launch carry generation + 1; the generation only moves when the last CTA of a launch has finished.
-  const int want = lora ? ld_acquire_gpu(p.lora_gen) + 1 : 0;
+  if constexpr (LORA) {
+    if (lora) {
+      load_lora_entries(p, ents);
+      __syncthreads();
+    }
+  }
 
   // Work item w -> (tile, split).  Tiles are ordered with the A tile index fastest inside one B tile so that
   // CTAs running at the same time share the B operand through L2.
@@ -309,15 +347,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      bool shrink_seen = false;
       if constexpr (LORA) {
         for (int idx = (int)blockIdx.x; ok && idx < n_shrink; idx += (int)gridDim.x) {
           ShrinkItem it;
-          if (!decode_shrink_item(p, idx, kblocks, it)) continue;
+          if (!decode_shrink_item(p, ents, idx, kblocks, it)) continue;
           const CUtensorMap* ma = p.lora_slot_tmaps + (long long)it.slot * p.lora_maps_per_slot + p.lora_map_a;
           tensormap_fence_acquire_g(ma);
           const CUtensorMap* mx = &xmaps.m[it.wn / 16 - 1];
-          const uint32_t bytes = (uint32_t)((it.box_rows + it.wn) * kBK * 2);
-          for (int kb = it.kb0; kb < it.kb1; ++kb) {
+          // the operands of a shrink item are thin: several k-blocks share a stage, so that the ring holds enough bytes in flight
+          const int a_sub = it.box_rows * kBK * 2, x_sub = it.wn * kBK * 2;
+          const int kps = shrink_kblocks_per_stage(S::kABytes, S::kBBytes, a_sub, x_sub);
+          for (int kb = it.kb0; kb < it.kb1; kb += kps) {
+            const int n = min(kps, it.kb1 - kb);
             if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
               report_status(p.status, kTimeoutEmptyBarrier, -1 - idx);
               *abort_flag = 1;
@@ -325,9 +367,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
               break;
             }
             uint8_t* sa = tiles + stage * S::kStageBytes;
-            mbar_expect_tx(&full_bar[stage], bytes);
-            tma_load_3d(sa, ma, &full_bar[stage], kb * kBK, it.chunk * kBM, p.lora_layer);
-            tma_load_2d_hint(sa + S::kABytes, mx, &full_bar[stage], kb * kBK, it.w0, pol_b);
+            mbar_expect_tx(&full_bar[stage], (uint32_t)(n * (a_sub + x_sub)));
+            for (int q = 0; q < n; ++q) {
+              tma_load_3d(sa + q * a_sub, ma, &full_bar[stage], (kb + q) * kBK, it.chunk * kBM, p.lora_layer);
+              tma_load_2d_hint(sa + S::kABytes + q * x_sub, mx, &full_bar[stage], (kb + q) * kBK, it.w0, pol_b);
+            }
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         }
@@ -352,41 +396,56 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
         if constexpr (LORA) {
-          if (ok && lora && w.kb0 == 0) {
-            // the LoRA delta of this tile: one stage per table entry whose rows meet the token tile
+          if (ok && lora && w.kb0 == 0 && !(p.lora_skip & 2)) {
+            // the LoRA delta of this tile: K slices of 16 ranks of every table entry whose rows meet the token tile, four per stage
             const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
             const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
-            for (int lt = 0; ok && lt < p.lora_num_tiles; ++lt) {
-              ExpandItem e;
-              const int rc = decode_expand_item(p, lt, part, j0, jlim, e);
-              if (rc < 0) break;
-              if (rc == 0) continue;
-              for (int ch = e.chunk_lo; ch <= e.chunk_hi; ++ch) {
-                if (!wait_flag(&p.lora_flags[lt * p.lora_chunks + ch], want, abort_flag)) {
-                  report_status(p.status, kTimeoutSplitK, lt);
-                  *abort_flag = 1;
-                  ok = false;
-                  break;
-                }
+            if (!shrink_seen) {
+              if (!wait_flag(&p.lora_sync[1], (int)gridDim.x, abort_flag)) {
+                report_status(p.status, kTimeoutSplitK, w.tile);
+                *abort_flag = 1;
+                ok = false;
               }
-              if (!ok) break;
-              fence_proxy_async_all();       // the image was written with ordinary stores; the bulk copy reads it
+              fence_proxy_async_all();       // the images were written with ordinary stores; bulk copies read them
+              shrink_seen = true;
+            }
+            const CUtensorMap* umap[kLoraUnitsPerStage];
+            const __nv_bfloat16* uimg[kLoraUnitsPerStage];
+            int uk[kLoraUnitsPerStage];
+            int nu = 0;
+            auto flush = [&]() -> bool {
+              if (nu == 0) return true;
               if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
                 report_status(p.status, kTimeoutEmptyBarrier, w.tile);
                 *abort_flag = 1;
-                ok = false;
-                break;
+                return false;
               }
               uint8_t* sa = tiles + stage * S::kStageBytes;
-              const CUtensorMap* mb = p.lora_slot_tmaps + (long long)e.slot * p.lora_maps_per_slot + p.lora_map_b;
-              tensormap_fence_acquire_g(mb);
-              const uint32_t vbytes = (uint32_t)((e.c1 - e.c0) * kBK * 2);
-              mbar_expect_tx(&full_bar[stage], (uint32_t)S::kABytes + vbytes);
-              tma_load_3d(sa, mb, &full_bar[stage], 0, i0, p.lora_layer);
-              bulk_load_1d(sa + S::kABytes, p.lora_vimg + ((long long)(lt * p.lora_nparts + part) * kLoraWin + (e.c0 - e.w0)) * 64, vbytes,
-                           &full_bar[stage]);
+              const bool no_b = (p.lora_skip & 8) != 0, no_v = (p.lora_skip & 16) != 0;      // measurement only
+              mbar_expect_tx(&full_bar[stage], (uint32_t)(nu * ((no_b ? 0 : kLoraBTileBytes) + (no_v ? 0 : kLoraSliceBytes))));
+              for (int u = 0; u < nu; ++u) {
+                const CUtensorMap* mb = (p.lora_skip & 4) ? umap[0] : umap[u];
+                if (p.lora_fence_maps) tensormap_fence_acquire_g(mb);
+                if (!no_b) tma_load_3d(sa + u * kLoraBTileBytes, mb, &full_bar[stage], uk[u], i0, p.lora_layer);
+                if (!no_v) bulk_load_1d(sa + S::kABytes + u * kLoraSliceBytes, uimg[u], kLoraSliceBytes, &full_bar[stage]);
+              }
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
+              nu = 0;
+              return true;
+            };
+            for (int lt = 0; ok && lt < p.lora_num_tiles; ++lt) {
+              ExpandItem e;
+              const int rc = decode_expand_item(ents, lt, j0, jlim, e);
+              if (rc < 0) break;
+              if (rc == 0) continue;
+              for (int sl = 0; ok && sl < e.r / 16; ++sl) {
+                umap[nu] = p.lora_slot_tmaps + (long long)e.slot * p.lora_maps_per_slot + p.lora_map_b;
+                uimg[nu] = p.lora_vimg + (long long)(lt * p.lora_nparts + part) * kLoraImgElems + sl * kLoraSliceElems;
+                uk[nu] = sl * 16;
+                if (++nu == kLoraUnitsPerStage) ok = flush();
+              }
             }
+            if (ok) ok = flush();
           }
         }
       }
@@ -403,7 +462,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if constexpr (LORA) {
         for (int idx = (int)blockIdx.x; ok && idx < n_shrink; idx += (int)gridDim.x) {
           ShrinkItem it;
-          if (!decode_shrink_item(p, idx, kblocks, it)) continue;
+          if (!decode_shrink_item(p, ents, idx, kblocks, it)) continue;
           if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1, abort_flag)) {
             report_status(p.status, kTimeoutTmemEmpty, -1 - idx);
             *abort_flag = 1;
@@ -413,7 +472,10 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           tc_fence_after();
           const uint32_t tmem_d = tmem_base + (uint32_t)(acc * S::kAcc);
           const uint32_t idesc_s = make_idesc(kBM, (uint32_t)it.wn, kFmtBF16, kFmtBF16);
-          for (int kb = it.kb0; kb < it.kb1; ++kb) {
+          const int a_sub = it.box_rows * kBK * 2, x_sub = it.wn * kBK * 2;
+          const int kps = shrink_kblocks_per_stage(S::kABytes, S::kBBytes, a_sub, x_sub);
+          for (int kb = it.kb0; kb < it.kb1; kb += kps) {
+            const int n = min(kps, it.kb1 - kb);
             if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
               report_status(p.status, kTimeoutFullBarrier, -1 - idx);
               *abort_flag = 1;
@@ -422,11 +484,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             }
             tc_fence_after();
             const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
-            const uint64_t da = make_desc_k_sw128(sa);
-            const uint64_t db = make_desc_k_sw128(sa + S::kABytes);
+            for (int q = 0; q < n; ++q) {
+              const uint64_t da = make_desc_k_sw128(sa + (uint32_t)(q * a_sub));
+              const uint64_t db = make_desc_k_sw128(sa + (uint32_t)(S::kABytes + q * x_sub));
 #pragma unroll
-            for (int k = 0; k < kBK / 16; ++k) {
-              umma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb > it.kb0 || k > 0) ? 1u : 0u);
+              for (int k = 0; k < kBK / 16; ++k) {
+                umma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb + q > it.kb0 || k > 0) ? 1u : 0u);
+              }
             }
             tc_commit(&empty_bar[stage]);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -468,33 +532,44 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
         if (!ok) break;
         if constexpr (LORA) {
-          if (lora && kb0 == 0) {
+          if (lora && kb0 == 0 && !(p.lora_skip & 2)) {
             const int ta = p.b_fastest ? w.tile / tiles_b : w.tile % tiles_a;
             const int tb = p.b_fastest ? w.tile % tiles_b : w.tile / tiles_a;
             const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
             const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
-            for (int lt = 0; ok && lt < p.lora_num_tiles; ++lt) {
-              ExpandItem e;
-              const int rc = decode_expand_item(p, lt, part, j0, jlim, e);
-              if (rc < 0) break;
-              if (rc == 0) continue;
+            int uc0[kLoraUnitsPerStage], uc1[kLoraUnitsPerStage], uw0[kLoraUnitsPerStage];
+            int nu = 0;
+            auto flush = [&]() -> bool {
+              if (nu == 0) return true;
               if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
                 report_status(p.status, kTimeoutFullBarrier, w.tile);
                 *abort_flag = 1;
-                ok = false;
-                break;
+                return false;
               }
               tc_fence_after();
               const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
-              const uint64_t da = make_desc_k_sw128(sa);
-              const uint64_t db = make_desc_k_sw128(sa + S::kABytes);
-              const uint32_t idesc_e = make_idesc(kBM, (uint32_t)(e.c1 - e.c0), kFmtBF16, kFmtBF16);
-              for (int k = 0; k < e.r / 16; ++k) {
-                umma_f16_ss(tmem_d + (uint32_t)(e.c0 - j0), da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_e, 1u);
+              for (int u = 0; u < nu; ++u) {
+                const uint64_t da = make_desc_k_sw32(sa + (uint32_t)(u * kLoraBTileBytes));
+                const uint64_t db = make_desc_k_sw32(sa + (uint32_t)(S::kABytes + u * kLoraSliceBytes + (uc0[u] - uw0[u]) * 32));
+                umma_f16_ss(tmem_d + (uint32_t)(uc0[u] - j0), da, db, make_idesc(kBM, (uint32_t)(uc1[u] - uc0[u]), kFmtBF16, kFmtBF16), 1u);
               }
               tc_commit(&empty_bar[stage]);
               if (++stage == STAGES) { stage = 0; phase ^= 1; }
+              nu = 0;
+              return true;
+            };
+            for (int lt = 0; ok && lt < p.lora_num_tiles; ++lt) {
+              ExpandItem e;
+              const int rc = decode_expand_item(ents, lt, j0, jlim, e);
+              if (rc < 0) break;
+              if (rc == 0) continue;
+              for (int sl = 0; ok && sl < e.r / 16; ++sl) {
+                uc0[nu] = e.c0; uc1[nu] = e.c1; uw0[nu] = e.w0;
+                if (++nu == kLoraUnitsPerStage) ok = flush();
+              }
             }
+            if (ok) ok = flush();
+            (void)i0;
             if (!ok) break;
           }
         }
@@ -515,7 +590,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const int n_ids = p.lora_num_tiles * p.lora_chunks;
       for (int idx = (int)blockIdx.x; alive && idx < n_shrink; idx += (int)gridDim.x) {
         ShrinkItem it;
-        if (!decode_shrink_item(p, idx, kblocks, it)) continue;
+        if (!decode_shrink_item(p, ents, idx, kblocks, it)) continue;
         if (!mbar_wait(&tmem_full[acc], acc_phase[acc], abort_flag)) {
           report_status(p.status, kTimeoutTmemFull, -1 - idx);
           *abort_flag = 1;
@@ -576,23 +651,25 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           const int j = it.chunk * kBM + row_in_tile;          // row of A_cat = (part, rank index)
           if (j < it.R) {
             const int pp = j / it.r, i = j - pp * it.r;
-            __nv_bfloat16* img = p.lora_vimg + (long long)(it.lt * p.lora_nparts + pp) * kLoraImgElems;
+            __nv_bfloat16* img = p.lora_vimg + (long long)(it.lt * p.lora_nparts + pp) * kLoraImgElems + (i >> 4) * kLoraSliceElems;
+            const int ch = (i >> 3) & 1, within = i & 7;
 #pragma unroll
             for (int c = 0; c < kLoraWin; ++c) {
               if (c < it.wn) {
                 const int t = it.w0 + c;
                 const bool live = t >= it.row0 && t < it.row0 + it.nrows;
-                img[c * 64 + ((((i >> 3) ^ (c & 7)) << 3) | (i & 7))] = __float2bfloat16(live ? v[c] : 0.f);
+                img[c * 16 + (((ch ^ ((c >> 2) & 1)) << 3) | within)] = __float2bfloat16(live ? v[c] : 0.f);
               }
             }
           }
-          __threadfence();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (threadIdx.x == 64) {
-            fence_proxy_async_all();
-            st_release_gpu(&p.lora_flags[item_id], want);
-          }
         }
+      }
+      // this CTA's shrink items are done (a K split that was not the last to arrive has handed its partial over)
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (lora && threadIdx.x == 64) {
+        fence_proxy_async_all();
+        red_release_gpu_add(&p.lora_sync[1], 1);
       }
     }
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
@@ -766,14 +843,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if constexpr (LORA) {
-    // the generation moves when every CTA of the launch is past its waits
+    // the last CTA to finish clears the two counters for the next launch (every CTA is past its wait by then)
     if (lora && threadIdx.x == 0) {
       __threadfence();
-      const int prev = atomicAdd(&p.lora_gen[1], 1);
+      const int prev = atomicAdd(&p.lora_sync[0], 1);
       if (prev == (int)gridDim.x - 1) {
-        p.lora_gen[1] = 0;
+        p.lora_sync[0] = 0;
+        p.lora_sync[1] = 0;
         __threadfence();
-        st_release_gpu(p.lora_gen, want);
       }
     }
   }
@@ -947,8 +1024,9 @@ struct LxLoraFused {
   int nparts, n0, n1, layer, max_rank, ksplit;
   void* vimg; long long vimg_bytes;
   float* vpart; long long vpart_bytes;
-  int* flags; int* counters; int n_flags;
-  int* gen;
+  int* counters; int n_counters;
+  int* sync;                    // two ints, zero before the first launch
+  int fence_maps;
 };
 
 static int gemm_impl(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
@@ -1045,7 +1123,11 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
     const long long ids = (long long)lora->num_tiles * p.lora_chunks;
     while (ks > 1 && (long long)ks * ids * kLoraWin * kBM * 4 > lora->vpart_bytes) --ks;
     p.lora_ksplit = ks;
-    p.lora_flags = lora->flags; p.lora_counters = lora->counters; p.lora_gen = lora->gen;
+    p.lora_counters = lora->counters; p.lora_sync = lora->sync; p.lora_fence_maps = lora->fence_maps;
+    {
+      const char* e = getenv("LORAX_LORA_SKIP");       // measurement only
+      p.lora_skip = e ? atoi(e) : 0;
+    }
     p.lora_T = T;
     LoraXMaps xm;
     for (int i = 0; i < 3; ++i) {
@@ -1101,7 +1183,7 @@ int lx_gemm_bf16_lora(const void* x, const void* w, void* out, const void* bias,
   const bool bounds_ok = (lora->nparts == 1) || ((lora->n0 % lx::kBM) == 0 && (lora->nparts == 2 || (lora->n1 % lx::kBM) == 0));
   if (!bounds_ok || lora->max_rank > 64 || lora->max_rank <= 0 || lora->nparts < 1 || lora->nparts > 3 || N < lx::kBM) return 1;
   if ((long long)lora->num_tiles * lora->nparts * lx::kLoraImgElems * 2 > lora->vimg_bytes) return 1;
-  if ((long long)lora->num_tiles * chunks > lora->n_flags) return 1;
+  if ((long long)lora->num_tiles * chunks > lora->n_counters || lora->num_tiles > lx::kLoraMaxEntries) return 1;
   return gemm_impl(x, w, out, bias, T, N, K, ldx, ldw, ldo, 1.f, ws, ws_bytes, counters, status, num_sms, 1, 0, lora, stream_);
 }
 

@@ -50,8 +50,9 @@ struct LxLoraFused {
   int nparts, n0, n1, layer, max_rank, ksplit;
   void* vimg; long long vimg_bytes;
   float* vpart; long long vpart_bytes;
-  int* flags; int* counters; int n_flags;
-  int* gen;
+  int* counters; int n_counters;
+  int* sync;
+  int fence_maps;
 };
 int lx_gemm_bf16_lora(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
                       long long ldw, long long ldo, void* ws, long long ws_bytes, int* counters, int* status, int num_sms,
@@ -106,7 +107,7 @@ struct LxModelDesc {
   int num_slots, max_rank, groups_per_slot, fused_lora;      // fused_lora: LoRA inside the GEMM launch where it can serve the step
   // scratch of the GEMM that carries LoRA in its own launch
   void* lora_vimg; long long lora_vimg_bytes; float* lora_vpart; long long lora_vpart_bytes;
-  int* lora_flags; int* lora_item_counters; int n_lora_flags; int pad4_; int* lora_gen;
+  int* lora_item_counters; int n_lora_item_counters; int lora_fence_maps; int* lora_sync;
 };
 
 struct LxStepDesc {
@@ -152,7 +153,7 @@ int linear_with_lora(const LxModelDesc& m, const LxLayerDesc& l, const LxStepDes
     if (ks > ((K + 63) / 64) / 8) ks = ((K + 63) / 64) / 8;
     f.ksplit = ks < 1 ? 1 : ks;
     f.vimg = m.lora_vimg; f.vimg_bytes = m.lora_vimg_bytes; f.vpart = m.lora_vpart; f.vpart_bytes = m.lora_vpart_bytes;
-    f.flags = m.lora_flags; f.counters = m.lora_item_counters; f.n_flags = m.n_lora_flags; f.gen = m.lora_gen;
+    f.counters = m.lora_item_counters; f.n_counters = m.n_lora_item_counters; f.sync = m.lora_sync; f.fence_maps = m.lora_fence_maps;
     const int rc = lx_gemm_bf16_lora(x, w, y, bias, s.T, N, K, ldx, ldw, ldy, m.gemm_ws, m.gemm_ws_bytes, m.gemm_counters, m.status, m.num_sms,
                                      &f, stream);
     if (rc != 1) return rc;          // 1: this step does not fit the fused launch, use the separate kernels below

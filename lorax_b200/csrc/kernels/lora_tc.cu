@@ -397,6 +397,23 @@ int lx_lora_encode_tmap(void* out, const void* base, int K, int R, long long lay
   return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
 }
 
+// Tensor map of one B_cat family for the GEMM that adds the LoRA delta by UMMAs: {r, N, layers} read in boxes of 16 ranks x
+// 128 features with the 32-byte swizzle (one K slice of a UMMA operand).  base: layer 0's B_cat [N, r].
+int lx_lora_encode_tmap_b(void* out, const void* base, int r, int N, long long layer_stride, int layers) {
+  using namespace lx;
+  EncodeTiledFn2 fn = encode_fn2();
+  if (fn == nullptr) return -1;
+  if ((r % 8) != 0 || (layer_stride % 8) != 0 || (reinterpret_cast<uintptr_t>(base) & 15)) return -2;
+  cuuint64_t dims[3] = {(cuuint64_t)r, (cuuint64_t)N, (cuuint64_t)layers};
+  cuuint64_t strides[2] = {(cuuint64_t)r * 2, (cuuint64_t)layer_stride * 2};
+  cuuint32_t box[3] = {16, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult rc = fn(reinterpret_cast<CUtensorMap*>(out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box,
+                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return rc == CUDA_SUCCESS ? 0 : -(int)rc - 100;
+}
+
 // v[T, ldv] = x[T, K] @ A_cat(slot)^T for every tile of the table.  max_tile_rows selects the token-tile width
 // (<= 32: decode, <= 128: prefill); max_rank bounds the number of 128-row chunks of A_cat.
 int lx_lora_shrink_tc(const void* x, long long ldx, const void* tiles, int num_tiles, int max_tile_rows, const void* slot_tmaps,

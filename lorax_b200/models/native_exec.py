@@ -48,7 +48,7 @@ class LxModelDesc(Structure):
                 ("arena", P), ("slot_base", P), ("slot_rank", P), ("slot_tmaps", P),
                 ("num_slots", I), ("max_rank", I), ("groups_per_slot", I), ("fused_lora", I),
                 ("lora_vimg", P), ("lora_vimg_bytes", L), ("lora_vpart", P), ("lora_vpart_bytes", L),
-                ("lora_flags", P), ("lora_item_counters", P), ("n_lora_flags", I), ("pad4_", I), ("lora_gen", P)]
+                ("lora_item_counters", P), ("n_lora_item_counters", I), ("lora_fence_maps", I), ("lora_sync", P)]
 
 
 class LxStepDesc(Structure):
@@ -139,8 +139,8 @@ class NativeExecutor:
             m.fused_lora = int(model.fused_lora)
             m.lora_vimg, m.lora_vimg_bytes = ws.lora_vimg.data_ptr(), ws.lora_vimg.numel() * 2
             m.lora_vpart, m.lora_vpart_bytes = ws.lora_vpart.data_ptr(), ws.lora_vpart.numel() * 4
-            m.lora_flags, m.lora_item_counters, m.n_lora_flags = ws.lora_flags.data_ptr(), ws.lora_item_counters.data_ptr(), ws.lora_flags.numel()
-            m.lora_gen = ws.lora_gen.data_ptr()
+            m.lora_item_counters, m.n_lora_item_counters = ws.lora_item_counters.data_ptr(), ws.lora_item_counters.numel()
+            m.lora_fence_maps, m.lora_sync = native.LORA_FENCE_MAPS, ws.lora_sync.data_ptr()
         self.m = m
         self.layers = (LxLayerDesc * len(model.layers))()
         for li, lw in enumerate(model.layers):

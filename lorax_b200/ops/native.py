@@ -69,6 +69,7 @@ def load() -> ctypes.CDLL:
         "lx_lora_expand": ([P, I, P, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
         "lx_tensormap_bytes": ([], I),
         "lx_lora_encode_tmap": ([P, P, I, I, L, I], I),
+        "lx_lora_encode_tmap_b": ([P, P, I, I, L, I], I),
         "lx_lora_shrink_tc": ([P, L, P, I, I, P, I, I, P, I, I, I, P, I, L, I, P, P, I, I, I, I, P, P], I),
         "lx_gemm_bf16_lora": ([P, P, P, P, I, I, I, L, L, L, P, L, P, P, I, P, P], I),
         "lx_lora_fused_desc_bytes": ([], I),
@@ -78,6 +79,11 @@ def load() -> ctypes.CDLL:
         "lx_wq4_gemm": ([P, L, P, P, P, P, L, I, I, I, I, P], I),
         "lx_wq4_gemm_ex": ([P, L, P, P, P, P, L, I, I, I, I, I, P], I),
         "lx_lora_expand_tiled": ([P, I, L, I, P, I, I, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
+        "lx_moe_router_logits": ([P, L, P, L, P, I, I, I, P], I),
+        "lx_moe_route": ([P, I, I, I, I, I, P, P, P, P, P, P], I),
+        "lx_moe_gather": ([P, L, P, P, I, P, L, I, I, P], I),
+        "lx_moe_combine": ([P, L, P, P, I, P, L, I, I, P], I),
+        "lx_moe_grouped_gemm": ([P, L, P, L, P, L, P, I, I, I, I, I, P, I, P], I),
     }
     for name, (argtypes, restype) in sigs.items():
         fn = getattr(lib, name)
@@ -102,6 +108,10 @@ def _check(rc: int, what: str):
         raise NativeError(f"{what} failed with code {rc}")
 
 
+STATUS_NAMES = {1: "TMA data never landed", 2: "smem stage never released", 3: "accumulator never completed",
+                4: "accumulator never drained", 5: "peer flag timeout", 6: "split-K / LoRA image timeout", 7: "index out of range"}
+
+
 class Workspace:
     """Device scratch shared by the kernels of one process: split-K partials and counters, split-KV partials,
     the status words written by bounded waits, and the LoRA intermediate."""
@@ -120,13 +130,12 @@ class Workspace:
         self.lora_v = torch.zeros(max_tokens, max_lora_cols, dtype=torch.float32, device=device)     # shrink result
         self.lora_counters = torch.zeros(16384, dtype=torch.int32, device=device)
         # LoRA inside the GEMM launch: bf16 operand images of the shrink results (6 KB per table entry and part), fp32 partials
-        # of their K splits, completion flags and split counters per (entry, 128-row chunk), and the launch generation
+        # of their K splits, split counters per (entry, 128-row chunk), and the two launch-wide counters
         self.lora_max_entries = 1024
         self.lora_vimg = torch.zeros(self.lora_max_entries * 3 * 48 * 64, dtype=torch.bfloat16, device=device)
         self.lora_vpart = torch.empty(1024 * 48 * 128, dtype=torch.float32, device=device)
-        self.lora_flags = torch.zeros(2 * self.lora_max_entries, dtype=torch.int32, device=device)
         self.lora_item_counters = torch.zeros(2 * self.lora_max_entries, dtype=torch.int32, device=device)
-        self.lora_gen = torch.zeros(2, dtype=torch.int32, device=device)
+        self.lora_sync = torch.zeros(2, dtype=torch.int32, device=device)
         self.attn_part_tokens = 256
         self.attn_splits = attn_splits
         self.attn_part_o = torch.empty(self.attn_part_tokens * num_heads * attn_splits * head_dim, dtype=torch.float32, device=device)
@@ -138,9 +147,7 @@ class Workspace:
         st = self.status.tolist()
         if st[0] != 0:
             self.status.zero_()
-            names = {1: "TMA data never landed", 2: "smem stage never released", 3: "accumulator never completed",
-                     4: "accumulator never drained", 5: "peer flag timeout", 6: "split-K timeout", 7: "index out of range"}
-            raise NativeError(f"device status {st[0]} ({names.get(st[0], '?')}), detail {st[1]}")
+            raise NativeError(f"device status {st[0]} ({STATUS_NAMES.get(st[0], '?')}), detail {st[1]}")
 
 
 _workspaces = {}
@@ -177,6 +184,9 @@ class LoraEpilogue(NamedTuple):
     n1: int
 
 
+LORA_FENCE_MAPS = int(os.environ.get("LORAX_LORA_FENCE_MAPS", "1"))
+
+
 class LxLoraFused(ctypes.Structure):
     """Mirror of the C struct of the same name (csrc/kernels/gemm_bf16.cu)."""
     _fields_ = [("tiles", ctypes.c_void_p), ("num_tiles", ctypes.c_int),
@@ -186,8 +196,8 @@ class LxLoraFused(ctypes.Structure):
                 ("max_rank", ctypes.c_int), ("ksplit", ctypes.c_int),
                 ("vimg", ctypes.c_void_p), ("vimg_bytes", ctypes.c_longlong),
                 ("vpart", ctypes.c_void_p), ("vpart_bytes", ctypes.c_longlong),
-                ("flags", ctypes.c_void_p), ("counters", ctypes.c_void_p), ("n_flags", ctypes.c_int),
-                ("gen", ctypes.c_void_p)]
+                ("counters", ctypes.c_void_p), ("n_counters", ctypes.c_int),
+                ("sync", ctypes.c_void_p), ("fence_maps", ctypes.c_int)]
 
 
 class LoraFused(NamedTuple):
@@ -219,8 +229,9 @@ def lora_fused_desc(ws: "Workspace", lf: LoraFused, K: int) -> LxLoraFused:
     d.ksplit = max(1, min(8, ws.num_sms // max(1, live * chunks), ((K + 63) // 64) // 8))      # about one round of shrink items per CTA
     d.vimg, d.vimg_bytes = ws.lora_vimg.data_ptr(), ws.lora_vimg.numel() * 2
     d.vpart, d.vpart_bytes = ws.lora_vpart.data_ptr(), ws.lora_vpart.numel() * 4
-    d.flags, d.counters, d.n_flags = ws.lora_flags.data_ptr(), ws.lora_item_counters.data_ptr(), ws.lora_flags.numel()
-    d.gen = ws.lora_gen.data_ptr()
+    d.counters, d.n_counters = ws.lora_item_counters.data_ptr(), ws.lora_item_counters.numel()
+    d.sync = ws.lora_sync.data_ptr()
+    d.fence_maps = LORA_FENCE_MAPS
     return d
 
 
@@ -267,6 +278,67 @@ def gemm_lora_fused(x: torch.Tensor, w: torch.Tensor, lf: LoraFused, bias: Optio
         return None
     _check(rc, "lx_gemm_bf16_lora")
     return out if given is None else given
+
+
+# ------------------------------------------------------------------------------------------------ mixture of experts
+class MoeRouting(NamedTuple):
+    topk_ids: torch.Tensor     # [T, k] int32
+    topk_w: torch.Tensor       # [T, k] fp32, renormalised over the kept experts
+    seg: torch.Tensor          # [e_local + 1] int32: rows of every local expert in the sorted order
+    pos: torch.Tensor          # [T, k] int32: sorted row of (token, choice), -1 when the expert lives on another rank
+    sorted_tok: torch.Tensor   # [T * k] int32
+
+
+def moe_route(x: torch.Tensor, router_w: torch.Tensor, k: int, e0: int, e_local: int) -> MoeRouting:
+    """Router logits (fp32), softmax over all experts, top-k, renormalise, and the sorted order of the rows routed to the
+    experts [e0, e0 + e_local) this rank owns: two launches, everything stays on the device."""
+    T, H = x.shape
+    E = router_w.shape[0]
+    dev = x.device
+    logits = torch.empty(T, E, dtype=torch.float32, device=dev)
+    lib = load()
+    _check(lib.lx_moe_router_logits(_ptr(x), x.stride(0), _ptr(router_w), router_w.stride(0), _ptr(logits), T, E, H, _stream()), "lx_moe_router_logits")
+    r = MoeRouting(torch.empty(T, k, dtype=torch.int32, device=dev), torch.empty(T, k, dtype=torch.float32, device=dev),
+                   torch.empty(e_local + 1, dtype=torch.int32, device=dev), torch.empty(T, k, dtype=torch.int32, device=dev),
+                   torch.empty(T * k, dtype=torch.int32, device=dev))
+    _check(lib.lx_moe_route(_ptr(logits), T, E, k, e0, e_local, _ptr(r.topk_ids), _ptr(r.topk_w), _ptr(r.seg), _ptr(r.pos), _ptr(r.sorted_tok),
+                            _stream()), "lx_moe_route")
+    return r
+
+
+def moe_grouped_gemm(xg: torch.Tensor, w: torch.Tensor, seg: torch.Tensor, avg_rows: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[q] = xg[q] @ w[e(q)]^T for every sorted row q (e(q): the expert whose run [seg[e], seg[e+1]) holds q).
+    w: [e_local, n_w, K] bf16, n_w a multiple of 128."""
+    e_local, n_w, K = w.shape
+    rows = xg.shape[0]
+    assert w.is_contiguous() and xg.stride(1) == 1 and xg.shape[1] == K
+    if out is None:
+        out = torch.empty(rows, n_w, dtype=torch.bfloat16, device=xg.device)
+    ws = workspace(xg.device)
+    rc = load().lx_moe_grouped_gemm(_ptr(xg), xg.stride(0), _ptr(w), K, _ptr(out), out.stride(0), _ptr(seg), e_local, rows, n_w, K, avg_rows,
+                                    _ptr(ws.status), ws.num_sms, _stream())
+    _check(rc, "lx_moe_grouped_gemm")
+    return out
+
+
+def moe_ffn(x: torch.Tensor, router_w: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, k: int, e0: int, act: str = "silu") -> torch.Tensor:
+    """Top-k mixture-of-experts feed-forward of this rank's experts: route, gather, grouped w1|w3 GEMM, act * up, grouped w2
+    GEMM, weighted combine.  w13: [e_local, 2I, H], w2: [e_local, H, I].  Returns [T, H] (a partial sum under expert parallelism)."""
+    T, H = x.shape
+    e_local, two_i, _ = w13.shape
+    E = router_w.shape[0]
+    r = moe_route(x, router_w, k, e0, e_local)
+    rows = T * k
+    lib = load()
+    xg = torch.empty(rows, H, dtype=torch.bfloat16, device=x.device)
+    _check(lib.lx_moe_gather(_ptr(x), x.stride(0), _ptr(r.sorted_tok), _ptr(r.seg), e_local, _ptr(xg), xg.stride(0), rows, H, _stream()), "lx_moe_gather")
+    avg = max(1, (rows + E - 1) // E)
+    gu = moe_grouped_gemm(xg, w13, r.seg, avg)
+    a = act_mul(gu, two_i // 2, act, gated=True)
+    y = moe_grouped_gemm(a, w2, r.seg, avg)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=x.device)
+    _check(lib.lx_moe_combine(_ptr(y), y.stride(0), _ptr(r.pos), _ptr(r.topk_w), k, _ptr(out), out.stride(0), T, H, _stream()), "lx_moe_combine")
+    return out
 
 
 def quant_act_fp8(x: torch.Tensor):
@@ -465,6 +537,14 @@ def lora_encode_tmap(out_host: torch.Tensor, base_ptr: int, K: int, R: int, laye
     rc = load().lx_lora_encode_tmap(out_host.data_ptr(), base_ptr, K, R, layer_stride, layers)
     if rc != 0:
         raise NativeError(f"lx_lora_encode_tmap failed with code {rc}")
+
+
+def lora_encode_tmap_b(out_host: torch.Tensor, base_ptr: int, r: int, N: int, layer_stride: int, layers: int):
+    """Encode the 3-D tensor map {r, N, layers} of one adapter's B_cat family (boxes of 16 ranks x 128 features, 32-byte
+    swizzle: the operand slices of the GEMM that adds the LoRA delta itself) into 128 bytes of host memory."""
+    rc = load().lx_lora_encode_tmap_b(out_host.data_ptr(), base_ptr, r, N, layer_stride, layers)
+    if rc != 0:
+        raise NativeError(f"lx_lora_encode_tmap_b failed with code {rc}")
 
 
 def lora_shrink_tiles(x: torch.Tensor, tiles: torch.Tensor, num_tiles: int, max_tile_rows: int, slot_tmaps: torch.Tensor,

@@ -116,6 +116,13 @@ class ModelRunner:
             self.anchor_ev.record()
             self.anchor_ev.synchronize()
             self.anchor_host = time.perf_counter()
+        # the kernels' status word rides in every ring entry: a device-side wait that ran out is seen when the step's result is read
+        self.ring_status = [torch.zeros(2, dtype=torch.int32, **pin) for _ in range(self.n_ring)]
+        self.status_word = None
+        if self.is_cuda:
+            from ..ops import native
+            self.status_word = native.workspace(self.device).status
+        self.device_failed = None          # message of the first device-side failure (the shard reports unhealthy from then on)
         self.ring_pos = 0
         self.steps = 0
         self.h2d_bytes = 0
@@ -479,6 +486,8 @@ class ModelRunner:
         self.ring_lp[k][:b].copy_(st.logprobs[:b], non_blocking=True)
         self.d2h_bytes += b * 8
         if self.is_cuda:
+            self.ring_status[k].copy_(self.status_word, non_blocking=True)
+            self.d2h_bytes += 8
             self.ring_ev[k].record()
         self.steps += 1
         return k, b, logits
@@ -492,12 +501,24 @@ class ModelRunner:
         self.ring_lp[k][:n].copy_(lps, non_blocking=True)
         self.d2h_bytes += n * 8
         if self.is_cuda:
+            self.ring_status[k].copy_(self.status_word, non_blocking=True)
+            self.d2h_bytes += 8
             self.ring_ev[k].record()
         return k
 
     def wait(self, k: int):
+        """Results of ring entry `k`.  Raises when a kernel of the step (or an earlier one) gave up on a bounded wait: a peer GPU
+        that stopped answering, a pipeline that never filled.  The status word is cleared so that the next batch starts clean."""
         if self.is_cuda:
             self.ring_ev[k].synchronize()
+            code, detail = int(self.ring_status[k][0]), int(self.ring_status[k][1])
+            if code != 0:
+                from ..ops import native
+                self.status_word.zero_()
+                for st in self.ring_status:
+                    st.zero_()
+                self.device_failed = f"device status {code} ({native.STATUS_NAMES.get(code, '?')}), detail {detail}"
+                raise native.NativeError(self.device_failed)
         return self.ring_ids[k], self.ring_lp[k]
 
     def ring_time(self, k: int) -> float:

@@ -142,6 +142,11 @@ class ShardRuntime:
         return r
 
     def health(self):
+        """Unhealthy once a kernel has given up on a bounded wait (a peer GPU that stopped answering): the step that saw it
+        failed its batch, and the launcher restarts the shard group (the reference's health check fails the same way when a
+        shard's prefill raises, router/src/health.rs:150-178)."""
+        if getattr(self.runner, "device_failed", None):
+            raise RuntimeError("shard is unhealthy: " + self.runner.device_failed)
         if self.model.device.type == "cuda":
             torch.zeros(2, 2, device=self.model.device)
         return self.pb.HealthResponse()

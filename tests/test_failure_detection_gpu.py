@@ -76,3 +76,24 @@ def test_all_reduce_gives_up_on_an_absent_peer_and_recovers():
     finally:
         lib.lx_set_wait_budget_ns(0)
     assert lib.lx_get_wait_budget_ns() == 2_000_000_000
+
+
+def test_status_word_reaches_the_host_with_the_step_result():
+    """A kernel that gave up on a wait writes the status word; it travels in the pinned result ring with the step's tokens, so the
+    engine fails that step without an extra synchronisation, the word is cleared, and the next request is served."""
+    from lorax_b200.config import EngineConfig, tiny_llama
+    from lorax_b200.models.decoder import DecoderModel
+    from lorax_b200.ops import native
+    from lorax_b200.runtime.engine import Engine
+    cfg = tiny_llama()
+    model = DecoderModel.random_init(cfg, torch.device("cuda", 0), torch.bfloat16, seed=0)
+    eng = Engine(model, EngineConfig(max_total_tokens=128, max_batch_prefill_tokens=256), num_blocks=64, max_batch=4)
+    want = eng.generate([[5, 6, 7, 8, 9]], max_new_tokens=4)[0]
+    ws = native.workspace(model.device)
+    ws.status.copy_(torch.tensor([5, 4007], dtype=torch.int32))          # what a timed-out peer wait leaves behind
+    with pytest.raises(native.NativeError, match="peer flag timeout.*4007"):
+        eng.generate([[5, 6, 7, 8, 9]], max_new_tokens=4)
+    assert ws.status.tolist() == [0, 0] and "4007" in eng.runner.device_failed
+    # a fresh engine on the same context serves again
+    eng2 = Engine(model, EngineConfig(max_total_tokens=128, max_batch_prefill_tokens=256), num_blocks=64, max_batch=4)
+    assert eng2.generate([[5, 6, 7, 8, 9]], max_new_tokens=4)[0] == want

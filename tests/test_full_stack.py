@@ -385,6 +385,34 @@ def test_prefix_cache_holds_only_tokens_whose_kv_was_written(stack):
             proc.kill()
 
 
+def test_health_turns_false_after_a_device_side_failure(stack):
+    """A step that finds the kernels' status word set (a bounded wait that ran out on the device) fails its batch: the client
+    gets 424, the router drops the batch, and /health, which probes the shard after a failed generation as the reference does
+    (router/src/health.rs:150-178), stays 503 until the shard is healthy again."""
+    from lorax_b200.ops.native import NativeError
+    port, rt = stack["port"], stack["rt"]
+    inner = rt.runner.wait
+
+    def failing_wait(k):
+        rt.runner.device_failed = "device status 5 (peer flag timeout), detail 4007"
+        raise NativeError(rt.runner.device_failed)
+    rt.runner.wait = failing_wait
+    try:
+        st, body, _ = _post(port, "/generate", {"inputs": "w5 w6 w7", "parameters": {"max_new_tokens": 4}})
+        assert st == 424 and "peer flag timeout" in body, (st, body)
+        with pytest.raises(urllib.error.HTTPError) as ei:
+            urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=5)
+        assert ei.value.code == 503
+    finally:
+        rt.runner.wait = inner
+        rt.runner.device_failed = None
+    assert not rt.seqs                                                   # the failed batch was cleared on the shard
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=5) as r:
+        assert r.status == 200
+    st, body, _ = _post(port, "/generate", {"inputs": "w5 w6 w7", "parameters": {"max_new_tokens": 4}})
+    assert st == 200, body
+
+
 def test_merge_adapter_weights_equals_the_adapter_applied_at_run_time(stack):
     """`--merge-adapter-weights`: the adapter folded into the base weights at load time generates what the same adapter applied
     per request generates."""

@@ -359,7 +359,7 @@ def test_gemm_with_lora_in_the_same_launch(nat, T, K, parts, ranks):
     tm_host = torch.zeros(len(ranks) * 2 * G * 128, dtype=torch.uint8).pin_memory()
     for s, r in enumerate(ranks):
         nat.lora_encode_tmap(tm_host[(s * 2 * G + 0) * 128:], arena.data_ptr() + bases[s] * 2, K, nparts * r, r * layer_units, L)
-        nat.lora_encode_tmap(tm_host[(s * 2 * G + G) * 128:], arena.data_ptr() + (bases[s] + r * nparts * K) * 2, r, N, r * layer_units, L)
+        nat.lora_encode_tmap_b(tm_host[(s * 2 * G + G) * 128:], arena.data_ptr() + (bases[s] + r * nparts * K) * 2, r, N, r * layer_units, L)
     tmaps = tm_host.cuda()
     seg = [(-1, 3), (0, 5), (2, T // 3), (1, 1), (3, T // 4), (-1, 2)]
     rows = []
@@ -396,6 +396,55 @@ def test_gemm_with_lora_in_the_same_launch(nat, T, K, parts, ranks):
         untouched = [i for i, s_ in enumerate(rows) if s_ < 0]
         base = nat.gemm(x, w, bias=b, mode=1)
         assert _rel_err(got[untouched], base[untouched]) < 1e-6
+
+
+@pytest.mark.parametrize("T,E,k,H,I,e0,e_local", [(7, 8, 2, 512, 256, 0, 8), (256, 8, 2, 1024, 768, 0, 8), (300, 8, 2, 512, 256, 2, 2),
+                                                  (1500, 16, 4, 256, 128, 0, 16), (64, 4, 1, 256, 384, 1, 1)])
+def test_moe_ffn_on_the_device(nat, T, E, k, H, I, e0, e_local):
+    """Routing kernel, gather, grouped tcgen05 GEMMs and combine against the dense fp32 mixture of experts: softmax over all
+    experts, top-k, renormalised weights; under expert parallelism (e_local < E) only the local experts' share."""
+    torch.manual_seed(T + E)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    wr = (torch.randn(E, H, device="cuda") * 0.3).to(torch.bfloat16)
+    w13 = (torch.randn(e_local, 2 * I, H, device="cuda") / math.sqrt(H)).to(torch.bfloat16)
+    w2 = (torch.randn(e_local, H, I, device="cuda") / math.sqrt(I)).to(torch.bfloat16)
+    r = nat.moe_route(x, wr, k, e0, e_local)
+    torch.cuda.synchronize()
+    logits = x.float() @ wr.float().t()
+    probs = torch.softmax(logits, -1)
+    topv, topi = probs.topk(k, -1)
+    # the kernel's choice may differ from torch's on near ties: compare the kept probability mass, and ids where the gap is clear
+    gap = (probs.sort(-1, descending=True).values[:, k - 1] - probs.sort(-1, descending=True).values[:, k]) if k < E else torch.ones(T, device="cuda")
+    clear = gap > 1e-3
+    assert torch.equal(r.topk_ids[clear].long().sort(-1).values, topi[clear].sort(-1).values)
+    wsum = r.topk_w.sum(-1)
+    assert torch.allclose(wsum, torch.ones_like(wsum), atol=1e-5)
+    seg = r.seg.tolist()
+    assert seg[0] == 0 and all(a <= b for a, b in zip(seg, seg[1:]))
+    ids = r.topk_ids.long()
+    for e in range(e_local):
+        assert seg[e + 1] - seg[e] == int((ids == e0 + e).sum())
+    pos = r.pos.long()
+    local = (ids >= e0) & (ids < e0 + e_local)
+    assert (pos[~local] == -1).all() and (pos[local] >= 0).all()
+    st = r.sorted_tok.long()
+    tok = torch.arange(T, device="cuda")[:, None].expand(T, k)
+    assert torch.equal(st[pos[local]], tok[local])
+    out = nat.moe_ffn(x, wr, w13, w2, k, e0, "silu")
+    torch.cuda.synchronize()
+    nat.workspace().check_status()
+    # oracle with the kernel's own routing decision (so that near ties do not matter), dense fp32 experts
+    want = torch.zeros(T, H, device="cuda")
+    for e in range(e_local):
+        sel = (ids == e0 + e)
+        wt = (r.topk_w * sel).sum(-1)
+        rows = wt > 0
+        if rows.any():
+            gu = x[rows].float() @ w13[e].float().t()
+            a = (torch.nn.functional.silu(gu[:, :I]) * gu[:, I:]).to(torch.bfloat16).float()
+            y = (a @ w2[e].float().t()).to(torch.bfloat16).float()
+            want[rows] += y * wt[rows, None]
+    assert _rel_err(out, want) < 1.2e-2
 
 
 @pytest.mark.parametrize("T,N,K", [(1, 256, 256), (16, 4096, 4096), (48, 1024, 14336), (100, 6144, 4096), (128, 384, 512),
