@@ -286,6 +286,10 @@ class EngineConfig:
     max_batch_total_tokens: Optional[int] = None
     waiting_served_ratio: float = 1.2
     max_waiting_tokens: int = 20
+    # in-process engine, saturated queue: let this many rows drain (for at most that many decode steps) before new prompts
+    # interrupt the running batch, so that one prefill pass serves several prompts and most steps stay pure decode graphs
+    prefill_min_rows: int = 8
+    prefill_max_wait_steps: int = 8
     max_active_adapters: int = 1024
     adapter_cycle_time_s: int = 2
     adapter_memory_fraction: float = 0.1

@@ -74,7 +74,7 @@ struct GemmParams {
   int lora_ksplit, lora_chunks;        // K splits of a shrink item; 128-row chunks of A_cat (nparts * max rank / 128, rounded up)
   int* lora_counters;                  // [tile * chunks] arrivals of the K splits, zero between launches
   int* lora_sync;                      // [2] CTAs of this launch that have finished / whose shrink items are done; zero between launches
-  int lora_fence_maps;                 // 1: acquire-fence a slot's B_cat map before every use (0: once, with its A_cat map, per shrink item)
+  int lora_fence_maps;                 // 1: acquire-fence a slot's B_cat map before every use (0: never; measurement only)
   int lora_skip;                       // measurement only: bit 0 leaves out the shrink items, bit 1 the expand stages (results are then wrong)
   int lora_T;                          // rows of the step
 };
@@ -259,6 +259,38 @@ struct GemmWorkIter {
   }
 };
 
+// ---- expand units, built by a whole warp ------------------------------------------------------------------------
+// A unit = one K slice (16 ranks) of one table entry that meets the token tile.  The producer warp and the MMA warp each
+// build the same list in their own shared-memory area, 32 entries at a time (one per lane, ranks -> slices by a warp prefix
+// sum): walking the table in a single thread costs more than the base tile itself.
+constexpr int kLoraListCap = 256;       // units a list holds; it is worked off whenever it holds 128 or more
+template <bool PRODUCER>
+LX_DEVICE int lora_build_units(const GemmParams& p, const LoraEnt* ents, int lt0, int part, int j0, int jlim, int4* list, int n, bool& ended) {
+  const int lane = threadIdx.x & 31;
+  const int lt = lt0 + lane;
+  ExpandItem e;
+  const int rc = lt < p.lora_num_tiles ? decode_expand_item(ents, lt, j0, jlim, e) : -1;
+  const unsigned endmask = __ballot_sync(0xffffffffu, rc < 0);
+  const int first_end = endmask ? __ffs(endmask) - 1 : 32;
+  const int nsl = (rc == 1 && lane < first_end) ? e.r / 16 : 0;
+  int incl = nsl;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= d) incl += t;
+  }
+  const int excl = incl - nsl;
+  const int total = __shfl_sync(0xffffffffu, incl, 31);
+  for (int sl = 0; sl < nsl; ++sl) {
+    const int idx = n + excl + sl;
+    if (idx < kLoraListCap)
+      list[idx] = PRODUCER ? make_int4(e.slot, (lt * p.lora_nparts + part) * 4 + sl, sl * 16, 0) : make_int4(e.c0, e.c1, e.w0, 0);
+  }
+  ended = endmask != 0;
+  __syncwarp();
+  return min(n + total, kLoraListCap);
+}
+
 // x through boxes of 16, 32 and 48 rows: a shrink item loads only the 16-aligned window its rows lie in.
 struct LoraXMaps { CUtensorMap m[3]; };
 
@@ -274,7 +306,7 @@ struct GemmSmem {
   static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kEntBytes = LORA ? kLoraMaxEntries * (int)sizeof(LoraEnt) : 0;
+  static constexpr int kEntBytes = LORA ? kLoraMaxEntries * (int)sizeof(LoraEnt) + 2 * kLoraListCap * 16 : 0;    // entry table + two unit lists
   static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + kEntBytes + 1024;  // +1024 for manual alignment
 };
 
@@ -295,6 +327,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_base_slot + 2));
   LoraEnt* ents = reinterpret_cast<LoraEnt*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes);
+  int4* ulist_p = reinterpret_cast<int4*>(ents + kLoraMaxEntries);      // producer warp's expand units
+  int4* ulist_m = ulist_p + kLoraListCap;                               // MMA warp's
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -341,14 +375,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   // Work item w -> (tile, split).  Tiles are ordered with the A tile index fastest inside one B tile so that
   // CTAs running at the same time share the B operand through L2.
   if (warp == 0) {
-    if (lane == 0) {
-      const uint64_t pol_a = p.hint_a_first ? policy_evict_first() : policy_evict_last();
-      const uint64_t pol_b = p.hint_a_first ? policy_evict_last() : policy_evict_first();
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      bool shrink_seen = false;
-      if constexpr (LORA) {
+    // Lane 0 feeds the ring for shrink items and base k-blocks; the LoRA stages of a tile are fed by the whole warp.
+    const uint64_t pol_a = p.hint_a_first ? policy_evict_first() : policy_evict_last();
+    const uint64_t pol_b = p.hint_a_first ? policy_evict_last() : policy_evict_first();
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    bool shrink_seen = false;
+    if constexpr (LORA) {
+      if (lane == 0) {
         for (int idx = (int)blockIdx.x; ok && idx < n_shrink; idx += (int)gridDim.x) {
           ShrinkItem it;
           if (!decode_shrink_item(p, ents, idx, kblocks, it)) continue;
@@ -376,11 +411,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           }
         }
       }
-      GemmWorkIter<BN> it(p, num_tiles, kblocks);
-      GemmWork w;
-      while (ok && it.next(w)) {
-        const int ta = p.b_fastest ? w.tile / tiles_b : w.tile % tiles_a;
-        const int tb = p.b_fastest ? w.tile % tiles_b : w.tile / tiles_a;
+    }
+    GemmWorkIter<BN> it(p, num_tiles, kblocks);
+    GemmWork w;
+    while (it.next(w)) {
+      const int ta = p.b_fastest ? w.tile / tiles_b : w.tile % tiles_a;
+      const int tb = p.b_fastest ? w.tile % tiles_b : w.tile / tiles_a;
+      if (lane == 0 && ok) {
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
             report_status(p.status, kTimeoutEmptyBarrier, w.tile);
@@ -395,71 +432,82 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           tma_load_2d_hint(sb, &tmap_b, &full_bar[stage], kb * kBK, tb * p.bn, pol_b);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if constexpr (LORA) {
-          if (ok && lora && w.kb0 == 0 && !(p.lora_skip & 2)) {
-            // the LoRA delta of this tile: K slices of 16 ranks of every table entry whose rows meet the token tile, four per stage
-            const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
-            const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
-            if (!shrink_seen) {
+      }
+      if constexpr (LORA) {
+        if (lora && w.kb0 == 0 && !(p.lora_skip & 2)) {
+          // the LoRA delta of this tile: K slices of 16 ranks of every table entry whose rows meet the token tile, four per stage
+          __syncwarp();
+          stage = __shfl_sync(0xffffffffu, stage, 0);
+          phase = __shfl_sync(0xffffffffu, phase, 0);
+          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+          const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
+          const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
+          if (ok && !shrink_seen) {
+            if (lane == 0) {
               if (!wait_flag(&p.lora_sync[1], (int)gridDim.x, abort_flag)) {
                 report_status(p.status, kTimeoutSplitK, w.tile);
                 *abort_flag = 1;
-                ok = false;
-              }
-              fence_proxy_async_all();       // the images were written with ordinary stores; bulk copies read them
-              shrink_seen = true;
-            }
-            const CUtensorMap* umap[kLoraUnitsPerStage];
-            const __nv_bfloat16* uimg[kLoraUnitsPerStage];
-            int uk[kLoraUnitsPerStage];
-            int nu = 0;
-            auto flush = [&]() -> bool {
-              if (nu == 0) return true;
-              if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
-                report_status(p.status, kTimeoutEmptyBarrier, w.tile);
-                *abort_flag = 1;
-                return false;
-              }
-              uint8_t* sa = tiles + stage * S::kStageBytes;
-              const bool no_b = (p.lora_skip & 8) != 0, no_v = (p.lora_skip & 16) != 0;      // measurement only
-              mbar_expect_tx(&full_bar[stage], (uint32_t)(nu * ((no_b ? 0 : kLoraBTileBytes) + (no_v ? 0 : kLoraSliceBytes))));
-              for (int u = 0; u < nu; ++u) {
-                const CUtensorMap* mb = (p.lora_skip & 4) ? umap[0] : umap[u];
-                if (p.lora_fence_maps) tensormap_fence_acquire_g(mb);
-                if (!no_b) tma_load_3d(sa + u * kLoraBTileBytes, mb, &full_bar[stage], uk[u], i0, p.lora_layer);
-                if (!no_v) bulk_load_1d(sa + S::kABytes + u * kLoraSliceBytes, uimg[u], kLoraSliceBytes, &full_bar[stage]);
-              }
-              if (++stage == STAGES) { stage = 0; phase ^= 1; }
-              nu = 0;
-              return true;
-            };
-            for (int lt = 0; ok && lt < p.lora_num_tiles; ++lt) {
-              ExpandItem e;
-              const int rc = decode_expand_item(ents, lt, j0, jlim, e);
-              if (rc < 0) break;
-              if (rc == 0) continue;
-              for (int sl = 0; ok && sl < e.r / 16; ++sl) {
-                umap[nu] = p.lora_slot_tmaps + (long long)e.slot * p.lora_maps_per_slot + p.lora_map_b;
-                uimg[nu] = p.lora_vimg + (long long)(lt * p.lora_nparts + part) * kLoraImgElems + sl * kLoraSliceElems;
-                uk[nu] = sl * 16;
-                if (++nu == kLoraUnitsPerStage) ok = flush();
               }
             }
-            if (ok) ok = flush();
+            __syncwarp();
+            ok = (*abort_flag == 0);
+            fence_proxy_async_all();       // the images were written with ordinary stores; bulk copies read them
+            shrink_seen = true;
+          }
+          constexpr int kRound = STAGES * kLoraUnitsPerStage;       // units that fill the ring once (<= 32)
+          int n = 0;
+          bool ended = false;
+          for (int lt0 = 0; ok && !ended && lt0 < p.lora_num_tiles; lt0 += 32) {
+            n = lora_build_units<true>(p, ents, lt0, part, j0, jlim, ulist_p, n, ended);
+            const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
+            if (n < 128 && !last) continue;
+            // work the list off, one trip around the ring per round: lane i feeds unit i of the round
+            for (int base = 0; ok && base < n; base += kRound) {
+              const int gu = base + lane;
+              if (lane < kRound && gu < n) {
+                const int sidx = lane / kLoraUnitsPerStage, u = lane % kLoraUnitsPerStage;
+                const int pos = stage + sidx;
+                const int sring = pos >= STAGES ? pos - STAGES : pos;
+                const uint32_t ph = phase ^ (pos >= STAGES ? 1u : 0u);
+                if (!mbar_wait(&empty_bar[sring], ph ^ 1, abort_flag)) {
+                  report_status(p.status, kTimeoutEmptyBarrier, w.tile);
+                  *abort_flag = 1;
+                } else {
+                  uint8_t* sa = tiles + sring * S::kStageBytes;
+                  if (u == 0) {
+                    const int in_stage = min(kLoraUnitsPerStage, n - (base + sidx * kLoraUnitsPerStage));
+                    mbar_expect_tx(&full_bar[sring], (uint32_t)(in_stage * (kLoraBTileBytes + kLoraSliceBytes)));
+                  }
+                  const int4 q = ulist_p[gu];
+                  const CUtensorMap* mb = p.lora_slot_tmaps + (long long)q.x * p.lora_maps_per_slot + p.lora_map_b;
+                  if (p.lora_fence_maps) tensormap_fence_acquire_g(mb);
+                  tma_load_3d(sa + u * kLoraBTileBytes, mb, &full_bar[sring], q.z, i0, p.lora_layer);
+                  bulk_load_1d(sa + S::kABytes + u * kLoraSliceBytes, p.lora_vimg + (long long)q.y * kLoraSliceElems, kLoraSliceBytes,
+                               &full_bar[sring]);
+                }
+              }
+              const int used = min(kRound, n - base);
+              const int pos = stage + (used + kLoraUnitsPerStage - 1) / kLoraUnitsPerStage;
+              if (pos >= STAGES) { stage = pos - STAGES; phase ^= 1; } else stage = pos;
+              __syncwarp();
+              ok = (*abort_flag == 0);
+            }
+            n = 0;
           }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = make_idesc(kBM, (uint32_t)p.umma_n, kFmtBF16, kFmtBF16);
-      int stage = 0;
-      uint32_t phase = 0;
-      int acc = 0;
-      uint32_t acc_phase[2] = {0, 0};
-      bool ok = true;
-      if constexpr (LORA) {
+    // Lane 0 issues every MMA; the whole warp builds the unit list of a tile's LoRA stages.
+    const uint32_t idesc = make_idesc(kBM, (uint32_t)p.umma_n, kFmtBF16, kFmtBF16);
+    int stage = 0;
+    uint32_t phase = 0;
+    int acc = 0;
+    uint32_t acc_phase[2] = {0, 0};
+    bool ok = true;
+    if constexpr (LORA) {
+      if (lane == 0) {
         for (int idx = (int)blockIdx.x; ok && idx < n_shrink; idx += (int)gridDim.x) {
           ShrinkItem it;
           if (!decode_shrink_item(p, ents, idx, kblocks, it)) continue;
@@ -501,18 +549,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           acc ^= 1;
         }
       }
-      GemmWorkIter<BN> it(p, num_tiles, kblocks);
-      GemmWork w;
-      while (ok && it.next(w)) {
-        const int kb0 = w.kb0, kb1 = w.kb1;
+    }
+    GemmWorkIter<BN> it(p, num_tiles, kblocks);
+    GemmWork w;
+    while (it.next(w)) {
+      const int kb0 = w.kb0, kb1 = w.kb1;
+      const uint32_t tmem_d = tmem_base + (uint32_t)(acc * S::kAcc);
+      if (lane == 0 && ok) {
         if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1, abort_flag)) {
           report_status(p.status, kTimeoutTmemEmpty, w.tile);
           *abort_flag = 1;
-          break;
+          ok = false;
         }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + (uint32_t)(acc * S::kAcc);
-        for (int kb = kb0; kb < kb1; ++kb) {
+        for (int kb = kb0; ok && kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
             report_status(p.status, kTimeoutFullBarrier, w.tile);
             *abort_flag = 1;
@@ -530,53 +580,53 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           tc_commit(&empty_bar[stage]);   // releases the smem stage when these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (!ok) break;
-        if constexpr (LORA) {
-          if (lora && kb0 == 0 && !(p.lora_skip & 2)) {
-            const int ta = p.b_fastest ? w.tile / tiles_b : w.tile % tiles_a;
-            const int tb = p.b_fastest ? w.tile % tiles_b : w.tile / tiles_a;
-            const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
-            const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
-            int uc0[kLoraUnitsPerStage], uc1[kLoraUnitsPerStage], uw0[kLoraUnitsPerStage];
-            int nu = 0;
-            auto flush = [&]() -> bool {
-              if (nu == 0) return true;
-              if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
-                report_status(p.status, kTimeoutFullBarrier, w.tile);
-                *abort_flag = 1;
-                return false;
-              }
-              tc_fence_after();
-              const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
-              for (int u = 0; u < nu; ++u) {
-                const uint64_t da = make_desc_k_sw32(sa + (uint32_t)(u * kLoraBTileBytes));
-                const uint64_t db = make_desc_k_sw32(sa + (uint32_t)(S::kABytes + u * kLoraSliceBytes + (uc0[u] - uw0[u]) * 32));
-                umma_f16_ss(tmem_d + (uint32_t)(uc0[u] - j0), da, db, make_idesc(kBM, (uint32_t)(uc1[u] - uc0[u]), kFmtBF16, kFmtBF16), 1u);
-              }
-              tc_commit(&empty_bar[stage]);
-              if (++stage == STAGES) { stage = 0; phase ^= 1; }
-              nu = 0;
-              return true;
-            };
-            for (int lt = 0; ok && lt < p.lora_num_tiles; ++lt) {
-              ExpandItem e;
-              const int rc = decode_expand_item(ents, lt, j0, jlim, e);
-              if (rc < 0) break;
-              if (rc == 0) continue;
-              for (int sl = 0; ok && sl < e.r / 16; ++sl) {
-                uc0[nu] = e.c0; uc1[nu] = e.c1; uw0[nu] = e.w0;
-                if (++nu == kLoraUnitsPerStage) ok = flush();
+      }
+      if constexpr (LORA) {
+        if (lora && kb0 == 0 && !(p.lora_skip & 2)) {
+          __syncwarp();
+          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+          const int ta = p.b_fastest ? w.tile / tiles_b : w.tile % tiles_a;
+          const int tb = p.b_fastest ? w.tile % tiles_b : w.tile / tiles_a;
+          const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
+          const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
+          int n = 0;
+          bool ended = false;
+          for (int lt0 = 0; ok && !ended && lt0 < p.lora_num_tiles; lt0 += 32) {
+            n = lora_build_units<false>(p, ents, lt0, part, j0, jlim, ulist_m, n, ended);
+            const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
+            if (n < 128 && !last) continue;
+            if (lane == 0) {
+              for (int base = 0; ok && base < n; base += kLoraUnitsPerStage) {
+                if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+                  report_status(p.status, kTimeoutFullBarrier, w.tile);
+                  *abort_flag = 1;
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
+                const int nu = min(kLoraUnitsPerStage, n - base);
+                for (int u = 0; u < nu; ++u) {
+                  const int4 q = ulist_m[base + u];                  // (c0, c1, w0): accumulator columns [c0, c1) of a window that starts at w0
+                  const uint64_t da = make_desc_k_sw32(sa + (uint32_t)(u * kLoraBTileBytes));
+                  const uint64_t db = make_desc_k_sw32(sa + (uint32_t)(S::kABytes + u * kLoraSliceBytes + (q.x - q.z) * 32));
+                  if (!(p.lora_skip & 32))
+                    umma_f16_ss(tmem_d + (uint32_t)(q.x - j0), da, db, make_idesc(kBM, (uint32_t)(q.y - q.x), kFmtBF16, kFmtBF16), 1u);
+                }
+                tc_commit(&empty_bar[stage]);
+                if (++stage == STAGES) { stage = 0; phase ^= 1; }
               }
             }
-            if (ok) ok = flush();
-            (void)i0;
-            if (!ok) break;
+            __syncwarp();                                            // the list is rebuilt by every lane
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            n = 0;
           }
+          (void)i0;
         }
-        tc_commit(&tmem_full[acc]);       // accumulator complete
-        acc_phase[acc] ^= 1;
-        acc ^= 1;
       }
+      if (lane == 0 && ok) tc_commit(&tmem_full[acc]);       // accumulator complete
+      acc_phase[acc] ^= 1;
+      acc ^= 1;
     }
     __syncwarp();
   } else {

@@ -104,7 +104,7 @@ struct LxModelDesc {
   float* attn_part_o; float* attn_part_lse; int attn_splits; int attn_part_tokens;
   // adapters
   const void* arena; const long long* slot_base; const int* slot_rank; const void* slot_tmaps;
-  int num_slots, max_rank, groups_per_slot, fused_lora;      // fused_lora: LoRA inside the GEMM launch where it can serve the step
+  int num_slots, max_rank, groups_per_slot, fused_lora;      // fused_lora: rows up to which LoRA rides inside the GEMM launch (0: never)
   // scratch of the GEMM that carries LoRA in its own launch
   void* lora_vimg; long long lora_vimg_bytes; float* lora_vpart; long long lora_vpart_bytes;
   int* lora_item_counters; int n_lora_item_counters; int lora_fence_maps; int* lora_sync;
@@ -139,7 +139,7 @@ int linear_with_lora(const LxModelDesc& m, const LxLayerDesc& l, const LxStepDes
                      const void* w, long long ldw, const void* bias, void* y, long long ldy, int N, int K, void* stream) {
   const LxLoraSite& site = l.lora[site_idx];
   const bool lora = s.tok_slot != nullptr && site.enabled && m.max_rank > 0 && (s.lora_tiles == nullptr || s.num_tiles > 0);
-  if (lora && s.lora_tiles != nullptr && m.fused_lora && s.max_tile_rows <= 32) {
+  if (lora && s.lora_tiles != nullptr && s.T <= m.fused_lora && s.max_tile_rows <= 32) {
     // one launch: shrink items, base tiles, expand UMMAs
     LxLoraFused f{};
     f.tiles = s.lora_tiles; f.num_tiles = s.num_tiles;

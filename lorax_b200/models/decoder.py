@@ -155,7 +155,11 @@ class DecoderModel:
         self.use_native_layers = self.device.type == "cuda" and os.environ.get("LORAX_NATIVE_LAYERS", "1") != "0"
         # LoRA expand inside the GEMM epilogue instead of its own launch (slower than the separate kernel at present:
         # four epilogue warps cannot hide the latency of the per-token B rows)
-        self.fused_lora = os.environ.get("LORAX_FUSED_LORA", "0") != "0"      # LoRA inside the GEMM launch (0: separate kernels)
+        # LoRA inside the GEMM launch for steps of up to this many rows (0: always separate shrink / expand kernels).  Measured on
+        # B200: ahead of the three launches for decode batches, behind them from about a thousand rows (the fused launch keeps the
+        # weights on the UMMA M side, which the plain GEMM gives up above 128 rows)
+        self.fused_lora_max_tokens = int(os.environ.get("LORAX_FUSED_LORA_MAX_TOKENS", "512")) if os.environ.get("LORAX_FUSED_LORA", "1") != "0" else 0
+        self.fused_lora = self.fused_lora_max_tokens > 0
         self.gated = c.model_type not in ("gpt2", "gpt_bigcode", "gpt_neox", "falcon", "RefinedWeb", "RefinedWebModel", "phi", "bloom",
                                           "mpt", "opt")
         if c.alibi:
@@ -391,7 +395,8 @@ class DecoderModel:
         that is ONE launch (shrink items, base tiles, expand UMMAs); otherwise a shrink launch, the GEMM and an expand launch."""
         ts = tok_slot if tok_slot is not None else inp.tok_slot
         epi = None
-        if (self.fused_lora and self.adapters is not None and ts is not None and inp.lora_tiles is not None and x.is_cuda
+        if (self.fused_lora and x.shape[0] <= self.fused_lora_max_tokens and self.adapters is not None and ts is not None
+                and inp.lora_tiles is not None and x.is_cuda
                 and isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16):
             lf = self.adapters.fused(group, layer, inp.lora_tiles)
             if lf is not None:

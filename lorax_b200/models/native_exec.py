@@ -136,7 +136,7 @@ class NativeExecutor:
             m.arena, m.slot_base, m.slot_rank, m.slot_tmaps = (ad.arena.data_ptr(), ad.slot_base.data_ptr(), ad.slot_rank.data_ptr(),
                                                                ad.slot_tmaps.data_ptr())
             m.num_slots, m.max_rank, m.groups_per_slot = ad.slot_rank.shape[0], ad.max_rank, ad.groups_per_slot
-            m.fused_lora = int(model.fused_lora)
+            m.fused_lora = int(model.fused_lora_max_tokens)        # rows up to which LoRA rides inside the GEMM launch
             m.lora_vimg, m.lora_vimg_bytes = ws.lora_vimg.data_ptr(), ws.lora_vimg.numel() * 2
             m.lora_vpart, m.lora_vpart_bytes = ws.lora_vpart.data_ptr(), ws.lora_vpart.numel() * 4
             m.lora_item_counters, m.n_lora_item_counters = ws.lora_item_counters.data_ptr(), ws.lora_item_counters.numel()
@@ -232,7 +232,7 @@ class NativeExecutor:
             native._check(rc, "lx_run_layers")
             pending = fused.ar_out[: T * m.H].view(T, m.H) if ar is not None else out_a
             assert out_ptr.value == pending.data_ptr()
-            fused_lora = bool(m.fused_lora) and s.lora_tiles and s.max_tile_rows <= 32 and m.max_rank <= 64     # LoRA adds no launch then
+            fused_lora = T <= m.fused_lora and s.lora_tiles and s.max_tile_rows <= 32 and m.max_rank <= 64     # LoRA adds no launch then
             lora_sites = 4 if (s.tok_slot and not fused_lora) else 0
             attn_kernels = (1 if s.n_decode else 0) + (1 if T > s.n_decode else 0)
             native.launch_count += nL * (10 + attn_kernels + 2 * lora_sites + (2 if ar is not None else 0)) - 1      # `_check` counted one

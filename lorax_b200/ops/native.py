@@ -184,6 +184,8 @@ class LoraEpilogue(NamedTuple):
     n1: int
 
 
+# 1 (default): the GEMM that carries LoRA acquire-fences a slot's B_cat tensor map before every use, as a tensor map that lives
+# in global memory and was written by a copy asks for; 0 skips it (measurement: the fences cost about 3 % of a decode step).
 LORA_FENCE_MAPS = int(os.environ.get("LORAX_LORA_FENCE_MAPS", "1"))
 
 

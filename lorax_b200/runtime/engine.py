@@ -172,6 +172,10 @@ class Engine:
             # a shrinking batch makes room: admit when the gap to the target batch is worth a prefill step
             if len(self.waiting) < min(min_size, free_rows):
                 return []
+            # enough requests wait to fill every free row: gather a few rows first, one prefill pass then serves several prompts
+            if (free_rows < min(self.cfg.prefill_min_rows, len(self.waiting), self.runner.max_batch)
+                    and self.steps_since_prefill < self.cfg.prefill_max_wait_steps):
+                return []
         picked: List[Tuple[GenRequest, List[int]]] = []
         self._picking = set()           # adapters of requests admitted in this pass: not eviction candidates
         budget = self.cfg.max_batch_prefill_tokens
