@@ -628,6 +628,59 @@ class App {
   }
 
   // ---------------------------------------------------------------- embeddings / classification
+  // Token classes -> entities, the "simple" aggregation of the reference (router/src/infer.rs:1765-1819): a B- tag, or a tag that
+  // differs from the open entity's group, starts an entity at the token's character offsets; other tokens extend the open
+  // entity (end offset, mean score); an untagged class counts as group "0", so a run of them after an entity becomes an
+  // entity of that group, as it does there.  `word` is the lower-cased text span.  The class list carries one entry per token
+  // of the input as the shard tokenised it, with the tokenizer's special tokens at both ends when it adds any.
+  Value aggregate_entities(const std::string& input, const gen::ClassifyPredictionList& l) {
+    Value q = Value::object();
+    q.set("inputs", input);
+    q.set("add_special_tokens", false);
+    Value toks;
+    std::string err;
+    if (!json::parse(client_->helper(101, q.dump()), toks) || !toks.is_array()) toks = Value::array();
+    const size_t n_tok = toks.size();
+    const size_t skip = l.predictions.size() >= n_tok + 2 ? 1 : 0;          // [CLS] ... [SEP]
+    struct Ent { std::string group; float score; size_t start, end; };
+    std::vector<Ent> ents;
+    bool open = false;
+    Ent cur{};
+    std::vector<float> scores;
+    for (size_t i = 0; i < n_tok && i + skip < l.predictions.size(); ++i) {
+      const std::string& cls = l.predictions[i + skip];
+      const float score = i + skip < l.scores.size() ? l.scores[i + skip] : 0.f;
+      std::string bi = "0", tag = "0";
+      const size_t dash = cls.find('-');
+      if (dash != std::string::npos && cls.find('-', dash + 1) == std::string::npos) { bi = cls.substr(0, dash); tag = cls.substr(dash + 1); }
+      const size_t a = (size_t)toks.items()[i]["start"].as_int(0), b = (size_t)toks.items()[i]["stop"].as_int(0);
+      if (bi == "B" || (open && tag != cur.group)) {
+        if (open) { ents.push_back(cur); scores.clear(); scores.push_back(score); }
+        cur = Ent{tag, score, a, b};
+        open = true;
+      } else if (open) {
+        scores.push_back(score);
+        float sum = 0.f;
+        for (float f : scores) sum += f;
+        cur.score = sum / (float)scores.size();
+        cur.end = b;
+      }
+    }
+    if (open) ents.push_back(cur);
+    Value out = Value::array();
+    for (auto& e : ents) {
+      Value v = Value::object();
+      v.set("entity_group", e.group);
+      v.set("score", e.score);
+      std::string word = (e.start <= e.end && e.end <= input.size()) ? input.substr(e.start, e.end - e.start) : "";
+      for (auto& ch : word) ch = (char)std::tolower((unsigned char)ch);
+      v.set("word", word);
+      v.set("start", (unsigned long long)e.start);
+      v.set("end", (unsigned long long)e.end);
+      out.push(v);
+    }
+    return out;
+  }
   gen::Batch one_shot_batch(const std::vector<std::string>& inputs) {
     gen::Batch b;
     b.id = 1u << 31 | (uint32_t)(++openai_id_);
@@ -701,7 +754,15 @@ class App {
       for (auto& l : resp.classify_prediction_lists) n_out += l.predictions.size();
       metrics_.observe("lorax_request_classify_output_count", (double)n_out);
       Value all = Value::array();
-      for (auto& l : resp.classify_prediction_lists) {
+      for (size_t li = 0; li < resp.classify_prediction_lists.size(); ++li) {
+        auto& l = resp.classify_prediction_lists[li];
+        bool bio = false;
+        for (auto& pr : l.predictions) bio = bio || pr.find('-') != std::string::npos;
+        if (bio && li < inputs.size()) {
+          all.push(aggregate_entities(inputs[li], l));
+          continue;
+        }
+        // labels without a B- / I- prefix: one entry per token
         Value ents = Value::array();
         for (size_t i = 0; i < l.predictions.size(); ++i) {
           Value e = Value::object();
@@ -872,7 +933,52 @@ int main(int argc, char** argv) {
   R("GET", "/startup", [&](auto&, auto& w) { app.health(w); });
   R("GET", "/info", [&](auto&, auto& w) { app.info(w); });
   R("GET", "/", [&](auto&, auto& w) { app.health(w); });
-  R("GET", "/metrics", [&](auto&, auto& w) { w.send(200, app.metrics().render(), "text/plain; version=0.0.4"); });
+  // Prometheus text by default; JSON with ?format=json or "Accept: application/json" (reference router/src/server.rs:1200-1290):
+  // {family: {"type": counter|gauge|histogram, "data": [{"key": labelled series name | "sum" | "count" | "", "value": v}]}}
+  R("GET", "/metrics", [&](auto& req, auto& w) {
+    const std::string text = app.metrics().render();
+    std::string fmt = req.query_param("format");
+    for (auto& ch : fmt) ch = (char)std::tolower((unsigned char)ch);
+    const bool want_json = fmt.empty() ? req.header("accept").find("application/json") != std::string::npos : fmt == "json";
+    if (!want_json) return (void)w.send(200, text, "text/plain; version=0.0.4");
+    Value out = Value::object();
+    std::string current;
+    std::map<std::string, std::pair<std::string, Value>> fams;
+    size_t pos = 0;
+    while (pos < text.size()) {
+      size_t nl = text.find('\n', pos);
+      std::string line = text.substr(pos, nl == std::string::npos ? std::string::npos : nl - pos);
+      pos = nl == std::string::npos ? text.size() : nl + 1;
+      if (line.empty()) continue;
+      if (line.rfind("# TYPE ", 0) == 0) {
+        const size_t sp = line.find(' ', 7);
+        if (sp != std::string::npos) {
+          current = line.substr(7, sp - 7);
+          fams[current] = {line.substr(sp + 1), Value::array()};
+        }
+        continue;
+      }
+      auto it = fams.find(current);
+      const size_t sp = line.rfind(' ');
+      if (it == fams.end() || sp == std::string::npos) continue;
+      const std::string name = line.substr(0, sp);
+      Value dp = Value::object();
+      std::string key;
+      if (name.find('{') != std::string::npos) key = name;
+      else if (name.size() > 4 && name.compare(name.size() - 4, 4, "_sum") == 0) key = "sum";
+      else if (name.size() > 6 && name.compare(name.size() - 6, 6, "_count") == 0) key = "count";
+      dp.set("key", key);
+      dp.set("value", std::strtod(line.c_str() + sp + 1, nullptr));
+      it->second.second.push(dp);
+    }
+    for (auto& kv : fams) {
+      Value fam = Value::object();
+      fam.set("type", kv.second.first);
+      fam.set("data", kv.second.second);
+      out.set(kv.first, fam);
+    }
+    w.send(200, out.dump());
+  });
   R("GET", "/docs", [&](auto&, auto& w) { w.send(200, kOpenApi); });
   R("GET", "/api-doc/openapi.json", [&](auto&, auto& w) { w.send(200, kOpenApi); });
   int bound = server.listen_and_serve(host, port);

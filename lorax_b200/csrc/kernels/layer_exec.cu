@@ -27,6 +27,10 @@ int lx_attn_decode(const void* q, long long ldq, const void* kv, const int* bloc
 int lx_attn_prefill(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
                     const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
                     int nkv, int d, int window, float scale, float softcap, void* stream);
+int lx_attn_prefill_tc_supported(int nh, int nkv, int d, long long ldq, long long ldo);
+int lx_attn_prefill_tc(const void* q, long long ldq, int T, const void* kv, int num_blocks, const int* block_tables, int max_blocks,
+                       const int* cu_q, const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo,
+                       int nh, int nkv, int d, int window, float scale, float softcap, const float* alibi, int* status, void* stream);
 int lx_lora_shrink(const void* x, long long ldx, const int* tok_slot, const void* arena, const long long* slot_base,
                    const int* slot_rank, int num_slots, long long unit_off, int nparts, float* v, int ldv, int T, int K,
                    int max_rank, int* status, void* stream);
@@ -108,6 +112,7 @@ struct LxModelDesc {
   // scratch of the GEMM that carries LoRA in its own launch
   void* lora_vimg; long long lora_vimg_bytes; float* lora_vpart; long long lora_vpart_bytes;
   int* lora_item_counters; int n_lora_item_counters; int lora_fence_maps; int* lora_sync;
+  int tc_prefill, kv_blocks;     // tensor-core prefill attention where the shape allows; blocks of the paged cache
 };
 
 struct LxStepDesc {
@@ -225,9 +230,15 @@ int lx_layer_attention(const LxModelDesc* m, const LxLayerDesc* l, const LxStepD
                           nd, m->nh, m->nkv, m->d, l->window, m->attn_scale, m->softcap, nsplit, stream));
   }
   if (T > nd) {
-    LX_TRY(lx_attn_prefill(q + (long long)nd * ldq * 2, ldq, l->kv_cache, s->block_tables, s->max_blocks, s->cu_q, s->cache_lens, s->tile_seq,
-                           s->tile_q0, s->n_attn_tiles, a + (long long)nd * lda * 2, lda, m->nh, m->nkv, m->d, l->window, m->attn_scale,
-                           m->softcap, stream));
+    if (m->tc_prefill && lx_attn_prefill_tc_supported(m->nh, m->nkv, m->d, ldq, lda)) {
+      LX_TRY(lx_attn_prefill_tc(q + (long long)nd * ldq * 2, ldq, T - nd, l->kv_cache, m->kv_blocks, s->block_tables, s->max_blocks, s->cu_q,
+                                s->cache_lens, s->tile_seq, s->tile_q0, s->n_attn_tiles, a + (long long)nd * lda * 2, lda, m->nh, m->nkv, m->d,
+                                l->window, m->attn_scale, m->softcap, nullptr, m->status, stream));
+    } else {
+      LX_TRY(lx_attn_prefill(q + (long long)nd * ldq * 2, ldq, l->kv_cache, s->block_tables, s->max_blocks, s->cu_q, s->cache_lens, s->tile_seq,
+                             s->tile_q0, s->n_attn_tiles, a + (long long)nd * lda * 2, lda, m->nh, m->nkv, m->d, l->window, m->attn_scale,
+                             m->softcap, stream));
+    }
   }
   return linear_with_lora(*m, *l, *s, 1, s->attn, lda, l->o_w, l->ld_o, l->o_b, out, H, H, m->n_o_in, stream);
 }

@@ -48,7 +48,8 @@ class LxModelDesc(Structure):
                 ("arena", P), ("slot_base", P), ("slot_rank", P), ("slot_tmaps", P),
                 ("num_slots", I), ("max_rank", I), ("groups_per_slot", I), ("fused_lora", I),
                 ("lora_vimg", P), ("lora_vimg_bytes", L), ("lora_vpart", P), ("lora_vpart_bytes", L),
-                ("lora_item_counters", P), ("n_lora_item_counters", I), ("lora_fence_maps", I), ("lora_sync", P)]
+                ("lora_item_counters", P), ("n_lora_item_counters", I), ("lora_fence_maps", I), ("lora_sync", P),
+                ("tc_prefill", I), ("kv_blocks", I)]
 
 
 class LxStepDesc(Structure):
@@ -113,6 +114,7 @@ class NativeExecutor:
         m = LxModelDesc()
         m.H, m.nh, m.nkv, m.d, m.inter, m.rot = model.hidden, model.nh, model.nkv, model.d, model.inter, c.rotary_dim
         m.page = kv_layers[0].shape[3]
+        m.tc_prefill, m.kv_blocks = int(native.TC_PREFILL), kv_layers[0].shape[0]
         m.apply_rope = int(not c.learned_positions)
         m.act, m.gated = native._ACTS[c.hidden_act], int(model.gated)
         m.layernorm = int(c.norm_type.startswith("layernorm"))

@@ -79,6 +79,8 @@ def load() -> ctypes.CDLL:
         "lx_wq4_gemm": ([P, L, P, P, P, P, L, I, I, I, I, P], I),
         "lx_wq4_gemm_ex": ([P, L, P, P, P, P, L, I, I, I, I, I, P], I),
         "lx_lora_expand_tiled": ([P, I, L, I, P, I, I, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
+        "lx_attn_prefill_tc_supported": ([I, I, I, L, L], I),
+        "lx_attn_prefill_tc": ([P, L, I, P, I, P, I, P, P, P, P, I, P, L, I, I, I, I, F, F, P, P, P], I),
         "lx_moe_router_logits": ([P, L, P, L, P, I, I, I, P], I),
         "lx_moe_route": ([P, I, I, I, I, I, P, P, P, P, P, P], I),
         "lx_moe_gather": ([P, L, P, P, I, P, L, I, I, P], I),
@@ -187,6 +189,7 @@ class LoraEpilogue(NamedTuple):
 # 1 (default): the GEMM that carries LoRA acquire-fences a slot's B_cat tensor map before every use, as a tensor map that lives
 # in global memory and was written by a copy asks for; 0 skips it (measurement: the fences cost about 3 % of a decode step).
 LORA_FENCE_MAPS = int(os.environ.get("LORAX_LORA_FENCE_MAPS", "1"))
+TC_PREFILL = os.environ.get("LORAX_TC_PREFILL", "1") != "0"       # 0: the mma.sync prefill attention kernel for every shape
 
 
 class LxLoraFused(ctypes.Structure):
@@ -505,7 +508,15 @@ def attn_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Te
     T = q.shape[0]
     if out is None:
         out = torch.empty(T, nh * d, dtype=q.dtype, device=q.device)
-    rc = load().lx_attn_prefill_alibi(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(cu_q),
+    lib = load()
+    if TC_PREFILL and q.dtype == torch.bfloat16 and lib.lx_attn_prefill_tc_supported(nh, nkv, d, q.stride(0), out.stride(0)):
+        # tcgen05 flash kernel: two query heads of a KV group per CTA, K / V pages by TMA from the paged cache
+        rc = lib.lx_attn_prefill_tc(_ptr(q), q.stride(0), T, _ptr(kv_cache), kv_cache.shape[0], _ptr(block_tables), block_tables.shape[1],
+                                    _ptr(cu_q), _ptr(cache_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0], _ptr(out), out.stride(0),
+                                    nh, nkv, d, window, scale, softcap, _ptr(alibi), _ptr(workspace(q.device).status), _stream())
+        _check(rc, "lx_attn_prefill_tc")
+        return out
+    rc = lib.lx_attn_prefill_alibi(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(cu_q),
                                       _ptr(cache_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0], _ptr(out), out.stride(0), nh,
                                       nkv, d, window, scale, softcap, _ptr(alibi), _stream())
     _check(rc, "lx_attn_prefill")

@@ -956,6 +956,9 @@ class EncoderRuntime:
         return self.tokenizer.encode(text, add_special_tokens=add_special).ids
 
     def tokenize_detailed(self, body: dict) -> list:
+        if self.tokenizer is not None:          # character offsets: the router turns token classes into entity spans with them
+            enc = self.tokenizer.encode(body.get("inputs", ""), add_special_tokens=body.get("add_special_tokens", True))
+            return [{"id": i, "text": t, "start": o[0], "stop": o[1]} for i, t, o in zip(enc.ids, enc.tokens, enc.offsets)]
         return [{"id": i, "text": str(i), "start": 0, "stop": 0} for i in self.tokenize(body.get("inputs", ""))]
 
     def apply_chat_template(self, body: dict) -> str:

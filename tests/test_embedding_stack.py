@@ -22,6 +22,7 @@ def emb_stack(tmp_path_factory):
     root = tmp_path_factory.mktemp("emb")
     raw = {"model_type": "distilbert", "vocab_size": 512, "dim": 64, "n_layers": 2, "n_heads": 4, "hidden_dim": 128,
            "max_position_embeddings": 64, "id2label": {str(i): f"TAG{i}" for i in range(4)}}
+
     cfg = EncoderConfig.from_dict(raw)
     sd = random_encoder_state_dict(cfg, seed=11, num_labels=4)
     mdir = root / "model"
@@ -102,3 +103,63 @@ def test_embed_and_classify_routes(emb_stack):
     for name in ('lorax_batch_inference_success{method="classify"}', 'lorax_batch_inference_success{method="embed"}',
                  "lorax_request_input_count_bucket", "lorax_request_classify_output_count_bucket"):
         assert name in m, name
+
+
+def test_metrics_as_json(emb_stack):
+    """`/metrics?format=json` (and `Accept: application/json`): the Prometheus families as {type, data: [{key, value}]}."""
+    port = emb_stack["port"]
+    _post(port, "/embed", {"inputs": "w1 w2"})
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics?format=json", timeout=5) as r:
+        assert r.status == 200
+        m = json.loads(r.read().decode())
+    fam = m["lorax_batch_inference_success"]
+    assert fam["type"] == "counter" and any(d["key"].endswith('{method="embed"}') and d["value"] >= 1 for d in fam["data"])
+    hist = m["lorax_request_input_count"]
+    assert hist["type"] == "histogram" and {"sum", "count"} <= {d["key"] for d in hist["data"]}
+    req = urllib.request.Request(f"http://127.0.0.1:{port}/metrics", headers={"Accept": "application/json"})
+    with urllib.request.urlopen(req, timeout=5) as r:
+        assert "lorax_batch_inference_success" in json.loads(r.read().decode())
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5) as r:
+        assert r.read().decode().startswith("# TYPE")
+
+
+def test_token_classes_become_entities(emb_stack):
+    """Labels in the B- / I- scheme are aggregated into entities with character offsets, as the reference's router does
+    (router/src/infer.rs:1765-1819): the same rule restated in Python over the shard's per-token output."""
+    port, rt = emb_stack["port"], emb_stack["rt"]
+    saved = dict(rt.model.config.id2label)
+    rt.model.config.id2label = {i: n for i, n in enumerate(["O", "B-PER", "I-PER", "B-LOC"])}
+    try:
+        text = "w5 w9 w77 w3 w300 w12 w8 w41 w6"
+        labels, scores = rt.model.classify([rt.tokenize(text)])
+        labels, scores = labels[0], scores[0]
+        assert any("-" in l for l in labels)
+        words = text.split()
+        offs, p0 = [], 0
+        for wd in words:
+            a = text.index(wd, p0)
+            offs.append((a, a + len(wd)))
+            p0 = a + len(wd)
+        want, cur, sc = [], None, []
+        for (a, b), cls, s_ in zip(offs, labels, scores):
+            parts = cls.split("-")
+            bi, tag = (parts[0], parts[1]) if len(parts) == 2 else ("0", "0")
+            if bi == "B" or (cur is not None and tag != cur["entity_group"]):
+                if cur is not None:
+                    want.append(cur)
+                    sc = [s_]
+                cur = {"entity_group": tag, "score": s_, "start": a, "end": b}
+            elif cur is not None:
+                sc.append(s_)
+                cur["score"] = sum(sc) / len(sc)
+                cur["end"] = b
+        if cur is not None:
+            want.append(cur)
+        st, body, _ = _post(port, "/classify", {"inputs": text})
+        assert st == 200, body
+        got = json.loads(body)
+        assert [(e["entity_group"], e["start"], e["end"]) for e in got] == [(e["entity_group"], e["start"], e["end"]) for e in want]
+        assert all(abs(g["score"] - w["score"]) < 1e-4 for g, w in zip(got, want))
+        assert all(g["word"] == text[g["start"]:g["end"]].lower() for g in got)
+    finally:
+        rt.model.config.id2label = saved

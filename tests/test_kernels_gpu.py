@@ -216,6 +216,36 @@ def test_attn_prefill(nat, nh, nkv, d, window, cached):
     assert _rel_err(got, want) < 1e-2
 
 
+@pytest.mark.parametrize("nh,nkv,window,softcap,q_lens,cache_lens", [
+    (32, 8, 0, 0.0, [700, 1300, 3], [0, 0, 0]),                # several key blocks per tile: both TMEM buffers and both K/V stages cycle
+    (8, 2, 0, 0.0, [200, 64, 129], [900, 37, 128]),            # chunks that continue a cached prefix (chunked prefill, prefix cache)
+    (16, 4, 300, 0.0, [1000, 50], [0, 2000]),                  # sliding window: key blocks left of the window are skipped
+    (8, 4, 0, 30.0, [333], [5])])                              # soft-capped scores
+def test_attn_prefill_tensor_core(nat, nh, nkv, window, softcap, q_lens, cache_lens):
+    """tcgen05 flash prefill (two heads of a KV group per CTA, K / V pages by TMA from the paged cache) against fp32 attention."""
+    torch.manual_seed(16)
+    d = 128
+    assert nat.load().lx_attn_prefill_tc_supported(nh, nkv, d, nh * d, nh * d) == 1
+    B = len(q_lens)
+    max_len = max(a + b for a, b in zip(q_lens, cache_lens))
+    cache, bt = _make_cache(B, max_len, nkv, d, seed=4)
+    T = sum(q_lens)
+    q = torch.randn(T, nh * d, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    cl = torch.tensor(cache_lens, device="cuda", dtype=torch.int32)
+    ts, tq = ref.prefill_tiles(q_lens)
+    ts = torch.tensor(ts, device="cuda", dtype=torch.int32)
+    tq = torch.tensor(tq, device="cuda", dtype=torch.int32)
+    scale = d ** -0.5
+    for _ in range(2):
+        got = nat.attn_prefill(q, cache, bt, cu, cl, ts, tq, nh, nkv, d, scale, window, softcap)
+        torch.cuda.synchronize()
+        nat.workspace().check_status()
+        want = ref.attn_prefill(q, cache, bt, cu, cl, ts, tq, nh, nkv, d, scale, window, softcap)
+        assert _rel_err(got, want) < 1e-2
+        assert torch.isfinite(got.float()).all()
+
+
 @pytest.mark.parametrize("nh,nkv,d,nsplit", [(12, 12, 64, 1), (32, 8, 128, 3), (6, 6, 128, 1)])
 def test_attn_alibi(nat, nh, nkv, d, nsplit):
     """ALiBi slopes in both attention kernels (BLOOM, MPT): bias -slope_h * (query position - key position)."""

@@ -59,6 +59,8 @@ def main():
     dtype = torch.bfloat16 if cuda else torch.float32
     out = {"world": tp.world_size, "device": dev.type}
     cfg = tiny_llama()
+    if tp.world_size > 2:          # shapes that still split over 4 and 8 ranks (heads, K shards that are multiples of 8)
+        cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads = 512, 1024, 8, 2
     g = torch.Generator().manual_seed(3)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (20, 33, 47)]
     ads = [1, 0, 2]
@@ -99,6 +101,21 @@ def main():
             dist.all_gather(gathered, res)
             eq.append(all(torch.equal(gathered[0], t) for t in gathered))      # every rank holds the same bits
         fc.check()
+        # 7B-sized output width with the K shards of the O and down projections: both token-tile regimes and the K-split variants
+        fc_big = fz.FusedCollectives(tp, n_max=4096, max_rows=512)
+        for it, (T, N, K) in enumerate([(32, 4096, 4096 // tp.world_size), (256, 4096, 14336 // tp.world_size), (100, 4096, 512)]):
+            gen = torch.Generator(device=dev).manual_seed(500 + 100 * it + tp.rank)
+            x = torch.randn(T, K, device=dev, dtype=dtype, generator=gen)
+            w = torch.randn(N, K, device=dev, dtype=dtype, generator=gen) / K ** 0.5
+            res = fc_big.gemm_allreduce(x, w, None, None).clone()
+            part = x.float() @ w.float().t()
+            dist.all_reduce(part)
+            torch.cuda.synchronize()
+            errs.append(((res.float() - part).norm() / part.norm()).item())
+            gathered = [torch.empty_like(res) for _ in range(tp.world_size)]
+            dist.all_gather(gathered, res)
+            eq.append(all(torch.equal(gathered[0], t) for t in gathered))
+        fc_big.check()
         out["gemm_allreduce_relerr"] = max(errs)
         out["gemm_allreduce_ranks_identical"] = all(eq)
         # two-shot all-reduce kernel against an fp32 sum of the ranks' inputs
