@@ -164,7 +164,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x;
+  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;      // later tiles of a sequence see more keys: start the long ones first
   const int h0 = blockIdx.y * 2;                 // first of the two query heads
   const int kvh = h0 / p.group;
 

@@ -79,6 +79,7 @@ class Engine:
         self.cfg = cfg or EngineConfig()
         c = model.config
         page = self.cfg.block_size
+        self._max_batch = max_batch
         if num_blocks is None:
             num_blocks = self._auto_blocks(page)
         self.kv = KVCache(c.num_hidden_layers, num_blocks, model.nkv, model.d, model.dtype, model.device, page)
@@ -108,9 +109,8 @@ class Engine:
         m, c = self.model, self.model.config
         per_block = KVCache.bytes_per_block(c.num_hidden_layers, m.nkv, m.d, m.dtype, page)
         if m.device.type == "cuda":
-            free, _ = torch.cuda.mem_get_info(m.device)
-            budget = int(free * self.cfg.memory_wiggle_room) - (6 << 30)
-            return max(int(budget // per_block), 64)
+            from .kv_cache import plan_kv_blocks
+            return plan_kv_blocks(m, self.cfg, self._max_batch, page, reserve_bytes=2 << 30)
         return 512
 
     # ------------------------------------------------------------------ API
@@ -159,6 +159,45 @@ class Engine:
         self.stats["adapter_loads"] = self.stats.get("adapter_loads", 0) + 1
         self.adapter_lru[adapter_index] = None
         return True
+
+    def _prefetch_adapters(self, lookahead: int = 64, max_loads: int = 2):
+        """Bring the adapters of requests that are still queued into HBM ahead of their turn: the copy runs on the exchange
+        stream while the batch decodes, so the request does not wait for it when it reaches the head of the queue (the
+        reference loads an adapter when its queue becomes active, `router/src/queue.rs:338-451`).  Adapters that neither the
+        running batch nor the look-ahead window needs make room, least recently used first."""
+        ad = self.model.adapters
+        if ad is None or not self.adapter_keys or not self.waiting or self.on_adapter_needed is not None:
+            return
+        wanted: List[int] = []
+        for i, req in enumerate(self.waiting):
+            if i >= lookahead:
+                break
+            a = req.adapter_index
+            if a and a not in wanted and a in self.adapter_keys:
+                wanted.append(a)
+        if all(ad.is_loaded(a) for a in wanted):
+            return
+        keep = ({s.req.adapter_index for s in self.running.values()} | {s.req.adapter_index for s in self.draining.values()}
+                | set(wanted))
+        loads = 0
+        for a in wanted:
+            if loads >= max_loads:
+                break
+            if ad.is_loaded(a):
+                continue
+            ok = ad.load(a, self.adapter_keys[a])
+            while not ok:
+                victim = next((i for i in self.adapter_lru if i not in keep and ad.is_loaded(i)), None)
+                if victim is None:
+                    return                      # everything resident is needed sooner
+                ad.offload(victim)
+                del self.adapter_lru[victim]
+                self.stats["adapter_evictions"] = self.stats.get("adapter_evictions", 0) + 1
+                ok = ad.load(a, self.adapter_keys[a])
+            self.adapter_lru[a] = None
+            self.stats["adapter_loads"] = self.stats.get("adapter_loads", 0) + 1
+            self.stats["adapter_prefetches"] = self.stats.get("adapter_prefetches", 0) + 1
+            loads += 1
 
     def _select_prefill(self) -> List[Tuple[GenRequest, List[int]]]:
         if not self.waiting:
@@ -318,6 +357,7 @@ class Engine:
     def step(self) -> List[TokenEvent]:
         events: List[TokenEvent] = []
         queued_before = len(self.inflight)
+        self._prefetch_adapters()
         picked = self._select_prefill()
         launched = False
         if picked:

@@ -62,3 +62,45 @@ class BlockAllocator:
     @property
     def free_blocks(self) -> int:
         return len(self.free)
+
+
+def plan_kv_blocks(model, cfg, max_batch: int, page: int = PAGE_SIZE, reserve_bytes: int = 1 << 30) -> int:
+    """How many KV blocks fit, measured instead of guessed: run one prefill of `max_batch_prefill_tokens` tokens (prompts of
+    `max_input_length`) against a throw-away cache, read the peak of the allocator, and give the cache what is left of the free
+    memory after that peak, the decode state and a reserve for CUDA-graph pools (the reference's warm-up does the same with a
+    maximum batch, `server/lorax_server/models/flash_causal_lm.py:1293-1401`).  Under tensor parallelism every rank calls this at
+    the same time (the prefill contains collectives) and the ranks agree on the minimum."""
+    from .runner import ModelRunner, PrefillItem
+    c, dev = model.config, model.device
+    per_block = KVCache.bytes_per_block(c.num_hidden_layers, model.nkv, model.d, model.dtype, page)
+    if dev.type != "cuda":
+        return 1024
+    tokens = max(int(cfg.max_batch_prefill_tokens), 16)
+    seq = max(1, min(int(cfg.max_input_length), tokens))
+    lens = [seq] * (tokens // seq) + ([tokens % seq] if tokens % seq else [])
+    window = c.sliding_window
+    blocks_per = [min((n + page - 1) // page, (window + page - 1) // page + 1) if window else (n + page - 1) // page for n in lens]
+    tmp = KVCache(c.num_hidden_layers, sum(blocks_per) + 2, model.nkv, model.d, model.dtype, dev, page)
+    runner = ModelRunner(model, tmp, max_batch=max_batch, max_seq_tokens=cfg.max_total_tokens, max_prefill_tokens=tokens, use_graphs=False)
+    torch.cuda.synchronize(dev)
+    torch.cuda.reset_peak_memory_stats(dev)
+    base = torch.cuda.memory_allocated(dev)
+    items, nxt = [], 1
+    for n, nb in zip(lens, blocks_per):
+        items.append(PrefillItem([1] * n, 0, list(range(nxt, nxt + nb))))
+        nxt += nb
+    runner.prefill(items)
+    torch.cuda.synchronize(dev)
+    peak = torch.cuda.max_memory_allocated(dev) - base
+    del runner, tmp, items
+    torch.cuda.empty_cache()
+    free, _ = torch.cuda.mem_get_info(dev)
+    budget = int(free * cfg.memory_wiggle_room) - int(peak * 1.1) - reserve_bytes
+    blocks = max(int(budget // per_block), 64)
+    tp = model.tp
+    if tp.world_size > 1:
+        import torch.distributed as dist
+        t = torch.tensor([blocks], dtype=torch.int64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN, group=tp.group)
+        blocks = int(t.item())
+    return blocks

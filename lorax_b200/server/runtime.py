@@ -104,8 +104,8 @@ class ShardRuntime:
         if num_blocks is None:
             per_block = KVCache.bytes_per_block(c.num_hidden_layers, model.nkv, model.d, model.dtype, page)
             if dev.type == "cuda":
-                free, _ = torch.cuda.mem_get_info(dev)
-                num_blocks = max(int((free * self.cfg.memory_wiggle_room - (4 << 30)) // per_block), 64)
+                from ..runtime.kv_cache import plan_kv_blocks
+                num_blocks = plan_kv_blocks(model, self.cfg, max_batch, page)      # a maximum prefill runs first: its peak is measured
             else:
                 num_blocks = 1024
         self.kv = KVCache(c.num_hidden_layers, num_blocks, model.nkv, model.d, model.dtype, dev, page)
@@ -152,7 +152,8 @@ class ShardRuntime:
         return self.pb.HealthResponse()
 
     def warmup(self, req):
-        """The KV cache is sized at construction from free memory; report what it can hold."""
+        """The KV cache was sized at construction, after a maximum prefill had run and its memory peak had been measured
+        (`runtime/kv_cache.py:plan_kv_blocks`); report what it can hold."""
         return self.pb.WarmupResponse(max_supported_total_tokens=self.kv.max_tokens)
 
     # ------------------------------------------------------------------ tokenizer helpers
@@ -1044,7 +1045,10 @@ def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel]
     if quantize is None and isinstance(qc, dict) and qc.get("quant_method") == "fp8":
         quantize = "fp8"
     if quantize == "fp8-kv":
-        quantize = "fp8"                   # the KV cache stays in the model dtype; the weights take the fp8 path
+        # the weights take the fp8 path; the KV cache stays in the model dtype (fp8 pages are not built), and the log says so
+        print(json.dumps({"level": "WARN", "message": "--quantize fp8-kv: base weights are served in block-scaled fp8, the KV cache stays "
+                          + str(dtype).replace("torch.", "")}), flush=True)
+        quantize = "fp8"
     if quantize in ("gptq", "awq") and w.quant is None:
         raise ValueError(f"--quantize {quantize} needs a {quantize} checkpoint (no quantization_config / quantize_config.json found)")
     if quantize is not None and not (quantize in ("gptq", "awq") and model.quantized):

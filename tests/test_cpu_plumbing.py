@@ -158,6 +158,9 @@ def test_adapter_exchange_under_memory_pressure():
     tight, stats, mgr = run(2)
     assert tight == full
     assert stats.get("adapter_evictions", 0) >= 3 and len(mgr.resident) <= 2
+    # with room for one adapter more than the batch can use, adapters of queued requests are brought in ahead of their turn
+    roomy, stats3, _ = run(4)
+    assert roomy == full and stats3.get("adapter_prefetches", 0) >= 1
 
 
 def test_device_sampler_distribution_and_filters():
