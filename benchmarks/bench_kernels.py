@@ -162,6 +162,26 @@ def bench_lora(results, peaks):
             del ws, arena
 
 
+def bench_moe(results, peaks):
+    """Mixtral-8x7B expert block (8 experts, top 2) on one GPU: the device path (grouped tcgen05 GEMMs) against the bytes it must
+    stream (every expert's weights once when each expert has at least one row) and the FLOPs of the routed rows."""
+    E, k, H, I = 8, 2, 4096, 14336
+    wr = (torch.randn(E, H, device="cuda") * 0.3).to(torch.bfloat16)
+    w13 = torch.randn(E, 2 * I, H, device="cuda", dtype=torch.bfloat16) / math.sqrt(H)
+    w2 = torch.randn(E, H, I, device="cuda", dtype=torch.bfloat16) / math.sqrt(I)
+    for T in (16, 256, 2048, 4096):
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        ms = _time(lambda i: native.moe_ffn(x, wr, w13, w2, k, 0, "silu"), 1, iters=10)
+        native.workspace().check_status()
+        wbytes = (w13.numel() + w2.numel()) * 2
+        flops = 2.0 * T * k * 3 * H * I
+        results.append({"kernel": "moe_ffn (route, gather, 2 grouped GEMMs, act, combine)", "shape": f"T={T} E={E} top{k} H={H} I={I}",
+                        "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1), "weight_gbs": round(wbytes / ms / 1e6, 1),
+                        "frac_of_measured_hbm": round(wbytes / ms / 1e6 / peaks["hbm_gbs"], 3),
+                        "frac_of_measured_bf16": round(flops / ms / 1e9 / peaks["bf16_tflops"], 3)})
+        print(results[-1], flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--json", default=None)
@@ -174,7 +194,7 @@ def main():
     except OSError:
         pass
     results = []
-    for name, fn in (("gemm", bench_gemm), ("lora", bench_lora), ("attn_decode", bench_attn_decode), ("attn_prefill", bench_attn_prefill),
+    for name, fn in (("gemm", bench_gemm), ("lora", bench_lora), ("moe", bench_moe), ("attn_decode", bench_attn_decode), ("attn_prefill", bench_attn_prefill),
                      ("small", bench_small)):
         if a.only and a.only != name:
             continue

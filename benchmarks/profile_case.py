@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for `ncu` captures of single kernels.
 
-    python benchmarks/profile_case.py --case gemm_decode|gemm_mid|gemm_prefill|gemm_fp8_decode|gemm_fp8_prefill|gemm_lora_decode|gemm_lora_decode_gateup|gemm_lora_prefill|attn_decode|attn_prefill|lora_shrink|lora_expand
+    python benchmarks/profile_case.py --case gemm_decode|gemm_mid|gemm_prefill|gemm_fp8_decode|gemm_fp8_prefill|gemm_lora_decode|gemm_lora_decode_gateup|gemm_lora_prefill|attn_decode|attn_prefill|lora_shrink|lora_expand|moe_decode|moe_prefill
 
 Each case launches the kernel a handful of times on inputs larger than the 126 MB L2 but at most a few GB, and
 exits 0; run it plain first, then under
@@ -140,6 +140,19 @@ def gemm_int4_case(T):
         native.gemm_wq(x, ws[i % 3], out=out)
 
 
+def moe_case(T):
+    """Mixtral-8x7B expert shapes (8 experts, top 2, hidden 4096, intermediate 14336) on one GPU: routing, gather, grouped w1|w3
+    GEMM, act * up, grouped w2 GEMM, combine.  2.8 GB of expert weights: every launch streams them from HBM."""
+    import math
+    E, k, H, I = 8, 2, 4096, 14336
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    wr = (torch.randn(E, H, device="cuda") * 0.3).to(torch.bfloat16)
+    w13 = (torch.randn(E, 2 * I, H, device="cuda", dtype=torch.bfloat16) / math.sqrt(H))
+    w2 = (torch.randn(E, H, I, device="cuda", dtype=torch.bfloat16) / math.sqrt(I))
+    for _ in range(3):
+        native.moe_ffn(x, wr, w13, w2, k, 0, "silu")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--case", required=True)
@@ -149,7 +162,8 @@ def main():
      "attn_prefill": attn_prefill_case, "gemm_lora_decode": lambda: gemm_lora_case(256), "gemm_lora_decode_gateup": lambda: gemm_lora_case(256, (14336, 14336)), "gemm_lora_prefill": lambda: gemm_lora_case(576),
      "gemm_fp8_decode": lambda: gemm_fp8_case(64), "gemm_fp8_prefill": lambda: gemm_fp8_case(2048), "gemm_mid": lambda: gemm_case(256),
      "gemm_int4_decode": lambda: gemm_int4_case(8),
-     "lora_shrink": lambda: lora_case("shrink"), "lora_expand": lambda: lora_case("expand")}[a.case]()
+     "lora_shrink": lambda: lora_case("shrink"), "lora_expand": lambda: lora_case("expand"),
+     "moe_decode": lambda: moe_case(256), "moe_prefill": lambda: moe_case(2048)}[a.case]()
     torch.cuda.synchronize()
     native.workspace().check_status()
     print("ok", a.case)

@@ -13,6 +13,7 @@ from __future__ import annotations
 import argparse
 import concurrent.futures as cf
 import hashlib
+import json
 import os
 import shutil
 import subprocess
@@ -100,6 +101,15 @@ def build_host(force: bool = False, verbose: bool = False):
     # the protobuf codec of the wire contract is generated from proto/generate.proto
     from lorax_b200.server import protogen
     protogen.main([str(HOST_DIR / "pb_gen.hpp")])
+    # the OpenAPI document the router serves at /docs and /api-doc/openapi.json is the one of the documentation
+    spec = PKG.parent / "docs" / "reference" / "openapi.json"
+    body = json.dumps(json.loads(spec.read_text()), separators=(",", ":")) if spec.exists() else '{"openapi":"3.0.3","info":{"title":"lorax-b200","version":"0.2.0"},"paths":{}}'
+    chunks = [body[i:i + 8000] for i in range(0, len(body), 8000)]       # string literals are limited in length by the standard
+    gen = "// generated from docs/reference/openapi.json by csrc/build.py\n#pragma once\nstatic const char* const kOpenApiChunks[] = {\n" + \
+        "".join('  R"OAPI(' + c + ')OAPI",\n' for c in chunks) + "  nullptr};\n"
+    out = HOST_DIR / "openapi_gen.hpp"
+    if not out.exists() or out.read_text() != gen:
+        out.write_text(gen)
     headers = sorted(HOST_DIR.glob("*.h")) + sorted(HOST_DIR.glob("*.hpp"))
     BUILD_DIR.mkdir(exist_ok=True)
     BIN_DIR.mkdir(exist_ok=True)
@@ -139,6 +149,15 @@ def build_host_selftest(sanitizer: str, verbose: bool = False) -> Path:
     undefined-behaviour checks) or "thread".  Returns the binary; running it prints OK and exits 0 when nothing was found."""
     from lorax_b200.server import protogen
     protogen.main([str(HOST_DIR / "pb_gen.hpp")])
+    # the OpenAPI document the router serves at /docs and /api-doc/openapi.json is the one of the documentation
+    spec = PKG.parent / "docs" / "reference" / "openapi.json"
+    body = json.dumps(json.loads(spec.read_text()), separators=(",", ":")) if spec.exists() else '{"openapi":"3.0.3","info":{"title":"lorax-b200","version":"0.2.0"},"paths":{}}'
+    chunks = [body[i:i + 8000] for i in range(0, len(body), 8000)]       # string literals are limited in length by the standard
+    gen = "// generated from docs/reference/openapi.json by csrc/build.py\n#pragma once\nstatic const char* const kOpenApiChunks[] = {\n" + \
+        "".join('  R"OAPI(' + c + ')OAPI",\n' for c in chunks) + "  nullptr};\n"
+    out = HOST_DIR / "openapi_gen.hpp"
+    if not out.exists() or out.read_text() != gen:
+        out.write_text(gen)
     BUILD_DIR.mkdir(exist_ok=True)
     flags = {"address": ["-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"], "thread": ["-fsanitize=thread"]}[sanitizer]
     out = BUILD_DIR / f"host_selftest_{sanitizer}"

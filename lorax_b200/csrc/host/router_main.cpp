@@ -11,6 +11,7 @@
 #include <cstdlib>
 #include <iostream>
 
+#include "openapi_gen.hpp"
 #include "http.hpp"
 #include "infer.hpp"
 #include "json.hpp"
@@ -836,11 +837,12 @@ class App {
   std::atomic<uint64_t> openai_id_{0};
 };
 
-const char* kOpenApi = R"J({"openapi":"3.0.3","info":{"title":"lorax_b200 router","version":"0.1.0"},"paths":{
-"/generate":{"post":{"summary":"Generate tokens"}},"/generate_stream":{"post":{"summary":"Generate a stream of tokens (SSE)"}},
-"/v1/completions":{"post":{"summary":"OpenAI-compatible completions"}},"/v1/chat/completions":{"post":{"summary":"OpenAI-compatible chat"}},
-"/v1/embeddings":{"post":{"summary":"OpenAI-compatible embeddings"}},"/embed":{"post":{}},"/classify":{"post":{}},"/classify_batch":{"post":{}},
-"/tokenize":{"post":{}},"/info":{"get":{}},"/health":{"get":{}},"/metrics":{"get":{}}}})J";
+// the OpenAPI document of docs/reference/openapi.json, embedded at build time
+static std::string open_api_document() {
+  std::string doc;
+  for (const char* const* c = kOpenApiChunks; *c != nullptr; ++c) doc += *c;
+  return doc;
+}
 
 }  // namespace
 
@@ -979,8 +981,9 @@ int main(int argc, char** argv) {
     }
     w.send(200, out.dump());
   });
-  R("GET", "/docs", [&](auto&, auto& w) { w.send(200, kOpenApi); });
-  R("GET", "/api-doc/openapi.json", [&](auto&, auto& w) { w.send(200, kOpenApi); });
+  const std::string open_api = open_api_document();
+  R("GET", "/docs", [&](auto&, auto& w) { w.send(200, open_api); });
+  R("GET", "/api-doc/openapi.json", [&](auto&, auto& w) { w.send(200, open_api); });
   int bound = server.listen_and_serve(host, port);
   if (!bound) { log_json("ERROR", "cannot bind port " + std::to_string(port)); return 1; }
   log_json("INFO", "Connected; listening on " + host + ":" + std::to_string(bound));

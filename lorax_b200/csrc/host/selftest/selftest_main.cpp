@@ -7,7 +7,10 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstring>
+#include <memory>
 #include <string>
+
+#include "flag_protocols.hpp"
 #include <vector>
 
 extern "C" {
@@ -74,6 +77,11 @@ int main() {
   out = lx_infer_fake_run(reqs.c_str(), 3, 4, 512, 0);
   if (count(out, "\"ok\":true") + count(out, "\"ok\":false") != 36) return fail("failing shard", out.substr(0, 400));
   if (count(out, "\"ok\":false") == 0) return fail("failure was not injected");
+  // CPU-thread models of the device-side flag protocols (races would be reported by ThreadSanitizer, wrong sums here)
+  if (!lx_model::model_all_reduce(4, 3, 257, 6)) return fail("two-shot all-reduce protocol model");
+  if (!lx_model::model_all_reduce(2, 5, 64, 10)) return fail("two-shot all-reduce protocol model (2 ranks)");
+  if (!lx_model::model_lora_sync(6, 17, 2, 5)) return fail("LoRA-in-GEMM protocol model");
+  if (!lx_model::model_lora_sync(4, 9, 1, 5)) return fail("LoRA-in-GEMM protocol model (no K split)");
   std::printf("OK\n");
   return 0;
 }

@@ -385,6 +385,14 @@ def test_prefix_cache_holds_only_tokens_whose_kv_was_written(stack):
             proc.kill()
 
 
+def test_openapi_document_is_served(stack):
+    """`/api-doc/openapi.json` (and `/docs`) serve the OpenAPI document of docs/reference/openapi.json."""
+    with urllib.request.urlopen(f"http://127.0.0.1:{stack['port']}/api-doc/openapi.json", timeout=5) as r:
+        doc = json.loads(r.read().decode())
+    assert doc["openapi"].startswith("3.") and {"/generate", "/generate_stream", "/v1/chat/completions", "/classify", "/metrics"} <= set(doc["paths"])
+    assert "GenerateParameters" in doc["components"]["schemas"] and "merged_adapters" in doc["components"]["schemas"]["GenerateParameters"]["properties"]
+
+
 def test_health_turns_false_after_a_device_side_failure(stack):
     """A step that finds the kernels' status word set (a bounded wait that ran out on the device) fails its batch: the client
     gets 424, the router drops the batch, and /health, which probes the shard after a failed generation as the reference does
