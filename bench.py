@@ -256,7 +256,7 @@ def main():
     mgr.fence()
     torch.cuda.synchronize(dev)
 
-    ecfg = EngineConfig(max_total_tokens=max_total, max_batch_prefill_tokens=4096, max_input_length=args.max_prompt,
+    ecfg = EngineConfig(max_total_tokens=max_total, max_batch_prefill_tokens=max(4096, args.max_prompt), max_input_length=args.max_prompt,
                         compile=not args.no_graphs)
     if args.waiting_served_ratio is not None:
         ecfg.waiting_served_ratio = args.waiting_served_ratio

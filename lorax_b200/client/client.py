@@ -174,3 +174,31 @@ class AsyncClient:
                 if resp.status != 200:
                     raise parse_error(resp.status, payload)
                 return EmbedResponse(**payload)
+
+    async def _post_json(self, path: str, body: dict):
+        from aiohttp import ClientSession
+        async with ClientSession(headers=self.headers, cookies=self.cookies, timeout=self.timeout) as session:
+            async with session.post(self.base_url + path, json=body) as resp:
+                payload = await resp.json()
+                if resp.status != 200:
+                    raise parse_error(resp.status, payload)
+                return payload
+
+    async def classify(self, inputs: str) -> ClassifyResponse:
+        """Token classification of one text (entities when the model's labels follow the B- / I- scheme)."""
+        return ClassifyResponse(entities=await self._post_json("/classify", {"inputs": inputs}))
+
+    async def classify_batch(self, inputs: List[str]) -> List[ClassifyResponse]:
+        return [ClassifyResponse(entities=e) for e in await self._post_json("/classify_batch", {"inputs": inputs})]
+
+    async def info(self) -> dict:
+        from aiohttp import ClientSession
+        async with ClientSession(headers=self.headers, cookies=self.cookies, timeout=self.timeout) as session:
+            async with session.get(self.base_url + "/info") as resp:
+                return await resp.json()
+
+    async def health(self) -> bool:
+        from aiohttp import ClientSession
+        async with ClientSession(headers=self.headers, cookies=self.cookies, timeout=self.timeout) as session:
+            async with session.get(self.base_url + "/health") as resp:
+                return resp.status == 200

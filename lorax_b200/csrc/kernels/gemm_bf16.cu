@@ -85,7 +85,7 @@ constexpr int kLoraSliceElems = kLoraWin * 16;      // one K slice (16 ranks) of
 constexpr int kLoraSliceBytes = kLoraSliceElems * 2;
 constexpr int kLoraImgElems = 4 * kLoraSliceElems;  // ranks up to 64
 constexpr int kLoraBTileBytes = kBM * 32;           // 128 features x 16 ranks of B_cat
-constexpr int kLoraUnitsPerStage = 4;
+constexpr int kLoraUnitBytes = kLoraBTileBytes + kLoraSliceBytes;     // what one expand unit occupies in a pipeline stage
 
 LX_DEVICE int ld_acquire_gpu(const int* p) {
   int v;
@@ -305,6 +305,8 @@ struct GemmSmem {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = kBRows * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
+  // expand units that share a stage: B_cat tiles first, then the image slices
+  static constexpr int kUnits = (kStageBytes / kLoraUnitBytes) < 8 ? (kStageBytes / kLoraUnitBytes) : 8;
   static constexpr int kBarrierBytes = 256;
   static constexpr int kEntBytes = LORA ? kLoraMaxEntries * (int)sizeof(LoraEnt) + 2 * kLoraListCap * 16 : 0;    // entry table + two unit lists
   static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + kEntBytes + 1024;  // +1024 for manual alignment
@@ -364,13 +366,15 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_base_slot;
-  pdl_wait();      // barriers, TMEM and descriptors are set up while the previous kernel drains; its data is read from here on
   if constexpr (LORA) {
+    // the table, the slot ranks and the slot offsets are written by copies that the stream orders before every kernel, never by
+    // the kernel in front of this one: reading them does not have to wait for that kernel to drain
     if (lora) {
       load_lora_entries(p, ents);
       __syncthreads();
     }
   }
+  pdl_wait();      // barriers, TMEM and descriptors are set up while the previous kernel drains; its data is read from here on
 
   // Work item w -> (tile, split).  Tiles are ordered with the A tile index fastest inside one B tile so that
   // CTAs running at the same time share the B operand through L2.
@@ -454,7 +458,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             fence_proxy_async_all();       // the images were written with ordinary stores; bulk copies read them
             shrink_seen = true;
           }
-          constexpr int kRound = STAGES * kLoraUnitsPerStage;       // units that fill the ring once (<= 32)
+          constexpr int kU = S::kUnits;
+          constexpr int kRound = STAGES * kU;       // units that fill the ring once (<= 32)
+          static_assert(kRound <= 32, "one lane per unit of a round");
           int n = 0;
           bool ended = false;
           for (int lt0 = 0; ok && !ended && lt0 < p.lora_num_tiles; lt0 += 32) {
@@ -465,7 +471,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             for (int base = 0; ok && base < n; base += kRound) {
               const int gu = base + lane;
               if (lane < kRound && gu < n) {
-                const int sidx = lane / kLoraUnitsPerStage, u = lane % kLoraUnitsPerStage;
+                const int sidx = lane / kU, u = lane % kU;
                 const int pos = stage + sidx;
                 const int sring = pos >= STAGES ? pos - STAGES : pos;
                 const uint32_t ph = phase ^ (pos >= STAGES ? 1u : 0u);
@@ -475,19 +481,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 } else {
                   uint8_t* sa = tiles + sring * S::kStageBytes;
                   if (u == 0) {
-                    const int in_stage = min(kLoraUnitsPerStage, n - (base + sidx * kLoraUnitsPerStage));
-                    mbar_expect_tx(&full_bar[sring], (uint32_t)(in_stage * (kLoraBTileBytes + kLoraSliceBytes)));
+                    const int in_stage = min(kU, n - (base + sidx * kU));
+                    mbar_expect_tx(&full_bar[sring], (uint32_t)(in_stage * kLoraUnitBytes));
                   }
                   const int4 q = ulist_p[gu];
                   const CUtensorMap* mb = p.lora_slot_tmaps + (long long)q.x * p.lora_maps_per_slot + p.lora_map_b;
                   if (p.lora_fence_maps) tensormap_fence_acquire_g(mb);
                   tma_load_3d(sa + u * kLoraBTileBytes, mb, &full_bar[sring], q.z, i0, p.lora_layer);
-                  bulk_load_1d(sa + S::kABytes + u * kLoraSliceBytes, p.lora_vimg + (long long)q.y * kLoraSliceElems, kLoraSliceBytes,
+                  bulk_load_1d(sa + kU * kLoraBTileBytes + u * kLoraSliceBytes, p.lora_vimg + (long long)q.y * kLoraSliceElems, kLoraSliceBytes,
                                &full_bar[sring]);
                 }
               }
               const int used = min(kRound, n - base);
-              const int pos = stage + (used + kLoraUnitsPerStage - 1) / kLoraUnitsPerStage;
+              const int pos = stage + (used + kU - 1) / kU;
               if (pos >= STAGES) { stage = pos - STAGES; phase ^= 1; } else stage = pos;
               __syncwarp();
               ok = (*abort_flag == 0);
@@ -596,7 +602,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
             if (n < 128 && !last) continue;
             if (lane == 0) {
-              for (int base = 0; ok && base < n; base += kLoraUnitsPerStage) {
+              constexpr int kU = S::kUnits;
+              for (int base = 0; ok && base < n; base += kU) {
                 if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
                   report_status(p.status, kTimeoutFullBarrier, w.tile);
                   *abort_flag = 1;
@@ -605,11 +612,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
                 tc_fence_after();
                 const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
-                const int nu = min(kLoraUnitsPerStage, n - base);
+                const int nu = min(kU, n - base);
                 for (int u = 0; u < nu; ++u) {
                   const int4 q = ulist_m[base + u];                  // (c0, c1, w0): accumulator columns [c0, c1) of a window that starts at w0
                   const uint64_t da = make_desc_k_sw32(sa + (uint32_t)(u * kLoraBTileBytes));
-                  const uint64_t db = make_desc_k_sw32(sa + (uint32_t)(S::kABytes + u * kLoraSliceBytes + (q.x - q.z) * 32));
+                  const uint64_t db = make_desc_k_sw32(sa + (uint32_t)(kU * kLoraBTileBytes + u * kLoraSliceBytes + (q.x - q.z) * 32));
                   if (!(p.lora_skip & 32))
                     umma_f16_ss(tmem_d + (uint32_t)(q.x - j0), da, db, make_idesc(kBM, (uint32_t)(q.y - q.x), kFmtBF16, kFmtBF16), 1u);
                 }

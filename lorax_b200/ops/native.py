@@ -75,6 +75,7 @@ def load() -> ctypes.CDLL:
         "lx_lora_fused_desc_bytes": ([], I),
         "lx_quant_act_fp8": ([P, L, P, L, P, I, I, I, P], I),
         "lx_gemm_fp8_block128": ([P, L, P, I, P, L, P, P, L, P, I, I, I, P, L, P, I, P], I),
+        "lx_fp8_block128_dequant": ([P, L, P, I, P, L, I, I, P], I),
         "lx_wq_dequant": ([P, P, P, P, L, I, I, I, I, P], I),
         "lx_wq4_gemm": ([P, L, P, P, P, P, L, I, I, I, I, P], I),
         "lx_wq4_gemm_ex": ([P, L, P, P, P, P, L, I, I, I, I, I, P], I),
@@ -120,7 +121,7 @@ class Workspace:
 
     LORA_KSPLIT = 8
 
-    def __init__(self, device: torch.device, max_tokens: int = 8192, max_lora_cols: int = 3 * 64,
+    def __init__(self, device: torch.device, max_tokens: int = 16384, max_lora_cols: int = 3 * 64,
                  attn_splits: int = 8, num_heads: int = 64, head_dim: int = 128):
         lib = load()
         self.device = device
@@ -138,6 +139,7 @@ class Workspace:
         self.lora_vpart = torch.empty(1024 * 48 * 128, dtype=torch.float32, device=device)
         self.lora_item_counters = torch.zeros(2 * self.lora_max_entries, dtype=torch.int32, device=device)
         self.lora_sync = torch.zeros(2, dtype=torch.int32, device=device)
+        self.fp8_scratch = None              # bf16 image of one fp8 projection (long prefills), allocated on first use
         self.attn_part_tokens = 256
         self.attn_splits = attn_splits
         self.attn_part_o = torch.empty(self.attn_part_tokens * num_heads * attn_splits * head_dim, dtype=torch.float32, device=device)
@@ -189,7 +191,9 @@ class LoraEpilogue(NamedTuple):
 # 1 (default): the GEMM that carries LoRA acquire-fences a slot's B_cat tensor map before every use, as a tensor map that lives
 # in global memory and was written by a copy asks for; 0 skips it (measurement: the fences cost about 3 % of a decode step).
 LORA_FENCE_MAPS = int(os.environ.get("LORAX_LORA_FENCE_MAPS", "1"))
-TC_PREFILL = os.environ.get("LORAX_TC_PREFILL", "1") != "0"       # 0: the mma.sync prefill attention kernel for every shape
+TC_PREFILL = os.environ.get("LORAX_TC_PREFILL", "1") != "0"
+# rows from which an fp8 projection is expanded to bf16 in front of the bf16 GEMM instead of running on the fp8 tensor-core kernel
+FP8_EXPAND_MIN_TOKENS = int(os.environ.get("LORAX_FP8_EXPAND_MIN_TOKENS", "512"))       # 0: the mma.sync prefill attention kernel for every shape
 
 
 class LxLoraFused(ctypes.Structure):
@@ -366,8 +370,18 @@ def gemm_fp8(x: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, bias: Opt
     assert wq.shape[1] == K and w_scale.shape == ((N + 127) // 128, (K + 127) // 128) and w_scale.is_contiguous()
     if out is None:
         out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
-    xq, sa = quant_act_fp8(x)
     ws = workspace(x.device)
+    if T >= FP8_EXPAND_MIN_TOKENS and K % 16 == 0 and wq.stride(0) % 16 == 0:
+        # long prefills: expand this projection's weights to bf16 (one pass, a few per cent of the GEMM) and run the bf16 GEMM; the
+        # fp8 tensor-core kernel below is bound by the per-128 promotion of its partial sums at this size
+        need = N * K
+        if ws.fp8_scratch is None or ws.fp8_scratch.numel() < need:
+            ws.fp8_scratch = torch.empty(need, dtype=torch.bfloat16, device=x.device)
+        w16 = ws.fp8_scratch[:need].view(N, K)
+        _check(load().lx_fp8_block128_dequant(_ptr(wq), wq.stride(0), _ptr(w_scale), w_scale.stride(0), _ptr(w16), K, N, K, _stream()),
+               "lx_fp8_block128_dequant")
+        return gemm(x, w16, bias=bias, out=out)
+    xq, sa = quant_act_fp8(x)
     rc = load().lx_gemm_fp8_block128(_ptr(xq), xq.stride(0), _ptr(sa), sa.stride(0), _ptr(wq), wq.stride(0), _ptr(w_scale), _ptr(out),
                                      out.stride(0), _ptr(bias), T, N, K, _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.status),
                                      ws.num_sms, _stream())

@@ -163,3 +163,25 @@ def test_token_classes_become_entities(emb_stack):
         assert all(g["word"] == text[g["start"]:g["end"]].lower() for g in got)
     finally:
         rt.model.config.id2label = saved
+
+
+def test_python_clients_classify_and_embed(emb_stack):
+    """The synchronous and the asyncio client against the routes of an embedding / token-classification deployment."""
+    import asyncio
+    from lorax_b200.client import AsyncClient, Client
+    url = f"http://127.0.0.1:{emb_stack['port']}"
+    c = Client(url)
+    one = c.classify("w5 w9 w77")
+    many = c.classify_batch(["w5 w9 w77", "w8"])
+    assert len(one.entities) == 3 and len(many) == 2 and many[0].entities == one.entities
+    assert len(c.embed("w5 w9").embeddings) == 64
+
+    async def run():
+        ac = AsyncClient(url)
+        a = await ac.classify("w5 w9 w77")
+        b = await ac.classify_batch(["w5 w9 w77", "w8"])
+        e = await ac.embed("w5 w9")
+        return a, b, e, await ac.health(), await ac.info()
+    a, b, e, ok, info = asyncio.run(run())
+    assert a.entities == one.entities and [x.entities for x in b] == [x.entities for x in many]
+    assert len(e.embeddings) == 64 and ok and info["model_id"] == "tiny-distilbert"

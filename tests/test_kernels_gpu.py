@@ -496,11 +496,27 @@ def test_gemm_fp8_block128(nat, T, N, K):
     a, b_ = xq.view(torch.float8_e4m3fn).float(), xq_ref.float()
     assert ((a - b_).abs() <= b_.abs() * 0.13 + 2e-3).all()          # x * (1 / s) against x / s: at most one e4m3 step apart
     assert (a != b_).float().mean().item() < 0.03
-    out = nat.gemm_fp8(x, wq, ws, bias=b)
+    saved = nat.FP8_EXPAND_MIN_TOKENS
+    nat.FP8_EXPAND_MIN_TOKENS = 1 << 30            # the fp8 tensor-core kernel at every size
+    try:
+        out = nat.gemm_fp8(x, wq, ws, bias=b)
+    finally:
+        nat.FP8_EXPAND_MIN_TOKENS = saved
     torch.cuda.synchronize()
     nat.workspace().check_status()
     want = ref.gemm_fp8(x, wq, ws, bias=b)
     assert _rel_err(out, want) < 6e-3
+    # long prefills expand the weights to bf16 and keep the activations in bf16: the oracle is x @ dequant(w)^T
+    nat.FP8_EXPAND_MIN_TOKENS = 1
+    try:
+        out2 = nat.gemm_fp8(x, wq, ws, bias=b)
+    finally:
+        nat.FP8_EXPAND_MIN_TOKENS = saved
+    torch.cuda.synchronize()
+    nat.workspace().check_status()
+    want2 = x.float() @ ref.dequantize_weight_fp8_block128(wq, ws).float().t()[:K, :N] + b.float() if False else \
+        x.float() @ ref.dequantize_weight_fp8_block128(wq, ws)[:N, :K].float().t() + b.float()
+    assert _rel_err(out2, want2) < 6e-3
     # and the quantised product is close to the bf16 one
     full = x.float() @ w.float().t() + b.float()
     assert _rel_err(out, full) < 6e-2
