@@ -146,7 +146,7 @@ def bench_lora(results, peaks):
             out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
             n0 = parts[0] if nparts > 1 else N
             n1 = parts[0] + parts[1] if nparts > 2 else N
-            lf = native.LoraFused(tiles, tiles.shape[0], len(tl), tmaps, 2 * G, 0, G, slot_rank, slot_base, nparts, n0, n1, 0, r)
+            lf = native.LoraFused(tiles, tiles.shape[0], len(tl), tmaps, 2 * G, 0, G, slot_rank, slot_base, nparts, n0, n1, 0, r, arena, 0, nparts * K)
 
             def separate(i):
                 v = native.lora_shrink_tiles(x, tiles, tiles.shape[0], 32, tmaps, 2 * G, 0, slot_rank, nparts, 0, r, live_tiles=len(tl))

@@ -109,7 +109,7 @@ def gemm_lora_case(T, parts=(4096, 1024, 1024)):
     out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
     n0 = parts[0] if nparts > 1 else N
     n1 = parts[0] + parts[1] if nparts > 2 else N
-    lf = native.LoraFused(tiles, tiles.shape[0], len(tl), tmaps, 2 * G, 0, G, slot_rank, slot_base, nparts, n0, n1, 0, r)
+    lf = native.LoraFused(tiles, tiles.shape[0], len(tl), tmaps, 2 * G, 0, G, slot_rank, slot_base, nparts, n0, n1, 0, r, arena, 0, nparts * K)
     for i in range(4):
         assert native.gemm_lora_fused(x, ws[i], lf, out=out) is not None
 

@@ -3,7 +3,8 @@
     python benchmarks/profile_step.py [--model mistral-7b] [--batch 256] [--ctx 700] [--prefill 1024] [--adapters 100]
 
 Runs the steps eagerly (no CUDA graph) with every operator bracketed by CUDA events, so the numbers include the
-launch gap of each kernel; the shares tell where a step spends its time.
+launch gap of each kernel; the shares tell where a step spends its time.  With `--graph-steps N` the decode step is captured
+in a CUDA graph and replayed N times instead (the serving path); a launch list taken over that run gives each kernel's own time.
 """
 
 from __future__ import annotations
@@ -37,6 +38,9 @@ def main():
     ap.add_argument("--rank", type=int, default=16)
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--graph-steps", type=int, default=0,
+                    help="instead of the eager breakdown, replay the captured decode graph this many times and print the mean step "
+                         "time; under `ncu --metrics gpu__time_duration.sum` this lists every kernel of a decode step")
     a = ap.parse_args()
     mc = {"mistral-7b": cfgs.mistral_7b, "llama3-8b": cfgs.llama3_8b, "tiny": cfgs.tiny_llama}[a.model]()
     if a.layers:
@@ -57,7 +61,7 @@ def main():
     page = 32
     blocks_per = (a.ctx + 64 + page - 1) // page
     kv = KVCache(mc.num_hidden_layers, a.batch * blocks_per + 64, model.nkv, model.d, torch.bfloat16, dev)
-    runner = ModelRunner(model, kv, max_batch=a.batch, max_seq_tokens=a.ctx + 64, max_prefill_tokens=max(a.prefill, 4096), use_graphs=False)
+    runner = ModelRunner(model, kv, max_batch=a.batch, max_seq_tokens=a.ctx + 64, max_prefill_tokens=max(a.prefill, 4096), use_graphs=a.graph_steps > 0)
     g = torch.Generator().manual_seed(0)
     rows = [runner.state.take_row(i) for i in range(a.batch)]
     blocks = [[1 + i * blocks_per + j for j in range(blocks_per)] for i in range(a.batch)]
@@ -65,6 +69,21 @@ def main():
     runner.install(rows, [1] * a.batch, [a.ctx] * a.batch, blocks, ads)
     runner.resort()
     results = {}
+    if a.graph_steps:
+        for _ in range(3):
+            runner.decode()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.graph_steps):
+            runner.decode()
+        e1.record()
+        torch.cuda.synchronize()
+        native.workspace().check_status()
+        key = next(iter(runner.graph_kernels))
+        print(json.dumps(dict(batch=a.batch, ctx=a.ctx, layers=mc.num_hidden_layers, graph_steps=a.graph_steps,
+                              kernels_per_step=runner.graph_kernels[key], step_ms=round(e0.elapsed_time(e1) / a.graph_steps, 3))))
+        return
     # ---- decode
     for _ in range(2):
         runner.decode()

@@ -332,7 +332,8 @@ class AdapterManager:
         n0, n1 = gi.bounds
         g = TMAP_GROUPS.index(group)
         return LoraFused(tiles.table, tiles.num_tiles, tiles.live, self.slot_tmaps, self.groups_per_slot, g, len(TMAP_GROUPS) + g,
-                         self.slot_rank, self.slot_base, len(gi.parts), n0, n1, 0 if group == LM_HEAD else layer, self.max_rank)
+                         self.slot_rank, self.slot_base, len(gi.parts), n0, n1, 0 if group == LM_HEAD else layer, self.max_rank,
+                         self.arena, self.layout.unit_off(group, layer, "A"), self.layout.unit_off(group, layer, "B"))
 
     def expand(self, ops, epi, y: torch.Tensor, tiles: Optional[LoraTiles] = None):
         """y += v B_cat(slot(t))^T: the second half of the LoRA delta as its own launch (`epi` comes from `shrink`)."""

@@ -12,16 +12,16 @@
 //     HBM exactly once.  Small grids are widened with split-K; the last CTA to finish a tile reduces the
 //     fp32 partials in a fixed order (deterministic) and writes bf16.
 //
-// Multi-adapter LoRA rides in the same launch (template flag LORA, weights on the M side).  The reference runs a
-// shrink kernel, the base GEMM and an expand kernel per projection and rank group
-// (server/lorax_server/utils/layers.py:114-164); here a CTA first works through "shrink items" -- for one run of rows of
-// one adapter, v = x A_cat^T on the tensor cores, stored as a bf16 image already in the shared-memory layout of a UMMA
-// operand -- and then through the base tiles, where after the K loop the delta is added by further UMMAs
-// (B_cat tile of the adapter x that image, K = rank) straight into the TMEM accumulator.  The epilogue is unchanged.
-// The operands of those UMMAs are 32-byte-swizzled K slices of 16 ranks (4 KB of B_cat, 1.5 KB of image), four of them per
-// pipeline stage, so a base tile pays one stage per four adapters of its rows.  A CTA counts itself in when its shrink
-// items are done and the first base tile that needs an image waits until every CTA of the launch has; every CTA
-// finishes its shrink items before its first base tile, so that wait cannot deadlock, and it is bounded like the others.
+// Multi-adapter LoRA (template flag LORA, weights on the M side).  The reference runs a shrink kernel, the base GEMM and an
+// expand kernel per projection and rank group (server/lorax_server/utils/layers.py:114-164).  Here the shrink of a step of up
+// to a few hundred rows is a launch of matrix-vector products (`lora_shrink_rows_kernel`, one CTA per four rows of an adapter
+// and 16 rank rows) that writes v = x A_cat^T as bf16 images already in the shared-memory layout of a UMMA operand, and the
+// expand rides inside the GEMM: after the K loop of a base tile the delta is added by further UMMAs (B_cat tile of the adapter
+// x that image, K = rank) straight into the TMEM accumulator, so the epilogue is unchanged and the output is written once.
+// The operands of those UMMAs are 32-byte-swizzled K slices of 16 ranks (4 KB of B_cat, 1.5 KB of image), up to eight per
+// pipeline stage.  B_cat tiles of every adapter come through four arena-wide tensor maps (one per rank class) that are kernel
+// parameters: a third coordinate, in 16-byte steps, says where the adapter's B_cat starts, so no per-adapter descriptor is
+// fetched or fenced.  The list of a token tile's units is built once per CTA and reused for every feature tile.
 //
 // Structure: persistent CTAs of 6 warps.  Warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and
 // TMEM owner, warps 2..5 = epilogue (each warp reads its own 32-lane TMEM quadrant with tcgen05.ld).  A STAGES
@@ -69,13 +69,11 @@ struct GemmParams {
   int lora_num_slots;
   int lora_nparts, lora_n0, lora_n1;   // parts of the fused projection (q | k | v, gate | up) and their boundaries (multiples of 128)
   int lora_layer;
-  __nv_bfloat16* lora_vimg;            // [tile][part][4 K slices][48 rows][16] bf16: v as K-major, 32-byte-swizzled UMMA operand images
-  float* lora_vpart;                   // [ksplit][tile * chunks][48][128] fp32 partials of the K splits (ksplit > 1)
-  int lora_ksplit, lora_chunks;        // K splits of a shrink item; 128-row chunks of A_cat (nparts * max rank / 128, rounded up)
-  int* lora_counters;                  // [tile * chunks] arrivals of the K splits, zero between launches
-  int* lora_sync;                      // [2] CTAs of this launch that have finished / whose shrink items are done; zero between launches
+  __nv_bfloat16* lora_vimg;            // [part][4 K slices][entry][48 rows][16] bf16: v as K-major, 32-byte-swizzled UMMA operand images
+  long long lora_off_b;                // B_cat of the group and layer: slot_base + rank * lora_off_b (elements)
+  int lora_arena_maps;                 // 1: B_cat tiles come through the four arena-wide maps of the launch (LoraBMaps), not the slots' own
   int lora_fence_maps;                 // 1: acquire-fence a slot's B_cat map before every use (0: never; measurement only)
-  int lora_skip;                       // measurement only: bit 0 leaves out the shrink items, bit 1 the expand stages (results are then wrong)
+  int lora_skip;                       // measurement only: bit 0 leaves out the shrink launch, bit 1 the expand stages (results are then wrong)
   int lora_T;                          // rows of the step
 };
 
@@ -107,67 +105,35 @@ LX_DEVICE uint64_t make_desc_k_sw32(uint32_t smem_addr) {
   return d;
 }
 
-// Bounded wait for *flag == want.  False when the budget ran out.
-LX_DEVICE bool wait_flag(const int* flag, int want, volatile int* abort_flag) {
-  uint64_t t0 = 0;
-  uint32_t polls = 0;
-  while (ld_acquire_gpu(flag) != want) {
-    if ((++polls & 255u) == 0) {
-      if (abort_flag != nullptr && *abort_flag != 0) return false;
-      const uint64_t now = global_timer_ns();
-      if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitBudgetNs) return false;
-    }
-  }
-  return true;
-}
-
 // The table of the step, checked once per CTA and kept in shared memory: the producer and the MMA thread walk it for every
 // base tile, and a walk through global memory (entry -> slot -> rank, each a trip to L2) costs more than the tile itself.
 constexpr int kLoraMaxEntries = 512;
-struct LoraEnt { int slot, row0, nrows, r; };          // r == 0: nothing to do for the entry; slot < 0: end of the live entries
+struct LoraEnt { int slot, row0; short nrows, r; int boff; };    // r == 0: nothing to do for the entry; slot < 0: end of the live entries
+static_assert(sizeof(LoraEnt) == 16, "one 16-byte word per entry");
 LX_DEVICE void load_lora_entries(const GemmParams& p, LoraEnt* ents) {
   for (int lt = threadIdx.x; lt < p.lora_num_tiles; lt += blockDim.x) {
     const LoraTileG t = p.lora_tiles[lt];
-    LoraEnt e{t.slot, t.row0, min(min(t.nrows, 32), p.lora_T - t.row0), 0};
+    LoraEnt e{t.slot, t.row0, (short)max(min(min(t.nrows, 32), p.lora_T - t.row0), -1), 0, 0};
     if (t.slot >= 0 && t.slot < p.lora_num_slots && e.nrows > 0 && t.row0 >= 0) {
       const int r = p.lora_slot_rank[t.slot];
-      if (r > 0 && r <= 64 && (r & 15) == 0 && p.lora_slot_base[t.slot] >= 0) e.r = r;
+      const long long base = p.lora_slot_base[t.slot];
+      if (r > 0 && r <= 64 && (r & 15) == 0 && base >= 0) {
+        const long long b = base + (long long)r * p.lora_off_b;      // first element of B_cat, as a coordinate in 16-byte steps
+        if (p.lora_arena_maps && ((b & 7) != 0 || (b >> 3) > 0x7fffffffll)) {
+          report_status(p.status, kBadIndex, lt);                    // a blob that the arena-wide maps cannot address
+        } else {
+          e.r = (short)r;
+          e.boff = (int)(b >> 3);
+        }
+      }
     }
     ents[lt] = e;
   }
 }
 
-LX_DEVICE int shrink_kblocks_per_stage(int a_region, int x_region, int a_sub, int x_sub) {
-  return max(1, min(min(a_region / a_sub, x_region / x_sub), 4));
-}
-
-// One shrink item: k-blocks [kb0, kb1) of chunk `chunk` (128 rows of A_cat) of table entry `lt`.
-struct ShrinkItem {
-  int lt, chunk, split, slot, row0, nrows, r, R, box_rows, w0, wn, kb0, kb1;
-};
-LX_DEVICE bool decode_shrink_item(const GemmParams& p, const LoraEnt* ents, int idx, int kblocks, ShrinkItem& it) {
-  const int per_tile = p.lora_chunks * p.lora_ksplit;
-  it.lt = idx / per_tile;
-  const int rem = idx - it.lt * per_tile;
-  it.chunk = rem / p.lora_ksplit;
-  it.split = rem - it.chunk * p.lora_ksplit;
-  const LoraEnt t = ents[it.lt];
-  if (t.r == 0) return false;
-  it.slot = t.slot; it.row0 = t.row0; it.nrows = t.nrows; it.r = t.r;
-  it.R = it.r * p.lora_nparts;
-  if (it.chunk * kBM >= it.R) return false;
-  it.box_rows = min(kBM, (it.R + 15) / 16 * 16);       // must match the encoder of the A_cat maps
-  it.w0 = t.row0 & ~15;
-  it.wn = ((t.row0 + it.nrows + 15) & ~15) - it.w0;    // 16, 32 or 48
-  it.kb0 = (int)((long long)kblocks * it.split / p.lora_ksplit);
-  it.kb1 = (int)((long long)kblocks * (it.split + 1) / p.lora_ksplit);
-  return it.kb1 > it.kb0;
-}
-
 // The part of table entry `lt` that adds to accumulator columns [c0, c1) of the token tile whose rows are [j0, jlim).
 struct ExpandItem {
-  int slot, r, w0, c0, c1;
+  int slot, r, w0, c0, c1, boff;
 };
 // -1: end of the live entries, 0: nothing to add for this entry, 1: `e` is valid.
 LX_DEVICE int decode_expand_item(const LoraEnt* ents, int lt, int j0, int jlim, ExpandItem& e) {
@@ -176,6 +142,7 @@ LX_DEVICE int decode_expand_item(const LoraEnt* ents, int lt, int j0, int jlim, 
   if (t.r == 0) return 0;
   e.slot = t.slot;
   e.r = t.r;
+  e.boff = t.boff;
   e.w0 = t.row0 & ~15;
   const int w1 = (t.row0 + t.nrows + 15) & ~15;
   e.c0 = max(e.w0, j0);
@@ -260,12 +227,20 @@ struct GemmWorkIter {
 };
 
 // ---- expand units, built by a whole warp ------------------------------------------------------------------------
-// A unit = one K slice (16 ranks) of one table entry that meets the token tile.  The producer warp and the MMA warp each
-// build the same list in their own shared-memory area, 32 entries at a time (one per lane, ranks -> slices by a warp prefix
-// sum): walking the table in a single thread costs more than the base tile itself.
+// A unit = one K slice (16 ranks) of one table entry that meets the token tile.  The producer warp and the MMA warp each build
+// the same list in their own shared-memory area, 32 entries at a time (one per lane, ranks -> slices by a warp prefix sum), and
+// keep it while the token tile stays the same: it does not depend on the feature tile.
+struct LoraUnit {
+  int slot, img;        // img = entry * 4 + slice
+  int c0, c1;           // accumulator columns [c0, c1) the unit adds to
+  int w0;               // first row of the entry's 16-aligned window
+  int boff;             // B_cat of the slot, group and layer in 16-byte steps from the arena's start
+  int rclass;           // rank / 16 - 1: which arena-wide map has the slot's row pitch
+  int pad_;
+};
+static_assert(sizeof(LoraUnit) == 32, "two 16-byte words per unit");
 constexpr int kLoraListCap = 256;       // units a list holds; it is worked off whenever it holds 128 or more
-template <bool PRODUCER>
-LX_DEVICE int lora_build_units(const GemmParams& p, const LoraEnt* ents, int lt0, int part, int j0, int jlim, int4* list, int n, bool& ended) {
+LX_DEVICE int lora_build_units(const GemmParams& p, const LoraEnt* ents, int lt0, int j0, int jlim, LoraUnit* list, int n, bool& ended) {
   const int lane = threadIdx.x & 31;
   const int lt = lt0 + lane;
   ExpandItem e;
@@ -283,16 +258,17 @@ LX_DEVICE int lora_build_units(const GemmParams& p, const LoraEnt* ents, int lt0
   const int total = __shfl_sync(0xffffffffu, incl, 31);
   for (int sl = 0; sl < nsl; ++sl) {
     const int idx = n + excl + sl;
-    if (idx < kLoraListCap)
-      list[idx] = PRODUCER ? make_int4(e.slot, (lt * p.lora_nparts + part) * 4 + sl, sl * 16, 0) : make_int4(e.c0, e.c1, e.w0, 0);
+    if (idx < kLoraListCap) list[idx] = LoraUnit{e.slot, lt * 4 + sl, e.c0, e.c1, e.w0, e.boff, e.r / 16 - 1, 0};
   }
   ended = endmask != 0;
   __syncwarp();
   return min(n + total, kLoraListCap);
 }
 
-// x through boxes of 16, 32 and 48 rows: a shrink item loads only the 16-aligned window its rows lie in.
-struct LoraXMaps { CUtensorMap m[3]; };
+// B_cat of every slot through one map per rank class: dims {rank, N, arena / 16 bytes} with strides {2 * rank, 16} bytes, box
+// {16, 128, 1}, 32-byte swizzle.  The third coordinate is where the slot's B_cat starts, so one descriptor, passed as a kernel
+// parameter, serves every adapter: nothing to fetch from memory per slot and nothing to fence.
+struct LoraBMaps { CUtensorMap m[4]; };
 
 LX_DEVICE void tensormap_fence_acquire_g(const CUtensorMap* m) {
   asm volatile("fence.proxy.tensormap::generic.acquire.gpu [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
@@ -308,16 +284,18 @@ struct GemmSmem {
   // expand units that share a stage: B_cat tiles first, then the image slices
   static constexpr int kUnits = (kStageBytes / kLoraUnitBytes) < 8 ? (kStageBytes / kLoraUnitBytes) : 8;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kEntBytes = LORA ? kLoraMaxEntries * (int)sizeof(LoraEnt) + 2 * kLoraListCap * 16 : 0;    // entry table + two unit lists
-  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + kEntBytes + 1024;  // +1024 for manual alignment
+  static constexpr int kEntBytes = LORA ? kLoraMaxEntries * (int)sizeof(LoraEnt) + 2 * kLoraListCap * 32 : 0;    // entry table + two unit lists
+  static constexpr int kEpiBytes = 4 * 32 * 32 * 2;     // per epilogue warp, 32 tokens x 32 features: the transposing store of the weights-on-M path
+  static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + kEntBytes + kEpiBytes + 1024;  // +1024 for manual alignment
 };
 
 template <int BN, int STAGES, bool LORA>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                         const __grid_constant__ LoraXMaps xmaps, const GemmParams p) {
+                         const __grid_constant__ LoraBMaps bmaps, const GemmParams p) {
   pdl_trigger();
   using S = GemmSmem<BN, STAGES, LORA>;
+  static_assert(S::kTotal <= 227 * 1024, "shared memory of one CTA");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* tiles = smem;
@@ -329,8 +307,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_base_slot + 2));
   LoraEnt* ents = reinterpret_cast<LoraEnt*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes);
-  int4* ulist_p = reinterpret_cast<int4*>(ents + kLoraMaxEntries);      // producer warp's expand units
-  int4* ulist_m = ulist_p + kLoraListCap;                               // MMA warp's
+  LoraUnit* ulist_p = reinterpret_cast<LoraUnit*>(ents + kLoraMaxEntries);      // producer warp's expand units
+  LoraUnit* ulist_m = ulist_p + kLoraListCap;                                   // MMA warp's
+  __nv_bfloat16* epi_stage = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes + S::kEntBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -341,7 +320,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const int num_tiles = tiles_a * tiles_b;
   const int kblocks = (p.K + kBK - 1) / kBK;
   const bool lora = LORA && p.lora_tiles != nullptr;
-  const int n_shrink = (lora && !(p.lora_skip & 1)) ? p.lora_num_tiles * p.lora_chunks * p.lora_ksplit : 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -379,43 +357,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   // Work item w -> (tile, split).  Tiles are ordered with the A tile index fastest inside one B tile so that
   // CTAs running at the same time share the B operand through L2.
   if (warp == 0) {
-    // Lane 0 feeds the ring for shrink items and base k-blocks; the LoRA stages of a tile are fed by the whole warp.
+    // Lane 0 feeds the ring with base k-blocks; the LoRA stages of a tile are fed by the whole warp, one lane per unit.
     const uint64_t pol_a = p.hint_a_first ? policy_evict_first() : policy_evict_last();
     const uint64_t pol_b = p.hint_a_first ? policy_evict_last() : policy_evict_first();
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    bool shrink_seen = false;
-    if constexpr (LORA) {
-      if (lane == 0) {
-        for (int idx = (int)blockIdx.x; ok && idx < n_shrink; idx += (int)gridDim.x) {
-          ShrinkItem it;
-          if (!decode_shrink_item(p, ents, idx, kblocks, it)) continue;
-          const CUtensorMap* ma = p.lora_slot_tmaps + (long long)it.slot * p.lora_maps_per_slot + p.lora_map_a;
-          tensormap_fence_acquire_g(ma);
-          const CUtensorMap* mx = &xmaps.m[it.wn / 16 - 1];
-          // the operands of a shrink item are thin: several k-blocks share a stage, so that the ring holds enough bytes in flight
-          const int a_sub = it.box_rows * kBK * 2, x_sub = it.wn * kBK * 2;
-          const int kps = shrink_kblocks_per_stage(S::kABytes, S::kBBytes, a_sub, x_sub);
-          for (int kb = it.kb0; kb < it.kb1; kb += kps) {
-            const int n = min(kps, it.kb1 - kb);
-            if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
-              report_status(p.status, kTimeoutEmptyBarrier, -1 - idx);
-              *abort_flag = 1;
-              ok = false;
-              break;
-            }
-            uint8_t* sa = tiles + stage * S::kStageBytes;
-            mbar_expect_tx(&full_bar[stage], (uint32_t)(n * (a_sub + x_sub)));
-            for (int q = 0; q < n; ++q) {
-              tma_load_3d(sa + q * a_sub, ma, &full_bar[stage], (kb + q) * kBK, it.chunk * kBM, p.lora_layer);
-              tma_load_2d_hint(sa + S::kABytes + q * x_sub, mx, &full_bar[stage], (kb + q) * kBK, it.w0, pol_b);
-            }
-            if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          }
-        }
-      }
-    }
+    int list_tb = -1, list_n = 0;          // token tile whose complete unit list sits in ulist_p
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
     GemmWork w;
     while (it.next(w)) {
@@ -439,65 +387,64 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       }
       if constexpr (LORA) {
         if (lora && w.kb0 == 0 && !(p.lora_skip & 2)) {
-          // the LoRA delta of this tile: K slices of 16 ranks of every table entry whose rows meet the token tile, four per stage
+          // the LoRA delta of this tile: one unit per K slice of 16 ranks of every table entry whose rows meet the token tile
           __syncwarp();
           stage = __shfl_sync(0xffffffffu, stage, 0);
           phase = __shfl_sync(0xffffffffu, phase, 0);
           ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
           const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
           const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
-          if (ok && !shrink_seen) {
-            if (lane == 0) {
-              if (!wait_flag(&p.lora_sync[1], (int)gridDim.x, abort_flag)) {
-                report_status(p.status, kTimeoutSplitK, w.tile);
-                *abort_flag = 1;
-              }
-            }
-            __syncwarp();
-            ok = (*abort_flag == 0);
-            fence_proxy_async_all();       // the images were written with ordinary stores; bulk copies read them
-            shrink_seen = true;
-          }
+          const long long img_part = (long long)part * 4 * p.lora_num_tiles;      // images: [part][slice][entry][48 x 16]
           constexpr int kU = S::kUnits;
-          constexpr int kRound = STAGES * kU;       // units that fill the ring once (<= 32)
-          static_assert(kRound <= 32, "one lane per unit of a round");
-          int n = 0;
+          const bool cached = (list_tb == tb);
+          int n = cached ? list_n : 0;
           bool ended = false;
-          for (int lt0 = 0; ok && !ended && lt0 < p.lora_num_tiles; lt0 += 32) {
-            n = lora_build_units<true>(p, ents, lt0, part, j0, jlim, ulist_p, n, ended);
-            const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
-            if (n < 128 && !last) continue;
-            // work the list off, one trip around the ring per round: lane i feeds unit i of the round
-            for (int base = 0; ok && base < n; base += kRound) {
-              const int gu = base + lane;
-              if (lane < kRound && gu < n) {
-                const int sidx = lane / kU, u = lane % kU;
-                const int pos = stage + sidx;
-                const int sring = pos >= STAGES ? pos - STAGES : pos;
-                const uint32_t ph = phase ^ (pos >= STAGES ? 1u : 0u);
-                if (!mbar_wait(&empty_bar[sring], ph ^ 1, abort_flag)) {
+          int flushes = 0;
+          for (int lt0 = 0; ok && (cached || (!ended && lt0 < p.lora_num_tiles)); lt0 += 32) {
+            if (!cached) {
+              n = lora_build_units(p, ents, lt0, j0, jlim, ulist_p, n, ended);
+              const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
+              if (n < 128 && !last) continue;
+              if (last && flushes == 0) { list_tb = tb; list_n = n; }        // the whole tile in one piece: the next tile reuses it
+              ++flushes;
+            }
+            for (int base = 0; ok && base < n; base += kU) {
+              const int nu = min(kU, n - base);
+              if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+                if (lane == 0) {
                   report_status(p.status, kTimeoutEmptyBarrier, w.tile);
                   *abort_flag = 1;
+                }
+                ok = false;
+                break;
+              }
+              uint8_t* sa = tiles + stage * S::kStageBytes;
+              if (lane == 0) mbar_expect_tx(&full_bar[stage], (uint32_t)(nu * kLoraUnitBytes));
+              __syncwarp();
+              LoraUnit q{};
+              if (lane < nu) q = ulist_p[base + lane];
+              // image slices of consecutive entries are consecutive in memory: one copy serves the stage
+              const int y0 = __shfl_sync(0xffffffffu, q.img, 0);
+              const bool in_row = lane >= nu || (q.img == y0 + 4 * lane && (q.img & 3) == 0);
+              const bool one_copy = __all_sync(0xffffffffu, in_row);
+              if (lane < nu) {
+                if (p.lora_arena_maps) {
+                  tma_load_3d(sa + lane * kLoraBTileBytes, &bmaps.m[q.rclass], &full_bar[stage], (q.img & 3) * 16, i0, q.boff);
                 } else {
-                  uint8_t* sa = tiles + sring * S::kStageBytes;
-                  if (u == 0) {
-                    const int in_stage = min(kU, n - (base + sidx * kU));
-                    mbar_expect_tx(&full_bar[sring], (uint32_t)(in_stage * kLoraUnitBytes));
-                  }
-                  const int4 q = ulist_p[gu];
-                  const CUtensorMap* mb = p.lora_slot_tmaps + (long long)q.x * p.lora_maps_per_slot + p.lora_map_b;
+                  const CUtensorMap* mb = p.lora_slot_tmaps + (long long)q.slot * p.lora_maps_per_slot + p.lora_map_b;
                   if (p.lora_fence_maps) tensormap_fence_acquire_g(mb);
-                  tma_load_3d(sa + u * kLoraBTileBytes, mb, &full_bar[sring], q.z, i0, p.lora_layer);
-                  bulk_load_1d(sa + kU * kLoraBTileBytes + u * kLoraSliceBytes, p.lora_vimg + (long long)q.y * kLoraSliceElems, kLoraSliceBytes,
-                               &full_bar[sring]);
+                  tma_load_3d(sa + lane * kLoraBTileBytes, mb, &full_bar[stage], (q.img & 3) * 16, i0, p.lora_layer);
+                }
+                const long long img = (img_part + (long long)(q.img & 3) * p.lora_num_tiles + (q.img >> 2)) * kLoraSliceElems;
+                if (!one_copy) {
+                  bulk_load_1d(sa + kU * kLoraBTileBytes + lane * kLoraSliceBytes, p.lora_vimg + img, kLoraSliceBytes, &full_bar[stage]);
+                } else if (lane == 0) {
+                  bulk_load_1d(sa + kU * kLoraBTileBytes, p.lora_vimg + img, (uint32_t)(nu * kLoraSliceBytes), &full_bar[stage]);
                 }
               }
-              const int used = min(kRound, n - base);
-              const int pos = stage + (used + kU - 1) / kU;
-              if (pos >= STAGES) { stage = pos - STAGES; phase ^= 1; } else stage = pos;
-              __syncwarp();
-              ok = (*abort_flag == 0);
+              if (++stage == STAGES) { stage = 0; phase ^= 1; }
             }
+            if (cached) break;
             n = 0;
           }
         }
@@ -512,50 +459,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
     bool ok = true;
-    if constexpr (LORA) {
-      if (lane == 0) {
-        for (int idx = (int)blockIdx.x; ok && idx < n_shrink; idx += (int)gridDim.x) {
-          ShrinkItem it;
-          if (!decode_shrink_item(p, ents, idx, kblocks, it)) continue;
-          if (!mbar_wait(&tmem_empty[acc], acc_phase[acc] ^ 1, abort_flag)) {
-            report_status(p.status, kTimeoutTmemEmpty, -1 - idx);
-            *abort_flag = 1;
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint32_t tmem_d = tmem_base + (uint32_t)(acc * S::kAcc);
-          const uint32_t idesc_s = make_idesc(kBM, (uint32_t)it.wn, kFmtBF16, kFmtBF16);
-          const int a_sub = it.box_rows * kBK * 2, x_sub = it.wn * kBK * 2;
-          const int kps = shrink_kblocks_per_stage(S::kABytes, S::kBBytes, a_sub, x_sub);
-          for (int kb = it.kb0; kb < it.kb1; kb += kps) {
-            const int n = min(kps, it.kb1 - kb);
-            if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
-              report_status(p.status, kTimeoutFullBarrier, -1 - idx);
-              *abort_flag = 1;
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
-            for (int q = 0; q < n; ++q) {
-              const uint64_t da = make_desc_k_sw128(sa + (uint32_t)(q * a_sub));
-              const uint64_t db = make_desc_k_sw128(sa + (uint32_t)(S::kABytes + q * x_sub));
-#pragma unroll
-              for (int k = 0; k < kBK / 16; ++k) {
-                umma_f16_ss(tmem_d, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc_s, (kb + q > it.kb0 || k > 0) ? 1u : 0u);
-              }
-            }
-            tc_commit(&empty_bar[stage]);
-            if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          }
-          if (!ok) break;
-          tc_commit(&tmem_full[acc]);
-          acc_phase[acc] ^= 1;
-          acc ^= 1;
-        }
-      }
-    }
+    int list_tb = -1, list_n = 0;
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
     GemmWork w;
     while (it.next(w)) {
@@ -591,16 +495,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         if (lora && kb0 == 0 && !(p.lora_skip & 2)) {
           __syncwarp();
           ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-          const int ta = p.b_fastest ? w.tile / tiles_b : w.tile % tiles_a;
           const int tb = p.b_fastest ? w.tile % tiles_b : w.tile / tiles_a;
-          const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
-          const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
-          int n = 0;
+          const int j0 = tb * p.bn, jlim = j0 + p.umma_n;
+          const bool cached = (list_tb == tb);
+          int n = cached ? list_n : 0;
           bool ended = false;
-          for (int lt0 = 0; ok && !ended && lt0 < p.lora_num_tiles; lt0 += 32) {
-            n = lora_build_units<false>(p, ents, lt0, part, j0, jlim, ulist_m, n, ended);
-            const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
-            if (n < 128 && !last) continue;
+          int flushes = 0;
+          for (int lt0 = 0; ok && (cached || (!ended && lt0 < p.lora_num_tiles)); lt0 += 32) {
+            if (!cached) {
+              n = lora_build_units(p, ents, lt0, j0, jlim, ulist_m, n, ended);
+              const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
+              if (n < 128 && !last) continue;
+              if (last && flushes == 0) { list_tb = tb; list_n = n; }
+              ++flushes;
+            }
             if (lane == 0) {
               constexpr int kU = S::kUnits;
               for (int base = 0; ok && base < n; base += kU) {
@@ -614,11 +522,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
                 const int nu = min(kU, n - base);
                 for (int u = 0; u < nu; ++u) {
-                  const int4 q = ulist_m[base + u];                  // (c0, c1, w0): accumulator columns [c0, c1) of a window that starts at w0
+                  const LoraUnit q = ulist_m[base + u];
+                  const int c0 = q.c0, c1 = q.c1;
                   const uint64_t da = make_desc_k_sw32(sa + (uint32_t)(u * kLoraBTileBytes));
-                  const uint64_t db = make_desc_k_sw32(sa + (uint32_t)(kU * kLoraBTileBytes + u * kLoraSliceBytes + (q.x - q.z) * 32));
+                  const uint64_t db = make_desc_k_sw32(sa + (uint32_t)(kU * kLoraBTileBytes + u * kLoraSliceBytes + (c0 - q.w0) * 32));
                   if (!(p.lora_skip & 32))
-                    umma_f16_ss(tmem_d + (uint32_t)(q.x - j0), da, db, make_idesc(kBM, (uint32_t)(q.y - q.x), kFmtBF16, kFmtBF16), 1u);
+                    umma_f16_ss(tmem_d + (uint32_t)(c0 - j0), da, db, make_idesc(kBM, (uint32_t)(c1 - c0), kFmtBF16, kFmtBF16), 1u);
                 }
                 tc_commit(&empty_bar[stage]);
                 if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -626,9 +535,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             }
             __syncwarp();                                            // the list is rebuilt by every lane
             ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            if (cached) break;
             n = 0;
           }
-          (void)i0;
         }
       }
       if (lane == 0 && ok) tc_commit(&tmem_full[acc]);       // accumulator complete
@@ -643,92 +552,6 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
     bool alive = true;
-    if constexpr (LORA) {
-      const int n_ids = p.lora_num_tiles * p.lora_chunks;
-      for (int idx = (int)blockIdx.x; alive && idx < n_shrink; idx += (int)gridDim.x) {
-        ShrinkItem it;
-        if (!decode_shrink_item(p, ents, idx, kblocks, it)) continue;
-        if (!mbar_wait(&tmem_full[acc], acc_phase[acc], abort_flag)) {
-          report_status(p.status, kTimeoutTmemFull, -1 - idx);
-          *abort_flag = 1;
-          alive = false;
-          break;
-        }
-        tc_fence_after();
-        acc_phase[acc] ^= 1;
-        const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * S::kAcc);
-        float v[kLoraWin];
-        {
-          uint32_t ra[32], rb[16];
-          tmem_ld_32x32b_x32(taddr, ra);
-          tmem_ld_32x32b_x16(taddr + 32, rb);     // columns 32..47: defined only when the window is 48 wide, masked below
-          tc_wait_ld();
-#pragma unroll
-          for (int q = 0; q < 32; ++q) v[q] = __uint_as_float(ra[q]);
-#pragma unroll
-          for (int q = 0; q < 16; ++q) v[32 + q] = __uint_as_float(rb[q]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
-        acc ^= 1;
-        const int item_id = it.lt * p.lora_chunks + it.chunk;
-        bool writer = true;
-        if (p.lora_ksplit > 1) {
-          // park the partial [column][128 rows]; the last split to arrive adds them up in split order
-          float* __restrict__ mine = p.lora_vpart + ((long long)it.split * n_ids + item_id) * (kLoraWin * kBM) + row_in_tile;
-#pragma unroll
-          for (int c = 0; c < kLoraWin; ++c) {
-            if (c < it.wn) __stcg(mine + c * kBM, v[c]);
-          }
-          __threadfence();
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (threadIdx.x == 64) {
-            const int prev = atomicAdd(&p.lora_counters[item_id], 1);
-            *last_flag = (prev == p.lora_ksplit - 1) ? 1 : 0;
-            if (prev == p.lora_ksplit - 1) p.lora_counters[item_id] = 0;
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          writer = (*last_flag != 0);
-          if (writer) {
-            __threadfence();
-#pragma unroll
-            for (int c = 0; c < kLoraWin; ++c) v[c] = 0.f;
-            for (int sp = 0; sp < p.lora_ksplit; ++sp) {
-              const float* __restrict__ src = p.lora_vpart + ((long long)sp * n_ids + item_id) * (kLoraWin * kBM) + row_in_tile;
-#pragma unroll
-              for (int c = 0; c < kLoraWin; ++c) {
-                if (c < it.wn) v[c] += __ldcg(src + c * kBM);
-              }
-            }
-          }
-          asm volatile("bar.sync 1, 128;" ::: "memory");      // last_flag is reused by the next item
-        }
-        if (writer) {
-          const int j = it.chunk * kBM + row_in_tile;          // row of A_cat = (part, rank index)
-          if (j < it.R) {
-            const int pp = j / it.r, i = j - pp * it.r;
-            __nv_bfloat16* img = p.lora_vimg + (long long)(it.lt * p.lora_nparts + pp) * kLoraImgElems + (i >> 4) * kLoraSliceElems;
-            const int ch = (i >> 3) & 1, within = i & 7;
-#pragma unroll
-            for (int c = 0; c < kLoraWin; ++c) {
-              if (c < it.wn) {
-                const int t = it.w0 + c;
-                const bool live = t >= it.row0 && t < it.row0 + it.nrows;
-                img[c * 16 + (((ch ^ ((c >> 2) & 1)) << 3) | within)] = __float2bfloat16(live ? v[c] : 0.f);
-              }
-            }
-          }
-        }
-      }
-      // this CTA's shrink items are done (a K split that was not the last to arrive has handed its partial over)
-      __threadfence();
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      if (lora && threadIdx.x == 64) {
-        fence_proxy_async_all();
-        red_release_gpu_add(&p.lora_sync[1], 1);
-      }
-    }
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
     GemmWork w;
     while (alive && it.next(w)) {
@@ -747,8 +570,39 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       const int ncols = min(p.bn, p.umma_n);
       const int jend = min(p.b_rows, j0 + ncols);     // columns past it belong to the next tile (or to nobody)
       constexpr int CH = (BN >= 32) ? 32 : 16;
+      // Weights on M: a thread holds one feature of CH tokens, the output rows run along the features.  The warp turns its
+      // 32 x CH block around in shared memory and stores 16 bytes per lane (8 features of one token) instead of 2.
+      const bool turn = p.ldo_a == 1 && (p.ldo_b & 7) == 0 && (p.a_rows & 7) == 0 && (p.bias == nullptr || p.bias_on_a) &&
+                        (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
 
-      if (w.nparts == 0) {
+      if (w.nparts == 0 && turn) {
+        __nv_bfloat16* st = epi_stage + quad * (32 * 32);
+        const float bias_i = (p.bias != nullptr && i < p.a_rows) ? __bfloat162float(p.bias[i]) : 0.f;
+        const int fbase = ta * kBM + quad * 32 + (lane & 3) * 8;
+#pragma unroll 1
+        for (int c = 0; c < ncols; c += CH) {
+          uint32_t r[CH];
+          if constexpr (CH == 32) tmem_ld_32x32b_x32(taddr + c, r);
+          else tmem_ld_32x32b_x16(taddr + c, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int q = 0; q < CH; ++q) st[q * 32 + lane] = __float2bfloat16(__uint_as_float(r[q]) * p.out_scale + bias_i);
+          __syncwarp();
+#pragma unroll
+          for (int h = 0; h < CH / 8; ++h) {
+            const int tq = h * 8 + (lane >> 2);
+            const int t = j0 + c + tq;
+            if (t < jend && fbase < p.a_rows) {
+              const uint4 val = *reinterpret_cast<const uint4*>(st + tq * 32 + (lane & 3) * 8);
+              *reinterpret_cast<uint4*>(p.out + (long long)t * p.ldo_b + fbase) = val;
+            }
+          }
+          __syncwarp();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[acc]);
+      } else if (w.nparts == 0) {
 #pragma unroll 1
         for (int c = 0; c < ncols; c += CH) {
           float v[CH];
@@ -899,18 +753,199 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-  if constexpr (LORA) {
-    // the last CTA to finish clears the two counters for the next launch (every CTA is past its wait by then)
-    if (lora && threadIdx.x == 0) {
-      __threadfence();
-      const int prev = atomicAdd(&p.lora_sync[0], 1);
-      if (prev == (int)gridDim.x - 1) {
-        p.lora_sync[0] = 0;
-        p.lora_sync[1] = 0;
-        __threadfence();
+}
+
+// ---- LoRA shrink of a decode-sized step: v = A_cat(slot(t)) x[t] as matrix-vector products ---------------------------------
+// The rows of a step are few and every one needs r * nparts dot products of length K with its own adapter's A_cat: bound by
+// how fast A_cat streams in.  A CTA takes up to four rows of one table entry (they share the adapter, so A_cat is read once for
+// them) and 16 of the rank rows, two per warp; a lane keeps 16 loads of 16 bytes in flight.  The results are written straight into the operand image of the entry (the layout the expand UMMAs of the GEMM read:
+// [part][K slice][entry][48 rows][16 ranks], 32-byte swizzle); the CTAs that hold the first and the last row of an entry also
+// clear the rows of the 16-aligned window that belong to neighbouring entries.
+struct LoraShrinkRowsParams {
+  const __nv_bfloat16* x;
+  long long ldx;
+  int T, K;
+  const LoraTileG* tiles;
+  int num_tiles;
+  const __nv_bfloat16* arena;
+  const int* slot_rank;
+  const long long* slot_base;
+  int num_slots;
+  long long off_a;          // A_cat of the projection group and layer starts at slot_base + r * off_a (elements)
+  int nparts;
+  __nv_bfloat16* vimg;
+};
+
+LX_DEVICE float dot8_bf16(const uint4& a, const uint4& b) {
+  const __nv_bfloat162* pa = reinterpret_cast<const __nv_bfloat162*>(&a);
+  const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&b);
+  float s = 0.f;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float2 fa = __bfloat1622float2(pa[q]), fb = __bfloat1622float2(pb[q]);
+    s = fmaf(fa.x, fb.x, s);
+    s = fmaf(fa.y, fb.y, s);
+  }
+  return s;
+}
+
+constexpr int kShrinkRowsThreads = 256;
+constexpr int kShrinkG = 4;             // rows of one entry that share a CTA
+__global__ void __launch_bounds__(kShrinkRowsThreads) lora_shrink_rows_kernel(const LoraShrinkRowsParams p) {
+  pdl_trigger();
+  extern __shared__ uint8_t smem_raw[];
+  uint4* xs = reinterpret_cast<uint4*>(smem_raw);                    // up to four rows of x, K bf16 each
+  __shared__ int s_ent[5];                                           // entry index, slot, first row of the entry, its rows, group
+  __shared__ int s_warp[8];
+  __shared__ float s_v[3 * 64 * kShrinkG];
+  const int tid = (int)threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) s_ent[0] = -1;
+  // CTA b -> (entry, group of four rows): groups are numbered entry by entry (a prefix sum over the table).  The table is
+  // written by copies that the stream orders before every kernel: it may be read before the wait below.
+  int seen = 0;                                                      // groups of the entries before this round
+  for (int lt0 = 0; lt0 < p.num_tiles; lt0 += kShrinkRowsThreads) {
+    const int lt = lt0 + tid;
+    int cnt = 0, slot = -1, row0 = 0, nr = 0;
+    if (lt < p.num_tiles) {
+      const LoraTileG e = p.tiles[lt];
+      nr = min(min(e.nrows, 32), p.T - e.row0);
+      slot = e.slot; row0 = e.row0;
+      if (e.slot >= 0 && e.slot < p.num_slots && e.row0 >= 0 && nr > 0) cnt = (nr + kShrinkG - 1) / kShrinkG;
+    }
+    int incl = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += v;
+    }
+    __syncthreads();                                                 // s_warp of the round before has been read
+    if (lane == 31) s_warp[warp] = incl;
+    __syncthreads();
+    int before = seen;
+    for (int w = 0; w < warp; ++w) before += s_warp[w];
+    const int first = before + incl - cnt;                           // this entry's groups are [first, first + cnt)
+    const int b = (int)blockIdx.x;
+    if (cnt > 0 && b >= first && b < first + cnt) {
+      s_ent[0] = lt; s_ent[1] = slot; s_ent[2] = row0; s_ent[3] = nr; s_ent[4] = b - first;
+    }
+    for (int w = 0; w < 8; ++w) seen += s_warp[w];
+  }
+  __syncthreads();
+  pdl_wait();
+  const int lt = s_ent[0];
+  if (lt < 0) return;
+  const int slot = s_ent[1], row0 = s_ent[2], nrows = s_ent[3];
+  const int t0 = row0 + s_ent[4] * kShrinkG;
+  const int nt = min(kShrinkG, row0 + nrows - t0);                   // rows of this CTA: [t0, t0 + nt)
+  const int r = p.slot_rank[slot];
+  const long long base = p.slot_base[slot];
+  if (r <= 0 || r > 64 || (r & 15) != 0 || base < 0) return;         // the GEMM skips the entry for the same reasons
+  const int R = r * p.nparts;
+  const int j_lo = (int)blockIdx.y * 16, j_hi = min(j_lo + 16, R);   // rank rows of this CTA, two per warp
+  if (j_lo >= R) return;
+  const int half = j_hi - j_lo;
+  const int K8 = p.K >> 3;
+  for (int q = 0; q < nt; ++q) {
+    const uint4* xg = reinterpret_cast<const uint4*>(p.x + (long long)(t0 + q) * p.ldx);
+    for (int k = tid; k < K8; k += kShrinkRowsThreads) xs[q * K8 + k] = xg[k];
+  }
+  __syncthreads();
+  const __nv_bfloat16* a_cat = p.arena + base + (long long)r * p.off_a;
+  {
+    const int j = j_lo + 2 * warp;          // r is a multiple of 16: both rows exist
+    const uint4* a0 = reinterpret_cast<const uint4*>(a_cat + (long long)j * p.K);
+    const uint4* a1 = reinterpret_cast<const uint4*>(a_cat + (long long)(j + 1) * p.K);
+    constexpr bool two = true;
+    float s0[kShrinkG], s1[kShrinkG];
+#pragma unroll
+    for (int q = 0; q < kShrinkG; ++q) s0[q] = s1[q] = 0.f;
+    for (int k0 = lane; k0 < K8; k0 += 32 * 8) {
+      uint4 va[8], vb[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int k = k0 + 32 * u;
+        va[u] = k < K8 ? __ldg(a0 + k) : make_uint4(0, 0, 0, 0);
+        vb[u] = (two && k < K8) ? __ldg(a1 + k) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int k = k0 + 32 * u;
+        if (k < K8) {
+#pragma unroll
+          for (int q = 0; q < kShrinkG; ++q) {
+            if (q < nt) {
+              const uint4 xv = xs[q * K8 + k];
+              s0[q] += dot8_bf16(va[u], xv);
+              s1[q] += dot8_bf16(vb[u], xv);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < kShrinkG; ++q) {
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) {
+        s0[q] += __shfl_xor_sync(0xffffffffu, s0[q], d);
+        s1[q] += __shfl_xor_sync(0xffffffffu, s1[q], d);
+      }
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int q = 0; q < kShrinkG; ++q) {
+        s_v[q * 192 + j] = s0[q];
+        if (two) s_v[q * 192 + j + 1] = s1[q];
       }
     }
   }
+  __syncthreads();
+  // image rows: 16 bytes = 8 ranks of one part; row c of the window holds row w0 + c of the step
+  const int w0 = row0 & ~15;
+  const int wn = ((row0 + nrows + 15) & ~15) - w0;
+  const int nchunks = half >> 3;
+  for (int u = tid; u < nchunks * nt; u += kShrinkRowsThreads) {
+    const int q = u / nchunks, uc = u - q * nchunks;
+    const int c = t0 + q - w0;
+    const int j = j_lo + uc * 8;
+    const int pp = j / r, i = j - pp * r;
+    const int sl = i >> 4, ch = (i >> 3) & 1;
+    __nv_bfloat16* img = p.vimg + ((long long)(pp * 4 + sl) * p.num_tiles + lt) * kLoraSliceElems;
+    uint32_t pk[4];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) pk[h] = pack_bf16x2(s_v[q * 192 + j + 2 * h], s_v[q * 192 + j + 2 * h + 1]);
+    *reinterpret_cast<uint4*>(img + c * 16 + ((ch ^ ((c >> 2) & 1)) << 3)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+  }
+  // rows of the window outside the entry: [0, z_lo) by the CTA of the first row, [z_hi, wn) by the CTA of the last one
+  const int z_lo = (t0 == row0) ? row0 - w0 : 0;
+  const int z_hi = (t0 + nt == row0 + nrows) ? row0 + nrows - w0 : wn;
+  const int zrows = z_lo + (wn - z_hi);
+  for (int u = tid; u < nchunks * zrows; u += kShrinkRowsThreads) {
+    const int cz = u / nchunks, uc = u - cz * nchunks;
+    const int row = cz < z_lo ? cz : z_hi + (cz - z_lo);
+    const int j = j_lo + uc * 8;
+    const int pp = j / r, i = j - pp * r;
+    const int sl = i >> 4, ch = (i >> 3) & 1;
+    __nv_bfloat16* img = p.vimg + ((long long)(pp * 4 + sl) * p.num_tiles + lt) * kLoraSliceElems;
+    *reinterpret_cast<uint4*>(img + row * 16 + (ch << 3)) = make_uint4(0, 0, 0, 0);      // both chunks of a row are cleared: no swizzle needed
+  }
+}
+
+static int launch_lora_shrink_rows(const LoraShrinkRowsParams& p, int max_rank, int num_sms, cudaStream_t stream) {
+  const size_t smem = (size_t)p.K * 2 * kShrinkG;
+  if (smem > 200 * 1024) return 1;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || !configured[dev])) {
+    cudaError_t e = cudaFuncSetAttribute(lora_shrink_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return -(int)e;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int gy = (p.nparts * max_rank + 15) / 16;
+  (void)num_sms;
+  launch_pdl(lora_shrink_rows_kernel, dim3(p.T, gy), dim3(kShrinkRowsThreads), smem, stream, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -(int)e;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -948,8 +983,38 @@ int make_tmap_bf16_kmajor(CUtensorMap* out, const void* base, uint64_t rows, uin
   return r == CUDA_SUCCESS ? 0 : -(int)r - 100;
 }
 
+// The four arena-wide B_cat maps of a projection with N output features (see LoraBMaps).  0 on success.
+static int make_lora_bmaps(LoraBMaps* out, const void* arena, long long arena_elems, int N) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr || (reinterpret_cast<uintptr_t>(arena) & 15) != 0) return -1;
+  struct Key { const void* arena; long long elems; int N; };
+  static Key keys[8];
+  static LoraBMaps vals[8];
+  static int used = 0, next = 0;
+  for (int i = 0; i < used; ++i) {
+    if (keys[i].arena == arena && keys[i].elems == arena_elems && keys[i].N == N) { *out = vals[i]; return 0; }
+  }
+  LoraBMaps bm{};
+  for (int c = 0; c < 4; ++c) {
+    const cuuint64_t r = 16 * (c + 1);
+    cuuint64_t dims[3] = {r, (cuuint64_t)N, (cuuint64_t)(arena_elems / 8)};
+    cuuint64_t strides[2] = {r * 2, 16};
+    cuuint32_t box[3] = {16, (cuuint32_t)kBM, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult rc = fn(&bm.m[c], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(arena), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) return -2;
+  }
+  const int slot = used < 8 ? used++ : (next++ & 7);
+  keys[slot] = Key{arena, arena_elems, N};
+  vals[slot] = bm;
+  *out = bm;
+  return 0;
+}
+
 template <int BN, int STAGES, bool LORA>
-static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const LoraXMaps& xm, const GemmParams& p, int grid,
+static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const LoraBMaps& bm, const GemmParams& p, int grid,
                          cudaStream_t stream) {
   using S = GemmSmem<BN, STAGES, LORA>;
   // the shared-memory opt-in is a per-device attribute: one flag per device ordinal
@@ -961,14 +1026,14 @@ static int launch_gemm_t(const CUtensorMap& ta, const CUtensorMap& tb, const Lor
     if (e != cudaSuccess) return -(int)e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
-  launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, LORA>, dim3(grid), dim3(kGemmThreads), (size_t)S::kTotal, stream, ta, tb, xm, p);
+  launch_pdl(gemm_bf16_tcgen05_kernel<BN, STAGES, LORA>, dim3(grid), dim3(kGemmThreads), (size_t)S::kTotal, stream, ta, tb, bm, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -(int)e;
 }
 
 template <int BN, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
-  static const LoraXMaps none{};
+  static const LoraBMaps none{};
   return launch_gemm_t<BN, STAGES, false>(ta, tb, none, p, grid, stream);
 }
 
@@ -1072,18 +1137,17 @@ extern "C" {
 long long lx_gemm_ws_bytes() { return 64ll << 20; }
 int lx_gemm_max_tiles() { return 8192; }
 
-// Everything the LoRA part of a launch needs (see GemmParams).  `ksplit` is the K split of the shrink items the caller
-// wants (it knows how many table entries are live); the scratch sizes bound what can be served.
+// Everything the LoRA part of a launch needs (see GemmParams): the table of the step, the slots' B_cat tensor maps for the
+// expand stages, where the slots' blobs lie for the shrink kernel, and the scratch the operand images go to.
 struct LxLoraFused {
   const void* tiles; int num_tiles;
   const void* slot_tmaps; int maps_per_slot, map_a, map_b;
   const int* slot_rank; const long long* slot_base; int num_slots;
-  int nparts, n0, n1, layer, max_rank, ksplit;
+  int nparts, n0, n1, layer, max_rank;
   void* vimg; long long vimg_bytes;
-  float* vpart; long long vpart_bytes;
-  int* counters; int n_counters;
-  int* sync;                    // two ints, zero before the first launch
   int fence_maps;
+  const void* arena; long long off_a;      // A_cat of the group and layer: arena + slot_base + rank * off_a (elements)
+  long long off_b, arena_elems;            // B_cat likewise; the arena's size bounds the arena-wide maps
 };
 
 static int gemm_impl(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
@@ -1173,29 +1237,36 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
     p.lora_slot_rank = lora->slot_rank; p.lora_slot_base = lora->slot_base; p.lora_num_slots = lora->num_slots;
     p.lora_nparts = lora->nparts; p.lora_n0 = lora->n0; p.lora_n1 = lora->n1; p.lora_layer = lora->layer;
     p.lora_vimg = reinterpret_cast<__nv_bfloat16*>(lora->vimg);
-    p.lora_vpart = lora->vpart;
-    p.lora_chunks = (lora->nparts * lora->max_rank + kBM - 1) / kBM;
-    int ks = lora->ksplit < 1 ? 1 : lora->ksplit;
-    if (ks > kblocks_all / 4) ks = kblocks_all / 4 < 1 ? 1 : kblocks_all / 4;
-    const long long ids = (long long)lora->num_tiles * p.lora_chunks;
-    while (ks > 1 && (long long)ks * ids * kLoraWin * kBM * 4 > lora->vpart_bytes) --ks;
-    p.lora_ksplit = ks;
-    p.lora_counters = lora->counters; p.lora_sync = lora->sync; p.lora_fence_maps = lora->fence_maps;
+    p.lora_fence_maps = lora->fence_maps;
+    p.lora_off_b = lora->off_b;
+    LoraBMaps bm{};
+    p.lora_arena_maps = (lora->arena_elems > 0 && make_lora_bmaps(&bm, lora->arena, lora->arena_elems, N) == 0) ? 1 : 0;
+    {
+      const char* e = getenv("LORAX_LORA_ARENA_MAPS");       // measurement only
+      if (e && atoi(e) == 0) p.lora_arena_maps = 0;
+    }
     {
       const char* e = getenv("LORAX_LORA_SKIP");       // measurement only
       p.lora_skip = e ? atoi(e) : 0;
     }
     p.lora_T = T;
-    LoraXMaps xm;
-    for (int i = 0; i < 3; ++i) {
-      if (make_tmap_bf16_kmajor(&xm.m[i], x, T, K, ldx, 16 * (i + 1))) return -1004;
+    if (!(p.lora_skip & 1)) {
+      LoraShrinkRowsParams sp{};
+      sp.x = reinterpret_cast<const __nv_bfloat16*>(x); sp.ldx = ldx; sp.T = T; sp.K = K;
+      sp.tiles = p.lora_tiles; sp.num_tiles = p.lora_num_tiles;
+      sp.arena = reinterpret_cast<const __nv_bfloat16*>(lora->arena);
+      sp.slot_rank = lora->slot_rank; sp.slot_base = lora->slot_base; sp.num_slots = lora->num_slots;
+      sp.off_a = lora->off_a; sp.nparts = lora->nparts;
+      sp.vimg = p.lora_vimg;
+      const int rc = launch_lora_shrink_rows(sp, lora->max_rank, num_sms, stream);
+      if (rc != 0) return rc;
     }
     switch (template_bn(bn)) {
-      case 16:  return launch_gemm_t<16, 8, true>(ta, tb, xm, p, pl.grid, stream);
-      case 32:  return launch_gemm_t<32, 8, true>(ta, tb, xm, p, pl.grid, stream);
-      case 64:  return launch_gemm_t<64, 8, true>(ta, tb, xm, p, pl.grid, stream);
-      case 128: return launch_gemm_t<128, 6, true>(ta, tb, xm, p, pl.grid, stream);
-      default:  return launch_gemm_t<256, 4, true>(ta, tb, xm, p, pl.grid, stream);
+      case 16:  return launch_gemm_t<16, 8, true>(ta, tb, bm, p, pl.grid, stream);
+      case 32:  return launch_gemm_t<32, 8, true>(ta, tb, bm, p, pl.grid, stream);
+      case 64:  return launch_gemm_t<64, 8, true>(ta, tb, bm, p, pl.grid, stream);
+      case 128: return launch_gemm_t<128, 6, true>(ta, tb, bm, p, pl.grid, stream);
+      default:  return launch_gemm_t<256, 4, true>(ta, tb, bm, p, pl.grid, stream);
     }
   }
   switch (template_bn(bn)) {
@@ -1207,11 +1278,6 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   }
 }
 
-// out[T, N] = x[T, K] @ w[N, K]^T (+ bias[N]).  `ldx`, `ldw`, `ldo` are row strides in elements.
-// mode: low byte 0 = choose, 1 = force weights on the M side (small T), 2 = force activations on the M side; bits 8..9 the
-// stream-K policy (0 by cost, 1 whole tiles only, 2 stream-K whenever a wave is partly filled).
-// force_split: low 16 bits an exact classic K split, high 16 bits a forced token tile.
-// Returns 0 or a negative error; device-side timeouts are reported through `status` (2 ints, zeroed by the caller).
 // The plan the weights-on-M path would use for a shape: out5 = {token tile, classic split, whole tiles, stream-K CTAs, grid}.
 int lx_gemm_plan(int T, int N, int K, int num_sms, long long ws_bytes, int force_split, int sk_policy, int* out5) {
   lx::GemmPlan pl = lx::choose_plan_swap(T, N, K, num_sms, ws_bytes, ws_bytes > 0, force_split & 0xffff, force_split >> 16, sk_policy);
@@ -1219,6 +1285,11 @@ int lx_gemm_plan(int T, int N, int K, int num_sms, long long ws_bytes, int force
   return 0;
 }
 
+// out[T, N] = x[T, K] @ w[N, K]^T (+ bias[N]).  `ldx`, `ldw`, `ldo` are row strides in elements.
+// mode: low byte 0 = choose, 1 = force weights on the M side (small T), 2 = force activations on the M side; bits 8..9 the
+// stream-K policy (0 by cost, 1 whole tiles only, 2 stream-K whenever a wave is partly filled).
+// force_split: low 16 bits an exact classic K split, high 16 bits a forced token tile.
+// Returns 0 or a negative error; device-side timeouts are reported through `status` (2 ints, zeroed by the caller).
 int lx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
                  long long ldw, long long ldo, float out_scale, void* ws, long long ws_bytes, int* counters,
                  int* status, int num_sms, int mode, int force_split, void* stream_) {
@@ -1226,21 +1297,20 @@ int lx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, int 
                    nullptr, stream_);
 }
 
-// The same GEMM with the multi-adapter LoRA of the step in the same launch: shrink items first, then the base tiles with the
-// delta added by UMMAs into their accumulators (see the top of this file).  One launch replaces the shrink kernel, the base
-// GEMM and the expand kernel of the reference (server/lorax_server/utils/layers.py:114-164).
-// Returns 1 (nothing launched) when the launch cannot serve the step: a part boundary that is not a multiple of 128, a rank
+// The same GEMM with the multi-adapter LoRA of the step: a row-wise shrink launch that writes the operand images, then the
+// base tiles with the delta added by UMMAs into their accumulators (see the top of this file).  They replace the shrink
+// kernel, the base GEMM and the expand kernel of the reference (server/lorax_server/utils/layers.py:114-164).
+// Returns 1 (nothing launched) when the step cannot be served this way: a part boundary that is not a multiple of 128, a rank
 // above 64, or scratch too small for the table; the caller then runs shrink, GEMM and expand as separate launches.
 int lx_gemm_bf16_lora(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
                       long long ldw, long long ldo, void* ws, long long ws_bytes, int* counters, int* status, int num_sms,
                       const LxLoraFused* lora, void* stream_) {
   if (lora == nullptr || lora->tiles == nullptr || lora->num_tiles <= 0)
     return gemm_impl(x, w, out, bias, T, N, K, ldx, ldw, ldo, 1.f, ws, ws_bytes, counters, status, num_sms, 0, 0, nullptr, stream_);
-  const int chunks = (lora->nparts * lora->max_rank + lx::kBM - 1) / lx::kBM;
   const bool bounds_ok = (lora->nparts == 1) || ((lora->n0 % lx::kBM) == 0 && (lora->nparts == 2 || (lora->n1 % lx::kBM) == 0));
   if (!bounds_ok || lora->max_rank > 64 || lora->max_rank <= 0 || lora->nparts < 1 || lora->nparts > 3 || N < lx::kBM) return 1;
   if ((long long)lora->num_tiles * lora->nparts * lx::kLoraImgElems * 2 > lora->vimg_bytes) return 1;
-  if ((long long)lora->num_tiles * chunks > lora->n_counters || lora->num_tiles > lx::kLoraMaxEntries) return 1;
+  if (lora->num_tiles > lx::kLoraMaxEntries || lora->arena == nullptr || (K & 7) != 0) return 1;
   return gemm_impl(x, w, out, bias, T, N, K, ldx, ldw, ldo, 1.f, ws, ws_bytes, counters, status, num_sms, 1, 0, lora, stream_);
 }
 

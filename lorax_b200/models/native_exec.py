@@ -47,8 +47,7 @@ class LxModelDesc(Structure):
                 ("attn_part_o", P), ("attn_part_lse", P), ("attn_splits", I), ("attn_part_tokens", I),
                 ("arena", P), ("slot_base", P), ("slot_rank", P), ("slot_tmaps", P),
                 ("num_slots", I), ("max_rank", I), ("groups_per_slot", I), ("fused_lora", I),
-                ("lora_vimg", P), ("lora_vimg_bytes", L), ("lora_vpart", P), ("lora_vpart_bytes", L),
-                ("lora_item_counters", P), ("n_lora_item_counters", I), ("lora_fence_maps", I), ("lora_sync", P),
+                ("lora_vimg", P), ("lora_vimg_bytes", L), ("arena_elems", L), ("lora_fence_maps", I),
                 ("tc_prefill", I), ("kv_blocks", I)]
 
 
@@ -140,9 +139,8 @@ class NativeExecutor:
             m.num_slots, m.max_rank, m.groups_per_slot = ad.slot_rank.shape[0], ad.max_rank, ad.groups_per_slot
             m.fused_lora = int(model.fused_lora_max_tokens)        # rows up to which LoRA rides inside the GEMM launch
             m.lora_vimg, m.lora_vimg_bytes = ws.lora_vimg.data_ptr(), ws.lora_vimg.numel() * 2
-            m.lora_vpart, m.lora_vpart_bytes = ws.lora_vpart.data_ptr(), ws.lora_vpart.numel() * 4
-            m.lora_item_counters, m.n_lora_item_counters = ws.lora_item_counters.data_ptr(), ws.lora_item_counters.numel()
-            m.lora_fence_maps, m.lora_sync = native.LORA_FENCE_MAPS, ws.lora_sync.data_ptr()
+            m.arena_elems = ad.arena.numel()
+            m.lora_fence_maps = native.LORA_FENCE_MAPS
         self.m = m
         self.layers = (LxLayerDesc * len(model.layers))()
         for li, lw in enumerate(model.layers):

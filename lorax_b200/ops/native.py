@@ -132,13 +132,9 @@ class Workspace:
         self.lora_v3 = torch.zeros(self.LORA_KSPLIT, max_tokens, max_lora_cols, dtype=torch.float32, device=device)
         self.lora_v = torch.zeros(max_tokens, max_lora_cols, dtype=torch.float32, device=device)     # shrink result
         self.lora_counters = torch.zeros(16384, dtype=torch.int32, device=device)
-        # LoRA inside the GEMM launch: bf16 operand images of the shrink results (6 KB per table entry and part), fp32 partials
-        # of their K splits, split counters per (entry, 128-row chunk), and the two launch-wide counters
+        # LoRA expand inside the GEMM launch: bf16 operand images of the shrink results (6 KB per table entry and part)
         self.lora_max_entries = 1024
         self.lora_vimg = torch.zeros(self.lora_max_entries * 3 * 48 * 64, dtype=torch.bfloat16, device=device)
-        self.lora_vpart = torch.empty(1024 * 48 * 128, dtype=torch.float32, device=device)
-        self.lora_item_counters = torch.zeros(2 * self.lora_max_entries, dtype=torch.int32, device=device)
-        self.lora_sync = torch.zeros(2, dtype=torch.int32, device=device)
         self.fp8_scratch = None              # bf16 image of one fp8 projection (long prefills), allocated on first use
         self.attn_part_tokens = 256
         self.attn_splits = attn_splits
@@ -202,11 +198,11 @@ class LxLoraFused(ctypes.Structure):
                 ("slot_tmaps", ctypes.c_void_p), ("maps_per_slot", ctypes.c_int), ("map_a", ctypes.c_int), ("map_b", ctypes.c_int),
                 ("slot_rank", ctypes.c_void_p), ("slot_base", ctypes.c_void_p), ("num_slots", ctypes.c_int),
                 ("nparts", ctypes.c_int), ("n0", ctypes.c_int), ("n1", ctypes.c_int), ("layer", ctypes.c_int),
-                ("max_rank", ctypes.c_int), ("ksplit", ctypes.c_int),
+                ("max_rank", ctypes.c_int),
                 ("vimg", ctypes.c_void_p), ("vimg_bytes", ctypes.c_longlong),
-                ("vpart", ctypes.c_void_p), ("vpart_bytes", ctypes.c_longlong),
-                ("counters", ctypes.c_void_p), ("n_counters", ctypes.c_int),
-                ("sync", ctypes.c_void_p), ("fence_maps", ctypes.c_int)]
+                ("fence_maps", ctypes.c_int),
+                ("arena", ctypes.c_void_p), ("off_a", ctypes.c_longlong),
+                ("off_b", ctypes.c_longlong), ("arena_elems", ctypes.c_longlong)]
 
 
 class LoraFused(NamedTuple):
@@ -225,6 +221,9 @@ class LoraFused(NamedTuple):
     n1: int
     layer: int
     max_rank: int
+    arena: Optional[torch.Tensor] = None      # the slots' blobs; A_cat of the group and layer at slot_base + rank * off_a (elements)
+    off_a: int = 0
+    off_b: int = 0                            # B_cat likewise
 
 
 def lora_fused_desc(ws: "Workspace", lf: LoraFused, K: int) -> LxLoraFused:
@@ -233,13 +232,9 @@ def lora_fused_desc(ws: "Workspace", lf: LoraFused, K: int) -> LxLoraFused:
     d.slot_tmaps, d.maps_per_slot, d.map_a, d.map_b = lf.slot_tmaps.data_ptr(), lf.maps_per_slot, lf.map_a, lf.map_b
     d.slot_rank, d.slot_base, d.num_slots = lf.slot_rank.data_ptr(), lf.slot_base.data_ptr(), lf.slot_rank.shape[0]
     d.nparts, d.n0, d.n1, d.layer, d.max_rank = lf.nparts, lf.n0, lf.n1, lf.layer, lf.max_rank
-    chunks = (lf.nparts * lf.max_rank + 127) // 128
-    live = lf.live or lf.num_tiles
-    d.ksplit = max(1, min(8, ws.num_sms // max(1, live * chunks), ((K + 63) // 64) // 8))      # about one round of shrink items per CTA
     d.vimg, d.vimg_bytes = ws.lora_vimg.data_ptr(), ws.lora_vimg.numel() * 2
-    d.vpart, d.vpart_bytes = ws.lora_vpart.data_ptr(), ws.lora_vpart.numel() * 4
-    d.counters, d.n_counters = ws.lora_item_counters.data_ptr(), ws.lora_item_counters.numel()
-    d.sync = ws.lora_sync.data_ptr()
+    d.arena, d.off_a = (lf.arena.data_ptr() if lf.arena is not None else None), lf.off_a
+    d.off_b, d.arena_elems = lf.off_b, (lf.arena.numel() if lf.arena is not None else 0)
     d.fence_maps = LORA_FENCE_MAPS
     return d
 

@@ -405,7 +405,7 @@ def test_gemm_with_lora_in_the_same_launch(nat, T, K, parts, ranks):
     b = torch.randn(N, device="cuda", dtype=torch.bfloat16)
     for call in range(2):
         x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
-        lf = nat.LoraFused(tiles, tiles.shape[0], len(tl), tmaps, 2 * G, 0, G, slot_rank, slot_base, nparts, n0, n1, layer, max(ranks))
+        lf = nat.LoraFused(tiles, tiles.shape[0], len(tl), tmaps, 2 * G, 0, G, slot_rank, slot_base, nparts, n0, n1, layer, max(ranks), arena, layer * layer_units, layer * layer_units + nparts * K)
         got = nat.gemm_lora_fused(x, w, lf, bias=b)
         assert got is not None
         torch.cuda.synchronize()
