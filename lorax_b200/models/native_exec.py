@@ -232,10 +232,10 @@ class NativeExecutor:
             native._check(rc, "lx_run_layers")
             pending = fused.ar_out[: T * m.H].view(T, m.H) if ar is not None else out_a
             assert out_ptr.value == pending.data_ptr()
-            fused_lora = T <= m.fused_lora and s.lora_tiles and s.max_tile_rows <= 32 and m.max_rank <= 64     # LoRA adds no launch then
-            lora_sites = 4 if (s.tok_slot and not fused_lora) else 0
+            fused_lora = T <= m.fused_lora and s.lora_tiles and s.max_tile_rows <= 32 and m.max_rank <= 64     # expand rides in the GEMM then
+            lora_launches = (4 if fused_lora else 8) if s.tok_slot else 0        # per layer: shrink (+ expand) at four projections
             attn_kernels = (1 if s.n_decode else 0) + (1 if T > s.n_decode else 0)
-            native.launch_count += nL * (10 + attn_kernels + 2 * lora_sites + (2 if ar is not None else 0)) - 1      # `_check` counted one
+            native.launch_count += nL * (10 + attn_kernels + lora_launches + (2 if ar is not None else 0)) - 1      # `_check` counted one
             if ar is not None:
                 fused.ar_calls += 2 * nL
             self._keep = [normed, qkv, attn, gate_up, act, out_a, inp, ar]
@@ -248,8 +248,9 @@ class NativeExecutor:
             rc = lib.lx_layer_mlp(ctypes.byref(m), l, ctypes.byref(s), a_res.data_ptr(), residual.data_ptr(), rm, buf_b.data_ptr(), stream)
             native._check(rc, "lx_layer_mlp")
             pending = tp.all_reduce(buf_b) if tp.world_size > 1 else buf_b
-        lora_sites = 4 if s.tok_slot else 0
+        fused_lora = T <= m.fused_lora and s.lora_tiles and s.max_tile_rows <= 32 and m.max_rank <= 64
+        lora_launches = (4 if fused_lora else 8) if s.tok_slot else 0
         attn_kernels = (1 if s.n_decode else 0) + (1 if T > s.n_decode else 0)
-        native.launch_count += len(model.layers) * (8 + attn_kernels + 2 * lora_sites)
+        native.launch_count += len(model.layers) * (8 + attn_kernels + lora_launches)
         self._keep = [normed, qkv, attn, gate_up, act, out_a, inp]
         return pending, residual
