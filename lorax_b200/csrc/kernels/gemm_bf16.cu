@@ -12,16 +12,21 @@
 //     HBM exactly once.  Small grids are widened with split-K; the last CTA to finish a tile reduces the
 //     fp32 partials in a fixed order (deterministic) and writes bf16.
 //
-// Multi-adapter LoRA (template flag LORA, weights on the M side).  The reference runs a shrink kernel, the base GEMM and an
-// expand kernel per projection and rank group (server/lorax_server/utils/layers.py:114-164).  Here the shrink of a step of up
-// to a few hundred rows is a launch of matrix-vector products (`lora_shrink_rows_kernel`, one CTA per four rows of an adapter
-// and 16 rank rows) that writes v = x A_cat^T as bf16 images already in the shared-memory layout of a UMMA operand, and the
-// expand rides inside the GEMM: after the K loop of a base tile the delta is added by further UMMAs (B_cat tile of the adapter
-// x that image, K = rank) straight into the TMEM accumulator, so the epilogue is unchanged and the output is written once.
+// Multi-adapter LoRA rides in the same launch (template flag LORA, weights on the M side).  The reference runs a shrink kernel,
+// the base GEMM and an expand kernel per projection and rank group (server/lorax_server/utils/layers.py:114-164).  Here
+//   * the shrink, v = x A_cat^T for the few rows of a decode-sized step, is computed by the four epilogue warps while the first
+//     K loop runs (they would wait for the accumulator otherwise): matrix-vector work on mma.sync with operands loaded
+//     straight from global memory, written as bf16 images already in the shared-memory layout of a UMMA operand;
+//   * the expand is added after the K loop of every base tile by further UMMAs (B_cat tile of the adapter x that image,
+//     K = rank) straight into the TMEM accumulator, so the epilogue is unchanged and the output is written once.
 // The operands of those UMMAs are 32-byte-swizzled K slices of 16 ranks (4 KB of B_cat, 1.5 KB of image), up to eight per
 // pipeline stage.  B_cat tiles of every adapter come through four arena-wide tensor maps (one per rank class) that are kernel
 // parameters: a third coordinate, in 16-byte steps, says where the adapter's B_cat starts, so no per-adapter descriptor is
-// fetched or fenced.  The list of a token tile's units is built once per CTA and reused for every feature tile.
+// fetched or fenced.  The list of a token tile's units is built once per CTA and reused for every feature tile.  A CTA counts
+// itself in when its shrink units are done and the first expand stage of a CTA waits until every CTA of the launch has; the
+// launch has at most one CTA per SM, all resident, and the shrink waits for nothing, so that wait cannot deadlock, and it is
+// bounded like the others.  When that wait cannot be used (no counters, blobs the arena-wide maps cannot address) a launch of
+// `lora_shrink_rows_kernel` in front of the GEMM writes the images instead.
 //
 // Structure: persistent CTAs of 6 warps.  Warp 0 = TMA producer (one lane), warp 1 = MMA issuer (one lane) and
 // TMEM owner, warps 2..5 = epilogue (each warp reads its own 32-lane TMEM quadrant with tcgen05.ld).  A STAGES
@@ -71,6 +76,13 @@ struct GemmParams {
   int lora_layer;
   __nv_bfloat16* lora_vimg;            // [part][4 K slices][entry][48 rows][16] bf16: v as K-major, 32-byte-swizzled UMMA operand images
   long long lora_off_b;                // B_cat of the group and layer: slot_base + rank * lora_off_b (elements)
+  long long lora_off_a;                // A_cat likewise
+  const __nv_bfloat16* lora_arena;     // the slots' blobs
+  const __nv_bfloat16* lora_x;         // the step's activations [T, K] (operand B of the GEMM), row stride lora_ldx
+  long long lora_ldx;
+  int lora_max_r;                      // largest rank * parts of a resident adapter: bounds the 8-row blocks of a shrink unit
+  int lora_inline_shrink;              // 1: the epilogue warps compute the shrink during the first K loop (0: a launch in front did)
+  int* lora_sync;                      // [2] CTAs of this launch that have finished / whose shrink units are done; zero between launches
   int lora_arena_maps;                 // 1: B_cat tiles come through the four arena-wide maps of the launch (LoraBMaps), not the slots' own
   int lora_fence_maps;                 // 1: acquire-fence a slot's B_cat map before every use (0: never; measurement only)
   int lora_skip;                       // measurement only: bit 0 leaves out the shrink launch, bit 1 the expand stages (results are then wrong)
@@ -226,6 +238,188 @@ struct GemmWorkIter {
   }
 };
 
+// ---- shrink units, computed by the epilogue warps while the first K loop runs -----------------------------------------------
+// v = A_cat(slot) x for the rows of the step: the rows are few, the work is bound by how fast A_cat streams in, and the four
+// epilogue warps have nothing to do until the first accumulator is complete.  A unit is (a group of up to eight rows of one
+// table entry, 16 rank rows): the four warps split K in 32-element blocks, a lane loads 16 bytes of two rank rows and of one
+// row of x straight from global memory (no staging, no barrier inside the K loop) and feeds them to two mma.sync m16n8k16
+// (the order of k inside a block is permuted the same way for both operands, which a dot product does not see); the loads of
+// the next eight blocks are in flight while the current eight are multiplied.  The warps' partial sums meet in shared memory
+// and go straight into the operand images the expand stages read.  Units are dealt round-robin over the CTAs of the launch;
+// a CTA counts itself in when its units are done (see lora_sync).
+constexpr int kShrinkRows = 8;          // rows of x per unit (the N of the mma)
+LX_DEVICE void lora_group_prefix(const GemmParams& p, const LoraEnt* ents, unsigned short* gstart) {
+  const int lane = threadIdx.x & 31;
+  int run = 0;
+  for (int lt0 = 0; lt0 < p.lora_num_tiles; lt0 += 32) {
+    const int lt = lt0 + lane;
+    int cnt = 0;
+    if (lt < p.lora_num_tiles) {
+      const LoraEnt e = ents[lt];
+      if (e.slot >= 0 && e.r > 0) cnt = (e.nrows + kShrinkRows - 1) / kShrinkRows;
+    }
+    int incl = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, d);
+      if (lane >= d) incl += t;
+    }
+    if (lt < p.lora_num_tiles) gstart[lt] = (unsigned short)(run + incl - cnt);
+    run += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  if (lane == 0) gstart[p.lora_num_tiles] = (unsigned short)run;
+}
+
+struct ShrinkUnit {
+  int lt, t0, nt, r, j;          // entry, first row, rows (<= 8), rank of the slot, first of the unit's 16 rank rows (part * r + i)
+  const __nv_bfloat16* a;        // A_cat row j
+};
+
+LX_DEVICE bool decode_shrink_unit(const GemmParams& p, const LoraEnt* ents, const unsigned short* gstart, int u, int nblk, ShrinkUnit& s) {
+  const int g = u / nblk, jb = u - g * nblk;
+  int lo = 0, hi = p.lora_num_tiles;                     // last entry with gstart <= g
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if ((int)gstart[mid] <= g) lo = mid; else hi = mid;
+  }
+  const LoraEnt e = ents[lo];
+  if (e.slot < 0 || e.r <= 0) return false;
+  const int sub = g - (int)gstart[lo];
+  if (sub * kShrinkRows >= e.nrows || jb * 16 >= e.r * p.lora_nparts) return false;
+  s.lt = lo;
+  s.t0 = e.row0 + sub * kShrinkRows;
+  s.nt = min(kShrinkRows, e.row0 + e.nrows - s.t0);
+  s.r = e.r;
+  s.j = jb * 16;
+  s.a = p.lora_arena + (long long)e.boff * 8 + (long long)e.r * (p.lora_off_a - p.lora_off_b) + (long long)s.j * p.K;
+  return true;
+}
+
+LX_DEVICE void mma_bf16_16x8x16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int kSB = 8;                  // K blocks of a warp per batch of loads
+// The loads of kSB K blocks of this warp (blocks ewarp + 4 * (kSB * batch + i)): rank rows g and g + 8, row g of x.
+LX_DEVICE void shrink_loads(const GemmParams& p, const ShrinkUnit& s, int batch, int ewarp, int lane, uint4* ra, uint4* rb, uint4* rx) {
+  const int K8 = p.K >> 3;
+  const int g = lane >> 2, t = lane & 3;
+  const uint4* a0 = reinterpret_cast<const uint4*>(s.a + (long long)g * p.K);
+  const uint4* a1 = reinterpret_cast<const uint4*>(s.a + (long long)(g + 8) * p.K);
+  const uint4* xr = reinterpret_cast<const uint4*>(p.lora_x + (long long)(s.t0 + g) * p.lora_ldx);
+#pragma unroll
+  for (int i = 0; i < kSB; ++i) {
+    const int kk = (ewarp + 4 * (kSB * batch + i)) * 4 + t;          // 16-byte index inside the row
+    const bool in = kk < K8;
+    ra[i] = in ? __ldg(a0 + kk) : make_uint4(0, 0, 0, 0);
+    rb[i] = in ? __ldg(a1 + kk) : make_uint4(0, 0, 0, 0);
+    rx[i] = (in && g < s.nt) ? xr[kk] : make_uint4(0, 0, 0, 0);
+  }
+}
+
+LX_DEVICE void lora_shrink_units(const GemmParams& p, const LoraEnt* ents, const unsigned short* gstart, float* red, int ewarp, int lane) {
+  const int tid4 = ewarp * 32 + lane;
+  const int nblk = (p.lora_max_r + 15) >> 4;
+  const int U = (int)gstart[p.lora_num_tiles] * nblk;
+  const int nbatch = ((p.K + 31) / 32 + 4 * kSB - 1) / (4 * kSB);    // batches of kSB blocks per warp
+  ShrinkUnit cur;
+  int u = (int)blockIdx.x;
+  while (u < U && !decode_shrink_unit(p, ents, gstart, u, nblk, cur)) u += (int)gridDim.x;
+  if (u < U) {
+    int b = 0, par = 0;
+    uint4 ra[kSB], rb[kSB], rx[kSB];
+    shrink_loads(p, cur, 0, ewarp, lane, ra, rb, rx);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    while (true) {
+      // the batch after this one: the next of the unit, or the first of the CTA's next unit
+      ShrinkUnit nxt = cur;
+      int nb = b + 1, nu = u;
+      bool more = true;
+      if (nb == nbatch) {
+        nb = 0;
+        nu = u + (int)gridDim.x;
+        while (nu < U && !decode_shrink_unit(p, ents, gstart, nu, nblk, nxt)) nu += (int)gridDim.x;
+        more = nu < U;
+      }
+      uint4 na[kSB], nbv[kSB], nx[kSB];
+      if (more) shrink_loads(p, nxt, nb, ewarp, lane, na, nbv, nx);
+#pragma unroll
+      for (int i = 0; i < kSB; ++i) {
+        mma_bf16_16x8x16(acc, ra[i].x, rb[i].x, ra[i].y, rb[i].y, rx[i].x, rx[i].y);
+        mma_bf16_16x8x16(acc, ra[i].z, rb[i].z, ra[i].w, rb[i].w, rx[i].z, rx[i].w);
+      }
+      if (b == nbatch - 1) {
+        // the unit is complete: 16 ranks x up to 8 rows.  This warp holds (rank g, rows 2t, 2t+1) and (rank g + 8, same rows).
+        const int g = lane >> 2, t = lane & 3;
+        float* mine = red + (par * 4 + ewarp) * 128;                // [16 ranks][8 rows]
+        mine[g * 8 + 2 * t] = acc[0];
+        mine[g * 8 + 2 * t + 1] = acc[1];
+        mine[(g + 8) * 8 + 2 * t] = acc[2];
+        mine[(g + 8) * 8 + 2 * t + 1] = acc[3];
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const LoraEnt e = ents[cur.lt];
+        const int w0 = e.row0 & ~15;
+        const int wn = ((e.row0 + e.nrows + 15) & ~15) - w0;
+        const int pp = cur.j / cur.r, i0 = cur.j - pp * cur.r;
+        __nv_bfloat16* img = p.lora_vimg + ((long long)(pp * 4 + (i0 >> 4)) * p.lora_num_tiles + cur.lt) * kLoraSliceElems;
+        if (tid4 < 2 * cur.nt) {
+          // thread -> (row q of the unit, 8 ranks ch): one 16-byte chunk of the image
+          const int q = tid4 >> 1, ch = tid4 & 1;
+          const float* r0 = red + par * 4 * 128;
+          float v[8];
+#pragma unroll
+          for (int h = 0; h < 8; ++h) {
+            const int o = (ch * 8 + h) * 8 + q;
+            v[h] = r0[o] + r0[128 + o] + r0[256 + o] + r0[384 + o];
+          }
+          const int cr = cur.t0 + q - w0;
+          *reinterpret_cast<uint4*>(img + cr * 16 + ((ch ^ ((cr >> 2) & 1)) << 3)) =
+              make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+        }
+        // rows of the window outside the entry: [0, z_lo) with the entry's first group, [z_hi, wn) with its last
+        const int z_lo = (cur.t0 == e.row0) ? e.row0 - w0 : 0;
+        const int z_hi = (cur.t0 + cur.nt == e.row0 + e.nrows) ? e.row0 + e.nrows - w0 : wn;
+        const int zrows = z_lo + (wn - z_hi);
+        if (tid4 >= 32 && tid4 - 32 < 2 * zrows) {
+          const int cz = (tid4 - 32) >> 1, ch = (tid4 - 32) & 1;
+          const int row = cz < z_lo ? cz : z_hi + (cz - z_lo);
+          *reinterpret_cast<uint4*>(img + row * 16 + (ch << 3)) = make_uint4(0, 0, 0, 0);
+        }
+        par ^= 1;
+        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
+      }
+      if (!more) break;
+      cur = nxt; b = nb; u = nu;
+#pragma unroll
+      for (int i = 0; i < kSB; ++i) { ra[i] = na[i]; rb[i] = nbv[i]; rx[i] = nx[i]; }
+    }
+  }
+  // this CTA's units are done: make the images visible to the bulk copies of every CTA, then count in
+  __threadfence();
+  asm volatile("bar.sync 1, 128;" ::: "memory");
+  if (tid4 == 0) {
+    fence_proxy_async_all();
+    red_release_gpu_add(&p.lora_sync[1], 1);
+  }
+}
+
+// Bounded wait for *flag == want.  False when the budget ran out.
+LX_DEVICE bool wait_flag(const int* flag, int want, volatile int* abort_flag) {
+  uint64_t t0 = 0;
+  uint32_t polls = 0;
+  while (ld_acquire_gpu(flag) != want) {
+    if ((++polls & 255u) == 0) {
+      if (abort_flag != nullptr && *abort_flag != 0) return false;
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitBudgetNs) return false;
+    }
+  }
+  return true;
+}
+
 // ---- expand units, built by a whole warp ------------------------------------------------------------------------
 // A unit = one K slice (16 ranks) of one table entry that meets the token tile.  The producer warp and the MMA warp each build
 // the same list in their own shared-memory area, 32 entries at a time (one per lane, ranks -> slices by a warp prefix sum), and
@@ -284,7 +478,9 @@ struct GemmSmem {
   // expand units that share a stage: B_cat tiles first, then the image slices
   static constexpr int kUnits = (kStageBytes / kLoraUnitBytes) < 8 ? (kStageBytes / kLoraUnitBytes) : 8;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kEntBytes = LORA ? kLoraMaxEntries * (int)sizeof(LoraEnt) + 2 * kLoraListCap * 32 : 0;    // entry table + two unit lists
+  // entry table, two unit lists, groups-before-entry prefix (shrink units)
+  static constexpr int kShrinkBytes = LORA ? (kLoraMaxEntries + 8) * 2 : 0;
+  static constexpr int kEntBytes = LORA ? kLoraMaxEntries * (int)sizeof(LoraEnt) + 2 * kLoraListCap * 32 + kShrinkBytes : 0;
   static constexpr int kEpiBytes = 4 * 32 * 32 * 2;     // per epilogue warp, 32 tokens x 32 features: the transposing store of the weights-on-M path
   static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + kEntBytes + kEpiBytes + 1024;  // +1024 for manual alignment
 };
@@ -309,6 +505,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   LoraEnt* ents = reinterpret_cast<LoraEnt*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes);
   LoraUnit* ulist_p = reinterpret_cast<LoraUnit*>(ents + kLoraMaxEntries);      // producer warp's expand units
   LoraUnit* ulist_m = ulist_p + kLoraListCap;                                   // MMA warp's
+  unsigned short* gstart = reinterpret_cast<unsigned short*>(ulist_m + kLoraListCap);   // [entries + 1] four-row groups before an entry
   __nv_bfloat16* epi_stage = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes + S::kEntBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -350,6 +547,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (lora) {
       load_lora_entries(p, ents);
       __syncthreads();
+      if (p.lora_inline_shrink && warp == 2) lora_group_prefix(p, ents, gstart);
+      __syncthreads();
     }
   }
   pdl_wait();      // barriers, TMEM and descriptors are set up while the previous kernel drains; its data is read from here on
@@ -364,6 +563,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     uint32_t phase = 0;
     bool ok = true;
     int list_tb = -1, list_n = 0;          // token tile whose complete unit list sits in ulist_p
+    bool shrink_seen = false;
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
     GemmWork w;
     while (it.next(w)) {
@@ -395,6 +595,19 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           const int i0 = ta * kBM, j0 = tb * p.bn, jlim = j0 + p.umma_n;
           const int part = min(p.lora_nparts - 1, i0 < p.lora_n0 ? 0 : (i0 < p.lora_n1 ? 1 : 2));
           const long long img_part = (long long)part * 4 * p.lora_num_tiles;      // images: [part][slice][entry][48 x 16]
+          if (ok && p.lora_inline_shrink && !shrink_seen) {
+            // the images are written by the epilogue warps of every CTA of this launch; all CTAs are resident (one per SM)
+            if (lane == 0) {
+              if (!wait_flag(&p.lora_sync[1], (int)gridDim.x, abort_flag)) {
+                report_status(p.status, kTimeoutSplitK, w.tile);
+                *abort_flag = 1;
+              }
+            }
+            __syncwarp();
+            ok = (*abort_flag == 0);
+            fence_proxy_async_all();       // the images were written with ordinary stores; bulk copies read them
+            shrink_seen = true;
+          }
           constexpr int kU = S::kUnits;
           const bool cached = (list_tb == tb);
           int n = cached ? list_n : 0;
@@ -552,6 +765,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
     bool alive = true;
+    if constexpr (LORA) {
+      if (lora && p.lora_inline_shrink) lora_shrink_units(p, ents, gstart, reinterpret_cast<float*>(epi_stage), warp - 2, lane);
+    }
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
     GemmWork w;
     while (alive && it.next(w)) {
@@ -753,6 +969,18 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
+  if constexpr (LORA) {
+    // the last CTA to finish clears the two counters for the next launch (every CTA is past its wait by then)
+    if (lora && p.lora_inline_shrink && threadIdx.x == 0) {
+      __threadfence();
+      const int prev = atomicAdd(&p.lora_sync[0], 1);
+      if (prev == (int)gridDim.x - 1) {
+        p.lora_sync[0] = 0;
+        p.lora_sync[1] = 0;
+        __threadfence();
+      }
+    }
+  }
 }
 
 // ---- LoRA shrink of a decode-sized step: v = A_cat(slot(t)) x[t] as matrix-vector products ---------------------------------
@@ -831,41 +1059,57 @@ __global__ void __launch_bounds__(kShrinkRowsThreads) lora_shrink_rows_kernel(co
     for (int w = 0; w < 8; ++w) seen += s_warp[w];
   }
   __syncthreads();
-  pdl_wait();
+  // Everything up to the wait reads only the table and the adapters, which no kernel of the step writes: it runs under the tail
+  // of the kernel in front.  The first 8 loads per rank row are issued here, the rest of the two rows is pulled into L2.
   const int lt = s_ent[0];
-  if (lt < 0) return;
-  const int slot = s_ent[1], row0 = s_ent[2], nrows = s_ent[3];
+  const int slot = lt >= 0 ? s_ent[1] : 0, row0 = s_ent[2], nrows = s_ent[3];
   const int t0 = row0 + s_ent[4] * kShrinkG;
   const int nt = min(kShrinkG, row0 + nrows - t0);                   // rows of this CTA: [t0, t0 + nt)
-  const int r = p.slot_rank[slot];
-  const long long base = p.slot_base[slot];
-  if (r <= 0 || r > 64 || (r & 15) != 0 || base < 0) return;         // the GEMM skips the entry for the same reasons
+  const int r = lt >= 0 ? p.slot_rank[slot] : 0;
+  const long long base = lt >= 0 ? p.slot_base[slot] : -1;
+  const bool live = lt >= 0 && r > 0 && r <= 64 && (r & 15) == 0 && base >= 0;       // the GEMM skips the entry for the same reasons
   const int R = r * p.nparts;
   const int j_lo = (int)blockIdx.y * 16, j_hi = min(j_lo + 16, R);   // rank rows of this CTA, two per warp
-  if (j_lo >= R) return;
-  const int half = j_hi - j_lo;
+  const bool work = live && j_lo < R;
   const int K8 = p.K >> 3;
+  const int j = j_lo + 2 * warp;                                     // r is a multiple of 16: both rows exist
+  const __nv_bfloat16* a_cat = p.arena + (work ? base + (long long)r * p.off_a : 0);
+  const uint4* a0 = reinterpret_cast<const uint4*>(a_cat + (long long)j * p.K);
+  const uint4* a1 = reinterpret_cast<const uint4*>(a_cat + (long long)(j + 1) * p.K);
+  uint4 va[8], vb[8];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int k = lane + 32 * u;
+    const bool in = work && k < K8;
+    va[u] = in ? __ldg(a0 + k) : make_uint4(0, 0, 0, 0);
+    vb[u] = in ? __ldg(a1 + k) : make_uint4(0, 0, 0, 0);
+  }
+  if (work) {
+    for (int k = 256 + lane * 8; k < K8; k += 256) {               // one 128-byte line per lane and step
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a0 + k));
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a1 + k));
+    }
+  }
+  pdl_wait();
+  if (!work) return;
+  const int half = j_hi - j_lo;
   for (int q = 0; q < nt; ++q) {
     const uint4* xg = reinterpret_cast<const uint4*>(p.x + (long long)(t0 + q) * p.ldx);
     for (int k = tid; k < K8; k += kShrinkRowsThreads) xs[q * K8 + k] = xg[k];
   }
   __syncthreads();
-  const __nv_bfloat16* a_cat = p.arena + base + (long long)r * p.off_a;
   {
-    const int j = j_lo + 2 * warp;          // r is a multiple of 16: both rows exist
-    const uint4* a0 = reinterpret_cast<const uint4*>(a_cat + (long long)j * p.K);
-    const uint4* a1 = reinterpret_cast<const uint4*>(a_cat + (long long)(j + 1) * p.K);
-    constexpr bool two = true;
     float s0[kShrinkG], s1[kShrinkG];
 #pragma unroll
     for (int q = 0; q < kShrinkG; ++q) s0[q] = s1[q] = 0.f;
     for (int k0 = lane; k0 < K8; k0 += 32 * 8) {
-      uint4 va[8], vb[8];
+      if (k0 != lane) {
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int k = k0 + 32 * u;
-        va[u] = k < K8 ? __ldg(a0 + k) : make_uint4(0, 0, 0, 0);
-        vb[u] = (two && k < K8) ? __ldg(a1 + k) : make_uint4(0, 0, 0, 0);
+        for (int u = 0; u < 8; ++u) {
+          const int k = k0 + 32 * u;
+          va[u] = k < K8 ? __ldg(a0 + k) : make_uint4(0, 0, 0, 0);
+          vb[u] = k < K8 ? __ldg(a1 + k) : make_uint4(0, 0, 0, 0);
+        }
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
@@ -894,7 +1138,7 @@ __global__ void __launch_bounds__(kShrinkRowsThreads) lora_shrink_rows_kernel(co
 #pragma unroll
       for (int q = 0; q < kShrinkG; ++q) {
         s_v[q * 192 + j] = s0[q];
-        if (two) s_v[q * 192 + j + 1] = s1[q];
+        s_v[q * 192 + j + 1] = s1[q];
       }
     }
   }
@@ -1148,6 +1392,7 @@ struct LxLoraFused {
   int fence_maps;
   const void* arena; long long off_a;      // A_cat of the group and layer: arena + slot_base + rank * off_a (elements)
   long long off_b, arena_elems;            // B_cat likewise; the arena's size bounds the arena-wide maps
+  int* sync;                               // two ints, zero before the first launch (see GemmParams::lora_sync)
 };
 
 static int gemm_impl(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
@@ -1250,7 +1495,20 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
       p.lora_skip = e ? atoi(e) : 0;
     }
     p.lora_T = T;
-    if (!(p.lora_skip & 1)) {
+    p.lora_off_a = lora->off_a;
+    p.lora_arena = reinterpret_cast<const __nv_bfloat16*>(lora->arena);
+    p.lora_x = reinterpret_cast<const __nv_bfloat16*>(x);
+    p.lora_ldx = ldx;
+    p.lora_max_r = lora->nparts * lora->max_rank;
+    p.lora_sync = lora->sync;
+    // the epilogue warps compute the shrink when every CTA of the launch is resident at once (the expand stages wait for all of
+    // them) and the arena-wide maps give the entries their offsets; otherwise a launch in front does
+    p.lora_inline_shrink = (lora->sync != nullptr && p.lora_arena_maps && pl.grid <= num_sms && !(p.lora_skip & 1)) ? 1 : 0;
+    {
+      const char* e = getenv("LORAX_LORA_INLINE_SHRINK");       // measurement only
+      if (e && atoi(e) == 0) p.lora_inline_shrink = 0;
+    }
+    if (!(p.lora_skip & 1) && !p.lora_inline_shrink) {
       LoraShrinkRowsParams sp{};
       sp.x = reinterpret_cast<const __nv_bfloat16*>(x); sp.ldx = ldx; sp.T = T; sp.K = K;
       sp.tiles = p.lora_tiles; sp.num_tiles = p.lora_num_tiles;
@@ -1297,9 +1555,9 @@ int lx_gemm_bf16(const void* x, const void* w, void* out, const void* bias, int 
                    nullptr, stream_);
 }
 
-// The same GEMM with the multi-adapter LoRA of the step: a row-wise shrink launch that writes the operand images, then the
-// base tiles with the delta added by UMMAs into their accumulators (see the top of this file).  They replace the shrink
-// kernel, the base GEMM and the expand kernel of the reference (server/lorax_server/utils/layers.py:114-164).
+// The same GEMM with the multi-adapter LoRA of the step in the same launch: the epilogue warps compute the shrink during the
+// first K loop, the delta is added by UMMAs into the accumulators of the base tiles (see the top of this file).  One launch
+// replaces the shrink kernel, the base GEMM and the expand kernel of the reference (server/lorax_server/utils/layers.py:114-164).
 // Returns 1 (nothing launched) when the step cannot be served this way: a part boundary that is not a multiple of 128, a rank
 // above 64, or scratch too small for the table; the caller then runs shrink, GEMM and expand as separate launches.
 int lx_gemm_bf16_lora(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,

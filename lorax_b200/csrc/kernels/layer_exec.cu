@@ -56,6 +56,7 @@ struct LxLoraFused {
   int fence_maps;
   const void* arena; long long off_a;
   long long off_b, arena_elems;
+  int* sync;
 };
 int lx_gemm_bf16_lora(const void* x, const void* w, void* out, const void* bias, int T, int N, int K, long long ldx,
                       long long ldw, long long ldo, void* ws, long long ws_bytes, int* counters, int* status, int num_sms,
@@ -109,7 +110,7 @@ struct LxModelDesc {
   const void* arena; const long long* slot_base; const int* slot_rank; const void* slot_tmaps;
   int num_slots, max_rank, groups_per_slot, fused_lora;      // fused_lora: rows up to which LoRA rides inside the GEMM launch (0: never)
   // scratch of the GEMM that carries LoRA in its own launch
-  void* lora_vimg; long long lora_vimg_bytes; long long arena_elems; int lora_fence_maps;
+  void* lora_vimg; long long lora_vimg_bytes; long long arena_elems; int* lora_sync; int lora_fence_maps;
   int tc_prefill, kv_blocks;     // tensor-core prefill attention where the shape allows; blocks of the paged cache
 };
 
@@ -143,14 +144,14 @@ int linear_with_lora(const LxModelDesc& m, const LxLayerDesc& l, const LxStepDes
   const LxLoraSite& site = l.lora[site_idx];
   const bool lora = s.tok_slot != nullptr && site.enabled && m.max_rank > 0 && (s.lora_tiles == nullptr || s.num_tiles > 0);
   if (lora && s.lora_tiles != nullptr && s.T <= m.fused_lora && s.max_tile_rows <= 32) {
-    // a row-wise shrink launch, then base tiles and expand UMMAs in one
+    // one launch: shrink on the epilogue warps, base tiles, expand UMMAs
     LxLoraFused f{};
     f.tiles = s.lora_tiles; f.num_tiles = s.num_tiles;
     f.slot_tmaps = m.slot_tmaps; f.maps_per_slot = m.groups_per_slot; f.map_a = site.tmap_group; f.map_b = m.groups_per_slot / 2 + site.tmap_group;
     f.slot_rank = m.slot_rank; f.slot_base = m.slot_base; f.num_slots = m.num_slots;
     f.nparts = site.nparts; f.n0 = site.n0; f.n1 = site.n1; f.layer = l.layer_index; f.max_rank = m.max_rank;
     f.vimg = m.lora_vimg; f.vimg_bytes = m.lora_vimg_bytes; f.fence_maps = m.lora_fence_maps;
-    f.arena = m.arena; f.off_a = site.off_a; f.off_b = site.off_b; f.arena_elems = m.arena_elems;
+    f.arena = m.arena; f.off_a = site.off_a; f.off_b = site.off_b; f.arena_elems = m.arena_elems; f.sync = m.lora_sync;
     const int rc = lx_gemm_bf16_lora(x, w, y, bias, s.T, N, K, ldx, ldw, ldy, m.gemm_ws, m.gemm_ws_bytes, m.gemm_counters, m.status, m.num_sms,
                                      &f, stream);
     if (rc != 1) return rc;          // 1: this step does not fit the fused launch, use the separate kernels below

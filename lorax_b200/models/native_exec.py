@@ -47,7 +47,7 @@ class LxModelDesc(Structure):
                 ("attn_part_o", P), ("attn_part_lse", P), ("attn_splits", I), ("attn_part_tokens", I),
                 ("arena", P), ("slot_base", P), ("slot_rank", P), ("slot_tmaps", P),
                 ("num_slots", I), ("max_rank", I), ("groups_per_slot", I), ("fused_lora", I),
-                ("lora_vimg", P), ("lora_vimg_bytes", L), ("arena_elems", L), ("lora_fence_maps", I),
+                ("lora_vimg", P), ("lora_vimg_bytes", L), ("arena_elems", L), ("lora_sync", P), ("lora_fence_maps", I),
                 ("tc_prefill", I), ("kv_blocks", I)]
 
 
@@ -140,6 +140,7 @@ class NativeExecutor:
             m.fused_lora = int(model.fused_lora_max_tokens)        # rows up to which LoRA rides inside the GEMM launch
             m.lora_vimg, m.lora_vimg_bytes = ws.lora_vimg.data_ptr(), ws.lora_vimg.numel() * 2
             m.arena_elems = ad.arena.numel()
+            m.lora_sync = ws.lora_sync.data_ptr()
             m.lora_fence_maps = native.LORA_FENCE_MAPS
         self.m = m
         self.layers = (LxLayerDesc * len(model.layers))()
@@ -232,8 +233,8 @@ class NativeExecutor:
             native._check(rc, "lx_run_layers")
             pending = fused.ar_out[: T * m.H].view(T, m.H) if ar is not None else out_a
             assert out_ptr.value == pending.data_ptr()
-            fused_lora = T <= m.fused_lora and s.lora_tiles and s.max_tile_rows <= 32 and m.max_rank <= 64     # expand rides in the GEMM then
-            lora_launches = (4 if fused_lora else 8) if s.tok_slot else 0        # per layer: shrink (+ expand) at four projections
+            fused_lora = T <= m.fused_lora and s.lora_tiles and s.max_tile_rows <= 32 and m.max_rank <= 64     # shrink and expand ride in the GEMM then
+            lora_launches = (0 if fused_lora else 8) if s.tok_slot else 0        # per layer: shrink and expand at four projections
             attn_kernels = (1 if s.n_decode else 0) + (1 if T > s.n_decode else 0)
             native.launch_count += nL * (10 + attn_kernels + lora_launches + (2 if ar is not None else 0)) - 1      # `_check` counted one
             if ar is not None:
@@ -249,7 +250,7 @@ class NativeExecutor:
             native._check(rc, "lx_layer_mlp")
             pending = tp.all_reduce(buf_b) if tp.world_size > 1 else buf_b
         fused_lora = T <= m.fused_lora and s.lora_tiles and s.max_tile_rows <= 32 and m.max_rank <= 64
-        lora_launches = (4 if fused_lora else 8) if s.tok_slot else 0
+        lora_launches = (0 if fused_lora else 8) if s.tok_slot else 0
         attn_kernels = (1 if s.n_decode else 0) + (1 if T > s.n_decode else 0)
         native.launch_count += len(model.layers) * (8 + attn_kernels + lora_launches)
         self._keep = [normed, qkv, attn, gate_up, act, out_a, inp]

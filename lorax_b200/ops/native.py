@@ -135,6 +135,7 @@ class Workspace:
         # LoRA expand inside the GEMM launch: bf16 operand images of the shrink results (6 KB per table entry and part)
         self.lora_max_entries = 1024
         self.lora_vimg = torch.zeros(self.lora_max_entries * 3 * 48 * 64, dtype=torch.bfloat16, device=device)
+        self.lora_sync = torch.zeros(2, dtype=torch.int32, device=device)       # launch-wide counters of the in-kernel shrink
         self.fp8_scratch = None              # bf16 image of one fp8 projection (long prefills), allocated on first use
         self.attn_part_tokens = 256
         self.attn_splits = attn_splits
@@ -202,7 +203,7 @@ class LxLoraFused(ctypes.Structure):
                 ("vimg", ctypes.c_void_p), ("vimg_bytes", ctypes.c_longlong),
                 ("fence_maps", ctypes.c_int),
                 ("arena", ctypes.c_void_p), ("off_a", ctypes.c_longlong),
-                ("off_b", ctypes.c_longlong), ("arena_elems", ctypes.c_longlong)]
+                ("off_b", ctypes.c_longlong), ("arena_elems", ctypes.c_longlong), ("sync", ctypes.c_void_p)]
 
 
 class LoraFused(NamedTuple):
@@ -235,6 +236,7 @@ def lora_fused_desc(ws: "Workspace", lf: LoraFused, K: int) -> LxLoraFused:
     d.vimg, d.vimg_bytes = ws.lora_vimg.data_ptr(), ws.lora_vimg.numel() * 2
     d.arena, d.off_a = (lf.arena.data_ptr() if lf.arena is not None else None), lf.off_a
     d.off_b, d.arena_elems = lf.off_b, (lf.arena.numel() if lf.arena is not None else 0)
+    d.sync = ws.lora_sync.data_ptr()
     d.fence_maps = LORA_FENCE_MAPS
     return d
 
@@ -261,10 +263,10 @@ def gemm(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, 
 
 def gemm_lora_fused(x: torch.Tensor, w: torch.Tensor, lf: LoraFused, bias: Optional[torch.Tensor] = None,
                     out: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
-    """out[T, N] = x @ w^T (+ bias) + the LoRA delta of every row's adapter: a row-wise shrink launch that writes the operand
-    images, then base tiles and expand UMMAs in one launch of `gemm_bf16_tcgen05_kernel<.., true>`.  None when the step cannot
-    be served this way (rank above 64, part boundaries off the 128 grid, table larger than the scratch): the caller then uses
-    the separate kernels."""
+    """out[T, N] = x @ w^T (+ bias) + the LoRA delta of every row's adapter in one launch of
+    `gemm_bf16_tcgen05_kernel<.., true>`: its epilogue warps compute the shrink while the first K loop runs, the expand is
+    added by UMMAs after the K loop of every base tile.  None when the step cannot be served this way (rank above 64, part
+    boundaries off the 128 grid, table larger than the scratch): the caller then uses the separate kernels."""
     assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
     T, K = x.shape
     N = w.shape[0]
@@ -282,8 +284,6 @@ def gemm_lora_fused(x: torch.Tensor, w: torch.Tensor, lf: LoraFused, bias: Optio
     if rc == 1:
         return None
     _check(rc, "lx_gemm_bf16_lora")
-    global launch_count
-    launch_count += 1                  # the shrink launch in front of the GEMM
     return out if given is None else given
 
 
