@@ -168,8 +168,14 @@ LX_DEVICE int decode_expand_item(const LoraEnt* ents, int lt, int j0, int jlim, 
 // counters[counter], and the last of the nparts contributors sums partials red_base + i * red_stride
 // (i = 0 .. nparts-1; the first one at red_first instead) in that fixed order.
 struct GemmWork {
-  int tile, kb0, kb1, nparts, counter;
+  int tile, kb0, kb1, nparts, counter, part_idx;     // part_idx: which of the nparts contributors this CTA is
   long long part_off, red_first, red_base, red_stride;
+};
+
+// A stream-K tile the CTA has parked a partial for: summed after the CTA's last unit of work.
+struct PendingTile {
+  int ta, tb, counter, nparts, part_idx;
+  long long red_first, red_base, red_stride;
 };
 
 // Enumerates a CTA's work.  Producer, MMA issuer and epilogue warps each run their own copy in lockstep.
@@ -198,6 +204,7 @@ struct GemmWorkIter {
       w.kb1 = (int)((long long)kblocks * (split + 1) / split_k);
       w.nparts = split_k;
       w.counter = w.tile;
+      w.part_idx = split;
       w.red_base = (long long)w.tile * split_k * kPart;
       w.red_first = w.red_base;
       w.red_stride = kPart;
@@ -229,6 +236,7 @@ struct GemmWorkIter {
     if (w.kb0 == 0 && w.kb1 == kblocks) { w.nparts = 0; return true; }
     const int first = sk_cta_of(t0), last = sk_cta_of(t0 + kblocks - 1);
     w.nparts = last - first + 1;
+    w.part_idx = cta - first;
     w.counter = r;
     w.part_off = (long long)(cta * 2 + (first_seg ? 0 : 1)) * kPart;
     w.red_base = (long long)(first * 2) * kPart;
@@ -765,6 +773,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
     bool alive = true;
+    PendingTile pending[2];
+    int n_pending = 0;
     if constexpr (LORA) {
       if (lora && p.lora_inline_shrink) lora_shrink_units(p, ents, gstart, reinterpret_cast<float*>(epi_stage), warp - 2, lane);
     }
@@ -896,6 +906,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         if (lane == 0) mbar_arrive(&tmem_empty[acc]);
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (p.split_k == 1) {
+          // Stream-K: the contributors of a tile are different CTAs that finish at about the same time.  Count in now; after
+          // its last unit of work every contributor sums its own share of the tile's columns (see below).
+          if (threadIdx.x == 64) atomicAdd(&p.counters[w.counter], 1);
+          if (n_pending < 2) pending[n_pending++] = PendingTile{ta, tb, w.counter, w.nparts, w.part_idx, w.red_first, w.red_base, w.red_stride};
+          acc ^= 1;
+          continue;
+        }
         if (threadIdx.x == 64) {
           const int prev = atomicAdd(&p.counters[w.counter], 1);
           *last_flag = (prev == w.nparts - 1) ? 1 : 0;
@@ -960,6 +978,92 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is reused by the next tile
       }
       acc ^= 1;
+    }
+    // ---- stream-K tiles this CTA contributed to: every contributor sums its share of the columns, 4 rows (16 bytes of
+    // every partial) per thread and step.  All contributors are running (one CTA per SM, each a consecutive K range of the
+    // same length), so the wait for the others is short; it is bounded like every wait.
+    for (int pi = 0; alive && pi < n_pending; ++pi) {
+      const PendingTile t = pending[pi];
+      if (threadIdx.x == 64) {
+        uint64_t t0 = 0;
+        uint32_t polls = 0;
+        while ((ld_acquire_gpu(&p.counters[t.counter]) & 0xffff) != t.nparts) {
+          if ((++polls & 255u) == 0) {
+            const uint64_t now = global_timer_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > kWaitBudgetNs) {
+              report_status(p.status, kTimeoutSplitK, t.counter);
+              *abort_flag = 1;
+              break;
+            }
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*abort_flag != 0) break;
+      const int j0 = t.tb * p.bn;
+      const int ncols = min(min(p.bn, p.umma_n), p.b_rows - j0);
+      const int c_lo = (int)((long long)ncols * t.part_idx / t.nparts), c_hi = (int)((long long)ncols * (t.part_idx + 1) / t.nparts);
+      const int tid4 = (int)threadIdx.x - 64;
+      const int items = (c_hi - c_lo) * (kBM / 4);
+      for (int it0 = tid4; it0 < items; it0 += 128 * 4) {
+        // four items per thread and pass, four partials of each in flight
+        float4 sum[4];
+        long long off[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int it1 = min(it0 + 128 * e, items - 1);
+          sum[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+          off[e] = (long long)(c_lo + it1 / (kBM / 4)) * kBM + (it1 % (kBM / 4)) * 4;
+        }
+        for (int sp0 = 0; sp0 < t.nparts; sp0 += 4) {
+          float4 v[4][4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int sp = min(sp0 + q, t.nparts - 1);
+            const float* src = p.ws + (sp == 0 ? t.red_first : t.red_base + sp * t.red_stride);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) v[q][e] = __ldcg(reinterpret_cast<const float4*>(src + off[e]));
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (sp0 + q < t.nparts) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) { sum[e].x += v[q][e].x; sum[e].y += v[q][e].y; sum[e].z += v[q][e].z; sum[e].w += v[q][e].w; }
+            }
+          }
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int it1 = it0 + 128 * e;
+          if (it1 >= items) break;
+          const int c = c_lo + it1 / (kBM / 4), r4 = (it1 % (kBM / 4)) * 4;
+          const int i = t.ta * kBM + r4, j = j0 + c;
+          float o[4] = {sum[e].x * p.out_scale, sum[e].y * p.out_scale, sum[e].z * p.out_scale, sum[e].w * p.out_scale};
+          if (p.bias != nullptr) {
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              if (p.bias_on_a) { if (i + h < p.a_rows) o[h] += __bfloat162float(p.bias[i + h]); }
+              else o[h] += __bfloat162float(p.bias[j]);
+            }
+          }
+          __nv_bfloat16* dst = p.out + (long long)i * p.ldo_a + (long long)j * p.ldo_b;
+          if (p.ldo_a == 1 && i + 4 <= p.a_rows && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+            *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16x2(o[0], o[1]), pack_bf16x2(o[2], o[3]));
+          } else {
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              if (i + h < p.a_rows) dst[(long long)h * p.ldo_a] = __float2bfloat16(o[h]);
+            }
+          }
+        }
+      }
+      // the last contributor to finish clears the counter for the next launch
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (threadIdx.x == 64) {
+        const int prev = atomicAdd(&p.counters[t.counter], 0x10000);
+        if ((prev >> 16) == t.nparts - 1) p.counters[t.counter] = 0;
+      }
     }
   }
 
@@ -1316,9 +1420,6 @@ static GemmPlan plan_tiles(int tiles, int kblocks, int K, int bn, int num_sms, l
   const int rem = tiles < num_sms ? tiles : R;
   const int dp = tiles < num_sms ? 0 : full_waves * G;
   if (rem == 0 || sk_policy == 1 || !have_counters) return pl;
-  // By cost, stream-K is only offered to grids smaller than the GPU with token tiles up to 128: there it replaces
-  // the classic K split.  For larger problems the fp32 round trip of the partials costs more than the idle SMs.
-  if (sk_policy == 0 && (dp != 0 || bn > 128)) return pl;
   const long long units = (long long)rem * kblocks;
   long long ctas = num_sms;
   if (ctas > units / 2) ctas = units / 2;
@@ -1435,8 +1536,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
     if (pl_tok.cost >= 1e30) pl_tok = plan_tiles(tiles_t * ((N + 255) / 256), kblocks_all, K, 256, num_sms, usable_ws, have_counters, sk_policy);
   }
   // Orientation.  Up to 128 tokens the weights take the M side (no padded MMA rows, the token tile is the small
-  // operand).  Above that both plans are costed; the weights-on-M epilogue writes 2 bytes per thread and store, which
-  // measures about 15 % slower at equal tiling.  The LoRA epilogue's fast path is written for weights on M.
+  // operand).  Above that both plans are costed.  The LoRA stages are written for weights on M.
   bool swap;
   GemmPlan pl_swap{};
   if (mode == 1 || has_lora || (mode == 0 && T <= 128)) {
@@ -1445,7 +1545,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
     swap = false;
   } else {
     pl_swap = choose_plan_swap(T, N, K, num_sms, usable_ws, have_counters, force_split & 0xffff, force_bn, sk_policy);
-    swap = pl_swap.cost * 1.15 < pl_tok.cost;
+    swap = pl_swap.cost <= pl_tok.cost;
   }
   if (swap) {
     p.a_rows = N; p.b_rows = T;
