@@ -123,7 +123,7 @@ def bench_lora(results, peaks):
     r, S, G = 16, 100, 5
     sites = [("qkv", [4096, 1024, 1024], 4096), ("o", [4096], 4096), ("gate_up", [14336, 14336], 4096), ("down", [4096], 14336)]
     wz = torch.tensor([1.0 / (k ** 1.1) for k in range(1, S + 1)], dtype=torch.float64)
-    for T in (64, 256, 1024):
+    for T in (64, 256, 1024, 4096):
         rows = sorted(int(v) for v in torch.multinomial(wz / wz.sum(), T, replacement=True, generator=torch.Generator().manual_seed(T)))
         tl = reference.build_lora_tiles(rows, 32)
         tiles = torch.full((len(tl) + 16, 4), -1, device="cuda", dtype=torch.int32)

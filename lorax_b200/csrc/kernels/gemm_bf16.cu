@@ -122,9 +122,10 @@ LX_DEVICE uint64_t make_desc_k_sw32(uint32_t smem_addr) {
 constexpr int kLoraMaxEntries = 512;
 struct LoraEnt { int slot, row0; short nrows, r; int boff; };    // r == 0: nothing to do for the entry; slot < 0: end of the live entries
 static_assert(sizeof(LoraEnt) == 16, "one 16-byte word per entry");
-LX_DEVICE void load_lora_entries(const GemmParams& p, LoraEnt* ents) {
+LX_DEVICE void load_lora_entries(const GemmParams& p, LoraEnt* ents, int* n_live) {
   for (int lt = threadIdx.x; lt < p.lora_num_tiles; lt += blockDim.x) {
     const LoraTileG t = p.lora_tiles[lt];
+    if (t.slot < 0) atomicMin(n_live, lt);
     LoraEnt e{t.slot, t.row0, (short)max(min(min(t.nrows, 32), p.lora_T - t.row0), -1), 0, 0};
     if (t.slot >= 0 && t.slot < p.lora_num_slots && e.nrows > 0 && t.row0 >= 0) {
       const int r = p.lora_slot_rank[t.slot];
@@ -147,10 +148,11 @@ LX_DEVICE void load_lora_entries(const GemmParams& p, LoraEnt* ents) {
 struct ExpandItem {
   int slot, r, w0, c0, c1, boff;
 };
-// -1: end of the live entries, 0: nothing to add for this entry, 1: `e` is valid.
+// -1: end of the live entries or of those that can meet the tile (they are sorted by row), 0: nothing to add for this
+// entry, 1: `e` is valid.
 LX_DEVICE int decode_expand_item(const LoraEnt* ents, int lt, int j0, int jlim, ExpandItem& e) {
   const LoraEnt t = ents[lt];
-  if (t.slot < 0) return -1;
+  if (t.slot < 0 || t.row0 >= jlim) return -1;
   if (t.r == 0) return 0;
   e.slot = t.slot;
   e.r = t.r;
@@ -432,6 +434,17 @@ LX_DEVICE bool wait_flag(const int* flag, int want, volatile int* abort_flag) {
 // A unit = one K slice (16 ranks) of one table entry that meets the token tile.  The producer warp and the MMA warp each build
 // the same list in their own shared-memory area, 32 entries at a time (one per lane, ranks -> slices by a warp prefix sum), and
 // keep it while the token tile stays the same: it does not depend on the feature tile.
+// First live entry whose 16-aligned window ends after row j0 (entries are sorted by row and do not overlap).
+LX_DEVICE int lora_first_entry(const LoraEnt* ents, int n_live, int j0) {
+  int lo = 0, hi = n_live;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    const LoraEnt t = ents[mid];
+    if (((t.row0 + t.nrows + 15) & ~15) > j0) hi = mid; else lo = mid + 1;
+  }
+  return lo;
+}
+
 struct LoraUnit {
   int slot, img;        // img = entry * 4 + slice
   int c0, c1;           // accumulator columns [c0, c1) the unit adds to
@@ -510,6 +523,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   uint32_t* tmem_base_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_base_slot + 1);
   int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_base_slot + 2));
+  int* n_live = reinterpret_cast<int*>(tmem_base_slot + 3);             // live entries of the LoRA table
   LoraEnt* ents = reinterpret_cast<LoraEnt*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes);
   LoraUnit* ulist_p = reinterpret_cast<LoraUnit*>(ents + kLoraMaxEntries);      // producer warp's expand units
   LoraUnit* ulist_m = ulist_p + kLoraListCap;                                   // MMA warp's
@@ -537,6 +551,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     }
     *abort_flag = 0;
     *last_flag = 0;
+    *n_live = LORA ? p.lora_num_tiles : 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
@@ -553,7 +568,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     // the table, the slot ranks and the slot offsets are written by copies that the stream orders before every kernel, never by
     // the kernel in front of this one: reading them does not have to wait for that kernel to drain
     if (lora) {
-      load_lora_entries(p, ents);
+      load_lora_entries(p, ents, n_live);
       __syncthreads();
       if (p.lora_inline_shrink && warp == 2) lora_group_prefix(p, ents, gstart);
       __syncthreads();
@@ -621,7 +636,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           int n = cached ? list_n : 0;
           bool ended = false;
           int flushes = 0;
-          for (int lt0 = 0; ok && (cached || (!ended && lt0 < p.lora_num_tiles)); lt0 += 32) {
+          for (int lt0 = cached ? 0 : lora_first_entry(ents, *n_live, j0); ok && (cached || (!ended && lt0 < p.lora_num_tiles)); lt0 += 32) {
             if (!cached) {
               n = lora_build_units(p, ents, lt0, j0, jlim, ulist_p, n, ended);
               const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
@@ -722,7 +737,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           int n = cached ? list_n : 0;
           bool ended = false;
           int flushes = 0;
-          for (int lt0 = 0; ok && (cached || (!ended && lt0 < p.lora_num_tiles)); lt0 += 32) {
+          for (int lt0 = cached ? 0 : lora_first_entry(ents, *n_live, j0); ok && (cached || (!ended && lt0 < p.lora_num_tiles)); lt0 += 32) {
             if (!cached) {
               n = lora_build_units(p, ents, lt0, j0, jlim, ulist_m, n, ended);
               const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
@@ -1541,7 +1556,7 @@ static int gemm_impl(const void* x, const void* w, void* out, const void* bias, 
   GemmPlan pl_swap{};
   if (mode == 1 || has_lora || (mode == 0 && T <= 128)) {
     swap = true;
-  } else if (mode == 2 || T > 2048) {
+  } else if (mode == 2) {
     swap = false;
   } else {
     pl_swap = choose_plan_swap(T, N, K, num_sms, usable_ws, have_counters, force_split & 0xffff, force_bn, sk_policy);
