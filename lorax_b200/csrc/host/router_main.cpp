@@ -802,6 +802,30 @@ class App {
       w.send(503, "{\"error\":\"unhealthy\",\"error_type\":\"healthcheck\"}");
     }
   }
+  // Startup probe: one real request through the whole stack, the kind the model serves (a one-token generation, an
+  // embedding or a classification of "Hello"), as the reference's probe does (router/src/server.rs:488-588); a shard that
+  // answers Health but cannot run a batch keeps the pod out of rotation.
+  void startup(http::ResponseWriter& w) {
+    try {
+      if (info_.supports_embeddings) {
+        auto resp = client_->embed(one_shot_batch({"Hello"}));
+        if (!resp.errorMsg.empty()) throw std::runtime_error(resp.errorMsg);
+      } else if (info_.supports_classification) {
+        auto resp = client_->classify(one_shot_batch({"Hello"}));
+        if (!resp.errorMsg.empty()) throw std::runtime_error(resp.errorMsg);
+      } else {
+        GenerateParams p;
+        p.max_new_tokens = 1;
+        (void)run("Hello", p);
+      }
+      w.send(200, "");
+    } catch (const std::exception& e) {
+      Value v = Value::object();
+      v.set("error", std::string("unhealthy: ") + e.what());
+      v.set("error_type", "healthcheck");
+      w.send(503, v.dump());
+    }
+  }
   void info(http::ResponseWriter& w) {
     Value v = Value::object();
     v.set("model_id", cfg_.model_id);
@@ -932,7 +956,7 @@ int main(int argc, char** argv) {
   R("POST", "/tokenize", [&](auto& q, auto& w) { app.tokenize(q, w); });
   R("GET", "/health", [&](auto&, auto& w) { app.health(w); });
   R("GET", "/ping", [&](auto&, auto& w) { app.health(w); });
-  R("GET", "/startup", [&](auto&, auto& w) { app.health(w); });
+  R("GET", "/startup", [&](auto&, auto& w) { app.startup(w); });
   R("GET", "/info", [&](auto&, auto& w) { app.info(w); });
   R("GET", "/", [&](auto&, auto& w) { app.health(w); });
   // Prometheus text by default; JSON with ?format=json or "Accept: application/json" (reference router/src/server.rs:1200-1290):

@@ -147,8 +147,16 @@ class ShardRuntime:
         shard's prefill raises, router/src/health.rs:150-178)."""
         if getattr(self.runner, "device_failed", None):
             raise RuntimeError("shard is unhealthy: " + self.runner.device_failed)
+        # A one-token prefill into block 0, which no request ever owns: every kernel of a step runs (and, under tensor
+        # parallelism, every collective: the router sends Health to all shards at once).
+        from ..runtime.runner import PrefillItem
+        _, lps, _ = self.runner.prefill([PrefillItem([0], 0, [0])])
         if self.model.device.type == "cuda":
-            torch.zeros(2, 2, device=self.model.device)
+            torch.cuda.synchronize(self.model.device)
+            from ..ops import native
+            native.workspace(self.model.device).check_status()
+        if lps is not None and not bool(torch.isfinite(lps.float()).all()):
+            raise RuntimeError("shard is unhealthy: the probe step returned a non-finite log-probability")
         return self.pb.HealthResponse()
 
     def warmup(self, req):

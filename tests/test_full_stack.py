@@ -393,6 +393,29 @@ def test_openapi_document_is_served(stack):
     assert "GenerateParameters" in doc["components"]["schemas"] and "merged_adapters" in doc["components"]["schemas"]["GenerateParameters"]["properties"]
 
 
+def test_startup_probe_runs_a_real_request_and_health_runs_a_step(stack):
+    """`/startup` sends one real one-token generation through router, scheduler and shard (router/src/server.rs:488-588 of the
+    reference does the same); the shard's Health answers only after a one-token prefill into the reserved block 0 has run."""
+    port, rt = stack["port"], stack["rt"]
+    calls = {"prefill": 0}
+    inner = rt.runner.prefill
+
+    def counting(items):
+        calls["prefill"] += 1
+        if len(items) == 1 and list(items[0].blocks) == [0]:
+            calls["probe"] = calls.get("probe", 0) + 1
+        return inner(items)
+    rt.runner.prefill = counting
+    try:
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}/startup", timeout=20) as r:
+            assert r.status == 200
+        assert calls["prefill"] >= 1                       # the probe request reached the model
+        rt.health()
+        assert calls.get("probe", 0) >= 1                  # Health itself runs a step on block 0
+    finally:
+        rt.runner.prefill = inner
+
+
 def test_health_turns_false_after_a_device_side_failure(stack):
     """A step that finds the kernels' status word set (a bounded wait that ran out on the device) fails its batch: the client
     gets 424, the router drops the batch, and /health, which probes the shard after a failed generation as the reference does
