@@ -6,15 +6,23 @@
 
 Workload (synthetic, random-init weights): Mistral-7B, bf16, tensor parallel over N GPUs, 100 random LoRA
 adapters of rank 16 on q,k,v,o,gate,up,down, adapter per request ~ Zipf(1.1), prompts of uniform-random token
-ids with length uniform in [128, 1024], 256 new tokens, greedy.  Requests arrive as a closed loop that keeps
-`--batch` requests in flight (a saturating Poisson stream and a closed loop admit the same way once a backlog
-exists).  A "step" is one iteration of the serving engine: admission + prefill of newly arrived requests when
-the scheduler decides to, then one decode step over the running batch.
+ids with length uniform in [128, 1024], 256 new tokens, greedy.  By default 2000 requests arrive as a Poisson
+stream at 400 requests/s, more than the engine serves, so a queue builds and the batch stays full
+(`--arrivals closed` keeps `--batch` requests in flight instead).  Before the timed window a ramp fills the
+decode batch, so the window measures the steady state.  A "step" is one iteration of the serving engine:
+admission + prefill of newly arrived requests when the scheduler decides to, then one decode step over the
+running batch.
 
-Two numbers are reported.  `value` is device-timed with CUDA events over exactly K steps.  `e2e.value` runs
-K more steps through the same public API (`Engine.add_request` / `Engine.step`) timed on the host clock; in
+Numbers reported.  `value` is device-timed with CUDA events over exactly K steps.  `p50_ttft_ms` (arrival to first
+token, for every request admitted in the window), `p50_tpot_ms` and `p99_tpot_ms` (intervals between consecutive
+tokens of running requests) come from the CUDA events the engine records with every step's results.  `e2e.value`
+runs K more steps through the same public API (`Engine.add_request` / `Engine.step`) timed on the host clock; in
 both windows every step copies the new requests' token ids from pinned host memory to the device and reads the
 sampled tokens back, and the bytes of those copies are counted from the tensors.
+
+Other configurations: `--model mixtral-8x7b` (experts on the device path), `--model llama3-8b --quantize fp8
+--min-prompt 8192 --max-prompt 8192` (block-scaled fp8 weights, long prompts), `--ranks 8,16,32,64 --resident 32`
+(mixed ranks, fewer HBM slots than adapters), `--kv-cache-dtype fp8` (e4m3 KV pages; named in `dtype`).
 """
 
 from __future__ import annotations
@@ -179,6 +187,8 @@ def main():
     ap.add_argument("--requests", type=int, default=2000, help="poisson: number of arrivals")
     ap.add_argument("--rate", type=float, default=400.0, help="poisson: arrivals per second")
     ap.add_argument("--quantize", default=None, choices=[None, "fp8"], help="base linear weights in block-scaled fp8 e4m3")
+    ap.add_argument("--kv-cache-dtype", default=None, choices=[None, "fp8"],
+                    help="e4m3 KV pages (scale 1); a reduced-precision cache, never the headline configuration")
     ap.add_argument("--resident", type=int, default=None,
                     help="adapters that fit the HBM arena (default: all). Fewer makes the engine exchange adapters with the pinned host tier")
     ap.add_argument("--min-prompt", type=int, default=128)
@@ -257,7 +267,7 @@ def main():
     torch.cuda.synchronize(dev)
 
     ecfg = EngineConfig(max_total_tokens=max_total, max_batch_prefill_tokens=max(4096, args.max_prompt), max_input_length=args.max_prompt,
-                        compile=not args.no_graphs)
+                        compile=not args.no_graphs, kv_cache_dtype=args.kv_cache_dtype)
     if args.waiting_served_ratio is not None:
         ecfg.waiting_served_ratio = args.waiting_served_ratio
     eng = Engine(model, ecfg, max_batch=args.batch)
@@ -382,7 +392,8 @@ def main():
         "metric": "output tok/s at 100 adapters, Mistral-7B arch, TP1-8; p50 TTFT/TPOT",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": tp.world_size, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(1e3 * w1["seconds"] / args.steps, 3), "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16" if not args.quantize else f"bf16 activations, {args.quantize} base weights",
+        "vs_baseline": None, "dtype": ("bf16" if not args.quantize else f"bf16 activations, {args.quantize} base weights")
+                                     + (f", {args.kv_cache_dtype} KV cache" if args.kv_cache_dtype else ""),
         "data": "synthetic (random token ids, random-init base and adapter weights)",
         "impl": "ours",
         "config": {

@@ -276,6 +276,7 @@ class EngineConfig:
     default_adapter_source: Optional[str] = None
     dtype: Optional[str] = None
     quantize: Optional[str] = None
+    kv_cache_dtype: Optional[str] = None            # "fp8": e4m3 pages with per-layer k / v scales (None: the model's dtype)
     num_shard: int = 1
     max_concurrent_requests: int = 1024
     max_best_of: int = 2
@@ -328,6 +329,7 @@ class EngineConfig:
         c.model_id = _env("MODEL_ID", c.model_id)
         c.num_shard = _env("NUM_SHARD", c.num_shard)
         c.quantize = _env("QUANTIZE", c.quantize, str)
+        c.kv_cache_dtype = _env("KV_CACHE_DTYPE", c.kv_cache_dtype, str)
         c.dtype = _env("DTYPE", c.dtype, str)
         c.max_input_length = _env("MAX_INPUT_LENGTH", c.max_input_length)
         c.max_total_tokens = _env("MAX_TOTAL_TOKENS", c.max_total_tokens)

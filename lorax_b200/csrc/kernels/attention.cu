@@ -13,6 +13,13 @@
 //
 // Cache layout (one tensor per layer): [num_blocks, kv_heads, 2, PAGE, D] -- for each (block, head) the K
 // plane [PAGE, D] is followed by the V plane, so one page of one head is a single contiguous 2*PAGE*D run.
+//
+// fp8 cache (template flag KV8): pages hold e4m3 bytes in the same layout, written by `rope_kvwrite` as value / scale with one
+// scale for K and one for V per layer (the reference's k_scale / v_scale, server/lorax_server/utils/paged_attention.py:23-47).
+// A page arrives in shared memory as bytes (half the traffic of the bf16 cache, which is what bounds decode attention) and is
+// expanded to a bf16 plane before the MMAs; the K scale is folded into the softmax scale and the V scale into the output.
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace lx {
@@ -51,6 +58,37 @@ LX_DEVICE void load_plane(uint32_t smem_base, const __nv_bfloat16* g, int tid, b
     const uint32_t dst = smem_base + swz<D>(r, cc);
     const int sz = valid ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(g + (long long)c * 8), "r"(sz) : "memory");
+  }
+}
+
+// Copy ROWS x D e4m3 bytes (contiguous in global memory) into a linear staging area.
+template <int D, int ROWS, int NT>
+LX_DEVICE void load_plane8(uint32_t smem_base, const uint8_t* g, int tid, bool valid) {
+  constexpr int CHUNKS = ROWS * D / 16;
+#pragma unroll
+  for (int c = tid; c < CHUNKS; c += NT) {
+    const int sz = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_base + c * 16), "l"(g + (long long)c * 16), "r"(sz) : "memory");
+  }
+}
+LX_DEVICE uint32_t e4m3x2_to_bf16x2(uint32_t two) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(two & 0xffffu), __NV_E4M3);
+  const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+  return pack_bf16x2(f.x, f.y);
+}
+// Expand a staged e4m3 plane into a swizzled bf16 plane (every e4m3 value is exact in bf16).
+template <int D, int ROWS, int NT>
+LX_DEVICE void expand_plane8(uint32_t dst_plane, uint32_t src8, int tid) {
+  constexpr int CHUNKS = ROWS * D / 16;
+#pragma unroll
+  for (int c = tid; c < CHUNKS; c += NT) {
+    uint32_t w0, w1, w2, w3;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3) : "r"(src8 + c * 16));
+    const int r = (c * 16) / D, cc = ((c * 16) % D) / 8;
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst_plane + swz<D>(r, cc)), "r"(e4m3x2_to_bf16x2(w0)),
+                 "r"(e4m3x2_to_bf16x2(w0 >> 16)), "r"(e4m3x2_to_bf16x2(w1)), "r"(e4m3x2_to_bf16x2(w1 >> 16)) : "memory");
+    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(dst_plane + swz<D>(r, cc + 1)), "r"(e4m3x2_to_bf16x2(w2)),
+                 "r"(e4m3x2_to_bf16x2(w2 >> 16)), "r"(e4m3x2_to_bf16x2(w3)), "r"(e4m3x2_to_bf16x2(w3 >> 16)) : "memory");
   }
 }
 
@@ -164,15 +202,18 @@ struct DecodeParams {
   float scale, softcap;
   int nsplit;
   const float* alibi;         // [nh] ALiBi slopes, or null
+  float v_scale;              // fp8 cache: multiplies the output (the K scale is folded into `scale` by the host)
 };
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool KV8>
 __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams p) {
   pdl_trigger();
   pdl_wait();      // every block waits, also those that return early below
   extern __shared__ __align__(1024) uint8_t dsm[];
   constexpr int PLANE = kPage * D * 2;
-  constexpr int STAGE = 2 * PLANE;
+  constexpr int PLANE8 = kPage * D;
+  constexpr int STAGE = KV8 ? 2 * PLANE8 : 2 * PLANE;
+  constexpr int WARP_BYTES = STAGES * STAGE + (KV8 ? 2 * PLANE : 0);     // fp8: staged bytes + one expanded K and V plane
   const int t = blockIdx.x;
   const int kvh = blockIdx.y / p.gchunks, gc = blockIdx.y % p.gchunks;
   const int split = blockIdx.z;
@@ -212,7 +253,8 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
     }
   }
 
-  const uint32_t wbase = smem_u32(dsm) + warp * STAGES * STAGE;
+  const uint32_t wbase = smem_u32(dsm) + warp * WARP_BYTES;
+  const uint32_t wwork = wbase + STAGES * STAGE;
   const int* bt = p.block_tables + (long long)t * p.max_blocks;
   float slope0 = 0.f, slope1 = 0.f;
   if (p.alibi != nullptr) {
@@ -227,10 +269,15 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
     if (i < my_count) {
       const int page = my_first + 4 * i;
       const long long blk = bt[page];
-      const __nv_bfloat16* src = p.kv + ((blk * p.nkv + kvh) * 2) * (long long)(kPage * D);
       const uint32_t sb = wbase + (i % STAGES) * STAGE;
-      load_plane<D, kPage, 32>(sb, src, lane, true);
-      load_plane<D, kPage, 32>(sb + PLANE, src + kPage * D, lane, true);
+      if constexpr (KV8) {
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(p.kv) + ((blk * p.nkv + kvh) * 2) * (long long)(kPage * D);
+        load_plane8<D, 2 * kPage, 32>(sb, src, lane, true);            // the K plane and the V plane are one contiguous run
+      } else {
+        const __nv_bfloat16* src = p.kv + ((blk * p.nkv + kvh) * 2) * (long long)(kPage * D);
+        load_plane<D, kPage, 32>(sb, src, lane, true);
+        load_plane<D, kPage, 32>(sb + PLANE, src + kPage * D, lane, true);
+      }
     }
     cp_async_commit();
   };
@@ -241,7 +288,13 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
     issue(i + STAGES - 1);
     cp_async_wait<STAGES - 1>();
     __syncwarp();
-    const uint32_t sb = wbase + (i % STAGES) * STAGE;
+    uint32_t sb = wbase + (i % STAGES) * STAGE;
+    if constexpr (KV8) {
+      expand_plane8<D, kPage, 32>(wwork, sb, lane);
+      expand_plane8<D, kPage, 32>(wwork + PLANE, sb + PLANE8, lane);
+      __syncwarp();
+      sb = wwork;
+    }
     const int page = my_first + 4 * i;
     float sacc[kPage / 8][4];
     qk_tile<D, kPage>(sacc, qf, sb, lane);
@@ -288,7 +341,7 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
       num += wgt * so[(w * 16 + g) * D + d];
       den += wgt * sl[w * 16 + g];
     }
-    const float o = den > 0.f ? num / den : 0.f;
+    const float o = (den > 0.f ? num / den : 0.f) * (KV8 ? p.v_scale : 1.f);
     const int head = head0 + g;
     if (p.nsplit == 1) {
       p.out[(long long)t * p.ldo + (long long)head * D + d] = __float2bfloat16(o);
@@ -338,16 +391,18 @@ struct PrefillParams {
   int window;
   float scale, softcap;
   const float* alibi;         // [nh] ALiBi slopes, or null
+  float v_scale;              // fp8 cache: multiplies the output
 };
 
-template <int D>
+template <int D, bool KV8>
 __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillParams p) {
   pdl_trigger();
   pdl_wait();      // every block waits, also those that return early below
   extern __shared__ __align__(1024) uint8_t psm[];
   constexpr int KT = 64;                         // keys per tile
   constexpr int PLANE = kPage * D * 2;           // one page of K or V
-  constexpr int STAGE = 4 * PLANE;               // K page0, K page1, V page0, V page1
+  constexpr int PLANE8 = kPage * D;
+  constexpr int STAGE = KV8 ? 4 * PLANE8 : 4 * PLANE;        // K page0, K page1, V page0, V page1 (fp8: K0 V0 K1 V1 as bytes)
   const int tile = blockIdx.x, head = blockIdx.y;
   const int kvh = head / (p.nh / p.nkv);
   const int b = p.tile_seq[tile];
@@ -394,13 +449,19 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillParams p
         const int page = kt * 2 + h;
         const bool valid = page < total_pages;
         const long long blk = valid ? bt[page] : 0;
-        const __nv_bfloat16* src = p.kv + ((blk * p.nkv + kvh) * 2) * (long long)(kPage * D);
-        load_plane<D, kPage, 128>(sb + h * PLANE, src, threadIdx.x, valid);
-        load_plane<D, kPage, 128>(sb + (2 + h) * PLANE, src + kPage * D, threadIdx.x, valid);
+        if constexpr (KV8) {
+          const uint8_t* src = reinterpret_cast<const uint8_t*>(p.kv) + ((blk * p.nkv + kvh) * 2) * (long long)(kPage * D);
+          load_plane8<D, 2 * kPage, 128>(sb + h * 2 * PLANE8, src, threadIdx.x, valid);
+        } else {
+          const __nv_bfloat16* src = p.kv + ((blk * p.nkv + kvh) * 2) * (long long)(kPage * D);
+          load_plane<D, kPage, 128>(sb + h * PLANE, src, threadIdx.x, valid);
+          load_plane<D, kPage, 128>(sb + (2 + h) * PLANE, src + kPage * D, threadIdx.x, valid);
+        }
       }
     }
     cp_async_commit();
   };
+  const uint32_t work = base + 2 * STAGE;        // fp8: the expanded bf16 planes of the tile being multiplied
 
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
   float oacc[D / 8][4];
@@ -413,7 +474,16 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillParams p
     issue(kt + 1);
     cp_async_wait<1>();
     __syncthreads();
-    const uint32_t sb = base + (kt & 1) * STAGE;
+    uint32_t sb = base + (kt & 1) * STAGE;
+    if constexpr (KV8) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        expand_plane8<D, kPage, 128>(work + h * PLANE, sb + h * 2 * PLANE8, threadIdx.x);
+        expand_plane8<D, kPage, 128>(work + (2 + h) * PLANE, sb + h * 2 * PLANE8 + PLANE8, threadIdx.x);
+      }
+      __syncthreads();
+      sb = work;
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       float sacc[kPage / 8][4];
@@ -430,7 +500,8 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillParams p
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
-  const float inv0 = l[0] > 0.f ? 1.f / l[0] : 0.f, inv1 = l[1] > 0.f ? 1.f / l[1] : 0.f;
+  const float vs = KV8 ? p.v_scale : 1.f;
+  const float inv0 = l[0] > 0.f ? vs / l[0] : 0.f, inv1 = l[1] > 0.f ? vs / l[1] : 0.f;
 #pragma unroll
   for (int nd = 0; nd < D / 8; ++nd) {
     const int c = nd * 8 + 2 * (lane & 3);
@@ -441,18 +512,20 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillParams p
   }
 }
 
-template <int D, int STAGES>
+template <int D, int STAGES, bool KV8>
 static int launch_decode(const DecodeParams& p, int T, cudaStream_t s) {
-  constexpr int SMEM = 4 * STAGES * 2 * kPage * D * 2;
+  constexpr int SMEM = KV8 ? 4 * (STAGES * 2 * kPage * D + 2 * kPage * D * 2) : 4 * STAGES * 2 * kPage * D * 2;
   static_assert(SMEM >= (4 * 16 * D + 128) * 4, "combine buffer must fit in the pipeline buffers");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  static bool configured[64] = {false};          // the shared-memory opt-in is a per-device attribute
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, STAGES, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return -(int)e;
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid(T, p.nkv * p.gchunks, p.nsplit);
-  launch_pdl(attn_decode_kernel<D, STAGES>, grid, dim3(128), (size_t)SMEM, s, p);
+  launch_pdl(attn_decode_kernel<D, STAGES, KV8>, grid, dim3(128), (size_t)SMEM, s, p);
   if (p.nsplit > 1) {
     dim3 g2(T, p.nh);
     launch_pdl(attn_combine_kernel<D>, g2, dim3(D), 0, s, p.part_o, p.part_lse, p.out, p.ldo, p.nh, p.nsplit);
@@ -460,17 +533,19 @@ static int launch_decode(const DecodeParams& p, int T, cudaStream_t s) {
   return -(int)cudaGetLastError();
 }
 
-template <int D>
+template <int D, bool KV8>
 static int launch_prefill(const PrefillParams& p, int num_tiles, cudaStream_t s) {
-  constexpr int SMEM = 2 * 4 * kPage * D * 2;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  constexpr int SMEM = KV8 ? 2 * 4 * kPage * D + 4 * kPage * D * 2 : 2 * 4 * kPage * D * 2;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return -(int)e;
-    configured = true;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid(num_tiles, p.nh);
-  launch_pdl(attn_prefill_kernel<D>, grid, dim3(128), (size_t)SMEM, s, p);
+  launch_pdl(attn_prefill_kernel<D, KV8>, grid, dim3(128), (size_t)SMEM, s, p);
   return -(int)cudaGetLastError();
 }
 
@@ -495,10 +570,9 @@ int lx_attn_decode(const void* q, long long ldq, const void* kv, const int* bloc
                               softcap, nsplit, nullptr, stream);
 }
 
-// `alibi`: [nh] fp32 slopes on the device (BLOOM, MPT), or null.
-int lx_attn_decode_alibi(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* ctx_lens,
-                         void* out, long long ldo, float* part_o, float* part_lse, int T, int nh, int nkv, int d, int window, float scale,
-                         float softcap, int nsplit, const float* alibi, void* stream) {
+static int attn_decode_impl(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* ctx_lens,
+                            void* out, long long ldo, float* part_o, float* part_lse, int T, int nh, int nkv, int d, int window, float scale,
+                            float softcap, int nsplit, const float* alibi, bool kv8, float k_scale, float v_scale, void* stream) {
   using namespace lx;
   if (T <= 0) return 0;
   if (nh % nkv != 0) return -1;
@@ -509,13 +583,35 @@ int lx_attn_decode_alibi(const void* q, long long ldq, const void* kv, const int
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
   p.part_o = part_o; p.part_lse = part_lse;
   p.nh = nh; p.nkv = nkv; p.group = nh / nkv; p.gchunks = (p.group + 15) / 16;
-  p.window = window; p.scale = scale; p.softcap = softcap; p.alibi = alibi;
+  p.window = window; p.scale = kv8 ? scale * k_scale : scale; p.softcap = softcap; p.alibi = alibi;
+  p.v_scale = v_scale;
   p.nsplit = nsplit < 1 ? 1 : nsplit;
   if (p.nsplit > 1 && (part_o == nullptr || part_lse == nullptr)) return -2;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (d == 128) return launch_decode<128, 3>(p, T, s);
-  if (d == 64) return launch_decode<64, 4>(p, T, s);
+  if (kv8) {
+    if (d == 128) return launch_decode<128, 3, true>(p, T, s);
+    if (d == 64) return launch_decode<64, 4, true>(p, T, s);
+    return -3;
+  }
+  if (d == 128) return launch_decode<128, 3, false>(p, T, s);
+  if (d == 64) return launch_decode<64, 4, false>(p, T, s);
   return -3;
+}
+
+// `alibi`: [nh] fp32 slopes on the device (BLOOM, MPT), or null.
+int lx_attn_decode_alibi(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* ctx_lens,
+                         void* out, long long ldo, float* part_o, float* part_lse, int T, int nh, int nkv, int d, int window, float scale,
+                         float softcap, int nsplit, const float* alibi, void* stream) {
+  return attn_decode_impl(q, ldq, kv, block_tables, max_blocks, ctx_lens, out, ldo, part_o, part_lse, T, nh, nkv, d, window, scale, softcap,
+                          nsplit, alibi, false, 1.f, 1.f, stream);
+}
+
+// The same over an e4m3 cache: stored value * k_scale (v_scale) is the key (value).
+int lx_attn_decode_kv8(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* ctx_lens,
+                       void* out, long long ldo, float* part_o, float* part_lse, int T, int nh, int nkv, int d, int window, float scale,
+                       float softcap, int nsplit, const float* alibi, float k_scale, float v_scale, void* stream) {
+  return attn_decode_impl(q, ldq, kv, block_tables, max_blocks, ctx_lens, out, ldo, part_o, part_lse, T, nh, nkv, d, window, scale, softcap,
+                          nsplit, alibi, true, k_scale, v_scale, stream);
 }
 
 int lx_attn_prefill(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
@@ -525,9 +621,10 @@ int lx_attn_prefill(const void* q, long long ldq, const void* kv, const int* blo
                                window, scale, softcap, nullptr, stream);
 }
 
-int lx_attn_prefill_alibi(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
-                          const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
-                          int nkv, int d, int window, float scale, float softcap, const float* alibi, void* stream) {
+static int attn_prefill_impl(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
+                             const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
+                             int nkv, int d, int window, float scale, float softcap, const float* alibi, bool kv8, float k_scale,
+                             float v_scale, void* stream) {
   using namespace lx;
   if (num_tiles <= 0) return 0;
   if (nh % nkv != 0) return -1;
@@ -537,11 +634,32 @@ int lx_attn_prefill_alibi(const void* q, long long ldq, const void* kv, const in
   p.block_tables = block_tables; p.max_blocks = max_blocks; p.cu_q = cu_q; p.cache_lens = cache_lens;
   p.tile_seq = tile_seq; p.tile_q0 = tile_q0;
   p.out = reinterpret_cast<__nv_bfloat16*>(out); p.ldo = ldo;
-  p.nh = nh; p.nkv = nkv; p.window = window; p.scale = scale; p.softcap = softcap; p.alibi = alibi;
+  p.nh = nh; p.nkv = nkv; p.window = window; p.scale = kv8 ? scale * k_scale : scale; p.softcap = softcap; p.alibi = alibi;
+  p.v_scale = v_scale;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-  if (d == 128) return launch_prefill<128>(p, num_tiles, s);
-  if (d == 64) return launch_prefill<64>(p, num_tiles, s);
+  if (kv8) {
+    if (d == 128) return launch_prefill<128, true>(p, num_tiles, s);
+    if (d == 64) return launch_prefill<64, true>(p, num_tiles, s);
+    return -3;
+  }
+  if (d == 128) return launch_prefill<128, false>(p, num_tiles, s);
+  if (d == 64) return launch_prefill<64, false>(p, num_tiles, s);
   return -3;
+}
+
+int lx_attn_prefill_alibi(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
+                          const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
+                          int nkv, int d, int window, float scale, float softcap, const float* alibi, void* stream) {
+  return attn_prefill_impl(q, ldq, kv, block_tables, max_blocks, cu_q, cache_lens, tile_seq, tile_q0, num_tiles, out, ldo, nh, nkv, d, window,
+                           scale, softcap, alibi, false, 1.f, 1.f, stream);
+}
+
+int lx_attn_prefill_kv8(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
+                        const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
+                        int nkv, int d, int window, float scale, float softcap, const float* alibi, float k_scale, float v_scale,
+                        void* stream) {
+  return attn_prefill_impl(q, ldq, kv, block_tables, max_blocks, cu_q, cache_lens, tile_seq, tile_q0, num_tiles, out, ldo, nh, nkv, d, window,
+                           scale, softcap, alibi, true, k_scale, v_scale, stream);
 }
 
 }  // extern "C"

@@ -6,6 +6,8 @@
 // `rotary_emb.apply_rotary` (utils/layers.py:627-633), `reshape_and_cache` (utils/paged_attention.py:29-51),
 // the eager `silu(gate) * up` (custom_modeling/flash_mistral_modeling.py:436-439) and the Triton metadata
 // kernels (models/metadata_kernels.py:154-329).
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 
 namespace lx {
@@ -131,10 +133,18 @@ norm_residual_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restr
 //   slots      [T] flat slot index = block * page + offset; negative = do not cache
 // One CTA per token; each thread rotates 4 pairs (8-byte loads).
 // ------------------------------------------------------------------------------------------------
+// Four bf16 (two packed words) times `inv_scale` as four e4m3 bytes, saturating.
+LX_DEVICE uint32_t bf16x4_to_e4m3x4(uint2 w, float inv_scale) {
+  const float2 a = unpack_bf16x2(w.x), b = unpack_bf16x2(w.y);
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a.x * inv_scale, a.y * inv_scale), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(b.x * inv_scale, b.y * inv_scale), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
 __global__ void __launch_bounds__(256)
 rope_kvwrite_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions, const float* __restrict__ cos_sin,
                     __nv_bfloat16* __restrict__ kv_cache, const int* __restrict__ slots, int nh, int nkv, int d, int rot,
-                    int page, long long ldq, int apply_rope, float k_scale_unused) {
+                    int page, long long ldq, int apply_rope, int kv_fp8, float k_inv_scale, float v_inv_scale) {
   pdl_trigger();
   pdl_wait();      // every block waits, also those that return early below
   const int t = blockIdx.x;
@@ -174,9 +184,17 @@ rope_kvwrite_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos
     }
     if (head >= nh && slot >= 0) {
       const int kh = head - nh;
-      __nv_bfloat16* dst = kv_cache + (((blk * nkv + kh) * 2 + 0) * page + off) * d;
-      *reinterpret_cast<uint2*>(dst + qd) = lo;
-      *reinterpret_cast<uint2*>(dst + half + qd) = hi;
+      const long long e0 = (((blk * nkv + kh) * 2 + 0) * page + off) * d;
+      if (kv_fp8) {
+        // e4m3 cache: value / scale, saturating; 4 bytes per store
+        uint8_t* dst = reinterpret_cast<uint8_t*>(kv_cache) + e0;
+        *reinterpret_cast<uint32_t*>(dst + qd) = bf16x4_to_e4m3x4(lo, k_inv_scale);
+        *reinterpret_cast<uint32_t*>(dst + half + qd) = bf16x4_to_e4m3x4(hi, k_inv_scale);
+      } else {
+        __nv_bfloat16* dst = kv_cache + e0;
+        *reinterpret_cast<uint2*>(dst + qd) = lo;
+        *reinterpret_cast<uint2*>(dst + half + qd) = hi;
+      }
     }
   }
   if (slot >= 0) {
@@ -185,14 +203,26 @@ rope_kvwrite_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ pos
     if (tail > 0) {
       for (int idx = threadIdx.x; idx < nkv * tail; idx += blockDim.x) {
         const int kh = idx / tail, e = rot + idx % tail;
-        kv_cache[(((blk * nkv + kh) * 2 + 0) * page + off) * d + e] = row[(nh + kh) * d + e];
+        const long long at = (((blk * nkv + kh) * 2 + 0) * page + off) * d + e;
+        if (kv_fp8) {
+          reinterpret_cast<uint8_t*>(kv_cache)[at] =
+              (uint8_t)__nv_cvt_float_to_fp8(__bfloat162float(row[(nh + kh) * d + e]) * k_inv_scale, __NV_SATFINITE, __NV_E4M3);
+        } else {
+          kv_cache[at] = row[(nh + kh) * d + e];
+        }
       }
     }
     const int vec_per_head = d / 8;
     for (int idx = threadIdx.x; idx < nkv * vec_per_head; idx += blockDim.x) {
       const int kh = idx / vec_per_head, e = (idx % vec_per_head) * 8;
       const uint4 v = *reinterpret_cast<const uint4*>(row + (nh + nkv + kh) * d + e);
-      *reinterpret_cast<uint4*>(kv_cache + (((blk * nkv + kh) * 2 + 1) * page + off) * d + e) = v;
+      const long long at = (((blk * nkv + kh) * 2 + 1) * page + off) * d + e;
+      if (kv_fp8) {
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint8_t*>(kv_cache) + at) =
+            make_uint2(bf16x4_to_e4m3x4(make_uint2(v.x, v.y), v_inv_scale), bf16x4_to_e4m3x4(make_uint2(v.z, v.w), v_inv_scale));
+      } else {
+        *reinterpret_cast<uint4*>(kv_cache + at) = v;
+      }
     }
   }
 }
@@ -393,15 +423,23 @@ int lx_norm_residual(const void* x, void* residual, const void* w, const void* b
   return -(int)cudaGetLastError();
 }
 
-int lx_rope_kvwrite(void* qkv, const int* positions, const float* cos_sin, void* kv_cache, const int* slots, int T, int nh,
-                    int nkv, int d, int rot, int page, long long ldq, int apply_rope, void* stream) {
+// kv_fp8 != 0: the cache holds e4m3 bytes, value / k_scale for keys and value / v_scale for values (same layout).
+int lx_rope_kvwrite_kv8(void* qkv, const int* positions, const float* cos_sin, void* kv_cache, const int* slots, int T, int nh,
+                        int nkv, int d, int rot, int page, long long ldq, int apply_rope, int kv_fp8, float k_scale, float v_scale,
+                        void* stream) {
   using namespace lx;
   if (T <= 0) return 0;
   if (d % 8 != 0 || rot % 8 != 0 || rot > d) return -1;
+  if (kv_fp8 && (k_scale <= 0.f || v_scale <= 0.f)) return -2;
   launch_pdl(rope_kvwrite_kernel, dim3(T), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
       reinterpret_cast<__nv_bfloat16*>(qkv), positions, cos_sin, reinterpret_cast<__nv_bfloat16*>(kv_cache), slots, nh, nkv, d,
-      rot, page, ldq, apply_rope, 1.f);
+      rot, page, ldq, apply_rope, kv_fp8, kv_fp8 ? 1.f / k_scale : 1.f, kv_fp8 ? 1.f / v_scale : 1.f);
   return -(int)cudaGetLastError();
+}
+
+int lx_rope_kvwrite(void* qkv, const int* positions, const float* cos_sin, void* kv_cache, const int* slots, int T, int nh,
+                    int nkv, int d, int rot, int page, long long ldq, int apply_rope, void* stream) {
+  return lx_rope_kvwrite_kv8(qkv, positions, cos_sin, kv_cache, slots, T, nh, nkv, d, rot, page, ldq, apply_rope, 0, 1.f, 1.f, stream);
 }
 
 int lx_act_mul(const void* in, void* out, int T, int I, long long ldi, long long ldo, int act, int gated, void* stream) {

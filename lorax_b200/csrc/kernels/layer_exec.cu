@@ -27,6 +27,16 @@ int lx_attn_decode(const void* q, long long ldq, const void* kv, const int* bloc
 int lx_attn_prefill(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
                     const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
                     int nkv, int d, int window, float scale, float softcap, void* stream);
+int lx_rope_kvwrite_kv8(void* qkv, const int* positions, const float* cos_sin, void* kv_cache, const int* slots, int T, int nh,
+                        int nkv, int d, int rot, int page, long long ldq, int apply_rope, int kv_fp8, float k_scale, float v_scale,
+                        void* stream);
+int lx_attn_decode_kv8(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* ctx_lens,
+                       void* out, long long ldo, float* part_o, float* part_lse, int T, int nh, int nkv, int d, int window, float scale,
+                       float softcap, int nsplit, const float* alibi, float k_scale, float v_scale, void* stream);
+int lx_attn_prefill_kv8(const void* q, long long ldq, const void* kv, const int* block_tables, int max_blocks, const int* cu_q,
+                        const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo, int nh,
+                        int nkv, int d, int window, float scale, float softcap, const float* alibi, float k_scale, float v_scale,
+                        void* stream);
 int lx_attn_prefill_tc_supported(int nh, int nkv, int d, long long ldq, long long ldo);
 int lx_attn_prefill_tc(const void* q, long long ldq, int T, const void* kv, int num_blocks, const int* block_tables, int max_blocks,
                        const int* cu_q, const int* cache_lens, const int* tile_seq, const int* tile_q0, int num_tiles, void* out, long long ldo,
@@ -95,6 +105,7 @@ struct LxLayerDesc {
   LxLoraSite lora[4];
   int layer_index;               // third coordinate of the adapter tensor maps
   int window;                    // sliding window of this layer (0 = none)
+  float k_scale, v_scale;        // e4m3 cache: stored value * scale is the key / value (see LxModelDesc::kv_fp8)
 };
 
 struct LxModelDesc {
@@ -112,6 +123,7 @@ struct LxModelDesc {
   // scratch of the GEMM that carries LoRA in its own launch
   void* lora_vimg; long long lora_vimg_bytes; long long arena_elems; int* lora_sync; int lora_fence_maps;
   int tc_prefill, kv_blocks;     // tensor-core prefill attention where the shape allows; blocks of the paged cache
+  int kv_fp8, pad3_;             // the cache holds e4m3 bytes
 };
 
 struct LxStepDesc {
@@ -209,8 +221,8 @@ int lx_layer_attention(const LxModelDesc* m, const LxLayerDesc* l, const LxStepD
                             m->layernorm, stream));
   }
   LX_TRY(linear_with_lora(*m, *l, *s, 0, s->normed, H, l->qkv_w, l->ld_qkv, l->qkv_b, s->qkv, m->n_qkv, m->n_qkv, H, stream));
-  LX_TRY(lx_rope_kvwrite(s->qkv, s->positions, m->cos_sin, l->kv_cache, s->slots, T, m->nh, m->nkv, m->d, m->rot, m->page, m->n_qkv,
-                         m->apply_rope, stream));
+  LX_TRY(lx_rope_kvwrite_kv8(s->qkv, s->positions, m->cos_sin, l->kv_cache, s->slots, T, m->nh, m->nkv, m->d, m->rot, m->page, m->n_qkv,
+                             m->apply_rope, m->kv_fp8, l->k_scale, l->v_scale, stream));
   const int nd = s->n_decode;
   const long long ldq = m->n_qkv, lda = m->n_o_in;
   char* q = reinterpret_cast<char*>(s->qkv);
@@ -219,11 +231,22 @@ int lx_layer_attention(const LxModelDesc* m, const LxLayerDesc* l, const LxStepD
     int nsplit = s->nsplit;
     if (nsplit > m->attn_splits) nsplit = m->attn_splits;
     if (nd > m->attn_part_tokens || nsplit < 1) nsplit = 1;
-    LX_TRY(lx_attn_decode(q, ldq, l->kv_cache, s->dec_block_tables, s->dec_max_blocks, s->ctx_lens, a, lda, m->attn_part_o, m->attn_part_lse,
-                          nd, m->nh, m->nkv, m->d, l->window, m->attn_scale, m->softcap, nsplit, stream));
+    if (m->kv_fp8) {
+      LX_TRY(lx_attn_decode_kv8(q, ldq, l->kv_cache, s->dec_block_tables, s->dec_max_blocks, s->ctx_lens, a, lda, m->attn_part_o,
+                                m->attn_part_lse, nd, m->nh, m->nkv, m->d, l->window, m->attn_scale, m->softcap, nsplit, nullptr,
+                                l->k_scale, l->v_scale, stream));
+    } else {
+      LX_TRY(lx_attn_decode(q, ldq, l->kv_cache, s->dec_block_tables, s->dec_max_blocks, s->ctx_lens, a, lda, m->attn_part_o, m->attn_part_lse,
+                            nd, m->nh, m->nkv, m->d, l->window, m->attn_scale, m->softcap, nsplit, stream));
+    }
   }
   if (T > nd) {
-    if (m->tc_prefill && lx_attn_prefill_tc_supported(m->nh, m->nkv, m->d, ldq, lda)) {
+    if (m->kv_fp8) {
+      // the tensor-core kernel reads bf16 pages by TMA; the e4m3 cache goes through the kernel that expands pages in shared memory
+      LX_TRY(lx_attn_prefill_kv8(q + (long long)nd * ldq * 2, ldq, l->kv_cache, s->block_tables, s->max_blocks, s->cu_q, s->cache_lens,
+                                 s->tile_seq, s->tile_q0, s->n_attn_tiles, a + (long long)nd * lda * 2, lda, m->nh, m->nkv, m->d, l->window,
+                                 m->attn_scale, m->softcap, nullptr, l->k_scale, l->v_scale, stream));
+    } else if (m->tc_prefill && lx_attn_prefill_tc_supported(m->nh, m->nkv, m->d, ldq, lda)) {
       LX_TRY(lx_attn_prefill_tc(q + (long long)nd * ldq * 2, ldq, T - nd, l->kv_cache, m->kv_blocks, s->block_tables, s->max_blocks, s->cu_q,
                                 s->cache_lens, s->tile_seq, s->tile_q0, s->n_attn_tiles, a + (long long)nd * lda * 2, lda, m->nh, m->nkv, m->d,
                                 l->window, m->attn_scale, m->softcap, nullptr, m->status, stream));

@@ -160,6 +160,7 @@ class DecoderModel:
         # weights on the UMMA M side, which the plain GEMM gives up above 128 rows)
         self.fused_lora_max_tokens = int(os.environ.get("LORAX_FUSED_LORA_MAX_TOKENS", "512")) if os.environ.get("LORAX_FUSED_LORA", "1") != "0" else 0
         self.fused_lora = self.fused_lora_max_tokens > 0
+        self.kv_scales = None        # per layer (k scale, v scale) of an e4m3 KV cache, set when the cache is built
         self.gated = c.model_type not in ("gpt2", "gpt_bigcode", "gpt_neox", "falcon", "RefinedWeb", "RefinedWebModel", "phi", "bloom",
                                           "mpt", "opt")
         if c.alibi:
@@ -515,9 +516,11 @@ class DecoderModel:
         qkv = self._linear(x, lw.qkv_w, lw.qkv_b, "qkv", li, inp)
         if c.clip_qkv:
             qkv.clamp_(-c.clip_qkv, c.clip_qkv)
+        kvs = {"kv_scale": self.kv_scales[li]} if (self.kv_scales and kv.dtype == torch.float8_e4m3fn) else {}
         ops.rope_kvwrite(qkv, inp.positions, self.cos_sin, kv, inp.slots, self.nh, self.nkv, self.d, c.rotary_dim,
-                         not (c.learned_positions or c.alibi))
+                         not (c.learned_positions or c.alibi), **kvs)
         ali = {"alibi": self.alibi_slopes} if self.alibi_slopes is not None else {}
+        ali.update(kvs)
         window = c.sliding_window or 0
         if c.model_type == "gemma2" and li % 2 == 1:
             window = 0

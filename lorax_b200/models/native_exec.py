@@ -32,7 +32,7 @@ class LxLayerDesc(Structure):
     _fields_ = [("input_norm_w", P), ("input_norm_b", P), ("post_norm_w", P), ("post_norm_b", P), ("qkv_w", P), ("qkv_b", P),
                 ("o_w", P), ("o_b", P), ("gate_up_w", P), ("gate_up_b", P), ("down_w", P), ("down_b", P),
                 ("ld_qkv", L), ("ld_o", L), ("ld_gate_up", L), ("ld_down", L), ("kv_cache", P), ("lora", LxLoraSite * 4),
-                ("layer_index", I), ("window", I)]
+                ("layer_index", I), ("window", I), ("k_scale", F), ("v_scale", F)]
 
 
 class LxModelDesc(Structure):
@@ -48,7 +48,7 @@ class LxModelDesc(Structure):
                 ("arena", P), ("slot_base", P), ("slot_rank", P), ("slot_tmaps", P),
                 ("num_slots", I), ("max_rank", I), ("groups_per_slot", I), ("fused_lora", I),
                 ("lora_vimg", P), ("lora_vimg_bytes", L), ("arena_elems", L), ("lora_sync", P), ("lora_fence_maps", I),
-                ("tc_prefill", I), ("kv_blocks", I)]
+                ("tc_prefill", I), ("kv_blocks", I), ("kv_fp8", I), ("pad3_", I)]
 
 
 class LxStepDesc(Structure):
@@ -114,6 +114,7 @@ class NativeExecutor:
         m.H, m.nh, m.nkv, m.d, m.inter, m.rot = model.hidden, model.nh, model.nkv, model.d, model.inter, c.rotary_dim
         m.page = kv_layers[0].shape[3]
         m.tc_prefill, m.kv_blocks = int(native.TC_PREFILL), kv_layers[0].shape[0]
+        m.kv_fp8 = int(kv_layers[0].dtype == torch.float8_e4m3fn)
         m.apply_rope = int(not c.learned_positions)
         m.act, m.gated = native._ACTS[c.hidden_act], int(model.gated)
         m.layernorm = int(c.norm_type.startswith("layernorm"))
@@ -151,6 +152,7 @@ class NativeExecutor:
             d.gate_up_w, d.gate_up_b, d.down_w, d.down_b = _p(lw.gate_up_w), _p(lw.gate_up_b), _p(lw.down_w), _p(lw.down_b)
             d.ld_qkv, d.ld_o, d.ld_gate_up, d.ld_down = lw.qkv_w.stride(0), lw.o_w.stride(0), lw.gate_up_w.stride(0), lw.down_w.stride(0)
             d.kv_cache = self.kv_ptrs[li]
+            d.k_scale, d.v_scale = (model.kv_scales[li] if getattr(model, "kv_scales", None) else (1.0, 1.0))
             d.layer_index = li
             d.window = c.sliding_window or 0
             for si, g in enumerate(self.SITES):

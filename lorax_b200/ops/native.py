@@ -442,11 +442,16 @@ def norm_residual(x: torch.Tensor, residual: Optional[torch.Tensor], weight: tor
 
 
 def rope_kvwrite(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor, kv_cache: torch.Tensor,
-                 slots: Optional[torch.Tensor], nh: int, nkv: int, d: int, rot: int, apply_rope: bool = True):
+                 slots: Optional[torch.Tensor], nh: int, nkv: int, d: int, rot: int, apply_rope: bool = True,
+                 kv_scale: Optional[Tuple[float, float]] = None):
+    """RoPE in place on q and k, then k and v into the paged cache.  A `torch.float8_e4m3fn` cache takes value / scale as e4m3
+    (`kv_scale` = (k scale, v scale), default 1)."""
     T = qkv.shape[0]
     page = kv_cache.shape[3]
-    rc = load().lx_rope_kvwrite(_ptr(qkv), _ptr(positions), _ptr(cos_sin), _ptr(kv_cache), _ptr(slots), T, nh, nkv, d, rot,
-                                page, qkv.stride(0), int(apply_rope), _stream())
+    fp8 = kv_cache.dtype == torch.float8_e4m3fn
+    ks, vs = kv_scale if (fp8 and kv_scale) else (1.0, 1.0)
+    rc = load().lx_rope_kvwrite_kv8(_ptr(qkv), _ptr(positions), _ptr(cos_sin), _ptr(kv_cache), _ptr(slots), T, nh, nkv, d, rot,
+                                    page, qkv.stride(0), int(apply_rope), int(fp8), ks, vs, _stream())
     _check(rc, "lx_rope_kvwrite")
 
 
@@ -497,8 +502,10 @@ def advance_decode(input_ids, next_ids, positions, ctx_lens, slots, block_tables
 # ------------------------------------------------------------------------------------------------ attention
 def attn_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Tensor, ctx_lens: torch.Tensor, nh: int, nkv: int,
                 d: int, scale: float, window: int = 0, softcap: float = 0.0, nsplit: int = 1,
-                out: Optional[torch.Tensor] = None, alibi: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """q: [T, >= nh*d] (row stride arbitrary), one query token per row.  Returns [T, nh*d].  `alibi`: [nh] fp32 slopes."""
+                out: Optional[torch.Tensor] = None, alibi: Optional[torch.Tensor] = None,
+                kv_scale: Optional[Tuple[float, float]] = None) -> torch.Tensor:
+    """q: [T, >= nh*d] (row stride arbitrary), one query token per row.  Returns [T, nh*d].  `alibi`: [nh] fp32 slopes.
+    An e4m3 cache is read as stored value * scale (`kv_scale` = (k scale, v scale))."""
     T = q.shape[0]
     if out is None:
         out = torch.empty(T, nh * d, dtype=q.dtype, device=q.device)
@@ -507,6 +514,13 @@ def attn_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Ten
         nsplit = min(nsplit, ws.attn_splits)
         if T > ws.attn_part_tokens:
             nsplit = 1
+    if kv_cache.dtype == torch.float8_e4m3fn:
+        ks, vs = kv_scale or (1.0, 1.0)
+        rc = load().lx_attn_decode_kv8(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(ctx_lens),
+                                       _ptr(out), out.stride(0), _ptr(ws.attn_part_o), _ptr(ws.attn_part_lse), T, nh, nkv, d, window,
+                                       scale, softcap, nsplit, _ptr(alibi), ks, vs, _stream())
+        _check(rc, "lx_attn_decode_kv8")
+        return out
     rc = load().lx_attn_decode_alibi(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(ctx_lens),
                                      _ptr(out), out.stride(0), _ptr(ws.attn_part_o), _ptr(ws.attn_part_lse), T, nh, nkv, d, window,
                                      scale, softcap, nsplit, _ptr(alibi), _stream())
@@ -516,11 +530,20 @@ def attn_decode(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Ten
 
 def attn_prefill(q: torch.Tensor, kv_cache: torch.Tensor, block_tables: torch.Tensor, cu_q: torch.Tensor, cache_lens: torch.Tensor,
                  tile_seq: torch.Tensor, tile_q0: torch.Tensor, nh: int, nkv: int, d: int, scale: float, window: int = 0,
-                 softcap: float = 0.0, out: Optional[torch.Tensor] = None, alibi: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 softcap: float = 0.0, out: Optional[torch.Tensor] = None, alibi: Optional[torch.Tensor] = None,
+                 kv_scale: Optional[Tuple[float, float]] = None) -> torch.Tensor:
     T = q.shape[0]
     if out is None:
         out = torch.empty(T, nh * d, dtype=q.dtype, device=q.device)
     lib = load()
+    if kv_cache.dtype == torch.float8_e4m3fn:
+        # e4m3 pages are expanded to bf16 in shared memory by the mma.sync kernel (the tcgen05 kernel reads bf16 pages by TMA)
+        ks, vs = kv_scale or (1.0, 1.0)
+        rc = lib.lx_attn_prefill_kv8(_ptr(q), q.stride(0), _ptr(kv_cache), _ptr(block_tables), block_tables.shape[1], _ptr(cu_q),
+                                     _ptr(cache_lens), _ptr(tile_seq), _ptr(tile_q0), tile_seq.shape[0], _ptr(out), out.stride(0), nh,
+                                     nkv, d, window, scale, softcap, _ptr(alibi), ks, vs, _stream())
+        _check(rc, "lx_attn_prefill_kv8")
+        return out
     if TC_PREFILL and q.dtype == torch.bfloat16 and lib.lx_attn_prefill_tc_supported(nh, nkv, d, q.stride(0), out.stride(0)):
         # tcgen05 flash kernel: two query heads of a KV group per CTA, K / V pages by TMA from the paged cache
         rc = lib.lx_attn_prefill_tc(_ptr(q), q.stride(0), T, _ptr(kv_cache), kv_cache.shape[0], _ptr(block_tables), block_tables.shape[1],

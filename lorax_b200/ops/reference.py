@@ -123,8 +123,13 @@ def apply_rope(x, cos, sin, rot):
     return torch.cat([o1.to(x.dtype), o2.to(x.dtype), rest], dim=-1)
 
 
-def rope_kvwrite(qkv, positions, cos_sin, kv_cache, slots, nh, nkv, d, rot, apply_rope_flag: bool = True):
-    """In place on qkv [T, (nh+2nkv)*d]; kv_cache [blocks, nkv, 2, page, d]."""
+def _to_e4m3_bytes(x, scale):
+    """x / scale as e4m3 bytes, saturating at +-448 like the kernel."""
+    return (x.float() / scale).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+
+
+def rope_kvwrite(qkv, positions, cos_sin, kv_cache, slots, nh, nkv, d, rot, apply_rope_flag: bool = True, kv_scale=None):
+    """In place on qkv [T, (nh+2nkv)*d]; kv_cache [blocks, nkv, 2, page, d] (bf16 / fp32, or e4m3 holding value / scale)."""
     T = qkv.shape[0]
     page = kv_cache.shape[3]
     q = qkv[:, : nh * d].view(T, nh, d)
@@ -139,8 +144,14 @@ def rope_kvwrite(qkv, positions, cos_sin, kv_cache, slots, nh, nkv, d, rot, appl
         ok = slots >= 0
         s = slots[ok].long()
         blk, off = s // page, s % page
-        kv_cache[blk, :, 0, off, :] = k[ok]
-        kv_cache[blk, :, 1, off, :] = v[ok]
+        if kv_cache.dtype == torch.float8_e4m3fn:
+            ks, vs = kv_scale or (1.0, 1.0)
+            raw = kv_cache.view(torch.uint8)
+            raw[blk, :, 0, off, :] = _to_e4m3_bytes(k[ok], ks)
+            raw[blk, :, 1, off, :] = _to_e4m3_bytes(v[ok], vs)
+        else:
+            kv_cache[blk, :, 0, off, :] = k[ok]
+            kv_cache[blk, :, 1, off, :] = v[ok]
 
 
 def _act(x, act):
@@ -205,11 +216,17 @@ def advance_decode(input_ids, next_ids, positions, ctx_lens, slots, block_tables
     slots.copy_(torch.where(live, new_slots.to(slots.dtype), torch.full_like(slots, -1)))
 
 
-def _gather_kv(kv_cache, block_table, n_keys, kvh):
+def _gather_kv(kv_cache, block_table, n_keys, kvh, kv_scale=None):
     """-> K [n_keys, d], V [n_keys, d] for one sequence and kv head."""
     page = kv_cache.shape[3]
     nblk = (n_keys + page - 1) // page
     blocks = block_table[:nblk].long()
+    if kv_cache.dtype == torch.float8_e4m3fn:
+        ks, vs = kv_scale or (1.0, 1.0)
+        raw = kv_cache.view(torch.uint8)
+        k = raw[blocks, kvh, 0].reshape(-1, kv_cache.shape[-1])[:n_keys].view(torch.float8_e4m3fn).float() * ks
+        v = raw[blocks, kvh, 1].reshape(-1, kv_cache.shape[-1])[:n_keys].view(torch.float8_e4m3fn).float() * vs
+        return k, v
     k = kv_cache[blocks, kvh, 0].reshape(-1, kv_cache.shape[-1])[:n_keys]
     v = kv_cache[blocks, kvh, 1].reshape(-1, kv_cache.shape[-1])[:n_keys]
     return k, v
@@ -234,7 +251,8 @@ def _attend(q, k, v, q_pos, scale, window, softcap, slope=None):
     return p @ v.float()
 
 
-def attn_decode(q, kv_cache, block_tables, ctx_lens, nh, nkv, d, scale, window=0, softcap=0.0, nsplit=1, out=None, alibi=None):
+def attn_decode(q, kv_cache, block_tables, ctx_lens, nh, nkv, d, scale, window=0, softcap=0.0, nsplit=1, out=None, alibi=None,
+                kv_scale=None):
     T = q.shape[0]
     res = torch.zeros(T, nh * d, dtype=q.dtype, device=q.device)
     g = nh // nkv
@@ -243,7 +261,7 @@ def attn_decode(q, kv_cache, block_tables, ctx_lens, nh, nkv, d, scale, window=0
         if n <= 0:
             continue
         for kvh in range(nkv):
-            k, v = _gather_kv(kv_cache, block_tables[t], n, kvh)
+            k, v = _gather_kv(kv_cache, block_tables[t], n, kvh, kv_scale)
             qh = q[t, kvh * g * d: (kvh + 1) * g * d].view(g, d)
             o = _attend(qh, k, v, torch.full((g,), n - 1, device=q.device), scale, window, softcap,
                         None if alibi is None else alibi[kvh * g: (kvh + 1) * g])
@@ -255,7 +273,7 @@ def attn_decode(q, kv_cache, block_tables, ctx_lens, nh, nkv, d, scale, window=0
 
 
 def attn_prefill(q, kv_cache, block_tables, cu_q, cache_lens, tile_seq, tile_q0, nh, nkv, d, scale, window=0, softcap=0.0,
-                 out=None, alibi=None):
+                 out=None, alibi=None, kv_scale=None):
     T = q.shape[0]
     res = torch.zeros(T, nh * d, dtype=q.dtype, device=q.device)
     g = nh // nkv
@@ -268,7 +286,7 @@ def attn_prefill(q, kv_cache, block_tables, cu_q, cache_lens, tile_seq, tile_q0,
         n = c + (e - s)
         pos = torch.arange(c, n, device=q.device)
         for kvh in range(nkv):
-            k, v = _gather_kv(kv_cache, block_tables[b], n, kvh)
+            k, v = _gather_kv(kv_cache, block_tables[b], n, kvh, kv_scale)
             for gi in range(g):
                 h = kvh * g + gi
                 o = _attend(q[s:e, h * d: (h + 1) * d], k, v, pos, scale, window, softcap, None if alibi is None else alibi[h])

@@ -82,7 +82,8 @@ class Engine:
         self._max_batch = max_batch
         if num_blocks is None:
             num_blocks = self._auto_blocks(page)
-        self.kv = KVCache(c.num_hidden_layers, num_blocks, model.nkv, model.d, model.dtype, model.device, page)
+        from .kv_cache import kv_dtype_of
+        self.kv = KVCache(c.num_hidden_layers, num_blocks, model.nkv, model.d, kv_dtype_of(model, self.cfg), model.device, page)
         self.alloc = BlockAllocator(num_blocks, page, c.sliding_window)
         self.runner = ModelRunner(model, self.kv, max_batch=max_batch, max_seq_tokens=self.cfg.max_total_tokens,
                                   max_prefill_tokens=self.cfg.max_batch_prefill_tokens,

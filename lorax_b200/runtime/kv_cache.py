@@ -19,6 +19,20 @@ import torch
 PAGE_SIZE = 32
 
 
+def kv_dtype_of(model, cfg) -> torch.dtype:
+    """The page dtype of a model's cache: e4m3 when the engine config asks for an fp8 cache (value / scale with one K and one
+    V scale per layer, `model.kv_scales`; the reference's fp8 KV cache, server/lorax_server/utils/paged_attention.py:23-47),
+    else the model's own dtype."""
+    want = getattr(cfg, "kv_cache_dtype", None)
+    if want in ("fp8", "fp8_e4m3", "float8_e4m3fn"):
+        if getattr(model, "kv_scales", None) is None:
+            model.kv_scales = [(1.0, 1.0)] * model.config.num_hidden_layers
+        return torch.float8_e4m3fn
+    if want not in (None, "", "auto"):
+        raise ValueError(f"unsupported kv_cache_dtype {want!r} (fp8 or unset)")
+    return model.dtype
+
+
 class KVCache:
     def __init__(self, num_layers: int, num_blocks: int, kv_heads: int, head_dim: int, dtype, device, page: int = PAGE_SIZE):
         self.page = page
@@ -72,7 +86,8 @@ def plan_kv_blocks(model, cfg, max_batch: int, page: int = PAGE_SIZE, reserve_by
     the same time (the prefill contains collectives) and the ranks agree on the minimum."""
     from .runner import ModelRunner, PrefillItem
     c, dev = model.config, model.device
-    per_block = KVCache.bytes_per_block(c.num_hidden_layers, model.nkv, model.d, model.dtype, page)
+    kv_dtype = kv_dtype_of(model, cfg)
+    per_block = KVCache.bytes_per_block(c.num_hidden_layers, model.nkv, model.d, kv_dtype, page)
     if dev.type != "cuda":
         return 1024
     tokens = max(int(cfg.max_batch_prefill_tokens), 16)
@@ -80,7 +95,7 @@ def plan_kv_blocks(model, cfg, max_batch: int, page: int = PAGE_SIZE, reserve_by
     lens = [seq] * (tokens // seq) + ([tokens % seq] if tokens % seq else [])
     window = c.sliding_window
     blocks_per = [min((n + page - 1) // page, (window + page - 1) // page + 1) if window else (n + page - 1) // page for n in lens]
-    tmp = KVCache(c.num_hidden_layers, sum(blocks_per) + 2, model.nkv, model.d, model.dtype, dev, page)
+    tmp = KVCache(c.num_hidden_layers, sum(blocks_per) + 2, model.nkv, model.d, kv_dtype, dev, page)
     runner = ModelRunner(model, tmp, max_batch=max_batch, max_seq_tokens=cfg.max_total_tokens, max_prefill_tokens=tokens, use_graphs=False)
     torch.cuda.synchronize(dev)
     torch.cuda.reset_peak_memory_stats(dev)

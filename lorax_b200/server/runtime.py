@@ -102,13 +102,13 @@ class ShardRuntime:
                                        host_bytes=int(self.cfg.host_adapter_cache_gb * (1 << 30)))
         page = self.cfg.block_size
         if num_blocks is None:
-            per_block = KVCache.bytes_per_block(c.num_hidden_layers, model.nkv, model.d, model.dtype, page)
             if dev.type == "cuda":
                 from ..runtime.kv_cache import plan_kv_blocks
                 num_blocks = plan_kv_blocks(model, self.cfg, max_batch, page)      # a maximum prefill runs first: its peak is measured
             else:
                 num_blocks = 1024
-        self.kv = KVCache(c.num_hidden_layers, num_blocks, model.nkv, model.d, model.dtype, dev, page)
+        from ..runtime.kv_cache import kv_dtype_of
+        self.kv = KVCache(c.num_hidden_layers, num_blocks, model.nkv, model.d, kv_dtype_of(model, self.cfg), dev, page)
         self.runner = ModelRunner(model, self.kv, max_batch=max_batch, max_seq_tokens=self.cfg.max_total_tokens,
                                   max_prefill_tokens=max(self.cfg.max_batch_prefill_tokens, 16), use_graphs=self.cfg.compile)
         self.seqs: Dict[int, SeqState] = {}
@@ -1005,6 +1005,27 @@ class EncoderRuntime:
         return self.pb.ClearCacheResponse()
 
 
+def _checkpoint_kv_scales(w, mc):
+    """Per-layer (k scale, v scale) of an fp8 KV cache: `...self_attn.k_scale` / `v_scale` (or the older single `kv_scale`) where
+    the checkpoint carries them (the reference reads the same tensors, server/lorax_server/models/flash_causal_lm.py:1240-1270),
+    else 1."""
+    out = []
+    for li in range(mc.num_hidden_layers):
+        ks = vs = 1.0
+        for pre in ("model.layers", "transformer.h"):
+            base = f"{pre}.{li}.self_attn"
+            try:
+                if w.has_tensor(f"{base}.k_scale"):
+                    ks = float(w.get_tensor(f"{base}.k_scale").float().item())
+                    vs = float(w.get_tensor(f"{base}.v_scale").float().item())
+                elif w.has_tensor(f"{base}.kv_scale"):
+                    ks = vs = float(w.get_tensor(f"{base}.kv_scale").float().item())
+            except Exception:
+                pass
+        out.append((ks, vs))
+    return out
+
+
 def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel] = None, dtype: Optional[torch.dtype] = None,
                   device: Optional[str] = None, source: str = "hub", revision: Optional[str] = None, **kw) -> ShardRuntime:
     tp = tp or TensorParallel.init_from_env()
@@ -1053,10 +1074,11 @@ def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel]
     if quantize is None and isinstance(qc, dict) and qc.get("quant_method") == "fp8":
         quantize = "fp8"
     if quantize == "fp8-kv":
-        # the weights take the fp8 path; the KV cache stays in the model dtype (fp8 pages are not built), and the log says so
-        print(json.dumps({"level": "WARN", "message": "--quantize fp8-kv: base weights are served in block-scaled fp8, the KV cache stays "
-                          + str(dtype).replace("torch.", "")}), flush=True)
+        # block-scaled fp8 weights and an e4m3 KV cache (per-layer k / v scales from the checkpoint where it has them, else 1)
+        cfg.kv_cache_dtype = "fp8"
         quantize = "fp8"
+    if cfg.kv_cache_dtype == "fp8":
+        model.kv_scales = _checkpoint_kv_scales(w, mc)
     if quantize in ("gptq", "awq") and w.quant is None:
         raise ValueError(f"--quantize {quantize} needs a {quantize} checkpoint (no quantization_config / quantize_config.json found)")
     if quantize is not None and not (quantize in ("gptq", "awq") and model.quantized):

@@ -91,6 +91,36 @@ def test_logits_close_to_hf(setup):
     assert torch.allclose(logits, want, atol=2e-4, rtol=1e-4)
 
 
+def test_fp8_kv_cache_stays_close_to_the_full_precision_cache(setup):
+    """`kv_cache_dtype="fp8"`: e4m3 pages with a K and a V scale per layer.  Prefill over a cached prefix and a decode step read
+    the quantised pages; the logits stay within the quantisation error of the full-precision cache, and half the bytes per block
+    are planned."""
+    cfg, model, mgr, adapters = setup
+    from lorax_b200.config import EngineConfig
+    from lorax_b200.runtime.kv_cache import KVCache, kv_dtype_of
+    from lorax_b200.runtime.runner import ModelRunner, PrefillItem
+    ecfg = EngineConfig(kv_cache_dtype="fp8")
+    saved = model.kv_scales
+    try:
+        assert kv_dtype_of(model, ecfg) == torch.float8_e4m3fn and len(model.kv_scales) == cfg.num_hidden_layers
+        model.kv_scales = [(0.05, 0.03)] * cfg.num_hidden_layers
+        g = torch.Generator().manual_seed(4)
+        p = torch.randint(0, cfg.vocab_size, (50,), generator=g).tolist()
+        outs = []
+        for dtype in (torch.float32, torch.float8_e4m3fn):
+            kv = KVCache(cfg.num_hidden_layers, 16, model.nkv, model.d, dtype, "cpu")
+            runner = ModelRunner(model, kv, max_batch=4, max_seq_tokens=128, max_prefill_tokens=256)
+            runner.prefill([PrefillItem(p[:33], 0, [1, 2], want_logits=False)])
+            _, _, logits = runner.prefill([PrefillItem(p[33:], 33, [1, 2], all_logprobs=True)])      # reads the cached prefix
+            outs.append(logits.float())
+        assert KVCache.bytes_per_block(2, 4, 64, torch.float8_e4m3fn) * 4 == KVCache.bytes_per_block(2, 4, 64, torch.float32)
+        err = (outs[0] - outs[1]).norm() / outs[0].norm()
+        assert 0 < err < 0.1, err
+        assert (outs[0].argmax(-1) == outs[1].argmax(-1)).float().mean() > 0.8
+    finally:
+        model.kv_scales = saved
+
+
 def test_prefill_riding_on_decode_steps_gives_same_tokens(setup):
     """Requests that arrive while others decode are prefilled in the same forward pass as the decode rows (one pass
     over the weights for both).  Tokens must equal those of the run where prefill and decode are separate passes."""

@@ -216,6 +216,58 @@ def test_attn_prefill(nat, nh, nkv, d, window, cached):
     assert _rel_err(got, want) < 1e-2
 
 
+@pytest.mark.parametrize("nh,nkv,d,rot", [(32, 8, 128, 128), (4, 2, 64, 32)])
+def test_fp8_kv_cache(nat, nh, nkv, d, rot):
+    """e4m3 KV pages with a K and a V scale: `rope_kvwrite` stores value / scale (saturating), decode and prefill attention read
+    stored value * scale.  The bytes written match the fp32 reference bit for bit (up to the rounding of the rotated bf16 value),
+    and attention over the same fp8 cache matches fp32 attention over its dequantised values; against the bf16 cache the error is
+    the quantisation's."""
+    torch.manual_seed(21)
+    page, ks, vs = 32, 0.05, 0.02
+    # ---- writes
+    T, blocks = 41, 12
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, device="cuda", dtype=torch.bfloat16) * 3
+    pos = torch.randint(0, 500, (T,), device="cuda", dtype=torch.int32)
+    cs = ref.rope_cache(rot, 512, 10000.0, device="cuda")
+    slots = torch.randperm(blocks * page, device="cuda")[:T].to(torch.int32)
+    slots[5] = -1
+    cache = torch.zeros(blocks, nkv, 2, page, d, device="cuda", dtype=torch.float8_e4m3fn)
+    cache_ref = torch.zeros_like(cache)
+    qkv_ref = qkv.clone()
+    ref.rope_kvwrite(qkv_ref, pos, cs, cache_ref, slots, nh, nkv, d, rot, kv_scale=(ks, vs))
+    nat.rope_kvwrite(qkv, pos, cs, cache, slots, nh, nkv, d, rot, kv_scale=(ks, vs))
+    a, b = cache.float(), cache_ref.float()
+    assert (a != b).float().mean() < 0.02                  # a rotated value that rounds differently in bf16 may land one e4m3 step away
+    assert _rel_err(a, b) < 2e-2
+    assert a.abs().max() <= 448 and torch.isfinite(a).all()        # 3 * N(0,1) / 0.02 saturates instead of overflowing
+    # ---- reads
+    B, max_len = 9, 600
+    wide, bt = _make_cache(B, max_len, nkv, d, seed=3)
+    kq = torch.empty_like(wide, dtype=torch.float8_e4m3fn)
+    kq.view(torch.uint8)[:, :, 0] = ref._to_e4m3_bytes(wide[:, :, 0], ks)
+    kq.view(torch.uint8)[:, :, 1] = ref._to_e4m3_bytes(wide[:, :, 1], vs)
+    ctx = torch.randint(1, max_len, (B,), device="cuda", dtype=torch.int32)
+    ctx[0], ctx[1] = 1, max_len
+    q = torch.randn(B, nh * d, device="cuda", dtype=torch.bfloat16)
+    scale = d ** -0.5
+    for nsplit in (1, 4):
+        got = nat.attn_decode(q, kq, bt, ctx, nh, nkv, d, scale, 0, 0.0, nsplit, kv_scale=(ks, vs))
+        want = ref.attn_decode(q, kq, bt, ctx, nh, nkv, d, scale, 0, 0.0, kv_scale=(ks, vs))
+        assert _rel_err(got, want) < 1e-2, nsplit
+    assert _rel_err(got, ref.attn_decode(q, wide, bt, ctx, nh, nkv, d, scale)) < 8e-2        # quantisation error only
+    q_lens, cache_lens = [70, 200, 33], [0, 150, 64]
+    Tq = sum(q_lens)
+    qp = torch.randn(Tq, nh * d, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    cl = torch.tensor(cache_lens, device="cuda", dtype=torch.int32)
+    ts, tq = ref.prefill_tiles(q_lens)
+    ts, tq = torch.tensor(ts, device="cuda", dtype=torch.int32), torch.tensor(tq, device="cuda", dtype=torch.int32)
+    got = nat.attn_prefill(qp, kq, bt[:3], cu, cl, ts, tq, nh, nkv, d, scale, 0, kv_scale=(ks, vs))
+    want = ref.attn_prefill(qp, kq, bt[:3], cu, cl, ts, tq, nh, nkv, d, scale, 0, kv_scale=(ks, vs))
+    assert _rel_err(got, want) < 1e-2
+    nat.workspace().check_status()
+
+
 @pytest.mark.parametrize("nh,nkv,window,softcap,q_lens,cache_lens", [
     (32, 8, 0, 0.0, [700, 1300, 3], [0, 0, 0]),                # several key blocks per tile: both TMEM buffers and both K/V stages cycle
     (8, 2, 0, 0.0, [200, 64, 129], [900, 37, 128]),            # chunks that continue a cached prefix (chunked prefill, prefix cache)
