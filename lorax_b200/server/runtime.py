@@ -850,6 +850,81 @@ class Seq2SeqRuntime(ShardRuntime):
         return self.pb.ClassifyResponse(errorMsg="this model is not a classifier")
 
 
+class MllamaRuntime(Seq2SeqRuntime):
+    """Shard runtime of Mllama (Llama 3.2 Vision): like the encoder-decoder runtime, a request carries its own state -- here the
+    cross-attention keys / values of its images and the self-attention store of the text model (reference: `MllamaCausalLM`,
+    `server/lorax_server/models/mllama.py`).  Images arrive as markdown links in the prompt and become one `<|image|>` token each
+    (the reference's router does the same with `router/src/config.rs` / `validation.rs:498-638`)."""
+
+    def __init__(self, model, tokenizer=None, cfg: Optional[EngineConfig] = None, model_id: str = ""):
+        super().__init__(model, tokenizer, cfg, model_id)
+        import collections
+        e = model.config.text.eos_token_id
+        self.eos_ids = frozenset(e if isinstance(e, (list, tuple)) else [e])
+        self.special_ids = set(self.eos_ids) | {model.config.pad_token_id, model.config.image_token_index}
+        self._images = collections.OrderedDict()
+
+    def _image(self, uri: str):
+        hit = self._images.get(uri)
+        if hit is not None:
+            self._images.move_to_end(uri)
+            return hit
+        from ..models.vlm import load_image
+        out = self.model.pixel_values(load_image(uri))
+        self._images[uri] = out
+        while len(self._images) > 32:
+            self._images.popitem(last=False)
+        return out
+
+    def tokenize(self, text: str, add_special: bool = True) -> List[int]:
+        from ..models.vlm import split_prompt
+        parts = split_prompt(text)
+        if not any(k == "image" for k, _ in parts):
+            return ShardRuntime.tokenize(self, text, add_special)
+        ids: List[int] = []
+        first = True
+        for kind, val in parts:
+            if kind == "text":
+                ids += ShardRuntime.tokenize(self, val, add_special and first)
+            else:
+                ids.append(self.model.config.image_token_index)
+            first = False
+        return ids
+
+    def prefill(self, req):
+        from ..models.vlm import split_prompt
+        pb = self.pb
+        batch = req.batch
+        seqs = []
+        for r in batch.requests:
+            ids = list(r.tokenized_inputs.ids) if r.HasField("tokenized_inputs") and len(r.tokenized_inputs.ids) else self.tokenize(r.inputs)
+            uris = [v for k, v in split_prompt(r.inputs) if k == "image"]
+            keep = r.truncate or self.cfg.max_input_length
+            if len(ids) > keep and uris:
+                raise ValueError(f"request {r.id}: a prompt with images cannot be truncated ({len(ids)} tokens, limit {keep})")
+            ids = ids[-keep:]
+            params = self._params_from_pb(r.parameters)
+            stopping = StoppingCriteria(r.stopping_parameters.max_new_tokens or 1, self.eos_ids, list(r.stopping_parameters.stop_sequences),
+                                        r.stopping_parameters.ignore_eos_token)
+            s = SeqState(r.id, batch.id, ids, [], 0, params, stopping, Detokenizer(self.tokenizer, []), seed=params.seed)
+            if params.schema:
+                s.grammar = compile_schema(params.schema, self.tokenizer, self.eos_ids)
+            with torch.inference_mode():
+                self.states[r.id] = self.model.encode(ids, [self._image(u) for u in uris])
+            self.seqs[r.id] = s
+            seqs.append(s)
+        with torch.inference_mode():
+            gens, finished = self._step(seqs)
+        for rid in finished:
+            self._drop(rid)
+        live = [s.request_id for s in seqs if s.request_id not in finished]
+        resp = pb.PrefillResponse(generations=gens)
+        if live:
+            self.batches[batch.id] = live
+            resp.batch.CopyFrom(self._cached(batch.id))
+        return resp
+
+
 class VlmRuntime(ShardRuntime):
     """Shard runtime of a vision-language model (LLaVA-NeXT): prompts may contain images as markdown, `![](data:image/png;base64,...)`
     or `![](http://...)`.  Tokenisation (which the router delegates to shard 0) replaces every image by as many `<image>` token ids
@@ -1043,6 +1118,13 @@ def build_runtime(model_id: str, cfg: EngineConfig, tp: Optional[TensorParallel]
         w = Weights(weight_files(model_dir), device="cpu", dtype=dtype)
         s2s = Seq2SeqModel.from_weights(Seq2SeqConfig.from_dict(raw_cfg), w, dev, dtype)
         return Seq2SeqRuntime(s2s, load_tokenizer(model_dir), cfg, model_id=model_id)
+    if raw_cfg.get("model_type") == "mllama":
+        if tp.world_size > 1:
+            raise ValueError("mllama is served on one shard")
+        from ..models.mllama import MllamaConfig, MllamaModel
+        w = Weights(weight_files(model_dir), device="cpu", dtype=dtype)
+        mm = MllamaModel.from_weights(MllamaConfig.from_dict(raw_cfg), w, dev, dtype)
+        return MllamaRuntime(mm, load_tokenizer(model_dir), cfg, model_id=model_id)
     from ..models.vlm import VLM_TYPES, LlavaNextConfig, LlavaNextModel
     if raw_cfg.get("model_type") in VLM_TYPES:
         vcfg = LlavaNextConfig.from_dict(raw_cfg)
