@@ -65,6 +65,9 @@ def load() -> ctypes.CDLL:
         "lx_attn_prefill": ([P, L, P, P, I, P, P, P, P, I, P, L, I, I, I, I, F, F, P], I),
         "lx_attn_decode_alibi": ([P, L, P, P, I, P, P, L, P, P, I, I, I, I, I, F, F, I, P, P], I),
         "lx_attn_prefill_alibi": ([P, L, P, P, I, P, P, P, P, I, P, L, I, I, I, I, F, F, P, P], I),
+        "lx_rope_kvwrite_kv8": ([P, P, P, P, P, I, I, I, I, I, I, L, I, I, F, F, P], I),
+        "lx_attn_decode_kv8": ([P, L, P, P, I, P, P, L, P, P, I, I, I, I, I, F, F, I, P, F, F, P], I),
+        "lx_attn_prefill_kv8": ([P, L, P, P, I, P, P, P, P, I, P, L, I, I, I, I, F, F, P, F, F, P], I),
         "lx_lora_shrink": ([P, L, P, P, P, P, I, L, I, P, I, I, I, I, P, P], I),
         "lx_lora_expand": ([P, I, P, P, P, P, I, L, P, L, I, I, I, I, P, P], I),
         "lx_tensormap_bytes": ([], I),
