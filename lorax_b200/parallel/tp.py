@@ -90,6 +90,20 @@ class TensorParallel:
         dist.all_gather(parts, x.contiguous(), group=self.group)
         return torch.cat(parts, dim=1)
 
+    def all_gather_stack(self, x: torch.Tensor) -> torch.Tensor:
+        """x per rank -> [world, *x.shape] (small tensors: sampling candidates)."""
+        if self.world_size == 1:
+            return x[None]
+        self.nccl_calls += 1
+        x = x.contiguous()
+        if x.is_cuda:
+            out = torch.empty((self.world_size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+            dist.all_gather_into_tensor(out, x, group=self.group)
+            return out
+        parts = [torch.empty_like(x) for _ in range(self.world_size)]
+        dist.all_gather(parts, x, group=self.group)
+        return torch.stack(parts)
+
     def barrier(self):
         if self.world_size > 1:
             dist.barrier(group=self.group)

@@ -27,7 +27,7 @@ from ..config import EngineConfig
 from ..models.decoder import DecoderModel
 from ..sampling.chooser import (FINISH_EOS, FINISH_LENGTH, FINISH_STOP, HeterogeneousNextTokenChooser, NextTokenParams,
                                 StoppingCriteria)
-from ..sampling.device import RowSampler, has_penalties, needs_device_step
+from ..sampling.device import RowSampler, has_penalties, needs_device_step, tp_eligible
 from ..sampling.device import supported as device_sampling_supported
 from .kv_cache import BlockAllocator, KVCache
 from .runner import ModelRunner, PrefillItem
@@ -347,12 +347,20 @@ class Engine:
         steps = [s.launched for s in seqs]                   # index of the token this step generates for the row
         rs = self._row_sampler
 
+        model = self.model
+        tp = model.tp
+
         def hook(logits, st):
-            ids, lp = rs(logits, steps)
+            if tp.world_size > 1 and logits.shape[1] != model.vocab:
+                # the head stayed vocabulary-parallel: draw from the shards, exchanging candidates instead of logits
+                ids, lp = rs.call_tp(logits, steps, model.vocab_start, model.vocab, tp.all_gather_stack)
+            else:
+                ids, lp = rs(logits, steps)
             ids32 = ids.to(st.next_ids.dtype)
             st.next_ids.index_copy_(0, rs.rows, ids32)
             st.logprobs.index_copy_(0, rs.rows, lp.to(st.logprobs.dtype))
             st.input_ids.index_copy_(0, rs.rows, ids32)      # the step advanced the state with the arg-max
+        hook.takes_shards = tp.world_size > 1 and all(tp_eligible(s.req.params) for s in seqs)
         return hook
 
     def step(self) -> List[TokenEvent]:
@@ -378,7 +386,8 @@ class Engine:
 
         if not launched and self.running:
             snapshot = {s.row: rid for rid, s in self.running.items() if not s.retired}
-            out = self.runner.decode(sampler=self._decode_sampler(snapshot)) if snapshot else None
+            hook = self._decode_sampler(snapshot) if snapshot else None
+            out = self.runner.decode(sampler=hook, sampler_takes_shards=bool(getattr(hook, "takes_shards", False))) if snapshot else None
             if out is not None:
                 self._after_decode_launch(out[0], out[1], snapshot)
                 launched = True

@@ -450,13 +450,16 @@ class ModelRunner:
         self.graphs[key] = g
         self.graph_out[key] = logits
 
-    def decode(self, lora: Optional[bool] = None, need_logits: bool = False, sampler=None):
+    def decode(self, lora: Optional[bool] = None, need_logits: bool = False, sampler=None, sampler_takes_shards: bool = False):
         """One decode step over rows [0, high_water).  Returns (ring index, bucket, logits or None); the sampled
         ids / log-probs land in the pinned ring entry once its event has completed.  `sampler(logits, state)` runs on the
         device right after the step and may overwrite `next_ids`, `logprobs` and the next `input_ids` of some rows (the
         step itself has already advanced the state with the arg-max)."""
         st = self.state
-        need_logits = need_logits or sampler is not None
+        # a sampler that draws from vocabulary shards (candidates exchanged, not logits) runs on the graph whose head stays local
+        shards = (sampler is not None and sampler_takes_shards and not need_logits and self.model.tp.world_size > 1
+                  and self.model.tp.fused is not None and not (self.model.config.final_logit_softcapping or 0.0))
+        need_logits = need_logits or (sampler is not None and not shards)
         n = st.high_water
         if n == 0:
             return None
@@ -473,7 +476,7 @@ class ModelRunner:
             self.capture(b, lora, variant)
             self.graphs[key].replay()
             self.replayed_launches += self.graph_kernels[key]
-            logits = self.graph_out[key] if need_logits else None
+            logits = self.graph_out[key] if (need_logits or shards) else None
         else:
             logits = self._decode_body(b, lora, need_logits)
             self._advance(b)

@@ -35,9 +35,10 @@ def _lsr(x: torch.Tensor, s: int) -> torch.Tensor:
     return (x >> s) & ((1 << (64 - s)) - 1)
 
 
-def uniform_noise(seeds: torch.Tensor, steps: torch.Tensor, vocab: int) -> torch.Tensor:
-    """[R, vocab] floats in (0, 1): a 64-bit mix (the finaliser of MurmurHash3) of seed, step and column."""
-    idx = torch.arange(vocab, dtype=torch.int64, device=seeds.device)[None, :]
+def uniform_noise(seeds: torch.Tensor, steps: torch.Tensor, vocab: int, offset: int = 0) -> torch.Tensor:
+    """[R, vocab] floats in (0, 1): a 64-bit mix (the finaliser of MurmurHash3) of seed, step and column.  `offset` is the
+    vocabulary index of column 0 (a tensor-parallel rank draws the noise of its own shard: the same numbers as the full row)."""
+    idx = torch.arange(offset, offset + vocab, dtype=torch.int64, device=seeds.device)[None, :]
     x = seeds[:, None] * _K_SEED + steps[:, None] * _K_STEP + idx * _K_IDX
     x = (x ^ _lsr(x, 33)) * _M1
     x = (x ^ _lsr(x, 33)) * _M2
@@ -118,6 +119,22 @@ def supported(p: NextTokenParams) -> bool:
     return not p.watermark and p.schema is None and p.return_k_alternatives == 0
 
 
+TP_CANDIDATES = 128     # candidates a tensor-parallel rank contributes per row: bounds the top-k that is exact without the logits
+
+
+def tp_eligible(p: NextTokenParams) -> bool:
+    """Whether a row can be sampled from vocabulary shards by exchanging candidates instead of logits: its filter must be
+    decided by the best TP_CANDIDATES tokens of every shard (top-k up to that, with or without top-p inside it), or there is no
+    filter at all (temperature only, or a greedy row that only carries penalties)."""
+    if not p.do_sample:
+        return True
+    if p.typical_p < 1.0:
+        return False
+    if p.top_k and p.top_k > 0:
+        return p.top_k <= TP_CANDIDATES
+    return p.top_p >= 1.0
+
+
 class RowSampler:
     """Parameter tensors for a set of rows, rebuilt only when the set changes."""
 
@@ -178,3 +195,77 @@ class RowSampler:
         if self.counts is not None:
             self.counts.scatter_add_(1, ids[:, None], torch.ones_like(ids, dtype=self.counts.dtype)[:, None])
         return ids, lp
+
+    # ------------------------------------------------------------------ vocabulary-parallel sampling
+    # The reference gathers the full logits on every rank before it samples (`layers/tensor_parallel.py:50-79`).  Here a rank
+    # keeps its vocabulary shard: the ranks exchange their best TP_CANDIDATES scores and the (max, sum of exponentials) of their
+    # shard per row, which fixes the cut-off of top-k / top-p and the normaliser exactly; every rank then draws inside its own
+    # shard with the noise of its own columns (the noise is a function of seed, step and vocabulary index, so the shards see
+    # the numbers the full row would) and the best (noisy score, log-probability, id) triple of all ranks wins.  A few hundred
+    # bytes per row cross the links instead of the vocabulary.
+    def tp_candidates(self, local_logits: torch.Tensor, v0: int, vocab: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        """-> (x [R, Vl]: penalised, temperature-scaled scores of this shard with padding columns at -inf,
+               payload [R, K + 2]: the K best of them, their maximum, and sum exp(x - maximum))."""
+        sel = local_logits.index_select(0, self.rows).float()
+        Vl = sel.shape[1]
+        if self.counts is not None:
+            sel = penalise(sel, self.counts[:, v0:v0 + Vl] if self.counts.shape[1] >= v0 + Vl else
+                           torch.nn.functional.pad(self.counts[:, v0:], (0, v0 + Vl - self.counts.shape[1])), self.rep, self.freq, self.pres)
+        x = sel / self.temperature[:, None].clamp_min(1e-6)
+        if v0 + Vl > vocab:
+            x[:, max(vocab - v0, 0):] = float("-inf")
+        k = min(TP_CANDIDATES, Vl)
+        top = x.topk(k, dim=-1).values
+        if k < TP_CANDIDATES:
+            top = torch.nn.functional.pad(top, (0, TP_CANDIDATES - k), value=float("-inf"))
+        m = top[:, :1]
+        ssum = torch.exp(x - m).sum(-1, keepdim=True)
+        return x, torch.cat([top, m, ssum], 1)
+
+    def tp_cutoff(self, payloads: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """payloads [ranks, R, K + 2] -> (tau [R]: scores below it are filtered, logz [R]: log of the sum of exp(score) over the
+        tokens that stay)."""
+        K = TP_CANDIDATES
+        ms, ss = payloads[:, :, K], payloads[:, :, K + 1]
+        M = ms.max(0).values
+        logz_all = M + torch.log((ss * torch.exp(ms - M[None])).sum(0))
+        cand = payloads[:, :, :K].permute(1, 0, 2).reshape(payloads.shape[1], -1).sort(dim=-1, descending=True).values      # [R, ranks * K]
+        neg = float("-inf")
+        has_k = self.top_k > 0
+        kth = cand.gather(1, (self.top_k.clamp(min=1, max=cand.shape[1]) - 1)[:, None])[:, 0]
+        kept = cand >= torch.where(has_k, kth, torch.full_like(kth, neg))[:, None]
+        c = torch.where(kept, cand, torch.full_like(cand, neg))
+        # top-p inside the top-k set (rows without top-k have top_p == 1: nothing to do)
+        probs = torch.softmax(c, -1)
+        before = probs.cumsum(-1) - probs
+        drop = (before >= self.top_p[:, None]) & has_k[:, None]
+        drop[:, 0] = False
+        c = c.masked_fill(drop, neg)
+        last = torch.where(torch.isfinite(c), c, torch.full_like(c, float("inf"))).min(-1).values
+        tau = torch.where(has_k, last, torch.full_like(last, neg))
+        logz = torch.where(has_k, torch.logsumexp(c, -1), logz_all)
+        return tau, logz
+
+    def tp_local_best(self, x: torch.Tensor, tau: torch.Tensor, logz: torch.Tensor, steps: Sequence[int], v0: int) -> torch.Tensor:
+        """-> [R, 3]: the best noisy score of this shard, the log-probability of that token, its vocabulary index."""
+        st = torch.tensor(list(steps), dtype=torch.int64, device=self.device)
+        logp = torch.where(x >= tau[:, None], x - logz[:, None], torch.full_like(x, float("-inf")))
+        e = -torch.log(uniform_noise(self.seeds, st, x.shape[1], offset=v0))
+        noisy = torch.where(self.sample[:, None], logp - torch.log(e), logp)
+        best, idx = noisy.max(-1)
+        return torch.stack([best, logp.gather(1, idx[:, None])[:, 0], (idx + v0).to(torch.float32)], 1)
+
+    def tp_finish(self, bests: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """bests [ranks, R, 3] -> (ids, logprobs); the histograms of the penalties are bumped at the drawn ids."""
+        win = bests[:, :, 0].argmax(0)                                        # the lowest rank wins a tie, as arg-max over the row would
+        pick = bests.gather(0, win[None, :, None].expand(1, -1, 3))[0]
+        ids = pick[:, 2].to(torch.int64)
+        if self.counts is not None:
+            self.counts.scatter_add_(1, ids[:, None].clamp(max=self.counts.shape[1] - 1), torch.ones_like(ids, dtype=self.counts.dtype)[:, None])
+        return ids, pick[:, 1]
+
+    def call_tp(self, local_logits: torch.Tensor, steps: Sequence[int], v0: int, vocab: int, all_gather) -> Tuple[torch.Tensor, torch.Tensor]:
+        """`all_gather(t)` returns the ranks' tensors stacked along a new first dimension."""
+        x, payload = self.tp_candidates(local_logits, v0, vocab)
+        tau, logz = self.tp_cutoff(all_gather(payload))
+        return self.tp_finish(all_gather(self.tp_local_best(x, tau, logz, steps, v0)))

@@ -193,6 +193,61 @@ def test_adapter_exchange_under_memory_pressure():
     assert roomy == full and stats3.get("adapter_prefetches", 0) >= 1
 
 
+def test_vocabulary_parallel_sampling_equals_sampling_from_the_full_row():
+    """Tensor-parallel ranks keep their vocabulary shard, exchange 128 candidates plus (max, sum exp) per row and the best
+    (noisy score, log-probability, id) triple: the drawn ids equal those of the sampler that sees the whole row, for
+    temperature-only rows, top-k rows with and without top-p, and greedy rows that only carry penalties."""
+    from lorax_b200.sampling import device as ds
+    from lorax_b200.sampling.chooser import NextTokenParams
+    torch.manual_seed(3)
+    V, ws = 1000, 4
+    pad = 1024                                   # the head is padded to a multiple of the ranks' shard: columns >= V must never win
+    params = [NextTokenParams(do_sample=True, temperature=0.8, seed=11), NextTokenParams(do_sample=True, temperature=1.3, top_k=40, seed=5),
+              NextTokenParams(do_sample=True, temperature=0.9, top_k=100, top_p=0.7, seed=9), NextTokenParams(do_sample=False, repetition_penalty=1.4, frequency_penalty=0.2),
+              NextTokenParams(do_sample=True, temperature=0.5, top_k=3, top_p=0.95, seed=2, presence_penalty=0.5)]
+    assert all(ds.tp_eligible(p) for p in params)
+    assert not ds.tp_eligible(NextTokenParams(do_sample=True, top_p=0.9)) and not ds.tp_eligible(NextTokenParams(do_sample=True, top_k=500))
+    assert not ds.tp_eligible(NextTokenParams(do_sample=True, top_k=10, typical_p=0.5))
+    rows = [0, 2, 3, 5, 6]
+    B = 8
+    for trial in range(6):
+        logits = torch.randn(B, pad) * 3
+        logits[:, V:] = 50.0                      # padding columns carry junk
+        hist = {i: torch.randint(0, 3, (V,)).float() for i in range(len(rows))}
+        steps = [trial + 4 * i for i in range(len(rows))]
+        full = ds.RowSampler("cpu")
+        store_a = {k: v.clone() for k, v in hist.items()}
+        full.bind(rows, params, list(range(len(rows))), store_a)
+        want_ids, want_lp = full(logits[:, :V], steps)
+        shard = pad // ws
+        samplers, stores = [], []
+        for r in range(ws):
+            sm = ds.RowSampler("cpu")
+            st = {k: v.clone() for k, v in hist.items()}
+            sm.bind(rows, params, list(range(len(rows))), st)
+            samplers.append(sm)
+            stores.append(st)
+        phase1 = [sm.tp_candidates(logits[:, r * shard:(r + 1) * shard], r * shard, V) for r, sm in enumerate(samplers)]
+        payloads = torch.stack([p for _, p in phase1])
+        assert payloads.shape == (ws, len(rows), ds.TP_CANDIDATES + 2)
+        bests = []
+        for r, sm in enumerate(samplers):
+            tau, logz = sm.tp_cutoff(payloads)
+            bests.append(sm.tp_local_best(phase1[r][0], tau, logz, steps, r * shard))
+        bests = torch.stack(bests)
+        for sm in samplers:
+            ids, lp = sm.tp_finish(bests)
+            assert torch.equal(ids, want_ids), (trial, ids, want_ids)
+            assert torch.allclose(lp, want_lp, atol=1e-4)
+            assert int(ids.max()) < V
+        for sm in samplers:
+            sm.release()
+        full.release()
+        for st in stores:                         # every rank bumped the same histogram entries as the full sampler
+            for k in st:
+                assert torch.equal(st[k], store_a[k])
+
+
 def test_device_sampler_distribution_and_filters():
     """The exponential-noise draw follows the warped distribution; top-k / top-p / typical-p keep exactly the reference's sets;
     the noise depends on (seed, step) only."""

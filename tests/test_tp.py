@@ -43,3 +43,4 @@ def test_tp_nccl_and_fused_kernels(world):
     assert r["gemm_allreduce_relerr"] < 6e-3 and r["gemm_allreduce_ranks_identical"]
     assert r["allreduce_sym_relerr"] < 6e-3 and r["allreduce_sym_ranks_identical"]
     assert r["argmax_tp_ok"]
+    assert r["sampled_shards_path_taken"] and r["sampled_from_shards_equals_gathered"]

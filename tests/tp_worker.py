@@ -52,6 +52,44 @@ def run_model(model, prompts, ads, n_decode, graphs):
     return outs, toks
 
 
+def run_sampled(model, prompts, ads, shards: bool, n_decode: int = 4):
+    """Sampled decoding (top-k with temperature, top-k + top-p, temperature only) through the device sampler: from vocabulary
+    shards with candidates exchanged, or from the gathered logits."""
+    from lorax_b200.sampling.chooser import NextTokenParams
+    from lorax_b200.sampling.device import RowSampler
+    cfg = model.config
+    kv = KVCache(cfg.num_hidden_layers, 64, model.nkv, model.d, model.dtype, model.device)
+    r = ModelRunner(model, kv, max_batch=8, max_seq_tokens=256, max_prefill_tokens=1024, use_graphs=True)
+    blocks = [[1 + 4 * i + j for j in range(4)] for i in range(len(prompts))]
+    ids, _, _ = r.prefill([PrefillItem(p, 0, blocks[i], adapter_index=ads[i]) for i, p in enumerate(prompts)])
+    rows = [r.state.take_row(i) for i in range(len(prompts))]
+    r.install(rows, ids.tolist(), [len(p) for p in prompts], blocks, ads)
+    mapping = r.resort()
+    params = [NextTokenParams(do_sample=True, temperature=0.9, top_k=20, seed=3), NextTokenParams(do_sample=True, temperature=1.2, top_k=50, top_p=0.8, seed=4),
+              NextTokenParams(do_sample=True, temperature=0.7, seed=5)]
+    rs = RowSampler(model.device)
+    live = sorted(mapping[x] for x in rows)
+    rs.bind(live, params)
+    toks, used_shards = [], []
+    tp = model.tp
+    for step in range(n_decode):
+        def hook(logits, st, step=step):
+            local = logits.shape[1] != model.vocab
+            used_shards.append(bool(local))
+            if local:
+                got, lp = rs.call_tp(logits, [step] * len(live), model.vocab_start, model.vocab, tp.all_gather_stack)
+            else:
+                got, lp = rs(logits, [step] * len(live))
+            g32 = got.to(st.next_ids.dtype)
+            st.next_ids.index_copy_(0, rs.rows, g32)
+            st.logprobs.index_copy_(0, rs.rows, lp.to(st.logprobs.dtype))
+            st.input_ids.index_copy_(0, rs.rows, g32)
+        k, b, _ = r.decode(sampler=hook, sampler_takes_shards=shards)
+        idp, _ = r.wait(k)
+        toks.append(idp[:len(prompts)].tolist())
+    return toks, used_shards
+
+
 def main():
     tp = TensorParallel.init_from_env()
     dev = tp.device
@@ -82,6 +120,12 @@ def main():
         if mode == "fused":
             tp.fused.check()
             out["fused_calls"] = tp.fused.calls
+            # sampling from vocabulary shards (candidates exchanged) draws what sampling from the gathered logits draws
+            a, used_a = run_sampled(shard, prompts, ads, shards=True)
+            b, used_b = run_sampled(shard, prompts, ads, shards=False)
+            out["sampled_from_shards_equals_gathered"] = a == b
+            out["sampled_shards_path_taken"] = all(used_a) and not any(used_b)
+            tp.fused.check()
     # ---- kernels
     if cuda:
         from lorax_b200.parallel import fused as fz
