@@ -403,6 +403,26 @@ __global__ void advance_decode_kernel(int* __restrict__ input_ids, const int* __
   slots[b] = blk * page + pos % page;
 }
 
+__global__ void __launch_bounds__(256)
+prefill_metadata_kernel(const int* __restrict__ cu_q, const int* __restrict__ cache_lens, const int* __restrict__ seq_slot,
+                        const int* __restrict__ block_tables, int max_blocks, int B, int page, int T, int* __restrict__ positions,
+                        int* __restrict__ slots, int* __restrict__ tok_slot) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  int lo = 0, hi = B;                     // last sequence whose first token is at or before t
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (cu_q[mid] <= t) lo = mid; else hi = mid;
+  }
+  const int pos = cache_lens[lo] + (t - cu_q[lo]);
+  positions[t] = pos;
+  const int blk = min(pos / page, max_blocks - 1);
+  slots[t] = block_tables[(long long)lo * max_blocks + blk] * page + pos % page;
+  if (tok_slot != nullptr) tok_slot[t] = seq_slot[lo];
+}
+
 }  // namespace lx
 
 extern "C" {
@@ -495,6 +515,19 @@ int lx_argmax_logprob(const void* logits, long long ld, int T, int V, int* ids, 
   if (T <= 0) return 0;
   launch_pdl(argmax_logprob_kernel, dim3(T), dim3(512), 0, reinterpret_cast<cudaStream_t>(stream), reinterpret_cast<const __nv_bfloat16*>(logits), ld, V,
                                                                              ids, logprobs, softcap);
+  return -(int)cudaGetLastError();
+}
+
+// Per-token metadata of a ragged prefill from its per-sequence description: positions[t] = cache_lens[b] + (t - cu_q[b]),
+// slots[t] = block_tables[b][position / page] * page + position % page, tok_slot[t] = seq_slot[b], for the sequence b that
+// holds token t (binary search in cu_q).  The reference assembles these arrays on the host for every batch
+// (server/lorax_server/models/flash_causal_lm.py:200-420).
+int lx_prefill_metadata(const int* cu_q, const int* cache_lens, const int* seq_slot, const int* block_tables, int max_blocks, int B,
+                        int page, int T, int* positions, int* slots, int* tok_slot, void* stream) {
+  using namespace lx;
+  if (T <= 0 || B <= 0) return 0;
+  launch_pdl(prefill_metadata_kernel, dim3((T + 255) / 256), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), cu_q, cache_lens, seq_slot,
+             block_tables, max_blocks, B, page, T, positions, slots, tok_slot);
   return -(int)cudaGetLastError();
 }
 

@@ -60,6 +60,7 @@ def load() -> ctypes.CDLL:
         "lx_embed": ([P, P, P, I, I, I, I, F, P], I),
         "lx_argmax_logprob": ([P, L, I, I, P, P, F, P], I),
         "lx_advance_decode": ([P, P, P, P, P, P, I, I, I, P], I),
+        "lx_prefill_metadata": ([P, P, P, P, I, I, I, I, P, P, P, P], I),
         "lx_attn_page_size": ([], I),
         "lx_attn_decode": ([P, L, P, P, I, P, P, L, P, P, I, I, I, I, I, F, F, I, P], I),
         "lx_attn_prefill": ([P, L, P, P, I, P, P, P, P, I, P, L, I, I, I, I, F, F, P], I),
@@ -500,6 +501,16 @@ def advance_decode(input_ids, next_ids, positions, ctx_lens, slots, block_tables
     rc = load().lx_advance_decode(_ptr(input_ids), _ptr(next_ids), _ptr(positions), _ptr(ctx_lens), _ptr(slots),
                                   _ptr(block_tables), block_tables.shape[1], page, B, _stream())
     _check(rc, "lx_advance_decode")
+
+
+def prefill_metadata(cu_q: torch.Tensor, cache_lens: torch.Tensor, seq_slot: torch.Tensor, block_tables: torch.Tensor, page: int, T: int):
+    """Per-token (positions, slots, adapter slot) of a ragged prefill from its per-sequence description, on the device."""
+    dev = cu_q.device
+    out = torch.empty(3, T, dtype=torch.int32, device=dev)
+    rc = load().lx_prefill_metadata(_ptr(cu_q), _ptr(cache_lens), _ptr(seq_slot), _ptr(block_tables), block_tables.shape[1], cache_lens.shape[0],
+                                    page, T, _ptr(out[0]), _ptr(out[1]), _ptr(out[2]), _stream())
+    _check(rc, "lx_prefill_metadata")
+    return out[0], out[1], out[2]
 
 
 # ------------------------------------------------------------------------------------------------ attention

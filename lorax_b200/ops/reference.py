@@ -216,6 +216,16 @@ def advance_decode(input_ids, next_ids, positions, ctx_lens, slots, block_tables
     slots.copy_(torch.where(live, new_slots.to(slots.dtype), torch.full_like(slots, -1)))
 
 
+def prefill_metadata(cu_q, cache_lens, seq_slot, block_tables, page, T):
+    """-> (positions [T], slots [T], tok_slot [T]) int32 of a ragged prefill whose sequence b owns tokens [cu_q[b], cu_q[b+1])."""
+    t = torch.arange(T, device=cu_q.device)
+    b = torch.searchsorted(cu_q[1:].long().contiguous(), t, right=True).clamp(max=cache_lens.shape[0] - 1)
+    pos = cache_lens.long()[b] + (t - cu_q.long()[b])
+    blk = (pos // page).clamp(max=block_tables.shape[1] - 1)
+    slots = block_tables.long()[b, blk] * page + pos % page
+    return pos.to(torch.int32), slots.to(torch.int32), seq_slot[b].to(torch.int32)
+
+
 def _gather_kv(kv_cache, block_table, n_keys, kvh, kv_scale=None):
     """-> K [n_keys, d], V [n_keys, d] for one sequence and kv head."""
     page = kv_cache.shape[3]

@@ -165,15 +165,17 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ prefill
     def _prefill_inputs(self, items: Sequence[PrefillItem], row_offset: int = 0, lead_tiles: Sequence[Tuple[int, int, int, int]] = ()):
-        """Host-side assembly of a ragged prefill: one packed H2D transfer for every int array.  Returns the
-        StepInputs and whether any prefill row has an adapter.  In the LoRA tile table the prefill rows are numbered
-        from `row_offset` and `lead_tiles` (tiles of rows that precede them in a mixed step) come first."""
+        """Assembly of a ragged prefill.  The host packs what it alone knows (token ids, per-sequence lengths, block tables, the
+        rows that want logits, the LoRA tile table) into one pinned buffer and one H2D transfer; the per-token positions, cache
+        slots and adapter slots are computed from the per-sequence arrays on the device (`ops.prefill_metadata`).  Returns the
+        StepInputs and whether any prefill row has an adapter.  In the LoRA tile table the prefill rows are numbered from
+        `row_offset` and `lead_tiles` (tiles of rows that precede them in a mixed step) come first."""
+        import numpy as np
         page = self.page
-        ids: List[int] = []
-        pos: List[int] = []
-        slots: List[int] = []
+        id_parts: List = []
         cu = [0]
-        cache_lens, tables, head_idx, tok_slot, head_slot, q_lens = [], [], [], [], [], []
+        cache_lens, tables, head_idx, head_slot, q_lens, seq_slot = [], [], [], [], [], []
+        tl: List[Tuple[int, int, int, int]] = list(lead_tiles)
         any_lora = False
         over_rows: List[int] = []
         over_vals: List[torch.Tensor] = []
@@ -182,19 +184,18 @@ class ModelRunner:
             if it.embeds is not None and len(it.embed_index or ()):
                 over_rows += [cu[-1] + int(i) for i in it.embed_index]
                 over_vals.append(it.embeds)
-            row = self._table_row(it.blocks)
             slot_id = self._slot_of(it.adapter_index)
             any_lora |= slot_id >= 0
-            c0 = it.cache_len
-            ids.extend(int(t) for t in it.token_ids)
-            pos.extend(range(c0, c0 + n))
-            slots.extend(row[p // page] * page + p % page for p in range(c0, c0 + n))
-            tok_slot += [slot_id] * n
+            id_parts.append(np.asarray(it.token_ids, dtype=np.int32))
             base = cu[-1]
             cu.append(base + n)
             cache_lens.append(it.cache_len)
-            tables.append(row)
+            tables.append(self._table_row(it.blocks))
             q_lens.append(n)
+            seq_slot.append(slot_id)
+            if slot_id >= 0:
+                # rows of one adapter in tiles of at most 32 (a run that continues the previous sequence's adapter starts a new tile)
+                tl += [(slot_id, base + a + row_offset, min(32, n - a), 0) for a in range(0, n, 32)]
             if it.want_logits:
                 if it.all_logprobs:
                     head_idx += list(range(base, base + n))
@@ -202,22 +203,26 @@ class ModelRunner:
                 else:
                     head_idx.append(base + n - 1)
                     head_slot.append(slot_id)
-        T = len(ids)
+        T = cu[-1]
         if T > self.max_prefill_tokens:
             raise ValueError(f"prefill of {T} tokens exceeds max_prefill_tokens={self.max_prefill_tokens}")
         ts, tq = reference.prefill_tiles(q_lens)
-        tl = reference.build_lora_tiles(tok_slot, 32) if any_lora else []
-        tl = list(lead_tiles) + [(sl, r0 + row_offset, nr, z) for (sl, r0, nr, z) in tl]
-        tl_flat = [x for t in tl for x in t]
-        segs = [ids, pos, slots, cu, cache_lens, ts, tq, head_idx, tok_slot, head_slot, tl_flat]
-        flat = [x for s in segs for x in s] + [x for row in tables for x in row]
-        dev = self._to_dev(flat)
+        if not any_lora:
+            tl = list(lead_tiles)
+        i32 = lambda v: np.asarray(v, dtype=np.int32).reshape(-1)
+        segs = [np.concatenate(id_parts) if id_parts else i32([]), i32(cu), i32(cache_lens), i32(seq_slot), i32(ts), i32(tq), i32(head_idx),
+                i32(head_slot), i32(tl), i32(tables)]
+        flat = torch.from_numpy(np.concatenate(segs))
+        if self.is_cuda:
+            flat = flat.pin_memory().to(self.device, non_blocking=True)
+        self.h2d_bytes += flat.numel() * 4
         views, o = [], 0
-        for s in segs:
-            views.append(dev[o:o + len(s)])
-            o += len(s)
-        bt = dev[o:].view(len(items), self.max_blocks)
-        d_ids, d_pos, d_slots, d_cu, d_cl, d_ts, d_tq, d_head, d_tokslot, d_headslot, d_tiles = views
+        for sgm in segs:
+            views.append(flat[o:o + sgm.shape[0]])
+            o += sgm.shape[0]
+        d_ids, d_cu, d_cl, d_seqslot, d_ts, d_tq, d_head, d_headslot, d_tiles, d_bt = views
+        bt = d_bt.view(len(items), self.max_blocks)
+        d_pos, d_slots, d_tokslot = self.model.ops.prefill_metadata(d_cu, d_cl, d_seqslot, bt, page, T)
         if any_lora and self.model.adapters is not None:
             self.model.adapters.fence()
         tiles = LoraTiles(d_tiles.view(-1, 4), len(tl), 32) if tl else None

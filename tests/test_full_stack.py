@@ -53,8 +53,8 @@ def stack(tmp_path_factory):
     d = cfg.to_dict()
     d["architectures"] = ["LlamaForCausalLM"]
     (mdir / "config.json").write_text(json.dumps(d))
-    vocab = {f"w{i}": i for i in range(512)}
-    vocab["<unk>"] = 0
+    vocab = {f"w{i}": i for i in range(511)}
+    vocab["<unk>"] = 511
     tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
     tok.pre_tokenizer = pre_tokenizers.Whitespace()
     tok.save(str(mdir / "tokenizer.json"))
@@ -407,8 +407,11 @@ def test_startup_probe_runs_a_real_request_and_health_runs_a_step(stack):
         return inner(items)
     rt.runner.prefill = counting
     try:
-        with urllib.request.urlopen(f"http://127.0.0.1:{port}/startup", timeout=20) as r:
-            assert r.status == 200
+        try:
+            with urllib.request.urlopen(f"http://127.0.0.1:{port}/startup", timeout=20) as r:
+                assert r.status == 200
+        except urllib.error.HTTPError as e:
+            raise AssertionError(f"/startup answered {e.code}: {e.read().decode()}")
         assert calls["prefill"] >= 1                       # the probe request reached the model
         rt.health()
         assert calls.get("probe", 0) >= 1                  # Health itself runs a step on block 0

@@ -133,6 +133,24 @@ def test_rope_kvwrite(nat, nh, nkv, d, rot):
     assert _rel_err(cache, cache_ref) < 4e-3
 
 
+def test_prefill_metadata(nat):
+    """Per-token positions, cache slots and adapter slots of a ragged prefill, computed on the device from the per-sequence arrays."""
+    q_lens, cache_lens, slots_of = [5, 64, 1, 130, 33], [0, 7, 99, 32, 0], [-1, 3, 3, 0, -1]
+    B, page, max_blocks = len(q_lens), 32, 9
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    cl = torch.tensor(cache_lens, device="cuda", dtype=torch.int32)
+    ss = torch.tensor(slots_of, device="cuda", dtype=torch.int32)
+    bt = torch.randint(1, 500, (B, max_blocks), device="cuda", dtype=torch.int32)
+    T = sum(q_lens)
+    got = nat.prefill_metadata(cu, cl, ss, bt, page, T)
+    want = ref.prefill_metadata(cu, cl, ss, bt, page, T)
+    for g, w in zip(got, want):
+        assert torch.equal(g, w)
+    # against the definition
+    t = 5 + 64 + 1 + 17                     # token 17 of sequence 3
+    assert int(got[0][t]) == 32 + 17 and int(got[1][t]) == int(bt[3, (32 + 17) // page]) * page + (32 + 17) % page and int(got[2][t]) == 0
+
+
 @pytest.mark.parametrize("act", ["silu", "gelu", "gelu_pytorch_tanh"])
 def test_act_mul(nat, act):
     x = torch.randn(19, 2 * 1376, device="cuda", dtype=torch.bfloat16)
