@@ -205,8 +205,10 @@ struct DecodeParams {
   float v_scale;              // fp8 cache: multiplies the output (the K scale is folded into `scale` by the host)
 };
 
-template <int D, int STAGES, bool KV8>
-__global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams p) {
+// NW warps per CTA split the pages of a (row, KV head): four for long contexts; two, so that two CTAs fit an SM and one streams
+// while the other starts or combines, for the short contexts of a large decode batch.
+template <int D, int STAGES, bool KV8, int NW>
+__global__ void __launch_bounds__(32 * NW) attn_decode_kernel(const DecodeParams p) {
   pdl_trigger();
   pdl_wait();      // every block waits, also those that return early below
   extern __shared__ __align__(1024) uint8_t dsm[];
@@ -263,11 +265,11 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
     slope1 = r1 < grows ? p.alibi[head0 + r1] : 0.f;
   }
   const int my_first = pb + warp;
-  const int my_count = my_first < pe ? (pe - my_first + 3) / 4 : 0;
+  const int my_count = my_first < pe ? (pe - my_first + NW - 1) / NW : 0;
 
   auto issue = [&](int i) {
     if (i < my_count) {
-      const int page = my_first + 4 * i;
+      const int page = my_first + NW * i;
       const long long blk = bt[page];
       const uint32_t sb = wbase + (i % STAGES) * STAGE;
       if constexpr (KV8) {
@@ -295,7 +297,7 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
       __syncwarp();
       sb = wwork;
     }
-    const int page = my_first + 4 * i;
+    const int page = my_first + NW * i;
     float sacc[kPage / 8][4];
     qk_tile<D, kPage>(sacc, qf, sb, lane);
     softmax_tile<D, kPage>(sacc, oacc, m, l, page * kPage, key_lo, ctx, key_lo, ctx, p.scale, p.softcap, lane, slope0, slope1);
@@ -311,9 +313,9 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
     l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
   }
-  float* so = reinterpret_cast<float*>(dsm);            // [4][16][D]
-  float* sm = so + 4 * 16 * D;                           // [4][16]
-  float* sl = sm + 4 * 16;                               // [4][16]
+  float* so = reinterpret_cast<float*>(dsm);            // [NW][16][D]
+  float* sm = so + NW * 16 * D;                          // [NW][16]
+  float* sl = sm + NW * 16;                              // [NW][16]
   {
     const int r0 = lane >> 2, r1 = r0 + 8;
 #pragma unroll
@@ -328,14 +330,14 @@ __global__ void __launch_bounds__(128, 1) attn_decode_kernel(const DecodeParams 
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < grows * D; idx += 128) {
+  for (int idx = threadIdx.x; idx < grows * D; idx += 32 * NW) {
     const int g = idx / D, d = idx % D;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, sm[w * 16 + g]);
+    for (int w = 0; w < NW; ++w) M = fmaxf(M, sm[w * 16 + g]);
     float num = 0.f, den = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < NW; ++w) {
       const float mw = sm[w * 16 + g];
       const float wgt = (mw == -INFINITY) ? 0.f : exp2f((mw - M) * kLog2e);
       num += wgt * so[(w * 16 + g) * D + d];
@@ -512,25 +514,40 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(const PrefillParams p
   }
 }
 
-template <int D, int STAGES, bool KV8>
-static int launch_decode(const DecodeParams& p, int T, cudaStream_t s) {
-  constexpr int SMEM = KV8 ? 4 * (STAGES * 2 * kPage * D + 2 * kPage * D * 2) : 4 * STAGES * 2 * kPage * D * 2;
-  static_assert(SMEM >= (4 * 16 * D + 128) * 4, "combine buffer must fit in the pipeline buffers");
+template <int D, int STAGES, bool KV8, int NW>
+static int launch_decode_nw(const DecodeParams& p, int T, cudaStream_t s) {
+  constexpr int SMEM = KV8 ? NW * (STAGES * 2 * kPage * D + 2 * kPage * D * 2) : NW * STAGES * 2 * kPage * D * 2;
+  static_assert(SMEM >= (NW * 16 * D + 2 * NW * 16) * 4, "combine buffer must fit in the pipeline buffers");
   static bool configured[64] = {false};          // the shared-memory opt-in is a per-device attribute
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64 || !configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, STAGES, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, STAGES, KV8, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return -(int)e;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   dim3 grid(T, p.nkv * p.gchunks, p.nsplit);
-  launch_pdl(attn_decode_kernel<D, STAGES, KV8>, grid, dim3(128), (size_t)SMEM, s, p);
+  launch_pdl(attn_decode_kernel<D, STAGES, KV8, NW>, grid, dim3(32 * NW), (size_t)SMEM, s, p);
   if (p.nsplit > 1) {
     dim3 g2(T, p.nh);
     launch_pdl(attn_combine_kernel<D>, g2, dim3(D), 0, s, p.part_o, p.part_lse, p.out, p.ldo, p.nh, p.nsplit);
   }
   return -(int)cudaGetLastError();
+}
+
+template <int D, int STAGES, bool KV8>
+static int launch_decode(const DecodeParams& p, int T, cudaStream_t s) {
+  // Enough CTAs for several waves over the GPU: two warps per CTA, two CTAs per SM (their start-up and combine phases overlap the
+  // other's streaming).  Few CTAs (small batches, split contexts): four warps each, so that one CTA keeps more pages in flight.
+  static int force = -1;
+  if (force < 0) {
+    const char* e = getenv("LORAX_ATTN_DECODE_WARPS");
+    force = e ? atoi(e) : 0;
+  }
+  const long long ctas = (long long)T * p.nkv * p.gchunks * p.nsplit;
+  const bool two = force == 2 || (force != 4 && ctas >= 2 * 148);
+  if (two) return launch_decode_nw<D, STAGES, KV8, 2>(p, T, s);
+  return launch_decode_nw<D, STAGES, KV8, 4>(p, T, s);
 }
 
 template <int D, bool KV8>
