@@ -14,6 +14,7 @@
 #include "openapi_gen.hpp"
 #include "http.hpp"
 #include "infer.hpp"
+#include "grpc_client.hpp"
 #include "json.hpp"
 
 using namespace lx;
@@ -870,6 +871,15 @@ static std::string open_api_document() {
 
 }  // namespace
 
+static lx::ShardedClient connect_grpc(const std::string& uds_path, int num_shards) {
+  std::vector<std::shared_ptr<lx::ShardClient>> v;
+  for (int r = 0; r < num_shards; ++r) {
+    auto framed = std::make_shared<lx::FramedUdsClient>(uds_path + "-" + std::to_string(r) + ".lx");
+    v.push_back(std::make_shared<lx::GrpcUdsClient>(uds_path + "-" + std::to_string(r), framed));
+  }
+  return lx::ShardedClient(std::move(v));
+}
+
 int main(int argc, char** argv) {
   Args a = parse_args(argc, argv);
   if (a.kv.count("help")) {
@@ -902,7 +912,13 @@ int main(int argc, char** argv) {
   const std::string host = a.get("hostname", "0.0.0.0");
   if (cfg.max_input_length >= cfg.max_total_tokens) { log_json("ERROR", "`max_input_length` must be < `max_total_tokens`"); return 2; }
 
-  auto client = std::make_shared<ShardedClient>(ShardedClient::connect_uds(uds, num_shard));
+  // framed socket (default) or the original gRPC contract on unix://{uds}-{rank}; the tokenizer helpers always use the framed one
+  const std::string transport = a.get("shard-transport", "framed");
+  if (transport != "framed" && transport != "grpc") {
+    std::cerr << "--shard-transport must be framed or grpc\n";
+    return 2;
+  }
+  auto client = std::make_shared<ShardedClient>(transport == "grpc" ? connect_grpc(uds, num_shard) : ShardedClient::connect_uds(uds, num_shard));
   gen::InfoResponse info;
   uint32_t num_blocks = 0;
   try {

@@ -279,3 +279,93 @@ def test_download_weights_fetches_the_default_adapter(tmp_path, capsys):
     assert "1 weight file(s) ready" in out and f"adapter {tmp_path / 'ad'} ready" in out
     with pytest.raises(Exception):
         cli.main(["download-weights", str(mdir), "--source", "local", "--adapter-id", str(tmp_path / "nope"), "--adapter-source", "local"])
+
+
+def test_router_speaks_grpc_to_the_shard(tmp_path):
+    """`lorax-router --shard-transport grpc`: the router's own HTTP/2 client reaches the shard's grpcio endpoint on
+    `unix://{uds}-0` for the service's RPCs (the tokenizer helpers stay on the framed socket).  A generation gives the tokens the
+    framed transport gives, a prompt longer than one flow-control window goes through, and a shard-side exception reaches the
+    HTTP client as text."""
+    import asyncio
+    import json
+    import subprocess
+    import threading
+    import time
+    import urllib.error
+    import urllib.request
+    from lorax_b200.csrc import build
+    from lorax_b200.server.runtime import build_runtime
+    from lorax_b200.server.transport import FramedServer, serve_grpc
+    from test_full_stack import ROUTER, _free_port, _post
+    build.build_host()
+    mdir = _model_dir(tmp_path)
+    rt = build_runtime(str(mdir), EngineConfig(max_input_length=1900, max_total_tokens=1964, max_batch_prefill_tokens=2000, compile=False),
+                       device="cpu", dtype=torch.float32, source="local", num_blocks=128, max_batch=8)
+    uds = str(tmp_path / "s")
+    framed = FramedServer(rt, uds + "-0.lx").start()
+    loop = asyncio.new_event_loop()
+    started = threading.Event()
+    holder = {}
+
+    def grpc_thread():
+        asyncio.set_event_loop(loop)
+
+        async def main():
+            holder["server"] = await serve_grpc(rt, uds, 0, 1, lock=framed.lock)
+            started.set()
+            await holder["server"].wait_for_termination()
+        loop.run_until_complete(main())
+    th = threading.Thread(target=grpc_thread, daemon=True)
+    th.start()
+    assert started.wait(20)
+    outs = {}
+    procs = []
+    try:
+        for transport in ("framed", "grpc"):
+            port = _free_port()
+            proc = subprocess.Popen([ROUTER, "--port", str(port), "--hostname", "127.0.0.1", "--master-shard-uds-path", uds, "--num-shard", "1",
+                                     "--max-input-length", "1900", "--max-total-tokens", "1964", "--max-batch-prefill-tokens", "2000",
+                                     "--model-id", "tiny", "--shard-transport", transport], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+            procs.append(proc)
+            for _ in range(100):
+                try:
+                    with urllib.request.urlopen(f"http://127.0.0.1:{port}/health", timeout=1) as r:
+                        if r.status == 200:
+                            break
+                except Exception:
+                    time.sleep(0.1)
+            else:
+                proc.kill()
+                raise RuntimeError("router did not come up: " + proc.stdout.read().decode()[-2000:])
+            st, body, _ = _post(port, "/generate", {"inputs": "w1 w2 w3 w4", "parameters": {"max_new_tokens": 5, "details": True}})
+            assert st == 200, body
+            outs[transport] = [t["id"] for t in json.loads(body)["details"]["tokens"]]
+            if transport == "grpc":
+                # 1500 long (unknown) words: the request message is larger than HTTP/2's default 65535-byte windows
+                long_prompt = " ".join("x" * 60 + str(i) for i in range(1500))
+                assert len(long_prompt) > 90000
+                st, body, _ = _post(port, "/generate", {"inputs": long_prompt, "parameters": {"max_new_tokens": 2}})
+                assert st == 200, body[:300]
+                # a failing shard call: the message travels in the trailers
+                inner = rt.prefill
+
+                def boom(req):
+                    raise RuntimeError("the shard says no: 100% sure")
+                rt.prefill = boom
+                try:
+                    st, body, _ = _post(port, "/generate", {"inputs": "w1 w2", "parameters": {"max_new_tokens": 2}})
+                finally:
+                    rt.prefill = inner
+                assert st == 424 and "the shard says no: 100% sure" in body, (st, body)
+                st, body, _ = _post(port, "/generate", {"inputs": "w1 w2 w3 w4", "parameters": {"max_new_tokens": 5, "details": True}})
+                assert st == 200 and [t["id"] for t in json.loads(body)["details"]["tokens"]] == outs["grpc"]
+        assert outs["framed"] == outs["grpc"] and len(outs["grpc"]) == 5
+    finally:
+        for proc in procs:
+            proc.terminate()
+            try:
+                proc.wait(timeout=10)
+            except subprocess.TimeoutExpired:
+                proc.kill()
+        loop.call_soon_threadsafe(lambda: asyncio.ensure_future(holder["server"].stop(0)))
+        framed.stop()
