@@ -291,12 +291,51 @@ def _pack_int32(q: torch.Tensor, bits: int, dim: int) -> torch.Tensor:
     return v.to(torch.int32)
 
 
+def _unpack_bitstream(t: torch.Tensor, bits: int, dim: int) -> torch.Tensor:
+    """Codes of a width that does not divide 32 (3-bit GPTQ): along `dim` every `bits` int32 hold 32 codes as one little-endian
+    bit stream, code j at bit j * bits (a code may straddle two words)."""
+    if dim == 1:
+        return _unpack_bitstream(t.t().contiguous(), bits, 0).t().contiguous()
+    R, C = t.shape
+    assert R % bits == 0, "rows must come in groups of `bits` words"
+    w = (t.to(torch.int64) & 0xFFFFFFFF).view(R // bits, bits, C)                     # unsigned words
+    j = torch.arange(32, device=t.device)
+    off = j * bits
+    word, shift = off // 32, off % 32
+    lo = w[:, word, :] >> shift.view(1, 32, 1)
+    nxt = torch.where(word + 1 < bits, word + 1, word)
+    hi = torch.where((shift + bits > 32).view(1, 32, 1), w[:, nxt, :] << (32 - shift).view(1, 32, 1), torch.zeros_like(lo))
+    return (((lo | hi) & ((1 << bits) - 1)).to(torch.int32)).reshape(R // bits * 32, C)
+
+
+def _pack_bitstream(q: torch.Tensor, bits: int, dim: int) -> torch.Tensor:
+    """Inverse of `_unpack_bitstream` (what AutoGPTQ's `pack` writes for 3 bits)."""
+    if dim == 1:
+        return _pack_bitstream(q.t().contiguous(), bits, 0).t().contiguous()
+    R, C = q.shape
+    assert R % 32 == 0
+    v = q.to(torch.int64).view(R // 32, 32, C)
+    out = torch.zeros(R // 32, bits, C, dtype=torch.int64, device=q.device)
+    for j in range(32):
+        off = j * bits
+        word, shift = off // 32, off % 32
+        out[:, word] |= (v[:, j] << shift) & 0xFFFFFFFF
+        if shift + bits > 32:
+            out[:, word + 1] |= v[:, j] >> (32 - shift)
+    out = torch.where(out >= 2 ** 31, out - 2 ** 32, out)
+    return out.to(torch.int32).reshape(R // 32 * bits, C)
+
+
 def gptq_unpack(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, bits: int, zero_offset: int = 1):
     """AutoGPTQ tensors (`qweight` int32 [K * bits / 32, N] packed along K, `qzeros` int32 [G, N * bits / 32] packed along N
     holding zero - 1, `scales` [G, N]) -> codes [N, K], scales [N, G], zeros [N, G].  `zero_offset=0` reads the v2 format,
     which stores the zero point itself."""
-    if bits not in (2, 4, 8):
+    if bits not in (2, 3, 4, 8):
         raise NotImplementedError(f"GPTQ with {bits} bits")
+    if bits == 3:                                      # 32 codes in three words, straddling word boundaries
+        q = _unpack_bitstream(qweight, 3, 0).t().contiguous()
+        z = (_unpack_bitstream(qzeros, 3, 1) + zero_offset) & 7
+        return q, scales.float().t().contiguous(), z[:, : scales.shape[1]].float().t().contiguous()
     q = _unpack_int32(qweight, bits, 0).t().contiguous()
     z = (_unpack_int32(qzeros, bits, 1) + zero_offset) & ((1 << bits) - 1)
     return q, scales.float().t().contiguous(), z[:, : scales.shape[1]].float().t().contiguous()
@@ -305,6 +344,13 @@ def gptq_unpack(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tenso
 def gptq_pack(q: torch.Tensor, scale: torch.Tensor, zero: torch.Tensor, bits: int, group: int, zero_offset: int = 1):
     """Inverse of `gptq_unpack`: codes [N, K], scale / zero [N, G] -> dict of AutoGPTQ tensors (with the trivial `g_idx`)."""
     N, K = q.shape
+    if bits == 3:
+        zz = ((zero.t().to(torch.int64) - zero_offset) & 7).contiguous()
+        pad = (-zz.shape[1]) % 32
+        if pad:
+            zz = torch.nn.functional.pad(zz, (0, pad))
+        return {"qweight": _pack_bitstream(q.t().contiguous(), 3, 0), "qzeros": _pack_bitstream(zz, 3, 1),
+                "scales": scale.t().contiguous().to(torch.float16), "g_idx": (torch.arange(K, dtype=torch.int32) // group)}
     return {"qweight": _pack_int32(q.t().contiguous(), bits, 0),
             "qzeros": _pack_int32(((zero.t().to(torch.int64) - zero_offset) & ((1 << bits) - 1)).contiguous(), bits, 1),
             "scales": scale.t().contiguous().to(torch.float16),
@@ -346,6 +392,8 @@ def from_checkpoint(tensors: dict, quant_method: str, bits: int, group: int, zer
     else:
         q, s, z = gptq_unpack(tensors["qweight"], tensors["qzeros"], tensors["scales"], bits, zero_offset)
         g_idx = tensors.get("g_idx")
+    if bits == 3:
+        bits = 4                                       # 3-bit codes and zero points are exact in the 4-bit resident layout
     N, K = q.shape
     G = s.shape[1]
     grp = K // G if group <= 0 else group

@@ -141,6 +141,32 @@ def test_hqq_beats_round_to_nearest_at_low_bits():
         assert (hqq - w).abs().pow(0.7).sum() < (rtn - w).abs().pow(0.7).sum()
 
 
+def test_three_bit_gptq_checkpoints_load_into_the_four_bit_layout():
+    """3-bit GPTQ packs 32 codes into three int32 as one bit stream (codes 10 and 21 straddle words; AutoGPTQ's `pack` writes the
+    low bits of a straddling code into the top of one word and the rest into the bottom of the next).  The codes and zero points
+    are exact in the resident 4-bit layout, so the layer is served packed."""
+    torch.manual_seed(7)
+    N, K, group = 32, 128, 64
+    q = torch.randint(0, 8, (N, K), dtype=torch.int32)
+    s = (torch.rand(N, K // group) * 0.1 + 0.01).to(torch.float16).float()
+    z = torch.randint(1, 8, (N, K // group)).float()
+    t = qf.gptq_pack(q, s, z, 3, group)
+    assert t["qweight"].shape == (K * 3 // 32, N) and t["qweight"].dtype == torch.int32
+    # the packing against AutoGPTQ's word-by-word description, for one column
+    col = q[5].tolist()
+    w0 = sum(col[j] << (3 * j) for j in range(10)) | ((col[10] << 30) & 0xFFFFFFFF)
+    w1 = ((col[10] >> 2) & 1) | sum(col[11 + j] << (3 * j + 1) for j in range(10)) | ((col[21] << 31) & 0xFFFFFFFF)
+    w2 = ((col[21] >> 1) & 3) | sum(col[22 + j] << (3 * j + 2) for j in range(10))
+    got = [int(v) & 0xFFFFFFFF for v in t["qweight"][:3, 5]]
+    assert got == [w0 & 0xFFFFFFFF, w1 & 0xFFFFFFFF, w2 & 0xFFFFFFFF]
+    uq, us, uz = qf.gptq_unpack(t["qweight"], t["qzeros"], t["scales"], 3)
+    assert torch.equal(uq, q) and torch.equal(uz, z) and torch.allclose(us, s, atol=1e-3)
+    packed, dense = qf.from_checkpoint(t, "gptq", 3, group)
+    want = (q.float() - z.repeat_interleave(group, 1)) * s.repeat_interleave(group, 1)
+    assert packed is not None and packed.bits == 4
+    assert torch.allclose(dense.float(), want, atol=2e-3) and torch.allclose(qf.dequantize(packed), want, atol=1e-6)
+
+
 def test_gptq_compensates_rounding_error_through_the_hessian():
     torch.manual_seed(4)
     w = torch.randn(64, 256)
