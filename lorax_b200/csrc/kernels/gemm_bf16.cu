@@ -480,6 +480,18 @@ LX_DEVICE int lora_build_units(const GemmParams& p, const LoraEnt* ents, int lt0
   return min(n + total, kLoraListCap);
 }
 
+// The complete unit list of token tile [j0, jlim), if it fits the list: built ahead of time (before the kernel waits for its
+// predecessor) for the CTA's first tile.  Returns the number of units, or -1 when the list would not hold them all.
+LX_DEVICE int lora_prebuild_units(const GemmParams& p, const LoraEnt* ents, int n_live, int j0, int jlim, LoraUnit* list) {
+  int n = 0;
+  bool ended = false;
+  for (int lt0 = lora_first_entry(ents, n_live, j0); !ended && lt0 < p.lora_num_tiles; lt0 += 32) {
+    if (n > kLoraListCap - 128) return -1;             // 32 entries yield up to 128 units
+    n = lora_build_units(p, ents, lt0, j0, jlim, list, n, ended);
+  }
+  return n;
+}
+
 // B_cat of every slot through one map per rank class: dims {rank, N, arena / 16 bytes} with strides {2 * rank, 16} bytes, box
 // {16, 128, 1}, 32-byte swizzle.  The third coordinate is where the slot's B_cat starts, so one descriptor, passed as a kernel
 // parameter, serves every adapter: nothing to fetch from memory per slot and nothing to fence.
@@ -539,6 +551,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const int num_tiles = tiles_a * tiles_b;
   const int kblocks = (p.K + kBK - 1) / kBK;
   const bool lora = LORA && p.lora_tiles != nullptr;
+  int pre_tb = -1, pre_n = 0;             // token tile whose unit list this warp (producer or MMA) has built ahead of its first tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -571,6 +584,29 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       load_lora_entries(p, ents, n_live);
       __syncthreads();
       if (p.lora_inline_shrink && warp == 2) lora_group_prefix(p, ents, gstart);
+      if (warp < 2 && !(p.lora_skip & 2)) {
+        // the producer warp and the MMA warp build the unit list of their first tile now, under the tail of the kernel in front;
+        // the producer also pulls that tile's B_cat rows (adapter weights, which no kernel of the step writes) into L2
+        GemmWorkIter<BN> it0(p, num_tiles, kblocks);
+        GemmWork w0;
+        if (it0.next(w0) && w0.kb0 == 0) {
+          const int ta0 = p.b_fastest ? w0.tile / tiles_b : w0.tile % tiles_a;
+          const int tb0 = p.b_fastest ? w0.tile % tiles_b : w0.tile / tiles_a;
+          const int n0 = lora_prebuild_units(p, ents, *n_live, tb0 * p.bn, tb0 * p.bn + p.umma_n, warp == 0 ? ulist_p : ulist_m);
+          if (n0 >= 0) { pre_tb = tb0; pre_n = n0; }
+          if (warp == 0 && n0 > 0 && p.lora_arena_maps) {
+            const int rows = min(kBM, p.a_rows - ta0 * kBM);
+            for (int u = lane; u < n0; u += 32) {
+              const LoraUnit q = ulist_p[u];
+              if ((q.img & 3) == 0) {
+                const int r = (q.rclass + 1) * 16;
+                const char* src = reinterpret_cast<const char*>(p.lora_arena) + (long long)q.boff * 16 + (long long)ta0 * kBM * r * 2;
+                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)(rows * r * 2)) : "memory");
+              }
+            }
+          }
+        }
+      }
       __syncthreads();
     }
   }
@@ -585,7 +621,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    int list_tb = -1, list_n = 0;          // token tile whose complete unit list sits in ulist_p
+    int list_tb = pre_tb, list_n = pre_n;  // token tile whose complete unit list sits in ulist_p
     bool shrink_seen = false;
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
     GemmWork w;
@@ -695,7 +731,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
     bool ok = true;
-    int list_tb = -1, list_n = 0;
+    int list_tb = pre_tb, list_n = pre_n;
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
     GemmWork w;
     while (it.next(w)) {
