@@ -94,6 +94,19 @@ def build_kernels(force: bool = False, verbose: bool = False) -> Path:
     return KERNELS_SO
 
 
+def _unicode_tables():
+    """`unicode_tables.hpp` (character classes, case and normalisation tables of the router's tokenizer) is generated from Python's
+    `unicodedata` when it is missing or older than its generator."""
+    out, gen = HOST_DIR / "unicode_tables.hpp", HOST_DIR / "gen_unicode_tables.py"
+    if out.exists() and out.stat().st_mtime >= gen.stat().st_mtime:
+        return
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("gen_unicode_tables", gen)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.main(str(out))
+
+
 def build_host(force: bool = False, verbose: bool = False):
     sources = sorted(HOST_DIR.glob("*.cpp"))
     if not sources:
@@ -101,6 +114,7 @@ def build_host(force: bool = False, verbose: bool = False):
     # the protobuf codec of the wire contract is generated from proto/generate.proto
     from lorax_b200.server import protogen
     protogen.main([str(HOST_DIR / "pb_gen.hpp")])
+    _unicode_tables()
     # the OpenAPI document the router serves at /docs and /api-doc/openapi.json is the one of the documentation
     spec = PKG.parent / "docs" / "reference" / "openapi.json"
     body = json.dumps(json.loads(spec.read_text()), separators=(",", ":")) if spec.exists() else '{"openapi":"3.0.3","info":{"title":"lorax-b200","version":"0.2.0"},"paths":{}}'
@@ -149,6 +163,7 @@ def build_host_selftest(sanitizer: str, verbose: bool = False) -> Path:
     undefined-behaviour checks) or "thread".  Returns the binary; running it prints OK and exits 0 when nothing was found."""
     from lorax_b200.server import protogen
     protogen.main([str(HOST_DIR / "pb_gen.hpp")])
+    _unicode_tables()
     # the OpenAPI document the router serves at /docs and /api-doc/openapi.json is the one of the documentation
     spec = PKG.parent / "docs" / "reference" / "openapi.json"
     body = json.dumps(json.loads(spec.read_text()), separators=(",", ":")) if spec.exists() else '{"openapi":"3.0.3","info":{"title":"lorax-b200","version":"0.2.0"},"paths":{}}'

@@ -6,6 +6,7 @@
 
 #include "infer.hpp"
 #include "json.hpp"
+#include "tokenizer.hpp"
 
 using namespace lx;
 
@@ -307,6 +308,47 @@ const char* lx_infer_fake_run(const char* requests_json, int max_active_adapters
   out.set("log", log);
   out.set("metrics", metrics.render());
   return ret(out.dump());
+}
+
+// ---- tokenizer: load a tokenizer.json, encode through a pool of `workers` threads.  `lx_tokenizer_load` returns null and
+// writes the reason (an unsupported component, an unreadable file) to `err`.
+struct TokHandle {
+  std::shared_ptr<const tok::Tokenizer> tok;
+  std::unique_ptr<tok::TokenizerPool> pool;
+  std::string last_error;
+};
+void* lx_tokenizer_load(const char* path, int workers, char* err, int err_cap) {
+  try {
+    auto h = std::make_unique<TokHandle>();
+    h->tok = tok::Tokenizer::load(path);
+    h->pool = std::make_unique<tok::TokenizerPool>(h->tok, workers);
+    return h.release();
+  } catch (const std::exception& e) {
+    if (err && err_cap > 0) { std::strncpy(err, e.what(), (size_t)err_cap - 1); err[err_cap - 1] = 0; }
+    return nullptr;
+  }
+}
+void lx_tokenizer_free(void* h) { delete static_cast<TokHandle*>(h); }
+// Number of ids (the first `cap` are written to `out`), or -1 with the reason in lx_tokenizer_error.
+long lx_tokenizer_encode(void* hv, const char* text, size_t len, int add_special, uint32_t* out, size_t cap) {
+  auto* h = static_cast<TokHandle*>(hv);
+  try {
+    const std::vector<uint32_t> ids = h->pool->encode(std::string(text, len), add_special != 0);
+    std::memcpy(out, ids.data(), std::min(cap, ids.size()) * sizeof(uint32_t));
+    return (long)ids.size();
+  } catch (const std::exception& e) {
+    h->last_error = e.what();
+    return -1;
+  }
+}
+const char* lx_tokenizer_error(void* h) { return static_cast<TokHandle*>(h)->last_error.c_str(); }
+// Normalisation form of a UTF-8 string ("NFC", "NFD", "NFKC", "NFKD", "lower"), for the Unicode tables' own test.
+const char* lx_unicode_normalize(const char* text, const char* form) {
+  const std::string f = form;
+  const uni::Text t = uni::from_utf8(text);
+  if (f == "lower") return ret(uni::to_utf8(uni::lowercase(t)));
+  const uni::Form which = f == "NFC" ? uni::Form::NFC : f == "NFD" ? uni::Form::NFD : f == "NFKC" ? uni::Form::NFKC : uni::Form::NFKD;
+  return ret(uni::to_utf8(uni::normalize(t, which)));
 }
 
 }  // extern "C"

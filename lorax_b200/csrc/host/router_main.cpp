@@ -946,6 +946,29 @@ int main(int argc, char** argv) {
   log_json("INFO", "connected to " + std::to_string(num_shard) + " shard(s); max_batch_total_tokens=" + std::to_string(cfg.max_batch_total_tokens));
 
   g_validation_workers = (int)a.geti("validation-workers", 2);
+  // Tokenisation inside the router, on `validation_workers` threads, from the tokenizer file of shard 0 (or --tokenizer-name: a
+  // tokenizer.json or a directory with one).  `--router-tokenizer off`, a runtime whose prompts need more than the tokenizer
+  // (image placeholders) or a file with a component the router does not implement leave tokenisation with shard 0.
+  if (a.get("router-tokenizer", "on") != "off") {
+    try {
+      std::shared_ptr<const tok::Tokenizer> t;
+      const std::string named = a.get("tokenizer-name", "");
+      if (!named.empty()) {
+        t = tok::Tokenizer::load(named);
+      } else {
+        const std::string file = client->helper(103, "");
+        json::Value root;
+        std::string perr;
+        if (file.empty()) throw tok::Unsupported("the shard keeps tokenisation to itself");
+        if (!json::parse(file, root, &perr)) throw std::runtime_error("tokenizer file: " + perr);
+        t = tok::Tokenizer::from_json(root);
+      }
+      client->set_local_tokenizer(std::make_shared<tok::TokenizerPool>(t, g_validation_workers));
+      log_json("INFO", "tokenising in the router on " + std::to_string(g_validation_workers) + " worker(s)");
+    } catch (const std::exception& e) {
+      log_json("INFO", std::string("shard 0 tokenises (router tokenizer not used: ") + e.what() + ")");
+    }
+  }
   const std::string otlp = a.get("otlp-endpoint", "");
   const char* logger_env = std::getenv("REQUEST_LOGGER_URL");
   App app(client, cfg, info, num_blocks, otlp, logger_env ? logger_env : "");
@@ -978,7 +1001,9 @@ int main(int argc, char** argv) {
   // Prometheus text by default; JSON with ?format=json or "Accept: application/json" (reference router/src/server.rs:1200-1290):
   // {family: {"type": counter|gauge|histogram, "data": [{"key": labelled series name | "sum" | "count" | "", "value": v}]}}
   R("GET", "/metrics", [&](auto& req, auto& w) {
-    const std::string text = app.metrics().render();
+    std::string text = app.metrics().render();
+    if (client->tokenizes_locally())
+      text += "# TYPE lorax_router_tokenizations counter\nlorax_router_tokenizations " + std::to_string(client->local_tokenizations()) + "\n";
     std::string fmt = req.query_param("format");
     for (auto& ch : fmt) ch = (char)std::tolower((unsigned char)ch);
     const bool want_json = fmt.empty() ? req.header("accept").find("application/json") != std::string::npos : fmt == "json";

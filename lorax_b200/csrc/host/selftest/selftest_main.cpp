@@ -9,6 +9,8 @@
 #include <cstring>
 #include <memory>
 #include <string>
+#include <thread>
+#include <unistd.h>
 
 #include "flag_protocols.hpp"
 #include <vector>
@@ -24,6 +26,33 @@ void lx_alloc_free(void* a, void* h, uint32_t adapter, const uint32_t* all_token
 const char* lx_json_roundtrip(const char* s);
 const char* lx_infer_fake_run(const char* requests_json, int max_active_adapters, int fail_decode_after, uint32_t num_blocks,
                               int prefix_caching);
+void* lx_tokenizer_load(const char* path, int workers, char* err, int err_cap);
+void lx_tokenizer_free(void* h);
+long lx_tokenizer_encode(void* h, const char* text, size_t len, int add_special, uint32_t* out, size_t cap);
+}
+
+// A byte-level BPE tokenizer file over printable ASCII: normaliser, regex split, merges, a special token and a template, so
+// that the router's tokenizer pipeline and its worker pool run under the sanitizers.
+static std::string tiny_tokenizer_json() {
+  std::string vocab = "\"<s>\":0";
+  int id = 1;
+  for (int c = '!'; c <= '~'; ++c) {
+    std::string key(1, (char)c);
+    if (c == '"' || c == '\\') key = std::string("\\") + (char)c;
+    vocab += ",\"" + key + "\":" + std::to_string(id++);
+  }
+  vocab += ",\"\u0120\":" + std::to_string(id++);
+  for (const char* m : {"th", "the", "\u0120t", "er", "in"}) vocab += std::string(",\"") + m + "\":" + std::to_string(id++);
+  return std::string("{\"added_tokens\":[{\"id\":0,\"content\":\"<s>\",\"single_word\":false,\"lstrip\":false,\"rstrip\":false,"
+                     "\"normalized\":false,\"special\":true}],"
+                     "\"normalizer\":{\"type\":\"Sequence\",\"normalizers\":[{\"type\":\"NFKC\"},{\"type\":\"Lowercase\"}]},"
+                     "\"pre_tokenizer\":{\"type\":\"Sequence\",\"pretokenizers\":[{\"type\":\"Split\",\"pattern\":{\"Regex\":"
+                     "\"'s|'t| ?\\\\p{L}+| ?\\\\p{N}+| ?[^\\\\s\\\\p{L}\\\\p{N}]+|\\\\s+(?!\\\\S)|\\\\s+\"},\"behavior\":\"Isolated\",\"invert\":false},"
+                     "{\"type\":\"ByteLevel\",\"add_prefix_space\":false,\"use_regex\":false}]},"
+                     "\"post_processor\":{\"type\":\"TemplateProcessing\",\"single\":[{\"SpecialToken\":{\"id\":\"<s>\",\"type_id\":0}},"
+                     "{\"Sequence\":{\"id\":\"A\",\"type_id\":0}}],\"special_tokens\":{\"<s>\":{\"id\":\"<s>\",\"ids\":[0],\"tokens\":[\"<s>\"]}}},"
+                     "\"model\":{\"type\":\"BPE\",\"unk_token\":null,\"vocab\":{") +
+         vocab + "},\"merges\":[\"t h\",\"th e\",\"\u0120 t\",\"e r\",\"i n\"]}}";
 }
 
 static int fail(const char* what, const std::string& detail = "") {
@@ -82,6 +111,40 @@ int main() {
   if (!lx_model::model_all_reduce(2, 5, 64, 10)) return fail("two-shot all-reduce protocol model (2 ranks)");
   if (!lx_model::model_lora_sync(6, 17, 2, 5)) return fail("LoRA-in-GEMM protocol model");
   if (!lx_model::model_lora_sync(4, 9, 1, 5)) return fail("LoRA-in-GEMM protocol model (no K split)");
+  {
+    // tokenizer: four request threads share a pool of two workers; every thread must see the ids a lone call produced
+    char path[] = "/tmp/lx_selftest_tok_XXXXXX";
+    const int fd = mkstemp(path);
+    if (fd < 0) return fail("mkstemp");
+    const std::string js = tiny_tokenizer_json();
+    if (write(fd, js.data(), js.size()) != (ssize_t)js.size()) return fail("write tokenizer file");
+    close(fd);
+    char err[256] = {0};
+    void* h = lx_tokenizer_load(path, 2, err, sizeof err);
+    unlink(path);
+    if (!h) return fail("tokenizer load", err);
+    const std::string text = "The other thing<s>in THE winter, isn't it?  42 times\n\n  there";
+    std::vector<uint32_t> want(256);
+    const long n = lx_tokenizer_encode(h, text.data(), text.size(), 1, want.data(), want.size());
+    if (n < 8 || want[0] != 0) return fail("tokenizer encode");
+    want.resize((size_t)n);
+    int bad = 0;
+    std::vector<std::thread> threads;
+    std::vector<int> bads(4, 0);
+    for (int t = 0; t < 4; ++t)
+      threads.emplace_back([&, t] {
+        for (int k = 0; k < 100; ++k) {
+          std::vector<uint32_t> got(256);
+          const long m = lx_tokenizer_encode(h, text.data(), text.size(), 1, got.data(), got.size());
+          got.resize(m < 0 ? 0 : (size_t)m);
+          if (got != want) ++bads[(size_t)t];
+        }
+      });
+    for (auto& th : threads) th.join();
+    for (int b : bads) bad += b;
+    lx_tokenizer_free(h);
+    if (bad) return fail("tokenizer pool", std::to_string(bad));
+  }
   std::printf("OK\n");
   return 0;
 }

@@ -30,6 +30,7 @@
 #include <vector>
 
 #include "pb_gen.hpp"
+#include "tokenizer.hpp"
 
 namespace lx {
 
@@ -198,9 +199,14 @@ class ShardedClient {
     r.batch = b;
     return all<gen::ClassifyResponse>(gen::M_Classify, r).front();
   }
-  // Helper calls outside LoraxService, answered by shard 0: tokenisation and chat templating live next to the
-  // tokenizer files (there is no tokenizer library for C++ on this machine).
+  // Request text -> ids.  With a local tokenizer (the router read the shard's tokenizer file and implements every component
+  // it uses) this runs on the router's tokenizer workers; otherwise shard 0 is asked.  Chat templating and `/tokenize` with
+  // character offsets are always helper calls to shard 0.
+  void set_local_tokenizer(std::shared_ptr<tok::TokenizerPool> pool) { local_tok_ = std::move(pool); }
+  bool tokenizes_locally() const { return local_tok_ != nullptr; }
+  uint64_t local_tokenizations() const { return local_tok_ ? local_tok_->served() : 0; }
   std::vector<uint32_t> tokenize(const std::string& text, bool add_special = true) {
+    if (local_tok_) return local_tok_->encode(text, add_special);
     std::string out = shards_.front()->call(gen::M_Tokenize, std::string(1, add_special ? '\1' : '\0') + text);
     std::vector<uint32_t> ids(out.size() / 4);
     std::memcpy(ids.data(), out.data(), ids.size() * 4);
@@ -225,6 +231,7 @@ class ShardedClient {
     return out;
   }
   std::vector<std::shared_ptr<ShardClient>> shards_;
+  std::shared_ptr<tok::TokenizerPool> local_tok_;
   struct TraceSlot {                      // movable holder: the client itself is passed around by value once
     std::mutex mu;
     std::string tp;

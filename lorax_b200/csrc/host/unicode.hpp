@@ -1,0 +1,211 @@
+// Unicode helpers for the router's tokenizer: UTF-8 <-> code points, character classes by binary search over the generated
+// range tables, lower-casing and the four normalisation forms.  No Unicode library is linked; `unicode_tables.hpp` is written
+// by gen_unicode_tables.py.
+#pragma once
+#include <algorithm>
+#include <cstdint>
+#include <string>
+#include <vector>
+
+#include "unicode_tables.hpp"
+
+namespace lx {
+namespace uni {
+
+using Text = std::vector<uint32_t>;        // code points
+
+inline void append_utf8(std::string& out, uint32_t cp) {
+  if (cp < 0x80) out.push_back((char)cp);
+  else if (cp < 0x800) { out.push_back((char)(0xC0 | (cp >> 6))); out.push_back((char)(0x80 | (cp & 0x3F))); }
+  else if (cp < 0x10000) {
+    out.push_back((char)(0xE0 | (cp >> 12))); out.push_back((char)(0x80 | ((cp >> 6) & 0x3F))); out.push_back((char)(0x80 | (cp & 0x3F)));
+  } else {
+    out.push_back((char)(0xF0 | (cp >> 18))); out.push_back((char)(0x80 | ((cp >> 12) & 0x3F)));
+    out.push_back((char)(0x80 | ((cp >> 6) & 0x3F))); out.push_back((char)(0x80 | (cp & 0x3F)));
+  }
+}
+inline std::string to_utf8(const uint32_t* p, size_t n) {
+  std::string s;
+  s.reserve(n);
+  for (size_t i = 0; i < n; ++i) append_utf8(s, p[i]);
+  return s;
+}
+inline std::string to_utf8(const Text& t) { return to_utf8(t.data(), t.size()); }
+
+// Ill-formed sequences decode to U+FFFD, one per offending byte (the text of a request reaches the router as JSON, whose
+// strings a Rust server would have rejected or replaced the same way).
+inline Text from_utf8(const std::string& s) {
+  Text out;
+  out.reserve(s.size());
+  const unsigned char* p = (const unsigned char*)s.data();
+  const size_t n = s.size();
+  for (size_t i = 0; i < n;) {
+    const unsigned char c = p[i];
+    if (c < 0x80) { out.push_back(c); ++i; continue; }
+    int len = c >= 0xF0 && c < 0xF8 ? 4 : c >= 0xE0 ? 3 : c >= 0xC2 && c < 0xE0 ? 2 : 0;
+    if (len == 0 || i + (size_t)len > n) { out.push_back(0xFFFD); ++i; continue; }
+    uint32_t cp = len == 4 ? (c & 0x07) : len == 3 ? (c & 0x0F) : (c & 0x1F);
+    bool ok = true;
+    for (int k = 1; k < len; ++k) {
+      if ((p[i + k] & 0xC0) != 0x80) { ok = false; break; }
+      cp = (cp << 6) | (p[i + k] & 0x3F);
+    }
+    if (!ok || (len == 3 && cp < 0x800) || (len == 4 && (cp < 0x10000 || cp > 0x10FFFF)) || (cp >= 0xD800 && cp < 0xE000)) {
+      out.push_back(0xFFFD); ++i; continue;
+    }
+    out.push_back(cp);
+    i += (size_t)len;
+  }
+  return out;
+}
+
+inline bool in_ranges(const uint32_t (*r)[2], int n, uint32_t cp) {
+  int lo = 0, hi = n - 1;
+  while (lo <= hi) {
+    const int mid = (lo + hi) / 2;
+    if (cp < r[mid][0]) hi = mid - 1;
+    else if (cp > r[mid][1]) lo = mid + 1;
+    else return true;
+  }
+  return false;
+}
+inline bool is_letter(uint32_t c) { return c < 0x80 ? ((c | 32) >= 'a' && (c | 32) <= 'z') : in_ranges(kLetter, kLetter_n, c); }
+inline bool is_number(uint32_t c) { return c < 0x80 ? (c >= '0' && c <= '9') : in_ranges(kNumber, kNumber_n, c); }
+inline bool is_decimal(uint32_t c) { return c < 0x80 ? (c >= '0' && c <= '9') : in_ranges(kDecimal, kDecimal_n, c); }
+inline bool is_mark(uint32_t c) { return c >= 0x300 && in_ranges(kMark, kMark_n, c); }
+inline bool is_nonspacing_mark(uint32_t c) { return c >= 0x300 && in_ranges(kNonspacingMark, kNonspacingMark_n, c); }
+inline bool is_punct_category(uint32_t c) { return in_ranges(kPunct, kPunct_n, c); }
+inline bool is_symbol(uint32_t c) { return in_ranges(kSymbol, kSymbol_n, c); }
+inline bool is_separator(uint32_t c) { return in_ranges(kSeparator, kSeparator_n, c); }
+inline bool is_other(uint32_t c) { return in_ranges(kControl, kControl_n, c); }     // Cc, Cf, Co, Cn
+inline bool is_space(uint32_t c) { return c < 0x80 ? (c == ' ' || (c >= 9 && c <= 13)) : in_ranges(kWhiteSpace, kWhiteSpace_n, c); }
+inline bool is_word(uint32_t c) {
+  return c < 0x80 ? (((c | 32) >= 'a' && (c | 32) <= 'z') || (c >= '0' && c <= '9') || c == '_') : in_ranges(kWord, kWord_n, c);
+}
+inline bool is_ascii_punct(uint32_t c) { return (c >= 33 && c <= 47) || (c >= 58 && c <= 64) || (c >= 91 && c <= 96) || (c >= 123 && c <= 126); }
+
+template <class Idx>
+inline const uint32_t* find3(const Idx& idx, int n, uint32_t cp) {
+  int lo = 0, hi = n - 1;
+  while (lo <= hi) {
+    const int mid = (lo + hi) / 2;
+    if (cp < idx[mid][0]) hi = mid - 1;
+    else if (cp > idx[mid][0]) lo = mid + 1;
+    else return idx[mid];
+  }
+  return nullptr;
+}
+
+inline void lower_into(Text& out, uint32_t c) {
+  if (c < 0x80) { out.push_back(c >= 'A' && c <= 'Z' ? c + 32 : c); return; }
+  if (const uint32_t* e = find3(kLower_idx, kLower_n, c)) {
+    for (uint32_t k = 0; k < e[2]; ++k) out.push_back(kLower_data[e[1] + k]);
+  } else {
+    out.push_back(c);
+  }
+}
+inline uint32_t lower1(uint32_t c) {          // first code point of the lower-case form (regex case folding)
+  if (c < 0x80) return c >= 'A' && c <= 'Z' ? c + 32 : c;
+  const uint32_t* e = find3(kLower_idx, kLower_n, c);
+  return e ? kLower_data[e[1]] : c;
+}
+inline Text lowercase(const Text& t) {
+  Text out;
+  out.reserve(t.size());
+  for (uint32_t c : t) lower_into(out, c);
+  return out;
+}
+
+inline uint32_t ccc(uint32_t c) {
+  if (c < 0x300) return 0;
+  int lo = 0, hi = kCcc_n - 1;
+  while (lo <= hi) {
+    const int mid = (lo + hi) / 2;
+    if (c < kCcc[mid][0]) hi = mid - 1;
+    else if (c > kCcc[mid][0]) lo = mid + 1;
+    else return kCcc[mid][1];
+  }
+  return 0;
+}
+
+// Decomposition (canonical, or compatibility when `compat`) followed by the canonical ordering of combining marks.
+inline Text decompose(const Text& t, bool compat) {
+  Text out;
+  out.reserve(t.size() + 8);
+  for (uint32_t c : t) {
+    if (c < 0xA0) { out.push_back(c); continue; }
+    if (c >= 0xAC00 && c <= 0xD7A3) {                  // Hangul syllable: L V (T) by arithmetic
+      const uint32_t s = c - 0xAC00;
+      out.push_back(0x1100 + s / 588);
+      out.push_back(0x1161 + (s % 588) / 28);
+      if (s % 28) out.push_back(0x11A7 + s % 28);
+      continue;
+    }
+    const uint32_t* e = compat ? find3(kNfkdExtra_idx, kNfkdExtra_n, c) : nullptr;
+    if (e) { for (uint32_t k = 0; k < e[2]; ++k) out.push_back(kNfkdExtra_data[e[1] + k]); continue; }
+    e = find3(kNfd_idx, kNfd_n, c);
+    if (e) { for (uint32_t k = 0; k < e[2]; ++k) out.push_back(kNfd_data[e[1] + k]); continue; }
+    out.push_back(c);
+  }
+  for (size_t i = 0; i < out.size();) {                // stable sort of each run of non-starters by combining class
+    if (ccc(out[i]) == 0) { ++i; continue; }
+    size_t j = i;
+    while (j < out.size() && ccc(out[j]) != 0) ++j;
+    std::stable_sort(out.begin() + (long)i, out.begin() + (long)j, [](uint32_t a, uint32_t b) { return ccc(a) < ccc(b); });
+    i = j;
+  }
+  return out;
+}
+
+inline uint32_t compose_pair(uint32_t a, uint32_t b) {
+  if (a >= 0x1100 && a < 0x1113 && b >= 0x1161 && b < 0x1176) return 0xAC00 + ((a - 0x1100) * 21 + (b - 0x1161)) * 28;
+  if (a >= 0xAC00 && a <= 0xD7A3 && (a - 0xAC00) % 28 == 0 && b > 0x11A7 && b < 0x11C3) return a + (b - 0x11A7);
+  int lo = 0, hi = kCompose_n - 1;
+  while (lo <= hi) {
+    const int mid = (lo + hi) / 2;
+    const uint32_t* e = kCompose[mid];
+    if (a < e[0] || (a == e[0] && b < e[1])) hi = mid - 1;
+    else if (a > e[0] || b > e[1]) lo = mid + 1;
+    else return e[2];
+  }
+  return 0;
+}
+
+// Canonical composition of a decomposed, canonically ordered text.
+inline Text compose(const Text& d) {
+  Text out;
+  out.reserve(d.size());
+  long starter = -1;
+  uint32_t last_ccc = 0;
+  for (uint32_t c : d) {
+    const uint32_t cc = ccc(c);
+    if (starter >= 0) {
+      const bool adjacent = (size_t)starter + 1 == out.size();
+      if (adjacent || (last_ccc < cc && cc != 0) ) {
+        // blocked only when a mark of the same or a higher class sits between the starter and c
+        if (adjacent || last_ccc < cc) {
+          const uint32_t m = compose_pair(out[(size_t)starter], c);
+          if (m) { out[(size_t)starter] = m; continue; }
+        }
+      }
+    }
+    if (cc == 0) { starter = (long)out.size(); last_ccc = 0; }
+    else last_ccc = cc;
+    out.push_back(c);
+  }
+  return out;
+}
+
+enum class Form { NFC, NFD, NFKC, NFKD };
+inline Text normalize(const Text& t, Form f) {
+  const bool compat = f == Form::NFKC || f == Form::NFKD;
+  const uint32_t quick = compat ? 0xA0 : 0xC0;         // nothing below decomposes or combines
+  bool plain = true;
+  for (uint32_t c : t) if (c >= quick) { plain = false; break; }
+  if (plain) return t;
+  Text d = decompose(t, compat);
+  return (f == Form::NFC || f == Form::NFKC) ? compose(d) : d;
+}
+
+}  // namespace uni
+}  // namespace lx

@@ -38,6 +38,11 @@ def load():
         "lx_json_roundtrip": ([c_char_p], c_char_p),
         "lx_queues_script": ([c_int, c_double, c_char_p], c_char_p),
         "lx_infer_fake_run": ([c_char_p, c_int, c_int, c_uint32, c_int], c_char_p),
+        "lx_tokenizer_load": ([c_char_p, c_int, c_char_p, c_int], c_void_p),
+        "lx_tokenizer_free": ([c_void_p], None),
+        "lx_tokenizer_encode": ([c_void_p, c_char_p, ctypes.c_size_t, c_int, U32P, ctypes.c_size_t], ctypes.c_long),
+        "lx_tokenizer_error": ([c_void_p], c_char_p),
+        "lx_unicode_normalize": ([c_char_p, c_char_p], c_char_p),
     }
     for name, (args, res) in sig.items():
         f = getattr(lib, name)
@@ -106,3 +111,42 @@ def infer_fake_run(requests, max_active_adapters: int = 8, fail_decode_after: in
                    prefix_caching: bool = False):
     out = load().lx_infer_fake_run(json.dumps(requests).encode(), max_active_adapters, fail_decode_after, num_blocks, int(prefix_caching))
     return json.loads(out.decode())
+
+
+class RouterTokenizer:
+    """The router's C++ tokenizer (``csrc/host/tokenizer.hpp``) on a pool of worker threads.  Raises ``ValueError`` with the
+    reason when the tokenizer file uses a component it does not implement (the router then asks shard 0 instead)."""
+
+    def __init__(self, path: str, workers: int = 2):
+        self._lib = load()
+        err = ctypes.create_string_buffer(512)
+        self._h = self._lib.lx_tokenizer_load(str(path).encode(), workers, err, len(err))
+        if not self._h:
+            raise ValueError(err.value.decode(errors="replace"))
+
+    def encode(self, text: str, add_special_tokens: bool = True) -> List[int]:
+        raw = text.encode("utf-8", errors="replace")
+        cap = max(16, len(raw) + 16)
+        buf = (c_uint32 * cap)()
+        n = self._lib.lx_tokenizer_encode(self._h, raw, len(raw), int(add_special_tokens), buf, cap)
+        if n < 0:
+            raise ValueError(self._lib.lx_tokenizer_error(self._h).decode(errors="replace"))
+        if n > cap:                                  # more ids than bytes: only with long special-token templates
+            buf = (c_uint32 * n)()
+            n = self._lib.lx_tokenizer_encode(self._h, raw, len(raw), int(add_special_tokens), buf, n)
+        return list(buf[:n])
+
+    def close(self):
+        if self._h:
+            self._lib.lx_tokenizer_free(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def unicode_normalize(text: str, form: str) -> str:
+    return load().lx_unicode_normalize(text.encode(), form.encode()).decode()

@@ -170,6 +170,12 @@ class ShardRuntime:
             return [int(x) for x in text.split()] if text.replace(" ", "").isdigit() else [ord(ch) % self.model.config.vocab_size for ch in text]
         return self.tokenizer.encode(text, add_special_tokens=add_special).ids
 
+    def router_tokenizer_json(self) -> str:
+        """The tokenizer file as a string, for the router to tokenise requests itself; empty when this runtime's `tokenize` does
+        more than run the tokenizer (image placeholders expand to feature tokens) or when there is no tokenizer file."""
+        plain = type(self).tokenize in (ShardRuntime.tokenize, EncoderRuntime.tokenize)
+        return self.tokenizer.to_str() if (plain and self.tokenizer is not None) else ""
+
     def tokenize_detailed(self, body: dict) -> list:
         text = body.get("inputs", "")
         if self.tokenizer is None:
@@ -1038,6 +1044,8 @@ class EncoderRuntime:
         if self.tokenizer is None:
             return [int(x) for x in text.split()] if text.replace(" ", "").isdigit() else [ord(ch) % self.model.config.vocab_size for ch in text]
         return self.tokenizer.encode(text, add_special_tokens=add_special).ids
+
+    router_tokenizer_json = ShardRuntime.router_tokenizer_json
 
     def tokenize_detailed(self, body: dict) -> list:
         if self.tokenizer is not None:          # character offsets: the router turns token classes into entity spans with them

@@ -26,7 +26,7 @@ import torch
 from .proto import load_pb
 from .tracing import TRACE_FLAG, TRACEPARENT_BYTES
 
-HELPER_TOKENIZE, HELPER_TOKENIZE_JSON, HELPER_CHAT_TEMPLATE = 100, 101, 102
+HELPER_TOKENIZE, HELPER_TOKENIZE_JSON, HELPER_CHAT_TEMPLATE, HELPER_TOKENIZER_FILE = 100, 101, 102, 103
 
 
 def _resolve_device(dev: torch.device) -> torch.device:
@@ -74,6 +74,9 @@ class FramedServer:
             return json.dumps(self.rt.tokenize_detailed(json.loads(payload.decode("utf-8")))).encode()
         if method == HELPER_CHAT_TEMPLATE:
             return self.rt.apply_chat_template(json.loads(payload.decode("utf-8"))).encode("utf-8")
+        if method == HELPER_TOKENIZER_FILE:
+            fn = getattr(self.rt, "router_tokenizer_json", None)
+            return (fn() if fn is not None else "").encode("utf-8")
         name = self.ids.get(method)
         if name is None:
             raise ValueError(f"unknown method id {method}")

@@ -170,6 +170,9 @@ def test_errors_and_misc_routes(stack):
     for name in ('lorax_batch_inference_success{method="prefill"}', 'lorax_batch_inference_success{method="decode"}',
                  "lorax_request_validation_duration_bucket", "lorax_request_max_new_tokens_bucket"):
         assert name in m, name
+    # requests were tokenised by the router's own workers, not by a call to shard 0
+    count = [l for l in m.splitlines() if l.startswith("lorax_router_tokenizations ")]
+    assert count and int(count[0].split()[1]) >= 2, count
     st, body, _ = _post(port, "/tokenize", {"inputs": "w7 w8"})
     assert st == 200 and [t["id"] for t in json.loads(body)] == [7, 8]
 
