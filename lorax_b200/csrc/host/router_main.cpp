@@ -14,6 +14,7 @@
 #include "openapi_gen.hpp"
 #include "http.hpp"
 #include "infer.hpp"
+#include "encoder_batcher.hpp"
 #include "grpc_client.hpp"
 #include "json.hpp"
 
@@ -159,8 +160,16 @@ class App {
         request_logger_(telemetry::parse_url(request_logger_url), telemetry::parse_url(request_logger_url).path) {
     infer_.set_tracer(&tracer_);
     infer_.start();
+    if (info_.supports_embeddings || info_.supports_classification) {
+      EncoderBatcher::Limits lim;
+      lim.max_input_length = cfg_.max_input_length;
+      lim.max_batch_tokens = std::max(cfg_.max_batch_prefill_tokens, cfg_.max_input_length);
+      lim.max_queued = cfg_.max_concurrent_requests ? cfg_.max_concurrent_requests * 4 : 4096;
+      encoder_ = std::make_unique<EncoderBatcher>(client_, lim, &metrics_);
+    }
   }
   void stop() {
+    encoder_.reset();
     infer_.stop();
     tracer_.shutdown();
     request_logger_.stop();
@@ -707,10 +716,18 @@ class App {
     if (in.is_array()) for (auto& s : in.items()) inputs.push_back(s.as_string());
     else inputs.push_back(in.as_string());
     try {
-      auto resp = client_->embed(one_shot_batch(inputs));
-      metrics_.inc("lorax_batch_inference_success", {{"method", "embed"}});
+      // every input joins the encoder queue; inputs of concurrent calls share shard batches
+      gen::EmbedResponse resp;
+      {
+        std::vector<std::future<EncoderBatcher::Result>> futs;
+        for (auto& in_text : inputs) futs.push_back(encoder_->submit(EncoderBatcher::Kind::Embed, in_text));
+        for (auto& f : futs) {
+          gen::Embedding e;
+          e.values = f.get().embedding;
+          resp.embeddings.push_back(std::move(e));
+        }
+      }
       metrics_.observe("lorax_request_input_count", (double)inputs.size());
-      if (!resp.errorMsg.empty()) throw ApiError(resp.errorMsg, "generation", 424);
       Value out = Value::object();
       if (openai) {
         Value data = Value::array();
@@ -734,6 +751,9 @@ class App {
       w.send(200, out.dump());
     } catch (const ApiError& e) {
       send_error(w, e);
+    } catch (const std::overflow_error& e) {
+      metrics_.inc("lorax_request_failure", {{"err", "overloaded"}});
+      send_error(w, ApiError(e.what(), "overloaded", 429));
     } catch (const std::exception& e) {
       send_error(w, ApiError(e.what(), "generation", 424));
     }
@@ -747,9 +767,12 @@ class App {
     else inputs.push_back(body["inputs"].as_string());
     try {
       auto t0 = Clock::now();
-      auto resp = client_->classify(one_shot_batch(inputs));
-      if (!resp.errorMsg.empty()) throw ApiError(resp.errorMsg, "generation", 424);
-      metrics_.inc("lorax_batch_inference_success", {{"method", "classify"}});
+      gen::ClassifyResponse resp;
+      {
+        std::vector<std::future<EncoderBatcher::Result>> futs;
+        for (auto& in_text : inputs) futs.push_back(encoder_->submit(EncoderBatcher::Kind::Classify, in_text));
+        for (auto& f : futs) resp.classify_prediction_lists.push_back(f.get().classes);
+      }
       metrics_.observe("lorax_request_input_count", (double)inputs.size());
       metrics_.observe("lorax_request_inference_duration", std::chrono::duration<double>(Clock::now() - t0).count());
       size_t n_out = 0;
@@ -778,6 +801,9 @@ class App {
       w.send(200, batch ? all.dump() : (all.size() ? all.items()[0].dump() : "[]"));
     } catch (const ApiError& e) {
       send_error(w, e);
+    } catch (const std::overflow_error& e) {
+      metrics_.inc("lorax_request_failure", {{"err", "overloaded"}});
+      send_error(w, ApiError(e.what(), "overloaded", 429));
     } catch (const std::exception& e) {
       send_error(w, ApiError(e.what(), "generation", 424));
     }
@@ -859,6 +885,7 @@ class App {
   Infer infer_;
   telemetry::Tracer tracer_;
   telemetry::BackgroundPoster request_logger_;
+  std::unique_ptr<EncoderBatcher> encoder_;       // queue + batching thread of /embed and /classify
   std::atomic<uint64_t> openai_id_{0};
 };
 

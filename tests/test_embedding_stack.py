@@ -185,3 +185,48 @@ def test_python_clients_classify_and_embed(emb_stack):
     a, b, e, ok, info = asyncio.run(run())
     assert a.entities == one.entities and [x.entities for x in b] == [x.entities for x in many]
     assert len(e.embeddings) == 64 and ok and info["model_id"] == "tiny-distilbert"
+
+
+def test_concurrent_inputs_share_shard_batches(emb_stack):
+    """Embed / classify inputs go through a queue and a batching thread in the router: while one batch is on the shard the
+    next one fills up, so concurrent HTTP calls end up in shared batches, each input still gets its own answer, and the queue
+    and batch metrics of the generation path are reported for them (the reference schedules these entries through its batching
+    task as well)."""
+    import concurrent.futures as cf
+    port, rt = emb_stack["port"], emb_stack["rt"]
+    sizes = []
+    real = rt.embed
+
+    def slow_embed(req):
+        sizes.append(len(req.batch.requests))
+        time.sleep(0.05)                      # long enough for the other calls to queue up behind the first batch
+        return real(req)
+    rt.embed = slow_embed
+    try:
+        texts = [f"w{i} w{i + 1} w{(i * 7) % 500}" for i in range(24)]
+        with cf.ThreadPoolExecutor(24) as pool:
+            outs = list(pool.map(lambda t: _post(port, "/embed", {"inputs": t}), texts))
+    finally:
+        rt.embed = real
+    assert all(st == 200 for st, _, _ in outs)
+    for t, (_, body, _) in zip(texts, outs):
+        want = rt.model.embed([rt.tokenize(t)])[0]
+        got = json.loads(body)["embeddings"]
+        assert max(abs(a - b) for a, b in zip(got, want)) < 1e-4
+    assert sum(sizes) == 24 and len(sizes) < 24 and max(sizes) > 1, sizes
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5) as r:
+        m = r.read().decode()
+    for name in ("lorax_batch_next_size_bucket", "lorax_request_queue_duration_bucket", 'lorax_queue_length{kind="encoder"}',
+                 'lorax_batch_inference_duration_bucket{method="embed"', "lorax_router_tokenizations"):
+        assert name in m, name
+    # a failing batch answers every input of it with an error and the route keeps working
+    def broken(req):
+        raise RuntimeError("encoder exploded")
+    rt.embed = broken
+    try:
+        st, body, _ = _post(port, "/embed", {"inputs": "w1"})
+    finally:
+        rt.embed = real
+    assert st == 424 and "error" in json.loads(body)
+    st, _, _ = _post(port, "/embed", {"inputs": "w1"})
+    assert st == 200
