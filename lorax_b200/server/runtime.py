@@ -718,12 +718,62 @@ class ShardRuntime:
 
 
 # ---------------------------------------------------------------------------------------------- construction
+def _token_text(tok) -> Optional[str]:
+    """`bos_token` / `eos_token` of a tokenizer_config.json: a string, or an AddedToken dictionary with `content`."""
+    if isinstance(tok, dict):
+        tok = tok.get("content")
+    return tok if isinstance(tok, str) and tok else None
+
+
+def llama_post_processor(tokenizer, tokenizer_config: dict):
+    """The template a Llama tokenizer gets from transformers at load time, which its tokenizer.json does not carry: BOS in front
+    when `add_bos_token` (default true), EOS behind when `add_eos_token` (default false).  The reference router applies the same
+    override (`router/src/main.rs:587-655`) for tokenizer classes LlamaTokenizer / LlamaTokenizerFast.  None when a token the
+    template needs is not in the vocabulary."""
+    from tokenizers import processors
+    add_bos = tokenizer_config.get("add_bos_token", True)
+    add_eos = tokenizer_config.get("add_eos_token", False)
+    bos, eos = _token_text(tokenizer_config.get("bos_token")), _token_text(tokenizer_config.get("eos_token"))
+    single, pair, special = [], [], []
+    for flag, tok in ((add_bos, bos), (add_eos, eos)):
+        if flag and (tok is None or tokenizer.token_to_id(tok) is None):
+            return None
+    if add_bos:
+        special.append((bos, tokenizer.token_to_id(bos)))
+        single.append(f"{bos}:0")
+        pair.append(f"{bos}:0")
+    single.append("$A:0")
+    pair.append("$A:0")
+    if add_eos:
+        special.append((eos, tokenizer.token_to_id(eos)))
+        single.append(f"{eos}:0")
+        pair.append(f"{eos}:0")
+    if add_bos:
+        pair.append(f"{bos}:1")
+    pair.append("$B:1")
+    if add_eos:
+        pair.append(f"{eos}:1")
+    return processors.TemplateProcessing(single=" ".join(single), pair=" ".join(pair), special_tokens=list(dict(special).items()))
+
+
 def load_tokenizer(model_dir: str):
     path = os.path.join(model_dir, "tokenizer.json")
-    if os.path.exists(path):
-        from tokenizers import Tokenizer
-        return Tokenizer.from_file(path)
-    return None
+    if not os.path.exists(path):
+        return None
+    from tokenizers import Tokenizer
+    tok = Tokenizer.from_file(path)
+    cfg_path = os.path.join(model_dir, "tokenizer_config.json")
+    if os.path.exists(cfg_path):
+        try:
+            with open(cfg_path) as f:
+                tcfg = json.load(f)
+        except (OSError, ValueError):
+            tcfg = {}
+        if tcfg.get("tokenizer_class") in ("LlamaTokenizer", "LlamaTokenizerFast"):
+            pp = llama_post_processor(tok, tcfg)
+            if pp is not None:
+                tok.post_processor = pp
+    return tok
 
 
 class Seq2SeqRuntime(ShardRuntime):

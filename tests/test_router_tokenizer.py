@@ -100,7 +100,6 @@ def sentencepiece_bpe(legacy: bool):
     special = ["<unk>", "<s>", "</s>"] + [f"<0x{b:02X}>" for b in range(256)]
     if legacy:           # Llama-2 / Mistral: the normaliser writes the metaspace, no pre-tokenizer
         tok.normalizer = normalizers.Sequence([normalizers.Prepend("▁"), normalizers.Replace(" ", "▁")])
-        train_pre = None
     else:
         tok.pre_tokenizer = pre_tokenizers.Metaspace(replacement="▁", prepend_scheme="first", split=False)
     trainer = trainers.BpeTrainer(vocab_size=700, special_tokens=special, show_progress=False)
@@ -215,3 +214,27 @@ def test_pool_serves_concurrent_callers(tmp_path):
     [t.start() for t in threads]
     [t.join() for t in threads]
     assert got == want
+
+
+def test_llama_tokenizer_class_gets_the_bos_template_on_both_sides(tmp_path):
+    """A Llama tokenizer file carries no post-processor; transformers adds BOS (and EOS when configured) at load time and the
+    reference router does the same for tokenizer classes LlamaTokenizer / LlamaTokenizerFast (router/src/main.rs:587-655).  The
+    shard applies the override when it loads the file, and the router tokenises from the shard's copy."""
+    from lorax_b200.server.runtime import load_tokenizer
+    tok = sentencepiece_bpe(legacy=True)
+    state = json.loads(tok.to_str())
+    state["post_processor"] = None
+    mdir = tmp_path / "m"
+    mdir.mkdir()
+    (mdir / "tokenizer.json").write_text(json.dumps(state))
+    (mdir / "tokenizer_config.json").write_text(json.dumps({"tokenizer_class": "LlamaTokenizerFast", "bos_token": {"content": "<s>"},
+                                                            "eos_token": "</s>", "add_eos_token": True}))
+    loaded = load_tokenizer(str(mdir))
+    bos, eos = loaded.token_to_id("<s>"), loaded.token_to_id("</s>")
+    ids = loaded.encode("hello world").ids
+    assert ids[0] == bos and ids[-1] == eos and loaded.encode("hello world", add_special_tokens=False).ids == ids[1:-1]
+    (tmp_path / "served.json").write_text(loaded.to_str())
+    mine = RouterTokenizer(str(tmp_path / "served.json"))
+    assert mine.encode("hello world") == ids
+    (mdir / "tokenizer_config.json").write_text(json.dumps({"tokenizer_class": "GPT2Tokenizer", "bos_token": "<s>"}))
+    assert load_tokenizer(str(mdir)).encode("hello world").ids == ids[1:-1]
