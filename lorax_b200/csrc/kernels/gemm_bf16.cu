@@ -454,6 +454,12 @@ struct LoraUnit {
   int pad_;
 };
 static_assert(sizeof(LoraUnit) == 32, "two 16-byte words per unit");
+// The units of one expand stage travel in the stage itself, behind its tiles: the producer warp builds the list, the MMA thread
+// reads what to issue after the stage's barrier.  `last` closes the run of expand stages of a tile.
+struct LoraStageHeader {
+  LoraUnit units[8];
+  int nu, last, pad_[2];
+};
 constexpr int kLoraListCap = 256;       // units a list holds; it is worked off whenever it holds 128 or more
 LX_DEVICE int lora_build_units(const GemmParams& p, const LoraEnt* ents, int lt0, int j0, int jlim, LoraUnit* list, int n, bool& ended) {
   const int lane = threadIdx.x & 31;
@@ -492,6 +498,20 @@ LX_DEVICE int lora_prebuild_units(const GemmParams& p, const LoraEnt* ents, int 
   return n;
 }
 
+// Pulls the B_cat rows that feature tile `ta` needs for the units of `list` into L2 (whole warp; adapter weights, which no kernel
+// of a step writes, so this may run before the kernel in front has drained).
+LX_DEVICE void lora_prefetch_b(const GemmParams& p, const LoraUnit* list, int n, int ta) {
+  const int rows = min(kBM, p.a_rows - ta * kBM);
+  for (int u = threadIdx.x & 31; u < n; u += 32) {
+    const LoraUnit q = list[u];
+    if ((q.img & 3) == 0) {
+      const int r = (q.rclass + 1) * 16;
+      const char* src = reinterpret_cast<const char*>(p.lora_arena) + (long long)q.boff * 16 + (long long)ta * kBM * r * 2;
+      asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)(rows * r * 2)) : "memory");
+    }
+  }
+}
+
 // B_cat of every slot through one map per rank class: dims {rank, N, arena / 16 bytes} with strides {2 * rank, 16} bytes, box
 // {16, 128, 1}, 32-byte swizzle.  The third coordinate is where the slot's B_cat starts, so one descriptor, passed as a kernel
 // parameter, serves every adapter: nothing to fetch from memory per slot and nothing to fence.
@@ -513,7 +533,8 @@ struct GemmSmem {
   static constexpr int kBarrierBytes = 256;
   // entry table, two unit lists, groups-before-entry prefix (shrink units)
   static constexpr int kShrinkBytes = LORA ? (kLoraMaxEntries + 8) * 2 : 0;
-  static constexpr int kEntBytes = LORA ? kLoraMaxEntries * (int)sizeof(LoraEnt) + 2 * kLoraListCap * 32 + kShrinkBytes : 0;
+  static constexpr int kEntBytes = LORA ? kLoraMaxEntries * (int)sizeof(LoraEnt) + kLoraListCap * 32 + kShrinkBytes : 0;
+  static_assert(!LORA || kStageBytes - kUnits * kLoraUnitBytes >= (int)sizeof(LoraStageHeader), "room for the unit list behind the tiles of a stage");
   static constexpr int kEpiBytes = 4 * 32 * 32 * 2;     // per epilogue warp, 32 tokens x 32 features: the transposing store of the weights-on-M path
   static constexpr int kTotal = STAGES * kStageBytes + kBarrierBytes + kEntBytes + kEpiBytes + 1024;  // +1024 for manual alignment
 };
@@ -537,9 +558,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_base_slot + 2));
   int* n_live = reinterpret_cast<int*>(tmem_base_slot + 3);             // live entries of the LoRA table
   LoraEnt* ents = reinterpret_cast<LoraEnt*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes);
-  LoraUnit* ulist_p = reinterpret_cast<LoraUnit*>(ents + kLoraMaxEntries);      // producer warp's expand units
-  LoraUnit* ulist_m = ulist_p + kLoraListCap;                                   // MMA warp's
-  unsigned short* gstart = reinterpret_cast<unsigned short*>(ulist_m + kLoraListCap);   // [entries + 1] four-row groups before an entry
+  LoraUnit* ulist_p = reinterpret_cast<LoraUnit*>(ents + kLoraMaxEntries);      // producer warp's expand units of the current token tile
+  unsigned short* gstart = reinterpret_cast<unsigned short*>(ulist_p + kLoraListCap);   // [entries + 1] four-row groups before an entry
   __nv_bfloat16* epi_stage = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * S::kStageBytes + S::kBarrierBytes + S::kEntBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -551,7 +571,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const int num_tiles = tiles_a * tiles_b;
   const int kblocks = (p.K + kBK - 1) / kBK;
   const bool lora = LORA && p.lora_tiles != nullptr;
-  int pre_tb = -1, pre_n = 0;             // token tile whose unit list this warp (producer or MMA) has built ahead of its first tile
+  int pre_tb = -1, pre_n = 0;             // token tile whose unit list the producer warp has built ahead of its first tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -584,27 +604,17 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       load_lora_entries(p, ents, n_live);
       __syncthreads();
       if (p.lora_inline_shrink && warp == 2) lora_group_prefix(p, ents, gstart);
-      if (warp < 2 && !(p.lora_skip & 2)) {
-        // the producer warp and the MMA warp build the unit list of their first tile now, under the tail of the kernel in front;
-        // the producer also pulls that tile's B_cat rows (adapter weights, which no kernel of the step writes) into L2
+      if (warp == 0 && !(p.lora_skip & 2)) {
+        // the producer warp builds the unit list of its first tile now, under the tail of the kernel in front, and pulls that
+        // tile's B_cat rows (adapter weights, which no kernel of the step writes) into L2
         GemmWorkIter<BN> it0(p, num_tiles, kblocks);
         GemmWork w0;
         if (it0.next(w0) && w0.kb0 == 0) {
           const int ta0 = p.b_fastest ? w0.tile / tiles_b : w0.tile % tiles_a;
           const int tb0 = p.b_fastest ? w0.tile % tiles_b : w0.tile / tiles_a;
-          const int n0 = lora_prebuild_units(p, ents, *n_live, tb0 * p.bn, tb0 * p.bn + p.umma_n, warp == 0 ? ulist_p : ulist_m);
+          const int n0 = lora_prebuild_units(p, ents, *n_live, tb0 * p.bn, tb0 * p.bn + p.umma_n, ulist_p);
           if (n0 >= 0) { pre_tb = tb0; pre_n = n0; }
-          if (warp == 0 && n0 > 0 && p.lora_arena_maps) {
-            const int rows = min(kBM, p.a_rows - ta0 * kBM);
-            for (int u = lane; u < n0; u += 32) {
-              const LoraUnit q = ulist_p[u];
-              if ((q.img & 3) == 0) {
-                const int r = (q.rclass + 1) * 16;
-                const char* src = reinterpret_cast<const char*>(p.lora_arena) + (long long)q.boff * 16 + (long long)ta0 * kBM * r * 2;
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"((uint32_t)(rows * r * 2)) : "memory");
-              }
-            }
-          }
+          if (n0 > 0 && p.lora_arena_maps) lora_prefetch_b(p, ulist_p, n0, ta0);
         }
       }
       __syncthreads();
@@ -622,12 +632,26 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     uint32_t phase = 0;
     bool ok = true;
     int list_tb = pre_tb, list_n = pre_n;  // token tile whose complete unit list sits in ulist_p
+    bool first_tile = pre_tb >= 0;         // its B_cat rows were prefetched before the dependent-launch wait
     bool shrink_seen = false;
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
     GemmWork w;
     while (it.next(w)) {
       const int ta = p.b_fastest ? w.tile / tiles_b : w.tile % tiles_a;
       const int tb = p.b_fastest ? w.tile % tiles_b : w.tile / tiles_a;
+      if constexpr (LORA) {
+        if (lora && w.kb0 == 0 && !(p.lora_skip & 2)) {
+          // the whole warp, while the ring still holds the stages of the tile before: this tile's unit list (kept while the token
+          // tile stays the same) and its B_cat rows on their way into L2 under the base k-blocks
+          if (list_tb != tb) {
+            const int n0 = lora_prebuild_units(p, ents, *n_live, tb * p.bn, tb * p.bn + p.umma_n, ulist_p);
+            list_tb = n0 >= 0 ? tb : -1;
+            list_n = n0 >= 0 ? n0 : 0;
+          }
+          if (list_tb == tb && list_n > 0 && p.lora_arena_maps && !first_tile) lora_prefetch_b(p, ulist_p, list_n, ta);
+          first_tile = false;
+        }
+      }
       if (lane == 0 && ok) {
         for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
@@ -668,70 +692,85 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             shrink_seen = true;
           }
           constexpr int kU = S::kUnits;
-          const bool cached = (list_tb == tb);
-          int n = cached ? list_n : 0;
-          bool ended = false;
-          int flushes = 0;
-          for (int lt0 = cached ? 0 : lora_first_entry(ents, *n_live, j0); ok && (cached || (!ended && lt0 < p.lora_num_tiles)); lt0 += 32) {
-            if (!cached) {
-              n = lora_build_units(p, ents, lt0, j0, jlim, ulist_p, n, ended);
-              const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
-              if (n < 128 && !last) continue;
-              if (last && flushes == 0) { list_tb = tb; list_n = n; }        // the whole tile in one piece: the next tile reuses it
-              ++flushes;
-            }
-            for (int base = 0; ok && base < n; base += kU) {
-              const int nu = min(kU, n - base);
-              if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
-                if (lane == 0) {
-                  report_status(p.status, kTimeoutEmptyBarrier, w.tile);
-                  *abort_flag = 1;
-                }
-                ok = false;
-                break;
+          // One expand stage: up to kU units, one lane each; the units are written behind the stage's tiles for the MMA thread.
+          auto send_stage = [&](int base, int nu, bool last) -> bool {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) {
+              if (lane == 0) {
+                report_status(p.status, kTimeoutEmptyBarrier, w.tile);
+                *abort_flag = 1;
               }
-              uint8_t* sa = tiles + stage * S::kStageBytes;
-              if (lane == 0) mbar_expect_tx(&full_bar[stage], (uint32_t)(nu * kLoraUnitBytes));
-              __syncwarp();
-              LoraUnit q{};
-              if (lane < nu) q = ulist_p[base + lane];
-              // image slices of consecutive entries are consecutive in memory: one copy serves the stage
-              const int y0 = __shfl_sync(0xffffffffu, q.img, 0);
-              const bool in_row = lane >= nu || (q.img == y0 + 4 * lane && (q.img & 3) == 0);
-              const bool one_copy = __all_sync(0xffffffffu, in_row);
-              if (lane < nu) {
-                if (p.lora_arena_maps) {
-                  tma_load_3d(sa + lane * kLoraBTileBytes, &bmaps.m[q.rclass], &full_bar[stage], (q.img & 3) * 16, i0, q.boff);
-                } else {
-                  const CUtensorMap* mb = p.lora_slot_tmaps + (long long)q.slot * p.lora_maps_per_slot + p.lora_map_b;
-                  if (p.lora_fence_maps) tensormap_fence_acquire_g(mb);
-                  tma_load_3d(sa + lane * kLoraBTileBytes, mb, &full_bar[stage], (q.img & 3) * 16, i0, p.lora_layer);
-                }
-                const long long img = (img_part + (long long)(q.img & 3) * p.lora_num_tiles + (q.img >> 2)) * kLoraSliceElems;
-                if (!one_copy) {
-                  bulk_load_1d(sa + kU * kLoraBTileBytes + lane * kLoraSliceBytes, p.lora_vimg + img, kLoraSliceBytes, &full_bar[stage]);
-                } else if (lane == 0) {
-                  bulk_load_1d(sa + kU * kLoraBTileBytes, p.lora_vimg + img, (uint32_t)(nu * kLoraSliceBytes), &full_bar[stage]);
-                }
-              }
-              if (++stage == STAGES) { stage = 0; phase ^= 1; }
+              return false;
             }
-            if (cached) break;
-            n = 0;
+            uint8_t* sa = tiles + stage * S::kStageBytes;
+            LoraStageHeader* hdr = reinterpret_cast<LoraStageHeader*>(sa + kU * kLoraUnitBytes);
+            LoraUnit q{};
+            if (lane < nu) {
+              q = ulist_p[base + lane];
+              hdr->units[lane] = q;
+            }
+            if (lane == 0) { hdr->nu = nu; hdr->last = last ? 1 : 0; }
+            fence_proxy_async_smem();          // the stage's bytes are written by bulk copies at other times
+            __syncwarp();
+            if (lane == 0) mbar_expect_tx(&full_bar[stage], (uint32_t)(nu * kLoraUnitBytes));
+            __syncwarp();
+            // image slices of consecutive entries are consecutive in memory: one copy serves the stage
+            const int y0 = __shfl_sync(0xffffffffu, q.img, 0);
+            const bool in_row = lane >= nu || (q.img == y0 + 4 * lane && (q.img & 3) == 0);
+            const bool one_copy = __all_sync(0xffffffffu, in_row);
+            if (lane < nu) {
+              if (p.lora_arena_maps) {
+                tma_load_3d(sa + lane * kLoraBTileBytes, &bmaps.m[q.rclass], &full_bar[stage], (q.img & 3) * 16, i0, q.boff);
+              } else {
+                const CUtensorMap* mb = p.lora_slot_tmaps + (long long)q.slot * p.lora_maps_per_slot + p.lora_map_b;
+                if (p.lora_fence_maps) tensormap_fence_acquire_g(mb);
+                tma_load_3d(sa + lane * kLoraBTileBytes, mb, &full_bar[stage], (q.img & 3) * 16, i0, p.lora_layer);
+              }
+              const long long img = (img_part + (long long)(q.img & 3) * p.lora_num_tiles + (q.img >> 2)) * kLoraSliceElems;
+              if (!one_copy) {
+                bulk_load_1d(sa + kU * kLoraBTileBytes + lane * kLoraSliceBytes, p.lora_vimg + img, kLoraSliceBytes, &full_bar[stage]);
+              } else if (lane == 0) {
+                bulk_load_1d(sa + kU * kLoraBTileBytes, p.lora_vimg + img, (uint32_t)(nu * kLoraSliceBytes), &full_bar[stage]);
+              }
+            }
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            return true;
+          };
+          // The stages of `n` listed units; the final one is marked when it `closes` the tile (an empty stage if there is no unit).
+          auto send_run = [&](int n, bool closes) {
+            if (n == 0 && closes) ok = send_stage(0, 0, true);
+            for (int base = 0; ok && base < n; base += kU) ok = send_stage(base, min(kU, n - base), closes && base + kU >= n);
+          };
+          if (!ok) {
+          } else if (list_tb == tb) {
+            send_run(list_n, true);
+          } else {
+            // more units than the list holds: built and sent in pieces
+            int n = 0;
+            bool ended = false;
+            for (int lt0 = lora_first_entry(ents, *n_live, j0); ok; lt0 += 32) {
+              bool last = true;
+              if (lt0 < p.lora_num_tiles) {
+                n = lora_build_units(p, ents, lt0, j0, jlim, ulist_p, n, ended);
+                last = ended || lt0 + 32 >= p.lora_num_tiles;
+                if (n < 128 && !last) continue;
+              }
+              send_run(n, last);
+              if (last) break;
+              n = 0;
+            }
           }
         }
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // Lane 0 issues every MMA; the whole warp builds the unit list of a tile's LoRA stages.
+    // Lane 0 issues every MMA.
     const uint32_t idesc = make_idesc(kBM, (uint32_t)p.umma_n, kFmtBF16, kFmtBF16);
     int stage = 0;
     uint32_t phase = 0;
     int acc = 0;
     uint32_t acc_phase[2] = {0, 0};
     bool ok = true;
-    int list_tb = pre_tb, list_n = pre_n;
     GemmWorkIter<BN> it(p, num_tiles, kblocks);
     GemmWork w;
     while (it.next(w)) {
@@ -764,51 +803,35 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         }
       }
       if constexpr (LORA) {
-        if (lora && kb0 == 0 && !(p.lora_skip & 2)) {
-          __syncwarp();
-          ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+        if (lora && kb0 == 0 && !(p.lora_skip & 2) && lane == 0) {
+          // the tile's expand stages: each carries its units; the one marked `last` ends the run (there is always one)
+          constexpr int kU = S::kUnits;
           const int tb = p.b_fastest ? w.tile % tiles_b : w.tile / tiles_a;
-          const int j0 = tb * p.bn, jlim = j0 + p.umma_n;
-          const bool cached = (list_tb == tb);
-          int n = cached ? list_n : 0;
-          bool ended = false;
-          int flushes = 0;
-          for (int lt0 = cached ? 0 : lora_first_entry(ents, *n_live, j0); ok && (cached || (!ended && lt0 < p.lora_num_tiles)); lt0 += 32) {
-            if (!cached) {
-              n = lora_build_units(p, ents, lt0, j0, jlim, ulist_m, n, ended);
-              const bool last = ended || lt0 + 32 >= p.lora_num_tiles;
-              if (n < 128 && !last) continue;
-              if (last && flushes == 0) { list_tb = tb; list_n = n; }
-              ++flushes;
+          const int j0 = tb * p.bn;
+          bool more = ok;
+          while (more) {
+            if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
+              report_status(p.status, kTimeoutFullBarrier, w.tile);
+              *abort_flag = 1;
+              ok = false;
+              break;
             }
-            if (lane == 0) {
-              constexpr int kU = S::kUnits;
-              for (int base = 0; ok && base < n; base += kU) {
-                if (!mbar_wait(&full_bar[stage], phase, abort_flag)) {
-                  report_status(p.status, kTimeoutFullBarrier, w.tile);
-                  *abort_flag = 1;
-                  ok = false;
-                  break;
-                }
-                tc_fence_after();
-                const uint32_t sa = smem_u32(tiles + stage * S::kStageBytes);
-                const int nu = min(kU, n - base);
-                for (int u = 0; u < nu; ++u) {
-                  const LoraUnit q = ulist_m[base + u];
-                  const int c0 = q.c0, c1 = q.c1;
-                  const uint64_t da = make_desc_k_sw32(sa + (uint32_t)(u * kLoraBTileBytes));
-                  const uint64_t db = make_desc_k_sw32(sa + (uint32_t)(kU * kLoraBTileBytes + u * kLoraSliceBytes + (c0 - q.w0) * 32));
-                  if (!(p.lora_skip & 32))
-                    umma_f16_ss(tmem_d + (uint32_t)(c0 - j0), da, db, make_idesc(kBM, (uint32_t)(c1 - c0), kFmtBF16, kFmtBF16), 1u);
-                }
-                tc_commit(&empty_bar[stage]);
-                if (++stage == STAGES) { stage = 0; phase ^= 1; }
-              }
+            tc_fence_after();
+            uint8_t* sp = tiles + stage * S::kStageBytes;
+            const LoraStageHeader* hdr = reinterpret_cast<const LoraStageHeader*>(sp + kU * kLoraUnitBytes);
+            const uint32_t sa = smem_u32(sp);
+            const int nu = min(hdr->nu, kU);
+            more = hdr->last == 0;
+            for (int u = 0; u < nu; ++u) {
+              const LoraUnit q = hdr->units[u];
+              const int c0 = q.c0, c1 = q.c1;
+              const uint64_t da = make_desc_k_sw32(sa + (uint32_t)(u * kLoraBTileBytes));
+              const uint64_t db = make_desc_k_sw32(sa + (uint32_t)(kU * kLoraBTileBytes + u * kLoraSliceBytes + (c0 - q.w0) * 32));
+              if (!(p.lora_skip & 32))
+                umma_f16_ss(tmem_d + (uint32_t)(c0 - j0), da, db, make_idesc(kBM, (uint32_t)(c1 - c0), kFmtBF16, kFmtBF16), 1u);
             }
-            __syncwarp();                                            // the list is rebuilt by every lane
-            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-            if (cached) break;
-            n = 0;
+            tc_commit(&empty_bar[stage]);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
           }
         }
       }

@@ -435,11 +435,15 @@ def test_lora_tiled_tensor_core(nat, T, max_rows):
     assert torch.equal(y[untouched], y_ref[untouched])
 
 
-@pytest.mark.parametrize("T,K,parts,ranks", [(40, 1024, [512, 128, 128], [16, 48, 64, 32]),
-                                             (256, 4096, [1024, 256, 256], [16, 16, 32, 64]),
-                                             (700, 2048, [768, 768], [16, 32, 16, 64]),
-                                             (300, 14336, [512], [16, 64, 32, 16])])
-def test_gemm_with_lora_in_the_same_launch(nat, T, K, parts, ranks):
+@pytest.mark.parametrize("T,K,parts,ranks,layout", [(40, 1024, [512, 128, 128], [16, 48, 64, 32], "blocks"),
+                                                    (256, 4096, [1024, 256, 256], [16, 16, 32, 64], "blocks"),
+                                                    (700, 2048, [768, 768], [16, 32, 16, 64], "blocks"),
+                                                    (300, 14336, [512], [16, 64, 32, 16], "blocks"),
+                                                    # a prefill-sized step: every CTA walks several token tiles and rebuilds its unit list
+                                                    (2304, 2048, [1536, 768], [16, 32, 16, 64], "runs"),
+                                                    # another adapter on every row: more expand units per token tile than the list holds
+                                                    (200, 1024, [512, 256], [16, 64, 32, 64], "alternating")])
+def test_gemm_with_lora_in_the_same_launch(nat, T, K, parts, ranks, layout):
     """Shrink items, base tiles and expand UMMAs in ONE launch of the GEMM kernel against fp32 PyTorch:
     x W^T + b + (x A_slot^T) B_slot^T per row, several adapters and ranks, base-model rows in between, rows of one adapter
     crossing 16-row and 256-row boundaries, rank 48 (a part that straddles two 128-row chunks of A_cat), two calls in a row."""
@@ -461,11 +465,20 @@ def test_gemm_with_lora_in_the_same_launch(nat, T, K, parts, ranks):
         nat.lora_encode_tmap(tm_host[(s * 2 * G + 0) * 128:], arena.data_ptr() + bases[s] * 2, K, nparts * r, r * layer_units, L)
         nat.lora_encode_tmap_b(tm_host[(s * 2 * G + G) * 128:], arena.data_ptr() + (bases[s] + r * nparts * K) * 2, r, N, r * layer_units, L)
     tmaps = tm_host.cuda()
-    seg = [(-1, 3), (0, 5), (2, T // 3), (1, 1), (3, T // 4), (-1, 2)]
-    rows = []
-    for sl, n in seg:
-        rows += [sl] * n
-    rows = (rows + [1] * T)[:T]
+    if layout == "blocks":
+        seg = [(-1, 3), (0, 5), (2, T // 3), (1, 1), (3, T // 4), (-1, 2)]
+        rows = []
+        for sl, n in seg:
+            rows += [sl] * n
+        rows = (rows + [1] * T)[:T]
+    elif layout == "runs":          # runs of 1 to 90 rows, adapters and base-model rows in turn
+        g = torch.Generator().manual_seed(T)
+        rows = []
+        while len(rows) < T:
+            rows += [int(torch.randint(-1, len(ranks), (1,), generator=g))] * int(torch.randint(1, 91, (1,), generator=g))
+        rows = rows[:T]
+    else:
+        rows = [(i % (len(ranks) + 1)) - 1 for i in range(T)]
     tl = ref.build_lora_tiles(rows, 32)
     tiles = torch.cat([torch.tensor(tl, device="cuda", dtype=torch.int32).view(-1, 4), torch.full((9, 4), -1, device="cuda", dtype=torch.int32)])
     n0 = parts[0] if nparts > 1 else N
