@@ -257,8 +257,12 @@ struct GemmWorkIter {
 // the next eight blocks are in flight while the current eight are multiplied.  The warps' partial sums meet in shared memory
 // and go straight into the operand images the expand stages read.  Units are dealt round-robin over the CTAs of the launch;
 // a CTA counts itself in when its units are done (see lora_sync).
-constexpr int kShrinkRows = 8;          // rows of x per unit (the N of the mma)
+constexpr int kShrinkRows = 8;          // rows of x per mma (its N); a unit has one such group, or four of them in long steps
+// Rows of x per shrink unit.  Decode-sized steps have few rows per adapter: one group of eight.  Long steps (prefill) have whole
+// entries of 32 rows: four groups share every load of the A_cat block, which halves the bytes a unit of work moves.
+LX_DEVICE int lora_shrink_unit_rows(const GemmParams& p) { return p.lora_T > 512 ? 4 * kShrinkRows : kShrinkRows; }
 LX_DEVICE void lora_group_prefix(const GemmParams& p, const LoraEnt* ents, unsigned short* gstart) {
+  const int unit_rows = lora_shrink_unit_rows(p);
   const int lane = threadIdx.x & 31;
   int run = 0;
   for (int lt0 = 0; lt0 < p.lora_num_tiles; lt0 += 32) {
@@ -266,7 +270,7 @@ LX_DEVICE void lora_group_prefix(const GemmParams& p, const LoraEnt* ents, unsig
     int cnt = 0;
     if (lt < p.lora_num_tiles) {
       const LoraEnt e = ents[lt];
-      if (e.slot >= 0 && e.r > 0) cnt = (e.nrows + kShrinkRows - 1) / kShrinkRows;
+      if (e.slot >= 0 && e.r > 0) cnt = (e.nrows + unit_rows - 1) / unit_rows;
     }
     int incl = cnt;
 #pragma unroll
@@ -281,11 +285,12 @@ LX_DEVICE void lora_group_prefix(const GemmParams& p, const LoraEnt* ents, unsig
 }
 
 struct ShrinkUnit {
-  int lt, t0, nt, r, j;          // entry, first row, rows (<= 8), rank of the slot, first of the unit's 16 rank rows (part * r + i)
+  int lt, t0, nt, r, j;          // entry, first row, rows (<= 8 or 32), rank of the slot, first of the unit's 16 rank rows (part * r + i)
   const __nv_bfloat16* a;        // A_cat row j
 };
 
-LX_DEVICE bool decode_shrink_unit(const GemmParams& p, const LoraEnt* ents, const unsigned short* gstart, int u, int nblk, ShrinkUnit& s) {
+LX_DEVICE bool decode_shrink_unit(const GemmParams& p, const LoraEnt* ents, const unsigned short* gstart, int u, int nblk, int unit_rows,
+                                  ShrinkUnit& s) {
   const int g = u / nblk, jb = u - g * nblk;
   int lo = 0, hi = p.lora_num_tiles;                     // last entry with gstart <= g
   while (hi - lo > 1) {
@@ -295,10 +300,10 @@ LX_DEVICE bool decode_shrink_unit(const GemmParams& p, const LoraEnt* ents, cons
   const LoraEnt e = ents[lo];
   if (e.slot < 0 || e.r <= 0) return false;
   const int sub = g - (int)gstart[lo];
-  if (sub * kShrinkRows >= e.nrows || jb * 16 >= e.r * p.lora_nparts) return false;
+  if (sub * unit_rows >= e.nrows || jb * 16 >= e.r * p.lora_nparts) return false;
   s.lt = lo;
-  s.t0 = e.row0 + sub * kShrinkRows;
-  s.nt = min(kShrinkRows, e.row0 + e.nrows - s.t0);
+  s.t0 = e.row0 + sub * unit_rows;
+  s.nt = min(unit_rows, e.row0 + e.nrows - s.t0);
   s.r = e.r;
   s.j = jb * 16;
   s.a = p.lora_arena + (long long)e.boff * 8 + (long long)e.r * (p.lora_off_a - p.lora_off_b) + (long long)s.j * p.K;
@@ -311,37 +316,46 @@ LX_DEVICE void mma_bf16_16x8x16(float* c, uint32_t a0, uint32_t a1, uint32_t a2,
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-constexpr int kSB = 8;                  // K blocks of a warp per batch of loads
-// The loads of kSB K blocks of this warp (blocks ewarp + 4 * (kSB * batch + i)): rank rows g and g + 8, row g of x.
-LX_DEVICE void shrink_loads(const GemmParams& p, const ShrinkUnit& s, int batch, int ewarp, int lane, uint4* ra, uint4* rb, uint4* rx) {
+// The loads of SB K blocks of this warp (blocks ewarp + 4 * (SB * batch + i)): rank rows g and g + 8 of A_cat, row g of each of
+// the unit's NG groups of x.  NG * SB stays 8 or 16 so that the loads in flight fill the same registers either way.
+template <int NG, int SB>
+LX_DEVICE void shrink_loads(const GemmParams& p, const ShrinkUnit& s, int batch, int ewarp, int lane, uint4* ra, uint4* rb, uint4 (*rx)[SB]) {
   const int K8 = p.K >> 3;
   const int g = lane >> 2, t = lane & 3;
   const uint4* a0 = reinterpret_cast<const uint4*>(s.a + (long long)g * p.K);
   const uint4* a1 = reinterpret_cast<const uint4*>(s.a + (long long)(g + 8) * p.K);
-  const uint4* xr = reinterpret_cast<const uint4*>(p.lora_x + (long long)(s.t0 + g) * p.lora_ldx);
 #pragma unroll
-  for (int i = 0; i < kSB; ++i) {
-    const int kk = (ewarp + 4 * (kSB * batch + i)) * 4 + t;          // 16-byte index inside the row
+  for (int i = 0; i < SB; ++i) {
+    const int kk = (ewarp + 4 * (SB * batch + i)) * 4 + t;          // 16-byte index inside the row
     const bool in = kk < K8;
     ra[i] = in ? __ldg(a0 + kk) : make_uint4(0, 0, 0, 0);
     rb[i] = in ? __ldg(a1 + kk) : make_uint4(0, 0, 0, 0);
-    rx[i] = (in && g < s.nt) ? xr[kk] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int q = 0; q < NG; ++q) {
+      const int row = q * kShrinkRows + g;
+      const uint4* xr = reinterpret_cast<const uint4*>(p.lora_x + (long long)(s.t0 + row) * p.lora_ldx);
+      rx[q][i] = (in && row < s.nt) ? xr[kk] : make_uint4(0, 0, 0, 0);
+    }
   }
 }
 
-LX_DEVICE void lora_shrink_units(const GemmParams& p, const LoraEnt* ents, const unsigned short* gstart, float* red, int ewarp, int lane) {
+template <int NG, int SB>
+LX_DEVICE void lora_shrink_units_t(const GemmParams& p, const LoraEnt* ents, const unsigned short* gstart, float* red, int ewarp, int lane) {
   const int tid4 = ewarp * 32 + lane;
   const int nblk = (p.lora_max_r + 15) >> 4;
   const int U = (int)gstart[p.lora_num_tiles] * nblk;
-  const int nbatch = ((p.K + 31) / 32 + 4 * kSB - 1) / (4 * kSB);    // batches of kSB blocks per warp
+  const int nbatch = ((p.K + 31) / 32 + 4 * SB - 1) / (4 * SB);    // batches of SB blocks per warp
+  constexpr int kUnitRows = NG * kShrinkRows;
   ShrinkUnit cur;
   int u = (int)blockIdx.x;
-  while (u < U && !decode_shrink_unit(p, ents, gstart, u, nblk, cur)) u += (int)gridDim.x;
+  while (u < U && !decode_shrink_unit(p, ents, gstart, u, nblk, kUnitRows, cur)) u += (int)gridDim.x;
   if (u < U) {
     int b = 0, par = 0;
-    uint4 ra[kSB], rb[kSB], rx[kSB];
-    shrink_loads(p, cur, 0, ewarp, lane, ra, rb, rx);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    uint4 ra[SB], rb[SB], rx[NG][SB];
+    shrink_loads<NG, SB>(p, cur, 0, ewarp, lane, ra, rb, rx);
+    float acc[NG][4];
+#pragma unroll
+    for (int q = 0; q < NG; ++q) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
     while (true) {
       // the batch after this one: the next of the unit, or the first of the CTA's next unit
       ShrinkUnit nxt = cur;
@@ -350,60 +364,77 @@ LX_DEVICE void lora_shrink_units(const GemmParams& p, const LoraEnt* ents, const
       if (nb == nbatch) {
         nb = 0;
         nu = u + (int)gridDim.x;
-        while (nu < U && !decode_shrink_unit(p, ents, gstart, nu, nblk, nxt)) nu += (int)gridDim.x;
+        while (nu < U && !decode_shrink_unit(p, ents, gstart, nu, nblk, kUnitRows, nxt)) nu += (int)gridDim.x;
         more = nu < U;
       }
-      uint4 na[kSB], nbv[kSB], nx[kSB];
-      if (more) shrink_loads(p, nxt, nb, ewarp, lane, na, nbv, nx);
+      uint4 na[SB], nbv[SB], nx[NG][SB];
+      if (more) shrink_loads<NG, SB>(p, nxt, nb, ewarp, lane, na, nbv, nx);
 #pragma unroll
-      for (int i = 0; i < kSB; ++i) {
-        mma_bf16_16x8x16(acc, ra[i].x, rb[i].x, ra[i].y, rb[i].y, rx[i].x, rx[i].y);
-        mma_bf16_16x8x16(acc, ra[i].z, rb[i].z, ra[i].w, rb[i].w, rx[i].z, rx[i].w);
+      for (int i = 0; i < SB; ++i) {
+#pragma unroll
+        for (int q = 0; q < NG; ++q) {
+          if (q * kShrinkRows < cur.nt) {
+            mma_bf16_16x8x16(acc[q], ra[i].x, rb[i].x, ra[i].y, rb[i].y, rx[q][i].x, rx[q][i].y);
+            mma_bf16_16x8x16(acc[q], ra[i].z, rb[i].z, ra[i].w, rb[i].w, rx[q][i].z, rx[q][i].w);
+          }
+        }
       }
       if (b == nbatch - 1) {
-        // the unit is complete: 16 ranks x up to 8 rows.  This warp holds (rank g, rows 2t, 2t+1) and (rank g + 8, same rows).
-        const int g = lane >> 2, t = lane & 3;
-        float* mine = red + (par * 4 + ewarp) * 128;                // [16 ranks][8 rows]
-        mine[g * 8 + 2 * t] = acc[0];
-        mine[g * 8 + 2 * t + 1] = acc[1];
-        mine[(g + 8) * 8 + 2 * t] = acc[2];
-        mine[(g + 8) * 8 + 2 * t + 1] = acc[3];
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        // the unit is complete: 16 ranks x up to 8 rows per group.  This warp holds (rank g, rows 2t, 2t+1) and (rank g + 8, same
+        // rows) of every group; the groups go through the two staging buffers one after the other.
         const LoraEnt e = ents[cur.lt];
         const int w0 = e.row0 & ~15;
         const int wn = ((e.row0 + e.nrows + 15) & ~15) - w0;
         const int pp = cur.j / cur.r, i0 = cur.j - pp * cur.r;
         __nv_bfloat16* img = p.lora_vimg + ((long long)(pp * 4 + (i0 >> 4)) * p.lora_num_tiles + cur.lt) * kLoraSliceElems;
-        if (tid4 < 2 * cur.nt) {
-          // thread -> (row q of the unit, 8 ranks ch): one 16-byte chunk of the image
-          const int q = tid4 >> 1, ch = tid4 & 1;
-          const float* r0 = red + par * 4 * 128;
-          float v[8];
 #pragma unroll
-          for (int h = 0; h < 8; ++h) {
-            const int o = (ch * 8 + h) * 8 + q;
-            v[h] = r0[o] + r0[128 + o] + r0[256 + o] + r0[384 + o];
+        for (int q = 0; q < NG; ++q) {
+          if (q * kShrinkRows < cur.nt) {              // the same for the four warps: they meet at the barrier below
+            const int t0g = cur.t0 + q * kShrinkRows;
+            const int ntg = min(kShrinkRows, cur.nt - q * kShrinkRows);
+            const int g = lane >> 2, t = lane & 3;
+            float* mine = red + (par * 4 + ewarp) * 128;                // [16 ranks][8 rows]
+            mine[g * 8 + 2 * t] = acc[q][0];
+            mine[g * 8 + 2 * t + 1] = acc[q][1];
+            mine[(g + 8) * 8 + 2 * t] = acc[q][2];
+            mine[(g + 8) * 8 + 2 * t + 1] = acc[q][3];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (tid4 < 2 * ntg) {
+              // thread -> (row rq of the group, 8 ranks ch): one 16-byte chunk of the image
+              const int rq = tid4 >> 1, ch = tid4 & 1;
+              const float* r0 = red + par * 4 * 128;
+              float v[8];
+#pragma unroll
+              for (int h = 0; h < 8; ++h) {
+                const int o = (ch * 8 + h) * 8 + rq;
+                v[h] = r0[o] + r0[128 + o] + r0[256 + o] + r0[384 + o];
+              }
+              const int cr = t0g + rq - w0;
+              *reinterpret_cast<uint4*>(img + cr * 16 + ((ch ^ ((cr >> 2) & 1)) << 3)) =
+                  make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
+            }
+            // rows of the window outside the entry: [0, z_lo) with the entry's first group, [z_hi, wn) with its last
+            const int z_lo = (t0g == e.row0) ? e.row0 - w0 : 0;
+            const int z_hi = (t0g + ntg == e.row0 + e.nrows) ? e.row0 + e.nrows - w0 : wn;
+            const int zrows = z_lo + (wn - z_hi);
+            if (tid4 >= 32 && tid4 - 32 < 2 * zrows) {
+              const int cz = (tid4 - 32) >> 1, ch = (tid4 - 32) & 1;
+              const int row = cz < z_lo ? cz : z_hi + (cz - z_lo);
+              *reinterpret_cast<uint4*>(img + row * 16 + (ch << 3)) = make_uint4(0, 0, 0, 0);
+            }
+            par ^= 1;
+            acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
           }
-          const int cr = cur.t0 + q - w0;
-          *reinterpret_cast<uint4*>(img + cr * 16 + ((ch ^ ((cr >> 2) & 1)) << 3)) =
-              make_uint4(pack_bf16x2(v[0], v[1]), pack_bf16x2(v[2], v[3]), pack_bf16x2(v[4], v[5]), pack_bf16x2(v[6], v[7]));
         }
-        // rows of the window outside the entry: [0, z_lo) with the entry's first group, [z_hi, wn) with its last
-        const int z_lo = (cur.t0 == e.row0) ? e.row0 - w0 : 0;
-        const int z_hi = (cur.t0 + cur.nt == e.row0 + e.nrows) ? e.row0 + e.nrows - w0 : wn;
-        const int zrows = z_lo + (wn - z_hi);
-        if (tid4 >= 32 && tid4 - 32 < 2 * zrows) {
-          const int cz = (tid4 - 32) >> 1, ch = (tid4 - 32) & 1;
-          const int row = cz < z_lo ? cz : z_hi + (cz - z_lo);
-          *reinterpret_cast<uint4*>(img + row * 16 + (ch << 3)) = make_uint4(0, 0, 0, 0);
-        }
-        par ^= 1;
-        acc[0] = acc[1] = acc[2] = acc[3] = 0.f;
       }
       if (!more) break;
       cur = nxt; b = nb; u = nu;
 #pragma unroll
-      for (int i = 0; i < kSB; ++i) { ra[i] = na[i]; rb[i] = nbv[i]; rx[i] = nx[i]; }
+      for (int i = 0; i < SB; ++i) {
+        ra[i] = na[i]; rb[i] = nbv[i];
+#pragma unroll
+        for (int q = 0; q < NG; ++q) rx[q][i] = nx[q][i];
+      }
     }
   }
   // this CTA's units are done: make the images visible to the bulk copies of every CTA, then count in
@@ -413,6 +444,11 @@ LX_DEVICE void lora_shrink_units(const GemmParams& p, const LoraEnt* ents, const
     fence_proxy_async_all();
     red_release_gpu_add(&p.lora_sync[1], 1);
   }
+}
+
+LX_DEVICE void lora_shrink_units(const GemmParams& p, const LoraEnt* ents, const unsigned short* gstart, float* red, int ewarp, int lane) {
+  if (lora_shrink_unit_rows(p) == kShrinkRows) lora_shrink_units_t<1, 8>(p, ents, gstart, red, ewarp, lane);
+  else lora_shrink_units_t<4, 4>(p, ents, gstart, red, ewarp, lane);
 }
 
 // Bounded wait for *flag == want.  False when the budget ran out.

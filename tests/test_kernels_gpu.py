@@ -442,7 +442,9 @@ def test_lora_tiled_tensor_core(nat, T, max_rows):
                                                     # a prefill-sized step: every CTA walks several token tiles and rebuilds its unit list
                                                     (2304, 2048, [1536, 768], [16, 32, 16, 64], "runs"),
                                                     # another adapter on every row: more expand units per token tile than the list holds
-                                                    (200, 1024, [512, 256], [16, 64, 32, 64], "alternating")])
+                                                    (200, 1024, [512, 256], [16, 64, 32, 64], "alternating"),
+                                                    # the same in a long step: one-row entries in the shrink units of four row groups
+                                                    (600, 1024, [512, 256], [16, 64, 32, 64], "alternating")])
 def test_gemm_with_lora_in_the_same_launch(nat, T, K, parts, ranks, layout):
     """Shrink items, base tiles and expand UMMAs in ONE launch of the GEMM kernel against fp32 PyTorch:
     x W^T + b + (x A_slot^T) B_slot^T per row, several adapters and ranks, base-model rows in between, rows of one adapter
