@@ -1,6 +1,6 @@
 """Small, self-terminating workloads for `ncu` captures of single kernels.
 
-    python benchmarks/profile_case.py --case gemm_decode|gemm_mid|gemm_prefill|gemm_fp8_decode|gemm_fp8_prefill|gemm_lora_decode|gemm_lora_decode_gateup|gemm_lora_prefill|attn_decode|attn_prefill|lora_shrink|lora_expand|moe_decode|moe_prefill
+    python benchmarks/profile_case.py --case gemm_decode|gemm_mid|gemm_prefill|gemm_fp8_decode|gemm_fp8_prefill|gemm_lora_decode|gemm_lora_decode_gateup|gemm_lora_prefill|gemm_lora_prefill_gateup|attn_decode|attn_prefill|lora_shrink|lora_expand|moe_decode|moe_prefill
 
 Each case launches the kernel a handful of times on inputs larger than the 126 MB L2 but at most a few GB, and
 exits 0; run it plain first, then under
@@ -102,7 +102,7 @@ def gemm_lora_case(T, parts=(4096, 1024, 1024)):
     w_ = torch.tensor([1.0 / (k ** 1.1) for k in range(1, S + 1)], dtype=torch.float64)
     rows = sorted(int(x) for x in torch.multinomial(w_ / w_.sum(), T, replacement=True))
     tl = reference.build_lora_tiles(rows, 32)
-    tiles = torch.full((max(T, len(tl)), 4), -1, device="cuda", dtype=torch.int32)
+    tiles = torch.full((min(max(T, len(tl)), len(tl) + 16), 4), -1, device="cuda", dtype=torch.int32)
     tiles[: len(tl)] = torch.tensor(tl, device="cuda", dtype=torch.int32)
     ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K) for _ in range(4)]
     x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
@@ -160,6 +160,7 @@ def main():
     native.load()
     {"gemm_decode": lambda: gemm_case(64), "gemm_prefill": lambda: gemm_case(4096), "attn_decode": attn_decode_case,
      "attn_prefill": attn_prefill_case, "gemm_lora_decode": lambda: gemm_lora_case(256), "gemm_lora_decode_gateup": lambda: gemm_lora_case(256, (14336, 14336)), "gemm_lora_prefill": lambda: gemm_lora_case(576),
+     "gemm_lora_prefill_gateup": lambda: gemm_lora_case(4096, (14336, 14336)),
      "gemm_fp8_decode": lambda: gemm_fp8_case(64), "gemm_fp8_prefill": lambda: gemm_fp8_case(2048), "gemm_mid": lambda: gemm_case(256),
      "gemm_int4_decode": lambda: gemm_int4_case(8),
      "lora_shrink": lambda: lora_case("shrink"), "lora_expand": lambda: lora_case("expand"),
