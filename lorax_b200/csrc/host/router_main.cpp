@@ -979,19 +979,22 @@ int main(int argc, char** argv) {
   if (a.get("router-tokenizer", "on") != "off") {
     try {
       std::shared_ptr<const tok::Tokenizer> t;
+      bool images_to_shard = false;
       const std::string named = a.get("tokenizer-name", "");
       if (!named.empty()) {
         t = tok::Tokenizer::load(named);
       } else {
-        const std::string file = client->helper(103, "");
+        std::string file = client->helper(103, "");
         json::Value root;
         std::string perr;
-        if (file.empty()) throw tok::Unsupported("the shard keeps tokenisation to itself");
+        if (file.empty()) throw tok::Unsupported("the shard has no tokenizer file");
+        if (file.rfind("#images\n", 0) == 0) { images_to_shard = true; file.erase(0, 8); }
         if (!json::parse(file, root, &perr)) throw std::runtime_error("tokenizer file: " + perr);
         t = tok::Tokenizer::from_json(root);
       }
-      client->set_local_tokenizer(std::make_shared<tok::TokenizerPool>(t, g_validation_workers));
-      log_json("INFO", "tokenising in the router on " + std::to_string(g_validation_workers) + " worker(s)");
+      client->set_local_tokenizer(std::make_shared<tok::TokenizerPool>(t, g_validation_workers), images_to_shard);
+      log_json("INFO", "tokenising in the router on " + std::to_string(g_validation_workers) + " worker(s)" +
+                           (images_to_shard ? "; prompts with images go to shard 0" : ""));
     } catch (const std::exception& e) {
       log_json("INFO", std::string("shard 0 tokenises (router tokenizer not used: ") + e.what() + ")");
     }

@@ -202,11 +202,15 @@ class ShardedClient {
   // Request text -> ids.  With a local tokenizer (the router read the shard's tokenizer file and implements every component
   // it uses) this runs on the router's tokenizer workers; otherwise shard 0 is asked.  Chat templating and `/tokenize` with
   // character offsets are always helper calls to shard 0.
-  void set_local_tokenizer(std::shared_ptr<tok::TokenizerPool> pool) { local_tok_ = std::move(pool); }
+  void set_local_tokenizer(std::shared_ptr<tok::TokenizerPool> pool, bool images_to_shard = false) {
+    local_tok_ = std::move(pool);
+    images_to_shard_ = images_to_shard;
+  }
   bool tokenizes_locally() const { return local_tok_ != nullptr; }
   uint64_t local_tokenizations() const { return local_tok_ ? local_tok_->served() : 0; }
   std::vector<uint32_t> tokenize(const std::string& text, bool add_special = true) {
-    if (local_tok_) return local_tok_->encode(text, add_special);
+    // a vision-language shard turns image markdown into feature tokens: only it knows how many
+    if (local_tok_ && !(images_to_shard_ && text.find("![") != std::string::npos)) return local_tok_->encode(text, add_special);
     std::string out = shards_.front()->call(gen::M_Tokenize, std::string(1, add_special ? '\1' : '\0') + text);
     std::vector<uint32_t> ids(out.size() / 4);
     std::memcpy(ids.data(), out.data(), ids.size() * 4);
@@ -232,6 +236,7 @@ class ShardedClient {
   }
   std::vector<std::shared_ptr<ShardClient>> shards_;
   std::shared_ptr<tok::TokenizerPool> local_tok_;
+  bool images_to_shard_ = false;
   struct TraceSlot {                      // movable holder: the client itself is passed around by value once
     std::mutex mu;
     std::string tp;

@@ -171,10 +171,13 @@ class ShardRuntime:
         return self.tokenizer.encode(text, add_special_tokens=add_special).ids
 
     def router_tokenizer_json(self) -> str:
-        """The tokenizer file as a string, for the router to tokenise requests itself; empty when this runtime's `tokenize` does
-        more than run the tokenizer (image placeholders expand to feature tokens) or when there is no tokenizer file."""
+        """The tokenizer file as a string, for the router to tokenise requests itself; empty when there is no tokenizer file.
+        A first line `#images` tells the router that this runtime expands image markdown (`![](uri)`) into feature tokens: prompts
+        that contain `![` keep coming to the shard, everything else is tokenised in the router."""
+        if self.tokenizer is None:
+            return ""
         plain = type(self).tokenize in (ShardRuntime.tokenize, EncoderRuntime.tokenize)
-        return self.tokenizer.to_str() if (plain and self.tokenizer is not None) else ""
+        return ("" if plain else "#images\n") + self.tokenizer.to_str()
 
     def tokenize_detailed(self, body: dict) -> list:
         text = body.get("inputs", "")

@@ -222,3 +222,8 @@ def test_image_prompt_through_router_matches_hf(vlm_stack):
     st, body, _ = _post(port, "/generate", {"inputs": "w1 ![](data:image/png;base64,AAAA) w2", "parameters": {"max_new_tokens": 2}})
     assert st >= 400
     assert not rt.seqs
+    # the router tokenised the text-only prompt itself; the prompts with image markdown went to the shard, which knows the feature counts
+    import urllib.request
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5) as r:
+        count = [l for l in r.read().decode().splitlines() if l.startswith("lorax_router_tokenizations ")]
+    assert count and int(count[0].split()[1]) == 1, count
