@@ -1,7 +1,7 @@
 // A small backtracking regular-expression engine over code points, for the patterns that tokenizer files carry (the GPT-2 /
 // cl100k / Llama-3 / Qwen2 split patterns, `Replace` normalisers): literals, escapes (\s \S \d \D \w \W \r \n \t \p{..} \P{..}),
 // character classes with ranges and negation, `.`, groups (capturing groups are treated as non-capturing), `(?i:..)` and a leading
-// `(?i)`, look-ahead `(?=..)` / `(?!..)`, alternation, `^` `$`, and the quantifiers ? * + {m} {m,} {m,n} with lazy (`?`) and
+// `(?i)`, look-ahead `(?=..)` / `(?!..)`, look-behind of fixed length `(?<=..)` / `(?<!..)`, `\b` `\B` `\A` `\z`, alternation, `^` `$`, and the quantifiers ? * + {m} {m,} {m,n} with lazy (`?`) and
 // possessive (`+`, run as greedy) suffixes.  Leftmost match, alternatives tried in order: the semantics of the Oniguruma engine
 // the `tokenizers` library splits with.  A pattern outside this subset fails to compile and the caller falls back.
 //
@@ -85,18 +85,20 @@ class MiniRegex {
   struct Node;
   using NodeP = std::unique_ptr<Node>;
   struct Node {
-    enum Kind { Set, Any, Seq, Alt, Repeat, Look, Bol, Eol } kind;
+    enum Kind { Set, Any, Seq, Alt, Repeat, Look, Bol, Eol, WordB } kind;
     Class cls;                               // Set
     std::vector<NodeP> kids;                 // Seq, Alt; Repeat and Look use kids[0]
     int min = 0, max = -1;                   // Repeat (max < 0: unbounded)
-    bool lazy = false, negative = false;     // Repeat / Look
+    bool lazy = false, negative = false;     // Repeat / Look / WordB
+    int behind = -1;                         // Look: code points in front of the position that must (not) match; -1: look-ahead
   };
   struct Inst {
-    enum Op { Set, Any, Split, Jmp, Look, Bol, Eol, Match } op;
+    enum Op { Set, Any, Split, Jmp, Look, Bol, Eol, WordB, Match } op;
     int x = 0, y = 0;                        // Split: first and second choice; Jmp: x
     int cls = -1;                            // Set
     int sub = -1;                            // Look: index of the sub-program
     bool negative = false;
+    int behind = -1;                         // Look: -1 ahead, else the fixed length looked at behind the position
   };
   using Prog = std::vector<Inst>;
 
@@ -162,6 +164,29 @@ class MiniRegex {
         a = std::move(r);
       }
       return a;
+    }
+    // Number of code points a node consumes: [lo, hi]; false when unbounded.
+    static bool width(const Node& n, int* lo, int* hi) {
+      switch (n.kind) {
+        case Node::Set: case Node::Any: *lo = *hi = 1; return true;
+        case Node::Bol: case Node::Eol: case Node::Look: case Node::WordB: *lo = *hi = 0; return true;
+        case Node::Seq: {
+          int a = 0, b = 0;
+          for (auto& k : n.kids) { int x, y; if (!width(*k, &x, &y)) return false; a += x; b += y; }
+          *lo = a; *hi = b; return true;
+        }
+        case Node::Alt: {
+          int a = 1 << 30, b = 0;
+          for (auto& k : n.kids) { int x, y; if (!width(*k, &x, &y)) return false; a = x < a ? x : a; b = y > b ? y : b; }
+          *lo = a; *hi = b; return true;
+        }
+        case Node::Repeat: {
+          int x, y;
+          if (n.max < 0 || !width(*n.kids[0], &x, &y)) return false;
+          *lo = x * n.min; *hi = y * n.max; return true;
+        }
+      }
+      return false;
     }
     NodeP literal(uint32_t c) {
       auto n = std::make_unique<Node>();
@@ -272,7 +297,7 @@ class MiniRegex {
       switch (c) {
         case '(': {
           bool saved = icase;
-          bool look = false, negative = false;
+          bool look = false, negative = false, behind = false;
           if (more() && peek() == '?') {
             ++pos;
             if (!more()) return fail("dangling (?");
@@ -282,8 +307,10 @@ class MiniRegex {
               look = true; negative = k == '!';
             } else if (k == 'i' && more() && peek() == ':') {
               ++pos; icase = true;
+            } else if (k == '<' && more() && (peek() == '=' || peek() == '!')) {
+              look = true; behind = true; negative = src[pos++] == '!';
             } else if (k == '<' || k == 'P' || k == '\'') {
-              return fail("named groups and look-behind are not supported");
+              return fail("named groups are not supported");
             } else {
               return fail("unsupported group flag");
             }
@@ -297,6 +324,11 @@ class MiniRegex {
           auto l = std::make_unique<Node>();
           l->kind = Node::Look;
           l->negative = negative;
+          if (behind) {
+            int lo = 0, hi = 0;
+            if (!width(*inner, &lo, &hi) || lo != hi) return fail("look-behind of variable length");
+            l->behind = lo;
+          }
           l->kids.push_back(std::move(inner));
           return l;
         }
@@ -305,6 +337,17 @@ class MiniRegex {
         case '^': { auto n = std::make_unique<Node>(); n->kind = Node::Bol; return n; }
         case '$': { auto n = std::make_unique<Node>(); n->kind = Node::Eol; return n; }
         case '\\': {
+          if (more() && (peek() == 'b' || peek() == 'B')) {
+            auto n = std::make_unique<Node>();
+            n->kind = Node::WordB;
+            n->negative = src[pos++] == 'B';
+            return n;
+          }
+          if (more() && (peek() == 'A' || peek() == 'z')) {
+            auto n = std::make_unique<Node>();
+            n->kind = src[pos++] == 'A' ? Node::Bol : Node::Eol;
+            return n;
+          }
           auto n = std::make_unique<Node>();
           n->kind = Node::Set;
           n->cls.icase = icase;
@@ -326,6 +369,7 @@ class MiniRegex {
       case Node::Any: out.push_back(Inst{Inst::Any}); break;
       case Node::Bol: out.push_back(Inst{Inst::Bol}); break;
       case Node::Eol: out.push_back(Inst{Inst::Eol}); break;
+      case Node::WordB: { Inst i{Inst::WordB}; i.negative = n.negative; out.push_back(i); break; }
       case Node::Seq: for (auto& k : n.kids) emit(*k, out); break;
       case Node::Alt: {
         std::vector<int> jumps;
@@ -374,6 +418,7 @@ class MiniRegex {
       case Node::Look: {
         Inst i{Inst::Look};
         i.negative = n.negative;
+        i.behind = n.behind;
         i.sub = (int)subs_.size();
         subs_.emplace_back();
         Prog sub;
@@ -413,8 +458,15 @@ class MiniRegex {
             stack.push_back({in.y, t.pos});
             t.pc = in.x;
             break;
+          case Inst::WordB: {
+            const bool before = t.pos > 0 && uni::is_word(s[t.pos - 1]), after = t.pos < n && uni::is_word(s[t.pos]);
+            if ((before != after) != in.negative) ++t.pc; else dead = true;
+            break;
+          }
           case Inst::Look: {
-            const bool hit = run(subs_[(size_t)in.sub], s, n, t.pos) >= 0;
+            bool hit;
+            if (in.behind < 0) hit = run(subs_[(size_t)in.sub], s, n, t.pos) >= 0;
+            else hit = t.pos >= (size_t)in.behind && run(subs_[(size_t)in.sub], s, n, t.pos - (size_t)in.behind) == (long)in.behind;
             if (hit != in.negative) ++t.pc; else dead = true;
             break;
           }

@@ -271,8 +271,13 @@ inline std::vector<Span> spans_by_regex(const Text& t, const MiniRegex& re, bool
   while (at <= t.size()) {
     size_t b, e;
     if (!re.search(t.data(), t.size(), at, &b, &e)) break;
-    if (e == b) { at = b + 1; continue; }            // empty matches split nothing
     if (b > last) spans.push_back({last, b, invert});
+    if (e == b) {                                    // a zero-width match (look-around, \b) cuts the text where it stands
+      spans.push_back({b, b, !invert});
+      last = b;
+      at = b + 1;
+      continue;
+    }
     spans.push_back({b, e, !invert});
     last = e;
     at = e;

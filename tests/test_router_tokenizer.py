@@ -189,7 +189,7 @@ def test_unsupported_files_are_refused_with_the_reason(tmp_path):
     with pytest.raises(ValueError, match="Precompiled"):
         RouterTokenizer(str(p))
     state["normalizer"] = None
-    state["pre_tokenizer"] = {"type": "Split", "pattern": {"Regex": r"(?<=a)b|\bfoo"}, "behavior": "Isolated", "invert": False}
+    state["pre_tokenizer"] = {"type": "Split", "pattern": {"Regex": r"(?P<x>a)\1|(?<=a+)b"}, "behavior": "Isolated", "invert": False}
     p.write_text(json.dumps(state))
     with pytest.raises(ValueError, match="regex"):
         RouterTokenizer(str(p))
@@ -238,3 +238,14 @@ def test_llama_tokenizer_class_gets_the_bos_template_on_both_sides(tmp_path):
     assert mine.encode("hello world") == ids
     (mdir / "tokenizer_config.json").write_text(json.dumps({"tokenizer_class": "GPT2Tokenizer", "bos_token": "<s>"}))
     assert load_tokenizer(str(mdir)).encode("hello world").ids == ids[1:-1]
+
+
+@pytest.mark.parametrize("behavior", ["isolated", "removed", "merged_with_previous", "merged_with_next", "contiguous"])
+def test_zero_width_and_look_behind_split_patterns(tmp_path, behavior):
+    """Look-behind, word boundaries and zero-width matches (camelCase cuts) in a Split pattern, under every split behaviour."""
+    pattern = r"(?<=[a-z])(?=[A-Z])|\b\d+\b|(?<!\S)-"
+    pre = pre_tokenizers.Sequence([pre_tokenizers.Split(Regex(pattern), behavior=behavior, invert=False),
+                                   pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tok = byte_level_bpe(pre)
+    extra = ["camelCaseWordsHere and snake_case 123 a1b2 -dash non-dash", "fooBar", "XMLHttpRequest 42", "- -a b-", "aB", "a", "9"]
+    check(tmp_path, tok, SAMPLES[:40] + extra)
