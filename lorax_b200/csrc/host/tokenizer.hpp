@@ -6,11 +6,12 @@
 //   added tokens -> normalizer -> pre-tokenizer -> model (BPE, WordPiece, WordLevel, Unigram) -> post-processor
 //
 // Only ids are produced (offsets stay with the shard's `/tokenize` helper).  A file that uses a component outside what is
-// implemented (a SentencePiece "Precompiled" character map, an unknown regex construct ...) makes `load` fail with the reason,
+// implemented (an unknown regex construct, a model type such as an n-gram language model ...) makes `load` fail with the reason,
 // and the router keeps asking shard 0 for that model.
 #pragma once
 #include <atomic>
 #include <condition_variable>
+#include <cstring>
 #include <deque>
 #include <fstream>
 #include <functional>
@@ -141,6 +142,98 @@ struct BertNorm : Normalizer {
   }
 };
 
+// SentencePiece's compiled character map (`Precompiled`): a double-array trie from byte strings to offsets into a pool of
+// replacement strings, applied grapheme cluster by grapheme cluster the way the `tokenizers` library does it (a cluster shorter than
+// six bytes is looked up as a whole and replaced by what its shortest matching prefix maps to; otherwise, and when nothing
+// matches, its characters are looked up one by one).
+struct PrecompiledNorm : Normalizer {
+  std::vector<uint32_t> trie;
+  std::string pool;
+
+  static std::string base64(const std::string& in) {
+    std::string out;
+    uint32_t acc = 0;
+    int bits = 0;
+    for (unsigned char c : in) {
+      int v;
+      if (c >= 'A' && c <= 'Z') v = c - 'A';
+      else if (c >= 'a' && c <= 'z') v = c - 'a' + 26;
+      else if (c >= '0' && c <= '9') v = c - '0' + 52;
+      else if (c == '+' || c == '-') v = 62;
+      else if (c == '/' || c == '_') v = 63;
+      else continue;                                   // padding, line breaks
+      acc = (acc << 6) | (uint32_t)v;
+      bits += 6;
+      if (bits >= 8) { bits -= 8; out.push_back((char)((acc >> bits) & 0xFF)); }
+    }
+    return out;
+  }
+  explicit PrecompiledNorm(const std::string& b64) {
+    if (!uni::kHasGcb) throw Unsupported("Precompiled normalizer (built without the grapheme break tables)");
+    const std::string blob = base64(b64);
+    if (blob.size() < 4) throw Unsupported("Precompiled normalizer with an empty character map");
+    uint32_t trie_bytes;
+    std::memcpy(&trie_bytes, blob.data(), 4);
+    if (trie_bytes % 4 != 0 || 4 + (size_t)trie_bytes > blob.size()) throw std::runtime_error("Precompiled character map: bad trie size");
+    trie.resize(trie_bytes / 4);
+    std::memcpy(trie.data(), blob.data() + 4, trie_bytes);
+    pool.assign(blob.data() + 4 + trie_bytes, blob.size() - 4 - trie_bytes);
+  }
+  static size_t offset_of(uint32_t u) { return (size_t)(u >> 10) << ((u & (1u << 9)) >> 6); }
+  // What the shortest prefix of `key` that the map knows is replaced by; false when no prefix is in the map.
+  bool transform(const std::string& key, std::string* out) const {
+    if (trie.empty()) return false;
+    size_t node = 0;
+    uint32_t unit = trie[0];
+    node ^= offset_of(unit);
+    for (unsigned char c : key) {
+      if (c == 0) break;
+      node ^= c;
+      if (node >= trie.size()) return false;
+      unit = trie[node];
+      if ((unit & ((1u << 31) | 0xFFu)) != c) return false;
+      node ^= offset_of(unit);
+      if (node >= trie.size()) return false;
+      if ((unit >> 8) & 1) {
+        const size_t at = trie[node] & ((1u << 31) - 1);
+        if (at > pool.size()) return false;
+        size_t end = at;
+        while (end < pool.size() && pool[end] != 0) ++end;
+        out->assign(pool, at, end - at);
+        return true;
+      }
+    }
+    return false;
+  }
+  Text apply(const Text& t) const override {
+    Text out;
+    out.reserve(t.size());
+    std::string key, repl;
+    size_t b = 0;
+    for (size_t e : uni::grapheme_ends(t)) {
+      key = uni::to_utf8(t.data() + b, e - b);
+      bool done = false;
+      if (key.size() < 6 && transform(key, &repl)) {
+        const Text r = uni::from_utf8(repl);
+        out.insert(out.end(), r.begin(), r.end());
+        done = true;
+      }
+      for (size_t i = b; !done && i < e; ++i) {
+        key.clear();
+        uni::append_utf8(key, t[i]);
+        if (transform(key, &repl)) {
+          const Text r = uni::from_utf8(repl);
+          out.insert(out.end(), r.begin(), r.end());
+        } else {
+          out.push_back(t[i]);
+        }
+      }
+      b = e;
+    }
+    return out;
+  }
+};
+
 inline std::unique_ptr<MiniRegex> compile_or_throw(const std::string& pattern) {
   std::string err;
   auto re = MiniRegex::compile(pattern, &err);
@@ -184,6 +277,7 @@ inline NormP make_normalizer(const Value& v) {
     b->strip_accents = v["strip_accents"].is_bool() ? v["strip_accents"].as_bool() : b->lower;
     return b;
   }
+  if (type == "Precompiled") return std::make_unique<PrecompiledNorm>(v["precompiled_charsmap"].as_string());
   throw Unsupported("normalizer " + type);
 }
 

@@ -207,5 +207,60 @@ inline Text normalize(const Text& t, Form f) {
   return (f == Form::NFC || f == Form::NFKC) ? compose(d) : d;
 }
 
+// Extended grapheme clusters (UAX #29, rules GB3-GB13 without the Indic conjunct rule GB9c): the end index of every cluster of `t`.
+// Needs the break tables of the generated header (`kHasGcb`).
+enum class Gcb { Other, CR, LF, Control, Extend, ZWJ, RI, Prepend, SpacingMark, L, V, T, LV, LVT };
+inline Gcb gcb_of(uint32_t c) {
+  if (c == '\r') return Gcb::CR;
+  if (c == '\n') return Gcb::LF;
+  if (c == 0x200D) return Gcb::ZWJ;
+  if (c < 0x300) return (c < 0x20 || (c >= 0x7F && c < 0xA0) || c == 0xAD) ? Gcb::Control : Gcb::Other;
+  if (c >= 0x1F1E6 && c <= 0x1F1FF) return Gcb::RI;
+  if ((c >= 0x1100 && c <= 0x115F) || (c >= 0xA960 && c <= 0xA97C)) return Gcb::L;
+  if ((c >= 0x1160 && c <= 0x11A7) || (c >= 0xD7B0 && c <= 0xD7C6)) return Gcb::V;
+  if ((c >= 0x11A8 && c <= 0x11FF) || (c >= 0xD7CB && c <= 0xD7FB)) return Gcb::T;
+  if (c >= 0xAC00 && c <= 0xD7A3) return (c - 0xAC00) % 28 == 0 ? Gcb::LV : Gcb::LVT;
+  if (in_ranges(kGcbExtend, kGcbExtend_n, c)) return Gcb::Extend;
+  if (in_ranges(kGcbSpacingMark, kGcbSpacingMark_n, c)) return Gcb::SpacingMark;
+  if (in_ranges(kGcbPrepend, kGcbPrepend_n, c)) return Gcb::Prepend;
+  if (in_ranges(kGcbControl, kGcbControl_n, c)) return Gcb::Control;
+  return Gcb::Other;
+}
+inline std::vector<size_t> grapheme_ends(const Text& t) {
+  std::vector<size_t> ends;
+  const size_t n = t.size();
+  size_t i = 0;
+  while (i < n) {
+    Gcb prev = gcb_of(t[i]);
+    bool pict_run = in_ranges(kExtPict, kExtPict_n, t[i]);     // ExtPict Extend* seen so far (GB11)
+    bool pict_zwj = false;                                      // ... followed by ZWJ
+    int ri = prev == Gcb::RI ? 1 : 0;
+    size_t j = i + 1;
+    for (; j < n; ++j) {
+      const Gcb next = gcb_of(t[j]);
+      bool join = false;
+      if (prev == Gcb::CR && next == Gcb::LF) join = true;                                                    // GB3
+      else if (prev == Gcb::CR || prev == Gcb::LF || prev == Gcb::Control) join = false;                      // GB4
+      else if (next == Gcb::CR || next == Gcb::LF || next == Gcb::Control) join = false;                      // GB5
+      else if (prev == Gcb::L && (next == Gcb::L || next == Gcb::V || next == Gcb::LV || next == Gcb::LVT)) join = true;   // GB6
+      else if ((prev == Gcb::LV || prev == Gcb::V) && (next == Gcb::V || next == Gcb::T)) join = true;        // GB7
+      else if ((prev == Gcb::LVT || prev == Gcb::T) && next == Gcb::T) join = true;                           // GB8
+      else if (next == Gcb::Extend || next == Gcb::ZWJ || next == Gcb::SpacingMark) join = true;              // GB9, GB9a
+      else if (prev == Gcb::Prepend) join = true;                                                             // GB9b
+      else if (pict_zwj && in_ranges(kExtPict, kExtPict_n, t[j])) join = true;                                // GB11
+      else if (prev == Gcb::RI && next == Gcb::RI && (ri & 1)) join = true;                                   // GB12, GB13
+      if (!join) break;
+      if (next == Gcb::ZWJ) { pict_zwj = pict_run; }
+      else if (next == Gcb::Extend) { pict_zwj = false; }                  // pict_run continues through Extend
+      else { pict_zwj = false; pict_run = in_ranges(kExtPict, kExtPict_n, t[j]); }
+      ri = next == Gcb::RI ? ri + 1 : 0;
+      prev = next;
+    }
+    ends.push_back(j);
+    i = j;
+  }
+  return ends;
+}
+
 }  // namespace uni
 }  // namespace lx

@@ -249,3 +249,36 @@ def test_zero_width_and_look_behind_split_patterns(tmp_path, behavior):
     tok = byte_level_bpe(pre)
     extra = ["camelCaseWordsHere and snake_case 123 a1b2 -dash non-dash", "fooBar", "XMLHttpRequest 42", "- -a b-", "aB", "a", "9"]
     check(tmp_path, tok, SAMPLES[:40] + extra)
+
+
+def test_sentencepiece_precompiled_character_map(tmp_path):
+    """A T5 / XLM-R style tokenizer: SentencePiece's compiled nmt_nfkc character map (taken from a model trained here), applied
+    grapheme cluster by grapheme cluster, in front of a Unigram model."""
+    spm = pytest.importorskip("sentencepiece")
+    from sentencepiece import sentencepiece_model_pb2 as pb
+    import io
+    import os
+    model = io.BytesIO()
+    devnull = os.open(os.devnull, os.O_WRONLY)
+    saved = os.dup(2)
+    os.dup2(devnull, 2)                      # the trainer logs to stderr
+    try:
+        spm.SentencePieceTrainer.train(sentence_iterator=iter(corpus(600, seed=2)), model_writer=model, vocab_size=300, model_type="unigram",
+                                       hard_vocab_limit=False)
+    finally:
+        os.dup2(saved, 2)
+        os.close(devnull)
+        os.close(saved)
+    proto = pb.ModelProto()
+    proto.ParseFromString(model.getvalue())
+    charsmap = proto.normalizer_spec.precompiled_charsmap
+    assert len(charsmap) > 100_000
+    vocab = [(p.piece, p.score) for p in proto.pieces]
+    tok = Tokenizer(models.Unigram(vocab, unk_id=0))
+    tok.normalizer = normalizers.Sequence([normalizers.Precompiled(charsmap), normalizers.Replace(Regex(" {2,}"), " ")])
+    tok.pre_tokenizer = pre_tokenizers.Metaspace(replacement="▁", prepend_scheme="always")
+    tok.post_processor = processors.TemplateProcessing(single="$A </s>", special_tokens=[("</s>", 2)])
+    hard = ["ﬁn ① ½ Ⅷ ｆｕｌｌ　ｗｉｄｔｈ ㎏ ℃ Å", "é ạ̈ ố ́alone", "اَّلسَّلَامُ عَلَيْكُمْ ؀123", "한국어 각 한́",
+            "a\r\nb\rc\nd\t\te", "👩‍👩‍👧 ❤‍🔥 🇩🇪🇫🇷 👍🏽", "क्षत्रिय हिन्दी กำลัง น้ำ", "soft­hyphen zero​width ‍j ﻿bom", "ǅ ﬃ ẛ̣ ™ ² ³ ¼ № ㍿",
+            "x́́́́ ำ ःa", "", " ", "   multiple   spaces   "]
+    check(tmp_path, tok, SAMPLES + hard)
