@@ -109,6 +109,19 @@ struct ReplaceNorm : Normalizer {
     return out;
   }
 };
+struct NmtNorm : Normalizer {                 // the clean-up in front of NMT models: control characters out, odd spaces to ' '
+  Text apply(const Text& t) const override {
+    Text out;
+    out.reserve(t.size());
+    for (uint32_t c : t) {
+      if ((c >= 1 && c <= 8) || c == 0xB || (c >= 0xE && c <= 0x1F) || c == 0x7F || c == 0x8F || c == 0x9F) continue;
+      const bool space = c == 9 || c == 0xA || c == 0xC || c == 0xD || c == 0x1680 || (c >= 0x200B && c <= 0x200F) || c == 0x2028 || c == 0x2029 ||
+                         c == 0x2581 || c == 0xFEFF || c == 0xFFFD;
+      out.push_back(space ? ' ' : c);
+    }
+    return out;
+  }
+};
 struct BertNorm : Normalizer {
   bool clean = true, chinese = true, strip_accents = true, lower = true;
   static bool cjk(uint32_t c) {
@@ -277,6 +290,7 @@ inline NormP make_normalizer(const Value& v) {
     b->strip_accents = v["strip_accents"].is_bool() ? v["strip_accents"].as_bool() : b->lower;
     return b;
   }
+  if (type == "Nmt") return std::make_unique<NmtNorm>();
   if (type == "Precompiled") return std::make_unique<PrecompiledNorm>(v["precompiled_charsmap"].as_string());
   throw Unsupported("normalizer " + type);
 }

@@ -32,7 +32,7 @@ SAMPLES = corpus(120, seed=7) + [
     "", " ", "  leading and trailing  ", "Hello, world!", "don't stop: we're here; I'll go. IT'S FINE", "a\n\nb\r\nc\t\td   ",
     "price: $1,234.56 (approx.) 100% sure", "naïve café — “quoted” … ½ ① ﬁn", "日本語のテキストと中文字符 mixed with English",
     "한국어 텍스트 각", "🙂🚀 emoji‍ sequence 👩‍👩‍👧", "é vs é and ẛ̣ क़", "tabs\tand\x00nul\x7f",
-    "x" * 300, "unknownwordzzzqqq " * 5, "İstanbul ΣΊΣΥΦΟΣ ǅ",
+    "x" * 300, "unknownwordzzzqqq " * 5, "İstanbul ΣΊΣΥΦΟΣ ǅ", "ctl\x01\x08\x0b\x1f\x7f\x8f\x9f sp\x0c\u1680\u200b\u200f\u2028\u2581\ufeff\ufffd end",
 ]
 
 
@@ -148,7 +148,7 @@ def test_unigram_with_metaspace(tmp_path):
 def test_word_level_whitespace_digits_and_punctuation(tmp_path):
     vocab = {w: i for i, w in enumerate(dict.fromkeys(["<unk>"] + [w.lower() for w in WORDS] + list("0123456789.,;!?()=+")))}
     tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
-    tok.normalizer = normalizers.Sequence([normalizers.NFD(), normalizers.StripAccents(), normalizers.Lowercase(), normalizers.Strip()])
+    tok.normalizer = normalizers.Sequence([normalizers.Nmt(), normalizers.NFD(), normalizers.StripAccents(), normalizers.Lowercase(), normalizers.Strip()])
     tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Whitespace(), pre_tokenizers.Digits(individual_digits=True), pre_tokenizers.Punctuation()])
     check(tmp_path, tok)
     tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.WhitespaceSplit(), pre_tokenizers.Digits(individual_digits=False)])
