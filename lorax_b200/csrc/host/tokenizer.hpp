@@ -553,6 +553,14 @@ inline PreP make_pretokenizer(const Value& v) {
     c->is_delim = [](uint32_t ch) { return uni::is_space(ch); };
     return c;
   }
+  if (type == "CharDelimiterSplit") {
+    const Text d = text_of(v["delimiter"].as_string());
+    if (d.size() != 1) throw Unsupported("CharDelimiterSplit without a one-character delimiter");
+    auto c = std::make_unique<CharPre>();
+    const uint32_t delim = d[0];
+    c->is_delim = [delim](uint32_t ch) { return ch == delim; };
+    return c;
+  }
   if (type == "BertPreTokenizer") return std::make_unique<BertPre>();
   if (type == "Punctuation") {
     auto c = std::make_unique<CharPre>();

@@ -153,6 +153,8 @@ def test_word_level_whitespace_digits_and_punctuation(tmp_path):
     check(tmp_path, tok)
     tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.WhitespaceSplit(), pre_tokenizers.Digits(individual_digits=False)])
     check(tmp_path, tok)
+    tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.CharDelimiterSplit(" "), pre_tokenizers.Punctuation("merged_with_previous")])
+    check(tmp_path, tok)
     no_unk = Tokenizer(models.WordLevel(vocab))                 # a word outside the vocabulary is an error, here as there
     no_unk.pre_tokenizer = pre_tokenizers.Whitespace()
     check(tmp_path, no_unk, ["the quick fox", "the zzzz fox"])
