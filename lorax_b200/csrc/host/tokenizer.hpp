@@ -41,6 +41,19 @@ struct Unsupported : std::runtime_error { using std::runtime_error::runtime_erro
 
 inline Text text_of(const std::string& s) { return uni::from_utf8(s); }
 
+// GPT-2's byte <-> printable code point table.
+inline const uint32_t* byte_to_char() {
+  static uint32_t table[256];
+  static std::once_flag once;
+  std::call_once(once, [] {
+    int n = 0;
+    for (int b = 0; b < 256; ++b) {
+      const bool keep = (b >= '!' && b <= '~') || (b >= 0xA1 && b <= 0xAC) || (b >= 0xAE && b <= 0xFF);
+      table[b] = keep ? (uint32_t)b : (uint32_t)(256 + n++);
+    }
+  });
+  return table;
+}
 // ------------------------------------------------------------------------------------------------ normalizers
 struct Normalizer {
   virtual ~Normalizer() = default;
@@ -106,6 +119,16 @@ struct ReplaceNorm : Normalizer {
       if (e == b) { if (b < t.size()) out.push_back(t[b]); at = b + 1; } else at = e;
     }
     if (at < t.size()) out.insert(out.end(), t.begin() + (long)at, t.end());
+    return out;
+  }
+};
+struct ByteLevelNorm : Normalizer {            // every byte of the text as its printable stand-in (the byte-level alphabet)
+  Text apply(const Text& t) const override {
+    const std::string bytes = uni::to_utf8(t);
+    const uint32_t* map = byte_to_char();
+    Text out;
+    out.reserve(bytes.size());
+    for (unsigned char b : bytes) out.push_back(map[b]);
     return out;
   }
 };
@@ -291,6 +314,7 @@ inline NormP make_normalizer(const Value& v) {
     return b;
   }
   if (type == "Nmt") return std::make_unique<NmtNorm>();
+  if (type == "ByteLevel") return std::make_unique<ByteLevelNorm>();
   if (type == "Precompiled") return std::make_unique<PrecompiledNorm>(v["precompiled_charsmap"].as_string());
   throw Unsupported("normalizer " + type);
 }
@@ -444,6 +468,12 @@ struct CharPre : PreTokenizer {              // WhitespaceSplit, Punctuation, Di
   Behavior how = Behavior::Removed;
   void apply(const Text& t, bool, std::vector<Text>& out) const override { split_spans(t, spans_by_char(t, is_delim), how, out); }
 };
+struct FixedLengthPre : PreTokenizer {         // chunks of `length` characters
+  size_t length = 5;
+  void apply(const Text& t, bool, std::vector<Text>& out) const override {
+    for (size_t i = 0; i < t.size(); i += length) out.emplace_back(t.begin() + (long)i, t.begin() + (long)std::min(t.size(), i + length));
+  }
+};
 struct BertPre : PreTokenizer {
   void apply(const Text& t, bool, std::vector<Text>& out) const override {
     std::vector<Text> words;
@@ -468,19 +498,6 @@ struct MetaspacePre : PreTokenizer {
   }
 };
 
-// GPT-2's byte <-> printable code point table.
-inline const uint32_t* byte_to_char() {
-  static uint32_t table[256];
-  static std::once_flag once;
-  std::call_once(once, [] {
-    int n = 0;
-    for (int b = 0; b < 256; ++b) {
-      const bool keep = (b >= '!' && b <= '~') || (b >= 0xA1 && b <= 0xAC) || (b >= 0xAE && b <= 0xFF);
-      table[b] = keep ? (uint32_t)b : (uint32_t)(256 + n++);
-    }
-  });
-  return table;
-}
 struct ByteLevelPre : PreTokenizer {
   bool add_prefix_space = true, use_regex = true;
   std::unique_ptr<MiniRegex> re;
@@ -560,6 +577,11 @@ inline PreP make_pretokenizer(const Value& v) {
     const uint32_t delim = d[0];
     c->is_delim = [delim](uint32_t ch) { return ch == delim; };
     return c;
+  }
+  if (type == "FixedLength") {
+    auto f = std::make_unique<FixedLengthPre>();
+    f->length = (size_t)std::max<long long>(1, v["length"].as_int(5));
+    return f;
   }
   if (type == "BertPreTokenizer") return std::make_unique<BertPre>();
   if (type == "Punctuation") {

@@ -284,3 +284,16 @@ def test_sentencepiece_precompiled_character_map(tmp_path):
             "a\r\nb\rc\nd\t\te", "👩‍👩‍👧 ❤‍🔥 🇩🇪🇫🇷 👍🏽", "क्षत्रिय हिन्दी กำลัง น้ำ", "soft­hyphen zero​width ‍j ﻿bom", "ǅ ﬃ ẛ̣ ™ ² ³ ¼ № ㍿",
             "x́́́́ ำ ःa", "", " ", "   multiple   spaces   "]
     check(tmp_path, tok, SAMPLES + hard)
+
+
+def test_byte_level_normaliser_and_fixed_length_chunks(tmp_path):
+    """The byte-level alphabet applied by the normaliser (newer tokenizer files) with a plain split pattern behind it, and the
+    FixedLength pre-tokenizer."""
+    tok = Tokenizer(models.BPE())
+    tok.normalizer = normalizers.ByteLevel()
+    tok.pre_tokenizer = pre_tokenizers.Split(Regex("Ġ?[^Ġ]+"), behavior="isolated")
+    trainer = trainers.BpeTrainer(vocab_size=500, special_tokens=["<|endoftext|>"], initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), show_progress=False)
+    tok.train_from_iterator(corpus(), trainer)
+    check(tmp_path, tok, SAMPLES + ["a<|endoftext|>b"])
+    tok.pre_tokenizer = pre_tokenizers.FixedLength(3)
+    check(tmp_path, tok, SAMPLES[:40])
