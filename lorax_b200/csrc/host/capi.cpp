@@ -342,6 +342,26 @@ long lx_tokenizer_encode(void* hv, const char* text, size_t len, int add_special
   }
 }
 const char* lx_tokenizer_error(void* h) { return static_cast<TokHandle*>(h)->last_error.c_str(); }
+// All matches of `pattern` in `text` as a JSON array of [begin, end) code point offsets (the scan the Split pre-tokenizer and the
+// Replace normaliser do); "error: ..." when the pattern is outside the engine's subset.
+const char* lx_regex_find_all(const char* pattern, const char* text) {
+  std::string err;
+  auto re = MiniRegex::compile(pattern, &err);
+  if (!re) return ret("error: " + err);
+  const uni::Text t = uni::from_utf8(text);
+  json::Value out = json::Value::array();
+  size_t at = 0;
+  while (at <= t.size()) {
+    size_t b, e;
+    if (!re->search(t.data(), t.size(), at, &b, &e)) break;
+    json::Value m = json::Value::array();
+    m.push((unsigned long long)b);
+    m.push((unsigned long long)e);
+    out.push(m);
+    at = e > b ? e : b + 1;
+  }
+  return ret(out.dump());
+}
 // Normalisation form of a UTF-8 string ("NFC", "NFD", "NFKC", "NFKD", "lower"), for the Unicode tables' own test.
 const char* lx_unicode_normalize(const char* text, const char* form) {
   const std::string f = form;

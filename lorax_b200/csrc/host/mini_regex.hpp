@@ -48,10 +48,11 @@ class MiniRegex {
  private:
   struct Class {                              // a set of code points
     std::vector<std::pair<uint32_t, uint32_t>> ranges;
-    std::vector<std::pair<char, bool>> props;     // (property letter, negated): s d w L N P M S Z C
+    std::vector<std::pair<int, bool>> props;      // (property, negated): a letter of s d w L N P M S Z C, or 256 + a two-letter category
     bool negated = false;
     bool icase = false;
-    static bool prop(char p, uint32_t c) {
+    static bool prop(int p, uint32_t c) {
+      if (p >= 256) return uni::category_of(c) == p - 256;
       switch (p) {
         case 's': return uni::is_space(c);
         case 'd': return uni::is_decimal(c);
@@ -201,8 +202,8 @@ class MiniRegex {
       const uint32_t c = src[pos++];
       *is_lit = false;
       switch (c) {
-        case 's': case 'd': case 'w': cls.props.push_back({(char)c, false}); return true;
-        case 'S': case 'D': case 'W': cls.props.push_back({(char)(c + 32), true}); return true;
+        case 's': case 'd': case 'w': cls.props.push_back({(int)c, false}); return true;
+        case 'S': case 'D': case 'W': cls.props.push_back({(int)(c + 32), true}); return true;
         case 'p': case 'P': {
           std::string name;
           if (more() && peek() == '{') {
@@ -215,7 +216,7 @@ class MiniRegex {
           }
           bool neg = c == 'P';
           if (!name.empty() && name[0] == '^') { neg = !neg; name.erase(0, 1); }
-          char p = 0;
+          int p = 0;
           if (name == "L" || name == "Letter") p = 'L';
           else if (name == "N" || name == "Number") p = 'N';
           else if (name == "P" || name == "Punctuation") p = 'P';
@@ -223,7 +224,7 @@ class MiniRegex {
           else if (name == "S" || name == "Symbol") p = 'S';
           else if (name == "Z" || name == "Separator") p = 'Z';
           else if (name == "C" || name == "Other") p = 'C';
-          else if (name == "Nd") p = 'd';
+          else if (uni::category_index(name) >= 0) p = 256 + uni::category_index(name);
           else { err = "unsupported property \\p{" + name + "}"; return false; }
           cls.props.push_back({p, neg});
           return true;

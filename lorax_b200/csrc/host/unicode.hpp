@@ -84,6 +84,22 @@ inline bool is_word(uint32_t c) {
 }
 inline bool is_ascii_punct(uint32_t c) { return (c >= 33 && c <= 47) || (c >= 58 && c <= 64) || (c >= 91 && c <= 96) || (c >= 123 && c <= 126); }
 
+// Index of the code point's two-letter general category in kCatNames, -1 for unassigned code points and surrogates.
+inline int category_of(uint32_t c) {
+  int lo = 0, hi = kCat_n - 1;
+  while (lo <= hi) {
+    const int mid = (lo + hi) / 2;
+    if (c < kCat[mid][0]) hi = mid - 1;
+    else if (c > kCat[mid][1]) lo = mid + 1;
+    else return (int)kCat[mid][2];
+  }
+  return -1;
+}
+inline int category_index(const std::string& name) {
+  for (int i = 0; i < kCatNames_n; ++i) if (name == kCatNames[i]) return i;
+  return -1;
+}
+
 template <class Idx>
 inline const uint32_t* find3(const Idx& idx, int n, uint32_t cp) {
   int lo = 0, hi = n - 1;

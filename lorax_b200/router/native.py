@@ -43,6 +43,7 @@ def load():
         "lx_tokenizer_encode": ([c_void_p, c_char_p, ctypes.c_size_t, c_int, U32P, ctypes.c_size_t], ctypes.c_long),
         "lx_tokenizer_error": ([c_void_p], c_char_p),
         "lx_unicode_normalize": ([c_char_p, c_char_p], c_char_p),
+        "lx_regex_find_all": ([c_char_p, c_char_p], c_char_p),
     }
     for name, (args, res) in sig.items():
         f = getattr(lib, name)
@@ -150,3 +151,11 @@ class RouterTokenizer:
 
 def unicode_normalize(text: str, form: str) -> str:
     return load().lx_unicode_normalize(text.encode(), form.encode()).decode()
+
+
+def regex_find_all(pattern: str, text: str) -> List[List[int]]:
+    """Matches of the router's regex engine as [begin, end) code point offsets; ``ValueError`` for a pattern outside its subset."""
+    out = load().lx_regex_find_all(pattern.encode(), text.encode()).decode()
+    if out.startswith("error: "):
+        raise ValueError(out[7:])
+    return json.loads(out)

@@ -12,7 +12,7 @@ import pytest
 tokenizers = pytest.importorskip("tokenizers")
 from tokenizers import Regex, Tokenizer, decoders, models, normalizers, pre_tokenizers, processors, trainers  # noqa: E402
 
-from lorax_b200.router.native import RouterTokenizer, unicode_normalize  # noqa: E402
+from lorax_b200.router.native import RouterTokenizer, regex_find_all, unicode_normalize  # noqa: E402
 
 WORDS = ("the quick brown fox jumps over lazy dog tokenizer adapter LoRA B200 serving request batch prefill decode "
          "naïve café résumé straße Ελληνικά привет мир 日本語 中文 字 한국어 emoji 🙂 🚀 don't we're I'll it's 12345 3.14 "
@@ -297,3 +297,30 @@ def test_byte_level_normaliser_and_fixed_length_chunks(tmp_path):
     check(tmp_path, tok, SAMPLES + ["a<|endoftext|>b"])
     tok.pre_tokenizer = pre_tokenizers.FixedLength(3)
     check(tmp_path, tok, SAMPLES[:40])
+
+
+REGEX_CASES = [
+    GPT2_SPLIT, LLAMA3_SPLIT, QWEN2_SPLIT, r"\w+|[^\w\s]+", r" {2,}", r"a+?b", r"(a|ab)(c|bcd)(d*)", r"x*", r"(?i)straße|ǅ", r"[A-Z][a-z]+|[A-Z]+(?![a-z])",
+    r"\d{2,4}-\d{1,2}", r"(?<=\s)\S+|^\S+", r"(?<![a-z])[a-z]{3}\b", r"\p{Lu}\p{Ll}*|\p{Nd}+|\p{P}", r"[^\x00-\x7f]+", r"[\u4e00-\u9fff]|[a-z]+",
+    r"(?:ab)+c?|b{2,}?", r"\S+\s*?", r".+?(?=,|$)", r"[\-\]\[]+", r"\bfoo\B|\Bbar\b", r"(?i:[a-c]+)x", r"'(?:[sdmt]|ll|ve|re)",
+]
+REGEX_TEXTS = ["Hello, World! it's 2024-05-17 and we're HERE: fooBar barfoo food", "  leading  spaces\tand\nnewlines\r\n  ", "STRASSE straße Ǆ ǅ ǆ",
+               "日本語のテキスト abc 中文 XYZabc ABCx aBcX", "aab abcd abbbcdd xx-][-", "", "a", "1234-5 12-345 123456-78", "naïve café — “q” … ½ ①"]
+
+
+@pytest.mark.parametrize("pattern", REGEX_CASES)
+def test_regex_engine_matches_like_a_backtracking_reference(pattern):
+    """The router's regex engine against the `regex` package (same leftmost, first-alternative-wins semantics as the engine the
+    library splits with) on the split patterns of well-known tokenizers and on constructs each alone."""
+    rx = pytest.importorskip("regex")
+    flags = rx.V0
+    want_re = rx.compile(pattern, flags)
+    for text in REGEX_TEXTS:
+        want = [[m.start(), m.end()] for m in want_re.finditer(text)]
+        assert regex_find_all(pattern, text) == want, (pattern, text)
+
+
+def test_regex_engine_refuses_what_it_does_not_implement():
+    for pattern in [r"(a)\1", r"(?P<n>a)", r"(?<=a+)b", r"[[:alpha:]]", r"a{1000}"]:
+        with pytest.raises(ValueError):
+            regex_find_all(pattern, "aab")
