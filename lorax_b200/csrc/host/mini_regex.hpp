@@ -48,10 +48,11 @@ class MiniRegex {
  private:
   struct Class {                              // a set of code points
     std::vector<std::pair<uint32_t, uint32_t>> ranges;
-    std::vector<std::pair<int, bool>> props;      // (property, negated): a letter of s d w L N P M S Z C, or 256 + a two-letter category
+    std::vector<std::pair<int, bool>> props;      // (property, negated): a letter of s d w L N P M S Z C, 256 + a two-letter category, or 512 + a script
     bool negated = false;
     bool icase = false;
     static bool prop(int p, uint32_t c) {
+      if (p >= 512) return uni::script_of(c) == p - 512;
       if (p >= 256) return uni::category_of(c) == p - 256;
       switch (p) {
         case 's': return uni::is_space(c);
@@ -196,6 +197,12 @@ class MiniRegex {
       n->cls.ranges.push_back({c, c});
       return n;
     }
+    // \p{Han}, \p{IsHan}, \p{Script=Han}, \p{sc=Han}, \p{scx=Han} (script extensions are read as the script)
+    static int script_name(std::string name) {
+      for (const char* pre : {"Script=", "Script_Extensions=", "sc=", "scx=", "Is"})
+        if (name.rfind(pre, 0) == 0) { name.erase(0, std::string(pre).size()); break; }
+      return uni::script_index(name);
+    }
     // After a backslash: a class escape adds to `cls` and returns true; a character escape sets `*lit`.
     bool escape(Class& cls, uint32_t* lit, bool* is_lit) {
       if (!more()) { err = "dangling backslash"; return false; }
@@ -225,6 +232,7 @@ class MiniRegex {
           else if (name == "Z" || name == "Separator") p = 'Z';
           else if (name == "C" || name == "Other") p = 'C';
           else if (uni::category_index(name) >= 0) p = 256 + uni::category_index(name);
+          else if (script_name(name) >= 0) p = 512 + script_name(name);
           else { err = "unsupported property \\p{" + name + "}"; return false; }
           cls.props.push_back({p, neg});
           return true;

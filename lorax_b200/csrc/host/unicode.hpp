@@ -100,6 +100,22 @@ inline int category_index(const std::string& name) {
   return -1;
 }
 
+// Index of the code point's script in kScriptNames (the scripts the table lists), -1 otherwise.
+inline int script_of(uint32_t c) {
+  int lo = 0, hi = kScript_n - 1;
+  while (lo <= hi) {
+    const int mid = (lo + hi) / 2;
+    if (c < kScript[mid][0]) hi = mid - 1;
+    else if (c > kScript[mid][1]) lo = mid + 1;
+    else return (int)kScript[mid][2];
+  }
+  return -1;
+}
+inline int script_index(const std::string& name) {
+  for (int i = 0; i < kScriptNames_n; ++i) if (name == kScriptNames[i]) return i;
+  return -1;
+}
+
 template <class Idx>
 inline const uint32_t* find3(const Idx& idx, int n, uint32_t cp) {
   int lo = 0, hi = n - 1;

@@ -302,10 +302,10 @@ def test_byte_level_normaliser_and_fixed_length_chunks(tmp_path):
 REGEX_CASES = [
     GPT2_SPLIT, LLAMA3_SPLIT, QWEN2_SPLIT, r"\w+|[^\w\s]+", r" {2,}", r"a+?b", r"(a|ab)(c|bcd)(d*)", r"x*", r"(?i)straße|ǅ", r"[A-Z][a-z]+|[A-Z]+(?![a-z])",
     r"\d{2,4}-\d{1,2}", r"(?<=\s)\S+|^\S+", r"(?<![a-z])[a-z]{3}\b", r"\p{Lu}\p{Ll}*|\p{Nd}+|\p{P}", r"[^\x00-\x7f]+", r"[\u4e00-\u9fff]|[a-z]+",
-    r"(?:ab)+c?|b{2,}?", r"\S+\s*?", r".+?(?=,|$)", r"[\-\]\[]+", r"\bfoo\B|\Bbar\b", r"(?i:[a-c]+)x", r"'(?:[sdmt]|ll|ve|re)",
+    r"\p{Han}+|\p{Hiragana}+|\p{IsKatakana}+|\p{Script=Latin}+|\p{sc=Cyrillic}+|\P{Common}", r"(?:ab)+c?|b{2,}?", r"\S+\s*?", r".+?(?=,|$)", r"[\-\]\[]+", r"\bfoo\B|\Bbar\b", r"(?i:[a-c]+)x", r"'(?:[sdmt]|ll|ve|re)",
 ]
 REGEX_TEXTS = ["Hello, World! it's 2024-05-17 and we're HERE: fooBar barfoo food", "  leading  spaces\tand\nnewlines\r\n  ", "STRASSE straße Ǆ ǅ ǆ",
-               "日本語のテキスト abc 中文 XYZabc ABCx aBcX", "aab abcd abbbcdd xx-][-", "", "a", "1234-5 12-345 123456-78", "naïve café — “q” … ½ ①"]
+               "日本語のテキスト abc 中文 XYZabc ABCx aBcX привет ーー",  "aab abcd abbbcdd xx-][-", "", "a", "1234-5 12-345 123456-78", "naïve café — “q” … ½ ①"]
 
 
 @pytest.mark.parametrize("pattern", REGEX_CASES)
