@@ -474,6 +474,27 @@ struct FixedLengthPre : PreTokenizer {         // chunks of `length` characters
     for (size_t i = 0; i < t.size(); i += length) out.emplace_back(t.begin() + (long)i, t.begin() + (long)std::min(t.size(), i + length));
   }
 };
+struct UnicodeScriptsPre : PreTokenizer {      // a new piece wherever the script changes; spaces belong to the piece in front
+  int han, hiragana, katakana;
+  UnicodeScriptsPre() : han(uni::script_index("Han")), hiragana(uni::script_index("Hiragana")), katakana(uni::script_index("Katakana")) {
+    if (han < 0 || hiragana < 0) throw Unsupported("UnicodeScripts pre-tokenizer (built without the script tables)");
+  }
+  void apply(const Text& t, bool, std::vector<Text>& out) const override {
+    constexpr int kAny = -2, kNone = -3;
+    int last = kNone;
+    std::vector<size_t> cuts;                 // the first one sits at the first character that is not a space: spaces in front are dropped
+    for (size_t i = 0; i < t.size(); ++i) {
+      const uint32_t c = t[i];
+      int sc = uni::script_of(c);
+      if (c == 0x30FC || sc == hiragana || sc == katakana) sc = han;       // Japanese text stays together
+      if (c == ' ') sc = kAny;
+      if (sc != kAny && last != sc) cuts.push_back(i);
+      if (sc != kAny) last = sc;
+    }
+    cuts.push_back(t.size());
+    for (size_t k = 0; k + 1 < cuts.size(); ++k) out.emplace_back(t.begin() + (long)cuts[k], t.begin() + (long)cuts[k + 1]);
+  }
+};
 struct BertPre : PreTokenizer {
   void apply(const Text& t, bool, std::vector<Text>& out) const override {
     std::vector<Text> words;
@@ -583,6 +604,7 @@ inline PreP make_pretokenizer(const Value& v) {
     f->length = (size_t)std::max<long long>(1, v["length"].as_int(5));
     return f;
   }
+  if (type == "UnicodeScripts") return std::make_unique<UnicodeScriptsPre>();
   if (type == "BertPreTokenizer") return std::make_unique<BertPre>();
   if (type == "Punctuation") {
     auto c = std::make_unique<CharPre>();

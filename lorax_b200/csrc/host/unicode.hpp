@@ -100,7 +100,7 @@ inline int category_index(const std::string& name) {
   return -1;
 }
 
-// Index of the code point's script in kScriptNames (the scripts the table lists), -1 otherwise.
+// The code point's script as the id kScriptIds gives its names, -1 for code points without one.
 inline int script_of(uint32_t c) {
   int lo = 0, hi = kScript_n - 1;
   while (lo <= hi) {
@@ -111,8 +111,10 @@ inline int script_of(uint32_t c) {
   }
   return -1;
 }
-inline int script_index(const std::string& name) {
-  for (int i = 0; i < kScriptNames_n; ++i) if (name == kScriptNames[i]) return i;
+inline int script_index(const std::string& name) {          // "Han", "han", "Old_Italic": case, '_', '-' and spaces do not count
+  std::string key;
+  for (char ch : name) if (ch != '_' && ch != '-' && ch != ' ') key.push_back((char)(ch >= 'a' && ch <= 'z' ? ch - 32 : ch));
+  for (int i = 0; i < kScriptNames_n; ++i) if (key == kScriptNames[i]) return kScriptIds[i];
   return -1;
 }
 

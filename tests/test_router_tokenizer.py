@@ -297,6 +297,8 @@ def test_byte_level_normaliser_and_fixed_length_chunks(tmp_path):
     check(tmp_path, tok, SAMPLES + ["a<|endoftext|>b"])
     tok.pre_tokenizer = pre_tokenizers.FixedLength(3)
     check(tmp_path, tok, SAMPLES[:40])
+    tok.pre_tokenizer = pre_tokenizers.UnicodeScripts()           # cuts where the script changes
+    check(tmp_path, tok, SAMPLES + ["Apples are りんご 林檎", " a  b ", "   ", "abc123, def! привет мир ーー カタカナ"])
 
 
 REGEX_CASES = [
