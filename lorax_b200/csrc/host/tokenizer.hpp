@@ -690,6 +690,7 @@ struct Bpe : Model {
   std::unordered_map<uint64_t, std::pair<uint32_t, uint32_t>, PairHash> merges;     // (a, b) -> (rank, merged id)
   std::optional<uint32_t> unk;
   bool fuse_unk = false, byte_fallback = false, ignore_merges = false;
+  std::string subword_prefix, word_suffix;      // continuing_subword_prefix ("##"), end_of_word_suffix ("</w>") of older BPE files
   uint32_t byte_ids[256];
   bool have_bytes = false;
 
@@ -706,14 +707,19 @@ struct Bpe : Model {
     bool pending_unk = false;
     auto push = [&](uint32_t id) { syms.push_back(Sym{id, (int)syms.size() - 1, (int)syms.size() + 1, true}); };
     std::string ch;
-    for (uint32_t c : piece) {
+    for (size_t ci = 0; ci < piece.size(); ++ci) {
+      const uint32_t c = piece[ci];
       ch.clear();
+      if (ci > 0) ch = subword_prefix;
       uni::append_utf8(ch, c);
+      if (ci + 1 == piece.size()) ch += word_suffix;
       auto it = vocab.find(ch);
       if (it != vocab.end()) { pending_unk = false; push(it->second); continue; }
       if (byte_fallback && have_bytes) {
         pending_unk = false;
-        for (unsigned char b : ch) push(byte_ids[b]);
+        std::string raw;
+        uni::append_utf8(raw, c);
+        for (unsigned char b : raw) push(byte_ids[b]);
         continue;
       }
       if (unk) {
@@ -866,8 +872,8 @@ inline std::unique_ptr<Model> make_model(const Value& v) {
   if (type == "BPE") {
     auto m = std::make_unique<Bpe>();
     if (v["dropout"].is_number() && v["dropout"].as_double() > 0) throw Unsupported("BPE dropout");
-    if (v["continuing_subword_prefix"].is_string() && !v["continuing_subword_prefix"].as_string().empty()) throw Unsupported("BPE continuing_subword_prefix");
-    if (v["end_of_word_suffix"].is_string() && !v["end_of_word_suffix"].as_string().empty()) throw Unsupported("BPE end_of_word_suffix");
+    if (v["continuing_subword_prefix"].is_string()) m->subword_prefix = v["continuing_subword_prefix"].as_string();
+    if (v["end_of_word_suffix"].is_string()) m->word_suffix = v["end_of_word_suffix"].as_string();
     m->vocab = read_vocab(v["vocab"]);
     m->fuse_unk = v["fuse_unk"].as_bool(false);
     m->byte_fallback = v["byte_fallback"].as_bool(false);
@@ -886,7 +892,10 @@ inline std::unique_ptr<Model> make_model(const Value& v) {
         if (sp == std::string::npos) throw Unsupported("malformed merge `" + s + "`");
         a = s.substr(0, sp); b = s.substr(sp + 1);
       }
-      auto ia = m->vocab.find(a), ib = m->vocab.find(b), im = m->vocab.find(a + b);
+      // the merged token drops the continuation prefix of its right half
+      const std::string& pre = m->subword_prefix;
+      const std::string ab = (!pre.empty() && b.rfind(pre, 0) == 0) ? a + b.substr(pre.size()) : a + b;
+      auto ia = m->vocab.find(a), ib = m->vocab.find(b), im = m->vocab.find(ab);
       if (ia == m->vocab.end() || ib == m->vocab.end() || im == m->vocab.end()) throw Unsupported("merge `" + a + " " + b + "` names a token outside the vocabulary");
       m->merges.emplace((uint64_t)ia->second << 32 | ib->second, std::make_pair(rank, im->second));
       ++rank;

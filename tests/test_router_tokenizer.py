@@ -326,3 +326,14 @@ def test_regex_engine_refuses_what_it_does_not_implement():
     for pattern in [r"(a)\1", r"(?P<n>a)", r"(?<=a+)b", r"[[:alpha:]]", r"a{1000}"]:
         with pytest.raises(ValueError):
             regex_find_all(pattern, "aab")
+
+
+def test_bpe_with_word_suffix_and_continuation_prefix(tmp_path):
+    """Older BPE files: `</w>` closes a word (CLIP, GPT-1), `##` marks a continuation."""
+    for kw in ({"end_of_word_suffix": "</w>"}, {"continuing_subword_prefix": "##"}, {"continuing_subword_prefix": "@@", "end_of_word_suffix": "</w>"}):
+        tok = Tokenizer(models.BPE(unk_token="<unk>", **kw))
+        tok.normalizer = normalizers.Sequence([normalizers.NFC(), normalizers.Lowercase()])
+        tok.pre_tokenizer = pre_tokenizers.Sequence([pre_tokenizers.Whitespace(), pre_tokenizers.Digits(individual_digits=True)])
+        trainer = trainers.BpeTrainer(vocab_size=400, special_tokens=["<unk>", "<|startoftext|>", "<|endoftext|>"], show_progress=False, **kw)
+        tok.train_from_iterator(corpus(), trainer)
+        check(tmp_path, tok)
