@@ -168,7 +168,7 @@ class FusedCollectives:
         return self.ar_out[: T * N].view(T, N)
 
     def all_reduce_self_test(self) -> bool:
-        """Two reductions of known values (a small and a large one, odd sizes) against the exact sums.  The verdict is combined
+        """Two reductions of known values (a small and a large one, odd sizes) against the exact sums.  The outcome is combined
         over the ranks with NCCL, so either every rank uses the kernel or none does."""
         import torch.distributed as dist
         ok = True
@@ -203,7 +203,7 @@ def enable(tp, model, max_rows: int = 512) -> FusedCollectives:
         # (with parallel residuals two all-reduce results are alive at once; the kernel keeps one output area)
         fc.setup_all_reduce(int(os.environ.get("LORAX_SYM_ALLREDUCE_TOKENS", "4352")), model.hidden)
         if not fc.all_reduce_self_test():
-            fc.ar_ptrs = None                   # every rank agrees (the verdict is itself reduced): NCCL carries the all-reduces
+            fc.ar_ptrs = None                   # every rank agrees (the outcome is itself reduced): NCCL carries the all-reduces
             print(json.dumps({"level": "WARN", "message": "two-shot all-reduce kernel failed its self test; using NCCL"}), flush=True)
     if model.embed is not None and model.embed.is_cuda and model.embed.dtype == torch.bfloat16 and model.pos_embed is None:
         model.embed = fc.share_embedding(model.embed, model.vocab_local * tp.world_size)
