@@ -46,6 +46,8 @@ def reference_arm(args):
     module, the importing file and the other native modules of that path that are missing here."""
     import importlib
     import traceback
+    if int(os.environ.get("RANK", "0")) != 0:        # launched one process per GPU: rank 0 prints the one line
+        return 0
     ref_root = os.path.join(REPO, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref_root, "lorax_server")):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/lorax_server is absent: run baseline/install_reference.py "
