@@ -765,6 +765,10 @@ def load_tokenizer(model_dir: str):
         return None
     from tokenizers import Tokenizer
     tok = Tokenizer.from_file(path)
+    # some files carry the padding / truncation of the run that saved them (sentence-transformers: pad to 128, cut at 512);
+    # transformers resets both on every call, and serving wants neither: length limits are the router's validation
+    tok.no_padding()
+    tok.no_truncation()
     cfg_path = os.path.join(model_dir, "tokenizer_config.json")
     if os.path.exists(cfg_path):
         try:

@@ -240,6 +240,12 @@ def test_llama_tokenizer_class_gets_the_bos_template_on_both_sides(tmp_path):
     assert mine.encode("hello world") == ids
     (mdir / "tokenizer_config.json").write_text(json.dumps({"tokenizer_class": "GPT2Tokenizer", "bos_token": "<s>"}))
     assert load_tokenizer(str(mdir)).encode("hello world").ids == ids[1:-1]
+    # padding and truncation saved with the file are dropped on load: both sides see the whole text and nothing else
+    state["padding"] = {"strategy": {"Fixed": 16}, "direction": "Right", "pad_to_multiple_of": None, "pad_id": 0, "pad_type_id": 0, "pad_token": "<unk>"}
+    state["truncation"] = {"direction": "Right", "max_length": 4, "strategy": "LongestFirst", "stride": 0}
+    (mdir / "tokenizer.json").write_text(json.dumps(state))
+    assert Tokenizer.from_file(str(mdir / "tokenizer.json")).encode("hello world").ids != ids[1:-1]
+    assert load_tokenizer(str(mdir)).encode("hello world").ids == ids[1:-1]
 
 
 @pytest.mark.parametrize("behavior", ["isolated", "removed", "merged_with_previous", "merged_with_next", "contiguous"])
