@@ -155,9 +155,10 @@ class DecoderModel:
         self.use_native_layers = self.device.type == "cuda" and os.environ.get("LORAX_NATIVE_LAYERS", "1") != "0"
         # LoRA inside the GEMM launch for steps of up to this many rows (0: always separate shrink / expand kernels).  Measured on
         # B200 over the four projections of a Mistral-7B layer with 100 rank-16 adapters: 0.30 ms against 0.38 ms for the three
-        # launches at 256 rows, 0.57 against 0.63 at 1024, 1.74 against 2.00 at 4096.  A step with more table entries than the
-        # kernel holds (512) falls back to the separate kernels by itself.
-        self.fused_lora_max_tokens = int(os.environ.get("LORAX_FUSED_LORA_MAX_TOKENS", "8192")) if os.environ.get("LORAX_FUSED_LORA", "1") != "0" else 0
+        # launches at 256 rows, 0.57 against 0.63 at 1024, 1.74 against 2.00 at 4096; steps of 8192 prompt tokens plus their decode rows
+        # (Llama-3-8B, fp8 weights expanded per projection) gained 4 % end to end.  A step with more table entries than the kernel
+        # holds (512) falls back to the separate kernels by itself.
+        self.fused_lora_max_tokens = int(os.environ.get("LORAX_FUSED_LORA_MAX_TOKENS", "16384")) if os.environ.get("LORAX_FUSED_LORA", "1") != "0" else 0
         self.fused_lora = self.fused_lora_max_tokens > 0
         self.kv_scales = None        # per layer (k scale, v scale) of an e4m3 KV cache, set when the cache is built
         self.gated = c.model_type not in ("gpt2", "gpt_bigcode", "gpt_neox", "falcon", "RefinedWeb", "RefinedWebModel", "phi", "bloom",
@@ -396,13 +397,17 @@ class DecoderModel:
         ts = tok_slot if tok_slot is not None else inp.tok_slot
         epi = None
         if (self.fused_lora and x.shape[0] <= self.fused_lora_max_tokens and self.adapters is not None and ts is not None
-                and inp.lora_tiles is not None and x.is_cuda
-                and isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 and x.dtype == torch.bfloat16):
-            lf = self.adapters.fused(group, layer, inp.lora_tiles)
+                and inp.lora_tiles is not None and x.is_cuda and x.dtype == torch.bfloat16):
+            bf16_w = isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16
+            # long steps run fp8 projections as bf16 GEMMs over expanded weights anyway: the adapters ride in that launch too
+            fp8_long = isinstance(w, Fp8Weight) and x.shape[0] >= getattr(self.ops, "FP8_EXPAND_MIN_TOKENS", 1 << 30)
+            lf = self.adapters.fused(group, layer, inp.lora_tiles) if (bf16_w or fp8_long) else None
             if lf is not None:
-                y = self.ops.gemm_lora_fused(x, w, lf, bias=b, out=out)      # shrink, base GEMM and expand: one launch
-                if y is not None:
-                    return y
+                wb = w if bf16_w else self.ops.fp8_expand(w.q, w.scale)
+                if wb is not None:
+                    y = self.ops.gemm_lora_fused(x, wb, lf, bias=b, out=out)      # shrink, base GEMM and expand: one launch
+                    if y is not None:
+                        return y
         if self.adapters is not None and ts is not None:
             epi = self.adapters.shrink(self.ops, x, ts, group, layer, tiles=inp.lora_tiles)
         if epi is None:

@@ -192,9 +192,9 @@ class LoraEpilogue(NamedTuple):
 # 1 (default): the GEMM that carries LoRA acquire-fences a slot's B_cat tensor map before every use, as a tensor map that lives
 # in global memory and was written by a copy asks for; 0 skips it (measurement: the fences cost about 3 % of a decode step).
 LORA_FENCE_MAPS = int(os.environ.get("LORAX_LORA_FENCE_MAPS", "1"))
-TC_PREFILL = os.environ.get("LORAX_TC_PREFILL", "1") != "0"
+TC_PREFILL = os.environ.get("LORAX_TC_PREFILL", "1") != "0"       # 0: the mma.sync prefill attention kernel for every shape
 # rows from which an fp8 projection is expanded to bf16 in front of the bf16 GEMM instead of running on the fp8 tensor-core kernel
-FP8_EXPAND_MIN_TOKENS = int(os.environ.get("LORAX_FP8_EXPAND_MIN_TOKENS", "512"))       # 0: the mma.sync prefill attention kernel for every shape
+FP8_EXPAND_MIN_TOKENS = int(os.environ.get("LORAX_FP8_EXPAND_MIN_TOKENS", "512"))
 
 
 class LxLoraFused(ctypes.Structure):
@@ -362,6 +362,22 @@ def quant_act_fp8(x: torch.Tensor):
     return xq, sa
 
 
+def fp8_expand(wq: torch.Tensor, w_scale: torch.Tensor) -> Optional[torch.Tensor]:
+    """Block-scaled e4m3 weights [N, K] -> bf16 [N, K] in the workspace's scratch buffer (valid until the next call; consumers are
+    queued on the same stream).  None when the layout does not fit the kernel (K or the row pitch not a multiple of 16)."""
+    N, K = wq.shape
+    if K % 16 != 0 or wq.stride(0) % 16 != 0:
+        return None
+    ws = workspace(wq.device)
+    need = N * K
+    if ws.fp8_scratch is None or ws.fp8_scratch.numel() < need:
+        ws.fp8_scratch = torch.empty(need, dtype=torch.bfloat16, device=wq.device)
+    w16 = ws.fp8_scratch[:need].view(N, K)
+    _check(load().lx_fp8_block128_dequant(_ptr(wq), wq.stride(0), _ptr(w_scale), w_scale.stride(0), _ptr(w16), K, N, K, _stream()),
+           "lx_fp8_block128_dequant")
+    return w16
+
+
 def gemm_fp8(x: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, bias: Optional[torch.Tensor] = None,
              out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[T, N] = x[T, K] @ dequant(wq[N, K], w_scale[N/128, K/128])^T (+ bias): activations are quantised to e4m3 per
@@ -373,16 +389,12 @@ def gemm_fp8(x: torch.Tensor, wq: torch.Tensor, w_scale: torch.Tensor, bias: Opt
     if out is None:
         out = torch.empty(T, N, dtype=torch.bfloat16, device=x.device)
     ws = workspace(x.device)
-    if T >= FP8_EXPAND_MIN_TOKENS and K % 16 == 0 and wq.stride(0) % 16 == 0:
+    if T >= FP8_EXPAND_MIN_TOKENS:
         # long prefills: expand this projection's weights to bf16 (one pass, a few per cent of the GEMM) and run the bf16 GEMM; the
         # fp8 tensor-core kernel below is bound by the per-128 promotion of its partial sums at this size
-        need = N * K
-        if ws.fp8_scratch is None or ws.fp8_scratch.numel() < need:
-            ws.fp8_scratch = torch.empty(need, dtype=torch.bfloat16, device=x.device)
-        w16 = ws.fp8_scratch[:need].view(N, K)
-        _check(load().lx_fp8_block128_dequant(_ptr(wq), wq.stride(0), _ptr(w_scale), w_scale.stride(0), _ptr(w16), K, N, K, _stream()),
-               "lx_fp8_block128_dequant")
-        return gemm(x, w16, bias=bias, out=out)
+        w16 = fp8_expand(wq, w_scale)
+        if w16 is not None:
+            return gemm(x, w16, bias=bias, out=out)
     xq, sa = quant_act_fp8(x)
     rc = load().lx_gemm_fp8_block128(_ptr(xq), xq.stride(0), _ptr(sa), sa.stride(0), _ptr(wq), wq.stride(0), _ptr(w_scale), _ptr(out),
                                      out.stride(0), _ptr(bias), T, N, K, _ptr(ws.gemm_ws), ws.gemm_ws.numel(), _ptr(ws.status),

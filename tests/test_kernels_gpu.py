@@ -605,3 +605,52 @@ def test_gemm_fp8_block128(nat, T, N, K):
     # and the quantised product is close to the bf16 one
     full = x.float() @ w.float().t() + b.float()
     assert _rel_err(out, full) < 6e-2
+
+
+def test_fp8_weights_expanded_for_long_steps_carry_lora_in_the_gemm_launch(nat):
+    """A long step over block-scaled e4m3 weights: the weights are expanded to bf16 once and the GEMM that carries the adapters runs
+    over them; against fp32 PyTorch on the dequantised weights."""
+    torch.manual_seed(11)
+    T, K, parts, ranks = 640, 1024, [512, 256], [16, 32]
+    nparts, N = len(parts), sum(parts)
+    layer_units = nparts * K + N
+    bases, off = [], 0
+    for r in ranks:
+        bases.append(off)
+        off += (r * layer_units + 63) // 64 * 64
+    arena = (torch.randn(off, device="cuda") * 0.05).to(torch.bfloat16)
+    slot_base = torch.tensor(bases, device="cuda", dtype=torch.int64)
+    slot_rank = torch.tensor(ranks, device="cuda", dtype=torch.int32)
+    G = 5
+    tm_host = torch.zeros(len(ranks) * 2 * G * 128, dtype=torch.uint8).pin_memory()
+    for s_, r in enumerate(ranks):
+        nat.lora_encode_tmap(tm_host[(s_ * 2 * G) * 128:], arena.data_ptr() + bases[s_] * 2, K, nparts * r, r * layer_units, 1)
+        nat.lora_encode_tmap_b(tm_host[(s_ * 2 * G + G) * 128:], arena.data_ptr() + (bases[s_] + r * nparts * K) * 2, r, N, r * layer_units, 1)
+    tmaps = tm_host.cuda()
+    rows = [0] * 200 + [-1] * 40 + [1] * 400
+    tl = ref.build_lora_tiles(rows, 32)
+    tiles = torch.cat([torch.tensor(tl, device="cuda", dtype=torch.int32).view(-1, 4), torch.full((7, 4), -1, device="cuda", dtype=torch.int32)])
+    w = torch.randn(N, K, device="cuda", dtype=torch.bfloat16) / math.sqrt(K)
+    wq, wscale = ref.quantize_weight_fp8_block128(w)
+    x = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    w16 = nat.fp8_expand(wq.view(torch.uint8), wscale)
+    assert w16 is not None
+    wd = ref.dequantize_weight_fp8_block128(wq, wscale)[:N, :K].float()
+    assert _rel_err(w16.float(), wd) < 1e-2
+    lf = nat.LoraFused(tiles, tiles.shape[0], len(tl), tmaps, 2 * G, 0, G, slot_rank, slot_base, nparts, parts[0], N, 0, max(ranks), arena, 0, nparts * K)
+    got = nat.gemm_lora_fused(x, w16, lf)
+    assert got is not None
+    torch.cuda.synchronize()
+    nat.workspace().check_status()
+    want = x.float() @ wd.t()
+    bounds = [0, parts[0], N]
+    for sl in (0, 1):
+        r = ranks[sl]
+        idx = torch.tensor([t for t, s_ in enumerate(rows) if s_ == sl], device="cuda")
+        A = arena[bases[sl]:][: nparts * r * K].view(nparts * r, K).float()
+        B = arena[bases[sl] + r * nparts * K:][: N * r].view(N, r).float()
+        v = (x[idx].float() @ A.t()).to(torch.bfloat16).float()
+        for pp in range(nparts):
+            lo, hi = bounds[pp], bounds[pp + 1]
+            want[idx, lo:hi] += v[:, pp * r:(pp + 1) * r] @ B[lo:hi].t()
+    assert _rel_err(got, want) < 6e-3
