@@ -761,8 +761,10 @@ struct Bpe : Model {
 };
 
 struct Unigram : Model {
-  struct TrieNode { std::unordered_map<unsigned char, int> next; int piece = -1; };
-  std::vector<TrieNode> trie{1};
+  // byte trie over the pieces: one hash map of (node, byte) -> node for the whole vocabulary (a quarter of a million pieces in
+  // multilingual models), piece id per node
+  std::unordered_map<uint64_t, int> edges;
+  std::vector<int> piece_of{-1};
   std::vector<double> scores;
   std::optional<uint32_t> unk;
   double min_score = 0;
@@ -770,20 +772,22 @@ struct Unigram : Model {
   uint32_t byte_ids[256];
   bool have_bytes = false;
 
+  int step(int node, unsigned char b) const {
+    auto it = edges.find((uint64_t)node << 8 | b);
+    return it == edges.end() ? -1 : it->second;
+  }
   void add(const std::string& piece, int id) {
     int node = 0;
     for (unsigned char b : piece) {
-      auto it = trie[(size_t)node].next.find(b);
-      if (it == trie[(size_t)node].next.end()) {
-        trie.emplace_back();
-        const int fresh = (int)trie.size() - 1;
-        trie[(size_t)node].next.emplace(b, fresh);
-        node = fresh;
-      } else {
-        node = it->second;
+      int next = step(node, b);
+      if (next < 0) {
+        next = (int)piece_of.size();
+        piece_of.push_back(-1);
+        edges.emplace((uint64_t)node << 8 | b, next);
       }
+      node = next;
     }
-    trie[(size_t)node].piece = id;
+    piece_of[(size_t)node] = id;
   }
   // Best segmentation by total score (Viterbi over byte positions); a character no piece covers costs the lowest score minus 10
   // and becomes the unknown token; neighbouring unknowns are one token.
@@ -802,10 +806,9 @@ struct Unigram : Model {
       bool single = false;
       int node = 0;
       for (size_t k = at; k < n; ++k) {
-        auto it = trie[(size_t)node].next.find((unsigned char)s[k]);
-        if (it == trie[(size_t)node].next.end()) break;
-        node = it->second;
-        const int id = trie[(size_t)node].piece;
+        node = step(node, (unsigned char)s[k]);
+        if (node < 0) break;
+        const int id = piece_of[(size_t)node];
         if (id >= 0) {
           const size_t end = k + 1;
           const double cand = base + scores[(size_t)id];
