@@ -4,6 +4,7 @@
 // commented out: router/src/loader.rs:345-564).
 #include <cstring>
 
+#include "encoder_batcher.hpp"
 #include "infer.hpp"
 #include "json.hpp"
 #include "tokenizer.hpp"
@@ -27,6 +28,7 @@ class FakeShard : public ShardClient {
   int decodes = 0;
   uint32_t block_size = 16;
   std::set<uint32_t> loaded;
+  std::vector<size_t> embed_batches;                  // sizes of the Embed batches seen
 
   std::string call(uint32_t method, const std::string& payload) override {
     std::lock_guard<std::mutex> g(mu);
@@ -128,6 +130,40 @@ class FakeShard : public ShardClient {
           }
         }
         return std::string((const char*)ids.data(), ids.size() * 4);
+      }
+      case gen::M_Embed: {
+        // embedding of request i: [number of input ids, first id, batch size]; a request whose text is "boom" fails the batch
+        gen::EmbedRequest q;
+        q.parse(payload);
+        gen::EmbedResponse r;
+        const gen::Batch none;
+        const gen::Batch& bt = q.batch ? *q.batch : none;
+        embed_batches.push_back(bt.requests.size());
+        for (auto& rq : bt.requests) {
+          if (rq.inputs == "boom") { r.errorMsg = "the encoder exploded"; r.embeddings.clear(); return r.serialize(); }
+          gen::Embedding e;
+          e.request_id = rq.id;
+          const auto& ids = rq.tokenized_inputs ? rq.tokenized_inputs->ids : std::vector<uint32_t>{};
+          e.values = {(float)ids.size(), ids.empty() ? -1.f : (float)ids[0], (float)bt.requests.size()};
+          r.embeddings.push_back(e);
+        }
+        std::this_thread::sleep_for(std::chrono::milliseconds(2));        // long enough for the next batch to fill up
+        return r.serialize();
+      }
+      case gen::M_Classify: {
+        gen::ClassifyRequest q;
+        q.parse(payload);
+        gen::ClassifyResponse r;
+        const gen::Batch none;
+        const gen::Batch& bt = q.batch ? *q.batch : none;
+        for (auto& rq : bt.requests) {
+          gen::ClassifyPredictionList l;
+          l.request_id = rq.id;
+          const size_t n = rq.tokenized_inputs ? rq.tokenized_inputs->ids.size() : 0;
+          for (size_t i = 0; i < n; ++i) { l.predictions.push_back("TAG" + std::to_string(i % 3)); l.scores.push_back(0.5f); }
+          r.classify_prediction_lists.push_back(l);
+        }
+        return r.serialize();
       }
       default: throw ShardError("method not implemented by the fake shard");
     }
@@ -306,6 +342,50 @@ const char* lx_infer_fake_run(const char* requests_json, int max_active_adapters
   json::Value log = json::Value::array();
   for (auto& l : fake->log) log.push(l);
   out.set("log", log);
+  out.set("metrics", metrics.render());
+  return ret(out.dump());
+}
+
+// Embed / classify inputs from `threads` caller threads, `each` inputs per thread, through the encoder batcher against the fake
+// shard.  JSON: {"ok": answers that carried the caller's own input, "failed": answers that were errors, "batches": [sizes]}.  Every
+// seventh input of thread 0 is the text that makes the fake shard fail its batch.
+const char* lx_encoder_batcher_fake_run(int threads, int each) {
+  auto fake = std::make_shared<FakeShard>();
+  auto client = std::make_shared<ShardedClient>(std::vector<std::shared_ptr<ShardClient>>{fake});
+  Metrics metrics(1024, 2048);
+  std::atomic<int> ok{0}, failed{0}, wrong{0};
+  {
+    EncoderBatcher::Limits lim;
+    lim.max_input_length = 64;
+    lim.max_batch_tokens = 256;
+    EncoderBatcher batcher(client, lim, &metrics);
+    std::vector<std::thread> ts;
+    for (int t = 0; t < threads; ++t)
+      ts.emplace_back([&, t] {
+        for (int k = 0; k < each; ++k) {
+          const bool boom = t == 0 && k % 7 == 3;
+          std::string text = boom ? "boom" : "";
+          for (int w = 0; !boom && w <= (t + k) % 5; ++w) text += "w" + std::to_string(t * 1000 + k) + " ";
+          const bool classify = (t + k) % 4 == 0 && !boom;
+          try {
+            auto res = batcher.submit(classify ? EncoderBatcher::Kind::Classify : EncoderBatcher::Kind::Embed, text).get();
+            const size_t words = (size_t)((t + k) % 5 + 1);
+            if (classify ? res.classes.predictions.size() == words : (res.embedding.size() == 3 && (size_t)res.embedding[0] == words)) ++ok;
+            else ++wrong;
+          } catch (const std::exception&) {
+            ++failed;
+          }
+        }
+      });
+    for (auto& th : ts) th.join();
+  }
+  json::Value out = json::Value::object();
+  out.set("ok", ok.load());
+  out.set("failed", failed.load());
+  out.set("wrong", wrong.load());
+  json::Value sizes = json::Value::array();
+  for (size_t n : fake->embed_batches) sizes.push((unsigned long long)n);
+  out.set("batches", sizes);
   out.set("metrics", metrics.render());
   return ret(out.dump());
 }

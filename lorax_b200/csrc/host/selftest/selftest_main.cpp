@@ -29,6 +29,7 @@ const char* lx_infer_fake_run(const char* requests_json, int max_active_adapters
 void* lx_tokenizer_load(const char* path, int workers, char* err, int err_cap);
 void lx_tokenizer_free(void* h);
 long lx_tokenizer_encode(void* h, const char* text, size_t len, int add_special, uint32_t* out, size_t cap);
+const char* lx_encoder_batcher_fake_run(int threads, int each);
 }
 
 // A byte-level BPE tokenizer file over printable ASCII: normaliser, regex split, merges, a special token and a template, so
@@ -144,6 +145,12 @@ int main() {
     for (int b : bads) bad += b;
     lx_tokenizer_free(h);
     if (bad) return fail("tokenizer pool", std::to_string(bad));
+  }
+  {
+    // embed / classify batcher: eight caller threads, shared batches, a failing batch now and then
+    const std::string out = lx_encoder_batcher_fake_run(8, 30);
+    if (out.find("\"wrong\":0") == std::string::npos) return fail("encoder batcher answers", out.substr(0, 200));
+    if (out.find("\"ok\":0,") != std::string::npos) return fail("encoder batcher: nothing succeeded");
   }
   std::printf("OK\n");
   return 0;

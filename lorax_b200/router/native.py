@@ -44,6 +44,7 @@ def load():
         "lx_tokenizer_error": ([c_void_p], c_char_p),
         "lx_unicode_normalize": ([c_char_p, c_char_p], c_char_p),
         "lx_regex_find_all": ([c_char_p, c_char_p], c_char_p),
+        "lx_encoder_batcher_fake_run": ([c_int, c_int], c_char_p),
     }
     for name, (args, res) in sig.items():
         f = getattr(lib, name)
@@ -159,3 +160,8 @@ def regex_find_all(pattern: str, text: str) -> List[List[int]]:
     if out.startswith("error: "):
         raise ValueError(out[7:])
     return json.loads(out)
+
+
+def encoder_batcher_fake_run(threads: int, each: int) -> dict:
+    """Concurrent embed / classify inputs through the router's encoder batcher against the fake shard (see capi.cpp)."""
+    return json.loads(load().lx_encoder_batcher_fake_run(threads, each).decode())

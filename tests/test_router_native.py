@@ -163,3 +163,15 @@ def test_host_code_under_sanitizers(sanitizer):
     env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", TSAN_OPTIONS="halt_on_error=1", UBSAN_OPTIONS="print_stacktrace=1")
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+
+
+def test_encoder_batcher_shares_batches_and_contains_failures():
+    """Embed / classify inputs from eight caller threads through the router's encoder batcher against the fake shard: every answer is
+    the one of the caller's own input, inputs that arrive while a batch is on the shard share the next one, and a batch the shard
+    fails answers its own inputs with the error and nobody else's."""
+    from lorax_b200.router.native import encoder_batcher_fake_run
+    r = encoder_batcher_fake_run(8, 30)
+    assert r["wrong"] == 0 and r["ok"] + r["failed"] == 240
+    assert 4 <= r["failed"] < 40                       # thread 0 sends four failing inputs; a few neighbours share their batches
+    assert max(r["batches"]) > 1 and sum(r["batches"]) < 240          # classify inputs are not counted here
+    assert 'lorax_batch_inference_failure{method="embed"}' in r["metrics"] and "lorax_request_queue_duration_bucket" in r["metrics"]
