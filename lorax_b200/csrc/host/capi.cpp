@@ -4,6 +4,7 @@
 // commented out: router/src/loader.rs:345-564).
 #include <cstring>
 
+#include "chat_template.hpp"
 #include "encoder_batcher.hpp"
 #include "infer.hpp"
 #include "json.hpp"
@@ -343,6 +344,27 @@ const char* lx_infer_fake_run(const char* requests_json, int max_active_adapters
   for (auto& l : fake->log) log.push(l);
   out.set("log", log);
   out.set("metrics", metrics.render());
+  return ret(out.dump());
+}
+
+// A chat request rendered by the router's template interpreter.  `request_json`: {"template", "bos_token", "eos_token", "messages",
+// "tools"?, "tool_prompt"?, "guideline"?}.  JSON out: {"text": ...}, {"error": ...} (the template raised or misused a value) or
+// {"unsupported": ...} (outside the interpreter's subset: the router would ask a shard).
+const char* lx_chat_render(const char* request_json) {
+  json::Value req, out = json::Value::object();
+  std::string err;
+  if (!json::parse(request_json, req, &err)) { out.set("error", "bad request json: " + err); return ret(out.dump()); }
+  try {
+    jinja::ChatRenderer r;
+    r.tmpl = jinja::Template::compile(req["template"].as_string());
+    r.bos_token = req["bos_token"].as_string();
+    r.eos_token = req["eos_token"].as_string();
+    out.set("text", r.render(req));
+  } catch (const jinja::Unsupported& e) {
+    out.set("unsupported", std::string(e.what()));
+  } catch (const std::exception& e) {
+    out.set("error", std::string(e.what()));
+  }
   return ret(out.dump());
 }
 

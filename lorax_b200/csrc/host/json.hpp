@@ -8,6 +8,7 @@
 #include <map>
 #include <memory>
 #include <string>
+#include <cstring>
 #include <utility>
 #include <vector>
 

@@ -95,6 +95,7 @@ const Flag kFlags[] = {
     {"tokenizer-config-path", "TOKENIZER_CONFIG_PATH", "", "tokenizer_config.json to take the chat template from"},
     {"tokenizer-name", "TOKENIZER_NAME", "", "tokenizer.json (or its directory) for the router; default: the file shard 0 loaded"},
     {"router-tokenizer", "ROUTER_TOKENIZER", "", "`off` leaves tokenisation of requests to shard 0"},
+    {"router-chat-template", "ROUTER_CHAT_TEMPLATE", "", "`off` leaves the rendering of chat templates to shard 0"},
     {"cors-allow-method", "CORS_ALLOW_METHOD", "", ""},
     {"cors-allow-header", "CORS_ALLOW_HEADER", "", ""},
     {"cors-expose-header", "CORS_EXPOSE_HEADER", "", ""},
@@ -445,7 +446,7 @@ int main(int argc, char** argv) {
   for (const char* opt : {"max-concurrent-requests", "max-best-of", "max-stop-sequences", "max-input-length", "max-total-tokens",
                           "max-batch-prefill-tokens", "max-batch-total-tokens", "waiting-served-ratio", "max-waiting-tokens",
                           "max-active-adapters", "adapter-cycle-time-s", "eager-prefill", "prefix-caching", "chunked-prefill", "hostname",
-                          "port", "adapter-source", "cors-allow-origin", "otlp-endpoint", "validation-workers", "tokenizer-name", "router-tokenizer", "cors-allow-method",
+                          "port", "adapter-source", "cors-allow-origin", "otlp-endpoint", "validation-workers", "tokenizer-name", "router-tokenizer", "router-chat-template", "cors-allow-method",
                           "cors-allow-header", "cors-expose-header", "cors-allow-credentials"})
     if (!c.get(opt).empty()) { rargs.push_back(std::string("--") + opt); rargs.push_back(c.get(opt)); }
   if (!c.get("default-adapter-source").empty()) {          // overrides --adapter-source for the router, as in the reference

@@ -14,6 +14,7 @@
 #include "openapi_gen.hpp"
 #include "http.hpp"
 #include "infer.hpp"
+#include "chat_template.hpp"
 #include "encoder_batcher.hpp"
 #include "grpc_client.hpp"
 #include "json.hpp"
@@ -175,6 +176,10 @@ class App {
     request_logger_.stop();
   }
   bool tracing() const { return tracer_.enabled(); }
+  // Chat templates rendered by the router itself (the shard's template, compiled at start-up); requests whose template needs
+  // something the interpreter lacks still go to shard 0.
+  void set_chat_renderer(std::shared_ptr<const jinja::ChatRenderer> r) { chat_renderer_ = std::move(r); }
+  uint64_t chat_templates_rendered() const { return chat_rendered_.load(); }
 
   // Runs one request to completion; `on_event` sees every stream event (used by the SSE routes).
   Collected run(const std::string& inputs, const GenerateParams& p, const std::function<bool(const StreamEvent&)>& on_event = nullptr,
@@ -472,7 +477,17 @@ class App {
       if (body["tool_prompt"].is_string()) treq.set("tool_prompt", body["tool_prompt"]);
       if (body["guideline"].is_string()) treq.set("guideline", body["guideline"]);
       treq.set("adapter_id", p.adapter_id ? Value(*p.adapter_id) : Value());
-      prompt = client_->helper(102, treq.dump());
+      bool rendered = false;
+      if (chat_renderer_) {
+        try {
+          prompt = chat_renderer_->render(treq);
+          rendered = true;
+          ++chat_rendered_;
+        } catch (const jinja::Unsupported&) {
+          // this request needs a part of Jinja the router lacks: the shard renders it
+        }
+      }
+      if (!rendered) prompt = client_->helper(102, treq.dump());
     } catch (const std::exception& e) {
       return send_error(w, ApiError(std::string("chat template error: ") + e.what(), "template_error", 422));
     }
@@ -886,6 +901,8 @@ class App {
   telemetry::Tracer tracer_;
   telemetry::BackgroundPoster request_logger_;
   std::unique_ptr<EncoderBatcher> encoder_;       // queue + batching thread of /embed and /classify
+  std::shared_ptr<const jinja::ChatRenderer> chat_renderer_;
+  std::atomic<uint64_t> chat_rendered_{0};
   std::atomic<uint64_t> openai_id_{0};
 };
 
@@ -1002,6 +1019,23 @@ int main(int argc, char** argv) {
   const std::string otlp = a.get("otlp-endpoint", "");
   const char* logger_env = std::getenv("REQUEST_LOGGER_URL");
   App app(client, cfg, info, num_blocks, otlp, logger_env ? logger_env : "");
+  if (a.get("router-chat-template", "on") != "off") {
+    try {
+      json::Value setup;
+      std::string perr;
+      if (!json::parse(client->helper(104, ""), setup, &perr)) throw std::runtime_error(perr);
+      if (setup["chat_template"].is_string()) {
+        auto r = std::make_shared<jinja::ChatRenderer>();
+        r->tmpl = jinja::Template::compile(setup["chat_template"].as_string());
+        r->bos_token = setup["bos_token"].as_string();
+        r->eos_token = setup["eos_token"].as_string();
+        app.set_chat_renderer(r);
+        log_json("INFO", "rendering chat templates in the router");
+      }
+    } catch (const std::exception& e) {
+      log_json("INFO", std::string("shard 0 renders chat templates (") + e.what() + ")");
+    }
+  }
   if (!otlp.empty()) log_json(app.tracing() ? "INFO" : "WARN", app.tracing() ? "tracing to " + otlp + (lx::telemetry::parse_url(otlp).grpc ? " (OTLP/gRPC)" : " (OTLP/HTTP JSON)")
                                                                               : "otlp endpoint must be an http:// or grpc:// URL; tracing is off");
   http::Server server;
@@ -1034,6 +1068,7 @@ int main(int argc, char** argv) {
     std::string text = app.metrics().render();
     if (client->tokenizes_locally())
       text += "# TYPE lorax_router_tokenizations counter\nlorax_router_tokenizations " + std::to_string(client->local_tokenizations()) + "\n";
+    text += "# TYPE lorax_router_chat_templates counter\nlorax_router_chat_templates " + std::to_string(app.chat_templates_rendered()) + "\n";
     std::string fmt = req.query_param("format");
     for (auto& ch : fmt) ch = (char)std::tolower((unsigned char)ch);
     const bool want_json = fmt.empty() ? req.header("accept").find("application/json") != std::string::npos : fmt == "json";

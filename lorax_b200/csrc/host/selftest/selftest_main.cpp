@@ -30,6 +30,7 @@ void* lx_tokenizer_load(const char* path, int workers, char* err, int err_cap);
 void lx_tokenizer_free(void* h);
 long lx_tokenizer_encode(void* h, const char* text, size_t len, int add_special, uint32_t* out, size_t cap);
 const char* lx_encoder_batcher_fake_run(int threads, int each);
+const char* lx_chat_render(const char* request_json);
 }
 
 // A byte-level BPE tokenizer file over printable ASCII: normaliser, regex split, merges, a special token and a template, so
@@ -151,6 +152,22 @@ int main() {
     const std::string out = lx_encoder_batcher_fake_run(8, 30);
     if (out.find("\"wrong\":0") == std::string::npos) return fail("encoder batcher answers", out.substr(0, 200));
     if (out.find("\"ok\":0,") != std::string::npos) return fail("encoder batcher: nothing succeeded");
+  }
+  {
+    // chat template interpreter: loops, namespace, filters, slices, white-space control; four threads render the same request
+    const std::string req =
+        "{\"template\":\"{%- set ns = namespace(n=0) -%}{% for m in messages if m.role != 'system' %}{% set ns.n = ns.n + 1 %}"
+        "<{{ m.role | upper }}>{{ m.content | trim }}{{ m.content[:2] ~ loop.index }}{% endfor %}|{{ ns.n }}|{{ tools | tojson }}"
+        "{% if add_generation_prompt %}<A>{% endif %}\",\"bos_token\":\"<s>\",\"eos_token\":\"</s>\",\"messages\":["
+        "{\"role\":\"system\",\"content\":\"sys\"},{\"role\":\"user\",\"content\":\"  hello  \"},{\"role\":\"assistant\",\"content\":\"hi\"}]}";
+    const std::string want = lx_chat_render(req.c_str());
+    if (want.find("\"text\":\"<USER>hello  1<ASSISTANT>hihi2|2|null<A>\"") == std::string::npos) return fail("chat template", want);
+    std::vector<std::thread> threads;
+    std::vector<int> bads(4, 0);
+    for (int t = 0; t < 4; ++t)
+      threads.emplace_back([&, t] { for (int k = 0; k < 50; ++k) if (std::string(lx_chat_render(req.c_str())) != want) ++bads[(size_t)t]; });
+    for (auto& th : threads) th.join();
+    for (int b : bads) if (b) return fail("chat template under threads");
   }
   std::printf("OK\n");
   return 0;

@@ -45,6 +45,7 @@ def load():
         "lx_unicode_normalize": ([c_char_p, c_char_p], c_char_p),
         "lx_regex_find_all": ([c_char_p, c_char_p], c_char_p),
         "lx_encoder_batcher_fake_run": ([c_int, c_int], c_char_p),
+        "lx_chat_render": ([c_char_p], c_char_p),
     }
     for name, (args, res) in sig.items():
         f = getattr(lib, name)
@@ -165,3 +166,9 @@ def regex_find_all(pattern: str, text: str) -> List[List[int]]:
 def encoder_batcher_fake_run(threads: int, each: int) -> dict:
     """Concurrent embed / classify inputs through the router's encoder batcher against the fake shard (see capi.cpp)."""
     return json.loads(load().lx_encoder_batcher_fake_run(threads, each).decode())
+
+
+def chat_render(template: str, messages, bos_token: str = "", eos_token: str = "", **extra) -> dict:
+    """The router's chat template interpreter: {"text"}, {"error"} or {"unsupported"} (see capi.cpp)."""
+    req = dict(template=template, messages=messages, bos_token=bos_token, eos_token=eos_token, **extra)
+    return json.loads(load().lx_chat_render(json.dumps(req).encode()).decode())

@@ -26,7 +26,7 @@ import torch
 from .proto import load_pb
 from .tracing import TRACE_FLAG, TRACEPARENT_BYTES
 
-HELPER_TOKENIZE, HELPER_TOKENIZE_JSON, HELPER_CHAT_TEMPLATE, HELPER_TOKENIZER_FILE = 100, 101, 102, 103
+HELPER_TOKENIZE, HELPER_TOKENIZE_JSON, HELPER_CHAT_TEMPLATE, HELPER_TOKENIZER_FILE, HELPER_CHAT_SETUP = 100, 101, 102, 103, 104
 
 
 def _resolve_device(dev: torch.device) -> torch.device:
@@ -74,6 +74,11 @@ class FramedServer:
             return json.dumps(self.rt.tokenize_detailed(json.loads(payload.decode("utf-8")))).encode()
         if method == HELPER_CHAT_TEMPLATE:
             return self.rt.apply_chat_template(json.loads(payload.decode("utf-8"))).encode("utf-8")
+        if method == HELPER_CHAT_SETUP:        # what the router needs to render chat templates itself
+            from .chat_template import DEFAULT_TEMPLATE
+            plain = getattr(type(self.rt).apply_chat_template, "__qualname__", "").startswith("ShardRuntime.")
+            return json.dumps({"chat_template": (getattr(self.rt, "chat_template", None) or DEFAULT_TEMPLATE) if plain else None,
+                               "bos_token": getattr(self.rt, "bos_token", "") or "", "eos_token": getattr(self.rt, "eos_token", "") or ""}).encode()
         if method == HELPER_TOKENIZER_FILE:
             fn = getattr(self.rt, "router_tokenizer_json", None)
             return (fn() if fn is not None else "").encode("utf-8")

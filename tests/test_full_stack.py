@@ -149,6 +149,12 @@ def test_stream_and_openai_routes(stack):
     assert st == 200, body
     j = json.loads(body)
     assert j["object"] == "chat.completion" and j["choices"][0]["message"]["role"] == "assistant" and j["usage"]["completion_tokens"] <= 4
+    # the router rendered the chat template itself (no helper call to the shard), and the prompt it built is the shard renderer's
+    with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5) as r:
+        count = [l for l in r.read().decode().splitlines() if l.startswith("lorax_router_chat_templates ")]
+    assert count and int(count[0].split()[1]) >= 1, count
+    want_prompt = stack["rt"].apply_chat_template({"messages": [{"role": "user", "content": "w4 w5"}]})
+    assert j["usage"]["prompt_tokens"] == len(stack["rt"].tokenize(want_prompt))
     st, body, _ = _post(port, "/v1/completions", {"model": "tiny", "prompt": "w4 w5", "max_tokens": 3, "stream": True})
     assert st == 200 and "[DONE]" in body
 

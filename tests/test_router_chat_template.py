@@ -1,0 +1,170 @@
+"""The router's chat template interpreter against Jinja2 (the shard's renderer, `lorax_b200.server.chat_template.render_chat`) on the
+templates of well-known model families and on the constructs each alone.  The reference router renders chat templates itself
+(minijinja, router/src/infer.rs:40-147)."""
+
+import pytest
+
+from lorax_b200.router.native import chat_render
+from lorax_b200.server.chat_template import DEFAULT_TEMPLATE, TemplateError, render_chat
+
+CHATML = ("{% for message in messages %}{{'<|im_start|>' + message['role'] + '\n' + message['content'] + '<|im_end|>' + '\n'}}{% endfor %}"
+          "{% if add_generation_prompt %}{{ '<|im_start|>assistant\n' }}{% endif %}")
+LLAMA3 = ("{% set loop_messages = messages %}{% for message in loop_messages %}{% set content = '<|start_header_id|>' + message['role'] + "
+          "'<|end_header_id|>\n\n'+ message['content'] | trim + '<|eot_id|>' %}{% if loop.index0 == 0 %}{% set content = bos_token + content %}"
+          "{% endif %}{{ content }}{% endfor %}{% if add_generation_prompt %}{{ '<|start_header_id|>assistant<|end_header_id|>\n\n' }}{% endif %}")
+MISTRAL = ("{{ bos_token }}{% for message in messages %}{% if (message['role'] == 'user') != (loop.index0 % 2 == 0) %}"
+           "{{ raise_exception('Conversation roles must alternate user/assistant/user/assistant/...') }}{% endif %}"
+           "{% if message['role'] == 'user' %}{{ '[INST] ' + message['content'] + ' [/INST]' }}{% elif message['role'] == 'assistant' %}"
+           "{{ message['content'] + eos_token}}{% else %}{{ raise_exception('Only user and assistant roles are supported!') }}{% endif %}{% endfor %}")
+LLAMA2 = ("{% if messages[0]['role'] == 'system' %}{% set loop_messages = messages[1:] %}{% set system_message = messages[0]['content'] %}"
+          "{% else %}{% set loop_messages = messages %}{% set system_message = false %}{% endif %}{% for message in loop_messages %}"
+          "{% if (message['role'] == 'user') != (loop.index0 % 2 == 0) %}{{ raise_exception('Conversation roles must alternate') }}{% endif %}"
+          "{% if loop.index0 == 0 and system_message != false %}{% set content = '<<SYS>>\\n' + system_message + '\\n<</SYS>>\\n\\n' + message['content'] %}"
+          "{% else %}{% set content = message['content'] %}{% endif %}{% if message['role'] == 'user' %}{{ bos_token + '[INST] ' + content.strip() + ' [/INST]' }}"
+          "{% elif message['role'] == 'assistant' %}{{ ' '  + content.strip() + ' ' + eos_token }}{% endif %}{% endfor %}")
+ZEPHYR = ("{% for message in messages %}\n{% if message['role'] == 'user' %}\n{{ '<|user|>\n' + message['content'] + eos_token }}\n"
+          "{% elif message['role'] == 'system' %}\n{{ '<|system|>\n' + message['content'] + eos_token }}\n{% elif message['role'] == 'assistant' %}\n"
+          "{{ '<|assistant|>\n'  + message['content'] + eos_token }}\n{% endif %}\n{% if loop.last and add_generation_prompt %}\n{{ '<|assistant|>' }}\n"
+          "{% endif %}\n{% endfor %}")
+GEMMA = ("{{ bos_token }}{% if messages[0]['role'] == 'system' %}{{ raise_exception('System role not supported') }}{% endif %}"
+         "{% for message in messages %}{% if (message['role'] == 'user') != (loop.index0 % 2 == 0) %}{{ raise_exception('Conversation roles must alternate') }}"
+         "{% endif %}{% if (message['role'] == 'assistant') %}{% set role = 'model' %}{% else %}{% set role = message['role'] %}{% endif %}"
+         "{{ '<start_of_turn>' + role + '\n' + message['content'] | trim + '<end_of_turn>\n' }}{% endfor %}"
+         "{% if add_generation_prompt %}{{'<start_of_turn>model\n'}}{% endif %}")
+PHI3 = ("{% for message in messages %}{% if message['role'] == 'system' %}{{'<|system|>\n' + message['content'] + '<|end|>\n'}}"
+        "{% elif message['role'] == 'user' %}{{'<|user|>\n' + message['content'] + '<|end|>\n'}}{% elif message['role'] == 'assistant' %}"
+        "{{'<|assistant|>\n' + message['content'] + '<|end|>\n'}}{% endif %}{% endfor %}{% if add_generation_prompt %}{{ '<|assistant|>\n' }}"
+        "{% else %}{{ eos_token }}{% endif %}")
+QWEN_TOOLS = """{%- if tools %}
+    {{- '<|im_start|>system\\n' }}
+    {%- if messages[0]['role'] == 'system' %}
+        {{- messages[0]['content'] }}
+    {%- else %}
+        {{- 'You are a helpful assistant.' }}
+    {%- endif %}
+    {{- "\\n\\n# Tools\\n\\nYou may call one or more functions.\\n<tools>" }}
+    {%- for tool in tools %}
+        {{- "\\n" }}
+        {{- tool | tojson }}
+    {%- endfor %}
+    {{- "\\n</tools><|im_end|>\\n" }}
+{%- else %}
+    {%- if messages[0]['role'] == 'system' %}
+        {{- '<|im_start|>system\\n' + messages[0]['content'] + '<|im_end|>\\n' }}
+    {%- endif %}
+{%- endif %}
+{%- for message in messages %}
+    {%- if (message.role == "user") or (message.role == "system" and not loop.first) or (message.role == "assistant" and not message.tool_calls) %}
+        {{- '<|im_start|>' + message.role + '\\n' + message.content + '<|im_end|>' + '\\n' }}
+    {%- elif message.role == "assistant" %}
+        {{- '<|im_start|>' + message.role }}
+        {%- if message.content %}
+            {{- '\\n' + message.content }}
+        {%- endif %}
+        {%- for tool_call in message.tool_calls %}
+            {%- if tool_call.function is defined %}
+                {%- set tool_call = tool_call.function %}
+            {%- endif %}
+            {{- '\\n<tool_call>\\n{"name": "' }}
+            {{- tool_call.name }}
+            {{- '", "arguments": ' }}
+            {{- tool_call.arguments | tojson }}
+            {{- '}\\n</tool_call>' }}
+        {%- endfor %}
+        {{- '<|im_end|>\\n' }}
+    {%- elif message.role == "tool" %}
+        {%- if (loop.index0 == 0) or (messages[loop.index0 - 1].role != "tool") %}
+            {{- '<|im_start|>user' }}
+        {%- endif %}
+        {{- '\\n<tool_response>\\n' }}
+        {{- message.content }}
+        {{- '\\n</tool_response>' }}
+        {%- if loop.last or (messages[loop.index0 + 1].role != "tool") %}
+            {{- '<|im_end|>\\n' }}
+        {%- endif %}
+    {%- endif %}
+{%- endfor %}
+{%- if add_generation_prompt %}
+    {{- '<|im_start|>assistant\\n' }}
+{%- endif %}
+"""
+NAMESPACE = """{% set ns = namespace(system='', n=0) %}
+{% for m in messages %}
+  {% if m.role == 'system' %}{% set ns.system = ns.system ~ m.content %}{% else %}{% set ns.n = ns.n + 1 %}{% endif %}
+{% endfor %}
+{# a comment #}
+{{ ns.system | upper }}|{{ ns.n }}|{{ messages | length }}|{{ messages[-1]['content'][:5] }}|{{ 'yes' if ns.n > 1 else 'no' }}
+{% for m in messages if m.role != 'system' %}{{ loop.index }}/{{ loop.length }}:{{ m.content | default('none') | replace('a', 'A') }}{{ ', ' if not loop.last }}{% else %}empty{% endfor %}
+{% for k, v in {'b': 1, 'a': [1, 2.5, true, none, 'x']}.items() %}{{ k }}={{ v | tojson }};{% endfor %}
+{{ [1, 2, 3] | join('-') }} {{ 'a,b' .split(',') | last }} {{ 7 // 2 }} {{ 7 % 3 }} {{ 2 * 3.5 }} {{ 1 / 4 }} {{ 'x' in 'xyz' }} {{ 3 not in [1, 2] }} {{ none is none }} {{ undefined_thing is defined }}
+{%- if messages[0].content.startswith('You') and messages[0].content is string %} starts{% endif %}
+{{ "tab\\there" }}{{ '\\u00e9' }}{{ messages[0]['missing'] }}|{{ {"k": "<v>"} | tojson }}|{{ "Title me" | title }}|{{ range(3) | list }}
+"""
+
+MESSAGES = [
+    [{"role": "user", "content": "Hello there"}],
+    [{"role": "system", "content": "You are a pirate. "}, {"role": "user", "content": "  What is 2+2?  "}, {"role": "assistant", "content": "Four, arr."},
+     {"role": "user", "content": "And naïve café 日本語 <tags> & 'quotes'?"}],
+    [{"role": "user", "content": "a"}, {"role": "assistant", "content": "b"}, {"role": "user", "content": [{"type": "text", "text": "part one "}, {"type": "text", "text": "part two"}]}],
+]
+TEMPLATES = {"default": DEFAULT_TEMPLATE, "chatml": CHATML, "llama3": LLAMA3, "mistral": MISTRAL, "llama2": LLAMA2, "zephyr": ZEPHYR, "gemma": GEMMA,
+             "phi3": PHI3, "qwen_tools": QWEN_TOOLS, "namespace": NAMESPACE}
+TOOLS = [{"type": "function", "function": {"name": "get_weather", "description": "Weather for a city <now> & 'later' é",
+                                            "parameters": {"type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}}, "required": ["city"]}}}]
+
+
+def both(template, messages, **kw):
+    try:
+        want = ("text", render_chat(messages, template, bos_token="<s>", eos_token="</s>", **kw))
+    except TemplateError as e:
+        want = ("error", str(e))
+    got = chat_render(template, messages, bos_token="<s>", eos_token="</s>", **kw)
+    return want, got
+
+
+@pytest.mark.parametrize("name", sorted(TEMPLATES))
+def test_templates_of_known_families_render_like_jinja2(name):
+    for messages in MESSAGES:
+        want, got = both(TEMPLATES[name], messages)
+        assert "unsupported" not in got, (name, got)
+        if want[0] == "text":
+            assert got.get("text") == want[1], (name, messages, got)
+        else:
+            assert "error" in got, (name, messages, got)
+            if "raise_exception" in TEMPLATES[name]:
+                assert got["error"] == want[1]
+
+
+def test_tools_go_into_the_template_or_into_the_last_message():
+    for name in ("qwen_tools", "chatml", "llama3"):
+        for extra in ({}, {"tool_prompt": "\nUse the tools.\n"}):
+            want, got = both(TEMPLATES[name], MESSAGES[1], tools=TOOLS, **extra)
+            assert got.get("text") == want[1], (name, got)
+    tool_turns = [{"role": "user", "content": "weather in Paris?"},
+                  {"role": "assistant", "content": "", "tool_calls": [{"type": "function", "function": {"name": "get_weather", "arguments": {"city": "Paris", "days": 2}}}]},
+                  {"role": "tool", "content": "{\"temp\": 21.5}"}, {"role": "tool", "content": "{\"temp\": 19}"}, {"role": "user", "content": "thanks"}]
+    want, got = both(QWEN_TOOLS, tool_turns, tools=TOOLS)
+    assert got.get("text") == want[1], got
+
+
+def test_guideline_and_whitespace_control():
+    t = "{% if guideline %}G:{{ guideline }}\n{% endif %}   {%- for m in messages %}\n  {% if true %}\n  x{{ m.content }}  \n  {%+ endif %}\n{% endfor -%}\n\n  end"
+    want, got = both(t, MESSAGES[0], guideline="be nice")
+    assert got.get("text") == want[1], (got, want)
+    want, got = both(t, MESSAGES[0])
+    assert want[0] == "error" and "error" in got and "guideline" in got["error"]
+    for t in ["a\n  {# c #}\nb {{ 1 }}\n  {{ 2 }}\n{% set x = 3 %}\n{{ x }}\n", "{{- 'a' -}}  \n  b  {{- 'c' }}\n{%- if true -%}\n d \n{%- endif -%}\n e",
+              "  {% if true %}  \n  {% endif %}  tail\n", "\t{%+ if true %}\tkept{% endif +%}\nnext"]:
+        want, got = both(t, MESSAGES[0])
+        assert got.get("text") == want[1], (t, got, want)
+
+
+def test_what_the_interpreter_does_not_implement_is_reported_as_such():
+    for t in ["{% macro f(x) %}{{ x }}{% endmacro %}{{ f(1) }}", "{{ messages | selectattr('role', 'equalto', 'user') | list }}", "{% filter upper %}a{% endfilter %}",
+              "{% for m in messages %}{{ loop.cycle('a', 'b') }}{% endfor %}", "{{ messages | map(attribute='role') | join(',') }}"]:
+        got = chat_render(t, MESSAGES[1])
+        assert "unsupported" in got, (t, got)
+    got = chat_render("{{ 'a' + 1 }}", MESSAGES[0])
+    assert "error" in got
+    got = chat_render("{{ messages[0].content.nope.deeper }}", MESSAGES[0])
+    assert "error" in got
