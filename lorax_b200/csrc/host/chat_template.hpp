@@ -338,6 +338,26 @@ inline std::string replace_all(std::string s, const std::string& a, const std::s
 
 struct Arg { std::string name; ExprP value; };
 
+inline bool apply_test(const std::string& t, const Val& x, const std::vector<Val>& args);
+inline Val get_attr(const Val& o, const std::string& key);
+// "a.b.c" looked up step by step (the attribute arguments of selectattr / map)
+inline Val get_path(const Val& o, const std::string& path) {
+  Val cur = o;
+  size_t p = 0;
+  while (true) {
+    const size_t q = path.find('.', p);
+    const std::string key = path.substr(p, q == std::string::npos ? std::string::npos : q - p);
+    if (cur.kind == Val::ListK && !key.empty() && std::isdigit((unsigned char)key[0])) {
+      const size_t k = (size_t)std::strtoul(key.c_str(), nullptr, 10);
+      cur = k < cur.list->size() ? (*cur.list)[k] : Val();
+    } else {
+      cur = cur.kind == Val::Undefined ? Val() : get_attr(cur, key);
+    }
+    if (q == std::string::npos) return cur;
+    p = q + 1;
+  }
+}
+
 inline Val apply_filter(const std::string& f, const Val& x, const std::vector<std::pair<std::string, Val>>& args) {
   auto arg = [&](size_t pos, const char* name) -> const Val* {
     for (auto& a : args) if (a.first == name) return &a.second;
@@ -415,6 +435,107 @@ inline Val apply_filter(const std::string& f, const Val& x, const std::vector<st
   if (f == "reverse") {
     if (x.kind == Val::ListK) return Val::make_list(List(x.list->rbegin(), x.list->rend()));
     throw Unsupported("reverse of something that is no list");
+  }
+  if (f == "selectattr" || f == "rejectattr" || f == "select" || f == "reject") {
+    if (x.kind != Val::ListK) throw TemplateError(f + " of something that is no list");
+    const bool by_attr = f == "selectattr" || f == "rejectattr";
+    const bool keep_if = f == "selectattr" || f == "select";
+    std::vector<Val> pos;
+    for (auto& a : args) if (a.first.empty()) pos.push_back(a.second);
+    if (by_attr && pos.empty()) throw TemplateError(f + " needs an attribute");
+    const size_t t0 = by_attr ? 1 : 0;
+    List out;
+    for (auto& item : *x.list) {
+      const Val v = by_attr ? get_path(item, to_text(pos[0])) : item;
+      bool hit;
+      if (pos.size() > t0) hit = apply_test(to_text(pos[t0]), v, std::vector<Val>(pos.begin() + (long)t0 + 1, pos.end()));
+      else hit = v.truthy();
+      if (hit == keep_if) out.push_back(item);
+    }
+    return Val::make_list(std::move(out));
+  }
+  if (f == "map") {
+    if (x.kind != Val::ListK) throw TemplateError("map of something that is no list");
+    const Val* attribute = nullptr;
+    const Val* dflt = nullptr;
+    std::vector<std::pair<std::string, Val>> rest;
+    const Val* fname = nullptr;
+    for (auto& a : args) {
+      if (a.first == "attribute") attribute = &a.second;
+      else if (a.first == "default") dflt = &a.second;
+      else if (a.first.empty() && !fname && !attribute) fname = &a.second;
+      else rest.push_back(a);
+    }
+    List out;
+    for (auto& item : *x.list) {
+      if (attribute) { Val v = get_path(item, to_text(*attribute)); out.push_back(v.kind == Val::Undefined && dflt ? *dflt : v); }
+      else if (fname) out.push_back(apply_filter(to_text(*fname), item, rest));
+      else throw TemplateError("map needs a filter or an attribute");
+    }
+    return Val::make_list(std::move(out));
+  }
+  if (f == "sum") {
+    if (x.kind != Val::ListK) throw TemplateError("sum of something that is no list");
+    bool fl = false;
+    double acc = 0;
+    for (auto& e : *x.list) { if (!e.is_number()) throw TemplateError("sum of something that is no number"); fl = fl || e.kind == Val::Float; acc += e.num(); }
+    return fl ? Val::real(acc) : Val::integer((long long)acc);
+  }
+  if (f == "min" || f == "max") {
+    if (x.kind != Val::ListK || x.list->empty()) return Val();
+    const Val* best = &(*x.list)[0];
+    for (auto& e : *x.list) {
+      bool less;
+      if (e.is_number() && best->is_number()) less = e.num() < best->num();
+      else if (e.kind == Val::Str && best->kind == Val::Str) less = e.s < best->s;
+      else throw TemplateError("values of these types are not ordered");
+      if (less == (f == "min") && !equal(e, *best)) best = &e;
+    }
+    return *best;
+  }
+  if (f == "dictsort") {
+    if (x.kind != Val::DictK) throw TemplateError("dictsort of something that is no mapping");
+    if (!args.empty()) throw Unsupported("dictsort with arguments");
+    std::vector<std::pair<std::string, Val>> items(x.dict->begin(), x.dict->end());
+    auto lower = [](std::string v) { for (auto& ch : v) if (ch >= 'A' && ch <= 'Z') ch = (char)(ch + 32); return v; };
+    std::stable_sort(items.begin(), items.end(), [&](auto& a, auto& b) { return lower(a.first) < lower(b.first); });
+    List l;
+    for (auto& kv : items) l.push_back(Val::make_list({Val::str(kv.first), kv.second}));
+    return Val::make_list(std::move(l));
+  }
+  if (f == "unique") {
+    if (x.kind != Val::ListK) throw TemplateError("unique of something that is no list");
+    List out;
+    for (auto& e : *x.list) { bool seen = false; for (auto& o : out) if (equal(o, e)) { seen = true; break; } if (!seen) out.push_back(e); }
+    return Val::make_list(std::move(out));
+  }
+  if (f == "abs" && x.is_number()) return x.kind == Val::Float ? Val::real(std::fabs(x.f)) : Val::integer(std::llabs((long long)x.num()));
+  if (f == "indent") {
+    const Val* w = nullptr;
+    bool first = false;
+    size_t k = 0;
+    for (auto& a : args) {
+      if (a.first == "width" || (a.first.empty() && k == 0)) w = &a.second;
+      else if (a.first == "first" || (a.first.empty() && k == 1)) first = a.second.truthy();
+      else throw Unsupported("indent with this argument");
+      if (a.first.empty()) ++k;
+    }
+    const std::string pad = w && w->kind == Val::Str ? w->s : std::string((size_t)(w && w->kind == Val::Int ? w->i : 4), ' ');
+    const std::string src = to_text(x);
+    std::string o;
+    size_t p = 0;
+    bool line0 = true;
+    while (p <= src.size()) {
+      const size_t q = src.find('\n', p);
+      const std::string line = src.substr(p, q == std::string::npos ? std::string::npos : q - p);
+      if (!line.empty() && (!line0 || first)) o += pad;
+      o += line;
+      if (q == std::string::npos) break;
+      o.push_back('\n');
+      p = q + 1;
+      line0 = false;
+    }
+    return Val::str(o);
   }
   throw Unsupported("filter " + f);
 }

@@ -101,6 +101,90 @@ NAMESPACE = """{% set ns = namespace(system='', n=0) %}
 {{ "tab\\there" }}{{ '\\u00e9' }}{{ messages[0]['missing'] }}|{{ {"k": "<v>"} | tojson }}|{{ "Title me" | title }}|{{ range(3) | list }}
 """
 
+MISTRAL_V3 = """{{- bos_token }}
+{%- set user_messages = messages | selectattr('role', 'equalto', 'user') | list %}
+{%- for message in messages %}
+    {%- if message['role'] == 'user' %}
+        {%- if tools and (message == user_messages[-1]) %}
+            {{- ' [AVAILABLE_TOOLS] ' }}{{ tools | map(attribute='function') | map(attribute='name') | join(', ') }}{{ tools[0].function.parameters.properties | dictsort | tojson }}{{- ' [/AVAILABLE_TOOLS]' }}
+        {%- endif %}
+        {{- ' [INST] ' + message['content'] + ' [/INST]' }}
+    {%- elif message['role'] == 'assistant' %}
+        {{- ' ' + message['content'] + eos_token }}
+    {%- else %}
+        {{- '(' ~ message.role ~ ')' ~ message.content | indent(2) }}
+    {%- endif %}
+{%- endfor %}
+{{- messages | rejectattr('role', 'in', ['user', 'system']) | map(attribute='content') | map('upper') | list | tojson }}
+{{- [3, 1, 2] | max }}{{ [3, 1.5] | sum }}{{ ['b', 'a', 'b'] | unique | join }}{{ messages | map(attribute='nope', default='-') | join }}"""
+LLAMA31 = """{{- bos_token }}
+{%- if custom_tools is defined %}
+    {%- set tools = custom_tools %}
+{%- endif %}
+{%- if not tools_in_user_message is defined %}
+    {%- set tools_in_user_message = true %}
+{%- endif %}
+{%- if not date_string is defined %}
+    {%- set date_string = "26 Jul 2024" %}
+{%- endif %}
+{%- if not tools is defined %}
+    {%- set tools = none %}
+{%- endif %}
+{#- This block extracts the system message, so we can slot it into the right place. #}
+{%- if messages[0]['role'] == 'system' %}
+    {%- set system_message = messages[0]['content']|trim %}
+    {%- set messages = messages[1:] %}
+{%- else %}
+    {%- set system_message = "" %}
+{%- endif %}
+{{- "<|start_header_id|>system<|end_header_id|>\n\n" }}
+{%- if tools is not none %}
+    {{- "Environment: ipython\n" }}
+{%- endif %}
+{{- "Cutting Knowledge Date: December 2023\n" }}
+{{- "Today Date: " + date_string + "\n\n" }}
+{%- if tools is not none and not tools_in_user_message %}
+    {{- "You have access to the following functions." }}
+    {%- for t in tools %}
+        {{- t | tojson(indent=4) }}
+        {{- "\n\n" }}
+    {%- endfor %}
+{%- endif %}
+{{- system_message }}
+{{- "<|eot_id|>" }}
+{%- for message in messages %}
+    {%- if not (message.role == 'ipython' or message.role == 'tool' or 'tool_calls' in message) %}
+        {{- '<|start_header_id|>' + message['role'] + '<|end_header_id|>\n\n'+ message['content'] | trim + '<|eot_id|>' }}
+    {%- elif 'tool_calls' in message %}
+        {%- if not message.tool_calls|length == 1 %}
+            {{- raise_exception("This model only supports single tool-calls at once!") }}
+        {%- endif %}
+        {%- set tool_call = message.tool_calls[0].function %}
+        {{- '<|start_header_id|>assistant<|end_header_id|>\n\n' -}}
+        {{- '{"name": "' + tool_call.name + '", ' }}
+        {{- '"parameters": ' }}
+        {{- tool_call.arguments | tojson }}
+        {{- "}" }}
+        {%- for arg_name, arg_val in tool_call.arguments | items %}
+            {{- arg_name ~ '="' ~ arg_val ~ '"' }}
+            {%- if not loop.last %}, {% endif %}
+        {%- endfor %}
+        {{- "<|eot_id|>" }}
+    {%- elif message.role == "tool" or message.role == "ipython" %}
+        {{- "<|start_header_id|>ipython<|end_header_id|>\n\n" }}
+        {%- if message.content is mapping or message.content is iterable %}
+            {{- message.content | tojson }}
+        {%- else %}
+            {{- message.content }}
+        {%- endif %}
+        {{- "<|eot_id|>" }}
+    {%- endif %}
+{%- endfor %}
+{%- if add_generation_prompt %}
+    {{- '<|start_header_id|>assistant<|end_header_id|>\n\n' }}
+{%- endif %}
+"""
+
 MESSAGES = [
     [{"role": "user", "content": "Hello there"}],
     [{"role": "system", "content": "You are a pirate. "}, {"role": "user", "content": "  What is 2+2?  "}, {"role": "assistant", "content": "Four, arr."},
@@ -108,7 +192,7 @@ MESSAGES = [
     [{"role": "user", "content": "a"}, {"role": "assistant", "content": "b"}, {"role": "user", "content": [{"type": "text", "text": "part one "}, {"type": "text", "text": "part two"}]}],
 ]
 TEMPLATES = {"default": DEFAULT_TEMPLATE, "chatml": CHATML, "llama3": LLAMA3, "mistral": MISTRAL, "llama2": LLAMA2, "zephyr": ZEPHYR, "gemma": GEMMA,
-             "phi3": PHI3, "qwen_tools": QWEN_TOOLS, "namespace": NAMESPACE}
+             "phi3": PHI3, "qwen_tools": QWEN_TOOLS, "namespace": NAMESPACE, "mistral_v3": MISTRAL_V3, "llama31": LLAMA31}
 TOOLS = [{"type": "function", "function": {"name": "get_weather", "description": "Weather for a city <now> & 'later' é",
                                             "parameters": {"type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}}, "required": ["city"]}}}]
 
@@ -136,15 +220,16 @@ def test_templates_of_known_families_render_like_jinja2(name):
 
 
 def test_tools_go_into_the_template_or_into_the_last_message():
-    for name in ("qwen_tools", "chatml", "llama3"):
+    for name in ("qwen_tools", "chatml", "llama3", "mistral_v3", "llama31"):
         for extra in ({}, {"tool_prompt": "\nUse the tools.\n"}):
             want, got = both(TEMPLATES[name], MESSAGES[1], tools=TOOLS, **extra)
             assert got.get("text") == want[1], (name, got)
     tool_turns = [{"role": "user", "content": "weather in Paris?"},
                   {"role": "assistant", "content": "", "tool_calls": [{"type": "function", "function": {"name": "get_weather", "arguments": {"city": "Paris", "days": 2}}}]},
                   {"role": "tool", "content": "{\"temp\": 21.5}"}, {"role": "tool", "content": "{\"temp\": 19}"}, {"role": "user", "content": "thanks"}]
-    want, got = both(QWEN_TOOLS, tool_turns, tools=TOOLS)
-    assert got.get("text") == want[1], got
+    for t in (QWEN_TOOLS, LLAMA31):
+        want, got = both(t, tool_turns, tools=TOOLS)
+        assert got.get("text") == want[1], got
 
 
 def test_guideline_and_whitespace_control():
@@ -160,8 +245,8 @@ def test_guideline_and_whitespace_control():
 
 
 def test_what_the_interpreter_does_not_implement_is_reported_as_such():
-    for t in ["{% macro f(x) %}{{ x }}{% endmacro %}{{ f(1) }}", "{{ messages | selectattr('role', 'equalto', 'user') | list }}", "{% filter upper %}a{% endfilter %}",
-              "{% for m in messages %}{{ loop.cycle('a', 'b') }}{% endfor %}", "{{ messages | map(attribute='role') | join(',') }}"]:
+    for t in ["{% macro f(x) %}{{ x }}{% endmacro %}{{ f(1) }}", "{{ messages | groupby('role') | list }}", "{% filter upper %}a{% endfilter %}",
+              "{% for m in messages %}{{ loop.cycle('a', 'b') }}{% endfor %}", "{% call f() %}x{% endcall %}"]:
         got = chat_render(t, MESSAGES[1])
         assert "unsupported" in got, (t, got)
     got = chat_render("{{ 'a' + 1 }}", MESSAGES[0])
