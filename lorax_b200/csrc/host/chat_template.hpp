@@ -5,7 +5,7 @@
 // `loop`, `{% set %}` (names and namespace attributes), comments, whitespace control (`-`, and the `trim_blocks` / `lstrip_blocks`
 // settings chat templates are rendered with), `{% generation %}` markers; expressions with literals, lists, dicts, attribute /
 // item access, slices, calls, filters, tests, comparisons, `in`, boolean operators, arithmetic, `~` and `a if c else b`.
-// Anything else (macros, `call`, `filter` blocks, an unknown filter or test ...) makes `compile` or `render` throw `Unsupported`, and
+// Macros are callable (`{{ f(x) }}`).  Anything else (`call`, `filter` blocks, an unknown filter or test ...) makes `compile` or `render` throw `Unsupported`, and
 // the router asks shard 0 (which runs Jinja2) for that template or request.
 #pragma once
 #include <algorithm>
@@ -233,8 +233,11 @@ struct Expr {
 };
 using ExprP = std::unique_ptr<Expr>;
 
+struct MacroDef;
 struct Context {
   std::vector<std::map<std::string, Val>> scopes;
+  std::map<std::string, const MacroDef*> macros;
+  int depth = 0;
   Val lookup(const std::string& name) const {
     for (size_t k = scopes.size(); k-- > 0;) { auto it = scopes[k].find(name); if (it != scopes[k].end()) return it->second; }
     return Val();
@@ -585,7 +588,8 @@ struct Test : Expr {
   }
 };
 
-// Calls: global functions, and the methods of strings / dicts / lists that templates use.
+Val call_macro(const MacroDef& m, const std::vector<std::pair<std::string, Val>>& args, Context& c);
+// Calls: macros, global functions, and the methods of strings / dicts / lists that templates use.
 struct Call : Expr {
   ExprP callee;                    // Name (function) or Attr (method)
   std::vector<Arg> args;
@@ -595,6 +599,8 @@ struct Call : Expr {
     auto pos = [&](size_t k) -> const Val* { size_t n = 0; for (auto& a : av) if (a.first.empty()) { if (n == k) return &a.second; ++n; } return nullptr; };
     if (auto* nm = dynamic_cast<const Name*>(callee.get())) {
       const std::string& fn = nm->n;
+      auto mi = c.macros.find(fn);
+      if (mi != c.macros.end()) return call_macro(*mi->second, av, c);
       if (fn == "raise_exception") throw TemplateError(pos(0) ? to_text(*pos(0)) : "template error");
       if (fn == "namespace") { Val ns = Val::make_dict(); ns.is_namespace = true; for (auto& a : av) if (!a.first.empty()) ns.set(a.first, a.second); return ns; }
       if (fn == "dict") { Val d = Val::make_dict(); for (auto& a : av) if (!a.first.empty()) d.set(a.first, a.second); return d; }
@@ -791,6 +797,47 @@ struct ForNode : Node {
     }
   }
 };
+
+struct MacroDef {
+  std::string name;
+  std::vector<std::pair<std::string, ExprP>> params;      // name, default (may be null)
+  Body body;
+};
+struct MacroNode : Node {
+  std::shared_ptr<MacroDef> def;
+  void render(Context& c, std::string&) const override { c.macros[def->name] = def.get(); }
+};
+inline Val call_macro(const MacroDef& m, const std::vector<std::pair<std::string, Val>>& args, Context& c) {
+  if (c.depth > 64) throw TemplateError("macro recursion too deep");
+  std::map<std::string, Val> frame;
+  size_t k = 0;
+  for (auto& a : args) {
+    if (a.first.empty()) { if (k >= m.params.size()) throw TemplateError("macro '" + m.name + "' takes fewer arguments"); frame[m.params[k++].first] = a.second; }
+  }
+  for (auto& a : args) {
+    if (a.first.empty()) continue;
+    bool known = false;
+    for (auto& p : m.params) if (p.first == a.first) known = true;
+    if (!known) throw TemplateError("macro '" + m.name + "' has no argument '" + a.first + "'");
+    frame[a.first] = a.second;
+  }
+  // a macro sees the template's globals and its own arguments, not the caller's loop variables
+  Context inner;
+  inner.scopes.push_back(c.scopes.front());
+  if (c.scopes.size() > 1) inner.scopes.push_back(c.scopes[1]);
+  inner.macros = c.macros;
+  inner.depth = c.depth + 1;
+  inner.scopes.emplace_back();
+  for (auto& p : m.params) {
+    auto it = frame.find(p.first);
+    if (it != frame.end()) inner.assign(p.first, it->second);
+    else if (p.second) inner.assign(p.first, p.second->eval(inner));
+    else inner.assign(p.first, Val());
+  }
+  std::string out;
+  render_body(m.body, inner, out);
+  return Val::str(out);
+}
 
 // ------------------------------------------------------------------------------------------------ lexer and parser
 struct Tok { enum Kind { End, Name, Int, Float, Str, Op } kind = End; std::string text; };
@@ -1083,11 +1130,14 @@ class Template {
       bool plus = false, strip_left = false;
       if (j < n && s[j] == '-') { strip_left = true; ++j; }
       else if (j < n && s[j] == '+' && kind != '{') { plus = true; ++j; }
-      size_t k = j;                    // the closing delimiter, outside string literals
+      size_t k = j;                    // the closing delimiter, outside string literals and outside dict literals ("}}" may close two)
       char quote = 0;
+      int braces = 0;
       while (k + 1 < n) {
         if (kind != '#' && quote) { if (s[k] == '\\') { k += 2; continue; } if (s[k] == quote) quote = 0; ++k; continue; }
         if (kind != '#' && (s[k] == '\'' || s[k] == '"')) { quote = s[k]; ++k; continue; }
+        if (kind != '#' && s[k] == '{') { ++braces; ++k; continue; }
+        if (kind != '#' && s[k] == '}' && braces > 0) { --braces; ++k; continue; }
         if (s[k] == close[0] && s[k + 1] == close[1]) break;
         ++k;
       }
@@ -1201,6 +1251,27 @@ class Template {
         if (!ep.eat_op("=")) throw Unsupported("block set");
         node->value = ep.expression();
         if (!ep.at_end()) throw Unsupported("unexpected `" + ep.peek().text + "` in a set");
+        body.push_back(std::move(node));
+      } else if (kw == "macro") {
+        ExprParser ep(rest, &names_);
+        auto def = std::make_shared<MacroDef>();
+        def->name = ep.expect_name();
+        ep.expect_op("(");
+        while (!ep.is_op(")")) {
+          std::string pn = ep.expect_name();
+          ExprP dflt;
+          if (ep.eat_op("=")) dflt = ep.expression();
+          def->params.emplace_back(pn, std::move(dflt));
+          if (!ep.eat_op(",")) break;
+        }
+        ep.expect_op(")");
+        if (!ep.at_end()) throw Unsupported("unexpected `" + ep.peek().text + "` in a macro");
+        std::string end;
+        def->body = parse_body(segs, pos, {"endmacro"}, &end);
+        if (pos >= segs.size()) throw Unsupported("macro without endmacro");
+        ++pos;
+        auto node = std::make_unique<MacroNode>();
+        node->def = std::move(def);
         body.push_back(std::move(node));
       } else if (kw == "generation" || kw == "endgeneration") {
         // markers around the assistant's text (used for training masks): nothing to render

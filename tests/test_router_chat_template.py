@@ -185,6 +185,35 @@ LLAMA31 = """{{- bos_token }}
 {%- endif %}
 """
 
+HERMES_MACRO = """{%- macro json_to_python_type(json_spec) %}
+{%- set basic_type_map = {"string": "str", "number": "float", "integer": "int", "boolean": "bool"} %}
+{%- if basic_type_map[json_spec.type] is defined %}
+    {{- basic_type_map[json_spec.type] }}
+{%- elif json_spec.type == "array" %}
+    {{- "list[" +  json_to_python_type(json_spec|items) + "]"}}
+{%- elif json_spec.type == "object" %}
+    {%- if json_spec.additionalProperties is defined %}
+        {{- "dict[str, " + json_to_python_type(json_spec.additionalProperties) + ']'}}
+    {%- else %}
+        {{- "dict" }}
+    {%- endif %}
+{%- else %}
+    {{- "Any" }}
+{%- endif %}
+{%- endmacro %}
+{%- macro greet(name, punct='!') %}Hello {{ name }}{{ punct }}{% endmacro %}
+{{- bos_token }}
+{%- for tool in tools or [] %}
+    {{- tool.function.name + "(" }}
+    {%- for param_name, param_fields in tool.function.parameters.properties|items %}
+        {{- param_name + ": " + json_to_python_type(param_fields) }}
+        {%- if not loop.last %}{{ ", " }}{% endif %}
+    {%- endfor %}
+    {{- ") -> " + json_to_python_type({"type": "object", "additionalProperties": {"type": "number"}}) + "\n" }}
+{%- endfor %}
+{%- for message in messages %}{{ greet(message.role) }}{{ greet(name=message.role, punct='?') }} {{ message.content }}
+{% endfor %}"""
+
 MESSAGES = [
     [{"role": "user", "content": "Hello there"}],
     [{"role": "system", "content": "You are a pirate. "}, {"role": "user", "content": "  What is 2+2?  "}, {"role": "assistant", "content": "Four, arr."},
@@ -192,7 +221,7 @@ MESSAGES = [
     [{"role": "user", "content": "a"}, {"role": "assistant", "content": "b"}, {"role": "user", "content": [{"type": "text", "text": "part one "}, {"type": "text", "text": "part two"}]}],
 ]
 TEMPLATES = {"default": DEFAULT_TEMPLATE, "chatml": CHATML, "llama3": LLAMA3, "mistral": MISTRAL, "llama2": LLAMA2, "zephyr": ZEPHYR, "gemma": GEMMA,
-             "phi3": PHI3, "qwen_tools": QWEN_TOOLS, "namespace": NAMESPACE, "mistral_v3": MISTRAL_V3, "llama31": LLAMA31}
+             "phi3": PHI3, "qwen_tools": QWEN_TOOLS, "namespace": NAMESPACE, "mistral_v3": MISTRAL_V3, "llama31": LLAMA31, "hermes_macro": HERMES_MACRO}
 TOOLS = [{"type": "function", "function": {"name": "get_weather", "description": "Weather for a city <now> & 'later' é",
                                             "parameters": {"type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}}, "required": ["city"]}}}]
 
@@ -220,7 +249,7 @@ def test_templates_of_known_families_render_like_jinja2(name):
 
 
 def test_tools_go_into_the_template_or_into_the_last_message():
-    for name in ("qwen_tools", "chatml", "llama3", "mistral_v3", "llama31"):
+    for name in ("qwen_tools", "chatml", "llama3", "mistral_v3", "llama31", "hermes_macro"):
         for extra in ({}, {"tool_prompt": "\nUse the tools.\n"}):
             want, got = both(TEMPLATES[name], MESSAGES[1], tools=TOOLS, **extra)
             assert got.get("text") == want[1], (name, got)
@@ -245,7 +274,7 @@ def test_guideline_and_whitespace_control():
 
 
 def test_what_the_interpreter_does_not_implement_is_reported_as_such():
-    for t in ["{% macro f(x) %}{{ x }}{% endmacro %}{{ f(1) }}", "{{ messages | groupby('role') | list }}", "{% filter upper %}a{% endfilter %}",
+    for t in ["{{ messages | groupby('role') | list }}", "{% filter upper %}a{% endfilter %}",
               "{% for m in messages %}{{ loop.cycle('a', 'b') }}{% endfor %}", "{% call f() %}x{% endcall %}"]:
         got = chat_render(t, MESSAGES[1])
         assert "unsupported" in got, (t, got)
