@@ -343,3 +343,14 @@ def test_bpe_with_word_suffix_and_continuation_prefix(tmp_path):
         trainer = trainers.BpeTrainer(vocab_size=400, special_tokens=["<unk>", "<|startoftext|>", "<|endoftext|>"], show_progress=False, **kw)
         tok.train_from_iterator(corpus(), trainer)
         check(tmp_path, tok)
+
+
+def test_random_strings_of_awkward_characters(tmp_path):
+    """Seeded fuzz: control characters, combining marks, joiners, regional indicators, Hangul jamo, private-use and replacement
+    characters and pieces of special tokens, against the library, for a byte-level and a SentencePiece-style tokenizer."""
+    rng = random.Random(1)
+    alphabet = [chr(c) for c in list(range(0, 0x250)) + [0x300, 0x301, 0x200D, 0x1F600, 0x1F1E6, 0xAC00, 0x1100, 0x1161, 0x11A8, 0xFE0F, 0x0600, 0x0E33,
+                                                          0xFFFD, 0x2028, 0x3000, 0x4E2D, 0xE000]] + ["<s>", "</s>", "<|eot_id|>", "<|begin_of_text|>"]
+    strings = ["".join(rng.choice(alphabet) for _ in range(rng.randint(0, 40))) for _ in range(600)]
+    check(tmp_path, byte_level_bpe(pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)), strings, special=(True,))
+    check(tmp_path, sentencepiece_bpe(True), strings, special=(True,))
