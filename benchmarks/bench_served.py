@@ -146,7 +146,7 @@ def main():
     srv = FramedServer(rt, uds + "-0.lx").start()
     port = _free_port()
     here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    router = subprocess.Popen([os.path.join(here, "bin", "lorax-router"), "--port", str(port), "--hostname", "127.0.0.1",
+    router = subprocess.Popen([os.path.join(here, "lorax_b200", "bin", "lorax-router"), "--port", str(port), "--hostname", "127.0.0.1",
                                "--master-shard-uds-path", uds, "--num-shard", "1", "--max-input-length", str(a.max_prompt),
                                "--max-total-tokens", str(max_total), "--max-batch-prefill-tokens", "4096", "--model-id", a.model,
                                "--adapter-source", "local", "--max-concurrent-requests", str(4 * a.concurrency),
