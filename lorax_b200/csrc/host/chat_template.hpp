@@ -702,6 +702,7 @@ struct Binary : Expr {
       throw TemplateError(std::string("can only concatenate str (not \"") + (y.kind == Val::Str ? "str" : y.kind == Val::None ? "NoneType" : y.kind == Val::Undefined ? "Undefined" : "object") + "\") to str");
     }
     if (op == "*" && x.kind == Val::Str && y.kind == Val::Int) { std::string o; for (long long k = 0; k < y.i && o.size() < (1u << 20); ++k) o += x.s; return Val::str(o); }
+    if (op == "%" && x.kind == Val::Str) throw Unsupported("string formatting with %");
     if (!x.is_number() || !y.is_number()) throw TemplateError("arithmetic on something that is no number");
     const bool fl = x.kind == Val::Float || y.kind == Val::Float;
     if (op == "-") return fl ? Val::real(x.num() - y.num()) : Val::integer((long long)x.num() - (long long)y.num());

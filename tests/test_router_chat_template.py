@@ -275,7 +275,8 @@ def test_guideline_and_whitespace_control():
 
 def test_what_the_interpreter_does_not_implement_is_reported_as_such():
     for t in ["{{ messages | groupby('role') | list }}", "{% filter upper %}a{% endfilter %}",
-              "{% for m in messages %}{{ loop.cycle('a', 'b') }}{% endfor %}", "{% call f() %}x{% endcall %}"]:
+              "{% for m in messages %}{{ loop.cycle('a', 'b') }}{% endfor %}", "{% call f() %}x{% endcall %}", "{{ '%s!' % messages[0].role }}", "{{ 'a{}'.format(1) }}", "{% set a, b = 1, 2 %}{{ a }}",
+              "{% for m in messages recursive %}{{ m.role }}{% endfor %}", "{{ messages[::-1] | length }}"]:
         got = chat_render(t, MESSAGES[1])
         assert "unsupported" in got, (t, got)
     got = chat_render("{{ 'a' + 1 }}", MESSAGES[0])
