@@ -753,6 +753,11 @@ struct SetNode : Node {
     ns.set(attr, std::move(v));
   }
 };
+struct LoopControl { bool is_break; };          // thrown by `break` / `continue`, caught by the enclosing for
+struct LoopControlNode : Node {
+  bool is_break = false;
+  void render(Context&, std::string&) const override { throw LoopControl{is_break}; }
+};
 struct ForNode : Node {
   std::vector<std::string> vars;
   ExprP iterable, filter;
@@ -793,8 +798,14 @@ struct ForNode : Node {
       if (k > 0) loop.set("previtem", items[(size_t)k - 1]);
       if (k + 1 < n) loop.set("nextitem", items[(size_t)k + 1]);
       c.assign("loop", loop);
-      render_body(body, c, out);
+      bool stop = false;
+      try {
+        render_body(body, c, out);
+      } catch (const LoopControl& lc) {
+        stop = lc.is_break;
+      }
       c.scopes.pop_back();
+      if (stop) break;
     }
   }
 };
@@ -1234,7 +1245,9 @@ class Template {
         if (ep.eat_name("if")) node->filter = ep.or_();
         if (!ep.at_end()) throw Unsupported("unexpected `" + ep.peek().text + "` in a for");
         std::string end;
+        ++in_loop_;
         node->body = parse_body(segs, pos, {"else", "endfor"}, &end);
+        --in_loop_;
         if (pos >= segs.size()) throw Unsupported("for without endfor");
         ++pos;
         if (end == "else") {
@@ -1274,6 +1287,11 @@ class Template {
         auto node = std::make_unique<MacroNode>();
         node->def = std::move(def);
         body.push_back(std::move(node));
+      } else if (kw == "break" || kw == "continue") {
+        if (!in_loop_) throw Unsupported("`" + kw + "` outside a loop");
+        auto node = std::make_unique<LoopControlNode>();
+        node->is_break = kw == "break";
+        body.push_back(std::move(node));
       } else if (kw == "generation" || kw == "endgeneration") {
         // markers around the assistant's text (used for training masks): nothing to render
       } else {
@@ -1286,6 +1304,7 @@ class Template {
 
   Body body_;
   std::set<std::string> names_;
+  int in_loop_ = 0;
 };
 
 // ------------------------------------------------------------------------------------------------ chat requests

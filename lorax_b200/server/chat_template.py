@@ -35,7 +35,8 @@ def render_chat(messages: List[dict], template: Optional[str], tools=None, bos_t
     def raise_exception(msg):
         raise TemplateError(msg)
 
-    env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True)
+    # `break` / `continue` in loops: transformers renders chat templates with this extension on
+    env = ImmutableSandboxedEnvironment(trim_blocks=True, lstrip_blocks=True, extensions=["jinja2.ext.loopcontrols"])
     env.globals["raise_exception"] = raise_exception
     env.globals["strftime_now"] = lambda fmt: datetime.datetime.now().strftime(fmt)
     source = template or DEFAULT_TEMPLATE

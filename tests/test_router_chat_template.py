@@ -267,9 +267,11 @@ def test_guideline_and_whitespace_control():
     assert got.get("text") == want[1], (got, want)
     want, got = both(t, MESSAGES[0])
     assert want[0] == "error" and "error" in got and "guideline" in got["error"]
-    for t in ["a\n  {# c #}\nb {{ 1 }}\n  {{ 2 }}\n{% set x = 3 %}\n{{ x }}\n", "{{- 'a' -}}  \n  b  {{- 'c' }}\n{%- if true -%}\n d \n{%- endif -%}\n e",
+    for t in ["{% for m in messages %}{% if m.role == 'system' %}{% continue %}{% endif %}{{ m.role }};{% if loop.index == 3 %}{% break %}{% endif %}{% endfor %}|"
+              "{% for i in range(5) %}{% for j in range(5) %}{% if j > i %}{% break %}{% endif %}{{ j }}{% endfor %},{% endfor %}",
+              "a\n  {# c #}\nb {{ 1 }}\n  {{ 2 }}\n{% set x = 3 %}\n{{ x }}\n", "{{- 'a' -}}  \n  b  {{- 'c' }}\n{%- if true -%}\n d \n{%- endif -%}\n e",
               "  {% if true %}  \n  {% endif %}  tail\n", "\t{%+ if true %}\tkept{% endif +%}\nnext"]:
-        want, got = both(t, MESSAGES[0])
+        want, got = both(t, MESSAGES[1])
         assert got.get("text") == want[1], (t, got, want)
 
 
