@@ -997,6 +997,7 @@ int main(int argc, char** argv) {
     try {
       std::shared_ptr<const tok::Tokenizer> t;
       bool images_to_shard = false;
+      img::ImagePolicy image_policy;
       const std::string named = a.get("tokenizer-name", "");
       if (!named.empty()) {
         t = tok::Tokenizer::load(named);
@@ -1005,13 +1006,21 @@ int main(int argc, char** argv) {
         json::Value root;
         std::string perr;
         if (file.empty()) throw tok::Unsupported("the shard has no tokenizer file");
-        if (file.rfind("#images\n", 0) == 0) { images_to_shard = true; file.erase(0, 8); }
+        if (file.rfind("#images", 0) == 0) {               // "#images {policy json}\n" in front of the tokenizer file
+          const size_t nl = file.find('\n');
+          if (nl == std::string::npos) throw std::runtime_error("tokenizer file: bad header");
+          images_to_shard = true;
+          json::Value pol;
+          if (nl > 8 && json::parse(file.substr(8, nl - 8), pol, &perr)) image_policy = img::ImagePolicy::from_json(pol);
+          file.erase(0, nl + 1);
+        }
         if (!json::parse(file, root, &perr)) throw std::runtime_error("tokenizer file: " + perr);
         t = tok::Tokenizer::from_json(root);
       }
-      client->set_local_tokenizer(std::make_shared<tok::TokenizerPool>(t, g_validation_workers), images_to_shard);
+      client->set_local_tokenizer(std::make_shared<tok::TokenizerPool>(t, g_validation_workers), images_to_shard, image_policy);
       log_json("INFO", "tokenising in the router on " + std::to_string(g_validation_workers) + " worker(s)" +
-                           (images_to_shard ? "; prompts with images go to shard 0" : ""));
+                           (!images_to_shard ? "" : image_policy.kind != img::ImagePolicy::None ? "; inline images are counted here, image URLs go to shard 0"
+                                                                                                : "; prompts with images go to shard 0"));
     } catch (const std::exception& e) {
       log_json("INFO", std::string("shard 0 tokenises (router tokenizer not used: ") + e.what() + ")");
     }

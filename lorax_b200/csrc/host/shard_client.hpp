@@ -29,6 +29,7 @@
 #include <string>
 #include <vector>
 
+#include "image_chunks.hpp"
 #include "pb_gen.hpp"
 #include "tokenizer.hpp"
 
@@ -202,15 +203,33 @@ class ShardedClient {
   // Request text -> ids.  With a local tokenizer (the router read the shard's tokenizer file and implements every component
   // it uses) this runs on the router's tokenizer workers; otherwise shard 0 is asked.  Chat templating and `/tokenize` with
   // character offsets are always helper calls to shard 0.
-  void set_local_tokenizer(std::shared_ptr<tok::TokenizerPool> pool, bool images_to_shard = false) {
+  void set_local_tokenizer(std::shared_ptr<tok::TokenizerPool> pool, bool images_to_shard = false, img::ImagePolicy policy = img::ImagePolicy()) {
     local_tok_ = std::move(pool);
     images_to_shard_ = images_to_shard;
+    image_policy_ = std::move(policy);
   }
   bool tokenizes_locally() const { return local_tok_ != nullptr; }
   uint64_t local_tokenizations() const { return local_tok_ ? local_tok_->served() : 0; }
   std::vector<uint32_t> tokenize(const std::string& text, bool add_special = true) {
-    // a vision-language shard turns image markdown into feature tokens: only it knows how many
-    if (local_tok_ && !(images_to_shard_ && text.find("![") != std::string::npos)) return local_tok_->encode(text, add_special);
+    if (local_tok_ && !(images_to_shard_ && text.find("![](") != std::string::npos)) return local_tok_->encode(text, add_special);
+    if (local_tok_ && image_policy_.kind != img::ImagePolicy::None) {
+      // a vision-language prompt: text parts through the tokenizer (special tokens with the first part only), every image as its
+      // feature tokens; an image the router cannot size (a URL, an unknown format) sends the whole prompt to the shard
+      std::vector<uint32_t> ids;
+      bool first = true, handled = true;
+      for (auto& part : img::split_prompt(text)) {
+        if (!part.first) {
+          const std::vector<uint32_t> t = local_tok_->encode(part.second, add_special && first);
+          ids.insert(ids.end(), t.begin(), t.end());
+        } else {
+          const long n = image_policy_.count(part.second);
+          if (n < 0) { handled = false; break; }
+          ids.insert(ids.end(), (size_t)n, image_policy_.image_token);
+        }
+        first = false;
+      }
+      if (handled) return ids;
+    }
     std::string out = shards_.front()->call(gen::M_Tokenize, std::string(1, add_special ? '\1' : '\0') + text);
     std::vector<uint32_t> ids(out.size() / 4);
     std::memcpy(ids.data(), out.data(), ids.size() * 4);
@@ -237,6 +256,7 @@ class ShardedClient {
   std::vector<std::shared_ptr<ShardClient>> shards_;
   std::shared_ptr<tok::TokenizerPool> local_tok_;
   bool images_to_shard_ = false;
+  img::ImagePolicy image_policy_;
   struct TraceSlot {                      // movable holder: the client itself is passed around by value once
     std::mutex mu;
     std::string tp;

@@ -173,11 +173,17 @@ class ShardRuntime:
     def router_tokenizer_json(self) -> str:
         """The tokenizer file as a string, for the router to tokenise requests itself; empty when there is no tokenizer file.
         A first line `#images` tells the router that this runtime expands image markdown (`![](uri)`) into feature tokens: prompts
-        that contain `![` keep coming to the shard, everything else is tokenised in the router."""
+        whose images the router cannot size itself (URLs, unknown formats) keep coming to the shard; the JSON behind `#images` tells
+        the router how many tokens an image becomes."""
         if self.tokenizer is None:
             return ""
         plain = type(self).tokenize in (ShardRuntime.tokenize, EncoderRuntime.tokenize)
-        return ("" if plain else "#images\n") + self.tokenizer.to_str()
+        return ("" if plain else "#images " + json.dumps(self.image_token_policy()) + "\n") + self.tokenizer.to_str()
+
+    def image_token_policy(self) -> dict:
+        """How many tokens an image in a prompt becomes, for the router's own count (`csrc/host/image_chunks.hpp`); `{}`: only this
+        runtime can tell."""
+        return {}
 
     def tokenize_detailed(self, body: dict) -> list:
         text = body.get("inputs", "")
@@ -927,6 +933,9 @@ class MllamaRuntime(Seq2SeqRuntime):
         self.special_ids = set(self.eos_ids) | {model.config.pad_token_id, model.config.image_token_index}
         self._images = collections.OrderedDict()
 
+    def image_token_policy(self) -> dict:
+        return {"kind": "one_per_image", "image_token": int(self.model.config.image_token_index)}
+
     def _image(self, uri: str):
         hit = self._images.get(uri)
         if hit is not None:
@@ -999,6 +1008,12 @@ class VlmRuntime(ShardRuntime):
         super().__init__(vlm_model.text, tokenizer, cfg, model_id=model_id, **kw)
         self.vlm = vlm_model
         self._images: "collections.OrderedDict[str, tuple]" = collections.OrderedDict()      # uri -> (tiles, (h, w)), most recent last
+
+    def image_token_policy(self) -> dict:
+        c, v = self.vlm.config, self.vlm.config.vision
+        return {"kind": "llava_next", "image_token": int(c.image_token_index), "image_size": int(v.image_size), "patch_size": int(v.patch_size),
+                "extra_tokens": int(v.extra_tokens), "strategy": c.vision_feature_select_strategy,
+                "pinpoints": [[int(h), int(w)] for h, w in c.image_grid_pinpoints]}
 
     def _image(self, uri: str):
         hit = self._images.get(uri)

@@ -222,8 +222,24 @@ def test_image_prompt_through_router_matches_hf(vlm_stack):
     st, body, _ = _post(port, "/generate", {"inputs": "w1 ![](data:image/png;base64,AAAA) w2", "parameters": {"max_new_tokens": 2}})
     assert st >= 400
     assert not rt.seqs
-    # the router tokenised the text-only prompt itself; the prompts with image markdown went to the shard, which knows the feature counts
+    # the router tokenised these prompts itself: it reads the size of an inline image from its header and computes the feature tokens
+    # from the vision configuration the shard handed over; only the broken image was left to the shard
     import urllib.request
-    with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5) as r:
-        count = [l for l in r.read().decode().splitlines() if l.startswith("lorax_router_tokenizations ")]
-    assert count and int(count[0].split()[1]) == 1, count
+
+    def local_tokenizations():
+        with urllib.request.urlopen(f"http://127.0.0.1:{port}/metrics", timeout=5) as r:
+            count = [l for l in r.read().decode().splitlines() if l.startswith("lorax_router_tokenizations ")]
+        return int(count[0].split()[1])
+    before = local_tokenizations()
+    assert before >= 3
+    # sizes on both sides of the aspect-ratio rules, four encodings: the router's count must be the shard's
+    for k, (h, w, fmt) in enumerate([(40, 70, "PNG"), (70, 40, "JPEG"), (33, 33, "GIF"), (20, 97, "BMP"), (97, 21, "WEBP"), (64, 64, "PNG"), (31, 200, "JPEG")]):
+        im = Image.fromarray((torch.rand(h, w, 3) * 255).to(torch.uint8).numpy())
+        b = io.BytesIO()
+        im.save(b, format=fmt)
+        u = f"data:image/{fmt.lower()};base64," + base64.b64encode(b.getvalue()).decode()
+        p = f"w1 ![]({u}) w2 ![]() w3"
+        st, body, _ = _post(port, "/generate", {"inputs": p, "parameters": {"max_new_tokens": 1, "details": True}})
+        assert st == 200, (fmt, body)
+        assert json.loads(body)["details"]["prompt_tokens"] == len(rt.tokenize(p)), (h, w, fmt)
+    assert local_tokenizations() == before + 14          # the two text parts of each of the seven prompts ("![]()" is no image)
