@@ -347,6 +347,14 @@ const char* lx_infer_fake_run(const char* requests_json, int max_active_adapters
   return ret(out.dump());
 }
 
+// Feature tokens the router counts for one image reference under an image policy (JSON as shard 0 sends it); -1: left to the shard.
+long lx_image_token_count(const char* policy_json, const char* uri) {
+  json::Value pol;
+  std::string err;
+  if (!json::parse(policy_json, pol, &err)) return -2;
+  return img::ImagePolicy::from_json(pol).count(uri);
+}
+
 // A chat request rendered by the router's template interpreter.  `request_json`: {"template", "bos_token", "eos_token", "messages",
 // "tools"?, "tool_prompt"?, "guideline"?}.  JSON out: {"text": ...}, {"error": ...} (the template raised or misused a value) or
 // {"unsupported": ...} (outside the interpreter's subset: the router would ask a shard).

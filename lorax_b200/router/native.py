@@ -46,6 +46,7 @@ def load():
         "lx_regex_find_all": ([c_char_p, c_char_p], c_char_p),
         "lx_encoder_batcher_fake_run": ([c_int, c_int], c_char_p),
         "lx_chat_render": ([c_char_p], c_char_p),
+        "lx_image_token_count": ([c_char_p, c_char_p], ctypes.c_long),
     }
     for name, (args, res) in sig.items():
         f = getattr(lib, name)
@@ -172,3 +173,8 @@ def chat_render(template: str, messages, bos_token: str = "", eos_token: str = "
     """The router's chat template interpreter: {"text"}, {"error"} or {"unsupported"} (see capi.cpp)."""
     req = dict(template=template, messages=messages, bos_token=bos_token, eos_token=eos_token, **extra)
     return json.loads(load().lx_chat_render(json.dumps(req).encode()).decode())
+
+
+def image_token_count(policy: dict, uri: str) -> int:
+    """Feature tokens the router counts for an image reference; -1 when it leaves the image to the shard."""
+    return load().lx_image_token_count(json.dumps(policy).encode(), uri.encode())

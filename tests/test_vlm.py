@@ -243,3 +243,31 @@ def test_image_prompt_through_router_matches_hf(vlm_stack):
         assert st == 200, (fmt, body)
         assert json.loads(body)["details"]["prompt_tokens"] == len(rt.tokenize(p)), (h, w, fmt)
     assert local_tokenizations() == before + 14          # the two text parts of each of the seven prompts ("![]()" is no image)
+
+
+def test_router_image_token_count_matches_the_model_over_random_sizes():
+    """The router's feature-token count (image size from a PNG header, any-resolution formula) against the model's own over 2000 random
+    sizes; references it cannot size are left to the shard."""
+    import random
+    import struct
+    import zlib
+    from lorax_b200.models.vlm import select_best_resolution, unpadded_grid
+    from lorax_b200.router.native import image_token_count
+    pol = {"kind": "llava_next", "image_token": 9, "image_size": 336, "patch_size": 14, "extra_tokens": 1, "strategy": "default",
+           "pinpoints": [[336, 672], [672, 336], [672, 672], [1008, 336], [336, 1008]]}
+
+    def png_header(w, h):
+        ihdr = struct.pack(">IIBBBBB", w, h, 8, 2, 0, 0, 0)
+        return b"\x89PNG\r\n\x1a\n" + struct.pack(">I", 13) + b"IHDR" + ihdr + struct.pack(">I", zlib.crc32(b"IHDR" + ihdr))
+    rng = random.Random(0)
+    side = 336 // 14
+    for _ in range(2000):
+        h, w = rng.randint(1, 3000), rng.randint(1, 3000)
+        bh, bw = select_best_resolution((h, w), pol["pinpoints"])
+        _, rows, _, cols = unpadded_grid((h, w), (bh // 336 * side, bw // 336 * side))
+        want = side * side + rows * (cols + 1)
+        assert image_token_count(pol, "data:image/png;base64," + base64.b64encode(png_header(w, h)).decode()) == want, (h, w)
+    assert image_token_count({"kind": "one_per_image", "image_token": 3}, "data:image/png;base64," + base64.b64encode(png_header(5, 5)).decode()) == 1
+    for uri in ("https://example.com/a.png", "data:image/png;base64,AAAA", "data:text/plain,hello", "data:image/tiff;base64," + base64.b64encode(b"II*\0" * 8).decode()):
+        assert image_token_count(pol, uri) == -1
+    assert image_token_count({}, "data:image/png;base64," + base64.b64encode(png_header(5, 5)).decode()) == -1
