@@ -669,3 +669,38 @@ def test_chat_template_tools_guideline_and_echo(stack):
     status, data, _ = _post(stack["port"], "/v1/chat/completions", {"model": "tiny", "max_tokens": 3, "guideline": "g", "tool_prompt": "p",
                                                                      "messages": [{"role": "user", "content": "w5 w6"}]})
     assert status == 200 and json.loads(data)["choices"][0]["message"]["role"] == "assistant"
+
+
+def test_router_leaves_tokenisation_and_templates_to_the_shard_when_told_to(stack):
+    """`--router-tokenizer off --router-chat-template off`: a second router on the same shard serves the same answers with shard 0
+    doing both (the path a tokenizer file or a template outside the router's subset takes by itself)."""
+    port2 = _free_port()
+    proc = subprocess.Popen([ROUTER, "--port", str(port2), "--hostname", "127.0.0.1", "--master-shard-uds-path", stack["uds"], "--num-shard", "1",
+                             "--max-input-length", "64", "--max-total-tokens", "128", "--max-batch-prefill-tokens", "256", "--model-id", "tiny",
+                             "--adapter-source", "local", "--router-tokenizer", "off", "--router-chat-template", "off"],
+                            stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    try:
+        for _ in range(100):
+            try:
+                with urllib.request.urlopen(f"http://127.0.0.1:{port2}/health", timeout=1) as r:
+                    if r.status == 200:
+                        break
+            except Exception:
+                time.sleep(0.1)
+        else:
+            raise RuntimeError("second router did not come up")
+        body = {"model": "tiny", "messages": [{"role": "user", "content": "w4 w5"}], "max_tokens": 4}
+        st1, b1, _ = _post(stack["port"], "/v1/chat/completions", body)
+        st2, b2, _ = _post(port2, "/v1/chat/completions", body)
+        assert st1 == 200 and st2 == 200
+        j1, j2 = json.loads(b1), json.loads(b2)
+        assert j1["choices"][0]["message"]["content"] == j2["choices"][0]["message"]["content"] and j1["usage"] == j2["usage"]
+        with urllib.request.urlopen(f"http://127.0.0.1:{port2}/metrics", timeout=5) as r:
+            m = r.read().decode()
+        assert "lorax_router_tokenizations" not in m and "lorax_router_chat_templates 0" in m
+    finally:
+        proc.terminate()
+        try:
+            proc.wait(timeout=10)
+        except subprocess.TimeoutExpired:
+            proc.kill()
