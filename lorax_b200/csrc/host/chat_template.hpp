@@ -656,6 +656,11 @@ struct Call : Expr {
       if (m == "items") { List l; for (auto& kv : *o.dict) l.push_back(Val::make_list({Val::str(kv.first), kv.second})); return Val::make_list(std::move(l)); }
       if (m == "keys") { List l; for (auto& kv : *o.dict) l.push_back(Val::str(kv.first)); return Val::make_list(std::move(l)); }
       if (m == "values") { List l; for (auto& kv : *o.dict) l.push_back(kv.second); return Val::make_list(std::move(l)); }
+      if (m == "cycle" && o.find("index0") && o.find("revindex0") && pos(0)) {       // loop.cycle('a', 'b', ...)
+        size_t n = 0;
+        while (pos(n)) ++n;
+        return *pos((size_t)o.find("index0")->i % n);
+      }
       if (m == "get" && pos(0)) { const Val* v = o.find(to_text(*pos(0))); return v ? *v : (pos(1) ? *pos(1) : Val::none()); }
       throw Unsupported("mapping method " + m);
     }
@@ -744,9 +749,12 @@ struct IfNode : Node {
 };
 struct SetNode : Node {
   std::string name, attr;       // attr: `set ns.attr = ...`
-  ExprP value;
+  ExprP value;                  // null: `{% set x %}...{% endset %}`, the rendered body is the value
+  Body block;
   void render(Context& c, std::string&) const override {
-    Val v = value->eval(c);
+    Val v;
+    if (value) v = value->eval(c);
+    else { std::string text; render_body(block, c, text); v = Val::str(text); }
     if (attr.empty()) { c.assign(name, std::move(v)); return; }
     Val ns = c.lookup(name);
     if (ns.kind != Val::DictK || !ns.is_namespace) throw TemplateError("cannot assign attribute on non-namespace object");
@@ -1262,9 +1270,16 @@ class Template {
         node->name = ep.expect_name();
         if (ep.eat_op(".")) node->attr = ep.expect_name();
         if (ep.is_op(",")) throw Unsupported("set of several names");
-        if (!ep.eat_op("=")) throw Unsupported("block set");
-        node->value = ep.expression();
-        if (!ep.at_end()) throw Unsupported("unexpected `" + ep.peek().text + "` in a set");
+        if (ep.eat_op("=")) {
+          node->value = ep.expression();
+          if (!ep.at_end()) throw Unsupported("unexpected `" + ep.peek().text + "` in a set");
+        } else {
+          if (!ep.at_end()) throw Unsupported("block set with a filter");
+          std::string end;
+          node->block = parse_body(segs, pos, {"endset"}, &end);
+          if (pos >= segs.size()) throw Unsupported("set without endset");
+          ++pos;
+        }
         body.push_back(std::move(node));
       } else if (kw == "macro") {
         ExprParser ep(rest, &names_);

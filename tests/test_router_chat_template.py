@@ -267,7 +267,8 @@ def test_guideline_and_whitespace_control():
     assert got.get("text") == want[1], (got, want)
     want, got = both(t, MESSAGES[0])
     assert want[0] == "error" and "error" in got and "guideline" in got["error"]
-    for t in ["{% for m in messages %}{% if m.role == 'system' %}{% continue %}{% endif %}{{ m.role }};{% if loop.index == 3 %}{% break %}{% endif %}{% endfor %}|"
+    for t in ["{% set block %}\n  <{{ messages | length }}>\n{% endset %}{{ block | trim }}{% for m in messages %}{{ loop.cycle('a', 'b', 'c') }}{% endfor %}",
+              "{% for m in messages %}{% if m.role == 'system' %}{% continue %}{% endif %}{{ m.role }};{% if loop.index == 3 %}{% break %}{% endif %}{% endfor %}|"
               "{% for i in range(5) %}{% for j in range(5) %}{% if j > i %}{% break %}{% endif %}{{ j }}{% endfor %},{% endfor %}",
               "a\n  {# c #}\nb {{ 1 }}\n  {{ 2 }}\n{% set x = 3 %}\n{{ x }}\n", "{{- 'a' -}}  \n  b  {{- 'c' }}\n{%- if true -%}\n d \n{%- endif -%}\n e",
               "  {% if true %}  \n  {% endif %}  tail\n", "\t{%+ if true %}\tkept{% endif +%}\nnext"]:
@@ -277,7 +278,7 @@ def test_guideline_and_whitespace_control():
 
 def test_what_the_interpreter_does_not_implement_is_reported_as_such():
     for t in ["{{ messages | groupby('role') | list }}", "{% filter upper %}a{% endfilter %}",
-              "{% for m in messages %}{{ loop.cycle('a', 'b') }}{% endfor %}", "{% call f() %}x{% endcall %}", "{{ '%s!' % messages[0].role }}", "{{ 'a{}'.format(1) }}", "{% set a, b = 1, 2 %}{{ a }}",
+"{% call f() %}x{% endcall %}", "{{ '%s!' % messages[0].role }}", "{{ 'a{}'.format(1) }}", "{% set a, b = 1, 2 %}{{ a }}",
               "{% for m in messages recursive %}{{ m.role }}{% endfor %}", "{{ messages[::-1] | length }}"]:
         got = chat_render(t, MESSAGES[1])
         assert "unsupported" in got, (t, got)
