@@ -14,6 +14,7 @@
 #include <cstring>
 #include <functional>
 #include <map>
+#include <cstdio>
 #include <string>
 #include <thread>
 #include <vector>
@@ -234,7 +235,15 @@ class Server {
           try {
             it->second(req, w);
           } catch (const std::exception& ex) {
-            if (!w.started()) w.send(500, std::string("{\"error\":\"") + ex.what() + "\",\"error_type\":\"internal\"}");
+            if (!w.started()) {
+              std::string msg;                     // the message as a JSON string
+              for (unsigned char ch : std::string(ex.what())) {
+                if (ch == '"' || ch == '\\') { msg.push_back('\\'); msg.push_back((char)ch); }
+                else if (ch < 0x20) { char buf[8]; std::snprintf(buf, sizeof buf, "\\u%04x", ch); msg += buf; }
+                else msg.push_back((char)ch);
+              }
+              w.send(500, "{\"error\":\"" + msg + "\",\"error_type\":\"internal\"}");
+            }
           }
           if (w.streaming()) w.end_stream();
         }

@@ -188,7 +188,17 @@ class Infer {
 
     // tokens
     v.inputs = inputs;
-    v.input_ids = p.input_ids.empty() ? client_->tokenize(inputs) : p.input_ids;
+    if (p.input_ids.empty()) {
+      try {
+        v.input_ids = client_->tokenize(inputs);
+      } catch (const ApiError&) {
+        throw;
+      } catch (const std::exception& e) {       // a word outside a vocabulary without an unknown token, an image that cannot be read ...
+        throw validation_error(std::string("tokenizer error ") + e.what());
+      }
+    } else {
+      v.input_ids = p.input_ids;
+    }
     if (p.truncate && v.input_ids.size() > *p.truncate) v.input_ids.erase(v.input_ids.begin(), v.input_ids.end() - *p.truncate);
     v.trace_id = p.trace_id;
     v.span_id = p.span_id;

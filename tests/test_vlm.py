@@ -220,7 +220,7 @@ def test_image_prompt_through_router_matches_hf(vlm_stack):
     st, body, _ = _post(port, "/generate", {"inputs": f"![]({uri}) w3 ![]({uri})", "parameters": {"max_new_tokens": 2}})
     assert st == 200, body
     st, body, _ = _post(port, "/generate", {"inputs": "w1 ![](data:image/png;base64,AAAA) w2", "parameters": {"max_new_tokens": 2}})
-    assert st >= 400
+    assert st == 422 and json.loads(body)["error_type"] == "validation" and "tokenizer error" in json.loads(body)["error"], body
     assert not rt.seqs
     # the router tokenised these prompts itself: it reads the size of an inline image from its header and computes the feature tokens
     # from the vision configuration the shard handed over; only the broken image was left to the shard
