@@ -355,6 +355,18 @@ long lx_image_token_count(const char* policy_json, const char* uri) {
   return img::ImagePolicy::from_json(pol).count(uri);
 }
 
+// The prompt cut at its image references: JSON [[is_image, text-or-uri], ...].
+const char* lx_split_image_prompt(const char* text) {
+  json::Value out = json::Value::array();
+  for (auto& part : img::split_prompt(text)) {
+    json::Value p = json::Value::array();
+    p.push(part.first);
+    p.push(part.second);
+    out.push(p);
+  }
+  return ret(out.dump());
+}
+
 // A chat request rendered by the router's template interpreter.  `request_json`: {"template", "bos_token", "eos_token", "messages",
 // "tools"?, "tool_prompt"?, "guideline"?}.  JSON out: {"text": ...}, {"error": ...} (the template raised or misused a value) or
 // {"unsupported": ...} (outside the interpreter's subset: the router would ask a shard).

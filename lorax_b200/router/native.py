@@ -47,6 +47,7 @@ def load():
         "lx_encoder_batcher_fake_run": ([c_int, c_int], c_char_p),
         "lx_chat_render": ([c_char_p], c_char_p),
         "lx_image_token_count": ([c_char_p, c_char_p], ctypes.c_long),
+        "lx_split_image_prompt": ([c_char_p], c_char_p),
     }
     for name, (args, res) in sig.items():
         f = getattr(lib, name)
@@ -178,3 +179,8 @@ def chat_render(template: str, messages, bos_token: str = "", eos_token: str = "
 def image_token_count(policy: dict, uri: str) -> int:
     """Feature tokens the router counts for an image reference; -1 when it leaves the image to the shard."""
     return load().lx_image_token_count(json.dumps(policy).encode(), uri.encode())
+
+
+def split_image_prompt(text: str):
+    """The router's cut of a prompt at its `![](uri)` references: [("text" | "image", value), ...]."""
+    return [("image" if is_img else "text", v) for is_img, v in json.loads(load().lx_split_image_prompt(text.encode()).decode())]

@@ -271,3 +271,14 @@ def test_router_image_token_count_matches_the_model_over_random_sizes():
     for uri in ("https://example.com/a.png", "data:image/png;base64,AAAA", "data:text/plain,hello", "data:image/tiff;base64," + base64.b64encode(b"II*\0" * 8).decode()):
         assert image_token_count(pol, uri) == -1
     assert image_token_count({}, "data:image/png;base64," + base64.b64encode(png_header(5, 5)).decode()) == -1
+
+
+def test_router_cuts_prompts_at_image_references_like_the_shard():
+    import random
+    from lorax_b200.models.vlm import split_prompt
+    from lorax_b200.router.native import split_image_prompt
+    rng = random.Random(4)
+    pieces = ["![](", ")", "![]", "(", "a", " b ", "data:x", "![]()", "!", "[", "]", "é", "\n"]
+    for _ in range(3000):
+        text = "".join(rng.choice(pieces) for _ in range(rng.randint(0, 12)))
+        assert split_image_prompt(text) == split_prompt(text), repr(text)
