@@ -130,7 +130,7 @@ class FakeShard : public ShardClient {
             wd += payload[i];
           }
         }
-        return std::string((const char*)ids.data(), ids.size() * 4);
+        return ids.empty() ? std::string() : std::string((const char*)ids.data(), ids.size() * 4);
       }
       case gen::M_Embed: {
         // embedding of request i: [number of input ids, first id, batch size]; a request whose text is "boom" fails the batch
@@ -218,8 +218,8 @@ void* lx_alloc_allocate(void* a, uint32_t adapter, uint32_t tokens, const uint32
 uint32_t lx_allocation_num_blocks(void* h) { return (uint32_t) static_cast<BlockAllocation*>(h)->blocks.size(); }
 uint32_t lx_allocation_prefix_len(void* h) { return static_cast<BlockAllocation*>(h)->prefix_len; }
 uint32_t lx_allocation_num_slots(void* h) { return (uint32_t) static_cast<BlockAllocation*>(h)->slots.size(); }
-void lx_allocation_blocks(void* h, uint32_t* out) { auto& b = static_cast<BlockAllocation*>(h)->blocks; std::memcpy(out, b.data(), b.size() * 4); }
-void lx_allocation_slots(void* h, uint32_t* out) { auto& b = static_cast<BlockAllocation*>(h)->slots; std::memcpy(out, b.data(), b.size() * 4); }
+void lx_allocation_blocks(void* h, uint32_t* out) { auto& b = static_cast<BlockAllocation*>(h)->blocks; if (!b.empty()) std::memcpy(out, b.data(), b.size() * 4); }
+void lx_allocation_slots(void* h, uint32_t* out) { auto& b = static_cast<BlockAllocation*>(h)->slots; if (!b.empty()) std::memcpy(out, b.data(), b.size() * 4); }
 void lx_alloc_free(void* a, void* h, uint32_t adapter, const uint32_t* all_tokens, uint32_t n) {
   std::vector<uint32_t> t;
   if (all_tokens) t.assign(all_tokens, all_tokens + n);
@@ -456,7 +456,7 @@ long lx_tokenizer_encode(void* hv, const char* text, size_t len, int add_special
   auto* h = static_cast<TokHandle*>(hv);
   try {
     const std::vector<uint32_t> ids = h->pool->encode(std::string(text, len), add_special != 0);
-    std::memcpy(out, ids.data(), std::min(cap, ids.size()) * sizeof(uint32_t));
+    if (!ids.empty() && cap > 0) std::memcpy(out, ids.data(), std::min(cap, ids.size()) * sizeof(uint32_t));
     return (long)ids.size();
   } catch (const std::exception& e) {
     h->last_error = e.what();

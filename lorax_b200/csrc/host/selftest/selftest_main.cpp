@@ -6,6 +6,7 @@
 // findings make the process exit non-zero on their own.
 #include <cstdint>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <memory>
 #include <string>
@@ -146,6 +147,38 @@ int main() {
     for (int b : bads) bad += b;
     lx_tokenizer_free(h);
     if (bad) return fail("tokenizer pool", std::to_string(bad));
+  }
+  if (const char* files = std::getenv("LX_SELFTEST_TOKENIZERS")) {
+    // tokenizer files and a text file from the caller (the Python tests write real pipelines: byte-level BPE, SentencePiece-style
+    // BPE, Unigram behind a compiled character map, WordPiece): every line through every tokenizer, for the sanitizers' eyes
+    const char* text_path = std::getenv("LX_SELFTEST_TEXT");
+    std::vector<std::string> lines;
+    if (text_path) {
+      if (FILE* f = std::fopen(text_path, "rb")) {
+        std::string cur;
+        for (int ch; (ch = std::fgetc(f)) != EOF;) { if (ch == '\x1e') { lines.push_back(cur); cur.clear(); } else cur.push_back((char)ch); }
+        lines.push_back(cur);
+        std::fclose(f);
+      }
+    }
+    std::string list = files;
+    size_t at = 0, total = 0;
+    while (at <= list.size()) {
+      const size_t colon = list.find(':', at);
+      const std::string path = list.substr(at, colon == std::string::npos ? std::string::npos : colon - at);
+      at = colon == std::string::npos ? list.size() + 1 : colon + 1;
+      if (path.empty()) continue;
+      char err[256] = {0};
+      void* h = lx_tokenizer_load(path.c_str(), 2, err, sizeof err);
+      if (!h) return fail("tokenizer load", path + ": " + err);
+      std::vector<uint32_t> ids(1 << 16);
+      for (auto& line : lines) {
+        const long n = lx_tokenizer_encode(h, line.data(), line.size(), 1, ids.data(), ids.size());
+        if (n > 0) total += (size_t)n;
+      }
+      lx_tokenizer_free(h);
+    }
+    std::printf("tokenizer files: %zu ids\n", total);
   }
   {
     // embed / classify batcher: eight caller threads, shared batches, a failing batch now and then

@@ -232,7 +232,7 @@ class ShardedClient {
     }
     std::string out = shards_.front()->call(gen::M_Tokenize, std::string(1, add_special ? '\1' : '\0') + text);
     std::vector<uint32_t> ids(out.size() / 4);
-    std::memcpy(ids.data(), out.data(), ids.size() * 4);
+    if (!ids.empty()) std::memcpy(ids.data(), out.data(), ids.size() * 4);
     return ids;
   }
   std::string helper(uint32_t method, const std::string& payload) { return shards_.front()->call(method, payload); }

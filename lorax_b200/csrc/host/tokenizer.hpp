@@ -212,7 +212,7 @@ struct PrecompiledNorm : Normalizer {
     std::memcpy(&trie_bytes, blob.data(), 4);
     if (trie_bytes % 4 != 0 || 4 + (size_t)trie_bytes > blob.size()) throw std::runtime_error("Precompiled character map: bad trie size");
     trie.resize(trie_bytes / 4);
-    std::memcpy(trie.data(), blob.data() + 4, trie_bytes);
+    if (trie_bytes) std::memcpy(trie.data(), blob.data() + 4, trie_bytes);
     pool.assign(blob.data() + 4 + trie_bytes, blob.size() - 4 - trie_bytes);
   }
   static size_t offset_of(uint32_t u) { return (size_t)(u >> 10) << ((u & (1u << 9)) >> 6); }

@@ -161,8 +161,31 @@ def test_host_code_under_sanitizers(sanitizer):
     except build.SanitizerUnavailable as e:
         pytest.skip(str(e))
     env = dict(os.environ, ASAN_OPTIONS="detect_leaks=1:abort_on_error=0", TSAN_OPTIONS="halt_on_error=1", UBSAN_OPTIONS="print_stacktrace=1")
+    # real tokenizer pipelines and awkward text for the router's tokenizer under the sanitizer (the files of the tokenizer tests)
+    try:
+        import tempfile
+        import test_router_tokenizer as T
+        from tokenizers import pre_tokenizers
+        d = tempfile.mkdtemp()
+        toks = {"bl": T.byte_level_bpe(pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)), "sp": T.sentencepiece_bpe(True),
+                "sp2": T.sentencepiece_bpe(False)}
+        try:
+            toks["uni"] = T.precompiled_unigram()
+        except BaseException:                      # no sentencepiece here
+            pass
+        paths = []
+        for name, tok in toks.items():
+            tok.save(os.path.join(d, name + ".json"))
+            paths.append(os.path.join(d, name + ".json"))
+        with open(os.path.join(d, "text"), "w", encoding="utf-8") as f:
+            f.write("\x1e".join(T.SAMPLES + T.HARD_UNICODE))
+        env.update(LX_SELFTEST_TOKENIZERS=":".join(paths), LX_SELFTEST_TEXT=os.path.join(d, "text"))
+    except ImportError:
+        pass
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+    if "LX_SELFTEST_TOKENIZERS" in env:
+        assert "tokenizer files:" in r.stdout and " 0 ids" not in r.stdout
 
 
 def test_encoder_batcher_shares_batches_and_contains_failures():

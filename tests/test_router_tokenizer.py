@@ -259,9 +259,8 @@ def test_zero_width_and_look_behind_split_patterns(tmp_path, behavior):
     check(tmp_path, tok, SAMPLES[:40] + extra)
 
 
-def test_sentencepiece_precompiled_character_map(tmp_path):
-    """A T5 / XLM-R style tokenizer: SentencePiece's compiled nmt_nfkc character map (taken from a model trained here), applied
-    grapheme cluster by grapheme cluster, in front of a Unigram model."""
+def precompiled_unigram():
+    """A T5 / XLM-R style tokenizer: Unigram behind SentencePiece's compiled nmt_nfkc character map, taken from a model trained here."""
     spm = pytest.importorskip("sentencepiece")
     from sentencepiece import sentencepiece_model_pb2 as pb
     import io
@@ -286,10 +285,18 @@ def test_sentencepiece_precompiled_character_map(tmp_path):
     tok.normalizer = normalizers.Sequence([normalizers.Precompiled(charsmap), normalizers.Replace(Regex(" {2,}"), " ")])
     tok.pre_tokenizer = pre_tokenizers.Metaspace(replacement="▁", prepend_scheme="always")
     tok.post_processor = processors.TemplateProcessing(single="$A </s>", special_tokens=[("</s>", 2)])
-    hard = ["ﬁn ① ½ Ⅷ ｆｕｌｌ　ｗｉｄｔｈ ㎏ ℃ Å", "é ạ̈ ố ́alone", "اَّلسَّلَامُ عَلَيْكُمْ ؀123", "한국어 각 한́",
-            "a\r\nb\rc\nd\t\te", "👩‍👩‍👧 ❤‍🔥 🇩🇪🇫🇷 👍🏽", "क्षत्रिय हिन्दी กำลัง น้ำ", "soft­hyphen zero​width ‍j ﻿bom", "ǅ ﬃ ẛ̣ ™ ² ³ ¼ № ㍿",
-            "x́́́́ ำ ःa", "", " ", "   multiple   spaces   "]
-    check(tmp_path, tok, SAMPLES + hard)
+    return tok
+
+
+HARD_UNICODE = ["ﬁn ① ½ Ⅷ ｆｕｌｌ　ｗｉｄｔｈ ㎏ ℃ Å", "é ạ̈ ố ́alone", "اَّلسَّلَامُ عَلَيْكُمْ ؀123", "한국어 각 한́",
+                "a\r\nb\rc\nd\t\te", "👩‍👩‍👧 ❤‍🔥 🇩🇪🇫🇷 👍🏽", "क्षत्रिय हिन्दी กำลัง น้ำ", "soft­hyphen zero​width ‍j ﻿bom", "ǅ ﬃ ẛ̣ ™ ² ³ ¼ № ㍿",
+                "x́́́́ ำ ःa", "", " ", "   multiple   spaces   "]
+
+
+def test_sentencepiece_precompiled_character_map(tmp_path):
+    """SentencePiece's compiled character map applied grapheme cluster by grapheme cluster, in front of a Unigram model."""
+    tok = precompiled_unigram()
+    check(tmp_path, tok, SAMPLES + HARD_UNICODE)
 
 
 def test_byte_level_normaliser_and_fixed_length_chunks(tmp_path):
