@@ -180,6 +180,23 @@ int main() {
     }
     std::printf("tokenizer files: %zu ids\n", total);
   }
+  if (const char* chat_path = std::getenv("LX_SELFTEST_CHAT")) {
+    // chat requests from the caller (the templates of the chat template tests with their conversations), one JSON document per record
+    size_t rendered = 0, records = 0;
+    if (FILE* f = std::fopen(chat_path, "rb")) {
+      std::string cur;
+      auto run = [&]() {
+        if (cur.empty()) return;
+        ++records;
+        if (std::string(lx_chat_render(cur.c_str())).find("\"text\"") != std::string::npos) ++rendered;
+        cur.clear();
+      };
+      for (int ch; (ch = std::fgetc(f)) != EOF;) { if (ch == '\x1e') run(); else cur.push_back((char)ch); }
+      run();
+      std::fclose(f);
+    }
+    std::printf("chat requests: %zu of %zu rendered\n", rendered, records);
+  }
   {
     // embed / classify batcher: eight caller threads, shared batches, a failing batch now and then
     const std::string out = lx_encoder_batcher_fake_run(8, 30);

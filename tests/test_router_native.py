@@ -182,10 +182,24 @@ def test_host_code_under_sanitizers(sanitizer):
         env.update(LX_SELFTEST_TOKENIZERS=":".join(paths), LX_SELFTEST_TEXT=os.path.join(d, "text"))
     except ImportError:
         pass
+    try:
+        import json
+        import tempfile
+        import test_router_chat_template as C
+        reqs = [json.dumps(dict(template=t, messages=m, bos_token="<s>", eos_token="</s>", **({"tools": C.TOOLS} if k % 2 else {})))
+                for t in C.TEMPLATES.values() for k, m in enumerate(C.MESSAGES)]
+        chat_file = os.path.join(tempfile.mkdtemp(), "chat")
+        with open(chat_file, "w", encoding="utf-8") as f:
+            f.write("\x1e".join(reqs))
+        env["LX_SELFTEST_CHAT"] = chat_file
+    except ImportError:
+        pass
     r = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
     if "LX_SELFTEST_TOKENIZERS" in env:
         assert "tokenizer files:" in r.stdout and " 0 ids" not in r.stdout
+    if "LX_SELFTEST_CHAT" in env:
+        assert "chat requests:" in r.stdout and "chat requests: 0 of" not in r.stdout
 
 
 def test_encoder_batcher_shares_batches_and_contains_failures():
