@@ -21,6 +21,8 @@
 
 namespace lx {
 
+struct EncoderInputError : std::runtime_error { using std::runtime_error::runtime_error; };     // the input could not be tokenised
+
 class EncoderBatcher {
  public:
   enum class Kind { Embed, Classify };
@@ -49,7 +51,11 @@ class EncoderBatcher {
     Item it;
     it.kind = kind;
     it.text = text;
-    it.ids = client_->tokenize(text);
+    try {
+      it.ids = client_->tokenize(text);
+    } catch (const std::exception& e) {
+      throw EncoderInputError(std::string("tokenizer error ") + e.what());
+    }
     if (it.ids.size() > lim_.max_input_length) it.ids.resize(lim_.max_input_length);
     it.enqueued = Clock::now();
     auto fut = it.done.get_future();

@@ -766,6 +766,8 @@ class App {
       w.send(200, out.dump());
     } catch (const ApiError& e) {
       send_error(w, e);
+    } catch (const EncoderInputError& e) {
+      send_error(w, ApiError(e.what(), "validation", 422));
     } catch (const std::overflow_error& e) {
       metrics_.inc("lorax_request_failure", {{"err", "overloaded"}});
       send_error(w, ApiError(e.what(), "overloaded", 429));
@@ -816,6 +818,8 @@ class App {
       w.send(200, batch ? all.dump() : (all.size() ? all.items()[0].dump() : "[]"));
     } catch (const ApiError& e) {
       send_error(w, e);
+    } catch (const EncoderInputError& e) {
+      send_error(w, ApiError(e.what(), "validation", 422));
     } catch (const std::overflow_error& e) {
       metrics_.inc("lorax_request_failure", {{"err", "overloaded"}});
       send_error(w, ApiError(e.what(), "overloaded", 429));
